@@ -1,0 +1,352 @@
+#include "enqueue.h"
+
+#include <string.h>
+
+#include <algorithm>
+
+#include "../trace/tracer.h"
+#include "b200coll/api_trace.h"
+#include "launch.h"
+
+namespace b200 {
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) {
+      cudaSetDevice(dev);
+      switched = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched && prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+struct ResolvedOp {
+  int base;          // ncclSum/Prod/Max/Min
+  int scaleMode;
+  unsigned long long bits;
+};
+
+ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, cudaStream_t stream, ResolvedOp* out) {
+  out->bits = 0;
+  out->scaleMode = SCALE_NONE;
+  if (op >= 0 && op < ncclNumOps) {
+    if (op == ncclAvg) {
+      out->base = ncclSum;
+      out->scaleMode = SCALE_POST_DIV_N;
+    } else {
+      out->base = op;
+    }
+    return ncclSuccess;
+  }
+  int idx = op - (int)ncclNumOps;
+  PreMulOp pm;
+  {
+    std::lock_guard<std::mutex> lk(c->mu);
+    if (idx < 0 || idx >= (int)c->premul.size() || !c->premul[idx].used) BFAIL(ncclInvalidArgument, "reduction operator %d does not exist on this communicator", op);
+    pm = c->premul[idx];
+  }
+  if (pm.dtype != dt) BFAIL(ncclInvalidArgument, "PreMulSum operator was created for %s, used with %s", dtypeName(pm.dtype), dtypeName(dt));
+  out->base = ncclSum;
+  out->scaleMode = SCALE_PRE_MUL;
+  if (pm.devPtr) {
+    unsigned long long bits = 0;
+    BCUDA(cudaMemcpyAsync(&bits, pm.devPtr, dtypeSize(dt), cudaMemcpyDeviceToHost, stream));
+    BCUDA(cudaStreamSynchronize(stream));
+    out->bits = bits;
+  } else {
+    out->bits = pm.bits;
+  }
+  return ncclSuccess;
+}
+
+int ctasFor(const Comm* c, size_t bytes, int algo) {
+  // One CTA per 256 KiB of payload, between the communicator's bounds. The in-switch path needs
+  // fewer CTAs for the same bandwidth, which leaves SMs to whatever overlaps with it.
+  size_t per = algo == ALGO_NVLS ? (512u << 10) : (256u << 10);
+  size_t want = (bytes + per - 1) / per;
+  int hi = c->maxCtas;
+  int ctas = (int)std::min<size_t>(want, (size_t)hi);
+  return std::max(ctas, c->minCtas);
+}
+
+bool findTuning(const Comm* c, int kind, size_t bytes, int* algo, int* ctas) {
+  for (const TuneEntry& t : c->tuning) {
+    if (t.coll >= 0 && t.coll != kind) continue;
+    if (bytes > t.maxBytes) continue;
+    *algo = t.algo;
+    *ctas = t.ctas;
+    return true;
+  }
+  return false;
+}
+
+size_t traceBytes(const CollReq& r) {
+  size_t b = r.count * dtypeSize(r.dt);
+  if (r.kind == COLL_ALLGATHER || r.kind == COLL_REDUCESCATTER) b *= r.comm->nranks;
+  return b;
+}
+
+}  // namespace
+
+static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* plan, CollArgs* args) {
+  Comm* c = r.comm;
+  const int n = c->nranks;
+  const size_t es = dtypeSize(r.dt);
+  const size_t bytes = r.count * es;  // per-rank slice for RS/AG
+  const Flags& fl = Flags::get();
+  const bool reducing = r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE;
+
+  int algo = r.forceAlgo, ctas = r.forceCtas;
+  if (algo == ALGO_AUTO) {
+    int ta = ALGO_AUTO, tc = 0;
+    if (findTuning(c, r.kind, bytes, &ta, &tc)) {
+      algo = ta;
+      if (!ctas) ctas = tc;
+    }
+  }
+  if (algo == ALGO_AUTO && !fl.algo.empty()) {
+    if (fl.algo == "ll") algo = ALGO_LL;
+    else if (fl.algo == "p2p" || fl.algo == "simple" || fl.algo == "ring" || fl.algo == "tree") algo = ALGO_P2P;
+    else if (fl.algo == "nvls") algo = ALGO_NVLS;
+  }
+  const bool nvlsOk = c->nvls && n > 1 && (!reducing || (nvlsReducible(r.dt, rop.base) && rop.scaleMode != SCALE_PRE_MUL)) &&
+                      (r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE || r.kind == COLL_BROADCAST);
+  const bool llOk = r.kind == COLL_ALLREDUCE && bytes <= fl.llMaxBytes && n > 1;
+  if (algo == ALGO_LL && !llOk) algo = ALGO_AUTO;
+  if (algo == ALGO_NVLS && !nvlsOk) algo = ALGO_AUTO;
+  if (algo == ALGO_AUTO) {
+    if (llOk) algo = ALGO_LL;
+    else if (nvlsOk && bytes * (r.kind == COLL_REDUCESCATTER ? n : 1) >= (32u << 10)) algo = ALGO_NVLS;
+    else algo = ALGO_P2P;
+  }
+
+  memset(args, 0, sizeof(*args));
+  args->send = r.send;
+  args->recv = r.recv;
+  args->count = r.count;
+  args->kind = r.kind;
+  args->root = r.root;
+  args->scaleMode = rop.scaleMode;
+  args->scalarBits = rop.bits;
+
+  // Zero-copy windows: buffers inside symmetric allocations (b200collSymAlloc, or ncclMemAlloc +
+  // ncclCommRegister) are read and written in place on every rank.
+  bool direct = false;
+  // Reduce with peer loads would need the root's recv window on ranks that may pass no recv.
+  const bool directKind = !(r.kind == COLL_REDUCE && algo != ALGO_NVLS);
+  if (algo != ALGO_LL && n > 1 && (bytes % 16) == 0 && directKind) {
+    const size_t sendBytes = r.kind == COLL_REDUCESCATTER ? bytes * n : bytes;
+    const size_t recvBytes = r.kind == COLL_ALLGATHER ? bytes * n : bytes;
+    const bool needSend = r.kind != COLL_BROADCAST;
+    const bool needRecv = r.kind == COLL_ALLREDUCE || r.kind == COLL_BROADCAST;
+    size_t so = 0, ro = 0;
+    Window* sw = nullptr;
+    Window* rw = nullptr;
+    {
+      std::lock_guard<std::mutex> lk(c->mu);
+      if (needSend && r.send) sw = c->findWindow(r.send, sendBytes, &so);
+      if (needRecv && r.recv) rw = c->findWindow(r.recv, recvBytes, &ro);
+    }
+    const bool aligned = ((((uintptr_t)(needSend ? r.send : nullptr)) | ((uintptr_t)r.recv)) & 15) == 0;
+    const bool mcOk = (!needSend || (sw && sw->seg.mc)) && (!needRecv || (rw && rw->seg.mc));
+    const bool mcNeeded = algo == ALGO_NVLS;
+    if (aligned && (!needSend || sw) && (!needRecv || rw) && (!mcNeeded || mcOk)) {
+      direct = true;
+      for (int p = 0; p < n; p++) {
+        args->sendPeer[p] = sw ? sw->seg.peer[p] + so : nullptr;
+        args->recvPeer[p] = rw ? rw->seg.peer[p] + ro : nullptr;
+      }
+      args->sendMc = sw && sw->seg.mc ? sw->seg.mc + so : nullptr;
+      args->recvMc = rw && rw->seg.mc ? rw->seg.mc + ro : nullptr;
+    }
+  }
+  args->direct = direct ? 1 : 0;
+
+  size_t chunks = 0;
+  if (algo != ALGO_LL && !direct) {
+    size_t cap = r.kind == COLL_REDUCESCATTER ? ((c->dev.stageBytes / n) & ~(size_t)15) : c->dev.stageBytes;
+    chunks = (bytes + cap - 1) / cap;
+  }
+  if (!ctas) {
+    size_t moved = bytes * ((r.kind == COLL_REDUCESCATTER || r.kind == COLL_ALLGATHER) ? n : 1);
+    ctas = algo == ALGO_LL ? (int)std::min<size_t>(16, (bytes / 8 + kCollThreads - 1) / kCollThreads) : ctasFor(c, moved, algo);
+  }
+  ctas = std::max(1, std::min(ctas, algo == ALGO_LL ? 16 : c->maxCtas));
+  plan->algo = algo;
+  plan->ctas = ctas;
+  plan->direct = direct;
+  plan->chunks = chunks;
+  return ncclSuccess;
+}
+
+ncclResult_t planColl(const CollReq& r, Plan* plan) {
+  ResolvedOp rop{ncclSum, SCALE_NONE, 0};
+  if (r.op >= 0 && r.op < ncclNumOps) {
+    rop.base = r.op == ncclAvg ? ncclSum : r.op;
+    rop.scaleMode = r.op == ncclAvg ? SCALE_POST_DIV_N : SCALE_NONE;
+  } else {
+    rop.scaleMode = SCALE_PRE_MUL;
+  }
+  CollArgs args;
+  return planInternal(r, rop, plan, &args);
+}
+
+ncclResult_t enqueueColl(const CollReq& r) {
+  Comm* c = r.comm;
+  BCHECK(commCheck(c));
+  const int n = c->nranks;
+  if ((int)r.dt < 0 || (int)r.dt >= ncclNumTypes) BFAIL(ncclInvalidArgument, "invalid datatype %d", (int)r.dt);
+  const bool reducing = r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE;
+  const bool rooted = r.kind == COLL_REDUCE || r.kind == COLL_BROADCAST;
+  if (rooted && (r.root < 0 || r.root >= n)) BFAIL(ncclInvalidArgument, "root %d outside [0, %d)", r.root, n);
+  if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+  if (r.count == 0) return ncclSuccess;
+  const bool needRecv = !(r.kind == COLL_REDUCE && c->rank != r.root);
+  const bool needSend = !(r.kind == COLL_BROADCAST && c->rank != r.root);
+  if ((needSend && !r.send) || (needRecv && !r.recv)) BFAIL(ncclInvalidArgument, "null buffer");
+  const size_t es = dtypeSize(r.dt);
+  if ((((uintptr_t)r.send) | ((uintptr_t)r.recv)) & (es - 1)) BFAIL(ncclInvalidArgument, "buffer not aligned to its element size");
+
+  DeviceGuard guard(c->cudaDev);
+  ResolvedOp rop{ncclSum, SCALE_NONE, 0};
+  if (reducing) BCHECK(resolveOp(c, r.op, r.dt, r.stream, &rop));
+
+  Tracer* tr = c->tracer;
+  TraceStamp* stamp = tr ? tr->begin(r.apiId, r.dt, r.count, traceBytes(r)) : nullptr;
+  auto finish = [&](bool launched, ncclResult_t res) {
+    if (tr) tr->end(launched);
+    return res;
+  };
+
+  // One rank: a copy, unless the operator rescales.
+  if (n == 1 && rop.scaleMode != SCALE_PRE_MUL) {
+    if (r.send != r.recv) {
+      cudaError_t e = cudaMemcpyAsync(r.recv, r.send, r.count * es, cudaMemcpyDeviceToDevice, r.stream);
+      if (e != cudaSuccess) return finish(false, ncclUnhandledCudaError);
+    }
+    return finish(false, ncclSuccess);
+  }
+
+  // Registered buffers are exchanged with the peers on first use.
+  if (!c->regs.empty()) {
+    if (r.send) BCHECK(commRegisterLazy(c, r.send, 1));
+    if (r.recv) BCHECK(commRegisterLazy(c, r.recv, 1));
+  }
+
+  Plan plan;
+  CollArgs args;
+  BCHECK(planInternal(r, rop, &plan, &args));
+  DevComm dc = c->dev;
+  dc.opSeq = ++c->opSeq;
+  dc.stamp = stamp;
+  if (tr) tr->setAlgo(plan.algo, plan.ctas);
+  BTRACE(SUB_COLL, "rank %d op#%llu kind %d count %zu %s algo %d ctas %d direct %d", c->rank, (unsigned long long)dc.opSeq, r.kind, r.count, dtypeName(r.dt), plan.algo, plan.ctas, (int)plan.direct);
+
+  cudaError_t e;
+  if (plan.algo == ALGO_LL) {
+    LLArgs la{};
+    la.send = r.send;
+    la.recv = r.recv;
+    la.count = r.count;
+    la.scaleMode = rop.scaleMode;
+    la.scalarBits = rop.bits;
+    if (++c->llSeq == 0) c->llSeq = 2;  // 0 is the "never written" value; keep the parity sequence
+    la.seq = c->llSeq;
+    e = launchLLAllReduce(r.dt, rop.base, plan.ctas, r.stream, dc, la);
+  } else {
+    args.stageHalf = (int)(c->stageParity & 1);
+    c->stageParity += (uint32_t)plan.chunks;
+    const bool nvls = plan.algo == ALGO_NVLS;
+    if (reducing) e = launchStagedReduce(r.dt, rop.base, nvls, plan.ctas, r.stream, dc, args);
+    else e = launchStagedCopy(nvls && r.kind == COLL_BROADCAST, plan.ctas, r.stream, dc, args, (int)es);
+  }
+  if (e != cudaSuccess) {
+    setLastError("kernel launch failed: %s", cudaGetErrorString(e));
+    BWARN("kernel launch failed: %s", cudaGetErrorString(e));
+    return finish(false, ncclUnhandledCudaError);
+  }
+  return finish(true, ncclSuccess);
+}
+
+ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops) {
+  BCHECK(commCheck(c));
+  if (ops.empty()) return ncclSuccess;
+  if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+  DeviceGuard guard(c->cudaDev);
+  const int n = c->nranks;
+  for (const P2pReq& o : ops)
+    if (o.peer < 0 || o.peer >= n) BFAIL(ncclInvalidArgument, "peer %d outside [0, %d)", o.peer, n);
+  cudaStream_t main = ops[0].stream;
+  // Other streams used in the group join the first one for the duration of the transfers.
+  std::vector<cudaStream_t> others;
+  for (const P2pReq& o : ops)
+    if (o.stream != main && std::find(others.begin(), others.end(), o.stream) == others.end()) others.push_back(o.stream);
+  for (cudaStream_t s : others) {
+    BCUDA(cudaEventRecord(c->scratchEvent, s));
+    BCUDA(cudaStreamWaitEvent(main, c->scratchEvent, 0));
+  }
+
+  // Self-sends pair with self-receives in order and become local copies.
+  std::vector<P2pReq*> selfSend, selfRecv;
+  std::vector<P2pReq*> rest;
+  for (P2pReq& o : ops) {
+    if (o.peer == c->rank) (o.isSend ? selfSend : selfRecv).push_back(&o);
+    else rest.push_back(&o);
+  }
+  if (selfSend.size() != selfRecv.size()) BFAIL(ncclInvalidUsage, "%zu sends to self but %zu receives from self in one group", selfSend.size(), selfRecv.size());
+  for (size_t i = 0; i < selfSend.size(); i++) {
+    if (selfSend[i]->bytes != selfRecv[i]->bytes) BFAIL(ncclInvalidUsage, "send-to-self of %zu bytes meets a receive of %zu bytes", selfSend[i]->bytes, selfRecv[i]->bytes);
+    if (selfSend[i]->bytes && selfSend[i]->buf != selfRecv[i]->buf)
+      BCUDA(cudaMemcpyAsync(selfRecv[i]->buf, selfSend[i]->buf, selfSend[i]->bytes, cudaMemcpyDeviceToDevice, main));
+  }
+
+  // Rounds: at most one send and one receive per peer in a launch, in the order they were made.
+  std::vector<bool> done(rest.size(), false);
+  size_t left = rest.size();
+  while (left) {
+    P2pArgs pa{};
+    bool sendUsed[kMaxRanks] = {}, recvUsed[kMaxRanks] = {};
+    for (size_t i = 0; i < rest.size(); i++) {
+      if (done[i]) continue;
+      P2pReq* o = rest[i];
+      bool* used = o->isSend ? sendUsed : recvUsed;
+      if (used[o->peer]) continue;
+      used[o->peer] = true;
+      done[i] = true;
+      left--;
+      if (o->bytes == 0) continue;
+      P2pWork& w = pa.work[pa.nwork++];
+      w.peer = o->peer;
+      w.isSend = o->isSend ? 1 : 0;
+      w.src = (const char*)o->buf;
+      w.dst = (char*)o->buf;
+      w.bytes = o->bytes;
+    }
+    if (pa.nwork == 0) continue;
+    Tracer* tr = c->tracer;
+    size_t tb = 0;
+    for (int i = 0; i < pa.nwork; i++) tb += pa.work[i].bytes;
+    TraceStamp* stamp = tr ? tr->begin(ops[0].apiId, ncclInt8, tb, tb) : nullptr;
+    DevComm dc = c->dev;
+    dc.opSeq = ++c->opSeq;
+    dc.stamp = stamp;
+    if (tr) tr->setAlgo(ALGO_P2P, pa.nwork * dc.p2pSubs);
+    cudaError_t e = launchP2p(pa.nwork * dc.p2pSubs, main, dc, pa);
+    if (tr) tr->end(e == cudaSuccess);
+    if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "send/recv launch failed: %s", cudaGetErrorString(e));
+  }
+  for (cudaStream_t s : others) {
+    BCUDA(cudaEventRecord(c->scratchEvent, main));
+    BCUDA(cudaStreamWaitEvent(s, c->scratchEvent, 0));
+  }
+  return ncclSuccess;
+}
+
+}  // namespace b200

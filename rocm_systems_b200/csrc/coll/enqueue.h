@@ -1,0 +1,41 @@
+// Host side of a collective call: validation, algorithm choice, launch.
+#pragma once
+
+#include <vector>
+
+#include "../core/comm.h"
+
+namespace b200 {
+
+struct CollReq {
+  int apiId;            // b200collApiId, for the tracer
+  int kind;             // CollKind
+  const void* send;
+  void* recv;
+  size_t count;
+  ncclDataType_t dt;
+  int op;               // raw ncclRedOp_t value (built-in or PreMulSum handle)
+  int root;
+  Comm* comm;
+  cudaStream_t stream;
+  int forceAlgo = ALGO_AUTO;  // schedule-file override
+  int forceCtas = 0;
+};
+ncclResult_t enqueueColl(const CollReq& r);
+
+struct P2pReq {
+  bool isSend;
+  void* buf;
+  size_t bytes;
+  int peer;
+  cudaStream_t stream;
+  int apiId;
+};
+// All sends and receives one group made on one communicator.
+ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops);
+
+// What the chooser would pick (exposed for tests and the tuner).
+struct Plan { int algo; int ctas; bool direct; size_t chunks; };
+ncclResult_t planColl(const CollReq& r, Plan* plan);
+
+}  // namespace b200

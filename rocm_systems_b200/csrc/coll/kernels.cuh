@@ -1,0 +1,444 @@
+// The collective kernels (sm_100a). One launch per collective call; CTA `b` of every rank forms
+// an independent lane that synchronises only with CTA `b` of its peers.
+//
+// Algorithms, by message size (semantics: rccl.h:548-934; in-place rules rccl.h:665-705):
+//   kLLAllReduce      one-shot all-reduce for small messages: every rank stores its data into
+//                     every peer's buffer as 16-byte lines {data, flag, data, flag}; the flag in
+//                     the line is the only synchronisation (one NVLink crossing of latency).
+//   kStagedReduce     AllReduce / ReduceScatter / Reduce through a symmetric staging buffer:
+//                     copy-in, barrier, each rank reduces its 1/n slice (peer loads, or one
+//                     multimem.ld_reduce that adds inside the NVSwitch), result goes straight to
+//                     where it is needed (peer stores / multimem.st / local recv), barrier,
+//                     copy-out. With registered symmetric buffers the copies disappear.
+//   kStagedCopy       AllGather (pull from peers' staging into recv) and Broadcast (root fills
+//                     staging, with one multicast store when NVLS is on; the others copy out).
+//   kP2p              grouped Send/Recv work list over per-peer FIFOs with credits; AllToAll(v),
+//                     Gather and Scatter are built from it.
+// Staging halves alternate per chunk; every chunk has a full barrier after its copy-in, which
+// is what makes reusing a half two chunks later safe without a trailing barrier.
+#pragma once
+
+#include "prims.cuh"
+#include "reduce_ops.cuh"
+
+namespace b200 {
+
+// ---- element-wise helpers (tails and unaligned buffers) -------------------------------------
+template <typename T>
+__device__ __forceinline__ void loadUnit8(const T* base, size_t count, size_t unit, bool aligned, T (&e)[8 / sizeof(T)]) {
+  constexpr int EPU = 8 / sizeof(T);
+  const size_t i0 = unit * EPU;
+  if (aligned && i0 + EPU <= count) {
+    union { uint2 v; T t[EPU]; } u;
+    u.v = *(const uint2*)(base + i0);
+#pragma unroll
+    for (int k = 0; k < EPU; k++) e[k] = u.t[k];
+  } else {
+#pragma unroll
+    for (int k = 0; k < EPU; k++) {
+      if (i0 + k < count) e[k] = base[i0 + k];
+      else e[k] = ElemTraits<T>::down(typename ElemTraits<T>::Acc(0));
+    }
+  }
+}
+
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_constant__ DevComm c, const __grid_constant__ LLArgs a) {
+  stampBegin(c);
+  constexpr int EPU = 8 / sizeof(T);
+  using Acc = typename ElemTraits<T>::Acc;
+  const int n = c.nranks, rank = c.rank;
+  const size_t units = (a.count + EPU - 1) / EPU;
+  const size_t halfOff = kWsLLOff + (size_t)(a.seq & 1) * (size_t)n * c.llSlotBytes;
+  const T* send = (const T*)a.send;
+  T* recv = (T*)a.recv;
+  const bool aligned = ((((uintptr_t)a.send) | ((uintptr_t)a.recv)) & 7) == 0;
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gn = (size_t)gridDim.x * blockDim.x;
+
+  for (size_t i = gtid; i < units; i += gn) {
+    T e[EPU];
+    loadUnit8<T>(send, a.count, i, aligned, e);
+    union { uint2 v; T t[EPU]; } u;
+#pragma unroll
+    for (int k = 0; k < EPU; k++) u.t[k] = e[k];
+    const uint4 line = make_uint4(u.v.x, a.seq, u.v.y, a.seq);
+    for (int d = 1; d < n; d++) {
+      const int p = (rank + d) % n;
+      stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, line);
+    }
+  }
+
+  const Acc scalar = scalarFromBits<T>(a.scalarBits);
+  for (size_t i = gtid; i < units; i += gn) {
+    Acc acc[EPU];
+    for (int s = 0; s < n; s++) {
+      union { uint2 v; T t[EPU]; } u;
+      if (s == rank) {
+        T e[EPU];
+        loadUnit8<T>(send, a.count, i, aligned, e);
+#pragma unroll
+        for (int k = 0; k < EPU; k++) u.t[k] = e[k];
+      } else {
+        const char* line = c.ws[rank] + halfOff + (size_t)s * c.llSlotBytes + i * 16;
+        uint4 v;
+        unsigned long long t0 = 0;
+        uint32_t spins = 0;
+        bool ok = true;
+        while (true) {
+          v = ldVolatile16(line);
+          if (v.y == a.seq && v.w == a.seq) break;
+          if ((++spins & 0xff) == 0) {
+            if (*(volatile uint32_t*)&c.local->failed) { ok = false; break; }
+            if (*c.abortFlag) { recordFailure(c, 2, WAIT_LL, s, a.seq, v.y); ok = false; break; }
+            unsigned long long now = globalTimerNs();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > c.timeoutNs) { recordFailure(c, 1, WAIT_LL, s, a.seq, v.y); ok = false; break; }
+          }
+        }
+        u.v = ok ? make_uint2(v.x, v.z) : make_uint2(0, 0);
+      }
+#pragma unroll
+      for (int k = 0; k < EPU; k++) {
+        Acc x = ElemTraits<T>::up(u.t[k]);
+        if (a.scaleMode == SCALE_PRE_MUL) x = x * scalar;
+        acc[k] = (s == 0) ? x : Op::apply(acc[k], x);
+      }
+    }
+    const size_t i0 = i * EPU;
+    union { uint2 v; T t[EPU]; } o;
+#pragma unroll
+    for (int k = 0; k < EPU; k++) {
+      Acc x = acc[k];
+      if (a.scaleMode == SCALE_POST_DIV_N) x = postDiv<T>(x, n);
+      o.t[k] = ElemTraits<T>::down(x);
+    }
+    if (aligned && i0 + EPU <= a.count) {
+      *(uint2*)(recv + i0) = o.v;
+    } else {
+#pragma unroll
+      for (int k = 0; k < EPU; k++)
+        if (i0 + k < a.count) recv[i0 + k] = o.t[k];
+    }
+  }
+  stampEnd(c);
+}
+
+// ---- staged / direct reduce -----------------------------------------------------------------
+// Store 16 bytes of results to a local user buffer that may be unaligned or end mid-unit.
+template <typename T>
+__device__ __forceinline__ void storeUser16(char* base, size_t byteOff, size_t limitBytes, uint4 v, bool aligned) {
+  if (aligned && byteOff + 16 <= limitBytes) {
+    st16(base + byteOff, v);
+  } else {
+    union { uint4 v; T t[16 / sizeof(T)]; } u;
+    u.v = v;
+#pragma unroll
+    for (int k = 0; k < (int)(16 / sizeof(T)); k++)
+      if (byteOff + (k + 1) * sizeof(T) <= limitBytes) *(T*)(base + byteOff + k * sizeof(T)) = u.t[k];
+  }
+}
+
+template <typename T, typename Op, bool NVLS>
+__global__ void __launch_bounds__(kCollThreads) kStagedReduce(const __grid_constant__ DevComm c, const __grid_constant__ CollArgs a) {
+  stampBegin(c);
+  using P = Pack<T>;
+  using Acc = typename ElemTraits<T>::Acc;
+  constexpr size_t ES = sizeof(T);
+  const int n = c.nranks, rank = c.rank, B = gridDim.x, b = blockIdx.x;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  uint32_t epoch = c.local->barEpoch[b];
+  const bool isRS = a.kind == COLL_REDUCESCATTER;
+  const bool isAR = a.kind == COLL_ALLREDUCE;
+  const bool isRed = a.kind == COLL_REDUCE;
+  const size_t total = a.count * ES;  // AllReduce/Reduce: the message; ReduceScatter: one rank's slice
+  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : (isRS ? (c.stageBytes / n) & ~(size_t)15 : c.stageBytes);
+  const Acc scalar = scalarFromBits<T>(a.scalarBits);
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  int half = a.stageHalf;
+
+  for (size_t off = 0; off < total; off += cap, half ^= 1) {
+    const size_t cb = (total - off < cap) ? total - off : cap;  // bytes of this chunk (per slice for RS)
+    const size_t U = (cb + 15) >> 4;
+    const size_t su = isRS ? U : (U + n - 1) / n;                // 16-byte units per slice
+    const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
+    // Where slice s starts: in the chunk (bytes), in staging, and how long it is.
+    auto sliceBytes = [&](int s) -> size_t {
+      if (isRS) return cb;
+      size_t lo = (size_t)s * su * 16;
+      if (lo >= cb) return 0;
+      size_t len = cb - lo;
+      return len < su * 16 ? len : su * 16;
+    };
+    auto sliceStage = [&](int s) -> size_t { return isRS ? (size_t)s * cap : (size_t)s * su * 16; };
+    auto sliceSrc = [&](int s) -> const char* {
+      return isRS ? send + ((size_t)s * a.count * ES + off) : send + off + (size_t)s * su * 16;
+    };
+
+    if (!a.direct) {
+      for (int i = 0; i < n; i++) {
+        const int s = (rank + i) % n;
+        const size_t sb = sliceBytes(s);
+        size_t lo, hi;
+        splitUnits((sb + 15) >> 4, B, b, lo, hi);
+        if (lo < hi) {
+          size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
+          ctaCopy(c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), sliceSrc(s) + (lo << 4), bytes);
+        }
+      }
+    }
+    ctaBarrier(c, epoch);
+
+    // Reduce. Normally this rank reduces slice `rank`; the NVLS Reduce root pulls every slice.
+    const bool pullAll = NVLS && isRed;
+    if (!pullAll || rank == a.root) {
+      for (int si = 0; si < (pullAll ? n : 1); si++) {
+        const int s = pullAll ? si : rank;
+        const size_t sb = sliceBytes(s);
+        size_t lo, hi;
+        splitUnits((sb + 15) >> 4, B, b, lo, hi);
+        // Byte offset of the slice inside the message (direct windows and user recv).
+        const size_t msgOff = isRS ? off : off + (size_t)s * su * 16;
+        const size_t stOff = stageBase + sliceStage(s);
+        const bool recvAligned = (((uintptr_t)(recv + (isRS ? off : msgOff))) & 15) == 0;
+        for (size_t u = lo + tid; u < hi; u += nt) {
+          uint4 out;
+          if constexpr (NVLS) {
+            const char* src = a.direct ? a.sendMc + (isRS ? (size_t)s * a.count * ES + off : msgOff) : c.wsMc + stOff;
+            out = McReduce<T>::ld(src + (u << 4));
+            if (a.scaleMode == SCALE_POST_DIV_N) {
+              Acc acc[P::N];
+              P::up(out, acc);
+#pragma unroll
+              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
+              out = P::down(acc);
+            }
+          } else {
+            uint4 v[kMaxRanks];
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; p++) {
+              if (p < n) {
+                const char* src = a.direct ? a.sendPeer[p] + (isRS ? (size_t)s * a.count * ES + off : msgOff) : c.ws[p] + stOff;
+                v[p] = ldStream16(src + (u << 4));
+              }
+            }
+            Acc acc[P::N];
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; p++) {
+              if (p < n) {
+                Acc x[P::N];
+                P::up(v[p], x);
+#pragma unroll
+                for (int k = 0; k < P::N; k++) {
+                  Acc y = x[k];
+                  if (a.scaleMode == SCALE_PRE_MUL) y = y * scalar;
+                  acc[k] = (p == 0) ? y : Op::apply(acc[k], y);
+                }
+              }
+            }
+            if (a.scaleMode == SCALE_POST_DIV_N) {
+#pragma unroll
+              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
+            }
+            out = P::down(acc);
+          }
+          // Deliver.
+          if (isRS) {
+            storeUser16<T>(recv, off + (u << 4), total, out, recvAligned);
+          } else if (isAR) {
+            if constexpr (NVLS) {
+              mcStore16((a.direct ? a.recvMc + msgOff : c.wsMc + stOff) + (u << 4), out);
+            } else {
+#pragma unroll
+              for (int p = 0; p < kMaxRanks; p++)
+                if (p < n) st16((a.direct ? a.recvPeer[p] + msgOff : c.ws[p] + stOff) + (u << 4), out);
+            }
+          } else {  // Reduce
+            if constexpr (NVLS) {
+              storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
+            } else {
+              st16((a.direct ? a.recvPeer[a.root] + msgOff : c.ws[a.root] + stOff) + (u << 4), out);
+            }
+          }
+        }
+      }
+    }
+
+    const bool needSecond = isAR || (isRed && !NVLS) || a.direct;
+    if (needSecond) ctaBarrier(c, epoch);
+
+    if (!a.direct && (isAR || (isRed && !NVLS && rank == a.root))) {
+      for (int i = 0; i < n; i++) {
+        const int s = (rank + i) % n;
+        const size_t sb = sliceBytes(s);
+        size_t lo, hi;
+        splitUnits((sb + 15) >> 4, B, b, lo, hi);
+        if (lo < hi) {
+          size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
+          ctaCopy(recv + off + (size_t)s * su * 16 + (lo << 4), c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), bytes);
+        }
+      }
+    }
+  }
+  if (tid == 0) c.local->barEpoch[b] = epoch;
+  stampEnd(c);
+}
+
+// ---- staged / direct copy collectives: AllGather and Broadcast ------------------------------
+__device__ __forceinline__ void ctaCopyToMc(char* mcDst, const char* src, size_t bytes) {
+  // Multicast store of whole 16-byte units (staging is padded, so rounding up is safe).
+  const size_t nvec = (bytes + 15) >> 4;
+  const bool aligned = (((uintptr_t)src) & 15) == 0;
+  for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+    uint4 v;
+    if (aligned && ((i + 1) << 4) <= bytes) {
+      v = ldStream16(src + (i << 4));
+    } else {
+      union { uint4 v; unsigned char c[16]; } u;
+      u.v = make_uint4(0, 0, 0, 0);
+      for (int k = 0; k < 16; k++)
+        if ((i << 4) + k < bytes) u.c[k] = ((const unsigned char*)src)[(i << 4) + k];
+      v = u.v;
+    }
+    mcStore16(mcDst + (i << 4), v);
+  }
+}
+
+template <bool NVLS>
+__global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constant__ DevComm c, const __grid_constant__ CollArgs a, const int elemSize) {
+  stampBegin(c);
+  const int n = c.nranks, rank = c.rank, B = gridDim.x, b = blockIdx.x;
+  uint32_t epoch = c.local->barEpoch[b];
+  const size_t total = a.count * (size_t)elemSize;  // AllGather: one rank's contribution; Broadcast: the message
+  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : c.stageBytes;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  int half = a.stageHalf;
+  const bool isAG = a.kind == COLL_ALLGATHER;
+
+  for (size_t off = 0; off < total; off += cap, half ^= 1) {
+    const size_t cb = (total - off < cap) ? total - off : cap;
+    const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
+    size_t lo, hi;
+    splitUnits((cb + 15) >> 4, B, b, lo, hi);
+    const size_t bytes = lo < hi ? (((hi << 4) < cb ? (hi << 4) : cb) - (lo << 4)) : 0;
+    const size_t bo = lo << 4;  // byte offset of this CTA's part inside the chunk
+
+    if (isAG) {
+      if (!a.direct) ctaCopy(c.ws[rank] + stageBase + bo, send + off + bo, bytes);
+      ctaBarrier(c, epoch);
+      for (int i = 0; i < n; i++) {
+        const int p = (rank + i) % n;
+        char* dst = recv + (size_t)p * total + off + bo;
+        if (p == rank) {
+          if (dst != send + off + bo) ctaCopy(dst, send + off + bo, bytes);
+        } else {
+          const char* src = a.direct ? a.sendPeer[p] + off + bo : c.ws[p] + stageBase + bo;
+          ctaCopy(dst, src, bytes);
+        }
+      }
+      if (a.direct) ctaBarrier(c, epoch);
+    } else {  // Broadcast
+      if (a.direct) {
+        ctaBarrier(c, epoch);
+        if (rank == a.root) {
+          if constexpr (NVLS) {
+            ctaCopyToMc(a.recvMc + off + bo, send + off + bo, bytes);
+          } else {
+            for (int i = 0; i < n; i++) {
+              const int p = (rank + i) % n;
+              if (p == rank && recv + off + bo == send + off + bo) continue;
+              ctaCopy(a.recvPeer[p] + off + bo, send + off + bo, bytes);
+            }
+          }
+        }
+        ctaBarrier(c, epoch);
+      } else {
+        if (rank == a.root) {
+          if constexpr (NVLS) ctaCopyToMc(c.wsMc + stageBase + bo, send + off + bo, bytes);
+          else ctaCopy(c.ws[rank] + stageBase + bo, send + off + bo, bytes);
+          if (recv != send) ctaCopy(recv + off + bo, send + off + bo, bytes);
+        }
+        ctaBarrier(c, epoch);
+        if (rank != a.root) {
+          const char* src = NVLS ? c.ws[rank] + stageBase + bo : c.ws[a.root] + stageBase + bo;
+          ctaCopy(recv + off + bo, src, bytes);
+        }
+      }
+    }
+  }
+  if (threadIdx.x == 0) c.local->barEpoch[b] = epoch;
+  stampEnd(c);
+}
+
+// ---- grouped send/recv ----------------------------------------------------------------------
+// Non-template kernels are compiled only by the translation unit that launches them.
+#ifdef B200_MISC_KERNELS
+__global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ DevComm c, const __grid_constant__ P2pArgs a) {
+  stampBegin(c);
+  const int subs = c.p2pSubs;
+  const int w = blockIdx.x / subs, j = blockIdx.x % subs;
+  if (w < a.nwork) {
+    const P2pWork& wk = a.work[w];
+    const int peer = wk.peer, rank = c.rank;
+    size_t lo, hi;
+    splitUnits((wk.bytes + 15) >> 4, subs, j, lo, hi);
+    const size_t begin = lo << 4;
+    const size_t end = (hi << 4) < wk.bytes ? (hi << 4) : wk.bytes;
+    const size_t chunk = c.p2pChunkBytes;
+    unsigned long long* myTail = (unsigned long long*)(c.ws[rank] + kWsP2pCtrlOff);
+    unsigned long long* myHead = myTail + kMaxRanks * 8;
+    unsigned long long* peerTail = (unsigned long long*)(c.ws[peer] + kWsP2pCtrlOff);
+    unsigned long long* peerHead = peerTail + kMaxRanks * 8;
+    __shared__ int okShared;
+    if (wk.isSend) {
+      unsigned long long sent = c.local->p2pSent[peer][j];
+      char* fifo = c.ws[peer] + c.p2pOff + ((size_t)(rank * subs + j) * c.p2pSlots) * chunk;
+      for (size_t o = begin; o < end; o += chunk) {
+        const size_t nb = end - o < chunk ? end - o : chunk;
+        if (threadIdx.x == 0) {
+          unsigned long long need = sent + 1 > (unsigned long long)c.p2pSlots ? sent + 1 - c.p2pSlots : 0;
+          okShared = waitGe64(c, &myHead[peer * 8 + j], need, WAIT_P2P_CREDIT, peer) ? 1 : 0;
+        }
+        __syncthreads();
+        if (okShared) ctaCopy(fifo + (size_t)(sent % c.p2pSlots) * chunk, wk.src + o, nb);
+        __syncthreads();
+        sent++;
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          stReleaseSys64(&peerTail[rank * 8 + j], sent);
+        }
+      }
+      if (threadIdx.x == 0) c.local->p2pSent[peer][j] = sent;
+    } else {
+      unsigned long long recvd = c.local->p2pRecvd[peer][j];
+      const char* fifo = c.ws[rank] + c.p2pOff + ((size_t)(peer * subs + j) * c.p2pSlots) * chunk;
+      for (size_t o = begin; o < end; o += chunk) {
+        const size_t nb = end - o < chunk ? end - o : chunk;
+        if (threadIdx.x == 0) okShared = waitGe64(c, &myTail[peer * 8 + j], recvd + 1, WAIT_P2P_DATA, peer) ? 1 : 0;
+        __syncthreads();
+        if (okShared) ctaCopy(wk.dst + o, fifo + (size_t)(recvd % c.p2pSlots) * chunk, nb);
+        __syncthreads();
+        recvd++;
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          stReleaseSys64(&peerHead[rank * 8 + j], recvd);
+        }
+      }
+      if (threadIdx.x == 0) c.local->p2pRecvd[peer][j] = recvd;
+    }
+  }
+  stampEnd(c);
+}
+
+__global__ void kBarrier(const __grid_constant__ DevComm c) {
+  stampBegin(c);
+  uint32_t epoch = c.local->barEpoch[0];
+  ctaBarrier(c, epoch);
+  if (threadIdx.x == 0) c.local->barEpoch[0] = epoch;
+  stampEnd(c);
+}
+#endif  // B200_MISC_KERNELS
+
+}  // namespace b200
