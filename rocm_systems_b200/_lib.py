@@ -105,6 +105,8 @@ def load() -> ctypes.CDLL:
     lib.mscclUnloadAlgo.argtypes = [i32]
     lib.mscclRunAlgo.argtypes = [vp, vp, vp, vp, vp, vp, sz, i32, i32, i32, i32, i32, vp, vp]
     lib.b200collGetApiTable.restype = vp
+    lib.b200collTestWaitTimeout.argtypes = [vp, i32, vp]
+    lib.b200collCommCaps.argtypes = [vp]
     _lib = lib
     return lib
 

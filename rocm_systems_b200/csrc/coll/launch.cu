@@ -44,6 +44,17 @@ cudaError_t launchP2p(int grid, cudaStream_t s, const DevComm& c, const P2pArgs&
   return cudaGetLastError();
 }
 
+// Waits on a flag word that nothing ever writes, so the wait budget runs out: the way the
+// time-out path (status word, async error) is exercised without any rank misbehaving.
+__global__ void kWaitUnsetFlag(const __grid_constant__ DevComm c) {
+  const uint32_t* flag = (const uint32_t*)(c.ws[c.rank] + kWsUserFlagsOff + 48 * 1024 - 64);
+  if (threadIdx.x == 0) waitGe(c, flag, 1u, WAIT_SHMEM, (uint32_t)c.rank);
+}
+cudaError_t launchWaitUnsetFlag(cudaStream_t s, const DevComm& c) {
+  kWaitUnsetFlag<<<1, 32, 0, s>>>(c);
+  return cudaGetLastError();
+}
+
 cudaError_t launchBarrier(cudaStream_t s, const DevComm& c) {
   kBarrier<<<1, 32, 0, s>>>(c);
   return cudaGetLastError();

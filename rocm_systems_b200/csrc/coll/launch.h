@@ -13,6 +13,7 @@ cudaError_t launchStagedReduce(ncclDataType_t dt, int op, bool nvls, int grid, c
 cudaError_t launchStagedCopy(bool nvls, int grid, cudaStream_t s, const DevComm& c, const CollArgs& a, int elemSize);
 cudaError_t launchP2p(int grid, cudaStream_t s, const DevComm& c, const P2pArgs& a);
 cudaError_t launchBarrier(cudaStream_t s, const DevComm& c);
+cudaError_t launchWaitUnsetFlag(cudaStream_t s, const DevComm& c);
 cudaError_t launchFill(void* dst, unsigned value, size_t bytes, cudaStream_t s);
 cudaError_t launchCopy(void* dst, const void* src, size_t bytes, int grid, cudaStream_t s);
 bool nvlsReducible(ncclDataType_t dt, int op);  // can the switch do this reduction?

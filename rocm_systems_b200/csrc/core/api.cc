@@ -801,5 +801,27 @@ ncclResult_t b200collBootClose(void* handle, int graceful) {
   return ncclSuccess;
 }
 void b200collRefreshFlags(void) { Flags::refresh(); }
+// Enqueue a wait on a flag nothing sets, with `timeoutMs` as its budget (test hook for the
+// time-out path; the communicator reports ncclRemoteError afterwards and must be destroyed).
+ncclResult_t b200collTestWaitTimeout(ncclComm_t comm, int timeoutMs, cudaStream_t stream) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  DevComm dc = c->dev;
+  dc.opSeq = ++c->opSeq;
+  dc.timeoutNs = (unsigned long long)timeoutMs * 1000000ull;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != c->cudaDev) cudaSetDevice(c->cudaDev);
+  cudaError_t e = launchWaitUnsetFlag(stream, dc);
+  if (prev != c->cudaDev && prev >= 0) cudaSetDevice(prev);
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "launch failed: %s", cudaGetErrorString(e));
+  return ncclSuccess;
+}
+// What the communicator was able to set up: bit 0 multicast (NVLS), bit 1 legacy IPC mode.
+int b200collCommCaps(ncclComm_t comm) {
+  Comm* c = asComm(comm);
+  if (!c || c->magic != kCommMagic) return -1;
+  return (c->nvls ? 1 : 0) | (c->ws.legacy ? 2 : 0);
+}
 const char* b200collLastError(void) { return lastError(); }
 }
