@@ -1,7 +1,7 @@
 """Collective bandwidth sweep, one process per GPU (run under torchrun):
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \
-        -m rocm_systems_b200.bench.coll_sweep --min 8 --max 1G --out sweep.json
+        -m rocm_systems_b200.bench.coll_sweep -b 8 -e 1G -f 4 --out sweep.json
 
 For every collective and size it times this library and, side by side, stock NCCL through
 ``torch.distributed`` on the same buffers, and prints the rccl-tests columns (size, count, type,
@@ -59,9 +59,9 @@ def time_op(fn, warmup: int, iters: int) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--min", default="8")
-    ap.add_argument("--max", default="256M")
-    ap.add_argument("--factor", type=int, default=4)
+    ap.add_argument("-b", "--minbytes", default="8")
+    ap.add_argument("-e", "--maxbytes", default="256M")
+    ap.add_argument("-f", "--stepfactor", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--dtype", default="float")
@@ -76,7 +76,7 @@ def main() -> None:
     dist.init_process_group("nccl" if not args.no_nccl else "gloo", device_id=comm.device if not args.no_nccl else None)
     dt = {"float": torch.float32, "bfloat16": torch.bfloat16, "half": torch.float16}[args.dtype]
     es = torch.empty((), dtype=dt).element_size()
-    lo, hi = parse_size(args.min), parse_size(args.max)
+    lo, hi = parse_size(args.minbytes), parse_size(args.maxbytes)
     maxel = hi // es
     if args.symmetric:
         sym = comm.sym_alloc(2 * hi + 4096)
@@ -94,7 +94,7 @@ def main() -> None:
     sizes = []
     while size <= hi:
         sizes.append(size)
-        size *= args.factor
+        size *= args.stepfactor
     for coll in args.colls.split(","):
         for size in sizes:
             count = max(size // es, 1)

@@ -140,7 +140,8 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   // ncclCommRegister) are read and written in place on every rank.
   bool direct = false;
   // Reduce with peer loads would need the root's recv window on ranks that may pass no recv.
-  const bool directKind = !(r.kind == COLL_REDUCE && algo != ALGO_NVLS);
+  // PreMulSum scales inputs while staging them, so it cannot skip staging.
+  const bool directKind = !(r.kind == COLL_REDUCE && algo != ALGO_NVLS) && rop.scaleMode != SCALE_PRE_MUL;
   if (algo != ALGO_LL && n > 1 && (bytes % 16) == 0 && directKind) {
     const size_t sendBytes = r.kind == COLL_REDUCESCATTER ? bytes * n : bytes;
     const size_t recvBytes = r.kind == COLL_ALLGATHER ? bytes * n : bytes;

@@ -42,6 +42,13 @@ __device__ __forceinline__ void loadUnit8(const T* base, size_t count, size_t un
   }
 }
 
+// PreMulSum multiplies a rank's own input by that rank's scalar, so the scaling happens where
+// the input is read (before it is sent or staged), never on the reducing side.
+template <typename T>
+__device__ __forceinline__ T preMul(T v, typename ElemTraits<T>::Acc scalar) {
+  return ElemTraits<T>::down(ElemTraits<T>::up(v) * scalar);
+}
+
 template <typename T, typename Op>
 __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_constant__ DevComm c, const __grid_constant__ LLArgs a) {
   stampBegin(c);
@@ -56,12 +63,14 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_consta
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gn = (size_t)gridDim.x * blockDim.x;
 
+  const Acc scalar = scalarFromBits<T>(a.scalarBits);
+  const bool pre = a.scaleMode == SCALE_PRE_MUL;
   for (size_t i = gtid; i < units; i += gn) {
     T e[EPU];
     loadUnit8<T>(send, a.count, i, aligned, e);
     union { uint2 v; T t[EPU]; } u;
 #pragma unroll
-    for (int k = 0; k < EPU; k++) u.t[k] = e[k];
+    for (int k = 0; k < EPU; k++) u.t[k] = pre ? preMul<T>(e[k], scalar) : e[k];
     const uint4 line = make_uint4(u.v.x, a.seq, u.v.y, a.seq);
     for (int d = 1; d < n; d++) {
       const int p = (rank + d) % n;
@@ -69,7 +78,6 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_consta
     }
   }
 
-  const Acc scalar = scalarFromBits<T>(a.scalarBits);
   for (size_t i = gtid; i < units; i += gn) {
     Acc acc[EPU];
     for (int s = 0; s < n; s++) {
@@ -78,7 +86,7 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_consta
         T e[EPU];
         loadUnit8<T>(send, a.count, i, aligned, e);
 #pragma unroll
-        for (int k = 0; k < EPU; k++) u.t[k] = e[k];
+        for (int k = 0; k < EPU; k++) u.t[k] = pre ? preMul<T>(e[k], scalar) : e[k];
       } else {
         const char* line = c.ws[rank] + halfOff + (size_t)s * c.llSlotBytes + i * 16;
         uint4 v;
@@ -101,7 +109,6 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_consta
 #pragma unroll
       for (int k = 0; k < EPU; k++) {
         Acc x = ElemTraits<T>::up(u.t[k]);
-        if (a.scaleMode == SCALE_PRE_MUL) x = x * scalar;
         acc[k] = (s == 0) ? x : Op::apply(acc[k], x);
       }
     }
@@ -136,6 +143,29 @@ __device__ __forceinline__ void storeUser16(char* base, size_t byteOff, size_t l
 #pragma unroll
     for (int k = 0; k < (int)(16 / sizeof(T)); k++)
       if (byteOff + (k + 1) * sizeof(T) <= limitBytes) *(T*)(base + byteOff + k * sizeof(T)) = u.t[k];
+  }
+}
+
+// Copy into staging while multiplying by this rank's PreMulSum scalar (staging is 16-byte
+// aligned; the user buffer may not be).
+template <typename T>
+__device__ __forceinline__ void ctaCopyScaled(char* dst, const char* src, size_t bytes, typename ElemTraits<T>::Acc scalar) {
+  using P = Pack<T>;
+  const int t = threadIdx.x, nt = blockDim.x;
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    const size_t nvec = bytes >> 4;
+    for (size_t i = t; i < nvec; i += nt) {
+      typename P::Acc a[P::N];
+      P::up(ldStream16(src + (i << 4)), a);
+#pragma unroll
+      for (int k = 0; k < P::N; k++) a[k] = a[k] * scalar;
+      st16(dst + (i << 4), P::down(a));
+    }
+    for (size_t b = (nvec << 4) + (size_t)t * sizeof(T); b + sizeof(T) <= bytes; b += (size_t)nt * sizeof(T))
+      *(T*)(dst + b) = preMul<T>(*(const T*)(src + b), scalar);
+  } else {
+    for (size_t b = (size_t)t * sizeof(T); b + sizeof(T) <= bytes; b += (size_t)nt * sizeof(T))
+      *(T*)(dst + b) = preMul<T>(*(const T*)(src + b), scalar);
   }
 }
 
@@ -184,7 +214,8 @@ __global__ void __launch_bounds__(kCollThreads) kStagedReduce(const __grid_const
         splitUnits((sb + 15) >> 4, B, b, lo, hi);
         if (lo < hi) {
           size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
-          ctaCopy(c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), sliceSrc(s) + (lo << 4), bytes);
+          if (a.scaleMode == SCALE_PRE_MUL) ctaCopyScaled<T>(c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), sliceSrc(s) + (lo << 4), bytes, scalar);
+          else ctaCopy(c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), sliceSrc(s) + (lo << 4), bytes);
         }
       }
     }
@@ -231,9 +262,7 @@ __global__ void __launch_bounds__(kCollThreads) kStagedReduce(const __grid_const
                 P::up(v[p], x);
 #pragma unroll
                 for (int k = 0; k < P::N; k++) {
-                  Acc y = x[k];
-                  if (a.scaleMode == SCALE_PRE_MUL) y = y * scalar;
-                  acc[k] = (p == 0) ? y : Op::apply(acc[k], y);
+                  acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
                 }
               }
             }

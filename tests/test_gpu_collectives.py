@@ -91,3 +91,18 @@ def test_multi_gpu_sweep(nproc):
     sys.stdout.write(p.stdout[-4000:])
     sys.stderr.write(p.stderr[-4000:])
     assert p.returncode == 0
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_torch_distributed_backend(nproc):
+    if gpu_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    env = dict(os.environ)
+    env.setdefault("B200COLL_WAIT_TIMEOUT_MS", "5000")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29700 + nproc), str(ROOT / "tests" / "workers" / "dist_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    sys.stdout.write(p.stdout[-4000:])
+    sys.stderr.write(p.stderr[-4000:])
+    assert p.returncode == 0
