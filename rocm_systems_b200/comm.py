@@ -28,6 +28,14 @@ if hasattr(torch, "float8_e4m3fn"):
 
 OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "avg": 4}
 
+LAUNCHES = 0  # collective kernels enqueued through this module (bench.py reports it)
+
+
+def _k(rc: int, where: str) -> None:
+    global LAUNCHES
+    _lib.check(rc, where)
+    LAUNCHES += 1
+
 
 def nccl_dtype(dt: torch.dtype) -> int:
     try:
@@ -158,58 +166,58 @@ class Communicator:
     def all_reduce(self, send: torch.Tensor, recv: Optional[torch.Tensor] = None, op="sum", stream=None) -> torch.Tensor:
         recv = send if recv is None else recv
         opv = OPS[op] if isinstance(op, str) else int(op)
-        _lib.check(self._lib.ncclAllReduce(send.data_ptr(), recv.data_ptr(), send.numel(), nccl_dtype(send.dtype), opv, self._h, _stream(stream)), "ncclAllReduce")
+        _k(self._lib.ncclAllReduce(send.data_ptr(), recv.data_ptr(), send.numel(), nccl_dtype(send.dtype), opv, self._h, _stream(stream)), "ncclAllReduce")
         return recv
 
     def reduce_scatter(self, send: torch.Tensor, recv: torch.Tensor, op="sum", stream=None) -> torch.Tensor:
         opv = OPS[op] if isinstance(op, str) else int(op)
         assert send.numel() == recv.numel() * self.nranks
-        _lib.check(self._lib.ncclReduceScatter(send.data_ptr(), recv.data_ptr(), recv.numel(), nccl_dtype(send.dtype), opv, self._h, _stream(stream)), "ncclReduceScatter")
+        _k(self._lib.ncclReduceScatter(send.data_ptr(), recv.data_ptr(), recv.numel(), nccl_dtype(send.dtype), opv, self._h, _stream(stream)), "ncclReduceScatter")
         return recv
 
     def all_gather(self, send: torch.Tensor, recv: torch.Tensor, stream=None) -> torch.Tensor:
         assert recv.numel() == send.numel() * self.nranks
-        _lib.check(self._lib.ncclAllGather(send.data_ptr(), recv.data_ptr(), send.numel(), nccl_dtype(send.dtype), self._h, _stream(stream)), "ncclAllGather")
+        _k(self._lib.ncclAllGather(send.data_ptr(), recv.data_ptr(), send.numel(), nccl_dtype(send.dtype), self._h, _stream(stream)), "ncclAllGather")
         return recv
 
     def broadcast(self, send: torch.Tensor, recv: Optional[torch.Tensor] = None, root: int = 0, stream=None) -> torch.Tensor:
         recv = send if recv is None else recv
-        _lib.check(self._lib.ncclBroadcast(send.data_ptr(), recv.data_ptr(), recv.numel(), nccl_dtype(recv.dtype), root, self._h, _stream(stream)), "ncclBroadcast")
+        _k(self._lib.ncclBroadcast(send.data_ptr(), recv.data_ptr(), recv.numel(), nccl_dtype(recv.dtype), root, self._h, _stream(stream)), "ncclBroadcast")
         return recv
 
     def reduce(self, send: torch.Tensor, recv: Optional[torch.Tensor], root: int = 0, op="sum", stream=None):
         opv = OPS[op] if isinstance(op, str) else int(op)
         rp = recv.data_ptr() if recv is not None else None
-        _lib.check(self._lib.ncclReduce(send.data_ptr(), rp, send.numel(), nccl_dtype(send.dtype), opv, root, self._h, _stream(stream)), "ncclReduce")
+        _k(self._lib.ncclReduce(send.data_ptr(), rp, send.numel(), nccl_dtype(send.dtype), opv, root, self._h, _stream(stream)), "ncclReduce")
         return recv
 
     def all_to_all(self, send: torch.Tensor, recv: torch.Tensor, stream=None) -> torch.Tensor:
         assert send.numel() == recv.numel() and send.numel() % self.nranks == 0
-        _lib.check(self._lib.ncclAllToAll(send.data_ptr(), recv.data_ptr(), send.numel() // self.nranks, nccl_dtype(send.dtype), self._h, _stream(stream)), "ncclAllToAll")
+        _k(self._lib.ncclAllToAll(send.data_ptr(), recv.data_ptr(), send.numel() // self.nranks, nccl_dtype(send.dtype), self._h, _stream(stream)), "ncclAllToAll")
         return recv
 
     def all_to_allv(self, send, sendcounts, sdispls, recv, recvcounts, rdispls, stream=None):
         n = self.nranks
         arr = lambda v: (ctypes.c_size_t * n)(*[int(x) for x in v])
-        _lib.check(self._lib.ncclAllToAllv(send.data_ptr(), arr(sendcounts), arr(sdispls), recv.data_ptr(), arr(recvcounts), arr(rdispls),
+        _k(self._lib.ncclAllToAllv(send.data_ptr(), arr(sendcounts), arr(sdispls), recv.data_ptr(), arr(recvcounts), arr(rdispls),
                                            nccl_dtype(send.dtype), self._h, _stream(stream)), "ncclAllToAllv")
         return recv
 
     def gather(self, send, recv, root=0, stream=None):
         rp = recv.data_ptr() if recv is not None else None
-        _lib.check(self._lib.ncclGather(send.data_ptr(), rp, send.numel(), nccl_dtype(send.dtype), root, self._h, _stream(stream)), "ncclGather")
+        _k(self._lib.ncclGather(send.data_ptr(), rp, send.numel(), nccl_dtype(send.dtype), root, self._h, _stream(stream)), "ncclGather")
         return recv
 
     def scatter(self, send, recv, root=0, stream=None):
         sp = send.data_ptr() if send is not None else None
-        _lib.check(self._lib.ncclScatter(sp, recv.data_ptr(), recv.numel(), nccl_dtype(recv.dtype), root, self._h, _stream(stream)), "ncclScatter")
+        _k(self._lib.ncclScatter(sp, recv.data_ptr(), recv.numel(), nccl_dtype(recv.dtype), root, self._h, _stream(stream)), "ncclScatter")
         return recv
 
     def send(self, t: torch.Tensor, peer: int, stream=None) -> None:
-        _lib.check(self._lib.ncclSend(t.data_ptr(), t.numel(), nccl_dtype(t.dtype), peer, self._h, _stream(stream)), "ncclSend")
+        _k(self._lib.ncclSend(t.data_ptr(), t.numel(), nccl_dtype(t.dtype), peer, self._h, _stream(stream)), "ncclSend")
 
     def recv(self, t: torch.Tensor, peer: int, stream=None) -> None:
-        _lib.check(self._lib.ncclRecv(t.data_ptr(), t.numel(), nccl_dtype(t.dtype), peer, self._h, _stream(stream)), "ncclRecv")
+        _k(self._lib.ncclRecv(t.data_ptr(), t.numel(), nccl_dtype(t.dtype), peer, self._h, _stream(stream)), "ncclRecv")
 
     def group_start(self) -> None:
         _lib.check(self._lib.ncclGroupStart(), "ncclGroupStart")
@@ -218,7 +226,7 @@ class Communicator:
         _lib.check(self._lib.ncclGroupEnd(), "ncclGroupEnd")
 
     def barrier(self, stream=None) -> None:
-        _lib.check(self._lib.b200collBarrier(self._h, _stream(stream)), "b200collBarrier")
+        _k(self._lib.b200collBarrier(self._h, _stream(stream)), "b200collBarrier")
 
     def host_barrier(self) -> None:
         _lib.check(self._lib.b200collHostBarrier(self._h), "b200collHostBarrier")

@@ -67,9 +67,10 @@ ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, cudaStream_t stream, 
 }
 
 int ctasFor(const Comm* c, size_t bytes, int algo) {
-  // One CTA per 256 KiB of payload, between the communicator's bounds. The in-switch path needs
-  // fewer CTAs for the same bandwidth, which leaves SMs to whatever overlaps with it.
-  size_t per = algo == ALGO_NVLS ? (512u << 10) : (256u << 10);
+  // Mid-size messages are bound by NVLink latency, not bandwidth, so they want many CTAs with
+  // little work each: one CTA per 64 KiB (128 KiB on the in-switch path, whose loads are wider
+  // per instruction), between the communicator's bounds.
+  size_t per = algo == ALGO_NVLS ? (128u << 10) : (64u << 10);
   size_t want = (bytes + per - 1) / per;
   int hi = c->maxCtas;
   int ctas = (int)std::min<size_t>(want, (size_t)hi);
@@ -265,7 +266,8 @@ ncclResult_t enqueueColl(const CollReq& r) {
     args.stageHalf = (int)(c->stageParity & 1);
     c->stageParity += (uint32_t)plan.chunks;
     const bool nvls = plan.algo == ALGO_NVLS;
-    if (reducing) e = launchStagedReduce(r.dt, rop.base, nvls, plan.ctas, r.stream, dc, args);
+    // Reducing kernels run 256-thread CTAs, so twice as many for the same thread count.
+    if (reducing) e = launchStagedReduce(r.dt, rop.base, nvls, std::min(2 * plan.ctas, kMaxCtas), r.stream, dc, args);
     else e = launchStagedCopy(nvls && r.kind == COLL_BROADCAST, plan.ctas, r.stream, dc, args, (int)es);
   }
   if (e != cudaSuccess) {

@@ -18,6 +18,8 @@
 // is what makes reusing a half two chunks later safe without a trailing barrier.
 #pragma once
 
+#include <type_traits>
+
 #include "prims.cuh"
 #include "reduce_ops.cuh"
 
@@ -170,7 +172,7 @@ __device__ __forceinline__ void ctaCopyScaled(char* dst, const char* src, size_t
 }
 
 template <typename T, typename Op, bool NVLS>
-__global__ void __launch_bounds__(kCollThreads) kStagedReduce(const __grid_constant__ DevComm c, const __grid_constant__ CollArgs a) {
+__global__ void __launch_bounds__(kReduceThreads) kStagedReduce(const __grid_constant__ DevComm c, const __grid_constant__ CollArgs a) {
   stampBegin(c);
   using P = Pack<T>;
   using Acc = typename ElemTraits<T>::Acc;
@@ -233,62 +235,96 @@ __global__ void __launch_bounds__(kCollThreads) kStagedReduce(const __grid_const
         const size_t msgOff = isRS ? off : off + (size_t)s * su * 16;
         const size_t stOff = stageBase + sliceStage(s);
         const bool recvAligned = (((uintptr_t)(recv + (isRS ? off : msgOff))) & 15) == 0;
-        for (size_t u = lo + tid; u < hi; u += nt) {
-          uint4 out;
-          if constexpr (NVLS) {
-            const char* src = a.direct ? a.sendMc + (isRS ? (size_t)s * a.count * ES + off : msgOff) : c.wsMc + stOff;
-            out = McReduce<T>::ld(src + (u << 4));
-            if (a.scaleMode == SCALE_POST_DIV_N) {
-              Acc acc[P::N];
-              P::up(out, acc);
-#pragma unroll
-              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
-              out = P::down(acc);
-            }
-          } else {
-            uint4 v[kMaxRanks];
-#pragma unroll
-            for (int p = 0; p < kMaxRanks; p++) {
-              if (p < n) {
-                const char* src = a.direct ? a.sendPeer[p] + (isRS ? (size_t)s * a.count * ES + off : msgOff) : c.ws[p] + stOff;
-                v[p] = ldStream16(src + (u << 4));
-              }
-            }
-            Acc acc[P::N];
-#pragma unroll
-            for (int p = 0; p < kMaxRanks; p++) {
-              if (p < n) {
-                Acc x[P::N];
-                P::up(v[p], x);
-#pragma unroll
-                for (int k = 0; k < P::N; k++) {
-                  acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
-                }
-              }
-            }
-            if (a.scaleMode == SCALE_POST_DIV_N) {
-#pragma unroll
-              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
-            }
-            out = P::down(acc);
-          }
-          // Deliver.
+        // Sources and destinations of this slice.
+        const size_t srcOff = isRS ? (size_t)s * a.count * ES + off : msgOff;
+        const char* mcSrc = NVLS ? (a.direct ? a.sendMc + srcOff : c.wsMc + stOff) : nullptr;
+        char* mcDst = (NVLS && isAR) ? (a.direct ? a.recvMc + msgOff : c.wsMc + stOff) : nullptr;
+        // Peer bases come from the kernel parameters (constant bank), indexed by unrolled loops.
+        auto pSrc = [&](int p) -> const char* { return a.direct ? a.sendPeer[p] + srcOff : c.ws[p] + stOff; };
+        auto pDst = [&](int p) -> char* { return a.direct ? a.recvPeer[p] + msgOff : c.ws[p] + stOff; };
+        auto deliver = [&](size_t u, uint4 out) {
           if (isRS) {
             storeUser16<T>(recv, off + (u << 4), total, out, recvAligned);
           } else if (isAR) {
             if constexpr (NVLS) {
-              mcStore16((a.direct ? a.recvMc + msgOff : c.wsMc + stOff) + (u << 4), out);
+              mcStore16(mcDst + (u << 4), out);
             } else {
 #pragma unroll
               for (int p = 0; p < kMaxRanks; p++)
-                if (p < n) st16((a.direct ? a.recvPeer[p] + msgOff : c.ws[p] + stOff) + (u << 4), out);
+                if (p < n) st16(pDst(p) + (u << 4), out);
             }
           } else {  // Reduce
-            if constexpr (NVLS) {
-              storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
-            } else {
-              st16((a.direct ? a.recvPeer[a.root] + msgOff : c.ws[a.root] + stOff) + (u << 4), out);
+            if constexpr (NVLS) storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
+            else st16(pDst(a.root) + (u << 4), out);
+          }
+        };
+        // `UN` independent 16-byte units per thread are loaded before any is consumed, so enough
+        // NVLink requests are in flight to cover the link latency.
+        auto body = [&](auto unTag, auto maxrTag, size_t u0) {
+          constexpr int UN = decltype(unTag)::value;
+          constexpr int MAXR = decltype(maxrTag)::value;  // upper bound on the rank count
+          uint4 out[UN];
+          if constexpr (NVLS) {
+#pragma unroll
+            for (int j = 0; j < UN; j++) out[j] = McReduce<T>::ld(mcSrc + ((u0 + (size_t)j * nt) << 4));
+            if (a.scaleMode == SCALE_POST_DIV_N) {
+#pragma unroll
+              for (int j = 0; j < UN; j++) {
+                Acc acc[P::N];
+                P::up(out[j], acc);
+#pragma unroll
+                for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
+                out[j] = P::down(acc);
+              }
             }
+          } else {
+            uint4 v[UN][MAXR];
+#pragma unroll
+            for (int j = 0; j < UN; j++) {
+#pragma unroll
+              for (int p = 0; p < MAXR; p++)
+                if (p < n) v[j][p] = ldStream16(pSrc(p) + ((u0 + (size_t)j * nt) << 4));
+            }
+#pragma unroll
+            for (int j = 0; j < UN; j++) {
+              Acc acc[P::N];
+#pragma unroll
+              for (int p = 0; p < MAXR; p++) {
+                if (p < n) {
+                  Acc x[P::N];
+                  P::up(v[j][p], x);
+#pragma unroll
+                  for (int k = 0; k < P::N; k++) acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
+                }
+              }
+              if (a.scaleMode == SCALE_POST_DIV_N) {
+#pragma unroll
+                for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
+              }
+              out[j] = P::down(acc);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < UN; j++) deliver(u0 + (size_t)j * nt, out[j]);
+        };
+        size_t u = lo + tid;
+        using I1 = std::integral_constant<int, 1>;
+        using I2 = std::integral_constant<int, 2>;
+        using I4 = std::integral_constant<int, 4>;
+        using I8 = std::integral_constant<int, 8>;
+        if constexpr (NVLS) {
+          for (; u + (size_t)7 * nt < hi; u += (size_t)8 * nt) body(I8{}, I1{}, u);
+          for (; u < hi; u += nt) body(I1{}, I1{}, u);
+        } else {
+          if (n <= 2) {
+            for (; u + (size_t)3 * nt < hi; u += (size_t)4 * nt) body(I4{}, I2{}, u);
+            for (; u < hi; u += nt) body(I1{}, I2{}, u);
+          } else if (n <= 4) {
+            for (; u + (size_t)3 * nt < hi; u += (size_t)4 * nt) body(I4{}, I4{}, u);
+            for (; u < hi; u += nt) body(I1{}, I4{}, u);
+          } else {
+            for (; u + (size_t)nt < hi; u += (size_t)2 * nt) body(I2{}, I8{}, u);
+            for (; u < hi; u += nt) body(I1{}, I8{}, u);
           }
         }
       }

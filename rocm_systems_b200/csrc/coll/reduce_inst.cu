@@ -23,17 +23,17 @@ cudaError_t B200_CAT(launchStaged_, B200_TN)(int op, bool nvls, int grid, cudaSt
   if (nvls) {
 #ifdef B200_NVLS_OK
     if (op != ncclSum) return cudaErrorInvalidValue;
-    kStagedReduce<B200_T, OpSum, true><<<grid, kCollThreads, 0, s>>>(c, a);
+    kStagedReduce<B200_T, OpSum, true><<<grid, kReduceThreads, 0, s>>>(c, a);
     return cudaGetLastError();
 #else
     return cudaErrorInvalidValue;
 #endif
   }
   switch (op) {
-    case ncclSum: kStagedReduce<B200_T, OpSum, false><<<grid, kCollThreads, 0, s>>>(c, a); break;
-    case ncclProd: kStagedReduce<B200_T, OpProd, false><<<grid, kCollThreads, 0, s>>>(c, a); break;
-    case ncclMax: kStagedReduce<B200_T, OpMax, false><<<grid, kCollThreads, 0, s>>>(c, a); break;
-    case ncclMin: kStagedReduce<B200_T, OpMin, false><<<grid, kCollThreads, 0, s>>>(c, a); break;
+    case ncclSum: kStagedReduce<B200_T, OpSum, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
+    case ncclProd: kStagedReduce<B200_T, OpProd, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
+    case ncclMax: kStagedReduce<B200_T, OpMax, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
+    case ncclMin: kStagedReduce<B200_T, OpMin, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();

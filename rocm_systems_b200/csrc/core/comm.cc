@@ -182,8 +182,9 @@ ncclResult_t commCreate(Comm** out, const ncclUniqueId& id, int nranks, int rank
   d.stageBytes = solo ? (1u << 16) : fl.stageBytes;
   d.p2pOff = d.stageOff + 2 * d.stageBytes;
   d.p2pChunkBytes = solo ? 4096 : fl.p2pChunkBytes;
-  d.p2pSubs = fl.p2pCtasPerPeer;
-  d.p2pSlots = 2;
+  // Few peers: more CTAs per peer so a pair of GPUs can still fill its links.
+  d.p2pSubs = fl.p2pCtasPerPeer > 0 ? fl.p2pCtasPerPeer : (nranks <= 2 ? 8 : (nranks <= 4 ? 6 : 4));
+  d.p2pSlots = 4;
   const size_t p2pBytes = (size_t)nranks * d.p2pSubs * d.p2pSlots * d.p2pChunkBytes;
   const size_t total = d.p2pOff + p2pBytes;
   BCHECK(symAlloc(c->boot, dev, total, true, c->symTag, &c->ws));

@@ -103,7 +103,7 @@ static void load(Flags& f) {
   f.llMaxBytes &= ~(size_t)0xff;
   if (f.p2pChunkBytes < (64u << 10)) f.p2pChunkBytes = 64u << 10;
   f.p2pChunkBytes &= ~(size_t)0xfff;
-  if (f.p2pCtasPerPeer < 1) f.p2pCtasPerPeer = 1;
+  if (f.p2pCtasPerPeer < 0) f.p2pCtasPerPeer = 0;
   if (f.p2pCtasPerPeer > 8) f.p2pCtasPerPeer = 8;
   if (f.waitTimeoutMs < 1) f.waitTimeoutMs = 1;
 }

@@ -15,6 +15,7 @@ namespace b200 {
 constexpr int kMaxRanks = 8;     // one NVSwitch domain
 constexpr int kMaxCtas = 128;    // flag slots per communicator; also the CTA ceiling of a kernel
 constexpr int kCollThreads = 512;
+constexpr int kReduceThreads = 256;  // reducing kernels: fewer threads, more registers for loads in flight
 
 // ---- logging ------------------------------------------------------------------------------
 // Levels and subsystem masks follow the NCCL_DEBUG / NCCL_DEBUG_SUBSYS convention; the role of
@@ -80,8 +81,8 @@ struct Flags {
   int minCtas = 0, maxCtas = 0;  // MIN_CTAS / MAX_CTAS (0: per-collective default)
   size_t stageBytes = 64ull << 20;   // BUFFSIZE: bytes per staging half
   size_t llMaxBytes = 64ull << 10;   // LL_THRESHOLD: largest message for the flag-in-data protocol
-  size_t p2pChunkBytes = 1ull << 20; // P2P_CHUNK: bytes per send/recv FIFO slot
-  int p2pCtasPerPeer = 4;        // P2P_CTAS: CTAs per (peer, direction)
+  size_t p2pChunkBytes = 512ull << 10; // P2P_CHUNK: bytes per send/recv FIFO slot
+  int p2pCtasPerPeer = 0;        // P2P_CTAS: CTAs per (peer, direction); 0 picks by rank count
   int waitTimeoutMs = 20000;     // WAIT_TIMEOUT_MS: device-side wait budget
   int bootTimeoutMs = 120000;    // BOOTSTRAP_TIMEOUT_MS: host rendezvous budget
   std::string commId;            // COMM_ID: "ip:port" of the rendezvous root

@@ -1,0 +1,267 @@
+"""Llama-architecture decoder trained with the FSDP engine of this package.
+
+The model is a list of flat parameter units (embedding, one per layer, head). The forward and
+backward passes are driven unit by unit so that parameter all-gathers run one unit ahead of the
+compute and gradient reduce-scatters plus the optimizer run behind it, on the communication
+stream (see :mod:`rocm_systems_b200.parallel.fsdp`). GEMMs are plain library GEMMs (cuBLAS via
+``torch.mm``) with the weight gradient written straight into the unit's flat gradient buffer;
+attention is the library SDPA kernel; norms, rotary embedding, SwiGLU, the loss, the embedding
+and AdamW are this package's CUDA kernels (:mod:`rocm_systems_b200.ops.train_ops`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import train_ops as ops
+from ..parallel.fsdp import AdamWConfig, FlatUnit, FSDPEngine, ParamSpec
+
+
+@dataclass
+class LlamaConfig:
+    vocab: int = 128256
+    hidden: int = 4096
+    layers: int = 32
+    heads: int = 32
+    kv_heads: int = 8
+    ffn: int = 14336
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    seq_len: int = 4096
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+    @staticmethod
+    def llama3_8b() -> "LlamaConfig":
+        return LlamaConfig()
+
+    @staticmethod
+    def tiny(seq_len: int = 128) -> "LlamaConfig":
+        return LlamaConfig(vocab=1024, hidden=256, layers=2, heads=4, kv_heads=2, ffn=512, seq_len=seq_len)
+
+    def param_count(self) -> int:
+        d = self.head_dim
+        per_layer = self.hidden * (self.heads + 2 * self.kv_heads) * d + self.hidden * self.hidden + 3 * self.hidden * self.ffn + 2 * self.hidden
+        return 2 * self.vocab * self.hidden + self.layers * per_layer + self.hidden
+
+    def flops_per_token(self) -> float:
+        """Training FLOPs per token: 6 per parameter in the GEMMs plus causal attention."""
+        d = self.head_dim
+        gemm_params = self.layers * (self.hidden * (self.heads + 2 * self.kv_heads) * d + self.hidden * self.hidden + 3 * self.hidden * self.ffn) + self.vocab * self.hidden
+        attn = self.layers * 6 * self.seq_len * self.hidden  # 2*S*H fwd for QK^T and PV, halved by causality, x3 for fwd+bwd
+        return 6.0 * gemm_params + attn
+
+
+class _LinearWG(torch.autograd.Function):
+    """``y = x @ w.T`` whose backward writes dW into ``w.grad_view`` (a slice of the unit's flat
+    gradient buffer) instead of returning a fresh tensor: no accumulate pass over the weights."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return torch.mm(x, w.t())
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy if dy.is_contiguous() else dy.contiguous()
+        dx = torch.mm(dy, w)
+        gv = getattr(w, "grad_view", None)
+        if gv is None:
+            return dx, torch.mm(dy.t(), x)
+        if getattr(w, "grad_accumulate", False):
+            gv.addmm_(dy.t(), x)
+        else:
+            torch.mm(dy.t(), x, out=gv)
+            w.grad_accumulate = True
+        return dx, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return _LinearWG.apply(x, w)
+
+
+def layer_specs(cfg: LlamaConfig) -> List[ParamSpec]:
+    d = cfg.head_dim
+    return [
+        ParamSpec("attn_norm", (cfg.hidden,), "ones"),
+        ParamSpec("wqkv", ((cfg.heads + 2 * cfg.kv_heads) * d, cfg.hidden), std=cfg.init_std),
+        ParamSpec("wo", (cfg.hidden, cfg.heads * d), std=cfg.init_std),
+        ParamSpec("mlp_norm", (cfg.hidden,), "ones"),
+        ParamSpec("w13", (2 * cfg.ffn, cfg.hidden), std=cfg.init_std),  # gate rows then up rows
+        ParamSpec("w2", (cfg.hidden, cfg.ffn), std=cfg.init_std),
+    ]
+
+
+def layer_forward(p: dict, x: torch.Tensor, cfg: LlamaConfig, rope: torch.Tensor, batch: int) -> torch.Tensor:
+    """One decoder layer on ``x`` [T, H] (T = batch * seq)."""
+    T = x.shape[0]
+    S = T // batch
+    d, nh, nkv = cfg.head_dim, cfg.heads, cfg.kv_heads
+    h = ops.rmsnorm(x, p["attn_norm"], cfg.eps)
+    qkv = linear(h, p["wqkv"]).view(T, nh + 2 * nkv, d)
+    qkv = ops.rope_(qkv, rope, nh + nkv)
+    q4 = qkv.view(batch, S, nh + 2 * nkv, d)
+    q = q4[:, :, :nh].transpose(1, 2)
+    k = q4[:, :, nh:nh + nkv].transpose(1, 2)
+    v = q4[:, :, nh + nkv:].transpose(1, 2)
+    a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=nkv != nh)
+    a = a.transpose(1, 2).reshape(T, nh * d)
+    x = x + linear(a, p["wo"])
+    h = ops.rmsnorm(x, p["mlp_norm"], cfg.eps)
+    x = x + linear(ops.swiglu(linear(h, p["w13"])), p["w2"])
+    return x
+
+
+class LlamaTrainer:
+    """The public training API: ``loss = trainer.step(tokens, targets)`` with host tensors in
+    pinned memory or device tensors; ``loss`` is a host float when ``return_loss`` is set."""
+
+    def __init__(self, cfg: LlamaConfig, comm=None, device: Optional[torch.device] = None, opt: Optional[AdamWConfig] = None,
+                 seed: int = 0, fused_rs: bool = True):
+        self.cfg = cfg
+        self.comm = comm
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        rank = comm.rank if comm is not None else 0
+        world = comm.nranks if comm is not None else 1
+        self.rank, self.world = rank, world
+        with torch.cuda.device(self.device):
+            units: List[FlatUnit] = []
+            units.append(FlatUnit("embed", [ParamSpec("tok", (cfg.vocab, cfg.hidden), std=cfg.init_std)], rank, world, self.device, seed))
+            for i in range(cfg.layers):
+                units.append(FlatUnit(f"layer{i}", layer_specs(cfg), rank, world, self.device, seed + 1 + i))
+            units.append(FlatUnit("head", [ParamSpec("norm", (cfg.hidden,), "ones"), ParamSpec("out", (cfg.vocab, cfg.hidden), std=cfg.init_std)],
+                                  rank, world, self.device, seed + 1 + cfg.layers))
+            self.engine = FSDPEngine(comm, units, opt or AdamWConfig(), fused_rs=fused_rs)
+            self.rope = ops.rope_table(cfg.seq_len, cfg.head_dim, cfg.rope_theta, self.device)
+        self.embed, self.layers, self.head = units[0], units[1:-1], units[-1]
+        self._tok_dev: Optional[torch.Tensor] = None
+        self._tgt_dev: Optional[torch.Tensor] = None
+        self._loss_host = torch.zeros(1, dtype=torch.float32).pin_memory() if torch.cuda.is_available() else torch.zeros(1)
+
+    # ---- one optimisation step ---------------------------------------------------------------------
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor, return_loss: bool = True):
+        cfg, eng = self.cfg, self.engine
+        with torch.cuda.device(self.device):
+            if not tokens.is_cuda:
+                if self._tok_dev is None or self._tok_dev.shape != tokens.shape:
+                    self._tok_dev = torch.empty(tokens.shape, dtype=torch.int64, device=self.device)
+                    self._tgt_dev = torch.empty(targets.shape, dtype=torch.int64, device=self.device)
+                self._tok_dev.copy_(tokens, non_blocking=True)
+                self._tgt_dev.copy_(targets, non_blocking=True)
+                tokens, targets = self._tok_dev, self._tgt_dev
+            batch, S = tokens.shape
+            T = batch * S
+            tok = tokens.reshape(T)
+            tgt = targets.reshape(T)
+
+            # ---- forward ----
+            eng.wait_params(self.embed)
+            eng.prefetch(self.layers[0])
+            x = ops.embedding(tok, self.embed.params["tok"])
+            if eng.reshard:
+                eng.release(self.embed)
+            inputs, outputs = [], []
+            units = self.layers
+            for i, u in enumerate(units):
+                eng.wait_params(u)
+                eng.prefetch(units[i + 1] if i + 1 < len(units) else self.head)
+                xin = x.detach().requires_grad_(True)
+                with torch.enable_grad():
+                    y = layer_forward(u.params, xin, cfg, self.rope, batch)
+                inputs.append(xin)
+                outputs.append(y)
+                x = y
+                if eng.reshard and i + 1 < len(units):
+                    eng.release(u)
+
+            # ---- head: norm, logits, loss and logit gradient in place, then back through the head ----
+            eng.wait_params(self.head)
+            hin = x.detach().requires_grad_(True)
+            with torch.enable_grad():
+                hn = ops.rmsnorm(hin, self.head.params["norm"], cfg.eps)
+            w_out = self.head.params["out"]
+            logits = torch.mm(hn.detach(), w_out.t())
+            loss_rows = ops.cross_entropy_inplace(logits, tgt, 1.0 / T)
+            loss = loss_rows.mean()
+            eng.alloc_grad(self.head)
+            dhn = torch.mm(logits, w_out.detach())
+            torch.mm(logits.t(), hn.detach(), out=self.head.grad_view("out"))
+            del logits
+            self.head.params["norm"].grad = None
+            torch.autograd.backward(hn, dhn)
+            self.head.grad_view("norm").copy_(self.head.params["norm"].grad)
+            self.head.params["norm"].grad = None
+            g = hin.grad
+            eng.reduce_and_step(self.head)
+            if eng.reshard:
+                eng.release(self.head)
+
+            # ---- backward through the layers, last to first ----
+            for i in range(len(units) - 1, -1, -1):
+                u = units[i]
+                eng.wait_params(u)
+                if i > 0:
+                    eng.prefetch(units[i - 1])
+                eng.alloc_grad(u)
+                for name, prm in u.params.items():
+                    prm.grad = None
+                    if prm.dim() == 2:
+                        prm.grad_view = u.grad_view(name)
+                        prm.grad_accumulate = False
+                torch.autograd.backward(outputs[i], g)
+                for name, prm in u.params.items():
+                    if prm.dim() == 1:
+                        u.grad_view(name).copy_(prm.grad)
+                        prm.grad = None
+                    else:
+                        prm.grad_view = None
+                g = inputs[i].grad
+                outputs[i] = None
+                inputs[i] = None
+                eng.reduce_and_step(u)
+                if eng.reshard:
+                    eng.release(u)
+
+            # ---- embedding gradient (fp32, rows repeat) ----
+            dtable = torch.zeros(self.embed.padded, dtype=torch.float32, device=self.device)
+            ops.embedding_bwd_(tok, g, dtable[: cfg.vocab * cfg.hidden].view(cfg.vocab, cfg.hidden))
+            eng.reduce_and_step(self.embed, fp32_full_grad=dtable)
+            eng.prefetch(self.embed)  # next step starts with it
+            eng.finish_step()
+            if return_loss:
+                self._loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                return float(self._loss_host.item())
+            return loss
+
+    def eval_loss(self, tokens: torch.Tensor, targets: torch.Tensor) -> float:
+        """Forward only (no update); used by tests to watch the loss go down."""
+        cfg, eng = self.cfg, self.engine
+        with torch.cuda.device(self.device), torch.no_grad():
+            tokens, targets = tokens.to(self.device), targets.to(self.device)
+            batch, S = tokens.shape
+            eng.wait_params(self.embed)
+            x = ops.embedding(tokens.reshape(-1), self.embed.params["tok"])
+            for u in self.layers:
+                eng.wait_params(u)
+                x = layer_forward(u.params, x, cfg, self.rope, batch)
+                if eng.reshard:
+                    eng.release(u)
+            eng.wait_params(self.head)
+            hn = ops.rmsnorm(x, self.head.params["norm"], cfg.eps)
+            logits = torch.mm(hn, self.head.params["out"].t())
+            out = float(F.cross_entropy(logits.float(), targets.reshape(-1)).item())
+            if eng.reshard:
+                eng.release(self.head)
+                eng.release(self.embed)
+            return out
+
+    def memory_summary(self) -> dict:
+        return {"allocated_gb": torch.cuda.memory_allocated(self.device) / 2 ** 30, "peak_gb": torch.cuda.max_memory_allocated(self.device) / 2 ** 30}

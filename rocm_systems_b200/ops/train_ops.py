@@ -1,0 +1,181 @@
+"""Torch-facing wrappers of the hand-written training kernels (``csrc/fused/train_ops.cu``).
+
+Each op calls the exported C symbol with raw device pointers on the current CUDA stream. There is
+no eager-PyTorch fallback: on a machine with a GPU the kernels must be there, and a missing
+library raises at import of :mod:`rocm_systems_b200._lib`.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from .. import _lib
+
+LAUNCHES = 0  # kernels of this package launched through this module (bench.py reports it)
+
+_sigs_done = False
+
+
+def _lib_ops():
+    global _sigs_done
+    lib = _lib.load()
+    if not _sigs_done:
+        vp, ll, i32, f32 = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+        lib.b200ops_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, ll, i32, f32, vp]
+        lib.b200ops_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ll, i32, vp]
+        lib.b200ops_rope.argtypes = [vp, vp, ll, i32, i32, i32, i32, f32, vp]
+        lib.b200ops_swiglu_fwd.argtypes = [vp, vp, ll, i32, vp]
+        lib.b200ops_swiglu_bwd.argtypes = [vp, vp, vp, ll, i32, vp]
+        lib.b200ops_cross_entropy.argtypes = [vp, vp, vp, ll, i32, ll, f32, vp]
+        lib.b200ops_adamw.argtypes = [vp, vp, vp, vp, vp, ll, f32, f32, f32, f32, f32, i32, f32, vp]
+        lib.b200ops_embedding_fwd.argtypes = [vp, vp, vp, ll, i32, vp]
+        lib.b200ops_embedding_bwd.argtypes = [vp, vp, vp, ll, i32, vp]
+        lib.b200ops_cast_scale.argtypes = [vp, vp, ll, f32, i32, vp]
+        _sigs_done = True
+    return lib
+
+
+def _s() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ck(rc: int, what: str) -> None:
+    global LAUNCHES
+    if rc != 0:
+        raise RuntimeError(f"{what}: CUDA error {rc}")
+    LAUNCHES += 1
+
+
+def _bf16c(t: torch.Tensor) -> torch.Tensor:
+    assert t.is_cuda and t.dtype == torch.bfloat16, "bf16 CUDA tensor expected"
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# ---- RMSNorm ---------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x = _bf16c(x)
+        H = x.shape[-1]
+        T = x.numel() // H
+        y = torch.empty_like(x)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        _ck(_lib_ops().b200ops_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), T, H, eps, _s()), "rmsnorm_fwd")
+        ctx.save_for_backward(x, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dy = _bf16c(dy)
+        H = x.shape[-1]
+        T = x.numel() // H
+        dx = torch.empty_like(x)
+        dw = torch.zeros(H, dtype=torch.float32, device=x.device)
+        _ck(_lib_ops().b200ops_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), T, H, _s()), "rmsnorm_bwd")
+        return dx, dw.to(w.dtype), None
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    return _RMSNorm.apply(x, w, eps)
+
+
+# ---- rotary embedding ----------------------------------------------------------------------------------
+def rope_table(seq_len: int, head_dim: int, theta: float, device) -> torch.Tensor:
+    """[S, D/2, 2] float32 of (cos, sin) for positions 0..S-1 (rotate-half convention)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.outer(torch.arange(seq_len, dtype=torch.float64), inv)
+    return torch.stack([ang.cos(), ang.sin()], dim=-1).to(torch.float32).to(device).contiguous()
+
+
+class _Rope(torch.autograd.Function):
+    """Rotates the first ``heads`` heads of each token row of ``qkv`` ([T, total_heads, D])."""
+
+    @staticmethod
+    def forward(ctx, qkv, table, heads):
+        assert qkv.dtype == torch.bfloat16
+        out = qkv.clone(memory_format=torch.contiguous_format)
+        T, total, D = out.shape
+        ctx.table, ctx.heads = table, heads
+        _ck(_lib_ops().b200ops_rope(out.data_ptr(), table.data_ptr(), T, heads, D, total * D, table.shape[0], 1.0, _s()), "rope_fwd")
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.clone(memory_format=torch.contiguous_format)  # the inverse rotation runs in place on the copy
+        T, total, D = g.shape
+        _ck(_lib_ops().b200ops_rope(g.data_ptr(), ctx.table.data_ptr(), T, ctx.heads, D, total * D, ctx.table.shape[0], -1.0, _s()), "rope_bwd")
+        return g, None, None
+
+
+def rope_(qkv: torch.Tensor, table: torch.Tensor, heads: int) -> torch.Tensor:
+    return _Rope.apply(qkv, table, heads)
+
+
+# ---- SwiGLU -----------------------------------------------------------------------------------------------
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        gu = _bf16c(gu)
+        F = gu.shape[-1] // 2
+        T = gu.numel() // (2 * F)
+        out = torch.empty(*gu.shape[:-1], F, dtype=gu.dtype, device=gu.device)
+        _ck(_lib_ops().b200ops_swiglu_fwd(gu.data_ptr(), out.data_ptr(), T, F, _s()), "swiglu_fwd")
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        dout = _bf16c(dout)
+        F = gu.shape[-1] // 2
+        T = gu.numel() // (2 * F)
+        dgu = torch.empty_like(gu)
+        _ck(_lib_ops().b200ops_swiglu_bwd(gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), T, F, _s()), "swiglu_bwd")
+        return dgu
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """``silu(gu[..., :F]) * gu[..., F:]`` for a fused gate/up projection output."""
+    return _SwiGLU.apply(gu)
+
+
+# ---- loss, optimizer, embedding, casts (no autograd: the engine calls them explicitly) ---------------------
+def cross_entropy_inplace(logits: torch.Tensor, targets: torch.Tensor, grad_scale: float) -> torch.Tensor:
+    """Per-row loss of ``logits`` [T, V] (bf16); ``logits`` is overwritten with d(loss)/d(logits) * grad_scale."""
+    assert logits.dtype == torch.bfloat16 and logits.dim() == 2 and logits.stride(1) == 1
+    assert targets.dtype == torch.int64 and targets.is_contiguous()
+    T, V = logits.shape
+    loss = torch.empty(T, dtype=torch.float32, device=logits.device)
+    _ck(_lib_ops().b200ops_cross_entropy(logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), T, V, logits.stride(0), grad_scale, _s()), "cross_entropy")
+    return loss
+
+
+def adamw_(master, m, v, grad, param, lr, betas, eps, weight_decay, step, grad_scale=1.0) -> None:
+    n = master.numel()
+    assert m.numel() == n and v.numel() == n and grad.numel() == n and param.numel() == n
+    assert master.dtype == torch.float32 and grad.dtype == torch.float32 and param.dtype == torch.bfloat16
+    _ck(_lib_ops().b200ops_adamw(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(), param.data_ptr(), n, lr, betas[0], betas[1], eps,
+                                 weight_decay, step, grad_scale, _s()), "adamw")
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    assert tokens.dtype == torch.int64 and table.dtype == torch.bfloat16 and table.is_contiguous()
+    tokens = tokens.contiguous()
+    H = table.shape[1]
+    out = torch.empty(*tokens.shape, H, dtype=table.dtype, device=table.device)
+    _ck(_lib_ops().b200ops_embedding_fwd(tokens.data_ptr(), table.data_ptr(), out.data_ptr(), tokens.numel(), H, _s()), "embedding_fwd")
+    return out
+
+
+def embedding_bwd_(tokens: torch.Tensor, dout: torch.Tensor, dtable_f32: torch.Tensor) -> None:
+    dout = _bf16c(dout)
+    H = dtable_f32.shape[1]
+    _ck(_lib_ops().b200ops_embedding_bwd(tokens.contiguous().data_ptr(), dout.data_ptr(), dtable_f32.data_ptr(), tokens.numel(), H, _s()), "embedding_bwd")
+
+
+def cast_scale_(src_bf16: torch.Tensor, dst_f32: torch.Tensor, scale: float, accumulate: bool = False) -> None:
+    assert src_bf16.numel() == dst_f32.numel() and src_bf16.is_contiguous() and dst_f32.is_contiguous()
+    _ck(_lib_ops().b200ops_cast_scale(src_bf16.data_ptr(), dst_f32.data_ptr(), src_bf16.numel(), scale, int(accumulate), _s()), "cast_scale")

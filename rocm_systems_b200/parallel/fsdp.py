@@ -1,0 +1,206 @@
+"""Fully-sharded data parallelism (ZeRO-3) over the native communicator.
+
+Each *unit* (a transformer layer, the embedding, the head) owns one flat bf16 parameter buffer.
+Every rank keeps 1/N of it (its shard) together with the fp32 master copy and both AdamW moments
+of that shard. Around the compute of a unit the engine
+
+* all-gathers the bf16 shards into the unit's full flat buffer on a communication stream, one
+  unit ahead of the compute stream (prefetch), and frees the buffer afterwards;
+* reduce-scatters the unit's flat bf16 gradient into an fp32 gradient shard, scaled by 1/N, on
+  the communication stream while the compute stream runs the backward of the previous unit;
+* applies AdamW to the shard right behind the reduce-scatter (optimizer-in-backward), which
+  updates the fp32 master weights, both moments and the bf16 shard in one kernel.
+
+With one rank the gather and the scatter disappear: the full buffer *is* the shard.
+The reference has no training-side parallelism at all; this implements the FSDP/ZeRO-3 configuration
+of the benchmark on the collective library in this package.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import train_ops as ops
+
+ALIGN = 8  # elements: every parameter starts on a 16-byte boundary inside the flat buffer
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: Tuple[int, ...]
+    init: str = "normal"  # "normal" (std below) or "ones"
+    std: float = 0.02
+
+    @property
+    def numel(self) -> int:
+        return int(math.prod(self.shape))
+
+
+@dataclass
+class AdamWConfig:
+    lr: float = 3e-4
+    betas: Tuple[float, float] = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+
+
+class FlatUnit:
+    def __init__(self, name: str, specs: Sequence[ParamSpec], rank: int, world: int, device, seed: int):
+        self.name, self.specs, self.rank, self.world, self.device = name, list(specs), rank, world, device
+        offs, o = {}, 0
+        for s in self.specs:
+            offs[s.name] = o
+            o += (s.numel + ALIGN - 1) // ALIGN * ALIGN
+        self.offsets = offs
+        self.numel = o
+        per = (o + world - 1) // world
+        self.shard_numel = (per + ALIGN - 1) // ALIGN * ALIGN
+        self.padded = self.shard_numel * world
+        # Same full-precision initial values on every rank, then keep only this rank's slice.
+        g = torch.Generator(device=device).manual_seed(seed)
+        lo, hi = rank * self.shard_numel, (rank + 1) * self.shard_numel
+        master = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
+        for s in self.specs:
+            a, b = offs[s.name], offs[s.name] + s.numel
+            if s.init == "ones":
+                vals = torch.ones(s.numel, dtype=torch.float32, device=device)
+            else:
+                vals = torch.randn(s.numel, dtype=torch.float32, device=device, generator=g) * s.std
+            i0, i1 = max(a, lo), min(b, hi)
+            if i0 < i1:
+                master[i0 - lo:i1 - lo] = vals[i0 - a:i1 - a]
+            del vals
+        self.master = master
+        self.m = torch.zeros_like(master)
+        self.v = torch.zeros_like(master)
+        self.shard = master.to(torch.bfloat16)
+        self.grad_shard: Optional[torch.Tensor] = None
+        if world == 1:
+            self.full = self.shard  # no gather needed
+        else:
+            self.full = torch.empty(self.padded, dtype=torch.bfloat16, device=device)
+            self.full.untyped_storage().resize_(0)
+        self.gathered = world == 1
+        self.gather_event: Optional[torch.cuda.Event] = None
+        self.full_grad: Optional[torch.Tensor] = None
+        # Leaf tensors viewing the full buffer; they survive storage resizes.
+        self.params: Dict[str, torch.Tensor] = {}
+        for s in self.specs:
+            v = self.full.detach()[offs[s.name]:offs[s.name] + s.numel].view(*s.shape)
+            v.requires_grad_(True)
+            self.params[s.name] = v
+
+    def grad_view(self, name: str) -> torch.Tensor:
+        s = next(sp for sp in self.specs if sp.name == name)
+        o = self.offsets[name]
+        return self.full_grad[o:o + s.numel].view(*s.shape)
+
+    @property
+    def nbytes_full(self) -> int:
+        return self.padded * 2
+
+
+class FSDPEngine:
+    """Owns the units, the communication stream and the schedule primitives."""
+
+    def __init__(self, comm, units: List[FlatUnit], opt: AdamWConfig, reshard_after_forward: bool = True, fused_rs: bool = True):
+        self.comm, self.units, self.opt = comm, units, opt
+        self.world = comm.nranks if comm is not None else 1
+        self.rank = comm.rank if comm is not None else 0
+        self.reshard = reshard_after_forward and self.world > 1
+        self.comm_stream = torch.cuda.Stream(priority=-1)
+        self.step_count = 0
+        self.fused_rs = fused_rs
+        self._pending: List[torch.cuda.Event] = []
+
+    # ---- parameters -----------------------------------------------------------------------------
+    def prefetch(self, unit: FlatUnit) -> None:
+        """Start the all-gather of ``unit`` on the communication stream (no-op when gathered)."""
+        if unit.gathered:
+            return
+        unit.full.untyped_storage().resize_(unit.nbytes_full)
+        self.comm_stream.wait_stream(torch.cuda.current_stream())  # the memory may be recycled compute memory
+        with torch.cuda.stream(self.comm_stream):
+            self.comm.all_gather(unit.shard, unit.full, stream=self.comm_stream)
+            ev = torch.cuda.Event()
+            ev.record(self.comm_stream)
+        unit.gather_event = ev
+        unit.gathered = True
+
+    def wait_params(self, unit: FlatUnit) -> None:
+        """Make the compute stream wait until ``unit``'s parameters are in place."""
+        if not unit.gathered:
+            self.prefetch(unit)
+        if unit.gather_event is not None:
+            torch.cuda.current_stream().wait_event(unit.gather_event)
+            unit.gather_event = None
+
+    def release(self, unit: FlatUnit) -> None:
+        """Free the full parameter buffer (the shard stays)."""
+        if self.world == 1 or not unit.gathered:
+            return
+        unit.full.untyped_storage().resize_(0)
+        unit.gathered = False
+
+    # ---- gradients --------------------------------------------------------------------------------
+    def alloc_grad(self, unit: FlatUnit) -> None:
+        unit.full_grad = torch.zeros(unit.padded, dtype=torch.bfloat16, device=unit.device)
+
+    def reduce_and_step(self, unit: FlatUnit, fp32_full_grad: Optional[torch.Tensor] = None) -> None:
+        """Reduce-scatter ``unit``'s gradient (mean over ranks) into fp32 and apply AdamW to the
+        shard, all on the communication stream behind the compute already queued."""
+        o = self.opt
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.comm_stream.wait_event(ev)
+        src = fp32_full_grad if fp32_full_grad is not None else unit.full_grad
+        with torch.cuda.stream(self.comm_stream):
+            gshard = torch.empty(unit.shard_numel, dtype=torch.float32, device=unit.device)
+            if fp32_full_grad is not None:
+                if self.world == 1:
+                    gshard = fp32_full_grad[:unit.shard_numel]
+                else:
+                    self.comm.reduce_scatter(fp32_full_grad, gshard, op="avg", stream=self.comm_stream)
+            elif self.world == 1:
+                ops.cast_scale_(unit.full_grad[:unit.shard_numel], gshard, 1.0)
+            elif self.fused_rs:
+                from ..ops import comm_ops
+
+                comm_ops.reduce_scatter_cast(self.comm, unit.full_grad, gshard, 1.0 / self.world, stream=self.comm_stream)
+            else:
+                tmp = torch.empty(unit.shard_numel, dtype=torch.bfloat16, device=unit.device)
+                self.comm.reduce_scatter(unit.full_grad, tmp, op="avg", stream=self.comm_stream)
+                ops.cast_scale_(tmp, gshard, 1.0)
+            ops.adamw_(unit.master, unit.m, unit.v, gshard, unit.shard, o.lr, o.betas, o.eps, o.weight_decay, self.step_count + 1)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+        src.record_stream(self.comm_stream)
+        unit.full_grad = None
+        self._pending.append(done)
+
+    def finish_step(self) -> None:
+        """Join the communication stream: after this the shards hold the updated weights."""
+        cur = torch.cuda.current_stream()
+        for ev in self._pending:
+            cur.wait_event(ev)
+        self._pending.clear()
+        self.step_count += 1
+
+    # ---- checkpoint ---------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "world": self.world, "rank": self.rank,
+                "units": {u.name: {"master": u.master.cpu(), "m": u.m.cpu(), "v": u.v.cpu()} for u in self.units}}
+
+    def load_state_dict(self, sd: dict) -> None:
+        assert sd["world"] == self.world and sd["rank"] == self.rank, "sharded checkpoint belongs to another layout"
+        self.step_count = sd["step"]
+        for u in self.units:
+            s = sd["units"][u.name]
+            u.master.copy_(s["master"])
+            u.m.copy_(s["m"])
+            u.v.copy_(s["v"])
+            u.shard.copy_(u.master.to(torch.bfloat16))
