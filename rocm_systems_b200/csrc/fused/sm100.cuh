@@ -1,0 +1,146 @@
+// Blackwell (sm_100a) building blocks in inline PTX: mbarriers with bounded waits, TMA tile loads
+// (never with cluster multicast), tcgen05 tensor-memory allocation, UMMA descriptors, MMA issue,
+// commit and accumulator loads. Used by the GEMM and the fused GEMM+collective kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace b200 {
+namespace sm100 {
+
+__device__ __forceinline__ uint32_t smemAddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool electOne() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ---- mbarrier ----------------------------------------------------------------------------------
+__device__ __forceinline__ void mbarInit(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fenceBarrierInit() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbarArrive(uint64_t* bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbarArriveExpectTx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smemAddr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll already blocks for a hardware-defined
+// time slice), sets *err and returns false. Callers then drain and leave.
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile int* err, int code, uint32_t limit = 4000000u) {
+  for (uint32_t i = 0; i < limit; i++) {
+    if (mbarTryWait(bar, parity)) return true;
+    if ((i & 0x3ff) == 0x3ff && *err) return false;
+  }
+  atomicCAS((int*)err, 0, code);
+  return false;
+}
+
+// ---- TMA ------------------------------------------------------------------------------------------
+// 2-D tile load, global -> shared, completion counted in bytes on `bar`. x is the innermost
+// coordinate (elements) and must keep x * sizeof(element) a multiple of 16 bytes.
+__device__ __forceinline__ void tmaLoad2d(void* smemDst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smemAddr(smemDst)),
+               "l"(map), "r"(x), "r"(y), "r"(smemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmaStore2d(const CUtensorMap* map, const void* smemSrc, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smemAddr(smemSrc)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tmaStoreCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tmaStoreWaitRead0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void prefetchTensorMap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- tensor memory -----------------------------------------------------------------------------------
+// One whole warp allocates `cols` (power of two >= 32) columns; the base address lands in smem.
+__device__ __forceinline__ void tmemAlloc(uint32_t* smemOut, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(smemOut)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemDealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// ---- UMMA descriptors -----------------------------------------------------------------------------------
+// Shared-memory operand descriptor for a K-major tile whose rows are 128 bytes (64 bf16 / 128 fp8)
+// laid out by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smemDescSw128(uint32_t smemByteAddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smemByteAddr & 0x3ffff) >> 4);        // start address, 16-byte units
+  d |= (uint64_t)0 << 16;                                // leading-dimension byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride between 8-row groups
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                                // layout: SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D fp32; A, B of the given format (kind::f16: 0 fp16, 1 bf16;
+// kind::f8f6f4: 0 e4m3, 1 e5m2), both K-major, no negation, dense.
+__host__ __device__ constexpr uint32_t instrDesc(uint32_t M, uint32_t N, uint32_t abFormat) {
+  return (1u << 4) | (abFormat << 7) | (abFormat << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.
+__device__ __forceinline__ void mmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmemD),
+      "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mmaF8(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmemD),
+      "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on `bar` once every MMA this thread issued so far has finished.
+__device__ __forceinline__ void mmaCommit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets row (lane base + t).
+__device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace sm100
+}  // namespace b200

@@ -1,0 +1,79 @@
+/*
+ * b200shmem — OpenSHMEM-style symmetric heap and device-initiated communication on top of a
+ * b200coll communicator. Host API in this header; the device API (put/get, signals, atomics,
+ * barrier, callable from inside any CUDA kernel) is in b200coll/shmem_device.cuh.
+ *
+ * The reference snapshot holds no rocSHMEM source; what it has are the primitives such a layer
+ * stands on: peer-mapped IPC memory (rocr-runtime/runtime/hsa-runtime/core/runtime/runtime.cpp:1199-1545),
+ * cross-process signals (core/runtime/ipc_signal.cpp:71-91) and 64-bit signal atomics with four
+ * memory orders (core/runtime/default_signal.cpp:57-250). Here the heap is one symmetric VMM
+ * allocation mapped by every PE (plus its NVSwitch multicast alias), signals are 64-bit words in
+ * that heap, and every wait carries a time budget after which it returns a status instead of
+ * spinning on.
+ */
+#ifndef B200COLL_SHMEM_H_
+#define B200COLL_SHMEM_H_
+
+#include "b200coll/nccl.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200SHMEM_MAX_PES 8
+
+/* What a kernel needs to talk to its peers; passed by value as a kernel argument. */
+typedef struct b200shmem_dev {
+  int pe, npes;
+  char* heap[B200SHMEM_MAX_PES];  /* this PE's mapping of every PE's heap; heap[pe] is local */
+  char* heapMc;                   /* multicast alias of the heap (multimem.* only), or NULL */
+  unsigned long long heapBytes;
+  unsigned long long* syncFlags;  /* local: [B200SHMEM_MAX_PES] arrival words of barrier_all, inside the heap */
+  unsigned long long* syncEpoch;  /* local device memory: barriers completed so far */
+  int* status;                    /* local device memory: first failed wait (0 none) */
+  unsigned long long timeoutNs;   /* budget of every device-side wait */
+} b200shmem_dev_t;
+
+typedef struct b200shmem_ctx* b200shmem_ctx_t;
+
+enum { B200SHMEM_CMP_EQ = 0, B200SHMEM_CMP_NE, B200SHMEM_CMP_GT, B200SHMEM_CMP_GE, B200SHMEM_CMP_LT, B200SHMEM_CMP_LE };
+enum { B200SHMEM_SIGNAL_SET = 0, B200SHMEM_SIGNAL_ADD = 1 };
+enum { B200SHMEM_OK = 0, B200SHMEM_TIMEOUT = 1 };
+
+/* Collective over `comm`: reserve a symmetric heap of `heapBytes` on every PE. */
+ncclResult_t b200shmem_init(ncclComm_t comm, size_t heapBytes, b200shmem_ctx_t* ctx);
+ncclResult_t b200shmem_finalize(b200shmem_ctx_t ctx);
+int b200shmem_my_pe(b200shmem_ctx_t ctx);
+int b200shmem_n_pes(b200shmem_ctx_t ctx);
+/* Symmetric allocation: every PE must make the same sequence of malloc/free calls, which is what
+ * makes offsets agree (the OpenSHMEM rule). Returns NULL when the heap is exhausted. */
+void* b200shmem_malloc(b200shmem_ctx_t ctx, size_t size);
+void* b200shmem_align(b200shmem_ctx_t ctx, size_t alignment, size_t size);
+void b200shmem_free(b200shmem_ctx_t ctx, void* ptr);
+/* Address through which this PE reaches `pe`'s copy of a symmetric object. */
+void* b200shmem_ptr(b200shmem_ctx_t ctx, const void* ptr, int pe);
+void* b200shmem_mc_ptr(b200shmem_ctx_t ctx, const void* ptr);
+ncclResult_t b200shmem_device_ctx(b200shmem_ctx_t ctx, b200shmem_dev_t* out);
+/* Stream-ordered host-initiated operations. */
+ncclResult_t b200shmem_putmem_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
+ncclResult_t b200shmem_getmem_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
+ncclResult_t b200shmem_putmem_signal_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, unsigned long long* sigAddr,
+                                               unsigned long long signal, int sigOp, int pe, cudaStream_t stream);
+ncclResult_t b200shmem_signal_wait_until_on_stream(b200shmem_ctx_t ctx, unsigned long long* sigAddr, int cmp, unsigned long long value,
+                                                   cudaStream_t stream);
+ncclResult_t b200shmem_barrier_all_on_stream(b200shmem_ctx_t ctx, cudaStream_t stream);
+/* First device-side wait that ran out of budget since the last call (B200SHMEM_OK if none); synchronises the device. */
+int b200shmem_take_status(b200shmem_ctx_t ctx);
+
+/* Self-checks that run device-initiated traffic from inside kernels (used by the tests):
+ * ring: every PE puts `count` words to its right neighbour with put+signal, waits for its own
+ * signal, and verifies; atomics: every PE does fetch-add/compare-swap/and/or/xor/swap rounds on
+ * PE 0's words. Return the number of mismatches in *errors. */
+ncclResult_t b200shmem_selftest_ring(b200shmem_ctx_t ctx, size_t count, int rounds, cudaStream_t stream, int* errors);
+ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStream_t stream, int* errors);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200COLL_SHMEM_H_ */

@@ -1,0 +1,328 @@
+// b200shmem host API and the kernels behind its stream-ordered operations and self-tests.
+#include <map>
+#include <mutex>
+
+#include "../coll/launch.h"
+#include "../core/comm.h"
+#include "b200coll/shmem.h"
+#include "b200coll/shmem_device.cuh"
+
+using namespace b200;
+
+struct b200shmem_ctx {
+  Comm* comm = nullptr;
+  char* heap = nullptr;          // local base of the symmetric window
+  size_t heapBytes = 0;
+  b200shmem_dev_t dev{};
+  void* devState = nullptr;      // syncEpoch (u64) + status (int) in local device memory
+  std::mutex mu;
+  std::map<size_t, size_t> freeList;   // offset -> size
+  std::map<size_t, size_t> live;       // offset -> size
+};
+
+namespace {
+
+constexpr size_t kReserved = 4096;  // head of the heap: barrier arrival words
+constexpr size_t kAlign = 256;
+
+__global__ void kSignal(b200shmem_dev_t d, unsigned long long* sig, unsigned long long value, int op, int pe) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    b200shmem::signal_op(d, sig, value, op, pe);
+  }
+}
+__global__ void kSignalWait(b200shmem_dev_t d, const unsigned long long* sig, int cmp, unsigned long long value) {
+  if (threadIdx.x == 0) b200shmem::signal_wait_until(d, sig, cmp, value);
+}
+__global__ void kBarrierAll(b200shmem_dev_t d) { b200shmem::barrier_all_block(d); }
+
+// Ring exchange driven entirely from the device: put+signal to the right neighbour, wait for
+// the left neighbour's signal, verify, barrier, repeat.
+__global__ void kSelftestRing(b200shmem_dev_t d, unsigned long long* data /*[2][count]*/, unsigned long long* src, unsigned long long* sig /*[2]*/,
+                              size_t count, int rounds, int* errors) {
+  const int right = (d.pe + 1) % d.npes, left = (d.pe + d.npes - 1) % d.npes;
+  int bad = 0;
+  for (int r = 0; r < rounds; r++) {
+    unsigned long long* slot = data + (size_t)(r & 1) * count;
+    for (size_t i = threadIdx.x; i < count; i += blockDim.x) src[i] = (unsigned long long)d.pe * 1000003ull + (unsigned long long)r * 7ull + i;
+    __syncthreads();
+    b200shmem::putmem_signal_block(d, slot, src, count * sizeof(unsigned long long), sig + (r & 1), (unsigned long long)(r + 1), B200SHMEM_SIGNAL_SET, right);
+    __shared__ int rc;
+    if (threadIdx.x == 0) rc = b200shmem::signal_wait_until(d, sig + (r & 1), B200SHMEM_CMP_GE, (unsigned long long)(r + 1));
+    __syncthreads();
+    if (rc != B200SHMEM_OK) { bad++; break; }
+    for (size_t i = threadIdx.x; i < count; i += blockDim.x)
+      if (slot[i] != (unsigned long long)left * 1000003ull + (unsigned long long)r * 7ull + i) bad++;
+    if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) { bad++; break; }
+  }
+  if (bad) atomicAdd(errors, bad);
+}
+
+// words (on PE 0): [0] u64 counter (fetch_add), [1] u64 bit set (or), [2] u64 CAS counter,
+// [3] u64 xor accumulator, [4] u32 counter, [5] u64 swap slot, [6] u64 and-mask.
+__global__ void kSelftestAtomics(b200shmem_dev_t d, unsigned long long* words, int iters, int* errors) {
+  int bad = 0;
+  if (threadIdx.x == 0) {
+    if (d.pe == 0) words[6] = ~0ull;
+  }
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  if (threadIdx.x == 0) {
+    unsigned long long prev = 0;
+    for (int i = 0; i < iters; i++) {
+      unsigned long long old = b200shmem::atomic_fetch_add(d, &words[0], 1ull, 0);
+      if (i > 0 && old <= prev) bad++;  // a fetch-add sequence seen by one PE is strictly increasing
+      prev = old;
+      b200shmem::atomic_add(d, (unsigned int*)&words[4], 1u, 0);
+      // CAS increment
+      unsigned long long cur = b200shmem::atomic_fetch(d, &words[2], 0);
+      for (int tries = 0; tries < 100000; tries++) {
+        unsigned long long seen = b200shmem::atomic_compare_swap(d, &words[2], cur, cur + 1, 0);
+        if (seen == cur) break;
+        cur = seen;
+      }
+      b200shmem::atomic_xor(d, &words[3], 1ull << d.pe, 0);
+    }
+    b200shmem::atomic_or(d, &words[1], 1ull << d.pe, 0);
+    b200shmem::atomic_and(d, &words[6], ~(1ull << (d.pe + 32)), 0);
+    (void)b200shmem::atomic_swap(d, &words[5], (unsigned long long)(d.pe + 1), 0);
+  }
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  if (threadIdx.x == 0) {
+    const unsigned long long n = (unsigned long long)d.npes, it = (unsigned long long)iters;
+    if (b200shmem::g(d, &words[0], 0) != n * it) bad++;
+    if (b200shmem::g(d, &words[1], 0) != (1ull << d.npes) - 1) bad++;
+    if (b200shmem::g(d, &words[2], 0) != n * it) bad++;
+    if (b200shmem::g(d, &words[3], 0) != ((iters & 1) ? (1ull << d.npes) - 1 : 0ull)) bad++;
+    if (b200shmem::g(d, (unsigned int*)&words[4], 0) != (unsigned int)(n * it)) bad++;
+    const unsigned long long sw = b200shmem::g(d, &words[5], 0);
+    if (sw < 1 || sw > n) bad++;
+    unsigned long long mask = ~0ull;
+    for (int pe = 0; pe < d.npes; pe++) mask &= ~(1ull << (pe + 32));
+    if (b200shmem::g(d, &words[6], 0) != mask) bad++;
+  }
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  if (bad && threadIdx.x == 0) atomicAdd(errors, bad);
+}
+
+struct DevGuard {
+  int prev = -1, want;
+  explicit DevGuard(int dev) : want(dev) {
+    cudaGetDevice(&prev);
+    if (prev != want) cudaSetDevice(want);
+  }
+  ~DevGuard() {
+    if (prev != want && prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+ncclResult_t b200shmem_init(ncclComm_t comm, size_t heapBytes, b200shmem_ctx_t* out) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  if (!out || heapBytes == 0) BFAIL(ncclInvalidArgument, "b200shmem_init: bad arguments");
+  if (c->nranks > B200SHMEM_MAX_PES) BFAIL(ncclInvalidArgument, "b200shmem_init: at most %d PEs", B200SHMEM_MAX_PES);
+  std::unique_ptr<b200shmem_ctx> ctx(new b200shmem_ctx());
+  ctx->comm = c;
+  void* p = nullptr;
+  BCHECK(commSymAlloc(c, heapBytes + kReserved, &p));
+  ctx->heap = (char*)p;
+  ctx->heapBytes = heapBytes + kReserved;
+  DevGuard g(c->cudaDev);
+  BCUDA(cudaMalloc(&ctx->devState, 64));
+  BCUDA(cudaMemset(ctx->devState, 0, 64));
+  b200shmem_dev_t& d = ctx->dev;
+  d.pe = c->rank;
+  d.npes = c->nranks;
+  size_t off = 0;
+  Window* w;
+  {
+    std::lock_guard<std::mutex> lk(c->mu);
+    w = c->findWindow(p, 1, &off);
+  }
+  if (!w) BFAIL(ncclInternalError, "b200shmem_init: heap window not found");
+  for (int pe = 0; pe < c->nranks; pe++) d.heap[pe] = w->seg.peer[pe];
+  d.heapMc = w->seg.mc;
+  d.heapBytes = ctx->heapBytes;
+  d.syncFlags = (unsigned long long*)ctx->heap;
+  d.syncEpoch = (unsigned long long*)ctx->devState;
+  d.status = (int*)((char*)ctx->devState + 16);
+  d.timeoutNs = (unsigned long long)Flags::get().waitTimeoutMs * 1000000ull;
+  ctx->freeList[kReserved] = heapBytes;
+  *out = ctx.release();
+  return ncclSuccess;
+}
+
+ncclResult_t b200shmem_finalize(b200shmem_ctx_t ctx) {
+  if (!ctx) return ncclSuccess;
+  DevGuard g(ctx->comm->cudaDev);
+  cudaDeviceSynchronize();
+  ncclResult_t r = commSymFree(ctx->comm, ctx->heap);
+  if (ctx->devState) cudaFree(ctx->devState);
+  delete ctx;
+  return r;
+}
+
+int b200shmem_my_pe(b200shmem_ctx_t ctx) { return ctx ? ctx->dev.pe : -1; }
+int b200shmem_n_pes(b200shmem_ctx_t ctx) { return ctx ? ctx->dev.npes : 0; }
+
+void* b200shmem_align(b200shmem_ctx_t ctx, size_t alignment, size_t size) {
+  if (!ctx || size == 0) return nullptr;
+  if (alignment < kAlign) alignment = kAlign;
+  if (alignment & (alignment - 1)) return nullptr;
+  size = (size + kAlign - 1) / kAlign * kAlign;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  for (auto it = ctx->freeList.begin(); it != ctx->freeList.end(); ++it) {
+    const size_t start = it->first, len = it->second;
+    const size_t aligned = (start + alignment - 1) / alignment * alignment;
+    if (aligned + size > start + len) continue;
+    const size_t tailStart = aligned + size, tailLen = start + len - tailStart;
+    ctx->freeList.erase(it);
+    if (aligned > start) ctx->freeList[start] = aligned - start;
+    if (tailLen) ctx->freeList[tailStart] = tailLen;
+    ctx->live[aligned] = size;
+    return ctx->heap + aligned;
+  }
+  return nullptr;
+}
+void* b200shmem_malloc(b200shmem_ctx_t ctx, size_t size) { return b200shmem_align(ctx, kAlign, size); }
+
+void b200shmem_free(b200shmem_ctx_t ctx, void* ptr) {
+  if (!ctx || !ptr) return;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  const size_t off = (char*)ptr - ctx->heap;
+  auto it = ctx->live.find(off);
+  if (it == ctx->live.end()) return;
+  size_t start = off, len = it->second;
+  ctx->live.erase(it);
+  // merge with neighbours
+  auto next = ctx->freeList.lower_bound(start);
+  if (next != ctx->freeList.end() && next->first == start + len) {
+    len += next->second;
+    next = ctx->freeList.erase(next);
+  }
+  if (next != ctx->freeList.begin()) {
+    auto prev = std::prev(next);
+    if (prev->first + prev->second == start) {
+      start = prev->first;
+      len += prev->second;
+      ctx->freeList.erase(prev);
+    }
+  }
+  ctx->freeList[start] = len;
+}
+
+void* b200shmem_ptr(b200shmem_ctx_t ctx, const void* ptr, int pe) {
+  if (!ctx || pe < 0 || pe >= ctx->dev.npes) return nullptr;
+  const size_t off = (const char*)ptr - ctx->heap;
+  if (off >= ctx->heapBytes) return nullptr;
+  return ctx->dev.heap[pe] + off;
+}
+void* b200shmem_mc_ptr(b200shmem_ctx_t ctx, const void* ptr) {
+  if (!ctx || !ctx->dev.heapMc) return nullptr;
+  const size_t off = (const char*)ptr - ctx->heap;
+  if (off >= ctx->heapBytes) return nullptr;
+  return ctx->dev.heapMc + off;
+}
+
+ncclResult_t b200shmem_device_ctx(b200shmem_ctx_t ctx, b200shmem_dev_t* out) {
+  if (!ctx || !out) BFAIL(ncclInvalidArgument, "b200shmem_device_ctx: null argument");
+  *out = ctx->dev;
+  return ncclSuccess;
+}
+
+ncclResult_t b200shmem_putmem_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream) {
+  void* r = b200shmem_ptr(ctx, dest, pe);
+  if (!r) BFAIL(ncclInvalidArgument, "b200shmem_putmem: destination is not in the symmetric heap");
+  DevGuard g(ctx->comm->cudaDev);
+  BCUDA(launchCopy(r, source, bytes, 0, stream));
+  return ncclSuccess;
+}
+ncclResult_t b200shmem_getmem_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream) {
+  void* r = b200shmem_ptr(ctx, source, pe);
+  if (!r) BFAIL(ncclInvalidArgument, "b200shmem_getmem: source is not in the symmetric heap");
+  DevGuard g(ctx->comm->cudaDev);
+  BCUDA(launchCopy(dest, r, bytes, 0, stream));
+  return ncclSuccess;
+}
+ncclResult_t b200shmem_putmem_signal_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, unsigned long long* sigAddr,
+                                               unsigned long long signal, int sigOp, int pe, cudaStream_t stream) {
+  BCHECK(b200shmem_putmem_on_stream(ctx, dest, source, bytes, pe, stream));
+  if (!b200shmem_ptr(ctx, sigAddr, pe)) BFAIL(ncclInvalidArgument, "b200shmem_putmem_signal: signal word is not in the symmetric heap");
+  DevGuard g(ctx->comm->cudaDev);
+  kSignal<<<1, 32, 0, stream>>>(ctx->dev, sigAddr, signal, sigOp, pe);
+  BCUDA(cudaGetLastError());
+  return ncclSuccess;
+}
+ncclResult_t b200shmem_signal_wait_until_on_stream(b200shmem_ctx_t ctx, unsigned long long* sigAddr, int cmp, unsigned long long value, cudaStream_t stream) {
+  if (!ctx) BFAIL(ncclInvalidArgument, "null context");
+  DevGuard g(ctx->comm->cudaDev);
+  kSignalWait<<<1, 32, 0, stream>>>(ctx->dev, sigAddr, cmp, value);
+  BCUDA(cudaGetLastError());
+  return ncclSuccess;
+}
+ncclResult_t b200shmem_barrier_all_on_stream(b200shmem_ctx_t ctx, cudaStream_t stream) {
+  if (!ctx) BFAIL(ncclInvalidArgument, "null context");
+  DevGuard g(ctx->comm->cudaDev);
+  kBarrierAll<<<1, 32, 0, stream>>>(ctx->dev);
+  BCUDA(cudaGetLastError());
+  return ncclSuccess;
+}
+
+int b200shmem_take_status(b200shmem_ctx_t ctx) {
+  if (!ctx) return -1;
+  DevGuard g(ctx->comm->cudaDev);
+  int v = 0;
+  if (cudaMemcpy(&v, ctx->dev.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (v) cudaMemset(ctx->dev.status, 0, sizeof(int));
+  return v;
+}
+
+ncclResult_t b200shmem_selftest_ring(b200shmem_ctx_t ctx, size_t count, int rounds, cudaStream_t stream, int* errors) {
+  if (!ctx || !errors) BFAIL(ncclInvalidArgument, "null argument");
+  DevGuard g(ctx->comm->cudaDev);
+  unsigned long long* data = (unsigned long long*)b200shmem_malloc(ctx, 2 * count * 8);
+  unsigned long long* sig = (unsigned long long*)b200shmem_malloc(ctx, 256);
+  if (!data || !sig) BFAIL(ncclSystemError, "b200shmem_selftest_ring: symmetric heap too small");
+  unsigned long long* src = nullptr;
+  int* derr = nullptr;
+  BCUDA(cudaMalloc(&src, count * 8));
+  BCUDA(cudaMalloc(&derr, sizeof(int)));
+  BCUDA(cudaMemsetAsync(derr, 0, sizeof(int), stream));
+  BCUDA(cudaMemsetAsync(sig, 0, 256, stream));
+  BCHECK(b200shmem_barrier_all_on_stream(ctx, stream));  // signals are zero everywhere before anyone puts
+  kSelftestRing<<<1, 256, 0, stream>>>(ctx->dev, data, src, sig, count, rounds, derr);
+  BCUDA(cudaGetLastError());
+  BCUDA(cudaMemcpyAsync(errors, derr, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  BCUDA(cudaStreamSynchronize(stream));
+  cudaFree(src);
+  cudaFree(derr);
+  BCHECK(ctx->comm->boot.barrier());
+  b200shmem_free(ctx, sig);
+  b200shmem_free(ctx, data);
+  return ncclSuccess;
+}
+
+ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStream_t stream, int* errors) {
+  if (!ctx || !errors) BFAIL(ncclInvalidArgument, "null argument");
+  DevGuard g(ctx->comm->cudaDev);
+  unsigned long long* words = (unsigned long long*)b200shmem_malloc(ctx, 256);
+  if (!words) BFAIL(ncclSystemError, "b200shmem_selftest_atomics: symmetric heap too small");
+  int* derr = nullptr;
+  BCUDA(cudaMalloc(&derr, sizeof(int)));
+  BCUDA(cudaMemsetAsync(derr, 0, sizeof(int), stream));
+  BCUDA(cudaMemsetAsync(words, 0, 256, stream));
+  BCHECK(b200shmem_barrier_all_on_stream(ctx, stream));
+  kSelftestAtomics<<<1, 32, 0, stream>>>(ctx->dev, words, iters, derr);
+  BCUDA(cudaGetLastError());
+  BCUDA(cudaMemcpyAsync(errors, derr, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  BCUDA(cudaStreamSynchronize(stream));
+  cudaFree(derr);
+  BCHECK(ctx->comm->boot.barrier());
+  b200shmem_free(ctx, words);
+  return ncclSuccess;
+}
+
+}  // extern "C"

@@ -186,12 +186,12 @@ class LlamaTrainer:
             hin = x.detach().requires_grad_(True)
             with torch.enable_grad():
                 hn = ops.rmsnorm(hin, self.head.params["norm"], cfg.eps)
-            w_out = self.head.params["out"]
+            w_out = self.head.params["out"].detach()  # the head GEMMs are differentiated by hand below
             logits = torch.mm(hn.detach(), w_out.t())
             loss_rows = ops.cross_entropy_inplace(logits, tgt, 1.0 / T)
             loss = loss_rows.mean()
             eng.alloc_grad(self.head)
-            dhn = torch.mm(logits, w_out.detach())
+            dhn = torch.mm(logits, w_out)
             torch.mm(logits.t(), hn.detach(), out=self.head.grad_view("out"))
             del logits
             self.head.params["norm"].grad = None

@@ -179,3 +179,26 @@ def embedding_bwd_(tokens: torch.Tensor, dout: torch.Tensor, dtable_f32: torch.T
 def cast_scale_(src_bf16: torch.Tensor, dst_f32: torch.Tensor, scale: float, accumulate: bool = False) -> None:
     assert src_bf16.numel() == dst_f32.numel() and src_bf16.is_contiguous() and dst_f32.is_contiguous()
     _ck(_lib_ops().b200ops_cast_scale(src_bf16.data_ptr(), dst_f32.data_ptr(), src_bf16.numel(), scale, int(accumulate), _s()), "cast_scale")
+
+
+def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """``a @ b.T`` for bf16 row-major ``a`` [M, K] and ``b`` [N, K] on the hand-written tcgen05
+    kernel (TMA-fed, accumulators in tensor memory). Library GEMMs are not used on this path."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1]
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    lib = _lib_ops()
+    if not hasattr(lib, "_gemm_sig"):
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        lib.b200ops_gemm_bf16_tn.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        lib._gemm_sig = True
+    _ck(lib.b200ops_gemm_bf16_tn(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), bn, max_ctas, _s()), "gemm_bf16_tn")
+    return out
+
+
+def gemm_take_error() -> int:
+    """Code of the first bounded wait that gave up inside a tcgen05 kernel (0: none); synchronises."""
+    return int(_lib_ops().b200ops_gemm_take_error())

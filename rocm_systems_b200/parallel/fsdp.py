@@ -83,7 +83,6 @@ class FlatUnit:
             self.full = self.shard  # no gather needed
         else:
             self.full = torch.empty(self.padded, dtype=torch.bfloat16, device=device)
-            self.full.untyped_storage().resize_(0)
         self.gathered = world == 1
         self.gather_event: Optional[torch.cuda.Event] = None
         self.full_grad: Optional[torch.Tensor] = None
@@ -93,6 +92,8 @@ class FlatUnit:
             v = self.full.detach()[offs[s.name]:offs[s.name] + s.numel].view(*s.shape)
             v.requires_grad_(True)
             self.params[s.name] = v
+        if world > 1:
+            self.full.untyped_storage().resize_(0)  # views made above stay valid across resizes
 
     def grad_view(self, name: str) -> torch.Tensor:
         s = next(sp for sp in self.specs if sp.name == name)
