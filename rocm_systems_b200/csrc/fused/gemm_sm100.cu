@@ -49,17 +49,17 @@ int smCount() {
   return n[dev] ? n[dev] : 148;
 }
 
-template <int BN, typename Epi>
-cudaError_t launch(const Params& p, const Epi& epi, int ctas, cudaStream_t s) {
+template <int BN>
+cudaError_t launch(const Params& p, const PlainPolicy<BN>& pol, int ctas, cudaStream_t s) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemmKernel<BN, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemmKernel<BN, PlainPolicy<BN>>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  gemmKernel<BN, Epi><<<ctas, kThreads, Cfg<BN>::kSmemBytes, s>>>(p, epi);
+  gemmKernel<BN, PlainPolicy<BN>><<<ctas, kThreads, Cfg<BN>::kSmemBytes, s>>>(p, pol);
   return cudaGetLastError();
 }
 
@@ -75,12 +75,12 @@ cudaError_t gemmBf16TN(const void* A, const void* B, void* C, int M, int N, int 
   p.tilesN = (N + bn - 1) / bn;
   p.err = errWord();
   if (!p.err) return cudaErrorMemoryAllocation;
-  EpiStoreBf16 epi{(__nv_bfloat16*)C, ldc, N};
   int ctas = smCount();
   if (maxCtas > 0 && maxCtas < ctas) ctas = maxCtas;
   const int tiles = p.tilesM * p.tilesN;
   if (tiles < ctas) ctas = tiles;
-  return bn == 256 ? launch<256>(p, epi, ctas, s) : launch<128>(p, epi, ctas, s);
+  if (bn == 256) return launch<256>(p, PlainPolicy<256>{(__nv_bfloat16*)C, ldc, N}, ctas, s);
+  return launch<128>(p, PlainPolicy<128>{(__nv_bfloat16*)C, ldc, N}, ctas, s);
 }
 
 }  // namespace gemm

@@ -1,10 +1,11 @@
 // Persistent, warp-specialised bf16 GEMM on the 5th-generation tensor cores:
 //   C[M, N] = A[M, K] * B[N, K]^T   (both operands K-major, as in y = x W^T)
-// One CTA per SM walks output tiles of 128 x BN. Warp 0 feeds shared memory with TMA tile loads
-// through a ring of mbarrier-guarded stages, warp 1 issues tcgen05.mma from a single thread into
-// a double-buffered fp32 accumulator in tensor memory, warps 2..5 drain finished accumulators with
+// A CTA walks output tiles of 128 x BN. Warp 0 feeds shared memory with TMA tile loads through a
+// ring of mbarrier-guarded stages, warp 1 issues tcgen05.mma from a single thread into a
+// double-buffered fp32 accumulator in tensor memory, warps 2..5 drain finished accumulators with
 // tcgen05.ld and run the epilogue, so the epilogue of tile t overlaps the main loop of tile t+1.
-// The epilogue is a template hook, which is where the fused GEMM+collective kernels differ.
+// Tile order, operand readiness and the epilogue are hooks of a policy object, which is where the
+// fused GEMM+collective kernels differ from the plain GEMM.
 // Every wait is bounded; on a failed wait the kernel records an error code, drains and returns.
 #pragma once
 
@@ -34,11 +35,11 @@ struct Params {
   int* err;          // device word: 0, or the code of the first wait that gave up
 };
 
-enum ErrCode : int { ERR_PRODUCER_EMPTY = 1, ERR_MMA_FULL = 2, ERR_MMA_ACC_EMPTY = 3, ERR_EPI_ACC_FULL = 4, ERR_FLAG_WAIT = 5 };
+enum ErrCode : int { ERR_PRODUCER_EMPTY = 1, ERR_MMA_FULL = 2, ERR_MMA_ACC_EMPTY = 3, ERR_EPI_ACC_FULL = 4, ERR_FLAG_WAIT = 5, ERR_REDUCE_WAIT = 6 };
 
-// Tile order: walk M fastest inside bands of `kBand` N-tiles so that concurrently running CTAs
-// share B tiles (and, across a band, A tiles) in L2.
-__device__ __forceinline__ void tileCoord(int t, int tilesM, int tilesN, int& tm, int& tn) {
+// Default tile order: walk M fastest inside bands of `kBand` N-tiles so that concurrently running
+// CTAs share B tiles (and, across a band, A tiles) in L2.
+__device__ __forceinline__ void bandedCoord(int t, int tilesM, int tilesN, int& tm, int& tn) {
   constexpr int kBand = 8;
   const int perBand = kBand * tilesM;
   const int band = t / perBand;
@@ -48,16 +49,36 @@ __device__ __forceinline__ void tileCoord(int t, int tilesM, int tilesN, int& tm
   tm = inBand / bandW;
 }
 
-// Epilogue hook interface:
-//   struct Epi { __device__ void tile(int tm, int tn, int row, int col0, const uint32_t (&acc)[32], bool rowOk) }
-// called by each epilogue thread for its row and each group of 32 columns of the tile;
-//   __device__ bool waitTile(int tm, int tn, volatile int* err)  lets the producer block until the operands of a tile are ready
-//   __device__ void tileDone(int tm, int tn)                      called once per tile by one thread after all its rows are out.
-template <int BN, typename Epi>
-__global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant__ Params p, Epi epi) {
+// fp32 accumulator words -> bf16, 32 consecutive columns of one row, to global memory.
+__device__ __forceinline__ void storeRow32Bf16(__nv_bfloat16* dst, const uint32_t (&acc)[32], int validCols) {
+  if (validCols >= 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+      uint4 o;
+      uint32_t* ow = &o.x;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * i]), __uint_as_float(acc[v * 8 + 2 * i + 1]));
+        ow[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst + v * 8) = o;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+      if (i < validCols) dst[i] = __float2bfloat16(__uint_as_float(acc[i]));
+  }
+}
+
+// Policy interface (all __device__):
+//   void coord(int t, int tilesM, int tilesN, int& tm, int& tn)        tile order
+//   bool waitTile(int tm, int tn, volatile int* err)                   producer: operands of the tile are in place
+//   void drain(uint32_t taddr, int tm, int tn, int row, bool rowOk)    epilogue thread: read the accumulator row at taddr (+column) and emit it
+//   void tileDone(int tm, int tn, int q, int lane)                     epilogue thread, after its rows of the tile are out
+template <int BN, typename Policy>
+__device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, int nctas, uint8_t* smemRaw) {
   using C = Cfg<BN>;
   using namespace sm100;
-  extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
   uint8_t* smemA = smem;
   uint8_t* smemB = smem + (size_t)C::kStages * C::kABytes;
@@ -101,10 +122,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+      for (int t = cta; t < numTiles && ok; t += nctas) {
         int tm, tn;
-        tileCoord(t, p.tilesM, p.tilesN, tm, tn);
-        if (!epi.waitTile(tm, tn, err)) { ok = false; break; }
+        pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+        if (!pol.waitTile(tm, tn, err)) { ok = false; break; }
         for (int k = 0; k < kIters; k++) {
           if (!mbarWait(&empty[stage], phase ^ 1, err, ERR_PRODUCER_EMPTY)) { ok = false; break; }
           mbarArriveExpectTx(&full[stage], C::kStageBytes);
@@ -125,7 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, it++) {
+      for (int t = cta; t < numTiles && ok; t += nctas, it++) {
         const int b = it & 1;
         const uint32_t accPhase = (it >> 1) & 1;
         if (!mbarWait(&accEmpty[b], accPhase ^ 1, err, ERR_MMA_ACC_EMPTY)) { ok = false; break; }
@@ -149,26 +170,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
     const int q = warp & 3;  // the quarter of tensor-memory lanes this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, it++) {
+    for (int t = cta; t < numTiles && ok; t += nctas, it++) {
       int tm, tn;
-      tileCoord(t, p.tilesM, p.tilesN, tm, tn);
+      pol.coord(t, p.tilesM, p.tilesN, tm, tn);
       const int b = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
       if (!mbarWait(&accFull[b], accPhase, err, ERR_EPI_ACC_FULL)) { ok = false; break; }
       tcFenceAfter();
       const int row = tm * BM + q * 32 + lane;
-      const bool rowOk = row < p.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t acc[32];
-        tmemLoad32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + c * 32), acc);
-        tmemLoadWait();
-        epi.tile(tm, tn, row, tn * BN + c * 32, acc, rowOk);
-      }
+      pol.drain(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN), tm, tn, row, row < p.M);
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(&accEmpty[b]);
-      epi.tileDone(tm, tn, warp == 2 && lane == 0, q);
+      pol.tileDone(tm, tn, q, lane);
     }
   }
   tcFenceBefore();
@@ -176,35 +190,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant_
   if (warp == 1) tmemDealloc(tmem, C::kTmemCols);
 }
 
-// ---- the plain epilogue: C = bf16(acc) --------------------------------------------------------------
-struct EpiStoreBf16 {
+// ---- the plain GEMM: banded order, nothing to wait for, C = bf16(acc) ------------------------------------
+template <int BN> struct PlainPolicy {
   __nv_bfloat16* C;
   int ldc;
   int N;
+  __device__ __forceinline__ void coord(int t, int tilesM, int tilesN, int& tm, int& tn) const { bandedCoord(t, tilesM, tilesN, tm, tn); }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
-  __device__ __forceinline__ void tileDone(int, int, bool, int) const {}
-  __device__ __forceinline__ void tile(int, int, int row, int col0, const uint32_t (&acc)[32], bool rowOk) const {
-    if (!rowOk || col0 >= N) return;
-    __nv_bfloat16* dst = C + (size_t)row * ldc + col0;
-    if (col0 + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-      for (int v = 0; v < 4; v++) {
-        uint4 o;
-        uint32_t* ow = &o.x;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * i]), __uint_as_float(acc[v * 8 + 2 * i + 1]));
-          ow[i] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(dst + v * 8) = o;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; i++)
-        if (col0 + i < N) dst[i] = __float2bfloat16(__uint_as_float(acc[i]));
+  __device__ __forceinline__ void tileDone(int, int, int, int) const {}
+  __device__ __forceinline__ void drain(uint32_t taddr, int, int tn, int row, bool rowOk) const {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; c++) {
+      uint32_t acc[32];
+      sm100::tmemLoad32(taddr + c * 32, acc);
+      sm100::tmemLoadWait();
+      const int col0 = tn * BN + c * 32;
+      if (rowOk && col0 < N) storeRow32Bf16(C + (size_t)row * ldc + col0, acc, N - col0);
     }
   }
 };
+
+template <int BN, typename Policy>
+__global__ void __launch_bounds__(kThreads, 1) gemmKernel(const __grid_constant__ Params p, Policy pol) {
+  extern __shared__ uint8_t smemRaw[];
+  gemmCta<BN>(p, pol, blockIdx.x, gridDim.x, smemRaw);
+}
 
 }  // namespace gemm
 }  // namespace b200

@@ -1,0 +1,445 @@
+// Tensor-parallel hot paths as ONE kernel each: the collective runs inside the tcgen05 GEMM.
+//
+//   all-gather -> GEMM (+SwiGLU)   X is row-sharded over the ranks. A few "communication" CTAs pull
+//       the peers' shards over NVLink (plain peer loads) into this GPU's copy of X, 128 rows at a
+//       time, and publish a flag per block of rows; the GEMM CTAs start on the local shard and take
+//       the remote row blocks in the order they land, their TMA producer waiting on the flag of
+//       the block it needs. The remote tile crosses NVLink once, lands in local memory, and is read
+//       from there by ordinary (non-multicast) TMA loads.
+//   GEMM -> reduce-scatter         every rank multiplies its K-shard; the epilogue converts each
+//       accumulator tile to bf16 and stores it straight into the staging buffer of the rank that
+//       owns those rows (peer stores), tiles of remote owners first, then bumps a per-tile counter
+//       at the owner. When a CTA runs out of GEMM tiles it turns reducer: it waits for a tile's
+//       counter to reach the rank count, adds the n partials in fp32 and writes the owned rows.
+// No barrier between the ranks is needed on the GEMM->RS path: staging and counters are double
+// buffered by call parity and counters only grow. Every wait is bounded.
+#include <map>
+#include <mutex>
+
+#include "../coll/prims.cuh"
+#include "../core/comm.h"
+#include "b200coll/fused.h"
+#include "gemm_host.h"
+#include "gemm_sm100.cuh"
+
+namespace b200 {
+namespace tp {
+
+using namespace gemm;
+
+// ---- all-gather -> GEMM ---------------------------------------------------------------------------------
+struct AgArgs {
+  char* xLocal;                 // this rank's copy of X: [n * rowsPerRank, K] bf16
+  const char* xPeer[kMaxRanks]; // the peers' copies (their own shard is valid there)
+  uint32_t* flags;              // local device memory: [n * blocksPerRank], last sequence number landed
+  uint32_t seq;                 // sequence number of this call
+  int rowsPerRank, blocksPerRank;  // blocks of BM rows
+  size_t rowBytes;              // K * 2
+  int nComm;                    // communication CTAs (the first blocks of the grid)
+  __nv_bfloat16* out;           // [M, Nout]
+  int ldo, nOut;
+};
+
+__device__ __forceinline__ void pullBlock(char* dst, const char* src, size_t bytes) {
+  // 16 independent 16-byte loads per thread in flight: peer loads are latency bound.
+  const int t = threadIdx.x, nt = blockDim.x;
+  const size_t nvec = bytes >> 4;
+  const uint4* s = (const uint4*)src;
+  uint4* d = (uint4*)dst;
+  size_t i = t;
+  constexpr int U = 16;
+  for (; i + (size_t)(U - 1) * nt < nvec; i += (size_t)U * nt) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) v[u] = ldStream16(s + i + (size_t)u * nt);
+#pragma unroll
+    for (int u = 0; u < U; u++) st16(d + i + (size_t)u * nt, v[u]);
+  }
+  for (; i < nvec; i += nt) st16(d + i, ldStream16(s + i));
+}
+
+template <int BN, bool SWIGLU> struct AgPolicy {
+  AgArgs a;
+  int rank, n;
+  __device__ __forceinline__ void coord(int t, int, int tilesN, int& tm, int& tn) const {
+    // Row blocks in arrival order: the local shard, then peers rank+1, rank+2, ...
+    const int perGroup = a.blocksPerRank * tilesN;
+    const int g = t / perGroup, r = t - g * perGroup;
+    const int owner = (rank + g) % n;
+    tm = owner * a.blocksPerRank + r / tilesN;
+    tn = r % tilesN;
+  }
+  __device__ __forceinline__ bool waitTile(int tm, int, volatile int* err) const {
+    if (tm / a.blocksPerRank == rank) return true;
+    const uint32_t* f = a.flags + tm;
+    for (uint32_t i = 0; i < 200000000u; i++) {
+      uint32_t v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if ((int32_t)(v - a.seq) >= 0) {
+        asm volatile("fence.proxy.async;" ::: "memory");  // the TMA reads that follow see the pulled rows
+        return true;
+      }
+      if ((i & 0x3ff) == 0x3ff && *err) return false;
+      __nanosleep(32);
+    }
+    atomicCAS((int*)err, 0, ERR_FLAG_WAIT);
+    return false;
+  }
+  __device__ __forceinline__ void tileDone(int, int, int, int) const {}
+  __device__ __forceinline__ void drain(uint32_t taddr, int, int tn, int row, bool rowOk) const {
+    if constexpr (SWIGLU) {
+      // The weight rows are interleaved per tile: BN/2 gate rows then BN/2 up rows, so one tile
+      // holds both halves of BN/2 outputs.
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; c++) {
+        uint32_t g[32], u[32];
+        sm100::tmemLoad32(taddr + c * 32, g);
+        sm100::tmemLoad32(taddr + BN / 2 + c * 32, u);
+        sm100::tmemLoadWait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const float gv = __uint_as_float(g[i]);
+          g[i] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[i]));
+        }
+        const int col0 = tn * (BN / 2) + c * 32;
+        if (rowOk && col0 < a.nOut) storeRow32Bf16(a.out + (size_t)row * a.ldo + col0, g, a.nOut - col0);
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t acc[32];
+        sm100::tmemLoad32(taddr + c * 32, acc);
+        sm100::tmemLoadWait();
+        const int col0 = tn * BN + c * 32;
+        if (rowOk && col0 < a.nOut) storeRow32Bf16(a.out + (size_t)row * a.ldo + col0, acc, a.nOut - col0);
+      }
+    }
+  }
+};
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1) agGemmKernel(const __grid_constant__ Params p, const __grid_constant__ AgArgs a, const __grid_constant__ DevComm c) {
+  extern __shared__ uint8_t smemRaw[];
+  if ((int)blockIdx.x < a.nComm) {
+    const int j = blockIdx.x, n = c.nranks, rank = c.rank;
+    uint32_t epoch = c.local->barEpoch[j];
+    ctaBarrier(c, epoch);  // every rank's own shard is in place
+    const int total = (n - 1) * a.blocksPerRank;
+    const size_t blockBytes = (size_t)BM * a.rowBytes;
+    for (int id = j; id < total; id += a.nComm) {
+      const int peer = (rank + 1 + id / a.blocksPerRank) % n;
+      const int blk = peer * a.blocksPerRank + id % a.blocksPerRank;
+      pullBlock(a.xLocal + (size_t)blk * blockBytes, a.xPeer[peer] + (size_t)blk * blockBytes, blockBytes);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + blk), "r"(a.seq) : "memory");
+      }
+    }
+    ctaBarrier(c, epoch);  // the peers are done reading this rank's shard
+    if (threadIdx.x == 0) c.local->barEpoch[j] = epoch;
+    return;
+  }
+  AgPolicy<BN, SWIGLU> pol{a, c.rank, c.nranks};
+  gemmCta<BN>(p, pol, blockIdx.x - a.nComm, gridDim.x - a.nComm, smemRaw);
+}
+
+// ---- GEMM -> reduce-scatter --------------------------------------------------------------------------------
+struct RsArgs {
+  char* stagePeer[kMaxRanks];   // every rank's staging window as mapped here
+  size_t stageOff;              // byte offset of this call's parity half inside the window
+  size_t flagOff;               // byte offset of this call's parity counters inside the window
+  uint32_t target;              // counter value that means "all n partials of the tile are here"
+  int rowsPerRank, blocksPerRank;
+  int N;                        // columns of the output
+  __nv_bfloat16* y;             // [rowsPerRank, N] owned rows of the result
+  int ldy;
+};
+
+template <int BN> struct RsPolicy {
+  RsArgs a;
+  int rank, n;
+  __device__ __forceinline__ void coord(int t, int, int tilesN, int& tm, int& tn) const {
+    // Tiles of remote owners first (rank+1, rank+2, ...), the rows this rank owns last.
+    const int perGroup = a.blocksPerRank * tilesN;
+    const int g = t / perGroup, r = t - g * perGroup;
+    const int owner = (rank + 1 + g) % n;
+    tm = owner * a.blocksPerRank + r / tilesN;
+    tn = r % tilesN;
+  }
+  __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
+  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int row, bool rowOk) const {
+    const int owner = tm / a.blocksPerRank;
+    const int localRow = row - owner * a.rowsPerRank;
+    // Owner's staging: [src rank][rowsPerRank][N] bf16.
+    __nv_bfloat16* dst = (__nv_bfloat16*)(a.stagePeer[owner] + a.stageOff) + ((size_t)rank * a.rowsPerRank + localRow) * a.N;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; c++) {
+      uint32_t acc[32];
+      sm100::tmemLoad32(taddr + c * 32, acc);
+      sm100::tmemLoadWait();
+      const int col0 = tn * BN + c * 32;
+      if (rowOk && col0 < a.N) storeRow32Bf16(dst + col0, acc, a.N - col0);
+    }
+  }
+  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const {
+    // All four epilogue warps have stored their rows; then one thread tells the owner.
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (q == 0 && lane == 0) {
+      const int owner = tm / a.blocksPerRank;
+      const int tilesN = (a.N + BN - 1) / BN;
+      uint32_t* f = (uint32_t*)(a.stagePeer[owner] + a.flagOff) + (size_t)(tm - owner * a.blocksPerRank) * tilesN + tn;
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(f) : "memory");
+    }
+  }
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1) gemmRsKernel(const __grid_constant__ Params p, const __grid_constant__ RsArgs a, const __grid_constant__ DevComm c) {
+  extern __shared__ uint8_t smemRaw[];
+  RsPolicy<BN> pol{a, c.rank, c.nranks};
+  gemmCta<BN>(p, pol, blockIdx.x, gridDim.x, smemRaw);
+  // Reducer phase: sum the n staged partials of every tile this rank owns.
+  __shared__ int ok;
+  const int n = c.nranks, rank = c.rank;
+  const int tilesN = (a.N + BN - 1) / BN;
+  const int owned = a.blocksPerRank * tilesN;
+  const char* stage = a.stagePeer[rank] + a.stageOff;
+  const uint32_t* flags = (const uint32_t*)(a.stagePeer[rank] + a.flagOff);
+  const size_t slot = (size_t)a.rowsPerRank * a.N;  // elements per source rank
+  for (int idx = blockIdx.x; idx < owned; idx += gridDim.x) {
+    if (threadIdx.x == 0) {
+      int good = 0;
+      for (uint32_t i = 0; i < 200000000u; i++) {
+        if ((int32_t)(ldAcquireSys(flags + idx) - a.target) >= 0) { good = 1; break; }
+        if ((i & 0x3ff) == 0x3ff && *(volatile int*)p.err) break;
+        __nanosleep(32);
+      }
+      if (!good) atomicCAS(p.err, 0, ERR_REDUCE_WAIT);
+      ok = good;
+    }
+    __syncthreads();
+    if (ok) {
+      const int tmL = idx / tilesN, tn = idx % tilesN;
+      const int cols = min(BN, a.N - tn * BN);
+      const int vecPerRow = cols >> 3;
+      for (int v = threadIdx.x; v < BM * vecPerRow; v += blockDim.x) {
+        const int r = v / vecPerRow, cv = v - r * vecPerRow;
+        const int row = tmL * BM + r;
+        if (row >= a.rowsPerRank) continue;
+        const size_t e = (size_t)row * a.N + (size_t)tn * BN + (size_t)cv * 8;
+        float acc[8];
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; s++) {
+          if (s < n) {
+            const uint4 x = ldStream16(stage + (s * slot + e) * 2);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              const float2 f = __bfloat1622float2(h[k]);
+              acc[2 * k] = s == 0 ? f.x : acc[2 * k] + f.x;
+              acc[2 * k + 1] = s == 0 ? f.y : acc[2 * k + 1] + f.y;
+            }
+          }
+        }
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+          ow[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(a.y + (size_t)row * a.ldy + (size_t)tn * BN + (size_t)cv * 8) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace tp
+}  // namespace b200
+
+// =================================================================================================
+// Host entry points
+// =================================================================================================
+using namespace b200;
+using namespace b200::tp;
+
+namespace {
+
+struct AgState { uint32_t* flags = nullptr; uint32_t seq = 0; int cap = 0; };
+std::mutex gTpMu;
+std::map<Comm*, AgState> gAg;
+std::map<std::pair<Comm*, const void*>, unsigned long long> gRsCalls;
+
+template <typename K>
+cudaError_t allowSmem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+bool peersOf(Comm* c, const void* p, size_t bytes, char* (&out)[kMaxRanks]) {
+  size_t off = 0;
+  std::lock_guard<std::mutex> lk(c->mu);
+  Window* w = c->findWindow(p, bytes, &off);
+  if (!w) return false;
+  for (int r = 0; r < c->nranks; r++) out[r] = w->seg.peer[r] + off;
+  return true;
+}
+
+struct DevGuard2 {
+  int prev = -1, want;
+  explicit DevGuard2(int d) : want(d) { cudaGetDevice(&prev); if (prev != want) cudaSetDevice(want); }
+  ~DevGuard2() { if (prev != want && prev >= 0) cudaSetDevice(prev); }
+};
+
+}  // namespace
+
+extern "C" {
+
+size_t b200collGemmRsWorkspaceBytes(int rowsPerRank, int N, int nranks) {
+  const size_t stage = (size_t)nranks * rowsPerRank * N * 2;
+  const size_t flags = (((size_t)((rowsPerRank + 127) / 128) * ((N + 127) / 128) * 4) + 255) & ~(size_t)255;
+  return 2 * stage + 2 * flags;
+}
+
+ncclResult_t b200collAgGemm(ncclComm_t comm, void* xSym, const void* w, void* out, int rowsPerRank, int wRows, int K, int swiglu, int commCtas,
+                            cudaStream_t stream) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  const int n = c->nranks;
+  if (!xSym || !w || !out) BFAIL(ncclInvalidArgument, "b200collAgGemm: null buffer");
+  if (rowsPerRank <= 0 || rowsPerRank % BM) BFAIL(ncclInvalidArgument, "b200collAgGemm: rows per rank (%d) must be a multiple of %d", rowsPerRank, BM);
+  if (K % 8 || wRows % 128) BFAIL(ncclInvalidArgument, "b200collAgGemm: K %% 8 and weight rows %% 128 must be 0");
+  const int bn = (wRows % 256 == 0) ? 256 : 128;
+  const int M = rowsPerRank * n;
+  if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+  DevGuard2 g(c->cudaDev);
+  AgArgs a{};
+  char* peers[kMaxRanks] = {};
+  if (n > 1) {
+    if (!peersOf(c, xSym, (size_t)M * K * 2, peers)) BFAIL(ncclInvalidUsage, "b200collAgGemm: X must live in symmetric memory (b200collSymAlloc)");
+  } else {
+    peers[0] = (char*)xSym;
+  }
+  for (int r = 0; r < n; r++) a.xPeer[r] = peers[r];
+  a.xLocal = (char*)xSym;
+  a.rowsPerRank = rowsPerRank;
+  a.blocksPerRank = rowsPerRank / BM;
+  a.rowBytes = (size_t)K * 2;
+  a.nComm = n > 1 ? (commCtas > 0 ? commCtas : 20) : 0;
+  if (a.nComm > 64) a.nComm = 64;
+  a.out = (__nv_bfloat16*)out;
+  a.nOut = swiglu ? wRows / 2 : wRows;
+  a.ldo = a.nOut;
+  {
+    std::lock_guard<std::mutex> lk(gTpMu);
+    AgState& st = gAg[c];
+    const int need = n * a.blocksPerRank;
+    if (st.cap < need) {
+      if (st.flags) cudaFree(st.flags);
+      BCUDA(cudaMalloc(&st.flags, (size_t)need * 4));
+      BCUDA(cudaMemset(st.flags, 0, (size_t)need * 4));
+      st.cap = need;
+      st.seq = 0;
+    }
+    a.flags = st.flags;
+    a.seq = ++st.seq;
+  }
+  Params p{};
+  if (!makeTileMap(&p.mapA, xSym, M, K, K, BM, 2) || !makeTileMap(&p.mapB, w, wRows, K, K, bn, 2))
+    BFAIL(ncclInvalidArgument, "b200collAgGemm: operands must be 16-byte aligned with rows a multiple of 16 bytes");
+  p.M = M;
+  p.N = wRows;
+  p.K = K;
+  p.tilesM = M / BM;
+  p.tilesN = wRows / bn;
+  p.err = errWord();
+  if (!p.err) BFAIL(ncclUnhandledCudaError, "b200collAgGemm: no error word");
+  DevComm dc = c->dev;
+  dc.opSeq = ++c->opSeq;
+  dc.stamp = nullptr;
+  int gemmCtas = smCount() - a.nComm;
+  if (gemmCtas > p.tilesM * p.tilesN) gemmCtas = p.tilesM * p.tilesN;
+  const int grid = a.nComm + gemmCtas;
+  cudaError_t e;
+#define B200_AG_LAUNCH(BNV, SW)                                                              \
+  do {                                                                                       \
+    e = allowSmem(agGemmKernel<BNV, SW>, Cfg<BNV>::kSmemBytes);                               \
+    if (e == cudaSuccess) {                                                                  \
+      agGemmKernel<BNV, SW><<<grid, kThreads, Cfg<BNV>::kSmemBytes, stream>>>(p, a, dc);      \
+      e = cudaGetLastError();                                                                \
+    }                                                                                        \
+  } while (0)
+  if (bn == 256) { if (swiglu) B200_AG_LAUNCH(256, true); else B200_AG_LAUNCH(256, false); }
+  else { if (swiglu) B200_AG_LAUNCH(128, true); else B200_AG_LAUNCH(128, false); }
+#undef B200_AG_LAUNCH
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collAgGemm launch failed: %s", cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
+ncclResult_t b200collGemmRs(ncclComm_t comm, const void* a_, const void* w, void* workspaceSym, void* y, int rowsPerRank, int N, int K,
+                            cudaStream_t stream) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  const int n = c->nranks;
+  if (!a_ || !w || !workspaceSym || !y) BFAIL(ncclInvalidArgument, "b200collGemmRs: null buffer");
+  if (rowsPerRank <= 0 || rowsPerRank % BM) BFAIL(ncclInvalidArgument, "b200collGemmRs: rows per rank (%d) must be a multiple of %d", rowsPerRank, BM);
+  if (K % 8 || N % 128) BFAIL(ncclInvalidArgument, "b200collGemmRs: K %% 8 and N %% 128 must be 0");
+  const int bn = (N % 256 == 0) ? 256 : 128;
+  const int M = rowsPerRank * n;
+  if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+  DevGuard2 g(c->cudaDev);
+  const size_t wsBytes = b200collGemmRsWorkspaceBytes(rowsPerRank, N, n);
+  RsArgs a{};
+  char* peers[kMaxRanks] = {};
+  if (n > 1) {
+    if (!peersOf(c, workspaceSym, wsBytes, peers)) BFAIL(ncclInvalidUsage, "b200collGemmRs: the workspace must be symmetric memory of b200collGemmRsWorkspaceBytes()");
+  } else {
+    peers[0] = (char*)workspaceSym;
+  }
+  for (int r = 0; r < n; r++) a.stagePeer[r] = peers[r];
+  const size_t stage = (size_t)n * rowsPerRank * N * 2;
+  const size_t flags = (wsBytes - 2 * stage) / 2;
+  unsigned long long calls;
+  {
+    std::lock_guard<std::mutex> lk(gTpMu);
+    calls = gRsCalls[std::make_pair(c, (const void*)workspaceSym)]++;
+  }
+  const int parity = (int)(calls & 1);
+  a.stageOff = (size_t)parity * stage;
+  a.flagOff = 2 * stage + (size_t)parity * flags;
+  a.target = (uint32_t)((calls / 2 + 1) * (unsigned long long)n);
+  a.rowsPerRank = rowsPerRank;
+  a.blocksPerRank = rowsPerRank / BM;
+  a.N = N;
+  a.y = (__nv_bfloat16*)y;
+  a.ldy = N;
+  Params p{};
+  if (!makeTileMap(&p.mapA, a_, M, K, K, BM, 2) || !makeTileMap(&p.mapB, w, N, K, K, bn, 2))
+    BFAIL(ncclInvalidArgument, "b200collGemmRs: operands must be 16-byte aligned with rows a multiple of 16 bytes");
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.tilesM = M / BM;
+  p.tilesN = N / bn;
+  p.err = errWord();
+  if (!p.err) BFAIL(ncclUnhandledCudaError, "b200collGemmRs: no error word");
+  DevComm dc = c->dev;
+  dc.opSeq = ++c->opSeq;
+  dc.stamp = nullptr;
+  int grid = smCount();
+  if (grid > p.tilesM * p.tilesN) grid = p.tilesM * p.tilesN;
+  cudaError_t e;
+  if (bn == 256) {
+    e = allowSmem(gemmRsKernel<256>, Cfg<256>::kSmemBytes);
+    if (e == cudaSuccess) { gemmRsKernel<256><<<grid, kThreads, Cfg<256>::kSmemBytes, stream>>>(p, a, dc); e = cudaGetLastError(); }
+  } else {
+    e = allowSmem(gemmRsKernel<128>, Cfg<128>::kSmemBytes);
+    if (e == cudaSuccess) { gemmRsKernel<128><<<grid, kThreads, Cfg<128>::kSmemBytes, stream>>>(p, a, dc); e = cudaGetLastError(); }
+  }
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collGemmRs launch failed: %s", cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
+}  // extern "C"

@@ -1,0 +1,106 @@
+"""Tensor-parallel (with sequence-parallel activations) MLP on the fused kernels.
+
+``TensorParallelMLP`` holds this rank's shards of a SwiGLU MLP: ``w13`` (gate and up rows of its
+1/N of the hidden features, interleaved per 256-row tile as the fused kernel wants) and ``w2`` (the
+matching K-shard). ``forward`` takes this rank's rows of the activations and returns this rank's
+rows of the output:
+
+    all-gather(x) -> x @ w13^T -> SwiGLU -> @ w2^T -> reduce-scatter
+
+as two kernels, ``b200collAgGemm`` and ``b200collGemmRs`` (csrc/fused/tp_fused.cu), each of which
+moves its data over NVLink from inside the tcgen05 GEMM. ``reference_forward`` is the unfused
+composition (collectives of this package + library GEMMs) used as oracle and timing baseline.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from ..ops import train_ops
+
+_done = False
+
+
+def _lib_tp():
+    global _done
+    lib = _lib.load()
+    if not _done:
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        lib.b200collAgGemm.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        lib.b200collGemmRs.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]
+        lib.b200collGemmRsWorkspaceBytes.argtypes = [i32, i32, i32]
+        lib.b200collGemmRsWorkspaceBytes.restype = ctypes.c_size_t
+        _done = True
+    return lib
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, tile: int = 256) -> torch.Tensor:
+    """Stack gate and up rows so that every ``tile`` rows hold tile/2 gate rows then the tile/2 up
+    rows of the same output features (the layout the fused SwiGLU epilogue reads)."""
+    F, K = w_gate.shape
+    h = tile // 2
+    assert F % h == 0
+    g = w_gate.view(F // h, h, K)
+    u = w_up.view(F // h, h, K)
+    return torch.stack([g, u], dim=1).reshape(2 * F, K).contiguous()
+
+
+class TensorParallelMLP:
+    def __init__(self, comm, rows_per_rank: int, hidden: int, ffn_local: int, device=None, std: float = 0.02, seed: int = 0,
+                 comm_ctas: int = 0):
+        self.comm = comm
+        self.n, self.rank = comm.nranks, comm.rank
+        self.rows, self.hidden, self.f = rows_per_rank, hidden, ffn_local
+        self.device = device or comm.device
+        self.comm_ctas = comm_ctas
+        g = torch.Generator(device=self.device).manual_seed(seed + 7919 * self.rank)
+        wg = (torch.randn(ffn_local, hidden, device=self.device, generator=g) * std).to(torch.bfloat16)
+        wu = (torch.randn(ffn_local, hidden, device=self.device, generator=g) * std).to(torch.bfloat16)
+        self.w_gate, self.w_up = wg, wu
+        self.tile = 256 if (2 * ffn_local) % 256 == 0 else 128
+        self.w13 = interleave_gate_up(wg, wu, self.tile)
+        self.w2 = (torch.randn(hidden, ffn_local, device=self.device, generator=g) * std).to(torch.bfloat16)
+        M = self.n * rows_per_rank
+        lib = _lib_tp()
+        self._x_sym = comm.sym_alloc(M * hidden * 2)
+        self.x_full = self._x_sym.tensor((M, hidden), torch.bfloat16)
+        self._ws = comm.sym_alloc(int(lib.b200collGemmRsWorkspaceBytes(rows_per_rank, hidden, self.n)))
+        self.act = torch.empty(M, ffn_local, dtype=torch.bfloat16, device=self.device)
+        self.y = torch.empty(rows_per_rank, hidden, dtype=torch.bfloat16, device=self.device)
+
+    def my_rows(self) -> torch.Tensor:
+        """Where this rank writes its rows of the activations before ``forward``."""
+        return self.x_full[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def forward(self, x_local: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        if x_local is not None:
+            self.my_rows().copy_(x_local)
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        lib = _lib_tp()
+        _lib.check(lib.b200collAgGemm(self.comm.handle, self.x_full.data_ptr(), self.w13.data_ptr(), self.act.data_ptr(), self.rows,
+                                      2 * self.f, self.hidden, 1, self.comm_ctas, s), "b200collAgGemm")
+        _lib.check(lib.b200collGemmRs(self.comm.handle, self.act.data_ptr(), self.w2.data_ptr(), self._ws.ptr, self.y.data_ptr(), self.rows,
+                                      self.hidden, self.f, s), "b200collGemmRs")
+        train_ops.LAUNCHES += 2
+        return self.y
+
+    def reference_forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        """Unfused: all_gather, two library GEMMs, SwiGLU, reduce_scatter."""
+        M = self.n * self.rows
+        xg = torch.empty(M, self.hidden, dtype=torch.bfloat16, device=self.device)
+        self.comm.all_gather(x_local.contiguous(), xg)
+        g = xg @ self.w_gate.t()
+        u = xg @ self.w_up.t()
+        a = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+        part = a @ self.w2.t()
+        out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        self.comm.reduce_scatter(part, out)
+        return out
+
+    def free(self) -> None:
+        torch.cuda.synchronize()
+        self._x_sym.free()
+        self._ws.free()
