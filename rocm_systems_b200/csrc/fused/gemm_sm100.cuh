@@ -72,6 +72,8 @@ __device__ __forceinline__ void storeRow32Bf16(__nv_bfloat16* dst, const uint32_
 
 // Policy interface (all __device__):
 //   void coord(int t, int tilesM, int tilesN, int& tm, int& tn)        tile order
+//   bool valid(int tm, int tn)                                         false: the tile is skipped by every role
+//   int aRow(int tm), int bRow(int tm, int tn)                         first row of the tile in the A / B tensor maps
 //   bool waitTile(int tm, int tn, volatile int* err)                   producer: operands of the tile are in place
 //   void drain(uint32_t taddr, int tm, int tn, int row, bool rowOk)    epilogue thread: read the accumulator row at taddr (+column) and emit it
 //   void tileDone(int tm, int tn, int q, int lane)                     epilogue thread, after its rows of the tile are out
@@ -125,12 +127,14 @@ __device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, i
       for (int t = cta; t < numTiles && ok; t += nctas) {
         int tm, tn;
         pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+        if (!pol.valid(tm, tn)) continue;
         if (!pol.waitTile(tm, tn, err)) { ok = false; break; }
+        const int aRow = pol.aRow(tm), bRow = pol.bRow(tm, tn);
         for (int k = 0; k < kIters; k++) {
           if (!mbarWait(&empty[stage], phase ^ 1, err, ERR_PRODUCER_EMPTY)) { ok = false; break; }
           mbarArriveExpectTx(&full[stage], C::kStageBytes);
-          tmaLoad2d(smemA + (size_t)stage * C::kABytes, &p.mapA, k * BK, tm * BM, &full[stage]);
-          tmaLoad2d(smemB + (size_t)stage * C::kBBytes, &p.mapB, k * BK, tn * BN, &full[stage]);
+          tmaLoad2d(smemA + (size_t)stage * C::kABytes, &p.mapA, k * BK, aRow, &full[stage]);
+          tmaLoad2d(smemB + (size_t)stage * C::kBBytes, &p.mapB, k * BK, bRow, &full[stage]);
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -146,9 +150,15 @@ __device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, i
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = cta; t < numTiles && ok; t += nctas, it++) {
+      for (int t = cta; t < numTiles && ok; t += nctas) {
+        {
+          int tm, tn;
+          pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+          if (!pol.valid(tm, tn)) continue;
+        }
         const int b = it & 1;
         const uint32_t accPhase = (it >> 1) & 1;
+        it++;
         if (!mbarWait(&accEmpty[b], accPhase ^ 1, err, ERR_MMA_ACC_EMPTY)) { ok = false; break; }
         tcFenceAfter();
         const uint32_t d = tmem + (uint32_t)b * BN;
@@ -170,11 +180,13 @@ __device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, i
     const int q = warp & 3;  // the quarter of tensor-memory lanes this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = cta; t < numTiles && ok; t += nctas, it++) {
+    for (int t = cta; t < numTiles && ok; t += nctas) {
       int tm, tn;
       pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+      if (!pol.valid(tm, tn)) continue;
       const int b = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
+      it++;
       if (!mbarWait(&accFull[b], accPhase, err, ERR_EPI_ACC_FULL)) { ok = false; break; }
       tcFenceAfter();
       const int row = tm * BM + q * 32 + lane;
@@ -196,6 +208,9 @@ template <int BN> struct PlainPolicy {
   int ldc;
   int N;
   __device__ __forceinline__ void coord(int t, int tilesM, int tilesN, int& tm, int& tn) const { bandedCoord(t, tilesM, tilesN, tm, tn); }
+  __device__ __forceinline__ bool valid(int, int) const { return true; }
+  __device__ __forceinline__ int aRow(int tm) const { return tm * BM; }
+  __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ void tileDone(int, int, int, int) const {}
   __device__ __forceinline__ void drain(uint32_t taddr, int, int tn, int row, bool rowOk) const {

@@ -69,6 +69,9 @@ template <int BN, bool SWIGLU> struct AgPolicy {
     tm = owner * a.blocksPerRank + r / tilesN;
     tn = r % tilesN;
   }
+  __device__ __forceinline__ bool valid(int, int) const { return true; }
+  __device__ __forceinline__ int aRow(int tm) const { return tm * BM; }
+  __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
   __device__ __forceinline__ bool waitTile(int tm, int, volatile int* err) const {
     if (tm / a.blocksPerRank == rank) return true;
     const uint32_t* f = a.flags + tm;
@@ -167,6 +170,9 @@ template <int BN> struct RsPolicy {
     tm = owner * a.blocksPerRank + r / tilesN;
     tn = r % tilesN;
   }
+  __device__ __forceinline__ bool valid(int, int) const { return true; }
+  __device__ __forceinline__ int aRow(int tm) const { return tm * BM; }
+  __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int row, bool rowOk) const {
     const int owner = tm / a.blocksPerRank;

@@ -35,6 +35,31 @@ size_t b200collGemmRsWorkspaceBytes(int rowsPerRank, int N, int nranks);
 ncclResult_t b200collGemmRs(ncclComm_t comm, const void* a, const void* w, void* workspaceSym, void* y, int rowsPerRank, int N, int K,
                             cudaStream_t stream);
 
+/* ---- Mixture-of-experts expert parallelism (experts e*expertsLocal .. on rank e) ----------------
+ * One symmetric window of b200collEpWorkspaceBytes() bytes (zero-initialised) per MoE layer holds
+ * the per-expert receive buffers (fp8 rows + one fp32 scale per 128 channels), their row counters
+ * and the experts' bf16 outputs. `cap` rows are reserved per local expert (multiple of 128); rows
+ * beyond it are dropped and counted. hidden: multiple of 1024, at most 7168; k <= 8.
+ * A layer runs  Route -> Dispatch -> Experts -> Combine  on one stream. */
+size_t b200collEpWorkspaceBytes(int nranks, int expertsLocal, int cap, int hidden, int ffn);
+/* top-k expert ids (largest logit first) and softmax-of-selected gate weights per token. */
+ncclResult_t b200collEpRoute(const float* logits, int* topIdx, float* topW, int T, int E, int k, cudaStream_t stream);
+/* Quantise to fp8 e4m3 and put every (token, expert) row into the owning rank's buffer, from
+ * inside one kernel; sentSlot [T, k] receives the row index reserved at the destination (or -1). */
+ncclResult_t b200collEpDispatch(ncclComm_t comm, void* winSym, const void* xBf16, const int* topIdx, int* sentSlot, int T, int k,
+                                int expertsLocal, int cap, int hidden, int ffn, cudaStream_t stream);
+/* Dequantise the received rows and run the two grouped expert GEMMs (SwiGLU between them) on
+ * tcgen05. w13 [expertsLocal * 2 ffn, hidden]: per expert, per 256 (128) rows, gate rows then up
+ * rows; w2 [expertsLocal * hidden, ffn]. xb / act: scratch [expertsLocal * cap, hidden / ffn] bf16. */
+ncclResult_t b200collEpExperts(ncclComm_t comm, void* winSym, const void* w13, const void* w2, void* xb, void* act, int expertsLocal, int cap,
+                               int hidden, int ffn, cudaStream_t stream);
+/* out [T, hidden] bf16 = sum_k gate[t, k] * expert_output(row sent for (t, k)), pulled from the
+ * owning ranks inside one kernel, in the order k = 0 .. k-1. */
+ncclResult_t b200collEpCombine(ncclComm_t comm, void* winSym, const int* topIdx, const float* topW, const int* sentSlot, void* out, int T, int k,
+                               int expertsLocal, int cap, int hidden, int ffn, cudaStream_t stream);
+ncclResult_t b200collEpCounts(ncclComm_t comm, void* winSym, int expertsLocal, int cap, int hidden, int ffn, unsigned int* countsHost,
+                              int* droppedHost, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,163 @@
+"""Expert-parallel mixture-of-experts layer on the fused dispatch / combine kernels.
+
+``MoELayer`` owns this rank's experts (``experts_local`` of ``nranks * experts_local``) and one
+symmetric window. ``forward(x, router_logits)`` runs route -> dispatch (fp8 e4m3, one scale per
+128 channels, device-initiated puts) -> grouped expert GEMMs on tcgen05 with SwiGLU -> combine
+(pull + gate-weighted sum in bf16 output) on the current stream. ``reference_forward`` is the
+same computation in plain PyTorch (all_to_all of this package for the exchange) and serves as
+oracle and timing baseline.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _lib
+from ..ops import train_ops
+from .tp import interleave_gate_up
+
+_done = False
+
+
+def _lib_ep():
+    global _done
+    lib = _lib.load()
+    if not _done:
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        lib.b200collEpWorkspaceBytes.argtypes = [i32] * 5
+        lib.b200collEpWorkspaceBytes.restype = ctypes.c_size_t
+        lib.b200collEpRoute.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+        lib.b200collEpDispatch.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+        lib.b200collEpExperts.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+        lib.b200collEpCombine.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+        lib.b200collEpCounts.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp]
+        _done = True
+    return lib
+
+
+def quantize_e4m3_per128(x: torch.Tensor):
+    """Reference quantiser: fp8 e4m3 values and one fp32 scale per 128 channels (amax / 448)."""
+    T, H = x.shape
+    g = x.float().view(T, H // 128, 128)
+    scale = g.abs().amax(-1).clamp_min(1e-10) / 448.0
+    q = (g / scale.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    return q.view(T, H), scale
+
+
+def dequantize_e4m3_per128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    T, H = q.shape
+    return (q.float().view(T, H // 128, 128) * scale.unsqueeze(-1)).view(T, H).to(torch.bfloat16)
+
+
+class MoELayer:
+    def __init__(self, comm, experts_local: int, hidden: int, ffn: int, top_k: int, tokens: int, capacity: int = 0, std: float = 0.02, seed: int = 0):
+        self.comm, self.n, self.rank = comm, comm.nranks, comm.rank
+        self.el, self.hidden, self.ffn, self.k, self.T = experts_local, hidden, ffn, top_k, tokens
+        self.E = self.n * experts_local
+        dev = comm.device
+        self.device = dev
+        avg = max(1, self.n * tokens * top_k // self.E)
+        cap = capacity or 4 * avg
+        self.cap = (cap + 127) // 128 * 128
+        g = torch.Generator(device=dev).manual_seed(seed + 104729 * self.rank)
+        self.w_gate = (torch.randn(experts_local, ffn, hidden, device=dev, generator=g) * std).to(torch.bfloat16)
+        self.w_up = (torch.randn(experts_local, ffn, hidden, device=dev, generator=g) * std).to(torch.bfloat16)
+        self.w_down = (torch.randn(experts_local, hidden, ffn, device=dev, generator=g) * std).to(torch.bfloat16)
+        tile = 256 if (2 * ffn) % 256 == 0 else 128
+        self.w13 = torch.cat([interleave_gate_up(self.w_gate[e], self.w_up[e], tile) for e in range(experts_local)]).contiguous()
+        self.w2 = self.w_down.reshape(experts_local * hidden, ffn).contiguous()
+        lib = _lib_ep()
+        self._win = comm.sym_alloc(int(lib.b200collEpWorkspaceBytes(self.n, experts_local, self.cap, hidden, ffn)))
+        rows = experts_local * self.cap
+        self.xb = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=dev)
+        self.act = torch.zeros(rows, ffn, dtype=torch.bfloat16, device=dev)
+        self.top_idx = torch.empty(tokens, top_k, dtype=torch.int32, device=dev)
+        self.top_w = torch.empty(tokens, top_k, dtype=torch.float32, device=dev)
+        self.sent = torch.empty(tokens, top_k, dtype=torch.int32, device=dev)
+        self.out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+
+    def _args(self):
+        return (self.el, self.cap, self.hidden, self.ffn)
+
+    def route(self, logits: torch.Tensor) -> None:
+        assert logits.dtype == torch.float32 and logits.shape == (self.T, self.E) and logits.is_contiguous()
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib_ep().b200collEpRoute(logits.data_ptr(), self.top_idx.data_ptr(), self.top_w.data_ptr(), self.T, self.E, self.k, s), "b200collEpRoute")
+        train_ops.LAUNCHES += 1
+
+    def dispatch(self, x: torch.Tensor) -> None:
+        assert x.dtype == torch.bfloat16 and x.shape == (self.T, self.hidden) and x.is_contiguous()
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib_ep().b200collEpDispatch(self.comm.handle, self._win.ptr, x.data_ptr(), self.top_idx.data_ptr(), self.sent.data_ptr(), self.T,
+                                                self.k, *self._args(), s), "b200collEpDispatch")
+        train_ops.LAUNCHES += 1
+
+    def experts(self) -> None:
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib_ep().b200collEpExperts(self.comm.handle, self._win.ptr, self.w13.data_ptr(), self.w2.data_ptr(), self.xb.data_ptr(),
+                                               self.act.data_ptr(), *self._args(), s), "b200collEpExperts")
+        train_ops.LAUNCHES += 3
+
+    def combine(self) -> torch.Tensor:
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib_ep().b200collEpCombine(self.comm.handle, self._win.ptr, self.top_idx.data_ptr(), self.top_w.data_ptr(), self.sent.data_ptr(),
+                                               self.out.data_ptr(), self.T, self.k, *self._args(), s), "b200collEpCombine")
+        train_ops.LAUNCHES += 2
+        return self.out
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        self.route(logits)
+        self.dispatch(x)
+        self.experts()
+        return self.combine()
+
+    def counts(self):
+        c = (ctypes.c_uint * self.el)()
+        d = ctypes.c_int()
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib_ep().b200collEpCounts(self.comm.handle, self._win.ptr, *self._args(), c, ctypes.byref(d), s), "b200collEpCounts")
+        return list(c), d.value
+
+    # ---- plain PyTorch oracle ---------------------------------------------------------------------------
+    def reference_forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        n, el, k, T, H = self.n, self.el, self.k, self.T, self.hidden
+        top_v, top_i = torch.topk(logits, k, dim=-1)
+        w = torch.softmax(top_v, dim=-1)
+        q, sc = quantize_e4m3_per128(x)
+        xd = dequantize_e4m3_per128(q, sc)                      # what the experts see after fp8 transport
+        flat_e = top_i.reshape(-1)                               # [T*k]
+        flat_t = torch.arange(T, device=x.device).repeat_interleave(k)
+        dst = flat_e // el
+        order = torch.argsort(dst, stable=True)
+        send_rows = xd[flat_t[order]].contiguous()
+        send_e = (flat_e[order] % el).to(torch.int32).contiguous()
+        send_counts = torch.bincount(dst, minlength=n).to(torch.int64)
+        recv_counts = torch.empty_like(send_counts)
+        self.comm.all_to_all(send_counts, recv_counts)
+        sc_l, rc_l = send_counts.tolist(), recv_counts.tolist()
+        sd = [sum(sc_l[:i]) for i in range(n)]
+        rd = [sum(rc_l[:i]) for i in range(n)]
+        R = sum(rc_l)
+        recv_rows = torch.empty(max(R, 1), H, dtype=torch.bfloat16, device=x.device)
+        recv_e = torch.empty(max(R, 1), dtype=torch.int32, device=x.device)
+        self.comm.all_to_allv(send_rows, [c * H for c in sc_l], [d * H for d in sd], recv_rows, [c * H for c in rc_l], [d * H for d in rd])
+        self.comm.all_to_allv(send_e, sc_l, sd, recv_e, rc_l, rd)
+        y = torch.zeros(max(R, 1), H, dtype=torch.bfloat16, device=x.device)
+        for e in range(el):
+            m = (recv_e[:R] == e).nonzero().flatten()
+            if m.numel() == 0:
+                continue
+            xe = recv_rows[m]
+            a = (torch.nn.functional.silu((xe @ self.w_gate[e].t()).float()) * (xe @ self.w_up[e].t()).float()).to(torch.bfloat16)
+            y[m] = a @ self.w_down[e].t()
+        back = torch.empty(T * k, H, dtype=torch.bfloat16, device=x.device)
+        self.comm.all_to_allv(y, [c * H for c in rc_l], [d * H for d in rd], back, [c * H for c in sc_l], [d * H for d in sd])
+        contrib = torch.empty(T * k, H, dtype=torch.float32, device=x.device)
+        contrib[order] = back.float()
+        out = (contrib.view(T, k, H) * w.unsqueeze(-1)).sum(1)
+        return out.to(torch.bfloat16)
+
+    def free(self) -> None:
+        torch.cuda.synchronize()
+        self._win.free()
