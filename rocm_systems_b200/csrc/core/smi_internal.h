@@ -1,0 +1,38 @@
+// Shared between the two halves of b200smi (topo.cc, health.cc).
+#pragma once
+
+#include <nvml.h>
+
+#include "b200coll/smi.h"
+
+namespace b200 {
+namespace smi {
+
+struct NvmlFns {
+  nvmlReturn_t (*init)(void) = nullptr;
+  nvmlReturn_t (*shutdown)(void) = nullptr;
+  nvmlReturn_t (*count)(unsigned int*) = nullptr;
+  nvmlReturn_t (*handle)(unsigned int, nvmlDevice_t*) = nullptr;
+  nvmlReturn_t (*name)(nvmlDevice_t, char*, unsigned int) = nullptr;
+  nvmlReturn_t (*uuid)(nvmlDevice_t, char*, unsigned int) = nullptr;
+  nvmlReturn_t (*pci)(nvmlDevice_t, nvmlPciInfo_t*) = nullptr;
+  nvmlReturn_t (*clock)(nvmlDevice_t, nvmlClockType_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*maxClock)(nvmlDevice_t, nvmlClockType_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*power)(nvmlDevice_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*powerLimit)(nvmlDevice_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*temp)(nvmlDevice_t, nvmlTemperatureSensors_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*mem)(nvmlDevice_t, nvmlMemory_t*) = nullptr;
+  nvmlReturn_t (*ecc)(nvmlDevice_t, nvmlMemoryErrorType_t, nvmlEccCounterType_t, unsigned long long*) = nullptr;
+  nvmlReturn_t (*reasons)(nvmlDevice_t, unsigned long long*) = nullptr;
+  nvmlReturn_t (*util)(nvmlDevice_t, nvmlUtilization_t*) = nullptr;
+  nvmlReturn_t (*nvlinkState)(nvmlDevice_t, unsigned int, nvmlEnableState_t*) = nullptr;
+  nvmlReturn_t (*nvlinkRemote)(nvmlDevice_t, unsigned int, nvmlPciInfo_t*) = nullptr;
+  nvmlReturn_t (*setPowerLimit)(nvmlDevice_t, unsigned int) = nullptr;
+};
+extern NvmlFns gN;
+bool ready();
+b200smi_status_t deviceHandle(int device, nvmlDevice_t* h);
+void watchStopLocked();  // health.cc: stops the sampler thread (called at the last shutdown)
+
+}  // namespace smi
+}  // namespace b200

@@ -1,0 +1,264 @@
+// b200smi part 1: NVML loading, device readings and the link (topology) table.
+//
+// The reference discovers topology from sysfs (libhsakmt/src/topology.c:56-59, 1634-1931) and
+// exposes it through rocm-smi (rocm-smi-lib/src/rocm_smi.cc:4665-4910). On a B200 box every pair of
+// GPUs is one NVSwitch hop apart at full link bandwidth, so the table is uniform; it is still
+// derived from what NVML and the CUDA runtime report (links up, peer access, native atomics).
+#include <cuda_runtime_api.h>
+#include <dlfcn.h>
+#include <nvml.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "b200coll/smi.h"
+#include "mem.h"
+#include "smi_internal.h"
+
+namespace b200 {
+namespace smi {
+
+static std::mutex gMu;
+static int gRef = 0;
+static void* gLib = nullptr;
+NvmlFns gN;
+
+template <typename F> static bool sym(const char* name, F* out, bool required = true) {
+  *out = reinterpret_cast<F>(dlsym(gLib, name));
+  return *out != nullptr || !required;
+}
+
+static bool loadNvml() {
+  const char* override = getenv("B200SMI_NVML_LIBRARY");
+  const char* names[] = {override, "libnvidia-ml.so.1", "libnvidia-ml.so"};
+  for (const char* n : names) {
+    if (!n || !*n) continue;
+    gLib = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+    if (gLib) break;
+  }
+  if (!gLib) return false;
+  bool ok = true;
+  ok &= sym("nvmlInit_v2", &gN.init);
+  ok &= sym("nvmlShutdown", &gN.shutdown);
+  ok &= sym("nvmlDeviceGetCount_v2", &gN.count);
+  ok &= sym("nvmlDeviceGetHandleByIndex_v2", &gN.handle);
+  ok &= sym("nvmlDeviceGetName", &gN.name);
+  sym("nvmlDeviceGetUUID", &gN.uuid, false);
+  sym("nvmlDeviceGetPciInfo_v3", &gN.pci, false);
+  sym("nvmlDeviceGetClockInfo", &gN.clock, false);
+  sym("nvmlDeviceGetMaxClockInfo", &gN.maxClock, false);
+  sym("nvmlDeviceGetPowerUsage", &gN.power, false);
+  sym("nvmlDeviceGetEnforcedPowerLimit", &gN.powerLimit, false);
+  sym("nvmlDeviceGetTemperature", &gN.temp, false);
+  sym("nvmlDeviceGetMemoryInfo", &gN.mem, false);
+  sym("nvmlDeviceGetTotalEccErrors", &gN.ecc, false);
+  sym("nvmlDeviceGetCurrentClocksEventReasons", &gN.reasons, false);
+  if (!gN.reasons) sym("nvmlDeviceGetCurrentClocksThrottleReasons", &gN.reasons, false);
+  sym("nvmlDeviceGetUtilizationRates", &gN.util, false);
+  sym("nvmlDeviceGetNvLinkState", &gN.nvlinkState, false);
+  sym("nvmlDeviceGetNvLinkRemotePciInfo_v2", &gN.nvlinkRemote, false);
+  sym("nvmlDeviceSetPowerManagementLimit", &gN.setPowerLimit, false);
+  if (!ok) {
+    dlclose(gLib);
+    gLib = nullptr;
+  }
+  return ok;
+}
+
+bool ready() { return gRef > 0; }
+
+b200smi_status_t deviceHandle(int device, nvmlDevice_t* h) {
+  if (!ready()) return B200SMI_ERR_NOT_LOADED;
+  unsigned n = 0;
+  if (gN.count(&n) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  if (device < 0 || device >= (int)n) return B200SMI_ERR_INVALID;
+  return gN.handle((unsigned)device, h) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+static void countLinks(nvmlDevice_t h, uint32_t* total, uint32_t* active) {
+  *total = 0;
+  *active = 0;
+  if (!gN.nvlinkState) return;
+  for (unsigned l = 0; l < NVML_NVLINK_MAX_LINKS; l++) {
+    nvmlEnableState_t st;
+    nvmlReturn_t r = gN.nvlinkState(h, l, &st);
+    if (r != NVML_SUCCESS) continue;  // link index not present on this part
+    (*total)++;
+    if (st == NVML_FEATURE_ENABLED) (*active)++;
+  }
+}
+
+}  // namespace smi
+}  // namespace b200
+
+using namespace b200::smi;
+
+extern "C" {
+
+b200smi_status_t b200smi_init(void) {
+  std::lock_guard<std::mutex> lk(gMu);
+  if (gRef > 0) { gRef++; return B200SMI_OK; }
+  if (!gLib && !loadNvml()) return B200SMI_ERR_NOT_LOADED;
+  if (gN.init() != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  gRef = 1;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_shutdown(void) {
+  std::lock_guard<std::mutex> lk(gMu);
+  if (gRef == 0) return B200SMI_ERR_NOT_LOADED;
+  if (--gRef == 0) {
+    watchStopLocked();
+    gN.shutdown();
+  }
+  return B200SMI_OK;
+}
+
+const char* b200smi_status_string(b200smi_status_t s) {
+  switch (s) {
+    case B200SMI_OK: return "ok";
+    case B200SMI_ERR_NOT_LOADED: return "NVML is not loaded (no driver on this machine, or b200smi_init was not called)";
+    case B200SMI_ERR_INVALID: return "invalid argument";
+    case B200SMI_ERR_NOT_SUPPORTED: return "not supported by this device or driver";
+    case B200SMI_ERR_PERMISSION: return "changing GPU settings is disabled (needs B200SMI_ALLOW_SET=1 and allow=1)";
+    default: return "NVML call failed";
+  }
+}
+
+b200smi_status_t b200smi_device_count(int* count) {
+  if (!count) return B200SMI_ERR_INVALID;
+  if (!ready()) return B200SMI_ERR_NOT_LOADED;
+  unsigned n = 0;
+  if (gN.count(&n) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  *count = (int)n;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_device_info(int device, b200smi_device_info_t* info) {
+  if (!info) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  memset(info, 0, sizeof(*info));
+  gN.name(h, info->name, sizeof(info->name));
+  if (gN.uuid) gN.uuid(h, info->uuid, sizeof(info->uuid));
+  if (gN.pci) {
+    nvmlPciInfo_t p;
+    if (gN.pci(h, &p) == NVML_SUCCESS) strncpy(info->busId, p.busId, sizeof(info->busId) - 1);
+  }
+  if (gN.clock) {
+    gN.clock(h, NVML_CLOCK_SM, &info->smClockMhz);
+    gN.clock(h, NVML_CLOCK_MEM, &info->memClockMhz);
+  }
+  if (gN.maxClock) {
+    gN.maxClock(h, NVML_CLOCK_SM, &info->smClockMaxMhz);
+    gN.maxClock(h, NVML_CLOCK_MEM, &info->memClockMaxMhz);
+  }
+  if (gN.power) gN.power(h, &info->powerMilliwatt);
+  if (gN.powerLimit) gN.powerLimit(h, &info->powerLimitMilliwatt);
+  if (gN.temp) gN.temp(h, NVML_TEMPERATURE_GPU, &info->temperatureC);
+  if (gN.mem) {
+    nvmlMemory_t m;
+    if (gN.mem(h, &m) == NVML_SUCCESS) { info->memTotalBytes = m.total; info->memUsedBytes = m.used; }
+  }
+  if (gN.ecc) {
+    unsigned long long c = 0;
+    if (gN.ecc(h, NVML_MEMORY_ERROR_TYPE_CORRECTED, NVML_VOLATILE_ECC, &c) == NVML_SUCCESS) info->eccCorrected = c;
+    if (gN.ecc(h, NVML_MEMORY_ERROR_TYPE_UNCORRECTED, NVML_VOLATILE_ECC, &c) == NVML_SUCCESS) info->eccUncorrected = c;
+  }
+  if (gN.reasons) {
+    unsigned long long r = 0;
+    if (gN.reasons(h, &r) == NVML_SUCCESS) info->throttleReasons = r;
+  }
+  if (gN.util) {
+    nvmlUtilization_t u;
+    if (gN.util(h, &u) == NVML_SUCCESS) { info->gpuUtilPct = u.gpu; info->memUtilPct = u.memory; }
+  }
+  countLinks(h, &info->nvlinkCount, &info->nvlinkActive);
+  b200::MemCaps caps;
+  if (b200::queryMemCaps(device, &caps) == ncclSuccess) info->multicastCapable = caps.multicast ? 1 : 0;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_read_field(int device, int field, double* value) {
+  if (!value) return B200SMI_ERR_INVALID;
+  b200smi_device_info_t i;
+  b200smi_status_t st = b200smi_device_info(device, &i);
+  if (st != B200SMI_OK) return st;
+  switch (field) {
+    case B200SMI_FIELD_SM_CLOCK: *value = i.smClockMhz; break;
+    case B200SMI_FIELD_MEM_CLOCK: *value = i.memClockMhz; break;
+    case B200SMI_FIELD_POWER: *value = i.powerMilliwatt / 1000.0; break;
+    case B200SMI_FIELD_TEMP: *value = i.temperatureC; break;
+    case B200SMI_FIELD_MEM_USED: *value = (double)i.memUsedBytes; break;
+    case B200SMI_FIELD_GPU_UTIL: *value = i.gpuUtilPct; break;
+    case B200SMI_FIELD_MEM_UTIL: *value = i.memUtilPct; break;
+    case B200SMI_FIELD_ECC_CORRECTED: *value = (double)i.eccCorrected; break;
+    case B200SMI_FIELD_ECC_UNCORRECTED: *value = (double)i.eccUncorrected; break;
+    case B200SMI_FIELD_THROTTLE_REASONS: *value = (double)i.throttleReasons; break;
+    case B200SMI_FIELD_NVLINK_ACTIVE: *value = i.nvlinkActive; break;
+    default: return B200SMI_ERR_INVALID;
+  }
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_link(int from, int to, b200smi_link_t* link) {
+  if (!link) return B200SMI_ERR_INVALID;
+  nvmlDevice_t hf, ht;
+  b200smi_status_t st = deviceHandle(from, &hf);
+  if (st != B200SMI_OK) return st;
+  st = deviceHandle(to, &ht);
+  if (st != B200SMI_OK) return st;
+  memset(link, 0, sizeof(*link));
+  link->perfRank = -1;
+  if (from == to) {
+    link->type = B200SMI_LINK_SELF;
+    link->p2pAccessible = link->atomics32 = link->atomics64 = link->coherent = 1;
+    return B200SMI_OK;
+  }
+  uint32_t total = 0, active = 0, total2 = 0, active2 = 0;
+  countLinks(hf, &total, &active);
+  countLinks(ht, &total2, &active2);
+  const uint32_t up = active < active2 ? active : active2;
+  if (up > 0) {
+    // Every link of a B200 goes to the NVSwitch fabric, so the pair is one switch hop apart and
+    // can use all links that are up on both ends: 50 GB/s per direction per NVLink-5 link.
+    link->type = B200SMI_LINK_NVLINK;
+    link->hops = 1;
+    link->weight = 15;
+    link->nvlinks = up;
+    link->minBandwidthMBps = 50000ull;
+    link->maxBandwidthMBps = 50000ull * up;
+  } else {
+    link->type = B200SMI_LINK_PCIE;
+    link->hops = 2;
+    link->weight = 40;
+    link->minBandwidthMBps = link->maxBandwidthMBps = 64000ull;
+  }
+  int can = 0, atom = 0, rank = -1;
+  if (cudaDeviceCanAccessPeer(&can, from, to) == cudaSuccess) {
+    link->p2pAccessible = can;
+    if (cudaDeviceGetP2PAttribute(&atom, cudaDevP2PAttrNativeAtomicSupported, from, to) == cudaSuccess) link->atomics32 = link->atomics64 = atom;
+    if (cudaDeviceGetP2PAttribute(&rank, cudaDevP2PAttrPerformanceRank, from, to) == cudaSuccess) link->perfRank = rank;
+  } else {
+    (void)cudaGetLastError();
+    // No CUDA runtime view (e.g. a management-only process): NVLink peers are addressable and atomic-capable.
+    link->p2pAccessible = link->type == B200SMI_LINK_NVLINK;
+    link->atomics32 = link->atomics64 = link->type == B200SMI_LINK_NVLINK;
+  }
+  link->coherent = link->p2pAccessible;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_set_power_limit(int device, uint32_t milliwatt, int allow) {
+  const char* env = getenv("B200SMI_ALLOW_SET");
+  if (!allow || !env || strcmp(env, "1") != 0) return B200SMI_ERR_PERMISSION;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.setPowerLimit) return B200SMI_ERR_NOT_SUPPORTED;
+  return gN.setPowerLimit(h, milliwatt) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+}  // extern "C"

@@ -1,0 +1,206 @@
+"""``b200-smi``: device readings and topology tables, the CLI counterpart of rocm-smi
+(rocm-smi-lib/python_smi_tools/rocm_smi.py: showWeightTopology :3279, showHopsTopology :3326,
+showTypeTopology :3372, showNodesBw :3460) on top of the native ``b200smi_*`` API.
+
+    python -m rocm_systems_b200.tools.smi --showall
+    python -m rocm_systems_b200.tools.smi --showtopo [--json]
+
+Setters (``--setpowerlimit``) do nothing unless ``--allow-set`` is given AND B200SMI_ALLOW_SET=1 is
+in the environment; GPUs on shared hosts must be left as they were found.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import sys
+
+from .. import _lib
+
+FIELDS = {"sm_clock": 1, "mem_clock": 2, "power": 3, "temp": 4, "mem_used": 5, "gpu_util": 6, "mem_util": 7, "ecc_corrected": 8,
+          "ecc_uncorrected": 9, "throttle_reasons": 10, "nvlink_active": 11}
+REASON_BITS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+LINK_TYPES = {0: "SELF", 1: "NVLINK", 2: "PCIE", 3: "UNKNOWN"}
+
+
+class DeviceInfo(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 96), ("uuid", ctypes.c_char * 96), ("busId", ctypes.c_char * 32),
+                ("smClockMhz", ctypes.c_uint32), ("smClockMaxMhz", ctypes.c_uint32), ("memClockMhz", ctypes.c_uint32), ("memClockMaxMhz", ctypes.c_uint32),
+                ("powerMilliwatt", ctypes.c_uint32), ("powerLimitMilliwatt", ctypes.c_uint32), ("temperatureC", ctypes.c_uint32),
+                ("memTotalBytes", ctypes.c_uint64), ("memUsedBytes", ctypes.c_uint64), ("eccCorrected", ctypes.c_uint64), ("eccUncorrected", ctypes.c_uint64),
+                ("throttleReasons", ctypes.c_uint64), ("gpuUtilPct", ctypes.c_uint32), ("memUtilPct", ctypes.c_uint32),
+                ("nvlinkCount", ctypes.c_uint32), ("nvlinkActive", ctypes.c_uint32), ("multicastCapable", ctypes.c_uint32)]
+
+
+class Link(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("hops", ctypes.c_uint32), ("weight", ctypes.c_uint32), ("nvlinks", ctypes.c_uint32),
+                ("minBandwidthMBps", ctypes.c_uint64), ("maxBandwidthMBps", ctypes.c_uint64), ("p2pAccessible", ctypes.c_int),
+                ("atomics32", ctypes.c_int), ("atomics64", ctypes.c_int), ("coherent", ctypes.c_int), ("perfRank", ctypes.c_int)]
+
+
+class Sample(ctypes.Structure):
+    _fields_ = [("timestampNs", ctypes.c_uint64), ("value", ctypes.c_double)]
+
+
+class Stats(ctypes.Structure):
+    _fields_ = [("min", ctypes.c_double), ("max", ctypes.c_double), ("avg", ctypes.c_double), ("last", ctypes.c_double), ("samples", ctypes.c_uint64)]
+
+
+POLICY_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_double, ctypes.c_void_p)
+
+
+class Smi:
+    """Thin object wrapper over the C API; raises RuntimeError with the library's message."""
+
+    def __init__(self):
+        self.lib = _lib.load()
+        L = self.lib
+        L.b200smi_status_string.restype = ctypes.c_char_p
+        L.b200smi_device_info.argtypes = [ctypes.c_int, ctypes.POINTER(DeviceInfo)]
+        L.b200smi_link.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(Link)]
+        L.b200smi_read_field.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+        L.b200smi_watch_latest.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(Sample)]
+        L.b200smi_watch_history.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(Sample), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        L.b200smi_job_stats.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(Stats)]
+        L.b200smi_policy_set.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_int, POLICY_CB, ctypes.c_void_p]
+        L.b200smi_health.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_char_p, ctypes.c_int]
+        L.b200smi_set_power_limit.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_int]
+        self._cbs = []
+        self._ck(L.b200smi_init())
+
+    def _ck(self, st: int) -> None:
+        if st != 0:
+            raise RuntimeError(self.lib.b200smi_status_string(st).decode())
+
+    def close(self) -> None:
+        self.lib.b200smi_shutdown()
+
+    def count(self) -> int:
+        n = ctypes.c_int()
+        self._ck(self.lib.b200smi_device_count(ctypes.byref(n)))
+        return n.value
+
+    def info(self, dev: int) -> dict:
+        i = DeviceInfo()
+        self._ck(self.lib.b200smi_device_info(dev, ctypes.byref(i)))
+        d = {f[0]: getattr(i, f[0]) for f in DeviceInfo._fields_}
+        for k in ("name", "uuid", "busId"):
+            d[k] = d[k].decode()
+        d["throttleReasonNames"] = [n for b, n in REASON_BITS.items() if d["throttleReasons"] & b]
+        return d
+
+    def link(self, a: int, b: int) -> dict:
+        l = Link()
+        self._ck(self.lib.b200smi_link(a, b, ctypes.byref(l)))
+        d = {f[0]: getattr(l, f[0]) for f in Link._fields_}
+        d["typeName"] = LINK_TYPES.get(d["type"], "UNKNOWN")
+        return d
+
+    def read(self, dev: int, field: str) -> float:
+        v = ctypes.c_double()
+        self._ck(self.lib.b200smi_read_field(dev, FIELDS[field], ctypes.byref(v)))
+        return v.value
+
+    def watch_start(self, devs, fields, period_ms=1000, keep=600) -> None:
+        da = (ctypes.c_int * len(devs))(*devs)
+        fa = (ctypes.c_int * len(fields))(*[FIELDS[f] for f in fields])
+        self._ck(self.lib.b200smi_watch_start(da, len(devs), fa, len(fields), period_ms, keep))
+
+    def watch_stop(self) -> None:
+        self.lib.b200smi_watch_stop()
+
+    def history(self, dev: int, field: str, max_n: int = 4096):
+        n = ctypes.c_int()
+        arr = (Sample * max_n)()
+        self._ck(self.lib.b200smi_watch_history(dev, FIELDS[field], arr, max_n, ctypes.byref(n)))
+        return [(arr[i].timestampNs, arr[i].value) for i in range(min(n.value, max_n))]
+
+    def job_start(self, job: str) -> None:
+        self._ck(self.lib.b200smi_job_start(job.encode()))
+
+    def job_stop(self, job: str) -> None:
+        self._ck(self.lib.b200smi_job_stop(job.encode()))
+
+    def job_stats(self, job: str, dev: int, field: str) -> dict:
+        s = Stats()
+        self._ck(self.lib.b200smi_job_stats(job.encode(), dev, FIELDS[field], ctypes.byref(s)))
+        return {f[0]: getattr(s, f[0]) for f in Stats._fields_}
+
+    def policy(self, dev: int, field: str, threshold: float, above: bool, fn) -> None:
+        cb = POLICY_CB(lambda d, f, v, t, u: fn(d, f, v, t))
+        self._cbs.append(cb)
+        self._ck(self.lib.b200smi_policy_set(dev, FIELDS[field], threshold, 1 if above else -1, cb, None))
+
+    def health(self, dev: int):
+        lv = ctypes.c_int()
+        buf = ctypes.create_string_buffer(256)
+        self._ck(self.lib.b200smi_health(dev, ctypes.byref(lv), buf, 256))
+        return lv.value, buf.value.decode()
+
+    def set_power_limit(self, dev: int, milliwatt: int, allow: bool) -> None:
+        self._ck(self.lib.b200smi_set_power_limit(dev, milliwatt, int(allow)))
+
+
+def _matrix(smi: Smi, key: str, n: int):
+    return [[smi.link(i, j)[key] for j in range(n)] for i in range(n)]
+
+
+def _print_matrix(title: str, m, n: int) -> None:
+    print(f"\n=== {title} ===")
+    print("       " + "".join(f"GPU{j:<9}" for j in range(n)))
+    for i in range(n):
+        print(f"GPU{i:<4}" + "".join(f"{str(m[i][j]):<12}" for j in range(n)))
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="b200-smi", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--showall", action="store_true")
+    ap.add_argument("--showtopo", action="store_true", help="weight, hops, type and bandwidth tables")
+    ap.add_argument("--showhealth", action="store_true")
+    ap.add_argument("--json", action="store_true")
+    ap.add_argument("--setpowerlimit", nargs=2, metavar=("GPU", "WATTS"))
+    ap.add_argument("--allow-set", action="store_true", help="required (with B200SMI_ALLOW_SET=1) before any setter acts")
+    a = ap.parse_args(argv)
+    try:
+        smi = Smi()
+    except RuntimeError as e:
+        print(f"b200-smi: {e}", file=sys.stderr)
+        return 1
+    n = smi.count()
+    out = {}
+    if a.setpowerlimit:
+        try:
+            smi.set_power_limit(int(a.setpowerlimit[0]), int(float(a.setpowerlimit[1]) * 1000), a.allow_set)
+            print(f"power limit of GPU {a.setpowerlimit[0]} set to {a.setpowerlimit[1]} W")
+        except RuntimeError as e:
+            print(f"b200-smi: {e}", file=sys.stderr)
+            return 2
+    if a.showall or not (a.showtopo or a.showhealth or a.setpowerlimit):
+        out["devices"] = [smi.info(i) for i in range(n)]
+        if not a.json:
+            print(f"{'GPU':<4}{'Name':<22}{'Bus':<18}{'SM MHz':<12}{'Power W':<10}{'Temp C':<8}{'Mem used/total GiB':<22}{'NVLink':<8}{'Throttle'}")
+            for i, d in enumerate(out["devices"]):
+                print(f"{i:<4}{d['name'][:20]:<22}{d['busId']:<18}{str(d['smClockMhz']) + '/' + str(d['smClockMaxMhz']):<12}{d['powerMilliwatt'] / 1000:<10.1f}"
+                      f"{d['temperatureC']:<8}{d['memUsedBytes'] / 2**30:>6.1f} / {d['memTotalBytes'] / 2**30:<11.1f}{str(d['nvlinkActive']) + '/' + str(d['nvlinkCount']):<8}"
+                      f"{','.join(d['throttleReasonNames']) or '-'}")
+    if a.showtopo:
+        out["topology"] = {k: _matrix(smi, k, n) for k in ("weight", "hops", "typeName", "maxBandwidthMBps", "p2pAccessible", "atomics64")}
+        if not a.json:
+            _print_matrix("Weight between two GPUs", out["topology"]["weight"], n)
+            _print_matrix("Hops between two GPUs", out["topology"]["hops"], n)
+            _print_matrix("Link type between two GPUs", out["topology"]["typeName"], n)
+            _print_matrix("Max bandwidth (MB/s per direction)", out["topology"]["maxBandwidthMBps"], n)
+    if a.showhealth:
+        out["health"] = [dict(zip(("level", "reason"), smi.health(i))) for i in range(n)]
+        if not a.json:
+            for i, h in enumerate(out["health"]):
+                print(f"GPU{i}: {('PASS', 'WARN', 'FAIL')[h['level']]} - {h['reason']}")
+    if a.json:
+        print(json.dumps(out, indent=1))
+    smi.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,45 @@
+/* A stand-in for libnvidia-ml used by the CPU tests of b200smi: a fixed fleet of FAKE_NVML_GPUS
+ * (default 8) "B200" devices with 18 NVLinks each. Environment knobs change what it reports:
+ *   FAKE_NVML_LINK_DOWN=<gpu>      one link of that GPU is reported down
+ *   FAKE_NVML_ECC=<gpu>            that GPU reports 3 uncorrected ECC errors
+ *   FAKE_NVML_TEMP=<celsius>       temperature of every GPU
+ *   FAKE_NVML_RAMP=1               power rises by 10 W on every read (for watch / policy tests)
+ * The last power limit a setter wrote is kept in memory and returned by the getter. */
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+typedef struct fake_dev { int idx; } *nvmlDevice_t;
+typedef int nvmlReturn_t;
+#define NVML_SUCCESS 0
+#define NVML_ERROR_INVALID_ARGUMENT 2
+typedef struct { char busIdLegacy[16]; unsigned int domain, bus, device, pciDeviceId, pciSubSystemId; char busId[32]; } nvmlPciInfo_t;
+typedef struct { unsigned long long total, free, used; } nvmlMemory_t;
+typedef struct { unsigned int gpu, memory; } nvmlUtilization_t;
+
+static struct fake_dev devs[16];
+static unsigned int power_limit[16];
+static unsigned int reads = 0;
+
+static int ngpus(void) { const char* e = getenv("FAKE_NVML_GPUS"); int n = e ? atoi(e) : 8; return n < 1 ? 1 : (n > 16 ? 16 : n); }
+static int envint(const char* k, int d) { const char* e = getenv(k); return e ? atoi(e) : d; }
+
+nvmlReturn_t nvmlInit_v2(void) { for (int i = 0; i < 16; i++) { devs[i].idx = i; if (!power_limit[i]) power_limit[i] = 1000000; } return NVML_SUCCESS; }
+nvmlReturn_t nvmlShutdown(void) { return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetCount_v2(unsigned int* n) { *n = (unsigned)ngpus(); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetHandleByIndex_v2(unsigned int i, nvmlDevice_t* d) { if ((int)i >= ngpus()) return NVML_ERROR_INVALID_ARGUMENT; *d = &devs[i]; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetName(nvmlDevice_t d, char* s, unsigned int n) { (void)d; snprintf(s, n, "NVIDIA B200 (fake)"); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetUUID(nvmlDevice_t d, char* s, unsigned int n) { snprintf(s, n, "GPU-fake-%04d", d->idx); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetPciInfo_v3(nvmlDevice_t d, nvmlPciInfo_t* p) { memset(p, 0, sizeof(*p)); snprintf(p->busId, sizeof(p->busId), "00000000:%02X:00.0", 0x10 + d->idx); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetClockInfo(nvmlDevice_t d, int t, unsigned int* c) { (void)d; *c = t == 1 /*SM*/ ? 1500 : 3996; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetMaxClockInfo(nvmlDevice_t d, int t, unsigned int* c) { (void)d; *c = t == 1 ? 1965 : 3996; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetPowerUsage(nvmlDevice_t d, unsigned int* mw) { (void)d; reads++; *mw = 200000 + (envint("FAKE_NVML_RAMP", 0) ? reads * 10000 : 0); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetEnforcedPowerLimit(nvmlDevice_t d, unsigned int* mw) { *mw = power_limit[d->idx]; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceSetPowerManagementLimit(nvmlDevice_t d, unsigned int mw) { power_limit[d->idx] = mw; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetTemperature(nvmlDevice_t d, int s, unsigned int* t) { (void)d; (void)s; *t = (unsigned)envint("FAKE_NVML_TEMP", 45); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetMemoryInfo(nvmlDevice_t d, nvmlMemory_t* m) { (void)d; m->total = 183359ull << 20; m->used = 1024ull << 20; m->free = m->total - m->used; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetTotalEccErrors(nvmlDevice_t d, int type, int counter, unsigned long long* c) { (void)counter; *c = (type == 1 /*uncorrected*/ && envint("FAKE_NVML_ECC", -1) == d->idx) ? 3 : 0; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetCurrentClocksEventReasons(nvmlDevice_t d, unsigned long long* r) { (void)d; *r = 0x4; /* sw power cap */ return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetUtilizationRates(nvmlDevice_t d, nvmlUtilization_t* u) { (void)d; u->gpu = 97; u->memory = 40; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetNvLinkState(nvmlDevice_t d, unsigned int link, int* active) { if (link >= 18) return NVML_ERROR_INVALID_ARGUMENT; *active = !(envint("FAKE_NVML_LINK_DOWN", -1) == d->idx && link == 5); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetNvLinkRemotePciInfo_v2(nvmlDevice_t d, unsigned int link, nvmlPciInfo_t* p) { (void)d; (void)link; memset(p, 0, sizeof(*p)); snprintf(p->busId, sizeof(p->busId), "00000000:F0:00.0"); return NVML_SUCCESS; }

@@ -1,0 +1,103 @@
+"""b200smi against a fake NVML (no GPU): readings, topology table, watches, job statistics,
+policies, health and the guarded setter. The reference tests rocm-smi against overridden sysfs
+trees the same way (rocm-smi-lib/src/rocm_smi_main.cc:522-527)."""
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def fake_nvml(tmp_path_factory):
+    out = tmp_path_factory.mktemp("fake_nvml") / "libfake_nvml.so"
+    subprocess.check_call(["gcc", "-shared", "-fPIC", "-O1", "-o", str(out), str(ROOT / "tests" / "fake_nvml" / "fake_nvml.c")])
+    return str(out)
+
+
+def _run(code: str, fake: str, env=None):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake, PYTHONPATH=str(ROOT))
+    e.update(env or {})
+    p = subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr
+    return p.stdout
+
+
+def test_readings_and_topology(fake_nvml):
+    out = _run("""
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+assert s.count() == 8
+i = s.info(3)
+assert i['name'].startswith('NVIDIA B200') and i['nvlinkCount'] == 18 and i['nvlinkActive'] == 18
+assert i['smClockMaxMhz'] == 1965 and 'sw_power_cap' in i['throttleReasonNames']
+l = s.link(0, 5)
+assert l['typeName'] == 'NVLINK' and l['hops'] == 1 and l['weight'] == 15 and l['nvlinks'] == 18 and l['maxBandwidthMBps'] == 900000
+assert s.link(2, 2)['typeName'] == 'SELF'
+print('ok')
+""", fake_nvml)
+    assert "ok" in out
+
+
+def test_cli_tables(fake_nvml):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="4")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showall", "--showtopo", "--showhealth"], env=e, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    assert "Weight between two GPUs" in p.stdout and "NVLINK" in p.stdout and "PASS" in p.stdout
+
+
+def test_health_flags_link_down_and_ecc(fake_nvml):
+    out = _run("""
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+print(s.health(1)); print(s.health(2)); print(s.health(0))
+assert s.link(1, 0)['nvlinks'] == 17
+""", fake_nvml, {"FAKE_NVML_LINK_DOWN": "1", "FAKE_NVML_ECC": "2"})
+    lines = out.strip().splitlines()
+    assert lines[0].startswith("(2") and "17 of 18" in lines[0]
+    assert lines[1].startswith("(2") and "uncorrected ECC" in lines[1]
+    assert lines[2].startswith("(0")
+
+
+def test_watch_job_stats_and_policy(fake_nvml):
+    out = _run("""
+import time
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+fired = []
+s.policy(0, 'power', 260.0, True, lambda d, f, v, t: fired.append((d, v)))
+s.job_start('job1')
+s.watch_start([0, 1], ['power', 'temp'], period_ms=20, keep=50)
+time.sleep(0.6)
+s.job_stop('job1')
+s.watch_stop()
+h = s.history(0, 'power')
+st = s.job_stats('job1', 0, 'power')
+assert len(h) >= 5 and h[-1][1] > h[0][1]
+assert st['samples'] >= 5 and st['max'] > st['min'] and st['min'] <= st['avg'] <= st['max']
+assert fired and fired[0][0] == 0 and fired[0][1] > 260.0 and len(fired) == 1   # latched: fires once per excursion
+print('ok')
+""", fake_nvml, {"FAKE_NVML_RAMP": "1"})
+    assert "ok" in out
+
+
+def test_setter_is_off_by_default(fake_nvml):
+    code = """
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+for allow in (False, True):
+    try:
+        s.set_power_limit(0, 700000, allow)
+        print('set', allow)
+    except RuntimeError as e:
+        print('refused', allow)
+print(s.info(0)['powerLimitMilliwatt'])
+"""
+    out = _run(code, fake_nvml).split()
+    assert out == ["refused", "False", "refused", "True", "1000000"]          # env switch absent: nothing is written
+    out = _run(code, fake_nvml, {"B200SMI_ALLOW_SET": "1"}).split()
+    assert out == ["refused", "False", "set", "True", "700000"]               # only the fake GPU is ever touched
