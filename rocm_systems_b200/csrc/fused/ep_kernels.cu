@@ -261,33 +261,33 @@ template <int BN, bool SWIGLU> struct GroupPolicy {
   __device__ __forceinline__ int bRow(int tm, int tn) const { return (tm / capTiles) * wRows + tn * BN; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ void tileDone(int, int, int, int) const {}
-  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int row, bool) const {
+  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int q, int lane, uint8_t* sw) const {
     const int e = tm / capTiles;
-    const bool rowOk = row - e * cap < have(e);
+    const int row0 = tm * BM + q * 32;
+    const int rowsHave = have(e) - (row0 - e * cap);  // rows of this warp's 32 that hold tokens
     if constexpr (SWIGLU) {
-#pragma unroll 1
-      for (int c = 0; c < BN / 64; c++) {
-        uint32_t g[32], u[32];
-        sm100::tmemLoad32(taddr + c * 32, g);
-        sm100::tmemLoad32(taddr + BN / 2 + c * 32, u);
-        sm100::tmemLoadWait();
+      drainStaged(
+          sw, lane, BN / 2, nOut - tn * (BN / 2),
+          [&](int c, uint32_t(&g)[32]) {
+            uint32_t u[32];
+            sm100::tmemLoad32(taddr + c * 32, g);
+            sm100::tmemLoad32(taddr + BN / 2 + c * 32, u);
+            sm100::tmemLoadWait();
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const float gv = __uint_as_float(g[i]);
-          g[i] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[i]));
-        }
-        const int col0 = tn * (BN / 2) + c * 32;
-        if (rowOk && col0 < nOut) storeRow32Bf16(out + (size_t)row * ldo + col0, g, nOut - col0);
-      }
+            for (int i = 0; i < 32; i++) {
+              const float gv = __uint_as_float(g[i]);
+              g[i] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[i]));
+            }
+          },
+          [&](int r) -> __nv_bfloat16* { return r < rowsHave ? out + (size_t)(row0 + r) * ldo + (size_t)tn * (BN / 2) : nullptr; });
     } else {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t acc[32];
-        sm100::tmemLoad32(taddr + c * 32, acc);
-        sm100::tmemLoadWait();
-        const int col0 = tn * BN + c * 32;
-        if (rowOk && col0 < nOut) storeRow32Bf16(out + (size_t)row * ldo + col0, acc, nOut - col0);
-      }
+      drainStaged(
+          sw, lane, BN, nOut - tn * BN,
+          [&](int c, uint32_t(&acc)[32]) {
+            sm100::tmemLoad32(taddr + c * 32, acc);
+            sm100::tmemLoadWait();
+          },
+          [&](int r) -> __nv_bfloat16* { return r < rowsHave ? out + (size_t)(row0 + r) * ldo + (size_t)tn * BN : nullptr; });
     }
   }
 };

@@ -65,6 +65,7 @@ cudaError_t launch(const Params& p, const PlainPolicy<BN>& pol, int ctas, cudaSt
 
 cudaError_t gemmBf16TN(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int bn, int maxCtas, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0) return cudaSuccess;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || (ldc & 7)) return cudaErrorInvalidValue;  // rows of C are written in 16-byte pieces
   if (bn != 128 && bn != 256) bn = N >= 256 ? 256 : 128;
   Params p{};
   if (!makeTileMap(&p.mapA, A, M, K, lda, BM, 2) || !makeTileMap(&p.mapB, B, N, K, ldb, bn, 2)) return cudaErrorInvalidValue;
@@ -79,8 +80,8 @@ cudaError_t gemmBf16TN(const void* A, const void* B, void* C, int M, int N, int 
   if (maxCtas > 0 && maxCtas < ctas) ctas = maxCtas;
   const int tiles = p.tilesM * p.tilesN;
   if (tiles < ctas) ctas = tiles;
-  if (bn == 256) return launch<256>(p, PlainPolicy<256>{(__nv_bfloat16*)C, ldc, N}, ctas, s);
-  return launch<128>(p, PlainPolicy<128>{(__nv_bfloat16*)C, ldc, N}, ctas, s);
+  if (bn == 256) return launch<256>(p, PlainPolicy<256>{(__nv_bfloat16*)C, ldc, N, M}, ctas, s);
+  return launch<128>(p, PlainPolicy<128>{(__nv_bfloat16*)C, ldc, N, M}, ctas, s);
 }
 
 }  // namespace gemm

@@ -24,7 +24,9 @@ template <int BN> struct Cfg {
   static constexpr uint32_t kBBytes = BN * BK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t kEpiBytesPerWarp = 32 * 128 * 2;  // 32 rows x 128 bf16 columns staged per epilogue warp
+  static constexpr size_t kSmemBytes =
+      (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * kEpiBytesPerWarp;
 };
 
 struct Params {
@@ -70,12 +72,71 @@ __device__ __forceinline__ void storeRow32Bf16(__nv_bfloat16* dst, const uint32_
   }
 }
 
+// Epilogue through shared memory, so that global (or peer) stores are whole 256-byte row segments
+// instead of 64 bytes per thread. A warp owns 32 accumulator rows. For every group of 128 output
+// columns: each lane converts its row's 4 x 32 columns to bf16 and parks them in the warp's
+// staging buffer (16-byte chunks XOR-swizzled by the row so neither phase has bank conflicts);
+// then half-warps walk the rows and write 256 contiguous bytes each.
+//   loadChunk(c, acc)  fills acc[32] (fp32 bit patterns) with output columns [32c, 32c+32) of the lane's row
+//   rowPtr(r)          destination of output column 0 of the warp's r-th row, or nullptr to skip the row
+//   outCols            output columns of this tile (multiple of 32); colLimit: how many of them exist
+template <typename LoadChunk, typename RowPtr>
+__device__ __forceinline__ void drainStaged(uint8_t* sw, int lane, int outCols, int colLimit, LoadChunk loadChunk, RowPtr rowPtr) {
+  for (int h = 0; h * 128 < outCols; h++) {
+    const int colsHere = min(128, outCols - h * 128);
+    const int chunks32 = colsHere / 32;
+#pragma unroll 1
+    for (int c = 0; c < chunks32; c++) {
+      uint32_t acc[32];
+      loadChunk(h * 4 + c, acc);
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * i]), __uint_as_float(acc[v * 8 + 2 * i + 1]));
+          ow[i] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        const int j = c * 4 + v;  // 16-byte chunk inside the 256-byte staged row
+        *reinterpret_cast<uint4*>(sw + lane * 256 + ((j ^ (lane & 7)) << 4)) = o;
+      }
+    }
+    __syncwarp();
+    const int chunksRow = colsHere / 8;       // 16-byte chunks per staged row (16 for a full group)
+    const int sub = lane & 15, half = lane >> 4;
+    const int validChunks = max(0, min(chunksRow, (colLimit - h * 128) / 8));
+#pragma unroll 1
+    for (int r2 = 0; r2 < 32; r2 += 2) {
+      const int r = r2 + half;
+      __nv_bfloat16* dst = rowPtr(r);
+      if (dst != nullptr && sub < validChunks) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sw + r * 256 + ((sub ^ (r & 7)) << 4));
+        *reinterpret_cast<uint4*>(dst + h * 128 + sub * 8) = v;
+      }
+    }
+    // Ragged right edge (fewer than 8 columns left in a chunk): element by element.
+    const int tailStart = h * 128 + validChunks * 8;
+    const int tailEnd = min(colLimit, h * 128 + colsHere);
+    if (tailStart < tailEnd) {
+      __nv_bfloat16* dst = rowPtr(lane);
+      if (dst != nullptr)
+        for (int col = tailStart; col < tailEnd; col++) {
+          const int jj = (col - h * 128) >> 3;
+          dst[col] = reinterpret_cast<const __nv_bfloat16*>(sw + lane * 256 + ((jj ^ (lane & 7)) << 4))[col & 7];
+        }
+    }
+    __syncwarp();
+  }
+}
+
 // Policy interface (all __device__):
 //   void coord(int t, int tilesM, int tilesN, int& tm, int& tn)        tile order
 //   bool valid(int tm, int tn)                                         false: the tile is skipped by every role
 //   int aRow(int tm), int bRow(int tm, int tn)                         first row of the tile in the A / B tensor maps
 //   bool waitTile(int tm, int tn, volatile int* err)                   producer: operands of the tile are in place
-//   void drain(uint32_t taddr, int tm, int tn, int row, bool rowOk)    epilogue thread: read the accumulator row at taddr (+column) and emit it
+//   void drain(uint32_t taddr, int tm, int tn, int q, int lane, uint8_t* sw)  epilogue warp q: read its 32 accumulator rows at taddr (+column)
+//                                                                      and emit them (sw: the warp's 8 KiB staging buffer)
 //   void tileDone(int tm, int tn, int q, int lane)                     epilogue thread, after its rows of the tile are out
 template <int BN, typename Policy>
 __device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, int nctas, uint8_t* smemRaw) {
@@ -90,6 +151,7 @@ __device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, i
   uint64_t* accFull = bars + 2 * C::kStages;
   uint64_t* accEmpty = accFull + 2;
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmpty + 2);
+  uint8_t* epiStage = reinterpret_cast<uint8_t*>(bars) + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* err = p.err;
@@ -189,8 +251,7 @@ __device__ __forceinline__ void gemmCta(const Params& p, Policy& pol, int cta, i
       it++;
       if (!mbarWait(&accFull[b], accPhase, err, ERR_EPI_ACC_FULL)) { ok = false; break; }
       tcFenceAfter();
-      const int row = tm * BM + q * 32 + lane;
-      pol.drain(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN), tm, tn, row, row < p.M);
+      pol.drain(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN), tm, tn, q, lane, epiStage + (size_t)q * C::kEpiBytesPerWarp);
       tcFenceBefore();
       __syncwarp();
       if (lane == 0) mbarArrive(&accEmpty[b]);
@@ -213,15 +274,16 @@ template <int BN> struct PlainPolicy {
   __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ void tileDone(int, int, int, int) const {}
-  __device__ __forceinline__ void drain(uint32_t taddr, int, int tn, int row, bool rowOk) const {
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; c++) {
-      uint32_t acc[32];
-      sm100::tmemLoad32(taddr + c * 32, acc);
-      sm100::tmemLoadWait();
-      const int col0 = tn * BN + c * 32;
-      if (rowOk && col0 < N) storeRow32Bf16(C + (size_t)row * ldc + col0, acc, N - col0);
-    }
+  int M;
+  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int q, int lane, uint8_t* sw) const {
+    const int row0 = tm * BM + q * 32;
+    drainStaged(
+        sw, lane, BN, N - tn * BN,
+        [&](int c, uint32_t(&acc)[32]) {
+          sm100::tmemLoad32(taddr + c * 32, acc);
+          sm100::tmemLoadWait();
+        },
+        [&](int r) -> __nv_bfloat16* { return row0 + r < M ? C + (size_t)(row0 + r) * ldc + (size_t)tn * BN : nullptr; });
   }
 };
 

@@ -89,33 +89,33 @@ template <int BN, bool SWIGLU> struct AgPolicy {
     return false;
   }
   __device__ __forceinline__ void tileDone(int, int, int, int) const {}
-  __device__ __forceinline__ void drain(uint32_t taddr, int, int tn, int row, bool rowOk) const {
+  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int q, int lane, uint8_t* sw) const {
+    const int row0 = tm * BM + q * 32;
     if constexpr (SWIGLU) {
       // The weight rows are interleaved per tile: BN/2 gate rows then BN/2 up rows, so one tile
       // holds both halves of BN/2 outputs.
-#pragma unroll 1
-      for (int c = 0; c < BN / 64; c++) {
-        uint32_t g[32], u[32];
-        sm100::tmemLoad32(taddr + c * 32, g);
-        sm100::tmemLoad32(taddr + BN / 2 + c * 32, u);
-        sm100::tmemLoadWait();
+      drainStaged(
+          sw, lane, BN / 2, a.nOut - tn * (BN / 2),
+          [&](int c, uint32_t(&g)[32]) {
+            uint32_t u[32];
+            sm100::tmemLoad32(taddr + c * 32, g);
+            sm100::tmemLoad32(taddr + BN / 2 + c * 32, u);
+            sm100::tmemLoadWait();
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const float gv = __uint_as_float(g[i]);
-          g[i] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[i]));
-        }
-        const int col0 = tn * (BN / 2) + c * 32;
-        if (rowOk && col0 < a.nOut) storeRow32Bf16(a.out + (size_t)row * a.ldo + col0, g, a.nOut - col0);
-      }
+            for (int i = 0; i < 32; i++) {
+              const float gv = __uint_as_float(g[i]);
+              g[i] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[i]));
+            }
+          },
+          [&](int r) -> __nv_bfloat16* { return a.out + (size_t)(row0 + r) * a.ldo + (size_t)tn * (BN / 2); });
     } else {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t acc[32];
-        sm100::tmemLoad32(taddr + c * 32, acc);
-        sm100::tmemLoadWait();
-        const int col0 = tn * BN + c * 32;
-        if (rowOk && col0 < a.nOut) storeRow32Bf16(a.out + (size_t)row * a.ldo + col0, acc, a.nOut - col0);
-      }
+      drainStaged(
+          sw, lane, BN, a.nOut - tn * BN,
+          [&](int c, uint32_t(&acc)[32]) {
+            sm100::tmemLoad32(taddr + c * 32, acc);
+            sm100::tmemLoadWait();
+          },
+          [&](int r) -> __nv_bfloat16* { return a.out + (size_t)(row0 + r) * a.ldo + (size_t)tn * BN; });
     }
   }
 };
@@ -174,19 +174,18 @@ template <int BN> struct RsPolicy {
   __device__ __forceinline__ int aRow(int tm) const { return tm * BM; }
   __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
-  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int row, bool rowOk) const {
+  __device__ __forceinline__ void drain(uint32_t taddr, int tm, int tn, int q, int lane, uint8_t* sw) const {
     const int owner = tm / a.blocksPerRank;
-    const int localRow = row - owner * a.rowsPerRank;
-    // Owner's staging: [src rank][rowsPerRank][N] bf16.
-    __nv_bfloat16* dst = (__nv_bfloat16*)(a.stagePeer[owner] + a.stageOff) + ((size_t)rank * a.rowsPerRank + localRow) * a.N;
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; c++) {
-      uint32_t acc[32];
-      sm100::tmemLoad32(taddr + c * 32, acc);
-      sm100::tmemLoadWait();
-      const int col0 = tn * BN + c * 32;
-      if (rowOk && col0 < a.N) storeRow32Bf16(dst + col0, acc, a.N - col0);
-    }
+    const int localRow0 = tm * BM + q * 32 - owner * a.rowsPerRank;
+    // Owner's staging: [src rank][rowsPerRank][N] bf16; whole 256-byte row pieces go over NVLink.
+    __nv_bfloat16* base = (__nv_bfloat16*)(a.stagePeer[owner] + a.stageOff) + ((size_t)rank * a.rowsPerRank + localRow0) * a.N + (size_t)tn * BN;
+    drainStaged(
+        sw, lane, BN, a.N - tn * BN,
+        [&](int c, uint32_t(&acc)[32]) {
+          sm100::tmemLoad32(taddr + c * 32, acc);
+          sm100::tmemLoadWait();
+        },
+        [&](int r) -> __nv_bfloat16* { return base + (size_t)r * a.N; });
   }
   __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const {
     // All four epilogue warps have stored their rows; then one thread tells the owner.

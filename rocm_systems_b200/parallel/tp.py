@@ -75,17 +75,27 @@ class TensorParallelMLP:
         """Where this rank writes its rows of the activations before ``forward``."""
         return self.x_full[self.rank * self.rows:(self.rank + 1) * self.rows]
 
+    def ag_gemm(self, stream=None) -> torch.Tensor:
+        """all-gather(x) @ w13^T with SwiGLU: ``act`` [M, ffn_local]. This rank's rows must be in ``my_rows()``."""
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        _lib.check(_lib_tp().b200collAgGemm(self.comm.handle, self.x_full.data_ptr(), self.w13.data_ptr(), self.act.data_ptr(), self.rows,
+                                            2 * self.f, self.hidden, 1, self.comm_ctas, s), "b200collAgGemm")
+        train_ops.LAUNCHES += 1
+        return self.act
+
+    def gemm_rs(self, stream=None) -> torch.Tensor:
+        """reduce-scatter(act @ w2^T): this rank's rows of the output."""
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        _lib.check(_lib_tp().b200collGemmRs(self.comm.handle, self.act.data_ptr(), self.w2.data_ptr(), self._ws.ptr, self.y.data_ptr(), self.rows,
+                                            self.hidden, self.f, s), "b200collGemmRs")
+        train_ops.LAUNCHES += 1
+        return self.y
+
     def forward(self, x_local: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         if x_local is not None:
             self.my_rows().copy_(x_local)
-        s = (stream or torch.cuda.current_stream()).cuda_stream
-        lib = _lib_tp()
-        _lib.check(lib.b200collAgGemm(self.comm.handle, self.x_full.data_ptr(), self.w13.data_ptr(), self.act.data_ptr(), self.rows,
-                                      2 * self.f, self.hidden, 1, self.comm_ctas, s), "b200collAgGemm")
-        _lib.check(lib.b200collGemmRs(self.comm.handle, self.act.data_ptr(), self.w2.data_ptr(), self._ws.ptr, self.y.data_ptr(), self.rows,
-                                      self.hidden, self.f, s), "b200collGemmRs")
-        train_ops.LAUNCHES += 2
-        return self.y
+        self.ag_gemm(stream)
+        return self.gemm_rs(stream)
 
     def reference_forward(self, x_local: torch.Tensor) -> torch.Tensor:
         """Unfused: all_gather, two library GEMMs, SwiGLU, reduce_scatter."""

@@ -64,6 +64,13 @@ def main():
         mlp.my_rows().copy_(x)
         res["fused_ms"] = timed(lambda: mlp.forward(None), comm)
         res["unfused_ms"] = timed(lambda: mlp.reference_forward(x), comm)
+        res["ag_gemm_ms"] = timed(lambda: mlp.ag_gemm(), comm)
+        res["gemm_rs_ms"] = timed(lambda: mlp.gemm_rs(), comm)
+        # the same two GEMMs with no communication at all (library GEMM), as the compute floor
+        xg = torch.randn(n * args.rows, args.hidden, device=dev).to(torch.bfloat16)
+        w13 = torch.cat([mlp.w_gate, mlp.w_up])
+        res["local_gemm1_ms"] = timed(lambda: torch.mm(xg, w13.t()), comm)
+        res["local_gemm2_ms"] = timed(lambda: torch.mm(mlp.act, mlp.w2.t()), comm)
         M = n * args.rows
         flops = 2.0 * M * args.hidden * 2 * args.ffn + 2.0 * M * args.ffn * args.hidden
         res["fused_tflops_per_gpu"] = flops / (res["fused_ms"] * 1e-3) / 1e12
