@@ -1,0 +1,145 @@
+"""Tracing launcher: run any command (one process or a multi-rank launch) with tracing on, then
+collect what every process wrote into CSV / JSON / Perfetto / SQLite outputs and a statistics table.
+
+It plays the part of the reference's ``rocprofv3`` (rocprofiler-sdk/source/bin/rocprofv3.py:
+option groups, environment hand-off to the tool library, output formats, ``--stats``/``--summary``).
+
+    python -m rocm_systems_b200.tools.prof --kernel-trace --coll-trace --stats -d out -- \\
+        python -m torch.distributed.run --nproc-per-node 8 train.py
+
+What is traced, and by which part of the package:
+
+  --kernel-trace / --memory-copy-trace / --runtime-trace / --driver-trace / --sync-trace
+        ``libb200prof.so`` (CUPTI activity records), loaded into every CUDA process of the command
+        through ``CUDA_INJECTION64_PATH``;
+  --coll-trace    the communication library's own tracer (host and device times per collective);
+  --marker-trace  ``b200tx`` ranges the program pushes (rocm_systems_b200.utils.markers);
+  --sys-trace     all of the above.
+"""
+from __future__ import annotations
+
+import argparse
+import glob
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+from typing import List, Optional, Sequence
+
+from . import tracedb
+
+PKG = Path(__file__).resolve().parents[1]
+
+
+def build_env(a: argparse.Namespace, prefix: str) -> dict:
+    """The environment that turns the chosen tracing on in the children (exposed for tests)."""
+    env = dict(os.environ)
+    cupti = a.kernel_trace or a.memory_copy_trace or a.runtime_trace or a.driver_trace or a.sync_trace
+    if cupti:
+        lib = PKG / "lib" / "libb200prof.so"
+        if not lib.exists():
+            raise SystemExit(f"{lib} is missing: run `python -m rocm_systems_b200.utils.build`")
+        env["CUDA_INJECTION64_PATH"] = str(lib)
+        env["B200PROF_OUTPUT"] = prefix
+        env["B200PROF_KERNEL_TRACE"] = "1" if a.kernel_trace else "0"
+        env["B200PROF_MEMORY_COPY_TRACE"] = "1" if a.memory_copy_trace else "0"
+        env["B200PROF_RUNTIME_TRACE"] = "1" if a.runtime_trace else "0"
+        env["B200PROF_DRIVER_TRACE"] = "1" if a.driver_trace else "0"
+        env["B200PROF_SYNC_TRACE"] = "1" if a.sync_trace else "0"
+        if a.kernel_include_regex:
+            env["B200PROF_KERNEL_FILTER"] = a.kernel_include_regex
+        if a.max_records:
+            env["B200PROF_MAX_RECORDS"] = str(a.max_records)
+    if a.coll_trace or a.marker_trace:
+        env["B200COLL_TRACE"] = "1"
+        env["B200COLL_TRACE_FILE"] = prefix
+    if a.tool_library:
+        old = env.get("B200COLL_TOOL_LIBRARIES", "")
+        env["B200COLL_TOOL_LIBRARIES"] = ":".join([*a.tool_library, old] if old else a.tool_library)
+    return env
+
+
+def collect(prefix: str) -> List[str]:
+    """Every trace file the children left behind."""
+    files = sorted(set(glob.glob(prefix + ".*_kernel_trace.csv") + glob.glob(prefix + ".*_memory_copy_trace.csv") +
+                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv")))
+    return files
+
+
+def parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="prof", description=__doc__.split("\n\n")[0], formatter_class=argparse.RawDescriptionHelpFormatter)
+    g = ap.add_argument_group("tracing")
+    g.add_argument("--kernel-trace", action="store_true")
+    g.add_argument("--memory-copy-trace", action="store_true")
+    g.add_argument("--runtime-trace", action="store_true", help="CUDA runtime API calls")
+    g.add_argument("--driver-trace", action="store_true", help="CUDA driver API calls")
+    g.add_argument("--sync-trace", action="store_true", help="stream/event/context synchronisation")
+    g.add_argument("--coll-trace", action="store_true", help="collectives of the communication library")
+    g.add_argument("--marker-trace", action="store_true", help="b200tx ranges")
+    g.add_argument("--sys-trace", action="store_true", help="everything")
+    g = ap.add_argument_group("filtering")
+    g.add_argument("--kernel-include-regex", default="")
+    g.add_argument("--max-records", type=int, default=0, help="per kind and process")
+    g = ap.add_argument_group("output")
+    g.add_argument("-d", "--output-directory", default="prof_out")
+    g.add_argument("-o", "--output-file", default="trace")
+    g.add_argument("--output-format", nargs="+", choices=["csv", "json", "pftrace", "db"], default=["csv", "db"])
+    g.add_argument("--stats", action="store_true", help="print per-kernel / per-collective statistics")
+    g.add_argument("--summary", action="store_true", help="write the statistics as <output>_summary.json as well")
+    g.add_argument("--top", type=int, default=15)
+    g = ap.add_argument_group("tools")
+    g.add_argument("--tool-library", action="append", default=[], help="extra dispatch-table tool(s) to load into the communication library")
+    ap.add_argument("command", nargs=argparse.REMAINDER, help="-- command to run")
+    return ap
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    a = parser().parse_args(argv)
+    cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
+    if not cmd:
+        print("prof: no command given (put it after --)", file=sys.stderr)
+        return 2
+    if a.sys_trace:
+        a.kernel_trace = a.memory_copy_trace = a.runtime_trace = a.sync_trace = a.coll_trace = a.marker_trace = True
+    if not (a.kernel_trace or a.memory_copy_trace or a.runtime_trace or a.driver_trace or a.sync_trace or a.coll_trace or a.marker_trace):
+        a.kernel_trace = True
+    outdir = Path(a.output_directory)
+    outdir.mkdir(parents=True, exist_ok=True)
+    prefix = str(outdir / a.output_file)
+    rc = subprocess.call(cmd, env=build_env(a, prefix))
+    files = collect(prefix)
+    if not files:
+        print("prof: the command left no trace files (did it use the GPU / the communication library?)", file=sys.stderr)
+        return rc
+    db_path = prefix + ".db"
+    if os.path.exists(db_path):
+        os.remove(db_path)
+    with tracedb.TraceDB(db_path) as db:
+        total = sum(db.import_csv(f, command=" ".join(cmd)) for f in files)
+        summary = db.summary(a.top)
+        if "pftrace" in a.output_format:
+            db.to_perfetto(prefix + ".perfetto.json")
+        if "json" in a.output_format:
+            out = {}
+            for view in ("kernels", "regions", "collectives"):
+                names, rows = db.query(f"select * from {view}")
+                out[view] = [dict(zip(names, r)) for r in rows]
+            Path(prefix + ".json").write_text(json.dumps(out))
+        if "csv" in a.output_format:
+            db.to_csv(prefix)
+    if "db" not in a.output_format:
+        os.remove(db_path)
+    if "csv" not in a.output_format:
+        for f in files:
+            os.remove(f)
+    if a.stats:
+        tracedb.print_summary(summary)
+    if a.summary:
+        Path(prefix + "_summary.json").write_text(json.dumps(summary, indent=1))
+    print(f"prof: {total} records from {len(files)} file(s) under {outdir}", file=sys.stderr)
+    return rc
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,267 @@
+"""Telemetry daemon and client: sample device fields in the background, keep a history, expose
+them to Prometheus and over a small HTTP API, compute per-job statistics, report health.
+
+The counterpart of the reference's data-center tool: the ``rdcd`` daemon, the ``rdci`` client
+(rdc/rdci/src: discovery, dmon, group / field group, stats, diag) and its Prometheus plugin
+(rdc/python_binding/rdc_prometheus.py). The sampling itself is native (``b200smi_watch_*`` in
+csrc/core/health.cc, a sampler thread over NVML); this module is the service around it.
+
+    python -m rocm_systems_b200.tools.telemetry serve --port 9400 --period-ms 1000
+    curl localhost:9400/metrics
+    python -m rocm_systems_b200.tools.telemetry discovery
+    python -m rocm_systems_b200.tools.telemetry dmon -c 5 -d 1000 -e sm_clock power temp
+    python -m rocm_systems_b200.tools.telemetry client --url http://127.0.0.1:9400 job-start --job run1
+    python -m rocm_systems_b200.tools.telemetry client --url http://127.0.0.1:9400 job-stats --job run1
+
+Nothing here changes a device setting.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import threading
+import time
+import urllib.parse
+import urllib.request
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import List, Optional, Sequence
+
+from .smi import FIELDS, REASON_BITS, Smi
+
+DEFAULT_FIELDS = ["sm_clock", "mem_clock", "power", "temp", "mem_used", "gpu_util", "mem_util", "ecc_corrected", "ecc_uncorrected",
+                  "throttle_reasons", "nvlink_active"]
+# field -> (metric name, help, scale to the metric's unit)
+PROM = {
+    "sm_clock": ("b200_sm_clock_mhz", "SM clock in MHz", 1.0),
+    "mem_clock": ("b200_memory_clock_mhz", "memory clock in MHz", 1.0),
+    "power": ("b200_power_watts", "board power draw in watts", 1e-3),
+    "temp": ("b200_temperature_celsius", "GPU temperature", 1.0),
+    "mem_used": ("b200_memory_used_bytes", "device memory in use", 1.0),
+    "gpu_util": ("b200_gpu_utilization_percent", "fraction of time a kernel was running", 1.0),
+    "mem_util": ("b200_memory_utilization_percent", "fraction of time memory was read or written", 1.0),
+    "ecc_corrected": ("b200_ecc_corrected_total", "corrected ECC errors (volatile)", 1.0),
+    "ecc_uncorrected": ("b200_ecc_uncorrected_total", "uncorrected ECC errors (volatile)", 1.0),
+    "throttle_reasons": ("b200_clock_event_reasons", "bit mask of active clock event reasons", 1.0),
+    "nvlink_active": ("b200_nvlink_active_links", "NVLink links in the active state", 1.0),
+}
+
+
+class Telemetry:
+    """Field groups and device groups over the native watch, plus text renderings."""
+
+    def __init__(self, smi: Optional[Smi] = None):
+        self.smi = smi or Smi()
+        self.devices: List[int] = list(range(self.smi.count()))
+        self.fields: List[str] = list(DEFAULT_FIELDS)
+        self.watching = False
+        self.jobs: dict = {}
+
+    def start(self, devices: Optional[Sequence[int]] = None, fields: Optional[Sequence[str]] = None, period_ms: int = 1000, keep: int = 3600) -> None:
+        if devices is not None:
+            self.devices = list(devices)
+        if fields is not None:
+            unknown = [f for f in fields if f not in FIELDS]
+            if unknown:
+                raise ValueError(f"unknown field(s) {unknown}; known: {sorted(FIELDS)}")
+            self.fields = list(fields)
+        self.smi.watch_start(self.devices, self.fields, period_ms, keep)
+        self.watching = True
+
+    def stop(self) -> None:
+        if self.watching:
+            self.smi.watch_stop()
+            self.watching = False
+
+    def discovery(self) -> List[dict]:
+        out = []
+        for d in range(self.smi.count()):
+            i = self.smi.info(d)
+            out.append({"index": d, "name": i["name"], "uuid": i["uuid"], "bus_id": i["busId"], "memory_total_bytes": i["memTotalBytes"],
+                        "nvlinks": i["nvlinkCount"], "multicast_capable": bool(i["multicastCapable"])})
+        return out
+
+    def latest(self) -> dict:
+        """{device: {field: value}} read now (not from the history)."""
+        return {d: {f: self.smi.read(d, f) for f in self.fields} for d in self.devices}
+
+    def history(self, dev: int, field: str, max_n: int = 4096) -> list:
+        return self.smi.history(dev, field, max_n)
+
+    def job_start(self, job: str) -> None:
+        self.smi.job_start(job)
+        self.jobs[job] = {"start": time.time(), "stop": None}
+
+    def job_stop(self, job: str) -> None:
+        self.smi.job_stop(job)
+        if job in self.jobs:
+            self.jobs[job]["stop"] = time.time()
+
+    def job_stats(self, job: str) -> dict:
+        out = {"job": job, **self.jobs.get(job, {}), "devices": {}}
+        for d in self.devices:
+            out["devices"][d] = {f: self.smi.job_stats(job, d, f) for f in self.fields}
+        return out
+
+    def health(self) -> dict:
+        names = {0: "PASS", 1: "WARN", 2: "FAIL"}
+        out = {}
+        for d in self.devices:
+            level, msg = self.smi.health(d)
+            out[d] = {"level": names.get(level, str(level)), "message": msg}
+        return out
+
+    def prometheus(self) -> str:
+        vals = self.latest()
+        infos = {d: self.smi.info(d) for d in self.devices}
+        lines = []
+        for f in self.fields:
+            name, help_, scale = PROM[f]
+            kind = "counter" if name.endswith("_total") else "gauge"
+            lines.append(f"# HELP {name} {help_}")
+            lines.append(f"# TYPE {name} {kind}")
+            for d in self.devices:
+                lines.append(f'{name}{{gpu="{d}",uuid="{infos[d]["uuid"]}"}} {vals[d][f] * scale:g}')
+        if "throttle_reasons" in self.fields:
+            lines.append("# HELP b200_clock_event_reason one series per reason; 1 while it is active")
+            lines.append("# TYPE b200_clock_event_reason gauge")
+            for d in self.devices:
+                mask = int(vals[d]["throttle_reasons"])
+                for bit, reason in REASON_BITS.items():
+                    lines.append(f'b200_clock_event_reason{{gpu="{d}",reason="{reason}"}} {1 if mask & bit else 0}')
+        return "\n".join(lines) + "\n"
+
+
+def make_handler(t: Telemetry):
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *args) -> None:  # quiet
+            pass
+
+        def _send(self, code: int, body: str, ctype: str = "application/json") -> None:
+            data = body.encode()
+            self.send_response(code)
+            self.send_header("Content-Type", ctype)
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+        def do_GET(self) -> None:  # noqa: N802 - name fixed by the base class
+            url = urllib.parse.urlparse(self.path)
+            q = {k: v[0] for k, v in urllib.parse.parse_qs(url.query).items()}
+            try:
+                if url.path == "/metrics":
+                    self._send(200, t.prometheus(), "text/plain; version=0.0.4")
+                elif url.path == "/api/devices":
+                    self._send(200, json.dumps(t.discovery()))
+                elif url.path == "/api/latest":
+                    self._send(200, json.dumps(t.latest()))
+                elif url.path == "/api/history":
+                    self._send(200, json.dumps(t.history(int(q["dev"]), q["field"], int(q.get("max", 4096)))))
+                elif url.path == "/api/health":
+                    self._send(200, json.dumps(t.health()))
+                elif url.path == "/api/job/start":
+                    t.job_start(q["job"])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/job/stop":
+                    t.job_stop(q["job"])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/job/stats":
+                    self._send(200, json.dumps(t.job_stats(q["job"])))
+                else:
+                    self._send(404, json.dumps({"error": "unknown path"}))
+            except (KeyError, ValueError, RuntimeError) as e:
+                self._send(400, json.dumps({"error": str(e)}))
+
+    return Handler
+
+
+def serve(t: Telemetry, host: str, port: int) -> ThreadingHTTPServer:
+    """Starts the HTTP server on a thread and returns it (``shutdown()`` stops it)."""
+    srv = ThreadingHTTPServer((host, port), make_handler(t))
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv
+
+
+def _client(url: str, path: str, **q) -> object:
+    full = url.rstrip("/") + path + ("?" + urllib.parse.urlencode(q) if q else "")
+    with urllib.request.urlopen(full, timeout=10) as r:
+        body = r.read().decode()
+    return body if path == "/metrics" else json.loads(body)
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="telemetry", description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("serve", help="run the daemon")
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=9400)
+    p.add_argument("--period-ms", type=int, default=1000)
+    p.add_argument("--keep", type=int, default=3600, help="samples kept per device and field")
+    p.add_argument("-e", "--fields", nargs="+", default=DEFAULT_FIELDS)
+    p.add_argument("-i", "--devices", nargs="+", type=int)
+    p.add_argument("--duration", type=float, default=0.0, help="exit after this many seconds (0 = run until interrupted)")
+    sub.add_parser("discovery", help="list devices")
+    p = sub.add_parser("dmon", help="print readings periodically")
+    p.add_argument("-c", "--count", type=int, default=0)
+    p.add_argument("-d", "--delay-ms", type=int, default=1000)
+    p.add_argument("-e", "--fields", nargs="+", default=["sm_clock", "power", "temp", "gpu_util", "mem_used"])
+    p.add_argument("-i", "--devices", nargs="+", type=int)
+    sub.add_parser("health", help="one health verdict per device")
+    p = sub.add_parser("client", help="talk to a running daemon")
+    p.add_argument("--url", default="http://127.0.0.1:9400")
+    p.add_argument("what", choices=["devices", "latest", "health", "metrics", "history", "job-start", "job-stop", "job-stats"])
+    p.add_argument("--job", default="")
+    p.add_argument("--dev", type=int, default=0)
+    p.add_argument("--field", default="power")
+    a = ap.parse_args(argv)
+
+    if a.cmd == "client":
+        path = {"devices": "/api/devices", "latest": "/api/latest", "health": "/api/health", "metrics": "/metrics", "history": "/api/history",
+                "job-start": "/api/job/start", "job-stop": "/api/job/stop", "job-stats": "/api/job/stats"}[a.what]
+        q = {}
+        if a.what.startswith("job"):
+            q["job"] = a.job
+        if a.what == "history":
+            q = {"dev": a.dev, "field": a.field}
+        res = _client(a.url, path, **q)
+        print(res if isinstance(res, str) else json.dumps(res, indent=1))
+        return 0
+
+    t = Telemetry()
+    if a.cmd == "discovery":
+        for d in t.discovery():
+            print(f"{d['index']}\t{d['name']}\t{d['uuid']}\t{d['bus_id']}\t{d['memory_total_bytes'] / 2**30:.0f} GiB\tNVLink x{d['nvlinks']}")
+    elif a.cmd == "health":
+        for d, h in t.health().items():
+            print(f"GPU {d}: {h['level']} {h['message']}")
+    elif a.cmd == "dmon":
+        t.fields = a.fields
+        if a.devices:
+            t.devices = a.devices
+        print("GPU\t" + "\t".join(a.fields))
+        n = 0
+        while a.count == 0 or n < a.count:
+            for d, vals in t.latest().items():
+                print(f"{d}\t" + "\t".join(f"{vals[f]:g}" for f in a.fields), flush=True)
+            n += 1
+            if a.count == 0 or n < a.count:
+                time.sleep(a.delay_ms / 1e3)
+    elif a.cmd == "serve":
+        t.start(a.devices, a.fields, a.period_ms, a.keep)
+        srv = serve(t, a.host, a.port)
+        print(f"telemetry: serving http://{a.host}:{srv.server_address[1]}/metrics for {len(t.devices)} device(s)", flush=True)
+        try:
+            if a.duration > 0:
+                time.sleep(a.duration)
+            else:
+                while True:
+                    time.sleep(3600)
+        except KeyboardInterrupt:
+            pass
+        srv.shutdown()
+        t.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,349 @@
+"""Trace database: every trace this package produces, in one SQLite file that can be queried,
+summarised, merged across ranks and converted.
+
+It plays the role of the reference's ``rocpd`` (rocprofiler-sdk/source/lib/python/rocpd:
+``importer``, ``summary``, ``query``, ``csv``/``pftrace`` converters and the schema under
+rocprofiler-sdk/source/share/rocprofiler-sdk-rocpd/*.sql) with a schema of its own:
+
+    process(id, pid, rank, hostname, command)
+    string(id, value)                                  -- interned names
+    kernel_dispatch(process_id, device, stream, name_id, correlation_id, start_ns, end_ns,
+                    registers, static_smem, dynamic_smem, grid_x..z, block_x..z, cluster_x..z)
+    memory_copy(process_id, device, stream, direction_id, bytes, start_ns, end_ns, src_device, dst_device)
+    region(process_id, tid, category_id, name_id, correlation_id, start_ns, end_ns)      -- API calls, markers
+    collective(process_id, rank, name_id, correlation_id, count, dtype, bytes, algo, ctas,
+               host_start_ns, host_end_ns, device_start_ns, device_end_ns)
+
+and the views ``kernels``, ``regions``, ``collectives``, ``top_kernels``, ``top_collectives``, ``busy``.
+
+    python -m rocm_systems_b200.tools.tracedb import out/run*.csv -o run.db
+    python -m rocm_systems_b200.tools.tracedb summary run.db
+    python -m rocm_systems_b200.tools.tracedb query run.db "select * from top_kernels limit 5"
+    python -m rocm_systems_b200.tools.tracedb convert run.db --format perfetto -o run.json
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import os
+import re
+import socket
+import sqlite3
+import sys
+from pathlib import Path
+from typing import Iterable, List, Optional, Sequence
+
+SCHEMA = """
+create table if not exists process(id integer primary key, pid integer, rank integer, hostname text, command text);
+create table if not exists string(id integer primary key, value text unique);
+create table if not exists kernel_dispatch(id integer primary key, process_id integer, device integer, stream integer, name_id integer,
+    correlation_id integer, start_ns integer, end_ns integer, registers integer, static_smem integer, dynamic_smem integer,
+    grid_x integer, grid_y integer, grid_z integer, block_x integer, block_y integer, block_z integer,
+    cluster_x integer, cluster_y integer, cluster_z integer);
+create table if not exists memory_copy(id integer primary key, process_id integer, device integer, stream integer, direction_id integer,
+    bytes integer, start_ns integer, end_ns integer, src_device integer, dst_device integer);
+create table if not exists region(id integer primary key, process_id integer, tid integer, category_id integer, name_id integer,
+    correlation_id integer, start_ns integer, end_ns integer);
+create table if not exists collective(id integer primary key, process_id integer, rank integer, name_id integer, correlation_id integer,
+    count integer, dtype text, bytes integer, algo integer, ctas integer, host_start_ns integer, host_end_ns integer,
+    device_start_ns integer, device_end_ns integer);
+create index if not exists kd_name on kernel_dispatch(name_id);
+create index if not exists kd_start on kernel_dispatch(start_ns);
+create index if not exists rg_start on region(start_ns);
+create view if not exists kernels as
+    select k.id, p.pid, p.rank, k.device, k.stream, s.value as name, k.correlation_id, k.start_ns, k.end_ns, k.end_ns - k.start_ns as duration_ns,
+           k.registers, k.static_smem, k.dynamic_smem, k.grid_x, k.grid_y, k.grid_z, k.block_x, k.block_y, k.block_z
+    from kernel_dispatch k join string s on s.id = k.name_id join process p on p.id = k.process_id;
+create view if not exists regions as
+    select r.id, p.pid, p.rank, r.tid, c.value as category, s.value as name, r.correlation_id, r.start_ns, r.end_ns, r.end_ns - r.start_ns as duration_ns
+    from region r join string s on s.id = r.name_id join string c on c.id = r.category_id join process p on p.id = r.process_id;
+create view if not exists collectives as
+    select c.id, p.pid, c.rank, s.value as name, c.correlation_id, c.count, c.dtype, c.bytes, c.algo, c.ctas, c.host_start_ns, c.host_end_ns,
+           c.device_start_ns, c.device_end_ns, c.device_end_ns - c.device_start_ns as device_ns
+    from collective c join string s on s.id = c.name_id join process p on p.id = c.process_id;
+create view if not exists top_kernels as
+    select name, count(*) as calls, sum(duration_ns) as total_ns, avg(duration_ns) as mean_ns, min(duration_ns) as min_ns, max(duration_ns) as max_ns,
+           100.0 * sum(duration_ns) / (select sum(duration_ns) from kernels) as percent
+    from kernels group by name order by total_ns desc;
+create view if not exists top_collectives as
+    select name, bytes, count(*) as calls, sum(device_ns) as total_ns, avg(device_ns) as mean_ns, min(device_ns) as min_ns, max(device_ns) as max_ns,
+           case when avg(device_ns) > 0 then bytes / avg(device_ns) else 0 end as algbw_gbps
+    from collectives group by name, bytes order by total_ns desc;
+create view if not exists busy as
+    select p.rank, k.device, count(*) as kernels, sum(k.end_ns - k.start_ns) as kernel_ns, max(k.end_ns) - min(k.start_ns) as span_ns,
+           100.0 * sum(k.end_ns - k.start_ns) / max(1, max(k.end_ns) - min(k.start_ns)) as busy_percent
+    from kernel_dispatch k join process p on p.id = k.process_id group by p.rank, k.device;
+"""
+
+
+class TraceDB:
+    def __init__(self, path: str):
+        self.path = path
+        self.db = sqlite3.connect(path)
+        self.db.executescript(SCHEMA)
+        self._strings: dict = {}
+
+    def close(self) -> None:
+        self.db.commit()
+        self.db.close()
+
+    def __enter__(self) -> "TraceDB":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    # ---- building ----
+    def string_id(self, value: str) -> int:
+        sid = self._strings.get(value)
+        if sid is None:
+            row = self.db.execute("select id from string where value = ?", (value,)).fetchone()
+            if row:
+                sid = row[0]
+            else:
+                sid = self.db.execute("insert into string(value) values (?)", (value,)).lastrowid
+            self._strings[value] = sid
+        return sid
+
+    def process_id(self, pid: int, rank: int = -1, command: str = "") -> int:
+        row = self.db.execute("select id, rank from process where pid = ?", (pid,)).fetchone()
+        if row:
+            if rank >= 0 and row[1] < 0:
+                self.db.execute("update process set rank = ? where id = ?", (rank, row[0]))
+            return row[0]
+        return self.db.execute("insert into process(pid, rank, hostname, command) values (?,?,?,?)",
+                               (pid, rank, socket.gethostname(), command)).lastrowid
+
+    def import_csv(self, path: str, command: str = "") -> int:
+        """Imports one CSV file of any kind this package writes; the header decides the kind."""
+        with open(path, newline="") as f:
+            rows = list(csv.DictReader(f))
+        if not rows:
+            return 0
+        cols = set(rows[0].keys())
+        m = re.search(r"\.rank(\d+)\.", os.path.basename(path))
+        file_rank = int(m.group(1)) if m else -1
+        n = 0
+        if "Kernel_Name" in cols:
+            for r in rows:
+                pid = self.process_id(int(r["Process_Id"]), file_rank, command)
+                self.db.execute(
+                    "insert into kernel_dispatch(process_id, device, stream, name_id, correlation_id, start_ns, end_ns, registers, static_smem,"
+                    " dynamic_smem, grid_x, grid_y, grid_z, block_x, block_y, block_z, cluster_x, cluster_y, cluster_z)"
+                    " values (?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?)",
+                    (pid, int(r["Agent_Id"]), int(r["Queue_Id"]), self.string_id(r["Kernel_Name"]), int(r["Correlation_Id"]),
+                     int(r["Start_Timestamp"]), int(r["End_Timestamp"]), int(r.get("Registers_Per_Thread", 0) or 0),
+                     int(r.get("Static_Shared_Memory", 0) or 0), int(r.get("Dynamic_Shared_Memory", 0) or 0),
+                     int(r["Grid_Size_X"]), int(r["Grid_Size_Y"]), int(r["Grid_Size_Z"]), int(r["Workgroup_Size_X"]), int(r["Workgroup_Size_Y"]),
+                     int(r["Workgroup_Size_Z"]), int(r.get("Cluster_X", 0) or 0), int(r.get("Cluster_Y", 0) or 0), int(r.get("Cluster_Z", 0) or 0)))
+                n += 1
+        elif "Direction" in cols:
+            for r in rows:
+                pid = self.process_id(int(r["Process_Id"]), file_rank, command)
+                self.db.execute("insert into memory_copy(process_id, device, stream, direction_id, bytes, start_ns, end_ns, src_device, dst_device)"
+                                " values (?,?,?,?,?,?,?,?,?)",
+                                (pid, int(r["Agent_Id"]), int(r["Queue_Id"]), self.string_id(r["Direction"]), int(r["Bytes"]),
+                                 int(r["Start_Timestamp"]), int(r["End_Timestamp"]), int(r["Source_Agent_Id"]), int(r["Destination_Agent_Id"])))
+                n += 1
+        elif "Device_Start" in cols:  # collective trace of the communication library
+            for r in rows:
+                rank = int(r["Rank"])
+                pid = self.process_id(int(r["Process_Id"]), rank, command)
+                self.db.execute("insert into collective(process_id, rank, name_id, correlation_id, count, dtype, bytes, algo, ctas, host_start_ns,"
+                                " host_end_ns, device_start_ns, device_end_ns) values (?,?,?,?,?,?,?,?,?,?,?,?,?)",
+                                (pid, rank, self.string_id(r["Function"]), int(r["Correlation_Id"]), int(r["Count"]), r["Dtype"], int(r["Bytes"]),
+                                 int(r["Algo"]), int(r["Ctas"]), int(r["Start_Timestamp"]), int(r["End_Timestamp"]), int(r["Device_Start"]),
+                                 int(r["Device_End"])))
+                self.db.execute("insert into region(process_id, tid, category_id, name_id, correlation_id, start_ns, end_ns) values (?,?,?,?,?,?,?)",
+                                (pid, int(r["Thread_Id"]), self.string_id(r["Domain"]), self.string_id(r["Function"]), int(r["Correlation_Id"]),
+                                 int(r["Start_Timestamp"]), int(r["End_Timestamp"])))
+                n += 1
+        elif {"Domain", "Function", "Start_Timestamp"} <= cols:  # API and marker traces
+            for r in rows:
+                pid = self.process_id(int(r["Process_Id"]), file_rank, command)
+                self.db.execute("insert into region(process_id, tid, category_id, name_id, correlation_id, start_ns, end_ns) values (?,?,?,?,?,?,?)",
+                                (pid, int(r["Thread_Id"]), self.string_id(r["Domain"]), self.string_id(r["Function"]), int(r["Correlation_Id"]),
+                                 int(r["Start_Timestamp"]), int(r["End_Timestamp"])))
+                n += 1
+        else:
+            raise ValueError(f"{path}: not a trace CSV of this package (columns {sorted(cols)})")
+        self.db.commit()
+        return n
+
+    def merge(self, other_path: str) -> None:
+        """Appends another database (for example another rank's) into this one."""
+        src = sqlite3.connect(other_path)
+        pmap, smap = {}, {}
+        for sid, value in src.execute("select id, value from string"):
+            smap[sid] = self.string_id(value)
+        for pid_row in src.execute("select id, pid, rank, hostname, command from process"):
+            pmap[pid_row[0]] = self.db.execute("insert into process(pid, rank, hostname, command) values (?,?,?,?)", pid_row[1:]).lastrowid
+        for row in src.execute("select process_id, device, stream, name_id, correlation_id, start_ns, end_ns, registers, static_smem, dynamic_smem,"
+                               " grid_x, grid_y, grid_z, block_x, block_y, block_z, cluster_x, cluster_y, cluster_z from kernel_dispatch"):
+            row = list(row)
+            row[0], row[3] = pmap[row[0]], smap[row[3]]
+            self.db.execute("insert into kernel_dispatch(process_id, device, stream, name_id, correlation_id, start_ns, end_ns, registers,"
+                            " static_smem, dynamic_smem, grid_x, grid_y, grid_z, block_x, block_y, block_z, cluster_x, cluster_y, cluster_z)"
+                            " values (?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?,?)", row)
+        for row in src.execute("select process_id, device, stream, direction_id, bytes, start_ns, end_ns, src_device, dst_device from memory_copy"):
+            row = list(row)
+            row[0], row[3] = pmap[row[0]], smap[row[3]]
+            self.db.execute("insert into memory_copy(process_id, device, stream, direction_id, bytes, start_ns, end_ns, src_device, dst_device)"
+                            " values (?,?,?,?,?,?,?,?,?)", row)
+        for row in src.execute("select process_id, tid, category_id, name_id, correlation_id, start_ns, end_ns from region"):
+            row = list(row)
+            row[0], row[2], row[3] = pmap[row[0]], smap[row[2]], smap[row[3]]
+            self.db.execute("insert into region(process_id, tid, category_id, name_id, correlation_id, start_ns, end_ns) values (?,?,?,?,?,?,?)", row)
+        for row in src.execute("select process_id, rank, name_id, correlation_id, count, dtype, bytes, algo, ctas, host_start_ns, host_end_ns,"
+                               " device_start_ns, device_end_ns from collective"):
+            row = list(row)
+            row[0], row[2] = pmap[row[0]], smap[row[2]]
+            self.db.execute("insert into collective(process_id, rank, name_id, correlation_id, count, dtype, bytes, algo, ctas, host_start_ns,"
+                            " host_end_ns, device_start_ns, device_end_ns) values (?,?,?,?,?,?,?,?,?,?,?,?,?)", row)
+        src.close()
+        self.db.commit()
+
+    # ---- reading ----
+    def query(self, sql: str, params: Sequence = ()) -> tuple:
+        cur = self.db.execute(sql, params)
+        names = [d[0] for d in cur.description] if cur.description else []
+        return names, cur.fetchall()
+
+    def summary(self, top: int = 15) -> dict:
+        out = {}
+        names, rows = self.query(f"select * from top_kernels limit {int(top)}")
+        out["kernels"] = [dict(zip(names, r)) for r in rows]
+        names, rows = self.query(f"select * from top_collectives limit {int(top)}")
+        out["collectives"] = [dict(zip(names, r)) for r in rows]
+        names, rows = self.query("select category, name, count(*) as calls, sum(duration_ns) as total_ns, avg(duration_ns) as mean_ns from regions"
+                                 f" group by category, name order by total_ns desc limit {int(top)}")
+        out["regions"] = [dict(zip(names, r)) for r in rows]
+        names, rows = self.query("select s.value as direction, count(*) as calls, sum(bytes) as bytes, sum(end_ns - start_ns) as total_ns"
+                                 " from memory_copy m join string s on s.id = m.direction_id group by s.value order by total_ns desc")
+        out["memory_copies"] = [dict(zip(names, r)) for r in rows]
+        names, rows = self.query("select * from busy order by rank, device")
+        out["busy"] = [dict(zip(names, r)) for r in rows]
+        return out
+
+    def to_perfetto(self, path: str) -> int:
+        """Chrome/Perfetto JSON: one process per rank/pid; threads for host regions, streams for kernels and copies."""
+        events: List[dict] = []
+        for pid, rank in self.db.execute("select pid, rank from process"):
+            events.append({"ph": "M", "pid": pid, "name": "process_name", "args": {"name": f"rank {rank} (pid {pid})" if rank >= 0 else f"pid {pid}"}})
+        for pid, dev, stream, name, s, e, gx, bx, regs in self.db.execute(
+                "select pid, device, stream, name, start_ns, end_ns, grid_x, block_x, registers from kernels"):
+            events.append({"ph": "X", "pid": pid, "tid": f"gpu{dev} stream {stream}", "name": name, "cat": "kernel", "ts": s / 1e3,
+                           "dur": max(e - s, 1) / 1e3, "args": {"grid_x": gx, "block_x": bx, "registers": regs}})
+        for pid, dev, stream, direction, nbytes, s, e in self.db.execute(
+                "select p.pid, m.device, m.stream, st.value, m.bytes, m.start_ns, m.end_ns from memory_copy m join process p on p.id = m.process_id"
+                " join string st on st.id = m.direction_id"):
+            events.append({"ph": "X", "pid": pid, "tid": f"gpu{dev} stream {stream}", "name": direction, "cat": "memcpy", "ts": s / 1e3,
+                           "dur": max(e - s, 1) / 1e3, "args": {"bytes": nbytes}})
+        for pid, tid, cat, name, s, e in self.db.execute("select pid, tid, category, name, start_ns, end_ns from regions"):
+            events.append({"ph": "X", "pid": pid, "tid": f"{cat} {tid}", "name": name, "cat": cat, "ts": s / 1e3, "dur": max(e - s, 1) / 1e3})
+        for pid, rank, name, nbytes, s, e in self.db.execute("select pid, rank, name, bytes, device_start_ns, device_end_ns from collectives"):
+            if e > s:
+                events.append({"ph": "X", "pid": pid, "tid": "collectives (device)", "name": name, "cat": "collective", "ts": s / 1e3,
+                               "dur": (e - s) / 1e3, "args": {"bytes": nbytes, "rank": rank}})
+        with open(path, "w") as f:
+            json.dump({"traceEvents": events, "displayTimeUnit": "ns"}, f)
+        return len(events)
+
+    def to_csv(self, prefix: str) -> List[str]:
+        written = []
+        for view in ("kernels", "regions", "collectives", "top_kernels", "top_collectives", "busy"):
+            names, rows = self.query(f"select * from {view}")
+            if not rows:
+                continue
+            path = f"{prefix}_{view}.csv"
+            with open(path, "w", newline="") as f:
+                w = csv.writer(f, quoting=csv.QUOTE_NONNUMERIC)
+                w.writerow(names)
+                w.writerows(rows)
+            written.append(path)
+        return written
+
+
+def format_table(names: Sequence[str], rows: Iterable[Sequence], max_width: int = 60) -> str:
+    def cell(v) -> str:
+        if isinstance(v, float):
+            return f"{v:.2f}"
+        s = str(v)
+        return s if len(s) <= max_width else s[:max_width - 1] + "…"
+
+    table = [list(map(str, names))] + [[cell(v) for v in r] for r in rows]
+    widths = [max(len(r[i]) for r in table) for i in range(len(names))]
+    lines = ["  ".join(c.ljust(w) for c, w in zip(r, widths)) for r in table]
+    lines.insert(1, "  ".join("-" * w for w in widths))
+    return "\n".join(lines)
+
+
+def print_summary(summary: dict, file=sys.stdout) -> None:
+    titles = {"kernels": "KERNEL_DISPATCH", "collectives": "COLLECTIVES (device time)", "regions": "API / MARKER REGIONS",
+              "memory_copies": "MEMORY_COPY", "busy": "DEVICE BUSY"}
+    for key, title in titles.items():
+        rows = summary.get(key) or []
+        if not rows:
+            continue
+        print(f"\n== {title} ==", file=file)
+        names = list(rows[0].keys())
+        print(format_table(names, [[r[n] for n in names] for r in rows]), file=file)
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="tracedb", description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("import", help="CSV trace files -> database")
+    p.add_argument("files", nargs="+")
+    p.add_argument("-o", "--output", required=True)
+    p = sub.add_parser("merge", help="append databases into the first")
+    p.add_argument("target")
+    p.add_argument("others", nargs="+")
+    p = sub.add_parser("summary")
+    p.add_argument("db")
+    p.add_argument("--top", type=int, default=15)
+    p.add_argument("--json", action="store_true")
+    p = sub.add_parser("query")
+    p.add_argument("db")
+    p.add_argument("sql")
+    p.add_argument("--format", choices=["table", "csv", "json"], default="table")
+    p = sub.add_parser("convert")
+    p.add_argument("db")
+    p.add_argument("--format", choices=["perfetto", "csv"], required=True)
+    p.add_argument("-o", "--output", required=True)
+    a = ap.parse_args(argv)
+    if a.cmd == "import":
+        with TraceDB(a.output) as db:
+            total = sum(db.import_csv(f) for f in a.files)
+        print(f"{total} records -> {a.output}")
+    elif a.cmd == "merge":
+        with TraceDB(a.target) as db:
+            for o in a.others:
+                db.merge(o)
+    elif a.cmd == "summary":
+        with TraceDB(a.db) as db:
+            s = db.summary(a.top)
+        print(json.dumps(s, indent=1)) if a.json else print_summary(s)
+    elif a.cmd == "query":
+        with TraceDB(a.db) as db:
+            names, rows = db.query(a.sql)
+        if a.format == "json":
+            print(json.dumps([dict(zip(names, r)) for r in rows], indent=1))
+        elif a.format == "csv":
+            w = csv.writer(sys.stdout)
+            w.writerow(names)
+            w.writerows(rows)
+        else:
+            print(format_table(names, rows))
+    elif a.cmd == "convert":
+        with TraceDB(a.db) as db:
+            if a.format == "perfetto":
+                print(f"{db.to_perfetto(a.output)} events -> {a.output}")
+            else:
+                print("\n".join(db.to_csv(a.output)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

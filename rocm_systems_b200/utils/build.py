@@ -81,7 +81,7 @@ def _compile(src: Path, obj: Path, defs: list[str], stamp: str, verbose_ptxas: b
 def lib_jobs() -> list[tuple[Path, Path, list[str]]]:
     jobs: list[tuple[Path, Path, list[str]]] = []
     for rel in ["core/common.cc", "core/bootstrap.cc", "core/cudrv.cc", "core/mem.cc", "core/comm.cc", "core/api.cc",
-                "core/topo.cc", "coll/enqueue.cc", "coll/launch.cu", "trace/tracer.cc", "shmem/shmem_host.cc",
+                "core/topo.cc", "coll/enqueue.cc", "coll/launch.cu", "trace/tracer.cc", "trace/markers.cc", "shmem/shmem_host.cc",
                 "coll/verifiable.cu", "fused/train_ops.cu", "fused/fsdp_kernels.cu", "fused/gemm_sm100.cu", "fused/tp_fused.cu",
                 "fused/ep_kernels.cu", "fused/no_alloc.cu", "shmem/shmem_kernels.cu", "core/health.cc"]:
         src = CSRC / rel
@@ -105,6 +105,33 @@ def build_lib(verbose_ptxas: bool = False, jobs_n: int | None = None) -> Path:
     newest = max(o.stat().st_mtime_ns for o in objs)
     if not out.exists() or out.stat().st_mtime_ns < newest:
         _run([NVCC, *ARCH, "-shared", "-o", str(out), *map(str, objs), "-cudart", "static", "-lpthread", "-ldl", "-lrt"])
+    return out
+
+
+def build_sample_tool() -> Path | None:
+    """The example profiling tool for the dispatch table, as a shared object of its own."""
+    src = CSRC / "trace" / "sample_tool.cc"
+    if not src.exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200coll_sample_tool.so"
+    if not out.exists() or out.stat().st_mtime_ns < src.stat().st_mtime_ns:
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-I{CSRC / 'include'}", "-I/usr/local/cuda/include", str(src), "-o", str(out)])
+    return out
+
+
+def build_prof() -> Path | None:
+    """The CUPTI activity tracing library (in-process API and CUDA injection entry point)."""
+    src = CSRC / "prof" / "b200prof.cc"
+    cuda = Path(NVCC).resolve().parents[1]
+    if not src.exists() or not (cuda / "include" / "cupti.h").exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200prof.so"
+    hdr = CSRC / "include" / "b200coll" / "prof.h"
+    if not out.exists() or out.stat().st_mtime_ns < max(src.stat().st_mtime_ns, hdr.stat().st_mtime_ns):
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-I{CSRC / 'include'}", f"-I{cuda / 'include'}", str(src), "-o", str(out),
+              f"-L{cuda / 'lib64'}", "-lcupti", f"-Wl,-rpath,{cuda / 'lib64'}", "-lpthread"])
     return out
 
 
@@ -194,6 +221,10 @@ def build_torch_ext() -> Path | None:
 def build_all(verbose_ptxas: bool = False) -> dict:
     res = {"lib": str(build_lib(verbose_ptxas))}
     res["perf"] = [str(p) for p in build_perf()]
+    tool = build_sample_tool()
+    res["sample_tool"] = str(tool) if tool else None
+    prof = build_prof()
+    res["prof"] = str(prof) if prof else None
     ext = build_torch_ext()
     res["torch_ext"] = str(ext) if ext else None
     return res

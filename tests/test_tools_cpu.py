@@ -1,0 +1,218 @@
+"""CPU tests of the tooling around the library: dispatch-table tool loading, markers, the trace
+database and its converters, the tracing launcher's environment hand-off, the telemetry service
+against a fake NVML, the roofline report and the device dump."""
+import json
+import os
+import subprocess
+import sys
+import urllib.request
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def _py(code: str, env=None, timeout=120):
+    e = dict(os.environ, PYTHONPATH=str(ROOT))
+    e.update(env or {})
+    p = subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True, timeout=timeout)
+    assert p.returncode == 0, p.stdout + p.stderr
+    return p.stdout
+
+
+def test_sample_tool_wraps_dispatch_table(tmp_path):
+    from rocm_systems_b200.utils import build
+
+    tool = build.build_sample_tool()
+    out = tmp_path / "tool.txt"
+    _py("""
+import ctypes
+from rocm_systems_b200 import _lib
+lib = _lib.load()
+v = ctypes.c_int()
+for _ in range(3):
+    assert lib.ncclGetVersion(ctypes.byref(v)) == 0
+assert v.value == 22005, v.value
+""", {"B200COLL_TOOL_LIBRARIES": str(tool), "B200COLL_SAMPLE_TOOL_OUTPUT": str(out)})
+    text = out.read_text()
+    assert "ncclGetVersion calls=3" in text and "payload_bytes=0" in text
+
+
+def test_markers_nest_and_write_csv(tmp_path):
+    out = _py(f"""
+from rocm_systems_b200.utils import markers
+assert markers.range_push('ignored') == -1          # off until enabled
+markers.enable()
+with markers.range('outer'):
+    with markers.range('inner'):
+        markers.mark('point')
+rid = markers.range_start('async')
+markers.range_stop(rid)
+recs = markers.records()
+names = [r['message'] for r in recs]
+assert names == ['point', 'inner', 'outer', 'async'], names
+by = {{r['message']: r for r in recs}}
+assert by['inner']['depth'] == 1 and by['outer']['depth'] == 0 and by['point']['depth'] == 2
+assert by['outer']['begin_ns'] <= by['inner']['begin_ns'] <= by['inner']['end_ns'] <= by['outer']['end_ns']
+assert markers.write_csv(r'{tmp_path}/m.csv') == 4
+assert 'b200coll' in markers.build_info()
+print('ok')
+""")
+    assert "ok" in out
+    assert (tmp_path / "m.csv").read_text().count("MARKER_API") == 4
+
+
+def test_markers_written_at_exit_under_trace_env(tmp_path):
+    prefix = tmp_path / "t"
+    _py("""
+from rocm_systems_b200.utils import markers
+with markers.range('step'):
+    pass
+""", {"B200COLL_TRACE": "1", "B200COLL_TRACE_FILE": str(prefix)})
+    files = list(tmp_path.glob("t.markers.*.csv"))
+    assert len(files) == 1 and '"step"' in files[0].read_text()
+
+
+KERNEL_CSV = '''"Kind","Agent_Id","Queue_Id","Process_Id","Kernel_Name","Correlation_Id","Start_Timestamp","End_Timestamp","Registers_Per_Thread","Static_Shared_Memory","Dynamic_Shared_Memory","Local_Memory_Per_Thread","Workgroup_Size_X","Workgroup_Size_Y","Workgroup_Size_Z","Grid_Size_X","Grid_Size_Y","Grid_Size_Z","Cluster_X","Cluster_Y","Cluster_Z","Graph_Node_Id"
+"KERNEL_DISPATCH",0,7,100,"gemmKernel<Cfg>",1,1000,5000,168,0,200000,0,192,1,1,148,1,1,1,1,1,0
+"KERNEL_DISPATCH",0,7,100,"gemmKernel<Cfg>",2,6000,9000,168,0,200000,0,192,1,1,148,1,1,1,1,1,0
+"KERNEL_DISPATCH",0,7,100,"rmsnorm",3,9500,10000,32,0,0,0,256,1,1,4096,1,1,1,1,1,0
+'''
+COLL_CSV = '''"Domain","Function","Process_Id","Thread_Id","Correlation_Id","Start_Timestamp","End_Timestamp","Rank","Count","Dtype","Bytes","Algo","Ctas","Device_Start","Device_End","Device_Us","AlgBw_GBps"
+"B200COLL_API","ncclAllReduce",100,100,1,900,950,0,1048576,"float",4194304,2,64,2000,12000,10.000,419.430
+"B200COLL_API","ncclAllReduce",100,100,2,1900,1950,0,1048576,"float",4194304,2,64,22000,30000,8.000,524.288
+'''
+MARK_CSV = '''"Domain","Function","Process_Id","Thread_Id","Correlation_Id","Start_Timestamp","End_Timestamp","Depth"
+"MARKER_API","step 0",100,100,1,500,20000,0
+'''
+
+
+def test_tracedb_import_summary_convert(tmp_path):
+    from rocm_systems_b200.tools import tracedb
+
+    (tmp_path / "t.100_kernel_trace.csv").write_text(KERNEL_CSV)
+    (tmp_path / "t.rank0.csv").write_text(COLL_CSV)
+    (tmp_path / "t.markers.100.csv").write_text(MARK_CSV)
+    dbp = str(tmp_path / "t.db")
+    with tracedb.TraceDB(dbp) as db:
+        n = sum(db.import_csv(str(p)) for p in sorted(tmp_path.glob("t.*csv")))
+        assert n == 6
+        s = db.summary()
+        top = s["kernels"][0]
+        assert top["name"] == "gemmKernel<Cfg>" and top["calls"] == 2 and top["total_ns"] == 7000
+        assert abs(top["percent"] - 7000 / 7500 * 100) < 1e-6
+        assert s["collectives"][0]["calls"] == 2 and s["collectives"][0]["mean_ns"] == 9000
+        assert s["busy"][0]["kernels"] == 3 and s["busy"][0]["rank"] == 0      # rank learnt from the collective trace of the same pid
+        cats = {r["category"] for r in s["regions"]}
+        assert cats == {"B200COLL_API", "MARKER_API"}
+        ev = db.to_perfetto(str(tmp_path / "t.json"))
+        assert ev == 1 + 3 + 3 + 2      # process name, kernels, regions (2 API + 1 marker), device-side collectives
+        files = db.to_csv(str(tmp_path / "out"))
+        assert any(f.endswith("_top_kernels.csv") for f in files)
+    doc = json.loads((tmp_path / "t.json").read_text())
+    assert {e["ph"] for e in doc["traceEvents"]} == {"M", "X"}
+    # a second rank's database merges in
+    db2 = str(tmp_path / "r1.db")
+    (tmp_path / "u.rank1.csv").write_text(COLL_CSV.replace(",100,100,", ",200,200,").replace(",0,1048576", ",1,1048576"))
+    with tracedb.TraceDB(db2) as d2:
+        d2.import_csv(str(tmp_path / "u.rank1.csv"))
+    with tracedb.TraceDB(dbp) as db:
+        db.merge(db2)
+        names, rows = db.query("select rank, count(*) from collectives group by rank order by rank")
+        assert rows == [(0, 2), (1, 2)]
+    assert tracedb.main(["query", dbp, "select count(*) as n from kernels", "--format", "json"]) == 0
+
+
+def test_prof_launcher_env_and_collection(tmp_path):
+    from rocm_systems_b200.tools import prof
+
+    a = prof.parser().parse_args(["--kernel-trace", "--coll-trace", "--kernel-include-regex", "gemm", "--", "true"])
+    env = prof.build_env(a, str(tmp_path / "x"))
+    assert env["CUDA_INJECTION64_PATH"].endswith("libb200prof.so") and env["B200PROF_KERNEL_TRACE"] == "1"
+    assert env["B200PROF_MEMORY_COPY_TRACE"] == "0" and env["B200PROF_KERNEL_FILTER"] == "gemm"
+    assert env["B200COLL_TRACE"] == "1" and env["B200COLL_TRACE_FILE"] == str(tmp_path / "x")
+    # end to end without a GPU: the child pushes markers; the launcher collects them into the outputs
+    child = "from rocm_systems_b200.utils import markers\nwith markers.range('phase'):\n    markers.mark('tick')\n"
+    e = dict(os.environ, PYTHONPATH=str(ROOT))
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "--stats", "--summary", "--output-format", "csv", "db",
+                        "pftrace", "json", "-d", str(tmp_path / "o"), "--", sys.executable, "-c", child], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert "MARKER_API" in p.stdout and "phase" in p.stdout
+    for name in ("trace.db", "trace.perfetto.json", "trace.json", "trace_summary.json", "trace_regions.csv"):
+        assert (tmp_path / "o" / name).exists(), name
+
+
+@pytest.fixture(scope="module")
+def fake_nvml(tmp_path_factory):
+    out = tmp_path_factory.mktemp("fake_nvml_t") / "libfake_nvml.so"
+    subprocess.check_call(["gcc", "-shared", "-fPIC", "-O1", "-o", str(out), str(ROOT / "tests" / "fake_nvml" / "fake_nvml.c")])
+    return str(out)
+
+
+def test_telemetry_service_with_fake_nvml(fake_nvml):
+    out = _py("""
+import json, time, urllib.request
+from rocm_systems_b200.tools import telemetry
+t = telemetry.Telemetry()
+assert len(t.discovery()) == 2
+t.start(fields=['sm_clock', 'power', 'temp', 'throttle_reasons'], period_ms=20, keep=100)
+srv = telemetry.serve(t, '127.0.0.1', 0)
+url = 'http://127.0.0.1:%d' % srv.server_address[1]
+get = lambda p: urllib.request.urlopen(url + p, timeout=10).read().decode()
+get('/api/job/start?job=j1')
+time.sleep(0.3)
+get('/api/job/stop?job=j1')
+m = get('/metrics')
+assert '# TYPE b200_power_watts gauge' in m and 'b200_sm_clock_mhz{gpu="1"' in m
+assert 'b200_clock_event_reason{gpu="0",reason="sw_power_cap"} 1' in m
+st = json.loads(get('/api/job/stats?job=j1'))
+assert st['devices']['0']['power']['samples'] >= 3 and st['devices']['0']['power']['avg'] > 0
+h = json.loads(get('/api/history?dev=0&field=temp'))
+assert len(h) >= 3
+assert json.loads(get('/api/health'))['0']['level'] == 'PASS'
+try:
+    get('/api/history?dev=0&field=nope'); raise SystemExit('bad field accepted')
+except urllib.error.HTTPError as e:
+    assert e.code == 400
+srv.shutdown(); t.stop()
+print('ok')
+""", {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "2"})
+    assert "ok" in out
+
+
+NCU_CSV = '''"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","gpu__time_duration.sum","dram__bytes_read.sum","dram__bytes_write.sum","sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active","sm__warps_active.avg.pct_of_peak_sustained_active","launch__registers_per_thread"
+"","","","","","","","","","","","us","Mbyte","Mbyte","%","%","register/thread"
+"0","1","python","h","rmsnormKernel","1","7","(256, 1, 1)","(4096, 1, 1)","0","10.0","100","300","300","0","80","32"
+"1","1","python","h","gemmKernel","1","7","(192, 1, 1)","(148, 1, 1)","0","10.0","1000","200","134","90","9","168"
+'''
+
+
+def test_roofline_report_from_ncu_csv(tmp_path, capsys):
+    from rocm_systems_b200.tools import roofline
+
+    ks = roofline.parse_ncu_csv(NCU_CSV)
+    assert [k.name for k in ks] == ["rmsnormKernel", "gemmKernel"]
+    assert ks[0].duration_ns == 100e3 and ks[0].dram_bytes == 600e6 and abs(ks[0].gbs - 6000) < 1e-6
+    peaks = {"hbm_gbs": 6541.5, "bf16_tflops": 1601.7, "source": "measured"}
+    assert roofline.classify(ks[0], peaks) == "memory"
+    ks[1].flops = 2 * 8192.0 ** 3
+    assert roofline.classify(ks[1], peaks) == "compute" and abs(ks[1].tflops - 1099.5) < 1
+    (tmp_path / "p.json").write_text(json.dumps({"hbm_gbs": 6541.5, "bf16_tflops": 1601.7}))
+    (tmp_path / "raw.csv").write_text(NCU_CSV)
+    rc = roofline.main([str(tmp_path / "raw.csv"), "--peaks", str(tmp_path / "p.json"), "--flops", "gemm=1.0995e12", "--plot",
+                        "--point", "probe:1e9:1e9:1e-3"])
+    text = capsys.readouterr().out
+    assert rc == 0 and "of measured" in text and "latency/occupancy" in text and "A: gemmKernel" in text
+
+
+def test_info_runs_without_gpu():
+    e = dict(os.environ, PYTHONPATH=str(ROOT))
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.info", "--json"], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr
+    doc = json.loads(p.stdout)
+    assert "host" in doc and "b200coll" in doc["libraries"] and isinstance(doc["devices"], list)
+    from rocm_systems_b200.tools.info import arch_target
+
+    assert arch_target(10, 0) == "sm_100a" and arch_target(8, 0) == "sm_80"
