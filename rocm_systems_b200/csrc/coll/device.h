@@ -33,13 +33,13 @@ struct LocalState {
   uint32_t barEpoch[kMaxCtas];                 // barriers completed, per CTA slot
   uint32_t failed;                             // set once a wait gave up: later waits return at once
   uint32_t pad[3];
-  unsigned long long p2pSent[kMaxRanks][8];    // chunks pushed to (peer, sub-channel) so far
-  unsigned long long p2pRecvd[kMaxRanks][8];   // chunks consumed from (peer, sub-channel) so far
+  unsigned long long p2pSent[kMaxRanks][kMaxP2pSubs];    // chunks pushed to (peer, sub-channel) so far
+  unsigned long long p2pRecvd[kMaxRanks][kMaxP2pSubs];   // chunks consumed from (peer, sub-channel) so far
 };
 
 // Byte offsets inside the symmetric workspace of every rank.
 constexpr size_t kWsBarOff = 0;          // uint32 bar[kMaxCtas][kMaxRanks]
-constexpr size_t kWsP2pCtrlOff = 8192;   // uint64 tail[kMaxRanks][8], then head[kMaxRanks][8]
+constexpr size_t kWsP2pCtrlOff = 8192;   // uint64 tail[kMaxRanks][kMaxP2pSubs], then head[kMaxRanks][kMaxP2pSubs]
 constexpr size_t kWsUserFlagsOff = 16384;  // 48 KiB of flags for the shmem layer (barrier_all, …)
 constexpr size_t kWsLLOff = 65536;
 
@@ -82,6 +82,7 @@ struct CollArgs {
   char* sendMc;
   char* recvMc;
   int direct;            // 1: use the windows above
+  size_t chunkBytes;     // staged reduce: bytes per pipeline chunk (per slice for ReduceScatter); 0 = a whole staging half
 };
 
 struct LLArgs {

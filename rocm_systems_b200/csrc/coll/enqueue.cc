@@ -123,8 +123,12 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   if (algo == ALGO_LL && !llOk) algo = ALGO_AUTO;
   if (algo == ALGO_NVLS && !nvlsOk) algo = ALGO_AUTO;
   if (algo == ALGO_AUTO) {
+    // In-switch reduction moves S(1 + 1/n) bytes per GPU and direction for an all-reduce of S
+    // bytes (every rank's copy goes to the switch, the requester's own included) against
+    // 2S(n-1)/n with peer loads and stores: a win from four ranks up, a loss between two.
+    const bool nvlsPays = !reducing || n > 2;
     if (llOk) algo = ALGO_LL;
-    else if (nvlsOk && bytes * (r.kind == COLL_REDUCESCATTER ? n : 1) >= (32u << 10)) algo = ALGO_NVLS;
+    else if (nvlsOk && nvlsPays && bytes * (r.kind == COLL_REDUCESCATTER ? n : 1) >= (32u << 10)) algo = ALGO_NVLS;
     else algo = ALGO_P2P;
   }
 
@@ -172,8 +176,24 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   args->direct = direct ? 1 : 0;
 
   size_t chunks = 0;
+  args->chunkBytes = 0;
   if (algo != ALGO_LL && !direct) {
+    const bool reduceKind = r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE;
     size_t cap = r.kind == COLL_REDUCESCATTER ? ((c->dev.stageBytes / n) & ~(size_t)15) : c->dev.stageBytes;
+    if (reduceKind) {
+      // Pipeline chunk: an eighth of what moves through staging, between 8 MiB (below that the
+      // per-chunk barrier costs more than the overlap wins) and one staging half.
+      const size_t staged = r.kind == COLL_REDUCESCATTER ? bytes * n : bytes;
+      if (staged >= (size_t)16 << 20) {
+        size_t chunk = std::max<size_t>((size_t)8 << 20, ((staged / 8) + ((1u << 20) - 1)) & ~(size_t)((1u << 20) - 1));
+        chunk = std::min(chunk, c->dev.stageBytes);
+        const size_t perCall = r.kind == COLL_REDUCESCATTER ? (chunk / n) & ~(size_t)15 : chunk;
+        if (perCall >= 16 && perCall < cap) {
+          args->chunkBytes = perCall;
+          cap = perCall;
+        }
+      }
+    }
     chunks = (bytes + cap - 1) / cap;
   }
   if (!ctas) {

@@ -14,8 +14,9 @@
 //                     staging, with one multicast store when NVLS is on; the others copy out).
 //   kP2p              grouped Send/Recv work list over per-peer FIFOs with credits; AllToAll(v),
 //                     Gather and Scatter are built from it.
-// Staging halves alternate per chunk; every chunk has a full barrier after its copy-in, which
-// is what makes reusing a half two chunks later safe without a trailing barrier.
+// Staging halves alternate per chunk; every chunk's copy-in is followed by a full barrier before
+// anyone reads it, which is what makes reusing a half two chunks later safe without a trailing
+// barrier, also across calls.
 #pragma once
 
 #include <type_traits>
@@ -151,9 +152,8 @@ __device__ __forceinline__ void storeUser16(char* base, size_t byteOff, size_t l
 // Copy into staging while multiplying by this rank's PreMulSum scalar (staging is 16-byte
 // aligned; the user buffer may not be).
 template <typename T>
-__device__ __forceinline__ void ctaCopyScaled(char* dst, const char* src, size_t bytes, typename ElemTraits<T>::Acc scalar) {
+__device__ __forceinline__ void ctaCopyScaled(char* dst, const char* src, size_t bytes, typename ElemTraits<T>::Acc scalar, const int t, const int nt) {
   using P = Pack<T>;
-  const int t = threadIdx.x, nt = blockDim.x;
   if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
     const size_t nvec = bytes >> 4;
     for (size_t i = t; i < nvec; i += nt) {
@@ -171,8 +171,16 @@ __device__ __forceinline__ void ctaCopyScaled(char* dst, const char* src, size_t
   }
 }
 
+// Staged mode is software-pipelined over chunks: while one half of the CTA's threads reduces chunk
+// k over NVLink, the other half copies chunk k-1's results out of staging and chunk k+1's input
+// into it (both local HBM traffic), with one inter-rank barrier per chunk:
+//
+//     copyIn(0) | barrier | { reduce(k)  ||  copyOut(k-1); copyIn(k+1) } barrier | ... | copyOut(last)
+//
+// Chunk k lives in staging half (first + k) & 1. reduce(k) touches every rank's half k; the copies
+// touch only this rank's other half, which nobody reads remotely between the barriers around them.
 template <typename T, typename Op, bool NVLS>
-__global__ void __launch_bounds__(kReduceThreads) kStagedReduce(const __grid_constant__ DevComm c, const __grid_constant__ CollArgs a) {
+__global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedReduce(const __grid_constant__ DevComm c, const __grid_constant__ CollArgs a) {
   stampBegin(c);
   using P = Pack<T>;
   using Acc = typename ElemTraits<T>::Acc;
@@ -184,167 +192,203 @@ __global__ void __launch_bounds__(kReduceThreads) kStagedReduce(const __grid_con
   const bool isAR = a.kind == COLL_ALLREDUCE;
   const bool isRed = a.kind == COLL_REDUCE;
   const size_t total = a.count * ES;  // AllReduce/Reduce: the message; ReduceScatter: one rank's slice
-  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : (isRS ? (c.stageBytes / n) & ~(size_t)15 : c.stageBytes);
+  const size_t fullCap = isRS ? (c.stageBytes / n) & ~(size_t)15 : c.stageBytes;
+  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : ((a.chunkBytes && a.chunkBytes < fullCap) ? a.chunkBytes : fullCap);
   const Acc scalar = scalarFromBits<T>(a.scalarBits);
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
-  int half = a.stageHalf;
 
-  for (size_t off = 0; off < total; off += cap, half ^= 1) {
-    const size_t cb = (total - off < cap) ? total - off : cap;  // bytes of this chunk (per slice for RS)
-    const size_t U = (cb + 15) >> 4;
-    const size_t su = isRS ? U : (U + n - 1) / n;                // 16-byte units per slice
-    const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
-    // Where slice s starts: in the chunk (bytes), in staging, and how long it is.
-    auto sliceBytes = [&](int s) -> size_t {
-      if (isRS) return cb;
-      size_t lo = (size_t)s * su * 16;
-      if (lo >= cb) return 0;
-      size_t len = cb - lo;
-      return len < su * 16 ? len : su * 16;
-    };
-    auto sliceStage = [&](int s) -> size_t { return isRS ? (size_t)s * cap : (size_t)s * su * 16; };
-    auto sliceSrc = [&](int s) -> const char* {
-      return isRS ? send + ((size_t)s * a.count * ES + off) : send + off + (size_t)s * su * 16;
-    };
+  // Geometry of the chunk that starts at byte `off` (per slice for ReduceScatter).
+  struct Geo {
+    size_t off, cb, su, stageBase;
+  };
+  auto geo = [&](size_t off, int half) -> Geo {
+    Geo g;
+    g.off = off;
+    g.cb = (total - off < cap) ? total - off : cap;
+    const size_t U = (g.cb + 15) >> 4;
+    g.su = isRS ? U : (U + n - 1) / n;  // 16-byte units per slice
+    g.stageBase = c.stageOff + (size_t)half * c.stageBytes;
+    return g;
+  };
+  auto sliceBytes = [&](const Geo& g, int s) -> size_t {
+    if (isRS) return g.cb;
+    size_t lo = (size_t)s * g.su * 16;
+    if (lo >= g.cb) return 0;
+    size_t len = g.cb - lo;
+    return len < g.su * 16 ? len : g.su * 16;
+  };
+  auto sliceStage = [&](const Geo& g, int s) -> size_t { return isRS ? (size_t)s * cap : (size_t)s * g.su * 16; };
+  auto sliceSrc = [&](const Geo& g, int s) -> const char* {
+    return isRS ? send + ((size_t)s * a.count * ES + g.off) : send + g.off + (size_t)s * g.su * 16;
+  };
 
-    if (!a.direct) {
-      for (int i = 0; i < n; i++) {
-        const int s = (rank + i) % n;
-        const size_t sb = sliceBytes(s);
-        size_t lo, hi;
-        splitUnits((sb + 15) >> 4, B, b, lo, hi);
-        if (lo < hi) {
-          size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
-          if (a.scaleMode == SCALE_PRE_MUL) ctaCopyScaled<T>(c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), sliceSrc(s) + (lo << 4), bytes, scalar);
-          else ctaCopy(c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), sliceSrc(s) + (lo << 4), bytes);
-        }
+  // user send -> this rank's staging, by threads t of nt
+  auto copyIn = [&](const Geo& g, int t, int ntg) {
+    for (int i = 0; i < n; i++) {
+      const int s = (rank + i) % n;
+      const size_t sb = sliceBytes(g, s);
+      size_t lo, hi;
+      splitUnits((sb + 15) >> 4, B, b, lo, hi);
+      if (lo < hi) {
+        size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
+        char* dst = c.ws[rank] + g.stageBase + sliceStage(g, s) + (lo << 4);
+        if (a.scaleMode == SCALE_PRE_MUL) ctaCopyScaled<T>(dst, sliceSrc(g, s) + (lo << 4), bytes, scalar, t, ntg);
+        else groupCopy(dst, sliceSrc(g, s) + (lo << 4), bytes, t, ntg);
       }
     }
-    ctaBarrier(c, epoch);
+  };
+  // this rank's staging -> user recv (AllReduce; Reduce root without NVLS)
+  auto copyOut = [&](const Geo& g, int t, int ntg) {
+    for (int i = 0; i < n; i++) {
+      const int s = (rank + i) % n;
+      const size_t sb = sliceBytes(g, s);
+      size_t lo, hi;
+      splitUnits((sb + 15) >> 4, B, b, lo, hi);
+      if (lo < hi) {
+        size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
+        groupCopy(recv + g.off + (size_t)s * g.su * 16 + (lo << 4), c.ws[rank] + g.stageBase + sliceStage(g, s) + (lo << 4), bytes, t, ntg);
+      }
+    }
+  };
 
-    // Reduce. Normally this rank reduces slice `rank`; the NVLS Reduce root pulls every slice.
+  // Reduce. Normally this rank reduces slice `rank`; the NVLS Reduce root pulls every slice.
+  auto reduceChunk = [&](const Geo& g, const int t, const int ntg) {
+    const size_t off = g.off;
     const bool pullAll = NVLS && isRed;
-    if (!pullAll || rank == a.root) {
-      for (int si = 0; si < (pullAll ? n : 1); si++) {
-        const int s = pullAll ? si : rank;
-        const size_t sb = sliceBytes(s);
-        size_t lo, hi;
-        splitUnits((sb + 15) >> 4, B, b, lo, hi);
-        // Byte offset of the slice inside the message (direct windows and user recv).
-        const size_t msgOff = isRS ? off : off + (size_t)s * su * 16;
-        const size_t stOff = stageBase + sliceStage(s);
-        const bool recvAligned = (((uintptr_t)(recv + (isRS ? off : msgOff))) & 15) == 0;
-        // Sources and destinations of this slice.
-        const size_t srcOff = isRS ? (size_t)s * a.count * ES + off : msgOff;
-        const char* mcSrc = NVLS ? (a.direct ? a.sendMc + srcOff : c.wsMc + stOff) : nullptr;
-        char* mcDst = (NVLS && isAR) ? (a.direct ? a.recvMc + msgOff : c.wsMc + stOff) : nullptr;
-        // Peer bases come from the kernel parameters (constant bank), indexed by unrolled loops.
-        auto pSrc = [&](int p) -> const char* { return a.direct ? a.sendPeer[p] + srcOff : c.ws[p] + stOff; };
-        auto pDst = [&](int p) -> char* { return a.direct ? a.recvPeer[p] + msgOff : c.ws[p] + stOff; };
-        auto deliver = [&](size_t u, uint4 out) {
-          if (isRS) {
-            storeUser16<T>(recv, off + (u << 4), total, out, recvAligned);
-          } else if (isAR) {
-            if constexpr (NVLS) {
-              mcStore16(mcDst + (u << 4), out);
-            } else {
-#pragma unroll
-              for (int p = 0; p < kMaxRanks; p++)
-                if (p < n) st16(pDst(p) + (u << 4), out);
-            }
-          } else {  // Reduce
-            if constexpr (NVLS) storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
-            else st16(pDst(a.root) + (u << 4), out);
-          }
-        };
-        // `UN` independent 16-byte units per thread are loaded before any is consumed, so enough
-        // NVLink requests are in flight to cover the link latency.
-        auto body = [&](auto unTag, auto maxrTag, size_t u0) {
-          constexpr int UN = decltype(unTag)::value;
-          constexpr int MAXR = decltype(maxrTag)::value;  // upper bound on the rank count
-          uint4 out[UN];
+    if (pullAll && rank != a.root) return;
+    for (int si = 0; si < (pullAll ? n : 1); si++) {
+      const int s = pullAll ? si : rank;
+      const size_t sb = sliceBytes(g, s);
+      size_t lo, hi;
+      splitUnits((sb + 15) >> 4, B, b, lo, hi);
+      // Byte offset of the slice inside the message (direct windows and user recv).
+      const size_t msgOff = isRS ? off : off + (size_t)s * g.su * 16;
+      const size_t stOff = g.stageBase + sliceStage(g, s);
+      const bool recvAligned = (((uintptr_t)(recv + (isRS ? off : msgOff))) & 15) == 0;
+      // Sources and destinations of this slice.
+      const size_t srcOff = isRS ? (size_t)s * a.count * ES + off : msgOff;
+      const char* mcSrc = NVLS ? (a.direct ? a.sendMc + srcOff : c.wsMc + stOff) : nullptr;
+      char* mcDst = (NVLS && isAR) ? (a.direct ? a.recvMc + msgOff : c.wsMc + stOff) : nullptr;
+      // Peer bases come from the kernel parameters (constant bank), indexed by unrolled loops.
+      auto pSrc = [&](int p) -> const char* { return a.direct ? a.sendPeer[p] + srcOff : c.ws[p] + stOff; };
+      auto pDst = [&](int p) -> char* { return a.direct ? a.recvPeer[p] + msgOff : c.ws[p] + stOff; };
+      auto deliver = [&](size_t u, uint4 out) {
+        if (isRS) {
+          storeUser16<T>(recv, off + (u << 4), total, out, recvAligned);
+        } else if (isAR) {
           if constexpr (NVLS) {
-#pragma unroll
-            for (int j = 0; j < UN; j++) out[j] = McReduce<T>::ld(mcSrc + ((u0 + (size_t)j * nt) << 4));
-            if (a.scaleMode == SCALE_POST_DIV_N) {
-#pragma unroll
-              for (int j = 0; j < UN; j++) {
-                Acc acc[P::N];
-                P::up(out[j], acc);
-#pragma unroll
-                for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
-                out[j] = P::down(acc);
-              }
-            }
+            mcStore16(mcDst + (u << 4), out);
           } else {
-            uint4 v[UN][MAXR];
 #pragma unroll
-            for (int j = 0; j < UN; j++) {
+            for (int p = 0; p < kMaxRanks; p++)
+              if (p < n) st16(pDst(p) + (u << 4), out);
+          }
+        } else {  // Reduce
+          if constexpr (NVLS) storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
+          else st16(pDst(a.root) + (u << 4), out);
+        }
+      };
+      // `UN` independent 16-byte units per thread are loaded before any is consumed, so enough
+      // NVLink requests are in flight to cover the link latency.
+      auto body = [&](auto unTag, auto maxrTag, size_t u0) {
+        constexpr int UN = decltype(unTag)::value;
+        constexpr int MAXR = decltype(maxrTag)::value;  // upper bound on the rank count
+        uint4 out[UN];
+        if constexpr (NVLS) {
 #pragma unroll
-              for (int p = 0; p < MAXR; p++)
-                if (p < n) v[j][p] = ldStream16(pSrc(p) + ((u0 + (size_t)j * nt) << 4));
-            }
+          for (int j = 0; j < UN; j++) out[j] = McReduce<T>::ld(mcSrc + ((u0 + (size_t)j * ntg) << 4));
+          if (a.scaleMode == SCALE_POST_DIV_N) {
 #pragma unroll
             for (int j = 0; j < UN; j++) {
               Acc acc[P::N];
+              P::up(out[j], acc);
 #pragma unroll
-              for (int p = 0; p < MAXR; p++) {
-                if (p < n) {
-                  Acc x[P::N];
-                  P::up(v[j][p], x);
-#pragma unroll
-                  for (int k = 0; k < P::N; k++) acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
-                }
-              }
-              if (a.scaleMode == SCALE_POST_DIV_N) {
-#pragma unroll
-                for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
-              }
+              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
               out[j] = P::down(acc);
             }
           }
-#pragma unroll
-          for (int j = 0; j < UN; j++) deliver(u0 + (size_t)j * nt, out[j]);
-        };
-        size_t u = lo + tid;
-        using I1 = std::integral_constant<int, 1>;
-        using I2 = std::integral_constant<int, 2>;
-        using I4 = std::integral_constant<int, 4>;
-        using I8 = std::integral_constant<int, 8>;
-        if constexpr (NVLS) {
-          for (; u + (size_t)7 * nt < hi; u += (size_t)8 * nt) body(I8{}, I1{}, u);
-          for (; u < hi; u += nt) body(I1{}, I1{}, u);
         } else {
-          if (n <= 2) {
-            for (; u + (size_t)3 * nt < hi; u += (size_t)4 * nt) body(I4{}, I2{}, u);
-            for (; u < hi; u += nt) body(I1{}, I2{}, u);
-          } else if (n <= 4) {
-            for (; u + (size_t)3 * nt < hi; u += (size_t)4 * nt) body(I4{}, I4{}, u);
-            for (; u < hi; u += nt) body(I1{}, I4{}, u);
-          } else {
-            for (; u + (size_t)nt < hi; u += (size_t)2 * nt) body(I2{}, I8{}, u);
-            for (; u < hi; u += nt) body(I1{}, I8{}, u);
+          uint4 v[UN][MAXR];
+#pragma unroll
+          for (int j = 0; j < UN; j++) {
+#pragma unroll
+            for (int p = 0; p < MAXR; p++)
+              if (p < n) v[j][p] = ldStream16(pSrc(p) + ((u0 + (size_t)j * ntg) << 4));
+          }
+#pragma unroll
+          for (int j = 0; j < UN; j++) {
+            Acc acc[P::N];
+#pragma unroll
+            for (int p = 0; p < MAXR; p++) {
+              if (p < n) {
+                Acc x[P::N];
+                P::up(v[j][p], x);
+#pragma unroll
+                for (int k = 0; k < P::N; k++) acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
+              }
+            }
+            if (a.scaleMode == SCALE_POST_DIV_N) {
+#pragma unroll
+              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
+            }
+            out[j] = P::down(acc);
           }
         }
-      }
-    }
-
-    const bool needSecond = isAR || (isRed && !NVLS) || a.direct;
-    if (needSecond) ctaBarrier(c, epoch);
-
-    if (!a.direct && (isAR || (isRed && !NVLS && rank == a.root))) {
-      for (int i = 0; i < n; i++) {
-        const int s = (rank + i) % n;
-        const size_t sb = sliceBytes(s);
-        size_t lo, hi;
-        splitUnits((sb + 15) >> 4, B, b, lo, hi);
-        if (lo < hi) {
-          size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
-          ctaCopy(recv + off + (size_t)s * su * 16 + (lo << 4), c.ws[rank] + stageBase + sliceStage(s) + (lo << 4), bytes);
+#pragma unroll
+        for (int j = 0; j < UN; j++) deliver(u0 + (size_t)j * ntg, out[j]);
+      };
+      size_t u = lo + t;
+      using I1 = std::integral_constant<int, 1>;
+      using I2 = std::integral_constant<int, 2>;
+      using I4 = std::integral_constant<int, 4>;
+      using I8 = std::integral_constant<int, 8>;
+      if constexpr (NVLS) {
+        for (; u + (size_t)7 * ntg < hi; u += (size_t)8 * ntg) body(I8{}, I1{}, u);
+        for (; u < hi; u += ntg) body(I1{}, I1{}, u);
+      } else {
+        // 64 data registers per thread whatever the rank count: 1 KiB in flight per thread.
+        if (n <= 2) {
+          for (; u + (size_t)7 * ntg < hi; u += (size_t)8 * ntg) body(I8{}, I2{}, u);
+          for (; u < hi; u += ntg) body(I1{}, I2{}, u);
+        } else if (n <= 4) {
+          for (; u + (size_t)3 * ntg < hi; u += (size_t)4 * ntg) body(I4{}, I4{}, u);
+          for (; u < hi; u += ntg) body(I1{}, I4{}, u);
+        } else {
+          for (; u + (size_t)ntg < hi; u += (size_t)2 * ntg) body(I2{}, I8{}, u);
+          for (; u < hi; u += ntg) body(I1{}, I8{}, u);
         }
       }
     }
+  };
+
+  // Zero-copy windows (direct) are one chunk with no copies: a barrier before (inputs complete
+  // everywhere) and after (nobody leaves while a peer still reads its buffer or has stores to it
+  // in flight).
+  const bool hasOut = !a.direct && (isAR || (isRed && !NVLS && rank == a.root));  // results come back through staging
+  const bool barAfter = a.direct || isAR || (isRed && !NVLS);                     // every chunk's reduce ends with a barrier
+  int half = a.direct ? 0 : a.stageHalf;
+  if (!a.direct) copyIn(geo(0, half), tid, nt);
+  ctaBarrier(c, epoch);
+  for (size_t off = 0; off < total; off += cap, half ^= 1) {
+    const Geo g = geo(off, half);
+    const bool more = off + cap < total;
+    const bool prevOut = hasOut && off > 0;
+    // With local copies to overlap, the lower half of the CTA reduces over NVLink and the upper
+    // half copies; otherwise every thread reduces.
+    const int h = (more || prevOut) ? nt >> 1 : nt;
+    if (tid < h) {
+      reduceChunk(g, tid, h);
+    } else {
+      if (prevOut) {
+        copyOut(geo(off - cap, half ^ 1), tid - h, nt - h);
+        // the copy-in below overwrites what other threads of this group have just read
+        asm volatile("bar.sync 1, %0;" ::"r"(nt - h) : "memory");
+      }
+      if (more) copyIn(geo(off + cap, half ^ 1), tid - h, nt - h);
+    }
+    if (barAfter || more) ctaBarrier(c, epoch);
+    if (!more && hasOut) copyOut(g, tid, nt);
   }
   if (tid == 0) c.local->barEpoch[b] = epoch;
   stampEnd(c);
@@ -355,7 +399,21 @@ __device__ __forceinline__ void ctaCopyToMc(char* mcDst, const char* src, size_t
   // Multicast store of whole 16-byte units (staging is padded, so rounding up is safe).
   const size_t nvec = (bytes + 15) >> 4;
   const bool aligned = (((uintptr_t)src) & 15) == 0;
-  for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+  size_t i = threadIdx.x;
+  if (aligned) {
+    // whole units with eight loads in flight per thread; the ragged end goes through the loop below
+    const size_t whole = bytes >> 4;
+    constexpr int U = 8;
+    const size_t nt = blockDim.x;
+    for (; i + (U - 1) * nt < whole; i += U * nt) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) v[u] = ldStream16(src + ((i + u * nt) << 4));
+#pragma unroll
+      for (int u = 0; u < U; u++) mcStore16(mcDst + ((i + u * nt) << 4), v[u]);
+    }
+  }
+  for (; i < nvec; i += blockDim.x) {
     uint4 v;
     if (aligned && ((i + 1) << 4) <= bytes) {
       v = ldStream16(src + (i << 4));
@@ -382,6 +440,50 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
   int half = a.stageHalf;
   const bool isAG = a.kind == COLL_ALLGATHER;
 
+  // This CTA's part of the chunk at `off`: byte offset inside the chunk and length.
+  auto part = [&](size_t off, size_t& bo, size_t& bytes) {
+    const size_t cb = (total - off < cap) ? total - off : cap;
+    size_t lo, hi;
+    splitUnits((cb + 15) >> 4, B, b, lo, hi);
+    bytes = lo < hi ? (((hi << 4) < cb ? (hi << 4) : cb) - (lo << 4)) : 0;
+    bo = lo << 4;
+  };
+  if (isAG && !a.direct) {
+    // Staged all-gather, pipelined like the staged reduce: while the lower half of the CTA pulls
+    // chunk k from the peers' staging over NVLink, the upper half copies this rank's own part
+    // to its place in recv and stages chunk k+1 (both local). One barrier per chunk.
+    const int tid = threadIdx.x, nt = blockDim.x;
+    size_t bo, bytes;
+    part(0, bo, bytes);
+    ctaCopy(c.ws[rank] + c.stageOff + (size_t)half * c.stageBytes + bo, send + bo, bytes);
+    ctaBarrier(c, epoch);
+    for (size_t off = 0; off < total; off += cap, half ^= 1) {
+      const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
+      part(off, bo, bytes);
+      const bool more = off + cap < total;
+      const bool selfCopy = recv + (size_t)rank * total != send;
+      const bool split = more || selfCopy;
+      const int h = split ? nt >> 1 : nt;
+      if (tid < h) {
+        for (int i = 1; i < n; i++) {
+          const int p = (rank + i) % n;
+          groupCopy(recv + (size_t)p * total + off + bo, c.ws[p] + stageBase + bo, bytes, tid, h);
+        }
+      } else {
+        if (selfCopy) groupCopy(recv + (size_t)rank * total + off + bo, send + off + bo, bytes, tid - h, nt - h);
+        if (more) {
+          size_t nbo, nbytes;
+          part(off + cap, nbo, nbytes);
+          groupCopy(c.ws[rank] + c.stageOff + (size_t)(half ^ 1) * c.stageBytes + nbo, send + off + cap + nbo, nbytes, tid - h, nt - h);
+        }
+      }
+      if (more) ctaBarrier(c, epoch);
+    }
+    if (threadIdx.x == 0) c.local->barEpoch[b] = epoch;
+    stampEnd(c);
+    return;
+  }
+
   for (size_t off = 0; off < total; off += cap, half ^= 1) {
     const size_t cb = (total - off < cap) ? total - off : cap;
     const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
@@ -390,8 +492,7 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
     const size_t bytes = lo < hi ? (((hi << 4) < cb ? (hi << 4) : cb) - (lo << 4)) : 0;
     const size_t bo = lo << 4;  // byte offset of this CTA's part inside the chunk
 
-    if (isAG) {
-      if (!a.direct) ctaCopy(c.ws[rank] + stageBase + bo, send + off + bo, bytes);
+    if (isAG) {  // direct windows: pull straight from the peers' send buffers
       ctaBarrier(c, epoch);
       for (int i = 0; i < n; i++) {
         const int p = (rank + i) % n;
@@ -399,11 +500,10 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
         if (p == rank) {
           if (dst != send + off + bo) ctaCopy(dst, send + off + bo, bytes);
         } else {
-          const char* src = a.direct ? a.sendPeer[p] + off + bo : c.ws[p] + stageBase + bo;
-          ctaCopy(dst, src, bytes);
+          ctaCopy(dst, a.sendPeer[p] + off + bo, bytes);
         }
       }
-      if (a.direct) ctaBarrier(c, epoch);
+      ctaBarrier(c, epoch);
     } else {  // Broadcast
       if (a.direct) {
         ctaBarrier(c, epoch);
@@ -453,9 +553,9 @@ __global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ Dev
     const size_t end = (hi << 4) < wk.bytes ? (hi << 4) : wk.bytes;
     const size_t chunk = c.p2pChunkBytes;
     unsigned long long* myTail = (unsigned long long*)(c.ws[rank] + kWsP2pCtrlOff);
-    unsigned long long* myHead = myTail + kMaxRanks * 8;
+    unsigned long long* myHead = myTail + kMaxRanks * kMaxP2pSubs;
     unsigned long long* peerTail = (unsigned long long*)(c.ws[peer] + kWsP2pCtrlOff);
-    unsigned long long* peerHead = peerTail + kMaxRanks * 8;
+    unsigned long long* peerHead = peerTail + kMaxRanks * kMaxP2pSubs;
     __shared__ int okShared;
     if (wk.isSend) {
       unsigned long long sent = c.local->p2pSent[peer][j];
@@ -464,7 +564,7 @@ __global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ Dev
         const size_t nb = end - o < chunk ? end - o : chunk;
         if (threadIdx.x == 0) {
           unsigned long long need = sent + 1 > (unsigned long long)c.p2pSlots ? sent + 1 - c.p2pSlots : 0;
-          okShared = waitGe64(c, &myHead[peer * 8 + j], need, WAIT_P2P_CREDIT, peer) ? 1 : 0;
+          okShared = waitGe64(c, &myHead[peer * kMaxP2pSubs + j], need, WAIT_P2P_CREDIT, peer) ? 1 : 0;
         }
         __syncthreads();
         if (okShared) ctaCopy(fifo + (size_t)(sent % c.p2pSlots) * chunk, wk.src + o, nb);
@@ -472,7 +572,7 @@ __global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ Dev
         sent++;
         if (threadIdx.x == 0) {
           __threadfence_system();
-          stReleaseSys64(&peerTail[rank * 8 + j], sent);
+          stReleaseSys64(&peerTail[rank * kMaxP2pSubs + j], sent);
         }
       }
       if (threadIdx.x == 0) c.local->p2pSent[peer][j] = sent;
@@ -481,14 +581,14 @@ __global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ Dev
       const char* fifo = c.ws[rank] + c.p2pOff + ((size_t)(peer * subs + j) * c.p2pSlots) * chunk;
       for (size_t o = begin; o < end; o += chunk) {
         const size_t nb = end - o < chunk ? end - o : chunk;
-        if (threadIdx.x == 0) okShared = waitGe64(c, &myTail[peer * 8 + j], recvd + 1, WAIT_P2P_DATA, peer) ? 1 : 0;
+        if (threadIdx.x == 0) okShared = waitGe64(c, &myTail[peer * kMaxP2pSubs + j], recvd + 1, WAIT_P2P_DATA, peer) ? 1 : 0;
         __syncthreads();
         if (okShared) ctaCopy(wk.dst + o, fifo + (size_t)(recvd % c.p2pSlots) * chunk, nb);
         __syncthreads();
         recvd++;
         if (threadIdx.x == 0) {
           __threadfence_system();
-          stReleaseSys64(&peerHead[rank * 8 + j], recvd);
+          stReleaseSys64(&peerHead[rank * kMaxP2pSubs + j], recvd);
         }
       }
       if (threadIdx.x == 0) c.local->p2pRecvd[peer][j] = recvd;

@@ -141,9 +141,9 @@ __device__ __forceinline__ void splitUnits(size_t units, int parts, int i, size_
 }
 
 // ---- copies ---------------------------------------------------------------------------------
-// Copy `bytes` bytes with the whole CTA. Fast path when both ends are 16-byte aligned.
-__device__ __forceinline__ void ctaCopy(void* dst, const void* src, size_t bytes) {
-  const int t = threadIdx.x, nt = blockDim.x;
+// Copy `bytes` bytes with threads t = 0..nt-1 of a thread group (by default the whole CTA). Fast
+// path when both ends are 16-byte aligned.
+__device__ __forceinline__ void groupCopy(void* dst, const void* src, size_t bytes, const int t, const int nt) {
   if (bytes == 0) return;
   if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
     const size_t nvec = bytes >> 4;
@@ -171,6 +171,7 @@ __device__ __forceinline__ void ctaCopy(void* dst, const void* src, size_t bytes
     for (size_t b = t; b < bytes; b += nt) ((char*)dst)[b] = ((const char*)src)[b];
   }
 }
+__device__ __forceinline__ void ctaCopy(void* dst, const void* src, size_t bytes) { groupCopy(dst, src, bytes, threadIdx.x, blockDim.x); }
 
 // ---- multimem (NVLS) ------------------------------------------------------------------------
 // One 16-byte in-switch reduction over every rank's copy of `mcAddr`, and the matching

@@ -23,7 +23,7 @@ cudaError_t B200_CAT(launchStaged_, B200_TN)(int op, bool nvls, int grid, cudaSt
   if (nvls) {
 #ifdef B200_NVLS_OK
     if (op != ncclSum) return cudaErrorInvalidValue;
-    kStagedReduce<B200_T, OpSum, true><<<grid, kReduceThreads, 0, s>>>(c, a);
+    kStagedReduce<B200_T, OpSum, true><<<grid, kCollThreads, 0, s>>>(c, a);  // switch-side adds need few registers: full-size CTAs
     return cudaGetLastError();
 #else
     return cudaErrorInvalidValue;

@@ -183,7 +183,7 @@ ncclResult_t commCreate(Comm** out, const ncclUniqueId& id, int nranks, int rank
   d.p2pOff = d.stageOff + 2 * d.stageBytes;
   d.p2pChunkBytes = solo ? 4096 : fl.p2pChunkBytes;
   // Few peers: more CTAs per peer so a pair of GPUs can still fill its links.
-  d.p2pSubs = fl.p2pCtasPerPeer > 0 ? fl.p2pCtasPerPeer : (nranks <= 2 ? 8 : (nranks <= 4 ? 6 : 4));
+  d.p2pSubs = fl.p2pCtasPerPeer > 0 ? fl.p2pCtasPerPeer : (nranks <= 2 ? 16 : (nranks <= 4 ? 8 : 4));
   d.p2pSlots = 4;
   const size_t p2pBytes = (size_t)nranks * d.p2pSubs * d.p2pSlots * d.p2pChunkBytes;
   const size_t total = d.p2pOff + p2pBytes;

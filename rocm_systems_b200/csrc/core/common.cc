@@ -104,7 +104,7 @@ static void load(Flags& f) {
   if (f.p2pChunkBytes < (64u << 10)) f.p2pChunkBytes = 64u << 10;
   f.p2pChunkBytes &= ~(size_t)0xfff;
   if (f.p2pCtasPerPeer < 0) f.p2pCtasPerPeer = 0;
-  if (f.p2pCtasPerPeer > 8) f.p2pCtasPerPeer = 8;
+  if (f.p2pCtasPerPeer > kMaxP2pSubs) f.p2pCtasPerPeer = kMaxP2pSubs;
   if (f.waitTimeoutMs < 1) f.waitTimeoutMs = 1;
 }
 

@@ -15,6 +15,7 @@ namespace b200 {
 constexpr int kMaxRanks = 8;     // one NVSwitch domain
 constexpr int kMaxCtas = 128;    // flag slots per communicator; also the CTA ceiling of a kernel
 constexpr int kCollThreads = 512;
+constexpr int kMaxP2pSubs = 16;     // send/recv sub-channels (CTAs) per peer, at most
 constexpr int kReduceThreads = 256;  // reducing kernels: fewer threads, more registers for loads in flight
 
 // ---- logging ------------------------------------------------------------------------------

@@ -165,23 +165,139 @@ __global__ void __launch_bounds__(kThreads) rmsnormBwd(const __nv_bfloat16* __re
   }
 }
 
+// The same gradient without atomics: every CTA walks `rowsPerCta` rows with the next row's loads in
+// flight while the current row is reduced and stored, and leaves its partial dw in
+// partials[cta][H]; colSumKernel adds the partials in a fixed order, so dw is deterministic.
+template <int VPT>
+__global__ void __launch_bounds__(kThreads) rmsnormBwdRows(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstdIn,
+                                                           __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int T, int H, int rowsPerCta) {
+  __shared__ float sh[32];
+  const int nvec = H >> 3;
+  const Bf8* wr = reinterpret_cast<const Bf8*>(w);
+  Bf8 wraw[VPT], xn[VPT], gn[VPT];
+  float dwAcc[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    const int j = threadIdx.x + i * kThreads;
+    if (j < nvec) wraw[i] = wr[j];
+#pragma unroll
+    for (int k = 0; k < 8; k++) dwAcc[i][k] = 0.f;
+  }
+  const int r0 = blockIdx.x * rowsPerCta;
+  const int r1 = min(T, r0 + rowsPerCta);
+  auto loadRow = [&](int row) {
+    const Bf8* xr = reinterpret_cast<const Bf8*>(x + (size_t)row * H);
+    const Bf8* gr = reinterpret_cast<const Bf8*>(dy + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int j = threadIdx.x + i * kThreads;
+      if (j < nvec) {
+        xn[i] = xr[j];
+        gn[i] = gr[j];
+      }
+    }
+  };
+  if (r0 < r1) loadRow(r0);
+  for (int row = r0; row < r1; row++) {
+    Bf8* dxr = reinterpret_cast<Bf8*>(dx + (size_t)row * H);
+    const float rstd = rstdIn[row];
+    float xv[VPT][8], gw[VPT][8];  // x and dy*w of this row
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int j = threadIdx.x + i * kThreads;
+      if (j < nvec) {
+        float gv[8], wv[8];
+        unpack8(xn[i], xv[i]);
+        unpack8(gn[i], gv);
+        unpack8(wraw[i], wv);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          dwAcc[i][k] += gv[k] * xv[i][k] * rstd;
+          gw[i][k] = gv[k] * wv[k];
+          dot += gw[i][k] * xv[i][k];
+        }
+      }
+    }
+    if (row + 1 < r1) loadRow(row + 1);  // in flight across the reduction and the stores below
+    dot = blockSum<kThreads>(dot, sh);
+    const float c = dot * rstd * rstd / (float)H;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int j = threadIdx.x + i * kThreads;
+      if (j < nvec) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) o[k] = rstd * (gw[i][k] - xv[i][k] * c);
+        dxr[j] = pack8(o);
+      }
+    }
+  }
+  float4* pr = reinterpret_cast<float4*>(partials + (size_t)blockIdx.x * H);
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    const int j = threadIdx.x + i * kThreads;
+    if (j < nvec) {
+      pr[2 * j] = make_float4(dwAcc[i][0], dwAcc[i][1], dwAcc[i][2], dwAcc[i][3]);
+      pr[2 * j + 1] = make_float4(dwAcc[i][4], dwAcc[i][5], dwAcc[i][6], dwAcc[i][7]);
+    }
+  }
+}
+
+// out[j] = sum_r in[r][j] for a [rows, cols] fp32 matrix: 32 columns per CTA, 8 row groups whose
+// sums meet in shared memory. Output as bf16 or fp32.
+template <typename O>
+__global__ void __launch_bounds__(256) colSumKernel(const float* __restrict__ in, O* __restrict__ out, int rows, int cols) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
+  float acc = 0.f;
+  if (col < cols) {
+    int r = g;
+    for (; r + 24 < rows; r += 32) {
+      const float a0 = in[(size_t)r * cols + col], a1 = in[(size_t)(r + 8) * cols + col], a2 = in[(size_t)(r + 16) * cols + col],
+                  a3 = in[(size_t)(r + 24) * cols + col];
+      acc += (a0 + a1) + (a2 + a3);
+    }
+    for (; r < rows; r += 8) acc += in[(size_t)r * cols + col];
+  }
+  sh[g][cx] = acc;
+  __syncthreads();
+  if (g == 0 && col < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) t += sh[k][cx];
+    if constexpr (sizeof(O) == 2) out[col] = __float2bfloat16(t);
+    else out[col] = t;
+  }
+}
+
 // ---- rotary embedding (rotate-half convention), in place on q and k ------------------------------
 // qk: [T, heads, D] bf16 (q heads then k heads handled by two launches or one with heads = nq + nk
 // when they are contiguous); cs: [S, D/2] float2 (cos, sin); pos = token index % S.
-__global__ void __launch_bounds__(kThreads) ropeKernel(__nv_bfloat16* __restrict__ qk, const float2* __restrict__ cs, int T, int heads,
-                                                       int D, int rowStride, int S, float sinSign) {
+// `in` may equal `out` (in place). Heads [heads, copyHeads) of every row are copied unrotated, so
+// an out-of-place call over a packed q|k|v row needs no separate copy of v.
+__global__ void __launch_bounds__(kThreads) ropeKernel(const __nv_bfloat16* in, __nv_bfloat16* out, const float2* __restrict__ cs, int T, int heads,
+                                                       int copyHeads, int D, int rowStride, int S, float sinSign) {
   // One thread rotates 4 pairs: elements [4j, 4j+4) with their partners at +D/2.
   const int half = D >> 1;
   const int perHead = half >> 2;
-  const size_t total = (size_t)T * heads * perHead;
+  const size_t total = (size_t)T * copyHeads * perHead;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int j = (int)(idx % perHead);
-    const int h = (int)((idx / perHead) % heads);
-    const size_t t = idx / ((size_t)perHead * heads);
+    const int h = (int)((idx / perHead) % copyHeads);
+    const size_t t = idx / ((size_t)perHead * copyHeads);
     const int pos = (int)(t % S);
-    __nv_bfloat16* base = qk + t * rowStride + (size_t)h * D + 4 * j;
-    uint2 lo = *reinterpret_cast<uint2*>(base);
-    uint2 hi = *reinterpret_cast<uint2*>(base + half);
+    const size_t eoff = t * rowStride + (size_t)h * D + 4 * j;
+    __nv_bfloat16* base = out + eoff;
+    uint2 lo = *reinterpret_cast<const uint2*>(in + eoff);
+    uint2 hi = *reinterpret_cast<const uint2*>(in + eoff + half);
+    if (h >= heads) {
+      *reinterpret_cast<uint2*>(base) = lo;
+      *reinterpret_cast<uint2*>(base + half) = hi;
+      continue;
+    }
     __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
     __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
     const float2* c = cs + (size_t)pos * half + 4 * j;
@@ -314,16 +430,29 @@ __global__ void __launch_bounds__(1024) crossEntropyFwdBwd(__nv_bfloat16* __rest
 }
 
 // ---- AdamW on a shard --------------------------------------------------------------------------------
-// fp32 master weights and moments, fp32 gradient; writes the bf16 working copy in the same pass.
+// fp32 master weights and moments; the gradient is fp32 (a reduce-scattered shard) or bf16 (the
+// backward pass's own output, when there is nothing to reduce: no cast pass in between). Writes
+// the bf16 working copy in the same pass.
+__device__ __forceinline__ float4 loadGrad4(const float* g, size_t i) { return reinterpret_cast<const float4*>(g)[i]; }
+__device__ __forceinline__ float4 loadGrad4(const __nv_bfloat16* g, size_t i) {
+  const uint2 raw = reinterpret_cast<const uint2*>(g)[i];
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float loadGrad1(const float* g, size_t i) { return g[i]; }
+__device__ __forceinline__ float loadGrad1(const __nv_bfloat16* g, size_t i) { return __bfloat162float(g[i]); }
+
+template <typename G>
 __global__ void __launch_bounds__(kThreads) adamwKernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                                                        const float* __restrict__ grad, __nv_bfloat16* __restrict__ param, size_t n, float lr,
+                                                        const G* __restrict__ grad, __nv_bfloat16* __restrict__ param, size_t n, float lr,
                                                         float b1, float b2, float eps, float wd, float bc1, float bc2, float gradScale) {
   const size_t nvec = n >> 2;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
     float4 w4 = reinterpret_cast<float4*>(master)[i];
     float4 m4 = reinterpret_cast<float4*>(m)[i];
     float4 v4 = reinterpret_cast<float4*>(v)[i];
-    float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+    float4 g4 = loadGrad4(grad, i);
     float* w = &w4.x; float* mm = &m4.x; float* vv = &v4.x; float* g = &g4.x;
 #pragma unroll
     for (int k = 0; k < 4; k++) {
@@ -343,7 +472,7 @@ __global__ void __launch_bounds__(kThreads) adamwKernel(float* __restrict__ mast
     reinterpret_cast<uint2*>(param)[i] = packed;
   }
   for (size_t i = (nvec << 2) + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const float gk = grad[i] * gradScale;
+    const float gk = loadGrad1(grad, i) * gradScale;
     const float mk = b1 * m[i] + (1.f - b1) * gk;
     const float vk = b2 * v[i] + (1.f - b2) * gk * gk;
     const float wk = master[i] - lr * ((mk / bc1) / (sqrtf(vk / bc2) + eps) + wd * master[i]);
@@ -438,13 +567,52 @@ int b200ops_rmsnorm_bwd(const void* dy, const void* x, const void* w, const floa
   return (int)cudaGetLastError();
 }
 
+// Deterministic variant. `partials` holds b200ops_rmsnorm_bwd_ctas(T) * H floats of scratch; dw
+// (H elements, bf16 when dwIsBf16 else fp32) is overwritten with the sum over rows.
+int b200ops_rmsnorm_bwd_ctas(long long T) {
+  long long ctas = 148 * 2;
+  if (ctas > T) ctas = T;
+  if (ctas < 1) return 1;
+  const long long rowsPerCta = (T + ctas - 1) / ctas;
+  return (int)((T + rowsPerCta - 1) / rowsPerCta);
+}
+int b200ops_rmsnorm_bwd_det(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* partials, void* dw, int dwIsBf16,
+                            long long T, int H, cudaStream_t s) {
+  if (H % 8 || H > 8 * kThreads * 4) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  const int nvec = H >> 3;
+  const int vpt = (nvec + kThreads - 1) / kThreads;
+  const int ctas = b200ops_rmsnorm_bwd_ctas(T);
+  const int rowsPerCta = (int)((T + ctas - 1) / ctas);
+  auto X = (const __nv_bfloat16*)x;
+  auto DY = (const __nv_bfloat16*)dy;
+  auto W = (const __nv_bfloat16*)w;
+  auto DX = (__nv_bfloat16*)dx;
+  if (vpt <= 1) rmsnormBwdRows<1><<<ctas, kThreads, 0, s>>>(DY, X, W, rstd, DX, partials, (int)T, H, rowsPerCta);
+  else if (vpt == 2) rmsnormBwdRows<2><<<ctas, kThreads, 0, s>>>(DY, X, W, rstd, DX, partials, (int)T, H, rowsPerCta);
+  else rmsnormBwdRows<4><<<ctas, kThreads, 0, s>>>(DY, X, W, rstd, DX, partials, (int)T, H, rowsPerCta);
+  if (dwIsBf16) colSumKernel<__nv_bfloat16><<<(H + 31) / 32, 256, 0, s>>>(partials, (__nv_bfloat16*)dw, ctas, H);
+  else colSumKernel<float><<<(H + 31) / 32, 256, 0, s>>>(partials, (float*)dw, ctas, H);
+  return (int)cudaGetLastError();
+}
+
 // Rotates `heads` heads of width D per token in place; rowStride is the element distance between
 // tokens. sinSign = +1 forward, -1 backward (the inverse rotation is the gradient).
 int b200ops_rope(void* qk, const float* cosSin, long long T, int heads, int D, int rowStride, int S, float sinSign, cudaStream_t s) {
   if (D % 8) return (int)cudaErrorInvalidValue;
   if (T == 0) return 0;
   const size_t total = (size_t)T * heads * (D >> 3);
-  ropeKernel<<<gridFor(total), kThreads, 0, s>>>((__nv_bfloat16*)qk, (const float2*)cosSin, (int)T, heads, D, rowStride, S, sinSign);
+  ropeKernel<<<gridFor(total), kThreads, 0, s>>>((const __nv_bfloat16*)qk, (__nv_bfloat16*)qk, (const float2*)cosSin, (int)T, heads, heads, D, rowStride, S, sinSign);
+  return (int)cudaGetLastError();
+}
+// Out of place over rows of `totalHeads` heads: the first `heads` are rotated, the rest copied.
+int b200ops_rope_oop(const void* in, void* out, const float* cosSin, long long T, int heads, int totalHeads, int D, int S, float sinSign,
+                     cudaStream_t s) {
+  if (D % 8 || heads > totalHeads) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  const size_t total = (size_t)T * totalHeads * (D >> 3);
+  ropeKernel<<<gridFor(total), kThreads, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, (const float2*)cosSin, (int)T, heads, totalHeads, D,
+                                                  totalHeads * D, S, sinSign);
   return (int)cudaGetLastError();
 }
 
@@ -473,7 +641,18 @@ int b200ops_adamw(float* master, float* m, float* v, const float* grad, void* pa
                   int step, float gradScale, cudaStream_t s) {
   if (n == 0) return 0;
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
-  adamwKernel<<<gridFor((size_t)n, 4), kThreads, 0, s>>>(master, m, v, grad, (__nv_bfloat16*)param, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, gradScale);
+  adamwKernel<float><<<gridFor((size_t)n, 4), kThreads, 0, s>>>(master, m, v, grad, (__nv_bfloat16*)param, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, gradScale);
+  return (int)cudaGetLastError();
+}
+
+// The same update from a bf16 gradient (8-byte aligned).
+int b200ops_adamw_bf16g(float* master, float* m, float* v, const void* grad, void* param, long long n, float lr, float b1, float b2, float eps,
+                        float wd, int step, float gradScale, cudaStream_t s) {
+  if (n == 0) return 0;
+  if ((uintptr_t)grad & 7) return (int)cudaErrorInvalidValue;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  adamwKernel<__nv_bfloat16><<<gridFor((size_t)n, 4), kThreads, 0, s>>>(master, m, v, (const __nv_bfloat16*)grad, (__nv_bfloat16*)param, (size_t)n, lr, b1, b2,
+                                                                         eps, wd, bc1, bc2, gradScale);
   return (int)cudaGetLastError();
 }
 

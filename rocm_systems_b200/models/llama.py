@@ -87,6 +87,27 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return _LinearWG.apply(x, w)
 
 
+class _SplitQKV(torch.autograd.Function):
+    """``[B, S, nh + 2 nkv, d]`` -> q, k, v as ``[B, heads, S, d]`` views. The backward writes the three
+    gradients into one buffer with three strided copies; slicing through autograd would zero-fill a
+    full-size tensor per slice and then add them up."""
+
+    @staticmethod
+    def forward(ctx, qkv4, nh, nkv):
+        ctx.nh, ctx.nkv = nh, nkv
+        return (qkv4[:, :, :nh].transpose(1, 2), qkv4[:, :, nh:nh + nkv].transpose(1, 2), qkv4[:, :, nh + nkv:].transpose(1, 2))
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        nh, nkv = ctx.nh, ctx.nkv
+        B, _, S, d = dq.shape
+        out = torch.empty(B, S, nh + 2 * nkv, d, dtype=dq.dtype, device=dq.device)
+        out[:, :, :nh].copy_(dq.transpose(1, 2))
+        out[:, :, nh:nh + nkv].copy_(dk.transpose(1, 2))
+        out[:, :, nh + nkv:].copy_(dv.transpose(1, 2))
+        return out, None, None
+
+
 def layer_specs(cfg: LlamaConfig) -> List[ParamSpec]:
     d = cfg.head_dim
     return [
@@ -107,10 +128,7 @@ def layer_forward(p: dict, x: torch.Tensor, cfg: LlamaConfig, rope: torch.Tensor
     h = ops.rmsnorm(x, p["attn_norm"], cfg.eps)
     qkv = linear(h, p["wqkv"]).view(T, nh + 2 * nkv, d)
     qkv = ops.rope_(qkv, rope, nh + nkv)
-    q4 = qkv.view(batch, S, nh + 2 * nkv, d)
-    q = q4[:, :, :nh].transpose(1, 2)
-    k = q4[:, :, nh:nh + nkv].transpose(1, 2)
-    v = q4[:, :, nh + nkv:].transpose(1, 2)
+    q, k, v = _SplitQKV.apply(qkv.view(batch, S, nh + 2 * nkv, d), nh, nkv)
     a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=nkv != nh)
     a = a.transpose(1, 2).reshape(T, nh * d)
     x = x + linear(a, p["wo"])

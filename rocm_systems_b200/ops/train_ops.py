@@ -25,7 +25,11 @@ def _lib_ops():
         vp, ll, i32, f32 = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
         lib.b200ops_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, ll, i32, f32, vp]
         lib.b200ops_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ll, i32, vp]
+        lib.b200ops_rmsnorm_bwd_ctas.argtypes = [ll]
+        lib.b200ops_rmsnorm_bwd_det.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, ll, i32, vp]
+        lib.b200ops_adamw_bf16g.argtypes = [vp, vp, vp, vp, vp, ll, f32, f32, f32, f32, f32, i32, f32, vp]
         lib.b200ops_rope.argtypes = [vp, vp, ll, i32, i32, i32, i32, f32, vp]
+        lib.b200ops_rope_oop.argtypes = [vp, vp, vp, ll, i32, i32, i32, i32, f32, vp]
         lib.b200ops_swiglu_fwd.argtypes = [vp, vp, ll, i32, vp]
         lib.b200ops_swiglu_bwd.argtypes = [vp, vp, vp, ll, i32, vp]
         lib.b200ops_cross_entropy.argtypes = [vp, vp, vp, ll, i32, ll, f32, vp]
@@ -73,9 +77,16 @@ class _RMSNorm(torch.autograd.Function):
         H = x.shape[-1]
         T = x.numel() // H
         dx = torch.empty_like(x)
-        dw = torch.zeros(H, dtype=torch.float32, device=x.device)
-        _ck(_lib_ops().b200ops_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), T, H, _s()), "rmsnorm_bwd")
-        return dx, dw.to(w.dtype), None
+        lib = _lib_ops()
+        # per-CTA partial sums of dw, added in a fixed order by a second small kernel: no atomics
+        partials = torch.empty(int(lib.b200ops_rmsnorm_bwd_ctas(T)) * H, dtype=torch.float32, device=x.device)
+        dw = torch.empty(H, dtype=w.dtype, device=x.device)
+        assert w.dtype in (torch.bfloat16, torch.float32)
+        _ck(lib.b200ops_rmsnorm_bwd_det(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), partials.data_ptr(), dw.data_ptr(),
+                                        1 if w.dtype == torch.bfloat16 else 0, T, H, _s()), "rmsnorm_bwd")
+        global LAUNCHES
+        LAUNCHES += 1  # the column sum
+        return dx, dw, None
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
@@ -95,19 +106,20 @@ class _Rope(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, table, heads):
-        assert qkv.dtype == torch.bfloat16
-        out = qkv.clone(memory_format=torch.contiguous_format)
+        qkv = _bf16c(qkv)
+        out = torch.empty_like(qkv)
         T, total, D = out.shape
         ctx.table, ctx.heads = table, heads
-        _ck(_lib_ops().b200ops_rope(out.data_ptr(), table.data_ptr(), T, heads, D, total * D, table.shape[0], 1.0, _s()), "rope_fwd")
+        _ck(_lib_ops().b200ops_rope_oop(qkv.data_ptr(), out.data_ptr(), table.data_ptr(), T, heads, total, D, table.shape[0], 1.0, _s()), "rope_fwd")
         return out
 
     @staticmethod
     def backward(ctx, g):
-        g = g.clone(memory_format=torch.contiguous_format)  # the inverse rotation runs in place on the copy
+        g = _bf16c(g)  # the gradient is the inverse rotation
+        out = torch.empty_like(g)
         T, total, D = g.shape
-        _ck(_lib_ops().b200ops_rope(g.data_ptr(), ctx.table.data_ptr(), T, ctx.heads, D, total * D, ctx.table.shape[0], -1.0, _s()), "rope_bwd")
-        return g, None, None
+        _ck(_lib_ops().b200ops_rope_oop(g.data_ptr(), out.data_ptr(), ctx.table.data_ptr(), T, ctx.heads, total, D, ctx.table.shape[0], -1.0, _s()), "rope_bwd")
+        return out, None, None
 
 
 def rope_(qkv: torch.Tensor, table: torch.Tensor, heads: int) -> torch.Tensor:
@@ -156,7 +168,12 @@ def cross_entropy_inplace(logits: torch.Tensor, targets: torch.Tensor, grad_scal
 def adamw_(master, m, v, grad, param, lr, betas, eps, weight_decay, step, grad_scale=1.0) -> None:
     n = master.numel()
     assert m.numel() == n and v.numel() == n and grad.numel() == n and param.numel() == n
-    assert master.dtype == torch.float32 and grad.dtype == torch.float32 and param.dtype == torch.bfloat16
+    assert master.dtype == torch.float32 and param.dtype == torch.bfloat16
+    if grad.dtype == torch.bfloat16:  # straight from the backward pass: no fp32 copy of the gradient
+        _ck(_lib_ops().b200ops_adamw_bf16g(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(), param.data_ptr(), n, lr, betas[0], betas[1],
+                                           eps, weight_decay, step, grad_scale, _s()), "adamw")
+        return
+    assert grad.dtype == torch.float32
     _ck(_lib_ops().b200ops_adamw(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(), param.data_ptr(), n, lr, betas[0], betas[1], eps,
                                  weight_decay, step, grad_scale, _s()), "adamw")
 

@@ -57,9 +57,18 @@ class FlatUnit:
             o += (s.numel + ALIGN - 1) // ALIGN * ALIGN
         self.offsets = offs
         self.numel = o
+        # Ranges of the flat buffer no parameter covers (alignment gaps and the tail padding).
+        self.gaps: List[Tuple[int, int]] = []
+        for sp in self.specs:
+            end = offs[sp.name] + sp.numel
+            nxt = (end + ALIGN - 1) // ALIGN * ALIGN
+            if nxt > end:
+                self.gaps.append((end, nxt))
         per = (o + world - 1) // world
         self.shard_numel = (per + ALIGN - 1) // ALIGN * ALIGN
         self.padded = self.shard_numel * world
+        if self.padded > o:
+            self.gaps.append((o, self.padded))
         # Same full-precision initial values on every rank, then keep only this rank's slice.
         g = torch.Generator(device=device).manual_seed(seed)
         lo, hi = rank * self.shard_numel, (rank + 1) * self.shard_numel
@@ -149,7 +158,11 @@ class FSDPEngine:
 
     # ---- gradients --------------------------------------------------------------------------------
     def alloc_grad(self, unit: FlatUnit) -> None:
-        unit.full_grad = torch.zeros(unit.padded, dtype=torch.bfloat16, device=unit.device)
+        """The flat gradient buffer of ``unit``. Every parameter's gradient is written (not
+        accumulated) into its view by the backward pass, so only the gaps need zeroing."""
+        unit.full_grad = torch.empty(unit.padded, dtype=torch.bfloat16, device=unit.device)
+        for a, b in unit.gaps:
+            unit.full_grad[a:b].zero_()
 
     def reduce_and_step(self, unit: FlatUnit, fp32_full_grad: Optional[torch.Tensor] = None) -> None:
         """Reduce-scatter ``unit``'s gradient (mean over ranks) into fp32 and apply AdamW to the
@@ -160,14 +173,16 @@ class FSDPEngine:
         self.comm_stream.wait_event(ev)
         src = fp32_full_grad if fp32_full_grad is not None else unit.full_grad
         with torch.cuda.stream(self.comm_stream):
-            gshard = torch.empty(unit.shard_numel, dtype=torch.float32, device=unit.device)
+            gshard = None
+            if self.world > 1:
+                gshard = torch.empty(unit.shard_numel, dtype=torch.float32, device=unit.device)
             if fp32_full_grad is not None:
                 if self.world == 1:
                     gshard = fp32_full_grad[:unit.shard_numel]
                 else:
                     self.comm.reduce_scatter(fp32_full_grad, gshard, op="avg", stream=self.comm_stream)
             elif self.world == 1:
-                ops.cast_scale_(unit.full_grad[:unit.shard_numel], gshard, 1.0)
+                gshard = unit.full_grad[:unit.shard_numel]  # AdamW reads the bf16 gradient directly
             elif self.fused_rs:
                 from ..ops import comm_ops
 

@@ -1,0 +1,49 @@
+"""Multi-GPU tests of the fused compute+collective kernels, the device-initiated (shmem) layer and
+the FSDP engine. Each test launches child ranks, one per GPU; a worker exits non-zero on any
+mismatch against its unfused / single-rank oracle."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from conftest import gpu_count
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _launch(nproc: int, port: int, worker: str, *args: str, timeout: int = 900) -> None:
+    if gpu_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    env = dict(os.environ)
+    env.setdefault("B200COLL_WAIT_TIMEOUT_MS", "5000")
+    env.setdefault("B200COLL_BOOTSTRAP_TIMEOUT_MS", "60000")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "workers" / worker), *args]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    sys.stdout.write(p.stdout[-4000:])
+    sys.stderr.write(p.stderr[-4000:])
+    assert p.returncode == 0
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_tp_fused_mlp_matches_unfused(nproc):
+    _launch(nproc, 29810 + nproc, "tp_worker.py")
+    _launch(nproc, 29820 + nproc, "tp_worker.py", "--rows", "512", "--hidden", "2048", "--ffn", "1024")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_ep_dispatch_experts_combine(nproc):
+    _launch(nproc, 29830 + nproc, "ep_worker.py")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_shmem_put_get_signal_atomics(nproc):
+    _launch(nproc, 29840 + nproc, "shmem_worker.py")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_fsdp_matches_single_rank(nproc):
+    _launch(nproc, 29850 + nproc, "fsdp_worker.py")
