@@ -20,7 +20,7 @@ struct DevStatus {
   uint32_t seen;      // flag value last read
   uint64_t opSeq;     // sequence number of the collective on this communicator
 };
-enum WaitKind : uint32_t { WAIT_BARRIER = 1, WAIT_LL = 2, WAIT_P2P_DATA = 3, WAIT_P2P_CREDIT = 4, WAIT_SHMEM = 5, WAIT_FUSED = 6 };
+enum WaitKind : uint32_t { WAIT_BARRIER = 1, WAIT_LL = 2, WAIT_P2P_DATA = 3, WAIT_P2P_CREDIT = 4, WAIT_SHMEM = 5, WAIT_FUSED = 6, WAIT_BULK = 7 };
 
 // One record per traced collective, filled by the kernel with %globaltimer stamps.
 struct TraceStamp {

@@ -179,21 +179,25 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   args->chunkBytes = 0;
   if (algo != ALGO_LL && !direct) {
     const bool reduceKind = r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE;
-    size_t cap = r.kind == COLL_REDUCESCATTER ? ((c->dev.stageBytes / n) & ~(size_t)15) : c->dev.stageBytes;
-    if (reduceKind) {
-      // Pipeline chunk: an eighth of what moves through staging, between 8 MiB (below that the
-      // per-chunk barrier costs more than the overlap wins) and one staging half.
+    const size_t fullCap = r.kind == COLL_REDUCESCATTER ? ((c->dev.stageBytes / n) & ~(size_t)15) : c->dev.stageBytes;
+    size_t capMax = fullCap;
+    if (reduceKind && fl.pipeChunkBytes != 0) {
+      // Pipeline chunk of the reducing kernels: an eighth of what moves through staging, between
+      // 8 MiB (below that the per-chunk barrier costs more than the overlap wins) and one half.
       const size_t staged = r.kind == COLL_REDUCESCATTER ? bytes * n : bytes;
-      if (staged >= (size_t)16 << 20) {
+      if (staged >= (size_t)16 << 20 || fl.pipeChunkBytes > 0) {
         size_t chunk = std::max<size_t>((size_t)8 << 20, ((staged / 8) + ((1u << 20) - 1)) & ~(size_t)((1u << 20) - 1));
-        chunk = std::min(chunk, c->dev.stageBytes);
+        if (fl.pipeChunkBytes > 0) chunk = ((size_t)fl.pipeChunkBytes + 4095) & ~(size_t)4095;
         const size_t perCall = r.kind == COLL_REDUCESCATTER ? (chunk / n) & ~(size_t)15 : chunk;
-        if (perCall >= 16 && perCall < cap) {
-          args->chunkBytes = perCall;
-          cap = perCall;
-        }
+        if (perCall >= 16 && perCall < capMax) capMax = perCall;
       }
     }
+    // Equal chunks: the kernels place data in staging by the chunk capacity alone, so a short
+    // last chunk would leave most lanes idle.
+    const size_t k = (bytes + capMax - 1) / capMax;
+    size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;  // k == 1: the message itself, so every lane gets a share
+    if (cap > capMax) cap = capMax;
+    if (cap < fullCap) args->chunkBytes = cap;
     chunks = (bytes + cap - 1) / cap;
   }
   if (!ctas) {

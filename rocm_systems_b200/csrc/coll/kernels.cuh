@@ -198,29 +198,57 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
 
+  // Shared-memory ring of the peer-load path (kernels without in-switch reduction only).
+  extern __shared__ __align__(128) unsigned char bulkSmem[];
+  uint64_t* bulkFull = reinterpret_cast<uint64_t*>(bulkSmem);
+  char* bulkStage = reinterpret_cast<char*>(bulkSmem) + 128;
+  uint32_t tileSeq = 0;     // tiles consumed so far by this CTA (same value in every thread)
+  uint32_t bulkIssued = 0;  // tiles issued so far (meaningful in the issuing thread)
+  if constexpr (!NVLS) {
+    if (tid == 0) {
+      for (int i = 0; i < kBulkStages; i++) cmbarInit(&bulkFull[i], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+  }
+
   // Geometry of the chunk that starts at byte `off` (per slice for ReduceScatter).
+  // Geometry. Where a piece of a chunk lives in staging, and which lane (CTA index) handles it,
+  // depends only on the chunk capacity `cap`, never on how full a chunk is: a lane's ranges of a
+  // short last chunk then lie inside its ranges of a full one, so what one lane writes into a
+  // staging half can never overlap what another lane (which it does not synchronise with) still
+  // reads there from an earlier chunk.
   struct Geo {
-    size_t off, cb, su, stageBase;
+    size_t off, cb, stageBase;
   };
+  const size_t capUnits = (cap + 15) >> 4;
+  const size_t su = isRS ? capUnits : (capUnits + n - 1) / n;  // 16-byte units per slice of a full chunk
+  const size_t perLane = (su + B - 1) / B;                      // units of a slice per lane
   auto geo = [&](size_t off, int half) -> Geo {
     Geo g;
     g.off = off;
     g.cb = (total - off < cap) ? total - off : cap;
-    const size_t U = (g.cb + 15) >> 4;
-    g.su = isRS ? U : (U + n - 1) / n;  // 16-byte units per slice
     g.stageBase = c.stageOff + (size_t)half * c.stageBytes;
     return g;
   };
   auto sliceBytes = [&](const Geo& g, int s) -> size_t {
     if (isRS) return g.cb;
-    size_t lo = (size_t)s * g.su * 16;
+    size_t lo = (size_t)s * su * 16;
     if (lo >= g.cb) return 0;
     size_t len = g.cb - lo;
-    return len < g.su * 16 ? len : g.su * 16;
+    return len < su * 16 ? len : su * 16;
   };
-  auto sliceStage = [&](const Geo& g, int s) -> size_t { return isRS ? (size_t)s * cap : (size_t)s * g.su * 16; };
+  // This lane's units [lo, hi) of a slice that holds `sb` bytes.
+  auto laneRange = [&](size_t sb, size_t& lo, size_t& hi) {
+    const size_t units = (sb + 15) >> 4;
+    lo = (size_t)b * perLane;
+    if (lo > units) lo = units;
+    hi = lo + perLane;
+    if (hi > units) hi = units;
+  };
+  auto sliceStage = [&](const Geo&, int s) -> size_t { return isRS ? (size_t)s * cap : (size_t)s * su * 16; };
   auto sliceSrc = [&](const Geo& g, int s) -> const char* {
-    return isRS ? send + ((size_t)s * a.count * ES + g.off) : send + g.off + (size_t)s * g.su * 16;
+    return isRS ? send + ((size_t)s * a.count * ES + g.off) : send + g.off + (size_t)s * su * 16;
   };
 
   // user send -> this rank's staging, by threads t of nt
@@ -229,7 +257,7 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
       const int s = (rank + i) % n;
       const size_t sb = sliceBytes(g, s);
       size_t lo, hi;
-      splitUnits((sb + 15) >> 4, B, b, lo, hi);
+      laneRange(sb, lo, hi);
       if (lo < hi) {
         size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
         char* dst = c.ws[rank] + g.stageBase + sliceStage(g, s) + (lo << 4);
@@ -244,10 +272,10 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
       const int s = (rank + i) % n;
       const size_t sb = sliceBytes(g, s);
       size_t lo, hi;
-      splitUnits((sb + 15) >> 4, B, b, lo, hi);
+      laneRange(sb, lo, hi);
       if (lo < hi) {
         size_t bytes = ((hi << 4) < sb ? (hi << 4) : sb) - (lo << 4);
-        groupCopy(recv + g.off + (size_t)s * g.su * 16 + (lo << 4), c.ws[rank] + g.stageBase + sliceStage(g, s) + (lo << 4), bytes, t, ntg);
+        groupCopy(recv + g.off + (size_t)s * su * 16 + (lo << 4), c.ws[rank] + g.stageBase + sliceStage(g, s) + (lo << 4), bytes, t, ntg);
       }
     }
   };
@@ -261,9 +289,9 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
       const int s = pullAll ? si : rank;
       const size_t sb = sliceBytes(g, s);
       size_t lo, hi;
-      splitUnits((sb + 15) >> 4, B, b, lo, hi);
+      laneRange(sb, lo, hi);
       // Byte offset of the slice inside the message (direct windows and user recv).
-      const size_t msgOff = isRS ? off : off + (size_t)s * g.su * 16;
+      const size_t msgOff = isRS ? off : off + (size_t)s * su * 16;
       const size_t stOff = g.stageBase + sliceStage(g, s);
       const bool recvAligned = (((uintptr_t)(recv + (isRS ? off : msgOff))) & 15) == 0;
       // Sources and destinations of this slice.
@@ -289,13 +317,11 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
           else st16(pDst(a.root) + (u << 4), out);
         }
       };
-      // `UN` independent 16-byte units per thread are loaded before any is consumed, so enough
-      // NVLink requests are in flight to cover the link latency.
-      auto body = [&](auto unTag, auto maxrTag, size_t u0) {
-        constexpr int UN = decltype(unTag)::value;
-        constexpr int MAXR = decltype(maxrTag)::value;  // upper bound on the rank count
-        uint4 out[UN];
-        if constexpr (NVLS) {
+      if constexpr (NVLS) {
+        // One switch-side reduction per 16-byte unit; eight are in flight per thread.
+        auto body = [&](auto unTag, size_t u0) {
+          constexpr int UN = decltype(unTag)::value;
+          uint4 out[UN];
 #pragma unroll
           for (int j = 0; j < UN; j++) out[j] = McReduce<T>::ld(mcSrc + ((u0 + (size_t)j * ntg) << 4));
           if (a.scaleMode == SCALE_POST_DIV_N) {
@@ -308,55 +334,62 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
               out[j] = P::down(acc);
             }
           }
-        } else {
-          uint4 v[UN][MAXR];
 #pragma unroll
-          for (int j = 0; j < UN; j++) {
-#pragma unroll
-            for (int p = 0; p < MAXR; p++)
-              if (p < n) v[j][p] = ldStream16(pSrc(p) + ((u0 + (size_t)j * ntg) << 4));
-          }
-#pragma unroll
-          for (int j = 0; j < UN; j++) {
-            Acc acc[P::N];
-#pragma unroll
-            for (int p = 0; p < MAXR; p++) {
-              if (p < n) {
-                Acc x[P::N];
-                P::up(v[j][p], x);
-#pragma unroll
-                for (int k = 0; k < P::N; k++) acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
-              }
-            }
-            if (a.scaleMode == SCALE_POST_DIV_N) {
-#pragma unroll
-              for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
-            }
-            out[j] = P::down(acc);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < UN; j++) deliver(u0 + (size_t)j * ntg, out[j]);
-      };
-      size_t u = lo + t;
-      using I1 = std::integral_constant<int, 1>;
-      using I2 = std::integral_constant<int, 2>;
-      using I4 = std::integral_constant<int, 4>;
-      using I8 = std::integral_constant<int, 8>;
-      if constexpr (NVLS) {
-        for (; u + (size_t)7 * ntg < hi; u += (size_t)8 * ntg) body(I8{}, I1{}, u);
-        for (; u < hi; u += ntg) body(I1{}, I1{}, u);
+          for (int j = 0; j < UN; j++) deliver(u0 + (size_t)j * ntg, out[j]);
+        };
+        size_t u = lo + t;
+        for (; u + (size_t)7 * ntg < hi; u += (size_t)8 * ntg) body(std::integral_constant<int, 8>{}, u);
+        for (; u < hi; u += ntg) body(std::integral_constant<int, 1>{}, u);
       } else {
-        // 64 data registers per thread whatever the rank count: 1 KiB in flight per thread.
-        if (n <= 2) {
-          for (; u + (size_t)7 * ntg < hi; u += (size_t)8 * ntg) body(I8{}, I2{}, u);
-          for (; u < hi; u += ntg) body(I1{}, I2{}, u);
-        } else if (n <= 4) {
-          for (; u + (size_t)3 * ntg < hi; u += (size_t)4 * ntg) body(I4{}, I4{}, u);
-          for (; u < hi; u += ntg) body(I1{}, I4{}, u);
-        } else {
-          for (; u + (size_t)ntg < hi; u += (size_t)2 * ntg) body(I2{}, I8{}, u);
-          for (; u < hi; u += ntg) body(I1{}, I8{}, u);
+        // Peer loads as bulk asynchronous copies: thread 0 of the group keeps kBulkStages - 1
+        // tiles (every rank's copy of the same range) in flight into a shared-memory ring; all
+        // threads reduce a landed tile from shared memory and send the result on its way.
+        const uint32_t tileBytes = kBulkStageBytes / (n <= 2 ? 2 : (n <= 4 ? 4 : 8));
+        const size_t rangeBytes = (hi - lo) << 4;
+        const uint32_t tiles = (uint32_t)((rangeBytes + tileBytes - 1) / tileBytes);
+        auto issue = [&](uint32_t i) {
+          const uint32_t seq = tileSeq + i, st = seq % kBulkStages;
+          const size_t left = rangeBytes - (size_t)i * tileBytes;
+          const uint32_t tb = left < tileBytes ? (uint32_t)left : tileBytes;
+          // The stage was last read, and the sources last written (by copy-in here or on a peer,
+          // ordered before this point by the inter-rank barrier), through the generic proxy.
+          asm volatile("fence.proxy.async;" ::: "memory");
+          cmbarExpectTx(&bulkFull[st], tb * (uint32_t)n);
+          for (int p = 0; p < n; p++)
+            bulkLoad(bulkStage + (size_t)st * kBulkStageBytes + (size_t)p * tileBytes, pSrc(p) + (lo << 4) + (size_t)i * tileBytes, tb, &bulkFull[st]);
+          bulkIssued = seq + 1;
+        };
+        if (t == 0)
+          for (uint32_t i = 0; i < tiles && i < (uint32_t)kBulkStages - 1; i++) issue(i);
+        for (uint32_t i = 0; i < tiles; i++) {
+          const uint32_t seq = tileSeq + i, st = seq % kBulkStages;
+          const bool ok = cmbarWaitBounded(c, &bulkFull[st], (seq / kBulkStages) & 1, (uint32_t)rank);
+          // The stage read in the previous iteration is free: everyone passed the barrier below.
+          if (t == 0 && ok && i + kBulkStages - 1 < tiles) issue(i + kBulkStages - 1);
+          if (ok) {
+            const size_t left = rangeBytes - (size_t)i * tileBytes;
+            const uint32_t units = (uint32_t)((left < tileBytes ? left : tileBytes) >> 4);
+            const char* stage = bulkStage + (size_t)st * kBulkStageBytes;
+            const size_t ubase = lo + (size_t)i * (tileBytes >> 4);
+            for (uint32_t uu = t; uu < units; uu += ntg) {
+              Acc acc[P::N];
+#pragma unroll
+              for (int p = 0; p < kMaxRanks; p++) {
+                if (p < n) {
+                  Acc x[P::N];
+                  P::up(*reinterpret_cast<const uint4*>(stage + (size_t)p * tileBytes + ((size_t)uu << 4)), x);
+#pragma unroll
+                  for (int k = 0; k < P::N; k++) acc[k] = (p == 0) ? x[k] : Op::apply(acc[k], x[k]);
+                }
+              }
+              if (a.scaleMode == SCALE_POST_DIV_N) {
+#pragma unroll
+                for (int k = 0; k < P::N; k++) acc[k] = postDiv<T>(acc[k], n);
+              }
+              deliver(ubase + uu, P::down(acc));
+            }
+          }
+          asm volatile("bar.sync 2, %0;" ::"r"(ntg) : "memory");
         }
       }
     }
@@ -365,6 +398,14 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
   // Zero-copy windows (direct) are one chunk with no copies: a barrier before (inputs complete
   // everywhere) and after (nobody leaves while a peer still reads its buffer or has stores to it
   // in flight).
+  // Tiles the peer-load path consumes for this CTA's share of slice `rank` of a chunk.
+  auto tilesOf = [&](const Geo& g) -> uint32_t {
+    const size_t sb = sliceBytes(g, rank);
+    size_t lo, hi;
+    laneRange(sb, lo, hi);
+    const uint32_t tileBytes = kBulkStageBytes / (n <= 2 ? 2 : (n <= 4 ? 4 : 8));
+    return (uint32_t)((((hi - lo) << 4) + tileBytes - 1) / tileBytes);
+  };
   const bool hasOut = !a.direct && (isAR || (isRed && !NVLS && rank == a.root));  // results come back through staging
   const bool barAfter = a.direct || isAR || (isRed && !NVLS);                     // every chunk's reduce ends with a barrier
   int half = a.direct ? 0 : a.stageHalf;
@@ -387,8 +428,18 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
       }
       if (more) copyIn(geo(off + cap, half ^ 1), tid - h, nt - h);
     }
+    if constexpr (!NVLS) tileSeq += tilesOf(g);
     if (barAfter || more) ctaBarrier(c, epoch);
     if (!more && hasOut) copyOut(g, tid, nt);
+  }
+  if constexpr (!NVLS) {
+    // After a wait that was given up, copies may still be on their way into this CTA's shared
+    // memory: give each issued tile one more bounded wait before the CTA ends.
+    if (tid == 0 && *(volatile uint32_t*)&c.local->failed) {
+      for (uint32_t seq = bulkIssued > (uint32_t)kBulkStages ? bulkIssued - kBulkStages : 0; seq < bulkIssued; seq++)
+        for (uint32_t spin = 0; spin < (1u << 16) && !cmbarTryWait(&bulkFull[seq % kBulkStages], (seq / kBulkStages) & 1); spin++) {
+        }
+    }
   }
   if (tid == 0) c.local->barEpoch[b] = epoch;
   stampEnd(c);
@@ -434,17 +485,22 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
   const int n = c.nranks, rank = c.rank, B = gridDim.x, b = blockIdx.x;
   uint32_t epoch = c.local->barEpoch[b];
   const size_t total = a.count * (size_t)elemSize;  // AllGather: one rank's contribution; Broadcast: the message
-  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : c.stageBytes;
+  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : ((a.chunkBytes && a.chunkBytes < c.stageBytes) ? a.chunkBytes : c.stageBytes);
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   int half = a.stageHalf;
   const bool isAG = a.kind == COLL_ALLGATHER;
 
   // This CTA's part of the chunk at `off`: byte offset inside the chunk and length.
+  // The lane's range is fixed by the chunk capacity, not by how full the chunk is (see the note
+  // on geometry in kStagedReduce): lanes never touch one another's part of a staging half.
+  const size_t perLane = (((cap + 15) >> 4) + B - 1) / B;
   auto part = [&](size_t off, size_t& bo, size_t& bytes) {
     const size_t cb = (total - off < cap) ? total - off : cap;
-    size_t lo, hi;
-    splitUnits((cb + 15) >> 4, B, b, lo, hi);
+    const size_t units = (cb + 15) >> 4;
+    size_t lo = (size_t)b * perLane, hi;
+    if (lo > units) lo = units;
+    hi = lo + perLane < units ? lo + perLane : units;
     bytes = lo < hi ? (((hi << 4) < cb ? (hi << 4) : cb) - (lo << 4)) : 0;
     bo = lo << 4;
   };
@@ -485,12 +541,9 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
   }
 
   for (size_t off = 0; off < total; off += cap, half ^= 1) {
-    const size_t cb = (total - off < cap) ? total - off : cap;
     const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
-    size_t lo, hi;
-    splitUnits((cb + 15) >> 4, B, b, lo, hi);
-    const size_t bytes = lo < hi ? (((hi << 4) < cb ? (hi << 4) : cb) - (lo << 4)) : 0;
-    const size_t bo = lo << 4;  // byte offset of this CTA's part inside the chunk
+    size_t bo, bytes;  // byte offset of this CTA's part inside the chunk, and its length
+    part(off, bo, bytes);
 
     if (isAG) {  // direct windows: pull straight from the peers' send buffers
       ctaBarrier(c, epoch);

@@ -111,6 +111,51 @@ __device__ __forceinline__ bool waitGe64(const DevComm& c, const unsigned long l
   }
 }
 
+// ---- bulk asynchronous copies into shared memory --------------------------------------------
+// cp.async.bulk (the untiled TMA copy, never with cluster multicast) brings a contiguous range of
+// global memory, this GPU's or a peer's, into shared memory and counts the bytes on an mbarrier.
+// What is in flight is bounded by shared memory instead of by registers, which is what lets one
+// CTA per SM keep an NVLink direction busy. Both addresses and the size are multiples of 16.
+__device__ __forceinline__ uint32_t smemU32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cmbarInit(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemU32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void cmbarExpectTx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smemU32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool cmbarTryWait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smemU32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulkLoad(void* smemDst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smemU32(smemDst)), "l"(gsrc),
+               "r"(bytes), "r"(smemU32(bar))
+               : "memory");
+}
+// Wait for a phase of `bar` for at most c.timeoutNs; a wait that is given up is recorded like any
+// other (the kernel keeps going on valid addresses and ends normally).
+__device__ __forceinline__ bool cmbarWaitBounded(const DevComm& c, uint64_t* bar, uint32_t parity, uint32_t peer) {
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (cmbarTryWait(bar, parity)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*(volatile uint32_t*)&c.local->failed) return false;
+      if (*c.abortFlag) { recordFailure(c, 2, WAIT_BULK, peer, parity, 0); return false; }
+      unsigned long long now = globalTimerNs();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > c.timeoutNs) { recordFailure(c, 1, WAIT_BULK, peer, parity, 0); return false; }
+    }
+  }
+}
+
 // ---- barrier between CTA `blockIdx.x` of every rank -----------------------------------------
 // Everything this CTA wrote before the call is visible to the matching CTA of every rank after
 // it. `epoch` is the CTA's running barrier count (loaded from LocalState at kernel entry).

@@ -29,11 +29,20 @@ cudaError_t B200_CAT(launchStaged_, B200_TN)(int op, bool nvls, int grid, cudaSt
     return cudaErrorInvalidValue;
 #endif
   }
+  // The peer-load kernels stage tiles in a shared-memory ring larger than the default limit.
+  static const cudaError_t attr = [] {
+    cudaError_t e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpSum, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpProd, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpMax, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpMin, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
+    return e;
+  }();
+  if (attr != cudaSuccess) return attr;
   switch (op) {
-    case ncclSum: kStagedReduce<B200_T, OpSum, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
-    case ncclProd: kStagedReduce<B200_T, OpProd, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
-    case ncclMax: kStagedReduce<B200_T, OpMax, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
-    case ncclMin: kStagedReduce<B200_T, OpMin, false><<<grid, kReduceThreads, 0, s>>>(c, a); break;
+    case ncclSum: kStagedReduce<B200_T, OpSum, false><<<grid, kReduceThreads, kBulkSmemBytes, s>>>(c, a); break;
+    case ncclProd: kStagedReduce<B200_T, OpProd, false><<<grid, kReduceThreads, kBulkSmemBytes, s>>>(c, a); break;
+    case ncclMax: kStagedReduce<B200_T, OpMax, false><<<grid, kReduceThreads, kBulkSmemBytes, s>>>(c, a); break;
+    case ncclMin: kStagedReduce<B200_T, OpMin, false><<<grid, kReduceThreads, kBulkSmemBytes, s>>>(c, a); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();

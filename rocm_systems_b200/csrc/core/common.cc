@@ -86,6 +86,7 @@ static void load(Flags& f) {
   f.llMaxBytes = parseSize(envOf("LL_THRESHOLD", false), f.llMaxBytes);
   f.p2pChunkBytes = parseSize(envOf("P2P_CHUNK", false), f.p2pChunkBytes);
   f.p2pCtasPerPeer = parseInt(envOf("P2P_CTAS", false), f.p2pCtasPerPeer);
+  if (const char* v = envOf("PIPELINE_CHUNK", false)) f.pipeChunkBytes = (long long)parseSize(v, 0);
   f.waitTimeoutMs = parseInt(envOf("WAIT_TIMEOUT_MS", false), f.waitTimeoutMs);
   f.bootTimeoutMs = parseInt(envOf("BOOTSTRAP_TIMEOUT_MS", false), f.bootTimeoutMs);
   if (const char* v = envOf("COMM_ID")) f.commId = v;

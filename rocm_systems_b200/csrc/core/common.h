@@ -16,6 +16,9 @@ constexpr int kMaxRanks = 8;     // one NVSwitch domain
 constexpr int kMaxCtas = 128;    // flag slots per communicator; also the CTA ceiling of a kernel
 constexpr int kCollThreads = 512;
 constexpr int kMaxP2pSubs = 16;     // send/recv sub-channels (CTAs) per peer, at most
+constexpr int kBulkStages = 4;            // shared-memory ring of the peer-load reduce
+constexpr int kBulkStageBytes = 32 << 10;  // per stage: every rank's tile of the same range
+constexpr int kBulkSmemBytes = 128 + kBulkStages * kBulkStageBytes;
 constexpr int kReduceThreads = 256;  // reducing kernels: fewer threads, more registers for loads in flight
 
 // ---- logging ------------------------------------------------------------------------------
@@ -90,6 +93,7 @@ struct Flags {
   std::string ifaddr = "127.0.0.1";  // SOCKET_ADDR: address the root listens on
   std::string tuningFile;        // TUNING_FILE: JSON size->algorithm table
   std::string toolLibs;          // TOOL_LIBRARIES: ':'-separated tools given the dispatch table
+  long long pipeChunkBytes = -1;  // PIPELINE_CHUNK: staged-reduce pipeline chunk; -1 picks by size, 0 disables
   int traceEnable = 0;           // TRACE: record per-collective device timestamps
   std::string traceFile;         // TRACE_FILE: CSV written at communicator destroy
   std::string failKey;           // FAIL_KEY: host-side fault-injection points (tests)
