@@ -518,19 +518,35 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
       part(off, bo, bytes);
       const bool more = off + cap < total;
       const bool selfCopy = recv + (size_t)rank * total != send;
-      const bool split = more || selfCopy;
+      // The local copies are 2/(n-1) of the bytes the pulls move: worth half the CTA's threads
+      // only between few ranks, and only when there is a next chunk to stage meanwhile.
+      const bool split = more && n <= 4;
       const int h = split ? nt >> 1 : nt;
+      const int warps = h >> 5, peers = n - 1;
       if (tid < h) {
-        for (int i = 1; i < n; i++) {
-          const int p = (rank + i) % n;
-          groupCopy(recv + (size_t)p * total + off + bo, c.ws[p] + stageBase + bo, bytes, tid, h);
+        if (bytes <= (size_t)(64u << 10) && warps >= peers && peers > 1) {
+          // Short parts: pulling peer after peer would pay one NVLink round trip per peer in
+          // sequence, so the warps share out the peers and all pulls are in flight together.
+          const int per = warps / peers;              // warps per peer
+          const int w = tid >> 5;
+          if (w < per * peers) {
+            const int p = (rank + 1 + w / per) % n;
+            groupCopy(recv + (size_t)p * total + off + bo, c.ws[p] + stageBase + bo, bytes, (w % per) * 32 + (tid & 31), per * 32);
+          }
+        } else {
+          for (int i = 1; i < n; i++) {
+            const int p = (rank + i) % n;
+            groupCopy(recv + (size_t)p * total + off + bo, c.ws[p] + stageBase + bo, bytes, tid, h);
+          }
         }
-      } else {
-        if (selfCopy) groupCopy(recv + (size_t)rank * total + off + bo, send + off + bo, bytes, tid - h, nt - h);
+      }
+      if (tid >= h || !split) {
+        const int t2 = split ? tid - h : tid, n2 = split ? nt - h : nt;
+        if (selfCopy) groupCopy(recv + (size_t)rank * total + off + bo, send + off + bo, bytes, t2, n2);
         if (more) {
           size_t nbo, nbytes;
           part(off + cap, nbo, nbytes);
-          groupCopy(c.ws[rank] + c.stageOff + (size_t)(half ^ 1) * c.stageBytes + nbo, send + off + cap + nbo, nbytes, tid - h, nt - h);
+          groupCopy(c.ws[rank] + c.stageOff + (size_t)(half ^ 1) * c.stageBytes + nbo, send + off + cap + nbo, nbytes, t2, n2);
         }
       }
       if (more) ctaBarrier(c, epoch);
@@ -547,15 +563,20 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
 
     if (isAG) {  // direct windows: pull straight from the peers' send buffers
       ctaBarrier(c, epoch);
-      for (int i = 0; i < n; i++) {
-        const int p = (rank + i) % n;
-        char* dst = recv + (size_t)p * total + off + bo;
-        if (p == rank) {
-          if (dst != send + off + bo) ctaCopy(dst, send + off + bo, bytes);
-        } else {
-          ctaCopy(dst, a.sendPeer[p] + off + bo, bytes);
+      const int tid = threadIdx.x, warps = blockDim.x >> 5, peers = n - 1;
+      if (bytes <= (size_t)(64u << 10) && warps >= peers && peers > 1) {
+        const int per = warps / peers, w = tid >> 5;  // short parts: all peers in flight at once
+        if (w < per * peers) {
+          const int p = (rank + 1 + w / per) % n;
+          groupCopy(recv + (size_t)p * total + off + bo, a.sendPeer[p] + off + bo, bytes, (w % per) * 32 + (tid & 31), per * 32);
+        }
+      } else {
+        for (int i = 1; i < n; i++) {
+          const int p = (rank + i) % n;
+          ctaCopy(recv + (size_t)p * total + off + bo, a.sendPeer[p] + off + bo, bytes);
         }
       }
+      if (recv + (size_t)rank * total != send) ctaCopy(recv + (size_t)rank * total + off + bo, send + off + bo, bytes);
       ctaBarrier(c, epoch);
     } else {  // Broadcast
       if (a.direct) {
