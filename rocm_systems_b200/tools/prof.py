@@ -14,6 +14,8 @@ What is traced, and by which part of the package:
         through ``CUDA_INJECTION64_PATH``;
   --coll-trace    the communication library's own tracer (host and device times per collective);
   --marker-trace  ``b200tx`` ranges the program pushes (rocm_systems_b200.utils.markers);
+  --sys-sample N  a background sampler in the launcher (``tools/sysmon.py``): GPU clocks / power / temperature /
+                  utilisation / memory, host CPU and memory, the command's resident set, every N ms;
   --sys-trace     all of the above.
 """
 from __future__ import annotations
@@ -63,7 +65,7 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
 def collect(prefix: str) -> List[str]:
     """Every trace file the children left behind."""
     files = sorted(set(glob.glob(prefix + ".*_kernel_trace.csv") + glob.glob(prefix + ".*_memory_copy_trace.csv") +
-                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv")))
+                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv") + glob.glob(prefix + ".sysmon.csv")))
     return files
 
 
@@ -78,6 +80,8 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--coll-trace", action="store_true", help="collectives of the communication library")
     g.add_argument("--marker-trace", action="store_true", help="b200tx ranges")
     g.add_argument("--sys-trace", action="store_true", help="everything")
+    g.add_argument("--sys-sample", type=int, default=0, metavar="PERIOD_MS",
+                   help="sample GPU readings (NVML), host CPU / memory and the command's resident set in the background")
     g = ap.add_argument_group("filtering")
     g.add_argument("--kernel-include-regex", default="")
     g.add_argument("--max-records", type=int, default=0, help="per kind and process")
@@ -107,7 +111,15 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     outdir = Path(a.output_directory)
     outdir.mkdir(parents=True, exist_ok=True)
     prefix = str(outdir / a.output_file)
-    rc = subprocess.call(cmd, env=build_env(a, prefix))
+    if a.sys_sample > 0:
+        from .sysmon import SystemSampler
+
+        child = subprocess.Popen(cmd, env=build_env(a, prefix))
+        with SystemSampler(period_ms=a.sys_sample, pids=[child.pid]) as sampler:
+            rc = child.wait()
+        sampler.write_csv(prefix + ".sysmon.csv")
+    else:
+        rc = subprocess.call(cmd, env=build_env(a, prefix))
     files = collect(prefix)
     if not files:
         print("prof: the command left no trace files (did it use the GPU / the communication library?)", file=sys.stderr)

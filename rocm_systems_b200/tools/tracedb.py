@@ -13,6 +13,7 @@ rocprofiler-sdk/source/share/rocprofiler-sdk-rocpd/*.sql) with a schema of its o
     region(process_id, tid, category_id, name_id, correlation_id, start_ns, end_ns)      -- API calls, markers
     collective(process_id, rank, name_id, correlation_id, count, dtype, bytes, algo, ctas,
                host_start_ns, host_end_ns, device_start_ns, device_end_ns)
+    counter_sample(name_id, device, ts_ns, value)                                       -- system sampler
 
 and the views ``kernels``, ``regions``, ``collectives``, ``top_kernels``, ``top_collectives``, ``busy``.
 
@@ -48,6 +49,7 @@ create table if not exists region(id integer primary key, process_id integer, ti
 create table if not exists collective(id integer primary key, process_id integer, rank integer, name_id integer, correlation_id integer,
     count integer, dtype text, bytes integer, algo integer, ctas integer, host_start_ns integer, host_end_ns integer,
     device_start_ns integer, device_end_ns integer);
+create table if not exists counter_sample(id integer primary key, name_id integer, device integer, ts_ns integer, value real);
 create index if not exists kd_name on kernel_dispatch(name_id);
 create index if not exists kd_start on kernel_dispatch(start_ns);
 create index if not exists rg_start on region(start_ns);
@@ -138,6 +140,11 @@ class TraceDB:
                      int(r["Grid_Size_X"]), int(r["Grid_Size_Y"]), int(r["Grid_Size_Z"]), int(r["Workgroup_Size_X"]), int(r["Workgroup_Size_Y"]),
                      int(r["Workgroup_Size_Z"]), int(r.get("Cluster_X", 0) or 0), int(r.get("Cluster_Y", 0) or 0), int(r.get("Cluster_Z", 0) or 0)))
                 n += 1
+        elif {"Counter", "Device", "Timestamp", "Value"} <= cols:  # system sampler
+            for r in rows:
+                self.db.execute("insert into counter_sample(name_id, device, ts_ns, value) values (?,?,?,?)",
+                                (self.string_id(r["Counter"]), int(r["Device"]), int(r["Timestamp"]), float(r["Value"])))
+                n += 1
         elif "Direction" in cols:
             for r in rows:
                 pid = self.process_id(int(r["Process_Id"]), file_rank, command)
@@ -224,6 +231,9 @@ class TraceDB:
         out["memory_copies"] = [dict(zip(names, r)) for r in rows]
         names, rows = self.query("select * from busy order by rank, device")
         out["busy"] = [dict(zip(names, r)) for r in rows]
+        names, rows = self.query("select s.value as counter, c.device, count(*) as samples, min(c.value) as min, avg(c.value) as mean, max(c.value) as max"
+                                 " from counter_sample c join string s on s.id = c.name_id group by s.value, c.device order by s.value, c.device")
+        out["counters"] = [dict(zip(names, r)) for r in rows]
         return out
 
     def to_perfetto(self, path: str) -> int:
@@ -246,6 +256,9 @@ class TraceDB:
             if e > s:
                 events.append({"ph": "X", "pid": pid, "tid": "collectives (device)", "name": name, "cat": "collective", "ts": s / 1e3,
                                "dur": (e - s) / 1e3, "args": {"bytes": nbytes, "rank": rank}})
+        for name, dev, ts, val in self.db.execute("select s.value, c.device, c.ts_ns, c.value from counter_sample c join string s on s.id = c.name_id"):
+            track = name if dev < 0 else f"{name} [{dev}]"
+            events.append({"ph": "C", "pid": 0, "name": track, "ts": ts / 1e3, "args": {"value": val}})
         with open(path, "w") as f:
             json.dump({"traceEvents": events, "displayTimeUnit": "ns"}, f)
         return len(events)
@@ -281,7 +294,7 @@ def format_table(names: Sequence[str], rows: Iterable[Sequence], max_width: int 
 
 def print_summary(summary: dict, file=sys.stdout) -> None:
     titles = {"kernels": "KERNEL_DISPATCH", "collectives": "COLLECTIVES (device time)", "regions": "API / MARKER REGIONS",
-              "memory_copies": "MEMORY_COPY", "busy": "DEVICE BUSY"}
+              "memory_copies": "MEMORY_COPY", "busy": "DEVICE BUSY", "counters": "SAMPLED COUNTERS"}
     for key, title in titles.items():
         rows = summary.get(key) or []
         if not rows:

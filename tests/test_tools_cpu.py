@@ -216,3 +216,21 @@ def test_info_runs_without_gpu():
     from rocm_systems_b200.tools.info import arch_target
 
     assert arch_target(10, 0) == "sm_100a" and arch_target(8, 0) == "sm_80"
+
+
+def test_system_sampler_and_launcher_counter_tracks(tmp_path, fake_nvml):
+    e = dict(os.environ, PYTHONPATH=str(ROOT), B200SMI_NVML_LIBRARY=fake_nvml, FAKE_NVML_GPUS="2")
+    child = "import time\nfrom rocm_systems_b200.utils import markers\nwith markers.range('sleep'):\n    time.sleep(0.5)\n"
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "--sys-sample", "50", "--summary", "--output-format", "db",
+                        "pftrace", "-d", str(tmp_path), "--", sys.executable, "-c", child], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr
+    s = json.loads((tmp_path / "trace_summary.json").read_text())
+    names = {(c["counter"], c["device"]) for c in s["counters"]}
+    assert ("gpu_power", 0) in names and ("gpu_power", 1) in names and ("host_mem_used_bytes", -1) in names
+    assert any(c["counter"] == "process_rss_bytes" and c["samples"] >= 3 for c in s["counters"])
+    ev = json.loads((tmp_path / "trace.perfetto.json").read_text())["traceEvents"]
+    assert any(x["ph"] == "C" and x["name"].startswith("gpu_sm_clock") for x in ev)
+    # sampler and marker share a clock: the samples bracket the range
+    rng = next(x for x in ev if x["ph"] == "X" and x["name"] == "sleep")
+    ts = [x["ts"] for x in ev if x["ph"] == "C"]
+    assert min(ts) <= rng["ts"] + 2e5 and max(ts) >= rng["ts"] + rng["dur"] - 2e5
