@@ -764,6 +764,18 @@ ncclResult_t b200collTraceWrite(ncclComm_t comm, const char* path, const char* f
 
 // ---- host-only rendezvous handles (used by tests and by the Python layer without a GPU) ---------
 extern "C" {
+// Copies the JSON description of every setting into `buf` (NUL-terminated, truncated to `cap`);
+// returns the length the full text needs.
+size_t b200collDescribeSettings(char* buf, size_t cap) {
+  const std::string s = describeSettings();
+  if (buf && cap) {
+    const size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+    memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return s.size() + 1;
+}
+
 ncclResult_t b200collBootCreate(const ncclUniqueId* id, int rank, int nranks, void** handle) {
   if (!id || !handle) BFAIL(ncclInvalidArgument, "b200collBootCreate: null argument");
   Bootstrap* b = new Bootstrap();

@@ -195,3 +195,90 @@ uint64_t nowNs() {
 }
 
 }  // namespace b200
+
+namespace b200 {
+// ---- settings listing --------------------------------------------------------------------------
+// Every knob with its environment names, current value, default and meaning, as JSON: what
+// `python -m rocm_systems_b200.tools.avail` prints (the role rocprof-sys-avail plays for its
+// settings: rocprofiler-systems/source/bin/rocprof-sys-avail).
+namespace {
+struct SettingDoc {
+  const char* name;
+  bool ncclAlias;
+  const char* dflt;
+  const char* doc;
+};
+const SettingDoc kSettings[] = {
+    {"DEBUG", true, "WARN", "log level: NONE, WARN, INFO, TRACE"},
+    {"DEBUG_SUBSYS", true, "ALL", "comma list of INIT,COLL,P2P,MEM,BOOTSTRAP,TOPO,TRACE,TUNING,SHMEM for INFO/TRACE lines"},
+    {"NVLS_ENABLE", true, "1", "0: never use in-switch reduction / multicast; 1: when the box supports it"},
+    {"ALGO", true, "", "force an algorithm: ll, p2p or nvls (a forced choice that cannot serve a call falls back)"},
+    {"MIN_CTAS", true, "0", "lower bound of CTAs per collective launch (0: built-in)"},
+    {"MAX_CTAS", true, "0", "upper bound of CTAs per collective launch (0: built-in)"},
+    {"BUFFSIZE", true, "64M", "bytes per staging half (two halves per communicator), at least 1M"},
+    {"LL_THRESHOLD", false, "64K", "largest all-reduce served by the flag-in-data protocol, at most 256K"},
+    {"P2P_CHUNK", false, "512K", "bytes per send/recv FIFO slot"},
+    {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
+    {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},
+    {"WAIT_TIMEOUT_MS", false, "20000", "budget of every device-side wait; on expiry the kernel records the wait and returns"},
+    {"BOOTSTRAP_TIMEOUT_MS", false, "120000", "budget of the host rendezvous"},
+    {"COMM_ID", true, "", "ip:port of the rendezvous root (ncclGetUniqueId then needs no out-of-band exchange)"},
+    {"SOCKET_ADDR", false, "127.0.0.1", "address the rendezvous root listens on"},
+    {"TUNING_FILE", false, "", "JSON table of rows {coll, max_bytes, algo, ctas} consulted before the built-in thresholds"},
+    {"TOOL_LIBRARIES", false, "", "':'-separated shared objects given the dispatch table through b200coll_tool_configure"},
+    {"TRACE", false, "0", "1: record host and device times of every collective (and b200tx ranges)"},
+    {"TRACE_FILE", false, "", "prefix of the CSV files written when a communicator is destroyed / at exit"},
+    {"FAIL_KEY", false, "", "comma list of host-side fault-injection points (tests only)"},
+    {"IPC_MODE_LEGACY", false, "0", "1: share memory through cudaIpc handles instead of VMM file descriptors"},
+};
+
+std::string currentValue(const Flags& f, const std::string& n) {
+  auto num = [](long long v) { return std::to_string(v); };
+  if (n == "DEBUG") return f.debugLevel == LOG_NONE ? "NONE" : f.debugLevel == LOG_WARN ? "WARN" : f.debugLevel == LOG_INFO ? "INFO" : "TRACE";
+  if (n == "DEBUG_SUBSYS") return f.debugSubsys == SUB_ALL ? "ALL" : num(f.debugSubsys);
+  if (n == "NVLS_ENABLE") return num(f.nvlsEnable);
+  if (n == "ALGO") return f.algo;
+  if (n == "MIN_CTAS") return num(f.minCtas);
+  if (n == "MAX_CTAS") return num(f.maxCtas);
+  if (n == "BUFFSIZE") return num((long long)f.stageBytes);
+  if (n == "LL_THRESHOLD") return num((long long)f.llMaxBytes);
+  if (n == "P2P_CHUNK") return num((long long)f.p2pChunkBytes);
+  if (n == "P2P_CTAS") return num(f.p2pCtasPerPeer);
+  if (n == "PIPELINE_CHUNK") return num(f.pipeChunkBytes);
+  if (n == "WAIT_TIMEOUT_MS") return num(f.waitTimeoutMs);
+  if (n == "BOOTSTRAP_TIMEOUT_MS") return num(f.bootTimeoutMs);
+  if (n == "COMM_ID") return f.commId;
+  if (n == "SOCKET_ADDR") return f.ifaddr;
+  if (n == "TUNING_FILE") return f.tuningFile;
+  if (n == "TOOL_LIBRARIES") return f.toolLibs;
+  if (n == "TRACE") return num(f.traceEnable);
+  if (n == "TRACE_FILE") return f.traceFile;
+  if (n == "FAIL_KEY") return f.failKey;
+  if (n == "IPC_MODE_LEGACY") return num(f.ipcLegacy);
+  return "";
+}
+
+std::string jsonEscape(const std::string& s) {
+  std::string o;
+  for (char ch : s) {
+    if (ch == '"' || ch == '\\') o += '\\';
+    if ((unsigned char)ch < 0x20) continue;
+    o += ch;
+  }
+  return o;
+}
+}  // namespace
+
+std::string describeSettings() {
+  const Flags& f = Flags::get();
+  std::string out = "[";
+  bool first = true;
+  for (const SettingDoc& s : kSettings) {
+    if (!first) out += ",";
+    first = false;
+    out += std::string("{\"name\":\"") + s.name + "\",\"env\":[\"B200COLL_" + s.name + "\"" + (s.ncclAlias ? std::string(",\"NCCL_") + s.name + "\"" : "") +
+           "],\"value\":\"" + jsonEscape(currentValue(f, s.name)) + "\",\"default\":\"" + s.dflt + "\",\"doc\":\"" + jsonEscape(s.doc) + "\"}";
+  }
+  return out + "]";
+}
+}  // namespace b200

@@ -103,6 +103,7 @@ struct Flags {
   static void refresh();  // re-read the environment (tests)
 };
 bool failPoint(const char* name);  // true when FAIL_KEY lists `name`
+std::string describeSettings();    // JSON array: every knob with its environment names, value, default and meaning
 
 // ---- dtype helpers -------------------------------------------------------------------------
 inline size_t dtypeSize(ncclDataType_t t) {

@@ -234,3 +234,38 @@ def test_system_sampler_and_launcher_counter_tracks(tmp_path, fake_nvml):
     rng = next(x for x in ev if x["ph"] == "X" and x["name"] == "sleep")
     ts = [x["ts"] for x in ev if x["ph"] == "C"]
     assert min(ts) <= rng["ts"] + 2e5 and max(ts) >= rng["ts"] + rng["dur"] - 2e5
+
+
+def test_settings_listing_reflects_environment():
+    out = _py("""
+import json
+from rocm_systems_b200.tools import avail
+rows = {r['name']: r for r in avail.settings()}
+assert rows['BUFFSIZE']['value'] == str(32 << 20) and rows['BUFFSIZE']['env'] == ['B200COLL_BUFFSIZE', 'NCCL_BUFFSIZE']
+assert rows['ALGO']['value'] == 'p2p' and rows['WAIT_TIMEOUT_MS']['value'] == '20000'
+assert rows['PIPELINE_CHUNK']['default'] == '-1' and len(rows) >= 20
+assert avail.main(['--changed']) == 0
+print('ok')
+""", {"B200COLL_BUFFSIZE": "32M", "NCCL_ALGO": "P2P"})
+    assert "ok" in out and "B200COLL_BUFFSIZE" in out and "B200COLL_TRACE " not in out
+
+
+def test_tuning_table_from_sweeps(tmp_path):
+    from rocm_systems_b200.tools import tune
+
+    def doc(times):
+        return {"nranks": 8, "rows": [{"coll": "all_reduce", "bytes": b, "ours_us": t} for b, t in times.items()]}
+
+    ll = doc({1024: 10, 65536: 14, 1 << 20: 90})
+    p2p = doc({1024: 20, 65536: 13.8, 1 << 20: 40, 1 << 26: 700})
+    nvls = doc({1024: 22, 65536: 25, 1 << 20: 30, 1 << 26: 400})
+    t = tune.build_table({"ll": ll, "p2p": p2p, "nvls": nvls})
+    rows = [(e["max_bytes"], e["algo"]) for e in t["entries"]]
+    # ll keeps 64 KiB although p2p is 1.4 % faster there (inside the margin); nvls takes over from 1 MiB
+    assert rows == [(65536, "ll"), (1 << 62, "nvls")], rows
+    (tmp_path / "a.json").write_text(json.dumps(ll))
+    (tmp_path / "b.json").write_text(json.dumps(nvls))
+    assert tune.main([f"ll={tmp_path / 'a.json'}", f"nvls={tmp_path / 'b.json'}", "-o", str(tmp_path / "t.json")]) == 0
+    assert json.loads((tmp_path / "t.json").read_text())["entries"][0]["coll"] == "all_reduce"
+    with pytest.raises(ValueError):
+        tune.build_table({"ll": ll, "p2p": dict(p2p, nranks=4)})
