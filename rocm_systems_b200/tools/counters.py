@@ -1,0 +1,237 @@
+"""Derived counters: named expressions over raw profiler metrics, defined in YAML and evaluated per
+kernel launch.
+
+The counterpart of the reference's counter service (rocprofiler-sdk/source/lib/rocprofiler-sdk/counters:
+YAML definitions, an expression parser — ``parser/scanner.l`` and ``parser.y`` — and AST
+evaluation in ``evaluate_ast.cpp``). The raw values here come from Nsight Compute's raw page
+(``ncu -i FILE --page raw --csv``) instead of hardware counter blocks; the grammar is
+
+    expr   := term (('+' | '-') term)*
+    term   := unary (('*' | '/') unary)*
+    unary  := '-' unary | atom
+    atom   := NUMBER | IDENT | IDENT '(' expr (',' expr)* ')' | '(' expr ')'
+    IDENT  := letters, digits, '_' and '.', e.g. dram__bytes_read.sum, peak.hbm_gbs, arg.flops
+
+with the functions ``min``, ``max``, ``abs``, ``sqrt`` and ``select(cond, a, b)`` (a when cond is non-zero).
+
+    python -m rocm_systems_b200.tools.counters raw.csv --peaks MEASURED_PEAKS.json --arg flops=1.0995e12
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import re
+import sys
+from pathlib import Path
+from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
+
+Node = Union[Tuple[str, float], Tuple[str, str], Tuple[str, str, list], Tuple[str, "Node"], Tuple[str, str, "Node", "Node"]]
+_TOKEN = re.compile(r"\s*(?:(\d+\.?\d*(?:[eE][+-]?\d+)?|\.\d+(?:[eE][+-]?\d+)?)|([A-Za-z_][A-Za-z0-9_.]*)|(.))")
+FUNCS: Dict[str, Callable[..., float]] = {
+    "min": lambda *a: min(a), "max": lambda *a: max(a), "abs": lambda x: abs(x), "sqrt": lambda x: math.sqrt(x),
+    "select": lambda c, a, b: a if c != 0 else b,
+}
+
+
+class ParseError(ValueError):
+    pass
+
+
+def tokenize(text: str) -> List[Tuple[str, str]]:
+    out, pos = [], 0
+    while pos < len(text):
+        m = _TOKEN.match(text, pos)
+        if not m or m.end() == pos:
+            break
+        pos = m.end()
+        num, ident, op = m.groups()
+        if num is not None:
+            out.append(("num", num))
+        elif ident is not None:
+            out.append(("id", ident))
+        elif op.strip():
+            if op not in "+-*/(),":
+                raise ParseError(f"unexpected character {op!r} in {text!r}")
+            out.append(("op", op))
+    return out
+
+
+class Parser:
+    def __init__(self, text: str):
+        self.text, self.toks, self.i = text, tokenize(text), 0
+
+    def peek(self) -> Tuple[str, str]:
+        return self.toks[self.i] if self.i < len(self.toks) else ("end", "")
+
+    def take(self, kind: Optional[str] = None, value: Optional[str] = None) -> Tuple[str, str]:
+        t = self.peek()
+        if (kind and t[0] != kind) or (value and t[1] != value):
+            raise ParseError(f"expected {value or kind} at token {self.i} of {self.text!r}, found {t[1]!r}")
+        self.i += 1
+        return t
+
+    def parse(self):
+        node = self.expr()
+        if self.peek()[0] != "end":
+            raise ParseError(f"trailing input {self.peek()[1]!r} in {self.text!r}")
+        return node
+
+    def expr(self):
+        node = self.term()
+        while self.peek() in (("op", "+"), ("op", "-")):
+            op = self.take()[1]
+            node = ("bin", op, node, self.term())
+        return node
+
+    def term(self):
+        node = self.unary()
+        while self.peek() in (("op", "*"), ("op", "/")):
+            op = self.take()[1]
+            node = ("bin", op, node, self.unary())
+        return node
+
+    def unary(self):
+        if self.peek() == ("op", "-"):
+            self.take()
+            return ("neg", self.unary())
+        return self.atom()
+
+    def atom(self):
+        kind, val = self.peek()
+        if kind == "num":
+            self.take()
+            return ("num", float(val))
+        if kind == "id":
+            self.take()
+            if self.peek() == ("op", "("):
+                self.take()
+                args = [self.expr()]
+                while self.peek() == ("op", ","):
+                    self.take()
+                    args.append(self.expr())
+                self.take("op", ")")
+                if val not in FUNCS:
+                    raise ParseError(f"unknown function {val!r} in {self.text!r}")
+                return ("call", val, args)
+            return ("id", val)
+        if (kind, val) == ("op", "("):
+            self.take()
+            node = self.expr()
+            self.take("op", ")")
+            return node
+        raise ParseError(f"unexpected {val or 'end of input'!r} in {self.text!r}")
+
+
+def parse(text: str):
+    return Parser(text).parse()
+
+
+def identifiers(node) -> List[str]:
+    k = node[0]
+    if k == "id":
+        return [node[1]]
+    if k == "bin":
+        return identifiers(node[2]) + identifiers(node[3])
+    if k == "neg":
+        return identifiers(node[1])
+    if k == "call":
+        return [i for a in node[2] for i in identifiers(a)]
+    return []
+
+
+def evaluate(node, env: Dict[str, float]) -> float:
+    """Evaluates an AST; a missing identifier raises KeyError, a division by zero gives NaN."""
+    k = node[0]
+    if k == "num":
+        return node[1]
+    if k == "id":
+        return float(env[node[1]])
+    if k == "neg":
+        return -evaluate(node[1], env)
+    if k == "bin":
+        a, b = evaluate(node[2], env), evaluate(node[3], env)
+        if node[1] == "+":
+            return a + b
+        if node[1] == "-":
+            return a - b
+        if node[1] == "*":
+            return a * b
+        return a / b if b != 0 else float("nan")
+    if k == "call":
+        return float(FUNCS[node[1]](*[evaluate(a, env) for a in node[2]]))
+    raise ValueError(k)
+
+
+class CounterSet:
+    def __init__(self, defs: Sequence[dict]):
+        self.defs = []
+        seen = set()
+        for d in defs:
+            if d["name"] in seen:
+                raise ValueError(f"counter {d['name']!r} is defined twice")
+            seen.add(d["name"])
+            self.defs.append({**d, "ast": parse(str(d["expression"]))})
+
+    @staticmethod
+    def load(path: Optional[str] = None) -> "CounterSet":
+        import yaml
+
+        p = Path(path) if path else Path(__file__).with_name("counter_defs.yaml")
+        return CounterSet(yaml.safe_load(p.read_text())["counters"])
+
+    def required_metrics(self) -> List[str]:
+        """Raw metric names the definitions read (what to pass to ``ncu --metrics``)."""
+        names = sorted({i for d in self.defs for i in identifiers(d["ast"]) if not i.startswith(("peak.", "arg."))})
+        return names
+
+    def evaluate(self, raw: Dict[str, float], peaks: Optional[dict] = None, args: Optional[dict] = None) -> Dict[str, Optional[float]]:
+        env = dict(raw)
+        env.update({f"peak.{k}": v for k, v in (peaks or {}).items() if isinstance(v, (int, float))})
+        env.update({f"arg.{k}": v for k, v in (args or {}).items()})
+        out: Dict[str, Optional[float]] = {}
+        for d in self.defs:
+            try:
+                out[d["name"]] = evaluate(d["ast"], env)
+            except KeyError:
+                out[d["name"]] = None  # an input is not in this capture
+        return out
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    from . import roofline
+
+    ap = argparse.ArgumentParser(prog="counters", description=__doc__.split("\n\n")[0])
+    ap.add_argument("inputs", nargs="*", help=".ncu-rep files or raw-page CSV files")
+    ap.add_argument("--defs", default=None, help="YAML definitions (default: the file next to this module)")
+    ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
+    ap.add_argument("--arg", action="append", default=[], help="NAME=VALUE readable as arg.NAME")
+    ap.add_argument("--list", action="store_true", help="print the definitions and the raw metrics they need")
+    ap.add_argument("--json", action="store_true")
+    a = ap.parse_args(argv)
+    cs = CounterSet.load(a.defs)
+    if a.list:
+        for d in cs.defs:
+            print(f"{d['name']:<22} [{d.get('unit', '')}] = {d['expression']}\n{'':<22} {d.get('description', '')}")
+        print("\nraw metrics: " + ",".join(cs.required_metrics()))
+        return 0
+    peaks = roofline.load_peaks(a.peaks)
+    args = {k: float(v) for k, v in (s.split("=", 1) for s in a.arg)}
+    rows = []
+    for path in a.inputs:
+        for k in roofline.read_ncu(path):
+            raw = dict(k.raw) if hasattr(k, "raw") else {}
+            rows.append({"kernel": k.name, **cs.evaluate(raw, peaks, args)})
+    if a.json:
+        print(json.dumps(rows, indent=1))
+    else:
+        for r in rows:
+            print(r["kernel"])
+            for name, v in r.items():
+                if name != "kernel" and v is not None:
+                    print(f"  {name:<22} {v:.4g}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

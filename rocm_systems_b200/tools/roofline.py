@@ -54,6 +54,7 @@ class Kernel:
     dram_bytes: float = 0.0
     flops: float = 0.0          # algorithmic, when known
     counters: Dict[str, float] = field(default_factory=dict)
+    raw: Dict[str, float] = field(default_factory=dict)   # every numeric column of the report under its raw name
 
     @property
     def gbs(self) -> float:
@@ -102,6 +103,13 @@ def parse_ncu_csv(text: str) -> List[Kernel]:
             except ValueError:
                 continue
             k.counters[key] = v * UNIT_SCALE.get(units[i], 1.0) if key.endswith(("_bytes", "_ns")) else v
+        # every numeric column under its raw name, bytes and times normalised (for tools/counters.py)
+        for name, i in col.items():
+            if i < len(r) and r[i] not in ("", "n/a"):
+                try:
+                    k.raw[name] = float(r[i].replace(",", "")) * UNIT_SCALE.get(units[i], 1.0)
+                except ValueError:
+                    pass
         k.duration_ns = k.counters.get("duration_ns", 0.0)
         k.dram_bytes = k.counters.get("dram_read_bytes", 0.0) + k.counters.get("dram_write_bytes", 0.0)
         out.append(k)

@@ -269,3 +269,31 @@ def test_tuning_table_from_sweeps(tmp_path):
     assert json.loads((tmp_path / "t.json").read_text())["entries"][0]["coll"] == "all_reduce"
     with pytest.raises(ValueError):
         tune.build_table({"ll": ll, "p2p": dict(p2p, nranks=4)})
+
+
+def test_derived_counters_parser_and_evaluation(tmp_path, capsys):
+    from rocm_systems_b200.tools import counters, roofline
+
+    ast = counters.parse("max(1, (a.b + 2 * -c) / 4) - select(d, 10, 20)")
+    assert counters.evaluate(ast, {"a.b": 10, "c": 1, "d": 0}) == 2.0 - 20
+    assert counters.evaluate(ast, {"a.b": 2, "c": 1, "d": 5}) == 1.0 - 10
+    assert sorted(set(counters.identifiers(ast))) == ["a.b", "c", "d"]
+    assert counters.evaluate(counters.parse("1e3 / 0"), {}) != counters.evaluate(counters.parse("1e3 / 0"), {})   # NaN, not an exception
+    for bad in ("1 +", "foo(1)", "(1", "1 $ 2", "1 2"):
+        with pytest.raises(counters.ParseError):
+            counters.parse(bad)
+    cs = counters.CounterSet.load()
+    need = cs.required_metrics()
+    assert "dram__bytes_read.sum" in need and "gpu__time_duration.sum" in need and not any(n.startswith(("peak.", "arg.")) for n in need)
+    k = roofline.parse_ncu_csv(NCU_CSV)[1]     # the GEMM row: 1000 us, 200 + 134 MB
+    vals = cs.evaluate(k.raw, {"hbm_gbs": 6541.5, "bf16_tflops": 1601.7}, {"flops": 2 * 8192.0 ** 3})
+    assert abs(vals["hbm_gbs"] - 334.0) < 1e-6 and abs(vals["tflops"] - 1099.5) < 0.1 and abs(vals["bf16_fraction"] - 0.6865) < 1e-3
+    assert vals["tensor_active_pct"] == 90 and vals["reread_factor"] is None          # arg.bytes was not given
+    with pytest.raises(ValueError):
+        counters.CounterSet([{"name": "x", "expression": "1"}, {"name": "x", "expression": "2"}])
+    (tmp_path / "raw.csv").write_text(NCU_CSV)
+    (tmp_path / "p.json").write_text(json.dumps({"hbm_gbs": 6541.5, "bf16_tflops": 1601.7}))
+    assert counters.main([str(tmp_path / "raw.csv"), "--peaks", str(tmp_path / "p.json"), "--arg", "flops=1.0995e12"]) == 0
+    out = capsys.readouterr().out
+    assert "gemmKernel" in out and "bf16_fraction" in out
+    assert counters.main(["--list"]) == 0
