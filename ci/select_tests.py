@@ -1,0 +1,87 @@
+#!/usr/bin/env python3
+"""Choose what CI has to build and test from the list of changed paths.
+
+The counterpart of the reference's mono-repo tooling (.github/scripts/therock_configure_ci.py and
+its subtree detection): there a changed project selects the projects to configure; here a changed
+layer of the package selects the test files that cover it and says whether the native code must be
+rebuilt and whether a GPU box is needed.
+
+    git diff --name-only origin/main... | python ci/select_tests.py            # JSON on stdout
+    python ci/select_tests.py --paths rocm_systems_b200/csrc/coll/kernels.cuh
+"""
+from __future__ import annotations
+
+import argparse
+import fnmatch
+import json
+import sys
+from typing import Iterable, List
+
+# (pattern, cpu tests, gpu tests, needs native rebuild)
+RULES = [
+    ("rocm_systems_b200/csrc/core/bootstrap.*", ["tests/test_bootstrap.py", "tests/test_sanitizers_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/core/topo.cc", ["tests/test_smi_fake.py", "tests/test_tools_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/core/health.cc", ["tests/test_smi_fake.py", "tests/test_tools_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/core/*", ["tests/test_bootstrap.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
+    ("rocm_systems_b200/csrc/coll/verifiable*", ["tests/test_verifiable_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/coll/*", [], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py"], True),
+    ("rocm_systems_b200/csrc/shmem/*", [], ["tests/test_gpu_fused_multi.py"], True),
+    ("rocm_systems_b200/csrc/fused/*", [], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_no_alloc.py"], True),
+    ("rocm_systems_b200/csrc/torch/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_collectives.py"], True),
+    ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),
+    ("rocm_systems_b200/csrc/prof/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),
+    ("rocm_systems_b200/csrc/perf/*", ["tests/test_verifiable_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/include/*", ["tests/test_bootstrap.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
+    ("rocm_systems_b200/tools/*", ["tests/test_tools_cpu.py", "tests/test_smi_fake.py"], [], False),
+    ("rocm_systems_b200/parallel/pp.py", ["tests/test_parallel_cpu.py"], [], False),
+    ("rocm_systems_b200/parallel/cp.py", ["tests/test_parallel_cpu.py"], [], False),
+    ("rocm_systems_b200/parallel/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_fused_multi.py"], False),
+    ("rocm_systems_b200/utils/elastic.py", ["tests/test_elastic_cpu.py"], [], False),
+    ("rocm_systems_b200/utils/checkpoint.py", ["tests/test_elastic_cpu.py"], [], False),
+    ("rocm_systems_b200/utils/build.py", ["tests"], ["tests"], True),
+    ("rocm_systems_b200/*", ["tests"], ["tests"], False),
+    ("tests/*", ["{path}"], ["{path}"], False),
+    ("bench.py", [], ["tests/test_gpu_fused_multi.py"], False),
+    ("*.md", [], [], False),
+    ("profiles/*", [], [], False),
+]
+
+
+def select(paths: Iterable[str]) -> dict:
+    cpu: List[str] = []
+    gpu: List[str] = []
+    rebuild = False
+    unknown: List[str] = []
+    for p in paths:
+        p = p.strip()
+        if not p:
+            continue
+        for pat, c, g, r in RULES:
+            if fnmatch.fnmatch(p, pat):
+                cpu += [x.format(path=p) for x in c if "{path}" not in x or p.endswith(".py")]
+                gpu += [x.format(path=p) for x in g if "{path}" not in x or p.endswith(".py")]
+                rebuild |= r
+                break
+        else:
+            unknown.append(p)
+    if unknown:  # something no rule knows: be safe, run everything
+        cpu, gpu, rebuild = ["tests"], ["tests"], True
+
+    def norm(xs: List[str]) -> List[str]:
+        xs = sorted(set(xs))
+        return ["tests"] if "tests" in xs else xs
+
+    return {"rebuild_native": rebuild, "cpu_tests": norm(cpu), "gpu_tests": norm(gpu), "needs_gpu": bool(gpu), "unmatched": unknown}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--paths", nargs="*", help="changed paths (default: one per line on stdin)")
+    a = ap.parse_args(argv)
+    paths = a.paths if a.paths is not None else sys.stdin.read().splitlines()
+    print(json.dumps(select(paths), indent=1))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
