@@ -67,9 +67,10 @@ class Geometry:
         return base + lo * U, base + hi * U
 
 
-def accesses(g: Geometry):
+def accesses(g: Geometry, half0: int = 0):
     """All staging accesses of one launch of the pipelined staged reduce (all-reduce or
-    reduce-scatter): tuples (rank, lane, group, epoch, target_rank, half, lo, hi, is_write)."""
+    reduce-scatter): tuples (rank, lane, group, epoch, target_rank, half, lo, hi, is_write).
+    ``half0`` is the staging half of the launch's first chunk."""
     out = []
     K = g.chunks()
     has_out = g.kind == "ar"
@@ -78,7 +79,7 @@ def accesses(g: Geometry):
             for s in range(g.n):
                 lo, hi = g.lane_range(k, s, b)
                 if lo < hi:
-                    out.append((r, b, group, epoch, r, k & 1, lo, hi, write))
+                    out.append((r, b, group, epoch, r, (k + half0) & 1, lo, hi, write))
         copy(0, 0, True, "all")                                   # prologue: copy-in of chunk 0, then barrier
         for k in range(K):
             epoch = k + 1
@@ -87,9 +88,9 @@ def accesses(g: Geometry):
             lo, hi = g.lane_range(k, r, b)                        # this rank reduces slice r
             if lo < hi:
                 for p in range(g.n):
-                    out.append((r, b, "reduce" if split else "all", epoch, p, k & 1, lo, hi, False))
+                    out.append((r, b, "reduce" if split else "all", epoch, p, (k + half0) & 1, lo, hi, False))
                     if has_out:
-                        out.append((r, b, "reduce" if split else "all", epoch, p, k & 1, lo, hi, True))
+                        out.append((r, b, "reduce" if split else "all", epoch, p, (k + half0) & 1, lo, hi, True))
             if prev_out:
                 copy(k - 1, epoch, False, "copy")                 # copy-out of the previous chunk ...
             if more:
@@ -173,3 +174,43 @@ def test_chunk_sized_geometry_is_caught():
     assert a[1] != c[1] and (a[8] or c[8])                         # different lanes, one of them writing
     # with equal chunks the two geometries coincide and nothing is wrong
     assert races(accesses(Geometry(2, 4, 4 * 4096, 4096, "ar", by_capacity=False))) == []
+
+
+def last_epoch(g: Geometry) -> int:
+    """Epoch of the accesses after the launch's last barrier (all-reduce: the epilogue copy-out;
+    reduce-scatter: the last chunk's reduce, which no barrier follows)."""
+    return g.chunks() + 1 if g.kind == "ar" else g.chunks()
+
+
+def cross_call_races(ga: Geometry, gb: Geometry):
+    """Launch A then launch B on every rank's stream, B starting on the half after A's last chunk.
+    A rank's own launches are ordered by its stream; across ranks an access of A is ordered before an
+    access of B if a barrier follows it in A (every rank takes part in every lane's barriers and
+    finishes A before it starts B) or a barrier precedes the other in B. What is left unordered is
+    A's accesses after its last barrier against B's prologue, on different ranks."""
+    a_tail = [x for x in accesses(ga, 0) if x[3] == last_epoch(ga)]
+    b_head = [y for y in accesses(gb, ga.chunks() & 1) if y[3] == 0]
+    found = []
+    for x in a_tail:
+        for y in b_head:
+            if x[0] != y[0] and x[4] == y[4] and x[5] == y[5] and x[6] < y[7] and y[6] < x[7] and (x[8] or y[8]):
+                found.append((x, y))
+    return found
+
+
+def test_back_to_back_launches_need_no_trailing_barrier():
+    rng = random.Random(11)
+    for _ in range(40):
+        n = rng.choice([2, 4, 8])
+        cap = U * rng.randint(n, 200)
+        ga = Geometry(n, rng.randint(1, 5), rng.randint(1, 5 * cap), cap, rng.choice(["ar", "rs"]))
+        capb = U * rng.randint(n, 200)
+        gb = Geometry(n, rng.randint(1, 5), rng.randint(1, 5 * capb), capb, rng.choice(["ar", "rs"]))   # other size, other lane count
+        assert cross_call_races(ga, gb) == []
+    # the invariant is the alternation of halves: start B on the half A just used and a reduce-scatter's
+    # last peer reads meet the next launch's copy-in
+    ga = Geometry(2, 2, 3 * 1024, 1024, "rs")
+    gb = Geometry(2, 2, 1024, 1024, "rs")
+    a_tail = [x for x in accesses(ga, 0) if x[3] == last_epoch(ga)]
+    b_head_wrong = [y for y in accesses(gb, (ga.chunks() - 1) & 1) if y[3] == 0]
+    assert any(x[0] != y[0] and x[4] == y[4] and x[5] == y[5] and x[6] < y[7] and y[6] < x[7] and (x[8] or y[8]) for x in a_tail for y in b_head_wrong)
