@@ -28,6 +28,11 @@ struct NvmlFns {
   nvmlReturn_t (*nvlinkState)(nvmlDevice_t, unsigned int, nvmlEnableState_t*) = nullptr;
   nvmlReturn_t (*nvlinkRemote)(nvmlDevice_t, unsigned int, nvmlPciInfo_t*) = nullptr;
   nvmlReturn_t (*setPowerLimit)(nvmlDevice_t, unsigned int) = nullptr;
+  nvmlReturn_t (*driverVersion)(char*, unsigned int) = nullptr;
+  nvmlReturn_t (*processes)(nvmlDevice_t, unsigned int*, nvmlProcessInfo_t*) = nullptr;
+  nvmlReturn_t (*nvlinkError)(nvmlDevice_t, unsigned int, nvmlNvLinkErrorCounter_t, unsigned long long*) = nullptr;
+  nvmlReturn_t (*pcieGen)(nvmlDevice_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*pcieWidth)(nvmlDevice_t, unsigned int*) = nullptr;
 };
 extern NvmlFns gN;
 bool ready();

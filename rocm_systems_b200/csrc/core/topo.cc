@@ -59,6 +59,11 @@ static bool loadNvml() {
   sym("nvmlDeviceGetNvLinkState", &gN.nvlinkState, false);
   sym("nvmlDeviceGetNvLinkRemotePciInfo_v2", &gN.nvlinkRemote, false);
   sym("nvmlDeviceSetPowerManagementLimit", &gN.setPowerLimit, false);
+  sym("nvmlSystemGetDriverVersion", &gN.driverVersion, false);
+  sym("nvmlDeviceGetComputeRunningProcesses_v3", &gN.processes, false);
+  sym("nvmlDeviceGetNvLinkErrorCounter", &gN.nvlinkError, false);
+  sym("nvmlDeviceGetCurrPcieLinkGeneration", &gN.pcieGen, false);
+  sym("nvmlDeviceGetCurrPcieLinkWidth", &gN.pcieWidth, false);
   if (!ok) {
     dlclose(gLib);
     gLib = nullptr;
@@ -259,6 +264,83 @@ b200smi_status_t b200smi_set_power_limit(int device, uint32_t milliwatt, int all
   if (st != B200SMI_OK) return st;
   if (!gN.setPowerLimit) return B200SMI_ERR_NOT_SUPPORTED;
   return gN.setPowerLimit(h, milliwatt) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+}  // extern "C"
+
+// ---- driver, processes, link errors, PCIe ------------------------------------------------------
+extern "C" {
+
+b200smi_status_t b200smi_driver_version(char* buf, int len) {
+  using namespace b200::smi;
+  if (!buf || len < 2) return B200SMI_ERR_INVALID;
+  if (!ready()) return B200SMI_ERR_NOT_LOADED;
+  if (!gN.driverVersion) return B200SMI_ERR_NOT_SUPPORTED;
+  return gN.driverVersion(buf, (unsigned)len) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+b200smi_status_t b200smi_processes(int device, b200smi_process_t* out, int max, int* n) {
+  using namespace b200::smi;
+  if (!n || max < 0 || (max > 0 && !out)) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.processes) return B200SMI_ERR_NOT_SUPPORTED;
+  nvmlProcessInfo_t infos[256];
+  unsigned int count = 256;
+  nvmlReturn_t r = gN.processes(h, &count, infos);
+  if (r != NVML_SUCCESS && r != NVML_ERROR_INSUFFICIENT_SIZE) return B200SMI_ERR_NVML;
+  if (count > 256) count = 256;
+  *n = (int)count;
+  for (unsigned i = 0; i < count && (int)i < max; i++) {
+    out[i].pid = infos[i].pid;
+    out[i].usedMemoryBytes = infos[i].usedGpuMemory;
+    out[i].name[0] = 0;
+    char path[64];
+    snprintf(path, sizeof(path), "/proc/%u/comm", infos[i].pid);
+    if (FILE* f = fopen(path, "r")) {
+      if (fgets(out[i].name, sizeof(out[i].name), f)) {
+        size_t l = strlen(out[i].name);
+        if (l && out[i].name[l - 1] == '\n') out[i].name[l - 1] = 0;
+      }
+      fclose(f);
+    }
+  }
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_nvlink_errors(int device, b200smi_nvlink_errors_t* out) {
+  using namespace b200::smi;
+  if (!out) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.nvlinkError) return B200SMI_ERR_NOT_SUPPORTED;
+  memset(out, 0, sizeof(*out));
+  for (unsigned link = 0; link < NVML_NVLINK_MAX_LINKS; link++) {
+    unsigned long long v = 0;
+    if (gN.nvlinkError(h, link, NVML_NVLINK_ERROR_DL_REPLAY, &v) != NVML_SUCCESS) continue;  // link not present
+    out->linksRead++;
+    out->replay += v;
+    if (gN.nvlinkError(h, link, NVML_NVLINK_ERROR_DL_RECOVERY, &v) == NVML_SUCCESS) out->recovery += v;
+    if (gN.nvlinkError(h, link, NVML_NVLINK_ERROR_DL_CRC_FLIT, &v) == NVML_SUCCESS) out->crcFlit += v;
+    if (gN.nvlinkError(h, link, NVML_NVLINK_ERROR_DL_CRC_DATA, &v) == NVML_SUCCESS) out->crcData += v;
+  }
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_pcie(int device, uint32_t* generation, uint32_t* width) {
+  using namespace b200::smi;
+  if (!generation || !width) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.pcieGen || !gN.pcieWidth) return B200SMI_ERR_NOT_SUPPORTED;
+  unsigned g = 0, w = 0;
+  if (gN.pcieGen(h, &g) != NVML_SUCCESS || gN.pcieWidth(h, &w) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  *generation = g;
+  *width = w;
+  return B200SMI_OK;
 }
 
 }  // extern "C"

@@ -75,6 +75,15 @@ b200smi_status_t b200smi_device_count(int* count);
 b200smi_status_t b200smi_device_info(int device, b200smi_device_info_t* info);
 b200smi_status_t b200smi_read_field(int device, int field, double* value);
 b200smi_status_t b200smi_link(int from, int to, b200smi_link_t* link);
+/* Driver version string, compute processes on a device, NVLink error counters summed over the
+ * device's links, and the PCIe link it trains at (rocm-smi: --showdriverversion, --showpids,
+ * rsmi_dev_xgmi_error_status, --showbus). */
+typedef struct { uint32_t pid; uint64_t usedMemoryBytes; char name[64]; } b200smi_process_t;
+typedef struct { uint64_t replay, recovery, crcFlit, crcData; uint32_t linksRead; } b200smi_nvlink_errors_t;
+b200smi_status_t b200smi_driver_version(char* buf, int len);
+b200smi_status_t b200smi_processes(int device, b200smi_process_t* out, int max, int* n);
+b200smi_status_t b200smi_nvlink_errors(int device, b200smi_nvlink_errors_t* out);
+b200smi_status_t b200smi_pcie(int device, uint32_t* generation, uint32_t* width);
 /* Watches: a sampler thread reads the watched fields every periodMs into a per-(device, field)
  * ring of `keep` samples (the watch table and cache of rdc_libs/rdc/src/RdcWatchTableImpl.cc). */
 b200smi_status_t b200smi_watch_start(const int* devices, int ndev, const int* fields, int nfields, int periodMs, int keep);

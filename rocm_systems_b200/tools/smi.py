@@ -47,6 +47,15 @@ class Stats(ctypes.Structure):
     _fields_ = [("min", ctypes.c_double), ("max", ctypes.c_double), ("avg", ctypes.c_double), ("last", ctypes.c_double), ("samples", ctypes.c_uint64)]
 
 
+class Process(ctypes.Structure):
+    _fields_ = [("pid", ctypes.c_uint32), ("usedMemoryBytes", ctypes.c_uint64), ("name", ctypes.c_char * 64)]
+
+
+class NvlinkErrors(ctypes.Structure):
+    _fields_ = [("replay", ctypes.c_uint64), ("recovery", ctypes.c_uint64), ("crcFlit", ctypes.c_uint64), ("crcData", ctypes.c_uint64),
+                ("linksRead", ctypes.c_uint32)]
+
+
 POLICY_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_double, ctypes.c_void_p)
 
 
@@ -66,6 +75,10 @@ class Smi:
         L.b200smi_policy_set.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_int, POLICY_CB, ctypes.c_void_p]
         L.b200smi_health.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_char_p, ctypes.c_int]
         L.b200smi_set_power_limit.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_int]
+        L.b200smi_driver_version.argtypes = [ctypes.c_char_p, ctypes.c_int]
+        L.b200smi_processes.argtypes = [ctypes.c_int, ctypes.POINTER(Process), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        L.b200smi_nvlink_errors.argtypes = [ctypes.c_int, ctypes.POINTER(NvlinkErrors)]
+        L.b200smi_pcie.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32)]
         self._cbs = []
         self._ck(L.b200smi_init())
 
@@ -138,6 +151,29 @@ class Smi:
         self._ck(self.lib.b200smi_health(dev, ctypes.byref(lv), buf, 256))
         return lv.value, buf.value.decode()
 
+    def driver_version(self) -> str:
+        buf = ctypes.create_string_buffer(96)
+        self._ck(self.lib.b200smi_driver_version(buf, 96))
+        return buf.value.decode()
+
+    def processes(self, dev: int) -> list:
+        """Compute processes on the device: pid, device memory in use, command name."""
+        n = ctypes.c_int()
+        arr = (Process * 256)()
+        self._ck(self.lib.b200smi_processes(dev, arr, 256, ctypes.byref(n)))
+        return [{"pid": arr[i].pid, "used_memory_bytes": arr[i].usedMemoryBytes, "name": arr[i].name.decode(errors="replace")}
+                for i in range(min(n.value, 256))]
+
+    def nvlink_errors(self, dev: int) -> dict:
+        e = NvlinkErrors()
+        self._ck(self.lib.b200smi_nvlink_errors(dev, ctypes.byref(e)))
+        return {f[0]: getattr(e, f[0]) for f in NvlinkErrors._fields_}
+
+    def pcie(self, dev: int) -> dict:
+        g, w = ctypes.c_uint32(), ctypes.c_uint32()
+        self._ck(self.lib.b200smi_pcie(dev, ctypes.byref(g), ctypes.byref(w)))
+        return {"generation": g.value, "width": w.value}
+
     def set_power_limit(self, dev: int, milliwatt: int, allow: bool) -> None:
         self._ck(self.lib.b200smi_set_power_limit(dev, milliwatt, int(allow)))
 
@@ -158,6 +194,10 @@ def main(argv=None) -> int:
     ap.add_argument("--showall", action="store_true")
     ap.add_argument("--showtopo", action="store_true", help="weight, hops, type and bandwidth tables")
     ap.add_argument("--showhealth", action="store_true")
+    ap.add_argument("--showpids", action="store_true", help="compute processes per GPU")
+    ap.add_argument("--showdriverversion", action="store_true")
+    ap.add_argument("--shownvlinkerrors", action="store_true", help="replay / recovery / CRC counters summed over each GPU's links")
+    ap.add_argument("--showbus", action="store_true", help="PCIe generation and width")
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--setpowerlimit", nargs=2, metavar=("GPU", "WATTS"))
     ap.add_argument("--allow-set", action="store_true", help="required (with B200SMI_ALLOW_SET=1) before any setter acts")
@@ -176,7 +216,30 @@ def main(argv=None) -> int:
         except RuntimeError as e:
             print(f"b200-smi: {e}", file=sys.stderr)
             return 2
-    if a.showall or not (a.showtopo or a.showhealth or a.setpowerlimit):
+    if a.showdriverversion or a.showall:
+        out["driver_version"] = smi.driver_version()
+        if not a.json:
+            print(f"Driver version: {out['driver_version']}")
+    if a.showpids:
+        out["processes"] = {i: smi.processes(i) for i in range(n)}
+        if not a.json:
+            print(f"{'GPU':<4}{'PID':<10}{'Memory GiB':<12}Name")
+            for i, ps in out["processes"].items():
+                for pr in ps:
+                    print(f"{i:<4}{pr['pid']:<10}{pr['used_memory_bytes'] / 2**30:<12.2f}{pr['name']}")
+    if a.shownvlinkerrors:
+        out["nvlink_errors"] = [smi.nvlink_errors(i) for i in range(n)]
+        if not a.json:
+            print(f"{'GPU':<4}{'links':<7}{'replay':<10}{'recovery':<10}{'crc flit':<10}{'crc data':<10}")
+            for i, e in enumerate(out["nvlink_errors"]):
+                print(f"{i:<4}{e['linksRead']:<7}{e['replay']:<10}{e['recovery']:<10}{e['crcFlit']:<10}{e['crcData']:<10}")
+    if a.showbus:
+        out["pcie"] = [smi.pcie(i) for i in range(n)]
+        if not a.json:
+            for i, e in enumerate(out["pcie"]):
+                print(f"GPU{i}: PCIe gen {e['generation']} x{e['width']}")
+    only_new = a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    if a.showall or not (a.showtopo or a.showhealth or a.setpowerlimit or only_new):
         out["devices"] = [smi.info(i) for i in range(n)]
         if not a.json:
             print(f"{'GPU':<4}{'Name':<22}{'Bus':<18}{'SM MHz':<12}{'Power W':<10}{'Temp C':<8}{'Mem used/total GiB':<22}{'NVLink':<8}{'Throttle'}")

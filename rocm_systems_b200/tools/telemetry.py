@@ -129,6 +129,16 @@ class Telemetry:
                 mask = int(vals[d]["throttle_reasons"])
                 for bit, reason in REASON_BITS.items():
                     lines.append(f'b200_clock_event_reason{{gpu="{d}",reason="{reason}"}} {1 if mask & bit else 0}')
+        try:  # link error counters, where the driver exposes them
+            errs = {d: self.smi.nvlink_errors(d) for d in self.devices}
+            for key, metric in (("replay", "b200_nvlink_replay_errors_total"), ("recovery", "b200_nvlink_recovery_errors_total"),
+                                ("crcFlit", "b200_nvlink_crc_flit_errors_total"), ("crcData", "b200_nvlink_crc_data_errors_total")):
+                lines.append(f"# HELP {metric} NVLink {key} errors summed over the device's links")
+                lines.append(f"# TYPE {metric} counter")
+                for d in self.devices:
+                    lines.append(f'{metric}{{gpu="{d}"}} {errs[d][key]}')
+        except RuntimeError:
+            pass
         return "\n".join(lines) + "\n"
 
 

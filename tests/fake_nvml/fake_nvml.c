@@ -8,6 +8,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
 
 typedef struct fake_dev { int idx; } *nvmlDevice_t;
 typedef int nvmlReturn_t;
@@ -43,3 +44,27 @@ nvmlReturn_t nvmlDeviceGetCurrentClocksEventReasons(nvmlDevice_t d, unsigned lon
 nvmlReturn_t nvmlDeviceGetUtilizationRates(nvmlDevice_t d, nvmlUtilization_t* u) { (void)d; u->gpu = 97; u->memory = 40; return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetNvLinkState(nvmlDevice_t d, unsigned int link, int* active) { if (link >= 18) return NVML_ERROR_INVALID_ARGUMENT; *active = !(envint("FAKE_NVML_LINK_DOWN", -1) == d->idx && link == 5); return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetNvLinkRemotePciInfo_v2(nvmlDevice_t d, unsigned int link, nvmlPciInfo_t* p) { (void)d; (void)link; memset(p, 0, sizeof(*p)); snprintf(p->busId, sizeof(p->busId), "00000000:F0:00.0"); return NVML_SUCCESS; }
+
+/* driver version, processes, NVLink error counters, PCIe link */
+typedef struct { unsigned int pid; unsigned long long usedGpuMemory; unsigned int gpuInstanceId, computeInstanceId; } nvmlProcessInfo_t;
+nvmlReturn_t nvmlSystemGetDriverVersion(char* s, unsigned int n) { snprintf(s, n, "580.159.fake"); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetComputeRunningProcesses_v3(nvmlDevice_t d, unsigned int* count, nvmlProcessInfo_t* infos) {
+  /* GPU 0 runs two processes (this one and pid 1), the others none */
+  unsigned int have = d->idx == 0 ? 2 : 0;
+  if (*count < have) { *count = have; return 7; /* NVML_ERROR_INSUFFICIENT_SIZE */ }
+  *count = have;
+  if (have) {
+    memset(infos, 0, have * sizeof(*infos));
+    infos[0].pid = (unsigned)getpid(); infos[0].usedGpuMemory = 3ull << 30;
+    infos[1].pid = 1; infos[1].usedGpuMemory = 1ull << 30;
+  }
+  return NVML_SUCCESS;
+}
+nvmlReturn_t nvmlDeviceGetNvLinkErrorCounter(nvmlDevice_t d, unsigned int link, int counter, unsigned long long* v) {
+  if (link >= 18) return NVML_ERROR_INVALID_ARGUMENT;
+  /* FAKE_NVML_LINK_ERRORS=<gpu>: that GPU shows 5 replays on link 3 */
+  *v = (envint("FAKE_NVML_LINK_ERRORS", -1) == d->idx && link == 3 && counter == 0) ? 5 : 0;
+  return NVML_SUCCESS;
+}
+nvmlReturn_t nvmlDeviceGetCurrPcieLinkGeneration(nvmlDevice_t d, unsigned int* g) { (void)d; *g = 5; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetCurrPcieLinkWidth(nvmlDevice_t d, unsigned int* w) { (void)d; *w = 16; return NVML_SUCCESS; }

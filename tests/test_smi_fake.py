@@ -101,3 +101,25 @@ print(s.info(0)['powerLimitMilliwatt'])
     assert out == ["refused", "False", "refused", "True", "1000000"]          # env switch absent: nothing is written
     out = _run(code, fake_nvml, {"B200SMI_ALLOW_SET": "1"}).split()
     assert out == ["refused", "False", "set", "True", "700000"]               # only the fake GPU is ever touched
+
+
+def test_driver_processes_link_errors_and_bus(fake_nvml):
+    out = _run("""
+import os
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+assert s.driver_version() == '580.159.fake'
+ps = s.processes(0)
+assert [p['pid'] for p in ps] == [os.getpid(), 1] and ps[0]['used_memory_bytes'] == 3 << 30 and ps[0]['name'].startswith('python')
+assert s.processes(1) == []
+e = s.nvlink_errors(2)
+assert e['linksRead'] == 18 and e['replay'] == 5 and e['crcFlit'] == 0 and s.nvlink_errors(0)['replay'] == 0
+assert s.pcie(3) == {'generation': 5, 'width': 16}
+print('ok')
+""", fake_nvml, {"FAKE_NVML_LINK_ERRORS": "2"})
+    assert "ok" in out
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showpids", "--shownvlinkerrors", "--showbus", "--showdriverversion"],
+                       env=e, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    assert "580.159.fake" in p.stdout and "PCIe gen 5 x16" in p.stdout and "Memory GiB" in p.stdout and "SM MHz" not in p.stdout
