@@ -99,6 +99,8 @@ def main() -> None:
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--collectives", default="b200coll", choices=["b200coll", "nccl"],
+                    help="nccl: the same trainer with stock NCCL collectives (control run; the metric name gets a _nccl_collectives suffix)")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
@@ -121,12 +123,20 @@ def main() -> None:
         print(f"# note: --gpus {args.gpus} but WORLD_SIZE {world}; using WORLD_SIZE", file=sys.stderr)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    comm = bcomm.init_from_env(device=local)
+    if args.collectives == "nccl" and world > 1:
+        import torch.distributed as dist
+
+        from rocm_systems_b200.parallel.nccl_comm import NcclComm
+
+        dist.init_process_group("nccl", device_id=dev)
+        comm = NcclComm()
+    else:
+        comm = bcomm.init_from_env(device=local)
 
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny(512)
     if args.seq:
         cfg.seq_len = args.seq
-    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev)
+    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl")
     S, B = cfg.seq_len, 1
     nbatches = 4
     g = torch.Generator().manual_seed(1234 + rank)
@@ -172,7 +182,7 @@ def main() -> None:
     tokens_per_step = world * B * S
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     out = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC + ("_nccl_collectives" if args.collectives == "nccl" else ""), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic tokens uniform over the vocabulary (seeded), random-init weights N(0,0.02)",
         "config": {"model": "llama3-8b" if args.model == "llama3_8b" else "tiny", "global_batch": world * B, "seq_len": S,
