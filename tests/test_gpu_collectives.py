@@ -106,3 +106,20 @@ def test_torch_distributed_backend(nproc):
     sys.stdout.write(p.stdout[-4000:])
     sys.stderr.write(p.stderr[-4000:])
     assert p.returncode == 0
+
+
+@pytest.mark.multigpu
+def test_large_messages_through_many_pipeline_chunks():
+    """80 MB messages (several pipeline chunks with a short last one) for every dtype and operator,
+    bit-exact; once with the default chunking and once with 1 MiB chunks."""
+    if gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    for i, extra in enumerate(({}, {"B200COLL_PIPELINE_CHUNK": "1M"})):
+        env = dict(os.environ, **extra)
+        env.setdefault("B200COLL_WAIT_TIMEOUT_MS", "5000")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+               "--master-port", str(29650 + i), str(ROOT / "tests" / "workers" / "coll_worker.py")]
+        p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+        sys.stdout.write(p.stdout[-3000:])
+        sys.stderr.write(p.stderr[-3000:])
+        assert p.returncode == 0
