@@ -297,3 +297,17 @@ def test_derived_counters_parser_and_evaluation(tmp_path, capsys):
     out = capsys.readouterr().out
     assert "gemmKernel" in out and "bf16_fraction" in out
     assert counters.main(["--list"]) == 0
+
+
+def test_tracing_overhead_harness(tmp_path):
+    from rocm_systems_b200.bench import prof_overhead
+
+    child = "from rocm_systems_b200.utils import markers\nimport time\nwith markers.range('w'):\n    time.sleep(0.05)\n"
+    os.environ.setdefault("PYTHONPATH", str(ROOT))
+    res = prof_overhead.measure([sys.executable, "-c", child], {"markers": "--marker-trace"}, repeat=2)
+    assert len(res["baseline_s"]) == 2 and res["configs"]["markers"]["median_s"] > 0
+    prof_overhead.store(str(tmp_path / "o.db"), res)
+    import sqlite3
+
+    rows = sqlite3.connect(str(tmp_path / "o.db")).execute("select config, repeat from overhead").fetchall()
+    assert rows == [("markers", 2)]
