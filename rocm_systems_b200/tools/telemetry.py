@@ -56,6 +56,73 @@ class Telemetry:
         self.fields: List[str] = list(DEFAULT_FIELDS)
         self.watching = False
         self.jobs: dict = {}
+        self.groups: dict = {"all": list(self.devices)}          # device groups by name
+        self.field_groups: dict = {"default": list(DEFAULT_FIELDS)}
+
+    # ---- groups (rdc: rdc_group_gpu_create / rdc_group_field_create / rdc_field_watch) ----
+    def create_group(self, name: str, devices: Sequence[int]) -> None:
+        n = self.smi.count()
+        bad = [d for d in devices if not 0 <= d < n]
+        if bad:
+            raise ValueError(f"no such device(s) {bad}; this host has {n}")
+        self.groups[name] = list(devices)
+
+    def create_field_group(self, name: str, fields: Sequence[str]) -> None:
+        unknown = [f for f in fields if f not in FIELDS]
+        if unknown:
+            raise ValueError(f"unknown field(s) {unknown}; known: {sorted(FIELDS)}")
+        self.field_groups[name] = list(fields)
+
+    def watch(self, group: str = "all", field_group: str = "default", period_ms: int = 1000, keep: int = 3600) -> None:
+        self.start(self.groups[group], self.field_groups[field_group], period_ms, keep)
+
+    def diagnose(self, level: int = 1) -> List[dict]:
+        """Short diagnostics per device (rdc: rdc_diagnostic_run). Level 1 reads only: health verdict,
+        every link up, no uncorrected ECC, no link errors, PCIe link trained at full width. Level 2
+        adds a device-memory bandwidth check when this process can use CUDA."""
+        out = []
+        for d in self.devices:
+            checks = []
+            lvl, msg = self.smi.health(d)
+            checks.append({"check": "health", "pass": lvl == 0, "detail": msg})
+            i = self.smi.info(d)
+            checks.append({"check": "nvlink_up", "pass": i["nvlinkActive"] == i["nvlinkCount"], "detail": f"{i['nvlinkActive']}/{i['nvlinkCount']} links"})
+            checks.append({"check": "ecc_uncorrected", "pass": i["eccUncorrected"] == 0, "detail": str(i["eccUncorrected"])})
+            try:
+                e = self.smi.nvlink_errors(d)
+                bad = e["replay"] + e["recovery"] + e["crcFlit"] + e["crcData"]
+                checks.append({"check": "nvlink_errors", "pass": bad == 0, "detail": json.dumps(e)})
+                pc = self.smi.pcie(d)
+                checks.append({"check": "pcie_link", "pass": pc["width"] >= 16, "detail": f"gen {pc['generation']} x{pc['width']}"})
+            except RuntimeError as err:
+                checks.append({"check": "nvlink_errors", "pass": True, "detail": f"not available: {err}"})
+            if level >= 2:
+                checks.append(self._bandwidth_check(d))
+            out.append({"device": d, "pass": all(c["pass"] for c in checks), "checks": checks})
+        return out
+
+    @staticmethod
+    def _bandwidth_check(dev: int, nbytes: int = 1 << 30, floor_gbs: float = 3000.0) -> dict:
+        try:
+            import torch
+
+            if not torch.cuda.is_available() or dev >= torch.cuda.device_count():
+                return {"check": "memory_bandwidth", "pass": True, "detail": "skipped: CUDA not usable from this process"}
+            with torch.cuda.device(dev):
+                a = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+                b = torch.empty_like(a)
+                for _ in range(2):
+                    b.copy_(a)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(5):
+                    b.copy_(a)
+                e.record()
+                torch.cuda.synchronize()
+                gbs = 2 * nbytes * 5 / (s.elapsed_time(e) * 1e-3) / 1e9
+            return {"check": "memory_bandwidth", "pass": gbs >= floor_gbs, "detail": f"{gbs:.0f} GB/s copy (floor {floor_gbs:.0f})"}
+        except Exception as err:  # noqa: BLE001 - a diagnostic reports, it does not raise
+            return {"check": "memory_bandwidth", "pass": False, "detail": str(err)}
 
     def start(self, devices: Optional[Sequence[int]] = None, fields: Optional[Sequence[str]] = None, period_ms: int = 1000, keep: int = 3600) -> None:
         if devices is not None:
@@ -217,6 +284,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("-e", "--fields", nargs="+", default=["sm_clock", "power", "temp", "gpu_util", "mem_used"])
     p.add_argument("-i", "--devices", nargs="+", type=int)
     sub.add_parser("health", help="one health verdict per device")
+    p = sub.add_parser("diag", help="short diagnostics per device")
+    p.add_argument("--level", type=int, default=1, choices=[1, 2])
     p = sub.add_parser("client", help="talk to a running daemon")
     p.add_argument("--url", default="http://127.0.0.1:9400")
     p.add_argument("what", choices=["devices", "latest", "health", "metrics", "history", "job-start", "job-stop", "job-stats"])
@@ -244,6 +313,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     elif a.cmd == "health":
         for d, h in t.health().items():
             print(f"GPU {d}: {h['level']} {h['message']}")
+    elif a.cmd == "diag":
+        res = t.diagnose(a.level)
+        for r in res:
+            print(f"GPU {r['device']}: {'PASS' if r['pass'] else 'FAIL'}")
+            for c in r["checks"]:
+                print(f"    {c['check']:<18} {'ok' if c['pass'] else 'FAILED':<7} {c['detail']}")
+        return 0 if all(r["pass"] for r in res) else 1
     elif a.cmd == "dmon":
         t.fields = a.fields
         if a.devices:

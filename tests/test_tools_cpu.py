@@ -311,3 +311,27 @@ def test_tracing_overhead_harness(tmp_path):
 
     rows = sqlite3.connect(str(tmp_path / "o.db")).execute("select config, repeat from overhead").fetchall()
     assert rows == [("markers", 2)]
+
+
+def test_telemetry_groups_and_diagnostics(fake_nvml):
+    out = _py("""
+from rocm_systems_b200.tools import telemetry
+t = telemetry.Telemetry()
+t.create_group('pair', [0, 2]); t.create_field_group('thermal', ['temp', 'power'])
+try:
+    t.create_group('bad', [9]); raise SystemExit('bad group accepted')
+except ValueError:
+    pass
+t.watch('pair', 'thermal', period_ms=20, keep=10)
+assert t.devices == [0, 2] and t.fields == ['temp', 'power']
+t.stop()
+d = {r['device']: r for r in t.diagnose(1)}
+assert d[0]['pass'] and not d[2]['pass']
+failed = [c['check'] for c in d[2]['checks'] if not c['pass']]
+assert failed == ['nvlink_errors'], failed
+print('ok')
+""", {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "4", "FAKE_NVML_LINK_ERRORS": "2"})
+    assert "ok" in out
+    e = dict(os.environ, PYTHONPATH=str(ROOT), B200SMI_NVML_LIBRARY=fake_nvml, FAKE_NVML_GPUS="2", FAKE_NVML_ECC="1")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.telemetry", "diag"], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 1 and "GPU 1: FAIL" in p.stdout and "GPU 0: PASS" in p.stdout, p.stdout + p.stderr
