@@ -5,18 +5,23 @@
 //   kLLAllReduce      one-shot all-reduce for small messages: every rank stores its data into
 //                     every peer's buffer as 16-byte lines {data, flag, data, flag}; the flag in
 //                     the line is the only synchronisation (one NVLink crossing of latency).
-//   kStagedReduce     AllReduce / ReduceScatter / Reduce through a symmetric staging buffer:
-//                     copy-in, barrier, each rank reduces its 1/n slice (peer loads, or one
-//                     multimem.ld_reduce that adds inside the NVSwitch), result goes straight to
-//                     where it is needed (peer stores / multimem.st / local recv), barrier,
-//                     copy-out. With registered symmetric buffers the copies disappear.
-//   kStagedCopy       AllGather (pull from peers' staging into recv) and Broadcast (root fills
-//                     staging, with one multicast store when NVLS is on; the others copy out).
+//   kStagedReduce     AllReduce / ReduceScatter / Reduce through a symmetric staging buffer,
+//                     software-pipelined over chunks: while half of the CTA reduces chunk k over
+//                     NVLink (one multimem.ld_reduce that adds inside the NVSwitch, or bulk
+//                     asynchronous copies of every rank's tile into a shared-memory ring), the
+//                     other half copies chunk k-1 out of staging and chunk k+1 into it. Results go
+//                     straight to where they are needed (multimem.st / peer stores / local recv).
+//                     With registered symmetric buffers the copies disappear.
+//   kStagedCopy       AllGather (pull from peers' staging into recv, pipelined the same way
+//                     between few ranks; short parts are pulled from all peers at once) and
+//                     Broadcast (root fills staging, with one multicast store when NVLS is on;
+//                     the others copy out).
 //   kP2p              grouped Send/Recv work list over per-peer FIFOs with credits; AllToAll(v),
 //                     Gather and Scatter are built from it.
 // Staging halves alternate per chunk; every chunk's copy-in is followed by a full barrier before
 // anyone reads it, which is what makes reusing a half two chunks later safe without a trailing
-// barrier, also across calls.
+// barrier, also across calls. Where data of a chunk lives in a half, and which lane handles it,
+// depends on the chunk capacity alone (see the note on geometry in kStagedReduce).
 #pragma once
 
 #include <type_traits>
