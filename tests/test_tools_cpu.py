@@ -335,3 +335,22 @@ print('ok')
     e = dict(os.environ, PYTHONPATH=str(ROOT), B200SMI_NVML_LIBRARY=fake_nvml, FAKE_NVML_GPUS="2", FAKE_NVML_ECC="1")
     p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.telemetry", "diag"], env=e, capture_output=True, text=True, timeout=120)
     assert p.returncode == 1 and "GPU 1: FAIL" in p.stdout and "GPU 0: PASS" in p.stdout, p.stdout + p.stderr
+
+
+def test_roofline_and_counters_on_a_recorded_capture(capsys):
+    """A recorded Nsight Compute raw page of the tcgen05 GEMM (4096^3 bf16 on a B200), reduced to the
+    columns the tools read: analysis needs no GPU, as with the reference's recorded workloads."""
+    from rocm_systems_b200.tools import counters, roofline
+
+    path = str(ROOT / "tests" / "fixtures" / "gemm_tcgen05_ncu_raw.csv")
+    ks = roofline.read_ncu(path)
+    assert len(ks) >= 1 and "gemmKernel" in ks[0].name
+    k = ks[0]
+    assert 50e3 < k.duration_ns < 500e3 and k.counters["tensor_pct"] > 50 and k.counters["registers"] > 0
+    k.flops = 2 * 4096.0 ** 3
+    peaks = {"hbm_gbs": 6541.5, "bf16_tflops": 1601.7, "source": "measured"}
+    assert roofline.classify(k, peaks) == "compute" and 0.5 < k.tflops / peaks["bf16_tflops"] < 1.1
+    vals = counters.CounterSet.load().evaluate(k.raw, peaks, {"flops": k.flops, "bytes": 3 * 4096 * 4096 * 2})
+    assert vals["tensor_active_pct"] > 50 and 0.9 < vals["reread_factor"] < 2.0 and vals["arithmetic_intensity"] > 500
+    assert roofline.main([path, "--peaks", "/nonexistent.json", "--flops", "gemm=1.374e11"]) == 0
+    assert "of nominal" in capsys.readouterr().out
