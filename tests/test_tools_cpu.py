@@ -354,3 +354,26 @@ def test_roofline_and_counters_on_a_recorded_capture(capsys):
     assert vals["tensor_active_pct"] > 50 and 0.9 < vals["reread_factor"] < 2.0 and vals["arithmetic_intensity"] > 500
     assert roofline.main([path, "--peaks", "/nonexistent.json", "--flops", "gemm=1.374e11"]) == 0
     assert "of nominal" in capsys.readouterr().out
+
+
+def test_tool_registration_is_once_under_concurrent_first_use(tmp_path):
+    """Many threads make the first API call at once: the dispatch table is built once, the tool is
+    configured once (listing it twice does not load it twice) and no call is lost."""
+    from rocm_systems_b200.utils import build
+
+    tool = build.build_sample_tool()
+    out = tmp_path / "tool.txt"
+    _py("""
+import ctypes, threading
+from rocm_systems_b200 import _lib
+lib = _lib.load()
+start = threading.Barrier(16)
+def work():
+    v = ctypes.c_int()
+    start.wait()
+    for _ in range(50):
+        assert lib.ncclGetVersion(ctypes.byref(v)) == 0 and v.value == 22005
+ts = [threading.Thread(target=work) for _ in range(16)]
+[t.start() for t in ts]; [t.join() for t in ts]
+""", {"B200COLL_TOOL_LIBRARIES": f"{tool}:{tool}", "B200COLL_SAMPLE_TOOL_OUTPUT": str(out)})
+    assert "ncclGetVersion calls=800" in out.read_text()
