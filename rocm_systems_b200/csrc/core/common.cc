@@ -140,6 +140,11 @@ bool failPoint(const char* name) {
   return false;
 }
 
+const char* baseName(const char* path) {
+  const char* b = strrchr(path, '/');
+  return b ? b + 1 : path;
+}
+
 int logLevel() { return Flags::get().debugLevel; }
 unsigned logSubsys() { return Flags::get().debugSubsys; }
 

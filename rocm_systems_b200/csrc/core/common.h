@@ -30,6 +30,7 @@ enum LogSubsys : unsigned {
   SUB_INIT = 1, SUB_COLL = 2, SUB_P2P = 4, SUB_MEM = 8, SUB_BOOT = 16, SUB_TOPO = 32,
   SUB_TRACE = 64, SUB_TUNE = 128, SUB_SHMEM = 256, SUB_ALL = ~0u
 };
+const char* baseName(const char* path);  // file name without directories (messages never carry build paths)
 int logLevel();
 unsigned logSubsys();
 void logMsg(LogLevel lvl, unsigned subsys, const char* file, int line, const char* fmt, ...)
@@ -59,7 +60,7 @@ const char* lastError();
   do {                                                                                     \
     cudaError_t e__ = (call);                                                              \
     if (e__ != cudaSuccess) {                                                              \
-      ::b200::setLastError("%s:%d CUDA error '%s' from %s", __FILE__, __LINE__,            \
+      ::b200::setLastError("%s:%d CUDA error '%s' from %s", ::b200::baseName(__FILE__), __LINE__,            \
                            cudaGetErrorString(e__), #call);                                \
       BWARN("CUDA error '%s' from %s", cudaGetErrorString(e__), #call);                    \
       return ncclUnhandledCudaError;                                                       \

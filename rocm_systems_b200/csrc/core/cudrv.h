@@ -44,7 +44,7 @@ const char* cuErrStr(CUresult r);
   do {                                                                                     \
     CUresult r__ = (call);                                                                 \
     if (r__ != CUDA_SUCCESS) {                                                             \
-      ::b200::setLastError("%s:%d driver error '%s' from %s", __FILE__, __LINE__,          \
+      ::b200::setLastError("%s:%d driver error '%s' from %s", ::b200::baseName(__FILE__), __LINE__,          \
                            ::b200::cuErrStr(r__), #call);                                  \
       BWARN("driver error '%s' from %s", ::b200::cuErrStr(r__), #call);                    \
       return ncclUnhandledCudaError;                                                       \

@@ -1,0 +1,84 @@
+"""Host-side behaviour of the C API that needs no GPU: result strings, argument checks that answer
+with a result code instead of crashing, group bookkeeping, identifiers, and error text that names
+file and line without a build path."""
+import ctypes
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+SUCCESS, CUDA_ERR, SYSTEM_ERR, INTERNAL, INVALID_ARG, INVALID_USAGE, REMOTE, IN_PROGRESS = range(8)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from rocm_systems_b200 import _lib
+
+    L = _lib.load()
+    L.ncclGetErrorString.restype = ctypes.c_char_p
+    L.ncclGetLastError.restype = ctypes.c_char_p
+    L.ncclGetLastError.argtypes = [ctypes.c_void_p]
+    return L
+
+
+def test_result_strings(lib):
+    texts = [lib.ncclGetErrorString(i).decode() for i in range(9)]
+    assert texts[SUCCESS] == "no error" and "invalid argument" in texts[INVALID_ARG] and "invalid usage" in texts[INVALID_USAGE]
+    assert "peer" in texts[REMOTE] and "in progress" in texts[IN_PROGRESS] and "unknown" in texts[8]
+    assert len(set(texts)) == 9
+
+
+def test_version_and_unique_ids(lib):
+    v = ctypes.c_int()
+    assert lib.ncclGetVersion(ctypes.byref(v)) == SUCCESS and v.value == 22005
+    assert lib.ncclGetVersion(None) == INVALID_ARG
+    U = lib.ncclGetUniqueId.argtypes[0]._type_
+    a, b = U(), U()
+    assert lib.ncclGetUniqueId(ctypes.byref(a)) == SUCCESS and lib.ncclGetUniqueId(ctypes.byref(b)) == SUCCESS
+    ra, rb = ctypes.string_at(ctypes.addressof(a), 128), ctypes.string_at(ctypes.addressof(b), 128)
+    assert ra != rb and any(ra) and len(ra) == 128      # every id names its own rendezvous
+    assert lib.ncclGetUniqueId(None) == INVALID_ARG
+
+
+def test_bad_handles_and_arguments_answer_with_codes(lib):
+    vp = ctypes.c_void_p
+    lib.ncclAllReduce.argtypes = [vp, vp, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, vp, vp]
+    lib.ncclSend.argtypes = [vp, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, vp, vp]
+    lib.ncclCommCount.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
+    lib.ncclCommDestroy.argtypes = [vp]
+    n = ctypes.c_int()
+    junk = (ctypes.c_char * 4096)()                      # readable memory that is not a communicator
+    assert lib.ncclAllReduce(None, None, 4, 7, 0, None, None) == INVALID_ARG
+    assert lib.ncclSend(None, 4, 7, 0, None, None) == INVALID_ARG
+    assert lib.ncclCommCount(None, ctypes.byref(n)) == INVALID_ARG
+    assert lib.ncclCommCount(ctypes.addressof(junk), ctypes.byref(n)) == INVALID_ARG
+    assert b"invalid communicator handle" in lib.ncclGetLastError(None)
+    assert lib.ncclCommDestroy(None) == SUCCESS          # like free(NULL)
+
+
+def test_group_bookkeeping(lib):
+    assert lib.ncclGroupEnd() == INVALID_USAGE           # nothing open
+    assert lib.ncclGroupStart() == SUCCESS and lib.ncclGroupStart() == SUCCESS      # groups nest
+    assert lib.ncclGroupEnd() == SUCCESS and lib.ncclGroupEnd() == SUCCESS
+    assert lib.ncclGroupEnd() == INVALID_USAGE
+
+
+def test_init_argument_checks_and_error_text(lib):
+    U = lib.ncclGetUniqueId.argtypes[0]._type_
+    u = U()
+    lib.ncclGetUniqueId(ctypes.byref(u))
+    comm = ctypes.c_void_p()
+    assert lib.ncclCommInitRank(ctypes.byref(comm), 0, u, 0) == INVALID_ARG
+    assert lib.ncclCommInitRank(ctypes.byref(comm), 9, u, 0) == INVALID_ARG       # one NVSwitch domain: at most 8
+    assert lib.ncclCommInitRank(ctypes.byref(comm), 2, u, 5) == INVALID_ARG
+    assert lib.ncclCommInitRank(None, 1, u, 0) == INVALID_ARG
+    import torch
+
+    if not torch.cuda.is_available():
+        rc = lib.ncclCommInitRank(ctypes.byref(comm), 1, u, 0)
+        assert rc == CUDA_ERR and not comm.value
+        msg = lib.ncclGetLastError(None).decode()
+        assert msg.startswith("comm.cc:") and "/" not in msg.split(" ")[0] and "cudaGetDevice" in msg
