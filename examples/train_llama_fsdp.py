@@ -1,0 +1,45 @@
+"""Train a small Llama with the FSDP engine on every GPU of the box, checkpoint, and resume.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 examples/train_llama_fsdp.py --steps 20
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from rocm_systems_b200.comm import init_from_env  # noqa: E402
+from rocm_systems_b200.models.llama import LlamaConfig, LlamaTrainer  # noqa: E402
+from rocm_systems_b200.utils import checkpoint, markers  # noqa: E402
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--ckpt", default="ckpt_example")
+    ap.add_argument("--resume", action="store_true")
+    a = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    comm = init_from_env(device=local) if world > 1 else None
+    cfg = LlamaConfig(vocab=8192, hidden=1024, layers=8, heads=16, kv_heads=4, ffn=4096, seq_len=1024)
+    trainer = LlamaTrainer(cfg, comm, torch.device("cuda", local))
+    if a.resume:
+        checkpoint.load_engine(trainer.engine, a.ckpt)  # re-shards when the world size changed
+    g = torch.Generator().manual_seed(1 + (comm.rank if comm else 0))
+    for step in range(a.steps):
+        tok = torch.randint(0, cfg.vocab, (2, cfg.seq_len), generator=g).pin_memory()
+        with markers.range(f"step {step}"):  # shows up in traces taken with tools.prof --marker-trace
+            loss = trainer.step(tok, tok.roll(-1, 1).pin_memory())
+        if (comm is None or comm.rank == 0) and step % 5 == 0:
+            print(f"step {step}: loss {loss:.4f}", flush=True)
+    checkpoint.save_engine(trainer.engine, a.ckpt)
+    if comm is not None:
+        comm.host_barrier()
+        comm.destroy()
+
+
+if __name__ == "__main__":
+    main()

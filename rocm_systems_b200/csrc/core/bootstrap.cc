@@ -213,21 +213,40 @@ ncclResult_t bootCreateRoot(ncclUniqueId* out) {
     ::close(lfd);
     BFAIL(ncclInvalidArgument, "bootstrap: bad address '%s'", addr.c_str());
   }
+  // With COMM_ID every rank calls this and has to end up with the same id and exactly one root:
+  // the id is derived from the string alone, and the rank that gets the port serves the rendezvous
+  // (the others find the address taken, which means the root is already up).
+  const bool shared = !fl.commId.empty();
+  bool haveRoot = true;
   if (::bind(lfd, (sockaddr*)&sa, sizeof(sa)) != 0 || ::listen(lfd, 64) != 0) {
     int e = errno;
     ::close(lfd);
-    BFAIL(ncclSystemError, "bootstrap: bind/listen on %s:%d failed: %s", addr.c_str(), wantPort, strerror(e));
+    lfd = -1;
+    if (!(shared && e == EADDRINUSE)) BFAIL(ncclSystemError, "bootstrap: bind/listen on %s:%d failed: %s", addr.c_str(), wantPort, strerror(e));
+    haveRoot = false;
   }
-  socklen_t sl = sizeof(sa);
-  getsockname(lfd, (sockaddr*)&sa, &sl);
-  std::random_device rd;
   BootId id{};
   id.magic = kBootMagic;
-  id.nonce = ((uint64_t)rd() << 32) ^ rd() ^ ((uint64_t)getpid() << 17) ^ nowNs();
-  id.ip = sa.sin_addr.s_addr;
-  id.port = ntohs(sa.sin_port);
+  if (shared) {
+    uint64_t h = 0xcbf29ce484222325ull;  // FNV-1a of the COMM_ID string: the same nonce on every rank
+    for (char ch : fl.commId) h = (h ^ (unsigned char)ch) * 0x100000001b3ull;
+    id.nonce = h ? h : 1;
+    inet_pton(AF_INET, addr.c_str(), &id.ip);
+    id.port = (uint16_t)wantPort;
+  } else {
+    socklen_t sl = sizeof(sa);
+    getsockname(lfd, (sockaddr*)&sa, &sl);
+    std::random_device rd;
+    id.nonce = ((uint64_t)rd() << 32) ^ rd() ^ ((uint64_t)getpid() << 17) ^ nowNs();
+    id.ip = sa.sin_addr.s_addr;
+    id.port = ntohs(sa.sin_port);
+  }
   static_assert(sizeof(BootId) <= NCCL_UNIQUE_ID_BYTES, "BootId must fit in ncclUniqueId");
   memcpy(out->internal, &id, sizeof(id));
+  if (!haveRoot) {
+    BINFO(SUB_BOOT, "bootstrap root for COMM_ID %s is served by another process", fl.commId.c_str());
+    return ncclSuccess;
+  }
   std::thread(rootLoop, lfd, id.nonce, fl.bootTimeoutMs).detach();
   BINFO(SUB_BOOT, "bootstrap root listening on %s:%d nonce %016lx", addr.c_str(), (int)id.port,
         (unsigned long)id.nonce);

@@ -130,3 +130,51 @@ def test_silent_rank_times_out_cleanly():
     out = _run(2, "silent", env=env)
     assert time.time() - t0 < 30
     assert out[0][0] == "rc" and out[0][1] in (2, 6)  # system (timeout) or remote error
+
+
+def _comm_id_worker(rank, n, comm_id, q):
+    os.environ["B200COLL_COMM_ID"] = comm_id
+    lib = _lib.load()
+    lib.b200collRefreshFlags()
+    uid = _lib.UniqueId()
+    if rank:
+        time.sleep(0.05 * rank)                       # not everybody asks at the same instant
+    rc = lib.ncclGetUniqueId(ctypes.byref(uid))       # every rank asks for "the" id itself
+    if rc != 0:
+        q.put((rank, "id", rc))
+        return
+    h = ctypes.c_void_p()
+    rc = lib.b200collBootCreate(ctypes.byref(uid), rank, n, ctypes.byref(h))
+    if rc != 0:
+        q.put((rank, "init", rc))
+        return
+    send = (ctypes.c_int * 1)(100 + rank)
+    recv = (ctypes.c_int * n)()
+    rc = lib.b200collBootAllGather(h, send, recv, 4)
+    assert lib.b200collBootBarrier(h) == 0
+    q.put((rank, "ok", (ctypes.string_at(ctypes.addressof(uid), 128).hex(), list(recv), rc)))
+    lib.b200collBootClose(h, 1)
+
+
+def test_comm_id_gives_every_rank_the_same_id_without_an_exchange():
+    """With COMM_ID=ip:port nobody has to ship the unique id around: every rank derives the same id
+    from the string, and whichever rank gets the port serves the rendezvous."""
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    n = 3
+    procs = [ctx.Process(target=_comm_id_worker, args=(r, n, f"127.0.0.1:{port}", q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert all(r[1] == "ok" for r in res), res
+    ids = {r[2][0] for r in res}
+    assert len(ids) == 1
+    assert all(r[2][1] == [100, 101, 102] and r[2][2] == 0 for r in res)

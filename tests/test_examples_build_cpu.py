@@ -1,0 +1,30 @@
+"""The public headers have to be usable the way a user would use them: nccl.h from plain C, the
+device-initiated API from a user's own CUDA kernel. The examples are compiled (not run) here."""
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+INC = ROOT / "rocm_systems_b200" / "csrc" / "include"
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc")
+def test_c_example_compiles_as_c(tmp_path):
+    p = subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-c", str(ROOT / "examples" / "allreduce.c"), f"-I{INC}", "-I/usr/local/cuda/include",
+                        "-o", str(tmp_path / "a.o")], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+
+
+@pytest.mark.skipif(not Path("/usr/local/cuda/bin/nvcc").exists(), reason="needs nvcc")
+def test_device_api_example_compiles_for_sm100a(tmp_path):
+    p = subprocess.run(["/usr/local/cuda/bin/nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-c", str(ROOT / "examples" / "shmem_ring.cu"),
+                        f"-I{INC}", "-o", str(tmp_path / "s.o")], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+
+
+def test_python_example_parses():
+    import ast
+
+    ast.parse((ROOT / "examples" / "train_llama_fsdp.py").read_text())
