@@ -42,6 +42,10 @@ RULES = [
     ("rocm_systems_b200/*", ["tests"], ["tests"], False),
     ("tests/*", ["{path}"], ["{path}"], False),
     ("bench.py", [], ["tests/test_gpu_fused_multi.py"], False),
+    ("examples/*", ["tests/test_examples_build_cpu.py"], [], False),
+    ("ci/*", ["tests/test_ci_select.py"], [], False),
+    (".github/*", [], [], False),
+    ("docs/*", [], [], False),
     ("*.md", [], [], False),
     ("profiles/*", [], [], False),
 ]
