@@ -20,6 +20,7 @@ from rocm_systems_b200 import _lib  # noqa: E402
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 
 FAILS = []
+SKEW = {"ms": 0.0, "rng": None}  # --skew-ms: a random host-side pause per rank between operations
 
 
 def gen(rank, n, dtype, seed, lo=-4, hi=5, device="cuda"):
@@ -46,6 +47,8 @@ def reduce_ref(parts, op):
 
 
 def check(name, got, want):
+    if SKEW["ms"] > 0:  # ranks then enter the next operation at different times (protocol races show as wrong data)
+        time.sleep(SKEW["rng"].uniform(0.0, SKEW["ms"]) / 1e3)
     w = want.to(torch.float32).to(got.dtype) if got.dtype.is_floating_point else want.to(got.dtype)
     a = got.view(torch.uint8) if got.element_size() == 1 else got
     b = w.view(torch.uint8) if w.element_size() == 1 else w
@@ -68,8 +71,13 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--skew-ms", type=float, default=0.0, help="random pause per rank between operations, up to this many ms")
     args = ap.parse_args()
     comm = init_from_env()
+    if args.skew_ms > 0:
+        import random
+
+        SKEW["ms"], SKEW["rng"] = args.skew_ms, random.Random(977 * comm.rank + 1)
     lib = _lib.load()
     rank, n = comm.rank, comm.nranks
     dev = comm.device
