@@ -214,3 +214,46 @@ def test_back_to_back_launches_need_no_trailing_barrier():
     a_tail = [x for x in accesses(ga, 0) if x[3] == last_epoch(ga)]
     b_head_wrong = [y for y in accesses(gb, (ga.chunks() - 1) & 1) if y[3] == 0]
     assert any(x[0] != y[0] and x[4] == y[4] and x[5] == y[5] and x[6] < y[7] and y[6] < x[7] and (x[8] or y[8]) for x in a_tail for y in b_head_wrong)
+
+
+# ---- the pipelined all-gather (kStagedCopy): staging holds the rank's own contribution only ----
+def ag_part(total, cap, lanes, k, b, by_capacity=True):
+    cb = min(cap, total - k * cap)
+    units = ceil_div(cb, U)
+    per = ceil_div(ceil_div(cap, U), lanes) if by_capacity else (ceil_div(units, lanes) if units else 0)
+    lo = min(b * per, units)
+    hi = min(lo + per, units)
+    return lo * U, hi * U
+
+
+def ag_accesses(n, lanes, total, cap, by_capacity=True):
+    out = []
+    K = ceil_div(total, cap)
+    for r, b in itertools.product(range(n), range(lanes)):
+        lo, hi = ag_part(total, cap, lanes, 0, b, by_capacity)
+        if lo < hi:
+            out.append((r, b, "all", 0, r, 0, lo, hi, True))                    # prologue: stage chunk 0
+        for k in range(K):
+            epoch, more = k + 1, k + 1 < K
+            lo, hi = ag_part(total, cap, lanes, k, b, by_capacity)
+            if lo < hi:
+                for p in range(n):
+                    if p != r:
+                        out.append((r, b, "pull", epoch, p, k & 1, lo, hi, False))   # read the peers' staging
+            if more:
+                lo, hi = ag_part(total, cap, lanes, k + 1, b, by_capacity)
+                if lo < hi:
+                    out.append((r, b, "copy", epoch, r, (k + 1) & 1, lo, hi, True))  # stage the next chunk meanwhile
+    return out
+
+
+def test_pipelined_all_gather_is_race_free_and_the_old_split_is_not():
+    rng = random.Random(3)
+    for _ in range(60):
+        n, lanes = rng.choice([2, 3, 4, 8]), rng.randint(1, 6)
+        cap = U * rng.randint(4, 200)
+        total = rng.randint(1, 6 * cap)
+        assert races(ag_accesses(n, lanes, total, cap)) == [], (n, lanes, total, cap)
+    # ranges that follow the chunk's own size: a short last chunk staged by one lane overlaps what a
+    # remote rank's other lane still pulls of the chunk before last
+    assert races(ag_accesses(2, 4, 5 * 4096 + 1520, 4096, by_capacity=False))
