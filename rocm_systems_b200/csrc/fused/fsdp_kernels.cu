@@ -19,6 +19,7 @@ struct RsCastArgs {
   size_t count;
   float scale;
   int stageHalf;
+  size_t chunkBytes;          // bytes of one rank's slice per chunk (equalised by the host); 0 = a whole staging share
 };
 
 __device__ __forceinline__ void accum8(const uint4& v, float (&acc)[8], bool first) {
@@ -63,15 +64,21 @@ __global__ void __launch_bounds__(kReduceThreads) kReduceScatterCast(const __gri
   const int n = c.nranks, rank = c.rank, B = gridDim.x, b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   uint32_t epoch = c.local->barEpoch[b];
   const size_t total = a.count * 2;  // bytes of one rank's slice
-  const size_t cap = (c.stageBytes / n) & ~(size_t)15;
+  const size_t fullCap = (c.stageBytes / n) & ~(size_t)15;
+  const size_t cap = (a.chunkBytes && a.chunkBytes < fullCap) ? a.chunkBytes : fullCap;
+  // A lane's range follows the chunk capacity, not how full a chunk is: what this lane stages into
+  // a half can then never overlap what another lane of a peer (which this lane does not
+  // synchronise with) still reads there from two chunks earlier.
+  const size_t perLane = (((cap + 15) >> 4) + B - 1) / B;
   const char* send = (const char*)a.send;
   int half = a.stageHalf;
   for (size_t off = 0; off < total; off += cap, half ^= 1) {
     const size_t cb = total - off < cap ? total - off : cap;
     const size_t U = (cb + 15) >> 4;
     const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
-    size_t lo, hi;
-    splitUnits(U, B, b, lo, hi);
+    size_t lo = (size_t)b * perLane, hi;
+    if (lo > U) lo = U;
+    hi = lo + perLane < U ? lo + perLane : U;
     const size_t bytes = lo < hi ? (((hi << 4) < cb ? (hi << 4) : cb) - (lo << 4)) : 0;
     for (int i = 0; i < n; i++) {
       const int s = (rank + i) % n;
@@ -125,9 +132,15 @@ extern "C" ncclResult_t b200collReduceScatterCast(ncclComm_t comm, const void* s
     kCastScaleSolo<<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale);
     e = cudaGetLastError();
   } else {
-    RsCastArgs a{(const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale, (int)(c->stageParity & 1)};
-    const size_t cap = (c->dev.stageBytes / c->nranks) & ~(size_t)15;
-    c->stageParity += (uint32_t)((recvcount * 2 + cap - 1) / cap);
+    // Equal chunks: the kernel lays data out by the chunk capacity alone, so a short last chunk
+    // would leave most lanes idle.
+    const size_t bytes = recvcount * 2;
+    const size_t capMax = (c->dev.stageBytes / c->nranks) & ~(size_t)15;
+    const size_t k = (bytes + capMax - 1) / capMax;
+    size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;
+    if (cap > capMax) cap = capMax;
+    RsCastArgs a{(const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale, (int)(c->stageParity & 1), cap};
+    c->stageParity += (uint32_t)((bytes + cap - 1) / cap);
     DevComm dc = c->dev;
     dc.opSeq = ++c->opSeq;
     dc.stamp = stamp;

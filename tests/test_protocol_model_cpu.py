@@ -257,3 +257,35 @@ def test_pipelined_all_gather_is_race_free_and_the_old_split_is_not():
     # ranges that follow the chunk's own size: a short last chunk staged by one lane overlaps what a
     # remote rank's other lane still pulls of the chunk before last
     assert races(ag_accesses(2, 4, 5 * 4096 + 1520, 4096, by_capacity=False))
+
+
+# ---- the fused reduce-scatter + cast of the FSDP path: same staging, no software pipeline ----
+def rs_cast_accesses(g: Geometry):
+    """copy-in(k) | barrier | reduce(k) | copy-in(k+1) | barrier | ... : one barrier per chunk, the next
+    copy-in follows the reduce without one."""
+    out = []
+    for r, b in itertools.product(range(g.n), range(g.B)):
+        epoch = 0
+        for k in range(g.chunks()):
+            for s in range(g.n):
+                lo, hi = g.lane_range(k, s, b)
+                if lo < hi:
+                    out.append((r, b, "all", epoch, r, k & 1, lo, hi, True))
+            epoch += 1                                                     # the barrier
+            lo, hi = g.lane_range(k, r, b)
+            if lo < hi:
+                for p in range(g.n):
+                    out.append((r, b, "all", epoch, p, k & 1, lo, hi, False))
+    return out
+
+
+def test_fused_reduce_scatter_cast_geometry():
+    rng = random.Random(5)
+    for _ in range(60):
+        n, lanes = rng.choice([2, 4, 8]), rng.randint(1, 6)
+        cap = U * rng.randint(2, 200)
+        g = Geometry(n, lanes, rng.randint(1, 7 * cap), cap, "rs", by_capacity=True)
+        assert races(rs_cast_accesses(g)) == [], (n, lanes, g.total, cap)
+    # lane ranges cut from each chunk's own size: the short last chunk's copy-in crosses into ranges
+    # that another lane of a peer may still be reading from two chunks earlier
+    assert races(rs_cast_accesses(Geometry(2, 4, 6 * 4096 + 1520, 4096, "rs", by_capacity=False)))
