@@ -99,6 +99,7 @@ def main() -> None:
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sym-shards", action="store_true", help="keep the bf16 parameter shards in symmetric memory (zero-copy all-gather); experimental")
     ap.add_argument("--collectives", default="b200coll", choices=["b200coll", "nccl"],
                     help="nccl: the same trainer with stock NCCL collectives (control run; the metric name gets a _nccl_collectives suffix)")
     args = ap.parse_args()
@@ -136,7 +137,7 @@ def main() -> None:
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny(512)
     if args.seq:
         cfg.seq_len = args.seq
-    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl")
+    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=args.sym_shards)
     S, B = cfg.seq_len, 1
     nbatches = 4
     g = torch.Generator().manual_seed(1234 + rank)

@@ -117,7 +117,8 @@ class FlatUnit:
 class FSDPEngine:
     """Owns the units, the communication stream and the schedule primitives."""
 
-    def __init__(self, comm, units: List[FlatUnit], opt: AdamWConfig, reshard_after_forward: bool = True, fused_rs: bool = True):
+    def __init__(self, comm, units: List[FlatUnit], opt: AdamWConfig, reshard_after_forward: bool = True, fused_rs: bool = True,
+                 sym_shards: bool = False):
         self.comm, self.units, self.opt = comm, units, opt
         self.world = comm.nranks if comm is not None else 1
         self.rank = comm.rank if comm is not None else 0
@@ -126,6 +127,27 @@ class FSDPEngine:
         self.step_count = 0
         self.fused_rs = fused_rs
         self._pending: List[torch.cuda.Event] = []
+        self._sym_shards = None
+        if sym_shards and self.world > 1 and hasattr(comm, "sym_alloc"):
+            self._place_shards_in_symmetric_memory()
+
+    def _place_shards_in_symmetric_memory(self) -> None:
+        """Move every unit's bf16 shard into one symmetric allocation. The parameter all-gather then
+        reads the peers' shards in place (the zero-copy path of the collective engine) instead of
+        staging them; AdamW keeps writing the shard where it now lives. Opt-in: it changes where
+        16 GB / N of memory comes from, not what is computed."""
+        align = 256
+        offs, total = [], 0
+        for u in self.units:
+            offs.append(total)
+            total += (u.shard_numel * 2 + align - 1) // align * align
+        self._sym_shards = self.comm.sym_alloc(total)
+        for u, o in zip(self.units, offs):
+            t = self._sym_shards.tensor((u.shard_numel,), torch.bfloat16, offset_bytes=o)
+            t.copy_(u.shard)
+            u.shard = t
+        torch.cuda.synchronize()
+        self.comm.host_barrier()  # every rank's shards are in place before anyone gathers
 
     # ---- parameters -----------------------------------------------------------------------------
     def prefetch(self, unit: FlatUnit) -> None:
