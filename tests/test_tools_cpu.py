@@ -377,3 +377,28 @@ ts = [threading.Thread(target=work) for _ in range(16)]
 [t.start() for t in ts]; [t.join() for t in ts]
 """, {"B200COLL_TOOL_LIBRARIES": f"{tool}:{tool}", "B200COLL_SAMPLE_TOOL_OUTPUT": str(out)})
     assert "ncclGetVersion calls=800" in out.read_text()
+
+
+def test_output_validators(tmp_path):
+    from rocm_systems_b200.tools import tracedb, validate
+
+    (tmp_path / "t.100_kernel_trace.csv").write_text(KERNEL_CSV)
+    (tmp_path / "t.rank0.csv").write_text(COLL_CSV)
+    (tmp_path / "t.markers.100.csv").write_text(MARK_CSV)
+    dbp = str(tmp_path / "t.db")
+    with tracedb.TraceDB(dbp) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        db.to_perfetto(str(tmp_path / "t.json"))
+    assert validate.check_perfetto(str(tmp_path / "t.json"), categories=["kernel", "collective", "MARKER_API"], names=["gemmKernel"], min_slices=8) == []
+    errs = validate.check_perfetto(str(tmp_path / "t.json"), categories=["memcpy"], counters=["gpu_power"], min_slices=100)
+    assert len(errs) == 3
+    assert validate.check_db(dbp, ["kernel_dispatch:3", "collective:2", "top_kernels:2"]) == []
+    assert validate.check_db(dbp, ["kernel_dispatch:4", "nope"]) == ["kernel_dispatch: 3 rows, expected at least 4", "no table or view 'nope'"]
+    assert validate.check_csv(str(tmp_path / "t.rank0.csv"), ["Device_Us", "AlgBw_GBps"], ["ncclAllReduce"]) == []
+    assert validate.check_csv(str(tmp_path / "t.rank0.csv"), ["Nope"], ["ncclBroadcast"], min_rows=5) != []
+    # partially overlapping slices on one track are flagged
+    bad = {"traceEvents": [{"ph": "X", "pid": 1, "tid": "a", "name": "x", "ts": 0, "dur": 10}, {"ph": "X", "pid": 1, "tid": "a", "name": "y", "ts": 5, "dur": 10}]}
+    (tmp_path / "bad.json").write_text(json.dumps(bad))
+    assert any("overlap" in e for e in validate.check_perfetto(str(tmp_path / "bad.json")))
+    assert validate.main(["db", dbp, "--table", "region:1"]) == 0
