@@ -105,6 +105,63 @@ __global__ void __launch_bounds__(kReduceThreads) kReduceScatterCast(const __gri
   stampEnd(c);
 }
 
+// Zero-copy variant for gradient buffers that live in symmetric memory (the same offset of a
+// b200collSymAlloc window on every rank): nothing is staged, every rank reads its slice straight
+// out of the peers' buffers. One barrier before (every rank has finished writing its gradients:
+// each launches this kernel behind its own backward pass) and one after (a rank's buffer may be
+// overwritten by its next backward pass only once no peer reads it any more).
+struct RsCastDirectArgs {
+  const char* sendPeer[kMaxRanks];  // every rank's gradient buffer as mapped here
+  float* recv;
+  size_t count;                     // elements of one rank's slice; count * 2 is a multiple of 16
+  float scale;
+};
+
+template <int MAXR, int UN>
+__device__ __forceinline__ void reduceUnitsDirect(const RsCastDirectArgs& a, int n, size_t sliceOff, size_t u0, int nt) {
+  uint4 v[UN][MAXR];
+#pragma unroll
+  for (int j = 0; j < UN; j++)
+#pragma unroll
+    for (int p = 0; p < MAXR; p++)
+      if (p < n) v[j][p] = ldStream16(a.sendPeer[p] + sliceOff + ((u0 + (size_t)j * nt) << 4));
+#pragma unroll
+  for (int j = 0; j < UN; j++) {
+    float acc[8];
+#pragma unroll
+    for (int p = 0; p < MAXR; p++)
+      if (p < n) accum8(v[j][p], acc, p == 0);
+    float4* o = reinterpret_cast<float4*>(a.recv + (u0 + (size_t)j * nt) * 8);  // recv is 16-byte aligned, whole units only
+    o[0] = make_float4(acc[0] * a.scale, acc[1] * a.scale, acc[2] * a.scale, acc[3] * a.scale);
+    o[1] = make_float4(acc[4] * a.scale, acc[5] * a.scale, acc[6] * a.scale, acc[7] * a.scale);
+  }
+}
+
+__global__ void __launch_bounds__(kReduceThreads) kReduceScatterCastDirect(const __grid_constant__ DevComm c, const __grid_constant__ RsCastDirectArgs a) {
+  stampBegin(c);
+  const int n = c.nranks, rank = c.rank, B = gridDim.x, b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  uint32_t epoch = c.local->barEpoch[b];
+  const size_t total = a.count * 2;  // bytes of one rank's slice
+  const size_t sliceOff = (size_t)rank * total;
+  size_t lo, hi;
+  splitUnits(total >> 4, B, b, lo, hi);
+  ctaBarrier(c, epoch);
+  size_t u = lo + tid;
+  if (n <= 2) {
+    for (; u + (size_t)3 * nt < hi; u += (size_t)4 * nt) reduceUnitsDirect<2, 4>(a, n, sliceOff, u, nt);
+    for (; u < hi; u += nt) reduceUnitsDirect<2, 1>(a, n, sliceOff, u, nt);
+  } else if (n <= 4) {
+    for (; u + (size_t)nt < hi; u += (size_t)2 * nt) reduceUnitsDirect<4, 2>(a, n, sliceOff, u, nt);
+    for (; u < hi; u += nt) reduceUnitsDirect<4, 1>(a, n, sliceOff, u, nt);
+  } else {
+    for (; u + (size_t)nt < hi; u += (size_t)2 * nt) reduceUnitsDirect<8, 2>(a, n, sliceOff, u, nt);
+    for (; u < hi; u += nt) reduceUnitsDirect<8, 1>(a, n, sliceOff, u, nt);
+  }
+  ctaBarrier(c, epoch);
+  if (tid == 0) c.local->barEpoch[b] = epoch;
+  stampEnd(c);
+}
+
 // n == 1: nothing to exchange, only the cast and the scale.
 __global__ void __launch_bounds__(256) kCastScaleSolo(const __nv_bfloat16* in, float* out, size_t n, float scale) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = __bfloat162float(in[i]) * scale;
@@ -132,21 +189,44 @@ extern "C" ncclResult_t b200collReduceScatterCast(ncclComm_t comm, const void* s
     kCastScaleSolo<<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale);
     e = cudaGetLastError();
   } else {
+    const size_t bytes = recvcount * 2;
+    DevComm dc = c->dev;
+    size_t moved = recvcount * 2 * c->nranks;
+    int ctas = (int)std::min<size_t>((moved + (64u << 10) - 1) / (64u << 10), (size_t)c->maxCtas);
+    ctas = std::min(std::max(ctas, c->minCtas) * 2, kMaxCtas);
+    // Gradient buffer inside a symmetric window, whole 16-byte units, aligned ends: read the peers in place.
+    size_t woff = 0;
+    Window* win = nullptr;
+    if ((bytes & 15) == 0 && (((uintptr_t)sendBf16 | (uintptr_t)recvF32) & 15) == 0) {
+      std::lock_guard<std::mutex> lk(c->mu);
+      win = c->findWindow(sendBf16, bytes * c->nranks, &woff);
+    }
+    if (win) {
+      RsCastDirectArgs da{};
+      for (int p = 0; p < c->nranks; p++) da.sendPeer[p] = win->seg.peer[p] + woff;
+      da.recv = recvF32;
+      da.count = recvcount;
+      da.scale = scale;
+      dc.opSeq = ++c->opSeq;
+      dc.stamp = stamp;
+      if (tr) tr->setAlgo(ALGO_P2P, ctas);
+      kReduceScatterCastDirect<<<ctas, kReduceThreads, 0, stream>>>(dc, da);
+      e = cudaGetLastError();
+      if (tr) tr->end(e == cudaSuccess);
+      if (prev != c->cudaDev && prev >= 0) cudaSetDevice(prev);
+      if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collReduceScatterCast launch failed: %s", cudaGetErrorString(e));
+      return ncclSuccess;
+    }
     // Equal chunks: the kernel lays data out by the chunk capacity alone, so a short last chunk
     // would leave most lanes idle.
-    const size_t bytes = recvcount * 2;
     const size_t capMax = (c->dev.stageBytes / c->nranks) & ~(size_t)15;
     const size_t k = (bytes + capMax - 1) / capMax;
     size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;
     if (cap > capMax) cap = capMax;
     RsCastArgs a{(const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale, (int)(c->stageParity & 1), cap};
     c->stageParity += (uint32_t)((bytes + cap - 1) / cap);
-    DevComm dc = c->dev;
     dc.opSeq = ++c->opSeq;
     dc.stamp = stamp;
-    size_t moved = recvcount * 2 * c->nranks;
-    int ctas = (int)std::min<size_t>((moved + (64u << 10) - 1) / (64u << 10), (size_t)c->maxCtas);
-    ctas = std::min(std::max(ctas, c->minCtas) * 2, kMaxCtas);
     if (tr) tr->setAlgo(ALGO_P2P, ctas);
     kReduceScatterCast<<<ctas, kReduceThreads, 0, stream>>>(dc, a);
     e = cudaGetLastError();

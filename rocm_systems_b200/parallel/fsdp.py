@@ -128,6 +128,7 @@ class FSDPEngine:
         self.fused_rs = fused_rs
         self._pending: List[torch.cuda.Event] = []
         self._sym_shards = None
+        self._grad_slots = None
         if sym_shards and self.world > 1 and hasattr(comm, "sym_alloc"):
             self._place_shards_in_symmetric_memory()
 
@@ -146,6 +147,16 @@ class FSDPEngine:
             t = self._sym_shards.tensor((u.shard_numel,), torch.bfloat16, offset_bytes=o)
             t.copy_(u.shard)
             u.shard = t
+        # Two symmetric gradient buffers, used alternately by consecutive units: the fused
+        # reduce-scatter then reads the peers' gradients in place. A buffer is handed out again only
+        # after the reduce-scatter that read it has finished (its kernel ends with a barrier, so by
+        # then no peer reads this rank's copy either).
+        slot_elems = max(u.padded for u in self.units)
+        slot_bytes = (slot_elems * 2 + align - 1) // align * align
+        self._sym_grads = self.comm.sym_alloc(2 * slot_bytes)
+        self._grad_slots = [self._sym_grads.tensor((slot_elems,), torch.bfloat16, offset_bytes=i * slot_bytes) for i in range(2)]
+        self._grad_slot_done = [None, None]
+        self._grad_slot_next = 0
         torch.cuda.synchronize()
         self.comm.host_barrier()  # every rank's shards are in place before anyone gathers
 
@@ -182,7 +193,16 @@ class FSDPEngine:
     def alloc_grad(self, unit: FlatUnit) -> None:
         """The flat gradient buffer of ``unit``. Every parameter's gradient is written (not
         accumulated) into its view by the backward pass, so only the gaps need zeroing."""
-        unit.full_grad = torch.empty(unit.padded, dtype=torch.bfloat16, device=unit.device)
+        if self._grad_slots is not None:
+            slot = self._grad_slot_next
+            self._grad_slot_next ^= 1
+            if self._grad_slot_done[slot] is not None:
+                torch.cuda.current_stream().wait_event(self._grad_slot_done[slot])
+            unit.full_grad = self._grad_slots[slot][:unit.padded]
+            unit.grad_slot = slot
+        else:
+            unit.full_grad = torch.empty(unit.padded, dtype=torch.bfloat16, device=unit.device)
+            unit.grad_slot = None
         for a, b in unit.gaps:
             unit.full_grad[a:b].zero_()
 
@@ -213,6 +233,10 @@ class FSDPEngine:
                 tmp = torch.empty(unit.shard_numel, dtype=torch.bfloat16, device=unit.device)
                 self.comm.reduce_scatter(unit.full_grad, tmp, op="avg", stream=self.comm_stream)
                 ops.cast_scale_(tmp, gshard, 1.0)
+            if fp32_full_grad is None and getattr(unit, "grad_slot", None) is not None:
+                read = torch.cuda.Event()
+                read.record(self.comm_stream)  # the reduce-scatter is behind us on this stream: the buffer may be reused after it
+                self._grad_slot_done[unit.grad_slot] = read
             ops.adamw_(unit.master, unit.m, unit.v, gshard, unit.shard, o.lr, o.betas, o.eps, o.weight_decay, self.step_count + 1)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
