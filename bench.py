@@ -27,7 +27,6 @@ import statistics
 import subprocess
 import sys
 import threading
-import time
 
 METRIC = "llama3_8b_fsdp_train_tokens_per_sec"
 

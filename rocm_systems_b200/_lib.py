@@ -6,7 +6,6 @@ another implementation. If the shared object is missing the import fails with th
 from __future__ import annotations
 
 import ctypes
-import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent

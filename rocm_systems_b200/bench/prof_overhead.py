@@ -10,7 +10,6 @@ workload under tracing configurations and stores the timings in SQLite).
 from __future__ import annotations
 
 import argparse
-import json
 import shlex
 import sqlite3
 import statistics

@@ -7,7 +7,6 @@ library raises at import of :mod:`rocm_systems_b200._lib`.
 from __future__ import annotations
 
 import ctypes
-import math
 
 import torch
 

@@ -5,7 +5,6 @@ collectives behind a ``c10d::Backend``, csrc/torch/pg_b200.cpp) and offers an
 from __future__ import annotations
 
 import datetime
-import os
 from typing import Optional
 
 import torch

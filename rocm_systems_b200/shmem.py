@@ -14,7 +14,7 @@ OpenSHMEM names the device header uses.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 

@@ -32,7 +32,6 @@ import re
 import socket
 import sqlite3
 import sys
-from pathlib import Path
 from typing import Iterable, List, Optional, Sequence
 
 SCHEMA = """

@@ -1,6 +1,5 @@
 """The change-to-tests selection used by CI."""
 import importlib.util
-import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent

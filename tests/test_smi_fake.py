@@ -4,7 +4,6 @@ trees the same way (rocm-smi-lib/src/rocm_smi_main.cc:522-527)."""
 import os
 import subprocess
 import sys
-import time
 from pathlib import Path
 
 import pytest

@@ -2,7 +2,6 @@
 against the unfused composition, plus device timings of both."""
 import argparse
 import json
-import os
 import sys
 from pathlib import Path
 
