@@ -18,7 +18,8 @@ def main():
     dev = comm.device
     cfg = LlamaConfig.tiny(64)
     fused = os.environ.get("FSDP_FUSED_RS", "1") == "1"
-    sharded = LlamaTrainer(cfg, comm, dev, seed=3, fused_rs=fused)
+    sym = os.environ.get("FSDP_SYM_SHARDS", "0") == "1"   # shards and gradient buffers in symmetric memory (zero-copy collectives)
+    sharded = LlamaTrainer(cfg, comm, dev, seed=3, fused_rs=fused, sym_shards=sym)
     single = LlamaTrainer(cfg, None, dev, seed=3)
     g = torch.Generator().manual_seed(5)
     steps = 6
@@ -50,7 +51,7 @@ def main():
     if bad:
         print(f"[rank {rank}] FSDP MISMATCH: {bad}", flush=True)
     elif rank == 0:
-        print(f"fsdp_worker OK on {world} ranks (max weight diff {diff:.2e}, fused_rs={fused})", flush=True)
+        print(f"fsdp_worker OK on {world} ranks (max weight diff {diff:.2e}, fused_rs={fused}, sym_shards={sym})", flush=True)
     torch.cuda.synchronize()
     comm.destroy()
     sys.exit(1 if any(f[0] for f in flags) else 0)
