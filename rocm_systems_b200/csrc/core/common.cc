@@ -75,6 +75,16 @@ static void load(Flags& f) {
     else if (s == "NONE" || s == "VERSION") f.debugLevel = LOG_NONE;
   }
   f.debugSubsys = parseSubsys(envOf("DEBUG_SUBSYS"));
+  if (const char* v = envOf("DEBUG_FILE")) {
+    // %h -> host name, %p -> process id, so every rank can write its own file
+    char host[64] = "";
+    gethostname(host, sizeof(host) - 1);
+    for (const char* c = v; *c; ++c) {
+      if (c[0] == '%' && c[1] == 'h') { f.debugFile += host; ++c; }
+      else if (c[0] == '%' && c[1] == 'p') { f.debugFile += std::to_string((long)getpid()); ++c; }
+      else f.debugFile += *c;
+    }
+  }
   f.nvlsEnable = parseInt(envOf("NVLS_ENABLE"), f.nvlsEnable);
   if (const char* v = envOf("ALGO")) {
     f.algo = v;
@@ -162,8 +172,25 @@ void logMsg(LogLevel lvl, unsigned subsys, const char* file, int line, const cha
   va_start(ap, fmt);
   vsnprintf(buf + n, sizeof(buf) - n, fmt, ap);
   va_end(ap);
-  fprintf(lvl == LOG_WARN ? stderr : stdout, "%s\n", buf);
-  fflush(lvl == LOG_WARN ? stderr : stdout);
+  FILE* out = lvl == LOG_WARN ? stderr : stdout;
+  const std::string& path = Flags::get().debugFile;
+  if (!path.empty()) {
+    static std::mutex fileMu;
+    static FILE* file = nullptr;
+    static std::string opened;
+    std::lock_guard<std::mutex> lk(fileMu);
+    if (!file || opened != path) {  // the path can change when tests re-read the environment
+      if (file) fclose(file);
+      file = fopen(path.c_str(), "a");
+      opened = path;
+    }
+    if (file) out = file;
+    fprintf(out, "%s\n", buf);
+    fflush(out);
+    return;
+  }
+  fprintf(out, "%s\n", buf);
+  fflush(out);
 }
 
 static thread_local char tlsLastError[1024] = "";
@@ -215,6 +242,7 @@ struct SettingDoc {
 };
 const SettingDoc kSettings[] = {
     {"DEBUG", true, "WARN", "log level: NONE, WARN, INFO, TRACE"},
+    {"DEBUG_FILE", true, "", "write log lines to this file instead of stdout / stderr; %h is the host name, %p the process id"},
     {"DEBUG_SUBSYS", true, "ALL", "comma list of INIT,COLL,P2P,MEM,BOOTSTRAP,TOPO,TRACE,TUNING,SHMEM for INFO/TRACE lines"},
     {"NVLS_ENABLE", true, "1", "0: never use in-switch reduction / multicast; 1: when the box supports it"},
     {"ALGO", true, "", "force an algorithm: ll, p2p or nvls (a forced choice that cannot serve a call falls back)"},
@@ -240,6 +268,7 @@ const SettingDoc kSettings[] = {
 std::string currentValue(const Flags& f, const std::string& n) {
   auto num = [](long long v) { return std::to_string(v); };
   if (n == "DEBUG") return f.debugLevel == LOG_NONE ? "NONE" : f.debugLevel == LOG_WARN ? "WARN" : f.debugLevel == LOG_INFO ? "INFO" : "TRACE";
+  if (n == "DEBUG_FILE") return f.debugFile;
   if (n == "DEBUG_SUBSYS") return f.debugSubsys == SUB_ALL ? "ALL" : num(f.debugSubsys);
   if (n == "NVLS_ENABLE") return num(f.nvlsEnable);
   if (n == "ALGO") return f.algo;

@@ -81,6 +81,7 @@ const char* lastError();
 struct Flags {
   int debugLevel = LOG_WARN;
   unsigned debugSubsys = SUB_ALL;
+  std::string debugFile;         // DEBUG_FILE: log lines go to this file instead of stdout/stderr (%h host, %p pid)
   int nvlsEnable = 1;            // NVLS_ENABLE: 0 never, 1 when the box supports multicast
   std::string algo;              // ALGO: "", "ll", "p2p", "nvls"
   int minCtas = 0, maxCtas = 0;  // MIN_CTAS / MAX_CTAS (0: per-collective default)

@@ -82,3 +82,23 @@ def test_init_argument_checks_and_error_text(lib):
         assert rc == CUDA_ERR and not comm.value
         msg = lib.ncclGetLastError(None).decode()
         assert msg.startswith("comm.cc:") and "/" not in msg.split(" ")[0] and "cudaGetDevice" in msg
+
+
+def test_debug_file_receives_the_log_lines(tmp_path):
+    import os
+    import subprocess
+
+    code = """
+import ctypes
+from rocm_systems_b200 import _lib
+lib = _lib.load()
+lib.ncclCommCount.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+n = ctypes.c_int()
+assert lib.ncclCommCount(None, ctypes.byref(n)) == 4
+"""
+    e = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_DEBUG_FILE=str(tmp_path / "log.%p.txt"))
+    p = subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr
+    files = list(tmp_path.glob("log.*.txt"))
+    assert len(files) == 1 and files[0].name != "log.%p.txt"
+    assert "invalid communicator handle" in files[0].read_text() and "invalid communicator handle" not in p.stderr
