@@ -35,7 +35,7 @@ DEFAULT_FIELDS = ["sm_clock", "mem_clock", "power", "temp", "mem_used", "gpu_uti
 PROM = {
     "sm_clock": ("b200_sm_clock_mhz", "SM clock in MHz", 1.0),
     "mem_clock": ("b200_memory_clock_mhz", "memory clock in MHz", 1.0),
-    "power": ("b200_power_watts", "board power draw in watts", 1e-3),
+    "power": ("b200_power_watts", "board power draw in watts", 1.0),
     "temp": ("b200_temperature_celsius", "GPU temperature", 1.0),
     "mem_used": ("b200_memory_used_bytes", "device memory in use", 1.0),
     "gpu_util": ("b200_gpu_utilization_percent", "fraction of time a kernel was running", 1.0),
@@ -164,6 +164,31 @@ class Telemetry:
         if job in self.jobs:
             self.jobs[job]["stop"] = time.time()
 
+    # ---- policies (rdc: rdc_policy_set / rdc_policy_register: a threshold on a field fires a notification) ----
+    def policy_set(self, dev: int, field: str, threshold: float, above: bool = True) -> None:
+        """Record an event whenever ``field`` of ``dev`` crosses ``threshold`` while it is being watched.
+        Events accumulate in ``policy_events()``; nothing is done to the device."""
+        if field not in FIELDS:
+            raise ValueError(f"unknown field {field!r}; known: {sorted(FIELDS)}")
+        if not hasattr(self, "_events"):
+            self._events = []
+            self._events_lock = threading.Lock()
+        names = {v: k for k, v in FIELDS.items()}
+
+        def fire(d, f, value, thr):
+            with self._events_lock:
+                self._events.append({"time": time.time(), "device": d, "field": names.get(f, str(f)), "value": value, "threshold": thr,
+                                     "direction": "above" if above else "below"})
+                del self._events[:-1000]  # keep the last thousand
+
+        self.smi.policy(dev, field, threshold, above, fire)
+
+    def policy_events(self) -> list:
+        if not hasattr(self, "_events"):
+            return []
+        with self._events_lock:
+            return list(self._events)
+
     def job_stats(self, job: str) -> dict:
         out = {"job": job, **self.jobs.get(job, {}), "devices": {}}
         for d in self.devices:
@@ -244,6 +269,11 @@ def make_handler(t: Telemetry):
                     self._send(200, json.dumps({"ok": True}))
                 elif url.path == "/api/job/stats":
                     self._send(200, json.dumps(t.job_stats(q["job"])))
+                elif url.path == "/api/policy/set":
+                    t.policy_set(int(q["dev"]), q["field"], float(q["threshold"]), q.get("direction", "above") != "below")
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/policy/events":
+                    self._send(200, json.dumps(t.policy_events()))
                 else:
                     self._send(404, json.dumps({"error": "unknown path"}))
             except (KeyError, ValueError, RuntimeError) as e:

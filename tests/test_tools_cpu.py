@@ -165,6 +165,9 @@ time.sleep(0.3)
 get('/api/job/stop?job=j1')
 m = get('/metrics')
 assert '# TYPE b200_power_watts gauge' in m and 'b200_sm_clock_mhz{gpu="1"' in m
+line = next(l for l in m.splitlines() if l.startswith('b200_power_watts{gpu="0"'))
+watts = float(line.rsplit(' ', 1)[1])
+assert 150 < watts < 2000, watts          # watts, not milliwatts or kilowatts
 assert 'b200_clock_event_reason{gpu="0",reason="sw_power_cap"} 1' in m
 st = json.loads(get('/api/job/stats?job=j1'))
 assert st['devices']['0']['power']['samples'] >= 3 and st['devices']['0']['power']['avg'] > 0
@@ -401,3 +404,29 @@ def test_output_validators(tmp_path):
     (tmp_path / "bad.json").write_text(json.dumps(bad))
     assert any("overlap" in e for e in validate.check_perfetto(str(tmp_path / "bad.json")))
     assert validate.main(["db", dbp, "--table", "region:1"]) == 0
+
+
+def test_telemetry_policy_events_over_http(fake_nvml):
+    out = _py("""
+import json, time, urllib.request
+from rocm_systems_b200.tools import telemetry
+t = telemetry.Telemetry()
+srv = telemetry.serve(t, '127.0.0.1', 0)
+url = 'http://127.0.0.1:%d' % srv.server_address[1]
+get = lambda p: urllib.request.urlopen(url + p, timeout=10).read().decode()
+get('/api/policy/set?dev=0&field=power&threshold=250&direction=above')     # watts; the stand-in ramps by 10 W per read
+t.start(devices=[0], fields=['power'], period_ms=20, keep=100)
+deadline = time.time() + 5
+ev = []
+while time.time() < deadline and not ev:
+    time.sleep(0.1)
+    ev = json.loads(get('/api/policy/events'))
+assert ev and ev[0]['device'] == 0 and ev[0]['field'] == 'power' and ev[0]['value'] > 250 and ev[0]['direction'] == 'above'
+try:
+    get('/api/policy/set?dev=0&field=nope&threshold=1'); raise SystemExit('bad field accepted')
+except urllib.error.HTTPError as e:
+    assert e.code == 400
+srv.shutdown(); t.stop()
+print('ok')
+""", {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "2", "FAKE_NVML_RAMP": "1"})
+    assert "ok" in out
