@@ -207,6 +207,8 @@ class TraceDB:
             row[0], row[2] = pmap[row[0]], smap[row[2]]
             self.db.execute("insert into collective(process_id, rank, name_id, correlation_id, count, dtype, bytes, algo, ctas, host_start_ns,"
                             " host_end_ns, device_start_ns, device_end_ns) values (?,?,?,?,?,?,?,?,?,?,?,?,?)", row)
+        for name_id, device, ts_ns, value in src.execute("select name_id, device, ts_ns, value from counter_sample"):
+            self.db.execute("insert into counter_sample(name_id, device, ts_ns, value) values (?,?,?,?)", (smap[name_id], device, ts_ns, value))
         src.close()
         self.db.commit()
 
