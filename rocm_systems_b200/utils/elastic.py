@@ -102,7 +102,9 @@ def agree_survivors(store, hb: Heartbeat, generation: int, settle: float = 1.0) 
     Returns the sorted list of old ranks that form the next group."""
     mine = [r for r in hb.members if r not in set(hb.lost())]
     store.set(f"gen{generation}/proposal/{hb.rank}", ",".join(map(str, mine)))
-    deadline = time.monotonic() + max(settle, hb.timeout)
+    # Survivors notice a loss at slightly different times; wait several heartbeat timeouts for the
+    # proposals of everyone this rank still believes in before deciding without them.
+    deadline = time.monotonic() + max(settle, 5 * hb.timeout)
     proposals = {}
     while time.monotonic() < deadline:
         proposals = {}
