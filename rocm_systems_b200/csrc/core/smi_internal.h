@@ -33,6 +33,10 @@ struct NvmlFns {
   nvmlReturn_t (*nvlinkError)(nvmlDevice_t, unsigned int, nvmlNvLinkErrorCounter_t, unsigned long long*) = nullptr;
   nvmlReturn_t (*pcieGen)(nvmlDevice_t, unsigned int*) = nullptr;
   nvmlReturn_t (*pcieWidth)(nvmlDevice_t, unsigned int*) = nullptr;
+  nvmlReturn_t (*computeMode)(nvmlDevice_t, nvmlComputeMode_t*) = nullptr;
+  nvmlReturn_t (*persistence)(nvmlDevice_t, nvmlEnableState_t*) = nullptr;
+  nvmlReturn_t (*migMode)(nvmlDevice_t, unsigned int*, unsigned int*) = nullptr;
+  nvmlReturn_t (*eccMode)(nvmlDevice_t, nvmlEnableState_t*, nvmlEnableState_t*) = nullptr;
 };
 extern NvmlFns gN;
 bool ready();

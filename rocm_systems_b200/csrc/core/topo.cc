@@ -64,6 +64,10 @@ static bool loadNvml() {
   sym("nvmlDeviceGetNvLinkErrorCounter", &gN.nvlinkError, false);
   sym("nvmlDeviceGetCurrPcieLinkGeneration", &gN.pcieGen, false);
   sym("nvmlDeviceGetCurrPcieLinkWidth", &gN.pcieWidth, false);
+  sym("nvmlDeviceGetComputeMode", &gN.computeMode, false);
+  sym("nvmlDeviceGetPersistenceMode", &gN.persistence, false);
+  sym("nvmlDeviceGetMigMode", &gN.migMode, false);
+  sym("nvmlDeviceGetEccMode", &gN.eccMode, false);
   if (!ok) {
     dlclose(gLib);
     gLib = nullptr;
@@ -340,6 +344,23 @@ b200smi_status_t b200smi_pcie(int device, uint32_t* generation, uint32_t* width)
   if (gN.pcieGen(h, &g) != NVML_SUCCESS || gN.pcieWidth(h, &w) != NVML_SUCCESS) return B200SMI_ERR_NVML;
   *generation = g;
   *width = w;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_modes(int device, b200smi_modes_t* out) {
+  using namespace b200::smi;
+  if (!out) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  out->computeMode = out->persistence = out->mig = out->ecc = -1;
+  nvmlComputeMode_t cm;
+  if (gN.computeMode && gN.computeMode(h, &cm) == NVML_SUCCESS) out->computeMode = (int)cm;
+  nvmlEnableState_t e, pending;
+  if (gN.persistence && gN.persistence(h, &e) == NVML_SUCCESS) out->persistence = e == NVML_FEATURE_ENABLED;
+  unsigned int cur = 0, pend = 0;
+  if (gN.migMode && gN.migMode(h, &cur, &pend) == NVML_SUCCESS) out->mig = (int)cur;
+  if (gN.eccMode && gN.eccMode(h, &e, &pending) == NVML_SUCCESS) out->ecc = e == NVML_FEATURE_ENABLED;
   return B200SMI_OK;
 }
 

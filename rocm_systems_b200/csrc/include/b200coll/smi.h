@@ -84,6 +84,10 @@ b200smi_status_t b200smi_driver_version(char* buf, int len);
 b200smi_status_t b200smi_processes(int device, b200smi_process_t* out, int max, int* n);
 b200smi_status_t b200smi_nvlink_errors(int device, b200smi_nvlink_errors_t* out);
 b200smi_status_t b200smi_pcie(int device, uint32_t* generation, uint32_t* width);
+/* Modes of a device, read only (this library never changes them): compute mode (0 default, 1 exclusive thread, 2 prohibited,
+ * 3 exclusive process), persistence, MIG and ECC enabled flags; -1 where the driver does not report one. */
+typedef struct { int computeMode, persistence, mig, ecc; } b200smi_modes_t;
+b200smi_status_t b200smi_modes(int device, b200smi_modes_t* out);
 /* Watches: a sampler thread reads the watched fields every periodMs into a per-(device, field)
  * ring of `keep` samples (the watch table and cache of rdc_libs/rdc/src/RdcWatchTableImpl.cc). */
 b200smi_status_t b200smi_watch_start(const int* devices, int ndev, const int* fields, int nfields, int periodMs, int keep);

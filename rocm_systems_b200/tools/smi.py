@@ -56,6 +56,10 @@ class NvlinkErrors(ctypes.Structure):
                 ("linksRead", ctypes.c_uint32)]
 
 
+class Modes(ctypes.Structure):
+    _fields_ = [("computeMode", ctypes.c_int), ("persistence", ctypes.c_int), ("mig", ctypes.c_int), ("ecc", ctypes.c_int)]
+
+
 POLICY_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_double, ctypes.c_void_p)
 
 
@@ -78,6 +82,7 @@ class Smi:
         L.b200smi_driver_version.argtypes = [ctypes.c_char_p, ctypes.c_int]
         L.b200smi_processes.argtypes = [ctypes.c_int, ctypes.POINTER(Process), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         L.b200smi_nvlink_errors.argtypes = [ctypes.c_int, ctypes.POINTER(NvlinkErrors)]
+        L.b200smi_modes.argtypes = [ctypes.c_int, ctypes.POINTER(Modes)]
         L.b200smi_pcie.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32)]
         self._cbs = []
         self._ck(L.b200smi_init())
@@ -174,6 +179,13 @@ class Smi:
         self._ck(self.lib.b200smi_pcie(dev, ctypes.byref(g), ctypes.byref(w)))
         return {"generation": g.value, "width": w.value}
 
+    def modes(self, dev: int) -> dict:
+        """Compute / persistence / MIG / ECC modes as the driver reports them (read only; -1 = not reported)."""
+        m = Modes()
+        self._ck(self.lib.b200smi_modes(dev, ctypes.byref(m)))
+        names = {0: "default", 1: "exclusive_thread", 2: "prohibited", 3: "exclusive_process"}
+        return {"compute_mode": names.get(m.computeMode, str(m.computeMode)), "persistence": m.persistence, "mig": m.mig, "ecc": m.ecc}
+
     def set_power_limit(self, dev: int, milliwatt: int, allow: bool) -> None:
         self._ck(self.lib.b200smi_set_power_limit(dev, milliwatt, int(allow)))
 
@@ -198,6 +210,7 @@ def main(argv=None) -> int:
     ap.add_argument("--showdriverversion", action="store_true")
     ap.add_argument("--shownvlinkerrors", action="store_true", help="replay / recovery / CRC counters summed over each GPU's links")
     ap.add_argument("--showbus", action="store_true", help="PCIe generation and width")
+    ap.add_argument("--showmodes", action="store_true", help="compute, persistence, MIG and ECC modes (read only)")
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--setpowerlimit", nargs=2, metavar=("GPU", "WATTS"))
     ap.add_argument("--allow-set", action="store_true", help="required (with B200SMI_ALLOW_SET=1) before any setter acts")
@@ -238,7 +251,12 @@ def main(argv=None) -> int:
         if not a.json:
             for i, e in enumerate(out["pcie"]):
                 print(f"GPU{i}: PCIe gen {e['generation']} x{e['width']}")
-    only_new = a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    if a.showmodes:
+        out["modes"] = [smi.modes(i) for i in range(n)]
+        if not a.json:
+            for i, m in enumerate(out["modes"]):
+                print(f"GPU{i}: compute mode {m['compute_mode']}, persistence {m['persistence']}, MIG {m['mig']}, ECC {m['ecc']}")
+    only_new = a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     if a.showall or not (a.showtopo or a.showhealth or a.setpowerlimit or only_new):
         out["devices"] = [smi.info(i) for i in range(n)]
         if not a.json:

@@ -68,3 +68,9 @@ nvmlReturn_t nvmlDeviceGetNvLinkErrorCounter(nvmlDevice_t d, unsigned int link, 
 }
 nvmlReturn_t nvmlDeviceGetCurrPcieLinkGeneration(nvmlDevice_t d, unsigned int* g) { (void)d; *g = 5; return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetCurrPcieLinkWidth(nvmlDevice_t d, unsigned int* w) { (void)d; *w = 16; return NVML_SUCCESS; }
+
+/* modes (read only) */
+nvmlReturn_t nvmlDeviceGetComputeMode(nvmlDevice_t d, int* m) { (void)d; *m = 0; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetPersistenceMode(nvmlDevice_t d, int* e) { (void)d; *e = 1; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetMigMode(nvmlDevice_t d, unsigned int* cur, unsigned int* pend) { (void)d; *cur = 0; *pend = 0; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetEccMode(nvmlDevice_t d, int* cur, int* pend) { (void)d; *cur = 1; *pend = 1; return NVML_SUCCESS; }

@@ -114,6 +114,7 @@ assert s.processes(1) == []
 e = s.nvlink_errors(2)
 assert e['linksRead'] == 18 and e['replay'] == 5 and e['crcFlit'] == 0 and s.nvlink_errors(0)['replay'] == 0
 assert s.pcie(3) == {'generation': 5, 'width': 16}
+assert s.modes(1) == {'compute_mode': 'default', 'persistence': 1, 'mig': 0, 'ecc': 1}
 print('ok')
 """, fake_nvml, {"FAKE_NVML_LINK_ERRORS": "2"})
     assert "ok" in out
