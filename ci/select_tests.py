@@ -22,9 +22,9 @@ RULES = [
     ("rocm_systems_b200/csrc/core/bootstrap.*", ["tests/test_bootstrap.py", "tests/test_sanitizers_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/core/topo.cc", ["tests/test_smi_fake.py", "tests/test_tools_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/core/health.cc", ["tests/test_smi_fake.py", "tests/test_tools_cpu.py"], [], True),
-    ("rocm_systems_b200/csrc/core/*", ["tests/test_bootstrap.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
+    ("rocm_systems_b200/csrc/core/*", ["tests/test_api_cpu.py", "tests/test_bootstrap.py", "tests/test_planner_cpu.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
     ("rocm_systems_b200/csrc/coll/verifiable*", ["tests/test_verifiable_cpu.py"], [], True),
-    ("rocm_systems_b200/csrc/coll/*", ["tests/test_protocol_model_cpu.py"], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py"], True),
+    ("rocm_systems_b200/csrc/coll/*", ["tests/test_planner_cpu.py", "tests/test_protocol_model_cpu.py"], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py"], True),
     ("rocm_systems_b200/csrc/shmem/*", [], ["tests/test_gpu_fused_multi.py"], True),
     ("rocm_systems_b200/csrc/fused/*", [], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_no_alloc.py"], True),
     ("rocm_systems_b200/csrc/torch/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_collectives.py"], True),

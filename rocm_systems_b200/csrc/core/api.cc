@@ -4,6 +4,7 @@
 // Table hand-off follows the pattern the reference's registration shim tests with its mock RCCL
 // (rocprofiler-register/tests/rccl/rccl.cpp:35-126): build the table of implementations once,
 // give tools one chance to wrap slots, then route every public call through it.
+#include <memory>
 #include <dlfcn.h>
 #include <string.h>
 
@@ -764,6 +765,50 @@ ncclResult_t b200collTraceWrite(ncclComm_t comm, const char* path, const char* f
 
 // ---- host-only rendezvous handles (used by tests and by the Python layer without a GPU) ---------
 extern "C" {
+// What the planner would choose for a collective on a communicator of `nranks` ranks, with or without
+// a multicast alias, without any device or peer: the algorithm (1 flag-in-data, 2 peer loads, 3 in-switch),
+// CTAs, whether the zero-copy path applies (never here: the buffers are not in a window) and the number of
+// pipeline chunks. Honours the environment and the tuning file exactly as a real communicator does.
+// `kind`: 0 all-reduce, 1 reduce-scatter, 2 reduce, 3 all-gather, 4 broadcast.
+struct b200collPlanInfo {
+  int algo, ctas, direct;
+  unsigned long long chunks;
+};
+ncclResult_t b200collPlanDry(int nranks, int nvls, int kind, size_t count, ncclDataType_t dt, ncclRedOp_t op, b200collPlanInfo* out) {
+  if (!out || nranks < 1 || nranks > kMaxRanks || kind < 0 || kind > COLL_BROADCAST || (int)dt < 0 || (int)dt >= ncclNumTypes)
+    BFAIL(ncclInvalidArgument, "b200collPlanDry: bad argument");
+  const Flags& fl = Flags::get();
+  auto c = std::make_unique<Comm>();
+  c->magic = kCommMagic;
+  c->rank = 0;
+  c->nranks = nranks;
+  c->nvls = nvls != 0 && fl.nvlsEnable != 0 && nranks > 1;
+  c->dev.rank = 0;
+  c->dev.nranks = nranks;
+  c->dev.stageBytes = nranks == 1 ? (1u << 16) : fl.stageBytes;
+  if (fl.maxCtas > 0) c->maxCtas = fl.maxCtas;
+  if (fl.minCtas > 0) c->minCtas = fl.minCtas;
+  if (c->maxCtas > kMaxCtas) c->maxCtas = kMaxCtas;
+  if (c->minCtas > c->maxCtas) c->minCtas = c->maxCtas;
+  loadTuning(c.get());
+  CollReq r{};
+  r.kind = kind;
+  r.send = reinterpret_cast<const void*>(0x10000);  // never dereferenced on the host; aligned, outside any window
+  r.recv = reinterpret_cast<void*>(0x20000);
+  r.count = count;
+  r.dt = dt;
+  r.op = (int)op;
+  r.root = 0;
+  r.comm = c.get();
+  Plan plan{};
+  BCHECK(planColl(r, &plan));
+  out->algo = plan.algo;
+  out->ctas = plan.ctas;
+  out->direct = plan.direct ? 1 : 0;
+  out->chunks = plan.chunks;
+  return ncclSuccess;
+}
+
 // Copies the JSON description of every setting into `buf` (NUL-terminated, truncated to `cap`);
 // returns the length the full text needs.
 size_t b200collDescribeSettings(char* buf, size_t cap) {

@@ -1,0 +1,98 @@
+"""The collective planner without a device: which algorithm, how many CTAs and how many pipeline
+chunks a message gets, under the built-in thresholds, the environment and a tuning file."""
+import ctypes
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+AR, RS, RED, AG, BC = range(5)
+LL, P2P, NVLS = 1, 2, 3
+F32, SUM, MAX = 7, 0, 2
+
+CODE = """
+import ctypes, json, sys
+from rocm_systems_b200 import _lib
+lib = _lib.load()
+class Info(ctypes.Structure):
+    _fields_ = [("algo", ctypes.c_int), ("ctas", ctypes.c_int), ("direct", ctypes.c_int), ("chunks", ctypes.c_ulonglong)]
+lib.b200collPlanDry.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.POINTER(Info)]
+out = []
+for nranks, nvls, kind, count, dt, op in json.loads(sys.argv[1]):
+    i = Info()
+    rc = lib.b200collPlanDry(nranks, nvls, kind, count, dt, op, ctypes.byref(i))
+    out.append([rc, i.algo, i.ctas, i.direct, i.chunks])
+print(json.dumps(out))
+"""
+
+
+def plan(cases, env=None):
+    e = dict(os.environ, PYTHONPATH=str(ROOT))
+    for k in list(e):
+        if k.startswith(("B200COLL_", "NCCL_")):
+            del e[k]
+    e.update(env or {})
+    p = subprocess.run([sys.executable, "-c", CODE, json.dumps(cases)], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr
+    return json.loads(p.stdout.strip().splitlines()[-1])
+
+
+def test_builtin_choices():
+    MiB = 1 << 20
+    r = plan([
+        [8, 1, AR, 1024, F32, SUM],            # 4 KiB: flag-in-data
+        [8, 1, AR, 16 * 1024, F32, SUM],       # 64 KiB: still flag-in-data
+        [8, 1, AR, 16 * 1024 + 4, F32, SUM],   # just above: in-switch
+        [8, 1, AR, 64 * MiB // 4, F32, MAX],   # max is not an in-switch operation: peer loads
+        [2, 1, AR, 64 * MiB // 4, F32, SUM],   # two ranks: peer loads move fewer bytes than the switch
+        [8, 0, AR, 64 * MiB // 4, F32, SUM],   # no multicast: peer loads
+        [8, 1, AG, MiB, F32, SUM],             # copies never reduce in the switch
+        [8, 1, AR, 8, 6, SUM],                 # fp16 is 6: tiny, flag-in-data
+    ])
+    assert [x[0] for x in r] == [0] * 8
+    assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL]
+    assert all(x[3] == 0 for x in r)           # nothing is in a registered window here
+
+
+def test_pipeline_chunks_are_equalised():
+    MiB = 1 << 20
+    r = plan([
+        [8, 1, AR, 8 * MiB // 4, F32, SUM],        # 8 MiB: one chunk
+        [8, 1, AR, 16 * MiB // 4, F32, SUM],       # 16 MiB: two chunks of 8 MiB
+        [8, 1, AR, 80 * 1000 * 1000 // 4, F32, SUM],   # 80 MB: chunk = 1/8 rounded up to 1 MiB -> 10 MiB -> 8 chunks
+        [8, 1, AR, 1024 * MiB // 4, F32, SUM],     # 1 GiB: a staging half (64 MiB) caps the chunk: 16
+        [8, 1, RS, 128 * MiB // 4, F32, SUM],      # per-rank slice 128 MiB -> staged 1 GiB -> 8 MiB per slice and chunk: 16
+        [8, 1, AG, 200 * MiB // 4, F32, SUM],      # copies are chunked by the staging half only: ceil(200 / 64) = 4
+    ])
+    assert [x[4] for x in r] == [1, 2, 8, 16, 16, 4]
+    off = plan([[8, 1, AR, 1024 * MiB // 4, F32, SUM]], {"B200COLL_PIPELINE_CHUNK": "0"})
+    assert off[0][4] == 16                         # 64 MiB halves either way at this size
+    small = plan([[8, 1, AR, 32 * MiB // 4, F32, SUM]], {"B200COLL_PIPELINE_CHUNK": "1M"})
+    assert small[0][4] == 32
+
+
+def test_environment_and_cta_bounds():
+    MiB = 1 << 20
+    base = plan([[8, 1, AR, 64 * MiB // 4, F32, SUM]])[0]
+    assert base[1] == NVLS and base[2] == 32       # the default upper bound
+    forced = plan([[8, 1, AR, 64 * MiB // 4, F32, SUM]], {"NCCL_ALGO": "P2P", "NCCL_MAX_CTAS": "8"})[0]
+    assert forced[1] == P2P and forced[2] == 8
+    no_nvls = plan([[8, 1, AR, 64 * MiB // 4, F32, SUM]], {"NCCL_NVLS_ENABLE": "0"})[0]
+    assert no_nvls[1] == P2P
+    # a forced algorithm that cannot serve the call falls back: flag-in-data does not do 64 MiB
+    assert plan([[8, 1, AR, 64 * MiB // 4, F32, SUM]], {"B200COLL_ALGO": "ll"})[0][1] == NVLS
+
+
+def test_tuning_file_wins_over_thresholds(tmp_path):
+    MiB = 1 << 20
+    t = tmp_path / "tune.json"
+    t.write_text(json.dumps({"entries": [{"coll": "all_reduce", "nranks": 8, "max_bytes": MiB, "algo": "p2p", "ctas": 5},
+                                         {"coll": "all_reduce", "nranks": 4, "max_bytes": 1 << 40, "algo": "ll"},
+                                         {"coll": "all_reduce", "max_bytes": 1 << 40, "algo": "nvls"}]}))
+    r = plan([[8, 1, AR, 1024, F32, SUM], [8, 1, AR, 4 * MiB // 4, F32, SUM], [8, 1, RS, 1024, F32, SUM]], {"B200COLL_TUNING_FILE": str(t)})
+    assert r[0][1] == P2P and r[0][2] == 5        # first row covers 4 KiB
+    assert r[1][1] == NVLS                         # beyond the first row; the 4-rank row is skipped at 8 ranks
+    assert r[2][1] == NVLS                         # no reduce_scatter rows: built-in choice (4 KiB x 8 ranks = 32 KiB staged)
+    assert plan([[0, 1, AR, 4, F32, SUM]])[0][0] == 4   # nranks 0: invalid argument
