@@ -56,8 +56,13 @@ struct Args {
   int iters = 20, warmup = 5, agg = 1, cycles = 1, check = 1;
   std::string op = "sum", dtype = "float";
   int root = 0, blocking = 0, average = 1, reg = 0, outOfPlace = -1, graph = 0, cputime = 0, timeoutSec = 0;
+  int parallelInit = 0, streamNull = 0, delayUs = 0, rotating = 0;
+  std::string memType = "coarse";
   std::string outFile, outFormat = "csv";
 };
+
+// -E: consecutive iterations use buffers this far apart (rccl-tests common.cpp:32, 631-634).
+static const size_t kRotateBytes = 192u << 20;
 
 struct TypeInfo { const char* name; ncclDataType_t dt; int bytes; };
 static const TypeInfo kTypes[] = {{"int8", ncclInt8, 1}, {"uint8", ncclUint8, 1}, {"int32", ncclInt32, 4}, {"uint32", ncclUint32, 4},
@@ -323,8 +328,8 @@ static void crossRank(RankCtx& c, double* dbuf, double v[3], cudaStream_t st) {
 static void runRank(RankCtx& c) {
   const Args& a = *c.a;
   CK(cudaSetDevice(c.dev));
-  cudaStream_t st;
-  CK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  cudaStream_t st = nullptr;  // -y 1: the NULL stream
+  if (!a.streamNull) CK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
   const int n = c.n, rank = c.rank;
   std::vector<int> typeIdx, opIdx;
   const int nTypes = (int)(sizeof(kTypes) / sizeof(kTypes[0]));
@@ -334,7 +339,9 @@ static void runRank(RankCtx& c) {
   if (typeIdx.empty() || opIdx.empty()) { if (rank == 0) fprintf(stderr, "unknown -d %s or -o %s\n", a.dtype.c_str(), a.op.c_str()); exit(1); }
 
   // Buffers sized for the largest message; with -R they come from ncclMemAlloc and are registered.
-  const size_t maxBytes = a.maxBytes + 4096;
+  // -E adds the rotation distance; -Y picks where unregistered buffers live (coarse and fine are both plain device
+  // memory here: CUDA has no uncached device allocation).
+  const size_t maxBytes = a.maxBytes + 4096 + (a.rotating ? kRotateBytes : 0);
   void *send = nullptr, *recv = nullptr, *expect = nullptr;
   void *hs = nullptr, *hr = nullptr;
   if (a.reg) {
@@ -342,10 +349,18 @@ static void runRank(RankCtx& c) {
     NK(ncclMemAlloc(&recv, maxBytes));
     NK(ncclCommRegister(c.comm, send, maxBytes, &hs));
     NK(ncclCommRegister(c.comm, recv, maxBytes, &hr));
+  } else if (a.memType == "host") {
+    CK(cudaHostAlloc(&send, maxBytes, cudaHostAllocPortable));
+    CK(cudaHostAlloc(&recv, maxBytes, cudaHostAllocPortable));
+  } else if (a.memType == "managed") {
+    CK(cudaMallocManaged(&send, maxBytes));
+    CK(cudaMallocManaged(&recv, maxBytes));
   } else {
     CK(cudaMalloc(&send, maxBytes));
     CK(cudaMalloc(&recv, maxBytes));
   }
+  CK(cudaMemset(send, 1, maxBytes));  // places that only the timed loop visits hold finite values too
+  CK(cudaMemset(recv, 1, maxBytes));
   CK(cudaMalloc(&expect, maxBytes));
   double* dbuf;
   CK(cudaMalloc(&dbuf, 64));
@@ -404,25 +419,33 @@ static void runRank(RankCtx& c) {
           }
         };
         initData(seed);
-        for (int w = 0; w < a.warmup; w++) NK(runColl(sp, rp, s, dt, op, a.root, rank, n, eb, c.comm, st));
+        // Every iteration works at a different offset so that a message is not served from cache and buffer
+        // exchange is exercised: with -E two places 192 MiB apart, otherwise as many places as the largest
+        // message leaves room for (common.cpp:625-640). Offsets are multiples of 512 bytes.
+        const size_t span = (std::max(s.sendCount, s.recvCount) * eb + 511) & ~(size_t)511;
+        const size_t places = a.rotating ? 2 : std::max<size_t>(1, a.maxBytes / std::max<size_t>(span, 1));
+        auto shiftOf = [&](int it) -> size_t { return a.rotating ? kRotateBytes * (it & 1) : span * ((size_t)it % places); };
+        auto timedColl = [&](int it) { const size_t sh = shiftOf(it); return runColl(sp + sh, rp + sh, s, dt, op, a.root, rank, n, eb, c.comm, st); };
+        for (int w = 0; w < a.warmup; w++) NK(timedColl(w));
         CK(cudaStreamSynchronize(st));
         double agg[3] = {0, 0, 0};
         crossRank(c, dbuf, agg, st);  // barrier
         cudaGraph_t graph = nullptr;
         cudaGraphExec_t gexec = nullptr;
-        if (a.graph) {
+        const bool useGraph = a.graph && !a.streamNull;  // the NULL stream cannot be captured
+        if (useGraph) {
           CK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-          for (int it = 0; it < a.iters; it++) for (int m = 0; m < a.agg; m++) NK(runColl(sp, rp, s, dt, op, a.root, rank, n, eb, c.comm, st));
+          for (int it = 0; it < a.iters; it++) for (int m = 0; m < a.agg; m++) NK(timedColl(it));
           CK(cudaStreamEndCapture(st, &graph));
           CK(cudaGraphInstantiate(&gexec, graph, 0));
         }
         auto t0 = std::chrono::steady_clock::now();
         CK(cudaEventRecord(e0, st));
-        if (a.graph) {
+        if (useGraph) {
           CK(cudaGraphLaunch(gexec, st));
         } else {
           for (int it = 0; it < a.iters; it++) {
-            for (int m = 0; m < a.agg; m++) NK(runColl(sp, rp, s, dt, op, a.root, rank, n, eb, c.comm, st));
+            for (int m = 0; m < a.agg; m++) NK(timedColl(it));
             if (a.blocking) CK(cudaStreamSynchronize(st));
           }
         }
@@ -473,6 +496,7 @@ static void runRank(RankCtx& c) {
         wrong[inplace] = a.check > 0 ? v[1] : -1;
         devUs[inplace] = v[2];
         c.wrongTotal += (long long)v[1];
+        if (!inplace && a.delayUs > 0) usleep(a.delayUs);  // -q: pause between the out-of-place and the in-place run
       }
       if (rank == 0) {
         char line[512];
@@ -512,7 +536,8 @@ static void runRank(RankCtx& c) {
 static void usage() {
   printf("USAGE: %s_perf [-g ngpus] [-b minbytes] [-e maxbytes] [-i stepbytes] [-f stepfactor] [-n iters] [-w warmup_iters] [-m agg_iters]\n"
          "       [-N run_cycles] [-c check] [-o sum|prod|max|min|avg|mulsum|all] [-d type|all] [-r root] [-z blocking] [-G cudagraph]\n"
-         "       [-C report_cputime] [-a average 0|1] [-R local_register] [-O out_of_place 0|1] [-T timeout_s] [-x output_file] [-Z csv|json]\n", PERF_NAME);
+         "       [-C report_cputime] [-a average 0|1] [-R local_register] [-O out_of_place 0|1] [-T timeout_s] [-x output_file] [-Z csv|json]\n"
+         "       [-p parallel_init] [-y stream_null] [-q delay_inout_place_us] [-E rotating_tensor] [-Y coarse|fine|host|managed]\n", PERF_NAME);
 }
 
 static bool idFromFile(ncclUniqueId* id, int rank) {
@@ -569,7 +594,15 @@ int main(int argc, char** argv) {
     else if (f == "-T" || f == "--timeout") a.timeoutSec = atoi(next());
     else if (f == "-x" || f == "--output_file") a.outFile = next();
     else if (f == "-Z" || f == "--output_format") a.outFormat = next();
-    else if (f == "-p" || f == "-y" || f == "-q" || f == "-E" || f == "-Y" || f == "-u" || f == "-F") (void)next();  // accepted, no effect here
+    else if (f == "-p" || f == "--parallel_init") a.parallelInit = atoi(next());
+    else if (f == "-y" || f == "--stream_null") a.streamNull = atoi(next());
+    else if (f == "-q" || f == "--delay_inout_place") a.delayUs = atoi(next());
+    else if (f == "-E" || f == "--rotating_tensor") a.rotating = atoi(next());
+    else if (f == "-Y" || f == "--memory_type") {
+      a.memType = next();
+      if (a.memType != "coarse" && a.memType != "fine" && a.memType != "host" && a.memType != "managed") { fprintf(stderr, "unknown -Y %s\n", a.memType.c_str()); return 1; }
+    }
+    else if (f == "-u" || f == "--cumask" || f == "-F" || f == "--cache_flush") (void)next();  // AMD-only knobs: accepted, no effect
     else if (f == "-h" || f == "--help") { usage(); return 0; }
     else { fprintf(stderr, "unknown flag %s\n", f.c_str()); usage(); return 1; }
   }
@@ -610,9 +643,17 @@ int main(int argc, char** argv) {
     NK(ncclCommDestroy(comm));
   } else {
     std::vector<ncclComm_t> comms(n);
-    NK(ncclCommInitAll(comms.data(), n, nullptr));
-    for (int r = 0; r < n; r++) ctx.push_back(RankCtx{r, n, r, comms[r], &a, r == 0 ? out : nullptr});
     std::vector<std::thread> th;
+    if (a.parallelInit) {  // -p 1: every thread brings up its own rank from a shared id (common.cpp:1697-1700)
+      ncclUniqueId id;
+      NK(ncclGetUniqueId(&id));
+      for (int r = 0; r < n; r++) th.emplace_back([&, r]() { CK(cudaSetDevice(r)); NK(ncclCommInitRank(&comms[r], n, id, r)); });
+      for (auto& t : th) t.join();
+      th.clear();
+    } else {
+      NK(ncclCommInitAll(comms.data(), n, nullptr));
+    }
+    for (int r = 0; r < n; r++) ctx.push_back(RankCtx{r, n, r, comms[r], &a, r == 0 ? out : nullptr});
     for (int r = 0; r < n; r++) th.emplace_back(runRank, std::ref(ctx[r]));
     for (auto& t : th) t.join();
     for (int r = 0; r < n; r++) NK(ncclCommDestroy(comms[r]));
