@@ -21,6 +21,7 @@ extern "C" {
 #endif
 
 #define B200SHMEM_MAX_PES 8
+#define B200SHMEM_MAX_DMA_GANG 8
 
 /* What a kernel needs to talk to its peers; passed by value as a kernel argument. */
 typedef struct b200shmem_dev {
@@ -62,6 +63,17 @@ ncclResult_t b200shmem_putmem_signal_on_stream(b200shmem_ctx_t ctx, void* dest, 
 ncclResult_t b200shmem_signal_wait_until_on_stream(b200shmem_ctx_t ctx, unsigned long long* sigAddr, int cmp, unsigned long long value,
                                                    cudaStream_t stream);
 ncclResult_t b200shmem_barrier_all_on_stream(b200shmem_ctx_t ctx, cudaStream_t stream);
+/* Copy-engine variants of put / get / put+signal: the bytes move by DMA, no SM takes part, and a large transfer is
+ * split over `gang` engines (0: chosen from the size, or B200COLL_DMA_GANG). They are stream-ordered like the others
+ * and can be captured into a CUDA graph. The signal of the put+signal form is stored by one warp after the copies. */
+ncclResult_t b200shmem_putmem_dma_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, int gang, cudaStream_t stream);
+ncclResult_t b200shmem_getmem_dma_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, int gang, cudaStream_t stream);
+ncclResult_t b200shmem_putmem_signal_dma_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, unsigned long long* sigAddr,
+                                                   unsigned long long signal, int sigOp, int pe, int gang, cudaStream_t stream);
+/* How a transfer of `bytes` is cut: returns the number of parts and fills offsets/lengths (each may be NULL). Pure. */
+int b200shmem_dma_plan(size_t bytes, int gang, size_t* offsets, size_t* lengths);
+/* Number of asynchronous copy engines of this PE's GPU, or -1. */
+int b200shmem_dma_engines(b200shmem_ctx_t ctx);
 /* First device-side wait that ran out of budget since the last call (B200SHMEM_OK if none); synchronises the device. */
 int b200shmem_take_status(b200shmem_ctx_t ctx);
 

@@ -18,6 +18,10 @@ struct b200shmem_ctx {
   std::mutex mu;
   std::map<size_t, size_t> freeList;   // offset -> size
   std::map<size_t, size_t> live;       // offset -> size
+  // Copy-engine transfers: side streams a large copy is split over, created on first use.
+  cudaStream_t dmaStream[B200SHMEM_MAX_DMA_GANG] = {};
+  cudaEvent_t dmaFork = nullptr, dmaJoin[B200SHMEM_MAX_DMA_GANG] = {};
+  int dmaReady = 0;
 };
 
 namespace {
@@ -159,6 +163,11 @@ ncclResult_t b200shmem_finalize(b200shmem_ctx_t ctx) {
   if (!ctx) return ncclSuccess;
   DevGuard g(ctx->comm->cudaDev);
   cudaDeviceSynchronize();
+  for (int i = 0; i < ctx->dmaReady; i++) {
+    cudaStreamDestroy(ctx->dmaStream[i]);
+    cudaEventDestroy(ctx->dmaJoin[i]);
+  }
+  if (ctx->dmaFork) cudaEventDestroy(ctx->dmaFork);
   ncclResult_t r = commSymFree(ctx->comm, ctx->heap);
   if (ctx->devState) cudaFree(ctx->devState);
   delete ctx;
@@ -323,6 +332,98 @@ ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStre
   BCHECK(ctx->comm->boot.barrier());
   b200shmem_free(ctx, words);
   return ncclSuccess;
+}
+
+// ---- copy-engine transfers -----------------------------------------------------------------------------------------
+// The reference runtime moves bulk peer data with DMA engines and may gang several engines on one copy
+// (rocr-runtime core/runtime/amd_gpu_agent.cpp:1013-1108); the count it gangs comes from the link (amd_topology.cpp:442-484).
+// Here a transfer is a cudaMemcpyAsync between this PE's mapping of two heaps, which the driver runs on a copy engine,
+// and a large one is cut into page-aligned parts on side streams that fork from and join the caller's stream with
+// events, so it stays stream-ordered (and capturable) as a whole. No SM takes part: the path for bulk data that must
+// not compete with running GEMMs (pipeline stages, checkpoint traffic).
+
+int b200shmem_dma_plan(size_t bytes, int gang, size_t* offsets, size_t* lengths) {
+  if (gang <= 0) {
+    const long env = Flags::get().dmaGang;
+    gang = env > 0 ? (int)env : (bytes >= (64u << 20) ? 4 : bytes >= (8u << 20) ? 2 : 1);
+  }
+  if (gang > B200SHMEM_MAX_DMA_GANG) gang = B200SHMEM_MAX_DMA_GANG;
+  constexpr size_t kPart = 64u << 10;  // parts are multiples of 64 KiB, so that none is too small to be worth an engine
+  const size_t units = (bytes + kPart - 1) / kPart;
+  if ((size_t)gang > units) gang = units ? (int)units : 1;
+  size_t off = 0;
+  for (int i = 0; i < gang; i++) {
+    const size_t u = units / gang + ((size_t)i < units % gang ? 1 : 0);
+    size_t len = u * kPart;
+    if (off + len > bytes) len = bytes - off;
+    if (offsets) offsets[i] = off;
+    if (lengths) lengths[i] = len;
+    off += len;
+  }
+  return gang;
+}
+
+static ncclResult_t dmaSetup(b200shmem_ctx_t ctx, int gang) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  if (!ctx->dmaFork) BCUDA(cudaEventCreateWithFlags(&ctx->dmaFork, cudaEventDisableTiming));
+  while (ctx->dmaReady < gang) {
+    const int i = ctx->dmaReady;
+    BCUDA(cudaStreamCreateWithFlags(&ctx->dmaStream[i], cudaStreamNonBlocking));
+    BCUDA(cudaEventCreateWithFlags(&ctx->dmaJoin[i], cudaEventDisableTiming));
+    ctx->dmaReady = i + 1;
+  }
+  return ncclSuccess;
+}
+
+static ncclResult_t dmaCopy(b200shmem_ctx_t ctx, char* dst, const char* src, size_t bytes, int gang, cudaStream_t stream) {
+  if (bytes == 0) return ncclSuccess;
+  size_t off[B200SHMEM_MAX_DMA_GANG], len[B200SHMEM_MAX_DMA_GANG];
+  const int g = b200shmem_dma_plan(bytes, gang, off, len);
+  DevGuard dg(ctx->comm->cudaDev);
+  if (g == 1) {
+    BCUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream));
+    return ncclSuccess;
+  }
+  BCHECK(dmaSetup(ctx, g - 1));
+  // Part 0 stays on the caller's stream; the others fork after everything already queued there and join before
+  // anything queued later.
+  BCUDA(cudaEventRecord(ctx->dmaFork, stream));
+  for (int i = 1; i < g; i++) {
+    cudaStream_t s = ctx->dmaStream[i - 1];
+    BCUDA(cudaStreamWaitEvent(s, ctx->dmaFork, 0));
+    BCUDA(cudaMemcpyAsync(dst + off[i], src + off[i], len[i], cudaMemcpyDeviceToDevice, s));
+    BCUDA(cudaEventRecord(ctx->dmaJoin[i - 1], s));
+  }
+  BCUDA(cudaMemcpyAsync(dst + off[0], src + off[0], len[0], cudaMemcpyDeviceToDevice, stream));
+  for (int i = 1; i < g; i++) BCUDA(cudaStreamWaitEvent(stream, ctx->dmaJoin[i - 1], 0));
+  return ncclSuccess;
+}
+
+ncclResult_t b200shmem_putmem_dma_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, int gang, cudaStream_t stream) {
+  void* r = b200shmem_ptr(ctx, dest, pe);
+  if (!r) BFAIL(ncclInvalidArgument, "b200shmem_putmem_dma: destination is not in the symmetric heap");
+  return dmaCopy(ctx, (char*)r, (const char*)source, bytes, gang, stream);
+}
+ncclResult_t b200shmem_getmem_dma_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, int gang, cudaStream_t stream) {
+  void* r = b200shmem_ptr(ctx, source, pe);
+  if (!r) BFAIL(ncclInvalidArgument, "b200shmem_getmem_dma: source is not in the symmetric heap");
+  return dmaCopy(ctx, (char*)dest, (const char*)r, bytes, gang, stream);
+}
+ncclResult_t b200shmem_putmem_signal_dma_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, unsigned long long* sigAddr,
+                                                   unsigned long long signal, int sigOp, int pe, int gang, cudaStream_t stream) {
+  if (!b200shmem_ptr(ctx, sigAddr, pe)) BFAIL(ncclInvalidArgument, "b200shmem_putmem_signal_dma: signal word is not in the symmetric heap");
+  BCHECK(b200shmem_putmem_dma_on_stream(ctx, dest, source, bytes, pe, gang, stream));
+  // The signal follows the joined copies in stream order; one warp stores it with release semantics at system scope.
+  DevGuard g(ctx->comm->cudaDev);
+  kSignal<<<1, 32, 0, stream>>>(ctx->dev, sigAddr, signal, sigOp, pe);
+  BCUDA(cudaGetLastError());
+  return ncclSuccess;
+}
+int b200shmem_dma_engines(b200shmem_ctx_t ctx) {
+  if (!ctx) return -1;
+  int v = 0;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrAsyncEngineCount, ctx->comm->cudaDev) != cudaSuccess) return -1;
+  return v;
 }
 
 }  // extern "C"

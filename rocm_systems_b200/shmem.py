@@ -50,12 +50,25 @@ def _l():
         lib.b200shmem_signal_wait_until_on_stream.argtypes = [vp, vp, i32, u64, vp]
         lib.b200shmem_barrier_all_on_stream.argtypes = [vp, vp]
         lib.b200shmem_take_status.argtypes = [vp]
+        lib.b200shmem_putmem_dma_on_stream.argtypes = [vp, vp, vp, sz, i32, i32, vp]
+        lib.b200shmem_getmem_dma_on_stream.argtypes = [vp, vp, vp, sz, i32, i32, vp]
+        lib.b200shmem_putmem_signal_dma_on_stream.argtypes = [vp, vp, vp, sz, vp, u64, i32, i32, i32, vp]
+        lib.b200shmem_dma_plan.argtypes = [sz, i32, ctypes.POINTER(sz), ctypes.POINTER(sz)]
+        lib.b200shmem_dma_engines.argtypes = [vp]
         _sigs = True
     return lib
 
 
 def _stream(stream) -> int:
     return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+def dma_plan(nbytes: int, gang: int = 0) -> list[tuple[int, int]]:
+    """(offset, length) of the parts a copy-engine transfer of ``nbytes`` is cut into. Needs no GPU."""
+    lib = _l()
+    offs, lens = (ctypes.c_size_t * 8)(), (ctypes.c_size_t * 8)()
+    n = lib.b200shmem_dma_plan(nbytes, gang, offs, lens)
+    return [(int(offs[i]), int(lens[i])) for i in range(n)]
 
 
 class Shmem:
@@ -121,6 +134,24 @@ class Shmem:
         nbytes = source.numel() * source.element_size()
         _lib.check(self.lib.b200shmem_putmem_signal_on_stream(self._ctx, dest.data_ptr(), source.data_ptr(), nbytes, sig.data_ptr(), value, op, pe,
                                                               _stream(stream)), "putmem_signal")
+
+    # ---- the same by copy engine: no SM takes part, large transfers are split over `gang` engines ----
+    def put_dma(self, dest: torch.Tensor, source: torch.Tensor, pe: int, gang: int = 0, stream=None) -> None:
+        nbytes = source.numel() * source.element_size()
+        _lib.check(self.lib.b200shmem_putmem_dma_on_stream(self._ctx, dest.data_ptr(), source.data_ptr(), nbytes, pe, gang, _stream(stream)), "putmem_dma")
+
+    def get_dma(self, dest: torch.Tensor, source: torch.Tensor, pe: int, gang: int = 0, stream=None) -> None:
+        nbytes = dest.numel() * dest.element_size()
+        _lib.check(self.lib.b200shmem_getmem_dma_on_stream(self._ctx, dest.data_ptr(), source.data_ptr(), nbytes, pe, gang, _stream(stream)), "getmem_dma")
+
+    def put_signal_dma(self, dest: torch.Tensor, source: torch.Tensor, sig: torch.Tensor, value: int, pe: int, op: int = SIGNAL_SET, gang: int = 0,
+                       stream=None) -> None:
+        nbytes = source.numel() * source.element_size()
+        _lib.check(self.lib.b200shmem_putmem_signal_dma_on_stream(self._ctx, dest.data_ptr(), source.data_ptr(), nbytes, sig.data_ptr(), value, op, pe,
+                                                                  gang, _stream(stream)), "putmem_signal_dma")
+
+    def dma_engines(self) -> int:
+        return int(self.lib.b200shmem_dma_engines(self._ctx))
 
     def wait_until(self, sig: torch.Tensor, cmp: int, value: int, stream=None) -> None:
         """Bounded device-side wait on a local signal word; a wait that runs out shows in ``take_status``."""

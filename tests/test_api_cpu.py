@@ -102,3 +102,18 @@ assert lib.ncclCommCount(None, ctypes.byref(n)) == 4
     files = list(tmp_path.glob("log.*.txt"))
     assert len(files) == 1 and files[0].name != "log.%p.txt"
     assert "invalid communicator handle" in files[0].read_text() and "invalid communicator handle" not in p.stderr
+
+
+def test_copy_engine_transfers_are_cut_into_whole_64k_parts_that_cover_the_message():
+    from rocm_systems_b200 import shmem
+
+    for nbytes, gang in [(1, 0), (65536, 4), (65537, 4), (8 << 20, 0), (64 << 20, 0), (3 << 20, 8), ((1 << 30) + 12345, 0), (100 << 20, 3), (1 << 20, 64)]:
+        parts = shmem.dma_plan(nbytes, gang)
+        assert 1 <= len(parts) <= 8
+        assert parts[0][0] == 0 and sum(n for _, n in parts) == nbytes
+        for (o0, n0), (o1, _) in zip(parts, parts[1:]):
+            assert o0 + n0 == o1 and n0 % 65536 == 0 and n0 > 0
+        sizes = [n for _, n in parts]
+        assert max(sizes) - min(sizes) <= 2 * 65536
+    assert len(shmem.dma_plan(1 << 20)) == 1 and len(shmem.dma_plan(8 << 20)) == 2 and len(shmem.dma_plan(64 << 20)) == 4
+    assert len(shmem.dma_plan(128 << 10, 8)) == 2            # never more parts than 64 KiB units
