@@ -205,6 +205,11 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="b200-smi", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--showall", action="store_true")
     ap.add_argument("--showtopo", action="store_true", help="weight, hops, type and bandwidth tables")
+    ap.add_argument("--showtopoweight", action="store_true", help="only the weight table")
+    ap.add_argument("--showtopohops", action="store_true", help="only the hops table")
+    ap.add_argument("--showtopotype", action="store_true", help="only the link-type table")
+    ap.add_argument("--showtopoaccess", action="store_true", help="only the peer-accessibility table")
+    ap.add_argument("--shownodesbw", action="store_true", help="only the bandwidth table")
     ap.add_argument("--showhealth", action="store_true")
     ap.add_argument("--showpids", action="store_true", help="compute processes per GPU")
     ap.add_argument("--showdriverversion", action="store_true")
@@ -257,7 +262,11 @@ def main(argv=None) -> int:
             for i, m in enumerate(out["modes"]):
                 print(f"GPU{i}: compute mode {m['compute_mode']}, persistence {m['persistence']}, MIG {m['mig']}, ECC {m['ecc']}")
     only_new = a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
-    if a.showall or not (a.showtopo or a.showhealth or a.setpowerlimit or only_new):
+    tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
+              ("typeName", "Link type between two GPUs", a.showtopotype), ("maxBandwidthMBps", "Max bandwidth (MB/s per direction)", a.shownodesbw),
+              ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]
+    one_table = any(t[2] for t in tables)
+    if a.showall or not (a.showtopo or one_table or a.showhealth or a.setpowerlimit or only_new):
         out["devices"] = [smi.info(i) for i in range(n)]
         if not a.json:
             print(f"{'GPU':<4}{'Name':<22}{'Bus':<18}{'SM MHz':<12}{'Power W':<10}{'Temp C':<8}{'Mem used/total GiB':<22}{'NVLink':<8}{'Throttle'}")
@@ -272,6 +281,12 @@ def main(argv=None) -> int:
             _print_matrix("Hops between two GPUs", out["topology"]["hops"], n)
             _print_matrix("Link type between two GPUs", out["topology"]["typeName"], n)
             _print_matrix("Max bandwidth (MB/s per direction)", out["topology"]["maxBandwidthMBps"], n)
+    if one_table and not a.showtopo:
+        out["topology"] = {k: _matrix(smi, k, n) for k, _, on in tables if on}
+        if not a.json:
+            for k, title, on in tables:
+                if on:
+                    _print_matrix(title, out["topology"][k], n)
     if a.showhealth:
         out["health"] = [dict(zip(("level", "reason"), smi.health(i))) for i in range(n)]
         if not a.json:

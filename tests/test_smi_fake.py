@@ -47,6 +47,14 @@ def test_cli_tables(fake_nvml):
     p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showall", "--showtopo", "--showhealth"], env=e, capture_output=True, text=True)
     assert p.returncode == 0, p.stderr
     assert "Weight between two GPUs" in p.stdout and "NVLINK" in p.stdout and "PASS" in p.stdout
+    # one table at a time, as the reference CLI offers them (rocm_smi.py showWeightTopology / showHopsTopology / showTypeTopology / showNodesBw)
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showtopohops", "--shownodesbw"], env=e, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    assert "Hops between two GPUs" in p.stdout and "Max bandwidth" in p.stdout
+    assert "Weight between two GPUs" not in p.stdout and "Name" not in p.stdout
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showtopoaccess", "--json"], env=e, capture_output=True, text=True)
+    import json
+    assert list(json.loads(p.stdout)["topology"]) == ["p2pAccessible"]
 
 
 def test_health_flags_link_down_and_ecc(fake_nvml):
