@@ -27,4 +27,15 @@ def test_device_api_example_compiles_for_sm100a(tmp_path):
 def test_python_example_parses():
     import ast
 
-    ast.parse((ROOT / "examples" / "train_llama_fsdp.py").read_text())
+    for name in ("train_llama_fsdp.py", "tensor_parallel_mlp.py", "moe_expert_parallel.py"):
+        ast.parse((ROOT / "examples" / name).read_text())
+
+
+@pytest.mark.parametrize("example,port,marker", [("pipeline_1f1b.py", 29921, "pipeline_1f1b OK"), ("long_context_attention.py", 29922, "long_context_attention OK")])
+def test_parallel_examples_run_on_cpu_ranks(example, port, marker):
+    import sys
+
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), str(ROOT / "examples" / example)], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert marker in p.stdout
