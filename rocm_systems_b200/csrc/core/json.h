@@ -50,8 +50,17 @@ class JsonParser {
     if (s_.compare(p_, n, w) == 0) { p_ += n; return true; }
     return false;
   }
+  // Containers nest at most kMaxDepth deep: the parser recurses once per level and the text is a user's file.
+  static constexpr int kMaxDepth = 64;
+  struct Level {
+    int& d;
+    explicit Level(int& depth) : d(depth) { d++; }
+    ~Level() { d--; }
+  };
   bool value(JsonValue* v) {
     if (p_ >= s_.size()) return false;
+    Level level(depth_);
+    if (depth_ > kMaxDepth) return false;
     char c = s_[p_];
     if (c == '{') {
       v->kind = JsonValue::Object;
@@ -123,6 +132,7 @@ class JsonParser {
   }
   const std::string& s_;
   size_t p_ = 0;
+  int depth_ = 0;
 };
 
 }  // namespace b200
