@@ -59,6 +59,26 @@ def check(name, got, want):
     return True
 
 
+GUARD_BYTES = 256
+GUARD_FILL = 0x5A
+
+
+def guarded(cnt, dt, dev, lead=0):
+    """A zeroed receive buffer of ``cnt`` elements with ``lead`` elements before it and 256 bytes after it filled with a
+    pattern, so that a kernel writing outside its output shows up. Returns (raw bytes, output view)."""
+    es = torch.empty((), dtype=dt).element_size()
+    raw = torch.full(((lead + cnt) * es + GUARD_BYTES,), GUARD_FILL, dtype=torch.uint8, device=dev)
+    raw[lead * es:(lead + cnt) * es] = 0
+    return raw, raw[:(lead + cnt) * es].view(dt)[lead:]
+
+
+def check_guards(name, raw, cnt, dt, lead=0):
+    es = torch.empty((), dtype=dt).element_size()
+    front, back = raw[:lead * es], raw[(lead + cnt) * es:]
+    if not (bool((front == GUARD_FILL).all()) and bool((back == GUARD_FILL).all())):
+        FAILS.append(f"{name}/guard: {int((front != GUARD_FILL).sum()) + int((back != GUARD_FILL).sum())} bytes outside the output were written")
+
+
 def set_algo(lib, algo):
     if algo == "auto":
         os.environ.pop("B200COLL_ALGO", None)
@@ -109,9 +129,10 @@ def main():
                     parts = [gen(r, cnt, dt, seed, lo, hi) for r in range(n)]
                     want = reduce_ref(parts, op)
                     # all_reduce out of place (misaligned by one element) and in place
-                    out = torch.zeros(cnt + 1, dtype=torch.float32, device=dev).to(dt) if dt.is_floating_point else torch.zeros(cnt + 1, dtype=dt, device=dev)
-                    comm.all_reduce(parts[rank], out[1:], op=op)
-                    check(f"all_reduce/{algo}/{dt}/{op}/{cnt}/oop", out[1:], want)
+                    raw, out = guarded(cnt, dt, dev, lead=1)
+                    comm.all_reduce(parts[rank], out, op=op)
+                    check(f"all_reduce/{algo}/{dt}/{op}/{cnt}/oop", out, want)
+                    check_guards(f"all_reduce/{algo}/{dt}/{op}/{cnt}/oop", raw, cnt, dt, lead=1)
                     inp = parts[rank].clone()
                     comm.all_reduce(inp, op=op)
                     check(f"all_reduce/{algo}/{dt}/{op}/{cnt}/inplace", inp, want)
@@ -122,9 +143,10 @@ def main():
                         if per:
                             full = [p[: per * n] for p in parts]
                             w = reduce_ref(full, op)[rank * per:(rank + 1) * per]
-                            o = torch.zeros(per, dtype=torch.float32, device=dev).to(dt) if dt.is_floating_point else torch.zeros(per, dtype=dt, device=dev)
+                            raw, o = guarded(per, dt, dev)
                             comm.reduce_scatter(full[rank].clone(), o, op=op)
                             check(f"reduce_scatter/{algo}/{dt}/{op}/{per}", o, w)
+                            check_guards(f"reduce_scatter/{algo}/{dt}/{op}/{per}", raw, per, dt)
                             # in place: recv is the rank's slice of send
                             s2 = full[rank].clone()
                             comm.reduce_scatter(s2, s2[rank * per:(rank + 1) * per], op=op)
@@ -140,9 +162,10 @@ def main():
                     for cnt in sizes:
                         seed += 1
                         parts = [gen(r, cnt, dt, seed, 0, 100) for r in range(n)]
-                        o = torch.zeros(cnt * n, dtype=torch.float32, device=dev).to(dt) if dt.is_floating_point else torch.zeros(cnt * n, dtype=dt, device=dev)
+                        raw, o = guarded(cnt * n, dt, dev)
                         comm.all_gather(parts[rank], o)
                         check(f"all_gather/{algo}/{dt}/{cnt}", o, torch.cat(parts).to(torch.float64 if dt.is_floating_point else torch.int64))
+                        check_guards(f"all_gather/{algo}/{dt}/{cnt}", raw, cnt * n, dt)
                         o2 = o.clone().zero_()
                         o2[rank * cnt:(rank + 1) * cnt] = parts[rank]
                         comm.all_gather(o2[rank * cnt:(rank + 1) * cnt], o2)
@@ -175,17 +198,19 @@ def main():
         for cnt in (1, 1000, 300007, 3 * (1 << 20) + 1):
             seed += 1
             parts = [gen(r, cnt * n, dt, seed, 0, 100) for r in range(n)]
-            o = torch.zeros_like(parts[0])
+            raw, o = guarded(cnt * n, dt, dev)
             comm.all_to_all(parts[rank], o)
             want = torch.cat([parts[s][rank * cnt:(rank + 1) * cnt] for s in range(n)])
             check(f"all_to_all/{dt}/{cnt}", o, want.to(torch.float64))
+            check_guards(f"all_to_all/{dt}/{cnt}", raw, cnt * n, dt)
             # ring send/recv
-            r_buf = torch.zeros(cnt, dtype=dt, device=dev)
+            raw, r_buf = guarded(cnt, dt, dev)
             comm.group_start()
             comm.send(parts[rank][:cnt], (rank + 1) % n)
             comm.recv(r_buf, (rank - 1) % n)
             comm.group_end()
             check(f"sendrecv/{dt}/{cnt}", r_buf, parts[(rank - 1) % n][:cnt].to(torch.float64))
+            check_guards(f"sendrecv/{dt}/{cnt}", raw, cnt, dt)
             # gather / scatter
             g = torch.zeros(cnt * n, dtype=dt, device=dev) if rank == 0 else None
             comm.gather(parts[rank][:cnt], g, root=0)
