@@ -19,22 +19,29 @@ from typing import Iterable, List
 
 # (pattern, cpu tests, gpu tests, needs native rebuild)
 RULES = [
+    ("rocm_systems_b200/csrc/CMakeLists.txt", ["tests/test_cmake_build_cpu.py"], [], False),
+    ("rocm_systems_b200/csrc/core/json.h", ["tests/test_sanitizers_cpu.py", "tests/test_planner_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/core/bootstrap.*", ["tests/test_bootstrap.py", "tests/test_sanitizers_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/core/topo.cc", ["tests/test_smi_fake.py", "tests/test_tools_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/core/health.cc", ["tests/test_smi_fake.py", "tests/test_tools_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/core/*", ["tests/test_api_cpu.py", "tests/test_bootstrap.py", "tests/test_planner_cpu.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
     ("rocm_systems_b200/csrc/coll/verifiable*", ["tests/test_verifiable_cpu.py"], [], True),
-    ("rocm_systems_b200/csrc/coll/*", ["tests/test_planner_cpu.py", "tests/test_protocol_model_cpu.py"], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py"], True),
-    ("rocm_systems_b200/csrc/shmem/*", [], ["tests/test_gpu_fused_multi.py"], True),
+    ("rocm_systems_b200/csrc/coll/*", ["tests/test_planner_cpu.py", "tests/test_protocol_model_cpu.py", "tests/test_staged_emulation_cpu.py"], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py"], True),
+    ("rocm_systems_b200/csrc/shmem/*", ["tests/test_api_cpu.py"], ["tests/test_gpu_fused_multi.py", "tests/test_zz_shmem_dma_gpu.py"], True),
+    ("rocm_systems_b200/csrc/fused/fsdp_kernels.cu", ["tests/test_fsdp_rscast_emulation_cpu.py", "tests/test_protocol_model_cpu.py"], ["tests/test_gpu_fused_multi.py"], True),
+    ("rocm_systems_b200/csrc/fused/gemm_fp8*", ["tests/test_fp8_reference_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/fused/*", [], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_no_alloc.py"], True),
     ("rocm_systems_b200/csrc/torch/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_collectives.py"], True),
-    ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),
+    ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py", "tests/test_sanitizers_cpu.py"], ["tests/test_profiler_gpu.py"], True),
     ("rocm_systems_b200/csrc/prof/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),
-    ("rocm_systems_b200/csrc/perf/*", ["tests/test_verifiable_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/perf/*", ["tests/test_verifiable_cpu.py", "tests/test_perf_cli_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/include/*", ["tests/test_bootstrap.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
     ("rocm_systems_b200/tools/*", ["tests/test_tools_cpu.py", "tests/test_smi_fake.py"], [], False),
-    ("rocm_systems_b200/parallel/pp.py", ["tests/test_parallel_cpu.py"], [], False),
-    ("rocm_systems_b200/parallel/cp.py", ["tests/test_parallel_cpu.py"], [], False),
+    ("rocm_systems_b200/parallel/pp.py", ["tests/test_parallel_cpu.py", "tests/test_examples_build_cpu.py"], [], False),
+    ("rocm_systems_b200/parallel/cp.py", ["tests/test_parallel_cpu.py", "tests/test_examples_build_cpu.py"], [], False),
+    ("rocm_systems_b200/parallel/fsdp.py", ["tests/test_fsdp_layout_cpu.py"], ["tests/test_gpu_fused_multi.py"], False),
+    ("rocm_systems_b200/ops/fp8.py", ["tests/test_fp8_reference_cpu.py"], [], False),
+    ("rocm_systems_b200/shmem.py", ["tests/test_api_cpu.py"], ["tests/test_zz_shmem_dma_gpu.py"], False),
     ("rocm_systems_b200/parallel/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_fused_multi.py"], False),
     ("rocm_systems_b200/utils/elastic.py", ["tests/test_elastic_cpu.py"], [], False),
     ("rocm_systems_b200/utils/checkpoint.py", ["tests/test_elastic_cpu.py"], [], False),
