@@ -20,7 +20,7 @@ def test_kernel_change_needs_gpu_and_rebuild():
 
 def test_specific_rules_win_over_general_ones():
     r = sel.select(["rocm_systems_b200/csrc/core/bootstrap.cc", "rocm_systems_b200/parallel/pp.py"])
-    assert r["cpu_tests"] == ["tests/test_bootstrap.py", "tests/test_parallel_cpu.py", "tests/test_sanitizers_cpu.py"] and not r["needs_gpu"]
+    assert r["cpu_tests"] == ["tests/test_bootstrap.py", "tests/test_examples_build_cpu.py", "tests/test_parallel_cpu.py", "tests/test_sanitizers_cpu.py"] and not r["needs_gpu"]
 
 
 def test_changed_test_file_runs_itself_and_unknown_paths_run_everything():
