@@ -84,6 +84,10 @@ def parser() -> argparse.ArgumentParser:
                    help="sample GPU readings (NVML), host CPU / memory and the command's resident set in the background")
     g = ap.add_argument_group("filtering")
     g.add_argument("--kernel-include-regex", default="")
+    g.add_argument("--kernel-exclude-regex", default="", help="drop kernels whose name matches (applied when the trace is imported)")
+    g.add_argument("--truncate-kernels", action="store_true", help="kernel names without return type, namespaces, template and call arguments")
+    g.add_argument("--collection-period", default="", metavar="DELAY_MS:DURATION_MS",
+                   help="keep only what started in this window after the first record (applied when the trace is imported)")
     g.add_argument("--max-records", type=int, default=0, help="per kind and process")
     g = ap.add_argument_group("output")
     g.add_argument("-d", "--output-directory", default="prof_out")
@@ -129,6 +133,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         os.remove(db_path)
     with tracedb.TraceDB(db_path) as db:
         total = sum(db.import_csv(f, command=" ".join(cmd)) for f in files)
+        if a.collection_period:
+            delay, _, duration = a.collection_period.partition(":")
+            db.keep_window(float(delay or 0), float(duration or 0))
+        if a.kernel_exclude_regex:
+            db.drop_kernels(a.kernel_exclude_regex)
+        if a.truncate_kernels:
+            db.truncate_kernel_names()
         summary = db.summary(a.top)
         if "pftrace" in a.output_format:
             db.to_perfetto(prefix + ".perfetto.json")

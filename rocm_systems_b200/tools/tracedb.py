@@ -177,6 +177,60 @@ class TraceDB:
         self.db.commit()
         return n
 
+    # ---- post-processing (what rocprofv3 offers as --kernel-exclude-regex, --truncate-kernels, --collection-period) ----
+    def drop_kernels(self, exclude_regex: str) -> int:
+        """Deletes kernel rows whose name matches; returns how many went."""
+        rx = re.compile(exclude_regex)
+        ids = [i for i, v in self.db.execute("select id, value from string") if rx.search(v)]
+        n = 0
+        for i in ids:
+            n += self.db.execute("delete from kernel_dispatch where name_id = ?", (i,)).rowcount
+        self.db.commit()
+        return n
+
+    @staticmethod
+    def short_kernel_name(name: str) -> str:
+        """``void ns::kernel<int, Foo<3> >(Args...)`` -> ``kernel``: return type, namespaces, template and call arguments go."""
+        depth, out = 0, []
+        for ch in name:
+            if ch in "<(":
+                depth += 1
+            elif ch in ">)":
+                depth -= 1
+            elif depth == 0:
+                out.append(ch)
+        flat = "".join(out).strip()
+        flat = flat.split(" ")[-1] if " " in flat else flat
+        return flat.split("::")[-1] or name
+
+    def truncate_kernel_names(self) -> int:
+        """Rewrites every kernel name to its short form; instantiations of one template then aggregate in the statistics."""
+        names = self.db.execute("select distinct s.id, s.value from string s join kernel_dispatch k on k.name_id = s.id").fetchall()
+        changed = 0
+        for sid, value in names:
+            short = self.short_kernel_name(value)
+            if short != value:
+                self.db.execute("update kernel_dispatch set name_id = ? where name_id = ?", (self.string_id(short), sid))
+                changed += 1
+        self.db.commit()
+        return changed
+
+    def keep_window(self, delay_ms: float, duration_ms: float) -> int:
+        """Keeps only what started within ``duration_ms`` after ``delay_ms`` from the first record; returns rows deleted."""
+        starts = [r[0] for r in (self.db.execute("select min(start_ns) from kernel_dispatch").fetchone(), self.db.execute("select min(start_ns) from region").fetchone(),
+                                 self.db.execute("select min(host_start_ns) from collective").fetchone(), self.db.execute("select min(start_ns) from memory_copy").fetchone())
+                  if r and r[0] is not None]
+        if not starts:
+            return 0
+        lo = min(starts) + int(delay_ms * 1e6)
+        hi = lo + int(duration_ms * 1e6) if duration_ms > 0 else 1 << 62
+        n = 0
+        for table, col in (("kernel_dispatch", "start_ns"), ("memory_copy", "start_ns"), ("region", "start_ns"), ("collective", "host_start_ns")):
+            n += self.db.execute(f"delete from {table} where {col} < ? or {col} >= ?", (lo, hi)).rowcount
+        n += self.db.execute("delete from counter_sample where ts_ns < ? or ts_ns >= ?", (lo, hi)).rowcount
+        self.db.commit()
+        return n
+
     def merge(self, other_path: str) -> None:
         """Appends another database (for example another rank's) into this one."""
         src = sqlite3.connect(other_path)

@@ -430,3 +430,39 @@ srv.shutdown(); t.stop()
 print('ok')
 """, {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "2", "FAKE_NVML_RAMP": "1"})
     assert "ok" in out
+
+
+def test_tracedb_postprocessing_filters(tmp_path):
+    """Exclusion by regex, short kernel names and the collection window (rocprofv3's --kernel-exclude-regex,
+    --truncate-kernels and --collection-period, applied to the imported trace)."""
+    from rocm_systems_b200.tools import tracedb
+
+    assert tracedb.TraceDB.short_kernel_name("void b200::gemm::gemmKernel<256, b200::gemm::PlainPolicy<256> >(b200::gemm::Params, int)") == "gemmKernel"
+    assert tracedb.TraceDB.short_kernel_name("rmsnorm") == "rmsnorm"
+    assert tracedb.TraceDB.short_kernel_name("void at::native::(anonymous namespace)::vectorized_elementwise_kernel<4, Foo>(int)") == "vectorized_elementwise_kernel"
+    csv_text = KERNEL_CSV.replace('"gemmKernel<Cfg>",1,', '"void ns::gemmKernel<128, P<128> >(Params)",1,').replace('"gemmKernel<Cfg>",2,', '"void ns::gemmKernel<256, P<256> >(Params)",2,')
+    (tmp_path / "t.100_kernel_trace.csv").write_text(csv_text)
+    (tmp_path / "t.rank0.csv").write_text(COLL_CSV)
+    with tracedb.TraceDB(str(tmp_path / "a.db")) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        assert len(db.summary()["kernels"]) == 3                               # two instantiations and rmsnorm
+        assert db.truncate_kernel_names() == 2
+        top = db.summary()["kernels"][0]
+        assert top["name"] == "gemmKernel" and top["calls"] == 2               # the instantiations aggregate
+        assert db.drop_kernels("^rms") == 1
+        assert [k["name"] for k in db.summary()["kernels"]] == ["gemmKernel"]
+    with tracedb.TraceDB(str(tmp_path / "b.db")) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        # first record starts at 900 ns (a collective's host entry); keep [900 + 5000, 900 + 5000 + 4000) ns
+        gone = db.keep_window(0.005, 0.004)
+        names, rows = db.query("select start_ns from kernels order by start_ns")
+        assert rows == [(6000,), (9500,)] and gone == 1 + 2 + 2      # one kernel, both collectives and their two API regions
+
+
+def test_prof_launcher_applies_filters(tmp_path):
+    from rocm_systems_b200.tools import prof
+
+    a = prof.parser().parse_args(["--kernel-trace", "--kernel-exclude-regex", "rms", "--truncate-kernels", "--collection-period", "0:100", "--", "true"])
+    assert a.kernel_exclude_regex == "rms" and a.truncate_kernels and a.collection_period == "0:100"
