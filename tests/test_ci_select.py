@@ -15,7 +15,7 @@ def test_docs_only_changes_need_nothing():
 
 def test_kernel_change_needs_gpu_and_rebuild():
     r = sel.select(["rocm_systems_b200/csrc/coll/kernels.cuh"])
-    assert r["rebuild_native"] and r["needs_gpu"] and "tests/test_gpu_collectives.py" in r["gpu_tests"] and r["cpu_tests"] == ["tests/test_planner_cpu.py", "tests/test_protocol_model_cpu.py", "tests/test_staged_emulation_cpu.py"]
+    assert r["rebuild_native"] and r["needs_gpu"] and "tests/test_gpu_collectives.py" in r["gpu_tests"] and r["cpu_tests"] == ["tests/test_planner_cpu.py", "tests/test_protocol_interleavings_cpu.py", "tests/test_protocol_model_cpu.py", "tests/test_staged_emulation_cpu.py"]
 
 
 def test_specific_rules_win_over_general_ones():

@@ -1,0 +1,179 @@
+"""Exhaustive interleaving checks of the two flag protocols that are not barrier-based
+(csrc/coll/kernels.cuh): the send/recv FIFO with credits (kP2p) and the flag-in-data all-reduce (kLLAllReduce).
+
+Each rank is a small state machine whose steps are the protocol's individually atomic memory operations
+(a wait that is satisfied, one piece of a slot copy, a release store of a counter, one 16-byte line store).
+Every reachable interleaving is explored. A run must never read a slot or a line that does not hold exactly
+the message it expects, and must never get stuck before every rank has finished. The same explorer has to find a
+counterexample in broken variants of each protocol (no credit wait, counter published before the data, a single
+line buffer), which shows that it can."""
+from collections import deque
+
+
+def explore(initial, step, done, nprocs, limit=2_000_000):
+    """Breadth-first search over all interleavings. ``step(state, pid)`` returns the next state, None when pid cannot
+    move (blocked or finished), or raises AssertionError on a safety violation. Returns (states, deadlocks)."""
+    seen = {initial}
+    queue = deque([initial])
+    deadlocks = 0
+    while queue:
+        s = queue.popleft()
+        moved = False
+        for pid in range(nprocs):
+            t = step(s, pid)
+            if t is None:
+                continue
+            moved = True
+            if t not in seen:
+                seen.add(t)
+                assert len(seen) < limit, "state space larger than expected"
+                queue.append(t)
+        if not moved and not done(s):
+            deadlocks += 1
+    return len(seen), deadlocks
+
+
+# ---- FIFO with credits ---------------------------------------------------------------------------------------------
+# State: (s_pc, sent, r_pc, recvd, tail, head, slots) with slots a tuple of (first half, second half) message ids.
+def fifo_model(nslots, nmsgs, wait_credit=True, publish_after_write=True):
+    def step(st, pid):
+        s_pc, sent, r_pc, recvd, tail, head, slots = st
+        if pid == 0:  # sender
+            if sent == nmsgs:
+                return None
+            slot = sent % nslots
+            if s_pc == 0:  # waitGe64(head, sent + 1 - slots)
+                if wait_credit and head < sent + 1 - nslots:
+                    return None
+                if not publish_after_write:  # broken variant: the tail moves before the data is there
+                    return (1, sent, r_pc, recvd, sent + 1, head, slots)
+                return (1, sent, r_pc, recvd, tail, head, slots)
+            if s_pc in (1, 2):  # the copy into the slot, in two pieces
+                a, b = slots[slot]
+                piece = (sent, b) if s_pc == 1 else (a, sent)
+                return (s_pc + 1, sent, r_pc, recvd, tail, head, slots[:slot] + (piece,) + slots[slot + 1:])
+            return (0, sent + 1, r_pc, recvd, max(tail, sent + 1), head, slots)  # fence + release store of the tail
+        if recvd == nmsgs:  # receiver
+            return None
+        slot = recvd % nslots
+        if r_pc == 0:  # waitGe64(tail, recvd + 1)
+            return (s_pc, sent, 1, recvd, tail, head, slots) if tail >= recvd + 1 else None
+        if r_pc in (1, 2):  # the copy out of the slot, in two pieces
+            got = slots[slot][r_pc - 1]
+            assert got == recvd, f"message {recvd}: read piece {r_pc} of slot {slot} holding {got}"
+            return (s_pc, sent, r_pc + 1, recvd, tail, head, slots)
+        return (s_pc, sent, 0, recvd + 1, tail, recvd + 1, slots)  # release store of the head
+
+    initial = (0, 0, 0, 0, 0, 0, tuple((-1, -1) for _ in range(nslots)))
+    return initial, step, (lambda st: st[1] == nmsgs and st[3] == nmsgs)
+
+
+def test_fifo_with_credits_delivers_every_message_in_every_interleaving():
+    for nslots, nmsgs in [(1, 4), (2, 7), (4, 11)]:
+        initial, step, done = fifo_model(nslots, nmsgs)
+        states, deadlocks = explore(initial, step, done, 2)
+        assert deadlocks == 0 and states > nmsgs * 8
+
+
+def _violates(initial, step, done, nprocs):
+    try:
+        _, deadlocks = explore(initial, step, done, nprocs)
+    except AssertionError:
+        return True
+    return deadlocks > 0
+
+
+def test_fifo_checker_finds_the_bugs_it_is_meant_to_find():
+    assert _violates(*fifo_model(2, 5, wait_credit=False), 2)            # a slot is overwritten before it was read
+    assert _violates(*fifo_model(2, 5, publish_after_write=False), 2)    # the receiver is told before the data is there
+
+
+# ---- flag-in-data all-reduce -----------------------------------------------------------------------------------------
+# Per rank: call number k (1-based), phase ("send", next peer index) or ("recv", next peer index); memory:
+# line[dst][buf][src] = (data, flag) written in one store. Data of rank r in call k is (r, k).
+def ll_model(n, ncalls, nbufs=2):
+    peers = [[(r + d) % n for d in range(1, n)] for r in range(n)]
+
+    def step(st, pid):
+        procs, mem = st
+        k, phase, idx = procs[pid]
+        if k > ncalls:
+            return None
+        buf = k % nbufs
+        if phase == 0:  # one 16-byte line {data, flag} into the next peer
+            dst = peers[pid][idx]
+            cell = (dst * nbufs + buf) * n + pid
+            mem2 = mem[:cell] + (((pid, k), k),) + mem[cell + 1:]
+            nxt = (k, 0, idx + 1) if idx + 1 < n - 1 else (k, 1, 0)
+            return (procs[:pid] + (nxt,) + procs[pid + 1:], mem2)
+        src = peers[pid][idx]  # spin on the line of the next source
+        data, flag = mem[(pid * nbufs + buf) * n + src]
+        if flag != k:
+            return None
+        assert data == (src, k), f"rank {pid} call {k}: line of {src} holds {data}"
+        nxt = (k, 1, idx + 1) if idx + 1 < n - 1 else (k + 1, 0, 0)
+        return (procs[:pid] + (nxt,) + procs[pid + 1:], mem)
+
+    initial = (tuple((1, 0, 0) for _ in range(n)), tuple(((None, None), 0) for _ in range(n * nbufs * n)))
+    return initial, step, (lambda st: all(p[0] > ncalls for p in st[0]))
+
+
+def test_ll_all_reduce_with_two_alternating_buffers_never_loses_a_line():
+    for n, ncalls in [(2, 6), (3, 4)]:
+        initial, step, done = ll_model(n, ncalls)
+        states, deadlocks = explore(initial, step, done, n)
+        assert deadlocks == 0 and states > 3 * n * ncalls
+
+
+def test_ll_checker_finds_the_single_buffer_overwrite():
+    # With one buffer a rank that is a call ahead overwrites a line its peer has not consumed; the peer then waits for a
+    # flag value that is gone.
+    assert _violates(*ll_model(2, 3, nbufs=1), 2)
+    assert _violates(*ll_model(3, 3, nbufs=1), 3)
+
+
+def test_ll_all_reduce_four_ranks():
+    initial, step, done = ll_model(4, 2)
+    states, deadlocks = explore(initial, step, done, 4)
+    assert deadlocks == 0 and states > 1000
+
+
+# ---- the lane barrier -----------------------------------------------------------------------------------------------
+# ctaBarrier: epoch += 1; store the epoch into slot [rank] of every peer (release); wait until every slot of the own
+# workspace has reached the epoch (acquire). Between barriers a rank does one unit of "work" on a shared counter that
+# lets the model see whether anybody ran ahead: work of round k may start only after every rank finished round k - 1.
+def barrier_model(n, rounds, compare_ge=True):
+    def step(st, pid):
+        procs, slots, work = st
+        k, pc, idx = procs[pid]          # round (1-based), 0 = work, 1 = stores, 2 = waits
+        if k > rounds:
+            return None
+        if pc == 0:
+            assert all(w >= k - 1 for w in work), f"rank {pid} started round {k} while a peer had not finished round {k - 1}: {work}"
+            work2 = work[:pid] + (k,) + work[pid + 1:]
+            return (procs[:pid] + ((k, 1, 0),) + procs[pid + 1:], slots, work2)
+        if pc == 1:  # one release store per peer, own slot included
+            cell = idx * n + pid
+            slots2 = slots[:cell] + (k,) + slots[cell + 1:]
+            nxt = (k, 1, idx + 1) if idx + 1 < n else (k, 2, 0)
+            return (procs[:pid] + (nxt,) + procs[pid + 1:], slots2, work)
+        seen = slots[pid * n + idx]
+        if (seen < k) if compare_ge else (seen != k):
+            return None
+        nxt = (k, 2, idx + 1) if idx + 1 < n else (k + 1, 0, 0)
+        return (procs[:pid] + (nxt,) + procs[pid + 1:], slots, work)
+
+    initial = (tuple((1, 0, 0) for _ in range(n)), tuple(0 for _ in range(n * n)), tuple(0 for _ in range(n)))
+    return initial, step, (lambda st: all(p[0] > rounds for p in st[0]))
+
+
+def test_lane_barrier_orders_rounds_and_never_sticks():
+    for n, rounds in [(2, 5), (3, 3)]:
+        initial, step, done = barrier_model(n, rounds)
+        states, deadlocks = explore(initial, step, done, n)
+        assert deadlocks == 0 and states > 10 * n * rounds
+
+
+def test_barrier_checker_finds_the_equality_wait():
+    # Waiting for "slot == epoch" instead of ">=": a fast peer may already have stored the next epoch.
+    assert _violates(*barrier_model(2, 3, compare_ge=False), 2)
