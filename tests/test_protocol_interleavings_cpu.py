@@ -177,3 +177,127 @@ def test_lane_barrier_orders_rounds_and_never_sticks():
 def test_barrier_checker_finds_the_equality_wait():
     # Waiting for "slot == epoch" instead of ">=": a fast peer may already have stored the next epoch.
     assert _violates(*barrier_model(2, 3, compare_ge=False), 2)
+
+
+# ---- expert-parallel dispatch / combine across calls (csrc/fused/ep_kernels.cu) ------------------------------------
+# One expert per rank, every rank sends one row to every rank (itself included) per call. Steps of a rank in call k,
+# parity p = k & 1:  clear cnt[p ^ 1] locally;  per destination: reserve a row (remote atomic add on cnt[p]) and store
+# the payload;  store done[p][rank] = k // 2 + 1 at every rank;  wait until every done[p][*] has reached it;  read the
+# local payload rows and cnt[p] (dequantise + expert GEMM) and write the output rows;  barrier;  pull the own token's
+# output row from every owner (combine). Payload and output buffers are NOT double buffered, only the counters are.
+def ep_model(n, ncalls, barrier_before_combine=True):
+    CLEAR, SEND, DONE, WAIT, EXPERT, BAR_IN, BAR_OUT, PULL = range(8)
+
+    def step(st, pid):
+        procs, cnt, done, payload, out, bar = st
+        k, pc, idx = procs[pid]
+        if k > ncalls:
+            return None
+        p = k & 1
+        mark = k // 2 + 1
+
+        def upd(t, i, v):
+            return t[:i] + (v,) + t[i + 1:]
+
+        def goto(npc, nidx=0, nk=None):
+            return upd(procs, pid, (k if nk is None else nk, npc, nidx))
+
+        if pc == CLEAR:
+            return (goto(SEND), upd(cnt, pid * 2 + (p ^ 1), 0), done, payload, out, bar)
+        if pc == SEND:  # reserve a row at rank idx and store (source, call) there
+            row = cnt[idx * 2 + p]
+            assert row < n, f"rank {pid} call {k}: expert of rank {idx} already holds {row} rows"
+            cnt2 = upd(cnt, idx * 2 + p, row + 1)
+            pay2 = upd(payload, idx * n + row, (pid, k))
+            return (goto(SEND, idx + 1) if idx + 1 < n else goto(DONE), cnt2, done, pay2, out, bar)
+        if pc == DONE:
+            d2 = upd(done, (idx * 2 + p) * n + pid, mark)
+            return (goto(DONE, idx + 1) if idx + 1 < n else goto(WAIT), cnt, d2, payload, out, bar)
+        if pc == WAIT:
+            if done[(pid * 2 + p) * n + idx] < mark:
+                return None
+            return (goto(WAIT, idx + 1) if idx + 1 < n else goto(EXPERT), cnt, done, payload, out, bar)
+        if pc == EXPERT:  # every row of this call is here, nothing of another call; outputs keyed by source rank
+            assert cnt[pid * 2 + p] == n, f"rank {pid} call {k}: {cnt[pid * 2 + p]} rows"
+            rows = payload[pid * n:(pid + 1) * n]
+            assert sorted(rows) == [(s, k) for s in range(n)], f"rank {pid} call {k}: rows {rows}"
+            out2 = out
+            for s, _ in rows:
+                out2 = upd(out2, pid * n + s, k)
+            return (goto(BAR_IN if barrier_before_combine else PULL), cnt, done, payload, out2, bar)
+        if pc == BAR_IN:  # the communicator's barrier: arrive, then wait for everybody
+            return (goto(BAR_OUT), cnt, done, payload, out, upd(bar, pid, bar[pid] + 1))
+        if pc == BAR_OUT:
+            if min(bar) < bar[pid]:
+                return None
+            return (goto(PULL), cnt, done, payload, out, bar)
+        got = out[idx * n + pid]  # PULL: the row expert idx computed for this rank's token
+        assert got == k, f"rank {pid} call {k}: pulled an output of call {got} from rank {idx}"
+        return (goto(PULL, idx + 1) if idx + 1 < n else goto(CLEAR, 0, k + 1), cnt, done, payload, out, bar)
+
+    initial = (tuple((1, CLEAR, 0) for _ in range(n)), tuple(0 for _ in range(2 * n)), tuple(0 for _ in range(2 * n * n)),
+               tuple((None, 0) for _ in range(n * n)), tuple(0 for _ in range(n * n)), tuple(0 for _ in range(n)))
+    return initial, step, (lambda st: all(pr[0] > ncalls for pr in st[0]))
+
+
+def test_ep_dispatch_combine_is_safe_across_calls_with_single_payload_and_output_buffers():
+    initial, step, done = ep_model(2, 4)
+    states, deadlocks = explore(initial, step, done, 2)
+    assert deadlocks == 0 and states > 200
+    initial, step, done = ep_model(3, 2)
+    states, deadlocks = explore(initial, step, done, 3)
+    assert deadlocks == 0
+
+
+def test_ep_checker_finds_the_missing_barrier():
+    # Without the barrier between the expert GEMMs and the combine a rank pulls an output row its owner has not written yet.
+    assert _violates(*ep_model(2, 2, barrier_before_combine=False), 2)
+
+
+# ---- GEMM -> reduce-scatter without a barrier (csrc/fused/tp_fused.cu) -------------------------------------------------
+# One tile per owner. In call k (parity p) a rank stores its partial of every tile into the owner's staging
+# [p][source], remote owners first, and bumps the owner's counter [p]; then it waits until its own counter [p] shows
+# all n partials of this call and sums them. Counters only grow: the target of call k is n * (calls of that parity so
+# far). Nothing else orders the ranks; the claim is that two staging halves are enough.
+def gemm_rs_model(n, ncalls, nbufs=2):
+    def step(st, pid):
+        procs, stage, cnt = st
+        k, pc, idx = procs[pid]
+        if k > ncalls:
+            return None
+        p = k % nbufs
+        target = n * ((k + nbufs - 1) // nbufs) if nbufs == 2 else n * k
+
+        def upd(t, i, v):
+            return t[:i] + (v,) + t[i + 1:]
+
+        if pc == 0:  # store the partial of the tile owned by rank (pid + 1 + idx) % n
+            owner = (pid + 1 + idx) % n
+            return (upd(procs, pid, (k, 1, idx)), upd(stage, (owner * nbufs + p) * n + pid, (pid, k)), cnt)
+        if pc == 1:  # red.release.sys.add on the owner's counter
+            owner = (pid + 1 + idx) % n
+            cell = owner * nbufs + p
+            nxt = (k, 0, idx + 1) if idx + 1 < n else (k, 2, 0)
+            return (upd(procs, pid, nxt), stage, upd(cnt, cell, cnt[cell] + 1))
+        if pc == 2:  # reducer: wait for the counter, then read the n partials one by one
+            if cnt[pid * nbufs + p] < target:
+                return None
+            return (upd(procs, pid, (k, 3, 0)), stage, cnt)
+        got = stage[(pid * nbufs + p) * n + idx]
+        assert got == (idx, k), f"rank {pid} call {k}: partial of rank {idx} is {got}"
+        nxt = (k, 3, idx + 1) if idx + 1 < n else (k + 1, 0, 0)
+        return (upd(procs, pid, nxt), stage, cnt)
+
+    initial = (tuple((1, 0, 0) for _ in range(n)), tuple((None, 0) for _ in range(n * nbufs * n)), tuple(0 for _ in range(n * nbufs)))
+    return initial, step, (lambda st: all(pr[0] > ncalls for pr in st[0]))
+
+
+def test_gemm_reduce_scatter_needs_no_barrier_with_two_staging_halves():
+    for n, ncalls in [(2, 6), (3, 3)]:
+        initial, step, done = gemm_rs_model(n, ncalls)
+        states, deadlocks = explore(initial, step, done, n)
+        assert deadlocks == 0 and states > 20 * ncalls
+
+
+def test_gemm_rs_checker_finds_the_single_half_overwrite():
+    assert _violates(*gemm_rs_model(2, 3, nbufs=1), 2)
