@@ -42,6 +42,45 @@ class LlamaConfig:
         return LlamaConfig()
 
     @staticmethod
+    def llama3_70b() -> "LlamaConfig":
+        return LlamaConfig(hidden=8192, layers=80, heads=64, kv_heads=8, ffn=28672, seq_len=8192)
+
+    @staticmethod
+    def llama32_1b() -> "LlamaConfig":
+        return LlamaConfig(hidden=2048, layers=16, heads=32, kv_heads=8, ffn=8192, seq_len=4096)
+
+    @staticmethod
+    def llama32_3b() -> "LlamaConfig":
+        return LlamaConfig(hidden=3072, layers=28, heads=24, kv_heads=8, ffn=8192, seq_len=4096)
+
+    @staticmethod
+    def llama2_7b() -> "LlamaConfig":
+        return LlamaConfig(vocab=32000, hidden=4096, layers=32, heads=32, kv_heads=32, ffn=11008, rope_theta=10000.0, seq_len=4096)
+
+    @staticmethod
+    def by_name(name: str) -> "LlamaConfig":
+        table = {"llama3-8b": LlamaConfig.llama3_8b, "llama3-70b": LlamaConfig.llama3_70b, "llama3.2-1b": LlamaConfig.llama32_1b,
+                 "llama3.2-3b": LlamaConfig.llama32_3b, "llama2-7b": LlamaConfig.llama2_7b, "tiny": LlamaConfig.tiny}
+        if name not in table:
+            raise KeyError(f"unknown model {name!r}; known: {', '.join(sorted(table))}")
+        return table[name]()
+
+    def memory_per_gpu_gib(self, world: int, micro_tokens: int) -> dict:
+        """A planning estimate for ZeRO-3 training on ``world`` GPUs: persistent state per GPU (bf16 shard, fp32 master
+        and both AdamW moments: 14 bytes per parameter / world), the two gathered units alive at once, and the
+        activations kept for backward (about 34 bytes per token, layer and hidden channel with bf16 activations and no
+        recomputation, plus the logits)."""
+        params = self.param_count()
+        d = self.head_dim
+        unit = self.hidden * (self.heads + 2 * self.kv_heads) * d + self.hidden * self.hidden + 3 * self.hidden * self.ffn + 2 * self.hidden
+        unit = max(unit, self.vocab * self.hidden)
+        state = 14.0 * params / world
+        gathered = 2 * 2.0 * unit + 2.0 * unit          # two parameter buffers and one gradient buffer
+        acts = micro_tokens * (34.0 * self.hidden * self.layers + 6.0 * self.vocab)
+        gib = 1 << 30
+        return {"state": state / gib, "gathered": gathered / gib, "activations": acts / gib, "total": (state + gathered + acts) / gib}
+
+    @staticmethod
     def tiny(seq_len: int = 128) -> "LlamaConfig":
         return LlamaConfig(vocab=1024, hidden=256, layers=2, heads=4, kv_heads=2, ffn=512, seq_len=seq_len)
 

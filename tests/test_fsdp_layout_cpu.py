@@ -82,3 +82,35 @@ def test_checkpoint_round_trip_across_world_sizes(tmp_path, old_world, new_world
         got = torch.cat([getattr(e.units[0], k) for e in news])
         assert torch.equal(got[:want[k].numel()], want[k])
         assert torch.equal(got[want[k].numel():], torch.zeros(got.numel() - want[k].numel()))   # padding reads zero
+
+
+def test_model_table_and_parameter_counts():
+    from rocm_systems_b200.models.llama import LlamaConfig
+
+    assert abs(LlamaConfig.by_name("llama3-8b").param_count() / 1e9 - 8.03) < 0.01
+    assert abs(LlamaConfig.by_name("llama3-70b").param_count() / 1e9 - 70.55) < 0.05
+    assert abs(LlamaConfig.by_name("llama2-7b").param_count() / 1e9 - 6.74) < 0.01
+    assert abs(LlamaConfig.by_name("llama3.2-1b").param_count() / 1e9 - 1.50) < 0.01      # untied embeddings: 1.24 B + the output matrix
+    with pytest.raises(KeyError):
+        LlamaConfig.by_name("nope")
+    m8 = LlamaConfig.llama3_8b().memory_per_gpu_gib(8, 4096)
+    m1 = LlamaConfig.llama3_8b().memory_per_gpu_gib(1, 4096)
+    assert abs(m1["state"] - 14 * 8.03e9 / 2**30) < 0.5 and abs(m8["state"] * 8 - m1["state"]) < 1e-6
+    assert m1["total"] < 180                                                   # the benchmark's configuration fits one 180 GB GPU
+    big = LlamaConfig.llama3_70b()
+    assert big.memory_per_gpu_gib(8, 8192)["total"] > 180 > big.memory_per_gpu_gib(8, 2048)["total"]   # 70B on 8 GPUs: 2048 tokens per micro-batch fit, 8192 do not
+
+
+def test_learning_rate_schedules():
+    from rocm_systems_b200.utils import schedule
+
+    s = schedule.warmup_cosine(peak=1.0, warmup=10, total=110, floor=0.1)
+    assert s(0) == pytest.approx(0.1) and s(9) == pytest.approx(1.0) and s(10) == pytest.approx(1.0)
+    assert s(60) == pytest.approx(0.55) and s(110) == pytest.approx(0.1) and s(10_000) == pytest.approx(0.1)
+    assert all(s(i) >= s(i + 1) for i in range(10, 120))
+    lin = schedule.warmup_linear(1.0, 0, 100)
+    assert lin(0) == 1.0 and lin(50) == pytest.approx(0.5) and lin(100) == 0.0
+    wsd = schedule.warmup_stable_decay(2.0, 5, 50, 100, floor=0.0)
+    assert wsd(4) == pytest.approx(2.0) and wsd(49) == 2.0 and wsd(75) == pytest.approx(1.0) and wsd(100) == 0.0
+    with pytest.raises(ValueError):
+        schedule.warmup_cosine(1.0, 10, 10)
