@@ -46,6 +46,7 @@ class AdamWConfig:
     betas: Tuple[float, float] = (0.9, 0.95)
     eps: float = 1e-8
     weight_decay: float = 0.1
+    max_grad_norm: Optional[float] = None  # clip the global gradient norm to this; None: every unit updates right behind its reduce-scatter
 
 
 class FlatUnit:
@@ -129,6 +130,10 @@ class FSDPEngine:
         self._pending: List[torch.cuda.Event] = []
         self._sym_shards = None
         self._grad_slots = None
+        # Global-norm clipping: the update of every unit waits for the norm of all of them.
+        self._held: List[tuple] = []          # (unit, reduced gradient shard) until finish_step
+        self._sumsq: Optional[torch.Tensor] = None
+        self.last_grad_norm: Optional[torch.Tensor] = None   # device scalar of the latest step (before clipping)
         if sym_shards and self.world > 1 and hasattr(comm, "sym_alloc"):
             self._place_shards_in_symmetric_memory()
 
@@ -237,15 +242,42 @@ class FSDPEngine:
                 read = torch.cuda.Event()
                 read.record(self.comm_stream)  # the reduce-scatter is behind us on this stream: the buffer may be reused after it
                 self._grad_slot_done[unit.grad_slot] = read
-            ops.adamw_(unit.master, unit.m, unit.v, gshard, unit.shard, o.lr, o.betas, o.eps, o.weight_decay, self.step_count + 1)
+            if o.max_grad_norm is not None:
+                sq = torch.sum(gshard.float() ** 2) if gshard.dtype != torch.float32 else torch.dot(gshard, gshard)
+                self._sumsq = sq if self._sumsq is None else self._sumsq + sq
+                self._held.append((unit, gshard))
+            else:
+                ops.adamw_(unit.master, unit.m, unit.v, gshard, unit.shard, o.lr, o.betas, o.eps, o.weight_decay, self.step_count + 1)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
         src.record_stream(self.comm_stream)
         unit.full_grad = None
         self._pending.append(done)
 
+    def _clip_and_update(self) -> None:
+        """With ``max_grad_norm``: sum the squared norms over the ranks, scale every held gradient shard by
+        ``min(1, max_norm / norm)`` on the device (no host round trip) and run the deferred AdamW updates."""
+        o = self.opt
+        with torch.cuda.stream(self.comm_stream):
+            total = self._sumsq.reshape(1).float()
+            if self.world > 1:
+                self.comm.all_reduce(total, op="sum", stream=self.comm_stream)
+            norm = total.sqrt()
+            coef = (o.max_grad_norm / (norm + 1e-6)).clamp(max=1.0)
+            self.last_grad_norm = norm
+            for unit, gshard in self._held:
+                gshard.mul_(coef.to(gshard.dtype))
+                ops.adamw_(unit.master, unit.m, unit.v, gshard, unit.shard, o.lr, o.betas, o.eps, o.weight_decay, self.step_count + 1)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+        self._held.clear()
+        self._sumsq = None
+        self._pending.append(done)
+
     def finish_step(self) -> None:
         """Join the communication stream: after this the shards hold the updated weights."""
+        if self._held:
+            self._clip_and_update()
         cur = torch.cuda.current_stream()
         for ev in self._pending:
             cur.wait_event(ev)
