@@ -385,6 +385,9 @@ static ncclResult_t dmaCopy(b200shmem_ctx_t ctx, char* dst, const char* src, siz
     return ncclSuccess;
   }
   BCHECK(dmaSetup(ctx, g - 1));
+  // The fork / join events are shared by all transfers of the context: one transfer is enqueued at a time.
+  static std::mutex enqueueMu;
+  std::lock_guard<std::mutex> lk(enqueueMu);
   // Part 0 stays on the caller's stream; the others fork after everything already queued there and join before
   // anything queued later.
   BCUDA(cudaEventRecord(ctx->dmaFork, stream));
