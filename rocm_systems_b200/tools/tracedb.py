@@ -311,6 +311,16 @@ class TraceDB:
             if e > s:
                 events.append({"ph": "X", "pid": pid, "tid": "collectives (device)", "name": name, "cat": "collective", "ts": s / 1e3,
                                "dur": (e - s) / 1e3, "args": {"bytes": nbytes, "rank": rank}})
+        # Communication volume as cumulative counter tracks per rank, classified the way the reference's system profiler does
+        # (rocprofiler-systems source/lib/rocprof-sys/library/rocprofiler-sdk/rccl.cpp:105-180): gather-like and reducing
+        # collectives and receives count as received bytes, broadcast / reduce-scatter / sends as sent bytes.
+        sent_like = ("ncclBroadcast", "ncclBcast", "ncclReduceScatter", "ncclSend", "ncclScatter")
+        totals: dict = {}
+        for pid, rank, name, nbytes, ts in self.db.execute("select pid, rank, name, bytes, host_start_ns from collectives order by host_start_ns"):
+            kind = "Comm Send" if name in sent_like else "Comm Recv"
+            key = (pid, kind)
+            totals[key] = totals.get(key, 0) + (nbytes or 0)
+            events.append({"ph": "C", "pid": pid, "name": f"{kind} (bytes)", "cat": "comm_data", "ts": ts / 1e3, "args": {"value": totals[key]}})
         for name, dev, ts, val in self.db.execute("select s.value, c.device, c.ts_ns, c.value from counter_sample c join string s on s.id = c.name_id"):
             track = name if dev < 0 else f"{name} [{dev}]"
             events.append({"ph": "C", "pid": 0, "name": track, "ts": ts / 1e3, "args": {"value": val}})

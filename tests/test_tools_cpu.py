@@ -107,11 +107,13 @@ def test_tracedb_import_summary_convert(tmp_path):
         cats = {r["category"] for r in s["regions"]}
         assert cats == {"B200COLL_API", "MARKER_API"}
         ev = db.to_perfetto(str(tmp_path / "t.json"))
-        assert ev == 1 + 3 + 3 + 2      # process name, kernels, regions (2 API + 1 marker), device-side collectives
+        assert ev == 1 + 3 + 3 + 2 + 2  # process name, kernels, regions (2 API + 1 marker), device-side collectives, comm-volume counter points
         files = db.to_csv(str(tmp_path / "out"))
         assert any(f.endswith("_top_kernels.csv") for f in files)
     doc = json.loads((tmp_path / "t.json").read_text())
-    assert {e["ph"] for e in doc["traceEvents"]} == {"M", "X"}
+    assert {e["ph"] for e in doc["traceEvents"]} == {"M", "X", "C"}
+    vol = [e for e in doc["traceEvents"] if e["ph"] == "C"]
+    assert [e["name"] for e in vol] == ["Comm Recv (bytes)"] * 2 and [e["args"]["value"] for e in vol] == [4194304, 8388608]   # all-reduce counts as received; cumulative
     # a second rank's database merges in
     db2 = str(tmp_path / "r1.db")
     (tmp_path / "u.rank1.csv").write_text(COLL_CSV.replace(",100,100,", ",200,200,").replace(",0,1048576", ",1,1048576"))
