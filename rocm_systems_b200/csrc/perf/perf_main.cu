@@ -630,9 +630,11 @@ int main(int argc, char** argv) {
     }
   }
 
+  // NCCL_TESTS_DEVICE: the first GPU to use (common.cpp:1706); ranks take consecutive devices from there.
+  const int devBase = getenv("NCCL_TESTS_DEVICE") ? atoi(getenv("NCCL_TESTS_DEVICE")) : 0;
   std::vector<RankCtx> ctx;
   if (procMode) {
-    const int local = atoi(getenv("LOCAL_RANK") ? getenv("LOCAL_RANK") : "0");
+    const int local = devBase + atoi(getenv("LOCAL_RANK") ? getenv("LOCAL_RANK") : "0");
     CK(cudaSetDevice(local));
     ncclUniqueId id;
     if (!idFromFile(&id, myRank)) { fprintf(stderr, "rank %d: no unique id\n", myRank); return 5; }
@@ -647,13 +649,15 @@ int main(int argc, char** argv) {
     if (a.parallelInit) {  // -p 1: every thread brings up its own rank from a shared id (common.cpp:1697-1700)
       ncclUniqueId id;
       NK(ncclGetUniqueId(&id));
-      for (int r = 0; r < n; r++) th.emplace_back([&, r]() { CK(cudaSetDevice(r)); NK(ncclCommInitRank(&comms[r], n, id, r)); });
+      for (int r = 0; r < n; r++) th.emplace_back([&, r]() { CK(cudaSetDevice(devBase + r)); NK(ncclCommInitRank(&comms[r], n, id, r)); });
       for (auto& t : th) t.join();
       th.clear();
     } else {
-      NK(ncclCommInitAll(comms.data(), n, nullptr));
+      std::vector<int> devs(n);
+      for (int r = 0; r < n; r++) devs[r] = devBase + r;
+      NK(ncclCommInitAll(comms.data(), n, devs.data()));
     }
-    for (int r = 0; r < n; r++) ctx.push_back(RankCtx{r, n, r, comms[r], &a, r == 0 ? out : nullptr});
+    for (int r = 0; r < n; r++) ctx.push_back(RankCtx{r, n, devBase + r, comms[r], &a, r == 0 ? out : nullptr});
     for (int r = 0; r < n; r++) th.emplace_back(runRank, std::ref(ctx[r]));
     for (auto& t : th) t.join();
     for (int r = 0; r < n; r++) NK(ncclCommDestroy(comms[r]));

@@ -8,6 +8,47 @@
 
 namespace b200 {
 
+namespace {
+
+__global__ void kReadGlobalTimer(unsigned long long* out) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *out = t;
+}
+
+// What has to be added to a %globaltimer reading of the current GPU to get CLOCK_MONOTONIC nanoseconds. A one-thread
+// kernel takes the reading between two reads of the host clock; of several tries the one with the narrowest bracket
+// counts and the reading is placed in its middle. 0 when anything fails: device stamps then stay in the GPU's time base.
+long long globalTimerOffsetNs() {
+  unsigned long long* d = nullptr;
+  if (cudaMalloc(&d, sizeof(*d)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  long long best = 0;
+  uint64_t bestWidth = ~0ull;
+  for (int i = 0; i < 8; i++) {
+    cudaDeviceSynchronize();
+    const uint64_t t0 = nowNs();
+    kReadGlobalTimer<<<1, 1>>>(d);
+    unsigned long long g = 0;
+    if (cudaMemcpy(&g, d, sizeof(g), cudaMemcpyDeviceToHost) != cudaSuccess || g == 0) {
+      (void)cudaGetLastError();
+      best = 0;
+      break;
+    }
+    const uint64_t t1 = nowNs();
+    if (t1 - t0 < bestWidth) {
+      bestWidth = t1 - t0;
+      best = (long long)(t0 + (t1 - t0) / 2) - (long long)g;
+    }
+  }
+  cudaFree(d);
+  return best;
+}
+
+}  // namespace
+
 static const char* kApiNames[] = {
     "ncclAllGather", "ncclAllReduce", "ncclAllToAll", "ncclAllToAllv", "ncclBroadcast", "ncclGather", "ncclReduce",
     "ncclReduceScatter", "ncclScatter", "ncclSend", "ncclRecv", "ncclRedOpCreatePreMulSum", "ncclRedOpDestroy",
@@ -80,12 +121,24 @@ void Tracer::drain() {
   cudaDeviceSynchronize();
   std::vector<TraceStamp> host(ringUsed_);
   cudaMemcpy(host.data(), devRing_, sizeof(TraceStamp) * ringUsed_, cudaMemcpyDeviceToHost);
+  const long long offset = globalTimerOffsetNs();
+  const uint64_t now = nowNs();
   for (size_t i = 0; i < recs_.size(); i++) {
     int s = slotOf_[i];
     if (s < 0 || s >= ringUsed_) continue;
     unsigned long long b = host[s].begin, e = host[s].end;
     if (b == std::numeric_limits<unsigned long long>::max() || e == 0) { b = 0; e = 0; }
     if (e < b) std::swap(b, e);  // same repair the reference applies to swapped device stamps
+    if (e != 0) {
+      // Into the host's clock, then the reference's two shifts against clock skew, which keep the duration
+      // (rocprofiler-sdk tracing/profiling_time.hpp:137-145): the interval ends no later than now and starts no
+      // earlier than the call that enqueued it.
+      long long B = (long long)b + offset, E = (long long)e + offset;
+      if (E > (long long)now) { B -= E - (long long)now; E = (long long)now; }
+      if (B < (long long)recs_[i].hostBeginNs) { E += (long long)recs_[i].hostBeginNs - B; B = (long long)recs_[i].hostBeginNs; }
+      b = (unsigned long long)B;
+      e = (unsigned long long)E;
+    }
     recs_[i].devBeginNs = b;
     recs_[i].devEndNs = e;
     slotOf_[i] = -1;
