@@ -14,6 +14,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <strings.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -308,7 +309,8 @@ struct RankCtx {
   int rank, n, dev;
   ncclComm_t comm;
   const Args* a;
-  FILE* out;          // result file (rank 0 only)
+  FILE* out;          // result file (the reporting rank only)
+  bool report;        // prints the table: rank 0 of the whole job, as in the reference harness
   double bwSum = 0;
   int bwCount = 0;
   long long wrongTotal = 0;
@@ -336,7 +338,7 @@ static void runRank(RankCtx& c) {
   for (int i = 0; i < nTypes; i++) if (a.dtype == "all" || a.dtype == kTypes[i].name) typeIdx.push_back(i);
   if (reducing()) { for (int i = 0; i < 6; i++) if (a.op == "all" || a.op == kOps[i]) opIdx.push_back(i); }
   else opIdx.push_back(0);
-  if (typeIdx.empty() || opIdx.empty()) { if (rank == 0) fprintf(stderr, "unknown -d %s or -o %s\n", a.dtype.c_str(), a.op.c_str()); exit(1); }
+  if (typeIdx.empty() || opIdx.empty()) { if (c.report) fprintf(stderr, "unknown -d %s or -o %s\n", a.dtype.c_str(), a.op.c_str()); exit(1); }
 
   // Buffers sized for the largest message; with -R they come from ncclMemAlloc and are registered.
   // -E adds the rotation distance; -Y picks where unregistered buffers live (coarse and fine are both plain device
@@ -498,7 +500,7 @@ static void runRank(RankCtx& c) {
         c.wrongTotal += (long long)v[1];
         if (!inplace && a.delayUs > 0) usleep(a.delayUs);  // -q: pause between the out-of-place and the in-place run
       }
-      if (rank == 0) {
+      if (c.report) {
         char line[512];
         int o = snprintf(line, sizeof(line), "%12zu  %12zu  %8s  %6s  %4d", ab, s.paramCount, kTypes[ti].name, reducing() ? kOps[oi] : "none", rooted() ? a.root : -1);
         for (int ip = 0; ip < 2; ip++) {
@@ -532,6 +534,41 @@ static void runRank(RankCtx& c) {
   }
 }
 
+// ---- communicator splitting ---------------------------------------------------------------------------------------------
+// NCCL_TESTS_SPLIT_MASK=<hex> or NCCL_TESTS_SPLIT=AND<n> | OR<n> | MOD<n> | DIV<n> (also & | % /) give every rank a colour;
+// ranks of one colour form one communicator and the benchmark runs in all of them at once (common.cpp:1640-1672).
+static int colorOf(int proc) {
+  if (const char* m = getenv("NCCL_TESTS_SPLIT_MASK")) return proc & (int)strtoul(m, nullptr, 16);
+  const char* e = getenv("NCCL_TESTS_SPLIT");
+  if (!e) return 0;
+  struct { const char* word; const char* sym; int op; } forms[] = {{"AND", "&", 0}, {"OR", "|", 1}, {"MOD", "%", 2}, {"DIV", "/", 3}};
+  for (auto& f : forms) {
+    const char* arg = nullptr;
+    if (strncasecmp(e, f.word, strlen(f.word)) == 0) arg = e + strlen(f.word);
+    else if (strncmp(e, f.sym, 1) == 0) arg = e + 1;
+    if (!arg) continue;
+    char* end = nullptr;
+    const long v = strtol(arg, &end, 0);
+    if (end == arg) continue;
+    switch (f.op) {
+      case 0: return proc & (int)v;
+      case 1: return proc | (int)v;
+      case 2: return v > 0 ? proc % (int)v : 0;
+      default: return v > 0 ? proc / (int)v : 0;
+    }
+  }
+  return 0;
+}
+
+// The ranks that share `proc`'s colour, in rank order.
+static std::vector<int> groupOf(int proc, int nprocs) {
+  std::vector<int> g;
+  const int col = colorOf(proc);
+  for (int p = 0; p < nprocs; p++)
+    if (colorOf(p) == col) g.push_back(p);
+  return g;
+}
+
 // ---- main ------------------------------------------------------------------------------------------------------------
 static void usage() {
   printf("USAGE: %s_perf [-g ngpus] [-b minbytes] [-e maxbytes] [-i stepbytes] [-f stepfactor] [-n iters] [-w warmup_iters] [-m agg_iters]\n"
@@ -540,10 +577,11 @@ static void usage() {
          "       [-p parallel_init] [-y stream_null] [-q delay_inout_place_us] [-E rotating_tensor] [-Y coarse|fine|host|managed]\n", PERF_NAME);
 }
 
-static bool idFromFile(ncclUniqueId* id, int rank) {
+static bool idFromFile(ncclUniqueId* id, int rank, int color) {
   const char* over = getenv("B200_PERF_ID_FILE");
   std::string path = over ? over : std::string("/tmp/b200_perf_id.") + (getenv("MASTER_PORT") ? getenv("MASTER_PORT") : "0") + "." +
                                        (getenv("TORCHELASTIC_RUN_ID") ? getenv("TORCHELASTIC_RUN_ID") : "run") + "." PERF_IMPL "." PERF_NAME;
+  path += ".c" + std::to_string(color);
   if (rank == 0) {
     NK(ncclGetUniqueId(id));
     std::string tmp = path + ".tmp";
@@ -603,6 +641,16 @@ int main(int argc, char** argv) {
       if (a.memType != "coarse" && a.memType != "fine" && a.memType != "host" && a.memType != "managed") { fprintf(stderr, "unknown -Y %s\n", a.memType.c_str()); return 1; }
     }
     else if (f == "-u" || f == "--cumask" || f == "-F" || f == "--cache_flush") (void)next();  // AMD-only knobs: accepted, no effect
+    else if (f == "--print-split") {  // how NCCL_TESTS_SPLIT[_MASK] groups this many ranks; needs no GPU
+      const int np = atoi(next());
+      for (int pr = 0; pr < np; pr++) {
+        const std::vector<int> g = groupOf(pr, np);
+        int idx = 0;
+        while (g[idx] != pr) idx++;
+        printf("%d color %d rank %d of %zu\n", pr, colorOf(pr), idx, g.size());
+      }
+      return 0;
+    }
     else if (f == "-h" || f == "--help") { usage(); return 0; }
     else { fprintf(stderr, "unknown flag %s\n", f.c_str()); usage(); return 1; }
   }
@@ -611,14 +659,20 @@ int main(int argc, char** argv) {
   const char* wsEnv = getenv("WORLD_SIZE");
   const int world = wsEnv ? atoi(wsEnv) : 1;
   const bool procMode = world > 1;
-  const int n = procMode ? world : a.nGpus;
-  if (a.root < 0 || a.root >= n) a.root = 0;
+  const int nAll = procMode ? world : a.nGpus;
   const int myRank = procMode ? atoi(getenv("RANK") ? getenv("RANK") : "0") : 0;
+  const std::vector<int> firstGroup = groupOf(0, nAll);
+  const int n = (int)firstGroup.size();  // size of the communicator the reporting rank is in
+  {
+    size_t smallest = nAll;
+    for (int pr = 0; pr < nAll; pr++) smallest = std::min(smallest, groupOf(pr, nAll).size());
+    if (a.root < 0 || a.root >= (int)smallest) a.root = 0;
+  }
 
   FILE* out = nullptr;
   if (myRank == 0) {
-    printf("# %s_perf (%s): ranks %d %s, bytes %zu..%zu, warmup %d, iters %d, agg %d, check %d\n", PERF_NAME, PERF_IMPL, n,
-           procMode ? "processes" : "threads", a.minBytes, a.maxBytes, a.warmup, a.iters, a.agg, a.check);
+    printf("# %s_perf (%s): ranks %d %s%s, bytes %zu..%zu, warmup %d, iters %d, agg %d, check %d\n", PERF_NAME, PERF_IMPL, n,
+           procMode ? "processes" : "threads", n != nAll ? " per communicator (split)" : "", a.minBytes, a.maxBytes, a.warmup, a.iters, a.agg, a.check);
     printf("#\n# %10s  %12s  %8s  %6s  %4s  %46s  %46s\n", "", "", "", "", "", "out-of-place", "in-place");
     printf("# %10s  %12s  %8s  %6s  %4s  %9s %7s %7s %6s %9s  %9s %7s %7s %6s %9s\n", "size", "count", "type", "redop", "root", "time", "algbw", "busbw",
            "#wrong", "dev_time", "time", "algbw", "busbw", "#wrong", "dev_time");
@@ -636,31 +690,48 @@ int main(int argc, char** argv) {
   if (procMode) {
     const int local = devBase + atoi(getenv("LOCAL_RANK") ? getenv("LOCAL_RANK") : "0");
     CK(cudaSetDevice(local));
+    const std::vector<int> group = groupOf(myRank, nAll);
+    int groupRank = 0;
+    while (group[groupRank] != myRank) groupRank++;
     ncclUniqueId id;
-    if (!idFromFile(&id, myRank)) { fprintf(stderr, "rank %d: no unique id\n", myRank); return 5; }
+    if (!idFromFile(&id, groupRank, colorOf(myRank))) { fprintf(stderr, "rank %d: no unique id\n", myRank); return 5; }
     ncclComm_t comm;
-    NK(ncclCommInitRank(&comm, n, id, myRank));
-    ctx.push_back(RankCtx{myRank, n, local, comm, &a, out});
+    NK(ncclCommInitRank(&comm, (int)group.size(), id, groupRank));
+    ctx.push_back(RankCtx{groupRank, (int)group.size(), local, comm, &a, out, myRank == 0});
     runRank(ctx[0]);
     NK(ncclCommDestroy(comm));
   } else {
-    std::vector<ncclComm_t> comms(n);
+    std::vector<ncclComm_t> comms(nAll);
     std::vector<std::thread> th;
-    if (a.parallelInit) {  // -p 1: every thread brings up its own rank from a shared id (common.cpp:1697-1700)
-      ncclUniqueId id;
-      NK(ncclGetUniqueId(&id));
-      for (int r = 0; r < n; r++) th.emplace_back([&, r]() { CK(cudaSetDevice(devBase + r)); NK(ncclCommInitRank(&comms[r], n, id, r)); });
-      for (auto& t : th) t.join();
-      th.clear();
-    } else {
-      std::vector<int> devs(n);
-      for (int r = 0; r < n; r++) devs[r] = devBase + r;
-      NK(ncclCommInitAll(comms.data(), n, devs.data()));
+    std::vector<int> groupRankOf(nAll), groupSizeOf(nAll);
+    std::vector<bool> seen(nAll, false);
+    for (int lead = 0; lead < nAll; lead++) {  // one communicator per colour
+      if (seen[lead]) continue;
+      const std::vector<int> group = groupOf(lead, nAll);
+      const int gn = (int)group.size();
+      std::vector<ncclComm_t> gc(gn);
+      if (a.parallelInit) {  // -p 1: every thread brings up its own rank from a shared id (common.cpp:1697-1700)
+        ncclUniqueId id;
+        NK(ncclGetUniqueId(&id));
+        for (int r = 0; r < gn; r++) th.emplace_back([&, r]() { CK(cudaSetDevice(devBase + group[r])); NK(ncclCommInitRank(&gc[r], gn, id, r)); });
+        for (auto& t : th) t.join();
+        th.clear();
+      } else {
+        std::vector<int> devs(gn);
+        for (int r = 0; r < gn; r++) devs[r] = devBase + group[r];
+        NK(ncclCommInitAll(gc.data(), gn, devs.data()));
+      }
+      for (int r = 0; r < gn; r++) {
+        comms[group[r]] = gc[r];
+        groupRankOf[group[r]] = r;
+        groupSizeOf[group[r]] = gn;
+        seen[group[r]] = true;
+      }
     }
-    for (int r = 0; r < n; r++) ctx.push_back(RankCtx{r, n, devBase + r, comms[r], &a, r == 0 ? out : nullptr});
-    for (int r = 0; r < n; r++) th.emplace_back(runRank, std::ref(ctx[r]));
+    for (int r = 0; r < nAll; r++) ctx.push_back(RankCtx{groupRankOf[r], groupSizeOf[r], devBase + r, comms[r], &a, r == 0 ? out : nullptr, r == 0});
+    for (int r = 0; r < nAll; r++) th.emplace_back(runRank, std::ref(ctx[r]));
     for (auto& t : th) t.join();
-    for (int r = 0; r < n; r++) NK(ncclCommDestroy(comms[r]));
+    for (int r = 0; r < nAll; r++) NK(ncclCommDestroy(comms[r]));
   }
   int rc = 0;
   if (myRank == 0) {

@@ -37,3 +37,25 @@ def test_one_binary_per_collective_and_a_stock_nccl_twin(perf_bin):
         assert f"{coll}_perf" in perf_bin
     twins = [n for n in perf_bin if n.endswith("_perf_nccl")]
     assert twins == [] or "all_reduce_perf_nccl" in twins   # present wherever a system nccl.h exists
+
+
+def test_communicator_split_by_environment(perf_bin):
+    """NCCL_TESTS_SPLIT_MASK / NCCL_TESTS_SPLIT group the ranks as the reference harness does (common.cpp:1640-1672)."""
+    import os
+
+    exe = str(perf_bin["all_gather_perf"])
+
+    def groups(n, **env):
+        e = {k: v for k, v in os.environ.items() if not k.startswith("NCCL_TESTS_")}
+        e.update(env)
+        out = subprocess.run([exe, "--print-split", str(n)], capture_output=True, text=True, env=e, timeout=60).stdout
+        rows = [line.split() for line in out.strip().splitlines()]
+        return [(int(r[0]), int(r[2]), int(r[4]), int(r[6])) for r in rows]      # proc, colour, rank in group, group size
+
+    assert groups(3) == [(0, 0, 0, 3), (1, 0, 1, 3), (2, 0, 2, 3)]
+    assert groups(4, NCCL_TESTS_SPLIT_MASK="0x1") == [(0, 0, 0, 2), (1, 1, 0, 2), (2, 0, 1, 2), (3, 1, 1, 2)]
+    assert [g[1] for g in groups(8, NCCL_TESTS_SPLIT="DIV4")] == [0, 0, 0, 0, 1, 1, 1, 1]
+    assert [g[1] for g in groups(6, NCCL_TESTS_SPLIT="MOD 3")] == [0, 1, 2, 0, 1, 2]
+    assert [g[1] for g in groups(4, NCCL_TESTS_SPLIT="%2")] == [0, 1, 0, 1]
+    assert [g[1] for g in groups(4, NCCL_TESTS_SPLIT="AND2")] == [0, 0, 2, 2]
+    assert [g[1] for g in groups(4, NCCL_TESTS_SPLIT="|1")] == [1, 1, 3, 3]
