@@ -37,6 +37,11 @@ struct NvmlFns {
   nvmlReturn_t (*persistence)(nvmlDevice_t, nvmlEnableState_t*) = nullptr;
   nvmlReturn_t (*migMode)(nvmlDevice_t, unsigned int*, unsigned int*) = nullptr;
   nvmlReturn_t (*eccMode)(nvmlDevice_t, nvmlEnableState_t*, nvmlEnableState_t*) = nullptr;
+  nvmlReturn_t (*eventSetCreate)(nvmlEventSet_t*) = nullptr;
+  nvmlReturn_t (*eventSetFree)(nvmlEventSet_t) = nullptr;
+  nvmlReturn_t (*supportedEvents)(nvmlDevice_t, unsigned long long*) = nullptr;
+  nvmlReturn_t (*registerEvents)(nvmlDevice_t, unsigned long long, nvmlEventSet_t) = nullptr;
+  nvmlReturn_t (*eventSetWait)(nvmlEventSet_t, nvmlEventData_t*, unsigned int) = nullptr;
 };
 extern NvmlFns gN;
 bool ready();

@@ -68,6 +68,11 @@ static bool loadNvml() {
   sym("nvmlDeviceGetPersistenceMode", &gN.persistence, false);
   sym("nvmlDeviceGetMigMode", &gN.migMode, false);
   sym("nvmlDeviceGetEccMode", &gN.eccMode, false);
+  sym("nvmlEventSetCreate", &gN.eventSetCreate, false);
+  sym("nvmlEventSetFree", &gN.eventSetFree, false);
+  sym("nvmlDeviceGetSupportedEventTypes", &gN.supportedEvents, false);
+  sym("nvmlDeviceRegisterEvents", &gN.registerEvents, false);
+  sym("nvmlEventSetWait_v2", &gN.eventSetWait, false);
   if (!ok) {
     dlclose(gLib);
     gLib = nullptr;
@@ -131,6 +136,7 @@ const char* b200smi_status_string(b200smi_status_t s) {
     case B200SMI_ERR_INVALID: return "invalid argument";
     case B200SMI_ERR_NOT_SUPPORTED: return "not supported by this device or driver";
     case B200SMI_ERR_PERMISSION: return "changing GPU settings is disabled (needs B200SMI_ALLOW_SET=1 and allow=1)";
+    case B200SMI_ERR_TIMEOUT: return "nothing happened within the time given";
     default: return "NVML call failed";
   }
 }
@@ -361,6 +367,80 @@ b200smi_status_t b200smi_modes(int device, b200smi_modes_t* out) {
   unsigned int cur = 0, pend = 0;
   if (gN.migMode && gN.migMode(h, &cur, &pend) == NVML_SUCCESS) out->mig = (int)cur;
   if (gN.eccMode && gN.eccMode(h, &e, &pending) == NVML_SUCCESS) out->ecc = e == NVML_FEATURE_ENABLED;
+  return B200SMI_OK;
+}
+
+// ---- asynchronous events -------------------------------------------------------------------------------------------
+// XID errors, ECC errors, power-state and clock changes as they happen, through one NVML event set over all devices:
+// the counterpart of rsmi_event_notification_init / _mask_set / _get (rocm_smi_lib src/rocm_smi.cc:6116-6184), which the
+// reference's health monitoring builds on. Read-only: nothing is acknowledged or cleared on the device.
+namespace {
+std::mutex gEvMu;
+nvmlEventSet_t gEvSet = nullptr;
+}  // namespace
+
+b200smi_status_t b200smi_events_open(uint64_t mask) {
+  using namespace b200::smi;
+  if (!ready()) return B200SMI_ERR_NOT_LOADED;
+  if (!gN.eventSetCreate || !gN.registerEvents || !gN.eventSetWait || !gN.eventSetFree) return B200SMI_ERR_NOT_SUPPORTED;
+  std::lock_guard<std::mutex> lk(gEvMu);
+  if (gEvSet) return B200SMI_OK;
+  nvmlEventSet_t set = nullptr;
+  if (gN.eventSetCreate(&set) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  unsigned n = 0;
+  gN.count(&n);
+  int registered = 0;
+  for (unsigned i = 0; i < n; i++) {
+    nvmlDevice_t h;
+    if (gN.handle(i, &h) != NVML_SUCCESS) continue;
+    unsigned long long types = mask;
+    unsigned long long supported = ~0ull;
+    if (gN.supportedEvents && gN.supportedEvents(h, &supported) != NVML_SUCCESS) supported = 0;
+    types = (mask ? mask : ~0ull) & supported;
+    if (types && gN.registerEvents(h, types, set) == NVML_SUCCESS) registered++;
+  }
+  if (!registered) {
+    gN.eventSetFree(set);
+    return B200SMI_ERR_NOT_SUPPORTED;
+  }
+  gEvSet = set;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_events_wait(int timeoutMs, b200smi_event_t* out) {
+  using namespace b200::smi;
+  if (!out) return B200SMI_ERR_INVALID;
+  nvmlEventSet_t set;
+  {
+    std::lock_guard<std::mutex> lk(gEvMu);
+    set = gEvSet;
+  }
+  if (!set) return B200SMI_ERR_INVALID;
+  nvmlEventData_t d;
+  memset(&d, 0, sizeof(d));
+  const nvmlReturn_t r = gN.eventSetWait(set, &d, timeoutMs < 0 ? 0 : (unsigned)timeoutMs);
+  if (r == NVML_ERROR_TIMEOUT) return B200SMI_ERR_TIMEOUT;
+  if (r != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  out->device = -1;
+  unsigned n = 0;
+  gN.count(&n);
+  for (unsigned i = 0; i < n; i++) {
+    nvmlDevice_t h;
+    if (gN.handle(i, &h) == NVML_SUCCESS && h == d.device) out->device = (int)i;
+  }
+  out->type = d.eventType;
+  out->data = d.eventData;
+  timespec ts;
+  clock_gettime(CLOCK_REALTIME, &ts);
+  out->timestampNs = (uint64_t)ts.tv_sec * 1000000000ull + ts.tv_nsec;
+  return B200SMI_OK;
+}
+
+b200smi_status_t b200smi_events_close(void) {
+  using namespace b200::smi;
+  std::lock_guard<std::mutex> lk(gEvMu);
+  if (gEvSet && gN.eventSetFree) gN.eventSetFree(gEvSet);
+  gEvSet = nullptr;
   return B200SMI_OK;
 }
 

@@ -22,7 +22,8 @@ typedef enum {
   B200SMI_ERR_INVALID = 2,
   B200SMI_ERR_NOT_SUPPORTED = 3,
   B200SMI_ERR_PERMISSION = 4,    /* a setter was called without being allowed */
-  B200SMI_ERR_NVML = 5
+  B200SMI_ERR_NVML = 5,
+  B200SMI_ERR_TIMEOUT = 6        /* no event within the time given */
 } b200smi_status_t;
 
 typedef struct {
@@ -88,6 +89,18 @@ b200smi_status_t b200smi_pcie(int device, uint32_t* generation, uint32_t* width)
  * 3 exclusive process), persistence, MIG and ECC enabled flags; -1 where the driver does not report one. */
 typedef struct { int computeMode, persistence, mig, ecc; } b200smi_modes_t;
 b200smi_status_t b200smi_modes(int device, b200smi_modes_t* out);
+
+/* Asynchronous events of all devices (read only). Types are NVML's bits. */
+#define B200SMI_EVENT_ECC_SINGLE 0x1ull
+#define B200SMI_EVENT_ECC_DOUBLE 0x2ull
+#define B200SMI_EVENT_PSTATE 0x4ull
+#define B200SMI_EVENT_XID 0x8ull          /* data = the XID number */
+#define B200SMI_EVENT_CLOCK 0x10ull
+#define B200SMI_EVENT_POWER_SOURCE 0x80ull
+typedef struct { int device; uint64_t type; uint64_t data; uint64_t timestampNs; } b200smi_event_t;
+b200smi_status_t b200smi_events_open(uint64_t mask);                       /* 0: every type a device supports */
+b200smi_status_t b200smi_events_wait(int timeoutMs, b200smi_event_t* out);  /* B200SMI_ERR_TIMEOUT when nothing happened */
+b200smi_status_t b200smi_events_close(void);
 /* Watches: a sampler thread reads the watched fields every periodMs into a per-(device, field)
  * ring of `keep` samples (the watch table and cache of rdc_libs/rdc/src/RdcWatchTableImpl.cc). */
 b200smi_status_t b200smi_watch_start(const int* devices, int ndev, const int* fields, int nfields, int periodMs, int keep);

@@ -63,6 +63,14 @@ class Modes(ctypes.Structure):
 POLICY_CB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_double, ctypes.c_void_p)
 
 
+class Event(ctypes.Structure):
+    _fields_ = [("device", ctypes.c_int), ("type", ctypes.c_uint64), ("data", ctypes.c_uint64), ("timestampNs", ctypes.c_uint64)]
+
+
+EVENT_NAMES = {0x1: "ecc_single_bit", 0x2: "ecc_double_bit", 0x4: "pstate", 0x8: "xid", 0x10: "clock", 0x80: "power_source"}
+ERR_TIMEOUT = 6
+
+
 class Smi:
     """Thin object wrapper over the C API; raises RuntimeError with the library's message."""
 
@@ -84,6 +92,8 @@ class Smi:
         L.b200smi_nvlink_errors.argtypes = [ctypes.c_int, ctypes.POINTER(NvlinkErrors)]
         L.b200smi_modes.argtypes = [ctypes.c_int, ctypes.POINTER(Modes)]
         L.b200smi_pcie.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32)]
+        L.b200smi_events_open.argtypes = [ctypes.c_uint64]
+        L.b200smi_events_wait.argtypes = [ctypes.c_int, ctypes.POINTER(Event)]
         self._cbs = []
         self._ck(L.b200smi_init())
 
@@ -186,6 +196,26 @@ class Smi:
         names = {0: "default", 1: "exclusive_thread", 2: "prohibited", 3: "exclusive_process"}
         return {"compute_mode": names.get(m.computeMode, str(m.computeMode)), "persistence": m.persistence, "mig": m.mig, "ecc": m.ecc}
 
+    def events(self, timeout_ms: int = 1000, mask: int = 0, max_events: int = 0, stop=None):
+        """Yields asynchronous device events (XID errors, ECC errors, power-state and clock changes) as dicts until
+        ``timeout_ms`` passes without one, or ``max_events`` have been seen. With ``stop`` (a ``threading.Event``) quiet
+        periods do not end the stream: it runs, on one event set, until ``stop`` is set. Read only."""
+        self._ck(self.lib.b200smi_events_open(mask))
+        try:
+            seen = 0
+            while not max_events or seen < max_events:
+                ev = Event()
+                st = self.lib.b200smi_events_wait(timeout_ms, ctypes.byref(ev))
+                if st == ERR_TIMEOUT:
+                    if stop is not None and not stop.is_set():
+                        continue
+                    return
+                self._ck(st)
+                seen += 1
+                yield {"device": ev.device, "type": EVENT_NAMES.get(ev.type, hex(ev.type)), "data": ev.data, "timestamp_ns": ev.timestampNs}
+        finally:
+            self.lib.b200smi_events_close()
+
     def set_power_limit(self, dev: int, milliwatt: int, allow: bool) -> None:
         self._ck(self.lib.b200smi_set_power_limit(dev, milliwatt, int(allow)))
 
@@ -216,6 +246,8 @@ def main(argv=None) -> int:
     ap.add_argument("--shownvlinkerrors", action="store_true", help="replay / recovery / CRC counters summed over each GPU's links")
     ap.add_argument("--showbus", action="store_true", help="PCIe generation and width")
     ap.add_argument("--showmodes", action="store_true", help="compute, persistence, MIG and ECC modes (read only)")
+    ap.add_argument("--showevents", type=float, default=0.0, metavar="SECONDS",
+                    help="print XID / ECC / power-state / clock events as they happen; stops after this long without one")
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--setpowerlimit", nargs=2, metavar=("GPU", "WATTS"))
     ap.add_argument("--allow-set", action="store_true", help="required (with B200SMI_ALLOW_SET=1) before any setter acts")
@@ -261,7 +293,13 @@ def main(argv=None) -> int:
         if not a.json:
             for i, m in enumerate(out["modes"]):
                 print(f"GPU{i}: compute mode {m['compute_mode']}, persistence {m['persistence']}, MIG {m['mig']}, ECC {m['ecc']}")
-    only_new = a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    if a.showevents > 0:
+        out["events"] = []
+        for ev in smi.events(timeout_ms=int(a.showevents * 1000)):
+            out["events"].append(ev)
+            if not a.json:
+                print(f"GPU{ev['device']}: {ev['type']} data={ev['data']} at {ev['timestamp_ns']}", flush=True)
+    only_new = a.showevents > 0 or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
               ("typeName", "Link type between two GPUs", a.showtopotype), ("maxBandwidthMBps", "Max bandwidth (MB/s per direction)", a.shownodesbw),
               ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]

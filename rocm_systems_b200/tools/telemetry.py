@@ -58,6 +58,9 @@ class Telemetry:
         self.jobs: dict = {}
         self.groups: dict = {"all": list(self.devices)}          # device groups by name
         self.field_groups: dict = {"default": list(DEFAULT_FIELDS)}
+        self.device_events: List[dict] = []                      # XID / ECC / clock events seen by the listener
+        self._event_thread: Optional[threading.Thread] = None
+        self._event_stop = threading.Event()
 
     # ---- groups (rdc: rdc_group_gpu_create / rdc_group_field_create / rdc_field_watch) ----
     def create_group(self, name: str, devices: Sequence[int]) -> None:
@@ -139,6 +142,33 @@ class Telemetry:
         if self.watching:
             self.smi.watch_stop()
             self.watching = False
+        self.stop_event_listener()
+
+    # ---- asynchronous device events (rdc notifications / rsmi_event_notification_*) ----
+    def start_event_listener(self, keep: int = 1000) -> None:
+        """A background thread that records XID errors, ECC errors and clock / power-state changes as they happen."""
+        if self._event_thread is not None:
+            return
+        self._event_stop.clear()
+
+        def run() -> None:
+            try:
+                for ev in self.smi.events(timeout_ms=200, stop=self._event_stop):
+                    self.device_events.append(ev)
+                    del self.device_events[:-keep]
+                    if self._event_stop.is_set():
+                        break
+            except RuntimeError:  # the driver has no event support: nothing to listen to
+                return
+
+        self._event_thread = threading.Thread(target=run, daemon=True)
+        self._event_thread.start()
+
+    def stop_event_listener(self) -> None:
+        if self._event_thread is not None:
+            self._event_stop.set()
+            self._event_thread.join(timeout=2)
+            self._event_thread = None
 
     def discovery(self) -> List[dict]:
         out = []
@@ -231,6 +261,14 @@ class Telemetry:
                     lines.append(f'{metric}{{gpu="{d}"}} {errs[d][key]}')
         except RuntimeError:
             pass
+        if self.device_events:
+            lines.append("# HELP b200_device_events_total asynchronous device events seen since the listener started")
+            lines.append("# TYPE b200_device_events_total counter")
+            counts: dict = {}
+            for ev in self.device_events:
+                counts[(ev["device"], ev["type"])] = counts.get((ev["device"], ev["type"]), 0) + 1
+            for (d, kind), c in sorted(counts.items()):
+                lines.append(f'b200_device_events_total{{gpu="{d}",type="{kind}"}} {c}')
         return "\n".join(lines) + "\n"
 
 
@@ -272,6 +310,8 @@ def make_handler(t: Telemetry):
                 elif url.path == "/api/policy/set":
                     t.policy_set(int(q["dev"]), q["field"], float(q["threshold"]), q.get("direction", "above") != "below")
                     self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/events":
+                    self._send(200, json.dumps(t.device_events))
                 elif url.path == "/api/policy/events":
                     self._send(200, json.dumps(t.policy_events()))
                 else:
@@ -318,14 +358,14 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("--level", type=int, default=1, choices=[1, 2])
     p = sub.add_parser("client", help="talk to a running daemon")
     p.add_argument("--url", default="http://127.0.0.1:9400")
-    p.add_argument("what", choices=["devices", "latest", "health", "metrics", "history", "job-start", "job-stop", "job-stats"])
+    p.add_argument("what", choices=["devices", "latest", "health", "metrics", "history", "events", "job-start", "job-stop", "job-stats"])
     p.add_argument("--job", default="")
     p.add_argument("--dev", type=int, default=0)
     p.add_argument("--field", default="power")
     a = ap.parse_args(argv)
 
     if a.cmd == "client":
-        path = {"devices": "/api/devices", "latest": "/api/latest", "health": "/api/health", "metrics": "/metrics", "history": "/api/history",
+        path = {"devices": "/api/devices", "latest": "/api/latest", "health": "/api/health", "metrics": "/metrics", "history": "/api/history", "events": "/api/events",
                 "job-start": "/api/job/start", "job-stop": "/api/job/stop", "job-stats": "/api/job/stats"}[a.what]
         q = {}
         if a.what.startswith("job"):
@@ -364,6 +404,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                 time.sleep(a.delay_ms / 1e3)
     elif a.cmd == "serve":
         t.start(a.devices, a.fields, a.period_ms, a.keep)
+        t.start_event_listener()
         srv = serve(t, a.host, a.port)
         print(f"telemetry: serving http://{a.host}:{srv.server_address[1]}/metrics for {len(t.devices)} device(s)", flush=True)
         try:

@@ -4,6 +4,7 @@
  *   FAKE_NVML_ECC=<gpu>            that GPU reports 3 uncorrected ECC errors
  *   FAKE_NVML_TEMP=<celsius>       temperature of every GPU
  *   FAKE_NVML_RAMP=1               power rises by 10 W on every read (for watch / policy tests)
+ *   FAKE_NVML_EVENTS=<gpu>:<type>:<data>[,...]   events the event set hands out, one per wait, then time-outs
  * The last power limit a setter wrote is kept in memory and returned by the getter. */
 #include <stdio.h>
 #include <stdlib.h>
@@ -74,3 +75,32 @@ nvmlReturn_t nvmlDeviceGetComputeMode(nvmlDevice_t d, int* m) { (void)d; *m = 0;
 nvmlReturn_t nvmlDeviceGetPersistenceMode(nvmlDevice_t d, int* e) { (void)d; *e = 1; return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetMigMode(nvmlDevice_t d, unsigned int* cur, unsigned int* pend) { (void)d; *cur = 0; *pend = 0; return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetEccMode(nvmlDevice_t d, int* cur, int* pend) { (void)d; *cur = 1; *pend = 1; return NVML_SUCCESS; }
+
+/* events: a set hands out the FAKE_NVML_EVENTS list in order, one per wait, for devices registered with a matching type */
+typedef struct fake_set { unsigned long long types[16]; int next; } *nvmlEventSet_t;
+typedef struct { nvmlDevice_t device; unsigned long long eventType, eventData; unsigned int gpuInstanceId, computeInstanceId; } nvmlEventData_t;
+static struct fake_set the_set;
+nvmlReturn_t nvmlEventSetCreate(nvmlEventSet_t* s) { memset(&the_set, 0, sizeof(the_set)); *s = &the_set; return NVML_SUCCESS; }
+nvmlReturn_t nvmlEventSetFree(nvmlEventSet_t s) { (void)s; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetSupportedEventTypes(nvmlDevice_t d, unsigned long long* t) { (void)d; *t = 0x1f; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceRegisterEvents(nvmlDevice_t d, unsigned long long types, nvmlEventSet_t s) { s->types[d->idx] |= types; return NVML_SUCCESS; }
+nvmlReturn_t nvmlEventSetWait_v2(nvmlEventSet_t s, nvmlEventData_t* out, unsigned int timeoutms) {
+  const char* e = getenv("FAKE_NVML_EVENTS");
+  int k = 0;
+  while (e && *e) {
+    int gpu = 0;
+    unsigned long long type = 0, data = 0;
+    if (sscanf(e, "%d:%llu:%llu", &gpu, &type, &data) != 3) break;
+    if (k++ >= s->next) {
+      s->next = k;
+      if (gpu >= 0 && gpu < 16 && (s->types[gpu] & type)) {
+        out->device = &devs[gpu]; out->eventType = type; out->eventData = data; out->gpuInstanceId = out->computeInstanceId = 0xffffffffu;
+        return NVML_SUCCESS;
+      }
+    }
+    e = strchr(e, ',');
+    if (e) e++;
+  }
+  usleep((timeoutms > 50 ? 50 : timeoutms) * 1000);
+  return 10; /* NVML_ERROR_TIMEOUT */
+}

@@ -131,3 +131,27 @@ print('ok')
                        env=e, capture_output=True, text=True)
     assert p.returncode == 0, p.stderr
     assert "580.159.fake" in p.stdout and "PCIe gen 5 x16" in p.stdout and "Memory GiB" in p.stdout and "SM MHz" not in p.stdout
+
+
+def test_event_stream(fake_nvml):
+    """XID / ECC events come out of the event set in order with device index, type name and payload; a quiet period ends
+    the stream; a mask filters types before registration."""
+    out = _run("""
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+evs = list(s.events(timeout_ms=100))
+print([(e['device'], e['type'], e['data']) for e in evs])
+only_xid = list(s.events(timeout_ms=100, mask=0x8))
+print([(e['device'], e['type'], e['data']) for e in only_xid])
+s.close()
+""", fake_nvml, {"FAKE_NVML_EVENTS": "2:8:79,0:2:1,3:16:0", "FAKE_NVML_GPUS": "4"})
+    lines = out.strip().splitlines()
+    assert lines[0] == "[(2, 'xid', 79), (0, 'ecc_double_bit', 1), (3, 'clock', 0)]"
+    assert lines[1] == "[(2, 'xid', 79)]"
+
+
+def test_event_cli(fake_nvml):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2", FAKE_NVML_EVENTS="1:8:94")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showevents", "0.1"], env=e, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    assert "GPU1: xid data=94" in p.stdout and "Name" not in p.stdout

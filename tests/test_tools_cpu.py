@@ -468,3 +468,26 @@ def test_prof_launcher_applies_filters(tmp_path):
 
     a = prof.parser().parse_args(["--kernel-trace", "--kernel-exclude-regex", "rms", "--truncate-kernels", "--collection-period", "0:100", "--", "true"])
     assert a.kernel_exclude_regex == "rms" and a.truncate_kernels and a.collection_period == "0:100"
+
+
+def test_telemetry_device_events_over_http_and_prometheus(fake_nvml):
+    out = _py("""
+import json, time, urllib.request
+from rocm_systems_b200.tools import telemetry
+t = telemetry.Telemetry()
+srv = telemetry.serve(t, '127.0.0.1', 0)
+url = 'http://127.0.0.1:%d' % srv.server_address[1]
+get = lambda p: urllib.request.urlopen(url + p, timeout=10).read().decode()
+t.start_event_listener()
+deadline = time.time() + 5
+ev = []
+while time.time() < deadline and len(ev) < 2:
+    time.sleep(0.1)
+    ev = json.loads(get('/api/events'))
+assert [(e['device'], e['type'], e['data']) for e in ev] == [(1, 'xid', 79), (0, 'ecc_double_bit', 2)], ev
+text = get('/metrics')
+assert 'b200_device_events_total{gpu="1",type="xid"} 1' in text and 'b200_device_events_total{gpu="0",type="ecc_double_bit"} 1' in text
+srv.shutdown(); t.stop()
+print('ok')
+""", {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "2", "FAKE_NVML_EVENTS": "1:8:79,0:2:2"})
+    assert "ok" in out
