@@ -316,15 +316,16 @@ struct RankCtx {
   long long wrongTotal = 0;
 };
 
-// Aggregates over the ranks with the communicator under test (sum of v[0..1], max of v[2]).
-static void crossRank(RankCtx& c, double* dbuf, double v[3], cudaStream_t st) {
-  double sums[2] = {v[0], v[1]};
-  CK(cudaMemcpyAsync(dbuf, sums, 16, cudaMemcpyHostToDevice, st));
-  CK(cudaMemcpyAsync(dbuf + 2, &v[2], 8, cudaMemcpyHostToDevice, st));
+// Aggregates over the ranks with the communicator under test: v[0], v[1] are summed, v[2] is maximised; v[3] and v[4]
+// come back as the maximum and the minimum of v[0] (for -a 3 and -a 2).
+static void crossRank(RankCtx& c, double* dbuf, double v[5], cudaStream_t st) {
+  double in[5] = {v[0], v[1], v[2], v[0], -v[0]};
+  CK(cudaMemcpyAsync(dbuf, in, sizeof(in), cudaMemcpyHostToDevice, st));
   NK(ncclAllReduce(dbuf, dbuf, 2, ncclFloat64, ncclSum, c.comm, st));
-  NK(ncclAllReduce(dbuf + 2, dbuf + 2, 1, ncclFloat64, ncclMax, c.comm, st));
-  CK(cudaMemcpyAsync(v, dbuf, 24, cudaMemcpyDeviceToHost, st));
+  NK(ncclAllReduce(dbuf + 2, dbuf + 2, 3, ncclFloat64, ncclMax, c.comm, st));
+  CK(cudaMemcpyAsync(v, dbuf, sizeof(in), cudaMemcpyDeviceToHost, st));
   CK(cudaStreamSynchronize(st));
+  v[4] = -v[4];
 }
 
 static void runRank(RankCtx& c) {
@@ -430,7 +431,7 @@ static void runRank(RankCtx& c) {
         auto timedColl = [&](int it) { const size_t sh = shiftOf(it); return runColl(sp + sh, rp + sh, s, dt, op, a.root, rank, n, eb, c.comm, st); };
         for (int w = 0; w < a.warmup; w++) NK(timedColl(w));
         CK(cudaStreamSynchronize(st));
-        double agg[3] = {0, 0, 0};
+        double agg[5] = {0, 0, 0, 0, 0};
         crossRank(c, dbuf, agg, st);  // barrier
         cudaGraph_t graph = nullptr;
         cudaGraphExec_t gexec = nullptr;
@@ -492,9 +493,10 @@ static void runRank(RankCtx& c) {
             }
           }
         }
-        double v[3] = {wallUs, bad, (double)ms * 1e3 / calls};
+        double v[5] = {wallUs, bad, (double)ms * 1e3 / calls, 0, 0};
         crossRank(c, dbuf, v, st);
-        timeUs[inplace] = a.average == 1 ? v[0] / n : wallUs;
+        // -a: 0 this (reporting) rank, 1 average, 2 minimum, 3 maximum over the ranks (common.cpp:1452-1455)
+        timeUs[inplace] = a.average == 1 ? v[0] / n : a.average == 2 ? v[4] : a.average == 3 ? v[3] : wallUs;
         wrong[inplace] = a.check > 0 ? v[1] : -1;
         devUs[inplace] = v[2];
         c.wrongTotal += (long long)v[1];
@@ -573,7 +575,7 @@ static std::vector<int> groupOf(int proc, int nprocs) {
 static void usage() {
   printf("USAGE: %s_perf [-g ngpus] [-b minbytes] [-e maxbytes] [-i stepbytes] [-f stepfactor] [-n iters] [-w warmup_iters] [-m agg_iters]\n"
          "       [-N run_cycles] [-c check] [-o sum|prod|max|min|avg|mulsum|all] [-d type|all] [-r root] [-z blocking] [-G cudagraph]\n"
-         "       [-C report_cputime] [-a average 0|1] [-R local_register] [-O out_of_place 0|1] [-T timeout_s] [-x output_file] [-Z csv|json]\n"
+         "       [-C report_cputime] [-a average 0|1|2|3] [-R local_register] [-O out_of_place 0|1] [-T timeout_s] [-x output_file] [-Z csv|json]\n"
          "       [-p parallel_init] [-y stream_null] [-q delay_inout_place_us] [-E rotating_tensor] [-Y coarse|fine|host|managed]\n", PERF_NAME);
 }
 
