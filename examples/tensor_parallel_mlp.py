@@ -16,7 +16,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 from rocm_systems_b200.ops import train_ops  # noqa: E402
-from rocm_systems_b200.parallel.tp import TensorParallelMLP  # noqa: E402
+from rocm_systems_b200.parallel.tp import TensorParallelAttention, TensorParallelMLP  # noqa: E402
 
 
 def main() -> int:
@@ -24,6 +24,9 @@ def main() -> int:
     ap.add_argument("--rows", type=int, default=1024, help="tokens per rank")
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--ffn", type=int, default=28672, help="whole intermediate size")
+    ap.add_argument("--attention", action="store_true", help="also run the tensor-parallel attention half of the layer")
+    ap.add_argument("--heads", type=int, default=64)
+    ap.add_argument("--kv-heads", type=int, default=8)
     a = ap.parse_args()
     comm = init_from_env()
     mlp = TensorParallelMLP(comm, a.rows, a.hidden, a.ffn // comm.nranks, comm.device, seed=1)
@@ -50,6 +53,21 @@ def main() -> int:
               f"{ms:.3f} ms per layer, {flops / ms / 1e9:.0f} TFLOP/s per GPU, kernel status {code}", flush=True)
     ok = code == 0 and err <= 3e-2 * scale + 1e-3
     mlp.free()
+    if a.attention:
+        # The other half of the layer on the same two kernels: QKV projection inside the all-gather, output projection
+        # inside the reduce-scatter, this rank's heads attended locally.
+        seq = min(4096, a.rows * comm.nranks)
+        att = TensorParallelAttention(comm, a.rows, a.hidden, a.heads, a.kv_heads, seq, comm.device, seed=2)
+        want = att.reference_forward(x).float()
+        got = att.forward(x).float()
+        torch.cuda.synchronize()
+        aerr, ascale = float((got - want).abs().max()), float(want.abs().max())
+        acode = train_ops.gemm_take_error()
+        if comm.rank == 0:
+            print(f"attention: {a.heads} heads ({a.kv_heads} kv) over TP={comm.nranks}, sequences of {seq}: max |error| {aerr:.3e} (output scale {ascale:.3e}), "
+                  f"kernel status {acode}", flush=True)
+        ok = ok and acode == 0 and aerr <= 3e-2 * ascale + 1e-3
+        att.free()
     comm.destroy()
     return 0 if ok else 1
 

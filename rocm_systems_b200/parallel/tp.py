@@ -114,3 +114,83 @@ class TensorParallelMLP:
         torch.cuda.synchronize()
         self._x_sym.free()
         self._ws.free()
+
+
+class TensorParallelAttention:
+    """The attention half of a tensor-parallel transformer layer with sequence-parallel activations.
+
+    Tokens come in row-sharded ([rows_per_rank, hidden] per rank, ranks in sequence order). The column-parallel QKV
+    projection runs inside the all-gather (``b200collAgGemm`` without the SwiGLU epilogue) and yields, for all
+    ``n * rows_per_rank`` tokens, the ``heads / n`` query heads and ``kv_heads / n`` key/value heads this rank owns;
+    rotary embedding and causal attention for those heads are local; the row-parallel output projection runs inside the
+    reduce-scatter (``b200collGemmRs``) and leaves this rank's rows of the result. Together with
+    :class:`TensorParallelMLP` this is a whole layer with two fused kernels per half and no stand-alone collective.
+    """
+
+    def __init__(self, comm, rows_per_rank: int, hidden: int, heads: int, kv_heads: int, seq_len: int, device=None, rope_theta: float = 500000.0,
+                 std: float = 0.02, seed: int = 0, comm_ctas: int = 0):
+        self.comm = comm
+        self.n, self.rank = comm.nranks, comm.rank
+        assert heads % self.n == 0 and kv_heads % self.n == 0, "heads and kv_heads must divide by the tensor-parallel size"
+        self.rows, self.hidden, self.seq = rows_per_rank, hidden, seq_len
+        self.M = self.n * rows_per_rank
+        assert self.M % seq_len == 0, "the gathered tokens must be whole sequences"
+        self.hq, self.hkv, self.d = heads // self.n, kv_heads // self.n, hidden // heads
+        self.device = device or comm.device
+        self.comm_ctas = comm_ctas
+        g = torch.Generator(device=self.device).manual_seed(seed + 104729 * self.rank)
+        qkv_rows = (self.hq + 2 * self.hkv) * self.d
+        assert qkv_rows % 128 == 0 and (self.hq * self.d) % 64 == 0
+        self.w_qkv = (torch.randn(qkv_rows, hidden, device=self.device, generator=g) * std).to(torch.bfloat16)      # q heads, k heads, v heads
+        self.w_o = (torch.randn(hidden, self.hq * self.d, device=self.device, generator=g) * std).to(torch.bfloat16)
+        self.rope = train_ops.rope_table(seq_len, self.d, rope_theta, self.device)
+        lib = _lib_tp()
+        self._x_sym = comm.sym_alloc(self.M * hidden * 2)
+        self.x_full = self._x_sym.tensor((self.M, hidden), torch.bfloat16)
+        self._ws = comm.sym_alloc(int(lib.b200collGemmRsWorkspaceBytes(rows_per_rank, hidden, self.n)))
+        self.qkv = torch.empty(self.M, qkv_rows, dtype=torch.bfloat16, device=self.device)
+        self.ctx = torch.empty(self.M, self.hq * self.d, dtype=torch.bfloat16, device=self.device)
+        self.y = torch.empty(rows_per_rank, hidden, dtype=torch.bfloat16, device=self.device)
+
+    def my_rows(self) -> torch.Tensor:
+        return self.x_full[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def _attend(self, qkv: torch.Tensor, out: torch.Tensor) -> None:
+        """Rotary embedding and causal attention of this rank's heads over whole sequences: qkv [M, (hq + 2 hkv) d] -> out [M, hq d]."""
+        B = self.M // self.seq
+        t = train_ops.rope_(qkv.view(self.M, self.hq + 2 * self.hkv, self.d), self.rope, self.hq + self.hkv)
+        q = t[:, :self.hq].reshape(B, self.seq, self.hq, self.d).transpose(1, 2)
+        k = t[:, self.hq:self.hq + self.hkv].reshape(B, self.seq, self.hkv, self.d).transpose(1, 2)
+        v = t[:, self.hq + self.hkv:].reshape(B, self.seq, self.hkv, self.d).transpose(1, 2)
+        o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.hq != self.hkv)
+        out.copy_(o.transpose(1, 2).reshape(self.M, self.hq * self.d))
+
+    def forward(self, x_local: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        if x_local is not None:
+            self.my_rows().copy_(x_local)
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        lib = _lib_tp()
+        _lib.check(lib.b200collAgGemm(self.comm.handle, self.x_full.data_ptr(), self.w_qkv.data_ptr(), self.qkv.data_ptr(), self.rows, self.w_qkv.shape[0],
+                                      self.hidden, 0, self.comm_ctas, s), "b200collAgGemm")
+        self._attend(self.qkv, self.ctx)
+        _lib.check(lib.b200collGemmRs(self.comm.handle, self.ctx.data_ptr(), self.w_o.data_ptr(), self._ws.ptr, self.y.data_ptr(), self.rows, self.hidden,
+                                      self.hq * self.d, s), "b200collGemmRs")
+        train_ops.LAUNCHES += 2
+        return self.y
+
+    def reference_forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        """Unfused: all_gather, library GEMM, the same local attention, library GEMM, reduce_scatter."""
+        xg = torch.empty(self.M, self.hidden, dtype=torch.bfloat16, device=self.device)
+        self.comm.all_gather(x_local.contiguous(), xg)
+        qkv = xg @ self.w_qkv.t()
+        ctx = torch.empty_like(self.ctx)
+        self._attend(qkv, ctx)
+        part = ctx @ self.w_o.t()
+        out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        self.comm.reduce_scatter(part, out)
+        return out
+
+    def free(self) -> None:
+        torch.cuda.synchronize()
+        self._x_sym.free()
+        self._ws.free()
