@@ -194,3 +194,34 @@ class TensorParallelAttention:
         torch.cuda.synchronize()
         self._x_sym.free()
         self._ws.free()
+
+
+class TensorParallelLayer:
+    """A whole pre-norm transformer layer with tensor-parallel weights and sequence-parallel activations:
+
+        h = x + attention(rmsnorm(x));  y = h + mlp(rmsnorm(h))
+
+    The residual stream and both norms live on this rank's ``rows_per_rank`` tokens only; the all-gather in front of each
+    half and the reduce-scatter behind it are inside the halves' GEMM kernels. Forward only (inference and the
+    forward-pass benchmark); weights are random."""
+
+    def __init__(self, comm, rows_per_rank: int, hidden: int, heads: int, kv_heads: int, ffn: int, seq_len: int, device=None, eps: float = 1e-5,
+                 seed: int = 0, comm_ctas: int = 0):
+        self.attn = TensorParallelAttention(comm, rows_per_rank, hidden, heads, kv_heads, seq_len, device, seed=seed, comm_ctas=comm_ctas)
+        self.mlp = TensorParallelMLP(comm, rows_per_rank, hidden, ffn // comm.nranks, device, seed=seed + 1, comm_ctas=comm_ctas)
+        dev = self.attn.device
+        self.norm1 = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
+        self.norm2 = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
+        self.eps = eps
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        h = x_local + self.attn.forward(train_ops.rmsnorm(x_local, self.norm1, self.eps))
+        return h + self.mlp.forward(train_ops.rmsnorm(h, self.norm2, self.eps))
+
+    def reference_forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        h = x_local + self.attn.reference_forward(train_ops.rmsnorm(x_local, self.norm1, self.eps))
+        return h + self.mlp.reference_forward(train_ops.rmsnorm(h, self.norm2, self.eps))
+
+    def free(self) -> None:
+        self.attn.free()
+        self.mlp.free()
