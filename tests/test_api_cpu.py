@@ -117,3 +117,34 @@ def test_copy_engine_transfers_are_cut_into_whole_64k_parts_that_cover_the_messa
         assert max(sizes) - min(sizes) <= 2 * 65536
     assert len(shmem.dma_plan(1 << 20)) == 1 and len(shmem.dma_plan(8 << 20)) == 2 and len(shmem.dma_plan(64 << 20)) == 4
     assert len(shmem.dma_plan(128 << 10, 8)) == 2            # never more parts than 64 KiB units
+
+
+def test_every_function_declared_in_a_public_header_is_exported():
+    """A user who compiles against csrc/include/b200coll must be able to link: every declared entry point exists in
+    libb200coll.so (or, for the activity tracer, libb200prof.so)."""
+    import re
+    import subprocess
+    from pathlib import Path
+
+    from rocm_systems_b200.utils import build
+
+    root = Path(build.CSRC) / "include" / "b200coll"
+    declared = set()
+    prefixes = r"(?:p?nccl[A-Z]|b200coll[A-Z_]|b200shmem_|b200smi_|b200tx[A-Z]|b200prof[A-Z]|b200ops_|msccl[A-Z])"
+    for h in root.glob("*.h"):
+        text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
+        text = re.sub(r"//.*", "", text)
+        declared |= {m.group(1) for m in re.finditer(r"\b(" + prefixes + r"\w*)\s*\(", text)}
+        declared |= {m.group(1) for m in re.finditer(r"B200COLL_DECL\(\s*[^,]+,\s*(\w+)\s*,", text)}
+    declared = {d for d in declared if not d.endswith("_t") and not d.endswith("_fn") and not d.endswith("_cb") and d != "name"}   # "name": the macro's own parameter
+    assert len(declared) > 100
+    exported = set()
+    libs = [build.build_lib()]
+    prof = build.build_prof()
+    if prof:
+        libs.append(prof)
+    for lib in libs:
+        out = subprocess.check_output(["nm", "-D", "--defined-only", str(lib)], text=True)
+        exported |= {line.split()[-1] for line in out.splitlines() if line.strip()}
+    missing = sorted(d for d in declared if d not in exported and (prof or not d.startswith("b200prof")))
+    assert missing == [], missing
