@@ -148,3 +148,62 @@ def test_every_function_declared_in_a_public_header_is_exported():
         exported |= {line.split()[-1] for line in out.splitlines() if line.strip()}
     missing = sorted(d for d in declared if d not in exported and (prof or not d.startswith("b200prof")))
     assert missing == [], missing
+
+
+def test_every_native_symbol_the_python_package_calls_exists():
+    """ctypes resolves names at call time, so a misspelt entry point in a wrapper that no CPU test calls would only show
+    up on a GPU. Every ``.b200...`` / ``.nccl...`` attribute used in the package must be an exported symbol."""
+    import re
+    import subprocess
+    from pathlib import Path
+
+    from rocm_systems_b200.utils import build
+
+    pkg = Path(build.PKG)
+    used = {}
+    for py in list(pkg.rglob("*.py")) + [pkg.parent / "bench.py"]:
+        for m in re.finditer(r"\.((?:b200coll|b200shmem_|b200smi_|b200tx|b200prof|b200ops_|nccl[A-Z])\w*)\b", py.read_text()):
+            used.setdefault(m.group(1), py.name)
+    assert len(used) > 80
+    exported = set()
+    libs = [build.build_lib()] + ([build.build_prof()] if build.build_prof() else [])
+    for lib in libs:
+        out = subprocess.check_output(["nm", "-D", "--defined-only", str(lib)], text=True)
+        exported |= {line.split()[-1] for line in out.splitlines() if line.strip()}
+    missing = sorted((n, f) for n, f in used.items() if n not in exported)
+    assert missing == [], missing
+
+
+def test_ctypes_signatures_have_the_arity_of_the_c_functions():
+    """The number of ``argtypes`` every wrapper module declares equals the parameter count of the C definition."""
+    import re
+    from pathlib import Path
+
+    from rocm_systems_b200 import _lib, shmem
+    from rocm_systems_b200.ops import fp8, train_ops
+    from rocm_systems_b200.parallel import ep, tp
+    from rocm_systems_b200.utils import build
+
+    lib = _lib.load()
+    for setup in (shmem._l, train_ops._lib_ops, fp8._lib, tp._lib_tp, ep._lib_ep):
+        setup()                                   # these only declare signatures; nothing touches a GPU
+    arity = {}
+    pat = re.compile(r"\b((?:b200coll|b200shmem_|b200ops_)\w*)\s*\(([^(){};]*(?:\([^()]*\)[^(){};]*)*)\)\s*\{")
+    for src in list(Path(build.CSRC).rglob("*.cu")) + list(Path(build.CSRC).rglob("*.cc")):
+        text = re.sub(r"/\*.*?\*/", "", src.read_text(), flags=re.S)
+        text = re.sub(r"//.*", "", text)
+        for m in pat.finditer(text):
+            params = m.group(2).strip()
+            if params and params != "void" and not re.search(r"\b(int|void|size_t|float|char|double|uint\w+|unsigned|long|const|nccl\w+|cuda\w+|b200\w+_t)\b", params):
+                continue                          # a call, not a definition
+            arity[m.group(1)] = 0 if params in ("", "void") else len(re.split(r",(?![^()]*\))", params))
+    checked, bad = 0, []
+    for name, n in arity.items():
+        fn = getattr(lib, name, None)
+        if fn is None or fn.argtypes is None:
+            continue
+        checked += 1
+        if len(fn.argtypes) != n:
+            bad.append((name, len(fn.argtypes), n))
+    assert checked > 60, checked
+    assert bad == [], bad
