@@ -187,7 +187,7 @@ def test_ctypes_signatures_have_the_arity_of_the_c_functions():
     lib = _lib.load()
     for setup in (shmem._l, train_ops._lib_ops, fp8._lib, tp._lib_tp, ep._lib_ep):
         setup()                                   # these only declare signatures; nothing touches a GPU
-    arity = {}
+    arity, signatures = {}, {}
     pat = re.compile(r"\b((?:b200coll|b200shmem_|b200ops_)\w*)\s*\(([^(){};]*(?:\([^()]*\)[^(){};]*)*)\)\s*\{")
     for src in list(Path(build.CSRC).rglob("*.cu")) + list(Path(build.CSRC).rglob("*.cc")):
         text = re.sub(r"/\*.*?\*/", "", src.read_text(), flags=re.S)
@@ -196,7 +196,9 @@ def test_ctypes_signatures_have_the_arity_of_the_c_functions():
             params = m.group(2).strip()
             if params and params != "void" and not re.search(r"\b(int|void|size_t|float|char|double|uint\w+|unsigned|long|const|nccl\w+|cuda\w+|b200\w+_t)\b", params):
                 continue                          # a call, not a definition
-            arity[m.group(1)] = 0 if params in ("", "void") else len(re.split(r",(?![^()]*\))", params))
+            plist = [] if params in ("", "void") else re.split(r",(?![^()]*\))", params)
+            arity[m.group(1)] = len(plist)
+            signatures[m.group(1)] = plist
     checked, bad = 0, []
     for name, n in arity.items():
         fn = getattr(lib, name, None)
@@ -207,3 +209,36 @@ def test_ctypes_signatures_have_the_arity_of_the_c_functions():
             bad.append((name, len(fn.argtypes), n))
     assert checked > 60, checked
     assert bad == [], bad
+
+    # ... and every argument has the class (pointer, 32-bit, 64-bit, float, double) of the C parameter.
+    import ctypes
+
+    def c_class(param: str) -> str:
+        param = re.sub(r"\s*=.*$", "", param.strip())
+        if "*" in param or "[" in param or re.search(r"\b(cudaStream_t|ncclComm_t|b200shmem_ctx_t)\b", param):
+            return "ptr"
+        ctype = " ".join(param.replace("const", " ").split()[:-1])
+        if ctype in ("int", "unsigned", "unsigned int", "uint32_t", "int32_t", "ncclDataType_t", "ncclRedOp_t"):
+            return "i32"
+        if ctype in ("long long", "unsigned long long", "uint64_t", "int64_t", "size_t", "long", "unsigned long"):
+            return "i64"
+        return {"float": "f32", "double": "f64"}.get(ctype, "?" + ctype)
+
+    def py_class(a) -> str:
+        if a in (ctypes.c_void_p, ctypes.c_char_p) or (isinstance(a, type) and issubclass(a, ctypes._Pointer)):
+            return "ptr"
+        if a in (ctypes.c_int, ctypes.c_uint, ctypes.c_int32, ctypes.c_uint32):
+            return "i32"
+        if a in (ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_size_t, ctypes.c_uint64, ctypes.c_int64, ctypes.c_long, ctypes.c_ulong):
+            return "i64"
+        return {ctypes.c_float: "f32", ctypes.c_double: "f64"}.get(a, "?" + str(a))
+
+    mismatched = []
+    for name, params in signatures.items():
+        fn = getattr(lib, name, None)
+        if fn is None or fn.argtypes is None or len(params) != len(fn.argtypes):
+            continue
+        for i, (cp, at) in enumerate(zip(params, fn.argtypes)):
+            if c_class(cp) != py_class(at):
+                mismatched.append((name, i, cp.strip(), str(at)))
+    assert mismatched == [], mismatched
