@@ -96,3 +96,38 @@ def test_tuning_file_wins_over_thresholds(tmp_path):
     assert r[1][1] == NVLS                         # beyond the first row; the 4-rank row is skipped at 8 ranks
     assert r[2][1] == NVLS                         # no reduce_scatter rows: built-in choice (4 KiB x 8 ranks = 32 KiB staged)
     assert plan([[0, 1, AR, 4, F32, SUM]])[0][0] == 4   # nranks 0: invalid argument
+
+
+def test_planner_invariants_over_random_messages():
+    """Properties that hold for every message: a valid algorithm, a CTA count inside the limits, at least one chunk,
+    flag-in-data only for small all-reduces, the in-switch path only where the switch can add (float sums, more than two
+    ranks, multicast present), and chunk counts that grow with the message."""
+    import random
+
+    rng = random.Random(11)
+    cases = []
+    for _ in range(400):
+        nranks = rng.choice([2, 3, 4, 8])
+        kind = rng.choice([AR, RS, RED, AG, BC])
+        count = rng.choice([1, 3, 17, 1000, 4099, 16384, 16385, 70001, 1 << 20, (1 << 22) + 5, 1 << 26, (1 << 28) + 1, 1 << 29])
+        cases.append([nranks, rng.choice([0, 1]), kind, count, rng.choice([F32, 2, 9, 0]), rng.choice([SUM, MAX])])   # 2: int32, 9: bf16, 0: int8
+    res = plan(cases)
+    for (nranks, nvls, kind, count, dt, op), (rc, algo, ctas, direct, chunks) in zip(cases, res):
+        es = {F32: 4, 2: 4, 9: 2, 0: 1}[dt]
+        nbytes = count * es
+        assert rc == 0 and algo in (LL, P2P, NVLS) and 1 <= ctas <= 128 and direct == 0, (nranks, kind, count, algo, ctas, chunks)
+        assert (chunks == 0) if algo == LL else (chunks >= 1), (nranks, kind, count, algo, chunks)      # flag-in-data uses no staging
+        if algo == LL:
+            assert kind == AR and nbytes <= 64 * 1024
+        if algo == NVLS:
+            assert nvls == 1
+            if kind in (AR, RS, RED):
+                assert nranks > 2 and op == SUM and dt in (F32, 9)
+        if nbytes <= 1 << 20 and algo != LL:
+            assert chunks == 1
+    # more bytes never means fewer chunks (same collective, ranks and type)
+    sizes = [1 << k for k in range(10, 30)]
+    for kind in (AR, RS, AG):
+        r = plan([[8, 1, kind, s, F32, SUM] for s in sizes])
+        chunk_counts = [x[4] for x in r]
+        assert chunk_counts == sorted(chunk_counts) and chunk_counts[-1] > 1
