@@ -301,3 +301,72 @@ def test_gemm_reduce_scatter_needs_no_barrier_with_two_staging_halves():
 
 def test_gemm_rs_checker_finds_the_single_half_overwrite():
     assert _violates(*gemm_rs_model(2, 3, nbufs=1), 2)
+
+
+# ---- shared-memory ring of bulk asynchronous peer loads (kStagedReduce, peer-load path) ------------------------------
+# A group of threads walks tiles 0..K-1 through S stages. Thread 0 issues tile i into stage i % S (arming the stage's
+# mbarrier; the copy engine completes it at any later time, which stores the data and flips the barrier's phase);
+# every thread waits for tile i on parity (i / S) & 1, thread 0 then issues tile i + S - 1, all reduce the tile, and all
+# meet at a named barrier. Before the loop thread 0 has issued tiles 0..S-2.
+def bulk_ring_model(nthreads, stages, tiles, issue_after_wait=True, lookahead=None):
+    ahead = stages - 1 if lookahead is None else lookahead
+
+    def step(st, pid):
+        threads, armed, phase, data, arrived, gen = st
+        # the last "process" is the copy engine: it completes any armed stage
+        if pid >= nthreads:
+            s = pid - nthreads
+            if armed[s] is None:
+                return None
+            return (threads, armed[:s] + (None,) + armed[s + 1:], phase[:s] + (phase[s] + 1,) + phase[s + 1:], data[:s] + (armed[s],) + data[s + 1:], arrived, gen)
+        i, pc, mygen = threads[pid]
+        if i >= tiles:
+            return None
+
+        def upd(t, k, v):
+            return t[:k] + (v,) + t[k + 1:]
+
+        def issue(armed_, phase_, tile):
+            s = tile % stages
+            assert armed_[s] is None, f"tile {tile}: stage {s} armed while tile {armed_[s]} is still in flight"
+            return upd(armed_, s, tile)
+
+        s = i % stages
+        if pc == 0:  # mbarrier.try_wait.parity: passes when the current phase's parity differs from the awaited one
+            if (phase[s] & 1) == ((i // stages) & 1):
+                return None
+            return (upd(threads, pid, (i, 1, mygen)), armed, phase, data, arrived, gen)
+        if pc == 1:  # thread 0 refills the stage everybody left at the end of the previous iteration
+            armed2 = armed
+            if pid == 0 and issue_after_wait and i + ahead < tiles:
+                armed2 = issue(armed, phase, i + ahead)
+            return (upd(threads, pid, (i, 2, mygen)), armed2, phase, data, arrived, gen)
+        if pc == 2:  # reduce the tile out of shared memory
+            assert data[s] == i, f"thread {pid} tile {i}: stage {s} holds tile {data[s]}"
+            return (upd(threads, pid, (i, 3, mygen)), armed, phase, data, arrived, gen)
+        if pc == 3:  # arrive at the named barrier
+            arrived2 = arrived + 1
+            if arrived2 == nthreads:
+                return (upd(threads, pid, (i, 4, mygen)), armed, phase, data, 0, gen + 1)
+            return (upd(threads, pid, (i, 4, mygen)), armed, phase, data, arrived2, gen)
+        if gen == mygen:  # pc == 4: leave the barrier once its generation has advanced
+            return None
+        return (upd(threads, pid, (i + 1, 0, gen)), armed, phase, data, arrived, gen)
+
+    armed = [None] * stages
+    for tile in range(min(ahead, tiles)):
+        armed[tile % stages] = tile
+    initial = (tuple((0, 0, 0) for _ in range(nthreads)), tuple(armed), tuple(0 for _ in range(stages)), tuple(-1 for _ in range(stages)), 0, 0)
+    return initial, step, (lambda st: all(t[0] >= tiles for t in st[0]))
+
+
+def test_bulk_load_ring_never_overwrites_or_misreads_a_stage():
+    for nthreads, stages, tiles in [(2, 4, 11), (3, 4, 9), (2, 2, 6)]:
+        initial, step, done = bulk_ring_model(nthreads, stages, tiles)
+        states, deadlocks = explore(initial, step, done, nthreads + stages)
+        assert deadlocks == 0 and states > 50
+
+
+def test_bulk_ring_checker_finds_a_refill_that_is_one_stage_too_eager():
+    # Keeping S tiles in flight instead of S - 1 refills the stage the other threads may still be reading.
+    assert _violates(*bulk_ring_model(2, 4, 9, lookahead=4), 2 + 4)
