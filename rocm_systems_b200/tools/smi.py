@@ -241,6 +241,10 @@ def main(argv=None) -> int:
     ap.add_argument("--showtopoaccess", action="store_true", help="only the peer-accessibility table")
     ap.add_argument("--shownodesbw", action="store_true", help="only the bandwidth table")
     ap.add_argument("--showhealth", action="store_true")
+    for flag, help_ in (("--showtemp", "temperature"), ("--showpower", "power draw and limit"), ("--showclocks", "SM and memory clocks, current / max"),
+                        ("--showmeminfo", "memory used / total"), ("--showuse", "GPU and memory utilisation"), ("--showuniqueid", "UUID"),
+                        ("--showproductname", "product name"), ("--showecc", "ECC error totals"), ("--showthrottle", "active clock event reasons")):
+        ap.add_argument(flag, action="store_true", help=help_ + " (one line per GPU)")
     ap.add_argument("--showpids", action="store_true", help="compute processes per GPU")
     ap.add_argument("--showdriverversion", action="store_true")
     ap.add_argument("--shownvlinkerrors", action="store_true", help="replay / recovery / CRC counters summed over each GPU's links")
@@ -299,7 +303,20 @@ def main(argv=None) -> int:
             out["events"].append(ev)
             if not a.json:
                 print(f"GPU{ev['device']}: {ev['type']} data={ev['data']} at {ev['timestamp_ns']}", flush=True)
-    only_new = a.showevents > 0 or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    singles = {"showtemp": lambda d: f"{d['temperatureC']} C", "showpower": lambda d: f"{d['powerMilliwatt'] / 1000:.1f} W (limit {d['powerLimitMilliwatt'] / 1000:.0f} W)",
+               "showclocks": lambda d: f"SM {d['smClockMhz']}/{d['smClockMaxMhz']} MHz, memory {d['memClockMhz']}/{d['memClockMaxMhz']} MHz",
+               "showmeminfo": lambda d: f"{d['memUsedBytes'] / 2**30:.1f} / {d['memTotalBytes'] / 2**30:.1f} GiB", "showuse": lambda d: f"GPU {d['gpuUtilPct']} %, memory {d['memUtilPct']} %",
+               "showuniqueid": lambda d: d["uuid"], "showproductname": lambda d: d["name"],
+               "showecc": lambda d: f"corrected {d['eccCorrected']}, uncorrected {d['eccUncorrected']}",
+               "showthrottle": lambda d: ",".join(d["throttleReasonNames"]) or "-"}
+    asked = [k for k in singles if getattr(a, k)]
+    if asked:
+        infos = [smi.info(i) for i in range(n)]
+        out["devices"] = infos
+        if not a.json:
+            for i, d in enumerate(infos):
+                print(f"GPU{i}: " + "; ".join(singles[k](d) for k in asked))
+    only_new = bool(asked) or a.showevents > 0 or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
               ("typeName", "Link type between two GPUs", a.showtopotype), ("maxBandwidthMBps", "Max bandwidth (MB/s per direction)", a.shownodesbw),
               ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]

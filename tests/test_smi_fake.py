@@ -155,3 +155,12 @@ def test_event_cli(fake_nvml):
     p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showevents", "0.1"], env=e, capture_output=True, text=True)
     assert p.returncode == 0, p.stderr
     assert "GPU1: xid data=94" in p.stdout and "Name" not in p.stdout
+
+
+def test_single_reading_flags(fake_nvml):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2", FAKE_NVML_TEMP="61")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showtemp", "--showclocks", "--showmeminfo", "--showthrottle"], env=e,
+                       capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    lines = p.stdout.strip().splitlines()
+    assert len(lines) == 2 and lines[0].startswith("GPU0: 61 C; SM 1500/1965 MHz") and "1.0 / 179.1 GiB" in lines[1] and "sw_power_cap" in lines[1]
