@@ -491,3 +491,32 @@ srv.shutdown(); t.stop()
 print('ok')
 """, {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "2", "FAKE_NVML_EVENTS": "1:8:79,0:2:2"})
     assert "ok" in out
+
+
+def test_hang_dump_reports_stacks_and_communicator_state(tmp_path):
+    """After the deadline: every thread's stack and each communicator's error text; a kick postpones it; exit_after ends
+    the process with 124."""
+    out = _py("""
+import io, sys, threading, time
+from rocm_systems_b200.utils import hang_dump
+class Fake:
+    rank, nranks = 2, 8
+    def async_error(self): return 6
+    def last_error(self): return 'wait BARRIER for rank 5 gave up: expected 12, saw 11'
+buf = io.StringIO()
+def stuck_worker():
+    time.sleep(2)
+threading.Thread(target=stuck_worker, daemon=True).start()
+hang_dump.arm(0.3, comms=[Fake()], file=sys.stdout)
+time.sleep(0.2); hang_dump.kick(); time.sleep(0.2)      # 0.4 s in, but kicked at 0.2: nothing yet
+print('QUIET' if True else '')
+time.sleep(0.4)
+hang_dump.disarm()
+print('END')
+""")
+    quiet, rest = out.split("QUIET", 1)
+    assert "hang_dump" not in quiet
+    assert "no progress for 0 s" in rest and "stuck_worker" in rest and "rank 2/8: async error 6" in rest and "expected 12, saw 11" in rest
+    p = subprocess.run([sys.executable, "-c", "import time\nfrom rocm_systems_b200.utils import hang_dump\nhang_dump.arm(0.2, exit_after=True)\ntime.sleep(5)"],
+                       env=dict(os.environ, PYTHONPATH=str(ROOT)), capture_output=True, text=True, timeout=60)
+    assert p.returncode == 124 and "hang_dump" in p.stderr
