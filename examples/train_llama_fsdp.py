@@ -11,7 +11,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 from rocm_systems_b200.models.llama import LlamaConfig, LlamaTrainer  # noqa: E402
-from rocm_systems_b200.utils import checkpoint, markers, schedule  # noqa: E402
+from rocm_systems_b200.utils import checkpoint, hang_dump, markers, schedule  # noqa: E402
 
 
 def main() -> None:
@@ -36,13 +36,16 @@ def main() -> None:
     if a.resume:
         checkpoint.load_engine(trainer.engine, a.ckpt)  # re-shards when the world size changed
     g = torch.Generator().manual_seed(1 + (comm.rank if comm else 0))
+    hang_dump.arm(600, comms=[comm] if comm else [])  # ten minutes without a finished step: say where everything is
     for step in range(a.steps):
         tok = torch.randint(0, cfg.vocab, (2, cfg.seq_len), generator=g).pin_memory()
         trainer.engine.opt.lr = lr_at(trainer.engine.step_count)  # the engine reads the rate at every unit's update
         with markers.range(f"step {step}"):  # shows up in traces taken with tools.prof --marker-trace
             loss = trainer.step(tok, tok.roll(-1, 1).pin_memory())
+        hang_dump.kick()
         if (comm is None or comm.rank == 0) and step % 5 == 0:
             print(f"step {step}: loss {loss:.4f}", flush=True)
+    hang_dump.disarm()
     checkpoint.save_engine(trainer.engine, a.ckpt)
     if comm is not None:
         comm.host_barrier()
