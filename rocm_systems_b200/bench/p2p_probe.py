@@ -58,8 +58,10 @@ def main() -> int:
     rounds = 0
     for d in range(1, n):
         to, frm = (me + d) % n, (me - d) % n
+        rounds = 0  # the signal word of this distance starts at zero
         t_put = _timed(lambda: sh.put(sym, local, to), sh, a.warmup, a.iters)
         t_get = _timed(lambda: sh.get(local, sym, to), sh, a.warmup, a.iters)
+        t_dma = _timed(lambda: sh.put_dma(sym, local, to), sh, a.warmup, a.iters)   # the same bytes by copy engine, no SM
         # latency: put a few bytes with a signal to `to`, wait for the one `frm` sends here
         def ping():
             nonlocal rounds
@@ -68,18 +70,19 @@ def main() -> int:
             sh.wait_until(sig[d:d + 1], CMP_GE, rounds)
         t_lat = _timed(ping, sh, a.warmup, max(a.iters, 20))
         rows.append({"distance": d, "to": to, "from": frm, "put_gbs": a.bytes / t_put / 1e9, "get_gbs": a.bytes / t_get / 1e9,
-                     "put_signal_wait_us": t_lat * 1e6})
+                     "put_dma_gbs": a.bytes / t_dma / 1e9, "put_signal_wait_us": t_lat * 1e6})
     status = sh.take_status()
-    parts = comm.host_all_gather(json.dumps({"rank": me, "status": status, "rows": rows}).encode().ljust(4096))
+    parts = comm.host_all_gather(json.dumps({"rank": me, "status": status, "rows": rows}).encode().ljust(8192))
     if me == 0:
         allr = [json.loads(p.decode().strip()) for p in parts]
         print(f"# p2p probe, {n} PEs, {a.bytes} bytes per transfer, every PE active; GB/s per direction (min over PEs), latency max over PEs")
-        print("# distance   put GB/s   get GB/s   put+signal+wait us")
+        print("# distance   put GB/s   get GB/s   put (copy engine) GB/s   put+signal+wait us")
         for i in range(n - 1):
             put = min(r["rows"][i]["put_gbs"] for r in allr)
             get = min(r["rows"][i]["get_gbs"] for r in allr)
+            dma = min(r["rows"][i]["put_dma_gbs"] for r in allr)
             lat = max(r["rows"][i]["put_signal_wait_us"] for r in allr)
-            print(f"  {i + 1:8d} {put:10.1f} {get:10.1f} {lat:12.2f}")
+            print(f"  {i + 1:8d} {put:10.1f} {get:10.1f} {dma:18.1f} {lat:18.2f}")
         if any(r["status"] for r in allr):
             print("# a bounded wait ran out on ranks:", [r["rank"] for r in allr if r["status"]])
         if a.out:
