@@ -20,7 +20,8 @@ SIZES = [1 << k for k in range(10, 30)]  # 1 KiB .. 512 MiB
 
 
 def _bw(dst: torch.Tensor, src: torch.Tensor, iters: int):
-    stream = torch.cuda.current_stream(dst.device if dst.is_cuda else src.device)
+    # torch runs a copy between two GPUs on the source device's current stream; a host copy runs on the GPU side's stream
+    stream = torch.cuda.current_stream(src.device if src.is_cuda else dst.device)
     for _ in range(2):
         dst.copy_(src, non_blocking=True)
     stream.synchronize()
