@@ -177,15 +177,15 @@ void logMsg(LogLevel lvl, unsigned subsys, const char* file, int line, const cha
   const std::string& path = Flags::get().debugFile;
   if (!path.empty()) {
     static std::mutex fileMu;
-    static FILE* file = nullptr;
+    static FILE* logFile = nullptr;
     static std::string opened;
     std::lock_guard<std::mutex> lk(fileMu);
-    if (!file || opened != path) {  // the path can change when tests re-read the environment
-      if (file) fclose(file);
-      file = fopen(path.c_str(), "a");
+    if (!logFile || opened != path) {  // the path can change when tests re-read the environment
+      if (logFile) fclose(logFile);
+      logFile = fopen(path.c_str(), "a");
       opened = path;
     }
-    if (file) out = file;
+    if (logFile) out = logFile;
     fprintf(out, "%s\n", buf);
     fflush(out);
     return;
