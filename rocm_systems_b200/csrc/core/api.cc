@@ -770,10 +770,6 @@ extern "C" {
 // CTAs, whether the zero-copy path applies (never here: the buffers are not in a window) and the number of
 // pipeline chunks. Honours the environment and the tuning file exactly as a real communicator does.
 // `kind`: 0 all-reduce, 1 reduce-scatter, 2 reduce, 3 all-gather, 4 broadcast.
-struct b200collPlanInfo {
-  int algo, ctas, direct;
-  unsigned long long chunks;
-};
 ncclResult_t b200collPlanDry(int nranks, int nvls, int kind, size_t count, ncclDataType_t dt, ncclRedOp_t op, b200collPlanInfo* out) {
   if (!out || nranks < 1 || nranks > kMaxRanks || kind < 0 || kind > COLL_BROADCAST || (int)dt < 0 || (int)dt >= ncclNumTypes)
     BFAIL(ncclInvalidArgument, "b200collPlanDry: bad argument");

@@ -67,10 +67,13 @@ void loadTuning(Comm* c) {
     if (e.kind != JsonValue::Object) continue;
     TuneEntry t;
     t.coll = collFromName(e.stringOr("coll", ""));
-    t.maxBytes = (size_t)e.numberOr("max_bytes", 1e30);
+    // Numbers come from a user's file: convert with saturation (a double outside the target's range is undefined behaviour).
+    auto toSize = [](double v) -> size_t { return !(v > 0) ? 0 : (v >= 1.8e19 ? ~(size_t)0 : (size_t)v); };
+    auto toInt = [](double v) -> int { return !(v > 0) ? 0 : (v >= 2e9 ? 2000000000 : (int)v); };
+    t.maxBytes = e.get("max_bytes") ? toSize(e.numberOr("max_bytes", 0)) : ~(size_t)0;
     t.algo = algoFromName(e.stringOr("algo", "auto"));
-    t.ctas = (int)e.numberOr("ctas", 0);
-    int nr = (int)e.numberOr("nranks", 0);
+    t.ctas = toInt(e.numberOr("ctas", 0));
+    int nr = toInt(e.numberOr("nranks", 0));
     if (nr && nr != c->nranks) continue;
     c->tuning.push_back(t);
   }

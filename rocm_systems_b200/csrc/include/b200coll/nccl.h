@@ -219,6 +219,21 @@ ncclResult_t b200collHostAllGather(ncclComm_t comm, const void* send, void* recv
 /* Device-side barrier enqueued on `stream`. */
 ncclResult_t b200collBarrier(ncclComm_t comm, cudaStream_t stream);
 
+/* ---- Extensions that need no GPU: what the planner would do, and the settings ------------ */
+
+/* What the planner chooses for a collective on a communicator of `nranks` ranks, with or without a multicast
+ * alias: algo 1 flag-in-data, 2 peer loads, 3 in-switch; CTAs; zero-copy (never here: the buffers are in no window);
+ * pipeline chunks. Honours the environment and the tuning file exactly as a real communicator does.
+ * kind: 0 all-reduce, 1 reduce-scatter, 2 reduce, 3 all-gather, 4 broadcast. */
+typedef struct b200collPlanInfo {
+  int algo, ctas, direct;
+  unsigned long long chunks;
+} b200collPlanInfo;
+ncclResult_t b200collPlanDry(int nranks, int nvls, int kind, size_t count, ncclDataType_t dt, ncclRedOp_t op, b200collPlanInfo* out);
+/* JSON description of every setting (environment names, current value, default, meaning) copied into `buf`
+ * (NUL-terminated, truncated to `cap`); returns the size the whole text needs. */
+size_t b200collDescribeSettings(char* buf, size_t cap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -68,3 +68,51 @@ def test_json_reader_and_marker_recorder_under_sanitizer(tmp_path, name, flags, 
     assert p.returncode == 0, (p.stdout + p.stderr)[-4000:]
     assert "markers OK" in p.stdout and (what != "all" or "json OK" in p.stdout)
     assert "ERROR: AddressSanitizer" not in p.stderr and "WARNING: ThreadSanitizer" not in p.stderr and "runtime error" not in p.stderr
+
+
+@pytest.mark.skipif(not Path("/usr/local/cuda/bin/nvcc").exists(), reason="needs nvcc")
+def test_planner_and_tuning_loader_under_sanitizers(tmp_path):
+    """The whole library compiled with ASan + UBSan (host side), then the planner on 20000 random requests, bad
+    arguments, the settings listing into short buffers, and tuning files with out-of-range and wrongly typed values."""
+    import concurrent.futures as cf
+    import sys
+
+    sys.path.insert(0, str(ROOT))
+    from rocm_systems_b200.utils import build
+
+    san = "-fPIC,-fsanitize=address,-fsanitize=undefined,-fsanitize=float-cast-overflow,-fno-omit-frame-pointer"
+
+    def compile_one(job):
+        src, obj, defs = job
+        out = tmp_path / obj.name
+        cmd = [build.NVCC, *build.ARCH, "-O1", "-g", "-std=c++17", "-Xcompiler", san, f"-I{CSRC / 'include'}", f"-I{CSRC}", "--expt-relaxed-constexpr", *defs,
+               "-c", str(src), "-o", str(out)]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        assert p.returncode == 0, p.stderr[-3000:]
+        return str(out)
+
+    with cf.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
+        objs = list(ex.map(compile_one, build.lib_jobs()))
+    exe = tmp_path / "planner_fuzz"
+    p = subprocess.run([build.NVCC, *build.ARCH, "-Xcompiler", "-fsanitize=address,-fsanitize=undefined", f"-I{CSRC / 'include'}",
+                        str(ROOT / "tests" / "native" / "planner_fuzz.cc"), *objs, "-o", str(exe), "-cudart", "static", "-lpthread", "-ldl", "-lrt",
+                        "-Xlinker", "-lasan", "-Xlinker", "-lubsan"], capture_output=True, text=True)
+    if p.returncode != 0 and "cannot find" in p.stderr:
+        pytest.skip("no sanitizer runtime for this toolchain")
+    assert p.returncode == 0, p.stderr[-3000:]
+    files = {
+        "good.json": '{"entries": [{"coll": "allreduce", "max_bytes": 1048576, "algo": "p2p", "ctas": 8}, {"coll": "allgather", "max_bytes": 1e12, "algo": "nvls", "ctas": 999999}]}',
+        "range.json": '{"entries": [{"max_bytes": 1e300, "ctas": 1e30, "nranks": -1e40}, {"coll": "reducescatter", "algo": "ll", "max_bytes": -5}]}',
+        "types.json": '{"entries": [{"coll": 5, "max_bytes": "x", "algo": null, "ctas": -3}, 7, "s", {"coll": "all_reduce"}], "extra": [[[[]]]]}',
+        "cut.json": '{"entries": [{"coll": "allreduce", "max_bytes": 1e308',
+    }
+    env = {k: v for k, v in os.environ.items() if not k.startswith(("B200COLL_", "NCCL_"))}
+    env.update(ASAN_OPTIONS="detect_leaks=0", UBSAN_OPTIONS="halt_on_error=1")
+    for name, text in [("", "")] + list(files.items()):
+        e = dict(env)
+        if name:
+            (tmp_path / name).write_text(text)
+            e["B200COLL_TUNING_FILE"] = str(tmp_path / name)
+        r = subprocess.run([str(exe)], env=e, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0 and "planner under sanitizers: 0 bad" in r.stdout, (name, (r.stdout + r.stderr)[-3000:])
+        assert "AddressSanitizer" not in r.stderr and "runtime error" not in r.stderr, (name, r.stderr[-3000:])
