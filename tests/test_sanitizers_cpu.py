@@ -107,7 +107,7 @@ def test_planner_and_tuning_loader_under_sanitizers(tmp_path):
         "cut.json": '{"entries": [{"coll": "allreduce", "max_bytes": 1e308',
     }
     env = {k: v for k, v in os.environ.items() if not k.startswith(("B200COLL_", "NCCL_"))}
-    env.update(ASAN_OPTIONS="detect_leaks=0", UBSAN_OPTIONS="halt_on_error=1")
+    env.update(ASAN_OPTIONS="detect_leaks=1", UBSAN_OPTIONS="halt_on_error=1")
     for name, text in [("", "")] + list(files.items()):
         e = dict(env)
         if name:
