@@ -10,6 +10,7 @@ import torch  # noqa: E402
 
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 from rocm_systems_b200.models.llama import LlamaConfig, LlamaTrainer  # noqa: E402
+from rocm_systems_b200.parallel.fsdp import AdamWConfig  # noqa: E402
 
 
 def main():
@@ -19,8 +20,10 @@ def main():
     cfg = LlamaConfig.tiny(64)
     fused = os.environ.get("FSDP_FUSED_RS", "1") == "1"
     sym = os.environ.get("FSDP_SYM_SHARDS", "0") == "1"   # shards and gradient buffers in symmetric memory (zero-copy collectives)
-    sharded = LlamaTrainer(cfg, comm, dev, seed=3, fused_rs=fused, sym_shards=sym)
-    single = LlamaTrainer(cfg, None, dev, seed=3)
+    clip = float(os.environ.get("FSDP_CLIP", "0"))         # > 0: global-norm clipping to this value on both trainers
+    opt = (lambda: AdamWConfig(max_grad_norm=clip)) if clip > 0 else (lambda: None)
+    sharded = LlamaTrainer(cfg, comm, dev, opt=opt(), seed=3, fused_rs=fused, sym_shards=sym)
+    single = LlamaTrainer(cfg, None, dev, opt=opt(), seed=3)
     g = torch.Generator().manual_seed(5)
     steps = 6
     toks = [torch.randint(0, cfg.vocab, (world, cfg.seq_len), generator=g) for _ in range(steps)]
@@ -51,7 +54,9 @@ def main():
     if bad:
         print(f"[rank {rank}] FSDP MISMATCH: {bad}", flush=True)
     elif rank == 0:
-        print(f"fsdp_worker OK on {world} ranks (max weight diff {diff:.2e}, fused_rs={fused}, sym_shards={sym})", flush=True)
+        norm = sharded.engine.last_grad_norm
+        print(f"fsdp_worker OK on {world} ranks (max weight diff {diff:.2e}, fused_rs={fused}, sym_shards={sym}, clip={clip}"
+              + (f", last gradient norm {float(norm):.4f}" if norm is not None else "") + ")", flush=True)
     torch.cuda.synchronize()
     comm.destroy()
     sys.exit(1 if any(f[0] for f in flags) else 0)
