@@ -98,6 +98,12 @@ def _tensor_from_ptr(ptr: int, shape: Sequence[int], dtype: torch.dtype, device:
 
 
 class Communicator:
+    """One rank of a communicator of the native library: a method per collective of the C API (rccl.h:655-1051 for the
+    semantics: in-place rules, grouped send/recv, PreMulSum operators, split colours), symmetric allocations, host-side
+    barrier / all-gather over the rendezvous network, and the per-collective trace records. Tensors are passed by
+    address on the current (or given) CUDA stream; nothing here synchronises the device unless it says so.
+    """
+
     def __init__(self, rank: int, nranks: int, unique_id: bytes, device: Optional[int] = None,
                  min_ctas: Optional[int] = None, max_ctas: Optional[int] = None):
         self._lib = _lib.load()

@@ -22,6 +22,8 @@ from ..parallel.fsdp import AdamWConfig, FlatUnit, FSDPEngine, ParamSpec
 
 @dataclass
 class LlamaConfig:
+    """Shape of a Llama-style decoder (grouped-query attention, SwiGLU MLP, RMSNorm, rotary embedding, untied output matrix)."""
+
     vocab: int = 128256
     hidden: int = 4096
     layers: int = 32

@@ -51,6 +51,12 @@ def dequantize_e4m3_per128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor
 
 
 class MoELayer:
+    """A mixture-of-experts layer with the experts spread over the ranks of ``comm``: top-k routing, one dispatch kernel that
+    permutes, quantises to fp8 e4m3 (a scale per 128 channels) and stores rows into the owning ranks, grouped expert GEMMs on
+    the tcgen05 kernel, and one combine kernel that pulls the expert outputs back and applies the gate weights in a fixed
+    order. ``reference_forward`` states the same layer in plain PyTorch with NCCL-style collectives.
+    """
+
     def __init__(self, comm, experts_local: int, hidden: int, ffn: int, top_k: int, tokens: int, capacity: int = 0, std: float = 0.02, seed: int = 0):
         self.comm, self.n, self.rank = comm, comm.nranks, comm.rank
         self.el, self.hidden, self.ffn, self.k, self.T = experts_local, hidden, ffn, top_k, tokens

@@ -30,6 +30,8 @@ ALIGN = 8  # elements: every parameter starts on a 16-byte boundary inside the f
 
 @dataclass
 class ParamSpec:
+    """Name, shape and initialisation of one parameter inside a unit's flat buffer."""
+
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"  # "normal" (std below) or "ones"
@@ -42,6 +44,8 @@ class ParamSpec:
 
 @dataclass
 class AdamWConfig:
+    """AdamW hyper-parameters; ``lr`` is read at every unit's update, so a schedule may change it between steps."""
+
     lr: float = 3e-4
     betas: Tuple[float, float] = (0.9, 0.95)
     eps: float = 1e-8
@@ -50,6 +54,11 @@ class AdamWConfig:
 
 
 class FlatUnit:
+    """One gather / reduce-scatter unit (an embedding, a layer, the head): all its parameters in one flat bf16 buffer padded
+    to a multiple of the world size, of which this rank keeps a shard (bf16 for the all-gather, fp32 master copy and AdamW
+    moments for the update). ``params`` are views into the full buffer, valid while it is gathered.
+    """
+
     def __init__(self, name: str, specs: Sequence[ParamSpec], rank: int, world: int, device, seed: int):
         self.name, self.specs, self.rank, self.world, self.device = name, list(specs), rank, world, device
         offs, o = {}, 0

@@ -12,6 +12,8 @@ _OPS = {"sum": dist.ReduceOp.SUM, "avg": dist.ReduceOp.AVG, "max": dist.ReduceOp
 
 
 class NcclComm:
+    """The collectives the FSDP engine calls, on stock NCCL through ``torch.distributed`` (control runs only)."""
+
     def __init__(self, group=None):
         if not dist.is_initialized():
             raise RuntimeError("init torch.distributed with backend='nccl' first")

@@ -49,6 +49,11 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, tile: int = 256
 
 
 class TensorParallelMLP:
+    """The MLP half of a tensor-parallel transformer layer with sequence-parallel activations: gate and up projections
+    (column-parallel, interleaved per tile) inside the all-gather with the SwiGLU in the epilogue, down projection
+    (row-parallel) inside the reduce-scatter. Forward only; weights are random.
+    """
+
     def __init__(self, comm, rows_per_rank: int, hidden: int, ffn_local: int, device=None, std: float = 0.02, seed: int = 0,
                  comm_ctas: int = 0):
         self.comm = comm

@@ -72,6 +72,10 @@ def dma_plan(nbytes: int, gang: int = 0) -> list[tuple[int, int]]:
 
 
 class Shmem:
+    """A symmetric heap on top of a communicator and the host-initiated, stream-ordered operations on it.
+    Every PE must allocate in the same order; waits are bounded and report through ``take_status``.
+    """
+
     def __init__(self, comm, heap_bytes: int = 64 << 20):
         self.comm = comm
         self.lib = _l()

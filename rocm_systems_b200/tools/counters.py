@@ -164,6 +164,8 @@ def evaluate(node, env: Dict[str, float]) -> float:
 
 
 class CounterSet:
+    """Named derived metrics, each an expression over raw Nsight Compute metrics, peaks and user arguments."""
+
     def __init__(self, defs: Sequence[dict]):
         self.defs = []
         seen = set()

@@ -47,6 +47,8 @@ def _rss(pid: int) -> Optional[int]:
 
 
 class SystemSampler:
+    """Background thread that samples GPU readings (NVML) and host counters at a fixed period; a context manager."""
+
     def __init__(self, period_ms: int = 100, pids: Sequence[int] = (), gpu: bool = True, gpu_fields: Sequence[str] = GPU_FIELDS):
         self.period = period_ms / 1e3
         self.pids = list(pids)

@@ -79,6 +79,11 @@ create view if not exists busy as
 
 
 class TraceDB:
+    """A trace as an SQLite database (the role of rocpd in the reference, rocprofiler-sdk source/lib/output/sql and
+    source/lib/python/rocpd): imports the CSV files the tracers write, merges ranks, answers SQL, summarises, exports
+    Perfetto JSON and CSV.
+    """
+
     def __init__(self, path: str):
         self.path = path
         self.db = sqlite3.connect(path)

@@ -75,6 +75,8 @@ def _rows(fn, typ) -> list:
 
 
 class Profiler:
+    """In-process control of the CUPTI activity tracer: ``with Profiler(kinds, output): ...`` collects and writes the records."""
+
     def __init__(self, kernels: bool = True, memops: bool = False, runtime_api: bool = False, driver_api: bool = False, sync: bool = False):
         self.kinds = (KERNEL if kernels else 0) | (MEMOP if memops else 0) | (RUNTIME_API if runtime_api else 0) | \
                      (DRIVER_API if driver_api else 0) | (SYNC if sync else 0)
