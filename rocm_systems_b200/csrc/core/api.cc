@@ -127,7 +127,7 @@ ncclResult_t pncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id, in
 
 ncclResult_t pncclCommInitAll(ncclComm_t* comms, int ndev, const int* devlist) {
   if (!comms || ndev < 1) BFAIL(ncclInvalidArgument, "ncclCommInitAll: bad arguments");
-  if (devlist)
+  if (devlist && !Flags::get().emulateRanks)
     for (int i = 0; i < ndev; i++)
       for (int j = i + 1; j < ndev; j++)
         if (devlist[i] == devlist[j]) BFAIL(ncclInvalidUsage, "ncclCommInitAll: device %d appears twice", devlist[i]);

@@ -122,9 +122,30 @@ ncclResult_t commPollStatus(Comm* c) {
   return ncclSuccess;
 }
 
+thread_local bool tlsEmuCall = false;
+
+static std::mutex gGroupsMu;
+static std::map<std::string, std::weak_ptr<LocalGroup>> gGroups;  // keyed by the unique id's bytes
+
+static std::shared_ptr<LocalGroup> joinLocalGroup(const ncclUniqueId& id) {
+  const std::string key(reinterpret_cast<const char*>(&id), sizeof(id));
+  std::lock_guard<std::mutex> lk(gGroupsMu);
+  std::shared_ptr<LocalGroup> g = gGroups[key].lock();
+  if (!g) {
+    g = std::make_shared<LocalGroup>();
+    gGroups[key] = g;
+  }
+  std::lock_guard<std::mutex> lg(g->mu);
+  g->members++;
+  return g;
+}
+
 ncclResult_t commCheck(const Comm* c) {
   if (!c || c->magic != kCommMagic) BFAIL(ncclInvalidArgument, "invalid communicator handle");
   if (c->aborted.load()) BFAIL(ncclInvalidUsage, "communicator was aborted");
+  if (c->destroyRequested.load()) BFAIL(ncclInvalidUsage, "communicator was destroyed");
+  // Ranks that share a GPU must never run as separate kernels that wait on one another: nothing makes them run together.
+  if (c->emulated && !tlsEmuCall) BFAIL(ncclInvalidUsage, "this communicator shares its GPU with other ranks (B200COLL_EMULATE_RANKS): only the b200collEmu* entry points run on it");
   return ncclSuccess;
 }
 
@@ -169,8 +190,10 @@ ncclResult_t commCreate(Comm** out, const ncclUniqueId& id, int nranks, int rank
   gethostname(me.host, sizeof(me.host) - 1);
   BCHECK(c->boot.allGather(&me, all, sizeof(Who)));
   for (int p = 0; p < nranks; p++) {
-    if (p != rank && strcmp(all[p].bus, me.bus) == 0 && strcmp(all[p].host, me.host) == 0)
-      BFAIL(ncclInvalidUsage, "ranks %d and %d both use GPU %s", rank, p, me.bus);
+    if (p != rank && strcmp(all[p].bus, me.bus) == 0 && strcmp(all[p].host, me.host) == 0) {
+      if (!fl.emulateRanks) BFAIL(ncclInvalidUsage, "ranks %d and %d both use GPU %s", rank, p, me.bus);
+      c->emulated = true;
+    }
     if (strcmp(all[p].host, me.host) != 0) BFAIL(ncclInvalidUsage, "rank %d is on host %s, rank %d on %s: one NVSwitch box only", rank, me.host, p, all[p].host);
   }
 
@@ -218,13 +241,49 @@ ncclResult_t commCreate(Comm** out, const ncclUniqueId& id, int nranks, int rank
   loadTuning(c.get());
   if (fl.traceEnable) c->tracer = new Tracer(rank, nranks, dev);
   c->watchdog = std::thread(watchdogLoop, c.get());
+  c->localGroup = joinLocalGroup(id);
   BINFO(SUB_INIT, "rank %d/%d on cuda:%d ready: workspace %zu MiB, nvls %d, ctas [%d,%d]", rank, nranks, dev, total >> 20, (int)c->nvls, c->minCtas, c->maxCtas);
   *out = c.release();
   return ncclSuccess;
 }
 
+static ncclResult_t commDestroyNow(Comm* c, bool abort);
+
 ncclResult_t commDestroy(Comm* c, bool abort) {
   if (!c || c->magic != kCommMagic) BFAIL(ncclInvalidArgument, "invalid communicator handle");
+  if (c->destroyRequested.exchange(true)) return ncclSuccess;  // already on its way out
+  std::shared_ptr<LocalGroup> g = c->localGroup;
+  if (!g) return commDestroyNow(c, abort);
+  std::vector<Comm*> run;
+  {
+    std::lock_guard<std::mutex> lk(g->mu);
+    if (abort) {
+      g->members--;  // an aborted rank takes no part in the collective teardown of the others
+    } else {
+      g->waiting.push_back(c);
+    }
+    if (g->members > 0 && (int)g->waiting.size() >= g->members) {
+      run.swap(g->waiting);
+      g->members = 0;
+    } else if (!abort) {
+      return ncclSuccess;  // deferred: runs when the last rank of this process is destroyed
+    }
+  }
+  ncclResult_t res = abort ? commDestroyNow(c, true) : ncclSuccess;
+  if (run.size() == 1) {
+    ncclResult_t r = commDestroyNow(run[0], false);
+    return res != ncclSuccess ? res : r;
+  }
+  std::vector<ncclResult_t> rs(run.size(), ncclSuccess);
+  std::vector<std::thread> th;
+  for (size_t i = 0; i < run.size(); i++) th.emplace_back([&, i] { rs[i] = commDestroyNow(run[i], false); });
+  for (auto& t : th) t.join();
+  for (ncclResult_t r : rs)
+    if (res == ncclSuccess && r != ncclSuccess) res = r;
+  return res;
+}
+
+static ncclResult_t commDestroyNow(Comm* c, bool abort) {
   int prevDev = -1;
   cudaGetDevice(&prevDev);
   cudaSetDevice(c->cudaDev);

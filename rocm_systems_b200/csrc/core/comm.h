@@ -50,6 +50,17 @@ struct TuneEntry {       // one row of the size -> algorithm table
 };
 enum Algo : int { ALGO_AUTO = 0, ALGO_LL = 1, ALGO_P2P = 2, ALGO_NVLS = 3 };
 
+// The ranks of one communicator that live in this process (ncclCommInitAll, or one thread per rank). Tearing a
+// communicator down is collective (every rank must have finished its device work before anyone unbinds memory), so a
+// thread that destroys its ranks one after the other would wait for ranks it has not come to yet: their teardown is
+// deferred until the last of them has been asked for and then runs for all of them at once.
+struct Comm;
+struct LocalGroup {
+  std::mutex mu;
+  int members = 0;
+  std::vector<Comm*> waiting;
+};
+
 struct Comm {
   uint64_t magic = 0;
   int rank = -1, nranks = 0, cudaDev = -1;
@@ -61,6 +72,7 @@ struct Comm {
   DevStatus* status = nullptr;       // mapped host memory
   uint32_t* abortFlag = nullptr;     // mapped host memory
   bool nvls = false;                 // workspace has a multicast alias
+  bool emulated = false;             // shares its GPU with other ranks of the communicator: only b200collEmu* may launch on it
   uint64_t opSeq = 0;
   uint32_t llSeq = 0;
   uint32_t stageParity = 0;
@@ -72,7 +84,8 @@ struct Comm {
   std::vector<PreMulOp> premul;
   std::vector<TuneEntry> tuning;
   std::atomic<int> asyncError{ncclSuccess};
-  std::atomic<bool> finalized{false}, aborted{false};
+  std::atomic<bool> finalized{false}, aborted{false}, destroyRequested{false};
+  std::shared_ptr<LocalGroup> localGroup;
   std::string lastErr;
   std::thread watchdog;
   std::atomic<bool> stopWatchdog{false};
@@ -82,6 +95,7 @@ struct Comm {
   // Finds the window containing [ptr, ptr+bytes) and the offset of ptr inside it.
   Window* findWindow(const void* ptr, size_t bytes, size_t* off);
 };
+extern thread_local bool tlsEmuCall;  // set while a b200collEmu* entry point runs on this thread
 constexpr uint64_t kCommMagic = 0xb200c0440000c033ull;
 
 ncclResult_t commCreate(Comm** out, const ncclUniqueId& id, int nranks, int rank, const ncclConfig_t* config);

@@ -98,6 +98,7 @@ static void load(Flags& f) {
   f.p2pCtasPerPeer = parseInt(envOf("P2P_CTAS", false), f.p2pCtasPerPeer);
   if (const char* v = envOf("PIPELINE_CHUNK", false)) f.pipeChunkBytes = (long long)parseSize(v, 0);
   f.dmaGang = parseInt(envOf("DMA_GANG", false), f.dmaGang);
+  f.emulateRanks = parseInt(envOf("EMULATE_RANKS", false), f.emulateRanks);
   f.waitTimeoutMs = parseInt(envOf("WAIT_TIMEOUT_MS", false), f.waitTimeoutMs);
   f.bootTimeoutMs = parseInt(envOf("BOOTSTRAP_TIMEOUT_MS", false), f.bootTimeoutMs);
   if (const char* v = envOf("COMM_ID")) f.commId = v;
@@ -255,6 +256,7 @@ const SettingDoc kSettings[] = {
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
     {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},
     {"DMA_GANG", false, "0", "copy engines one copy-engine put/get is split over (0: 1, 2 or 4 by size; at most 8)"},
+    {"EMULATE_RANKS", false, "0", "1: ranks may share a GPU; their communicators serve only the b200collEmu* entry points, which play all ranks in one kernel (tests)"},
     {"WAIT_TIMEOUT_MS", false, "20000", "budget of every device-side wait; on expiry the kernel records the wait and returns"},
     {"BOOTSTRAP_TIMEOUT_MS", false, "120000", "budget of the host rendezvous"},
     {"COMM_ID", true, "", "ip:port of the rendezvous root (ncclGetUniqueId then needs no out-of-band exchange)"},
@@ -282,6 +284,7 @@ std::string currentValue(const Flags& f, const std::string& n) {
   if (n == "P2P_CTAS") return num(f.p2pCtasPerPeer);
   if (n == "PIPELINE_CHUNK") return num(f.pipeChunkBytes);
   if (n == "DMA_GANG") return num(f.dmaGang);
+  if (n == "EMULATE_RANKS") return num(f.emulateRanks);
   if (n == "WAIT_TIMEOUT_MS") return num(f.waitTimeoutMs);
   if (n == "BOOTSTRAP_TIMEOUT_MS") return num(f.bootTimeoutMs);
   if (n == "COMM_ID") return f.commId;

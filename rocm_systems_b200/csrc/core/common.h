@@ -97,6 +97,7 @@ struct Flags {
   std::string toolLibs;          // TOOL_LIBRARIES: ':'-separated tools given the dispatch table
   long long pipeChunkBytes = -1;  // PIPELINE_CHUNK: staged-reduce pipeline chunk; -1 picks by size, 0 disables
   int dmaGang = 0;                // DMA_GANG: copy engines per copy-engine transfer; 0 picks by size
+  int emulateRanks = 0;           // EMULATE_RANKS: several ranks may share one GPU; such communicators only serve b200collEmu*
   int traceEnable = 0;           // TRACE: record per-collective device timestamps
   std::string traceFile;         // TRACE_FILE: CSV written at communicator destroy
   std::string failKey;           // FAIL_KEY: host-side fault-injection points (tests)
