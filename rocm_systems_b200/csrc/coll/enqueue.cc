@@ -224,6 +224,38 @@ ncclResult_t planColl(const CollReq& r, Plan* plan) {
   return planInternal(r, rop, plan, &args);
 }
 
+ncclResult_t emuPrepare(const CollReq& r, Plan* plan, CollArgs* args, LLArgs* ll, DevComm* dc) {
+  Comm* c = r.comm;
+  BCHECK(commCheck(c));
+  const int n = c->nranks;
+  if ((int)r.dt < 0 || (int)r.dt >= ncclNumTypes) BFAIL(ncclInvalidArgument, "invalid datatype %d", (int)r.dt);
+  if (r.op < 0 || r.op >= ncclNumOps) BFAIL(ncclInvalidArgument, "the emulation takes the built-in reduction operators only");
+  if (n < 2 || r.count == 0) BFAIL(ncclInvalidArgument, "the emulation needs at least two ranks and a non-empty message");
+  const bool rooted = r.kind == COLL_REDUCE || r.kind == COLL_BROADCAST;
+  if (rooted && (r.root < 0 || r.root >= n)) BFAIL(ncclInvalidArgument, "root %d outside [0, %d)", r.root, n);
+  const size_t es = dtypeSize(r.dt);
+  if ((((uintptr_t)r.send) | ((uintptr_t)r.recv)) & (es - 1)) BFAIL(ncclInvalidArgument, "buffer not aligned to its element size");
+  ResolvedOp rop{r.op == ncclAvg ? (int)ncclSum : r.op, r.op == ncclAvg ? SCALE_POST_DIV_N : SCALE_NONE, 0};
+  BCHECK(planInternal(r, rop, plan, args));
+  *dc = c->dev;
+  dc->opSeq = ++c->opSeq;
+  dc->stamp = nullptr;
+  memset(ll, 0, sizeof(*ll));
+  if (plan->algo == ALGO_LL) {
+    ll->send = r.send;
+    ll->recv = r.recv;
+    ll->count = r.count;
+    ll->scaleMode = rop.scaleMode;
+    ll->scalarBits = rop.bits;
+    if (++c->llSeq == 0) c->llSeq = 2;
+    ll->seq = c->llSeq;
+  } else {
+    args->stageHalf = (int)(c->stageParity & 1);
+    c->stageParity += (uint32_t)plan->chunks;
+  }
+  return ncclSuccess;
+}
+
 ncclResult_t enqueueColl(const CollReq& r) {
   Comm* c = r.comm;
   BCHECK(commCheck(c));

@@ -37,5 +37,9 @@ ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops);
 // What the chooser would pick (exposed for tests and the tuner).
 struct Plan { int algo; int ctas; bool direct; size_t chunks; };
 ncclResult_t planColl(const CollReq& r, Plan* plan);
+// One rank's share of a collective for the single-kernel emulation of several ranks on one GPU: everything enqueueColl
+// does up to the launch (validation, plan, kernel arguments, sequence numbers, staging parity), nothing launched.
+// plan->algo == ALGO_LL: `ll` is filled, otherwise `args`.
+ncclResult_t emuPrepare(const CollReq& r, Plan* plan, CollArgs* args, LLArgs* ll, DevComm* dc);
 
 }  // namespace b200

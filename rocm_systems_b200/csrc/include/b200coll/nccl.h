@@ -219,6 +219,17 @@ ncclResult_t b200collHostAllGather(ncclComm_t comm, const void* send, void* recv
 /* Device-side barrier enqueued on `stream`. */
 ncclResult_t b200collBarrier(ncclComm_t comm, cudaStream_t stream);
 
+/* ---- Extensions for tests on a single GPU: several ranks played by one cooperative kernel --------
+ * With B200COLL_EMULATE_RANKS=1 (and B200COLL_NVLS_ENABLE=0) ncclCommInitAll accepts the same device several times.
+ * Such communicators refuse every launching entry point except these: separate kernels of ranks that wait on one
+ * another must never share a GPU. kind: 0 all-reduce, 1 reduce-scatter, 2 reduce, 3 all-gather, 4 broadcast; types
+ * float, bfloat16, int32; operators sum, max, avg. send[r] / recv[r] are rank r's buffers. */
+ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const void* const* send, void* const* recv, size_t count, ncclDataType_t dt,
+                                   ncclRedOp_t op, int root, int ctasPerRank, cudaStream_t stream);
+/* Creates `nranks` such communicators on the current GPU, runs every collective in the three types on `count`
+ * elements, verifies on the host; *wrong = wrong elements, *status = first asynchronous error of any rank. */
+ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int* status);
+
 /* ---- Extensions that need no GPU: what the planner would do, and the settings ------------ */
 
 /* What the planner chooses for a collective on a communicator of `nranks` ranks, with or without a multicast
