@@ -21,6 +21,9 @@
 #include <vector>
 
 #include "../core/comm.h"
+#include "../trace/tracer.h"
+#include "b200coll/api_trace.h"
+#include "b200coll/fused.h"
 #include "b200coll/nccl.h"
 #include "device.h"
 #include "enqueue.h"
@@ -53,6 +56,16 @@ __device__ __forceinline__ Dim grid() { return Dim{gLanes, 1, 1}; }
 #define blockIdx (::b200::emu::block())
 #define gridDim (::b200::emu::grid())
 #include "kernels.cuh"
+#define B200_EMU_KERNELS_ONLY 1
+// Non-template functions get names of their own here: the library's other object file defines the originals.
+#define kReduceScatterCast emuReduceScatterCast
+#define kReduceScatterCastDirect emuReduceScatterCastDirect
+#define kCastScaleSolo emuCastScaleSolo
+#include "../fused/fsdp_kernels.cu"  // the kernels and their helpers only
+#undef kReduceScatterCast
+#undef kReduceScatterCastDirect
+#undef kCastScaleSolo
+#undef B200_EMU_KERNELS_ONLY
 #undef blockIdx
 #undef gridDim
 #pragma pop_macro("__grid_constant__")
@@ -83,7 +96,17 @@ __global__ void __launch_bounds__(kCollThreads) kCopy(const Pack* p) {
   kStagedCopy<false>(p->c[r], p->a[r], p->elemSize);
 }
 
-static cudaError_t launchCoop(const void* fn, int blocks, int threads, size_t smem, const Pack* devPack, unsigned lanes, cudaStream_t s) {
+struct RsCastPack {
+  DevComm c[kMaxRanks];
+  RsCastArgs a[kMaxRanks];
+  int lanes;
+};
+__global__ void __launch_bounds__(kReduceThreads) kRsCast(const RsCastPack* p) {
+  const unsigned r = blockIdx.x / (unsigned)p->lanes;
+  emuReduceScatterCast(p->c[r], p->a[r]);
+}
+
+static cudaError_t launchCoop(const void* fn, int blocks, int threads, size_t smem, const void* devPack, unsigned lanes, cudaStream_t s) {
   cudaError_t e = cudaMemcpyToSymbolAsync(gLanes, &lanes, sizeof(lanes), 0, cudaMemcpyHostToDevice, s);
   if (e != cudaSuccess) return e;
   if (smem > (48u << 10)) {
@@ -178,6 +201,44 @@ ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const voi
   return ncclSuccess;
 }
 
+// The fused FSDP gradient reduce-scatter (bf16 in, fp32 out, scaled) on emulated ranks: send[r] holds n * recvcount
+// bf16 elements, recv[r] receives rank r's recvcount fp32 sums. The host side restates what b200collReduceScatterCast
+// does for ordinary buffers (CTAs, equal chunks of one rank's staging share, staging parity).
+ncclResult_t b200collEmuReduceScatterCast(ncclComm_t* comms, int n, const void* const* send, float* const* recv, size_t recvcount, float scale,
+                                          int ctasPerRank, cudaStream_t stream) {
+  if (!comms || n < 2 || n > kMaxRanks || !send || !recv || recvcount == 0) BFAIL(ncclInvalidArgument, "b200collEmuReduceScatterCast: bad arguments");
+  struct Scope {
+    Scope() { tlsEmuCall = true; }
+    ~Scope() { tlsEmuCall = false; }
+  } scope;
+  emu::RsCastPack pack{};
+  const int lanes = ctasPerRank > 0 ? std::min(ctasPerRank, 16) : 8;
+  const size_t bytes = recvcount * 2;
+  for (int r = 0; r < n; r++) {
+    Comm* c = asComm(comms[r]);
+    BCHECK(commCheck(c));
+    if (!c->emulated || c->nranks != n || c->rank != r) BFAIL(ncclInvalidUsage, "b200collEmuReduceScatterCast: comms[%d] must be rank %d of %d ranks sharing one GPU", r, r, n);
+    const size_t capMax = (c->dev.stageBytes / n) & ~(size_t)15;
+    const size_t k = (bytes + capMax - 1) / capMax;
+    size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;
+    if (cap > capMax) cap = capMax;
+    pack.a[r] = RsCastArgs{(const __nv_bfloat16*)send[r], recv[r], recvcount, scale, (int)(c->stageParity & 1), cap};
+    c->stageParity += (uint32_t)((bytes + cap - 1) / cap);
+    pack.c[r] = c->dev;
+    pack.c[r].opSeq = ++c->opSeq;
+    pack.c[r].stamp = nullptr;
+  }
+  pack.lanes = lanes;
+  emu::RsCastPack* devPack = nullptr;
+  BCUDA(cudaMallocAsync((void**)&devPack, sizeof(pack), stream));
+  BCUDA(cudaMemcpyAsync(devPack, &pack, sizeof(pack), cudaMemcpyHostToDevice, stream));
+  BCUDA(cudaStreamSynchronize(stream));
+  cudaError_t e = emu::launchCoop((const void*)emu::kRsCast, n * lanes, kReduceThreads, 0, devPack, (unsigned)lanes, stream);
+  cudaFreeAsync(devPack, stream);
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collEmuReduceScatterCast: launch of %d x %d blocks failed: %s", n, lanes, cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
 // Self-check on the current GPU: `nranks` emulated ranks, all-reduce (sum, max, avg), reduce-scatter, reduce,
 // all-gather and broadcast of `count` elements in float, bfloat16 and int32, out of place, verified on the host against
 // sums of small integers (exact in every type). Returns the number of wrong elements, and in *status the first
@@ -259,6 +320,38 @@ ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int
           if (!(got >= want - tol && got <= want + tol)) (*wrong)++;
         }
         for (size_t b = recvElems * es; b < recvElems * es + 64; b++)  // the bytes behind the output keep their fill
+          if ((unsigned char)out[b] != 0xEE) (*wrong)++;
+      }
+    }
+  }
+  // The fused FSDP gradient path: bf16 gradients of every rank -> this rank's fp32 mean.
+  if (res == ncclSuccess) {
+    salt++;
+    const float scale = 1.0f / (float)nranks;
+    std::vector<float*> out32(nranks);
+    for (int r = 0; r < nranks; r++) {
+      std::vector<__nv_bfloat16> in(count * nranks);
+      for (size_t i = 0; i < in.size(); i++) in[i] = __float2bfloat16((float)value(r, i, salt));
+      BCUDA(cudaMemcpyAsync(send[r], in.data(), in.size() * 2, cudaMemcpyHostToDevice, st));
+      BCUDA(cudaMemsetAsync(recv[r], 0xEE, count * 4 + 64, st));
+      BCUDA(cudaStreamSynchronize(st));  // `in` goes out of scope
+      out32[r] = (float*)recv[r];
+    }
+    res = b200collEmuReduceScatterCast(comms.data(), nranks, send.data(), out32.data(), count, scale, 0, st);
+    if (res == ncclSuccess) {
+      BCUDA(cudaStreamSynchronize(st));
+      for (int r = 0; r < nranks; r++) {
+        std::vector<char> out(count * 4 + 64);
+        BCUDA(cudaMemcpy(out.data(), recv[r], out.size(), cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < count; i++) {
+          float sum = 0;
+          for (int p = 0; p < nranks; p++) sum += (float)value(p, (size_t)r * count + i, salt);
+          float got;
+          memcpy(&got, &out[i * 4], 4);
+          const float want = sum * scale;
+          if (!(got >= want - 1e-6f && got <= want + 1e-6f)) (*wrong)++;
+        }
+        for (size_t b = count * 4; b < count * 4 + 64; b++)
           if ((unsigned char)out[b] != 0xEE) (*wrong)++;
       }
     }

@@ -169,6 +169,7 @@ __global__ void __launch_bounds__(256) kCastScaleSolo(const __nv_bfloat16* in, f
 
 }  // namespace b200
 
+#ifndef B200_EMU_KERNELS_ONLY  // the emulation of several ranks on one GPU takes the kernels above and brings its own host side
 using namespace b200;
 
 extern "C" ncclResult_t b200collReduceScatterCast(ncclComm_t comm, const void* sendBf16, float* recvF32, size_t recvcount, float scale, cudaStream_t stream) {
@@ -236,3 +237,4 @@ extern "C" ncclResult_t b200collReduceScatterCast(ncclComm_t comm, const void* s
   if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collReduceScatterCast launch failed: %s", cudaGetErrorString(e));
   return ncclSuccess;
 }
+#endif  // B200_EMU_KERNELS_ONLY

@@ -226,8 +226,12 @@ ncclResult_t b200collBarrier(ncclComm_t comm, cudaStream_t stream);
  * float, bfloat16, int32; operators sum, max, avg. send[r] / recv[r] are rank r's buffers. */
 ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const void* const* send, void* const* recv, size_t count, ncclDataType_t dt,
                                    ncclRedOp_t op, int root, int ctasPerRank, cudaStream_t stream);
-/* Creates `nranks` such communicators on the current GPU, runs every collective in the three types on `count`
- * elements, verifies on the host; *wrong = wrong elements, *status = first asynchronous error of any rank. */
+/* The fused gradient reduce-scatter of the FSDP path on such communicators: send[r] holds n * recvcount bf16 values,
+ * recv[r] receives rank r's recvcount fp32 sums times `scale`. */
+ncclResult_t b200collEmuReduceScatterCast(ncclComm_t* comms, int n, const void* const* send, float* const* recv, size_t recvcount, float scale,
+                                          int ctasPerRank, cudaStream_t stream);
+/* Creates `nranks` such communicators on the current GPU, runs every collective in the three types and the fused
+ * reduce-scatter on `count` elements, verifies on the host; *wrong = wrong elements, *status = first asynchronous error of any rank. */
 ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int* status);
 
 /* ---- Extensions that need no GPU: what the planner would do, and the settings ------------ */
