@@ -55,7 +55,13 @@ __device__ __forceinline__ Dim grid() { return Dim{gLanes, 1, 1}; }
 #define __grid_constant__
 #define blockIdx (::b200::emu::block())
 #define gridDim (::b200::emu::grid())
+#define B200_MISC_KERNELS 1       // the send/recv kernel too, under names of its own (launch.cu defines the originals)
+#define kP2p emuP2p
+#define kBarrier emuBarrier
 #include "kernels.cuh"
+#undef kP2p
+#undef kBarrier
+#undef B200_MISC_KERNELS
 #define B200_EMU_KERNELS_ONLY 1
 // Non-template functions get names of their own here: the library's other object file defines the originals.
 #define kReduceScatterCast emuReduceScatterCast
@@ -94,6 +100,16 @@ template <typename T, typename Op> __global__ void __launch_bounds__(kCollThread
 __global__ void __launch_bounds__(kCollThreads) kCopy(const Pack* p) {
   const unsigned r = blockIdx.x / (unsigned)p->lanes;
   kStagedCopy<false>(p->c[r], p->a[r], p->elemSize);
+}
+
+struct P2pPack {
+  DevComm c[kMaxRanks];
+  P2pArgs a[kMaxRanks];
+  int lanes;
+};
+__global__ void __launch_bounds__(kCollThreads) kSendRecv(const P2pPack* p) {
+  const unsigned r = blockIdx.x / (unsigned)p->lanes;
+  emuP2p(p->c[r], p->a[r]);
 }
 
 struct RsCastPack {
@@ -198,6 +214,65 @@ ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const voi
   cudaError_t e = emu::launchCoop(fn, n * lanes, threads, smem, devPack, (unsigned)lanes, stream);
   cudaFreeAsync(devPack, stream);
   if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collEmuCollective: launch of %d x %d blocks failed: %s", n, lanes, cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
+// All-to-all of `bytesPerPeer` bytes between every pair of emulated ranks, as the grouped send/recv kernel runs it: one
+// send and one receive work item per peer and rank, each on the communicator's sub-channels, through the FIFO slots and
+// credits of the real workspaces. Rank r's own block is a local copy.
+ncclResult_t b200collEmuAllToAll(ncclComm_t* comms, int n, const void* const* send, void* const* recv, size_t bytesPerPeer, cudaStream_t stream) {
+  if (!comms || n < 2 || n > kMaxRanks || !send || !recv || bytesPerPeer == 0) BFAIL(ncclInvalidArgument, "b200collEmuAllToAll: bad arguments");
+  struct Scope {
+    Scope() { tlsEmuCall = true; }
+    ~Scope() { tlsEmuCall = false; }
+  } scope;
+  emu::P2pPack pack{};
+  int subs = 0;
+  for (int r = 0; r < n; r++) {
+    Comm* c = asComm(comms[r]);
+    BCHECK(commCheck(c));
+    if (!c->emulated || c->nranks != n || c->rank != r) BFAIL(ncclInvalidUsage, "b200collEmuAllToAll: comms[%d] must be rank %d of %d ranks sharing one GPU", r, r, n);
+    P2pArgs& pa = pack.a[r];
+    for (int d = 1; d < n; d++) {
+      const int to = (r + d) % n, from = (r - d + n) % n;
+      P2pWork& ws = pa.work[pa.nwork++];
+      ws.peer = to;
+      ws.isSend = 1;
+      ws.src = (const char*)send[r] + (size_t)to * bytesPerPeer;
+      ws.dst = nullptr;
+      ws.bytes = bytesPerPeer;
+      P2pWork& wr = pa.work[pa.nwork++];
+      wr.peer = from;
+      wr.isSend = 0;
+      wr.src = nullptr;
+      wr.dst = (char*)recv[r] + (size_t)from * bytesPerPeer;
+      wr.bytes = bytesPerPeer;
+    }
+    BCUDA(cudaMemcpyAsync((char*)recv[r] + (size_t)r * bytesPerPeer, (const char*)send[r] + (size_t)r * bytesPerPeer, bytesPerPeer, cudaMemcpyDeviceToDevice, stream));
+    pack.c[r] = c->dev;
+    pack.c[r].opSeq = ++c->opSeq;
+    pack.c[r].stamp = nullptr;
+    subs = c->dev.p2pSubs;
+  }
+  // All blocks must be resident together: use as many of the communicator's sub-channels as fit. Sender and receiver
+  // of a launch agree on the number (it is part of the device view both get), and the FIFOs are empty between launches.
+  int perSm = 0, dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  BCUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, (const void*)emu::kSendRecv, kCollThreads, 0));
+  const int fit = (perSm * sms) / (n * pack.a[0].nwork);
+  if (fit < 1) BFAIL(ncclInternalError, "b200collEmuAllToAll: %d ranks do not fit this GPU", n);
+  subs = std::min(subs, fit);
+  for (int r = 0; r < n; r++) pack.c[r].p2pSubs = subs;
+  const int lanes = pack.a[0].nwork * subs;
+  pack.lanes = lanes;
+  emu::P2pPack* devPack = nullptr;
+  BCUDA(cudaMallocAsync((void**)&devPack, sizeof(pack), stream));
+  BCUDA(cudaMemcpyAsync(devPack, &pack, sizeof(pack), cudaMemcpyHostToDevice, stream));
+  BCUDA(cudaStreamSynchronize(stream));
+  cudaError_t e = emu::launchCoop((const void*)emu::kSendRecv, n * lanes, kCollThreads, 0, devPack, (unsigned)lanes, stream);
+  cudaFreeAsync(devPack, stream);
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collEmuAllToAll: launch of %d x %d blocks failed: %s", n, lanes, cudaGetErrorString(e));
   return ncclSuccess;
 }
 
@@ -353,6 +428,32 @@ ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int
         }
         for (size_t b = count * 4; b < count * 4 + 64; b++)
           if ((unsigned char)out[b] != 0xEE) (*wrong)++;
+      }
+    }
+  }
+  // All-to-all through the send/recv FIFOs: rank s sends the block (s, d) to rank d.
+  if (res == ncclSuccess) {
+    salt++;
+    const size_t per = std::min<size_t>(count, (size_t)1 << 20) * 4;  // bytes per pair, several FIFO slots for the larger counts
+    const size_t words = per / 4;
+    for (int r = 0; r < nranks; r++) {
+      std::vector<int32_t> in(words * nranks);
+      for (size_t i = 0; i < in.size(); i++) in[i] = value(r, i, salt) + 100 * r;
+      BCUDA(cudaMemcpyAsync(send[r], in.data(), in.size() * 4, cudaMemcpyHostToDevice, st));
+      BCUDA(cudaMemsetAsync(recv[r], 0xEE, words * nranks * 4 + 64, st));
+      BCUDA(cudaStreamSynchronize(st));
+    }
+    res = b200collEmuAllToAll(comms.data(), nranks, send.data(), recv.data(), per, st);
+    if (res == ncclSuccess) {
+      BCUDA(cudaStreamSynchronize(st));
+      for (int r = 0; r < nranks; r++) {
+        std::vector<int32_t> out(words * nranks + 16);
+        BCUDA(cudaMemcpy(out.data(), recv[r], out.size() * 4, cudaMemcpyDeviceToHost));
+        for (int src = 0; src < nranks; src++)
+          for (size_t i = 0; i < words; i++)
+            if (out[(size_t)src * words + i] != value(src, (size_t)r * words + i, salt) + 100 * src) (*wrong)++;
+        for (size_t i = words * nranks; i < words * nranks + 16; i++)
+          if ((uint32_t)out[i] != 0xEEEEEEEEu) (*wrong)++;
       }
     }
   }

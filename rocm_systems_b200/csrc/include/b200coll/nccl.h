@@ -226,6 +226,8 @@ ncclResult_t b200collBarrier(ncclComm_t comm, cudaStream_t stream);
  * float, bfloat16, int32; operators sum, max, avg. send[r] / recv[r] are rank r's buffers. */
 ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const void* const* send, void* const* recv, size_t count, ncclDataType_t dt,
                                    ncclRedOp_t op, int root, int ctasPerRank, cudaStream_t stream);
+/* All-to-all of bytesPerPeer bytes per pair through the grouped send/recv kernel (FIFO slots and credits). */
+ncclResult_t b200collEmuAllToAll(ncclComm_t* comms, int n, const void* const* send, void* const* recv, size_t bytesPerPeer, cudaStream_t stream);
 /* The fused gradient reduce-scatter of the FSDP path on such communicators: send[r] holds n * recvcount bf16 values,
  * recv[r] receives rank r's recvcount fp32 sums times `scale`. */
 ncclResult_t b200collEmuReduceScatterCast(ncclComm_t* comms, int n, const void* const* send, float* const* recv, size_t recvcount, float scale,
