@@ -130,6 +130,8 @@ static std::map<std::string, std::weak_ptr<LocalGroup>> gGroups;  // keyed by th
 static std::shared_ptr<LocalGroup> joinLocalGroup(const ncclUniqueId& id) {
   const std::string key(reinterpret_cast<const char*>(&id), sizeof(id));
   std::lock_guard<std::mutex> lk(gGroupsMu);
+  if (gGroups.size() > 64)  // forget communicators that are long gone
+    for (auto it = gGroups.begin(); it != gGroups.end();) it = it->second.expired() ? gGroups.erase(it) : std::next(it);
   std::shared_ptr<LocalGroup> g = gGroups[key].lock();
   if (!g) {
     g = std::make_shared<LocalGroup>();
