@@ -25,6 +25,7 @@
 #include "b200coll/api_trace.h"
 #include "b200coll/fused.h"
 #include "b200coll/nccl.h"
+#include "b200coll/shmem.h"
 #include "device.h"
 #include "enqueue.h"
 #include "launch.h"
@@ -456,6 +457,12 @@ ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int
           if ((uint32_t)out[i] != 0xEEEEEEEEu) (*wrong)++;
       }
     }
+  }
+  // Device-initiated communication: put+signal ring and remote atomics, every PE a block of one kernel.
+  if (res == ncclSuccess) {
+    int errs = 0;
+    res = b200shmem_emu_selftest(comms.data(), nranks, 4099, 4, 51, &errs);
+    *wrong += errs;
   }
   for (int r = 0; r < nranks; r++) {
     ncclResult_t ae = ncclSuccess;

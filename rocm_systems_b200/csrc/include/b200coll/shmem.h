@@ -84,6 +84,10 @@ int b200shmem_take_status(b200shmem_ctx_t ctx);
 ncclResult_t b200shmem_selftest_ring(b200shmem_ctx_t ctx, size_t count, int rounds, cudaStream_t stream, int* errors);
 ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStream_t stream, int* errors);
 
+/* The two self-checks between `n` PEs that share the current GPU (communicators created under B200COLL_EMULATE_RANKS=1):
+ * every PE is one block of a single cooperative kernel. For tests on one GPU. */
+ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int rounds, int iters, int* errors);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,8 @@
 // b200shmem host API and the kernels behind its stream-ordered operations and self-tests.
 #include <map>
 #include <mutex>
+#include <thread>
+#include <vector>
 
 #include "../coll/launch.h"
 #include "../core/comm.h"
@@ -42,8 +44,8 @@ __global__ void kBarrierAll(b200shmem_dev_t d) { b200shmem::barrier_all_block(d)
 
 // Ring exchange driven entirely from the device: put+signal to the right neighbour, wait for
 // the left neighbour's signal, verify, barrier, repeat.
-__global__ void kSelftestRing(b200shmem_dev_t d, unsigned long long* data /*[2][count]*/, unsigned long long* src, unsigned long long* sig /*[2]*/,
-                              size_t count, int rounds, int* errors) {
+__device__ __forceinline__ void ringBody(const b200shmem_dev_t& d, unsigned long long* data /*[2][count]*/, unsigned long long* src,
+                                         unsigned long long* sig /*[2]*/, size_t count, int rounds, int* errors) {
   const int right = (d.pe + 1) % d.npes, left = (d.pe + d.npes - 1) % d.npes;
   int bad = 0;
   for (int r = 0; r < rounds; r++) {
@@ -62,9 +64,14 @@ __global__ void kSelftestRing(b200shmem_dev_t d, unsigned long long* data /*[2][
   if (bad) atomicAdd(errors, bad);
 }
 
+__global__ void kSelftestRing(b200shmem_dev_t d, unsigned long long* data, unsigned long long* src, unsigned long long* sig, size_t count, int rounds,
+                              int* errors) {
+  ringBody(d, data, src, sig, count, rounds, errors);
+}
+
 // words (on PE 0): [0] u64 counter (fetch_add), [1] u64 bit set (or), [2] u64 CAS counter,
 // [3] u64 xor accumulator, [4] u32 counter, [5] u64 swap slot, [6] u64 and-mask.
-__global__ void kSelftestAtomics(b200shmem_dev_t d, unsigned long long* words, int iters, int* errors) {
+__device__ __forceinline__ void atomicsBody(const b200shmem_dev_t& d, unsigned long long* words, int iters, int* errors) {
   int bad = 0;
   if (threadIdx.x == 0) {
     if (d.pe == 0) words[6] = ~0ull;
@@ -106,6 +113,29 @@ __global__ void kSelftestAtomics(b200shmem_dev_t d, unsigned long long* words, i
   }
   if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
   if (bad && threadIdx.x == 0) atomicAdd(errors, bad);
+}
+
+__global__ void kSelftestAtomics(b200shmem_dev_t d, unsigned long long* words, int iters, int* errors) { atomicsBody(d, words, iters, errors); }
+
+// Several PEs on one GPU: block r of ONE cooperative launch is PE r (kernels of PEs that wait on one another must never
+// be separate launches on one GPU). The bodies are the ones above, each on its PE's own device context.
+struct EmuShmemPack {
+  b200shmem_dev_t d[B200SHMEM_MAX_PES];
+  unsigned long long* data[B200SHMEM_MAX_PES];
+  unsigned long long* src[B200SHMEM_MAX_PES];
+  unsigned long long* sig[B200SHMEM_MAX_PES];
+  unsigned long long* words[B200SHMEM_MAX_PES];
+  size_t count;
+  int rounds, iters;
+  int* errors;
+};
+__global__ void kEmuRing(const EmuShmemPack* p) {
+  const int r = blockIdx.x;
+  ringBody(p->d[r], p->data[r], p->src[r], p->sig[r], p->count, p->rounds, p->errors);
+}
+__global__ void kEmuAtomics(const EmuShmemPack* p) {
+  const int r = blockIdx.x;
+  atomicsBody(p->d[r], p->words[r], p->iters, p->errors);
 }
 
 struct DevGuard {
@@ -427,6 +457,69 @@ int b200shmem_dma_engines(b200shmem_ctx_t ctx) {
   int v = 0;
   if (cudaDeviceGetAttribute(&v, cudaDevAttrAsyncEngineCount, ctx->comm->cudaDev) != cudaSuccess) return -1;
   return v;
+}
+
+// Device-initiated communication between `n` PEs that share the current GPU (communicators created under
+// B200COLL_EMULATE_RANKS=1): the put+signal ring and the remote-atomics check of the self-tests above, every PE a block of
+// one cooperative kernel. *errors = mismatches plus waits that ran out.
+ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int rounds, int iters, int* errors) {
+  if (!comms || !errors || n < 2 || n > B200SHMEM_MAX_PES || count == 0) BFAIL(ncclInvalidArgument, "b200shmem_emu_selftest: bad arguments");
+  *errors = 0;
+  std::vector<b200shmem_ctx_t> ctx(n, nullptr);
+  std::vector<ncclResult_t> rs(n, ncclSuccess);
+  const size_t heap = 2 * count * 8 + (4u << 20);
+  auto onEveryPe = [&](auto fn) {  // the heap calls are collective over the communicator: one thread per PE
+    std::vector<std::thread> th;
+    for (int r = 0; r < n; r++)
+      th.emplace_back([&, r] {
+        tlsEmuCall = true;
+        rs[r] = fn(r);
+        tlsEmuCall = false;
+      });
+    for (auto& t : th) t.join();
+    for (ncclResult_t r : rs)
+      if (r != ncclSuccess) return r;
+    return ncclSuccess;
+  };
+  BCHECK(onEveryPe([&](int r) { return b200shmem_init(comms[r], heap, &ctx[r]); }));
+  EmuShmemPack pack{};
+  pack.count = count;
+  pack.rounds = rounds;
+  pack.iters = iters;
+  int* derr = nullptr;
+  BCUDA(cudaMalloc(&derr, sizeof(int)));
+  BCUDA(cudaMemset(derr, 0, sizeof(int)));
+  pack.errors = derr;
+  for (int r = 0; r < n; r++) {
+    pack.d[r] = ctx[r]->dev;
+    pack.data[r] = (unsigned long long*)b200shmem_malloc(ctx[r], 2 * count * 8);
+    pack.sig[r] = (unsigned long long*)b200shmem_malloc(ctx[r], 256);
+    pack.words[r] = (unsigned long long*)b200shmem_malloc(ctx[r], 256);
+    if (!pack.data[r] || !pack.sig[r] || !pack.words[r]) BFAIL(ncclSystemError, "b200shmem_emu_selftest: symmetric heap too small");
+    BCUDA(cudaMalloc(&pack.src[r], count * 8));
+    BCUDA(cudaMemset(pack.sig[r], 0, 256));
+    BCUDA(cudaMemset(pack.words[r], 0, 256));
+  }
+  EmuShmemPack* dpack = nullptr;
+  BCUDA(cudaMalloc(&dpack, sizeof(pack)));
+  BCUDA(cudaMemcpy(dpack, &pack, sizeof(pack), cudaMemcpyHostToDevice));
+  BCUDA(cudaDeviceSynchronize());
+  void* args[] = {(void*)&dpack};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)kEmuRing, dim3(n), dim3(256), args, 0, 0);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaLaunchCooperativeKernel((const void*)kEmuAtomics, dim3(n), dim3(32), args, 0, 0);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200shmem_emu_selftest: %s", cudaGetErrorString(e));
+  BCUDA(cudaMemcpy(errors, derr, sizeof(int), cudaMemcpyDeviceToHost));
+  for (int r = 0; r < n; r++) {
+    int st = 0;
+    if (cudaMemcpy(&st, ctx[r]->dev.status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && st) (*errors)++;
+    cudaFree(pack.src[r]);
+  }
+  cudaFree(derr);
+  cudaFree(dpack);
+  BCHECK(onEveryPe([&](int r) { return b200shmem_finalize(ctx[r]); }));
+  return ncclSuccess;
 }
 
 }  // extern "C"

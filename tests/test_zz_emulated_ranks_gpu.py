@@ -1,6 +1,7 @@
 """Several ranks of one communicator on ONE GPU, played by one cooperative kernel (csrc/coll/emu.cu): the collective
 kernels' multi-rank paths — flag-in-data all-reduce, pipelined staged reduce with bulk asynchronous loads, staged copy,
-grouped send/recv through FIFO slots and credits, the fused FSDP reduce-scatter+cast — run where only one GPU is there. The check itself is native (b200collEmuSelftest: small-integer data, every collective in
+grouped send/recv through FIFO slots and credits, the fused FSDP reduce-scatter+cast, and the device-initiated layer's
+put+signal ring and remote atomics — run where only one GPU is there. The check itself is native (b200collEmuSelftest: small-integer data, every collective in
 float / bfloat16 / int32, verified on the host, guard bytes behind every output).
 
 The emulation was written after the last session with a GPU and has not run yet; until it has, a failure is reported as
