@@ -30,7 +30,7 @@ RULES = [
     ("rocm_systems_b200/csrc/shmem/*", ["tests/test_api_cpu.py"], ["tests/test_gpu_fused_multi.py", "tests/test_zz_shmem_dma_gpu.py"], True),
     ("rocm_systems_b200/csrc/fused/fsdp_kernels.cu", ["tests/test_fsdp_rscast_emulation_cpu.py", "tests/test_protocol_model_cpu.py"], ["tests/test_gpu_fused_multi.py"], True),
     ("rocm_systems_b200/csrc/fused/gemm_fp8*", ["tests/test_fp8_reference_cpu.py"], [], True),
-    ("rocm_systems_b200/csrc/fused/*", ["tests/test_kernel_resources_cpu.py"], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_no_alloc.py"], True),
+    ("rocm_systems_b200/csrc/fused/*", ["tests/test_kernel_resources_cpu.py"], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_fused_single_gpu.py", "tests/test_zz_no_alloc.py"], True),
     ("rocm_systems_b200/csrc/torch/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_collectives.py"], True),
     ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py", "tests/test_sanitizers_cpu.py"], ["tests/test_profiler_gpu.py"], True),
     ("rocm_systems_b200/csrc/prof/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),

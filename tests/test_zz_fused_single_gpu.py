@@ -1,0 +1,24 @@
+"""The fused tensor-parallel and expert-parallel paths on ONE GPU (a communicator of one rank): the tcgen05 GEMM with the
+all-gather→GEMM policy and SwiGLU epilogue, the GEMM→reduce-scatter epilogue, staging and reducer, the expert-parallel
+dispatch (route, fp8 quantise, row reservation by atomics, stores), grouped expert GEMMs and combine — all against their
+plain PyTorch compositions, through the same workers the multi-GPU tests use. The collective part degenerates (nothing
+crosses a link), the kernels and their schedules are the real ones.
+
+These single-rank runs were added after the last session with a GPU; until they have passed once on hardware a failure is
+reported as an expected one. Each runs in a child process; every device-side wait is limited to 5 s."""
+import pytest
+
+from test_gpu_fused_multi import _launch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
+def test_tensor_parallel_mlp_on_one_rank():
+    _launch(1, 29881, "tp_worker.py", timeout=600)
+    _launch(1, 29882, "tp_worker.py", "--rows", "512", "--hidden", "2048", "--ffn", "1024", timeout=600)
+
+
+@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
+def test_expert_parallel_layer_on_one_rank():
+    _launch(1, 29883, "ep_worker.py", timeout=600)
