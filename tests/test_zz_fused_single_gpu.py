@@ -22,3 +22,9 @@ def test_tensor_parallel_mlp_on_one_rank():
 @pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_expert_parallel_layer_on_one_rank():
     _launch(1, 29883, "ep_worker.py", timeout=600)
+
+
+@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
+def test_device_initiated_layer_on_one_pe():
+    """put+signal to itself, the atomics on its own words, the barrier of one: the device API's code paths on one GPU."""
+    _launch(1, 29884, "shmem_worker.py", timeout=600)
