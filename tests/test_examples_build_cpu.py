@@ -31,11 +31,15 @@ def test_python_example_parses():
         ast.parse((ROOT / "examples" / name).read_text())
 
 
-@pytest.mark.parametrize("example,port,marker", [("pipeline_1f1b.py", 29921, "pipeline_1f1b OK"), ("long_context_attention.py", 29922, "long_context_attention OK")])
-def test_parallel_examples_run_on_cpu_ranks(example, port, marker):
+@pytest.mark.parametrize("example,port,marker,extra", [
+    ("pipeline_1f1b.py", 29921, "pipeline_1f1b OK", []),
+    ("long_context_attention.py", 29922, "long_context_attention OK", []),
+    ("torch_fsdp_llama.py", 29923, "torch_fsdp_llama OK", ["--device", "cpu", "--backend", "gloo", "--steps", "2", "--warmup", "1"]),
+])
+def test_parallel_examples_run_on_cpu_ranks(example, port, marker, extra):
     import sys
 
     p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-                        "--master-port", str(port), str(ROOT / "examples" / example)], capture_output=True, text=True, timeout=600)
+                        "--master-port", str(port), str(ROOT / "examples" / example), *extra], capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert marker in p.stdout
