@@ -89,6 +89,23 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm)}
 
 
+def gpu_health(index: int):
+    """NVLink error counters, ECC totals and the health verdict of the GPU the numbers were taken on (read-only, through
+    NVML), recorded next to them; None when NVML cannot be read."""
+    try:
+        from rocm_systems_b200.tools.smi import Smi
+
+        s = Smi()
+        try:
+            info, (level, reason) = s.info(index), s.health(index)
+            return {"level": ("PASS", "WARN", "FAIL")[level] if 0 <= level <= 2 else str(level), "reason": reason, "nvlink_active": info["nvlinkActive"],
+                    "nvlink_count": info["nvlinkCount"], "ecc_uncorrected": info["eccUncorrected"], "nvlink_errors": s.nvlink_errors(index)}
+        finally:
+            s.close()
+    except Exception as e:  # noqa: BLE001 - an annotation must never fail the benchmark
+        return {"unavailable": str(e)[:120]}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,6 +213,7 @@ def main() -> None:
         out["e2e"] = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8,
                       "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None}
     if rank == 0:
+        out["health"] = gpu_health(local)
         print(json.dumps(out))
     sync_all()
     comm.destroy()

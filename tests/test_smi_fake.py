@@ -164,3 +164,19 @@ def test_single_reading_flags(fake_nvml):
     assert p.returncode == 0, p.stderr
     lines = p.stdout.strip().splitlines()
     assert len(lines) == 2 and lines[0].startswith("GPU0: 61 C; SM 1500/1965 MHz") and "1.0 / 179.1 GiB" in lines[1] and "sw_power_cap" in lines[1]
+
+
+def test_bench_health_annotation(fake_nvml):
+    """bench.py records the GPU's link, ECC and health state next to its numbers; without NVML it says so instead of failing."""
+    out = _run("""
+import json, bench
+h = bench.gpu_health(1)
+print(json.dumps(h))
+""", fake_nvml, {"FAKE_NVML_LINK_DOWN": "1", "FAKE_NVML_LINK_ERRORS": "1"})
+    import json
+
+    h = json.loads(out.strip().splitlines()[-1])
+    assert h["level"] == "FAIL" and h["nvlink_active"] == 17 and h["nvlink_count"] == 18 and h["nvlink_errors"]["replay"] == 5
+    e = dict(os.environ, B200SMI_NVML_LIBRARY="/nonexistent/libnvml.so", PYTHONPATH=str(ROOT))
+    p = subprocess.run([sys.executable, "-c", "import bench, json; print(json.dumps(bench.gpu_health(0)))"], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0 and "unavailable" in json.loads(p.stdout.strip().splitlines()[-1])
