@@ -309,6 +309,7 @@ static ncclResult_t commDestroyNow(Comm* c, bool abort) {
     c->tracer = nullptr;
   }
   if (!abort) c->boot.barrier();  // peers may still be reading our memory until they get here
+  notifyRelease(c, nullptr);
   for (auto& kv : c->windows) symFree(&kv.second->seg, c->cudaDev);
   c->windows.clear();
   for (Registration* r : c->regs) delete r;
@@ -322,6 +323,27 @@ static ncclResult_t commDestroyNow(Comm* c, bool abort) {
   delete c;
   if (prevDev >= 0) cudaSetDevice(prevDev);
   return ncclSuccess;
+}
+
+namespace {
+std::mutex gNotifyMu;
+std::vector<ReleaseFn> gNotifiers;
+}  // namespace
+
+void addReleaseNotifier(ReleaseFn fn) {
+  std::lock_guard<std::mutex> lk(gNotifyMu);
+  for (ReleaseFn f : gNotifiers)
+    if (f == fn) return;
+  gNotifiers.push_back(fn);
+}
+
+void notifyRelease(Comm* c, const void* base) {
+  std::vector<ReleaseFn> fns;
+  {
+    std::lock_guard<std::mutex> lk(gNotifyMu);
+    fns = gNotifiers;
+  }
+  for (ReleaseFn f : fns) f(c, base);
 }
 
 ncclResult_t commSymAlloc(Comm* c, size_t bytes, void** ptr) {
@@ -358,6 +380,7 @@ ncclResult_t commSymFree(Comm* c, void* ptr) {
     w = std::move(it->second);
     c->windows.erase(it);
   }
+  notifyRelease(c, ptr);
   cudaDeviceSynchronize();
   BCHECK(c->boot.barrier());
   return symFree(&w->seg, c->cudaDev);

@@ -105,6 +105,13 @@ ncclResult_t commPollStatus(Comm* c);                  // fold the device status
 ncclResult_t commRegisterLazy(Comm* c, const void* ptr, size_t bytes);  // exchange a registration on first use
 ncclResult_t commSymAlloc(Comm* c, size_t bytes, void** ptr);
 ncclResult_t commSymFree(Comm* c, void* ptr);
+// Release notifiers (the allocation-map notifiers of an HSA runtime, rocr-runtime core/runtime/runtime.cpp:313-467, for
+// symmetric memory): code that keeps host state per (communicator, symmetric allocation) registers a function that runs
+// when the allocation is freed (base = its address) and when the communicator goes away (base = nullptr), so that a
+// later allocation at the same address starts from a clean slate. Registering a function twice keeps one entry.
+using ReleaseFn = void (*)(Comm* c, const void* base);
+void addReleaseNotifier(ReleaseFn fn);
+void notifyRelease(Comm* c, const void* base);
 void loadTuning(Comm* c);
 
 inline Comm* asComm(ncclComm_t c) { return const_cast<Comm*>(reinterpret_cast<const Comm*>(c)); }

@@ -390,6 +390,20 @@ struct EpState {
 std::mutex gEpMu;
 std::map<std::pair<Comm*, const void*>, EpState> gEp;
 
+// A freed window (or a communicator that goes away) takes its call counter along: the next window at that address starts at call 0,
+// like its zeroed counters.
+void epForget(Comm* c, const void* base) {
+  std::lock_guard<std::mutex> lk(gEpMu);
+  for (auto it = gEp.begin(); it != gEp.end();) {
+    if (it->first.first == c && (base == nullptr || it->first.second == base)) {
+      if (it->second.ticket) cudaFree(it->second.ticket);
+      it = gEp.erase(it);
+    } else {
+      ++it;
+    }
+  }
+}
+
 bool epPeers(Comm* c, const void* p, size_t bytes, char* (&out)[kMaxRanks]) {
   if (c->nranks == 1) { out[0] = (char*)p; return true; }
   size_t off = 0;
@@ -452,6 +466,7 @@ ncclResult_t b200collEpDispatch(ncclComm_t comm, void* winSym, const void* xBf16
   DispatchArgs a{};
   a.L = makeLayout(c->nranks, expertsLocal, cap, hidden, ffn);
   if (!epPeers(c, winSym, a.L.total, a.win)) BFAIL(ncclInvalidUsage, "b200collEpDispatch: the window must be symmetric memory of b200collEpWorkspaceBytes()");
+  addReleaseNotifier(epForget);
   {
     std::lock_guard<std::mutex> lk(gEpMu);
     EpState& st = gEp[std::make_pair(c, (const void*)winSym)];

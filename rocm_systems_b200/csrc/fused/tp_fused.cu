@@ -16,11 +16,9 @@
 #include <map>
 #include <mutex>
 
-#include "../coll/prims.cuh"
-#include "../core/comm.h"
 #include "b200coll/fused.h"
 #include "gemm_host.h"
-#include "gemm_sm100.cuh"
+#include "tp_fused.cuh"
 
 namespace b200 {
 namespace tp {
@@ -39,24 +37,6 @@ struct AgArgs {
   __nv_bfloat16* out;           // [M, Nout]
   int ldo, nOut;
 };
-
-__device__ __forceinline__ void pullBlock(char* dst, const char* src, size_t bytes) {
-  // 16 independent 16-byte loads per thread in flight: peer loads are latency bound.
-  const int t = threadIdx.x, nt = blockDim.x;
-  const size_t nvec = bytes >> 4;
-  const uint4* s = (const uint4*)src;
-  uint4* d = (uint4*)dst;
-  size_t i = t;
-  constexpr int U = 16;
-  for (; i + (size_t)(U - 1) * nt < nvec; i += (size_t)U * nt) {
-    uint4 v[U];
-#pragma unroll
-    for (int u = 0; u < U; u++) v[u] = ldStream16(s + i + (size_t)u * nt);
-#pragma unroll
-    for (int u = 0; u < U; u++) st16(d + i + (size_t)u * nt, v[u]);
-  }
-  for (; i < nvec; i += nt) st16(d + i, ldStream16(s + i));
-}
 
 template <int BN, bool SWIGLU> struct AgPolicy {
   AgArgs a;
@@ -148,17 +128,6 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmKernel(const __grid_constan
 }
 
 // ---- GEMM -> reduce-scatter --------------------------------------------------------------------------------
-struct RsArgs {
-  char* stagePeer[kMaxRanks];   // every rank's staging window as mapped here
-  size_t stageOff;              // byte offset of this call's parity half inside the window
-  size_t flagOff;               // byte offset of this call's parity counters inside the window
-  uint32_t target;              // counter value that means "all n partials of the tile are here"
-  int rowsPerRank, blocksPerRank;
-  int N;                        // columns of the output
-  __nv_bfloat16* y;             // [rowsPerRank, N] owned rows of the result
-  int ldy;
-};
-
 template <int BN> struct RsPolicy {
   RsArgs a;
   int rank, n;
@@ -187,17 +156,7 @@ template <int BN> struct RsPolicy {
         },
         [&](int r) -> __nv_bfloat16* { return base + (size_t)r * a.N; });
   }
-  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const {
-    // All four epilogue warps have stored their rows; then one thread tells the owner.
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (q == 0 && lane == 0) {
-      const int owner = tm / a.blocksPerRank;
-      const int tilesN = (a.N + BN - 1) / BN;
-      uint32_t* f = (uint32_t*)(a.stagePeer[owner] + a.flagOff) + (size_t)(tm - owner * a.blocksPerRank) * tilesN + tn;
-      __threadfence_system();
-      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(f) : "memory");
-    }
-  }
+  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const { rsTileDone(a, BN, tm, tn, q, lane); }
 };
 
 template <int BN>
@@ -205,61 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemmRsKernel(const __grid_constan
   extern __shared__ uint8_t smemRaw[];
   RsPolicy<BN> pol{a, c.rank, c.nranks};
   gemmCta<BN>(p, pol, blockIdx.x, gridDim.x, smemRaw);
-  // Reducer phase: sum the n staged partials of every tile this rank owns.
-  __shared__ int ok;
-  const int n = c.nranks, rank = c.rank;
-  const int tilesN = (a.N + BN - 1) / BN;
-  const int owned = a.blocksPerRank * tilesN;
-  const char* stage = a.stagePeer[rank] + a.stageOff;
-  const uint32_t* flags = (const uint32_t*)(a.stagePeer[rank] + a.flagOff);
-  const size_t slot = (size_t)a.rowsPerRank * a.N;  // elements per source rank
-  for (int idx = blockIdx.x; idx < owned; idx += gridDim.x) {
-    if (threadIdx.x == 0) {
-      int good = 0;
-      for (uint32_t i = 0; i < 200000000u; i++) {
-        if ((int32_t)(ldAcquireSys(flags + idx) - a.target) >= 0) { good = 1; break; }
-        if ((i & 0x3ff) == 0x3ff && *(volatile int*)p.err) break;
-        __nanosleep(32);
-      }
-      if (!good) atomicCAS(p.err, 0, ERR_REDUCE_WAIT);
-      ok = good;
-    }
-    __syncthreads();
-    if (ok) {
-      const int tmL = idx / tilesN, tn = idx % tilesN;
-      const int cols = min(BN, a.N - tn * BN);
-      const int vecPerRow = cols >> 3;
-      for (int v = threadIdx.x; v < BM * vecPerRow; v += blockDim.x) {
-        const int r = v / vecPerRow, cv = v - r * vecPerRow;
-        const int row = tmL * BM + r;
-        if (row >= a.rowsPerRank) continue;
-        const size_t e = (size_t)row * a.N + (size_t)tn * BN + (size_t)cv * 8;
-        float acc[8];
-#pragma unroll
-        for (int s = 0; s < kMaxRanks; s++) {
-          if (s < n) {
-            const uint4 x = ldStream16(stage + (s * slot + e) * 2);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-              const float2 f = __bfloat1622float2(h[k]);
-              acc[2 * k] = s == 0 ? f.x : acc[2 * k] + f.x;
-              acc[2 * k + 1] = s == 0 ? f.y : acc[2 * k + 1] + f.y;
-            }
-          }
-        }
-        uint4 o;
-        uint32_t* ow = &o.x;
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-          ow[k] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(a.y + (size_t)row * a.ldy + (size_t)tn * BN + (size_t)cv * 8) = o;
-      }
-    }
-    __syncthreads();
-  }
+  reduceOwnedTiles<BN>(a, c.rank, c.nranks, p.err);
 }
 
 }  // namespace tp
@@ -274,14 +179,32 @@ using namespace b200::tp;
 namespace {
 
 struct AgState { uint32_t* flags = nullptr; uint32_t seq = 0; int cap = 0; };
+struct RsState { unsigned long long calls = 0; int tileW = 0; };
 std::mutex gTpMu;
 std::map<Comm*, AgState> gAg;
-std::map<std::pair<Comm*, const void*>, unsigned long long> gRsCalls;
+std::map<std::pair<Comm*, const void*>, RsState> gRs;
 
-template <typename K>
-cudaError_t allowSmem(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+// A freed workspace (or a communicator that goes away) takes its call counter along: the next workspace at that address
+// starts at call 0, like its zeroed tile counters.
+void tpForget(Comm* c, const void* base) {
+  std::lock_guard<std::mutex> lk(gTpMu);
+  for (auto it = gRs.begin(); it != gRs.end();) {
+    if (it->first.first == c && (base == nullptr || it->first.second == base)) it = gRs.erase(it);
+    else ++it;
+  }
+  if (base == nullptr) {
+    auto it = gAg.find(c);
+    if (it != gAg.end()) {
+      if (it->second.flags) cudaFree(it->second.flags);
+      gAg.erase(it);
+    }
+  }
 }
+
+}  // namespace
+
+namespace b200 {
+namespace tp {
 
 bool peersOf(Comm* c, const void* p, size_t bytes, char* (&out)[kMaxRanks]) {
   size_t off = 0;
@@ -292,13 +215,38 @@ bool peersOf(Comm* c, const void* p, size_t bytes, char* (&out)[kMaxRanks]) {
   return true;
 }
 
-struct DevGuard2 {
-  int prev = -1, want;
-  explicit DevGuard2(int d) : want(d) { cudaGetDevice(&prev); if (prev != want) cudaSetDevice(want); }
-  ~DevGuard2() { if (prev != want && prev >= 0) cudaSetDevice(prev); }
-};
+ncclResult_t agNextCall(Comm* c, int needFlags, uint32_t** flags, uint32_t* seq) {
+  addReleaseNotifier(tpForget);
+  std::lock_guard<std::mutex> lk(gTpMu);
+  AgState& st = gAg[c];
+  if (st.cap < needFlags) {
+    if (st.flags) cudaFree(st.flags);
+    st.flags = nullptr;
+    st.cap = 0;
+    BCUDA(cudaMalloc(&st.flags, (size_t)needFlags * 4));
+    BCUDA(cudaMemset(st.flags, 0, (size_t)needFlags * 4));
+    st.cap = needFlags;
+    st.seq = 0;
+  }
+  *flags = st.flags;
+  *seq = ++st.seq;
+  return ncclSuccess;
+}
 
-}  // namespace
+ncclResult_t rsNextCall(Comm* c, const void* workspace, int tileW, unsigned long long* calls) {
+  addReleaseNotifier(tpForget);
+  std::lock_guard<std::mutex> lk(gTpMu);
+  RsState& st = gRs[std::make_pair(c, workspace)];
+  if (st.tileW == 0) st.tileW = tileW;
+  if (st.tileW != tileW)
+    BFAIL(ncclInvalidUsage, "GEMM->reduce-scatter workspace %p was first used with %d-column tiles, this call needs %d: give each shape its own workspace",
+          workspace, st.tileW, tileW);
+  *calls = st.calls++;
+  return ncclSuccess;
+}
+
+}  // namespace tp
+}  // namespace b200
 
 extern "C" {
 
@@ -337,20 +285,7 @@ ncclResult_t b200collAgGemm(ncclComm_t comm, void* xSym, const void* w, void* ou
   a.out = (__nv_bfloat16*)out;
   a.nOut = swiglu ? wRows / 2 : wRows;
   a.ldo = a.nOut;
-  {
-    std::lock_guard<std::mutex> lk(gTpMu);
-    AgState& st = gAg[c];
-    const int need = n * a.blocksPerRank;
-    if (st.cap < need) {
-      if (st.flags) cudaFree(st.flags);
-      BCUDA(cudaMalloc(&st.flags, (size_t)need * 4));
-      BCUDA(cudaMemset(st.flags, 0, (size_t)need * 4));
-      st.cap = need;
-      st.seq = 0;
-    }
-    a.flags = st.flags;
-    a.seq = ++st.seq;
-  }
+  BCHECK(agNextCall(c, n * a.blocksPerRank, &a.flags, &a.seq));
   Params p{};
   if (!makeTileMap(&p.mapA, xSym, M, K, K, BM, 2) || !makeTileMap(&p.mapB, w, wRows, K, K, bn, 2))
     BFAIL(ncclInvalidArgument, "b200collAgGemm: operands must be 16-byte aligned with rows a multiple of 16 bytes");
@@ -407,10 +342,7 @@ ncclResult_t b200collGemmRs(ncclComm_t comm, const void* a_, const void* w, void
   const size_t stage = (size_t)n * rowsPerRank * N * 2;
   const size_t flags = (wsBytes - 2 * stage) / 2;
   unsigned long long calls;
-  {
-    std::lock_guard<std::mutex> lk(gTpMu);
-    calls = gRsCalls[std::make_pair(c, (const void*)workspaceSym)]++;
-  }
+  BCHECK(rsNextCall(c, workspaceSym, bn, &calls));
   const int parity = (int)(calls & 1);
   a.stageOff = (size_t)parity * stage;
   a.flagOff = 2 * stage + (size_t)parity * flags;

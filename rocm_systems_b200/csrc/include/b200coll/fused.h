@@ -35,6 +35,19 @@ size_t b200collGemmRsWorkspaceBytes(int rowsPerRank, int N, int nranks);
 ncclResult_t b200collGemmRs(ncclComm_t comm, const void* a, const void* w, void* workspaceSym, void* y, int rowsPerRank, int N, int K,
                             cudaStream_t stream);
 
+/* The same two kernels on block-scaled fp8 (e4m3) operands. Activations: one fp32 scale per row and 128 channels, stored
+ * [K / 128][rows]; weights: one scale per 128 x 128 block, stored [rows / 128][K / 128]. K and the weight rows are
+ * multiples of 128; tiles are 128 x 128, and with swiglu != 0 the weight holds, per block of 128 rows, 64 gate rows then
+ * the 64 up rows of the same outputs.
+ * AgGemmFp8: x8Sym [nranks * rowsPerRank, K] e4m3 and sASym [K / 128][nranks * rowsPerRank] both live in symmetric memory
+ * with this rank's rows (and their scales) in place; the kernel pulls rows and scales of the other ranks. out is bf16.
+ * GemmRsFp8: a8 / sA and w8 / sW are this rank's K-shards; workspace and y as for b200collGemmRs. A workspace serves
+ * either the bf16 or the fp8 form, not both. */
+ncclResult_t b200collAgGemmFp8(ncclComm_t comm, void* x8Sym, float* sASym, const void* w8, const float* sW, void* out, int rowsPerRank, int wRows,
+                               int K, int swiglu, int commCtas, cudaStream_t stream);
+ncclResult_t b200collGemmRsFp8(ncclComm_t comm, const void* a8, const float* sA, const void* w8, const float* sW, void* workspaceSym, void* y,
+                               int rowsPerRank, int N, int K, cudaStream_t stream);
+
 /* ---- Mixture-of-experts expert parallelism (experts e*expertsLocal .. on rank e) ----------------
  * One symmetric window of b200collEpWorkspaceBytes() bytes (zero-initialised) per MoE layer holds
  * the per-expert receive buffers (fp8 rows + one fp32 scale per 128 channels), their row counters

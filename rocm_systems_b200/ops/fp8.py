@@ -57,8 +57,9 @@ def ref_dequantize_weight(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (q.float().view(N, K // 128, 128) * s[rows].unsqueeze(-1)).view(N, K)
 
 
-def ref_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor) -> torch.Tensor:
-    """Block by block, as the kernel accumulates: fp32 partial products scaled and summed in K order."""
+def ref_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Block by block, as the kernel accumulates: fp32 partial products scaled and summed in K order.
+    ``out_dtype=torch.float32`` returns the accumulator before the final rounding (what a fused epilogue sees)."""
     M, K = xq.shape
     N = wq.shape[0]
     rows = torch.arange(N, device=wq.device) // 128
@@ -66,7 +67,7 @@ def ref_gemm(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     for kb in range(K // 128):
         part = xq[:, kb * 128:(kb + 1) * 128].float() @ wq[:, kb * 128:(kb + 1) * 128].float().t()
         out += part * xs[kb].unsqueeze(1) * ws[rows, kb].unsqueeze(0)
-    return out.to(torch.bfloat16)
+    return out.to(out_dtype)
 
 
 # ---- the kernels ---------------------------------------------------------------------------------------------------
@@ -75,6 +76,7 @@ def _lib():
     if not hasattr(lib, "_fp8_sig"):
         vp, i32 = ctypes.c_void_p, ctypes.c_int
         lib.b200ops_quant_e4m3_1x128.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        lib.b200ops_quant_e4m3_1x128_strided.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
         lib.b200ops_quant_e4m3_128x128.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
         lib.b200ops_gemm_fp8_block_tn.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
         lib._fp8_sig = True
@@ -88,6 +90,18 @@ def quantize_act(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     s = torch.empty(K // 128, M, dtype=torch.float32, device=x.device)
     train_ops._ck(_lib().b200ops_quant_e4m3_1x128(x.data_ptr(), q.data_ptr(), s.data_ptr(), M, K, x.stride(0), q.stride(0), train_ops._s()), "quant_e4m3_1x128")
     return q, s
+
+
+def quantize_act_into(x: torch.Tensor, q: torch.Tensor, s: torch.Tensor, row0: int) -> None:
+    """Quantise ``x`` [m, K] into rows ``row0 .. row0 + m`` of a larger ``q`` [M, K] and the matching columns of its scale
+    table ``s`` [K / 128, M] (a rank filling its shard of a gathered activation)."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 128 == 0
+    m, K = x.shape
+    M = q.shape[0]
+    assert q.dtype == torch.float8_e4m3fn and q.shape[1] == K and q.stride(1) == 1 and 0 <= row0 and row0 + m <= M
+    assert s.dtype == torch.float32 and tuple(s.shape) == (K // 128, M) and s.is_contiguous()
+    train_ops._ck(_lib().b200ops_quant_e4m3_1x128_strided(x.data_ptr(), q.data_ptr() + row0 * q.stride(0), s.data_ptr() + 4 * row0, m, K, x.stride(0), q.stride(0),
+                                                          M, train_ops._s()), "quant_e4m3_1x128_strided")
 
 
 def quantize_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

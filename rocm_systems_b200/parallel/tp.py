@@ -33,6 +33,8 @@ def _lib_tp():
         lib.b200collGemmRs.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]
         lib.b200collGemmRsWorkspaceBytes.argtypes = [i32, i32, i32]
         lib.b200collGemmRsWorkspaceBytes.restype = ctypes.c_size_t
+        lib.b200collAgGemmFp8.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+        lib.b200collGemmRsFp8.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]
         _done = True
     return lib
 
@@ -118,6 +120,99 @@ class TensorParallelMLP:
     def free(self) -> None:
         torch.cuda.synchronize()
         self._x_sym.free()
+        self._ws.free()
+
+
+def fp8_mlp_partial_oracle(x_full: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """What one rank of :class:`TensorParallelMLPFp8` contributes, in plain PyTorch with the kernels' arithmetic: the
+    gathered activations and the interleaved gate/up weight quantised block-wise to e4m3, fp32 accumulation, SwiGLU on the
+    fp32 accumulators, bf16 activations quantised again for the down projection, and the partial result rounded to bf16
+    (the form in which partials cross NVLink). Returns [M, hidden] bf16. Runs on any device."""
+    from ..ops import fp8
+    M = x_full.shape[0]
+    F = w_gate.shape[0]
+    xq, xs = fp8.ref_quantize_act(x_full)
+    wq, ws = fp8.ref_quantize_weight(interleave_gate_up(w_gate, w_up, 128))
+    h = fp8.ref_gemm(xq, xs, wq, ws, out_dtype=torch.float32).view(M, F // 64, 2, 64)
+    act = (torch.nn.functional.silu(h[:, :, 0]) * h[:, :, 1]).reshape(M, F).to(torch.bfloat16)
+    aq, a_s = fp8.ref_quantize_act(act)
+    w2q, w2s = fp8.ref_quantize_weight(w2)
+    return fp8.ref_gemm(aq, a_s, w2q, w2s)
+
+
+class TensorParallelMLPFp8:
+    """:class:`TensorParallelMLP` on block-scaled fp8 operands (``b200collAgGemmFp8`` / ``b200collGemmRsFp8``,
+    csrc/fused/tp_fused_fp8.cu). Each rank quantises its own rows (e4m3 + one scale per row and 128 channels) straight into
+    the symmetric buffers, so the all-gather moves half the bytes of the bf16 form; weights are quantised once per
+    128 x 128 block. ``hidden`` and ``ffn_local`` are multiples of 128.
+    """
+
+    def __init__(self, comm, rows_per_rank: int, hidden: int, ffn_local: int, device=None, std: float = 0.02, seed: int = 0,
+                 comm_ctas: int = 0):
+        from ..ops import fp8
+        assert hidden % 128 == 0 and ffn_local % 128 == 0
+        self.comm = comm
+        self.n, self.rank = comm.nranks, comm.rank
+        self.rows, self.hidden, self.f = rows_per_rank, hidden, ffn_local
+        self.device = device or comm.device
+        self.comm_ctas = comm_ctas
+        g = torch.Generator(device=self.device).manual_seed(seed + 7919 * self.rank)
+        self.w_gate = (torch.randn(ffn_local, hidden, device=self.device, generator=g) * std).to(torch.bfloat16)
+        self.w_up = (torch.randn(ffn_local, hidden, device=self.device, generator=g) * std).to(torch.bfloat16)
+        self.w2 = (torch.randn(hidden, ffn_local, device=self.device, generator=g) * std).to(torch.bfloat16)
+        self.w13_q, self.w13_s = fp8.quantize_weight(interleave_gate_up(self.w_gate, self.w_up, 128))
+        self.w2_q, self.w2_s = fp8.quantize_weight(self.w2)
+        M = self.M = self.n * rows_per_rank
+        lib = _lib_tp()
+        self._x_sym = comm.sym_alloc(M * hidden)
+        self._s_sym = comm.sym_alloc((hidden // 128) * M * 4)
+        self.x_q = self._x_sym.tensor((M, hidden), torch.float8_e4m3fn)
+        self.x_s = self._s_sym.tensor((hidden // 128, M), torch.float32)
+        self._ws = comm.sym_alloc(int(lib.b200collGemmRsWorkspaceBytes(rows_per_rank, hidden, self.n)))
+        self.act = torch.empty(M, ffn_local, dtype=torch.bfloat16, device=self.device)
+        self.y = torch.empty(rows_per_rank, hidden, dtype=torch.bfloat16, device=self.device)
+
+    def set_rows(self, x_local: torch.Tensor) -> None:
+        """Quantise this rank's rows of the activations into its shard of the gathered buffers."""
+        from ..ops import fp8
+        fp8.quantize_act_into(x_local, self.x_q, self.x_s, self.rank * self.rows)
+        train_ops.LAUNCHES += 1
+
+    def ag_gemm(self, stream=None) -> torch.Tensor:
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        _lib.check(_lib_tp().b200collAgGemmFp8(self.comm.handle, self.x_q.data_ptr(), self.x_s.data_ptr(), self.w13_q.data_ptr(), self.w13_s.data_ptr(),
+                                               self.act.data_ptr(), self.rows, 2 * self.f, self.hidden, 1, self.comm_ctas, s), "b200collAgGemmFp8")
+        train_ops.LAUNCHES += 1
+        return self.act
+
+    def gemm_rs(self, stream=None) -> torch.Tensor:
+        from ..ops import fp8
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        aq, a_s = fp8.quantize_act(self.act)
+        _lib.check(_lib_tp().b200collGemmRsFp8(self.comm.handle, aq.data_ptr(), a_s.data_ptr(), self.w2_q.data_ptr(), self.w2_s.data_ptr(), self._ws.ptr,
+                                               self.y.data_ptr(), self.rows, self.hidden, self.f, s), "b200collGemmRsFp8")
+        train_ops.LAUNCHES += 2
+        return self.y
+
+    def forward(self, x_local: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        if x_local is not None:
+            self.set_rows(x_local)
+        self.ag_gemm(stream)
+        return self.gemm_rs(stream)
+
+    def reference_forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        """The oracle's partial on this rank, summed over the ranks by the library's reduce-scatter."""
+        xg = torch.empty(self.M, self.hidden, dtype=torch.bfloat16, device=self.device)
+        self.comm.all_gather(x_local.contiguous(), xg)
+        part = fp8_mlp_partial_oracle(xg, self.w_gate, self.w_up, self.w2)
+        out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        self.comm.reduce_scatter(part.contiguous(), out)
+        return out
+
+    def free(self) -> None:
+        torch.cuda.synchronize()
+        self._x_sym.free()
+        self._s_sym.free()
         self._ws.free()
 
 

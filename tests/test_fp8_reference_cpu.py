@@ -43,3 +43,28 @@ def test_blockwise_gemm_equals_gemm_of_dequantised_operands():
     exact = x.float() @ w.float().t()
     rel = float((got - exact).norm() / exact.norm())
     assert rel < 0.05, rel                                                     # fp8 quantisation noise of both operands
+
+
+def test_tensor_parallel_fp8_mlp_oracle_tracks_the_exact_mlp():
+    """Two ranks' partials from the fp8 oracle of the fused tensor-parallel MLP, summed, against the same MLP in fp32:
+    the per-tile gate/up interleave, the second quantisation of the activations and the bf16 partials together cost a few
+    per cent, not more."""
+    from rocm_systems_b200.parallel.tp import fp8_mlp_partial_oracle, interleave_gate_up
+
+    torch.manual_seed(3)
+    M, H, F, n = 64, 256, 128, 2
+    x = torch.randn(M, H).to(torch.bfloat16)
+    exact = torch.zeros(M, H)
+    total = torch.zeros(M, H)
+    for r in range(n):
+        wg = (torch.randn(F, H) * 0.05).to(torch.bfloat16)
+        wu = (torch.randn(F, H) * 0.05).to(torch.bfloat16)
+        w2 = (torch.randn(H, F) * 0.05).to(torch.bfloat16)
+        w13 = interleave_gate_up(wg, wu, 128)
+        assert torch.equal(w13[:64], wg[:64]) and torch.equal(w13[64:128], wu[:64]) and torch.equal(w13[128:192], wg[64:])
+        part = fp8_mlp_partial_oracle(x, wg, wu, w2)
+        assert part.dtype == torch.bfloat16 and tuple(part.shape) == (M, H)
+        total += part.float()
+        exact += (torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())) @ w2.float().t()
+    err = (total - exact).abs().max().item()
+    assert err <= 0.06 * exact.abs().max().item()

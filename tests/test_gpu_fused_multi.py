@@ -34,6 +34,13 @@ def test_tp_fused_mlp_matches_unfused(nproc):
     _launch(nproc, 29820 + nproc, "tp_worker.py", "--rows", "512", "--hidden", "2048", "--ffn", "1024")
 
 
+@pytest.mark.xfail(reason="the fp8 form of the fused kernels has not run on hardware yet", strict=False)
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_tp_fused_mlp_fp8_matches_oracle(nproc):
+    _launch(nproc, 29870 + nproc, "tp_worker.py", "--fp8")
+    _launch(nproc, 29890 + nproc, "tp_worker.py", "--fp8", "--rows", "512", "--hidden", "2048", "--ffn", "1024")
+
+
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_ep_dispatch_experts_combine(nproc):
     _launch(nproc, 29830 + nproc, "ep_worker.py")

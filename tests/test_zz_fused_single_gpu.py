@@ -20,6 +20,13 @@ def test_tensor_parallel_mlp_on_one_rank():
 
 
 @pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
+def test_tensor_parallel_mlp_fp8_on_one_rank():
+    """Both fused kernels on block-scaled e4m3 operands against the PyTorch statement of the same arithmetic."""
+    _launch(1, 29885, "tp_worker.py", "--fp8", timeout=600)
+    _launch(1, 29886, "tp_worker.py", "--fp8", "--rows", "512", "--hidden", "2048", "--ffn", "1024", timeout=600)
+
+
+@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_expert_parallel_layer_on_one_rank():
     _launch(1, 29883, "ep_worker.py", timeout=600)
 

@@ -11,7 +11,7 @@ import torch  # noqa: E402
 
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 from rocm_systems_b200.ops import train_ops  # noqa: E402
-from rocm_systems_b200.parallel.tp import TensorParallelMLP  # noqa: E402
+from rocm_systems_b200.parallel.tp import TensorParallelMLP, TensorParallelMLPFp8  # noqa: E402
 
 
 def timed(fn, comm, warmup=3, iters=10):
@@ -35,13 +35,14 @@ def main():
     ap.add_argument("--rows", type=int, default=256)      # rows per rank
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--ffn", type=int, default=512)       # per rank
+    ap.add_argument("--fp8", action="store_true")         # the block-scaled e4m3 form of both kernels
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     comm = init_from_env()
     rank, n = comm.rank, comm.nranks
     dev = comm.device
-    mlp = TensorParallelMLP(comm, args.rows, args.hidden, args.ffn, dev, seed=11)
+    mlp = (TensorParallelMLPFp8 if args.fp8 else TensorParallelMLP)(comm, args.rows, args.hidden, args.ffn, dev, seed=11)
     bad = []
     for trial in range(3):
         g = torch.Generator(device=dev).manual_seed(100 * trial + rank)
@@ -60,9 +61,13 @@ def main():
     if args.time and not bad:
         g = torch.Generator(device=dev).manual_seed(rank)
         x = torch.randn(args.rows, args.hidden, device=dev, generator=g).to(torch.bfloat16)
-        mlp.my_rows().copy_(x)
+        if args.fp8:
+            mlp.set_rows(x)
+        else:
+            mlp.my_rows().copy_(x)
         res["fused_ms"] = timed(lambda: mlp.forward(None), comm)
-        res["unfused_ms"] = timed(lambda: mlp.reference_forward(x), comm)
+        if not args.fp8:
+            res["unfused_ms"] = timed(lambda: mlp.reference_forward(x), comm)
         res["ag_gemm_ms"] = timed(lambda: mlp.ag_gemm(), comm)
         res["gemm_rs_ms"] = timed(lambda: mlp.gemm_rs(), comm)
         # the same two GEMMs with no communication at all (library GEMM), as the compute floor
@@ -70,6 +75,7 @@ def main():
         w13 = torch.cat([mlp.w_gate, mlp.w_up])
         res["local_gemm1_ms"] = timed(lambda: torch.mm(xg, w13.t()), comm)
         res["local_gemm2_ms"] = timed(lambda: torch.mm(mlp.act, mlp.w2.t()), comm)
+        res["fp8"] = bool(args.fp8)
         M = n * args.rows
         flops = 2.0 * M * args.hidden * 2 * args.ffn + 2.0 * M * args.ffn * args.hidden
         res["fused_tflops_per_gpu"] = flops / (res["fused_ms"] * 1e-3) / 1e12
