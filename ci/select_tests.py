@@ -33,6 +33,7 @@ RULES = [
     ("rocm_systems_b200/csrc/fused/*", ["tests/test_kernel_resources_cpu.py"], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_fused_single_gpu.py", "tests/test_zz_no_alloc.py"], True),
     ("rocm_systems_b200/csrc/torch/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_collectives.py"], True),
     ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py", "tests/test_sanitizers_cpu.py"], ["tests/test_profiler_gpu.py"], True),
+    ("rocm_systems_b200/csrc/prof/sampler.cc", ["tests/test_host_sampler_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/prof/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),
     ("rocm_systems_b200/csrc/perf/*", ["tests/test_verifiable_cpu.py", "tests/test_perf_cli_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/include/*", ["tests/test_bootstrap.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),

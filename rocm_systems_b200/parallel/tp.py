@@ -187,16 +187,18 @@ class TensorParallelMLPFp8:
 
     def gemm_rs(self, stream=None) -> torch.Tensor:
         from ..ops import fp8
-        s = (stream or torch.cuda.current_stream()).cuda_stream
-        aq, a_s = fp8.quantize_act(self.act)
-        _lib.check(_lib_tp().b200collGemmRsFp8(self.comm.handle, aq.data_ptr(), a_s.data_ptr(), self.w2_q.data_ptr(), self.w2_s.data_ptr(), self._ws.ptr,
-                                               self.y.data_ptr(), self.rows, self.hidden, self.f, s), "b200collGemmRsFp8")
+        st = stream or torch.cuda.current_stream()
+        with torch.cuda.stream(st):      # the quantiser and its temporaries live on the stream of the kernel that reads them
+            aq, a_s = fp8.quantize_act(self.act)
+            _lib.check(_lib_tp().b200collGemmRsFp8(self.comm.handle, aq.data_ptr(), a_s.data_ptr(), self.w2_q.data_ptr(), self.w2_s.data_ptr(), self._ws.ptr,
+                                                   self.y.data_ptr(), self.rows, self.hidden, self.f, st.cuda_stream), "b200collGemmRsFp8")
         train_ops.LAUNCHES += 2
         return self.y
 
     def forward(self, x_local: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         if x_local is not None:
-            self.set_rows(x_local)
+            with torch.cuda.stream(stream or torch.cuda.current_stream()):
+                self.set_rows(x_local)
         self.ag_gemm(stream)
         return self.gemm_rs(stream)
 

@@ -16,7 +16,10 @@ What is traced, and by which part of the package:
   --marker-trace  ``b200tx`` ranges the program pushes (rocm_systems_b200.utils.markers);
   --sys-sample N  a background sampler in the launcher (``tools/sysmon.py``): GPU clocks / power / temperature /
                   utilisation / memory, host CPU and memory, the command's resident set, every N ms;
-  --sys-trace     all of the above.
+  --sys-trace     all of the above;
+  --host-sampling call stacks of the host threads, ``libb200sample.so`` preloaded into every process of the command
+                  (CPU-time or wall-clock timer; ``--stats`` then lists functions by self and inclusive share, and
+                  ``<output>.folded`` feeds a flame-graph tool).
 """
 from __future__ import annotations
 
@@ -56,6 +59,17 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
     if a.coll_trace or a.marker_trace:
         env["B200COLL_TRACE"] = "1"
         env["B200COLL_TRACE_FILE"] = prefix
+    if a.host_sampling:
+        lib = PKG / "lib" / "libb200sample.so"
+        if not lib.exists():
+            raise SystemExit(f"{lib} is missing: run `python -m rocm_systems_b200.utils.build`")
+        old = env.get("LD_PRELOAD", "")
+        env["LD_PRELOAD"] = f"{lib}:{old}" if old else str(lib)
+        env["B200SAMPLE_PREFIX"] = prefix
+        env["B200SAMPLE_FREQ"] = str(a.sampling_freq)
+        env["B200SAMPLE_CLOCK"] = a.sampling_clock
+        if a.sampling_delay > 0:
+            env["B200SAMPLE_DELAY"] = str(a.sampling_delay)
     if a.tool_library:
         old = env.get("B200COLL_TOOL_LIBRARIES", "")
         env["B200COLL_TOOL_LIBRARIES"] = ":".join([*a.tool_library, old] if old else a.tool_library)
@@ -65,7 +79,8 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
 def collect(prefix: str) -> List[str]:
     """Every trace file the children left behind."""
     files = sorted(set(glob.glob(prefix + ".*_kernel_trace.csv") + glob.glob(prefix + ".*_memory_copy_trace.csv") +
-                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv") + glob.glob(prefix + ".sysmon.csv")))
+                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv") + glob.glob(prefix + ".sysmon.csv") +
+                       glob.glob(prefix + ".*.samples.csv")))
     return files
 
 
@@ -82,6 +97,11 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--sys-trace", action="store_true", help="everything")
     g.add_argument("--sys-sample", type=int, default=0, metavar="PERIOD_MS",
                    help="sample GPU readings (NVML), host CPU / memory and the command's resident set in the background")
+    g.add_argument("--host-sampling", action="store_true", help="sample the call stacks of the host threads")
+    g.add_argument("--sampling-freq", type=float, default=100.0, metavar="HZ")
+    g.add_argument("--sampling-clock", choices=["cpu", "wall"], default="cpu",
+                   help="cpu: samples in proportion to CPU time used; wall: every thread every period, blocked ones included")
+    g.add_argument("--sampling-delay", type=float, default=0.0, metavar="SECONDS")
     g = ap.add_argument_group("filtering")
     g.add_argument("--kernel-include-regex", default="")
     g.add_argument("--kernel-exclude-regex", default="", help="drop kernels whose name matches (applied when the trace is imported)")
@@ -110,7 +130,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return 2
     if a.sys_trace:
         a.kernel_trace = a.memory_copy_trace = a.runtime_trace = a.sync_trace = a.coll_trace = a.marker_trace = True
-    if not (a.kernel_trace or a.memory_copy_trace or a.runtime_trace or a.driver_trace or a.sync_trace or a.coll_trace or a.marker_trace):
+    if not (a.kernel_trace or a.memory_copy_trace or a.runtime_trace or a.driver_trace or a.sync_trace or a.coll_trace or a.marker_trace
+            or a.host_sampling):
         a.kernel_trace = True
     outdir = Path(a.output_directory)
     outdir.mkdir(parents=True, exist_ok=True)
@@ -151,11 +172,15 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
             Path(prefix + ".json").write_text(json.dumps(out))
         if "csv" in a.output_format:
             db.to_csv(prefix)
+        if a.host_sampling:
+            db.to_folded(prefix + ".folded")
     if "db" not in a.output_format:
         os.remove(db_path)
     if "csv" not in a.output_format:
         for f in files:
             os.remove(f)
+    for f in glob.glob(prefix + ".*.folded"):   # per-process stacks: merged into <output>.folded above
+        os.remove(f)
     if a.stats:
         tracedb.print_summary(summary)
     if a.summary:

@@ -49,6 +49,8 @@ create table if not exists collective(id integer primary key, process_id integer
     count integer, dtype text, bytes integer, algo integer, ctas integer, host_start_ns integer, host_end_ns integer,
     device_start_ns integer, device_end_ns integer);
 create table if not exists counter_sample(id integer primary key, name_id integer, device integer, ts_ns integer, value real);
+create table if not exists host_sample(id integer primary key, process_id integer, tid integer, ts_ns integer, depth integer, clock text,
+    leaf_id integer, stack_id integer);
 create index if not exists kd_name on kernel_dispatch(name_id);
 create index if not exists kd_start on kernel_dispatch(start_ns);
 create index if not exists rg_start on region(start_ns);
@@ -144,6 +146,15 @@ class TraceDB:
                      int(r["Grid_Size_X"]), int(r["Grid_Size_Y"]), int(r["Grid_Size_Z"]), int(r["Workgroup_Size_X"]), int(r["Workgroup_Size_Y"]),
                      int(r["Workgroup_Size_Z"]), int(r.get("Cluster_X", 0) or 0), int(r.get("Cluster_Y", 0) or 0), int(r.get("Cluster_Z", 0) or 0)))
                 n += 1
+        elif {"timestamp_ns", "tid", "stack"} <= cols:  # host call-stack samples (libb200sample.so); the file name carries the pid
+            m2 = re.search(r"\.(\d+)\.samples\.csv$", os.path.basename(path))
+            pid = self.process_id(int(m2.group(1)) if m2 else 0, file_rank, command)
+            for r in rows:
+                stack = r["stack"]
+                self.db.execute("insert into host_sample(process_id, tid, ts_ns, depth, clock, leaf_id, stack_id) values (?,?,?,?,?,?,?)",
+                                (pid, int(r["tid"]), int(r["timestamp_ns"]), int(r["depth"]), r.get("clock", ""), self.string_id(stack.rsplit(";", 1)[-1]),
+                                 self.string_id(stack)))
+                n += 1
         elif {"Counter", "Device", "Timestamp", "Value"} <= cols:  # system sampler
             for r in rows:
                 self.db.execute("insert into counter_sample(name_id, device, ts_ns, value) values (?,?,?,?)",
@@ -233,6 +244,7 @@ class TraceDB:
         for table, col in (("kernel_dispatch", "start_ns"), ("memory_copy", "start_ns"), ("region", "start_ns"), ("collective", "host_start_ns")):
             n += self.db.execute(f"delete from {table} where {col} < ? or {col} >= ?", (lo, hi)).rowcount
         n += self.db.execute("delete from counter_sample where ts_ns < ? or ts_ns >= ?", (lo, hi)).rowcount
+        n += self.db.execute("delete from host_sample where ts_ns < ? or ts_ns >= ?", (lo, hi)).rowcount
         self.db.commit()
         return n
 
@@ -268,6 +280,11 @@ class TraceDB:
                             " host_end_ns, device_start_ns, device_end_ns) values (?,?,?,?,?,?,?,?,?,?,?,?,?)", row)
         for name_id, device, ts_ns, value in src.execute("select name_id, device, ts_ns, value from counter_sample"):
             self.db.execute("insert into counter_sample(name_id, device, ts_ns, value) values (?,?,?,?)", (smap[name_id], device, ts_ns, value))
+        if src.execute("select count(*) from sqlite_master where name = 'host_sample'").fetchone()[0]:
+            for row in src.execute("select process_id, tid, ts_ns, depth, clock, leaf_id, stack_id from host_sample"):
+                row = list(row)
+                row[0], row[5], row[6] = pmap[row[0]], smap[row[5]], smap[row[6]]
+                self.db.execute("insert into host_sample(process_id, tid, ts_ns, depth, clock, leaf_id, stack_id) values (?,?,?,?,?,?,?)", row)
         src.close()
         self.db.commit()
 
@@ -294,7 +311,33 @@ class TraceDB:
         names, rows = self.query("select s.value as counter, c.device, count(*) as samples, min(c.value) as min, avg(c.value) as mean, max(c.value) as max"
                                  " from counter_sample c join string s on s.id = c.name_id group by s.value, c.device order by s.value, c.device")
         out["counters"] = [dict(zip(names, r)) for r in rows]
+        out["host_samples"] = self.host_profile(top)
         return out
+
+    def host_profile(self, top: int = 15) -> List[dict]:
+        """Functions by the share of host call-stack samples they appear in: ``self`` counts samples whose innermost frame is
+        the function, ``inclusive`` samples that have it anywhere on the stack (once per sample, recursion or not)."""
+        total = self.db.execute("select count(*) from host_sample").fetchone()[0]
+        if not total:
+            return []
+        self_n: dict = {}
+        incl: dict = {}
+        for stack, leaf, cnt in self.db.execute("select st.value, lf.value, count(*) from host_sample h join string st on st.id = h.stack_id"
+                                                " join string lf on lf.id = h.leaf_id group by h.stack_id"):
+            self_n[leaf] = self_n.get(leaf, 0) + cnt
+            for fn in set(stack.split(";")):
+                incl[fn] = incl.get(fn, 0) + cnt
+        rows = sorted(incl.items(), key=lambda kv: (-self_n.get(kv[0], 0), -kv[1], kv[0]))[:top]
+        return [{"function": fn, "self": self_n.get(fn, 0), "self_pct": round(100.0 * self_n.get(fn, 0) / total, 2), "inclusive": n,
+                 "inclusive_pct": round(100.0 * n / total, 2)} for fn, n in rows]
+
+    def to_folded(self, path: str) -> int:
+        """Host samples as folded stacks (``outer;...;leaf count`` per line), the input of flame-graph tools."""
+        rows = self.db.execute("select st.value, count(*) from host_sample h join string st on st.id = h.stack_id group by h.stack_id order by 2 desc").fetchall()
+        with open(path, "w") as f:
+            for stack, cnt in rows:
+                f.write(f"{stack} {cnt}\n")
+        return len(rows)
 
     def to_perfetto(self, path: str) -> int:
         """Chrome/Perfetto JSON: one process per rank/pid; threads for host regions, streams for kernels and copies."""
@@ -329,6 +372,11 @@ class TraceDB:
         for name, dev, ts, val in self.db.execute("select s.value, c.device, c.ts_ns, c.value from counter_sample c join string s on s.id = c.name_id"):
             track = name if dev < 0 else f"{name} [{dev}]"
             events.append({"ph": "C", "pid": 0, "name": track, "ts": ts / 1e3, "args": {"value": val}})
+        # Host call-stack samples: one instant per sample on the sampled thread's track, named by the innermost frame.
+        for pid, tid, ts, leaf, stack in self.db.execute("select p.pid, h.tid, h.ts_ns, lf.value, st.value from host_sample h join process p on p.id = h.process_id"
+                                                         " join string lf on lf.id = h.leaf_id join string st on st.id = h.stack_id"):
+            events.append({"ph": "i", "s": "t", "pid": pid, "tid": f"samples {tid}", "name": leaf, "cat": "host_sample", "ts": ts / 1e3,
+                           "args": {"stack": stack.split(";")}})
         with open(path, "w") as f:
             json.dump({"traceEvents": events, "displayTimeUnit": "ns"}, f)
         return len(events)
@@ -364,7 +412,7 @@ def format_table(names: Sequence[str], rows: Iterable[Sequence], max_width: int 
 
 def print_summary(summary: dict, file=sys.stdout) -> None:
     titles = {"kernels": "KERNEL_DISPATCH", "collectives": "COLLECTIVES (device time)", "regions": "API / MARKER REGIONS",
-              "memory_copies": "MEMORY_COPY", "busy": "DEVICE BUSY", "counters": "SAMPLED COUNTERS"}
+              "memory_copies": "MEMORY_COPY", "busy": "DEVICE BUSY", "counters": "SAMPLED COUNTERS", "host_samples": "HOST CALL-STACK SAMPLES"}
     for key, title in titles.items():
         rows = summary.get(key) or []
         if not rows:
@@ -393,7 +441,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("--format", choices=["table", "csv", "json"], default="table")
     p = sub.add_parser("convert")
     p.add_argument("db")
-    p.add_argument("--format", choices=["perfetto", "csv"], required=True)
+    p.add_argument("--format", choices=["perfetto", "csv", "folded"], required=True)
     p.add_argument("-o", "--output", required=True)
     a = ap.parse_args(argv)
     if a.cmd == "import":
@@ -423,6 +471,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         with TraceDB(a.db) as db:
             if a.format == "perfetto":
                 print(f"{db.to_perfetto(a.output)} events -> {a.output}")
+            elif a.format == "folded":
+                print(f"{db.to_folded(a.output)} distinct stacks -> {a.output}")
             else:
                 print("\n".join(db.to_csv(a.output)))
     return 0

@@ -135,6 +135,19 @@ def build_prof() -> Path | None:
     return out
 
 
+def build_sampler() -> Path | None:
+    """The host call-stack sampler (preload library, plain C++, no CUDA)."""
+    src = CSRC / "prof" / "sampler.cc"
+    if not src.exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200sample.so"
+    hdr = CSRC / "include" / "b200coll" / "sample.h"
+    if not out.exists() or out.stat().st_mtime_ns < max(src.stat().st_mtime_ns, hdr.stat().st_mtime_ns):
+        _run(["g++", "-O2", "-g", "-std=c++17", "-fPIC", "-shared", f"-I{CSRC / 'include'}", str(src), "-o", str(out), "-lpthread", "-ldl"])
+    return out
+
+
 def build_perf(verbose_ptxas: bool = False) -> list[Path]:
     """rccl-tests-style benchmark binaries (one per collective) linked against the library."""
     BIN.mkdir(exist_ok=True)
@@ -225,6 +238,8 @@ def build_all(verbose_ptxas: bool = False) -> dict:
     res["sample_tool"] = str(tool) if tool else None
     prof = build_prof()
     res["prof"] = str(prof) if prof else None
+    samp = build_sampler()
+    res["sampler"] = str(samp) if samp else None
     ext = build_torch_ext()
     res["torch_ext"] = str(ext) if ext else None
     return res
