@@ -26,6 +26,7 @@
 #include "../coll/prims.cuh"
 #include "../core/comm.h"
 #include "b200coll/fused.h"
+#include "gemm_fp8_sm100.cuh"
 #include "gemm_host.h"
 #include "gemm_sm100.cuh"
 
@@ -292,6 +293,53 @@ template <int BN, bool SWIGLU> struct GroupPolicy {
   }
 };
 
+// ---- first expert GEMM straight on the received fp8 rows ---------------------------------------------------------
+// The rows in the window already are what the block-scaled GEMM wants: e4m3 with one fp32 scale per row and 128
+// channels (row-major here, [row][hidden / 128]). With the experts' gate/up weight quantised per 128 x 128 block
+// (interleaved per 128 rows: 64 gate rows, then the 64 up rows of the same outputs) the dequantisation pass and its
+// bf16 copy of the activations disappear, and the larger of the two GEMMs runs at fp8 rate.
+struct GroupPolicy8 {
+  const uint32_t* cnt;  // rows per expert (may exceed cap when rows were dropped)
+  int cap, capTiles;
+  int wRows;            // weight rows per expert (2 ffn)
+  const float* sA;      // [expertsLocal * cap][groups]
+  int groups;           // hidden / 128
+  __nv_bfloat16* out;   // act [expertsLocal * cap, nOut]
+  int ldo, nOut;
+  __device__ __forceinline__ int have(int e) const { return min((int)cnt[e], cap); }
+  __device__ __forceinline__ void coord(int t, int, int tilesN, int& tm, int& tn) const {
+    const int per = capTiles * tilesN;
+    const int e = t / per, r = t - e * per;
+    tm = e * capTiles + r / tilesN;
+    tn = r % tilesN;
+  }
+  __device__ __forceinline__ bool valid(int tm, int) const { return (tm % capTiles) * gemm::BM < have(tm / capTiles); }
+  __device__ __forceinline__ int bRow(int tm, int tn) const { return (tm / capTiles) * wRows + tn * gemm8::BN; }
+  __device__ __forceinline__ int scaleBOff(int tm, int tn) const { return ((tm / capTiles) * (wRows / gemm8::BN) + tn) * groups; }
+  __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
+  __device__ __forceinline__ bool epiBegin(int, volatile int*) const { return true; }
+  __device__ __forceinline__ float scaleA(int kb, int row) const { return __ldg(sA + (size_t)row * groups + kb); }
+  __device__ __forceinline__ void emit(float (&acc)[gemm8::BN], int tm, int tn, int q, int lane, uint8_t* sw) const {
+    constexpr int H = gemm8::BN / 2;
+    const int e = tm / capTiles;
+    const int row0 = tm * gemm::BM + q * 32;
+    const int rowsHave = have(e) - (row0 - e * cap);  // rows of this warp's 32 that hold tokens
+#pragma unroll
+    for (int i = 0; i < H; i++) {
+      const float g = acc[i];
+      acc[i] = g / (1.f + __expf(-g)) * acc[H + i];
+    }
+    gemm8::storeTile(sw, lane, H, acc,  // ffn is a multiple of 128: every tile has all of its 64 output columns
+                     [&](int r) -> __nv_bfloat16* { return r < rowsHave ? out + (size_t)(row0 + r) * ldo + (size_t)tn * H : nullptr; });
+  }
+  __device__ __forceinline__ void tileDone(int, int, int, int) const {}
+};
+
+__global__ void __launch_bounds__(gemm::kThreads, 1) groupedGemmFp8Kernel(const __grid_constant__ gemm8::Params p, const __grid_constant__ GroupPolicy8 pol) {
+  extern __shared__ uint8_t smemRaw[];
+  gemm8::gemmFp8Cta(p, pol, blockIdx.x, gridDim.x, smemRaw);
+}
+
 // ---- combine ---------------------------------------------------------------------------------------------------
 struct CombineArgs {
   const int* topIdx;      // [T, k]
@@ -494,40 +542,64 @@ ncclResult_t b200collEpDispatch(ncclComm_t comm, void* winSym, const void* xBf16
   return ncclSuccess;
 }
 
-// Dequantise what arrived and run both grouped expert GEMMs; results land in the window's
-// output region. xb [expertsLocal * cap, hidden] and act [expertsLocal * cap, ffn] are scratch.
-ncclResult_t b200collEpExperts(ncclComm_t comm, void* winSym, const void* w13, const void* w2, void* xb, void* act, int expertsLocal, int cap,
-                               int hidden, int ffn, cudaStream_t stream) {
+// Both grouped expert GEMMs on what arrived; results land in the window's output region. act [expertsLocal * cap, ffn] is
+// scratch. bf16 form: the rows are dequantised into xb [expertsLocal * cap, hidden] first. fp8 form (w13Scales != nullptr):
+// the first GEMM reads the window's e4m3 rows and scales in place against a block-quantised w13.
+static ncclResult_t epExperts(const char* what, ncclComm_t comm, void* winSym, const void* w13, const float* w13Scales, const void* w2, void* xb, void* act,
+                              int expertsLocal, int cap, int hidden, int ffn, cudaStream_t stream) {
+  const bool fp8 = w13Scales != nullptr;
   Comm* c = asComm(comm);
   BCHECK(commCheck(c));
   BCHECK(checkShape(expertsLocal, cap, hidden, ffn, 1));
-  if (!winSym || !w13 || !w2 || !xb || !act) BFAIL(ncclInvalidArgument, "b200collEpExperts: null buffer");
+  if (!winSym || !w13 || !w2 || (!fp8 && !xb) || !act) BFAIL(ncclInvalidArgument, "%s: null buffer", what);
   EpGuard g(c->cudaDev);
   const EpLayout L = makeLayout(c->nranks, expertsLocal, cap, hidden, ffn);
   int parity;
   {
     std::lock_guard<std::mutex> lk(gEpMu);
     auto it = gEp.find(std::make_pair(c, (const void*)winSym));
-    if (it == gEp.end() || it->second.calls == 0) BFAIL(ncclInvalidUsage, "b200collEpExperts: no dispatch has run on this window");
+    if (it == gEp.end() || it->second.calls == 0) BFAIL(ncclInvalidUsage, "%s: no dispatch has run on this window", what);
     parity = (int)((it->second.calls - 1) & 1);
   }
   const char* win = (const char*)winSym;
   const uint32_t* cnt = (const uint32_t*)(win + L.cntOff) + (size_t)parity * expertsLocal;
-  epDequant<<<4 * gemm::smCount(), 256, 0, stream>>>(win, L, parity, (__nv_bfloat16*)xb);
-  BCUDA(cudaGetLastError());
   const int rows = expertsLocal * cap;
-  // GEMM 1: act = swiglu(xb * w13^T), w13 [expertsLocal * 2 ffn, hidden] with gate/up interleaved per tile.
-  {
-    const int wRows = 2 * ffn;
+  const int wRows = 2 * ffn;
+  if (fp8) {
+    // GEMM 1: act = swiglu(dequant(rows) * dequant(w13)^T) on the window's payload.
+    gemm8::Params p{};
+    if (!gemm::makeTileMap(&p.mapA, win + L.payloadOff, rows, hidden, hidden, gemm::BM, 1) ||
+        !gemm::makeTileMap(&p.mapB, w13, (uint64_t)expertsLocal * wRows, hidden, hidden, gemm8::BN, 1))
+      BFAIL(ncclInvalidArgument, "%s: misaligned operands", what);
+    p.sA = (const float*)(win + L.scaleOff);
+    p.sB = w13Scales;
+    p.C = (__nv_bfloat16*)act;
+    p.M = rows; p.N = wRows; p.K = hidden; p.ldc = ffn;
+    p.tilesM = rows / gemm::BM; p.tilesN = wRows / gemm8::BN; p.kBlocks = hidden / 128;
+    p.err = gemm::errWord();
+    if (!p.err) BFAIL(ncclUnhandledCudaError, "%s: no error word", what);
+    GroupPolicy8 pol{cnt, cap, cap / gemm::BM, wRows, p.sA, hidden / 128, (__nv_bfloat16*)act, ffn, ffn};
+    cudaError_t e = cudaFuncSetAttribute(groupedGemmFp8Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm8::kSmemBytes);
+    if (e == cudaSuccess) {
+      int grid = gemm::smCount();
+      if (grid > p.tilesM * p.tilesN) grid = p.tilesM * p.tilesN;
+      groupedGemmFp8Kernel<<<grid, gemm::kThreads, gemm8::kSmemBytes, stream>>>(p, pol);
+      e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "%s: first grouped GEMM failed to launch: %s", what, cudaGetErrorString(e));
+  } else {
+    epDequant<<<4 * gemm::smCount(), 256, 0, stream>>>(win, L, parity, (__nv_bfloat16*)xb);
+    BCUDA(cudaGetLastError());
+    // GEMM 1: act = swiglu(xb * w13^T), w13 [expertsLocal * 2 ffn, hidden] with gate/up interleaved per tile.
     const int bn = wRows % 256 == 0 ? 256 : 128;
     gemm::Params p{};
     if (!gemm::makeTileMap(&p.mapA, xb, rows, hidden, hidden, gemm::BM, 2) || !gemm::makeTileMap(&p.mapB, w13, (uint64_t)expertsLocal * wRows, hidden, hidden, bn, 2))
-      BFAIL(ncclInvalidArgument, "b200collEpExperts: misaligned operands");
+      BFAIL(ncclInvalidArgument, "%s: misaligned operands", what);
     p.M = rows; p.N = wRows; p.K = hidden; p.tilesM = rows / gemm::BM; p.tilesN = wRows / bn; p.err = gemm::errWord();
     cudaError_t e;
     if (bn == 256) e = launchGrouped(p, GroupPolicy<256, true>{cnt, cap, cap / gemm::BM, wRows, (__nv_bfloat16*)act, ffn, ffn}, stream);
     else e = launchGrouped(p, GroupPolicy<128, true>{cnt, cap, cap / gemm::BM, wRows, (__nv_bfloat16*)act, ffn, ffn}, stream);
-    if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collEpExperts: first grouped GEMM failed to launch: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "%s: first grouped GEMM failed to launch: %s", what, cudaGetErrorString(e));
   }
   // GEMM 2: out = act * w2^T, w2 [expertsLocal * hidden, ffn].
   {
@@ -535,14 +607,25 @@ ncclResult_t b200collEpExperts(ncclComm_t comm, void* winSym, const void* w13, c
     gemm::Params p{};
     __nv_bfloat16* out = (__nv_bfloat16*)((char*)winSym + L.outOff);
     if (!gemm::makeTileMap(&p.mapA, act, rows, ffn, ffn, gemm::BM, 2) || !gemm::makeTileMap(&p.mapB, w2, (uint64_t)expertsLocal * hidden, ffn, ffn, bn, 2))
-      BFAIL(ncclInvalidArgument, "b200collEpExperts: misaligned operands");
+      BFAIL(ncclInvalidArgument, "%s: misaligned operands", what);
     p.M = rows; p.N = hidden; p.K = ffn; p.tilesM = rows / gemm::BM; p.tilesN = hidden / bn; p.err = gemm::errWord();
     cudaError_t e;
     if (bn == 256) e = launchGrouped(p, GroupPolicy<256, false>{cnt, cap, cap / gemm::BM, hidden, out, hidden, hidden}, stream);
     else e = launchGrouped(p, GroupPolicy<128, false>{cnt, cap, cap / gemm::BM, hidden, out, hidden, hidden}, stream);
-    if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collEpExperts: second grouped GEMM failed to launch: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "%s: second grouped GEMM failed to launch: %s", what, cudaGetErrorString(e));
   }
   return ncclSuccess;
+}
+
+ncclResult_t b200collEpExperts(ncclComm_t comm, void* winSym, const void* w13, const void* w2, void* xb, void* act, int expertsLocal, int cap,
+                               int hidden, int ffn, cudaStream_t stream) {
+  return epExperts("b200collEpExperts", comm, winSym, w13, nullptr, w2, xb, act, expertsLocal, cap, hidden, ffn, stream);
+}
+
+ncclResult_t b200collEpExpertsFp8(ncclComm_t comm, void* winSym, const void* w13Fp8, const float* w13Scales, const void* w2, void* act, int expertsLocal,
+                                  int cap, int hidden, int ffn, cudaStream_t stream) {
+  if (!w13Scales) BFAIL(ncclInvalidArgument, "b200collEpExpertsFp8: null weight scales");
+  return epExperts("b200collEpExpertsFp8", comm, winSym, w13Fp8, w13Scales, w2, nullptr, act, expertsLocal, cap, hidden, ffn, stream);
 }
 
 ncclResult_t b200collEpCombine(ncclComm_t comm, void* winSym, const int* topIdx, const float* topW, const int* sentSlot, void* out, int T, int k,

@@ -7,7 +7,7 @@ namespace gemm8 {
 
 __global__ void __launch_bounds__(kThreads, 1) gemmFp8BlockKernel(const __grid_constant__ Params p) {
   extern __shared__ uint8_t smemRaw[];
-  PlainPolicy8 pol{p.sA, p.C, p.M, p.N, p.ldc};
+  PlainPolicy8 pol{p};
   gemmFp8Cta(p, pol, blockIdx.x, gridDim.x, smemRaw);
 }
 

@@ -81,6 +81,9 @@ __device__ __forceinline__ void storeTile(uint8_t* sw, int lane, int colLimit, c
 
 // Policy interface (all __device__):
 //   void coord(int t, int tilesM, int tilesN, int& tm, int& tn)   tile order
+//   bool valid(int tm, int tn)                                   false: the tile is skipped by every role
+//   int bRow(int tm, int tn)                                     first row of the tile in the B tensor map
+//   int scaleBOff(int tm, int tn)                                offset into p.sB of the tile's weight scales (one per K block)
 //   bool waitTile(int tm, int tn, volatile int* err)             producer thread: the A rows of the tile are in place
 //   bool epiBegin(int tm, volatile int* err)                     every epilogue thread, before the first scale of a tile is read
 //   float scaleA(int kb, int row)                                activation scale of `row` for K block kb (row < M)
@@ -136,12 +139,14 @@ __device__ __forceinline__ void gemmFp8Cta(const Params& p, Policy& pol, int cta
       for (int t = cta; t < numTiles && ok; t += nctas) {
         int tm, tn;
         pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+        if (!pol.valid(tm, tn)) continue;
         if (!pol.waitTile(tm, tn, err)) { ok = false; break; }
+        const int bRow = pol.bRow(tm, tn);
         for (int k = 0; k < kIters; k++) {
           if (!mbarWait(&empty[stage], phase ^ 1, err, gemm::ERR_PRODUCER_EMPTY)) { ok = false; break; }
           mbarArriveExpectTx(&full[stage], kStageBytes);
           tmaLoad2d(smemA + (size_t)stage * kABytes, &p.mapA, k * BK, tm * BM, &full[stage]);
-          tmaLoad2d(smemB + (size_t)stage * kBBytes, &p.mapB, k * BK, tn * BN, &full[stage]);
+          tmaLoad2d(smemB + (size_t)stage * kBBytes, &p.mapB, k * BK, bRow, &full[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -155,6 +160,11 @@ __device__ __forceinline__ void gemmFp8Cta(const Params& p, Policy& pol, int cta
       uint32_t phase = 0, blk = 0;
       bool ok = true;
       for (int t = cta; t < numTiles && ok; t += nctas) {
+        {
+          int tm, tn;
+          pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+          if (!pol.valid(tm, tn)) continue;
+        }
         for (int k = 0; k < kIters; k++) {
           const uint32_t b = blk & 1, bPhase = (blk >> 1) & 1;
           blk++;
@@ -179,6 +189,7 @@ __device__ __forceinline__ void gemmFp8Cta(const Params& p, Policy& pol, int cta
     for (int t = cta; t < numTiles && ok; t += nctas) {
       int tm, tn;
       pol.coord(t, p.tilesM, p.tilesN, tm, tn);
+      if (!pol.valid(tm, tn)) continue;
       if (!pol.epiBegin(tm, err)) { ok = false; break; }
       const int row = tm * BM + q * 32 + lane;
       float acc[BN];
@@ -187,7 +198,7 @@ __device__ __forceinline__ void gemmFp8Cta(const Params& p, Policy& pol, int cta
       for (int k = 0; k < kIters; k++) {
         const uint32_t b = blk & 1, bPhase = (blk >> 1) & 1;
         blk++;
-        const float s = (row < p.M ? pol.scaleA(k, row) : 0.f) * __ldg(p.sB + (size_t)tn * p.kBlocks + k);
+        const float s = (row < p.M ? pol.scaleA(k, row) : 0.f) * __ldg(p.sB + (size_t)pol.scaleBOff(tm, tn) + k);
         if (!mbarWait(&partFull[b], bPhase, err, gemm::ERR_EPI_ACC_FULL)) { ok = false; break; }
         tcFenceAfter();
         const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + b * BN;
@@ -215,16 +226,18 @@ __device__ __forceinline__ void gemmFp8Cta(const Params& p, Policy& pol, int cta
 
 // ---- the plain GEMM: banded order, nothing to wait for, C = bf16(acc) ------------------------------------
 struct PlainPolicy8 {
-  const float* sA;
-  __nv_bfloat16* C;
-  int M, N, ldc;
+  const Params& p;  // the kernel's __grid_constant__ parameter
   __device__ __forceinline__ void coord(int t, int tilesM, int tilesN, int& tm, int& tn) const { gemm::bandedCoord(t, tilesM, tilesN, tm, tn); }
+  __device__ __forceinline__ bool valid(int, int) const { return true; }
+  __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
+  __device__ __forceinline__ int scaleBOff(int, int tn) const { return tn * p.kBlocks; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ bool epiBegin(int, volatile int*) const { return true; }
-  __device__ __forceinline__ float scaleA(int kb, int row) const { return __ldg(sA + (size_t)kb * M + row); }
+  __device__ __forceinline__ float scaleA(int kb, int row) const { return __ldg(p.sA + (size_t)kb * p.M + row); }
   __device__ __forceinline__ void emit(float (&acc)[BN], int tm, int tn, int q, int lane, uint8_t* sw) const {
     const int row0 = tm * BM + q * 32;
-    storeTile(sw, lane, N - tn * BN, acc, [&](int r) -> __nv_bfloat16* { return row0 + r < M ? C + (size_t)(row0 + r) * ldc + (size_t)tn * BN : nullptr; });
+    storeTile(sw, lane, p.N - tn * BN, acc,
+              [&](int r) -> __nv_bfloat16* { return row0 + r < p.M ? p.C + (size_t)(row0 + r) * p.ldc + (size_t)tn * BN : nullptr; });
   }
   __device__ __forceinline__ void tileDone(int, int, int, int) const {}
 };

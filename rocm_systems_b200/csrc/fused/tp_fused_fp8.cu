@@ -70,6 +70,9 @@ template <bool SWIGLU> struct AgPolicy {
     tm = owner * a.blocksPerRank + r / tilesN;
     tn = r % tilesN;
   }
+  __device__ __forceinline__ bool valid(int, int) const { return true; }
+  __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
+  __device__ __forceinline__ int scaleBOff(int, int tn) const { return tn * a.kBlocks; }
   __device__ __forceinline__ bool waitTile(int tm, int, volatile int* err) const {
     if (tm / a.blocksPerRank == rank) return true;
     return waitBlockFlag(a.flags + tm, a.seq, err, true);
@@ -130,9 +133,12 @@ __global__ void __launch_bounds__(kThreads, 1) agGemmFp8Kernel(const __grid_cons
 
 // ---- GEMM -> reduce-scatter --------------------------------------------------------------------------------
 struct RsPolicy {
-  RsArgs a;
+  const RsArgs& a;  // the kernel's __grid_constant__ parameter
   const float* sA;  // [K / 128][M], local
-  int M, rank, n;
+  int M, kBlocks, rank, n;
+  __device__ __forceinline__ bool valid(int, int) const { return true; }
+  __device__ __forceinline__ int bRow(int, int tn) const { return tn * BN; }
+  __device__ __forceinline__ int scaleBOff(int, int tn) const { return tn * kBlocks; }
   __device__ __forceinline__ void coord(int t, int, int tilesN, int& tm, int& tn) const {
     // Tiles of remote owners first (rank+1, rank+2, ...), the rows this rank owns last.
     const int perGroup = a.blocksPerRank * tilesN;
@@ -156,7 +162,7 @@ struct RsPolicy {
 
 __global__ void __launch_bounds__(kThreads, 1) gemmRsFp8Kernel(const __grid_constant__ Params p, const __grid_constant__ RsArgs a, const __grid_constant__ DevComm c) {
   extern __shared__ uint8_t smemRaw[];
-  RsPolicy pol{a, p.sA, p.M, c.rank, c.nranks};
+  RsPolicy pol{a, p.sA, p.M, p.kBlocks, c.rank, c.nranks};
   gemmFp8Cta(p, pol, blockIdx.x, gridDim.x, smemRaw);
   tp::reduceOwnedTiles<BN>(a, c.rank, c.nranks, p.err);
 }

@@ -66,6 +66,11 @@ ncclResult_t b200collEpDispatch(ncclComm_t comm, void* winSym, const void* xBf16
  * rows; w2 [expertsLocal * hidden, ffn]. xb / act: scratch [expertsLocal * cap, hidden / ffn] bf16. */
 ncclResult_t b200collEpExperts(ncclComm_t comm, void* winSym, const void* w13, const void* w2, void* xb, void* act, int expertsLocal, int cap,
                                int hidden, int ffn, cudaStream_t stream);
+/* The same with the first GEMM on the received fp8 rows as they are (no dequantisation pass, no xb): w13Fp8
+ * [expertsLocal * 2 ffn, hidden] e4m3 with, per block of 128 rows, 64 gate rows then the 64 up rows of the same outputs,
+ * and w13Scales [expertsLocal * 2 ffn / 128][hidden / 128], one fp32 scale per 128 x 128 block. w2 stays bf16. */
+ncclResult_t b200collEpExpertsFp8(ncclComm_t comm, void* winSym, const void* w13Fp8, const float* w13Scales, const void* w2, void* act, int expertsLocal,
+                                  int cap, int hidden, int ffn, cudaStream_t stream);
 /* out [T, hidden] bf16 = sum_k gate[t, k] * expert_output(row sent for (t, k)), pulled from the
  * owning ranks inside one kernel, in the order k = 0 .. k-1. */
 ncclResult_t b200collEpCombine(ncclComm_t comm, void* winSym, const int* topIdx, const float* topW, const int* sentSlot, void* out, int T, int k,

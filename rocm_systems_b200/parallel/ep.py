@@ -30,6 +30,7 @@ def _lib_ep():
         lib.b200collEpRoute.argtypes = [vp, vp, vp, i32, i32, i32, vp]
         lib.b200collEpDispatch.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
         lib.b200collEpExperts.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+        lib.b200collEpExpertsFp8.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
         lib.b200collEpCombine.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
         lib.b200collEpCounts.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp]
         _done = True
@@ -55,9 +56,13 @@ class MoELayer:
     permutes, quantises to fp8 e4m3 (a scale per 128 channels) and stores rows into the owning ranks, grouped expert GEMMs on
     the tcgen05 kernel, and one combine kernel that pulls the expert outputs back and applies the gate weights in a fixed
     order. ``reference_forward`` states the same layer in plain PyTorch with NCCL-style collectives.
+
+    ``fp8_experts=True`` quantises the gate/up weights once per 128 x 128 block and runs the first expert GEMM directly on
+    the fp8 rows that arrived (``b200collEpExpertsFp8``): no dequantisation pass, no bf16 copy of the received activations.
     """
 
-    def __init__(self, comm, experts_local: int, hidden: int, ffn: int, top_k: int, tokens: int, capacity: int = 0, std: float = 0.02, seed: int = 0):
+    def __init__(self, comm, experts_local: int, hidden: int, ffn: int, top_k: int, tokens: int, capacity: int = 0, std: float = 0.02, seed: int = 0,
+                 fp8_experts: bool = False):
         self.comm, self.n, self.rank = comm, comm.nranks, comm.rank
         self.el, self.hidden, self.ffn, self.k, self.T = experts_local, hidden, ffn, top_k, tokens
         self.E = self.n * experts_local
@@ -73,6 +78,15 @@ class MoELayer:
         tile = 256 if (2 * ffn) % 256 == 0 else 128
         self.w13 = torch.cat([interleave_gate_up(self.w_gate[e], self.w_up[e], tile) for e in range(experts_local)]).contiguous()
         self.w2 = self.w_down.reshape(experts_local * hidden, ffn).contiguous()
+        self.fp8_experts = fp8_experts
+        if fp8_experts:
+            from ..ops import fp8
+            w13_128 = torch.cat([interleave_gate_up(self.w_gate[e], self.w_up[e], 128) for e in range(experts_local)]).contiguous()
+            self.w13_q, self.w13_s = fp8.quantize_weight(w13_128)
+            # what the experts multiply by, for the oracle: the block-quantised weights back in bf16, de-interleaved
+            deq = fp8.ref_dequantize_weight(self.w13_q, self.w13_s).view(experts_local, 2 * ffn // 128, 2, 64, hidden)
+            self._w_gate_ref = deq[:, :, 0].reshape(experts_local, ffn, hidden).to(torch.bfloat16)
+            self._w_up_ref = deq[:, :, 1].reshape(experts_local, ffn, hidden).to(torch.bfloat16)
         lib = _lib_ep()
         self._win = comm.sym_alloc(int(lib.b200collEpWorkspaceBytes(self.n, experts_local, self.cap, hidden, ffn)))
         rows = experts_local * self.cap
@@ -101,6 +115,11 @@ class MoELayer:
 
     def experts(self) -> None:
         s = torch.cuda.current_stream().cuda_stream
+        if self.fp8_experts:
+            _lib.check(_lib_ep().b200collEpExpertsFp8(self.comm.handle, self._win.ptr, self.w13_q.data_ptr(), self.w13_s.data_ptr(), self.w2.data_ptr(),
+                                                      self.act.data_ptr(), *self._args(), s), "b200collEpExpertsFp8")
+            train_ops.LAUNCHES += 2
+            return
         _lib.check(_lib_ep().b200collEpExperts(self.comm.handle, self._win.ptr, self.w13.data_ptr(), self.w2.data_ptr(), self.xb.data_ptr(),
                                                self.act.data_ptr(), *self._args(), s), "b200collEpExperts")
         train_ops.LAUNCHES += 3
@@ -155,7 +174,8 @@ class MoELayer:
             if m.numel() == 0:
                 continue
             xe = recv_rows[m]
-            a = (torch.nn.functional.silu((xe @ self.w_gate[e].t()).float()) * (xe @ self.w_up[e].t()).float()).to(torch.bfloat16)
+            wg, wu = (self._w_gate_ref[e], self._w_up_ref[e]) if self.fp8_experts else (self.w_gate[e], self.w_up[e])
+            a = (torch.nn.functional.silu((xe @ wg.t()).float()) * (xe @ wu.t()).float()).to(torch.bfloat16)
             y[m] = a @ self.w_down[e].t()
         back = torch.empty(T * k, H, dtype=torch.bfloat16, device=x.device)
         self.comm.all_to_allv(y, [c * H for c in rc_l], [d * H for d in rd], back, [c * H for c in sc_l], [d * H for d in sd])

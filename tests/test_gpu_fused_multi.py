@@ -46,6 +46,12 @@ def test_ep_dispatch_experts_combine(nproc):
     _launch(nproc, 29830 + nproc, "ep_worker.py")
 
 
+@pytest.mark.xfail(reason="the fp8 expert GEMM has not run on hardware yet", strict=False)
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_ep_with_fp8_experts(nproc):
+    _launch(nproc, 29930 + nproc, "ep_worker.py", "--fp8-experts")
+
+
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_shmem_put_get_signal_atomics(nproc):
     _launch(nproc, 29840 + nproc, "shmem_worker.py")

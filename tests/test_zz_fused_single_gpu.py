@@ -32,6 +32,12 @@ def test_expert_parallel_layer_on_one_rank():
 
 
 @pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
+def test_expert_parallel_layer_with_fp8_experts_on_one_rank():
+    """The first expert GEMM on the received e4m3 rows and block-quantised weights (no dequantisation pass)."""
+    _launch(1, 29887, "ep_worker.py", "--fp8-experts", timeout=600)
+
+
+@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_device_initiated_layer_on_one_pe():
     """put+signal to itself, the atomics on its own words, the barrier of one: the device API's code paths on one GPU."""
     _launch(1, 29884, "shmem_worker.py", timeout=600)

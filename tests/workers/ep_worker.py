@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--ffn", type=int, default=256)
     ap.add_argument("--topk", type=int, default=4)
     ap.add_argument("--tokens", type=int, default=512)
+    ap.add_argument("--fp8-experts", action="store_true")   # first expert GEMM on the received fp8 rows
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--skip-check", action="store_true")
     ap.add_argument("--out", default="")
@@ -44,7 +45,7 @@ def main():
     comm = init_from_env()
     rank, n = comm.rank, comm.nranks
     dev = comm.device
-    moe = MoELayer(comm, args.experts_local, args.hidden, args.ffn, args.topk, args.tokens, seed=3)
+    moe = MoELayer(comm, args.experts_local, args.hidden, args.ffn, args.topk, args.tokens, seed=3, fp8_experts=args.fp8_experts)
     bad = []
     res = {"nranks": n, "experts": moe.E, "topk": args.topk, "hidden": args.hidden, "ffn": args.ffn, "tokens_per_rank": args.tokens, "cap": moe.cap}
     if not args.skip_check:
