@@ -303,6 +303,76 @@ def test_gemm_rs_checker_finds_the_single_half_overwrite():
     assert _violates(*gemm_rs_model(2, 3, nbufs=1), 2)
 
 
+# ---- all-gather -> GEMM (tp_fused.cu, tp_fused_fp8.cu): pulled row blocks behind sequence-numbered flags -------------
+# Per rank two actors of one kernel launch: the communication CTA (barrier: every shard is in place; pull each peer's
+# block into the local copy; publish the block's flag with the call's sequence number; barrier: the peers are done
+# reading my shard) and a GEMM CTA (own block at once, a peer's block after its flag reached the sequence number).
+# Launches of one rank are stream-ordered: call k + 1 starts, and the application overwrites the rank's own shard with
+# the next activations, only after both actors of call k are done. A block's content is modelled as the number of the
+# call it belongs to; a GEMM CTA must only ever multiply blocks of its own call.
+def ag_gemm_model(n, ncalls, end_barrier=True):
+    def upd(t, i, v):
+        return t[:i] + (v,) + t[i + 1:]
+
+    def step(st, pid):
+        comm, gemm, shard, local, flag, bar_a, bar_b = st
+        r = pid % n
+        if pid < n:  # communication CTA of rank r
+            k, pc, idx = comm[r]
+            if k > ncalls:
+                return None
+            if pc == 0:  # launch: previous kernel of this rank complete; the application has written the shard of call k
+                if gemm[r][0] < k:  # the GEMM CTA of call k - 1 is still running
+                    return None
+                return (upd(comm, r, (k, 1, 0)), gemm, upd(shard, r, k), local, flag, upd(bar_a, r, k), bar_b)
+            if pc == 1:  # first barrier
+                if any(b < k for b in bar_a):
+                    return None
+                return (upd(comm, r, (k, 2, 0)), gemm, shard, local, flag, bar_a, bar_b)
+            if pc == 2:  # pull the block of peer (r + 1 + idx) % n: read the owner's shard as it is now
+                peer = (r + 1 + idx) % n
+                return (upd(comm, r, (k, 3, idx)), gemm, shard, upd(local, r * n + peer, shard[peer]), flag, bar_a, bar_b)
+            if pc == 3:  # publish its flag
+                peer = (r + 1 + idx) % n
+                nxt = (k, 2, idx + 1) if idx + 2 < n else (k, 4, 0)
+                return (upd(comm, r, nxt), gemm, shard, local, upd(flag, r * n + peer, k), bar_a, bar_b)
+            if pc == 4:  # second barrier: arrive
+                return (upd(comm, r, (k, 5, 0)), gemm, shard, local, flag, bar_a, upd(bar_b, r, k))
+            if end_barrier and any(b < k for b in bar_b):
+                return None
+            return (upd(comm, r, (k + 1, 0, 0)), gemm, shard, local, flag, bar_a, bar_b)
+        k, idx = gemm[r]
+        if k > ncalls or comm[r][0] < k or (comm[r][0] == k and comm[r][1] == 0):
+            return None  # finished, or the kernel of call k has not been launched on this rank
+        owner = (r + idx) % n
+        if owner == r:
+            got = shard[r]
+        else:
+            if flag[r * n + owner] < k:
+                return None
+            got = local[r * n + owner]
+        assert got == k, f"rank {r} call {k}: block of rank {owner} belongs to call {got}"
+        nxt = (k, idx + 1) if idx + 1 < n else (k + 1, 0)
+        return (comm, upd(gemm, r, nxt), shard, local, flag, bar_a, bar_b)
+
+    zeros = tuple(0 for _ in range(n))
+    initial = (tuple((1, 0, 0) for _ in range(n)), tuple((1, 0) for _ in range(n)), zeros, tuple(0 for _ in range(n * n)),
+               tuple(0 for _ in range(n * n)), zeros, zeros)
+    return initial, step, (lambda st: all(c[0] > ncalls for c in st[0]) and all(g[0] > ncalls for g in st[1]))
+
+
+def test_all_gather_gemm_reads_only_blocks_of_its_own_call():
+    for n, ncalls in [(2, 4), (3, 2)]:
+        initial, step, done = ag_gemm_model(n, ncalls)
+        states, deadlocks = explore(initial, step, done, 2 * n)
+        assert deadlocks == 0 and states > 30 * ncalls
+
+
+def test_all_gather_gemm_checker_finds_the_missing_closing_barrier():
+    """Without the second barrier a fast rank starts its next call and overwrites its shard while a peer still pulls it."""
+    assert _violates(*ag_gemm_model(2, 2, end_barrier=False), 4)
+
+
 # ---- shared-memory ring of bulk asynchronous peer loads (kStagedReduce, peer-load path) ------------------------------
 # A group of threads walks tiles 0..K-1 through S stages. Thread 0 issues tile i into stage i % S (arming the stage's
 # mbarrier; the copy engine completes it at any later time, which stores the data and flips the barrier's phase);
