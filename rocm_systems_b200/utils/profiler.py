@@ -131,3 +131,73 @@ class Profiler:
         for k in self.kernels():
             acc[k["name"]].append(k["end_ns"] - k["start_ns"])
         return {n: {"calls": len(v), "total_ns": sum(v), "mean_ns": sum(v) / len(v), "min_ns": min(v), "max_ns": max(v)} for n, v in acc.items()}
+
+
+class HostSampler:
+    """In-process call-stack sampling of this process's host threads (``libb200sample.so``, csrc/prof/sampler.cc): the
+    part of the reference's system profiler that samples call stacks on a CPU-time or a wall-clock timer
+    (rocprofiler-systems source/lib/rocprof-sys/library/sampling.cpp).
+
+        with HostSampler(freq_hz=200, clock="wall") as s:
+            step()
+        s.write("out/step")            # out/step.samples.csv, out/step.folded
+        for fn, share in s.top(5): ...
+
+    One sampler per process at a time. Native frames only: Python code shows up as the interpreter's own functions.
+    """
+
+    _lib = None
+
+    def __init__(self, freq_hz: float = 100.0, clock: str = "cpu"):
+        assert clock in ("cpu", "wall")
+        self.freq_hz, self.clock = float(freq_hz), clock
+        if HostSampler._lib is None:
+            path = Path(__file__).resolve().parents[1] / "lib" / "libb200sample.so"
+            if not path.exists():
+                raise RuntimeError(f"{path} is missing: run `python -m rocm_systems_b200.utils.build`")
+            lib = ctypes.CDLL(str(path))
+            lib.b200sampleStart.argtypes = [ctypes.c_double, ctypes.c_int]
+            lib.b200sampleCount.restype = ctypes.c_uint64
+            lib.b200sampleDropped.restype = ctypes.c_uint64
+            lib.b200sampleWrite.argtypes = [ctypes.c_char_p]
+            HostSampler._lib = lib
+
+    def start(self) -> "HostSampler":
+        HostSampler._lib.b200sampleClear()
+        rc = HostSampler._lib.b200sampleStart(self.freq_hz, 0 if self.clock == "cpu" else 1)
+        if rc != 0:
+            raise RuntimeError(f"host sampler did not start (code {rc}: -1 already running, -2 bad argument, -4/-5 signal or timer set-up)")
+        return self
+
+    def stop(self) -> None:
+        HostSampler._lib.b200sampleStop()
+
+    __enter__ = start
+
+    def __exit__(self, *exc) -> None:
+        self.stop()
+
+    def count(self) -> int:
+        return int(HostSampler._lib.b200sampleCount())
+
+    def dropped(self) -> int:
+        return int(HostSampler._lib.b200sampleDropped())
+
+    def write(self, prefix: str) -> int:
+        rc = HostSampler._lib.b200sampleWrite(str(prefix).encode())
+        if rc < 0:
+            raise RuntimeError(f"host sampler could not write {prefix}.* (code {rc})")
+        return rc
+
+    def top(self, n: int = 10) -> List[tuple]:
+        """(innermost function, share of samples) for the ``n`` most sampled functions."""
+        import tempfile
+
+        with tempfile.TemporaryDirectory() as d:
+            self.write(f"{d}/s")
+            leaf: Dict[str, int] = defaultdict(int)
+            for line in Path(f"{d}/s.folded").read_text().splitlines():
+                stack, _, cnt = line.rpartition(" ")
+                leaf[stack.rsplit(";", 1)[-1]] += int(cnt)
+        total = sum(leaf.values()) or 1
+        return [(fn, c / total) for fn, c in sorted(leaf.items(), key=lambda kv: -kv[1])[:n]]

@@ -111,3 +111,20 @@ print(n)
     rows = (tmp_path / "inproc.samples.csv").read_text().splitlines()
     assert len(rows) == int(p.stdout.strip()) + 1
     assert any("_PyEval_EvalFrameDefault" in r for r in rows)
+
+
+def test_python_context_manager():
+    code = """
+from rocm_systems_b200.utils.profiler import HostSampler
+import zlib
+with HostSampler(freq_hz=500, clock="cpu") as s:
+    data = bytes(range(256)) * 40000
+    for _ in range(12): zlib.compress(data, 6)
+assert s.count() > 5 and s.dropped() == 0
+top = s.top(3)
+print(top)
+assert any("deflate" in fn or "longest_match" in fn or "compress" in fn or "libz" in fn for fn, _ in top), top
+assert abs(sum(share for _, share in s.top(10000)) - 1.0) < 1e-9
+"""
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=dict(os.environ, PYTHONPATH=str(ROOT)))
+    assert p.returncode == 0, p.stdout + p.stderr

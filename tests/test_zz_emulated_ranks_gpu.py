@@ -4,8 +4,8 @@ grouped send/recv through FIFO slots and credits, the fused FSDP reduce-scatter+
 put+signal ring and remote atomics — run where only one GPU is there. The check itself is native (b200collEmuSelftest: small-integer data, every collective in
 float / bfloat16 / int32, verified on the host, guard bytes behind every output).
 
-The emulation was written after the last session with a GPU and has not run yet; until it has, a failure is reported as
-an expected one instead of failing the suite. It runs in a child process with every device-side wait limited to 5 s."""
+The emulation has not passed on hardware yet; until it has, a failure is reported as an expected one instead of failing
+the suite (a pass shows as XPASS). It runs in a child process with every device-side wait limited to 5 s."""
 import os
 import subprocess
 import sys

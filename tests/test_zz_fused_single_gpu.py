@@ -4,8 +4,8 @@ dispatch (route, fp8 quantise, row reservation by atomics, stores), grouped expe
 plain PyTorch compositions, through the same workers the multi-GPU tests use. The collective part degenerates (nothing
 crosses a link), the kernels and their schedules are the real ones.
 
-These single-rank runs were added after the last session with a GPU; until they have passed once on hardware a failure is
-reported as an expected one. Each runs in a child process; every device-side wait is limited to 5 s."""
+These single-rank runs have not passed on hardware yet; until they have, a failure is reported as an expected one (a pass
+shows as XPASS). Each runs in a child process; every device-side wait is limited to 5 s."""
 import pytest
 
 from test_gpu_fused_multi import _launch

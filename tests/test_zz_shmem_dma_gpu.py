@@ -1,6 +1,6 @@
 """Copy-engine put / get / put+signal between 2 GPUs (csrc/shmem/shmem_kernels.cu, rocm_systems_b200/shmem.py).
 
-Written after the last session with a GPU: until it has passed once on hardware a failure is reported as an expected one."""
+Not yet passed on hardware: until it has, a failure is reported as an expected one (a pass shows as XPASS)."""
 import pytest
 
 from test_gpu_fused_multi import _launch
