@@ -278,8 +278,8 @@ ncclResult_t b200collEmuAllToAll(ncclComm_t* comms, int n, const void* const* se
 }
 
 // The fused FSDP gradient reduce-scatter (bf16 in, fp32 out, scaled) on emulated ranks: send[r] holds n * recvcount
-// bf16 elements, recv[r] receives rank r's recvcount fp32 sums. The host side restates what b200collReduceScatterCast
-// does for ordinary buffers (CTAs, equal chunks of one rank's staging share, staging parity).
+// bf16 elements, recv[r] receives rank r's recvcount fp32 sums, through the staged path of b200collReduceScatterCast
+// (same chunking and staging parity: rsCastStagedArgs).
 ncclResult_t b200collEmuReduceScatterCast(ncclComm_t* comms, int n, const void* const* send, float* const* recv, size_t recvcount, float scale,
                                           int ctasPerRank, cudaStream_t stream) {
   if (!comms || n < 2 || n > kMaxRanks || !send || !recv || recvcount == 0) BFAIL(ncclInvalidArgument, "b200collEmuReduceScatterCast: bad arguments");
@@ -289,17 +289,11 @@ ncclResult_t b200collEmuReduceScatterCast(ncclComm_t* comms, int n, const void* 
   } scope;
   emu::RsCastPack pack{};
   const int lanes = ctasPerRank > 0 ? std::min(ctasPerRank, 16) : 8;
-  const size_t bytes = recvcount * 2;
   for (int r = 0; r < n; r++) {
     Comm* c = asComm(comms[r]);
     BCHECK(commCheck(c));
     if (!c->emulated || c->nranks != n || c->rank != r) BFAIL(ncclInvalidUsage, "b200collEmuReduceScatterCast: comms[%d] must be rank %d of %d ranks sharing one GPU", r, r, n);
-    const size_t capMax = (c->dev.stageBytes / n) & ~(size_t)15;
-    const size_t k = (bytes + capMax - 1) / capMax;
-    size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;
-    if (cap > capMax) cap = capMax;
-    pack.a[r] = RsCastArgs{(const __nv_bfloat16*)send[r], recv[r], recvcount, scale, (int)(c->stageParity & 1), cap};
-    c->stageParity += (uint32_t)((bytes + cap - 1) / cap);
+    pack.a[r] = rsCastStagedArgs(c, send[r], recv[r], recvcount, scale);
     pack.c[r] = c->dev;
     pack.c[r].opSeq = ++c->opSeq;
     pack.c[r].stamp = nullptr;

@@ -22,6 +22,20 @@ struct RsCastArgs {
   size_t chunkBytes;          // bytes of one rank's slice per chunk (equalised by the host); 0 = a whole staging share
 };
 
+// Host side of a staged call: equal chunks of one rank's staging share (the kernel lays data out by the chunk capacity
+// alone, so a short last chunk would leave most lanes idle), this call's staging half, and the communicator's parity
+// advanced by the number of chunks. Every rank computes the same from the same arguments.
+inline RsCastArgs rsCastStagedArgs(Comm* c, const void* sendBf16, float* recvF32, size_t recvcount, float scale) {
+  const size_t bytes = recvcount * 2;
+  const size_t capMax = (c->dev.stageBytes / c->nranks) & ~(size_t)15;
+  const size_t k = (bytes + capMax - 1) / capMax;
+  size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;
+  if (cap > capMax) cap = capMax;
+  RsCastArgs a{(const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale, (int)(c->stageParity & 1), cap};
+  c->stageParity += (uint32_t)((bytes + cap - 1) / cap);
+  return a;
+}
+
 __device__ __forceinline__ void accum8(const uint4& v, float (&acc)[8], bool first) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -218,14 +232,7 @@ extern "C" ncclResult_t b200collReduceScatterCast(ncclComm_t comm, const void* s
       if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collReduceScatterCast launch failed: %s", cudaGetErrorString(e));
       return ncclSuccess;
     }
-    // Equal chunks: the kernel lays data out by the chunk capacity alone, so a short last chunk
-    // would leave most lanes idle.
-    const size_t capMax = (c->dev.stageBytes / c->nranks) & ~(size_t)15;
-    const size_t k = (bytes + capMax - 1) / capMax;
-    size_t cap = (((bytes + k - 1) / k) + 15) & ~(size_t)15;
-    if (cap > capMax) cap = capMax;
-    RsCastArgs a{(const __nv_bfloat16*)sendBf16, recvF32, recvcount, scale, (int)(c->stageParity & 1), cap};
-    c->stageParity += (uint32_t)((bytes + cap - 1) / cap);
+    const RsCastArgs a = rsCastStagedArgs(c, sendBf16, recvF32, recvcount, scale);
     dc.opSeq = ++c->opSeq;
     dc.stamp = stamp;
     if (tr) tr->setAlgo(ALGO_P2P, ctas);
