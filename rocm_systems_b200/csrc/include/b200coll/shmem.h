@@ -83,6 +83,9 @@ int b200shmem_take_status(b200shmem_ctx_t ctx);
  * PE 0's words. Return the number of mismatches in *errors. */
 ncclResult_t b200shmem_selftest_ring(b200shmem_ctx_t ctx, size_t count, int rounds, cudaStream_t stream, int* errors);
 ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStream_t stream, int* errors);
+/* The device API's block-scope collectives (broadcast, fcollect, alltoall, sum / max reduce), wait_until / test and the
+ * strided put on `count` 64-bit words per block, each checked against its closed form. Collective over the PEs. */
+ncclResult_t b200shmem_selftest_collectives(b200shmem_ctx_t ctx, size_t count, cudaStream_t stream, int* errors);
 
 /* The two self-checks between `n` PEs that share the current GPU (communicators created under B200COLL_EMULATE_RANKS=1):
  * every PE is one block of a single cooperative kernel. For tests on one GPU. */

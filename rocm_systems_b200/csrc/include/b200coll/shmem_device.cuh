@@ -194,4 +194,161 @@ __device__ __forceinline__ int barrier_all_block(const b200shmem_dev_t& d) {
 }
 __device__ __forceinline__ int sync_all_block(const b200shmem_dev_t& d) { return barrier_all_block(d); }
 
+// ---- identity -------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int my_pe(const b200shmem_dev_t& d) { return d.pe; }
+__device__ __forceinline__ int n_pes(const b200shmem_dev_t& d) { return d.npes; }
+
+// ---- point-to-point synchronisation on ordinary symmetric words (OpenSHMEM wait_until / test and their vector forms) -------
+// T: a 32- or 64-bit integer type. The word is local; a peer changes it with p(), a put or an atomic.
+template <typename T> __device__ __forceinline__ T load_acquire(const T* ivar) {
+  static_assert(sizeof(T) == 4 || sizeof(T) == 8, "wait_until / test work on 32- and 64-bit words");
+  if constexpr (sizeof(T) == 8) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ivar) : "memory");
+    return (T)v;
+  } else {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ivar) : "memory");
+    return (T)v;
+  }
+}
+template <typename T> __device__ __forceinline__ bool cmpOkT(T v, int cmp, T ref) {
+  switch (cmp) {
+    case B200SHMEM_CMP_EQ: return v == ref;
+    case B200SHMEM_CMP_NE: return v != ref;
+    case B200SHMEM_CMP_GT: return v > ref;
+    case B200SHMEM_CMP_GE: return v >= ref;
+    case B200SHMEM_CMP_LT: return v < ref;
+    default: return v <= ref;
+  }
+}
+template <typename T> __device__ __forceinline__ bool test(const T* ivar, int cmp, T value) { return cmpOkT(load_acquire(ivar), cmp, value); }
+// Index of the first of ivars[0..n) that satisfies the comparison, or -1 (one pass, no waiting): test_any.
+template <typename T> __device__ __forceinline__ int test_any(const T* ivars, int n, int cmp, T value) {
+  for (int i = 0; i < n; i++)
+    if (test(ivars + i, cmp, value)) return i;
+  return -1;
+}
+// Bounded like every wait: B200SHMEM_OK, or B200SHMEM_TIMEOUT once the context's time limit is spent (recorded in d.status).
+template <typename T> __device__ __forceinline__ int wait_until(const b200shmem_dev_t& d, const T* ivar, int cmp, T value) {
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    if (test(ivar, cmp, value)) return B200SHMEM_OK;
+    if ((++spins & 0xff) == 0) {
+      if (*(volatile int*)d.status) return B200SHMEM_TIMEOUT;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > d.timeoutNs) {
+        atomicCAS(d.status, 0, B200SHMEM_TIMEOUT);
+        return B200SHMEM_TIMEOUT;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+template <typename T> __device__ __forceinline__ int wait_until_all(const b200shmem_dev_t& d, const T* ivars, int n, int cmp, T value) {
+  for (int i = 0; i < n; i++)
+    if (wait_until(d, ivars + i, cmp, value) != B200SHMEM_OK) return B200SHMEM_TIMEOUT;
+  return B200SHMEM_OK;
+}
+// Waits until one of ivars[0..n) satisfies the comparison and stores its index in *which.
+template <typename T> __device__ __forceinline__ int wait_until_any(const b200shmem_dev_t& d, const T* ivars, int n, int cmp, T value, int* which) {
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    const int i = test_any(ivars, n, cmp, value);
+    if (i >= 0) { *which = i; return B200SHMEM_OK; }
+    if ((++spins & 0x3f) == 0) {
+      if (*(volatile int*)d.status) return B200SHMEM_TIMEOUT;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > d.timeoutNs) {
+        atomicCAS(d.status, 0, B200SHMEM_TIMEOUT);
+        return B200SHMEM_TIMEOUT;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// ---- strided and non-blocking transfers --------------------------------------------------------------------------------------
+// iput / iget: nelems elements, dest advancing by dst elements and source by sst elements per element (one thread).
+template <typename T> __device__ __forceinline__ void iput(const b200shmem_dev_t& d, T* dest, const T* source, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe) {
+  T* r = ptr(d, dest, pe);
+  for (size_t i = 0; i < nelems; i++) r[(ptrdiff_t)i * dst] = source[(ptrdiff_t)i * sst];
+}
+template <typename T> __device__ __forceinline__ void iget(const b200shmem_dev_t& d, T* dest, const T* source, ptrdiff_t dst, ptrdiff_t sst, size_t nelems, int pe) {
+  const T* r = ptr(d, source, pe);
+  for (size_t i = 0; i < nelems; i++) dest[(ptrdiff_t)i * dst] = r[(ptrdiff_t)i * sst];
+}
+// Stores to a peer are posted (the thread does not wait for them) and become visible at the latest at quiet(), a fence
+// or a barrier, so the non-blocking put is the put; a get has returned its data when the call returns.
+__device__ __forceinline__ void putmem_nbi(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int pe) { putmem(d, dest, source, bytes, pe); }
+__device__ __forceinline__ void getmem_nbi(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int pe) { getmem(d, dest, source, bytes, pe); }
+__device__ __forceinline__ void putmem_nbi_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int pe) { putmem_block(d, dest, source, bytes, pe); }
+__device__ __forceinline__ void getmem_nbi_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int pe) { getmem_block(d, dest, source, bytes, pe); }
+
+// ---- collectives of one block per PE -------------------------------------------------------------------------------------------
+// Like barrier_all_block these are called by every thread of ONE block per PE, by all PEs, with symmetric dest / source.
+// The pushing ones (broadcast, fcollect, alltoall) require, as OpenSHMEM does, that dest is free to be written on every PE
+// at entry; they return after a barrier, when every PE's dest is complete. All return B200SHMEM_OK or B200SHMEM_TIMEOUT.
+//
+// dest on every PE (the root's too, unless dest == source there) = the root's source.
+__device__ __forceinline__ int broadcastmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int root) {
+  if (d.pe == root) {
+    for (int i = 1; i < d.npes; i++) putmem_block(d, dest, source, bytes, (root + i) % d.npes);
+    if (dest != source) putmem_block(d, dest, source, bytes, root);
+  }
+  return barrier_all_block(d);
+}
+// dest [npes][bytes] on every PE: block p is PE p's source (all-gather; OpenSHMEM fcollect).
+__device__ __forceinline__ int fcollectmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes) {
+  for (int i = 0; i < d.npes; i++) putmem_block(d, (char*)dest + (size_t)d.pe * bytes, source, bytes, (d.pe + i) % d.npes);
+  return barrier_all_block(d);
+}
+// source [npes][bytes], dest [npes][bytes]: block p of this PE's source becomes block my_pe of PE p's dest.
+__device__ __forceinline__ int alltoallmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes) {
+  for (int i = 0; i < d.npes; i++) {
+    const int pe = (d.pe + i) % d.npes;
+    putmem_block(d, (char*)dest + (size_t)d.pe * bytes, (const char*)source + (size_t)pe * bytes, bytes, pe);
+  }
+  return barrier_all_block(d);
+}
+struct SumOp { template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a + b; } };
+struct MaxOp { template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a > b ? a : b; } };
+struct MinOp { template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a < b ? a : b; } };
+// dest[i] = op over all PEs of source[i] on every PE (OpenSHMEM *_reduce / *_to_all). Two steps: PE p folds slice p of
+// every PE's source in PE order 0, 1, ... into slice p of its own dest; then every PE fetches the other slices from their
+// owners. Each element is reduced exactly once, so the result is bit-identical everywhere, and dest may be source: slice
+// p of PE p is read by nobody but PE p in the first step, and the other slices are overwritten only after the barrier
+// that ends it. Barriers: before (all sources are written), between, and after (nobody reads this PE's dest any more).
+template <typename T, typename Op>
+__device__ __forceinline__ int reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t nreduce, Op op) {
+  int rc = barrier_all_block(d);
+  if (rc != B200SHMEM_OK) return rc;
+  const size_t per = (nreduce + d.npes - 1) / d.npes;
+  const size_t lo = per * d.pe < nreduce ? per * d.pe : nreduce;
+  const size_t hi = lo + per < nreduce ? lo + per : nreduce;
+  for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    T acc = *(volatile const T*)(ptr(d, source, 0) + i);
+    for (int pe = 1; pe < d.npes; pe++) acc = op(acc, (T) * (volatile const T*)(ptr(d, source, pe) + i));
+    dest[i] = acc;
+  }
+  rc = barrier_all_block(d);
+  if (rc != B200SHMEM_OK) return rc;
+  for (int k = 1; k < d.npes; k++) {
+    const int q = (d.pe + k) % d.npes;
+    const size_t qlo = per * q < nreduce ? per * q : nreduce;
+    const size_t qhi = qlo + per < nreduce ? qlo + per : nreduce;
+    if (qhi > qlo) getmem_block(d, dest + qlo, dest + qlo, (qhi - qlo) * sizeof(T), q);
+  }
+  return barrier_all_block(d);
+}
+template <typename T> __device__ __forceinline__ int sum_reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t n) { return reduce_block(d, dest, source, n, SumOp{}); }
+template <typename T> __device__ __forceinline__ int max_reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t n) { return reduce_block(d, dest, source, n, MaxOp{}); }
+template <typename T> __device__ __forceinline__ int min_reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t n) { return reduce_block(d, dest, source, n, MinOp{}); }
+
 }  // namespace b200shmem

@@ -117,6 +117,69 @@ __device__ __forceinline__ void atomicsBody(const b200shmem_dev_t& d, unsigned l
 
 __global__ void kSelftestAtomics(b200shmem_dev_t d, unsigned long long* words, int iters, int* errors) { atomicsBody(d, words, iters, errors); }
 
+// The block-scope collectives, the wait_until / test family and the strided put, each against its closed form.
+// buf (symmetric, zeroed): A [npes * cnt] | B [npes * cnt] | R [cnt] | F [8] 64-bit words. One block per PE.
+__device__ __forceinline__ void collBody(const b200shmem_dev_t& d, unsigned long long* buf, size_t cnt, int* errors) {
+  using u64 = unsigned long long;
+  const int n = d.npes, me = d.pe, right = (me + 1) % n, left = (me + n - 1) % n;
+  u64* A = buf;
+  u64* B = A + (size_t)n * cnt;
+  u64* R = B + (size_t)n * cnt;
+  u64* F = R + cnt;
+  int bad = 0;
+  const int root = 1 % n;
+  // broadcast
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) A[i] = (u64)me * 131 + i;
+  __syncthreads();
+  if (b200shmem::broadcastmem_block(d, B, A, cnt * 8, root) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x)
+    if (B[i] != (u64)root * 131 + i) bad++;
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;  // everyone has checked B before it is written again
+  // fcollect
+  if (b200shmem::fcollectmem_block(d, B, A, cnt * 8) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < (size_t)n * cnt; i += blockDim.x)
+    if (B[i] != (u64)(i / cnt) * 131 + i % cnt) bad++;
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  // alltoall
+  for (size_t i = threadIdx.x; i < (size_t)n * cnt; i += blockDim.x) A[i] = (u64)me * 100000 + (u64)(i / cnt) * 1000 + i % cnt;
+  __syncthreads();
+  if (b200shmem::alltoallmem_block(d, B, A, cnt * 8) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < (size_t)n * cnt; i += blockDim.x)
+    if (B[i] != (u64)(i / cnt) * 100000 + (u64)me * 1000 + i % cnt) bad++;
+  // reductions: sum in place, max out of place
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) R[i] = (u64)me + i;
+  __syncthreads();
+  if (b200shmem::sum_reduce_block(d, R, R, cnt) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x)
+    if (R[i] != (u64)n * i + (u64)n * (n - 1) / 2) bad++;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) A[i] = (u64)((me * 7 + i) % 13);
+  __syncthreads();
+  if (b200shmem::max_reduce_block(d, B, A, cnt) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) {
+    u64 m = 0;
+    for (int pe = 0; pe < n; pe++) m = max(m, (u64)((pe * 7 + i) % 13));
+    if (B[i] != m) bad++;
+  }
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  // strided put to the right neighbour (every second word of A there), then a flag word it waits on
+  if (threadIdx.x == 0) {
+    for (size_t i = 0; i < cnt; i++) R[i] = (u64)me * 17 + i + 1;
+    b200shmem::iput(d, A, R, 2, 1, cnt / 2, right);
+    b200shmem::fence();
+    b200shmem::p(d, F + 1, (u64)(me + 1), right);
+    if (b200shmem::wait_until(d, F + 1, B200SHMEM_CMP_EQ, (u64)(left + 1)) != B200SHMEM_OK) bad++;
+    if (!b200shmem::test(F + 1, B200SHMEM_CMP_GE, (u64)1) || b200shmem::test(F + 2, B200SHMEM_CMP_NE, (u64)0)) bad++;
+    int which = -1;
+    if (b200shmem::wait_until_any(d, F, 4, B200SHMEM_CMP_NE, (u64)0, &which) != B200SHMEM_OK || which != 1) bad++;
+    for (size_t i = 0; i < cnt / 2; i++)
+      if (A[2 * i] != (u64)left * 17 + i + 1) bad++;
+    if (b200shmem::my_pe(d) != me || b200shmem::n_pes(d) != n) bad++;
+  }
+  if (b200shmem::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  if (bad) atomicAdd(errors, bad);
+}
+__global__ void kSelftestColl(b200shmem_dev_t d, unsigned long long* buf, size_t cnt, int* errors) { collBody(d, buf, cnt, errors); }
+
 // Several PEs on one GPU: block r of ONE cooperative launch is PE r (kernels of PEs that wait on one another must never
 // be separate launches on one GPU). The bodies are the ones above, each on its PE's own device context.
 struct EmuShmemPack {
@@ -125,6 +188,8 @@ struct EmuShmemPack {
   unsigned long long* src[B200SHMEM_MAX_PES];
   unsigned long long* sig[B200SHMEM_MAX_PES];
   unsigned long long* words[B200SHMEM_MAX_PES];
+  unsigned long long* coll[B200SHMEM_MAX_PES];
+  size_t collCount;
   size_t count;
   int rounds, iters;
   int* errors;
@@ -136,6 +201,10 @@ __global__ void kEmuRing(const EmuShmemPack* p) {
 __global__ void kEmuAtomics(const EmuShmemPack* p) {
   const int r = blockIdx.x;
   atomicsBody(p->d[r], p->words[r], p->iters, p->errors);
+}
+__global__ void kEmuColl(const EmuShmemPack* p) {
+  const int r = blockIdx.x;
+  collBody(p->d[r], p->coll[r], p->collCount, p->errors);
 }
 
 struct DevGuard {
@@ -364,6 +433,30 @@ ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStre
   return ncclSuccess;
 }
 
+// Words of the symmetric buffer the collectives self-test needs for `count` elements per block.
+static size_t collWords(int npes, size_t count) { return 2 * (size_t)npes * count + count + 8; }
+
+ncclResult_t b200shmem_selftest_collectives(b200shmem_ctx_t ctx, size_t count, cudaStream_t stream, int* errors) {
+  if (!ctx || !errors || count < 2) BFAIL(ncclInvalidArgument, "b200shmem_selftest_collectives: bad arguments");
+  DevGuard g(ctx->comm->cudaDev);
+  const size_t bytes = collWords(ctx->dev.npes, count) * 8;
+  unsigned long long* buf = (unsigned long long*)b200shmem_malloc(ctx, bytes);
+  if (!buf) BFAIL(ncclSystemError, "b200shmem_selftest_collectives: symmetric heap too small");
+  int* derr = nullptr;
+  BCUDA(cudaMalloc(&derr, sizeof(int)));
+  BCUDA(cudaMemsetAsync(derr, 0, sizeof(int), stream));
+  BCUDA(cudaMemsetAsync(buf, 0, bytes, stream));
+  BCHECK(b200shmem_barrier_all_on_stream(ctx, stream));  // the flag words are zero everywhere before anyone writes one
+  kSelftestColl<<<1, 256, 0, stream>>>(ctx->dev, buf, count, derr);
+  BCUDA(cudaGetLastError());
+  BCUDA(cudaMemcpyAsync(errors, derr, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  BCUDA(cudaStreamSynchronize(stream));
+  cudaFree(derr);
+  BCHECK(ctx->comm->boot.barrier());
+  b200shmem_free(ctx, buf);
+  return ncclSuccess;
+}
+
 // ---- copy-engine transfers -----------------------------------------------------------------------------------------
 // The reference runtime moves bulk peer data with DMA engines and may gang several engines on one copy
 // (rocr-runtime core/runtime/amd_gpu_agent.cpp:1013-1108); the count it gangs comes from the link (amd_topology.cpp:442-484).
@@ -467,7 +560,8 @@ ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int 
   *errors = 0;
   std::vector<b200shmem_ctx_t> ctx(n, nullptr);
   std::vector<ncclResult_t> rs(n, ncclSuccess);
-  const size_t heap = 2 * count * 8 + (4u << 20);
+  const size_t collCount = 96;
+  const size_t heap = 2 * count * 8 + collWords(n, collCount) * 8 + (4u << 20);
   auto onEveryPe = [&](auto fn) {  // the heap calls are collective over the communicator: one thread per PE
     std::vector<std::thread> th;
     for (int r = 0; r < n; r++)
@@ -486,6 +580,7 @@ ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int 
   pack.count = count;
   pack.rounds = rounds;
   pack.iters = iters;
+  pack.collCount = collCount;
   int* derr = nullptr;
   BCUDA(cudaMalloc(&derr, sizeof(int)));
   BCUDA(cudaMemset(derr, 0, sizeof(int)));
@@ -495,7 +590,9 @@ ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int 
     pack.data[r] = (unsigned long long*)b200shmem_malloc(ctx[r], 2 * count * 8);
     pack.sig[r] = (unsigned long long*)b200shmem_malloc(ctx[r], 256);
     pack.words[r] = (unsigned long long*)b200shmem_malloc(ctx[r], 256);
-    if (!pack.data[r] || !pack.sig[r] || !pack.words[r]) BFAIL(ncclSystemError, "b200shmem_emu_selftest: symmetric heap too small");
+    pack.coll[r] = (unsigned long long*)b200shmem_malloc(ctx[r], collWords(n, collCount) * 8);
+    if (pack.coll[r]) BCUDA(cudaMemset(pack.coll[r], 0, collWords(n, collCount) * 8));
+    if (!pack.data[r] || !pack.sig[r] || !pack.words[r] || !pack.coll[r]) BFAIL(ncclSystemError, "b200shmem_emu_selftest: symmetric heap too small");
     BCUDA(cudaMalloc(&pack.src[r], count * 8));
     BCUDA(cudaMemset(pack.sig[r], 0, 256));
     BCUDA(cudaMemset(pack.words[r], 0, 256));
@@ -508,6 +605,8 @@ ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int 
   cudaError_t e = cudaLaunchCooperativeKernel((const void*)kEmuRing, dim3(n), dim3(256), args, 0, 0);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaLaunchCooperativeKernel((const void*)kEmuAtomics, dim3(n), dim3(32), args, 0, 0);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaLaunchCooperativeKernel((const void*)kEmuColl, dim3(n), dim3(256), args, 0, 0);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200shmem_emu_selftest: %s", cudaGetErrorString(e));
   BCUDA(cudaMemcpy(errors, derr, sizeof(int), cudaMemcpyDeviceToHost));

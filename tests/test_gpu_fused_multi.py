@@ -57,6 +57,12 @@ def test_shmem_put_get_signal_atomics(nproc):
     _launch(nproc, 29840 + nproc, "shmem_worker.py")
 
 
+@pytest.mark.xfail(reason="the device-side collectives have not run on hardware yet", strict=False)
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_shmem_device_collectives(nproc):
+    _launch(nproc, 29950 + nproc, "shmem_worker.py", "--collectives")
+
+
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_fsdp_matches_single_rank(nproc):
     _launch(nproc, 29850 + nproc, "fsdp_worker.py")

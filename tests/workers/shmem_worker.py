@@ -19,6 +19,7 @@ def main():
     lib.b200shmem_finalize.argtypes = [vp]
     lib.b200shmem_selftest_ring.argtypes = [vp, ctypes.c_size_t, ctypes.c_int, vp, ctypes.POINTER(ctypes.c_int)]
     lib.b200shmem_selftest_atomics.argtypes = [vp, ctypes.c_int, vp, ctypes.POINTER(ctypes.c_int)]
+    lib.b200shmem_selftest_collectives.argtypes = [vp, ctypes.c_size_t, vp, ctypes.POINTER(ctypes.c_int)]
     lib.b200shmem_take_status.argtypes = [vp]
     lib.b200shmem_malloc.argtypes = [vp, ctypes.c_size_t]
     lib.b200shmem_malloc.restype = vp
@@ -37,6 +38,10 @@ def main():
     _lib.check(lib.b200shmem_selftest_atomics(ctx, 101, s, ctypes.byref(errs)), "selftest_atomics")
     if errs.value != 0:
         bad.append(("atomics", errs.value))
+    if "--collectives" in sys.argv:   # block-scope collectives, wait_until / test, strided put of the device API
+        _lib.check(lib.b200shmem_selftest_collectives(ctx, 1000, s, ctypes.byref(errs)), "selftest_collectives")
+        if errs.value != 0:
+            bad.append(("collectives", errs.value))
     # host-initiated, stream-ordered put with signal to the right neighbour
     n, rank = comm.nranks, comm.rank
     count = 1 << 16
