@@ -27,6 +27,7 @@ RULES = [
     ("rocm_systems_b200/csrc/core/*", ["tests/test_api_cpu.py", "tests/test_bootstrap.py", "tests/test_planner_cpu.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
     ("rocm_systems_b200/csrc/coll/verifiable*", ["tests/test_verifiable_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/coll/*", ["tests/test_planner_cpu.py", "tests/test_protocol_interleavings_cpu.py", "tests/test_protocol_model_cpu.py", "tests/test_staged_emulation_cpu.py"], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_emulated_ranks_gpu.py"], True),
+    ("rocm_systems_b200/csrc/include/b200coll/shmem_device.cuh", ["tests/test_shmem_collectives_model_cpu.py", "tests/test_examples_build_cpu.py"], ["tests/test_gpu_fused_multi.py"], True),
     ("rocm_systems_b200/csrc/shmem/*", ["tests/test_api_cpu.py"], ["tests/test_gpu_fused_multi.py", "tests/test_zz_shmem_dma_gpu.py"], True),
     ("rocm_systems_b200/csrc/fused/fsdp_kernels.cu", ["tests/test_fsdp_rscast_emulation_cpu.py", "tests/test_protocol_model_cpu.py"], ["tests/test_gpu_fused_multi.py"], True),
     ("rocm_systems_b200/csrc/fused/gemm_fp8*", ["tests/test_fp8_reference_cpu.py"], [], True),
