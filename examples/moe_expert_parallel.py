@@ -23,9 +23,10 @@ def main() -> int:
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--ffn", type=int, default=1024)
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per rank")
+    ap.add_argument("--fp8-experts", action="store_true", help="run the gate/up expert GEMM on the fp8 rows as they arrived (block-quantised weights)")
     a = ap.parse_args()
     comm = init_from_env()
-    moe = MoELayer(comm, a.experts // comm.nranks, a.hidden, a.ffn, a.topk, a.tokens, seed=5)
+    moe = MoELayer(comm, a.experts // comm.nranks, a.hidden, a.ffn, a.topk, a.tokens, seed=5, fp8_experts=a.fp8_experts)
     x = torch.randn(a.tokens, a.hidden, device=comm.device).to(torch.bfloat16)
     logits = torch.randn(a.tokens, moe.E, device=comm.device)
     want = moe.reference_forward(x, logits).float()

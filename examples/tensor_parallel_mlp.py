@@ -16,7 +16,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 from rocm_systems_b200.ops import train_ops  # noqa: E402
-from rocm_systems_b200.parallel.tp import TensorParallelAttention, TensorParallelMLP  # noqa: E402
+from rocm_systems_b200.parallel.tp import TensorParallelAttention, TensorParallelMLP, TensorParallelMLPFp8  # noqa: E402
 
 
 def main() -> int:
@@ -24,12 +24,14 @@ def main() -> int:
     ap.add_argument("--rows", type=int, default=1024, help="tokens per rank")
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--ffn", type=int, default=28672, help="whole intermediate size")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 operands: half the all-gather bytes, fp8 tensor-core rate; "
+                    "compared with the PyTorch statement of the same quantised arithmetic")
     ap.add_argument("--attention", action="store_true", help="also run the tensor-parallel attention half of the layer")
     ap.add_argument("--heads", type=int, default=64)
     ap.add_argument("--kv-heads", type=int, default=8)
     a = ap.parse_args()
     comm = init_from_env()
-    mlp = TensorParallelMLP(comm, a.rows, a.hidden, a.ffn // comm.nranks, comm.device, seed=1)
+    mlp = (TensorParallelMLPFp8 if a.fp8 else TensorParallelMLP)(comm, a.rows, a.hidden, a.ffn // comm.nranks, comm.device, seed=1)
     x = (torch.randn(a.rows, a.hidden, device=comm.device) * 0.5).to(torch.bfloat16)
     want = mlp.reference_forward(x).float()
     got = mlp.forward(x).float()
@@ -49,7 +51,7 @@ def main() -> int:
     ms = start.elapsed_time(stop) / 10
     flops = 2.0 * a.rows * comm.nranks * a.hidden * (3 * a.ffn // comm.nranks)
     if comm.rank == 0:
-        print(f"TP={comm.nranks} tokens {a.rows * comm.nranks} hidden {a.hidden} ffn {a.ffn}: max |error| {err:.3e} (output scale {scale:.3e}), "
+        print(f"{'fp8 ' if a.fp8 else ''}TP={comm.nranks} tokens {a.rows * comm.nranks} hidden {a.hidden} ffn {a.ffn}: max |error| {err:.3e} (output scale {scale:.3e}), "
               f"{ms:.3f} ms per layer, {flops / ms / 1e9:.0f} TFLOP/s per GPU, kernel status {code}", flush=True)
     ok = code == 0 and err <= 3e-2 * scale + 1e-3
     mlp.free()
