@@ -16,7 +16,16 @@ synchronisation and timed with CUDA events (max over ranks):
                in pinned host memory (copied host->device inside the step) and the loss read
                back to the host every step.
 
-Rank 0 prints one JSON line. ``--impl reference`` prints why the reference arm cannot run.
+Rank 0 prints one JSON line. On two or more GPUs the line also carries the collective stack's own headline, taken after
+the timed regions: stock-NCCL time / this library's time per collective over a ladder of message sizes (``headline.
+collectives_vs_nccl``) and, on 8 GPUs, the fused tensor-parallel and expert-parallel paths as fractions of their
+rooflines (``headline.tp_roofline``, ``headline.ep_roofline``).
+
+``--impl reference``: the reference project has no collective library that can be built for this GPU, so this arm runs
+what its benchmark notes prescribe as the fallback, stock NCCL + cuBLAS on the same box: the same training job on
+``torch.distributed.fsdp.fully_shard`` over the ``nccl`` backend (baseline/stock_torch_fsdp.py; nothing of this package
+is imported there). ``vs_baseline`` of the normal line is ``value`` divided by that arm's number for the same N as
+recorded in BASELINE_TOKENS_PER_S below.
 """
 from __future__ import annotations
 
@@ -31,12 +40,8 @@ import threading
 METRIC = "llama3_8b_fsdp_train_tokens_per_sec"
 
 
-def reference_arm() -> None:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "reference snapshot has no RCCL/rocSHMEM sources and no Python package (pip: 'neither setup.py nor "
-                       "pyproject.toml found'); its collective code is HIP/AMD-only and cannot build for B200",
-    }))
+# Stock torch FSDP on NCCL (``--impl reference``), tokens/s per N as measured on this pool's B200 boxes; None: not measured yet.
+BASELINE_TOKENS_PER_S = {1: None, 2: None, 4: None, 8: None}
 
 
 class ClockSampler:
@@ -106,6 +111,36 @@ def gpu_health(index: int):
         return {"unavailable": str(e)[:120]}
 
 
+def take_headline(comm, trainer, dev, world: int) -> dict:
+    """busbw against stock NCCL per collective, and on 8 GPUs the fused TP / EP paths against their rooflines. Runs after the
+    timed regions, with the trainer's memory released first; a failure is recorded, it never fails the benchmark."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    out = {}
+    try:
+        trainer.engine = None
+        trainer.embed = trainer.layers = trainer.head = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        from rocm_systems_b200.bench import headline as hl
+
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+        out["collectives_vs_nccl"] = hl.collectives_vs_nccl(comm)
+        if world == 8:
+            out["tp_roofline"] = hl.tp_roofline(comm)
+            out["ep_roofline"] = hl.ep_roofline(comm)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        out["error"] = f"{type(e).__name__}: {e}"[:300]
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -118,13 +153,18 @@ def main() -> None:
     ap.add_argument("--sym-shards", action="store_true", help="keep the bf16 parameter shards in symmetric memory (zero-copy all-gather); experimental")
     ap.add_argument("--collectives", default="b200coll", choices=["b200coll", "nccl"],
                     help="nccl: the same trainer with stock NCCL collectives (control run; the metric name gets a _nccl_collectives suffix)")
+    ap.add_argument("--no-overlap", action="store_true", help="run communication and optimizer on the compute stream (a sequential schedule, for checking)")
+    ap.add_argument("--no-headline", action="store_true", help="skip the collective / fused-path summaries that follow the timed regions on 2+ GPUs")
+    ap.add_argument("--reference-checkpointing", action="store_true", help="--impl reference: per-layer activation checkpointing from the start")
     args = ap.parse_args()
-    if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
-            reference_arm()
-        return
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from baseline.stock_torch_fsdp import run as reference_run
+
+        reference_run(args, ClockSampler)
+        return
 
     import torch
 
@@ -153,7 +193,7 @@ def main() -> None:
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny(512)
     if args.seq:
         cfg.seq_len = args.seq
-    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=args.sym_shards)
+    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=args.sym_shards, overlap=not args.no_overlap)
     S, B = cfg.seq_len, 1
     nbatches = 4
     g = torch.Generator().manual_seed(1234 + rank)
@@ -198,20 +238,30 @@ def main() -> None:
 
     tokens_per_step = world * B * S
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    base = BASELINE_TOKENS_PER_S.get(world) if args.model == "llama3_8b" and not args.seq else None
+    peak_gb = trainer.memory_summary()["peak_gb"]
+    headline = None
+    if world > 1 and not args.no_headline and args.collectives == "b200coll":
+        headline = take_headline(comm, trainer, dev, world)
     out = {
         "metric": METRIC + ("_nccl_collectives" if args.collectives == "nccl" else ""), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": (value / base) if base else None, "dtype": "bf16",
         "data": "synthetic tokens uniform over the vocabulary (seeded), random-init weights N(0,0.02)",
         "config": {"model": "llama3-8b" if args.model == "llama3_8b" else "tiny", "global_batch": world * B, "seq_len": S,
                    "parallelism": f"fsdp{world}", "optimizer": "adamw fp32 master", "layers": cfg.layers, "hidden": cfg.hidden,
                    "l2": "working set per step (GBs of weights and activations) is far larger than the 126 MB L2; no flush needed"},
         "clocks": clocks, "gpu_launches": launches,
         "model_tflops_per_gpu": cfg.flops_per_token() * B * S / (ms_dev / args.steps / 1e3) / 1e12,
-        "peak_mem_gb": trainer.memory_summary()["peak_gb"],
+        "peak_mem_gb": peak_gb,
     }
+    if base:
+        out["baseline"] = {"what": "stock torch fully_shard on the nccl backend, same job, same pool (bench.py --impl reference)", "tokens_per_s": base}
+    if headline is not None:
+        out["headline"] = headline
     if ms_e2e is not None:
         out["e2e"] = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8,
-                      "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None}
+                      "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1] if losses else None,
+                      "losses": [round(float(x), 4) for x in losses]}
     if rank == 0:
         out["health"] = gpu_health(local)
         print(json.dumps(out))

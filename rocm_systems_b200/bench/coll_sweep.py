@@ -56,6 +56,60 @@ def time_op(fn, warmup: int, iters: int) -> float:
     return float(t.item())
 
 
+def make_ops(comm, coll: str, s: torch.Tensor, r: torch.Tensor, per: int, in_place: bool = False):
+    """The call of this library and the stock NCCL call (through ``torch.distributed``) for one collective on the same
+    buffers: ``s`` / ``r`` hold ``count`` elements, ``per`` is the per-rank part of the scattering / gathering ones.
+    ``in_place`` uses the in-place convention of the C API (all_gather: the rank's part inside the receive buffer;
+    reduce_scatter: the result inside the send buffer; all_reduce and broadcast: one buffer)."""
+    rank = comm.rank
+    if coll == "all_reduce":
+        if in_place:
+            return (lambda: comm.all_reduce(s, s)), (lambda: dist.all_reduce(s))
+        return (lambda: comm.all_reduce(s, r)), (lambda: dist.all_reduce(s))
+    if coll == "reduce_scatter":
+        out = s[rank * per:(rank + 1) * per] if in_place else r[:per]
+        return (lambda: comm.reduce_scatter(s, out)), (lambda: dist.reduce_scatter_tensor(out, s))
+    if coll == "all_gather":
+        src = r[rank * per:(rank + 1) * per] if in_place else s[:per]
+        return (lambda: comm.all_gather(src, r)), (lambda: dist.all_gather_into_tensor(r, src))
+    if coll == "broadcast":
+        if in_place:
+            return (lambda: comm.broadcast(s, s, root=0)), (lambda: dist.broadcast(s, 0))
+        return (lambda: comm.broadcast(s, r, root=0)), (lambda: dist.broadcast(s, 0))
+    if coll == "alltoall":
+        return (lambda: comm.all_to_all(s, r)), (lambda: dist.all_to_all_single(r, s))
+    raise SystemExit(f"unknown collective {coll}")
+
+
+def sweep(comm, colls, sizes, dt: torch.dtype, send_all: torch.Tensor, recv_all: torch.Tensor, warmup: int, iters: int, nccl: bool = True,
+          in_place: bool = False, on_row=None) -> list:
+    """Time every (collective, size) on this library and, when ``nccl``, on stock NCCL; rccl-tests columns per row."""
+    n = comm.nranks
+    es = torch.empty((), dtype=dt).element_size()
+    rows = []
+    for coll in colls:
+        for size in sizes:
+            count = max(size // es, 1)
+            per = count
+            if coll in ("reduce_scatter", "all_gather", "alltoall"):
+                per = max(count // n, 1)
+                count = per * n
+            s, r = send_all[:count], recv_all[:count]
+            ours, ref = make_ops(comm, coll, s, r, per, in_place)
+            it = iters if size <= (64 << 20) else max(iters // 4, 3)
+            t_ours = time_op(ours, warmup, it)
+            t_ref = time_op(ref, warmup, it) if nccl else float("nan")
+            nbytes = count * es
+            f = busbw_factor(coll, n)
+            row = {"coll": coll, "bytes": nbytes, "count": count, "in_place": in_place, "ours_us": t_ours, "nccl_us": t_ref,
+                   "ours_algbw": nbytes / t_ours / 1e3, "ours_busbw": nbytes / t_ours / 1e3 * f,
+                   "nccl_algbw": nbytes / t_ref / 1e3, "nccl_busbw": nbytes / t_ref / 1e3 * f}
+            rows.append(row)
+            if on_row:
+                on_row(row)
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("-b", "--minbytes", default="8")
@@ -63,9 +117,10 @@ def main() -> None:
     ap.add_argument("-f", "--stepfactor", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--dtype", default="float")
+    ap.add_argument("--dtype", default="float", help="float, bfloat16 or half; several separated by commas")
     ap.add_argument("--colls", default="all_reduce,reduce_scatter,all_gather,broadcast,alltoall")
     ap.add_argument("--symmetric", type=int, default=0, help="1: buffers in symmetric (registered) memory")
+    ap.add_argument("--placement", default="out", help="out, in or both: out-of-place and / or in-place buffers")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
@@ -73,63 +128,38 @@ def main() -> None:
     comm = init_from_env()
     rank, n = comm.rank, comm.nranks
     dist.init_process_group("nccl" if not args.no_nccl else "gloo", device_id=comm.device if not args.no_nccl else None)
-    dt = {"float": torch.float32, "bfloat16": torch.bfloat16, "half": torch.float16}[args.dtype]
-    es = torch.empty((), dtype=dt).element_size()
     lo, hi = parse_size(args.minbytes), parse_size(args.maxbytes)
-    maxel = hi // es
-    if args.symmetric:
-        sym = comm.sym_alloc(2 * hi + 4096)
-        send_all = sym.tensor((maxel,), dt)
-        recv_all = sym.tensor((maxel,), dt, offset_bytes=hi)
-    else:
-        send_all = torch.empty(maxel, dtype=dt, device="cuda")
-        recv_all = torch.empty(maxel, dtype=dt, device="cuda")
-    send_all.normal_()
-    rows = []
-    if rank == 0:
-        print(f"# nranks {n} dtype {args.dtype} nvls {comm.nvls} symmetric {args.symmetric} warmup {args.warmup} iters {args.iters}")
-        print(f"# {'coll':<15}{'size(B)':>12}{'count':>12}{'ours us':>11}{'algbw':>9}{'busbw':>9}{'nccl us':>11}{'algbw':>9}{'busbw':>9}{'ratio':>7}")
-    size = lo
     sizes = []
+    size = lo
     while size <= hi:
         sizes.append(size)
         size *= args.stepfactor
-    for coll in args.colls.split(","):
-        for size in sizes:
-            count = max(size // es, 1)
-            if coll in ("reduce_scatter", "all_gather", "alltoall"):
-                per = max(count // n, 1)
-                count = per * n
-            s, r = send_all[:count], recv_all[:count]
-            if coll == "all_reduce":
-                ours = lambda: comm.all_reduce(s, r)
-                ref = lambda: dist.all_reduce(s)
-            elif coll == "reduce_scatter":
-                ours = lambda: comm.reduce_scatter(s, r[:per])
-                ref = lambda: dist.reduce_scatter_tensor(r[:per], s)
-            elif coll == "all_gather":
-                ours = lambda: comm.all_gather(s[:per], r)
-                ref = lambda: dist.all_gather_into_tensor(r, s[:per])
-            elif coll == "broadcast":
-                ours = lambda: comm.broadcast(s, s, root=0)
-                ref = lambda: dist.broadcast(s, 0)
-            elif coll == "alltoall":
-                ours = lambda: comm.all_to_all(s, r)
-                ref = lambda: dist.all_to_all_single(r, s)
-            else:
-                raise SystemExit(f"unknown collective {coll}")
-            iters = args.iters if size <= (64 << 20) else max(args.iters // 4, 3)
-            t_ours = time_op(ours, args.warmup, iters)
-            t_ref = time_op(ref, args.warmup, iters) if not args.no_nccl else float("nan")
-            nbytes = count * es
-            f = busbw_factor(coll, n)
-            row = {"coll": coll, "bytes": nbytes, "count": count, "ours_us": t_ours, "nccl_us": t_ref,
-                   "ours_algbw": nbytes / t_ours / 1e3, "ours_busbw": nbytes / t_ours / 1e3 * f,
-                   "nccl_algbw": nbytes / t_ref / 1e3, "nccl_busbw": nbytes / t_ref / 1e3 * f}
-            rows.append(row)
+    if args.symmetric:
+        sym = comm.sym_alloc(2 * hi + 4096)
+        send_raw = sym.tensor((hi,), torch.uint8)
+        recv_raw = sym.tensor((hi,), torch.uint8, offset_bytes=hi)
+    else:
+        send_raw = torch.empty(hi, dtype=torch.uint8, device="cuda")
+        recv_raw = torch.empty(hi, dtype=torch.uint8, device="cuda")
+    rows = []
+    placements = {"out": [False], "in": [True], "both": [False, True]}[args.placement]
+    for dname in args.dtype.split(","):
+        dt = {"float": torch.float32, "bfloat16": torch.bfloat16, "half": torch.float16}[dname]
+        send_all, recv_all = send_raw.view(dt), recv_raw.view(dt)
+        send_all.normal_()
+        for in_place in placements:
             if rank == 0:
-                print(f"  {coll:<15}{nbytes:>12}{count:>12}{t_ours:>11.2f}{row['ours_algbw']:>9.2f}{row['ours_busbw']:>9.2f}"
-                      f"{t_ref:>11.2f}{row['nccl_algbw']:>9.2f}{row['nccl_busbw']:>9.2f}{t_ref / t_ours:>7.2f}", flush=True)
+                print(f"# nranks {n} dtype {dname} nvls {comm.nvls} symmetric {args.symmetric} in_place {int(in_place)} warmup {args.warmup} iters {args.iters}")
+                print(f"# {'coll':<15}{'size(B)':>12}{'count':>12}{'ours us':>11}{'algbw':>9}{'busbw':>9}{'nccl us':>11}{'algbw':>9}{'busbw':>9}{'ratio':>7}")
+
+            def show(row):
+                if rank == 0:
+                    print(f"  {row['coll']:<15}{row['bytes']:>12}{row['count']:>12}{row['ours_us']:>11.2f}{row['ours_algbw']:>9.2f}{row['ours_busbw']:>9.2f}"
+                          f"{row['nccl_us']:>11.2f}{row['nccl_algbw']:>9.2f}{row['nccl_busbw']:>9.2f}{row['nccl_us'] / row['ours_us']:>7.2f}", flush=True)
+
+            for row in sweep(comm, args.colls.split(","), sizes, dt, send_all, recv_all, args.warmup, args.iters, not args.no_nccl, in_place, show):
+                row["dtype"] = dname
+                rows.append(row)
     err = comm.async_error()
     if rank == 0 and args.out:
         Path(args.out).parent.mkdir(parents=True, exist_ok=True)

@@ -253,6 +253,17 @@ class Communicator:
         _lib.check(self._lib.ncclRedOpCreatePreMulSum(ctypes.byref(op), buf, nccl_dtype(dtype), 1, self._h), "ncclRedOpCreatePreMulSum")
         return op.value
 
+    def premul_sum_device(self, scalar: torch.Tensor) -> int:
+        """Create a PreMulSum operator whose scalar lives in device memory (a one-element tensor of the data type). The
+        reducing kernel reads it when it runs, in stream order: the value may be produced by earlier work on the same
+        stream, the call does not wait for the stream and can be captured in a graph. Keep the tensor alive until the
+        operator is destroyed."""
+        assert scalar.is_cuda and scalar.numel() == 1
+        op = ctypes.c_int()
+        _lib.check(self._lib.ncclRedOpCreatePreMulSum(ctypes.byref(op), ctypes.c_void_p(scalar.data_ptr()), nccl_dtype(scalar.dtype), 0, self._h),
+                   "ncclRedOpCreatePreMulSum")
+        return op.value
+
     def redop_destroy(self, op: int) -> None:
         _lib.check(self._lib.ncclRedOpDestroy(op, self._h), "ncclRedOpDestroy")
 

@@ -76,6 +76,7 @@ struct CollArgs {
   int scaleMode;
   int stageHalf;         // staging half of the first chunk; alternates per chunk
   unsigned long long scalarBits;  // PreMulSum scalar, in the element type, zero-extended
+  const void* scalarPtr;          // PreMulSum scalar in device memory (read by the kernel when it runs); null: scalarBits
   // Zero-copy windows: when both are set the buffers are symmetric and staging is skipped.
   char* sendPeer[kMaxRanks];
   char* recvPeer[kMaxRanks];
@@ -91,6 +92,7 @@ struct LLArgs {
   size_t count;
   int scaleMode;
   unsigned long long scalarBits;
+  const void* scalarPtr;  // see CollArgs
   uint32_t seq;          // flag value of this operation (never 0)
 };
 

@@ -31,10 +31,12 @@ struct ResolvedOp {
   int base;          // ncclSum/Prod/Max/Min
   int scaleMode;
   unsigned long long bits;
+  const void* devPtr = nullptr;  // PreMulSum scalar that lives in device memory: the kernel reads it
 };
 
-ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, cudaStream_t stream, ResolvedOp* out) {
+ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, ResolvedOp* out) {
   out->bits = 0;
+  out->devPtr = nullptr;
   out->scaleMode = SCALE_NONE;
   if (op >= 0 && op < ncclNumOps) {
     if (op == ncclAvg) {
@@ -55,14 +57,9 @@ ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, cudaStream_t stream, 
   if (pm.dtype != dt) BFAIL(ncclInvalidArgument, "PreMulSum operator was created for %s, used with %s", dtypeName(pm.dtype), dtypeName(dt));
   out->base = ncclSum;
   out->scaleMode = SCALE_PRE_MUL;
-  if (pm.devPtr) {
-    unsigned long long bits = 0;
-    BCUDA(cudaMemcpyAsync(&bits, pm.devPtr, dtypeSize(dt), cudaMemcpyDeviceToHost, stream));
-    BCUDA(cudaStreamSynchronize(stream));
-    out->bits = bits;
-  } else {
-    out->bits = pm.bits;
-  }
+  // A scalar in device memory is read by the kernel, in stream order: no host wait, and the call can be captured.
+  out->devPtr = pm.devPtr;
+  out->bits = pm.bits;
   return ncclSuccess;
 }
 
@@ -140,6 +137,7 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   args->root = r.root;
   args->scaleMode = rop.scaleMode;
   args->scalarBits = rop.bits;
+  args->scalarPtr = rop.devPtr;
 
   // Zero-copy windows: buffers inside symmetric allocations (b200collSymAlloc, or ncclMemAlloc +
   // ncclCommRegister) are read and written in place on every rank.
@@ -274,7 +272,7 @@ ncclResult_t enqueueColl(const CollReq& r) {
 
   DeviceGuard guard(c->cudaDev);
   ResolvedOp rop{ncclSum, SCALE_NONE, 0};
-  if (reducing) BCHECK(resolveOp(c, r.op, r.dt, r.stream, &rop));
+  if (reducing) BCHECK(resolveOp(c, r.op, r.dt, &rop));
 
   Tracer* tr = c->tracer;
   TraceStamp* stamp = tr ? tr->begin(r.apiId, r.dt, r.count, traceBytes(r)) : nullptr;
@@ -315,6 +313,7 @@ ncclResult_t enqueueColl(const CollReq& r) {
     la.count = r.count;
     la.scaleMode = rop.scaleMode;
     la.scalarBits = rop.bits;
+    la.scalarPtr = rop.devPtr;
     if (++c->llSeq == 0) c->llSeq = 2;  // 0 is the "never written" value; keep the parity sequence
     la.seq = c->llSeq;
     e = launchLLAllReduce(r.dt, rop.base, plan.ctas, r.stream, dc, la);

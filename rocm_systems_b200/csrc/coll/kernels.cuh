@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_consta
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gn = (size_t)gridDim.x * blockDim.x;
 
-  const Acc scalar = scalarFromBits<T>(a.scalarBits);
+  const Acc scalar = scalarOf<T>(a.scalarBits, a.scalarPtr);
   const bool pre = a.scaleMode == SCALE_PRE_MUL;
   for (size_t i = gtid; i < units; i += gn) {
     T e[EPU];
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
   const size_t total = a.count * ES;  // AllReduce/Reduce: the message; ReduceScatter: one rank's slice
   const size_t fullCap = isRS ? (c.stageBytes / n) & ~(size_t)15 : c.stageBytes;
   const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : ((a.chunkBytes && a.chunkBytes < fullCap) ? a.chunkBytes : fullCap);
-  const Acc scalar = scalarFromBits<T>(a.scalarBits);
+  const Acc scalar = scalarOf<T>(a.scalarBits, a.scalarPtr);
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
 

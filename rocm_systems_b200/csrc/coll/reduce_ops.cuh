@@ -88,6 +88,14 @@ __device__ __forceinline__ typename ElemTraits<T>::Acc scalarFromBits(unsigned l
   return ElemTraits<T>::up(u.t);
 }
 
+// The PreMulSum scalar of a call: an immediate captured when the operator was made, or a device word read now, by the
+// kernel, so that the host neither waits for the stream nor reads the value earlier than stream order says.
+template <typename T>
+__device__ __forceinline__ typename ElemTraits<T>::Acc scalarOf(unsigned long long bits, const void* devPtr) {
+  if (devPtr != nullptr) return ElemTraits<T>::up(*(const volatile T*)devPtr);
+  return scalarFromBits<T>(bits);
+}
+
 template <typename T>
 __device__ __forceinline__ typename ElemTraits<T>::Acc postDiv(typename ElemTraits<T>::Acc a, int n) {
   using Acc = typename ElemTraits<T>::Acc;

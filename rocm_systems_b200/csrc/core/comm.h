@@ -39,7 +39,7 @@ struct PreMulOp {
   bool used = false;
   ncclDataType_t dtype;
   unsigned long long bits;        // host-immediate scalar, in the element type
-  const void* devPtr = nullptr;   // device-resident scalar (read at enqueue with a stream copy)
+  const void* devPtr = nullptr;   // device-resident scalar: handed to the kernel, which reads it in stream order
 };
 
 struct TuneEntry {       // one row of the size -> algorithm table

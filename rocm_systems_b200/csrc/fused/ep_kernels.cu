@@ -65,6 +65,9 @@ __host__ inline EpLayout makeLayout(int nranks, int expertsLocal, int cap, int h
 // ---- routing ------------------------------------------------------------------------------------------
 // logits [T, E] fp32; E <= 1024, multiple of 32. Writes expert ids (int32) and gate weights (fp32,
 // softmax over the selected logits) for the top `k`, largest first; ties go to the lower expert id.
+// A NaN logit counts as -inf and +inf as the largest finite value, so every id written lies in [0, E)
+// and every weight is finite: a row with fewer than k selectable values (all NaN, mostly -inf) fills up
+// with the lowest expert ids not yet taken, and a row whose selected logits are all -inf gets weights 1/k.
 __global__ void __launch_bounds__(256) epRoute(const float* __restrict__ logits, int* __restrict__ topIdx, float* __restrict__ topW, int T, int E, int k) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T) return;
@@ -72,15 +75,20 @@ __global__ void __launch_bounds__(256) epRoute(const float* __restrict__ logits,
   const int per = E / 32;  // <= 32
   float v[32];
 #pragma unroll
-  for (int i = 0; i < 32; i++) v[i] = i < per ? row[i * 32 + lane] : -INFINITY;
+  for (int i = 0; i < 32; i++) {
+    float x = i < per ? row[i * 32 + lane] : -INFINITY;
+    x = x == x ? fminf(x, 3.402823466e38f) : -INFINITY;
+    v[i] = x;
+  }
+  uint32_t taken = 0;  // bit i: this lane's candidate i was selected in an earlier round
   float sel[kMaxTopK];
   int selIdx[kMaxTopK];
   for (int r = 0; r < k; r++) {
     float best = -INFINITY;
-    int bi = 0x7fffffff;
+    int bi = 0x7fffffff;  // no candidate on this lane (all taken)
 #pragma unroll
     for (int i = 0; i < 32; i++)
-      if (i < per && v[i] > best) { best = v[i]; bi = i * 32 + lane; }
+      if (i < per && !((taken >> i) & 1u) && (bi == 0x7fffffff || v[i] > best)) { best = v[i]; bi = i * 32 + lane; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -88,19 +96,17 @@ __global__ void __launch_bounds__(256) epRoute(const float* __restrict__ logits,
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
     sel[r] = best;
-    selIdx[r] = bi;
-    if ((bi & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < 32; i++)
-        if (i == (bi >> 5)) v[i] = -INFINITY;
-    }
+    selIdx[r] = bi;  // k <= E: some lane always had a candidate, so bi < E
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
   }
   if (lane == 0) {
-    float m = sel[0], s = 0.f;
-    for (int r = 0; r < k; r++) s += __expf(sel[r] - m);
+    const float m = sel[0];
+    float s = 0.f;
+    const bool flat = m == -INFINITY;  // nothing selectable in the row: uniform weights
+    for (int r = 0; r < k; r++) s += flat ? 1.f : __expf(sel[r] - m);
     for (int r = 0; r < k; r++) {
       topIdx[(size_t)warp * k + r] = selIdx[r];
-      topW[(size_t)warp * k + r] = __expf(sel[r] - m) / s;
+      topW[(size_t)warp * k + r] = (flat ? 1.f : __expf(sel[r] - m)) / s;
     }
   }
 }
@@ -152,13 +158,12 @@ __global__ void __launch_bounds__(256) epDispatch(const __grid_constant__ Dispat
         }
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 lanes = 128 channels
-        const float scale = fmaxf(amax, 1e-10f) / 448.f;
-        const float inv = 1.f / scale;
-        sc[j] = scale;
+        const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
+            sc[j] = scale;
         uint32_t w[2];
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-          const __nv_fp8x4_e4m3 p4(make_float4(f[4 * i] * inv, f[4 * i + 1] * inv, f[4 * i + 2] * inv, f[4 * i + 3] * inv));
+          const __nv_fp8x4_e4m3 p4(make_float4(__fdiv_rn(f[4 * i], scale), __fdiv_rn(f[4 * i + 1], scale), __fdiv_rn(f[4 * i + 2], scale), __fdiv_rn(f[4 * i + 3], scale)));
           w[i] = *reinterpret_cast<const uint32_t*>(&p4);
         }
         q[j] = make_uint2(w[0], w[1]);
@@ -166,6 +171,13 @@ __global__ void __launch_bounds__(256) epDispatch(const __grid_constant__ Dispat
     }
     for (int r = 0; r < a.k; r++) {
       const int e = a.topIdx[(size_t)t * a.k + r];
+      if (e < 0 || e >= a.L.nranks * a.L.expertsLocal) {  // not an expert: counted like a row that found its expert full, no window touched
+        if (lane == 0) {
+          atomicAdd(a.dropped, 1);
+          a.sentSlot[(size_t)t * a.k + r] = -1;
+        }
+        continue;
+      }
       const int dst = e / a.L.expertsLocal, el = e - dst * a.L.expertsLocal;
       int slot = 0;
       if (lane == 0) {
@@ -373,8 +385,8 @@ __global__ void __launch_bounds__(256) epCombine(const __grid_constant__ Combine
         w[rr] = 0.f;
         if (r < a.k) {
           const int slot = a.sentSlot[(size_t)t * a.k + r];
-          if (slot >= 0) {
-            const int e = a.topIdx[(size_t)t * a.k + r];
+          const int e = a.topIdx[(size_t)t * a.k + r];
+          if (slot >= 0 && slot < a.L.cap && e >= 0 && e < a.L.nranks * a.L.expertsLocal) {
             const int dst = e / a.L.expertsLocal, el = e - dst * a.L.expertsLocal;
             w[rr] = a.topW[(size_t)t * a.k + r];
             const uint4* src = reinterpret_cast<const uint4*>(a.win[dst] + a.L.outOff + ((size_t)el * a.L.cap + slot) * H * 2) + ch * 128;

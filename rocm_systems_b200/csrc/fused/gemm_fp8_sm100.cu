@@ -38,12 +38,11 @@ __global__ void __launch_bounds__(256) quantRows1x128(const __nv_bfloat16* x, ui
     }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float scale = fmaxf(amax, 1e-10f) / 448.f;
-    const float inv = 1.f / scale;
+    const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
     uint32_t w[2];
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-      const __nv_fp8x4_e4m3 p4(make_float4(f[4 * i] * inv, f[4 * i + 1] * inv, f[4 * i + 2] * inv, f[4 * i + 3] * inv));
+      const __nv_fp8x4_e4m3 p4(make_float4(__fdiv_rn(f[4 * i], scale), __fdiv_rn(f[4 * i + 1], scale), __fdiv_rn(f[4 * i + 2], scale), __fdiv_rn(f[4 * i + 3], scale)));
       w[i] = *reinterpret_cast<const uint32_t*>(&p4);
     }
     if (live) {
@@ -80,8 +79,7 @@ __global__ void __launch_bounds__(256) quantBlocks128x128(const __nv_bfloat16* w
   amax = red[0];
 #pragma unroll
   for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
-  const float scale = fmaxf(amax, 1e-10f) / 448.f;
-  const float inv = 1.f / scale;
+  const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
   if (t == 0) s[(size_t)nb * gridDim.x + kb] = scale;
 #pragma unroll
   for (int i = 0; i < 8; i++) {
@@ -98,7 +96,7 @@ __global__ void __launch_bounds__(256) quantBlocks128x128(const __nv_bfloat16* w
     uint32_t o[2];
 #pragma unroll
     for (int e = 0; e < 2; e++) {
-      const __nv_fp8x4_e4m3 p4(make_float4(f[4 * e] * inv, f[4 * e + 1] * inv, f[4 * e + 2] * inv, f[4 * e + 3] * inv));
+      const __nv_fp8x4_e4m3 p4(make_float4(__fdiv_rn(f[4 * e], scale), __fdiv_rn(f[4 * e + 1], scale), __fdiv_rn(f[4 * e + 2], scale), __fdiv_rn(f[4 * e + 3], scale)));
       o[e] = *reinterpret_cast<const uint32_t*>(&p4);
     }
     *reinterpret_cast<uint2*>(q + (size_t)row * ldq + (size_t)kb * 128 + sub * 8) = make_uint2(o[0], o[1]);

@@ -4,7 +4,7 @@
 Layout contract (what the kernel reads):
 
 * activations ``x`` [M, K]  ->  ``q`` [M, K] e4m3 and ``s`` [K / 128, M] fp32, one scale per row and 128 channels,
-  ``scale = max(amax, 1e-10) / 448`` and ``q = x / scale``;
+  ``scale = max(amax, 1e-10) * fp32(1 / 448)`` and ``q = x / scale`` (an IEEE division), so the kernels and these oracles agree bit for bit;
 * weights ``w`` [N, K]  ->  ``q`` [N, K] e4m3 and ``s`` [ceil(N / 128), K / 128] fp32, one scale per 128 x 128 block;
 * ``gemm(xq, xs, wq, ws)[m, n] = sum_kb xs[kb, m] * ws[n // 128, kb] * dot(xq[m, kb], wq[n, kb])`` with fp32 accumulation,
   rounded to bf16 once at the end.
@@ -29,7 +29,7 @@ def ref_quantize_act(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     M, K = x.shape
     assert K % 128 == 0
     g = x.float().view(M, K // 128, 128)
-    scale = g.abs().amax(-1).clamp_min(1e-10) / E4M3_MAX          # [M, K/128]
+    scale = g.abs().amax(-1).clamp_min(1e-10) * (1.0 / E4M3_MAX)  # [M, K/128]
     q = (g / scale.unsqueeze(-1)).to(torch.float8_e4m3fn).view(M, K)
     return q, scale.t().contiguous()                                # scales block-major: [K/128, M]
 
@@ -41,7 +41,7 @@ def ref_quantize_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     pad = torch.zeros(nb * 128, K, dtype=torch.float32, device=w.device)
     pad[:N] = w.float()
     blocks = pad.view(nb, 128, K // 128, 128)
-    scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-10) / E4M3_MAX   # [nb, K/128]
+    scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-10) * (1.0 / E4M3_MAX)   # [nb, K/128]
     q = (blocks / scale[:, None, :, None]).to(torch.float8_e4m3fn).view(nb * 128, K)[:N].contiguous()
     return q, scale.contiguous()
 

@@ -38,10 +38,10 @@ def _lib_ep():
 
 
 def quantize_e4m3_per128(x: torch.Tensor):
-    """Reference quantiser: fp8 e4m3 values and one fp32 scale per 128 channels (amax / 448)."""
+    """Reference quantiser: fp8 e4m3 values and one fp32 scale per 128 channels (amax * fp32(1 / 448))."""
     T, H = x.shape
     g = x.float().view(T, H // 128, 128)
-    scale = g.abs().amax(-1).clamp_min(1e-10) / 448.0
+    scale = g.abs().amax(-1).clamp_min(1e-10) * (1.0 / 448.0)
     q = (g / scale.unsqueeze(-1)).to(torch.float8_e4m3fn)
     return q.view(T, H), scale
 
@@ -49,6 +49,33 @@ def quantize_e4m3_per128(x: torch.Tensor):
 def dequantize_e4m3_per128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     T, H = q.shape
     return (q.float().view(T, H // 128, 128) * scale.unsqueeze(-1)).view(T, H).to(torch.bfloat16)
+
+
+def ref_route(logits: torch.Tensor, k: int):
+    """The routing rule of ``b200collEpRoute`` in plain PyTorch (any device): top ``k`` of each row, largest first, ties to
+    the lower expert id; a NaN counts as -inf and +inf as the largest finite value; when fewer than ``k`` values are above
+    -inf the row fills up with the lowest ids not yet taken; gate weights are the softmax over the selected values, or 1/k
+    each when all of them are -inf. Every id is in [0, E) and every weight finite, whatever the row holds."""
+    x = torch.nan_to_num(logits.float(), nan=float("-inf"), posinf=torch.finfo(torch.float32).max, neginf=float("-inf"))
+    T, E = x.shape
+    # stable descending sort = largest first, equal values in ascending id order (also among the -inf entries)
+    order = torch.sort(x, dim=-1, descending=True, stable=True).indices[:, :k]
+    sel = torch.gather(x, 1, order)
+    flat = torch.isinf(sel[:, :1]) & (sel[:, :1] < 0)
+    w = torch.softmax(torch.where(flat, torch.zeros_like(sel), sel), dim=-1)
+    return order.to(torch.int32), w
+
+
+def route(logits: torch.Tensor, k: int):
+    """``b200collEpRoute`` alone: expert ids [T, k] (int32) and gate weights [T, k] (fp32) of fp32 logits [T, E] on the GPU."""
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    T, E = logits.shape
+    idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    s = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib_ep().b200collEpRoute(logits.data_ptr(), idx.data_ptr(), w.data_ptr(), T, E, k, s), "b200collEpRoute")
+    train_ops.LAUNCHES += 1
+    return idx, w
 
 
 class MoELayer:

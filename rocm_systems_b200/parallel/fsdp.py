@@ -128,12 +128,14 @@ class FSDPEngine:
     """Owns the units, the communication stream and the schedule primitives."""
 
     def __init__(self, comm, units: List[FlatUnit], opt: AdamWConfig, reshard_after_forward: bool = True, fused_rs: bool = True,
-                 sym_shards: bool = False):
+                 sym_shards: bool = False, overlap: bool = True):
         self.comm, self.units, self.opt = comm, units, opt
         self.world = comm.nranks if comm is not None else 1
         self.rank = comm.rank if comm is not None else 0
         self.reshard = reshard_after_forward and self.world > 1
-        self.comm_stream = torch.cuda.Stream(priority=-1)
+        # overlap=False runs gathers, reductions and updates on the compute stream itself: the schedule of a step becomes
+        # strictly sequential, which is what a result obtained with overlap is checked against.
+        self.comm_stream = torch.cuda.Stream(priority=-1) if overlap else torch.cuda.current_stream()
         self.step_count = 0
         self.fused_rs = fused_rs
         self._pending: List[torch.cuda.Event] = []

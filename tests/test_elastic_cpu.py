@@ -168,6 +168,49 @@ def test_incomplete_checkpoint_is_refused(tmp_path):
     from rocm_systems_b200.utils import checkpoint
 
     sd = {"step": 3, "world": 2, "rank": 0, "units": {"p": {k: torch.zeros(4) for k in checkpoint.KEYS}}}
-    checkpoint.save_sharded(sd, str(tmp_path), {"p": 7})
+    with pytest.raises(checkpoint.CheckpointNotCommitted):              # rank 1 never writes: rank 0 gives up, nothing is committed
+        checkpoint.save_sharded(sd, str(tmp_path), {"p": 7}, commit_timeout_s=0.2)
+    assert checkpoint.complete_steps(str(tmp_path)) == []
     with pytest.raises(FileNotFoundError):
         checkpoint.load_shards(str(tmp_path))
+
+
+def test_rank_dying_mid_save_leaves_the_previous_step_loadable(tmp_path):
+    """Step 3 is saved by both ranks and committed. During the save of step 5 rank 1 dies after rank 0 wrote its shard
+    and before the commit marker exists: loading still gives step 3 on every rank, a shard of the wrong step is refused,
+    and the next complete save cleans the half-written step up."""
+    import json
+
+    import torch
+
+    from rocm_systems_b200.utils import checkpoint
+
+    d = str(tmp_path)
+
+    def state(step, rank, fill):
+        return {"step": step, "world": 2, "rank": rank, "units": {"p": {k: torch.full((4,), float(fill)) for k in checkpoint.KEYS}}}
+
+    checkpoint.save_sharded(state(3, 1, 31), d, {"p": 7})             # rank 1 first: it returns at once, rank 0 commits
+    checkpoint.save_sharded(state(3, 0, 30), d, {"p": 7})
+    assert checkpoint.complete_steps(d) == [3]
+    with pytest.raises(checkpoint.CheckpointNotCommitted):
+        checkpoint.save_sharded(state(5, 0, 50), d, {"p": 7}, commit_timeout_s=0.2)   # rank 1 is gone
+    assert checkpoint.all_steps(d) == [3, 5] and checkpoint.complete_steps(d) == [3]
+    for r in range(2):                                                  # both ranks resume from the same, complete step
+        sd = checkpoint.load_for(d, r, 2, {"p": 4})
+        assert sd["step"] == 3 and sd["rank"] == r and float(sd["units"]["p"]["master"][0]) == 30 + r
+    one = checkpoint.load_for(d, 0, 1, {"p": 8})                        # and a smaller world re-shards that step
+    assert one["step"] == 3 and one["units"]["p"]["m"].tolist() == [30.0] * 4 + [31.0] * 3 + [0.0]
+    # a shard that claims another step than the commit marker is refused on the same-world path too
+    torch.save(state(4, 1, 41), tmp_path / "step-3" / "rank1.pt")
+    with pytest.raises(ValueError):
+        checkpoint.load_for(d, 1, 2, {"p": 4})
+    torch.save(state(3, 1, 31), tmp_path / "step-3" / "rank1.pt")
+    # the next complete save commits, keeps the newest `keep` steps and removes the half-written one
+    checkpoint.save_sharded(state(7, 1, 71), d, {"p": 7})
+    checkpoint.save_sharded(state(7, 0, 70), d, {"p": 7}, keep=1)
+    assert checkpoint.all_steps(d) == [7] and json.loads((tmp_path / "step-7" / "meta.json").read_text())["step"] == 7
+    # files are read with weights_only=True: a pickled object is refused instead of executed
+    torch.save({"step": 7, "world": 2, "rank": 1, "units": {"p": {"master": object()}}}, tmp_path / "step-7" / "rank1.pt")
+    with pytest.raises(Exception):
+        checkpoint.load_for(d, 1, 2, {"p": 4})

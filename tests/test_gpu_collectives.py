@@ -52,6 +52,38 @@ def test_single_rank_collectives(solo_comm):
     assert c.async_error() == 0
 
 
+def test_premul_sum_reads_a_device_scalar_in_stream_order(solo_comm):
+    """The scalar is written by earlier work on the stream and changed right after the call: the kernel must see the value
+    that stream order gives it, the enqueue must not wait for the stream, and the call must be capturable in a graph."""
+    c = solo_comm
+    x = torch.arange(4096, dtype=torch.float32, device="cuda")
+    y = torch.zeros_like(x)
+    scalar = torch.zeros(1, dtype=torch.float32, device="cuda")
+    op = c.premul_sum_device(scalar)
+    scalar.fill_(5.0)            # stream-ordered before the collective
+    c.all_reduce(x, y, op=op)
+    scalar.fill_(-1.0)           # stream-ordered after it
+    torch.cuda.synchronize()
+    assert torch.equal(y, 5.0 * x)
+    # captured: the scalar of each replay is whatever the stream holds at that point
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        c.all_reduce(x, y, op=op)          # warm-up on the capture stream
+        side.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            c.all_reduce(x, y, op=op, stream=side)
+    for v in (2.0, 7.0):
+        scalar.fill_(v)
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, v * x)
+    c.redop_destroy(op)
+    assert c.async_error() == 0
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """A wait on a flag nothing sets runs out of budget: the kernel returns, the status word is
     set, the communicator reports a remote error, and the CUDA context stays usable."""

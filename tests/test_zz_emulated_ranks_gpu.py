@@ -4,8 +4,7 @@ grouped send/recv through FIFO slots and credits, the fused FSDP reduce-scatter+
 put+signal ring and remote atomics — run where only one GPU is there. The check itself is native (b200collEmuSelftest: small-integer data, every collective in
 float / bfloat16 / int32, verified on the host, guard bytes behind every output).
 
-The emulation has not passed on hardware yet; until it has, a failure is reported as an expected one instead of failing
-the suite (a pass shows as XPASS). It runs in a child process with every device-side wait limited to 5 s."""
+It runs in a child process with every device-side wait limited to 5 s."""
 import os
 import subprocess
 import sys
@@ -35,7 +34,6 @@ sys.exit(1 if bad else 0)
 """
 
 
-@pytest.mark.xfail(reason="first run on hardware pending", strict=False)
 def test_collectives_of_emulated_ranks_on_one_gpu():
     env = dict(os.environ, PYTHONPATH=str(ROOT), B200COLL_EMULATE_RANKS="1", B200COLL_NVLS_ENABLE="0", B200COLL_WAIT_TIMEOUT_MS="5000",
                B200COLL_BUFFSIZE="1M", B200COLL_BOOTSTRAP_TIMEOUT_MS="30000")

@@ -4,8 +4,8 @@ dispatch (route, fp8 quantise, row reservation by atomics, stores), grouped expe
 plain PyTorch compositions, through the same workers the multi-GPU tests use. The collective part degenerates (nothing
 crosses a link), the kernels and their schedules are the real ones.
 
-These single-rank runs have not passed on hardware yet; until they have, a failure is reported as an expected one (a pass
-shows as XPASS). Each runs in a child process; every device-side wait is limited to 5 s."""
+Each runs in a child process; every device-side wait is limited to 5 s. One rank holds all experts, and the router
+kernel wants a multiple of 32 of them, so the expert-parallel runs use 32 local experts."""
 import pytest
 
 from test_gpu_fused_multi import _launch
@@ -13,31 +13,26 @@ from test_gpu_fused_multi import _launch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_tensor_parallel_mlp_on_one_rank():
     _launch(1, 29881, "tp_worker.py", timeout=600)
     _launch(1, 29882, "tp_worker.py", "--rows", "512", "--hidden", "2048", "--ffn", "1024", timeout=600)
 
 
-@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_tensor_parallel_mlp_fp8_on_one_rank():
     """Both fused kernels on block-scaled e4m3 operands against the PyTorch statement of the same arithmetic."""
     _launch(1, 29885, "tp_worker.py", "--fp8", timeout=600)
     _launch(1, 29886, "tp_worker.py", "--fp8", "--rows", "512", "--hidden", "2048", "--ffn", "1024", timeout=600)
 
 
-@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_expert_parallel_layer_on_one_rank():
-    _launch(1, 29883, "ep_worker.py", timeout=600)
+    _launch(1, 29883, "ep_worker.py", "--experts-local", "32", timeout=600)
 
 
-@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_expert_parallel_layer_with_fp8_experts_on_one_rank():
     """The first expert GEMM on the received e4m3 rows and block-quantised weights (no dequantisation pass)."""
-    _launch(1, 29887, "ep_worker.py", "--fp8-experts", timeout=600)
+    _launch(1, 29887, "ep_worker.py", "--experts-local", "32", "--fp8-experts", timeout=600)
 
 
-@pytest.mark.xfail(reason="first single-rank run on hardware pending", strict=False)
 def test_device_initiated_layer_on_one_pe():
     """put+signal to itself, the atomics on its own words, the barrier of one: the device API's code paths on one GPU."""
     _launch(1, 29884, "shmem_worker.py", timeout=600)
