@@ -145,7 +145,9 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   // Reduce with peer loads would need the root's recv window on ranks that may pass no recv.
   // PreMulSum scales inputs while staging them, so it cannot skip staging.
   const bool directKind = !(r.kind == COLL_REDUCE && algo != ALGO_NVLS) && rop.scaleMode != SCALE_PRE_MUL;
-  if (algo != ALGO_LL && n > 1 && (bytes % 16) == 0 && directKind) {
+  plan->sendWin = plan->recvWin = 0;
+  plan->sendOff = plan->recvOff = 0;
+  if (algo != ALGO_LL && n > 1 && (bytes % 16) == 0 && directKind && r.allowDirect) {
     const size_t sendBytes = r.kind == COLL_REDUCESCATTER ? bytes * n : bytes;
     const size_t recvBytes = r.kind == COLL_ALLGATHER ? bytes * n : bytes;
     const bool needSend = r.kind != COLL_BROADCAST;
@@ -163,6 +165,10 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
     const bool mcNeeded = algo == ALGO_NVLS;
     if (aligned && (!needSend || sw) && (!needRecv || rw) && (!mcNeeded || mcOk)) {
       direct = true;
+      plan->sendWin = sw ? sw->id : 0;
+      plan->recvWin = rw ? rw->id : 0;
+      plan->sendOff = so;
+      plan->recvOff = ro;
       for (int p = 0; p < n; p++) {
         args->sendPeer[p] = sw ? sw->seg.peer[p] + so : nullptr;
         args->recvPeer[p] = rw ? rw->seg.peer[p] + ro : nullptr;
@@ -299,6 +305,21 @@ ncclResult_t enqueueColl(const CollReq& r) {
   Plan plan;
   CollArgs args;
   BCHECK(planInternal(r, rop, &plan, &args));
+  if (Flags::get().checkSymmetric && n > 1 && plan.algo != ALGO_LL) {
+    // The zero-copy path applies this rank's window offsets to every peer's mapping, so it is only right when all ranks
+    // passed the same place of the same window. Compare, and stage everywhere unless everybody agrees.
+    struct Where { uint64_t direct, sendWin, recvWin, sendOff, recvOff; } mine{plan.direct ? 1u : 0u, plan.sendWin, plan.recvWin, plan.sendOff, plan.recvOff};
+    std::vector<Where> all(n);
+    BCHECK(c->boot.allGather(&mine, all.data(), sizeof(Where)));
+    bool same = true;
+    for (int p = 0; p < n; p++) same = same && memcmp(&all[p], &all[0], sizeof(Where)) == 0;
+    if (!same || !all[0].direct) {
+      if (plan.direct) BINFO(SUB_COLL, "rank %d: buffers are in a symmetric window, but not at the same place on every rank: staging", c->rank);
+      CollReq staged = r;
+      staged.allowDirect = false;
+      BCHECK(planInternal(staged, rop, &plan, &args));
+    }
+  }
   DevComm dc = c->dev;
   dc.opSeq = ++c->opSeq;
   dc.stamp = stamp;

@@ -20,6 +20,7 @@ struct CollReq {
   cudaStream_t stream;
   int forceAlgo = ALGO_AUTO;  // schedule-file override
   int forceCtas = 0;
+  bool allowDirect = true;    // false: stage even when the buffers lie in symmetric windows
 };
 ncclResult_t enqueueColl(const CollReq& r);
 
@@ -35,7 +36,12 @@ struct P2pReq {
 ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops);
 
 // What the chooser would pick (exposed for tests and the tuner).
-struct Plan { int algo; int ctas; bool direct; size_t chunks; };
+struct Plan {
+  int algo; int ctas; bool direct; size_t chunks;
+  // What the zero-copy decision rests on, for the cross-rank check: ids and offsets of the windows the buffers lie in (0: none).
+  uint64_t sendWin = 0, recvWin = 0;
+  size_t sendOff = 0, recvOff = 0;
+};
 ncclResult_t planColl(const CollReq& r, Plan* plan);
 // One rank's share of a collective for the single-kernel emulation of several ranks on one GPU: everything enqueueColl
 // does up to the launch (validation, plan, kernel arguments, sequence numbers, staging parity), nothing launched.

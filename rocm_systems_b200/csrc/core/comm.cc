@@ -367,6 +367,7 @@ ncclResult_t commSymAlloc(Comm* c, size_t bytes, void** ptr) {
   BCHECK(r);
   *ptr = w->seg.peer[c->rank];
   std::lock_guard<std::mutex> lk(c->mu);
+  w->id = ++c->windowSeq;
   c->windows[(uintptr_t)*ptr] = std::move(w);
   return ncclSuccess;
 }
@@ -418,6 +419,7 @@ ncclResult_t commRegisterLazy(Comm* c, const void* ptr, size_t bytes) {
   w->fromRegister = true;
   hit->exchanged = true;
   std::lock_guard<std::mutex> lk(c->mu);
+  w->id = ++c->windowSeq;
   c->windows[(uintptr_t)la.ptr] = std::move(w);
   return ncclSuccess;
 }

@@ -26,6 +26,7 @@ struct Window {          // a symmetric range usable for zero-copy collectives
   SymSeg seg;
   void* userHandle = nullptr;  // what ncclCommRegister returned, if it came from there
   bool fromRegister = false;
+  uint64_t id = 0;             // position in the communicator's sequence of collective window creations: the same on every rank
 };
 
 struct Registration {    // ncclCommRegister bookkeeping (local until first collective use)
@@ -80,6 +81,7 @@ struct Comm {
   int maxCtas = 32, minCtas = 1;
   std::mutex mu;
   std::map<uintptr_t, std::unique_ptr<Window>> windows;   // keyed by local base address
+  uint64_t windowSeq = 0;                                  // windows created so far (creation is collective)
   std::vector<Registration*> regs;
   std::vector<PreMulOp> premul;
   std::vector<TuneEntry> tuning;

@@ -109,6 +109,7 @@ static void load(Flags& f) {
   if (const char* v = envOf("TRACE_FILE", false)) f.traceFile = v;
   if (const char* v = envOf("FAIL_KEY", false)) f.failKey = v;
   f.ipcLegacy = parseInt(envOf("IPC_MODE_LEGACY", false), 0);
+  f.checkSymmetric = parseInt(envOf("CHECK_SYMMETRIC", false), 0);
   // Sanity clamps: sizes must stay multiples of what the kernels vectorise on.
   if (f.stageBytes < (1u << 20)) f.stageBytes = 1u << 20;
   f.stageBytes &= ~(size_t)0xffff;
@@ -256,6 +257,8 @@ const SettingDoc kSettings[] = {
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
     {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},
     {"DMA_GANG", false, "0", "copy engines one copy-engine put/get is split over (0: 1, 2 or 4 by size; at most 8)"},
+    {"CHECK_SYMMETRIC", false, "0", "1: before a collective takes the zero-copy path the ranks compare, over the rendezvous network, which window and offset "
+                                   "each of them passed; on any difference all of them stage instead (a host exchange per call: for debugging)"},
     {"EMULATE_RANKS", false, "0", "1: ranks may share a GPU; their communicators serve only the b200collEmu* entry points, which play all ranks in one kernel (tests)"},
     {"WAIT_TIMEOUT_MS", false, "20000", "budget of every device-side wait; on expiry the kernel records the wait and returns"},
     {"BOOTSTRAP_TIMEOUT_MS", false, "120000", "budget of the host rendezvous"},
@@ -285,6 +288,7 @@ std::string currentValue(const Flags& f, const std::string& n) {
   if (n == "PIPELINE_CHUNK") return num(f.pipeChunkBytes);
   if (n == "DMA_GANG") return num(f.dmaGang);
   if (n == "EMULATE_RANKS") return num(f.emulateRanks);
+  if (n == "CHECK_SYMMETRIC") return num(f.checkSymmetric);
   if (n == "WAIT_TIMEOUT_MS") return num(f.waitTimeoutMs);
   if (n == "BOOTSTRAP_TIMEOUT_MS") return num(f.bootTimeoutMs);
   if (n == "COMM_ID") return f.commId;

@@ -103,6 +103,7 @@ struct Flags {
   std::string failKey;           // FAIL_KEY: host-side fault-injection points (tests)
   int ipcLegacy = 0;             // IPC_MODE_LEGACY: cudaIpc handles instead of VMM fds
   int graphRegister = 1;
+  int checkSymmetric = 0;         // CHECK_SYMMETRIC: ranks compare (window, offset) of every collective's buffers before choosing the zero-copy path
   static const Flags& get();
   static void refresh();  // re-read the environment (tests)
 };

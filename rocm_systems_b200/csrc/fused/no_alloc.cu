@@ -27,7 +27,16 @@ thread_local char tlsError[256] = "";
 // Device address of the array on the current device, looked up on the first call there.
 float* scratchForCurrentDevice() {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  cudaError_t ge = cudaGetDevice(&dev);
+  if (ge != cudaSuccess) {
+    snprintf(tlsError, sizeof(tlsError), "cudaGetDevice failed: %s", cudaGetErrorString(ge));
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    snprintf(tlsError, sizeof(tlsError), "device %d is outside the %d devices this entry point keeps an address for", dev, kMaxDevices);
+    return nullptr;
+  }
   std::lock_guard<std::mutex> lk(gSetupMu);
   if (!gScratchAddr[dev]) {
     void* p = nullptr;

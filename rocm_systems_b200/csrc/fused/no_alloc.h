@@ -20,7 +20,11 @@
  *  - The scratch is one array of B200OPS_NOALLOC_MAX_H floats (32 KiB) per GPU, resident from the
  *    moment the library is loaded on that GPU until the process exits.
  *  - The first call on each device looks up the device address of that array (with that device
- *    current). Make that first call outside of any stream capture.
+ *    current). Make that first call outside of any stream capture. With lazy module loading the
+ *    driver may also load this library's kernels, and take memory for them, during that first call:
+ *    "allocates nothing" holds from the second call on a device onwards.
+ *  - The address is kept for the life of the process. It does not survive cudaDeviceReset: a process
+ *    that resets a device must not call this entry point on that device afterwards.
  *  - Every call uses the same array and leaves its last weight gradient in it; each call clears it
  *    first. Two calls that may overlap on one GPU (different streams, no ordering between them)
  *    race on it: order them, e.g. put them on one stream.

@@ -78,6 +78,16 @@ ncclResult_t b200collEpCombine(ncclComm_t comm, void* winSym, const int* topIdx,
 ncclResult_t b200collEpCounts(ncclComm_t comm, void* winSym, int expertsLocal, int cap, int hidden, int ffn, unsigned int* countsHost,
                               int* droppedHost, cudaStream_t stream);
 
+/* ---- RMSNorm backward for callers that may not allocate device memory (no counterpart in the reference) -------------
+ * dx [T, H] and dw [H] (both bf16) of y = x * rstd * w; the fp32 accumulator of dw is a fixed 32 KiB array inside the
+ * library instead of caller memory, so the call makes no cudaMalloc / cudaFree. H: a multiple of 8, at most 8192 (wider
+ * rows are refused with -2 and a message). All calls on a GPU share that array: calls that may overlap on one GPU must
+ * be ordered by the caller. The first call on a device resolves the array's address (and may make the driver load this
+ * library's kernels): make it outside of stream capture. The full rules are in csrc/fused/no_alloc.h of the source tree. */
+int b200ops_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dwBf16, long long T, int H,
+                                cudaStream_t stream);
+const char* b200ops_rmsnorm_bwd_noalloc_error(void);
+
 #ifdef __cplusplus
 }
 #endif

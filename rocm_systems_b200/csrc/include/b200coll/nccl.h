@@ -205,7 +205,16 @@ B200COLL_DECL(ncclResult_t, ncclGroupEnd, void)
 /* ---- Extensions (no counterpart in NCCL 2.20): symmetric windows ------------------------ */
 
 /* Collective: every rank of `comm` allocates `size` bytes that all ranks map. `*ptr` is the
- * local address; collectives whose buffers lie in such a window skip the staging copies. */
+ * local address; collectives whose buffers lie in such a window skip the staging copies.
+ *
+ * The symmetric contract. A collective takes that zero-copy path when, on the calling rank, its
+ * buffers lie inside windows (these, or ncclMemAlloc memory after ncclCommRegister) and are 16-byte
+ * aligned; it then reaches every peer's buffer at the SAME offset of the SAME window. So all ranks
+ * of one call must pass the same place: window created by the same collective call, equal offset,
+ * or all of them ordinary memory. A call that mixes them computes on the wrong bytes or runs into
+ * its wait limit. With B200COLL_CHECK_SYMMETRIC=1 the ranks compare window and offset over the
+ * rendezvous network before each collective and all stage when they differ (one host exchange per
+ * call: a debugging aid). Windows must be created in the same order on every rank. */
 ncclResult_t b200collSymAlloc(ncclComm_t comm, size_t size, void** ptr);
 ncclResult_t b200collSymFree(ncclComm_t comm, void* ptr);
 /* Address through which this rank reaches `peer`'s copy of a symmetric pointer. */

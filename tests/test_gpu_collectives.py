@@ -155,3 +155,19 @@ def test_large_messages_through_many_pipeline_chunks():
         sys.stdout.write(p.stdout[-3000:])
         sys.stderr.write(p.stderr[-3000:])
         assert p.returncode == 0
+
+
+@pytest.mark.multigpu
+def test_mismatched_window_offsets_fall_back_to_staging():
+    """Buffers in one symmetric window but at rank-dependent offsets: with the cross-rank check on, nobody takes the
+    zero-copy path and the results stay exact."""
+    if gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, B200COLL_CHECK_SYMMETRIC="1")
+    env.setdefault("B200COLL_WAIT_TIMEOUT_MS", "5000")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29661", str(ROOT / "tests" / "workers" / "sym_offset_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    sys.stdout.write(p.stdout[-3000:])
+    sys.stderr.write(p.stderr[-3000:])
+    assert p.returncode == 0

@@ -16,15 +16,15 @@ import torch.nn.functional as F
 pytestmark = pytest.mark.gpu
 
 
-def _reference_grads(cfg, weights, tok, tgt):
+def _reference_grads(cfg, weights, tok, tgt, dtype=torch.float64):
     """fp32 autograd of the same decoder: rotate-half RoPE on q and k, grouped-query causal attention, SwiGLU with gate
     rows then up rows, RMSNorm, untied head, mean cross-entropy."""
     d, nh, nkv = cfg.head_dim, cfg.heads, cfg.kv_heads
-    W = {k: v.detach().double().requires_grad_(True) for k, v in weights.items()}
+    W = {k: v.detach().to(dtype).requires_grad_(True) for k, v in weights.items()}
     B, S = tok.shape
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, device=tok.device, dtype=torch.float64) / d))
     ang = torch.outer(torch.arange(S, device=tok.device, dtype=torch.float64), inv)
-    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    cos, sin = ang.cos()[None, :, None, :].to(dtype), ang.sin()[None, :, None, :].to(dtype)
 
     def norm(x, w):
         return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
@@ -50,20 +50,24 @@ def _reference_grads(cfg, weights, tok, tgt):
     return float(loss), {k: v.grad for k, v in W.items()}
 
 
-@pytest.mark.parametrize("shape", ["tiny", "wide"])
+@pytest.mark.parametrize("shape", ["tiny", "wide", "one_layer_of_8b"])
 def test_first_update_follows_the_autograd_gradient(shape):
     from rocm_systems_b200.models.llama import LlamaConfig, LlamaTrainer
     from rocm_systems_b200.parallel.fsdp import AdamWConfig
 
+    batch, ref_dtype = 2, torch.float64
     if shape == "tiny":
         cfg = LlamaConfig.tiny(64)
+    elif shape == "one_layer_of_8b":  # every kernel at the sizes of the benchmark: vocabulary 128256, FFN 14336, 4096 positions
+        cfg = LlamaConfig(layers=1)
+        batch, ref_dtype = 1, torch.float32
     else:  # rows of 4096 channels, 128-wide heads, grouped queries: the kernel configurations of the 8B model
         cfg = LlamaConfig(vocab=4096, hidden=4096, layers=2, heads=32, kv_heads=8, ffn=1024, seq_len=256)
     dev = torch.device("cuda", 0)
     tr = LlamaTrainer(cfg, None, dev, opt=AdamWConfig(lr=1e-3, weight_decay=0.0), seed=5)
     g = torch.Generator().manual_seed(3)
-    tok = torch.randint(0, cfg.vocab, (2, cfg.seq_len), generator=g).to(dev)
-    tgt = torch.randint(0, cfg.vocab, (2, cfg.seq_len), generator=g).to(dev)
+    tok = torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).to(dev)
+    tgt = torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).to(dev)
     units = [tr.embed, *tr.layers, tr.head]
     before = {}
     for u in units:
@@ -72,7 +76,8 @@ def test_first_update_follows_the_autograd_gradient(shape):
             before[f"{u.name}.{s.name}"] = u.master[o:o + s.numel].view(*s.shape).clone()
     # the reference sees the weights the kernels see: the bf16 working copy
     seen = {k: v.to(torch.bfloat16).float() for k, v in before.items()}
-    ref_loss, grads = _reference_grads(cfg, seen, tok, tgt)
+    ref_loss, grads = _reference_grads(cfg, seen, tok, tgt, ref_dtype)
+    del seen
     loss = tr.step(tok, tgt)
     torch.cuda.synchronize()
     assert abs(loss - ref_loss) < 0.02 * max(1.0, ref_loss), (loss, ref_loss)
