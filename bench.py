@@ -150,9 +150,11 @@ def main() -> None:
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--sym-shards", action="store_true", help="keep the bf16 parameter shards in symmetric memory (zero-copy all-gather); experimental")
+    ap.add_argument("--staged-shards", action="store_true",
+                    help="keep parameter shards and gradient buffers in ordinary memory: the collectives then stage (default: symmetric memory, zero-copy)")
     ap.add_argument("--collectives", default="b200coll", choices=["b200coll", "nccl"],
                     help="nccl: the same trainer with stock NCCL collectives (control run; the metric name gets a _nccl_collectives suffix)")
+    ap.add_argument("--gemm", default="own", choices=["own", "library"], help="linear layers on this package's tcgen05 kernel (default) or on cuBLAS")
     ap.add_argument("--no-overlap", action="store_true", help="run communication and optimizer on the compute stream (a sequential schedule, for checking)")
     ap.add_argument("--no-headline", action="store_true", help="skip the collective / fused-path summaries that follow the timed regions on 2+ GPUs")
     ap.add_argument("--reference-checkpointing", action="store_true", help="--impl reference: per-layer activation checkpointing from the start")
@@ -190,10 +192,13 @@ def main() -> None:
     else:
         comm = bcomm.init_from_env(device=local)
 
+    from rocm_systems_b200.models import llama as llama_mod
+
+    llama_mod.set_gemm(args.gemm)
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny(512)
     if args.seq:
         cfg.seq_len = args.seq
-    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=args.sym_shards, overlap=not args.no_overlap)
+    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=not args.staged_shards, overlap=not args.no_overlap)
     S, B = cfg.seq_len, 1
     nbatches = 4
     g = torch.Generator().manual_seed(1234 + rank)
@@ -249,6 +254,7 @@ def main() -> None:
         "data": "synthetic tokens uniform over the vocabulary (seeded), random-init weights N(0,0.02)",
         "config": {"model": "llama3-8b" if args.model == "llama3_8b" else "tiny", "global_batch": world * B, "seq_len": S,
                    "parallelism": f"fsdp{world}", "optimizer": "adamw fp32 master", "layers": cfg.layers, "hidden": cfg.hidden,
+                   "linear_gemm": "tcgen05 cta-pair kernel of this package" if args.gemm == "own" else "cuBLAS",
                    "l2": "working set per step (GBs of weights and activations) is far larger than the 126 MB L2; no flush needed"},
         "clocks": clocks, "gpu_launches": launches,
         "model_tflops_per_gpu": cfg.flops_per_token() * B * S / (ms_dev / args.steps / 1e3) / 1e12,

@@ -142,5 +142,68 @@ __device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA pairs (cta_group::2) ---------------------------------------------------------------------------------
+// Two CTAs of a cluster share one MMA: the even CTA of the pair issues it, each CTA holds half of the operands in its own
+// shared memory and half of the accumulator rows in its own tensor memory. Loads are ordinary tile loads (one CTA's
+// memory each, no multicast); what crosses the pair are mbarrier arrivals.
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `smemByteAddr` (an address in this CTA's shared memory) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapToCta(uint32_t smemByteAddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smemByteAddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void clusterArrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void clusterWait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// Tile load into THIS CTA's shared memory whose bytes are counted on a barrier of the pair's even CTA (`barClusterAddr`).
+__device__ __forceinline__ void tmaLoad2dPair(void* smemDst, const CUtensorMap* map, int x, int y, uint32_t barClusterAddr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smemAddr(smemDst)),
+               "l"(map), "r"(x), "r"(y), "r"(barClusterAddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmemAllocPair(uint32_t* smemOut, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(smemOut)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquishPair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemDeallocPair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void mmaF16Pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmemD),
+      "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at `barClusterAddr` (any CTA of the cluster) once every MMA this thread issued so far has finished.
+__device__ __forceinline__ void mmaCommitPair(uint32_t barClusterAddr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barClusterAddr) : "memory");
+}
+
+// Shared-memory operand descriptor for an MN-major tile laid out by TMA with the 128-byte swizzle: rows of 64 elements
+// (128 bytes) along M or N, one row per step of the reduction dimension, 8 rows = one 1024-byte swizzle group; the next 64
+// elements along M/N start `chunkBytes` further on (one TMA box).
+__device__ __forceinline__ uint64_t smemDescSw128Mn(uint32_t smemByteAddr, uint32_t chunkBytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smemByteAddr & 0x3ffff) >> 4);
+  d |= (uint64_t)((chunkBytes >> 4) & 0x3fff) << 16;      // leading-dimension byte offset: between 64-element chunks along M/N
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: between groups of 8 reduction rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor with the operands' majors: 0 K-major, 1 MN-major.
+__host__ __device__ constexpr uint32_t instrDescMajor(uint32_t M, uint32_t N, uint32_t abFormat, uint32_t aMn, uint32_t bMn) {
+  return (1u << 4) | (abFormat << 7) | (abFormat << 10) | (aMn << 15) | (bMn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
 }  // namespace sm100
 }  // namespace b200

@@ -3,13 +3,16 @@
 The model is a list of flat parameter units (embedding, one per layer, head). The forward and
 backward passes are driven unit by unit so that parameter all-gathers run one unit ahead of the
 compute and gradient reduce-scatters plus the optimizer run behind it, on the communication
-stream (see :mod:`rocm_systems_b200.parallel.fsdp`). GEMMs are plain library GEMMs (cuBLAS via
-``torch.mm``) with the weight gradient written straight into the unit's flat gradient buffer;
+stream (see :mod:`rocm_systems_b200.parallel.fsdp`). Every linear layer's three GEMMs (forward, input
+gradient, weight gradient) run on this package's tcgen05 CTA-pair kernel, which reads row-major and
+transposed operands alike, with the weight gradient written straight into the unit's flat gradient
+buffer (``set_gemm("library")`` switches them to cuBLAS through ``torch.mm`` for comparison);
 attention is the library SDPA kernel; norms, rotary embedding, SwiGLU, the loss, the embedding
 and AdamW are this package's CUDA kernels (:mod:`rocm_systems_b200.ops.train_ops`).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -99,27 +102,48 @@ class LlamaConfig:
         return 6.0 * gemm_params + attn
 
 
+_GEMM = {"impl": os.environ.get("B200_LINEAR_GEMM", "own")}
+
+
+def set_gemm(impl: str) -> None:
+    """``"own"``: the linear layers run on this package's tcgen05 kernel (default); ``"library"``: on cuBLAS via ``torch.mm``."""
+    assert impl in ("own", "library")
+    _GEMM["impl"] = impl
+
+
+def mm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a @ b.T`` for bf16 ``a`` [M, K], ``b`` [N, K], each row-major or the transposed view of a row-major matrix."""
+    if _GEMM["impl"] == "own" and a.is_cuda:
+        return ops.gemm(a, b, out=out)
+    return torch.mm(a, b.t(), out=out) if out is not None else torch.mm(a, b.t())
+
+
+def _rm(t: torch.Tensor) -> torch.Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
 class _LinearWG(torch.autograd.Function):
     """``y = x @ w.T`` whose backward writes dW into ``w.grad_view`` (a slice of the unit's flat
     gradient buffer) instead of returning a fresh tensor: no accumulate pass over the weights."""
 
     @staticmethod
     def forward(ctx, x, w):
+        x = _rm(x)
         ctx.save_for_backward(x, w)
-        return torch.mm(x, w.t())
+        return mm_nt(x, w)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = dy if dy.is_contiguous() else dy.contiguous()
-        dx = torch.mm(dy, w)
+        dx = mm_nt(dy, w.t())                       # dy [T, N] . w [N, K]
         gv = getattr(w, "grad_view", None)
         if gv is None:
-            return dx, torch.mm(dy.t(), x)
+            return dx, mm_nt(dy.t(), x.t())
         if getattr(w, "grad_accumulate", False):
             gv.addmm_(dy.t(), x)
         else:
-            torch.mm(dy.t(), x, out=gv)
+            mm_nt(dy.t(), x.t(), out=gv)            # dy^T [N, T] . x [T, K]
             w.grad_accumulate = True
         return dx, None
 
@@ -183,7 +207,7 @@ class LlamaTrainer:
     pinned memory or device tensors; ``loss`` is a host float when ``return_loss`` is set."""
 
     def __init__(self, cfg: LlamaConfig, comm=None, device: Optional[torch.device] = None, opt: Optional[AdamWConfig] = None,
-                 seed: int = 0, fused_rs: bool = True, sym_shards: bool = False, overlap: bool = True):
+                 seed: int = 0, fused_rs: bool = True, sym_shards: bool = True, overlap: bool = True):
         self.cfg = cfg
         self.comm = comm
         self.device = device or torch.device("cuda", torch.cuda.current_device())
@@ -246,12 +270,12 @@ class LlamaTrainer:
             with torch.enable_grad():
                 hn = ops.rmsnorm(hin, self.head.params["norm"], cfg.eps)
             w_out = self.head.params["out"].detach()  # the head GEMMs are differentiated by hand below
-            logits = torch.mm(hn.detach(), w_out.t())
+            logits = mm_nt(hn.detach(), w_out)
             loss_rows = ops.cross_entropy_inplace(logits, tgt, 1.0 / T)
             loss = loss_rows.mean()
             eng.alloc_grad(self.head)
-            dhn = torch.mm(logits, w_out)
-            torch.mm(logits.t(), hn.detach(), out=self.head.grad_view("out"))
+            dhn = mm_nt(logits, w_out.t())
+            mm_nt(logits.t(), hn.detach().t(), out=self.head.grad_view("out"))
             del logits
             self.head.params["norm"].grad = None
             torch.autograd.backward(hn, dhn)
@@ -315,7 +339,7 @@ class LlamaTrainer:
                     eng.release(u)
             eng.wait_params(self.head)
             hn = ops.rmsnorm(x, self.head.params["norm"], cfg.eps)
-            logits = torch.mm(hn, self.head.params["out"].t())
+            logits = mm_nt(hn, self.head.params["out"])
             out = float(F.cross_entropy(logits.float(), targets.reshape(-1)).item())
             if eng.reshard:
                 eng.release(self.head)

@@ -215,6 +215,42 @@ def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, bn:
     return out
 
 
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """``a @ b.T`` in bf16 with fp32 accumulation on the CTA-pair tcgen05 kernel (csrc/fused/gemm_pair_sm100.cuh).
+
+    ``a`` is [M, K] and ``b`` [N, K] as tensors; each may be a row-major matrix or the transposed view of one
+    (``x.t()``): the kernel reads either memory order directly (K-major or MN-major operand), so the three GEMMs of a
+    linear layer need no transposed copy:
+
+        y  = gemm(x, w)              # x [T, K], w [N, K]
+        dx = gemm(dy, w.t())         # dy [T, N], w.t() [K, N]
+        dw = gemm(dy.t(), x.t())     # dy.t() [N, T], x.t() [K, T]
+
+    ``out`` ([M, N], unit column stride) may be a view into a larger buffer."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
+    M, K = a.shape
+    N = b.shape[0]
+
+    def major(t):  # (stored with the row index contiguous?, leading dimension)
+        if t.stride(1) == 1:
+            return 0, t.stride(0)
+        assert t.stride(0) == 1, "operand must be a row-major matrix or the transpose of one"
+        return 1, t.stride(1)
+
+    a_mn, lda = major(a)
+    b_mn, ldb = major(b)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    assert out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1
+    lib = _lib_ops()
+    if not hasattr(lib, "_gemm_pair_sig"):
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        lib.b200ops_gemm_bf16_pair.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+        lib._gemm_pair_sig = True
+    _ck(lib.b200ops_gemm_bf16_pair(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, bn, max_ctas, _s()), "gemm_bf16_pair")
+    return out
+
+
 def gemm_take_error() -> int:
     """Code of the first bounded wait that gave up inside a tcgen05 kernel (0: none); synchronises."""
     return int(_lib_ops().b200ops_gemm_take_error())

@@ -82,7 +82,7 @@ def lib_jobs() -> list[tuple[Path, Path, list[str]]]:
     jobs: list[tuple[Path, Path, list[str]]] = []
     for rel in ["core/common.cc", "core/bootstrap.cc", "core/cudrv.cc", "core/mem.cc", "core/comm.cc", "core/api.cc",
                 "core/topo.cc", "coll/enqueue.cc", "coll/launch.cu", "coll/emu.cu", "trace/tracer.cc", "trace/markers.cc", "shmem/shmem_host.cc",
-                "coll/verifiable.cu", "fused/train_ops.cu", "fused/fsdp_kernels.cu", "fused/gemm_sm100.cu", "fused/tp_fused.cu", "fused/tp_fused_fp8.cu",
+                "coll/verifiable.cu", "fused/train_ops.cu", "fused/fsdp_kernels.cu", "fused/gemm_sm100.cu", "fused/gemm_pair_sm100.cu", "fused/tp_fused.cu", "fused/tp_fused_fp8.cu",
                 "fused/ep_kernels.cu", "fused/gemm_fp8_sm100.cu", "fused/no_alloc.cu", "shmem/shmem_kernels.cu", "core/health.cc"]:
         src = CSRC / rel
         if not src.exists():

@@ -14,10 +14,10 @@ ROOT = Path(__file__).resolve().parent.parent
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def _launch(nproc: int, port: int, worker: str, *args: str, timeout: int = 900) -> None:
+def _launch(nproc: int, port: int, worker: str, *args: str, timeout: int = 900, extra_env=None) -> None:
     if gpu_count() < nproc:
         pytest.skip(f"needs {nproc} GPUs")
-    env = dict(os.environ)
+    env = dict(os.environ, **(extra_env or {}))
     env.setdefault("B200COLL_WAIT_TIMEOUT_MS", "5000")
     env.setdefault("B200COLL_BOOTSTRAP_TIMEOUT_MS", "60000")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
@@ -34,7 +34,6 @@ def test_tp_fused_mlp_matches_unfused(nproc):
     _launch(nproc, 29820 + nproc, "tp_worker.py", "--rows", "512", "--hidden", "2048", "--ffn", "1024")
 
 
-@pytest.mark.xfail(reason="the fp8 form of the fused kernels has not run on hardware yet", strict=False)
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_tp_fused_mlp_fp8_matches_oracle(nproc):
     _launch(nproc, 29870 + nproc, "tp_worker.py", "--fp8")
@@ -46,7 +45,6 @@ def test_ep_dispatch_experts_combine(nproc):
     _launch(nproc, 29830 + nproc, "ep_worker.py")
 
 
-@pytest.mark.xfail(reason="the fp8 expert GEMM has not run on hardware yet", strict=False)
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_ep_with_fp8_experts(nproc):
     _launch(nproc, 29930 + nproc, "ep_worker.py", "--fp8-experts")
@@ -57,7 +55,6 @@ def test_shmem_put_get_signal_atomics(nproc):
     _launch(nproc, 29840 + nproc, "shmem_worker.py")
 
 
-@pytest.mark.xfail(reason="the device-side collectives have not run on hardware yet", strict=False)
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_shmem_device_collectives(nproc):
     _launch(nproc, 29950 + nproc, "shmem_worker.py", "--collectives")
@@ -65,4 +62,12 @@ def test_shmem_device_collectives(nproc):
 
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_fsdp_matches_single_rank(nproc):
+    """Shards and gradient buffers in symmetric memory (the default): zero-copy all-gather and reduce-scatter+cast."""
     _launch(nproc, 29850 + nproc, "fsdp_worker.py")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_fsdp_with_staged_collectives_matches_single_rank(nproc):
+    """Ordinary memory: the staged all-gather and the staged reduce-scatter+cast kernel; then with global-norm clipping."""
+    _launch(nproc, 29860 + nproc, "fsdp_worker.py", extra_env={"FSDP_SYM_SHARDS": "0"})
+    _launch(nproc, 29960 + nproc, "fsdp_worker.py", extra_env={"FSDP_CLIP": "1"})

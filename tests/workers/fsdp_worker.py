@@ -19,7 +19,7 @@ def main():
     dev = comm.device
     cfg = LlamaConfig.tiny(64)
     fused = os.environ.get("FSDP_FUSED_RS", "1") == "1"
-    sym = os.environ.get("FSDP_SYM_SHARDS", "0") == "1"   # shards and gradient buffers in symmetric memory (zero-copy collectives)
+    sym = os.environ.get("FSDP_SYM_SHARDS", "1") == "1"   # shards and gradient buffers in symmetric memory (zero-copy collectives)
     clip = float(os.environ.get("FSDP_CLIP", "0"))         # > 0: global-norm clipping to this value on both trainers
     opt = (lambda: AdamWConfig(max_grad_norm=clip)) if clip > 0 else (lambda: None)
     sharded = LlamaTrainer(cfg, comm, dev, opt=opt(), seed=3, fused_rs=fused, sym_shards=sym)
