@@ -9,9 +9,9 @@
 //               CTA 0 waits (bounded) until every peer said so, so when the kernel ends the receive
 //               buffers and the per-expert counts are complete.
 //   epDequant   fp8 rows -> bf16 rows for the grouped GEMMs.
-//   grouped GEMMs run on the tcgen05 kernel with a policy that walks (expert, row block, column
-//               block) and skips row blocks beyond an expert's token count; the first one applies
-//               SwiGLU in its epilogue.
+//   grouped GEMMs run on the tcgen05 kernel with a policy that walks a compact list of (expert, row block,
+//               column block): only row blocks that hold tokens are numbered, so the persistent CTAs share the
+//               real work evenly; the first one applies SwiGLU in its epilogue.
 //   epCombine   ONE kernel at the token's home rank: for each of the k experts it pulls the expert's
 //               output row from the owning rank (peer loads) and accumulates gate * row in fp32,
 //               in the fixed order k = 0..k-1, so the result is deterministic.
@@ -258,18 +258,26 @@ __global__ void __launch_bounds__(256) epDequant(const char* __restrict__ win, E
 using namespace gemm;
 template <int BN, bool SWIGLU> struct GroupPolicy {
   const uint32_t* cnt;   // rows per expert (may exceed cap when rows were dropped)
+  int experts;           // local experts
+  const int* prefix;     // shared memory, filled by the kernel: row blocks with tokens before expert e; [experts] = all of them
   int cap, capTiles;     // rows reserved per expert, in rows and in BM-row blocks
   int wRows;             // weight rows per expert
   __nv_bfloat16* out;    // [expertsLocal * cap, nOut]
   int ldo, nOut;
   __device__ __forceinline__ int have(int e) const { return min((int)cnt[e], cap); }
+  // Tile t of the COMPACT list: only row blocks that hold tokens are numbered, expert after expert, so every CTA of the
+  // persistent grid gets the same share of real work however unevenly the tokens fell (a buffer is sized for several
+  // times the average count, so most of its row blocks are empty). Indices past the end map to no tile.
   __device__ __forceinline__ void coord(int t, int, int tilesN, int& tm, int& tn) const {
-    const int per = capTiles * tilesN;
-    const int e = t / per, r = t - e * per;
-    tm = e * capTiles + r / tilesN;
-    tn = r % tilesN;
+    const int rb = t / tilesN;
+    tn = t - rb * tilesN;
+    tm = -1;
+    if (rb >= prefix[experts]) return;
+    int e = 0;
+    while (prefix[e + 1] <= rb) e++;  // prefix[] sits in shared memory: a few cycles per step
+    tm = e * capTiles + (rb - prefix[e]);
   }
-  __device__ __forceinline__ bool valid(int tm, int) const { return (tm % capTiles) * BM < have(tm / capTiles); }
+  __device__ __forceinline__ bool valid(int tm, int) const { return tm >= 0; }
   __device__ __forceinline__ int aRow(int tm) const { return tm * BM; }
   __device__ __forceinline__ int bRow(int tm, int tn) const { return (tm / capTiles) * wRows + tn * BN; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
@@ -312,6 +320,8 @@ template <int BN, bool SWIGLU> struct GroupPolicy {
 // bf16 copy of the activations disappear, and the larger of the two GEMMs runs at fp8 rate.
 struct GroupPolicy8 {
   const uint32_t* cnt;  // rows per expert (may exceed cap when rows were dropped)
+  int experts;          // local experts
+  const int* prefix;    // shared memory, filled by the kernel: row blocks with tokens before expert e; [experts] = all of them
   int cap, capTiles;
   int wRows;            // weight rows per expert (2 ffn)
   const float* sA;      // [expertsLocal * cap][groups]
@@ -319,13 +329,19 @@ struct GroupPolicy8 {
   __nv_bfloat16* out;   // act [expertsLocal * cap, nOut]
   int ldo, nOut;
   __device__ __forceinline__ int have(int e) const { return min((int)cnt[e], cap); }
+  // Tile t of the COMPACT list: only row blocks that hold tokens are numbered, expert after expert, so every CTA of the
+  // persistent grid gets the same share of real work however unevenly the tokens fell (a buffer is sized for several
+  // times the average count, so most of its row blocks are empty). Indices past the end map to no tile.
   __device__ __forceinline__ void coord(int t, int, int tilesN, int& tm, int& tn) const {
-    const int per = capTiles * tilesN;
-    const int e = t / per, r = t - e * per;
-    tm = e * capTiles + r / tilesN;
-    tn = r % tilesN;
+    const int rb = t / tilesN;
+    tn = t - rb * tilesN;
+    tm = -1;
+    if (rb >= prefix[experts]) return;
+    int e = 0;
+    while (prefix[e + 1] <= rb) e++;  // prefix[] sits in shared memory: a few cycles per step
+    tm = e * capTiles + (rb - prefix[e]);
   }
-  __device__ __forceinline__ bool valid(int tm, int) const { return (tm % capTiles) * gemm::BM < have(tm / capTiles); }
+  __device__ __forceinline__ bool valid(int tm, int) const { return tm >= 0; }
   __device__ __forceinline__ int bRow(int tm, int tn) const { return (tm / capTiles) * wRows + tn * gemm8::BN; }
   __device__ __forceinline__ int scaleBOff(int tm, int tn) const { return ((tm / capTiles) * (wRows / gemm8::BN) + tn) * groups; }
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
@@ -347,8 +363,26 @@ struct GroupPolicy8 {
   __device__ __forceinline__ void tileDone(int, int, int, int) const {}
 };
 
-__global__ void __launch_bounds__(gemm::kThreads, 1) groupedGemmFp8Kernel(const __grid_constant__ gemm8::Params p, const __grid_constant__ GroupPolicy8 pol) {
+constexpr int kMaxLocalExperts = 64;
+
+// Row blocks with tokens before every expert, once per CTA, into shared memory (the compact tile list of the policies).
+__device__ __forceinline__ void fillBlockPrefix(int* prefix, const uint32_t* cnt, int experts, int cap) {
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < experts; e++) {
+      prefix[e] = acc;
+      acc += (min((int)cnt[e], cap) + gemm::BM - 1) / gemm::BM;
+    }
+    prefix[experts] = acc;
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(gemm::kThreads, 1) groupedGemmFp8Kernel(const __grid_constant__ gemm8::Params p, GroupPolicy8 pol) {
   extern __shared__ uint8_t smemRaw[];
+  __shared__ int prefix[kMaxLocalExperts + 1];
+  fillBlockPrefix(prefix, pol.cnt, pol.experts, pol.cap);
+  pol.prefix = prefix;
   gemm8::gemmFp8Cta(p, pol, blockIdx.x, gridDim.x, smemRaw);
 }
 
@@ -429,6 +463,9 @@ __global__ void __launch_bounds__(256) epCombine(const __grid_constant__ Combine
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(gemm::kThreads, 1) groupedGemmKernel(const __grid_constant__ gemm::Params p, GroupPolicy<BN, SWIGLU> pol) {
   extern __shared__ uint8_t smemRaw[];
+  __shared__ int prefix[kMaxLocalExperts + 1];
+  fillBlockPrefix(prefix, pol.cnt, pol.experts, pol.cap);
+  pol.prefix = prefix;
   gemm::gemmCta<BN>(p, pol, blockIdx.x, gridDim.x, smemRaw);
 }
 
@@ -481,6 +518,7 @@ struct EpGuard {
 };
 
 ncclResult_t checkShape(int expertsLocal, int cap, int hidden, int ffn, int k) {
+  if (expertsLocal > kMaxLocalExperts) BFAIL(ncclInvalidArgument, "EP: at most %d experts per rank", kMaxLocalExperts);
   if (expertsLocal <= 0 || cap <= 0 || cap % 128) BFAIL(ncclInvalidArgument, "EP: capacity per expert (%d) must be a positive multiple of 128", cap);
   if (hidden % 1024 || hidden > 7168) BFAIL(ncclInvalidArgument, "EP: hidden (%d) must be a multiple of 1024, at most 7168", hidden);
   if (ffn % 128) BFAIL(ncclInvalidArgument, "EP: expert FFN width (%d) must be a multiple of 128", ffn);
@@ -590,7 +628,7 @@ static ncclResult_t epExperts(const char* what, ncclComm_t comm, void* winSym, c
     p.tilesM = rows / gemm::BM; p.tilesN = wRows / gemm8::BN; p.kBlocks = hidden / 128;
     p.err = gemm::errWord();
     if (!p.err) BFAIL(ncclUnhandledCudaError, "%s: no error word", what);
-    GroupPolicy8 pol{cnt, cap, cap / gemm::BM, wRows, p.sA, hidden / 128, (__nv_bfloat16*)act, ffn, ffn};
+    GroupPolicy8 pol{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, wRows, p.sA, hidden / 128, (__nv_bfloat16*)act, ffn, ffn};
     cudaError_t e = cudaFuncSetAttribute(groupedGemmFp8Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm8::kSmemBytes);
     if (e == cudaSuccess) {
       int grid = gemm::smCount();
@@ -609,8 +647,8 @@ static ncclResult_t epExperts(const char* what, ncclComm_t comm, void* winSym, c
       BFAIL(ncclInvalidArgument, "%s: misaligned operands", what);
     p.M = rows; p.N = wRows; p.K = hidden; p.tilesM = rows / gemm::BM; p.tilesN = wRows / bn; p.err = gemm::errWord();
     cudaError_t e;
-    if (bn == 256) e = launchGrouped(p, GroupPolicy<256, true>{cnt, cap, cap / gemm::BM, wRows, (__nv_bfloat16*)act, ffn, ffn}, stream);
-    else e = launchGrouped(p, GroupPolicy<128, true>{cnt, cap, cap / gemm::BM, wRows, (__nv_bfloat16*)act, ffn, ffn}, stream);
+    if (bn == 256) e = launchGrouped(p, GroupPolicy<256, true>{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, wRows, (__nv_bfloat16*)act, ffn, ffn}, stream);
+    else e = launchGrouped(p, GroupPolicy<128, true>{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, wRows, (__nv_bfloat16*)act, ffn, ffn}, stream);
     if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "%s: first grouped GEMM failed to launch: %s", what, cudaGetErrorString(e));
   }
   // GEMM 2: out = act * w2^T, w2 [expertsLocal * hidden, ffn].
@@ -622,8 +660,8 @@ static ncclResult_t epExperts(const char* what, ncclComm_t comm, void* winSym, c
       BFAIL(ncclInvalidArgument, "%s: misaligned operands", what);
     p.M = rows; p.N = hidden; p.K = ffn; p.tilesM = rows / gemm::BM; p.tilesN = hidden / bn; p.err = gemm::errWord();
     cudaError_t e;
-    if (bn == 256) e = launchGrouped(p, GroupPolicy<256, false>{cnt, cap, cap / gemm::BM, hidden, out, hidden, hidden}, stream);
-    else e = launchGrouped(p, GroupPolicy<128, false>{cnt, cap, cap / gemm::BM, hidden, out, hidden, hidden}, stream);
+    if (bn == 256) e = launchGrouped(p, GroupPolicy<256, false>{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, hidden, out, hidden, hidden}, stream);
+    else e = launchGrouped(p, GroupPolicy<128, false>{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, hidden, out, hidden, hidden}, stream);
     if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "%s: second grouped GEMM failed to launch: %s", what, cudaGetErrorString(e));
   }
   return ncclSuccess;

@@ -71,15 +71,9 @@ cudaError_t gemmPairBf16(const void* A, const void* B, void* C, int M, int N, in
                          cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0) return cudaSuccess;
   if ((reinterpret_cast<uintptr_t>(C) & 15) || (ldc & 7)) return cudaErrorInvalidValue;  // rows of C are written in 16-byte pieces
-  if (bn != 128 && bn != 256) {
-    // Tiles are handed out in rounds of one per CTA pair; the last round is as long as the others however few tiles it
-    // holds. 256-wide tiles move fewer operand bytes per FLOP, 128-wide ones fill the last round better: take the width
-    // whose rounds add up to less (a 128-wide tile costs a little more than half a 256-wide one).
-    const long tm = (M + 2 * BM - 1) / (2 * BM);
-    const long pairs = pairsOnDevice();
-    const long r256 = (tm * ((N + 255) / 256) + pairs - 1) / pairs, r128 = (tm * ((N + 127) / 128) + pairs - 1) / pairs;
-    bn = (N <= 128 || r128 * 128 * 107 < r256 * 256 * 100) ? 128 : 256;
-  }
+  // 256-wide tiles unless the caller says otherwise: on 128-wide ones the issuing thread's per-stage work (barrier wait,
+  // descriptors, commit) is no longer hidden behind the MMAs, and the kernel ran 1.6x slower on the same problem.
+  if (bn != 128 && bn != 256) bn = N > 128 ? 256 : 128;
   Params p{};
   const bool okA = aMn ? gemm::makeTileMap(&p.mapA, A, K, M, lda, 64, 2) : gemm::makeTileMap(&p.mapA, A, M, K, lda, BM, 2);
   const bool okB = bMn ? gemm::makeTileMap(&p.mapB, B, K, N, ldb, 64, 2) : gemm::makeTileMap(&p.mapB, B, N, K, ldb, bn / 2, 2);

@@ -10,9 +10,9 @@
 // Two CTAs of a cluster work on one 256 x BN output tile. Each loads its own 128 rows of A and its own half of the B
 // tile (BN / 2 rows) with ordinary TMA tile loads into its own shared memory; the even CTA's elected thread issues one
 // 256 x BN x 16 MMA per step that reads both halves and writes 128 accumulator rows into each CTA's tensor memory.
-// Against one CTA per tile that halves the shared-memory traffic of B and leaves room for six stages. The byte count of
+// Against one CTA per tile that halves the shared-memory traffic of B (three stages of 128 reduction steps fit). The byte count of
 // both CTAs' loads lands on the even CTA's `full` barrier; the MMA thread's commits arrive on the `empty` barriers of both
-// CTAs (two commits, one per CTA) and, at the end of a tile, on both `accFull` barriers; the epilogue warps of both CTAs
+// CTAs (one commit addressed to both) and, at the end of a tile, on both `accFull` barriers; the epilogue warps of both CTAs
 // arrive on the even CTA's `accEmpty`. Four epilogue warps per CTA drain tensor memory through a swizzled staging buffer
 // into 256-byte row segments while the next tile's main loop runs (two accumulators). Every wait is bounded; a CTA that
 // gives up still reaches the cluster barriers at the end.
@@ -27,12 +27,17 @@ using gemm::BK;
 using gemm::BM;
 using gemm::kThreads;
 
-constexpr int kStages = 6;
+// A stage holds 128 reduction steps (two TMA boxes of 64 per operand): eight MMAs per barrier round trip. With 64 the
+// issuing thread spent as long on the wait / commit pair of a stage as the tensor cores on its four MMAs.
+constexpr int kStages = 3;
+constexpr int kSub = 2;                        // 64-wide reduction slices per stage
 constexpr uint32_t kChunkBytes = 64 * BK * 2;  // one MN-major TMA box: 64 reduction rows of 64 elements
 
 template <int BN> struct Cfg {
-  static constexpr uint32_t kABytes = BM * BK * 2;          // this CTA's 128 rows of A
-  static constexpr uint32_t kBBytes = (BN / 2) * BK * 2;    // this CTA's half of the B tile
+  static constexpr uint32_t kASub = BM * BK * 2;            // this CTA's 128 rows of A, 64 reduction steps
+  static constexpr uint32_t kBSub = (BN / 2) * BK * 2;      // this CTA's half of the B tile, 64 reduction steps
+  static constexpr uint32_t kABytes = kSub * kASub;
+  static constexpr uint32_t kBBytes = kSub * kBSub;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kTmemCols = 2 * BN;
   static constexpr uint32_t kEpiBytesPerWarp = 32 * 128 * 2;
@@ -94,7 +99,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) gemmPai
   const uint32_t tmem = *tmemSlot;
 
   const int numTiles = p.tilesM * p.tilesN;
-  const int kIters = (p.K + BK - 1) / BK;
+  const int kIters = (p.K + kSub * BK - 1) / (kSub * BK);
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
   if (warp == 0) {
@@ -113,17 +118,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) gemmPai
           if (cr == 0) mbarArriveExpectTx(&full[stage], 2 * C::kStageBytes);  // both CTAs' bytes land here
           uint8_t* sa = smemA + (size_t)stage * C::kABytes;
           uint8_t* sb = smemB + (size_t)stage * C::kBBytes;
-          if constexpr (A_MN) {
 #pragma unroll
-            for (int c = 0; c < BM / 64; c++) tmaLoad2dPair(sa + c * kChunkBytes, &p.mapA, aRow + c * 64, k * BK, fullAddr);
-          } else {
-            tmaLoad2dPair(sa, &p.mapA, k * BK, aRow, fullAddr);
-          }
-          if constexpr (B_MN) {
+          for (int h = 0; h < kSub; h++) {
+            const int k0 = (k * kSub + h) * BK;  // a slice that starts beyond K reads zeros
+            if constexpr (A_MN) {
 #pragma unroll
-            for (int c = 0; c < BN / 2 / 64; c++) tmaLoad2dPair(sb + c * kChunkBytes, &p.mapB, bRow + c * 64, k * BK, fullAddr);
-          } else {
-            tmaLoad2dPair(sb, &p.mapB, k * BK, bRow, fullAddr);
+              for (int c = 0; c < BM / 64; c++) tmaLoad2dPair(sa + h * C::kASub + c * kChunkBytes, &p.mapA, aRow + c * 64, k0, fullAddr);
+            } else {
+              tmaLoad2dPair(sa + h * C::kASub, &p.mapA, k0, aRow, fullAddr);
+            }
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int c = 0; c < BN / 2 / 64; c++) tmaLoad2dPair(sb + h * C::kBSub + c * kChunkBytes, &p.mapB, bRow + c * 64, k0, fullAddr);
+            } else {
+              tmaLoad2dPair(sb + h * C::kBSub, &p.mapB, k0, bRow, fullAddr);
+            }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -151,22 +160,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) gemmPai
           const uint32_t aAddr = smemAddr(smemA + (size_t)stage * C::kABytes);
           const uint32_t bAddr = smemAddr(smemB + (size_t)stage * C::kBBytes);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; kk++) {
-            // 16 reduction steps: 32 bytes along a K-major row, 16 rows of 128 bytes in an MN-major tile
-            const uint64_t da = A_MN ? smemDescSw128Mn(aAddr + kk * 2048, kChunkBytes) : smemDescSw128(aAddr + kk * 32);
-            const uint64_t db = B_MN ? smemDescSw128Mn(bAddr + kk * 2048, kChunkBytes) : smemDescSw128(bAddr + kk * 32);
-            mmaF16Pair(d, da, db, idesc, (k | kk) != 0);
+          for (int h = 0; h < kSub; h++) {
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; kk++) {
+              // 16 reduction steps: 32 bytes along a K-major row, 16 rows of 128 bytes in an MN-major tile
+              const uint32_t ah = aAddr + h * C::kASub, bh = bAddr + h * C::kBSub;
+              const uint64_t da = A_MN ? smemDescSw128Mn(ah + kk * 2048, kChunkBytes) : smemDescSw128(ah + kk * 32);
+              const uint64_t db = B_MN ? smemDescSw128Mn(bh + kk * 2048, kChunkBytes) : smemDescSw128(bh + kk * 32);
+              mmaF16Pair(d, da, db, idesc, (k | h | kk) != 0);
+            }
           }
-          const uint32_t e = smemAddr(&empty[stage]);
-          mmaCommitPair(mapToCta(e, 0));  // the stage is free in both CTAs once these MMAs have read it
-          mmaCommitPair(mapToCta(e, 1));
+          mmaCommitBoth(smemAddr(&empty[stage]));  // the stage is free in both CTAs once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) {
-          const uint32_t f = smemAddr(&accFull[b]);
-          mmaCommitPair(mapToCta(f, 0));
-          mmaCommitPair(mapToCta(f, 1));
-        }
+        if (ok) mmaCommitBoth(smemAddr(&accFull[b]));
       }
     }
   } else {

@@ -187,6 +187,10 @@ __device__ __forceinline__ void mmaF16Pair(uint32_t tmemD, uint64_t descA, uint6
 __device__ __forceinline__ void mmaCommitPair(uint32_t barClusterAddr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barClusterAddr) : "memory");
 }
+// The same arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, with one instruction.
+__device__ __forceinline__ void mmaCommitBoth(uint32_t barAddr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(barAddr), "h"((uint16_t)3) : "memory");
+}
 
 // Shared-memory operand descriptor for an MN-major tile laid out by TMA with the 128-byte swizzle: rows of 64 elements
 // (128 bytes) along M or N, one row per step of the reduction dimension, 8 rows = one 1024-byte swizzle group; the next 64
