@@ -122,6 +122,8 @@ def run(args, clock_sampler_cls) -> None:
     c = dict(CFG if args.model == "llama3_8b" else TINY)
     if args.seq:
         c["seq_len"] = args.seq
+    if getattr(args, "layers", 0):
+        c["layers"] = args.layers
     S, B, nb = c["seq_len"], 1, 4
     g = torch.Generator().manual_seed(1234 + rank)
     host_tok = [torch.randint(0, c["vocab"], (B, S), generator=g, dtype=torch.int64).pin_memory() for _ in range(nb)]

@@ -149,6 +149,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
     ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (experiments; the headline uses the model's own)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--staged-shards", action="store_true",
                     help="keep parameter shards and gradient buffers in ordinary memory: the collectives then stage (default: symmetric memory, zero-copy)")
@@ -198,6 +199,8 @@ def main() -> None:
     cfg = LlamaConfig.llama3_8b() if args.model == "llama3_8b" else LlamaConfig.tiny(512)
     if args.seq:
         cfg.seq_len = args.seq
+    if args.layers:
+        cfg.layers = args.layers
     trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=not args.staged_shards, overlap=not args.no_overlap)
     S, B = cfg.seq_len, 1
     nbatches = 4
@@ -243,7 +246,7 @@ def main() -> None:
 
     tokens_per_step = world * B * S
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
-    base = BASELINE_TOKENS_PER_S.get(world) if args.model == "llama3_8b" and not args.seq else None
+    base = BASELINE_TOKENS_PER_S.get(world) if args.model == "llama3_8b" and not args.seq and not args.layers else None
     peak_gb = trainer.memory_summary()["peak_gb"]
     headline = None
     if world > 1 and not args.no_headline and args.collectives == "b200coll":

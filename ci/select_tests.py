@@ -28,7 +28,7 @@ RULES = [
     ("rocm_systems_b200/csrc/coll/verifiable*", ["tests/test_verifiable_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/coll/*", ["tests/test_planner_cpu.py", "tests/test_protocol_interleavings_cpu.py", "tests/test_protocol_model_cpu.py", "tests/test_staged_emulation_cpu.py"], ["tests/test_gpu_collectives.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_emulated_ranks_gpu.py"], True),
     ("rocm_systems_b200/csrc/include/b200coll/shmem_device.cuh", ["tests/test_shmem_collectives_model_cpu.py", "tests/test_examples_build_cpu.py"], ["tests/test_gpu_fused_multi.py"], True),
-    ("rocm_systems_b200/csrc/shmem/*", ["tests/test_api_cpu.py"], ["tests/test_gpu_fused_multi.py", "tests/test_zz_shmem_dma_gpu.py"], True),
+    ("rocm_systems_b200/csrc/shmem/*", ["tests/test_api_cpu.py"], ["tests/test_gpu_fused_multi.py", "tests/test_shmem_dma_gpu.py"], True),
     ("rocm_systems_b200/csrc/fused/fsdp_kernels.cu", ["tests/test_fsdp_rscast_emulation_cpu.py", "tests/test_protocol_model_cpu.py"], ["tests/test_gpu_fused_multi.py"], True),
     ("rocm_systems_b200/csrc/fused/gemm_fp8*", ["tests/test_fp8_reference_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/fused/*", ["tests/test_kernel_resources_cpu.py"], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_fused_single_gpu.py", "tests/test_zz_no_alloc.py"], True),
@@ -43,7 +43,7 @@ RULES = [
     ("rocm_systems_b200/parallel/cp.py", ["tests/test_parallel_cpu.py", "tests/test_examples_build_cpu.py"], [], False),
     ("rocm_systems_b200/parallel/fsdp.py", ["tests/test_fsdp_layout_cpu.py"], ["tests/test_gpu_fused_multi.py"], False),
     ("rocm_systems_b200/ops/fp8.py", ["tests/test_fp8_reference_cpu.py"], [], False),
-    ("rocm_systems_b200/shmem.py", ["tests/test_api_cpu.py"], ["tests/test_zz_shmem_dma_gpu.py"], False),
+    ("rocm_systems_b200/shmem.py", ["tests/test_api_cpu.py"], ["tests/test_shmem_dma_gpu.py"], False),
     ("rocm_systems_b200/parallel/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_fused_multi.py"], False),
     ("rocm_systems_b200/utils/elastic.py", ["tests/test_elastic_cpu.py"], [], False),
     ("rocm_systems_b200/utils/checkpoint.py", ["tests/test_elastic_cpu.py"], [], False),

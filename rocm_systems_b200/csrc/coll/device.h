@@ -96,6 +96,14 @@ struct LLArgs {
   uint32_t seq;          // flag value of this operation (never 0)
 };
 
+// All-to-all between receive buffers that lie in a symmetric window: every rank stores its chunk for peer p straight into
+// p's buffer, at the place of the sending rank.
+struct A2aDirectArgs {
+  const char* send;              // n chunks of chunkBytes, chunk p goes to rank p
+  char* recvPeer[kMaxRanks];     // every rank's receive buffer as mapped here
+  size_t chunkBytes;             // a multiple of 16
+};
+
 struct P2pWork {
   int peer;
   int isSend;

@@ -59,9 +59,11 @@ __device__ __forceinline__ Dim grid() { return Dim{gLanes, 1, 1}; }
 #define B200_MISC_KERNELS 1       // the send/recv kernel too, under names of its own (launch.cu defines the originals)
 #define kP2p emuP2p
 #define kBarrier emuBarrier
+#define kAllToAllDirect emuAllToAllDirect
 #include "kernels.cuh"
 #undef kP2p
 #undef kBarrier
+#undef kAllToAllDirect
 #undef B200_MISC_KERNELS
 #define B200_EMU_KERNELS_ONLY 1
 // Non-template functions get names of their own here: the library's other object file defines the originals.

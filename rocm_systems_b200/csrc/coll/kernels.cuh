@@ -676,6 +676,28 @@ __global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ Dev
   stampEnd(c);
 }
 
+// All-to-all by direct peer stores (the rccl-tests all-to-all moves count / nranks elements per peer pair in 16-byte
+// aligned chunks, rccl-tests/src/alltoall.cpp:16-18, 67; here a chunk goes over NVLink once, with no FIFO in between).
+// CTA b handles the same byte range of every chunk. Barrier before: every rank has entered the call, so its receive
+// buffer may be overwritten. Barrier after: everything stored into this rank's buffer has landed.
+__global__ void __launch_bounds__(kCollThreads) kAllToAllDirect(const __grid_constant__ DevComm c, const __grid_constant__ A2aDirectArgs a) {
+  stampBegin(c);
+  const int n = c.nranks, rank = c.rank;
+  uint32_t epoch = c.local->barEpoch[blockIdx.x];
+  size_t lo, hi;
+  splitUnits(a.chunkBytes >> 4, gridDim.x, blockIdx.x, lo, hi);
+  ctaBarrier(c, epoch);
+  if (lo < hi) {
+    for (int i = 0; i < n; i++) {
+      const int p = (rank + i) % n;  // own chunk first (local), then the peers in ring order so that no two ranks start on the same target
+      ctaCopy(a.recvPeer[p] + (size_t)rank * a.chunkBytes + (lo << 4), a.send + (size_t)p * a.chunkBytes + (lo << 4), (hi - lo) << 4);
+    }
+  }
+  ctaBarrier(c, epoch);
+  if (threadIdx.x == 0) c.local->barEpoch[blockIdx.x] = epoch;
+  stampEnd(c);
+}
+
 __global__ void kBarrier(const __grid_constant__ DevComm c) {
   stampBegin(c);
   uint32_t epoch = c.local->barEpoch[0];

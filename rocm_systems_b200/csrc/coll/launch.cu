@@ -55,6 +55,11 @@ cudaError_t launchWaitUnsetFlag(cudaStream_t s, const DevComm& c) {
   return cudaGetLastError();
 }
 
+cudaError_t launchAllToAllDirect(int grid, cudaStream_t s, const DevComm& c, const A2aDirectArgs& a) {
+  kAllToAllDirect<<<grid, kCollThreads, 0, s>>>(c, a);
+  return cudaGetLastError();
+}
+
 cudaError_t launchBarrier(cudaStream_t s, const DevComm& c) {
   kBarrier<<<1, 32, 0, s>>>(c);
   return cudaGetLastError();

@@ -12,6 +12,7 @@ cudaError_t launchLLAllReduce(ncclDataType_t dt, int op, int grid, cudaStream_t 
 cudaError_t launchStagedReduce(ncclDataType_t dt, int op, bool nvls, int grid, cudaStream_t s, const DevComm& c, const CollArgs& a);
 cudaError_t launchStagedCopy(bool nvls, int grid, cudaStream_t s, const DevComm& c, const CollArgs& a, int elemSize);
 cudaError_t launchP2p(int grid, cudaStream_t s, const DevComm& c, const P2pArgs& a);
+cudaError_t launchAllToAllDirect(int grid, cudaStream_t s, const DevComm& c, const A2aDirectArgs& a);
 cudaError_t launchBarrier(cudaStream_t s, const DevComm& c);
 cudaError_t launchWaitUnsetFlag(cudaStream_t s, const DevComm& c);
 cudaError_t launchFill(void* dst, unsigned value, size_t bytes, cudaStream_t s);

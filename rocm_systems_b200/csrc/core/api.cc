@@ -394,6 +394,40 @@ ncclResult_t pncclAllToAll(const void* send, void* recv, size_t count, ncclDataT
   if (send == recv && count) BFAIL(ncclInvalidUsage, "ncclAllToAll cannot run in place");
   const size_t es = dtypeSize(dt);
   if (!es) BFAIL(ncclInvalidArgument, "invalid datatype %d", (int)dt);
+  // Receive buffer inside a symmetric window (the same place on every rank), whole 16-byte units: peer stores, one kernel.
+  const size_t chunk = count * es;
+  if (c->nranks > 1 && tlsGroup.depth == 0 && chunk && (chunk & 15) == 0 && ((((uintptr_t)send) | ((uintptr_t)recv)) & 15) == 0 && !Flags::get().emulateRanks) {
+    if (!c->regs.empty()) BCHECK(commRegisterLazy(c, recv, 1));
+    size_t off = 0;
+    Window* w = nullptr;
+    {
+      std::lock_guard<std::mutex> lk(c->mu);
+      w = c->findWindow(recv, chunk * c->nranks, &off);
+    }
+    if (w) {
+      if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+      A2aDirectArgs a{};
+      a.send = (const char*)send;
+      for (int p = 0; p < c->nranks; p++) a.recvPeer[p] = w->seg.peer[p] + off;
+      a.chunkBytes = chunk;
+      int prev = -1;
+      cudaGetDevice(&prev);
+      if (prev != c->cudaDev) cudaSetDevice(c->cudaDev);
+      Tracer* tr = c->tracer;
+      TraceStamp* stamp = tr ? tr->begin(B200COLL_API_ID_ncclAllToAll, dt, count, chunk * c->nranks) : nullptr;
+      DevComm dc = c->dev;
+      dc.opSeq = ++c->opSeq;
+      dc.stamp = stamp;
+      const size_t want = (chunk * c->nranks + (256u << 10) - 1) / (256u << 10);  // one CTA per 256 KiB moved
+      const int ctas = (int)std::max<size_t>(1, std::min<size_t>(want, (size_t)c->maxCtas));
+      if (tr) tr->setAlgo(ALGO_P2P, ctas);
+      cudaError_t e = launchAllToAllDirect(ctas, s, dc, a);
+      if (tr) tr->end(e == cudaSuccess);
+      if (prev != c->cudaDev && prev >= 0) cudaSetDevice(prev);
+      if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "all-to-all launch failed: %s", cudaGetErrorString(e));
+      return ncclSuccess;
+    }
+  }
   pncclGroupStart();
   ncclResult_t r = ncclSuccess;
   for (int p = 0; p < c->nranks && r == ncclSuccess; p++) {

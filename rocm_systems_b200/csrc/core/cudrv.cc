@@ -49,6 +49,7 @@ const CuDrv& CuDrv::get() {
     B200_DRV_LOAD(cuTensorMapEncodeTiled)
     B200_DRV_LOAD(cuPointerGetAttribute)
 #undef B200_DRV_LOAD
+    loadOne("cuStreamWriteValue32", &gDrv.cuStreamWriteValue32);  // optional
     gDrv.ok = all;
     if (!all) BINFO(SUB_INIT, "CUDA driver entry points unavailable (no driver on this machine?)");
   });

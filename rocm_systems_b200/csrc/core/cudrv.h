@@ -34,6 +34,7 @@ struct CuDrv {
   B200_DRV_FN(cuMulticastGetGranularity)
   B200_DRV_FN(cuTensorMapEncodeTiled)
   B200_DRV_FN(cuPointerGetAttribute)
+  B200_DRV_FN(cuStreamWriteValue32)  // optional: null on a driver without stream memory operations
 #undef B200_DRV_FN
   static const CuDrv& get();  // loads once; `ok` is false when there is no driver
 };

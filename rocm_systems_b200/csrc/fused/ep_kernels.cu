@@ -347,20 +347,22 @@ struct GroupPolicy8 {
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ bool epiBegin(int, volatile int*) const { return true; }
   __device__ __forceinline__ float scaleA(int kb, int row) const { return __ldg(sA + (size_t)row * groups + kb); }
-  __device__ __forceinline__ void emit(float (&acc)[gemm8::BN], int tm, int tn, int q, int lane, uint8_t* sw) const {
+  __device__ __forceinline__ void emit(float (&acc)[gemm8::kAccCols], int tm, int tn, int q, int h, int lane, uint8_t* sw) const {
     constexpr int H = gemm8::BN / 2;
     const int e = tm / capTiles;
     const int row0 = tm * gemm::BM + q * 32;
     const int rowsHave = have(e) - (row0 - e * cap);  // rows of this warp's 32 that hold tokens
+    // gate columns 32h .. 32h+32 of the tile in acc[0..32), the up columns of the same outputs in acc[32..64)
 #pragma unroll
-    for (int i = 0; i < H; i++) {
+    for (int i = 0; i < 32; i++) {
       const float g = acc[i];
-      acc[i] = g / (1.f + __expf(-g)) * acc[H + i];
+      acc[i] = g / (1.f + __expf(-g)) * acc[32 + i];
     }
-    gemm8::storeTile(sw, lane, H, acc,  // ffn is a multiple of 128: every tile has all of its 64 output columns
-                     [&](int r) -> __nv_bfloat16* { return r < rowsHave ? out + (size_t)(row0 + r) * ldo + (size_t)tn * H : nullptr; });
+    gemm8::storeCols<32>(
+        sw, lane, H, acc,  // ffn is a multiple of 128: every tile has all of its 64 output columns
+        [&](int r) -> __nv_bfloat16* { return r < rowsHave ? out + (size_t)(row0 + r) * ldo + (size_t)tn * H : nullptr; }, [&](int) { return h * 32; });
   }
-  __device__ __forceinline__ void tileDone(int, int, int, int) const {}
+  __device__ __forceinline__ void tileDone(int, int, int, int, int) const {}
 };
 
 constexpr int kMaxLocalExperts = 64;
@@ -378,7 +380,7 @@ __device__ __forceinline__ void fillBlockPrefix(int* prefix, const uint32_t* cnt
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(gemm::kThreads, 1) groupedGemmFp8Kernel(const __grid_constant__ gemm8::Params p, GroupPolicy8 pol) {
+__global__ void __launch_bounds__(gemm8::kThreads, 1) groupedGemmFp8Kernel(const __grid_constant__ gemm8::Params p, GroupPolicy8 pol) {
   extern __shared__ uint8_t smemRaw[];
   __shared__ int prefix[kMaxLocalExperts + 1];
   fillBlockPrefix(prefix, pol.cnt, pol.experts, pol.cap);
@@ -633,7 +635,7 @@ static ncclResult_t epExperts(const char* what, ncclComm_t comm, void* winSym, c
     if (e == cudaSuccess) {
       int grid = gemm::smCount();
       if (grid > p.tilesM * p.tilesN) grid = p.tilesM * p.tilesN;
-      groupedGemmFp8Kernel<<<grid, gemm::kThreads, gemm8::kSmemBytes, stream>>>(p, pol);
+      groupedGemmFp8Kernel<<<grid, gemm8::kThreads, gemm8::kSmemBytes, stream>>>(p, pol);
       e = cudaGetLastError();
     }
     if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "%s: first grouped GEMM failed to launch: %s", what, cudaGetErrorString(e));

@@ -163,7 +163,7 @@ int b200ops_gemm_fp8_block_tn(const void* A8, const float* sA, const void* B8, c
   if (maxCtas > 0 && maxCtas < ctas) ctas = maxCtas;
   const int tiles = p.tilesM * p.tilesN;
   if (tiles < ctas) ctas = tiles;
-  gemm8::gemmFp8BlockKernel<<<ctas, gemm::kThreads, gemm8::kSmemBytes, st>>>(p);
+  gemm8::gemmFp8BlockKernel<<<ctas, gemm8::kThreads, gemm8::kSmemBytes, st>>>(p);
   return (int)cudaGetLastError();
 }
 

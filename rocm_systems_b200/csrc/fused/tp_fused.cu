@@ -16,6 +16,9 @@
 #include <map>
 #include <mutex>
 
+#include <algorithm>
+
+#include "../core/cudrv.h"
 #include "b200coll/fused.h"
 #include "gemm_host.h"
 #include "tp_fused.cuh"
@@ -156,7 +159,7 @@ template <int BN> struct RsPolicy {
         },
         [&](int r) -> __nv_bfloat16* { return base + (size_t)r * a.N; });
   }
-  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const { rsTileDone(a, BN, tm, tn, q, lane); }
+  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const { rsTileDone(a, BN, tm, tn, q == 0 && lane == 0, 128); }
 };
 
 template <int BN>
@@ -178,7 +181,11 @@ using namespace b200::tp;
 
 namespace {
 
-struct AgState { uint32_t* flags = nullptr; uint32_t seq = 0; int cap = 0; };
+struct AgState {
+  uint32_t* flags = nullptr; uint32_t seq = 0; int cap = 0;
+  cudaStream_t side = nullptr;          // copy-engine mode: the stream of the pulls
+  cudaEvent_t evStart = nullptr, evDone = nullptr;
+};
 struct RsState { unsigned long long calls = 0; int tileW = 0; };
 std::mutex gTpMu;
 std::map<Comm*, AgState> gAg;
@@ -196,6 +203,9 @@ void tpForget(Comm* c, const void* base) {
     auto it = gAg.find(c);
     if (it != gAg.end()) {
       if (it->second.flags) cudaFree(it->second.flags);
+      if (it->second.side) cudaStreamDestroy(it->second.side);
+      if (it->second.evStart) cudaEventDestroy(it->second.evStart);
+      if (it->second.evDone) cudaEventDestroy(it->second.evDone);
       gAg.erase(it);
     }
   }
@@ -230,6 +240,49 @@ ncclResult_t agNextCall(Comm* c, int needFlags, uint32_t** flags, uint32_t* seq)
   }
   *flags = st.flags;
   *seq = ++st.seq;
+  return ncclSuccess;
+}
+
+// Copy-engine form of the all-gather side: the peers' shards are pulled by cudaMemcpyAsync on a side stream, a few row
+// blocks per copy, in the order the GEMM takes them (rank + 1, rank + 2, ...); behind every copy a stream memory write
+// publishes the flags of its row blocks. No SM pulls anything, so the GEMM keeps all of them. The side stream starts once
+// `stream` has reached this call (this rank's own rows are written) and all ranks have met at a barrier; a second barrier
+// behind the copies tells every rank that its shard is no longer being read, and `stream` joins the side stream behind the
+// kernel the caller launches next. Flags and tile waits are the ones of the kernel's own communication CTAs.
+ncclResult_t agPullByCopyEngine(Comm* c, ncclComm_t comm, char* xLocal, char* const* xPeer, uint32_t* flags, uint32_t seq, int blocksPerRank,
+                                size_t blockBytes, cudaStream_t stream, cudaEvent_t* joinAfterKernel) {
+  const CuDrv& d = CuDrv::get();
+  if (!d.cuStreamWriteValue32) BFAIL(ncclInvalidUsage, "copy-engine all-gather needs stream memory operations (cuStreamWriteValue32), which this driver lacks");
+  cudaStream_t side;
+  cudaEvent_t evStart, evDone;
+  {
+    std::lock_guard<std::mutex> lk(gTpMu);
+    AgState& st = gAg[c];
+    if (!st.side) {
+      BCUDA(cudaStreamCreateWithFlags(&st.side, cudaStreamNonBlocking));
+      BCUDA(cudaEventCreateWithFlags(&st.evStart, cudaEventDisableTiming));
+      BCUDA(cudaEventCreateWithFlags(&st.evDone, cudaEventDisableTiming));
+    }
+    side = st.side; evStart = st.evStart; evDone = st.evDone;
+  }
+  const int n = c->nranks, rank = c->rank;
+  BCUDA(cudaEventRecord(evStart, stream));
+  BCUDA(cudaStreamWaitEvent(side, evStart, 0));
+  BCHECK(b200collBarrier(comm, side));  // every rank's own shard is in place
+  const int group = blocksPerRank >= 4 ? blocksPerRank / 4 : 1;  // row blocks per copy: four copies per peer shard
+  for (int i = 1; i < n; i++) {
+    const int peer = (rank + i) % n;
+    for (int b0 = 0; b0 < blocksPerRank; b0 += group) {
+      const int nb = std::min(group, blocksPerRank - b0);
+      const size_t off = (size_t)(peer * blocksPerRank + b0) * blockBytes;
+      BCUDA(cudaMemcpyAsync(xLocal + off, xPeer[peer] + off, (size_t)nb * blockBytes, cudaMemcpyDeviceToDevice, side));
+      for (int b = 0; b < nb; b++)
+        BCU(d.cuStreamWriteValue32((CUstream)side, (CUdeviceptr)(flags + peer * blocksPerRank + b0 + b), seq, CU_STREAM_WRITE_VALUE_DEFAULT));
+    }
+  }
+  BCHECK(b200collBarrier(comm, side));  // the peers are done reading this rank's shard
+  BCUDA(cudaEventRecord(evDone, side));
+  *joinAfterKernel = evDone;
   return ncclSuccess;
 }
 
@@ -280,12 +333,15 @@ ncclResult_t b200collAgGemm(ncclComm_t comm, void* xSym, const void* w, void* ou
   a.rowsPerRank = rowsPerRank;
   a.blocksPerRank = rowsPerRank / BM;
   a.rowBytes = (size_t)K * 2;
-  a.nComm = n > 1 ? (commCtas > 0 ? commCtas : 20) : 0;
+  const bool byCopyEngine = n > 1 && commCtas < 0;
+  a.nComm = (n > 1 && !byCopyEngine) ? (commCtas > 0 ? commCtas : 20) : 0;
   if (a.nComm > 64) a.nComm = 64;
   a.out = (__nv_bfloat16*)out;
   a.nOut = swiglu ? wRows / 2 : wRows;
   a.ldo = a.nOut;
   BCHECK(agNextCall(c, n * a.blocksPerRank, &a.flags, &a.seq));
+  cudaEvent_t join = nullptr;
+  if (byCopyEngine) BCHECK(agPullByCopyEngine(c, comm, a.xLocal, peers, a.flags, a.seq, a.blocksPerRank, (size_t)BM * a.rowBytes, stream, &join));
   Params p{};
   if (!makeTileMap(&p.mapA, xSym, M, K, K, BM, 2) || !makeTileMap(&p.mapB, w, wRows, K, K, bn, 2))
     BFAIL(ncclInvalidArgument, "b200collAgGemm: operands must be 16-byte aligned with rows a multiple of 16 bytes");
@@ -315,6 +371,7 @@ ncclResult_t b200collAgGemm(ncclComm_t comm, void* xSym, const void* w, void* ou
   else { if (swiglu) B200_AG_LAUNCH(128, true); else B200_AG_LAUNCH(128, false); }
 #undef B200_AG_LAUNCH
   if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collAgGemm launch failed: %s", cudaGetErrorString(e));
+  if (join) BCUDA(cudaStreamWaitEvent(stream, join, 0));  // what follows on `stream` also follows the pulls and the closing barrier
   return ncclSuccess;
 }
 

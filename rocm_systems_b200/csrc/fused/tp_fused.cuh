@@ -40,11 +40,12 @@ struct RsArgs {
   int ldy;
 };
 
-// Epilogue side of a finished partial tile: once all four epilogue warps have stored their rows, one thread bumps the
-// tile's counter at the owner. tileW: columns per tile (the counters are indexed in tiles of that width).
-__device__ __forceinline__ void rsTileDone(const RsArgs& a, int tileW, int tm, int tn, int q, int lane) {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
-  if (q == 0 && lane == 0) {
+// Epilogue side of a finished partial tile: once all epilogue warps (`epiThreads` threads) have stored their part, one
+// thread (`leader`) bumps the tile's counter at the owner. tileW: columns per tile (the counters are indexed in tiles of
+// that width).
+__device__ __forceinline__ void rsTileDone(const RsArgs& a, int tileW, int tm, int tn, bool leader, int epiThreads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(epiThreads) : "memory");
+  if (leader) {
     const int owner = tm / a.blocksPerRank;
     const int tilesN = (a.N + tileW - 1) / tileW;
     uint32_t* f = (uint32_t*)(a.stagePeer[owner] + a.flagOff) + (size_t)(tm - owner * a.blocksPerRank) * tilesN + tn;

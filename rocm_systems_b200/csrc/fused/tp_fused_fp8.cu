@@ -82,21 +82,25 @@ template <bool SWIGLU> struct AgPolicy {
     return waitBlockFlag(a.flags + tm, a.seq, err, false);
   }
   __device__ __forceinline__ float scaleA(int kb, int row) const { return ldScale(a.sLocal + (size_t)kb * a.M + row); }
-  __device__ __forceinline__ void emit(float (&acc)[BN], int tm, int tn, int q, int lane, uint8_t* sw) const {
+  __device__ __forceinline__ void emit(float (&acc)[kAccCols], int tm, int tn, int q, int h, int lane, uint8_t* sw) const {
     const int row0 = tm * BM + q * 32;
     if constexpr (SWIGLU) {
+      // The thread holds gate columns 32h .. 32h+32 of the tile in acc[0..32) and the up columns of the same outputs in acc[32..64).
 #pragma unroll
-      for (int i = 0; i < BN / 2; i++) {
+      for (int i = 0; i < 32; i++) {
         const float g = acc[i];
-        acc[i] = g / (1.f + __expf(-g)) * acc[BN / 2 + i];
+        acc[i] = g / (1.f + __expf(-g)) * acc[32 + i];
       }
-      storeTile(sw, lane, min(BN / 2, a.nOut - tn * (BN / 2)), acc,
-                [&](int r) -> __nv_bfloat16* { return a.out + (size_t)(row0 + r) * a.ldo + (size_t)tn * (BN / 2); });
+      storeCols<32>(
+          sw, lane, a.nOut - tn * (BN / 2), acc, [&](int r) -> __nv_bfloat16* { return a.out + (size_t)(row0 + r) * a.ldo + (size_t)tn * (BN / 2); },
+          [&](int) { return h * 32; });
     } else {
-      storeTile(sw, lane, a.nOut - tn * BN, acc, [&](int r) -> __nv_bfloat16* { return a.out + (size_t)(row0 + r) * a.ldo + (size_t)tn * BN; });
+      storeCols<64>(
+          sw, lane, a.nOut - tn * BN, acc, [&](int r) -> __nv_bfloat16* { return a.out + (size_t)(row0 + r) * a.ldo + (size_t)tn * BN; },
+          [&](int g) { return g * 64 + h * 32; });
     }
   }
-  __device__ __forceinline__ void tileDone(int, int, int, int) const {}
+  __device__ __forceinline__ void tileDone(int, int, int, int, int) const {}
 };
 
 template <bool SWIGLU>
@@ -150,14 +154,17 @@ struct RsPolicy {
   __device__ __forceinline__ bool waitTile(int, int, volatile int*) const { return true; }
   __device__ __forceinline__ bool epiBegin(int, volatile int*) const { return true; }
   __device__ __forceinline__ float scaleA(int kb, int row) const { return __ldg(sA + (size_t)kb * M + row); }
-  __device__ __forceinline__ void emit(float (&acc)[BN], int tm, int tn, int q, int lane, uint8_t* sw) const {
+  __device__ __forceinline__ void emit(float (&acc)[kAccCols], int tm, int tn, int q, int h, int lane, uint8_t* sw) const {
     const int owner = tm / a.blocksPerRank;
     const int localRow0 = tm * BM + q * 32 - owner * a.rowsPerRank;
-    // Owner's staging: [src rank][rowsPerRank][N] bf16; whole 256-byte row pieces go over NVLink.
+    // Owner's staging: [src rank][rowsPerRank][N] bf16; 64-byte row pieces go over NVLink.
     __nv_bfloat16* base = (__nv_bfloat16*)(a.stagePeer[owner] + a.stageOff) + ((size_t)rank * a.rowsPerRank + localRow0) * a.N + (size_t)tn * BN;
-    storeTile(sw, lane, a.N - tn * BN, acc, [&](int r) -> __nv_bfloat16* { return base + (size_t)r * a.N; });
+    storeCols<64>(
+        sw, lane, a.N - tn * BN, acc, [&](int r) -> __nv_bfloat16* { return base + (size_t)r * a.N; }, [&](int g) { return g * 64 + h * 32; });
   }
-  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int lane) const { tp::rsTileDone(a, BN, tm, tn, q, lane); }
+  __device__ __forceinline__ void tileDone(int tm, int tn, int q, int h, int lane) const {
+    tp::rsTileDone(a, BN, tm, tn, q == 0 && h == 0 && lane == 0, kEpiThreads);
+  }
 };
 
 __global__ void __launch_bounds__(kThreads, 1) gemmRsFp8Kernel(const __grid_constant__ Params p, const __grid_constant__ RsArgs a, const __grid_constant__ DevComm c) {

@@ -15,6 +15,16 @@ evaluation in ``evaluate_ast.cpp``). The raw values here come from Nsight Comput
 with the functions ``min``, ``max``, ``abs``, ``sqrt`` and ``select(cond, a, b)`` (a when cond is non-zero).
 
     python -m rocm_systems_b200.tools.counters raw.csv --peaks MEASURED_PEAKS.json --arg flops=1.0995e12
+
+Collection (the counterpart of the reference's counter collection service, which programs the hardware blocks for the
+counters a definition needs): ``--collect`` runs a command under Nsight Compute asking for exactly the raw metrics the
+chosen definitions read, one kernel pattern and a bounded number of launches, and evaluates the result:
+
+    python -m rocm_systems_b200.tools.counters --collect -k gemmPairKernel -c 2 --counter tensor_active_pct --counter hbm_gbs \
+        -- python -m rocm_systems_b200.bench.kernel_cases --case gemm
+
+The capture never locks the GPU's clocks (``--clock-control none``) and is bounded by ``-k`` / ``-c``; ``--print-command``
+shows the ``ncu`` line without running anything.
 """
 from __future__ import annotations
 
@@ -200,6 +210,16 @@ class CounterSet:
         return out
 
 
+def collect_command(metrics: Sequence[str], command: Sequence[str], kernel: str, count: int, skip: int, output: str) -> List[str]:
+    """The Nsight Compute line that gathers ``metrics`` for ``count`` launches of kernels matching ``kernel``."""
+    cmd = ["ncu", "--clock-control", "none", "--metrics", ",".join(metrics), "-c", str(int(count)), "-o", output, "-f"]
+    if kernel:
+        cmd += ["-k", f"regex:{kernel}"]
+    if skip:
+        cmd += ["-s", str(int(skip))]
+    return cmd + list(command)
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     from . import roofline
 
@@ -210,8 +230,42 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--arg", action="append", default=[], help="NAME=VALUE readable as arg.NAME")
     ap.add_argument("--list", action="store_true", help="print the definitions and the raw metrics they need")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--collect", action="store_true", help="run the command after -- under Nsight Compute for the metrics the counters need, then evaluate")
+    ap.add_argument("--counter", action="append", default=[], help="with --collect: only these definitions (default: all)")
+    ap.add_argument("-k", "--kernel", default="", help="with --collect: regular expression of the kernels to capture")
+    ap.add_argument("-c", "--count", type=int, default=3, help="with --collect: launches to capture (kept small on purpose)")
+    ap.add_argument("-s", "--skip", type=int, default=0, help="with --collect: matching launches to skip first")
+    ap.add_argument("-o", "--output", default="counters_capture", help="with --collect: report file (without .ncu-rep)")
+    ap.add_argument("--print-command", action="store_true", help="with --collect: print the ncu line and stop")
+    argv = list(sys.argv[1:] if argv is None else argv)
+    command: List[str] = []
+    if "--" in argv:
+        i = argv.index("--")
+        argv, command = argv[:i], argv[i + 1:]
     a = ap.parse_args(argv)
     cs = CounterSet.load(a.defs)
+    if a.collect:
+        import subprocess
+
+        if not command:
+            ap.error("--collect needs a command after --")
+        if a.count < 1 or a.count > 20:
+            ap.error("--count must be between 1 and 20: a capture replays every launch many times")
+        if a.counter:
+            known = {d["name"] for d in cs.defs}
+            missing = [c for c in a.counter if c not in known]
+            if missing:
+                ap.error(f"unknown counter(s): {', '.join(missing)}")
+            cs = CounterSet([d for d in cs.defs if d["name"] in a.counter])
+        cmd = collect_command(cs.required_metrics(), command, a.kernel, a.count, a.skip, a.output)
+        if a.print_command:
+            print(" ".join(cmd))
+            return 0
+        rc = subprocess.call(cmd)
+        if rc != 0:
+            print(f"counters: ncu exited with {rc}", file=sys.stderr)
+            return rc
+        a.inputs = [a.output + ".ncu-rep"]
     if a.list:
         for d in cs.defs:
             print(f"{d['name']:<22} [{d.get('unit', '')}] = {d['expression']}\n{'':<22} {d.get('description', '')}")

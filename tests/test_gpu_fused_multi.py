@@ -35,6 +35,13 @@ def test_tp_fused_mlp_matches_unfused(nproc):
 
 
 @pytest.mark.parametrize("nproc", [2, 8])
+def test_tp_fused_mlp_with_copy_engine_all_gather(nproc):
+    """The all-gather side pulled by copy engines on a side stream (flags by stream memory writes), every SM on the GEMM."""
+    _launch(nproc, 29970 + nproc, "tp_worker.py", "--comm-ctas", "-1")
+    _launch(nproc, 29980 + nproc, "tp_worker.py", "--comm-ctas", "-1", "--rows", "512", "--hidden", "2048", "--ffn", "1024")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
 def test_tp_fused_mlp_fp8_matches_oracle(nproc):
     _launch(nproc, 29870 + nproc, "tp_worker.py", "--fp8")
     _launch(nproc, 29890 + nproc, "tp_worker.py", "--fp8", "--rows", "512", "--hidden", "2048", "--ffn", "1024")

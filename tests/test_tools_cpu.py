@@ -520,3 +520,23 @@ print('END')
     p = subprocess.run([sys.executable, "-c", "import time\nfrom rocm_systems_b200.utils import hang_dump\nhang_dump.arm(0.2, exit_after=True)\ntime.sleep(5)"],
                        env=dict(os.environ, PYTHONPATH=str(ROOT)), capture_output=True, text=True, timeout=60)
     assert p.returncode == 124 and "hang_dump" in p.stderr
+
+
+def test_counters_collection_command_asks_for_exactly_the_needed_metrics(capsys):
+    """--collect builds a bounded Nsight Compute capture (clocks untouched, one kernel pattern, few launches) for the raw
+    metrics the chosen definitions read, and refuses an unbounded launch count."""
+    from rocm_systems_b200.tools import counters
+
+    rc = counters.main(["--collect", "-k", "gemmPairKernel", "-c", "2", "--counter", "tensor_active_pct", "--counter", "hbm_gbs", "--print-command",
+                        "--", "python", "-m", "rocm_systems_b200.bench.kernel_cases", "--case", "gemm"])
+    assert rc == 0
+    line = capsys.readouterr().out.strip().split()
+    assert line[0] == "ncu" and line[1:3] == ["--clock-control", "none"]
+    metrics = line[line.index("--metrics") + 1].split(",")
+    assert sorted(metrics) == ["dram__bytes_read.sum", "dram__bytes_write.sum", "gpu__time_duration.sum", "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active"]
+    assert line[line.index("-c") + 1] == "2" and line[line.index("-k") + 1] == "regex:gemmPairKernel"
+    assert line[-5:] == ["python", "-m", "rocm_systems_b200.bench.kernel_cases", "--case", "gemm"]
+    with pytest.raises(SystemExit):
+        counters.main(["--collect", "-c", "500", "--print-command", "--", "true"])
+    with pytest.raises(SystemExit):
+        counters.main(["--collect", "--counter", "no_such_counter", "--print-command", "--", "true"])

@@ -36,13 +36,14 @@ def main():
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--ffn", type=int, default=512)       # per rank
     ap.add_argument("--fp8", action="store_true")         # the block-scaled e4m3 form of both kernels
+    ap.add_argument("--comm-ctas", type=int, default=0)   # CTAs that pull the peers' rows inside the all-gather kernel; -1: copy engines pull, no SM does
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     comm = init_from_env()
     rank, n = comm.rank, comm.nranks
     dev = comm.device
-    mlp = (TensorParallelMLPFp8 if args.fp8 else TensorParallelMLP)(comm, args.rows, args.hidden, args.ffn, dev, seed=11)
+    mlp = (TensorParallelMLPFp8 if args.fp8 else TensorParallelMLP)(comm, args.rows, args.hidden, args.ffn, dev, seed=11, comm_ctas=args.comm_ctas)
     bad = []
     for trial in range(3):
         g = torch.Generator(device=dev).manual_seed(100 * trial + rank)
@@ -57,7 +58,7 @@ def main():
         scale = ref.abs().max().item()
         if not (err <= 3e-2 * scale + 1e-3):
             bad.append(("mismatch", trial, err, scale))
-    res = {"nranks": n, "rows_per_rank": args.rows, "hidden": args.hidden, "ffn_local": args.ffn}
+    res = {"nranks": n, "rows_per_rank": args.rows, "hidden": args.hidden, "ffn_local": args.ffn, "comm_ctas": args.comm_ctas}
     if args.time and not bad:
         g = torch.Generator(device=dev).manual_seed(rank)
         x = torch.randn(args.rows, args.hidden, device=dev, generator=g).to(torch.bfloat16)
