@@ -252,7 +252,7 @@ const SettingDoc kSettings[] = {
     {"MIN_CTAS", true, "0", "lower bound of CTAs per collective launch (0: built-in)"},
     {"MAX_CTAS", true, "0", "upper bound of CTAs per collective launch (0: built-in)"},
     {"BUFFSIZE", true, "64M", "bytes per staging half (two halves per communicator), at least 1M"},
-    {"LL_THRESHOLD", false, "64K", "largest all-reduce served by the flag-in-data protocol, at most 256K"},
+    {"LL_THRESHOLD", false, "256K", "largest all-reduce served by the flag-in-data protocol, at most 256K"},
     {"P2P_CHUNK", false, "512K", "bytes per send/recv FIFO slot"},
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
     {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},

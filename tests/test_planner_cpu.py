@@ -43,8 +43,8 @@ def test_builtin_choices():
     MiB = 1 << 20
     r = plan([
         [8, 1, AR, 1024, F32, SUM],            # 4 KiB: flag-in-data
-        [8, 1, AR, 16 * 1024, F32, SUM],       # 64 KiB: still flag-in-data
-        [8, 1, AR, 16 * 1024 + 4, F32, SUM],   # just above: in-switch
+        [8, 1, AR, 64 * 1024, F32, SUM],       # 256 KiB: still flag-in-data
+        [8, 1, AR, 64 * 1024 + 4, F32, SUM],   # just above: in-switch
         [8, 1, AR, 64 * MiB // 4, F32, MAX],   # max is not an in-switch operation: peer loads
         [2, 1, AR, 64 * MiB // 4, F32, SUM],   # two ranks: peer loads move fewer bytes than the switch
         [8, 0, AR, 64 * MiB // 4, F32, SUM],   # no multicast: peer loads
@@ -118,7 +118,7 @@ def test_planner_invariants_over_random_messages():
         assert rc == 0 and algo in (LL, P2P, NVLS) and 1 <= ctas <= 128 and direct == 0, (nranks, kind, count, algo, ctas, chunks)
         assert (chunks == 0) if algo == LL else (chunks >= 1), (nranks, kind, count, algo, chunks)      # flag-in-data uses no staging
         if algo == LL:
-            assert kind == AR and nbytes <= 64 * 1024
+            assert kind == AR and nbytes <= 256 * 1024
         if algo == NVLS:
             assert nvls == 1
             if kind in (AR, RS, RED):
