@@ -310,9 +310,11 @@ class Communicator:
         _lib.check(self._lib.b200collTraceWrite(self._h, path.encode(), fmt.encode()), "b200collTraceWrite")
 
 
-def init_from_env(device: Optional[int] = None, port_offset: int = 17) -> Communicator:
+def init_from_env(device: Optional[int] = None, port_offset: int = 17, min_ctas: Optional[int] = None, max_ctas: Optional[int] = None) -> Communicator:
     """Build a communicator from torchrun-style variables (RANK, WORLD_SIZE, LOCAL_RANK,
-    MASTER_ADDR, MASTER_PORT): rank 0 makes the id and shares it through a TCPStore."""
+    MASTER_ADDR, MASTER_PORT): rank 0 makes the id and shares it through a TCPStore. ``max_ctas`` caps the CTAs of its
+    collectives (a communicator whose collectives overlap GEMMs wants fewer than one that runs alone); a second
+    communicator of the same job needs another ``port_offset``."""
     from torch.distributed import TCPStore
 
     rank = int(os.environ.get("RANK", "0"))
@@ -322,7 +324,7 @@ def init_from_env(device: Optional[int] = None, port_offset: int = 17) -> Commun
         device = local
     torch.cuda.set_device(device)
     if world == 1:
-        return Communicator(0, 1, get_unique_id(), device)
+        return Communicator(0, 1, get_unique_id(), device, min_ctas, max_ctas)
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
     port = int(os.environ.get("MASTER_PORT", "29500")) + port_offset
     store = TCPStore(addr, port, world, is_master=(rank == 0), wait_for_workers=False)
@@ -331,6 +333,6 @@ def init_from_env(device: Optional[int] = None, port_offset: int = 17) -> Commun
         store.set("b200coll_uid", uid)
     else:
         uid = store.get("b200coll_uid")
-    comm = Communicator(rank, world, uid, device)
+    comm = Communicator(rank, world, uid, device, min_ctas, max_ctas)
     comm._store = store  # keep the store alive as long as the communicator
     return comm

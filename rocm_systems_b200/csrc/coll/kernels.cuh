@@ -202,6 +202,11 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
   const Acc scalar = scalarOf<T>(a.scalarBits, a.scalarPtr);
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
+  // The slice this rank reduces never needs to pass through its own staging: its copy is read straight from the user's
+  // send buffer (and, in an all-reduce, the result stored straight into the user's receive buffer). That takes 1/n of the
+  // copy-in and of the copy-out away: between two ranks the local copies, not NVLink, bound the large messages. Needs
+  // whole 16-byte units (the bulk loads read whole units) and no scaling while staging.
+  const bool ownDirect = !NVLS && !a.direct && a.scaleMode != SCALE_PRE_MUL && (((uintptr_t)send) & 15) == 0 && (total & 15) == 0;
 
   // Shared-memory ring of the peer-load path (kernels without in-switch reduction only).
   extern __shared__ __align__(128) unsigned char bulkSmem[];
@@ -258,7 +263,7 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
 
   // user send -> this rank's staging, by threads t of nt
   auto copyIn = [&](const Geo& g, int t, int ntg) {
-    for (int i = 0; i < n; i++) {
+    for (int i = ownDirect ? 1 : 0; i < n; i++) {
       const int s = (rank + i) % n;
       const size_t sb = sliceBytes(g, s);
       size_t lo, hi;
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
   };
   // this rank's staging -> user recv (AllReduce; Reduce root without NVLS)
   auto copyOut = [&](const Geo& g, int t, int ntg) {
-    for (int i = 0; i < n; i++) {
+    for (int i = (ownDirect && isAR) ? 1 : 0; i < n; i++) {
       const int s = (rank + i) % n;
       const size_t sb = sliceBytes(g, s);
       size_t lo, hi;
@@ -304,7 +309,10 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
       const char* mcSrc = NVLS ? (a.direct ? a.sendMc + srcOff : c.wsMc + stOff) : nullptr;
       char* mcDst = (NVLS && isAR) ? (a.direct ? a.recvMc + msgOff : c.wsMc + stOff) : nullptr;
       // Peer bases come from the kernel parameters (constant bank), indexed by unrolled loops.
-      auto pSrc = [&](int p) -> const char* { return a.direct ? a.sendPeer[p] + srcOff : c.ws[p] + stOff; };
+      auto pSrc = [&](int p) -> const char* {
+        if (a.direct) return a.sendPeer[p] + srcOff;
+        return (ownDirect && p == rank) ? send + srcOff : c.ws[p] + stOff;
+      };
       auto pDst = [&](int p) -> char* { return a.direct ? a.recvPeer[p] + msgOff : c.ws[p] + stOff; };
       auto deliver = [&](size_t u, uint4 out) {
         if (isRS) {
@@ -315,7 +323,8 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
           } else {
 #pragma unroll
             for (int p = 0; p < kMaxRanks; p++)
-              if (p < n) st16(pDst(p) + (u << 4), out);
+              if (p < n && !(ownDirect && p == rank)) st16(pDst(p) + (u << 4), out);
+            if (ownDirect) storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
           }
         } else {  // Reduce
           if constexpr (NVLS) storeUser16<T>(recv, msgOff + (u << 4), total, out, recvAligned);
@@ -422,7 +431,9 @@ __global__ void __launch_bounds__(NVLS ? kCollThreads : kReduceThreads) kStagedR
     const bool prevOut = hasOut && off > 0;
     // With local copies to overlap, the lower half of the CTA reduces over NVLink and the upper
     // half copies; otherwise every thread reduces.
-    const int h = (more || prevOut) ? nt >> 1 : nt;
+    // (three quarters reduce when the rank's own slice bypasses staging: the copies have 1/n less to move, and between
+    // two ranks the reducing threads, not the copies, were the slower group)
+    const int h = (more || prevOut) ? (ownDirect ? (nt * 3) >> 2 : nt >> 1) : nt;
     if (tid < h) {
       reduceChunk(g, tid, h);
     } else {

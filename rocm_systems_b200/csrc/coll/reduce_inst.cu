@@ -1,5 +1,6 @@
 // Instantiates the reducing kernels for one element type. Compiled once per type with
 // -DB200_T=<type> -DB200_TN=<suffix> [-DB200_NVLS_OK=1] so the twelve types build in parallel.
+#include <atomic>
 #include "kernels.cuh"
 #include "launch.h"
 
@@ -30,14 +31,18 @@ cudaError_t B200_CAT(launchStaged_, B200_TN)(int op, bool nvls, int grid, cudaSt
 #endif
   }
   // The peer-load kernels stage tiles in a shared-memory ring larger than the default limit.
-  static const cudaError_t attr = [] {
+  // The limit is a property of (function, device): a process that drives several GPUs (one thread per GPU) sets it on each.
+  static std::atomic<bool> allowed[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !allowed[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpSum, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpProd, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpMax, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kStagedReduce<B200_T, OpMin, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
-    return e;
-  }();
-  if (attr != cudaSuccess) return attr;
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) allowed[dev].store(true, std::memory_order_release);
+  }
   switch (op) {
     case ncclSum: kStagedReduce<B200_T, OpSum, false><<<grid, kReduceThreads, kBulkSmemBytes, s>>>(c, a); break;
     case ncclProd: kStagedReduce<B200_T, OpProd, false><<<grid, kReduceThreads, kBulkSmemBytes, s>>>(c, a); break;
