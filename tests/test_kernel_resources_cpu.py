@@ -20,6 +20,9 @@ KNOWN_SPILLS = {                      # kernel -> most bytes of spill stores tol
     "kReduceScatterCast": 352,        # three unrolled variants for 2, 4 and 8 ranks in one kernel; known, listed as open
     "ep::epRoute": 4,
     "ep::groupedGemmFp8Kernel": 24,   # 128 fp32 accumulators per thread plus the per-expert tile arithmetic: a few tile-level values spill
+    # the block-scaled fp8 main loop keeps 64 fp32 accumulators, 32 freshly loaded partial sums and both scale rows live in
+    # each promotion thread; a handful of tile-level values (coordinates, limits) go to local memory once per tile
+    "gemm8::gemmFp8BlockKernel": 24, "tp8::agGemmFp8Kernel": 16, "tp8::gemmRsFp8Kernel": 16,
     "emu::kRsCast": 512, "emu::kReduce": 128, "emu::kSendRecv": 256,   # the single-GPU emulation: by-value argument blocks live in local memory
 }
 
