@@ -140,7 +140,7 @@ def run(args, clock_sampler_cls) -> None:
         for blk in model.blocks:
             fully_shard(blk, mesh=mesh, mp_policy=mp)
         fully_shard(model, mesh=mesh, mp_policy=mp)
-        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+        opt = torch.optim.AdamW(model.parameters(), lr=getattr(args, "lr", 3e-4), betas=(0.9, 0.95), weight_decay=0.1, fused=True)
         return model, opt
 
     def step(model, opt, tok, tgt):
@@ -167,6 +167,15 @@ def run(args, clock_sampler_cls) -> None:
         torch.cuda.empty_cache()
         use_ckpt = True
         model, opt = make(True)
+    if getattr(args, "loss_curve", 0):
+        curve = [float(step(model, opt, dev_tok[i % nb], dev_tgt[i % nb]).item()) for i in range(args.loss_curve)]
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "n_gpus": world, "lr": getattr(args, "lr", 3e-4), "layers": c["layers"], "activation_checkpointing": use_ckpt,
+                              "loss_curve": [round(x, 4) for x in curve]}))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+
     for i in range(args.warmup):
         step(model, opt, dev_tok[i % nb], dev_tgt[i % nb])
 

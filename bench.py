@@ -155,6 +155,8 @@ def main() -> None:
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (experiments; the headline uses the model's own)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--loss-curve", type=int, default=0, help="no timing: run this many steps from the initial weights and print every step's loss (both arms; for comparing their curves)")
+    ap.add_argument("--lr", type=float, default=3e-4, help="AdamW learning rate of both arms (the headline uses the default)")
     ap.add_argument("--staged-shards", action="store_true",
                     help="keep parameter shards and gradient buffers in ordinary memory: the collectives then stage (default: symmetric memory, zero-copy)")
     ap.add_argument("--collectives", default="b200coll", choices=["b200coll", "nccl"],
@@ -178,6 +180,7 @@ def main() -> None:
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from rocm_systems_b200 import comm as bcomm
     from rocm_systems_b200.models.llama import LlamaConfig, LlamaTrainer
+    from rocm_systems_b200.parallel.fsdp import AdamWConfig
     from rocm_systems_b200.ops import train_ops
 
     rank = int(os.environ.get("RANK", "0"))
@@ -206,7 +209,7 @@ def main() -> None:
         cfg.seq_len = args.seq
     if args.layers:
         cfg.layers = args.layers
-    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, fused_rs=args.collectives != "nccl", sym_shards=not args.staged_shards, overlap=not args.no_overlap)
+    trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, opt=AdamWConfig(lr=args.lr), fused_rs=args.collectives != "nccl", sym_shards=not args.staged_shards, overlap=not args.no_overlap)
     S, B = cfg.seq_len, 1
     nbatches = 4
     g = torch.Generator().manual_seed(1234 + rank)
@@ -219,6 +222,14 @@ def main() -> None:
         torch.cuda.synchronize()
         comm.host_barrier()
         torch.cuda.synchronize()
+
+    if args.loss_curve:
+        curve = [float(trainer.step(dev_tok[i % nbatches], dev_tgt[i % nbatches], return_loss=True)) for i in range(args.loss_curve)]
+        if rank == 0:
+            print(json.dumps({"impl": "ours", "n_gpus": world, "lr": args.lr, "layers": cfg.layers, "loss_curve": [round(x, 4) for x in curve]}))
+        sync_all()
+        comm.destroy()
+        return
 
     for i in range(args.warmup):
         trainer.step(dev_tok[i % nbatches], dev_tgt[i % nbatches], return_loss=False)

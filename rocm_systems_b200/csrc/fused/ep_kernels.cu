@@ -462,6 +462,95 @@ __global__ void __launch_bounds__(256) epCombine(const __grid_constant__ Combine
   }
 }
 
+// ---- backward pass ---------------------------------------------------------------------------------------------
+// The gradient of combine is a dispatch and the gradient of dispatch is a combine, over the SAME rows: a token's row keeps
+// the slot it reserved in the forward pass (sentSlot at its home rank, meta at the expert's rank), so nothing is reserved
+// again and no count is exchanged.
+//   epGateGrad    home rank: d gate[t, r] = <dy[t], expert output row of (t, r)>, the row pulled from its owner as in combine.
+//   epGatherGrad  expert's rank: for every row that arrived, pull dy of its token from the token's home rank and scale it
+//                 by the token's gate weight there: the gradient with respect to the expert's output row.
+// The expert GEMMs' gradients are grouped GEMMs on the transposed weights (b200collEpGroupedGemm); the input gradient is
+// epCombine with unit weights over the rows the last grouped GEMM left in the window's output region.
+struct GateGradArgs {
+  const __nv_bfloat16* dy;  // [T, hidden]
+  const int* topIdx;        // [T, k]
+  const int* sentSlot;      // [T, k]
+  float* dGate;             // [T, k]
+  int T, k;
+  char* win[kMaxRanks];
+  EpLayout L;
+};
+
+__global__ void __launch_bounds__(256) epGateGrad(const __grid_constant__ GateGradArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int H = a.L.hidden;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
+  for (int task = gw; task < a.T * a.k; task += nw) {
+    const int t = task / a.k;
+    const int slot = a.sentSlot[task], e = a.topIdx[task];
+    float dot = 0.f;
+    if (slot >= 0 && slot < a.L.cap && e >= 0 && e < a.L.nranks * a.L.expertsLocal) {
+      const int dst = e / a.L.expertsLocal, el = e - dst * a.L.expertsLocal;
+      const uint4* row = reinterpret_cast<const uint4*>(a.win[dst] + a.L.outOff + ((size_t)el * a.L.cap + slot) * H * 2);
+      const uint4* g = reinterpret_cast<const uint4*>(a.dy + (size_t)t * H);
+      for (int j = lane; j < H / 8; j += 32) {
+        const uint4 rv = ldStream16(row + j), gv = g[j];
+        const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const float2 x = __bfloat1622float2(rh[i]), y = __bfloat1622float2(gh[i]);
+          dot += x.x * y.x + x.y * y.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) a.dGate[task] = dot;
+  }
+}
+
+struct GatherGradArgs {
+  const char* dyPeer[kMaxRanks];    // every rank's dy [T, hidden] bf16 (symmetric memory)
+  const char* gatePeer[kMaxRanks];  // every rank's gate weights [T, k] fp32 (symmetric memory)
+  const char* win;                  // this rank's window
+  EpLayout L;
+  int parity, k, T;
+  __nv_bfloat16* dOut;              // [expertsLocal * cap, hidden]
+};
+
+__global__ void __launch_bounds__(256) epGatherGrad(const __grid_constant__ GatherGradArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
+  const uint32_t* cnt = (const uint32_t*)(a.win + a.L.cntOff) + (size_t)a.parity * a.L.expertsLocal;
+  const int2* meta = reinterpret_cast<const int2*>(a.win + a.L.metaOff);
+  const int H = a.L.hidden;
+  const int totalRows = a.L.expertsLocal * a.L.cap;
+  for (int rowIdx = gw; rowIdx < totalRows; rowIdx += nw) {
+    const int e = rowIdx / a.L.cap, r = rowIdx - e * a.L.cap;
+    if (r >= min((int)cnt[e], a.L.cap)) continue;
+    const int2 m = meta[rowIdx];
+    const int src = m.x, t = m.y / kMaxTopK, kk = m.y - t * kMaxTopK;
+    uint4* dst = reinterpret_cast<uint4*>(a.dOut + (size_t)rowIdx * H);
+    if (src < 0 || src >= a.L.nranks || t < 0 || t >= a.T || kk >= a.k) {  // not a row of this pass: contributes nothing
+      for (int j = lane; j < H / 8; j += 32) dst[j] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const float g = *reinterpret_cast<const float*>(a.gatePeer[src] + ((size_t)t * a.k + kk) * 4);
+    const uint4* row = reinterpret_cast<const uint4*>(a.dyPeer[src] + (size_t)t * H * 2);
+    for (int j = lane; j < H / 8; j += 32) {
+      uint4 v = ldStream16(row + j);
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h[i]);
+        h[i] = __floats2bfloat162_rn(g * f.x, g * f.y);
+      }
+      dst[j] = v;
+    }
+  }
+}
+
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(gemm::kThreads, 1) groupedGemmKernel(const __grid_constant__ gemm::Params p, GroupPolicy<BN, SWIGLU> pol) {
   extern __shared__ uint8_t smemRaw[];
@@ -695,6 +784,91 @@ ncclResult_t b200collEpCombine(ncclComm_t comm, void* winSym, const int* topIdx,
   const int tasks = T * (hidden / 1024);
   int ctas = std::max(1, std::min((tasks + 7) / 8, 8 * gemm::smCount()));
   epCombine<<<ctas, 256, 0, stream>>>(a);
+  BCUDA(cudaGetLastError());
+  return ncclSuccess;
+}
+
+// ---- backward pass ---------------------------------------------------------------------------------------------
+static ncclResult_t epLatestParity(const char* what, Comm* c, const void* winSym, int* parity) {
+  std::lock_guard<std::mutex> lk(gEpMu);
+  auto it = gEp.find(std::make_pair(c, winSym));
+  if (it == gEp.end() || it->second.calls == 0) BFAIL(ncclInvalidUsage, "%s: no dispatch has run on this window", what);
+  *parity = (int)((it->second.calls - 1) & 1);
+  return ncclSuccess;
+}
+
+// out[rows of expert e] = a[rows of expert e] * w[e]^T for every local expert, over the rows of the latest dispatch:
+// a [expertsLocal * cap, K], w [expertsLocal * wRows, K], out [expertsLocal * cap, wRows] (nullptr: the window's output
+// region, which needs wRows == hidden). Row blocks without tokens are skipped. The three GEMMs of the experts' backward
+// pass (and the recomputation of the gate/up pre-activations) are calls of this with transposed weights.
+ncclResult_t b200collEpGroupedGemm(ncclComm_t comm, void* winSym, const void* a, const void* w, void* out, int wRows, int K, int expertsLocal, int cap,
+                                   int hidden, int ffn, cudaStream_t stream) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  BCHECK(checkShape(expertsLocal, cap, hidden, ffn, 1));
+  if (!winSym || !a || !w) BFAIL(ncclInvalidArgument, "b200collEpGroupedGemm: null buffer");
+  if (wRows <= 0 || wRows % 128 || K <= 0 || K % 8) BFAIL(ncclInvalidArgument, "b200collEpGroupedGemm: weight rows %% 128 and K %% 8 must be 0");
+  if (!out && wRows != hidden) BFAIL(ncclInvalidArgument, "b200collEpGroupedGemm: the window's output region holds rows of `hidden` columns");
+  EpGuard g(c->cudaDev);
+  const EpLayout L = makeLayout(c->nranks, expertsLocal, cap, hidden, ffn);
+  int parity;
+  BCHECK(epLatestParity("b200collEpGroupedGemm", c, winSym, &parity));
+  const uint32_t* cnt = (const uint32_t*)((const char*)winSym + L.cntOff) + (size_t)parity * expertsLocal;
+  const int rows = expertsLocal * cap;
+  const int bn = wRows % 256 == 0 ? 256 : 128;
+  __nv_bfloat16* o = out ? (__nv_bfloat16*)out : (__nv_bfloat16*)((char*)winSym + L.outOff);
+  gemm::Params p{};
+  if (!gemm::makeTileMap(&p.mapA, a, rows, K, K, gemm::BM, 2) || !gemm::makeTileMap(&p.mapB, w, (uint64_t)expertsLocal * wRows, K, K, bn, 2))
+    BFAIL(ncclInvalidArgument, "b200collEpGroupedGemm: misaligned operands");
+  p.M = rows; p.N = wRows; p.K = K; p.tilesM = rows / gemm::BM; p.tilesN = wRows / bn; p.err = gemm::errWord();
+  cudaError_t e;
+  if (bn == 256) e = launchGrouped(p, GroupPolicy<256, false>{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, wRows, o, wRows, wRows}, stream);
+  else e = launchGrouped(p, GroupPolicy<128, false>{cnt, expertsLocal, nullptr, cap, cap / gemm::BM, wRows, o, wRows, wRows}, stream);
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200collEpGroupedGemm: launch failed: %s", cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
+// d gate[t, r] = <dy[t], output row of expert (t, r)> at the tokens' home rank; the forward pass's expert outputs must still be
+// in the window (no grouped GEMM has written its output region since the combine).
+ncclResult_t b200collEpGateGrad(ncclComm_t comm, void* winSym, const void* dy, const int* topIdx, const int* sentSlot, float* dGate, int T, int k,
+                                int expertsLocal, int cap, int hidden, int ffn, cudaStream_t stream) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  BCHECK(checkShape(expertsLocal, cap, hidden, ffn, k));
+  if (!winSym || !dy || !topIdx || !sentSlot || !dGate) BFAIL(ncclInvalidArgument, "b200collEpGateGrad: null buffer");
+  EpGuard g(c->cudaDev);
+  GateGradArgs a{};
+  a.L = makeLayout(c->nranks, expertsLocal, cap, hidden, ffn);
+  if (!epPeers(c, winSym, a.L.total, a.win)) BFAIL(ncclInvalidUsage, "b200collEpGateGrad: the window must be symmetric memory");
+  a.dy = (const __nv_bfloat16*)dy; a.topIdx = topIdx; a.sentSlot = sentSlot; a.dGate = dGate; a.T = T; a.k = k;
+  if (T == 0) return ncclSuccess;
+  const int ctas = std::max(1, std::min((T * k + 7) / 8, 8 * gemm::smCount()));
+  epGateGrad<<<ctas, 256, 0, stream>>>(a);
+  BCUDA(cudaGetLastError());
+  return ncclSuccess;
+}
+
+// Gradient with respect to the expert output rows, gathered at the experts' rank: dOut[row] = gate * dy[token] for every row
+// of the latest dispatch. dySym [T, hidden] bf16 and gateSym [T, k] fp32 are symmetric memory that every rank filled before
+// this call on its stream; a barrier inside orders those writes (and every rank's epGateGrad) before the pulls.
+ncclResult_t b200collEpGatherGrad(ncclComm_t comm, void* winSym, const void* dySym, const void* gateSym, void* dOut, int T, int k, int expertsLocal,
+                                  int cap, int hidden, int ffn, cudaStream_t stream) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  BCHECK(checkShape(expertsLocal, cap, hidden, ffn, k));
+  if (!winSym || !dySym || !gateSym || !dOut) BFAIL(ncclInvalidArgument, "b200collEpGatherGrad: null buffer");
+  EpGuard g(c->cudaDev);
+  GatherGradArgs a{};
+  a.L = makeLayout(c->nranks, expertsLocal, cap, hidden, ffn);
+  char* dyPeer[kMaxRanks];
+  char* gatePeer[kMaxRanks];
+  if (!epPeers(c, dySym, (size_t)T * hidden * 2, dyPeer) || !epPeers(c, gateSym, (size_t)T * k * 4, gatePeer))
+    BFAIL(ncclInvalidUsage, "b200collEpGatherGrad: dy and the gate weights must lie in symmetric memory");
+  for (int r = 0; r < c->nranks; r++) { a.dyPeer[r] = dyPeer[r]; a.gatePeer[r] = gatePeer[r]; }
+  BCHECK(epLatestParity("b200collEpGatherGrad", c, winSym, &a.parity));
+  a.win = (const char*)winSym; a.k = k; a.T = T; a.dOut = (__nv_bfloat16*)dOut;
+  if (c->nranks > 1) BCHECK(b200collBarrier(comm, stream));
+  epGatherGrad<<<4 * gemm::smCount(), 256, 0, stream>>>(a);
   BCUDA(cudaGetLastError());
   return ncclSuccess;
 }

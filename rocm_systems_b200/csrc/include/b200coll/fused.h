@@ -80,6 +80,23 @@ ncclResult_t b200collEpCombine(ncclComm_t comm, void* winSym, const int* topIdx,
 ncclResult_t b200collEpCounts(ncclComm_t comm, void* winSym, int expertsLocal, int cap, int hidden, int ffn, unsigned int* countsHost,
                               int* droppedHost, cudaStream_t stream);
 
+/* Backward pass of the layer, on the rows and slots of the latest dispatch (nothing is reserved or counted again):
+ *   GateGrad     dGate [T, k] fp32 = <dy[t], expert output row of (t, k)>, at the tokens' home rank; run it before any
+ *                grouped GEMM writes the window's output region again.
+ *   GatherGrad   at the experts' rank: dOut [expertsLocal * cap, hidden] bf16 = gate * dy of each arrived row's token, pulled
+ *                from the token's home rank. dySym [T, hidden] bf16 and gateSym [T, k] fp32 are symmetric memory that every
+ *                rank filled earlier on its stream; a barrier inside orders them before the pulls.
+ *   GroupedGemm  out[rows of e] = a[rows of e] * w[e]^T per local expert (a [expertsLocal * cap, K], w [expertsLocal * wRows, K],
+ *                out [expertsLocal * cap, wRows]; nullptr: the window's output region, wRows == hidden), skipping row blocks
+ *                without tokens: with transposed weights, the experts' input-gradient GEMMs.
+ * The input gradient is then b200collEpCombine with unit weights. */
+ncclResult_t b200collEpGateGrad(ncclComm_t comm, void* winSym, const void* dy, const int* topIdx, const int* sentSlot, float* dGate, int T, int k,
+                                int expertsLocal, int cap, int hidden, int ffn, cudaStream_t stream);
+ncclResult_t b200collEpGatherGrad(ncclComm_t comm, void* winSym, const void* dySym, const void* gateSym, void* dOut, int T, int k, int expertsLocal,
+                                  int cap, int hidden, int ffn, cudaStream_t stream);
+ncclResult_t b200collEpGroupedGemm(ncclComm_t comm, void* winSym, const void* a, const void* w, void* out, int wRows, int K, int expertsLocal, int cap,
+                                   int hidden, int ffn, cudaStream_t stream);
+
 /* ---- RMSNorm backward for callers that may not allocate device memory (no counterpart in the reference) -------------
  * dx [T, H] and dw [H] (both bf16) of y = x * rstd * w; the fp32 accumulator of dw is a fixed 32 KiB array inside the
  * library instead of caller memory, so the call makes no cudaMalloc / cudaFree. H: a multiple of 8, at most 8192 (wider

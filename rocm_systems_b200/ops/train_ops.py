@@ -153,6 +153,18 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(gu)
 
 
+def swiglu_bwd(gu: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
+    """Gradient of :func:`swiglu` with respect to ``gu`` given the gradient of its output (no autograd graph: for
+    callers that schedule their backward pass themselves)."""
+    gu, dout = _bf16c(gu), _bf16c(dout)
+    F = gu.shape[-1] // 2
+    T = gu.numel() // (2 * F)
+    assert dout.numel() == T * F
+    dgu = torch.empty_like(gu)
+    _ck(_lib_ops().b200ops_swiglu_bwd(gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), T, F, _s()), "swiglu_bwd")
+    return dgu
+
+
 # ---- loss, optimizer, embedding, casts (no autograd: the engine calls them explicitly) ---------------------
 def cross_entropy_inplace(logits: torch.Tensor, targets: torch.Tensor, grad_scale: float) -> torch.Tensor:
     """Per-row loss of ``logits`` [T, V] (bf16); ``logits`` is overwritten with d(loss)/d(logits) * grad_scale."""

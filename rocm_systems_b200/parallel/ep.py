@@ -15,7 +15,7 @@ import torch
 
 from .. import _lib
 from ..ops import train_ops
-from .tp import interleave_gate_up
+from .tp import deinterleave_gate_up, interleave_gate_up
 
 _done = False
 
@@ -33,6 +33,9 @@ def _lib_ep():
         lib.b200collEpExpertsFp8.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
         lib.b200collEpCombine.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
         lib.b200collEpCounts.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp]
+        lib.b200collEpGateGrad.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+        lib.b200collEpGatherGrad.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+        lib.b200collEpGroupedGemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
         _done = True
     return lib
 
@@ -86,6 +89,12 @@ class MoELayer:
 
     ``fp8_experts=True`` quantises the gate/up weights once per 128 x 128 block and runs the first expert GEMM directly on
     the fp8 rows that arrived (``b200collEpExpertsFp8``): no dequantisation pass, no bf16 copy of the received activations.
+
+    ``backward(dy)`` (bf16 experts) returns the gradients with respect to the tokens and the router logits and leaves the
+    expert weights' gradients in ``grads``. It reuses the rows and slots of the forward dispatch: the gradient of combine is
+    a gather of ``gate * dy`` at the experts' ranks, the gradient of dispatch is a combine with unit weights, and the
+    experts' input-gradient GEMMs are grouped GEMMs on transposed weights. The fp8 transport of the forward pass is treated
+    as the identity (straight-through).
     """
 
     def __init__(self, comm, experts_local: int, hidden: int, ffn: int, top_k: int, tokens: int, capacity: int = 0, std: float = 0.02, seed: int = 0,
@@ -123,6 +132,10 @@ class MoELayer:
         self.top_w = torch.empty(tokens, top_k, dtype=torch.float32, device=dev)
         self.sent = torch.empty(tokens, top_k, dtype=torch.int32, device=dev)
         self.out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+        self.tile = tile
+        self._dy_sym = None      # backward buffers, made by the first backward()
+        self._w2_t = self._w13_t = None
+        self.grads: dict = {}
 
     def _args(self):
         return (self.el, self.cap, self.hidden, self.ffn)
@@ -171,6 +184,86 @@ class MoELayer:
         _lib.check(_lib_ep().b200collEpCounts(self.comm.handle, self._win.ptr, *self._args(), c, ctypes.byref(d), s), "b200collEpCounts")
         return list(c), d.value
 
+    # ---- backward ------------------------------------------------------------------------------------------
+    def weights_changed(self) -> None:
+        """Call after ``w13`` or ``w2`` was updated in place: the transposed copies used by ``backward`` are rebuilt."""
+        self._w2_t = self._w13_t = None
+
+    def _grouped(self, a: torch.Tensor, w: torch.Tensor, out, w_rows: int, K: int) -> None:
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib_ep().b200collEpGroupedGemm(self.comm.handle, self._win.ptr, a.data_ptr(), w.data_ptr(), out.data_ptr() if out is not None else None,
+                                                   w_rows, K, *self._args(), s), "b200collEpGroupedGemm")
+        train_ops.LAUNCHES += 1
+
+    def backward(self, dy: torch.Tensor):
+        """Gradients of the latest ``forward`` (bf16 experts), on the current stream: returns ``(dx [T, hidden] bf16,
+        d_logits [T, E] fp32)``; ``grads["w13"]`` ([experts_local * 2 ffn, hidden], interleaved like ``w13``) and
+        ``grads["w2"]`` ([experts_local * hidden, ffn]) hold the expert weights' gradients.
+
+        One host read per call: the number of rows each local expert received (the reduction length of its two
+        weight-gradient GEMMs); everything else is queued without a round trip."""
+        assert not self.fp8_experts, "backward is built for the bf16 expert GEMMs (the fp8 form keeps no bf16 copy of the received rows)"
+        assert dy.dtype == torch.bfloat16 and dy.shape == (self.T, self.hidden)
+        lib = _lib_ep()
+        s = torch.cuda.current_stream().cuda_stream
+        el, cap, H, f, T, k = self.el, self.cap, self.hidden, self.ffn, self.T, self.k
+        rows = el * cap
+        dev = self.device
+        if self._dy_sym is None:
+            self._dy_sym = self.comm.sym_alloc(T * H * 2)
+            self._gate_sym = self.comm.sym_alloc(T * k * 4)
+            self.dy_s = self._dy_sym.tensor((T, H), torch.bfloat16)
+            self.gate_s = self._gate_sym.tensor((T, k), torch.float32)
+            self.d_out = torch.zeros(rows, H, dtype=torch.bfloat16, device=dev)
+            self.d_act = torch.zeros(rows, f, dtype=torch.bfloat16, device=dev)
+            self.gu = torch.zeros(rows, 2 * f, dtype=torch.bfloat16, device=dev)
+            self.d_gate = torch.empty(T, k, dtype=torch.float32, device=dev)
+            self.ones = torch.ones(T, k, dtype=torch.float32, device=dev)
+            self.dx = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        if self._w2_t is None:
+            self._w2_t = self.w2.view(el, H, f).transpose(1, 2).reshape(el * f, H).contiguous()          # per expert [ffn, hidden]
+            self._w13_t = self.w13.view(el, 2 * f, H).transpose(1, 2).reshape(el * H, 2 * f).contiguous()  # per expert [hidden, 2 ffn]
+        self.dy_s.copy_(dy)
+        self.gate_s.copy_(self.top_w)
+        # d gate, from the forward pass's expert outputs (still in the window's output region)
+        _lib.check(lib.b200collEpGateGrad(self.comm.handle, self._win.ptr, self.dy_s.data_ptr(), self.top_idx.data_ptr(), self.sent.data_ptr(),
+                                          self.d_gate.data_ptr(), T, k, *self._args(), s), "b200collEpGateGrad")
+        # gradient of combine: gate * dy of every arrived row, pulled to the expert's rank
+        _lib.check(lib.b200collEpGatherGrad(self.comm.handle, self._win.ptr, self._dy_sym.ptr, self._gate_sym.ptr, self.d_out.data_ptr(), T, k,
+                                            *self._args(), s), "b200collEpGatherGrad")
+        train_ops.LAUNCHES += 3
+        self._grouped(self.d_out, self._w2_t, self.d_act, f, H)            # d_act = d_out @ w2
+        self._grouped(self.xb, self.w13, self.gu, 2 * f, H)                # gate/up pre-activations again (forward kept act only)
+        nt = 2 * f // self.tile
+        dgu = train_ops.swiglu_bwd(self.gu.view(rows * nt, self.tile), self.d_act.view(rows * nt, self.tile // 2)).view(rows, 2 * f)
+        self._grouped(dgu, self._w13_t, None, H, 2 * f)                    # d(rows) = d_gu @ w13, into the window's output region
+        counts, _ = self.counts()
+        dw13 = torch.zeros(el * 2 * f, H, dtype=torch.bfloat16, device=dev)
+        dw2 = torch.zeros(el * H, f, dtype=torch.bfloat16, device=dev)
+        for e in range(el):
+            c = min(int(counts[e]), cap)
+            if c == 0:
+                continue
+            r0 = e * cap
+            train_ops.gemm(self.d_out[r0:r0 + c].t(), self.act[r0:r0 + c].t(), out=dw2[e * H:(e + 1) * H])
+            train_ops.gemm(dgu[r0:r0 + c].t(), self.xb[r0:r0 + c].t(), out=dw13[e * 2 * f:(e + 1) * 2 * f])
+        self.grads["w13"], self.grads["w2"] = dw13, dw2
+        # gradient of dispatch: every token sums the rows of its k experts (a combine with unit weights)
+        _lib.check(lib.b200collEpCombine(self.comm.handle, self._win.ptr, self.top_idx.data_ptr(), self.ones.data_ptr(), self.sent.data_ptr(),
+                                         self.dx.data_ptr(), T, k, *self._args(), s), "b200collEpCombine (backward)")
+        train_ops.LAUNCHES += 2
+        # router: the gate weights are the softmax over the selected logits
+        p = self.top_w
+        d_sel = p * (self.d_gate - (self.d_gate * p).sum(-1, keepdim=True))
+        d_logits = torch.zeros(T, self.E, dtype=torch.float32, device=dev).scatter_(1, self.top_idx.long(), d_sel)
+        return self.dx, d_logits
+
+    def expert_weight_grads(self):
+        """``grads`` as (d w_gate, d w_up [experts_local, ffn, hidden], d w_down [experts_local, hidden, ffn])."""
+        el, f, H = self.el, self.ffn, self.hidden
+        parts = [deinterleave_gate_up(self.grads["w13"][e * 2 * f:(e + 1) * 2 * f], self.tile) for e in range(el)]
+        return (torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), self.grads["w2"].view(el, H, f))
+
     # ---- plain PyTorch oracle ---------------------------------------------------------------------------
     def reference_forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         n, el, k, T, H = self.n, self.el, self.k, self.T, self.hidden
@@ -214,3 +307,6 @@ class MoELayer:
     def free(self) -> None:
         torch.cuda.synchronize()
         self._win.free()
+        if self._dy_sym is not None:
+            self._dy_sym.free()
+            self._gate_sym.free()

@@ -50,10 +50,20 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, tile: int = 256
     return torch.stack([g, u], dim=1).reshape(2 * F, K).contiguous()
 
 
+def deinterleave_gate_up(w13: torch.Tensor, tile: int = 256):
+    """Inverse of :func:`interleave_gate_up`: (gate rows, up rows)."""
+    F2, K = w13.shape
+    h = tile // 2
+    v = w13.view(F2 // tile, 2, h, K)
+    return v[:, 0].reshape(F2 // 2, K), v[:, 1].reshape(F2 // 2, K)
+
+
 class TensorParallelMLP:
     """The MLP half of a tensor-parallel transformer layer with sequence-parallel activations: gate and up projections
     (column-parallel, interleaved per tile) inside the all-gather with the SwiGLU in the epilogue, down projection
-    (row-parallel) inside the reduce-scatter. Forward only; weights are random.
+    (row-parallel) inside the reduce-scatter. ``backward`` runs the same two fused kernels on the transposed weights
+    (the gradient of a reduce-scatter is an all-gather and the other way round) and leaves the weight gradients of this
+    rank's shards in ``grads``; weights are random.
     """
 
     def __init__(self, comm, rows_per_rank: int, hidden: int, ffn_local: int, device=None, std: float = 0.02, seed: int = 0,
@@ -77,10 +87,54 @@ class TensorParallelMLP:
         self._ws = comm.sym_alloc(int(lib.b200collGemmRsWorkspaceBytes(rows_per_rank, hidden, self.n)))
         self.act = torch.empty(M, ffn_local, dtype=torch.bfloat16, device=self.device)
         self.y = torch.empty(rows_per_rank, hidden, dtype=torch.bfloat16, device=self.device)
+        self._dy_sym = self._ws_b = None          # backward buffers, made by the first backward()
+        self._w2_t = self._w13_t = None           # transposed weights (the fused kernels read B with the reduction index contiguous)
+        self.grads: dict = {}
 
     def my_rows(self) -> torch.Tensor:
         """Where this rank writes its rows of the activations before ``forward``."""
         return self.x_full[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def weights_changed(self) -> None:
+        """Call after ``w13`` or ``w2`` was updated in place: the transposed copies used by ``backward`` are rebuilt."""
+        self._w2_t = self._w13_t = None
+        self.w_gate, self.w_up = deinterleave_gate_up(self.w13, self.tile)
+
+    def backward(self, dy_local: torch.Tensor) -> torch.Tensor:
+        """Gradients of the latest ``forward`` (its gathered input rows and its ``act`` must still be in place), on the
+        current stream.
+
+            d_act = all-gather(dy) @ w2          one fused kernel (all-gather -> GEMM); also leaves dy of all tokens here
+            gate/up pre-activations              recomputed from the gathered input with a local GEMM (not kept by forward)
+            d_gu  = SwiGLU'(gu) * d_act          element-wise, in the per-tile interleaved layout of w13
+            dx    = reduce-scatter(d_gu @ w13)   one fused kernel (GEMM -> reduce-scatter)
+            dw2   = dy^T @ act,  dw13 = d_gu^T @ x     local GEMMs over all tokens: this rank owns these shards alone
+
+        Returns this rank's rows of dx; ``grads["w13"]`` (interleaved like ``w13``) and ``grads["w2"]`` hold the weight gradients."""
+        lib = _lib_tp()
+        s = torch.cuda.current_stream().cuda_stream
+        M = self.n * self.rows
+        if self._dy_sym is None:
+            self._dy_sym = self.comm.sym_alloc(M * self.hidden * 2)
+            self.dy_full = self._dy_sym.tensor((M, self.hidden), torch.bfloat16)
+            self._ws_b = self.comm.sym_alloc(int(lib.b200collGemmRsWorkspaceBytes(self.rows, self.hidden, self.n)))
+            self.dact = torch.empty(M, self.f, dtype=torch.bfloat16, device=self.device)
+            self.dx = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        if self._w2_t is None:
+            self._w2_t = self.w2.t().contiguous()      # [ffn_local, hidden]
+            self._w13_t = self.w13.t().contiguous()    # [hidden, 2 ffn_local]
+        self.dy_full[self.rank * self.rows:(self.rank + 1) * self.rows].copy_(dy_local)
+        _lib.check(lib.b200collAgGemm(self.comm.handle, self.dy_full.data_ptr(), self._w2_t.data_ptr(), self.dact.data_ptr(), self.rows, self.f,
+                                      self.hidden, 0, self.comm_ctas, s), "b200collAgGemm (backward)")
+        gu = train_ops.gemm(self.x_full, self.w13)                                  # [M, 2 ffn_local], gate and up interleaved per tile
+        nt = 2 * self.f // self.tile
+        dgu = train_ops.swiglu_bwd(gu.view(M * nt, self.tile), self.dact.view(M * nt, self.tile // 2)).view(M, 2 * self.f)
+        _lib.check(lib.b200collGemmRs(self.comm.handle, dgu.data_ptr(), self._w13_t.data_ptr(), self._ws_b.ptr, self.dx.data_ptr(), self.rows,
+                                      self.hidden, 2 * self.f, s), "b200collGemmRs (backward)")
+        train_ops.LAUNCHES += 2
+        self.grads["w2"] = train_ops.gemm(self.dy_full.t(), self.act.t())           # [hidden, ffn_local]
+        self.grads["w13"] = train_ops.gemm(dgu.t(), self.x_full.t())                # [2 ffn_local, hidden]
+        return self.dx
 
     def ag_gemm(self, stream=None) -> torch.Tensor:
         """all-gather(x) @ w13^T with SwiGLU: ``act`` [M, ffn_local]. This rank's rows must be in ``my_rows()``."""
@@ -121,6 +175,9 @@ class TensorParallelMLP:
         torch.cuda.synchronize()
         self._x_sym.free()
         self._ws.free()
+        if self._dy_sym is not None:
+            self._dy_sym.free()
+            self._ws_b.free()
 
 
 def fp8_mlp_partial_oracle(x_full: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
@@ -253,19 +310,69 @@ class TensorParallelAttention:
         self.qkv = torch.empty(self.M, qkv_rows, dtype=torch.bfloat16, device=self.device)
         self.ctx = torch.empty(self.M, self.hq * self.d, dtype=torch.bfloat16, device=self.device)
         self.y = torch.empty(rows_per_rank, hidden, dtype=torch.bfloat16, device=self.device)
+        self._dy_sym = self._ws_b = None          # backward buffers, made by the first backward()
+        self._w_o_t = self._w_qkv_t = None
+        self.grads: dict = {}
 
     def my_rows(self) -> torch.Tensor:
         return self.x_full[self.rank * self.rows:(self.rank + 1) * self.rows]
 
-    def _attend(self, qkv: torch.Tensor, out: torch.Tensor) -> None:
-        """Rotary embedding and causal attention of this rank's heads over whole sequences: qkv [M, (hq + 2 hkv) d] -> out [M, hq d]."""
+    def _attention(self, qkv: torch.Tensor) -> torch.Tensor:
+        """Rotary embedding and causal attention of this rank's heads over whole sequences: qkv [M, (hq + 2 hkv) d] ->
+        [M, hq d]. Differentiable (the rotary op and the attention both carry their backward)."""
         B = self.M // self.seq
         t = train_ops.rope_(qkv.view(self.M, self.hq + 2 * self.hkv, self.d), self.rope, self.hq + self.hkv)
         q = t[:, :self.hq].reshape(B, self.seq, self.hq, self.d).transpose(1, 2)
         k = t[:, self.hq:self.hq + self.hkv].reshape(B, self.seq, self.hkv, self.d).transpose(1, 2)
         v = t[:, self.hq + self.hkv:].reshape(B, self.seq, self.hkv, self.d).transpose(1, 2)
         o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.hq != self.hkv)
-        out.copy_(o.transpose(1, 2).reshape(self.M, self.hq * self.d))
+        return o.transpose(1, 2).reshape(self.M, self.hq * self.d)
+
+    def _attend(self, qkv: torch.Tensor, out: torch.Tensor) -> None:
+        with torch.no_grad():
+            out.copy_(self._attention(qkv))
+
+    def weights_changed(self) -> None:
+        """Call after ``w_qkv`` or ``w_o`` was updated in place: the transposed copies used by ``backward`` are rebuilt."""
+        self._w_o_t = self._w_qkv_t = None
+
+    def backward(self, dy_local: torch.Tensor) -> torch.Tensor:
+        """Gradients of the latest ``forward`` (its gathered input rows and its ``qkv`` must still be in place), on the
+        current stream.
+
+            d_ctx = all-gather(dy) @ w_o         one fused kernel (all-gather -> GEMM); also leaves dy of all tokens here
+            d_qkv                                backward of the local rotary embedding + attention, recomputed from ``qkv``
+            dx    = reduce-scatter(d_qkv @ w_qkv)   one fused kernel (GEMM -> reduce-scatter)
+            dw_o  = dy^T @ ctx,  dw_qkv = d_qkv^T @ x     local GEMMs over all tokens
+
+        Returns this rank's rows of dx; ``grads["w_qkv"]`` and ``grads["w_o"]`` hold the weight gradients."""
+        lib = _lib_tp()
+        s = torch.cuda.current_stream().cuda_stream
+        cd = self.hq * self.d
+        if self._dy_sym is None:
+            assert cd % 128 == 0, "the fused kernels want this rank's head columns to be a multiple of 128"
+            self._dy_sym = self.comm.sym_alloc(self.M * self.hidden * 2)
+            self.dy_full = self._dy_sym.tensor((self.M, self.hidden), torch.bfloat16)
+            self._ws_b = self.comm.sym_alloc(int(lib.b200collGemmRsWorkspaceBytes(self.rows, self.hidden, self.n)))
+            self.dctx = torch.empty(self.M, cd, dtype=torch.bfloat16, device=self.device)
+            self.dx = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        if self._w_o_t is None:
+            self._w_o_t = self.w_o.t().contiguous()        # [hq d, hidden]
+            self._w_qkv_t = self.w_qkv.t().contiguous()    # [hidden, (hq + 2 hkv) d]
+        self.dy_full[self.rank * self.rows:(self.rank + 1) * self.rows].copy_(dy_local)
+        _lib.check(lib.b200collAgGemm(self.comm.handle, self.dy_full.data_ptr(), self._w_o_t.data_ptr(), self.dctx.data_ptr(), self.rows, cd,
+                                      self.hidden, 0, self.comm_ctas, s), "b200collAgGemm (backward)")
+        with torch.enable_grad():
+            leaf = self.qkv.detach().requires_grad_(True)
+            ctx = self._attention(leaf)
+            (dqkv,) = torch.autograd.grad(ctx, leaf, self.dctx)
+        dqkv = dqkv.contiguous()
+        _lib.check(lib.b200collGemmRs(self.comm.handle, dqkv.data_ptr(), self._w_qkv_t.data_ptr(), self._ws_b.ptr, self.dx.data_ptr(), self.rows,
+                                      self.hidden, self.w_qkv.shape[0], s), "b200collGemmRs (backward)")
+        train_ops.LAUNCHES += 2
+        self.grads["w_o"] = train_ops.gemm(self.dy_full.t(), self.ctx.t())          # [hidden, hq d]
+        self.grads["w_qkv"] = train_ops.gemm(dqkv.t(), self.x_full.t())             # [(hq + 2 hkv) d, hidden]
+        return self.dx
 
     def forward(self, x_local: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         if x_local is not None:
@@ -296,6 +403,9 @@ class TensorParallelAttention:
         torch.cuda.synchronize()
         self._x_sym.free()
         self._ws.free()
+        if self._dy_sym is not None:
+            self._dy_sym.free()
+            self._ws_b.free()
 
 
 class TensorParallelLayer:
@@ -304,8 +414,8 @@ class TensorParallelLayer:
         h = x + attention(rmsnorm(x));  y = h + mlp(rmsnorm(h))
 
     The residual stream and both norms live on this rank's ``rows_per_rank`` tokens only; the all-gather in front of each
-    half and the reduce-scatter behind it are inside the halves' GEMM kernels. Forward only (inference and the
-    forward-pass benchmark); weights are random."""
+    half and the reduce-scatter behind it are inside the halves' GEMM kernels, in the backward pass as in the forward
+    pass (four fused kernels each way and one small all-reduce per norm weight). Weights are random."""
 
     def __init__(self, comm, rows_per_rank: int, hidden: int, heads: int, kv_heads: int, ffn: int, seq_len: int, device=None, eps: float = 1e-5,
                  seed: int = 0, comm_ctas: int = 0):
@@ -315,10 +425,32 @@ class TensorParallelLayer:
         self.norm1 = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
         self.norm2 = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
         self.eps = eps
+        self.comm = comm
+        self.grads: dict = {}
+        self._saved = None
 
     def forward(self, x_local: torch.Tensor) -> torch.Tensor:
-        h = x_local + self.attn.forward(train_ops.rmsnorm(x_local, self.norm1, self.eps))
-        return h + self.mlp.forward(train_ops.rmsnorm(h, self.norm2, self.eps))
+        with torch.no_grad():
+            h = x_local + self.attn.forward(train_ops.rmsnorm(x_local, self.norm1, self.eps))
+            self._saved = (x_local, h)
+            return h + self.mlp.forward(train_ops.rmsnorm(h, self.norm2, self.eps))
+
+    def _norm_backward(self, x: torch.Tensor, w: torch.Tensor, d: torch.Tensor, name: str) -> torch.Tensor:
+        with torch.enable_grad():
+            xl, wl = x.detach().requires_grad_(True), w.detach().requires_grad_(True)
+            dx, dw = torch.autograd.grad(train_ops.rmsnorm(xl, wl, self.eps), (xl, wl), d)
+        dw = dw.float()
+        if self.comm.nranks > 1:  # every rank saw its own rows only: the norm weights are replicated, their gradient is the sum
+            self.comm.all_reduce(dw, op="sum")
+        self.grads[name] = dw
+        return dx
+
+    def backward(self, dy_local: torch.Tensor) -> torch.Tensor:
+        """Gradients of the latest ``forward``: returns this rank's rows of dx. Weight gradients land in ``attn.grads``,
+        ``mlp.grads`` and (summed over the ranks, fp32) ``grads["norm1"]`` / ``grads["norm2"]``."""
+        x, h = self._saved
+        dh = dy_local + self._norm_backward(h, self.norm2, self.mlp.backward(dy_local), "norm2")
+        return dh + self._norm_backward(x, self.norm1, self.attn.backward(dh), "norm1")
 
     def reference_forward(self, x_local: torch.Tensor) -> torch.Tensor:
         h = x_local + self.attn.reference_forward(train_ops.rmsnorm(x_local, self.norm1, self.eps))

@@ -48,8 +48,23 @@ def test_tp_fused_mlp_fp8_matches_oracle(nproc):
 
 
 @pytest.mark.parametrize("nproc", [2, 8])
+def test_tp_layer_forward_and_backward_match_float64_autograd(nproc):
+    """A whole tensor-parallel layer (attention and MLP halves, four fused kernels each way) and the MLP half alone at a
+    second shape: outputs, input gradients, every weight shard's gradient and the norm-weight gradients."""
+    _launch(nproc, 29740 + nproc, "tp_layer_worker.py", "--hidden", "2048", "--heads", "16", "--kv-heads", "8", "--ffn", "2048")
+    _launch(nproc, 29750 + nproc, "tp_layer_worker.py", "--what", "mlp", "--rows", "512", "--hidden", "1024", "--ffn", "4096", "--comm-ctas", "-1")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
 def test_ep_dispatch_experts_combine(nproc):
     _launch(nproc, 29830 + nproc, "ep_worker.py")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_ep_backward_matches_float64_autograd(nproc):
+    """Token, router-logit and expert-weight gradients of the layer (gate-gradient kernel, gradient gather, grouped GEMMs on
+    transposed weights, unit-weight combine) against autograd of the unsharded layer."""
+    _launch(nproc, 29760 + nproc, "ep_worker.py", "--backward")
 
 
 @pytest.mark.parametrize("nproc", [2, 8])

@@ -24,8 +24,18 @@ def test_tensor_parallel_mlp_fp8_on_one_rank():
     _launch(1, 29886, "tp_worker.py", "--fp8", "--rows", "512", "--hidden", "2048", "--ffn", "1024", timeout=600)
 
 
+def test_tensor_parallel_layer_forward_and_backward_on_one_rank():
+    """Forward and backward of the whole tensor-parallel layer, and of the MLP half at a second shape, against float64 autograd."""
+    _launch(1, 29888, "tp_layer_worker.py", timeout=600)
+    _launch(1, 29889, "tp_layer_worker.py", "--what", "mlp", "--rows", "512", "--hidden", "2048", "--ffn", "1024", timeout=600)
+
+
 def test_expert_parallel_layer_on_one_rank():
     _launch(1, 29883, "ep_worker.py", "--experts-local", "32", timeout=600)
+
+
+def test_expert_parallel_layer_backward_on_one_rank():
+    _launch(1, 29880, "ep_worker.py", "--experts-local", "32", "--backward", timeout=600)
 
 
 def test_expert_parallel_layer_with_fp8_experts_on_one_rank():

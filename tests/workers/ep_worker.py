@@ -11,7 +11,7 @@ import torch  # noqa: E402
 
 from rocm_systems_b200.comm import init_from_env  # noqa: E402
 from rocm_systems_b200.ops import train_ops  # noqa: E402
-from rocm_systems_b200.parallel.ep import MoELayer  # noqa: E402
+from rocm_systems_b200.parallel.ep import MoELayer, dequantize_e4m3_per128, quantize_e4m3_per128  # noqa: E402
 
 
 def dev_ms(fn, comm, warmup=2, iters=5):
@@ -30,8 +30,58 @@ def dev_ms(fn, comm, warmup=2, iters=5):
     return max(float.fromhex(p.decode().strip()) for p in parts)
 
 
+def gather(comm, t):
+    """All ranks' copies of ``t`` (same shape everywhere) concatenated along the first axis."""
+    t = t.contiguous()
+    out = torch.empty(comm.nranks * t.numel(), dtype=t.dtype, device=t.device)
+    comm.all_gather(t.view(-1), out)
+    torch.cuda.synchronize()
+    return out.view(comm.nranks * t.shape[0], *t.shape[1:])
+
+
+def check_backward(moe, comm, x, logits, dy, tol, bad):
+    """Forward + backward of the layer against float64 autograd of the whole (unsharded) layer over all ranks' tokens, the
+    fp8 transport of the dispatched rows treated as the identity in the backward direction."""
+    F = torch.nn.functional
+    D = torch.float64
+    T, k, el, rank = moe.T, moe.k, moe.el, comm.rank
+    X, L, DY = gather(comm, x), gather(comm, logits), gather(comm, dy).to(D)
+    WG, WU, WD = (gather(comm, w).to(D).requires_grad_(True) for w in (moe.w_gate, moe.w_up, moe.w_down))
+    Xl = X.to(D).requires_grad_(True)
+    Ll = L.to(D).requires_grad_(True)
+    Xq = dequantize_e4m3_per128(*quantize_e4m3_per128(X)).to(D)
+    Xe = Xl + (Xq - Xl).detach()
+    top_v, top_i = torch.topk(Ll, k, dim=-1)
+    w = torch.softmax(top_v, dim=-1)
+    out = torch.zeros_like(Xl)
+    for e in range(moe.E):
+        t, r = (top_i == e).nonzero(as_tuple=True)
+        if t.numel() == 0:
+            continue
+        rows = Xe[t]
+        y = (F.silu(rows @ WG[e].t()) * (rows @ WU[e].t())) @ WD[e].t()
+        out = out.index_add(0, t, w[t, r].unsqueeze(-1) * y)
+    out.backward(DY)
+    got = moe.forward(x, logits).clone()
+    dx, dlogits = moe.backward(dy)
+    torch.cuda.synchronize()
+    dwg, dwu, dwd = moe.expert_weight_grads()
+    lo, hi = rank * T, (rank + 1) * T
+    e0, e1 = rank * el, (rank + 1) * el
+    rel = {}
+    for name, a, b in (("y", got, out.detach()[lo:hi]), ("dx", dx, Xl.grad[lo:hi]), ("dlogits", dlogits, Ll.grad[lo:hi]),
+                       ("dw_gate", dwg, WG.grad[e0:e1]), ("dw_up", dwu, WU.grad[e0:e1]), ("dw_down", dwd, WD.grad[e0:e1])):
+        err = (a.to(D) - b).abs().max().item()
+        scale = b.abs().max().item()
+        rel[name] = err / max(scale, 1e-30)
+        if not (err <= tol * scale + 1e-7):
+            bad.append(("backward", name, err, scale))
+    return rel
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--backward", action="store_true")      # also check the layer's gradients against float64 autograd
     ap.add_argument("--experts-local", type=int, default=16)
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--ffn", type=int, default=256)
@@ -73,6 +123,16 @@ def main():
             if not (err <= 3e-2 * scale + 1e-4):
                 bad.append(("mismatch", trial, err, scale))
             res["rows_received"] = int(sum(counts))
+        if args.backward and not bad:
+            for trial in range(2):
+                g = torch.Generator(device=dev).manual_seed(900 + 50 * trial + rank)
+                x = torch.randn(args.tokens, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+                logits = torch.randn(args.tokens, moe.E, device=dev, generator=g)
+                dy = torch.randn(args.tokens, args.hidden, device=dev, generator=g).to(torch.bfloat16)
+                res[f"backward_rel_err_{trial}"] = {k: round(v, 5) for k, v in check_backward(moe, comm, x, logits, dy, 4e-2, bad).items()}
+                code = train_ops.gemm_take_error()
+                if code:
+                    bad.append(("gemm_error", code))
     if args.time and not bad:
         g = torch.Generator(device=dev).manual_seed(rank)
         x = torch.randn(args.tokens, args.hidden, device=dev, generator=g).to(torch.bfloat16)
