@@ -116,7 +116,7 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   }
   const bool nvlsOk = c->nvls && n > 1 && (!reducing || (nvlsReducible(r.dt, rop.base) && rop.scaleMode != SCALE_PRE_MUL)) &&
                       (r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE || r.kind == COLL_BROADCAST);
-  const bool llOk = r.kind == COLL_ALLREDUCE && bytes <= fl.llMaxBytes && n > 1;
+  const bool llOk = r.kind == COLL_ALLREDUCE && bytes <= fl.llLimit(n) && n > 1;
   if (algo == ALGO_LL && !llOk) algo = ALGO_AUTO;
   if (algo == ALGO_NVLS && !nvlsOk) algo = ALGO_AUTO;
   if (algo == ALGO_AUTO) {
@@ -187,10 +187,12 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
     size_t capMax = fullCap;
     if (reduceKind && fl.pipeChunkBytes != 0) {
       // Pipeline chunk of the reducing kernels: an eighth of what moves through staging, between
-      // 8 MiB (below that the per-chunk barrier costs more than the overlap wins) and one half.
+      // 32 MiB and one staging half. A chunk costs its inter-rank barriers (about 8 us measured between
+      // two GPUs): with 8 MiB chunks a 32 MiB all-reduce took 107 us, as one chunk 83 us, and every size
+      // up to 256 MiB was fastest with 32 MiB chunks.
       const size_t staged = r.kind == COLL_REDUCESCATTER ? bytes * n : bytes;
-      if (staged >= (size_t)16 << 20 || fl.pipeChunkBytes > 0) {
-        size_t chunk = std::max<size_t>((size_t)8 << 20, ((staged / 8) + ((1u << 20) - 1)) & ~(size_t)((1u << 20) - 1));
+      if (staged > (size_t)32 << 20 || fl.pipeChunkBytes > 0) {
+        size_t chunk = std::max<size_t>((size_t)32 << 20, ((staged / 8) + ((1u << 20) - 1)) & ~(size_t)((1u << 20) - 1));
         if (fl.pipeChunkBytes > 0) chunk = ((size_t)fl.pipeChunkBytes + 4095) & ~(size_t)4095;
         const size_t perCall = r.kind == COLL_REDUCESCATTER ? (chunk / n) & ~(size_t)15 : chunk;
         if (perCall >= 16 && perCall < capMax) capMax = perCall;
@@ -206,9 +208,11 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   }
   if (!ctas) {
     size_t moved = bytes * ((r.kind == COLL_REDUCESCATTER || r.kind == COLL_ALLGATHER) ? n : 1);
-    ctas = algo == ALGO_LL ? (int)std::min<size_t>(16, (bytes / 8 + kCollThreads - 1) / kCollThreads) : ctasFor(c, moved, algo);
+    ctas = algo == ALGO_LL ? (int)((bytes / 8 + kCollThreads - 1) / kCollThreads) : ctasFor(c, moved, algo);
   }
-  ctas = std::max(1, std::min(ctas, algo == ALGO_LL ? 16 : c->maxCtas));
+  // Flag-in-data: up to 16 CTAs for the latency-bound sizes, one more per 16 KiB beyond 256 KiB (64 at 1 MiB and above).
+  const int llCap = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
+  ctas = std::max(1, std::min(ctas, algo == ALGO_LL ? std::min(llCap, std::max(16, c->maxCtas)) : c->maxCtas));
   plan->algo = algo;
   plan->ctas = ctas;
   plan->direct = direct;

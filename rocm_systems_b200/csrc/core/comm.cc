@@ -204,7 +204,7 @@ ncclResult_t commCreate(Comm** out, const ncclUniqueId& id, int nranks, int rank
   d.rank = rank;
   d.nranks = nranks;
   const bool solo = nranks == 1;
-  d.llSlotBytes = solo ? 256 : 2 * fl.llMaxBytes;
+  d.llSlotBytes = solo ? 256 : 2 * fl.llLimit(nranks);
   const size_t llBytes = 2 * (size_t)nranks * d.llSlotBytes;
   d.stageOff = alignUp(kWsLLOff + llBytes, 1u << 16);
   d.stageBytes = solo ? (1u << 16) : fl.stageBytes;

@@ -113,7 +113,7 @@ static void load(Flags& f) {
   // Sanity clamps: sizes must stay multiples of what the kernels vectorise on.
   if (f.stageBytes < (1u << 20)) f.stageBytes = 1u << 20;
   f.stageBytes &= ~(size_t)0xffff;
-  if (f.llMaxBytes > (256u << 10)) f.llMaxBytes = 256u << 10;
+  if (f.llMaxBytes > (2u << 20)) f.llMaxBytes = 2u << 20;
   f.llMaxBytes &= ~(size_t)0xff;
   if (f.p2pChunkBytes < (64u << 10)) f.p2pChunkBytes = 64u << 10;
   f.p2pChunkBytes &= ~(size_t)0xfff;
@@ -252,7 +252,7 @@ const SettingDoc kSettings[] = {
     {"MIN_CTAS", true, "0", "lower bound of CTAs per collective launch (0: built-in)"},
     {"MAX_CTAS", true, "0", "upper bound of CTAs per collective launch (0: built-in)"},
     {"BUFFSIZE", true, "64M", "bytes per staging half (two halves per communicator), at least 1M"},
-    {"LL_THRESHOLD", false, "256K", "largest all-reduce served by the flag-in-data protocol, at most 256K"},
+    {"LL_THRESHOLD", false, "2M", "largest all-reduce served by the flag-in-data protocol: at most 2M between two ranks, 256K from three ranks up"},
     {"P2P_CHUNK", false, "512K", "bytes per send/recv FIFO slot"},
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
     {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},

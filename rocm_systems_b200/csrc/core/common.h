@@ -86,7 +86,14 @@ struct Flags {
   std::string algo;              // ALGO: "", "ll", "p2p", "nvls"
   int minCtas = 0, maxCtas = 0;  // MIN_CTAS / MAX_CTAS (0: per-collective default)
   size_t stageBytes = 64ull << 20;   // BUFFSIZE: bytes per staging half
-  size_t llMaxBytes = 256ull << 10;  // LL_THRESHOLD: largest message for the flag-in-data protocol
+  size_t llMaxBytes = 2ull << 20;    // LL_THRESHOLD: largest message for the flag-in-data protocol (see llLimit)
+  // Every rank stores its whole message (with as many bytes of flags) into every peer, so what the protocol may carry
+  // shrinks with the ranks: 2 MiB between two (measured there: staged 24-27 us at 512 KiB - 2 MiB against 19 us for NCCL),
+  // 256 KiB from three ranks up.
+  size_t llLimit(int nranks) const {
+    const size_t byRanks = nranks <= 2 ? (2ull << 20) : (256ull << 10);
+    return llMaxBytes < byRanks ? llMaxBytes : byRanks;
+  }
   size_t p2pChunkBytes = 512ull << 10; // P2P_CHUNK: bytes per send/recv FIFO slot
   int p2pCtasPerPeer = 0;        // P2P_CTAS: CTAs per (peer, direction); 0 picks by rank count
   int waitTimeoutMs = 20000;     // WAIT_TIMEOUT_MS: device-side wait budget

@@ -50,9 +50,13 @@ def test_builtin_choices():
         [8, 0, AR, 64 * MiB // 4, F32, SUM],   # no multicast: peer loads
         [8, 1, AG, MiB, F32, SUM],             # copies never reduce in the switch
         [8, 1, AR, 8, 6, SUM],                 # fp16 is 6: tiny, flag-in-data
+        [2, 1, AR, 2 * MiB // 4, F32, SUM],    # between two ranks flag-in-data carries up to 2 MiB, on up to 64 CTAs (within the communicator's budget)
+        [2, 1, AR, 2 * MiB // 4 + 4, F32, SUM],
     ])
-    assert [x[0] for x in r] == [0] * 8
-    assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL]
+    assert [x[0] for x in r] == [0] * 10
+    assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL, LL, P2P]
+    assert r[1][2] == 16 and r[8][2] == 32          # 64 by size, bounded by the CTA budget of the planning communicator (32)
+    assert plan([[2, 1, AR, 2 * MiB // 4, F32, SUM]], {"B200COLL_MAX_CTAS": "64"})[0][2] == 64
     assert all(x[3] == 0 for x in r)           # nothing is in a registered window here
 
 
@@ -60,13 +64,13 @@ def test_pipeline_chunks_are_equalised():
     MiB = 1 << 20
     r = plan([
         [8, 1, AR, 8 * MiB // 4, F32, SUM],        # 8 MiB: one chunk
-        [8, 1, AR, 16 * MiB // 4, F32, SUM],       # 16 MiB: two chunks of 8 MiB
-        [8, 1, AR, 80 * 1000 * 1000 // 4, F32, SUM],   # 80 MB: chunk = 1/8 rounded up to 1 MiB -> 10 MiB -> 8 chunks
+        [8, 1, AR, 16 * MiB // 4, F32, SUM],       # 16 MiB: still one chunk (a chunk costs its barriers; none below 32 MiB)
+        [8, 1, AR, 80 * 1000 * 1000 // 4, F32, SUM],   # 80 MB: an eighth is below the 32 MiB minimum -> three equal chunks
         [8, 1, AR, 1024 * MiB // 4, F32, SUM],     # 1 GiB: a staging half (64 MiB) caps the chunk: 16
         [8, 1, RS, 128 * MiB // 4, F32, SUM],      # per-rank slice 128 MiB -> staged 1 GiB -> 8 MiB per slice and chunk: 16
         [8, 1, AG, 200 * MiB // 4, F32, SUM],      # copies are chunked by the staging half only: ceil(200 / 64) = 4
     ])
-    assert [x[4] for x in r] == [1, 2, 8, 16, 16, 4]
+    assert [x[4] for x in r] == [1, 1, 3, 16, 16, 4]
     off = plan([[8, 1, AR, 1024 * MiB // 4, F32, SUM]], {"B200COLL_PIPELINE_CHUNK": "0"})
     assert off[0][4] == 16                         # 64 MiB halves either way at this size
     small = plan([[8, 1, AR, 32 * MiB // 4, F32, SUM]], {"B200COLL_PIPELINE_CHUNK": "1M"})
@@ -118,7 +122,7 @@ def test_planner_invariants_over_random_messages():
         assert rc == 0 and algo in (LL, P2P, NVLS) and 1 <= ctas <= 128 and direct == 0, (nranks, kind, count, algo, ctas, chunks)
         assert (chunks == 0) if algo == LL else (chunks >= 1), (nranks, kind, count, algo, chunks)      # flag-in-data uses no staging
         if algo == LL:
-            assert kind == AR and nbytes <= 256 * 1024
+            assert kind == AR and nbytes <= (2 << 20 if nranks == 2 else 256 * 1024)
         if algo == NVLS:
             assert nvls == 1
             if kind in (AR, RS, RED):
