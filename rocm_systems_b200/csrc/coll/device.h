@@ -89,7 +89,8 @@ struct CollArgs {
 struct LLArgs {
   const void* send;
   void* recv;
-  size_t count;
+  size_t count;          // elements per rank (all-reduce: the message; reduce-scatter / all-gather: one rank's slice); all-gather: bytes
+  int kind;              // COLL_ALLREDUCE, COLL_REDUCESCATTER or COLL_ALLGATHER
   int scaleMode;
   unsigned long long scalarBits;
   const void* scalarPtr;  // see CollArgs

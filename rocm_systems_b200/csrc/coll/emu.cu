@@ -60,7 +60,9 @@ __device__ __forceinline__ Dim grid() { return Dim{gLanes, 1, 1}; }
 #define kP2p emuP2p
 #define kBarrier emuBarrier
 #define kAllToAllDirect emuAllToAllDirect
+#define kLLAllGather emuLLAllGather
 #include "kernels.cuh"
+#undef kLLAllGather
 #undef kP2p
 #undef kBarrier
 #undef kAllToAllDirect
@@ -103,6 +105,10 @@ template <typename T, typename Op> __global__ void __launch_bounds__(kCollThread
 __global__ void __launch_bounds__(kCollThreads) kCopy(const Pack* p) {
   const unsigned r = blockIdx.x / (unsigned)p->lanes;
   kStagedCopy<false>(p->c[r], p->a[r], p->elemSize);
+}
+__global__ void __launch_bounds__(kCollThreads) kGatherLL(const Pack* p) {
+  const unsigned r = blockIdx.x / (unsigned)p->lanes;
+  emuLLAllGather(p->c[r], p->ll[r]);
 }
 
 struct P2pPack {
@@ -211,7 +217,7 @@ ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const voi
     const int base = op == ncclAvg ? (int)ncclSum : (int)op;
     fn = dt == ncclFloat32 ? emu::reduceFn<float>(base, ll) : dt == ncclBfloat16 ? emu::reduceFn<__nv_bfloat16>(base, ll) : emu::reduceFn<int32_t>(base, ll);
   } else {
-    fn = (const void*)emu::kCopy;
+    fn = ll ? (const void*)emu::kGatherLL : (const void*)emu::kCopy;
   }
   if (!fn) BFAIL(ncclInternalError, "b200collEmuCollective: no kernel for this operator");
   cudaError_t e = emu::launchCoop(fn, n * lanes, threads, smem, devPack, (unsigned)lanes, stream);

@@ -116,7 +116,8 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
   }
   const bool nvlsOk = c->nvls && n > 1 && (!reducing || (nvlsReducible(r.dt, rop.base) && rop.scaleMode != SCALE_PRE_MUL)) &&
                       (r.kind == COLL_ALLREDUCE || r.kind == COLL_REDUCESCATTER || r.kind == COLL_REDUCE || r.kind == COLL_BROADCAST);
-  const bool llOk = r.kind == COLL_ALLREDUCE && bytes <= fl.llLimit(n) && n > 1;
+  const bool llOk = n > 1 && ((r.kind == COLL_ALLREDUCE && bytes <= fl.llLimit(n)) ||
+                             ((r.kind == COLL_REDUCESCATTER || r.kind == COLL_ALLGATHER) && bytes <= fl.llSliceLimit(n)));
   if (algo == ALGO_LL && !llOk) algo = ALGO_AUTO;
   if (algo == ALGO_NVLS && !nvlsOk) algo = ALGO_AUTO;
   if (algo == ALGO_AUTO) {
@@ -252,7 +253,8 @@ ncclResult_t emuPrepare(const CollReq& r, Plan* plan, CollArgs* args, LLArgs* ll
   if (plan->algo == ALGO_LL) {
     ll->send = r.send;
     ll->recv = r.recv;
-    ll->count = r.count;
+    ll->kind = r.kind;
+    ll->count = r.kind == COLL_ALLGATHER ? r.count * es : r.count;
     ll->scaleMode = rop.scaleMode;
     ll->scalarBits = rop.bits;
     if (++c->llSeq == 0) c->llSeq = 2;
@@ -335,13 +337,14 @@ ncclResult_t enqueueColl(const CollReq& r) {
     LLArgs la{};
     la.send = r.send;
     la.recv = r.recv;
-    la.count = r.count;
+    la.kind = r.kind;
+    la.count = r.kind == COLL_ALLGATHER ? r.count * es : r.count;
     la.scaleMode = rop.scaleMode;
     la.scalarBits = rop.bits;
     la.scalarPtr = rop.devPtr;
     if (++c->llSeq == 0) c->llSeq = 2;  // 0 is the "never written" value; keep the parity sequence
     la.seq = c->llSeq;
-    e = launchLLAllReduce(r.dt, rop.base, plan.ctas, r.stream, dc, la);
+    e = r.kind == COLL_ALLGATHER ? launchLLAllGather(plan.ctas, r.stream, dc, la) : launchLLAllReduce(r.dt, rop.base, plan.ctas, r.stream, dc, la);
   } else {
     args.stageHalf = (int)(c->stageParity & 1);
     c->stageParity += (uint32_t)plan.chunks;

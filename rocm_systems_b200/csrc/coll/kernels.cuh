@@ -65,24 +65,42 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllReduce(const __grid_consta
   const int n = c.nranks, rank = c.rank;
   const size_t units = (a.count + EPU - 1) / EPU;
   const size_t halfOff = kWsLLOff + (size_t)(a.seq & 1) * (size_t)n * c.llSlotBytes;
+  // Reduce-scatter is the same exchange with one slice per destination: rank p gets slice p of everybody's input and
+  // nobody else's, so every line crosses the link once.
+  const bool rs = a.kind == COLL_REDUCESCATTER;
   const T* send = (const T*)a.send;
   T* recv = (T*)a.recv;
-  const bool aligned = ((((uintptr_t)a.send) | ((uintptr_t)a.recv)) & 7) == 0;
+  const bool aligned = ((((uintptr_t)a.send) | ((uintptr_t)a.recv)) & 7) == 0 && (!rs || (a.count * sizeof(T)) % 8 == 0);
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gn = (size_t)gridDim.x * blockDim.x;
 
   const Acc scalar = scalarOf<T>(a.scalarBits, a.scalarPtr);
   const bool pre = a.scaleMode == SCALE_PRE_MUL;
-  for (size_t i = gtid; i < units; i += gn) {
-    T e[EPU];
-    loadUnit8<T>(send, a.count, i, aligned, e);
-    union { uint2 v; T t[EPU]; } u;
+  if (rs) {
+    for (size_t i = gtid; i < units; i += gn) {
+      for (int d = 1; d < n; d++) {
+        const int p = (rank + d) % n;
+        T e[EPU];
+        loadUnit8<T>(send + (size_t)p * a.count, a.count, i, aligned, e);
+        union { uint2 v; T t[EPU]; } u;
 #pragma unroll
-    for (int k = 0; k < EPU; k++) u.t[k] = pre ? preMul<T>(e[k], scalar) : e[k];
-    const uint4 line = make_uint4(u.v.x, a.seq, u.v.y, a.seq);
-    for (int d = 1; d < n; d++) {
-      const int p = (rank + d) % n;
-      stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, line);
+        for (int k = 0; k < EPU; k++) u.t[k] = pre ? preMul<T>(e[k], scalar) : e[k];
+        stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, make_uint4(u.v.x, a.seq, u.v.y, a.seq));
+      }
+    }
+    send += (size_t)rank * a.count;  // this rank's own contribution to its slice
+  } else {
+    for (size_t i = gtid; i < units; i += gn) {
+      T e[EPU];
+      loadUnit8<T>(send, a.count, i, aligned, e);
+      union { uint2 v; T t[EPU]; } u;
+#pragma unroll
+      for (int k = 0; k < EPU; k++) u.t[k] = pre ? preMul<T>(e[k], scalar) : e[k];
+      const uint4 line = make_uint4(u.v.x, a.seq, u.v.y, a.seq);
+      for (int d = 1; d < n; d++) {
+        const int p = (rank + d) % n;
+        stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, line);
+      }
     }
   }
 
@@ -630,6 +648,76 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
 // ---- grouped send/recv ----------------------------------------------------------------------
 // Non-template kernels are compiled only by the translation unit that launches them.
 #ifdef B200_MISC_KERNELS
+// Flag-in-data all-gather: every rank stores its slice, 8 bytes of data and 8 of flags per line, into its slot of every
+// peer's buffer; a receiver copies a line out as soon as both flags show this operation's number. No barrier, no
+// staging round: one launch and one trip over the link. a.count is the slice in BYTES (the type does not matter).
+__device__ __forceinline__ uint2 llLoad8(const char* base, size_t bytes, size_t i, bool aligned) {
+  const size_t b0 = i * 8;
+  if (aligned && b0 + 8 <= bytes) return *(const uint2*)(base + b0);
+  union { uint2 v; unsigned char b[8]; } u;
+  u.v = make_uint2(0, 0);
+  for (int k = 0; k < 8; k++)
+    if (b0 + k < bytes) u.b[k] = (unsigned char)base[b0 + k];
+  return u.v;
+}
+__device__ __forceinline__ void llStore8(char* base, size_t bytes, size_t i, bool aligned, uint2 v) {
+  const size_t b0 = i * 8;
+  if (aligned && b0 + 8 <= bytes) { *(uint2*)(base + b0) = v; return; }
+  union { uint2 v; unsigned char b[8]; } u;
+  u.v = v;
+  for (int k = 0; k < 8; k++)
+    if (b0 + k < bytes) base[b0 + k] = (char)u.b[k];
+}
+
+__global__ void __launch_bounds__(kCollThreads) kLLAllGather(const __grid_constant__ DevComm c, const __grid_constant__ LLArgs a) {
+  stampBegin(c);
+  const int n = c.nranks, rank = c.rank;
+  const size_t bytes = a.count;
+  const size_t units = (bytes + 7) / 8;
+  const size_t halfOff = kWsLLOff + (size_t)(a.seq & 1) * (size_t)n * c.llSlotBytes;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  const bool aligned = (((((uintptr_t)a.send) | ((uintptr_t)a.recv)) & 7) == 0) && (bytes % 8 == 0);
+  const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gn = (size_t)gridDim.x * blockDim.x;
+  char* mine = recv + (size_t)rank * bytes;
+  const bool inPlace = mine == send;
+  for (size_t i = gtid; i < units; i += gn) {
+    const uint2 v = llLoad8(send, bytes, i, aligned);
+    const uint4 line = make_uint4(v.x, a.seq, v.y, a.seq);
+    for (int d = 1; d < n; d++) {
+      const int p = (rank + d) % n;
+      stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, line);
+    }
+    if (!inPlace) llStore8(mine, bytes, i, aligned, v);
+  }
+  for (int d = 1; d < n; d++) {
+    const int s = (rank + n - d) % n;
+    char* dst = recv + (size_t)s * bytes;
+    for (size_t i = gtid; i < units; i += gn) {
+      const char* line = c.ws[rank] + halfOff + (size_t)s * c.llSlotBytes + i * 16;
+      uint4 v;
+      unsigned long long t0 = 0;
+      uint32_t spins = 0;
+      bool ok = true;
+      while (true) {
+        v = ldVolatile16(line);
+        if (v.y == a.seq && v.w == a.seq) break;
+        if ((++spins & 0xff) == 0) {
+          if (*(volatile uint32_t*)&c.local->failed) { ok = false; break; }
+          if (*c.abortFlag) { recordFailure(c, 2, WAIT_LL, s, a.seq, v.y); ok = false; break; }
+          unsigned long long now = globalTimerNs();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > c.timeoutNs) { recordFailure(c, 1, WAIT_LL, s, a.seq, v.y); ok = false; break; }
+        }
+      }
+      if (!ok) break;  // the failure is recorded; leave the rest of this source's lines
+      llStore8(dst, bytes, i, aligned, make_uint2(v.x, v.z));
+    }
+  }
+  stampEnd(c);
+}
+
 __global__ void __launch_bounds__(kCollThreads) kP2p(const __grid_constant__ DevComm c, const __grid_constant__ P2pArgs a) {
   stampBegin(c);
   const int subs = c.p2pSubs;

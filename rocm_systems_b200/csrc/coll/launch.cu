@@ -39,6 +39,11 @@ cudaError_t launchStagedCopy(bool nvls, int grid, cudaStream_t s, const DevComm&
   return cudaGetLastError();
 }
 
+cudaError_t launchLLAllGather(int grid, cudaStream_t s, const DevComm& c, const LLArgs& a) {
+  kLLAllGather<<<grid, kCollThreads, 0, s>>>(c, a);
+  return cudaGetLastError();
+}
+
 cudaError_t launchP2p(int grid, cudaStream_t s, const DevComm& c, const P2pArgs& a) {
   kP2p<<<grid, kCollThreads, 0, s>>>(c, a);
   return cudaGetLastError();

@@ -8,7 +8,8 @@
 namespace b200 {
 
 // `op` is one of ncclSum/ncclProd/ncclMax/ncclMin; Avg and PreMulSum arrive as Sum + scaleMode.
-cudaError_t launchLLAllReduce(ncclDataType_t dt, int op, int grid, cudaStream_t s, const DevComm& c, const LLArgs& a);
+cudaError_t launchLLAllReduce(ncclDataType_t dt, int op, int grid, cudaStream_t s, const DevComm& c, const LLArgs& a);  // all-reduce and reduce-scatter (a.kind)
+cudaError_t launchLLAllGather(int grid, cudaStream_t s, const DevComm& c, const LLArgs& a);
 cudaError_t launchStagedReduce(ncclDataType_t dt, int op, bool nvls, int grid, cudaStream_t s, const DevComm& c, const CollArgs& a);
 cudaError_t launchStagedCopy(bool nvls, int grid, cudaStream_t s, const DevComm& c, const CollArgs& a, int elemSize);
 cudaError_t launchP2p(int grid, cudaStream_t s, const DevComm& c, const P2pArgs& a);

@@ -94,6 +94,9 @@ struct Flags {
     const size_t byRanks = nranks <= 2 ? (2ull << 20) : (256ull << 10);
     return llMaxBytes < byRanks ? llMaxBytes : byRanks;
   }
+  // Reduce-scatter and all-gather move one slice per peer: the limit on a slice, so that a rank's stores stay within
+  // what an all-reduce of llLimit bytes between two ranks puts on its link.
+  size_t llSliceLimit(int nranks) const { return nranks <= 2 ? llLimit(nranks) : llLimit(nranks) * 2 / (size_t)nranks; }
   size_t p2pChunkBytes = 512ull << 10; // P2P_CHUNK: bytes per send/recv FIFO slot
   int p2pCtasPerPeer = 0;        // P2P_CTAS: CTAs per (peer, direction); 0 picks by rank count
   int waitTimeoutMs = 20000;     // WAIT_TIMEOUT_MS: device-side wait budget

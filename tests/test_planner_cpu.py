@@ -52,9 +52,14 @@ def test_builtin_choices():
         [8, 1, AR, 8, 6, SUM],                 # fp16 is 6: tiny, flag-in-data
         [2, 1, AR, 2 * MiB // 4, F32, SUM],    # between two ranks flag-in-data carries up to 2 MiB, on up to 64 CTAs (within the communicator's budget)
         [2, 1, AR, 2 * MiB // 4 + 4, F32, SUM],
+        [8, 1, RS, 16 * 1024, F32, SUM],       # reduce-scatter / all-gather: flag-in-data for slices up to 2 x 256 KiB / ranks
+        [8, 1, RS, 16 * 1024 + 4, F32, SUM],
+        [8, 1, AG, 16 * 1024, F32, SUM],
+        [8, 1, AG, 16 * 1024 + 4, F32, SUM],
+        [2, 1, AG, 2 * MiB // 4, F32, SUM],    # two ranks: slices up to 2 MiB
     ])
-    assert [x[0] for x in r] == [0] * 10
-    assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL, LL, P2P]
+    assert [x[0] for x in r] == [0] * 15
+    assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL, LL, P2P, LL, NVLS, LL, P2P, LL]
     assert r[1][2] == 16 and r[8][2] == 32          # 64 by size, bounded by the CTA budget of the planning communicator (32)
     assert plan([[2, 1, AR, 2 * MiB // 4, F32, SUM]], {"B200COLL_MAX_CTAS": "64"})[0][2] == 64
     assert all(x[3] == 0 for x in r)           # nothing is in a registered window here
@@ -98,7 +103,7 @@ def test_tuning_file_wins_over_thresholds(tmp_path):
     r = plan([[8, 1, AR, 1024, F32, SUM], [8, 1, AR, 4 * MiB // 4, F32, SUM], [8, 1, RS, 1024, F32, SUM]], {"B200COLL_TUNING_FILE": str(t)})
     assert r[0][1] == P2P and r[0][2] == 5        # first row covers 4 KiB
     assert r[1][1] == NVLS                         # beyond the first row; the 4-rank row is skipped at 8 ranks
-    assert r[2][1] == NVLS                         # no reduce_scatter rows: built-in choice (4 KiB x 8 ranks = 32 KiB staged)
+    assert r[2][1] == LL                           # no reduce_scatter rows: built-in choice (slices of 4 KiB: flag-in-data)
     assert plan([[0, 1, AR, 4, F32, SUM]])[0][0] == 4   # nranks 0: invalid argument
 
 
@@ -122,7 +127,8 @@ def test_planner_invariants_over_random_messages():
         assert rc == 0 and algo in (LL, P2P, NVLS) and 1 <= ctas <= 128 and direct == 0, (nranks, kind, count, algo, ctas, chunks)
         assert (chunks == 0) if algo == LL else (chunks >= 1), (nranks, kind, count, algo, chunks)      # flag-in-data uses no staging
         if algo == LL:
-            assert kind == AR and nbytes <= (2 << 20 if nranks == 2 else 256 * 1024)
+            limit = 2 << 20 if nranks == 2 else 256 * 1024
+            assert kind in (AR, RS, AG) and nbytes <= (limit if kind == AR or nranks == 2 else limit * 2 // nranks)
         if algo == NVLS:
             assert nvls == 1
             if kind in (AR, RS, RED):
