@@ -62,7 +62,8 @@ struct DevComm {
   TraceStamp* stamp;       // null when tracing is off
 };
 
-enum CollKind : int { COLL_ALLREDUCE = 0, COLL_REDUCESCATTER = 1, COLL_REDUCE = 2, COLL_ALLGATHER = 3, COLL_BROADCAST = 4 };
+enum CollKind : int { COLL_ALLREDUCE = 0, COLL_REDUCESCATTER = 1, COLL_REDUCE = 2, COLL_ALLGATHER = 3, COLL_BROADCAST = 4,
+                      COLL_ALLTOALL = 5 /* flag-in-data kernel only; larger ones are grouped send/recv */ };
 
 // How a reducing collective post-processes: Avg divides, PreMulSum scales the inputs.
 enum ScaleMode : int { SCALE_NONE = 0, SCALE_POST_DIV_N = 1, SCALE_PRE_MUL = 2 };
@@ -90,7 +91,7 @@ struct LLArgs {
   const void* send;
   void* recv;
   size_t count;          // elements per rank (all-reduce: the message; reduce-scatter / all-gather: one rank's slice); all-gather: bytes
-  int kind;              // COLL_ALLREDUCE, COLL_REDUCESCATTER or COLL_ALLGATHER
+  int kind;              // COLL_ALLREDUCE, COLL_REDUCESCATTER, COLL_ALLGATHER or COLL_ALLTOALL (count: bytes per peer)
   int scaleMode;
   unsigned long long scalarBits;
   const void* scalarPtr;  // see CollArgs

@@ -361,6 +361,39 @@ ncclResult_t enqueueColl(const CollReq& r) {
   return finish(true, ncclSuccess);
 }
 
+// All-to-all of small chunks through the flag-in-data buffers: one launch, no FIFO credits, no barrier. The caller has
+// checked that bytesPerPeer fits (llAllToAllFits).
+bool llAllToAllFits(Comm* c, size_t bytesPerPeer) {
+  return c->nranks > 1 && bytesPerPeer > 0 && bytesPerPeer <= Flags::get().llSliceLimit(c->nranks);
+}
+
+ncclResult_t enqueueLLAllToAll(Comm* c, int apiId, const void* send, void* recv, size_t count, ncclDataType_t dt, cudaStream_t stream) {
+  BCHECK(commCheck(c));
+  if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+  if (!send || !recv) BFAIL(ncclInvalidArgument, "null buffer");
+  const size_t bytes = count * dtypeSize(dt);
+  DeviceGuard guard(c->cudaDev);
+  Tracer* tr = c->tracer;
+  TraceStamp* stamp = tr ? tr->begin(apiId, dt, count, bytes * c->nranks) : nullptr;
+  DevComm dc = c->dev;
+  dc.opSeq = ++c->opSeq;
+  dc.stamp = stamp;
+  LLArgs la{};
+  la.send = send;
+  la.recv = recv;
+  la.kind = COLL_ALLTOALL;
+  la.count = bytes;
+  if (++c->llSeq == 0) c->llSeq = 2;
+  la.seq = c->llSeq;
+  const int llCap = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
+  const int ctas = std::max(1, std::min((int)((bytes / 8 + kCollThreads - 1) / kCollThreads), std::min(llCap, std::max(16, c->maxCtas))));
+  if (tr) tr->setAlgo(ALGO_LL, ctas);
+  cudaError_t e = launchLLAllGather(ctas, stream, dc, la);
+  if (tr) tr->end(e == cudaSuccess);
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "all-to-all launch failed: %s", cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
 ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops) {
   BCHECK(commCheck(c));
   if (ops.empty()) return ncclSuccess;

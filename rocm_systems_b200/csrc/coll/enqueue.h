@@ -34,6 +34,9 @@ struct P2pReq {
 };
 // All sends and receives one group made on one communicator.
 ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops);
+// All-to-all of chunks small enough for the flag-in-data buffers (llAllToAllFits), as one kernel.
+bool llAllToAllFits(Comm* c, size_t bytesPerPeer);
+ncclResult_t enqueueLLAllToAll(Comm* c, int apiId, const void* send, void* recv, size_t count, ncclDataType_t dt, cudaStream_t stream);
 
 // What the chooser would pick (exposed for tests and the tuner).
 struct Plan {

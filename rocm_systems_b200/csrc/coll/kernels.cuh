@@ -651,6 +651,7 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
 // Flag-in-data all-gather: every rank stores its slice, 8 bytes of data and 8 of flags per line, into its slot of every
 // peer's buffer; a receiver copies a line out as soon as both flags show this operation's number. No barrier, no
 // staging round: one launch and one trip over the link. a.count is the slice in BYTES (the type does not matter).
+// With a.kind == COLL_ALLTOALL every destination gets its own chunk of a.count bytes instead of the same slice.
 __device__ __forceinline__ uint2 llLoad8(const char* base, size_t bytes, size_t i, bool aligned) {
   const size_t b0 = i * 8;
   if (aligned && b0 + 8 <= bytes) return *(const uint2*)(base + b0);
@@ -681,15 +682,27 @@ __global__ void __launch_bounds__(kCollThreads) kLLAllGather(const __grid_consta
   const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t gn = (size_t)gridDim.x * blockDim.x;
   char* mine = recv + (size_t)rank * bytes;
-  const bool inPlace = mine == send;
-  for (size_t i = gtid; i < units; i += gn) {
-    const uint2 v = llLoad8(send, bytes, i, aligned);
-    const uint4 line = make_uint4(v.x, a.seq, v.y, a.seq);
-    for (int d = 1; d < n; d++) {
-      const int p = (rank + d) % n;
-      stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, line);
+  if (a.kind == COLL_ALLTOALL) {
+    // The same exchange with a chunk of its own for every destination.
+    for (size_t i = gtid; i < units; i += gn) {
+      for (int d = 1; d < n; d++) {
+        const int p = (rank + d) % n;
+        const uint2 v = llLoad8(send + (size_t)p * bytes, bytes, i, aligned);
+        stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, make_uint4(v.x, a.seq, v.y, a.seq));
+      }
+      llStore8(mine, bytes, i, aligned, llLoad8(send + (size_t)rank * bytes, bytes, i, aligned));
     }
-    if (!inPlace) llStore8(mine, bytes, i, aligned, v);
+  } else {
+    const bool inPlace = mine == send;
+    for (size_t i = gtid; i < units; i += gn) {
+      const uint2 v = llLoad8(send, bytes, i, aligned);
+      const uint4 line = make_uint4(v.x, a.seq, v.y, a.seq);
+      for (int d = 1; d < n; d++) {
+        const int p = (rank + d) % n;
+        stVolatile16(c.ws[p] + halfOff + (size_t)rank * c.llSlotBytes + i * 16, line);
+      }
+      if (!inPlace) llStore8(mine, bytes, i, aligned, v);
+    }
   }
   for (int d = 1; d < n; d++) {
     const int s = (rank + n - d) % n;

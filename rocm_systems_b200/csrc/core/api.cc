@@ -394,8 +394,11 @@ ncclResult_t pncclAllToAll(const void* send, void* recv, size_t count, ncclDataT
   if (send == recv && count) BFAIL(ncclInvalidUsage, "ncclAllToAll cannot run in place");
   const size_t es = dtypeSize(dt);
   if (!es) BFAIL(ncclInvalidArgument, "invalid datatype %d", (int)dt);
-  // Receive buffer inside a symmetric window (the same place on every rank), whole 16-byte units: peer stores, one kernel.
   const size_t chunk = count * es;
+  // Small chunks: one kernel over the flag-in-data buffers (no credits, no barrier).
+  if (tlsGroup.depth == 0 && !Flags::get().emulateRanks && llAllToAllFits(c, chunk))
+    return enqueueLLAllToAll(c, B200COLL_API_ID_ncclAllToAll, send, recv, count, dt, s);
+  // Receive buffer inside a symmetric window (the same place on every rank), whole 16-byte units: peer stores, one kernel.
   if (c->nranks > 1 && tlsGroup.depth == 0 && chunk && (chunk & 15) == 0 && ((((uintptr_t)send) | ((uintptr_t)recv)) & 15) == 0 && !Flags::get().emulateRanks) {
     if (!c->regs.empty()) BCHECK(commRegisterLazy(c, recv, 1));
     size_t off = 0;
