@@ -35,6 +35,17 @@ typedef struct b200shmem_dev {
   unsigned long long timeoutNs;   /* budget of every device-side wait */
 } b200shmem_dev_t;
 
+/* A team: the PEs start, start + stride, ..., size of them (OpenSHMEM teams). Passed by value to kernels next to the
+ * device context. Its barrier words are a slot of their own in the heap's reserved head, so teams synchronise
+ * independently of one another and of barrier_all. */
+typedef struct b200shmem_team {
+  int start, stride, size;
+  int idx;                        /* this PE's index in the team, or -1 when it is not a member */
+  unsigned long long* syncFlags;  /* local: [B200SHMEM_MAX_PES] arrival words of this team, indexed by team index */
+  unsigned long long* syncEpoch;  /* local device memory: barriers of this team completed so far */
+} b200shmem_team_t;
+#define B200SHMEM_MAX_TEAMS 64
+
 typedef struct b200shmem_ctx* b200shmem_ctx_t;
 
 enum { B200SHMEM_CMP_EQ = 0, B200SHMEM_CMP_NE, B200SHMEM_CMP_GT, B200SHMEM_CMP_GE, B200SHMEM_CMP_LT, B200SHMEM_CMP_LE };
@@ -55,6 +66,19 @@ void b200shmem_free(b200shmem_ctx_t ctx, void* ptr);
 void* b200shmem_ptr(b200shmem_ctx_t ctx, const void* ptr, int pe);
 void* b200shmem_mc_ptr(b200shmem_ctx_t ctx, const void* ptr);
 ncclResult_t b200shmem_device_ctx(b200shmem_ctx_t ctx, b200shmem_dev_t* out);
+/* Teams. team_world gives the team of all PEs (it shares barrier_all's words). team_split_strided makes the team of the
+ * parent's members start, start + stride, ... (`size` of them, indices in the PARENT team); it must be called by EVERY PE
+ * of the context in the same order, members or not (that is what keeps the teams' barrier slots in step); a PE that is
+ * not a member gets idx == -1 and must not use the team in a collective. At most B200SHMEM_MAX_TEAMS - 1 splits per
+ * context; team_destroy releases nothing that could be reused and exists for symmetry. */
+ncclResult_t b200shmem_team_world(b200shmem_ctx_t ctx, b200shmem_team_t* team);
+ncclResult_t b200shmem_team_split_strided(b200shmem_ctx_t ctx, const b200shmem_team_t* parent, int start, int stride, int size, b200shmem_team_t* team);
+void b200shmem_team_destroy(b200shmem_ctx_t ctx, b200shmem_team_t* team);
+int b200shmem_team_my_pe(const b200shmem_team_t* team);
+int b200shmem_team_n_pes(const b200shmem_team_t* team);
+/* PE number in `dst` of member `idx` of `src`, or -1 when it is not a member of `dst`. */
+int b200shmem_team_translate_pe(const b200shmem_team_t* src, int idx, const b200shmem_team_t* dst);
+ncclResult_t b200shmem_team_sync_on_stream(b200shmem_ctx_t ctx, const b200shmem_team_t* team, cudaStream_t stream);
 /* Stream-ordered host-initiated operations. */
 ncclResult_t b200shmem_putmem_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
 ncclResult_t b200shmem_getmem_on_stream(b200shmem_ctx_t ctx, void* dest, const void* source, size_t bytes, int pe, cudaStream_t stream);
@@ -86,6 +110,10 @@ ncclResult_t b200shmem_selftest_atomics(b200shmem_ctx_t ctx, int iters, cudaStre
 /* The device API's block-scope collectives (broadcast, fcollect, alltoall, sum / max reduce), wait_until / test and the
  * strided put on `count` 64-bit words per block, each checked against its closed form. Collective over the PEs. */
 ncclResult_t b200shmem_selftest_collectives(b200shmem_ctx_t ctx, size_t count, cudaStream_t stream, int* errors);
+/* The same collectives inside teams: the PEs are split into the even and the odd ones (and, from four PEs up, the even
+ * team once more), every team runs sync / broadcast / fcollect / alltoall / sum reduce on its own members at the same
+ * time as the others. Collective over all PEs. */
+ncclResult_t b200shmem_selftest_teams(b200shmem_ctx_t ctx, size_t count, cudaStream_t stream, int* errors);
 
 /* The two self-checks between `n` PEs that share the current GPU (communicators created under B200COLL_EMULATE_RANKS=1):
  * every PE is one block of a single cooperative kernel. For tests on one GPU. */

@@ -171,27 +171,41 @@ template <typename T> __device__ __forceinline__ T atomic_fetch(const b200shmem_
 }
 template <typename T> __device__ __forceinline__ void atomic_set(const b200shmem_dev_t& d, T* dest, T value, int pe) { (void)atomic_swap(d, dest, value, pe); }
 
-// ---- barrier over all PEs -------------------------------------------------------------------------------------------
-// Called by every thread of ONE block per PE (the same block index on every PE). Completes all of
-// this block's earlier puts, then waits until every PE has arrived.
-__device__ __forceinline__ int barrier_all_block(const b200shmem_dev_t& d) {
+// ---- teams and barriers --------------------------------------------------------------------------------------------------
+// A team is the PEs start, start + stride, ...; member i is PE start + i * stride. The world team shares barrier_all's words.
+__device__ __forceinline__ b200shmem_team_t team_world(const b200shmem_dev_t& d) { return b200shmem_team_t{0, 1, d.npes, d.pe, d.syncFlags, d.syncEpoch}; }
+__device__ __forceinline__ int team_my_pe(const b200shmem_team_t& t) { return t.idx; }
+__device__ __forceinline__ int team_n_pes(const b200shmem_team_t& t) { return t.size; }
+__device__ __forceinline__ int team_pe(const b200shmem_team_t& t, int idx) { return t.start + idx * t.stride; }   // number in the world
+__device__ __forceinline__ int team_translate_pe(const b200shmem_team_t& src, int idx, const b200shmem_team_t& dst) {
+  if (idx < 0 || idx >= src.size) return -1;
+  const int off = team_pe(src, idx) - dst.start;
+  if (off < 0 || off % dst.stride) return -1;
+  return off / dst.stride < dst.size ? off / dst.stride : -1;
+}
+
+// Called by every thread of ONE block per member PE (the same block index on every PE). Completes all of this block's
+// earlier puts, then waits until every member has arrived. Teams have their own arrival words and count their own
+// barriers, so disjoint teams (and a team and its parent, used alternately) do not disturb one another.
+__device__ __forceinline__ int team_sync_block(const b200shmem_dev_t& d, const b200shmem_team_t& t) {
   __shared__ int result;
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned long long epoch = *d.syncEpoch + 1;
+    const unsigned long long epoch = *t.syncEpoch + 1;
     __threadfence_system();
-    for (int pe = 0; pe < d.npes; pe++) {
-      unsigned long long* r = ptr(d, d.syncFlags, pe) + d.pe;
+    for (int i = 0; i < t.size; i++) {
+      unsigned long long* r = ptr(d, t.syncFlags, team_pe(t, i)) + t.idx;
       asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(r), "l"(epoch) : "memory");
     }
     int rc = B200SHMEM_OK;
-    for (int pe = 0; pe < d.npes && rc == B200SHMEM_OK; pe++) rc = signal_wait_until(d, d.syncFlags + pe, B200SHMEM_CMP_GE, epoch);
-    *d.syncEpoch = epoch;
+    for (int i = 0; i < t.size && rc == B200SHMEM_OK; i++) rc = signal_wait_until(d, t.syncFlags + i, B200SHMEM_CMP_GE, epoch);
+    *t.syncEpoch = epoch;
     result = rc;
   }
   __syncthreads();
   return result;
 }
+__device__ __forceinline__ int barrier_all_block(const b200shmem_dev_t& d) { return team_sync_block(d, team_world(d)); }
 __device__ __forceinline__ int sync_all_block(const b200shmem_dev_t& d) { return barrier_all_block(d); }
 
 // ---- identity -------------------------------------------------------------------------------------------------------
@@ -296,57 +310,71 @@ __device__ __forceinline__ void getmem_nbi_block(const b200shmem_dev_t& d, void*
 // The pushing ones (broadcast, fcollect, alltoall) require, as OpenSHMEM does, that dest is free to be written on every PE
 // at entry; they return after a barrier, when every PE's dest is complete. All return B200SHMEM_OK or B200SHMEM_TIMEOUT.
 //
-// dest on every PE (the root's too, unless dest == source there) = the root's source.
-__device__ __forceinline__ int broadcastmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int root) {
-  if (d.pe == root) {
-    for (int i = 1; i < d.npes; i++) putmem_block(d, dest, source, bytes, (root + i) % d.npes);
-    if (dest != source) putmem_block(d, dest, source, bytes, root);
+// Every collective exists in two forms: over a team (member indices wherever a PE is named: `root`, the block order of
+// fcollect / alltoall) and over all PEs.
+//
+// dest on every member (the root's too, unless dest == source there) = the root's source.
+__device__ __forceinline__ int broadcastmem_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, void* dest, const void* source, size_t bytes, int root) {
+  if (t.idx == root) {
+    for (int i = 1; i < t.size; i++) putmem_block(d, dest, source, bytes, team_pe(t, (root + i) % t.size));
+    if (dest != source) putmem_block(d, dest, source, bytes, team_pe(t, root));
   }
-  return barrier_all_block(d);
+  return team_sync_block(d, t);
 }
-// dest [npes][bytes] on every PE: block p is PE p's source (all-gather; OpenSHMEM fcollect).
-__device__ __forceinline__ int fcollectmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes) {
-  for (int i = 0; i < d.npes; i++) putmem_block(d, (char*)dest + (size_t)d.pe * bytes, source, bytes, (d.pe + i) % d.npes);
-  return barrier_all_block(d);
+// dest [size][bytes] on every member: block i is member i's source (all-gather; OpenSHMEM fcollect).
+__device__ __forceinline__ int fcollectmem_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, void* dest, const void* source, size_t bytes) {
+  for (int i = 0; i < t.size; i++) putmem_block(d, (char*)dest + (size_t)t.idx * bytes, source, bytes, team_pe(t, (t.idx + i) % t.size));
+  return team_sync_block(d, t);
 }
-// source [npes][bytes], dest [npes][bytes]: block p of this PE's source becomes block my_pe of PE p's dest.
-__device__ __forceinline__ int alltoallmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes) {
-  for (int i = 0; i < d.npes; i++) {
-    const int pe = (d.pe + i) % d.npes;
-    putmem_block(d, (char*)dest + (size_t)d.pe * bytes, (const char*)source + (size_t)pe * bytes, bytes, pe);
+// source [size][bytes], dest [size][bytes]: block i of this member's source becomes block my-index of member i's dest.
+__device__ __forceinline__ int alltoallmem_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, void* dest, const void* source, size_t bytes) {
+  for (int i = 0; i < t.size; i++) {
+    const int m = (t.idx + i) % t.size;
+    putmem_block(d, (char*)dest + (size_t)t.idx * bytes, (const char*)source + (size_t)m * bytes, bytes, team_pe(t, m));
   }
-  return barrier_all_block(d);
+  return team_sync_block(d, t);
 }
 struct SumOp { template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a + b; } };
 struct MaxOp { template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a > b ? a : b; } };
 struct MinOp { template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a < b ? a : b; } };
-// dest[i] = op over all PEs of source[i] on every PE (OpenSHMEM *_reduce / *_to_all). Two steps: PE p folds slice p of
-// every PE's source in PE order 0, 1, ... into slice p of its own dest; then every PE fetches the other slices from their
-// owners. Each element is reduced exactly once, so the result is bit-identical everywhere, and dest may be source: slice
-// p of PE p is read by nobody but PE p in the first step, and the other slices are overwritten only after the barrier
-// that ends it. Barriers: before (all sources are written), between, and after (nobody reads this PE's dest any more).
+// dest[i] = op over the team's members of source[i] on every member (OpenSHMEM *_reduce / *_to_all). Two steps: member m
+// folds slice m of every member's source in member order 0, 1, ... into slice m of its own dest; then every member fetches
+// the other slices from their owners. Each element is reduced exactly once, so the result is bit-identical everywhere, and
+// dest may be source: slice m of member m is read by nobody but member m in the first step, and the other slices are
+// overwritten only after the barrier that ends it. Barriers: before (all sources are written), between, and after (nobody
+// reads this member's dest any more).
 template <typename T, typename Op>
-__device__ __forceinline__ int reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t nreduce, Op op) {
-  int rc = barrier_all_block(d);
+__device__ __forceinline__ int reduce_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, T* dest, const T* source, size_t nreduce, Op op) {
+  int rc = team_sync_block(d, t);
   if (rc != B200SHMEM_OK) return rc;
-  const size_t per = (nreduce + d.npes - 1) / d.npes;
-  const size_t lo = per * d.pe < nreduce ? per * d.pe : nreduce;
+  const size_t per = (nreduce + t.size - 1) / t.size;
+  const size_t lo = per * t.idx < nreduce ? per * t.idx : nreduce;
   const size_t hi = lo + per < nreduce ? lo + per : nreduce;
   for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    T acc = *(volatile const T*)(ptr(d, source, 0) + i);
-    for (int pe = 1; pe < d.npes; pe++) acc = op(acc, (T) * (volatile const T*)(ptr(d, source, pe) + i));
+    T acc = *(volatile const T*)(ptr(d, source, team_pe(t, 0)) + i);
+    for (int m = 1; m < t.size; m++) acc = op(acc, (T) * (volatile const T*)(ptr(d, source, team_pe(t, m)) + i));
     dest[i] = acc;
   }
-  rc = barrier_all_block(d);
+  rc = team_sync_block(d, t);
   if (rc != B200SHMEM_OK) return rc;
-  for (int k = 1; k < d.npes; k++) {
-    const int q = (d.pe + k) % d.npes;
+  for (int k = 1; k < t.size; k++) {
+    const int q = (t.idx + k) % t.size;
     const size_t qlo = per * q < nreduce ? per * q : nreduce;
     const size_t qhi = qlo + per < nreduce ? qlo + per : nreduce;
-    if (qhi > qlo) getmem_block(d, dest + qlo, dest + qlo, (qhi - qlo) * sizeof(T), q);
+    if (qhi > qlo) getmem_block(d, dest + qlo, dest + qlo, (qhi - qlo) * sizeof(T), team_pe(t, q));
   }
-  return barrier_all_block(d);
+  return team_sync_block(d, t);
 }
+template <typename T> __device__ __forceinline__ int sum_reduce_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, T* dest, const T* source, size_t n) { return reduce_block(d, t, dest, source, n, SumOp{}); }
+template <typename T> __device__ __forceinline__ int max_reduce_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, T* dest, const T* source, size_t n) { return reduce_block(d, t, dest, source, n, MaxOp{}); }
+template <typename T> __device__ __forceinline__ int min_reduce_block(const b200shmem_dev_t& d, const b200shmem_team_t& t, T* dest, const T* source, size_t n) { return reduce_block(d, t, dest, source, n, MinOp{}); }
+
+// The same over all PEs.
+__device__ __forceinline__ int broadcastmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes, int root) { return broadcastmem_block(d, team_world(d), dest, source, bytes, root); }
+__device__ __forceinline__ int fcollectmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes) { return fcollectmem_block(d, team_world(d), dest, source, bytes); }
+__device__ __forceinline__ int alltoallmem_block(const b200shmem_dev_t& d, void* dest, const void* source, size_t bytes) { return alltoallmem_block(d, team_world(d), dest, source, bytes); }
+template <typename T, typename Op>
+__device__ __forceinline__ int reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t nreduce, Op op) { return reduce_block(d, team_world(d), dest, source, nreduce, op); }
 template <typename T> __device__ __forceinline__ int sum_reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t n) { return reduce_block(d, dest, source, n, SumOp{}); }
 template <typename T> __device__ __forceinline__ int max_reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t n) { return reduce_block(d, dest, source, n, MaxOp{}); }
 template <typename T> __device__ __forceinline__ int min_reduce_block(const b200shmem_dev_t& d, T* dest, const T* source, size_t n) { return reduce_block(d, dest, source, n, MinOp{}); }

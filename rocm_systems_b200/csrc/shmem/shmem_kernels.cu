@@ -16,7 +16,8 @@ struct b200shmem_ctx {
   char* heap = nullptr;          // local base of the symmetric window
   size_t heapBytes = 0;
   b200shmem_dev_t dev{};
-  void* devState = nullptr;      // syncEpoch (u64) + status (int) in local device memory
+  void* devState = nullptr;      // syncEpoch (u64) + status (int) + one barrier count per team slot, in local device memory
+  int teamSlots = 1;             // slots of the heap's reserved head handed out so far (slot 0: all PEs)
   std::mutex mu;
   std::map<size_t, size_t> freeList;   // offset -> size
   std::map<size_t, size_t> live;       // offset -> size
@@ -28,7 +29,9 @@ struct b200shmem_ctx {
 
 namespace {
 
-constexpr size_t kReserved = 4096;  // head of the heap: barrier arrival words
+constexpr size_t kReserved = 4096;  // head of the heap: barrier arrival words, 64 bytes (8 PEs) per team slot
+constexpr size_t kDevStateBytes = 64 + 8 * B200SHMEM_MAX_TEAMS;   // epoch, status, then one epoch per team slot
+static_assert(kReserved >= 64 * B200SHMEM_MAX_TEAMS, "one 64-byte slot of arrival words per team");
 constexpr size_t kAlign = 256;
 
 __global__ void kSignal(b200shmem_dev_t d, unsigned long long* sig, unsigned long long value, int op, int pe) {
@@ -180,6 +183,62 @@ __device__ __forceinline__ void collBody(const b200shmem_dev_t& d, unsigned long
 }
 __global__ void kSelftestColl(b200shmem_dev_t d, unsigned long long* buf, size_t cnt, int* errors) { collBody(d, buf, cnt, errors); }
 
+// Collectives inside teams, every team at the same time as the others: `mine` is the team of this PE's parity, `sub` every
+// second member of the even team (idx < 0 where this PE is not in it). Same buffer layout as above.
+__device__ __forceinline__ void teamsBody(const b200shmem_dev_t& d, const b200shmem_team_t& mine, const b200shmem_team_t& sub, unsigned long long* buf,
+                                          size_t cnt, int* errors) {
+  using u64 = unsigned long long;
+  namespace sh = b200shmem;
+  const int n = d.npes, me = d.pe, ts = mine.size, ti = mine.idx;
+  u64* A = buf;
+  u64* B = A + (size_t)n * cnt;
+  u64* R = B + (size_t)n * cnt;
+  int bad = 0;
+  if (sh::team_my_pe(mine) != ti || sh::team_n_pes(mine) != ts || sh::team_pe(mine, ti) != me) bad++;
+  if (sh::team_translate_pe(mine, ti, sh::team_world(d)) != me || sh::team_translate_pe(sh::team_world(d), me, mine) != ti) bad++;
+  if (n > 1 && sh::team_translate_pe(sh::team_world(d), (me + 1) % n, mine) != -1) bad++;   // the neighbour has the other parity
+  if (sh::team_sync_block(d, mine) != B200SHMEM_OK) bad++;
+  const int root = ts - 1;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) A[i] = (u64)me * 131 + i;
+  __syncthreads();
+  if (sh::broadcastmem_block(d, mine, B, A, cnt * 8, root) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x)
+    if (B[i] != (u64)sh::team_pe(mine, root) * 131 + i) bad++;
+  if (sh::barrier_all_block(d) != B200SHMEM_OK) bad++;   // a barrier of all PEs between two team collectives: separate counters
+  if (sh::fcollectmem_block(d, mine, B, A, cnt * 8) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < (size_t)ts * cnt; i += blockDim.x)
+    if (B[i] != (u64)sh::team_pe(mine, (int)(i / cnt)) * 131 + i % cnt) bad++;
+  if (sh::team_sync_block(d, mine) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < (size_t)ts * cnt; i += blockDim.x) A[i] = (u64)me * 100000 + (u64)(i / cnt) * 1000 + i % cnt;
+  __syncthreads();
+  if (sh::alltoallmem_block(d, mine, B, A, cnt * 8) != B200SHMEM_OK) bad++;
+  for (size_t i = threadIdx.x; i < (size_t)ts * cnt; i += blockDim.x)
+    if (B[i] != (u64)sh::team_pe(mine, (int)(i / cnt)) * 100000 + (u64)ti * 1000 + i % cnt) bad++;
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) R[i] = (u64)me + i;
+  __syncthreads();
+  if (sh::sum_reduce_block(d, mine, R, R, cnt) != B200SHMEM_OK) bad++;
+  u64 peSum = 0;
+  for (int m = 0; m < ts; m++) peSum += (u64)sh::team_pe(mine, m);
+  for (size_t i = threadIdx.x; i < cnt; i += blockDim.x)
+    if (R[i] != (u64)ts * i + peSum) bad++;
+  if (sub.idx >= 0) {   // a team of a team: its members only
+    for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) A[i] = (u64)((me * 5 + i) % 11);
+    __syncthreads();
+    if (sh::max_reduce_block(d, sub, B, A, cnt) != B200SHMEM_OK) bad++;
+    for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) {
+      u64 m = 0;
+      for (int k = 0; k < sub.size; k++) m = max(m, (u64)((sh::team_pe(sub, k) * 5 + i) % 11));
+      if (B[i] != m) bad++;
+    }
+  }
+  if (sh::barrier_all_block(d) != B200SHMEM_OK) bad++;
+  if (bad) atomicAdd(errors, bad);
+}
+__global__ void kSelftestTeams(b200shmem_dev_t d, b200shmem_team_t mine, b200shmem_team_t sub, unsigned long long* buf, size_t cnt, int* errors) {
+  teamsBody(d, mine, sub, buf, cnt, errors);
+}
+__global__ void kTeamSync(b200shmem_dev_t d, b200shmem_team_t t) { b200shmem::team_sync_block(d, t); }
+
 // Several PEs on one GPU: block r of ONE cooperative launch is PE r (kernels of PEs that wait on one another must never
 // be separate launches on one GPU). The bodies are the ones above, each on its PE's own device context.
 struct EmuShmemPack {
@@ -189,6 +248,7 @@ struct EmuShmemPack {
   unsigned long long* sig[B200SHMEM_MAX_PES];
   unsigned long long* words[B200SHMEM_MAX_PES];
   unsigned long long* coll[B200SHMEM_MAX_PES];
+  b200shmem_team_t mine[B200SHMEM_MAX_PES], sub[B200SHMEM_MAX_PES];
   size_t collCount;
   size_t count;
   int rounds, iters;
@@ -205,6 +265,10 @@ __global__ void kEmuAtomics(const EmuShmemPack* p) {
 __global__ void kEmuColl(const EmuShmemPack* p) {
   const int r = blockIdx.x;
   collBody(p->d[r], p->coll[r], p->collCount, p->errors);
+}
+__global__ void kEmuTeams(const EmuShmemPack* p) {
+  const int r = blockIdx.x;
+  teamsBody(p->d[r], p->mine[r], p->sub[r], p->coll[r], p->collCount, p->errors);
 }
 
 struct DevGuard {
@@ -234,8 +298,8 @@ ncclResult_t b200shmem_init(ncclComm_t comm, size_t heapBytes, b200shmem_ctx_t* 
   ctx->heap = (char*)p;
   ctx->heapBytes = heapBytes + kReserved;
   DevGuard g(c->cudaDev);
-  BCUDA(cudaMalloc(&ctx->devState, 64));
-  BCUDA(cudaMemset(ctx->devState, 0, 64));
+  BCUDA(cudaMalloc(&ctx->devState, kDevStateBytes));
+  BCUDA(cudaMemset(ctx->devState, 0, kDevStateBytes));
   b200shmem_dev_t& d = ctx->dev;
   d.pe = c->rank;
   d.npes = c->nranks;
@@ -338,6 +402,57 @@ void* b200shmem_mc_ptr(b200shmem_ctx_t ctx, const void* ptr) {
 ncclResult_t b200shmem_device_ctx(b200shmem_ctx_t ctx, b200shmem_dev_t* out) {
   if (!ctx || !out) BFAIL(ncclInvalidArgument, "b200shmem_device_ctx: null argument");
   *out = ctx->dev;
+  return ncclSuccess;
+}
+
+// ---- teams ---------------------------------------------------------------------------------------------------------------
+ncclResult_t b200shmem_team_world(b200shmem_ctx_t ctx, b200shmem_team_t* team) {
+  if (!ctx || !team) BFAIL(ncclInvalidArgument, "b200shmem_team_world: null argument");
+  *team = b200shmem_team_t{0, 1, ctx->dev.npes, ctx->dev.pe, ctx->dev.syncFlags, ctx->dev.syncEpoch};
+  return ncclSuccess;
+}
+
+ncclResult_t b200shmem_team_split_strided(b200shmem_ctx_t ctx, const b200shmem_team_t* parent, int start, int stride, int size, b200shmem_team_t* team) {
+  if (!ctx || !team) BFAIL(ncclInvalidArgument, "b200shmem_team_split_strided: null argument");
+  b200shmem_team_t world;
+  BCHECK(b200shmem_team_world(ctx, &world));
+  const b200shmem_team_t& par = parent ? *parent : world;
+  if (size < 1 || stride < 1 || start < 0 || start + (size - 1) * stride >= par.size)
+    BFAIL(ncclInvalidArgument, "b200shmem_team_split_strided: members %d + i * %d, i < %d, do not lie inside a parent of %d", start, stride, size, par.size);
+  int slot;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (ctx->teamSlots >= B200SHMEM_MAX_TEAMS) BFAIL(ncclInvalidUsage, "b200shmem_team_split_strided: at most %d teams per context", B200SHMEM_MAX_TEAMS - 1);
+    slot = ctx->teamSlots++;   // every PE makes the same calls in the same order, so the slots agree
+  }
+  team->start = par.start + start * par.stride;
+  team->stride = stride * par.stride;
+  team->size = size;
+  const int off = ctx->dev.pe - team->start;
+  team->idx = (off >= 0 && off % team->stride == 0 && off / team->stride < size) ? off / team->stride : -1;
+  team->syncFlags = (unsigned long long*)(ctx->heap + 64 * (size_t)slot);
+  team->syncEpoch = (unsigned long long*)((char*)ctx->devState + 64 + 8 * (size_t)slot);
+  return ncclSuccess;
+}
+
+void b200shmem_team_destroy(b200shmem_ctx_t, b200shmem_team_t* team) {
+  if (team) *team = b200shmem_team_t{0, 1, 0, -1, nullptr, nullptr};
+}
+int b200shmem_team_my_pe(const b200shmem_team_t* team) { return team ? team->idx : -1; }
+int b200shmem_team_n_pes(const b200shmem_team_t* team) { return team ? team->size : 0; }
+int b200shmem_team_translate_pe(const b200shmem_team_t* src, int idx, const b200shmem_team_t* dst) {
+  if (!src || !dst || idx < 0 || idx >= src->size || dst->size < 1) return -1;
+  const int off = src->start + idx * src->stride - dst->start;
+  if (off < 0 || off % dst->stride) return -1;
+  return off / dst->stride < dst->size ? off / dst->stride : -1;
+}
+
+ncclResult_t b200shmem_team_sync_on_stream(b200shmem_ctx_t ctx, const b200shmem_team_t* team, cudaStream_t stream) {
+  if (!ctx || !team) BFAIL(ncclInvalidArgument, "b200shmem_team_sync_on_stream: null argument");
+  if (team->idx < 0) BFAIL(ncclInvalidUsage, "b200shmem_team_sync_on_stream: this PE is not a member of the team");
+  DevGuard g(ctx->comm->cudaDev);
+  kTeamSync<<<1, 32, 0, stream>>>(ctx->dev, *team);
+  BCUDA(cudaGetLastError());
   return ncclSuccess;
 }
 
@@ -449,6 +564,42 @@ ncclResult_t b200shmem_selftest_collectives(b200shmem_ctx_t ctx, size_t count, c
   BCHECK(b200shmem_barrier_all_on_stream(ctx, stream));  // the flag words are zero everywhere before anyone writes one
   kSelftestColl<<<1, 256, 0, stream>>>(ctx->dev, buf, count, derr);
   BCUDA(cudaGetLastError());
+  BCUDA(cudaMemcpyAsync(errors, derr, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  BCUDA(cudaStreamSynchronize(stream));
+  cudaFree(derr);
+  BCHECK(ctx->comm->boot.barrier());
+  b200shmem_free(ctx, buf);
+  return ncclSuccess;
+}
+
+// The PEs split into the even and the odd ones, the even team once more into every second member; the same calls on every PE.
+static ncclResult_t makeSelftestTeams(b200shmem_ctx_t ctx, b200shmem_team_t* mine, b200shmem_team_t* sub) {
+  const int n = ctx->dev.npes;
+  b200shmem_team_t even{}, odd{0, 1, 0, -1, nullptr, nullptr};
+  BCHECK(b200shmem_team_split_strided(ctx, nullptr, 0, 2, (n + 1) / 2, &even));
+  if (n >= 2) BCHECK(b200shmem_team_split_strided(ctx, nullptr, 1, 2, n / 2, &odd));
+  *sub = b200shmem_team_t{0, 1, 0, -1, nullptr, nullptr};
+  if (even.size >= 2) BCHECK(b200shmem_team_split_strided(ctx, &even, 0, 2, (even.size + 1) / 2, sub));
+  *mine = (ctx->dev.pe & 1) ? odd : even;
+  return ncclSuccess;
+}
+
+ncclResult_t b200shmem_selftest_teams(b200shmem_ctx_t ctx, size_t count, cudaStream_t stream, int* errors) {
+  if (!ctx || !errors || count < 2) BFAIL(ncclInvalidArgument, "b200shmem_selftest_teams: bad arguments");
+  DevGuard g(ctx->comm->cudaDev);
+  b200shmem_team_t mine, sub;
+  BCHECK(makeSelftestTeams(ctx, &mine, &sub));
+  const size_t bytes = collWords(ctx->dev.npes, count) * 8;
+  unsigned long long* buf = (unsigned long long*)b200shmem_malloc(ctx, bytes);
+  if (!buf) BFAIL(ncclSystemError, "b200shmem_selftest_teams: symmetric heap too small");
+  int* derr = nullptr;
+  BCUDA(cudaMalloc(&derr, sizeof(int)));
+  BCUDA(cudaMemsetAsync(derr, 0, sizeof(int), stream));
+  BCUDA(cudaMemsetAsync(buf, 0, bytes, stream));
+  BCHECK(b200shmem_barrier_all_on_stream(ctx, stream));
+  kSelftestTeams<<<1, 256, 0, stream>>>(ctx->dev, mine, sub, buf, count, derr);
+  BCUDA(cudaGetLastError());
+  BCHECK(b200shmem_team_sync_on_stream(ctx, &mine, stream));   // the stream-ordered form, on the team's own counter
   BCUDA(cudaMemcpyAsync(errors, derr, sizeof(int), cudaMemcpyDeviceToHost, stream));
   BCUDA(cudaStreamSynchronize(stream));
   cudaFree(derr);
@@ -597,6 +748,7 @@ ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int 
     BCUDA(cudaMemset(pack.sig[r], 0, 256));
     BCUDA(cudaMemset(pack.words[r], 0, 256));
   }
+  for (int r = 0; r < n; r++) BCHECK(makeSelftestTeams(ctx[r], &pack.mine[r], &pack.sub[r]));
   EmuShmemPack* dpack = nullptr;
   BCUDA(cudaMalloc(&dpack, sizeof(pack)));
   BCUDA(cudaMemcpy(dpack, &pack, sizeof(pack), cudaMemcpyHostToDevice));
@@ -607,6 +759,8 @@ ncclResult_t b200shmem_emu_selftest(ncclComm_t* comms, int n, size_t count, int 
   if (e == cudaSuccess) e = cudaLaunchCooperativeKernel((const void*)kEmuAtomics, dim3(n), dim3(32), args, 0, 0);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaLaunchCooperativeKernel((const void*)kEmuColl, dim3(n), dim3(256), args, 0, 0);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaLaunchCooperativeKernel((const void*)kEmuTeams, dim3(n), dim3(256), args, 0, 0);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "b200shmem_emu_selftest: %s", cudaGetErrorString(e));
   BCUDA(cudaMemcpy(errors, derr, sizeof(int), cudaMemcpyDeviceToHost));

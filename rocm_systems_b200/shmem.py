@@ -55,8 +55,23 @@ def _l():
         lib.b200shmem_putmem_signal_dma_on_stream.argtypes = [vp, vp, vp, sz, vp, u64, i32, i32, i32, vp]
         lib.b200shmem_dma_plan.argtypes = [sz, i32, ctypes.POINTER(sz), ctypes.POINTER(sz)]
         lib.b200shmem_dma_engines.argtypes = [vp]
+        tp = ctypes.POINTER(Team)
+        lib.b200shmem_team_world.argtypes = [vp, tp]
+        lib.b200shmem_team_split_strided.argtypes = [vp, tp, i32, i32, i32, tp]
+        lib.b200shmem_team_translate_pe.argtypes = [tp, i32, tp]
+        lib.b200shmem_team_sync_on_stream.argtypes = [vp, tp, vp]
         _sigs = True
     return lib
+
+
+class Team(ctypes.Structure):
+    """``b200shmem_team_t``: the PEs ``start + i * stride`` for ``i < size``; ``idx`` is this PE's index in it (-1: not a
+    member). Kernels take it by value next to the device context."""
+    _fields_ = [("start", ctypes.c_int), ("stride", ctypes.c_int), ("size", ctypes.c_int), ("idx", ctypes.c_int),
+                ("sync_flags", ctypes.c_void_p), ("sync_epoch", ctypes.c_void_p)]
+
+    def pes(self) -> list:
+        return [self.start + i * self.stride for i in range(self.size)]
 
 
 def _stream(stream) -> int:
@@ -166,3 +181,23 @@ class Shmem:
 
     def take_status(self) -> int:
         return int(self.lib.b200shmem_take_status(self._ctx))
+
+    # ---- teams ------------------------------------------------------------------------------------------------------
+    def team_world(self) -> Team:
+        t = Team()
+        _lib.check(self.lib.b200shmem_team_world(self._ctx, ctypes.byref(t)), "team_world")
+        return t
+
+    def team_split_strided(self, parent, start: int, stride: int, size: int) -> Team:
+        """The team of ``parent``'s members ``start, start + stride, ...`` (``size`` of them; ``parent=None``: all PEs).
+        EVERY PE of the context must make the same split calls in the same order, members or not."""
+        t = Team()
+        _lib.check(self.lib.b200shmem_team_split_strided(self._ctx, ctypes.byref(parent) if parent is not None else None, start, stride, size,
+                                                         ctypes.byref(t)), "team_split_strided")
+        return t
+
+    def team_translate_pe(self, src: Team, idx: int, dst: Team) -> int:
+        return int(self.lib.b200shmem_team_translate_pe(ctypes.byref(src), idx, ctypes.byref(dst)))
+
+    def team_sync(self, team: Team, stream=None) -> None:
+        _lib.check(self.lib.b200shmem_team_sync_on_stream(self._ctx, ctypes.byref(team), _stream(stream)), "team_sync")

@@ -86,3 +86,25 @@ def test_push_collectives_place_every_block():
     for i in range(n):
         dest[(1 + i) % n][:] = src[1]
     assert all(np.array_equal(d, src[1]) for d in dest)
+
+
+def test_team_pe_translation_matches_the_set_definition():
+    """b200shmem_team_translate_pe (host form; the device form is the same arithmetic) against the definition: member idx of
+    src is PE start + idx * stride; its number in dst is its position in dst's member list, or -1."""
+    import ctypes
+
+    from rocm_systems_b200 import shmem
+
+    lib = shmem._l()
+    teams = [(0, 1, 8), (0, 2, 4), (1, 2, 4), (0, 4, 2), (2, 3, 2), (5, 1, 3), (7, 1, 1)]
+    for s in teams:
+        for d in teams:
+            src, dst = shmem.Team(*s, 0, None, None), shmem.Team(*d, 0, None, None)
+            for idx in range(-1, s[2] + 1):
+                got = lib.b200shmem_team_translate_pe(ctypes.byref(src), idx, ctypes.byref(dst))
+                if 0 <= idx < s[2]:
+                    pe = s[0] + idx * s[1]
+                    want = dst.pes().index(pe) if pe in dst.pes() else -1
+                else:
+                    want = -1
+                assert got == want, (s, d, idx, got, want)

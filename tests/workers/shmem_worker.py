@@ -20,6 +20,7 @@ def main():
     lib.b200shmem_selftest_ring.argtypes = [vp, ctypes.c_size_t, ctypes.c_int, vp, ctypes.POINTER(ctypes.c_int)]
     lib.b200shmem_selftest_atomics.argtypes = [vp, ctypes.c_int, vp, ctypes.POINTER(ctypes.c_int)]
     lib.b200shmem_selftest_collectives.argtypes = [vp, ctypes.c_size_t, vp, ctypes.POINTER(ctypes.c_int)]
+    lib.b200shmem_selftest_teams.argtypes = [vp, ctypes.c_size_t, vp, ctypes.POINTER(ctypes.c_int)]
     lib.b200shmem_take_status.argtypes = [vp]
     lib.b200shmem_malloc.argtypes = [vp, ctypes.c_size_t]
     lib.b200shmem_malloc.restype = vp
@@ -42,6 +43,10 @@ def main():
         _lib.check(lib.b200shmem_selftest_collectives(ctx, 1000, s, ctypes.byref(errs)), "selftest_collectives")
         if errs.value != 0:
             bad.append(("collectives", errs.value))
+        # the same collectives inside teams (even PEs, odd PEs, every second even PE), all teams at once
+        _lib.check(lib.b200shmem_selftest_teams(ctx, 1000, s, ctypes.byref(errs)), "selftest_teams")
+        if errs.value != 0:
+            bad.append(("teams", errs.value))
     # host-initiated, stream-ordered put with signal to the right neighbour
     n, rank = comm.nranks, comm.rank
     count = 1 << 16

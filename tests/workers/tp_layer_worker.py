@@ -82,6 +82,9 @@ def main():
     ap.add_argument("--seq", type=int, default=256)
     ap.add_argument("--comm-ctas", type=int, default=0)
     ap.add_argument("--tol", type=float, default=4e-2)
+    ap.add_argument("--time", action="store_true")        # device time of forward + backward after the check
+    ap.add_argument("--skip-check", action="store_true")
+    ap.add_argument("--out", default="")
     args = ap.parse_args()
     comm = init_from_env()
     rank, n, dev = comm.rank, comm.nranks, comm.device
@@ -107,7 +110,7 @@ def main():
     mlp = mlps[0]
     shards_mlp = [{"wg": leaf(a), "wu": leaf(b), "w2": leaf(c)} for a, b, c in zip(gather(comm, mlp.w_gate), gather(comm, mlp.w_up), gather(comm, mlp.w2))]
 
-    for trial in range(2):   # the second pass runs on the buffers and call counters the first one left
+    for trial in range(0 if args.skip_check else 2):   # the second pass runs on the buffers and call counters the first one left
         for s in shards_mlp:
             for t in s.values():
                 t.grad = None
@@ -148,6 +151,31 @@ def main():
             rel[tag + "dw_o"] = close("dw_o", mod.attn.grads["w_o"], shards_att[rank]["wo"].grad, args.tol, bad)
             rel[tag + "dnorm1"] = close("dnorm1", mod.grads["norm1"], n1w.grad, args.tol, bad)
             rel[tag + "dnorm2"] = close("dnorm2", mod.grads["norm2"], n2w.grad, args.tol, bad)
+    if args.time and not bad:
+        def dev_ms(fn, warmup=3, iters=10):
+            for _ in range(warmup):
+                fn()
+            torch.cuda.synchronize()
+            comm.host_barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            parts = comm.host_all_gather(float(a.elapsed_time(b) / iters).hex().encode().ljust(32))
+            return max(float.fromhex(p.decode().strip()) for p in parts)
+
+        M, H = n * args.rows, args.hidden
+        f = args.ffn // n
+        gemm_flops = 2.0 * M * H * 3 * f                     # gate, up, down of this rank's shard
+        if args.what == "layer":
+            att = mod.attn
+            gemm_flops += 2.0 * M * H * (att.w_qkv.shape[0] + att.hq * att.d)
+        rel["forward_ms"] = dev_ms(lambda: mod.forward(x))
+        rel["forward_backward_ms"] = dev_ms(lambda: (mod.forward(x), mod.backward(dy)))
+        rel["gemm_tflops_per_gpu_fwd_bwd"] = 3.0 * gemm_flops / (rel["forward_backward_ms"] * 1e-3) / 1e12
+        rel["shape"] = {"rows_per_rank": args.rows, "hidden": H, "ffn_per_rank": f, "tp": n, "what": args.what}
     err = comm.async_error()
     if err:
         bad.append(("async_error", err, comm.last_error()))
@@ -155,7 +183,9 @@ def main():
     if bad:
         print(f"[rank {rank}] TP LAYER MISMATCH: {bad}", flush=True)
     elif rank == 0:
-        print(f"tp_layer_worker OK ({args.what}) on {n} ranks: {json.dumps({k: round(v, 5) for k, v in rel.items()})}", flush=True)
+        print(f"tp_layer_worker OK ({args.what}) on {n} ranks: {json.dumps({k: (round(v, 5) if isinstance(v, float) else v) for k, v in rel.items()})}", flush=True)
+        if args.out:
+            Path(args.out).write_text(json.dumps(rel))
     mod.free()
     comm.destroy()
     sys.exit(1 if any(f[0] for f in flags) else 0)
