@@ -628,16 +628,19 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
         }
         ctaBarrier(c, epoch);
       } else {
+        // The root pushes: one multicast store stream through the switch, or plain stores into every peer's staging
+        // (stores run faster over NVLink than the loads of a pull: 690 against 613 GB/s between two GPUs). Each
+        // receiver then copies out of its OWN staging half while the root fills the other one.
         if (rank == a.root) {
-          if constexpr (NVLS) ctaCopyToMc(c.wsMc + stageBase + bo, send + off + bo, bytes);
-          else ctaCopy(c.ws[rank] + stageBase + bo, send + off + bo, bytes);
+          if constexpr (NVLS) {
+            ctaCopyToMc(c.wsMc + stageBase + bo, send + off + bo, bytes);
+          } else {
+            for (int i = 1; i < n; i++) ctaCopy(c.ws[(rank + i) % n] + stageBase + bo, send + off + bo, bytes);
+          }
           if (recv != send) ctaCopy(recv + off + bo, send + off + bo, bytes);
         }
         ctaBarrier(c, epoch);
-        if (rank != a.root) {
-          const char* src = NVLS ? c.ws[rank] + stageBase + bo : c.ws[a.root] + stageBase + bo;
-          ctaCopy(recv + off + bo, src, bytes);
-        }
+        if (rank != a.root) ctaCopy(recv + off + bo, c.ws[rank] + stageBase + bo, bytes);
       }
     }
   }
