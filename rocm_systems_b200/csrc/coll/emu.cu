@@ -373,6 +373,9 @@ ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int
       res = b200collEmuCollective(comms.data(), nranks, cs.kind, send.data(), recv.data(), count, dt, cs.op, cs.root, 0, st);
       if (res != ncclSuccess) break;
       BCUDA(cudaStreamSynchronize(st));
+      const long long wrongBefore = *wrong;
+      long long firstBad = -1, lastBad = -1;
+      int firstBadRank = -1;
       for (int r = 0; r < nranks; r++) {
         if (cs.kind == COLL_REDUCE && r != cs.root) continue;
         std::vector<char> out(recvElems * es + 64);
@@ -395,11 +398,18 @@ ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int
           }
           const double got = decode(out, i);
           const double tol = cs.op == ncclAvg ? (dt == ncclBfloat16 ? 0.05 : 1e-5) : 0.0;
-          if (!(got >= want - tol && got <= want + tol)) (*wrong)++;
+          if (!(got >= want - tol && got <= want + tol)) {
+            (*wrong)++;
+            if (firstBad < 0) { firstBad = (long long)i; firstBadRank = r; }
+            lastBad = (long long)i;
+          }
         }
         for (size_t b = recvElems * es; b < recvElems * es + 64; b++)  // the bytes behind the output keep their fill
           if ((unsigned char)out[b] != 0xEE) (*wrong)++;
       }
+      if (*wrong != wrongBefore)
+        BWARN("emulated ranks: %lld wrong values in kind %d op %d type %s, %d ranks, count %zu; first at rank %d element %lld, last at element %lld",
+              *wrong - wrongBefore, cs.kind, (int)cs.op, dtypeName(dt), nranks, count, firstBadRank, firstBad, lastBad);
     }
   }
   // The fused FSDP gradient path: bf16 gradients of every rank -> this rank's fp32 mean.

@@ -196,7 +196,8 @@ __device__ __forceinline__ void teamsBody(const b200shmem_dev_t& d, const b200sh
   int bad = 0;
   if (sh::team_my_pe(mine) != ti || sh::team_n_pes(mine) != ts || sh::team_pe(mine, ti) != me) bad++;
   if (sh::team_translate_pe(mine, ti, sh::team_world(d)) != me || sh::team_translate_pe(sh::team_world(d), me, mine) != ti) bad++;
-  if (n > 1 && sh::team_translate_pe(sh::team_world(d), (me + 1) % n, mine) != -1) bad++;   // the neighbour has the other parity
+  const int nb = (me + 1) % n;   // a neighbour of the other parity is in no team of this one's
+  if (((nb ^ me) & 1) && sh::team_translate_pe(sh::team_world(d), nb, mine) != -1) bad++;
   if (sh::team_sync_block(d, mine) != B200SHMEM_OK) bad++;
   const int root = ts - 1;
   for (size_t i = threadIdx.x; i < cnt; i += blockDim.x) A[i] = (u64)me * 131 + i;
