@@ -195,6 +195,14 @@ ncclResult_t b200collEmuCollective(ncclComm_t* comms, int n, int kind, const voi
     q.stream = stream;
     q.forceCtas = ctasPerRank > 0 ? ctasPerRank : 4;
     Plan plan{};
+    if (kind == COLL_ALLTOALL) {  // the staged form for large chunks; `count` elements per pair
+      int ctas = 0;
+      stagedAllToAllArgs(c, send[r], recv[r], count, dt, q.forceCtas, &pack.a[r], &pack.c[r], &ctas);
+      plan.algo = ALGO_P2P;
+      plan.ctas = ctas;
+      if (r == 0) first = plan;
+      continue;
+    }
     BCHECK(emuPrepare(q, &plan, &pack.a[r], &pack.ll[r], &pack.c[r]));
     if (r == 0) first = plan;
     if (plan.algo != first.algo || plan.ctas != first.ctas || plan.chunks != first.chunks || plan.direct != first.direct)
@@ -468,6 +476,33 @@ ncclResult_t b200collEmuSelftest(int nranks, size_t count, long long* wrong, int
         for (size_t i = words * nranks; i < words * nranks + 16; i++)
           if ((uint32_t)out[i] != 0xEEEEEEEEu) (*wrong)++;
       }
+    }
+  }
+  // The same exchange through the staging halves (the form for large chunks): several steps with the small staging of this test.
+  if (res == ncclSuccess) {
+    salt++;
+    const size_t words = count;  // elements per pair
+    for (int r = 0; r < nranks; r++) {
+      std::vector<int32_t> in(words * nranks);
+      for (size_t i = 0; i < in.size(); i++) in[i] = value(r, i, salt) + 100 * r;
+      BCUDA(cudaMemcpyAsync(send[r], in.data(), in.size() * 4, cudaMemcpyHostToDevice, st));
+      BCUDA(cudaMemsetAsync(recv[r], 0xEE, words * nranks * 4 + 64, st));
+      BCUDA(cudaStreamSynchronize(st));
+    }
+    res = b200collEmuCollective(comms.data(), nranks, COLL_ALLTOALL, send.data(), recv.data(), words, ncclInt32, ncclSum, 0, 0, st);
+    if (res == ncclSuccess) {
+      BCUDA(cudaStreamSynchronize(st));
+      const long long before = *wrong;
+      for (int r = 0; r < nranks; r++) {
+        std::vector<int32_t> out(words * nranks + 16);
+        BCUDA(cudaMemcpy(out.data(), recv[r], out.size() * 4, cudaMemcpyDeviceToHost));
+        for (int src = 0; src < nranks; src++)
+          for (size_t i = 0; i < words; i++)
+            if (out[(size_t)src * words + i] != value(src, (size_t)r * words + i, salt) + 100 * src) (*wrong)++;
+        for (size_t i = words * nranks; i < words * nranks + 16; i++)
+          if ((uint32_t)out[i] != 0xEEEEEEEEu) (*wrong)++;
+      }
+      if (*wrong != before) BWARN("emulated ranks: %lld wrong values in the staged all-to-all, %d ranks, %zu elements per pair", *wrong - before, nranks, count);
     }
   }
   // Device-initiated communication: put+signal ring and remote atomics, every PE a block of one kernel.

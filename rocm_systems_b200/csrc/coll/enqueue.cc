@@ -396,6 +396,49 @@ ncclResult_t enqueueLLAllToAll(Comm* c, int apiId, const void* send, void* recv,
   return ncclSuccess;
 }
 
+// Arguments of the staged all-to-all for one rank: steps and staging parity as the kernel walks them. forceCtas: 0 = by size.
+void stagedAllToAllArgs(Comm* c, const void* send, void* recv, size_t count, ncclDataType_t dt, int forceCtas, CollArgs* args, DevComm* dc, int* ctas) {
+  const size_t bytes = count * dtypeSize(dt);
+  const int n = c->nranks;
+  *dc = c->dev;
+  dc->opSeq = ++c->opSeq;
+  dc->stamp = nullptr;
+  memset(args, 0, sizeof(*args));
+  args->send = send;
+  args->recv = recv;
+  args->count = count;
+  args->kind = COLL_ALLTOALL;
+  const size_t slotCap = (c->dev.stageBytes / (size_t)n) & ~(size_t)15;
+  const size_t cap = std::min(slotCap, (bytes + 15) & ~(size_t)15);
+  const size_t steps = (bytes + cap - 1) / cap;
+  args->stageHalf = (int)(c->stageParity & 1);
+  c->stageParity += (uint32_t)steps;
+  *ctas = forceCtas > 0 ? forceCtas : std::max(1, std::min(ctasFor(c, bytes * n, ALGO_P2P), c->maxCtas));
+}
+
+// All-to-all of large chunks through the staging halves (kStagedCopy, kind COLL_ALLTOALL): peer stores into per-source
+// slots, one barrier per step, local copy-out. count: elements per pair.
+ncclResult_t enqueueStagedAllToAll(Comm* c, int apiId, const void* send, void* recv, size_t count, ncclDataType_t dt, cudaStream_t stream) {
+  BCHECK(commCheck(c));
+  if (c->asyncError.load() != ncclSuccess) BFAIL((ncclResult_t)c->asyncError.load(), "communicator is in an error state: %s", c->lastErr.c_str());
+  if (!send || !recv) BFAIL(ncclInvalidArgument, "null buffer");
+  const size_t es = dtypeSize(dt), bytes = count * es;
+  const int n = c->nranks;
+  DeviceGuard guard(c->cudaDev);
+  Tracer* tr = c->tracer;
+  TraceStamp* stamp = tr ? tr->begin(apiId, dt, count, bytes * n) : nullptr;
+  DevComm dc;
+  CollArgs args;
+  int ctas = 0;
+  stagedAllToAllArgs(c, send, recv, count, dt, 0, &args, &dc, &ctas);
+  dc.stamp = stamp;
+  if (tr) tr->setAlgo(ALGO_P2P, ctas);
+  cudaError_t e = launchStagedCopy(false, ctas, stream, dc, args, (int)es);
+  if (tr) tr->end(e == cudaSuccess);
+  if (e != cudaSuccess) BFAIL(ncclUnhandledCudaError, "all-to-all launch failed: %s", cudaGetErrorString(e));
+  return ncclSuccess;
+}
+
 ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops) {
   BCHECK(commCheck(c));
   if (ops.empty()) return ncclSuccess;

@@ -519,7 +519,11 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
   const int n = c.nranks, rank = c.rank, B = gridDim.x, b = blockIdx.x;
   uint32_t epoch = c.local->barEpoch[b];
   const size_t total = a.count * (size_t)elemSize;  // AllGather: one rank's contribution; Broadcast: the message
-  const size_t cap = a.direct ? ((total + 15) & ~(size_t)15) : ((a.chunkBytes && a.chunkBytes < c.stageBytes) ? a.chunkBytes : c.stageBytes);
+  const bool isA2A = a.kind == COLL_ALLTOALL;
+  // All-to-all: a staging half holds one slot per source rank; a step moves at most a slot of every pair's chunk.
+  const size_t slotCap = (c.stageBytes / (size_t)n) & ~(size_t)15;
+  const size_t cap = isA2A ? (((total + 15) & ~(size_t)15) < slotCap ? ((total + 15) & ~(size_t)15) : slotCap)
+                           : (a.direct ? ((total + 15) & ~(size_t)15) : ((a.chunkBytes && a.chunkBytes < c.stageBytes) ? a.chunkBytes : c.stageBytes));
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   int half = a.stageHalf;
@@ -590,6 +594,35 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
     return;
   }
 
+  if (isA2A) {
+    // Staged all-to-all for large chunks (total = bytes per pair): every rank stores its piece for peer p into slot
+    // `rank` of p's staging half (plain peer stores, the fast direction of the link) while a quarter of its threads copy
+    // the rank's own block; after one barrier everybody copies its slots out, and the next step fills the other half.
+    // A half is written again only two steps later, after a barrier that every rank reaches behind its copy-out.
+    const int nt = blockDim.x, tid = threadIdx.x, hl = nt >> 2;
+    for (size_t off = 0; off < total; off += cap, half ^= 1) {
+      const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
+      size_t bo, bytes;
+      part(off, bo, bytes);
+      if (tid < hl) {
+        groupCopy(recv + (size_t)rank * total + off + bo, send + (size_t)rank * total + off + bo, bytes, tid, hl);
+      } else {
+        for (int i = 1; i < n; i++) {
+          const int p = (rank + i) % n;
+          groupCopy(c.ws[p] + stageBase + (size_t)rank * slotCap + bo, send + (size_t)p * total + off + bo, bytes, tid - hl, nt - hl);
+        }
+      }
+      ctaBarrier(c, epoch);
+      for (int i = 1; i < n; i++) {
+        const int s = (rank + n - i) % n;
+        ctaCopy(recv + (size_t)s * total + off + bo, c.ws[rank] + stageBase + (size_t)s * slotCap + bo, bytes);
+      }
+    }
+    if (threadIdx.x == 0) c.local->barEpoch[b] = epoch;
+    stampEnd(c);
+    return;
+  }
+
   for (size_t off = 0; off < total; off += cap, half ^= 1) {
     const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
     size_t bo, bytes;  // byte offset of this CTA's part inside the chunk, and its length
@@ -619,10 +652,14 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
           if constexpr (NVLS) {
             ctaCopyToMc(a.recvMc + off + bo, send + off + bo, bytes);
           } else {
-            for (int i = 0; i < n; i++) {
-              const int p = (rank + i) % n;
-              if (p == rank && recv + off + bo == send + off + bo) continue;
-              ctaCopy(a.recvPeer[p] + off + bo, send + off + bo, bytes);
+            // A quarter of the threads make the root's own copy (local memory, several times faster than the link)
+            // while the others store to the peers, instead of one after the other.
+            const int nt = blockDim.x, tid = threadIdx.x;
+            const int hl = (recv != send) ? nt >> 2 : 0;
+            if (tid < hl) {
+              groupCopy(recv + off + bo, send + off + bo, bytes, tid, hl);
+            } else {
+              for (int i = 1; i < n; i++) groupCopy(a.recvPeer[(rank + i) % n] + off + bo, send + off + bo, bytes, tid - hl, nt - hl);
             }
           }
         }
@@ -634,10 +671,16 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
         if (rank == a.root) {
           if constexpr (NVLS) {
             ctaCopyToMc(c.wsMc + stageBase + bo, send + off + bo, bytes);
+            if (recv != send) ctaCopy(recv + off + bo, send + off + bo, bytes);
           } else {
-            for (int i = 1; i < n; i++) ctaCopy(c.ws[(rank + i) % n] + stageBase + bo, send + off + bo, bytes);
+            const int nt = blockDim.x, tid = threadIdx.x;
+            const int hl = (recv != send) ? nt >> 2 : 0;   // the root's own copy runs beside the stores to the peers
+            if (tid < hl) {
+              groupCopy(recv + off + bo, send + off + bo, bytes, tid, hl);
+            } else {
+              for (int i = 1; i < n; i++) groupCopy(c.ws[(rank + i) % n] + stageBase + bo, send + off + bo, bytes, tid - hl, nt - hl);
+            }
           }
-          if (recv != send) ctaCopy(recv + off + bo, send + off + bo, bytes);
         }
         ctaBarrier(c, epoch);
         if (rank != a.root) ctaCopy(recv + off + bo, c.ws[rank] + stageBase + bo, bytes);

@@ -398,6 +398,12 @@ ncclResult_t pncclAllToAll(const void* send, void* recv, size_t count, ncclDataT
   // Small chunks: one kernel over the flag-in-data buffers (no credits, no barrier).
   if (tlsGroup.depth == 0 && !Flags::get().emulateRanks && llAllToAllFits(c, chunk))
     return enqueueLLAllToAll(c, B200COLL_API_ID_ncclAllToAll, send, recv, count, dt, s);
+  // Large chunks in ordinary buffers: peer stores into the staging halves, one barrier per step (see A2A_STAGED_MIN).
+  auto stagedWanted = [&]() {
+    const long long lim = Flags::get().a2aStagedMin;
+    if (lim >= 0) return chunk >= (size_t)lim;
+    return false;
+  };
   // Receive buffer inside a symmetric window (the same place on every rank), whole 16-byte units: peer stores, one kernel.
   if (c->nranks > 1 && tlsGroup.depth == 0 && chunk && (chunk & 15) == 0 && ((((uintptr_t)send) | ((uintptr_t)recv)) & 15) == 0 && !Flags::get().emulateRanks) {
     if (!c->regs.empty()) BCHECK(commRegisterLazy(c, recv, 1));
@@ -431,6 +437,8 @@ ncclResult_t pncclAllToAll(const void* send, void* recv, size_t count, ncclDataT
       return ncclSuccess;
     }
   }
+  if (c->nranks > 1 && tlsGroup.depth == 0 && chunk && !Flags::get().emulateRanks && stagedWanted())
+    return enqueueStagedAllToAll(c, B200COLL_API_ID_ncclAllToAll, send, recv, count, dt, s);
   pncclGroupStart();
   ncclResult_t r = ncclSuccess;
   for (int p = 0; p < c->nranks && r == ncclSuccess; p++) {

@@ -95,6 +95,7 @@ static void load(Flags& f) {
   f.stageBytes = parseSize(envOf("BUFFSIZE"), f.stageBytes);
   f.llMaxBytes = parseSize(envOf("LL_THRESHOLD", false), f.llMaxBytes);
   f.p2pChunkBytes = parseSize(envOf("P2P_CHUNK", false), f.p2pChunkBytes);
+  if (const char* v = envOf("A2A_STAGED_MIN", false)) f.a2aStagedMin = (long long)parseSize(v, 0);
   f.p2pCtasPerPeer = parseInt(envOf("P2P_CTAS", false), f.p2pCtasPerPeer);
   if (const char* v = envOf("PIPELINE_CHUNK", false)) f.pipeChunkBytes = (long long)parseSize(v, 0);
   f.dmaGang = parseInt(envOf("DMA_GANG", false), f.dmaGang);
@@ -254,6 +255,7 @@ const SettingDoc kSettings[] = {
     {"BUFFSIZE", true, "64M", "bytes per staging half (two halves per communicator), at least 1M"},
     {"LL_THRESHOLD", false, "2M", "largest all-reduce served by the flag-in-data protocol: at most 2M between two ranks, 256K from three ranks up"},
     {"P2P_CHUNK", false, "512K", "bytes per send/recv FIFO slot"},
+    {"A2A_STAGED_MIN", false, "-1", "all-to-all: chunks (bytes per pair) from this size move through the staging halves by peer stores instead of the send/recv FIFOs (-1: built-in choice)"},
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
     {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},
     {"DMA_GANG", false, "0", "copy engines one copy-engine put/get is split over (0: 1, 2 or 4 by size; at most 8)"},
@@ -284,6 +286,7 @@ std::string currentValue(const Flags& f, const std::string& n) {
   if (n == "BUFFSIZE") return num((long long)f.stageBytes);
   if (n == "LL_THRESHOLD") return num((long long)f.llMaxBytes);
   if (n == "P2P_CHUNK") return num((long long)f.p2pChunkBytes);
+  if (n == "A2A_STAGED_MIN") return num(f.a2aStagedMin);
   if (n == "P2P_CTAS") return num(f.p2pCtasPerPeer);
   if (n == "PIPELINE_CHUNK") return num(f.pipeChunkBytes);
   if (n == "DMA_GANG") return num(f.dmaGang);
