@@ -63,6 +63,15 @@ ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, ResolvedOp* out) {
   return ncclSuccess;
 }
 
+// Flag-in-data kernels: up to 16 CTAs for the latency-bound sizes; beyond that one per 16 KiB of the message past 256 KiB,
+// or one per 64 KiB of lines a rank stores into its peers (2 x bytes x (n - 1): between eight ranks a CTA of a 256 KiB
+// all-reduce would otherwise store 224 KiB of lines by itself), whichever is more, up to 64.
+int llCtaCap(size_t bytes, int nranks) {
+  const int bySize = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
+  const size_t stored = bytes * 2 * (size_t)std::max(1, nranks - 1);
+  return std::max(bySize, (int)std::min<size_t>(64, stored >> 16));
+}
+
 int ctasFor(const Comm* c, size_t bytes, int algo) {
   // Mid-size messages are bound by NVLink latency, not bandwidth, so they want many CTAs with
   // little work each: one CTA per 64 KiB (128 KiB on the in-switch path, whose loads are wider
@@ -120,6 +129,7 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
                              ((r.kind == COLL_REDUCESCATTER || r.kind == COLL_ALLGATHER) && bytes <= fl.llSliceLimit(n)));
   if (algo == ALGO_LL && !llOk) algo = ALGO_AUTO;
   if (algo == ALGO_NVLS && !nvlsOk) algo = ALGO_AUTO;
+  const bool builtinChoice = algo == ALGO_AUTO;
   if (algo == ALGO_AUTO) {
     // In-switch reduction moves S(1 + 1/n) bytes per GPU and direction for an all-reduce of S
     // bytes (every rank's copy goes to the switch, the requester's own included) against
@@ -181,6 +191,10 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
     }
   }
   args->direct = direct ? 1 : 0;
+  // A broadcast through staging goes by peer stores (scatter and forward: every link carries each byte once). One multicast
+  // store stream from the root reached 400 GB/s between eight GPUs against 640 - 680 for NCCL; it stays the way into
+  // symmetric windows, where the alternative would be n - 1 store streams from the root.
+  if (builtinChoice && r.kind == COLL_BROADCAST && algo == ALGO_NVLS && !direct) algo = ALGO_P2P;
 
   size_t chunks = 0;
   args->chunkBytes = 0;
@@ -213,8 +227,7 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
     size_t moved = bytes * ((r.kind == COLL_REDUCESCATTER || r.kind == COLL_ALLGATHER) ? n : 1);
     ctas = algo == ALGO_LL ? (int)((bytes / 8 + kCollThreads - 1) / kCollThreads) : ctasFor(c, moved, algo);
   }
-  // Flag-in-data: up to 16 CTAs for the latency-bound sizes, one more per 16 KiB beyond 256 KiB (64 at 1 MiB and above).
-  const int llCap = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
+  const int llCap = llCtaCap(bytes, n);
   ctas = std::max(1, std::min(ctas, algo == ALGO_LL ? std::min(llCap, std::max(16, c->maxCtas)) : c->maxCtas));
   plan->algo = algo;
   plan->ctas = ctas;
@@ -387,7 +400,7 @@ ncclResult_t enqueueLLAllToAll(Comm* c, int apiId, const void* send, void* recv,
   la.count = bytes;
   if (++c->llSeq == 0) c->llSeq = 2;
   la.seq = c->llSeq;
-  const int llCap = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
+  const int llCap = llCtaCap(bytes, c->nranks);
   const int ctas = std::max(1, std::min((int)((bytes / 8 + kCollThreads - 1) / kCollThreads), std::min(llCap, std::max(16, c->maxCtas))));
   if (tr) tr->setAlgo(ALGO_LL, ctas);
   cudaError_t e = launchLLAllGather(ctas, stream, dc, la);

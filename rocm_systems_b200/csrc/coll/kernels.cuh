@@ -596,31 +596,149 @@ __global__ void __launch_bounds__(kCollThreads) kStagedCopy(const __grid_constan
 
   if (isA2A) {
     // Staged all-to-all for large chunks (total = bytes per pair): every rank stores its piece for peer p into slot
-    // `rank` of p's staging half (plain peer stores, the fast direction of the link) while a quarter of its threads copy
-    // the rank's own block; after one barrier everybody copies its slots out, and the next step fills the other half.
-    // A half is written again only two steps later, after a barrier that every rank reaches behind its copy-out.
+    // `rank` of p's staging half (plain peer stores, the fast direction of the link); after a barrier everybody copies
+    // its slots out of its OWN half. Software pipeline: three quarters of a CTA's threads push step k+1 into the other
+    // half while the last quarter copies step k out (and, in the first step, makes the rank's own block), one barrier per
+    // step. A half is written again two steps later, behind a barrier that every rank reaches after its copy-out.
     const int nt = blockDim.x, tid = threadIdx.x, hl = nt >> 2;
-    for (size_t off = 0; off < total; off += cap, half ^= 1) {
-      const size_t stageBase = c.stageOff + (size_t)half * c.stageBytes;
+    auto push = [&](size_t off, int hf, int t, int tn) {
       size_t bo, bytes;
       part(off, bo, bytes);
-      if (tid < hl) {
-        groupCopy(recv + (size_t)rank * total + off + bo, send + (size_t)rank * total + off + bo, bytes, tid, hl);
-      } else {
-        for (int i = 1; i < n; i++) {
-          const int p = (rank + i) % n;
-          groupCopy(c.ws[p] + stageBase + (size_t)rank * slotCap + bo, send + (size_t)p * total + off + bo, bytes, tid - hl, nt - hl);
-        }
+      const size_t base = c.stageOff + (size_t)hf * c.stageBytes + (size_t)rank * slotCap + bo;
+      for (int i = 1; i < n; i++) {
+        const int p = (rank + i) % n;
+        groupCopy(c.ws[p] + base, send + (size_t)p * total + off + bo, bytes, t, tn);
       }
-      ctaBarrier(c, epoch);
+    };
+    auto copyOut = [&](size_t off, int hf, int t, int tn) {
+      size_t bo, bytes;
+      part(off, bo, bytes);
+      const size_t base = c.stageOff + (size_t)hf * c.stageBytes + bo;
       for (int i = 1; i < n; i++) {
         const int s = (rank + n - i) % n;
-        ctaCopy(recv + (size_t)s * total + off + bo, c.ws[rank] + stageBase + (size_t)s * slotCap + bo, bytes);
+        groupCopy(recv + (size_t)s * total + off + bo, c.ws[rank] + base + (size_t)s * slotCap, bytes, t, tn);
       }
+    };
+    push(0, half, tid, nt);
+    ctaBarrier(c, epoch);
+    for (size_t off = 0; off < total; off += cap, half ^= 1) {
+      const bool more = off + cap < total;
+      if (more) {
+        if (tid >= hl) push(off + cap, half ^ 1, tid - hl, nt - hl);
+        else copyOut(off, half, tid, hl);
+      } else {
+        copyOut(off, half, tid, nt);
+      }
+      if (tid < hl || !more) {   // the rank's own block, piece by piece beside the copy-out
+        size_t bo, bytes;
+        part(off, bo, bytes);
+        groupCopy(recv + (size_t)rank * total + off + bo, send + (size_t)rank * total + off + bo, bytes, tid, more ? hl : nt);
+      }
+      if (more) ctaBarrier(c, epoch);
     }
     if (threadIdx.x == 0) c.local->barEpoch[b] = epoch;
     stampEnd(c);
     return;
+  }
+
+  if constexpr (!NVLS) {
+    if (a.kind == COLL_BROADCAST && !a.direct && n > 2 && total >= ((size_t)512 << 10)) {
+      // Broadcast through staging by peer stores, every link carrying each byte once (scatter and forward): a lane's part
+      // of a chunk is cut into n - 1 regions, one per non-root rank. The root stores region o only into its owner's staging
+      // half; the owner forwards it into the same place of every other non-root rank's half and copies it to its own recv;
+      // after the step's barrier everybody copies the regions it was forwarded. So the root sends a chunk once, a non-root
+      // rank receives a chunk once and sends (n - 2) / (n - 1) of one: the line rate of one link direction, against
+      // 1 / (n - 1) of it if the root stored everything itself. Software pipeline, one barrier per chunk: in step k the root
+      // already stores chunk k + 1 into the other half, three quarters of a non-root CTA forward chunk k and the last
+      // quarter copies out (its own region of chunk k, the forwarded regions of chunk k - 1). A region of a half is
+      // written again two steps after it was last read, behind the barrier in between; the root's stores of chunk k + 1
+      // touch only the owner's own region of the other half, which nobody reads in step k. Short messages and two ranks
+      // take the plain push below (one barrier less, nothing to forward).
+      const int m = n - 1, root = a.root, tid = threadIdx.x, nt = blockDim.x;
+      const bool isRoot = rank == root;
+      const int own = (rank - root - 1 + n) % n;   // this rank's region (non-root ranks only)
+      // Where a region lies depends on the lane's capacity only, never on how full a chunk is (a short last chunk laid out
+      // differently would let the root's stores of chunk k + 1 land on regions of chunk k - 1 that are still being copied out).
+      const size_t laneCap = perLane << 4;
+      auto region = [&](size_t bo, size_t bytes, int o, size_t& ro, size_t& rb) {
+        const size_t sub = (((laneCap + m - 1) / m) + 15) & ~(size_t)15;
+        const size_t lo = (size_t)o * sub < bytes ? (size_t)o * sub : bytes;
+        const size_t hi = lo + sub < bytes ? lo + sub : bytes;
+        ro = bo + lo;
+        rb = hi - lo;
+      };
+      auto rootPush = [&](size_t off, int hf, int t, int tn) {
+        size_t bo, bytes;
+        part(off, bo, bytes);
+        const size_t base = c.stageOff + (size_t)hf * c.stageBytes;
+        for (int o = 0; o < m; o++) {
+          size_t ro, rb;
+          region(bo, bytes, o, ro, rb);
+          groupCopy(c.ws[(root + 1 + o) % n] + base + ro, send + off + ro, rb, t, tn);
+        }
+      };
+      const int hl = nt >> 2;
+      if (isRoot) rootPush(0, half, tid, nt);
+      ctaBarrier(c, epoch);
+      size_t prevOff = 0;
+      int prevHalf = half;
+      bool havePrev = false;
+      for (size_t off = 0; off < total; off += cap, half ^= 1) {
+        const bool more = off + cap < total;
+        size_t bo, bytes;
+        part(off, bo, bytes);
+        const size_t base = c.stageOff + (size_t)half * c.stageBytes;
+        if (isRoot) {
+          const bool selfCopy = recv != send;
+          if (tid >= hl || !selfCopy) {
+            if (more) rootPush(off + cap, half ^ 1, selfCopy ? tid - hl : tid, selfCopy ? nt - hl : nt);
+          } else {
+            groupCopy(recv + off + bo, send + off + bo, bytes, tid, hl);
+          }
+        } else {
+          size_t ro, rb;
+          region(bo, bytes, own, ro, rb);
+          if (tid >= hl) {  // forward this rank's region of chunk k to the other non-root ranks
+            for (int i = 1; i < n; i++) {
+              const int p = (rank + i) % n;
+              if (p == root) continue;
+              groupCopy(c.ws[p] + base + ro, c.ws[rank] + base + ro, rb, tid - hl, nt - hl);
+            }
+          } else {          // copy out: own region of chunk k, forwarded regions of chunk k - 1
+            groupCopy(recv + off + ro, c.ws[rank] + base + ro, rb, tid, hl);
+            if (havePrev) {
+              size_t pbo, pbytes;
+              part(prevOff, pbo, pbytes);
+              const size_t pbase = c.stageOff + (size_t)prevHalf * c.stageBytes;
+              for (int o = 0; o < m; o++) {
+                if (o == own) continue;
+                size_t qo, qb;
+                region(pbo, pbytes, o, qo, qb);
+                groupCopy(recv + prevOff + qo, c.ws[rank] + pbase + qo, qb, tid, hl);
+              }
+            }
+          }
+        }
+        ctaBarrier(c, epoch);
+        prevOff = off;
+        prevHalf = half;
+        havePrev = true;
+      }
+      if (!isRoot && havePrev) {  // the forwarded regions of the last chunk
+        size_t pbo, pbytes;
+        part(prevOff, pbo, pbytes);
+        const size_t pbase = c.stageOff + (size_t)prevHalf * c.stageBytes;
+        for (int o = 0; o < m; o++) {
+          if (o == own) continue;
+          size_t qo, qb;
+          region(pbo, pbytes, o, qo, qb);
+          ctaCopy(recv + prevOff + qo, c.ws[rank] + pbase + qo, qb);
+        }
+      }
+      if (threadIdx.x == 0) c.local->barEpoch[b] = epoch;
+      stampEnd(c);
+      return;
+    }
   }
 
   for (size_t off = 0; off < total; off += cap, half ^= 1) {

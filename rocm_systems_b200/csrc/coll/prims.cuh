@@ -247,7 +247,8 @@ template <> struct McReduce<__half> {
   }
 };
 __device__ __forceinline__ void mcStore16(void* p, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  // A weak store: ordering comes from the fence and release store of the barrier that follows every store phase.
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 // ---- trace stamps ---------------------------------------------------------------------------

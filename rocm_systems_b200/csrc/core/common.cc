@@ -255,7 +255,7 @@ const SettingDoc kSettings[] = {
     {"BUFFSIZE", true, "64M", "bytes per staging half (two halves per communicator), at least 1M"},
     {"LL_THRESHOLD", false, "2M", "largest all-reduce served by the flag-in-data protocol: at most 2M between two ranks, 256K from three ranks up"},
     {"P2P_CHUNK", false, "512K", "bytes per send/recv FIFO slot"},
-    {"A2A_STAGED_MIN", false, "-1", "all-to-all: chunks (bytes per pair) from this size move through the staging halves by peer stores instead of the send/recv FIFOs (-1: built-in choice)"},
+    {"A2A_STAGED_MIN", false, "-1", "all-to-all: chunks (bytes per pair) from this size move through the staging halves by peer stores instead of the send/recv FIFOs (-1: built-in choice, 1 MiB)"},
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},
     {"PIPELINE_CHUNK", false, "-1", "pipeline chunk of the staged reductions in bytes (-1: by message size, 0: no chunking)"},
     {"DMA_GANG", false, "0", "copy engines one copy-engine put/get is split over (0: 1, 2 or 4 by size; at most 8)"},

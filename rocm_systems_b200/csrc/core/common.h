@@ -98,7 +98,7 @@ struct Flags {
   // what an all-reduce of llLimit bytes between two ranks puts on its link.
   size_t llSliceLimit(int nranks) const { return nranks <= 2 ? llLimit(nranks) : llLimit(nranks) * 2 / (size_t)nranks; }
   size_t p2pChunkBytes = 512ull << 10; // P2P_CHUNK: bytes per send/recv FIFO slot
-  long long a2aStagedMin = -1;         // A2A_STAGED_MIN: all-to-all chunks (bytes per pair) from this size go through the staging halves; -1: built-in choice
+  long long a2aStagedMin = -1;         // A2A_STAGED_MIN: all-to-all chunks (bytes per pair) from this size go through the staging halves; -1: built-in choice (1 MiB)
   int p2pCtasPerPeer = 0;        // P2P_CTAS: CTAs per (peer, direction); 0 picks by rank count
   int waitTimeoutMs = 20000;     // WAIT_TIMEOUT_MS: device-side wait budget
   int bootTimeoutMs = 120000;    // BOOTSTRAP_TIMEOUT_MS: host rendezvous budget

@@ -60,7 +60,7 @@ def test_builtin_choices():
     ])
     assert [x[0] for x in r] == [0] * 15
     assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL, LL, P2P, LL, NVLS, LL, P2P, LL]
-    assert r[1][2] == 16 and r[8][2] == 32          # 64 by size, bounded by the CTA budget of the planning communicator (32)
+    assert r[0][2] == 1 and r[1][2] == 32 and r[8][2] == 32   # 256 KiB between 8 ranks: 3.5 MiB of lines per rank, one CTA per 64 KiB of them;          # 64 by size, bounded by the CTA budget of the planning communicator (32)
     assert plan([[2, 1, AR, 2 * MiB // 4, F32, SUM]], {"B200COLL_MAX_CTAS": "64"})[0][2] == 64
     assert all(x[3] == 0 for x in r)           # nothing is in a registered window here
 

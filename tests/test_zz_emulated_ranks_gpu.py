@@ -1,5 +1,6 @@
 """Several ranks of one communicator on ONE GPU, played by one cooperative kernel (csrc/coll/emu.cu): the collective
-kernels' multi-rank paths — flag-in-data all-reduce, pipelined staged reduce with bulk asynchronous loads, staged copy,
+kernels' multi-rank paths — the flag-in-data family, pipelined staged reduce with bulk asynchronous loads, staged copy, the
+scatter-and-forward broadcast and the staged all-to-all (several steps each: the staging is set to 1 MiB),
 grouped send/recv through FIFO slots and credits, the fused FSDP reduce-scatter+cast, and the device-initiated layer's
 put+signal ring and remote atomics — run where only one GPU is there. The check itself is native (b200collEmuSelftest: small-integer data, every collective in
 float / bfloat16 / int32, verified on the host, guard bytes behind every output).
@@ -24,7 +25,7 @@ torch.zeros(1, device='cuda')
 lib = _lib.load()
 lib.b200collEmuSelftest.argtypes = [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_int)]
 bad = 0
-for nranks, count in [(2, 1000), (4, 1000), (4, 70001), (3, 300007), (4, (1 << 20) + 8)]:
+for nranks, count in [(2, 1000), (4, 1000), (4, 70001), (3, 300007), (4, (1 << 20) + 8), (5, 700001), (8, 400003)]:
     wrong, status = ctypes.c_longlong(-1), ctypes.c_int(-1)
     rc = lib.b200collEmuSelftest(nranks, count, ctypes.byref(wrong), ctypes.byref(status))
     print(f"ranks {nranks} count {count}: rc {rc} wrong {wrong.value} status {status.value}", flush=True)
