@@ -207,7 +207,7 @@ class LlamaTrainer:
     pinned memory or device tensors; ``loss`` is a host float when ``return_loss`` is set."""
 
     def __init__(self, cfg: LlamaConfig, comm=None, device: Optional[torch.device] = None, opt: Optional[AdamWConfig] = None,
-                 seed: int = 0, fused_rs: bool = True, sym_shards: bool = True, overlap: bool = True):
+                 seed: int = 0, fused_rs: bool = True, sym_shards: bool = True, overlap: bool = True, copy_engine_gather: bool = True):
         self.cfg = cfg
         self.comm = comm
         self.device = device or torch.device("cuda", torch.cuda.current_device())
@@ -221,7 +221,8 @@ class LlamaTrainer:
                 units.append(FlatUnit(f"layer{i}", layer_specs(cfg), rank, world, self.device, seed + 1 + i))
             units.append(FlatUnit("head", [ParamSpec("norm", (cfg.hidden,), "ones"), ParamSpec("out", (cfg.vocab, cfg.hidden), std=cfg.init_std)],
                                   rank, world, self.device, seed + 1 + cfg.layers))
-            self.engine = FSDPEngine(comm, units, opt or AdamWConfig(), fused_rs=fused_rs, sym_shards=sym_shards, overlap=overlap)
+            self.engine = FSDPEngine(comm, units, opt or AdamWConfig(), fused_rs=fused_rs, sym_shards=sym_shards, overlap=overlap,
+                                     copy_engine_gather=copy_engine_gather)
             self.rope = ops.rope_table(cfg.seq_len, cfg.head_dim, cfg.rope_theta, self.device)
         self.embed, self.layers, self.head = units[0], units[1:-1], units[-1]
         self._tok_dev: Optional[torch.Tensor] = None

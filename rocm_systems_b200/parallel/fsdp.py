@@ -128,7 +128,7 @@ class FSDPEngine:
     """Owns the units, the communication stream and the schedule primitives."""
 
     def __init__(self, comm, units: List[FlatUnit], opt: AdamWConfig, reshard_after_forward: bool = True, fused_rs: bool = True,
-                 sym_shards: bool = True, overlap: bool = True):
+                 sym_shards: bool = True, overlap: bool = True, copy_engine_gather: bool = True):
         self.comm, self.units, self.opt = comm, units, opt
         self.world = comm.nranks if comm is not None else 1
         self.rank = comm.rank if comm is not None else 0
@@ -145,8 +145,13 @@ class FSDPEngine:
         self._held: List[tuple] = []          # (unit, reduced gradient shard) until finish_step
         self._sumsq: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None   # device scalar of the latest step (before clipping)
+        # With the shards in symmetric memory the parameter all-gather is made by the copy engines (the default): one
+        # peer-to-peer copy per peer behind a tiny barrier kernel, so that no SM is taken from the GEMMs it overlaps
+        # (8B model on 2 GPUs: 212 ms per step against 224 ms with the all-gather kernel, and 215 ms on one GPU).
+        self.copy_engine_gather = False
         if sym_shards and self.world > 1 and hasattr(comm, "sym_alloc"):
             self._place_shards_in_symmetric_memory()
+            self.copy_engine_gather = bool(copy_engine_gather)
 
     def _place_shards_in_symmetric_memory(self) -> None:
         """Move every unit's bf16 shard into one symmetric allocation. The parameter all-gather then
@@ -164,6 +169,7 @@ class FSDPEngine:
             t = self._sym_shards.tensor((u.shard_numel,), torch.bfloat16, offset_bytes=o)
             t.copy_(u.shard)
             u.shard = t
+            u.peer_shards = [self._sym_shards.tensor((u.shard_numel,), torch.bfloat16, offset_bytes=o, peer=p) for p in range(self.world)]
         # Two symmetric gradient buffers, used alternately by consecutive units: the fused
         # reduce-scatter then reads the peers' gradients in place. A buffer is handed out again only
         # after the reduce-scatter that read it has finished (its kernel ends with a barrier, so by
@@ -185,7 +191,22 @@ class FSDPEngine:
         unit.full.untyped_storage().resize_(unit.nbytes_full)
         self.comm_stream.wait_stream(torch.cuda.current_stream())  # the memory may be recycled compute memory
         with torch.cuda.stream(self.comm_stream):
-            self.comm.all_gather(unit.shard, unit.full, stream=self.comm_stream)
+            if self.copy_engine_gather:
+                # Every rank's shard is final once its communication stream reaches this barrier (its AdamW of this unit
+                # ran earlier on that stream). A shard is next written behind the unit's gradient reduce-scatter, a
+                # collective that no rank enters before it has used the gathered parameters, so no closing barrier is needed.
+                self.comm.barrier(stream=self.comm_stream)
+                n = unit.shard_numel
+                # a second tensor over the same memory: like the collective kernels, the copies must not count as in-place
+                # modifications of the parameter views that a saved forward pass still refers to
+                from ..comm import _tensor_from_ptr
+
+                dst = _tensor_from_ptr(unit.full.data_ptr(), (self.world * n,), torch.bfloat16, unit.device)
+                for i in range(self.world):
+                    p = (self.rank + i) % self.world
+                    dst[p * n:(p + 1) * n].copy_(unit.peer_shards[p], non_blocking=True)
+            else:
+                self.comm.all_gather(unit.shard, unit.full, stream=self.comm_stream)
             ev = torch.cuda.Event()
             ev.record(self.comm_stream)
         unit.gather_event = ev

@@ -84,8 +84,15 @@ def test_shmem_device_collectives(nproc):
 
 @pytest.mark.parametrize("nproc", [2, 8])
 def test_fsdp_matches_single_rank(nproc):
-    """Shards and gradient buffers in symmetric memory (the default): zero-copy all-gather and reduce-scatter+cast."""
+    """Shards and gradient buffers in symmetric memory (the default): parameter all-gather by the copy engines, zero-copy
+    reduce-scatter+cast kernel."""
     _launch(nproc, 29850 + nproc, "fsdp_worker.py")
+
+
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_fsdp_with_all_gather_kernel_matches_single_rank(nproc):
+    """The parameter all-gather by the zero-copy all-gather kernel instead of the copy engines."""
+    _launch(nproc, 29770 + nproc, "fsdp_worker.py", extra_env={"FSDP_COPY_ENGINE_GATHER": "0"})
 
 
 @pytest.mark.parametrize("nproc", [2, 8])
