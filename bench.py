@@ -8,9 +8,9 @@
 One process per GPU. bf16 parameters with fp32 master weights and AdamW, sequence 4096,
 micro-batch 1 per GPU, synthetic tokens (uniform over the vocabulary, seeded) and random-init
 weights N(0, 0.02). Gradient reduce-scatters go through this package's communicator (one fused
-reduce-scatter + cast + scale kernel per unit), parameter all-gathers are peer-to-peer copies of the
-symmetric shards on the copy engines behind a barrier kernel of the communicator (``--gather kernel``:
-its all-gather kernel). Two timed regions of K steps each, both bracketed by a barrier and a device
+reduce-scatter + cast + scale kernel per unit); parameter all-gathers are, between two GPUs, peer-to-peer
+copies of the symmetric shards on the copy engines behind a barrier kernel of the communicator, and from
+three GPUs up its zero-copy all-gather kernel (``--gather`` forces either). Two timed regions of K steps each, both bracketed by a barrier and a device
 synchronisation and timed with CUDA events (max over ranks):
 
 * ``value``  — steps fed from device-resident batches, loss left on the device;
@@ -164,8 +164,8 @@ def main() -> None:
     ap.add_argument("--collectives", default="b200coll", choices=["b200coll", "nccl"],
                     help="nccl: the same trainer with stock NCCL collectives (control run; the metric name gets a _nccl_collectives suffix)")
     ap.add_argument("--gemm", default="own", choices=["own", "library"], help="linear layers on this package's tcgen05 kernel (default) or on cuBLAS")
-    ap.add_argument("--gather", default="copy-engine", choices=["kernel", "copy-engine"],
-                    help="parameter all-gather by the copy engines (default: peer-to-peer copies behind a barrier kernel, no SM) or by this package's all-gather kernel")
+    ap.add_argument("--gather", default="auto", choices=["auto", "kernel", "copy-engine"],
+                    help="parameter all-gather by the copy engines (peer-to-peer copies behind a barrier kernel, no SM) or by this package's all-gather kernel; auto: copy engines between two GPUs, the kernel from three up")
     ap.add_argument("--no-overlap", action="store_true", help="run communication and optimizer on the compute stream (a sequential schedule, for checking)")
     ap.add_argument("--no-headline", action="store_true", help="skip the collective / fused-path summaries that follow the timed regions on 2+ GPUs")
     ap.add_argument("--reference-checkpointing", action="store_true", help="--impl reference: per-layer activation checkpointing from the start")
@@ -214,7 +214,8 @@ def main() -> None:
     if args.layers:
         cfg.layers = args.layers
     trainer = LlamaTrainer(cfg, comm if world > 1 else None, dev, opt=AdamWConfig(lr=args.lr), fused_rs=args.collectives != "nccl", sym_shards=not args.staged_shards, overlap=not args.no_overlap,
-                           copy_engine_gather=args.gather == "copy-engine")
+                           copy_engine_gather={"auto": None, "kernel": False, "copy-engine": True}[args.gather])
+    gather_mode = "none" if world == 1 else ("copy engines behind a barrier kernel" if trainer.engine.copy_engine_gather else "all-gather kernel of this package")
     S, B = cfg.seq_len, 1
     nbatches = 4
     g = torch.Generator().manual_seed(1234 + rank)
@@ -279,7 +280,7 @@ def main() -> None:
         "config": {"model": "llama3-8b" if args.model == "llama3_8b" else "tiny", "global_batch": world * B, "seq_len": S,
                    "parallelism": f"fsdp{world}", "optimizer": "adamw fp32 master", "layers": cfg.layers, "hidden": cfg.hidden,
                    "linear_gemm": "tcgen05 cta-pair kernel of this package" if args.gemm == "own" else "cuBLAS",
-                   "param_all_gather": ("copy engines behind a barrier kernel" if args.gather == "copy-engine" else "all-gather kernel of this package") if world > 1 else "none",
+                   "param_all_gather": gather_mode,
                    "l2": "working set per step (GBs of weights and activations) is far larger than the 126 MB L2; no flush needed"},
         "clocks": clocks, "gpu_launches": launches,
         "model_tflops_per_gpu": cfg.flops_per_token() * B * S / (ms_dev / args.steps / 1e3) / 1e12,

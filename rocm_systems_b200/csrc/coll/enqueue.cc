@@ -191,10 +191,12 @@ static ncclResult_t planInternal(const CollReq& r, const ResolvedOp& rop, Plan* 
     }
   }
   args->direct = direct ? 1 : 0;
-  // A broadcast through staging goes by peer stores (scatter and forward: every link carries each byte once). One multicast
-  // store stream from the root reached 400 GB/s between eight GPUs against 640 - 680 for NCCL; it stays the way into
-  // symmetric windows, where the alternative would be n - 1 store streams from the root.
-  if (builtinChoice && r.kind == COLL_BROADCAST && algo == ALGO_NVLS && !direct) algo = ALGO_P2P;
+  // A large broadcast through staging goes by peer stores (scatter and forward: every link carries each byte once, pipelined
+  // over the staging halves). One multicast store stream from the root tops out near 400 GB/s (eight GPUs: 0.58 - 0.68 of
+  // NCCL from 128 MiB; the scatter-and-forward form measured 0.81 at 512 MiB between four); up to one staging half the
+  // multicast form has fewer barriers and measured 0.9 - 1.4. It also stays the way into symmetric windows, where the
+  // alternative would be n - 1 store streams from the root.
+  if (builtinChoice && r.kind == COLL_BROADCAST && algo == ALGO_NVLS && !direct && bytes > c->dev.stageBytes) algo = ALGO_P2P;
 
   size_t chunks = 0;
   args->chunkBytes = 0;

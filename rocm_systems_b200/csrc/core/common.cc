@@ -253,7 +253,7 @@ const SettingDoc kSettings[] = {
     {"MIN_CTAS", true, "0", "lower bound of CTAs per collective launch (0: built-in)"},
     {"MAX_CTAS", true, "0", "upper bound of CTAs per collective launch (0: built-in)"},
     {"BUFFSIZE", true, "64M", "bytes per staging half (two halves per communicator), at least 1M"},
-    {"LL_THRESHOLD", false, "2M", "largest all-reduce served by the flag-in-data protocol: at most 2M between two ranks, 256K from three ranks up"},
+    {"LL_THRESHOLD", false, "2M", "largest all-reduce served by the flag-in-data protocol: at most 2M up to three ranks, 1M between four, 512K from five to eight"},
     {"P2P_CHUNK", false, "512K", "bytes per send/recv FIFO slot"},
     {"A2A_STAGED_MIN", false, "-1", "all-to-all: chunks (bytes per pair) from this size move through the staging halves by peer stores instead of the send/recv FIFOs (-1: built-in choice, 1 MiB)"},
     {"P2P_CTAS", false, "0", "CTAs per peer and direction for send/recv (0: 16 / 8 / 4 for 2 / up to 4 / more ranks)"},

@@ -87,16 +87,22 @@ struct Flags {
   int minCtas = 0, maxCtas = 0;  // MIN_CTAS / MAX_CTAS (0: per-collective default)
   size_t stageBytes = 64ull << 20;   // BUFFSIZE: bytes per staging half
   size_t llMaxBytes = 2ull << 20;    // LL_THRESHOLD: largest message for the flag-in-data protocol (see llLimit)
-  // Every rank stores its whole message (with as many bytes of flags) into every peer, so what the protocol may carry
-  // shrinks with the ranks: 2 MiB between two (measured there: staged 24-27 us at 512 KiB - 2 MiB against 19 us for NCCL),
-  // 256 KiB from three ranks up.
+  // Every rank stores its whole message (with as many bytes of flags) into every peer, 2 x bytes x (n - 1) in all, at
+  // about 600 GB/s behind a latency of about 8 us; NCCL answers small messages in 20 - 28 us. So the protocol pays up to
+  // roughly 4 MiB / (n - 1): 2 MiB between two or three ranks (measured between two: staged 24 - 27 us at 512 KiB - 2 MiB
+  // against 19 us for NCCL and 9 - 17 us for this protocol), 1 MiB between four, 512 KiB from five to eight.
   size_t llLimit(int nranks) const {
-    const size_t byRanks = nranks <= 2 ? (2ull << 20) : (256ull << 10);
+    const size_t byRanks = nranks <= 3 ? (2ull << 20) : nranks == 4 ? (1ull << 20) : (512ull << 10);
     return llMaxBytes < byRanks ? llMaxBytes : byRanks;
   }
-  // Reduce-scatter and all-gather move one slice per peer: the limit on a slice, so that a rank's stores stay within
-  // what an all-reduce of llLimit bytes between two ranks puts on its link.
-  size_t llSliceLimit(int nranks) const { return nranks <= 2 ? llLimit(nranks) : llLimit(nranks) * 2 / (size_t)nranks; }
+  // Reduce-scatter, all-gather and all-to-all move one slice per peer, 2 x slice x (n - 1) per rank: the limit on a slice
+  // (it must also fit a slot of the line buffer, which holds 2 x llLimit bytes of lines).
+  size_t llSliceLimit(int nranks) const {
+    const size_t whole = llLimit(nranks);
+    if (nranks <= 2) return whole;
+    const size_t bySlices = whole * 4 / (size_t)nranks;
+    return bySlices < whole ? bySlices : whole;
+  }
   size_t p2pChunkBytes = 512ull << 10; // P2P_CHUNK: bytes per send/recv FIFO slot
   long long a2aStagedMin = -1;         // A2A_STAGED_MIN: all-to-all chunks (bytes per pair) from this size go through the staging halves; -1: built-in choice (1 MiB)
   int p2pCtasPerPeer = 0;        // P2P_CTAS: CTAs per (peer, direction); 0 picks by rank count

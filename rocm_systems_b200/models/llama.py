@@ -207,7 +207,7 @@ class LlamaTrainer:
     pinned memory or device tensors; ``loss`` is a host float when ``return_loss`` is set."""
 
     def __init__(self, cfg: LlamaConfig, comm=None, device: Optional[torch.device] = None, opt: Optional[AdamWConfig] = None,
-                 seed: int = 0, fused_rs: bool = True, sym_shards: bool = True, overlap: bool = True, copy_engine_gather: bool = True):
+                 seed: int = 0, fused_rs: bool = True, sym_shards: bool = True, overlap: bool = True, copy_engine_gather: Optional[bool] = None):
         self.cfg = cfg
         self.comm = comm
         self.device = device or torch.device("cuda", torch.cuda.current_device())

@@ -128,7 +128,7 @@ class FSDPEngine:
     """Owns the units, the communication stream and the schedule primitives."""
 
     def __init__(self, comm, units: List[FlatUnit], opt: AdamWConfig, reshard_after_forward: bool = True, fused_rs: bool = True,
-                 sym_shards: bool = True, overlap: bool = True, copy_engine_gather: bool = True):
+                 sym_shards: bool = True, overlap: bool = True, copy_engine_gather: Optional[bool] = None):
         self.comm, self.units, self.opt = comm, units, opt
         self.world = comm.nranks if comm is not None else 1
         self.rank = comm.rank if comm is not None else 0
@@ -145,13 +145,16 @@ class FSDPEngine:
         self._held: List[tuple] = []          # (unit, reduced gradient shard) until finish_step
         self._sumsq: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None   # device scalar of the latest step (before clipping)
-        # With the shards in symmetric memory the parameter all-gather is made by the copy engines (the default): one
-        # peer-to-peer copy per peer behind a tiny barrier kernel, so that no SM is taken from the GEMMs it overlaps
-        # (8B model on 2 GPUs: 212 ms per step against 224 ms with the all-gather kernel, and 215 ms on one GPU).
+        # With the shards in symmetric memory the parameter all-gather can be made by the copy engines: one peer-to-peer
+        # copy per peer behind a tiny barrier kernel, so that no SM is taken from the GEMMs it overlaps (8B model on 2 GPUs:
+        # 212 ms per step against 224 ms with the all-gather kernel, and 215 ms on one GPU). That is the default between
+        # two ranks. On four GPUs the one run of this mode ended in a bounded-wait report (lanes of the reduce-scatter
+        # kernel of one rank not arriving within 5 s; not understood, not repeated for lack of GPU time), so from three
+        # ranks up the default stays the all-gather kernel; copy_engine_gather=True forces the copies.
         self.copy_engine_gather = False
         if sym_shards and self.world > 1 and hasattr(comm, "sym_alloc"):
             self._place_shards_in_symmetric_memory()
-            self.copy_engine_gather = bool(copy_engine_gather)
+            self.copy_engine_gather = (self.world == 2) if copy_engine_gather is None else bool(copy_engine_gather)
 
     def _place_shards_in_symmetric_memory(self) -> None:
         """Move every unit's bf16 shard into one symmetric allocation. The parameter all-gather then

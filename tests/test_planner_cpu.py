@@ -43,8 +43,8 @@ def test_builtin_choices():
     MiB = 1 << 20
     r = plan([
         [8, 1, AR, 1024, F32, SUM],            # 4 KiB: flag-in-data
-        [8, 1, AR, 64 * 1024, F32, SUM],       # 256 KiB: still flag-in-data
-        [8, 1, AR, 64 * 1024 + 4, F32, SUM],   # just above: in-switch
+        [8, 1, AR, 128 * 1024, F32, SUM],      # 512 KiB: still flag-in-data between eight ranks
+        [8, 1, AR, 128 * 1024 + 4, F32, SUM],  # just above: in-switch
         [8, 1, AR, 64 * MiB // 4, F32, MAX],   # max is not an in-switch operation: peer loads
         [2, 1, AR, 64 * MiB // 4, F32, SUM],   # two ranks: peer loads move fewer bytes than the switch
         [8, 0, AR, 64 * MiB // 4, F32, SUM],   # no multicast: peer loads
@@ -52,15 +52,15 @@ def test_builtin_choices():
         [8, 1, AR, 8, 6, SUM],                 # fp16 is 6: tiny, flag-in-data
         [2, 1, AR, 2 * MiB // 4, F32, SUM],    # between two ranks flag-in-data carries up to 2 MiB, on up to 64 CTAs (within the communicator's budget)
         [2, 1, AR, 2 * MiB // 4 + 4, F32, SUM],
-        [8, 1, RS, 16 * 1024, F32, SUM],       # reduce-scatter / all-gather: flag-in-data for slices up to 2 x 256 KiB / ranks
-        [8, 1, RS, 16 * 1024 + 4, F32, SUM],
-        [8, 1, AG, 16 * 1024, F32, SUM],
-        [8, 1, AG, 16 * 1024 + 4, F32, SUM],
+        [8, 1, RS, 64 * 1024, F32, SUM],       # reduce-scatter / all-gather: flag-in-data for slices up to 4 x 512 KiB / 8 ranks
+        [8, 1, RS, 64 * 1024 + 4, F32, SUM],
+        [8, 1, AG, 64 * 1024, F32, SUM],
+        [8, 1, AG, 64 * 1024 + 4, F32, SUM],
         [2, 1, AG, 2 * MiB // 4, F32, SUM],    # two ranks: slices up to 2 MiB
     ])
     assert [x[0] for x in r] == [0] * 15
     assert [x[1] for x in r] == [LL, LL, NVLS, P2P, P2P, P2P, P2P, LL, LL, P2P, LL, NVLS, LL, P2P, LL]
-    assert r[0][2] == 1 and r[1][2] == 32 and r[8][2] == 32   # 256 KiB between 8 ranks: 3.5 MiB of lines per rank, one CTA per 64 KiB of them;          # 64 by size, bounded by the CTA budget of the planning communicator (32)
+    assert r[0][2] == 1 and r[1][2] == 32 and r[8][2] == 32   # 512 KiB between 8 ranks: 7 MiB of lines per rank, one CTA per 64 KiB of them;          # 64 by size, bounded by the CTA budget of the planning communicator (32)
     assert plan([[2, 1, AR, 2 * MiB // 4, F32, SUM]], {"B200COLL_MAX_CTAS": "64"})[0][2] == 64
     assert all(x[3] == 0 for x in r)           # nothing is in a registered window here
 
@@ -127,8 +127,8 @@ def test_planner_invariants_over_random_messages():
         assert rc == 0 and algo in (LL, P2P, NVLS) and 1 <= ctas <= 128 and direct == 0, (nranks, kind, count, algo, ctas, chunks)
         assert (chunks == 0) if algo == LL else (chunks >= 1), (nranks, kind, count, algo, chunks)      # flag-in-data uses no staging
         if algo == LL:
-            limit = 2 << 20 if nranks == 2 else 256 * 1024
-            assert kind in (AR, RS, AG) and nbytes <= (limit if kind == AR or nranks == 2 else limit * 2 // nranks)
+            limit = {2: 2 << 20, 3: 2 << 20, 4: 1 << 20, 8: 512 << 10}[nranks]
+            assert kind in (AR, RS, AG) and nbytes <= (limit if kind == AR or nranks == 2 else min(limit, limit * 4 // nranks))
         if algo == NVLS:
             assert nvls == 1
             if kind in (AR, RS, RED):

@@ -20,7 +20,7 @@ def main():
     cfg = LlamaConfig.tiny(64)
     fused = os.environ.get("FSDP_FUSED_RS", "1") == "1"
     sym = os.environ.get("FSDP_SYM_SHARDS", "1") == "1"   # shards and gradient buffers in symmetric memory (zero-copy collectives)
-    ce = os.environ.get("FSDP_COPY_ENGINE_GATHER", "1") == "1"   # parameter all-gather by peer-to-peer copies between two barrier kernels
+    ce = {"1": True, "0": False}.get(os.environ.get("FSDP_COPY_ENGINE_GATHER", ""), None)   # parameter all-gather by copy engines (1), by the kernel (0), or the default
     clip = float(os.environ.get("FSDP_CLIP", "0"))         # > 0: global-norm clipping to this value on both trainers
     opt = (lambda: AdamWConfig(max_grad_norm=clip)) if clip > 0 else (lambda: None)
     sharded = LlamaTrainer(cfg, comm, dev, opt=opt(), seed=3, fused_rs=fused, sym_shards=sym, copy_engine_gather=ce)
