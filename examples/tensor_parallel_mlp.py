@@ -26,6 +26,8 @@ def main() -> int:
     ap.add_argument("--ffn", type=int, default=28672, help="whole intermediate size")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 operands: half the all-gather bytes, fp8 tensor-core rate; "
                     "compared with the PyTorch statement of the same quantised arithmetic")
+    ap.add_argument("--backward", action="store_true", help="also time forward + backward (the same two fused kernels on transposed weights, "
+                    "weight gradients as local GEMMs); bf16 form only")
     ap.add_argument("--attention", action="store_true", help="also run the tensor-parallel attention half of the layer")
     ap.add_argument("--heads", type=int, default=64)
     ap.add_argument("--kv-heads", type=int, default=8)
@@ -54,6 +56,25 @@ def main() -> int:
         print(f"{'fp8 ' if a.fp8 else ''}TP={comm.nranks} tokens {a.rows * comm.nranks} hidden {a.hidden} ffn {a.ffn}: max |error| {err:.3e} (output scale {scale:.3e}), "
               f"{ms:.3f} ms per layer, {flops / ms / 1e9:.0f} TFLOP/s per GPU, kernel status {code}", flush=True)
     ok = code == 0 and err <= 3e-2 * scale + 1e-3
+    if a.backward and not a.fp8:
+        dy = (torch.randn(a.rows, a.hidden, device=comm.device) * 0.5).to(torch.bfloat16)
+        for _ in range(3):
+            mlp.forward(x)
+            mlp.backward(dy)
+        torch.cuda.synchronize()
+        comm.host_barrier()
+        start.record()
+        for _ in range(10):
+            mlp.forward(x)
+            dx = mlp.backward(dy)
+        stop.record()
+        torch.cuda.synchronize()
+        bms = start.elapsed_time(stop) / 10
+        bcode = train_ops.gemm_take_error()
+        if comm.rank == 0:
+            print(f"forward + backward: {bms:.3f} ms, {3 * flops / bms / 1e9:.0f} TFLOP/s per GPU of model FLOPs; dx {tuple(dx.shape)}, "
+                  f"grads {', '.join(f'{k} {tuple(v.shape)}' for k, v in mlp.grads.items())}, kernel status {bcode}", flush=True)
+        ok = ok and bcode == 0
     mlp.free()
     if a.attention:
         # The other half of the layer on the same two kernels: QKV projection inside the all-gather, output projection

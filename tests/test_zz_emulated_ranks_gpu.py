@@ -25,7 +25,7 @@ torch.zeros(1, device='cuda')
 lib = _lib.load()
 lib.b200collEmuSelftest.argtypes = [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_int)]
 bad = 0
-for nranks, count in [(2, 1000), (4, 1000), (4, 70001), (3, 300007), (4, (1 << 20) + 8), (5, 700001), (8, 400003)]:
+for nranks, count in [(2, 1000), (4, 1000), (4, 70001), (3, 300007), (4, (1 << 20) + 8), (5, 700001), (8, 400003), (8, 100003)]:
     wrong, status = ctypes.c_longlong(-1), ctypes.c_int(-1)
     rc = lib.b200collEmuSelftest(nranks, count, ctypes.byref(wrong), ctypes.byref(status))
     print(f"ranks {nranks} count {count}: rc {rc} wrong {wrong.value} status {status.value}", flush=True)
