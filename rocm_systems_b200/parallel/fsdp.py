@@ -149,7 +149,7 @@ class FSDPEngine:
         # copy per peer behind a tiny barrier kernel, so that no SM is taken from the GEMMs it overlaps (8B model on 2 GPUs:
         # 212 ms per step against 224 ms with the all-gather kernel, and 215 ms on one GPU). That is the default between
         # two ranks. On four GPUs the one run of this mode ended in a bounded-wait report (lanes of the reduce-scatter
-        # kernel of one rank not arriving within 5 s; not understood, not repeated for lack of GPU time), so from three
+        # kernel of one rank not arriving within 5 s; the cause is not understood), so from three
         # ranks up the default stays the all-gather kernel; copy_engine_gather=True forces the copies.
         self.copy_engine_gather = False
         if sym_shards and self.world > 1 and hasattr(comm, "sym_alloc"):
