@@ -69,6 +69,14 @@ def ref_route(logits: torch.Tensor, k: int):
     return order.to(torch.int32), w
 
 
+def router_backward(top_w: torch.Tensor, top_idx: torch.Tensor, d_gate: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Gradient with respect to the router logits [T, E] given the gradient with respect to the gate weights [T, k]: the gate
+    weights are the softmax over the k selected logits, so d_sel = w * (d_gate - sum(d_gate * w)) lands on the selected
+    columns and every other column gets zero (the selection itself is piecewise constant)."""
+    d_sel = top_w * (d_gate - (d_gate * top_w).sum(-1, keepdim=True))
+    return torch.zeros(top_w.shape[0], num_experts, dtype=torch.float32, device=top_w.device).scatter_(1, top_idx.long(), d_sel.float())
+
+
 def route(logits: torch.Tensor, k: int):
     """``b200collEpRoute`` alone: expert ids [T, k] (int32) and gate weights [T, k] (fp32) of fp32 logits [T, E] on the GPU."""
     assert logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
@@ -252,11 +260,7 @@ class MoELayer:
         _lib.check(lib.b200collEpCombine(self.comm.handle, self._win.ptr, self.top_idx.data_ptr(), self.ones.data_ptr(), self.sent.data_ptr(),
                                          self.dx.data_ptr(), T, k, *self._args(), s), "b200collEpCombine (backward)")
         train_ops.LAUNCHES += 2
-        # router: the gate weights are the softmax over the selected logits
-        p = self.top_w
-        d_sel = p * (self.d_gate - (self.d_gate * p).sum(-1, keepdim=True))
-        d_logits = torch.zeros(T, self.E, dtype=torch.float32, device=dev).scatter_(1, self.top_idx.long(), d_sel)
-        return self.dx, d_logits
+        return self.dx, router_backward(self.top_w, self.top_idx, self.d_gate, self.E)
 
     def expert_weight_grads(self):
         """``grads`` as (d w_gate, d w_up [experts_local, ffn, hidden], d w_down [experts_local, hidden, ffn])."""

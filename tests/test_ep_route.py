@@ -55,3 +55,34 @@ def test_route_kernel_never_writes_a_bad_expert(E, k):
     assert torch.isfinite(w).all()
     assert torch.equal(idx.cpu(), ridx)
     assert torch.allclose(w.cpu(), rw, rtol=1e-4, atol=1e-6)
+
+
+def test_router_backward_matches_autograd_of_topk_softmax():
+    import torch
+
+    from rocm_systems_b200.parallel.ep import router_backward
+
+    g = torch.Generator().manual_seed(3)
+    T, E, k = 64, 32, 4
+    logits = torch.randn(T, E, generator=g, dtype=torch.float64, requires_grad=True)
+    d_gate = torch.randn(T, k, generator=g, dtype=torch.float64)
+    top_v, top_i = torch.topk(logits, k, dim=-1)
+    w = torch.softmax(top_v, dim=-1)
+    (w * d_gate).sum().backward()
+    got = router_backward(w.detach().float(), top_i.to(torch.int32), d_gate.float(), E)
+    assert torch.allclose(got.double(), logits.grad, atol=1e-6)
+
+
+def test_gate_up_interleaving_round_trips():
+    import torch
+
+    from rocm_systems_b200.parallel.tp import deinterleave_gate_up, interleave_gate_up
+
+    for tile in (128, 256):
+        g, u = torch.randn(512, 24), torch.randn(512, 24)
+        w13 = interleave_gate_up(g, u, tile)
+        assert w13.shape == (1024, 24)
+        # a tile holds tile/2 gate rows then the tile/2 up rows of the same outputs
+        assert torch.equal(w13[: tile // 2], g[: tile // 2]) and torch.equal(w13[tile // 2: tile], u[: tile // 2])
+        g2, u2 = deinterleave_gate_up(w13, tile)
+        assert torch.equal(g2, g) and torch.equal(u2, u)
