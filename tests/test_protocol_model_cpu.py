@@ -289,3 +289,106 @@ def test_fused_reduce_scatter_cast_geometry():
     # lane ranges cut from each chunk's own size: the short last chunk's copy-in crosses into ranges
     # that another lane of a peer may still be reading from two chunks earlier
     assert races(rs_cast_accesses(Geometry(2, 4, 6 * 4096 + 1520, 4096, "rs", by_capacity=False)))
+
+
+# ---- the scatter-and-forward broadcast (kStagedCopy, three ranks and more, peer stores only) ----
+def bc_region(part_lo, part_hi, lane_cap_bytes, m, o, by_capacity=True):
+    """Region o of the m regions a lane's part [part_lo, part_hi) of a chunk is cut into."""
+    nbytes = part_hi - part_lo
+    basis = lane_cap_bytes if by_capacity else nbytes
+    sub = ceil_div(ceil_div(basis, m), U) * U if basis else 0
+    lo = min(o * sub, nbytes)
+    hi = min(lo + sub, nbytes)
+    return part_lo + lo, part_lo + hi
+
+
+def bc_accesses(n, lanes, total, cap, root, by_capacity=True, half0=0):
+    out = []
+    K = ceil_div(total, cap)
+    m = n - 1
+    lane_cap = ceil_div(ceil_div(cap, U), lanes) * U
+    owner = lambda o: (root + 1 + o) % n
+    own = lambda r: (r - root - 1 + n) % n
+
+    def regions(k, b):
+        lo, hi = ag_part(total, cap, lanes, k, b)          # lane parts follow the capacity (as in the all-gather)
+        return [bc_region(lo, hi, lane_cap, m, o, by_capacity) for o in range(m)]
+
+    for b in range(lanes):
+        for o, (lo, hi) in enumerate(regions(0, b)):       # prologue: the root stores chunk 0, region o into its owner
+            if lo < hi:
+                out.append((root, b, "all", 0, owner(o), half0, lo, hi, True))
+        for k in range(K):
+            epoch, half, more = k + 1, (half0 + k) & 1, k + 1 < K
+            if more:
+                for o, (lo, hi) in enumerate(regions(k + 1, b)):
+                    if lo < hi:
+                        out.append((root, b, "push", epoch, owner(o), half ^ 1, lo, hi, True))
+            for r in range(n):
+                if r == root:
+                    continue
+                lo, hi = regions(k, b)[own(r)]
+                if lo < hi:
+                    out.append((r, b, "fwd", epoch, r, half, lo, hi, False))                  # read the region the root left here
+                    for p in range(n):
+                        if p not in (r, root):
+                            out.append((r, b, "fwd", epoch, p, half, lo, hi, True))          # forward it
+                    out.append((r, b, "out", epoch, r, half, lo, hi, False))                  # copy it to recv
+                if k > 0:
+                    for o, (qlo, qhi) in enumerate(regions(k - 1, b)):
+                        if o != own(r) and qlo < qhi:
+                            out.append((r, b, "out", epoch, r, half ^ 1, qlo, qhi, False))    # forwarded regions of the chunk before
+        for r in range(n):                                                                    # behind the last barrier
+            if r == root:
+                continue
+            for o, (qlo, qhi) in enumerate(regions(K - 1, b)):
+                if o != own(r) and qlo < qhi:
+                    out.append((r, b, "all", K + 1, r, (half0 + K - 1) & 1, qlo, qhi, False))
+    return out
+
+
+def test_scatter_and_forward_broadcast_is_race_free_and_chunk_sized_regions_are_not():
+    rng = random.Random(7)
+    for _ in range(80):
+        n, lanes = rng.choice([3, 4, 5, 8]), rng.randint(1, 5)
+        cap = U * rng.randint(6, 240)
+        total = rng.randint(1, 7 * cap)
+        root = rng.randrange(n)
+        assert races(bc_accesses(n, lanes, total, cap, root, half0=rng.randint(0, 1))) == [], (n, lanes, total, cap, root)
+    # regions cut from each chunk's own size: the root's stores of a short chunk k + 1 land on regions of chunk k - 1
+    # (same half) that their receivers are still copying out
+    assert races(bc_accesses(4, 4, 4 * 838880 + 838816, 838880, 1, by_capacity=False))
+
+
+# ---- the staged all-to-all: one slot per source rank in a staging half, push step k + 1 while step k is copied out ----
+def a2a_accesses(n, lanes, total, stage_bytes, half0=0):
+    out = []
+    slot = (stage_bytes // n) // U * U
+    cap = min(slot, ceil_div(total, U) * U)
+    K = ceil_div(total, cap)
+    for r, b in itertools.product(range(n), range(lanes)):
+        lo, hi = ag_part(total, cap, lanes, 0, b)
+        for p in range(n):
+            if p != r and lo < hi:
+                out.append((r, b, "all", 0, p, half0, r * slot + lo, r * slot + hi, True))
+        for k in range(K):
+            epoch, half, more = k + 1, (half0 + k) & 1, k + 1 < K
+            if more:
+                lo, hi = ag_part(total, cap, lanes, k + 1, b)
+                for p in range(n):
+                    if p != r and lo < hi:
+                        out.append((r, b, "push", epoch, p, half ^ 1, r * slot + lo, r * slot + hi, True))
+            lo, hi = ag_part(total, cap, lanes, k, b)
+            for s in range(n):
+                if s != r and lo < hi:
+                    out.append((r, b, "out" if more else "all", epoch, r, half, s * slot + lo, s * slot + hi, False))
+    return out
+
+
+def test_staged_all_to_all_is_race_free():
+    rng = random.Random(9)
+    for _ in range(80):
+        n, lanes = rng.choice([2, 3, 4, 8]), rng.randint(1, 5)
+        stage = U * n * rng.randint(8, 200)
+        total = rng.randint(1, 6 * (stage // n))
+        assert races(a2a_accesses(n, lanes, total, stage, half0=rng.randint(0, 1))) == [], (n, lanes, total, stage)
