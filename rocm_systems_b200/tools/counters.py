@@ -23,6 +23,12 @@ chosen definitions read, one kernel pattern and a bounded number of launches, an
     python -m rocm_systems_b200.tools.counters --collect -k gemmPairKernel -c 2 --counter tensor_active_pct --counter hbm_gbs \
         -- python -m rocm_systems_b200.bench.kernel_cases --case gemm
 
+``--analyze`` turns a report into the per-kernel analysis the reference's rocprofiler-compute prints (its "analyze" mode:
+panels of derived metrics per dispatch): the counters grouped by panel, the warp stall reasons ranked, and a one-line
+verdict on what bounds the launch:
+
+    python -m rocm_systems_b200.tools.counters prof.ncu-rep --analyze --peaks MEASURED_PEAKS.json
+
 The capture never locks the GPU's clocks (``--clock-control none``) and is bounded by ``-k`` / ``-c``; ``--print-command``
 shows the ``ncu`` line without running anything.
 """
@@ -220,6 +226,90 @@ def collect_command(metrics: Sequence[str], command: Sequence[str], kernel: str,
     return cmd + list(command)
 
 
+PANELS = ["speed_of_light", "memory", "cache", "compute", "occupancy", "launch"]
+_STALL = re.compile(r"^smsp__average_warps_issue_stalled_(.+)_per_issue_active\.ratio$")
+_STALL_HINT = {
+    "long_scoreboard": "waiting for global / local memory (or a remote rank's memory)",
+    "short_scoreboard": "waiting for shared memory or special-function results",
+    "barrier": "waiting at a CTA barrier",
+    "membar": "waiting for a memory fence",
+    "wait": "fixed-latency dependency",
+    "lg_throttle": "load/store queue full (too many memory instructions in flight per warp)",
+    "math_pipe_throttle": "the pipe the warp needs is busy",
+    "mio_throttle": "shared-memory / special-function queue full",
+    "tex_throttle": "texture / L1 queue full",
+    "not_selected": "eligible, another warp was issued (enough parallelism)",
+    "no_instruction": "instruction fetch",
+    "dispatch_stall": "dispatch unit busy",
+    "sleeping": "in nanosleep (a polling loop backing off)",
+    "drain": "draining stores at exit",
+    "imc_miss": "constant cache miss",
+    "branch_resolving": "waiting for a branch target",
+    "selected": "issuing",
+}
+
+
+def stall_ranking(raw: Dict[str, float], top: int = 5) -> List[Tuple[str, float, str]]:
+    """The warp stall reasons of a capture, largest first: (reason, stalled warps per issued instruction, what it means)."""
+    found = []
+    for name, v in raw.items():
+        m = _STALL.match(name)
+        if m and m.group(1) != "selected" and v == v:
+            found.append((m.group(1), float(v), _STALL_HINT.get(m.group(1), "")))
+    found.sort(key=lambda t: -t[1])
+    return found[:top]
+
+
+def verdict(values: Dict[str, Optional[float]], stalls: Sequence[Tuple[str, float, str]]) -> str:
+    """One line on what bounds the launch, from the speed-of-light counters (the analysis front page of the reference's
+    rocprofiler-compute, restated on these counters)."""
+    g = lambda k: values.get(k) if values.get(k) is not None else 0.0  # noqa: E731
+    mem = max(g("hbm_fraction") * 100, g("dram_throughput_pct"), g("memory_throughput_pct"))
+    frac = values.get("bf16_fraction") or 0.0
+    cmp_ = max(g("tensor_active_pct"), g("sm_throughput_pct"), frac * 100 if frac <= 1.2 else 0.0)   # arg.flops of another kernel gives nonsense
+    if mem >= 60 and mem >= cmp_:
+        return f"memory bound ({mem:.0f} % of the memory system's peak)"
+    if cmp_ >= 60:
+        return f"compute bound ({cmp_:.0f} % of the busiest SM unit)"
+    why = f"; warps mostly stall on {stalls[0][0]} ({stalls[0][2]})" if stalls else ""
+    if g("sm_active_pct") and g("sm_active_pct") < 50:
+        return f"under-filled: SMs had work in {g('sm_active_pct'):.0f} % of the cycles (grid of {g('grid_size'):.0f} CTAs, {g('waves_per_sm'):.2f} waves){why}"
+    return f"latency bound: memory {mem:.0f} %, compute {cmp_:.0f} % of peak{why}"
+
+
+def analyze(cs: "CounterSet", kernels, peaks: dict, args: dict) -> List[dict]:
+    """Per captured launch: the derived counters grouped by panel, the stall ranking and the verdict."""
+    out = []
+    for k in kernels:
+        raw = dict(k.raw) if hasattr(k, "raw") else {}
+        values = cs.evaluate(raw, peaks, args)
+        panels: Dict[str, list] = {p: [] for p in PANELS}
+        for d in cs.defs:
+            v = values.get(d["name"])
+            if v is not None and v == v:
+                panels.setdefault(d.get("panel", "speed_of_light"), []).append({"name": d["name"], "value": v, "unit": d.get("unit", ""), "description": d.get("description", "")})
+        stalls = stall_ranking(raw)
+        out.append({"kernel": k.name, "panels": {p: rows for p, rows in panels.items() if rows},
+                    "stalls": [{"reason": r, "warps_per_issue": v, "meaning": h} for r, v, h in stalls], "verdict": verdict(values, stalls)})
+    return out
+
+
+def format_analysis(items: Sequence[dict]) -> str:
+    lines = []
+    for it in items:
+        lines.append(f"== {it['kernel']}")
+        lines.append(f"   {it['verdict']}")
+        for p, rows in it["panels"].items():
+            lines.append(f"   [{p}]")
+            for r in rows:
+                lines.append(f"     {r['name']:<30} {r['value']:>12.4g} {r['unit']:<28} {r['description']}")
+        if it["stalls"]:
+            lines.append("   [stalls: stalled warps per issued instruction]")
+            for s_ in it["stalls"]:
+                lines.append(f"     {s_['reason']:<30} {s_['warps_per_issue']:>12.3g} {'':<28} {s_['meaning']}")
+    return "\n".join(lines)
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     from . import roofline
 
@@ -230,6 +320,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--arg", action="append", default=[], help="NAME=VALUE readable as arg.NAME")
     ap.add_argument("--list", action="store_true", help="print the definitions and the raw metrics they need")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--analyze", action="store_true", help="per launch: the counters grouped by panel (speed of light, memory, caches, compute, "
+                    "occupancy, launch), the warp stall ranking and a one-line verdict on what bounds it")
     ap.add_argument("--collect", action="store_true", help="run the command after -- under Nsight Compute for the metrics the counters need, then evaluate")
     ap.add_argument("--counter", action="append", default=[], help="with --collect: only these definitions (default: all)")
     ap.add_argument("-k", "--kernel", default="", help="with --collect: regular expression of the kernels to capture")
@@ -278,6 +370,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         for k in roofline.read_ncu(path):
             raw = dict(k.raw) if hasattr(k, "raw") else {}
             rows.append({"kernel": k.name, **cs.evaluate(raw, peaks, args)})
+    if a.analyze:
+        items = [it for path in a.inputs for it in analyze(cs, roofline.read_ncu(path), peaks, args)]
+        print(json.dumps(items, indent=1) if a.json else format_analysis(items))
+        return 0
     if a.json:
         print(json.dumps(rows, indent=1))
     else:

@@ -540,3 +540,51 @@ def test_counters_collection_command_asks_for_exactly_the_needed_metrics(capsys)
         counters.main(["--collect", "-c", "500", "--print-command", "--", "true"])
     with pytest.raises(SystemExit):
         counters.main(["--collect", "--counter", "no_such_counter", "--print-command", "--", "true"])
+
+
+ANALYZE_COLS = [
+    ("Kernel Name", ""), ("gpu__time_duration.sum", "us"), ("dram__bytes_read.sum", "Mbyte"), ("dram__bytes_write.sum", "Mbyte"),
+    ("gpu__dram_throughput.avg.pct_of_peak_sustained_elapsed", "%"), ("gpu__compute_memory_throughput.avg.pct_of_peak_sustained_elapsed", "%"),
+    ("sm__throughput.avg.pct_of_peak_sustained_elapsed", "%"), ("sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active", "%"),
+    ("sm__cycles_active.avg", "cycle"), ("sm__cycles_elapsed.avg", "cycle"), ("lts__t_sector_hit_rate.pct", "%"),
+    ("launch__grid_size", ""), ("launch__block_size", ""), ("launch__waves_per_multiprocessor", ""), ("launch__registers_per_thread", "register/thread"),
+    ("smsp__average_warps_issue_stalled_long_scoreboard_per_issue_active.ratio", "inst"),
+    ("smsp__average_warps_issue_stalled_barrier_per_issue_active.ratio", "inst"),
+    ("smsp__average_warps_issue_stalled_selected_per_issue_active.ratio", "inst"),
+]
+ANALYZE_ROWS = [
+    # a streaming kernel near the memory ceiling, a tensor-core kernel, and a 16-CTA kernel that mostly waits at barriers
+    ["streamKernel", "100", "300", "300", "78", "80", "20", "0", "95000", "100000", "2", "4096", "256", "6.9", "32", "9.0", "0.2", "1.0"],
+    ["mmaKernel", "1000", "200", "134", "5", "30", "85", "82", "99000", "100000", "70", "148", "192", "1.0", "168", "1.5", "0.4", "1.0"],
+    ["waitKernel", "700", "147", "182", "6", "6", "1", "0", "10000", "100000", "20", "16", "512", "0.11", "128", "20.4", "30.6", "1.0"],
+]
+
+
+def _analyze_csv() -> str:
+    q = lambda cells: ",".join(f'"{c}"' for c in cells)  # noqa: E731
+    return "\n".join([q([c for c, _ in ANALYZE_COLS]), q([u for _, u in ANALYZE_COLS])] + [q(r) for r in ANALYZE_ROWS]) + "\n"
+
+
+def test_counter_analysis_panels_stalls_and_verdicts(tmp_path, capsys):
+    from rocm_systems_b200.tools import counters, roofline
+
+    cs = counters.CounterSet.load()
+    assert {d.get("panel") for d in cs.defs} <= set(counters.PANELS)           # every definition sits in a known panel
+    items = counters.analyze(cs, roofline.parse_ncu_csv(_analyze_csv()), {"hbm_gbs": 6650.0, "bf16_tflops": 1600.0}, {})
+    by = {it["kernel"]: it for it in items}
+    assert by["streamKernel"]["verdict"].startswith("memory bound")            # 600 MB in 100 us = 6 TB/s of 6.65
+    assert by["mmaKernel"]["verdict"].startswith("compute bound")
+    assert by["waitKernel"]["verdict"].startswith("under-filled") and "barrier" in by["waitKernel"]["verdict"]
+    st = by["waitKernel"]["stalls"]
+    assert [s["reason"] for s in st] == ["barrier", "long_scoreboard"]         # ranked; "selected" (issuing) is not a stall
+    mem = {r["name"]: r["value"] for r in by["streamKernel"]["panels"]["memory"]}
+    assert abs(mem["hbm_gbs"] - 6000) < 1e-6 and abs(mem["dram_read_mb"] - 300) < 1e-9
+    sol = {r["name"]: r["value"] for r in by["waitKernel"]["panels"]["speed_of_light"]}
+    assert abs(sol["sm_active_pct"] - 10.0) < 1e-9
+    assert "compute" not in by["waitKernel"]["panels"] or all(r["name"] != "ipc_active" for r in by["waitKernel"]["panels"]["compute"])  # inputs absent: left out
+    # the command line prints the same analysis
+    (tmp_path / "raw.csv").write_text(_analyze_csv())
+    (tmp_path / "p.json").write_text('{"hbm_gbs": 6650.0, "bf16_tflops": 1600.0}')
+    assert counters.main([str(tmp_path / "raw.csv"), "--analyze", "--peaks", str(tmp_path / "p.json")]) == 0
+    text = capsys.readouterr().out
+    assert "== waitKernel" in text and "[stalls" in text and "under-filled" in text and "[memory]" in text
