@@ -116,15 +116,78 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--stats", action="store_true", help="print per-kernel / per-collective statistics")
     g.add_argument("--summary", action="store_true", help="write the statistics as <output>_summary.json as well")
     g.add_argument("--top", type=int, default=15)
+    g = ap.add_argument_group("counter collection")
+    g.add_argument("--pmc", nargs="+", default=[], metavar="COUNTER",
+                   help="collect these derived counters (tools/counter_defs.yaml; 'all' for every one) for the kernels of the command: the command runs "
+                        "under Nsight Compute for exactly the raw metrics they need, clocks untouched; writes <output>_counter_collection.csv")
+    g.add_argument("--pmc-kernel", default="", metavar="REGEX", help="kernels to capture (default: all, bounded by --pmc-count)")
+    g.add_argument("--pmc-count", type=int, default=5, help="launches to capture (a capture replays every launch several times: keep it small)")
+    g.add_argument("--pmc-skip", type=int, default=0, help="matching launches to skip first")
+    g.add_argument("--pmc-dry-run", action="store_true", help="print the Nsight Compute command line and stop")
+    g.add_argument("--list-pmc", action="store_true", help="list the derived counters and stop")
     g = ap.add_argument_group("tools")
     g.add_argument("--tool-library", action="append", default=[], help="extra dispatch-table tool(s) to load into the communication library")
     ap.add_argument("command", nargs=argparse.REMAINDER, help="-- command to run")
     return ap
 
 
+def collect_counters(a, cmd: Sequence[str], prefix: str) -> int:
+    """The ``--pmc`` mode: one bounded Nsight Compute run of the command for the chosen derived counters, then one row per
+    (launch, counter) in ``<output>_counter_collection.csv`` (the layout of the reference launcher's counter-collection file:
+    dispatch id, kernel name, counter name, value)."""
+    from . import counters, roofline
+
+    cs = counters.CounterSet.load()
+    if a.pmc != ["all"]:
+        known = {d["name"] for d in cs.defs}
+        missing = [c for c in a.pmc if c not in known]
+        if missing:
+            print(f"prof: unknown counter(s): {', '.join(missing)} (see --list-pmc)", file=sys.stderr)
+            return 2
+        cs = counters.CounterSet([{k: v for k, v in d.items() if k != "ast"} for d in cs.defs if d["name"] in a.pmc])
+    if not 1 <= a.pmc_count <= 20:
+        print("prof: --pmc-count must be between 1 and 20", file=sys.stderr)
+        return 2
+    ncu_cmd = counters.collect_command(cs.required_metrics(), cmd, a.pmc_kernel, a.pmc_count, a.pmc_skip, prefix + "_counters")
+    if a.pmc_dry_run:
+        print(" ".join(ncu_cmd))
+        return 0
+    rc = subprocess.call(ncu_cmd)
+    if rc != 0:
+        print(f"prof: ncu exited with {rc}", file=sys.stderr)
+        return rc
+    n = write_counter_collection(cs, roofline.read_ncu(prefix + "_counters.ncu-rep"), roofline.load_peaks("MEASURED_PEAKS.json"),
+                                 prefix + "_counter_collection.csv")
+    print(f"prof: {n} counter values in {prefix}_counter_collection.csv", file=sys.stderr)
+    return 0
+
+
+def write_counter_collection(cs, kernels, peaks: dict, path: str) -> int:
+    """One row per (captured launch, derived counter that could be evaluated); returns the number of rows."""
+    import csv as _csv
+
+    units = {d["name"]: d.get("unit", "") for d in cs.defs}
+    n = 0
+    with open(path, "w", newline="") as f:
+        w = _csv.writer(f)
+        w.writerow(["Dispatch_Id", "Kernel_Name", "Counter_Name", "Counter_Value", "Unit"])
+        for i, k in enumerate(kernels):
+            for name, v in cs.evaluate(dict(k.raw), peaks, {}).items():
+                if v is not None and v == v:
+                    w.writerow([i, k.name, name, f"{v:.6g}", units[name]])
+                    n += 1
+    return n
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     a = parser().parse_args(argv)
     cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
+    if a.list_pmc:
+        from . import counters
+
+        for d in counters.CounterSet.load().defs:
+            print(f"{d['name']:<30} [{d.get('panel', '')}] {d.get('unit', '')}: {d.get('description', '')}")
+        return 0
     if not cmd:
         print("prof: no command given (put it after --)", file=sys.stderr)
         return 2
@@ -136,6 +199,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     outdir = Path(a.output_directory)
     outdir.mkdir(parents=True, exist_ok=True)
     prefix = str(outdir / a.output_file)
+    if a.pmc:
+        return collect_counters(a, cmd, prefix)   # a run of its own: a profiled run is not a traced or a timed one
     if a.sys_sample > 0:
         from .sysmon import SystemSampler
 

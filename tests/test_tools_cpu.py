@@ -588,3 +588,28 @@ def test_counter_analysis_panels_stalls_and_verdicts(tmp_path, capsys):
     assert counters.main([str(tmp_path / "raw.csv"), "--analyze", "--peaks", str(tmp_path / "p.json")]) == 0
     text = capsys.readouterr().out
     assert "== waitKernel" in text and "[stalls" in text and "under-filled" in text and "[memory]" in text
+
+
+def test_profiler_launcher_counter_collection(tmp_path, capsys):
+    """``prof --pmc``: the Nsight Compute line asks for exactly the raw metrics of the chosen counters (bounded, clocks
+    untouched), and a capture becomes one row per (launch, counter)."""
+    import csv as _csv
+
+    from rocm_systems_b200.tools import counters, prof, roofline
+
+    rc = prof.main(["--pmc", "hbm_gbs", "tensor_active_pct", "--pmc-kernel", "gemm", "--pmc-count", "2", "--pmc-dry-run", "-d", str(tmp_path), "--", "python", "x.py"])
+    line = capsys.readouterr().out.strip()
+    assert rc == 0 and line.startswith("ncu --clock-control none --metrics ") and line.endswith("-k regex:gemm python x.py") and " -c 2 " in line
+    metrics = line.split("--metrics ")[1].split(" ")[0].split(",")
+    assert sorted(metrics) == ["dram__bytes_read.sum", "dram__bytes_write.sum", "gpu__time_duration.sum", "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active"]
+    assert prof.main(["--pmc", "no_such_counter", "--pmc-dry-run", "-d", str(tmp_path), "--", "true"]) == 2
+    assert prof.main(["--pmc", "hbm_gbs", "--pmc-count", "500", "--pmc-dry-run", "-d", str(tmp_path), "--", "true"]) == 2
+    capsys.readouterr()
+    assert prof.main(["--list-pmc"]) == 0 and "hbm_gbs" in capsys.readouterr().out
+    cs = counters.CounterSet.load()
+    n = prof.write_counter_collection(cs, roofline.parse_ncu_csv(_analyze_csv()), {"hbm_gbs": 6650.0, "bf16_tflops": 1600.0}, str(tmp_path / "cc.csv"))
+    rows = list(_csv.DictReader(open(tmp_path / "cc.csv")))
+    assert n == len(rows) and {r["Kernel_Name"] for r in rows} == {"streamKernel", "mmaKernel", "waitKernel"}
+    got = {(r["Kernel_Name"], r["Counter_Name"]): float(r["Counter_Value"]) for r in rows}
+    assert abs(got[("streamKernel", "hbm_gbs")] - 6000) < 1e-3 and got[("mmaKernel", "tensor_active_pct")] == 82
+    assert ("streamKernel", "tflops") not in got          # needs arg.flops: left out
