@@ -4,6 +4,7 @@ showTypeTopology :3372, showNodesBw :3460) on top of the native ``b200smi_*`` AP
 
     python -m rocm_systems_b200.tools.smi --showall
     python -m rocm_systems_b200.tools.smi --showtopo [--json]
+    python -m rocm_systems_b200.tools.smi metric -g 0 1 --csv        # subcommands: version list static metric topology process monitor event
 
 Setters (``--setpowerlimit``) do nothing unless ``--allow-set`` is given AND B200SMI_ALLOW_SET=1 is
 in the environment; GPUs on shared hosts must be left as they were found.
@@ -231,7 +232,125 @@ def _print_matrix(title: str, m, n: int) -> None:
         print(f"GPU{i:<4}" + "".join(f"{str(m[i][j]):<12}" for j in range(n)))
 
 
+SUBCOMMANDS = ("version", "list", "static", "metric", "topology", "process", "monitor", "event")
+
+
+def _sub_main(argv) -> int:
+    """The subcommand front end (the layout of the reference's newer amd-smi command line: ``list``, ``static``, ``metric``,
+    ``topology``, ``process``, ``monitor``, ``event``, ``version``), over the same readings as the flag front end. Every
+    subcommand takes ``-g GPU [GPU ...]`` and ``--json`` / ``--csv``; nothing here changes a device."""
+    ap = argparse.ArgumentParser(prog="b200-smi")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    subs = {}
+    for name, help_ in (("version", "tool, library and driver versions"), ("list", "index, bus id and UUID of every GPU"),
+                        ("static", "what does not change while the GPU runs: product, bus, limits, modes, link count"),
+                        ("metric", "what does: clocks, power, temperature, memory, utilisation, ECC totals, NVLink error counters, throttle reasons"),
+                        ("topology", "link type, hops, weight, bandwidth and peer access between every pair"),
+                        ("process", "compute processes per GPU"), ("monitor", "one line of readings per GPU and interval"),
+                        ("event", "XID / ECC / power-state / clock events as they happen")):
+        sp = sub.add_parser(name, help=help_)
+        sp.add_argument("-g", "--gpu", nargs="+", type=int, default=None, help="GPU indices (default: all)")
+        sp.add_argument("--json", action="store_true")
+        sp.add_argument("--csv", action="store_true")
+        subs[name] = sp
+    subs["monitor"].add_argument("-w", "--watch", type=float, default=1.0, metavar="SECONDS", help="interval between lines")
+    subs["monitor"].add_argument("-i", "--iterations", type=int, default=1, help="how many intervals (0: until interrupted)")
+    subs["event"].add_argument("-t", "--timeout", type=float, default=5.0, metavar="SECONDS", help="stop after this long without an event")
+    a = ap.parse_args(argv)
+    try:
+        smi = Smi()
+    except RuntimeError as e:
+        print(f"b200-smi: {e}", file=sys.stderr)
+        return 1
+    n = smi.count()
+    gpus = [g for g in (a.gpu if a.gpu is not None else range(n))]
+    bad = [g for g in gpus if not 0 <= g < n]
+    if bad:
+        print(f"b200-smi: no GPU {bad[0]} (there are {n})", file=sys.stderr)
+        smi.close()
+        return 2
+
+    def emit(rows):
+        """rows: a list of flat dicts (one per GPU, pair or process)."""
+        if a.json:
+            print(json.dumps(rows, indent=1))
+        elif a.csv:
+            import csv as _csv
+
+            keys = list(dict.fromkeys(k for r in rows for k in r))
+            w = _csv.writer(sys.stdout)
+            w.writerow(keys)
+            for r in rows:
+                w.writerow([r.get(k, "") for k in keys])
+        else:
+            for r in rows:
+                head = f"GPU {r['gpu']}" if "gpu" in r else ""
+                print((head + ": " if head else "") + ", ".join(f"{k} {v}" for k, v in r.items() if k != "gpu"))
+
+    if a.cmd == "version":
+        from .. import __version__
+
+        emit([{"tool": "b200-smi", "package": __version__, "driver": smi.driver_version()}])
+    elif a.cmd == "list":
+        emit([{"gpu": g, "bus_id": smi.info(g)["busId"], "uuid": smi.info(g)["uuid"]} for g in gpus])
+    elif a.cmd == "static":
+        rows = []
+        for g in gpus:
+            d, m, pc = smi.info(g), smi.modes(g), smi.pcie(g)
+            rows.append({"gpu": g, "name": d["name"], "bus_id": d["busId"], "uuid": d["uuid"], "memory_total_gib": round(d["memTotalBytes"] / 2**30, 1),
+                         "sm_clock_max_mhz": d["smClockMaxMhz"], "memory_clock_max_mhz": d["memClockMaxMhz"], "power_limit_w": d["powerLimitMilliwatt"] / 1000,
+                         "pcie_generation": pc["generation"], "pcie_width": pc["width"], "nvlink_links": d["nvlinkCount"], "compute_mode": m["compute_mode"],
+                         "persistence": m["persistence"], "mig": m["mig"], "ecc": m["ecc"]})
+        emit(rows)
+    elif a.cmd == "metric":
+        rows = []
+        for g in gpus:
+            d, e = smi.info(g), smi.nvlink_errors(g)
+            rows.append({"gpu": g, "sm_clock_mhz": d["smClockMhz"], "memory_clock_mhz": d["memClockMhz"], "power_w": round(d["powerMilliwatt"] / 1000, 1),
+                         "temperature_c": d["temperatureC"], "memory_used_gib": round(d["memUsedBytes"] / 2**30, 2), "gpu_util_pct": d["gpuUtilPct"],
+                         "memory_util_pct": d["memUtilPct"], "ecc_corrected": d["eccCorrected"], "ecc_uncorrected": d["eccUncorrected"],
+                         "nvlink_active": d["nvlinkActive"], "nvlink_replay": e["replay"], "nvlink_recovery": e["recovery"], "nvlink_crc": e["crcFlit"] + e["crcData"],
+                         "throttle": ",".join(d["throttleReasonNames"]) or "none"})
+        emit(rows)
+    elif a.cmd == "topology":
+        rows = []
+        for x in gpus:
+            for y in gpus:
+                if x != y:
+                    l = smi.link(x, y)
+                    rows.append({"gpu": x, "peer": y, "type": l["typeName"], "hops": l["hops"], "weight": l["weight"], "max_bandwidth_mbps": l["maxBandwidthMBps"],
+                                 "peer_access": bool(l["p2pAccessible"])})
+        emit(rows)
+    elif a.cmd == "process":
+        emit([{"gpu": g, "pid": pr["pid"], "name": pr["name"], "memory_gib": round(pr["used_memory_bytes"] / 2**30, 2)} for g in gpus for pr in smi.processes(g)])
+    elif a.cmd == "monitor":
+        import time
+
+        i = 0
+        try:
+            while a.iterations == 0 or i < a.iterations:
+                rows = []
+                for g in gpus:
+                    d = smi.info(g)
+                    rows.append({"gpu": g, "power_w": round(d["powerMilliwatt"] / 1000, 1), "temperature_c": d["temperatureC"], "sm_clock_mhz": d["smClockMhz"],
+                                 "gpu_util_pct": d["gpuUtilPct"], "memory_util_pct": d["memUtilPct"], "memory_used_gib": round(d["memUsedBytes"] / 2**30, 2)})
+                emit(rows)
+                i += 1
+                if a.iterations == 0 or i < a.iterations:
+                    time.sleep(max(0.0, a.watch))
+        except KeyboardInterrupt:
+            pass
+    elif a.cmd == "event":
+        rows = [ev for ev in smi.events(timeout_ms=int(a.timeout * 1000)) if ev["device"] in gpus]
+        emit([{"gpu": ev["device"], "type": ev["type"], "data": ev["data"], "timestamp_ns": ev["timestamp_ns"]} for ev in rows])
+    smi.close()
+    return 0
+
+
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in SUBCOMMANDS:
+        return _sub_main(argv)
     ap = argparse.ArgumentParser(prog="b200-smi", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--showall", action="store_true")
     ap.add_argument("--showtopo", action="store_true", help="weight, hops, type and bandwidth tables")

@@ -180,3 +180,33 @@ print(json.dumps(h))
     e = dict(os.environ, B200SMI_NVML_LIBRARY="/nonexistent/libnvml.so", PYTHONPATH=str(ROOT))
     p = subprocess.run([sys.executable, "-c", "import bench, json; print(json.dumps(bench.gpu_health(0)))"], env=e, capture_output=True, text=True, timeout=120)
     assert p.returncode == 0 and "unavailable" in json.loads(p.stdout.strip().splitlines()[-1])
+
+
+def test_subcommand_front_end(fake_nvml):
+    """``list`` / ``static`` / ``metric`` / ``topology`` / ``process`` / ``monitor`` / ``event`` / ``version`` over the same readings,
+    as JSON, CSV and text, with a GPU selection."""
+    import csv
+    import io
+    import json
+
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="4", FAKE_NVML_TEMP="58", FAKE_NVML_EVENTS="1:8:94")
+
+    def run(*args):
+        p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", *args], env=e, capture_output=True, text=True)
+        assert p.returncode == 0, p.stderr
+        return p.stdout
+
+    lst = json.loads(run("list", "--json"))
+    assert [r["gpu"] for r in lst] == [0, 1, 2, 3] and all(r["uuid"] and r["bus_id"] for r in lst)
+    st = json.loads(run("static", "-g", "1", "3", "--json"))
+    assert [r["gpu"] for r in st] == [1, 3] and st[0]["nvlink_links"] == 18 and st[0]["pcie_generation"] == 5 and "power_limit_w" in st[0]
+    rows = list(csv.DictReader(io.StringIO(run("metric", "--csv"))))
+    assert len(rows) == 4 and rows[0]["temperature_c"] == "58" and {"sm_clock_mhz", "power_w", "nvlink_replay", "throttle"} <= set(rows[0])
+    topo = json.loads(run("topology", "-g", "0", "2", "--json"))
+    assert {(r["gpu"], r["peer"]) for r in topo} == {(0, 2), (2, 0)} and topo[0]["type"] == "NVLINK" and topo[0]["peer_access"] is True
+    assert "GPU 0: power_w" in run("monitor", "-g", "0", "-i", "2", "-w", "0.01")
+    ev = json.loads(run("event", "-t", "0.3", "--json"))
+    assert ev and ev[0]["gpu"] == 1 and ev[0]["data"] == 94
+    assert "580.159.fake" in run("version")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "metric", "-g", "9"], env=e, capture_output=True, text=True)
+    assert p.returncode == 2 and "no GPU 9" in p.stderr
