@@ -76,8 +76,73 @@ class Telemetry:
             raise ValueError(f"unknown field(s) {unknown}; known: {sorted(FIELDS)}")
         self.field_groups[name] = list(fields)
 
+    def delete_group(self, name: str) -> None:
+        if name == "all":
+            raise ValueError("the group of all devices cannot be deleted")
+        if name not in self.groups:
+            raise KeyError(f"no device group {name!r}")
+        del self.groups[name]
+
+    def delete_field_group(self, name: str) -> None:
+        if name == "default":
+            raise ValueError("the default field group cannot be deleted")
+        if name not in self.field_groups:
+            raise KeyError(f"no field group {name!r}")
+        del self.field_groups[name]
+
     def watch(self, group: str = "all", field_group: str = "default", period_ms: int = 1000, keep: int = 3600) -> None:
+        if group not in self.groups:
+            raise KeyError(f"no device group {group!r}")
+        if field_group not in self.field_groups:
+            raise KeyError(f"no field group {field_group!r}")
+        if self.watching:
+            self.stop()
         self.start(self.groups[group], self.field_groups[field_group], period_ms, keep)
+
+    def topology(self, dev: int) -> List[dict]:
+        """The links of ``dev`` to every other device (rdc: rdc_device_topology_get)."""
+        n = self.smi.count()
+        if not 0 <= dev < n:
+            raise ValueError(f"no device {dev}; this host has {n}")
+        out = []
+        for peer in range(n):
+            if peer != dev:
+                l = self.smi.link(dev, peer)
+                out.append({"peer": peer, "type": l["typeName"], "hops": l["hops"], "weight": l["weight"], "max_bandwidth_mbps": l["maxBandwidthMBps"],
+                            "peer_access": bool(l["p2pAccessible"])})
+        return out
+
+    # ---- settings that outlive the daemon (rdc: RdcConfigSettingsImpl: groups, field groups and policies kept in a file) ----
+    def config(self) -> dict:
+        return {"groups": {k: v for k, v in self.groups.items() if k != "all"}, "field_groups": {k: v for k, v in self.field_groups.items() if k != "default"},
+                "policies": list(getattr(self, "_policies", []))}
+
+    def config_save(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(self.config(), f, indent=1)
+
+    def config_load(self, path: str) -> dict:
+        """Re-creates the groups, field groups and policies of a saved file; entries that do not fit this host (a device
+        index that is not there, an unknown field) are reported and skipped, the rest is applied."""
+        with open(path) as f:
+            cfg = json.load(f)
+        skipped = []
+        for name, devs in cfg.get("groups", {}).items():
+            try:
+                self.create_group(name, devs)
+            except ValueError as e:
+                skipped.append(f"group {name}: {e}")
+        for name, fields in cfg.get("field_groups", {}).items():
+            try:
+                self.create_field_group(name, fields)
+            except ValueError as e:
+                skipped.append(f"field group {name}: {e}")
+        for p in cfg.get("policies", []):
+            try:
+                self.policy_set(int(p["device"]), p["field"], float(p["threshold"]), p.get("direction", "above") != "below")
+            except (ValueError, KeyError, RuntimeError) as e:
+                skipped.append(f"policy {p}: {e}")
+        return {"applied": self.config(), "skipped": skipped}
 
     def diagnose(self, level: int = 1) -> List[dict]:
         """Short diagnostics per device (rdc: rdc_diagnostic_run). Level 1 reads only: health verdict,
@@ -212,6 +277,10 @@ class Telemetry:
                 del self._events[:-1000]  # keep the last thousand
 
         self.smi.policy(dev, field, threshold, above, fire)
+        if not hasattr(self, "_policies"):
+            self._policies = []
+        self._policies = [p for p in self._policies if not (p["device"] == dev and p["field"] == field and p["direction"] == ("above" if above else "below"))]
+        self._policies.append({"device": dev, "field": field, "threshold": threshold, "direction": "above" if above else "below"})
 
     def policy_events(self) -> list:
         if not hasattr(self, "_events"):
@@ -310,13 +379,43 @@ def make_handler(t: Telemetry):
                 elif url.path == "/api/policy/set":
                     t.policy_set(int(q["dev"]), q["field"], float(q["threshold"]), q.get("direction", "above") != "below")
                     self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/policy/list":
+                    self._send(200, json.dumps(list(getattr(t, "_policies", []))))
+                elif url.path == "/api/group/create":
+                    t.create_group(q["name"], [int(x) for x in q["devices"].split(",") if x != ""])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/group/delete":
+                    t.delete_group(q["name"])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/group/list":
+                    self._send(200, json.dumps(t.groups))
+                elif url.path == "/api/fieldgroup/create":
+                    t.create_field_group(q["name"], [x for x in q["fields"].split(",") if x])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/fieldgroup/delete":
+                    t.delete_field_group(q["name"])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/fieldgroup/list":
+                    self._send(200, json.dumps(t.field_groups))
+                elif url.path == "/api/watch":
+                    t.watch(q.get("group", "all"), q.get("fieldgroup", "default"), int(q.get("period_ms", 1000)), int(q.get("keep", 3600)))
+                    self._send(200, json.dumps({"ok": True, "devices": t.devices, "fields": t.fields}))
+                elif url.path == "/api/topo":
+                    self._send(200, json.dumps(t.topology(int(q.get("dev", 0)))))
+                elif url.path == "/api/config":
+                    self._send(200, json.dumps(t.config()))
+                elif url.path == "/api/config/save":
+                    t.config_save(q["path"])
+                    self._send(200, json.dumps({"ok": True}))
+                elif url.path == "/api/config/load":
+                    self._send(200, json.dumps(t.config_load(q["path"])))
                 elif url.path == "/api/events":
                     self._send(200, json.dumps(t.device_events))
                 elif url.path == "/api/policy/events":
                     self._send(200, json.dumps(t.policy_events()))
                 else:
                     self._send(404, json.dumps({"error": "unknown path"}))
-            except (KeyError, ValueError, RuntimeError) as e:
+            except (KeyError, ValueError, RuntimeError, OSError) as e:
                 self._send(400, json.dumps({"error": str(e)}))
 
     return Handler
@@ -329,7 +428,8 @@ def serve(t: Telemetry, host: str, port: int) -> ThreadingHTTPServer:
     return srv
 
 
-def _client(url: str, path: str, **q) -> object:
+def _client(url: str, endpoint: str, **q) -> object:
+    path = endpoint
     full = url.rstrip("/") + path + ("?" + urllib.parse.urlencode(q) if q else "")
     with urllib.request.urlopen(full, timeout=10) as r:
         body = r.read().decode()
@@ -358,20 +458,49 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("--level", type=int, default=1, choices=[1, 2])
     p = sub.add_parser("client", help="talk to a running daemon")
     p.add_argument("--url", default="http://127.0.0.1:9400")
-    p.add_argument("what", choices=["devices", "latest", "health", "metrics", "history", "events", "job-start", "job-stop", "job-stats"])
+    p.add_argument("what", choices=["devices", "latest", "health", "metrics", "history", "events", "job-start", "job-stop", "job-stats",
+                                    "group-create", "group-delete", "group-list", "fieldgroup-create", "fieldgroup-delete", "fieldgroup-list", "watch",
+                                    "policy-set", "policy-list", "policy-events", "topo", "config", "config-save", "config-load"])
     p.add_argument("--job", default="")
     p.add_argument("--dev", type=int, default=0)
     p.add_argument("--field", default="power")
+    p.add_argument("--name", default="", help="group or field group")
+    p.add_argument("--devices", nargs="+", type=int, default=[], help="group-create: device indices")
+    p.add_argument("--fields", nargs="+", default=[], help="fieldgroup-create: field names")
+    p.add_argument("--group", default="all", help="watch: device group")
+    p.add_argument("--fieldgroup", default="default", help="watch: field group")
+    p.add_argument("--period-ms", type=int, default=1000, help="watch: sampling period")
+    p.add_argument("--threshold", type=float, default=0.0, help="policy-set")
+    p.add_argument("--direction", choices=["above", "below"], default="above", help="policy-set")
+    p.add_argument("--path", default="", help="config-save / config-load: file on the daemon's host")
     a = ap.parse_args(argv)
 
     if a.cmd == "client":
         path = {"devices": "/api/devices", "latest": "/api/latest", "health": "/api/health", "metrics": "/metrics", "history": "/api/history", "events": "/api/events",
-                "job-start": "/api/job/start", "job-stop": "/api/job/stop", "job-stats": "/api/job/stats"}[a.what]
+                "job-start": "/api/job/start", "job-stop": "/api/job/stop", "job-stats": "/api/job/stats",
+                "group-create": "/api/group/create", "group-delete": "/api/group/delete", "group-list": "/api/group/list",
+                "fieldgroup-create": "/api/fieldgroup/create", "fieldgroup-delete": "/api/fieldgroup/delete", "fieldgroup-list": "/api/fieldgroup/list",
+                "watch": "/api/watch", "policy-set": "/api/policy/set", "policy-list": "/api/policy/list", "policy-events": "/api/policy/events",
+                "topo": "/api/topo", "config": "/api/config", "config-save": "/api/config/save", "config-load": "/api/config/load"}[a.what]
         q = {}
         if a.what.startswith("job"):
             q["job"] = a.job
         if a.what == "history":
             q = {"dev": a.dev, "field": a.field}
+        if a.what == "group-create":
+            q = {"name": a.name, "devices": ",".join(str(d) for d in a.devices)}
+        if a.what == "fieldgroup-create":
+            q = {"name": a.name, "fields": ",".join(a.fields)}
+        if a.what in ("group-delete", "fieldgroup-delete"):
+            q = {"name": a.name}
+        if a.what == "watch":
+            q = {"group": a.group, "fieldgroup": a.fieldgroup, "period_ms": a.period_ms}
+        if a.what == "policy-set":
+            q = {"dev": a.dev, "field": a.field, "threshold": a.threshold, "direction": a.direction}
+        if a.what == "topo":
+            q = {"dev": a.dev}
+        if a.what in ("config-save", "config-load"):
+            q = {"path": a.path}
         res = _client(a.url, path, **q)
         print(res if isinstance(res, str) else json.dumps(res, indent=1))
         return 0

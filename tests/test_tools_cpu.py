@@ -613,3 +613,46 @@ def test_profiler_launcher_counter_collection(tmp_path, capsys):
     got = {(r["Kernel_Name"], r["Counter_Name"]): float(r["Counter_Value"]) for r in rows}
     assert abs(got[("streamKernel", "hbm_gbs")] - 6000) < 1e-3 and got[("mmaKernel", "tensor_active_pct")] == 82
     assert ("streamKernel", "tflops") not in got          # needs arg.flops: left out
+
+
+def test_telemetry_group_management_and_saved_configuration(tmp_path, fake_nvml):
+    """Device groups, field groups, a watch on a (group, field group) pair, the policy list, a device's links and a settings
+    file that re-creates all of it in a second daemon: over HTTP and through the client command line."""
+    out = _py(f"""
+import json, io, contextlib, urllib.request, urllib.error
+from rocm_systems_b200.tools import telemetry
+t = telemetry.Telemetry()
+srv = telemetry.serve(t, '127.0.0.1', 0)
+url = 'http://127.0.0.1:%d' % srv.server_address[1]
+def cli(*args):
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert telemetry.main(['client', '--url', url, *args]) == 0
+    return json.loads(buf.getvalue())
+assert cli('group-create', '--name', 'pair', '--devices', '1', '3') == {{'ok': True}}
+assert cli('fieldgroup-create', '--name', 'thermal', '--fields', 'temp', 'power') == {{'ok': True}}
+assert cli('group-list') == {{'all': [0, 1, 2, 3], 'pair': [1, 3]}}
+assert cli('fieldgroup-list')['thermal'] == ['temp', 'power']
+w = cli('watch', '--group', 'pair', '--fieldgroup', 'thermal', '--period-ms', '20')
+assert w['devices'] == [1, 3] and w['fields'] == ['temp', 'power']
+assert sorted(cli('latest')) == ['1', '3']
+cli('policy-set', '--dev', '1', '--field', 'temp', '--threshold', '90', '--direction', 'above')
+assert cli('policy-list') == [{{'device': 1, 'field': 'temp', 'threshold': 90.0, 'direction': 'above'}}]
+topo = cli('topo', '--dev', '2')
+assert [l['peer'] for l in topo] == [0, 1, 3] and topo[0]['type'] == 'NVLINK'
+cli('config-save', '--path', r'{tmp_path}/cfg.json')
+for bad in ('/api/group/create?name=x&devices=9', '/api/group/delete?name=all', '/api/watch?group=nope', '/api/fieldgroup/create?name=y&fields=bogus'):
+    try:
+        urllib.request.urlopen(url + bad, timeout=10); raise SystemExit('accepted ' + bad)
+    except urllib.error.HTTPError as e:
+        assert e.code == 400, bad
+cli('group-delete', '--name', 'pair')
+assert 'pair' not in cli('group-list')
+srv.shutdown(); t.stop()
+# a second daemon takes the saved settings
+t2 = telemetry.Telemetry()
+res = t2.config_load(r'{tmp_path}/cfg.json')
+assert res['skipped'] == [] and t2.groups['pair'] == [1, 3] and t2.field_groups['thermal'] == ['temp', 'power'] and t2.config()['policies'][0]['threshold'] == 90.0
+print('ok')
+""", {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "4"})
+    assert "ok" in out
