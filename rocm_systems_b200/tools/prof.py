@@ -105,6 +105,8 @@ def parser() -> argparse.ArgumentParser:
     g = ap.add_argument_group("filtering")
     g.add_argument("--kernel-include-regex", default="")
     g.add_argument("--kernel-exclude-regex", default="", help="drop kernels whose name matches (applied when the trace is imported)")
+    g.add_argument("--kernel-rename", action="store_true", help="name every kernel after the innermost marker range open on its launching thread at launch "
+                   "(needs --marker-trace; with --runtime-trace the launching thread and time are exact)")
     g.add_argument("--truncate-kernels", action="store_true", help="kernel names without return type, namespaces, template and call arguments")
     g.add_argument("--collection-period", default="", metavar="DELAY_MS:DURATION_MS",
                    help="keep only what started in this window after the first record (applied when the trace is imported)")
@@ -226,6 +228,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
             db.drop_kernels(a.kernel_exclude_regex)
         if a.truncate_kernels:
             db.truncate_kernel_names()
+        if a.kernel_rename:
+            db.rename_kernels_by_marker()
         summary = db.summary(a.top)
         if "pftrace" in a.output_format:
             db.to_perfetto(prefix + ".perfetto.json")

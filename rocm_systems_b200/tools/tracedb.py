@@ -231,6 +231,34 @@ class TraceDB:
         self.db.commit()
         return changed
 
+    def rename_kernels_by_marker(self) -> int:
+        """Gives every kernel the name of the innermost marker range that was open on the launching thread when it was
+        launched (what the reference launcher offers as --kernel-rename: a region of the application then shows up as ONE
+        row of the kernel statistics). The launch is the runtime / driver API record with the kernel's correlation id (its
+        thread and start time); without API records the kernel's device start time inside a range of the same process is
+        used instead. Kernels outside every range keep their names. Returns how many were renamed."""
+        marker = self.db.execute("select id from string where value = 'MARKER_API'").fetchone()
+        if not marker:
+            return 0
+        ranges = {}   # process_id -> [(start, end, tid, name_id)], innermost first when sorted by start descending
+        for pid, tid, name_id, st, en in self.db.execute("select process_id, tid, name_id, start_ns, end_ns from region where category_id = ?", (marker[0],)):
+            ranges.setdefault(pid, []).append((st, en, tid, name_id))
+        for v in ranges.values():
+            v.sort(key=lambda r: -r[0])
+        launches = {}  # (process_id, correlation_id) -> (tid, start) of the API call that launched
+        for pid, tid, corr, st in self.db.execute("select process_id, tid, correlation_id, start_ns from region where category_id != ? and correlation_id != 0", (marker[0],)):
+            launches.setdefault((pid, corr), (tid, st))
+        renamed = 0
+        for kid, pid, corr, dev_start in self.db.execute("select id, process_id, correlation_id, start_ns from kernel_dispatch").fetchall():
+            tid, when = launches.get((pid, corr), (None, dev_start))
+            for st, en, rtid, name_id in ranges.get(pid, []):
+                if st <= when < en and (tid is None or rtid == tid):
+                    self.db.execute("update kernel_dispatch set name_id = ? where id = ?", (name_id, kid))
+                    renamed += 1
+                    break
+        self.db.commit()
+        return renamed
+
     def keep_window(self, delay_ms: float, duration_ms: float) -> int:
         """Keeps only what started within ``duration_ms`` after ``delay_ms`` from the first record; returns rows deleted."""
         starts = [r[0] for r in (self.db.execute("select min(start_ns) from kernel_dispatch").fetchone(), self.db.execute("select min(start_ns) from region").fetchone(),

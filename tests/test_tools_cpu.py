@@ -656,3 +656,35 @@ assert res['skipped'] == [] and t2.groups['pair'] == [1, 3] and t2.field_groups[
 print('ok')
 """, {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "4"})
     assert "ok" in out
+
+
+def test_kernels_renamed_after_the_marker_range_they_were_launched_in(tmp_path):
+    from rocm_systems_b200.tools import tracedb
+
+    api_csv = '''"Domain","Function","Process_Id","Thread_Id","Correlation_Id","Start_Timestamp","End_Timestamp"
+"CUDA_RUNTIME_API","cudaLaunchKernel",100,100,1,600,610
+"CUDA_RUNTIME_API","cudaLaunchKernel",100,100,2,700,710
+"CUDA_RUNTIME_API","cudaLaunchKernel",100,200,3,800,810
+'''
+    marks = '''"Domain","Function","Process_Id","Thread_Id","Correlation_Id","Start_Timestamp","End_Timestamp","Depth"
+"MARKER_API","step 0",100,100,1,500,20000,0
+"MARKER_API","attention",100,100,2,650,750,1
+'''
+    (tmp_path / "t.100_kernel_trace.csv").write_text(KERNEL_CSV)
+    (tmp_path / "t.100_runtime_trace.csv").write_text(api_csv)
+    (tmp_path / "t.markers.100.csv").write_text(marks)
+    with tracedb.TraceDB(str(tmp_path / "t.db")) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        assert db.rename_kernels_by_marker() == 2
+        _, rows = db.query("select name from kernels order by start_ns")
+        # launched at 600 in "step 0"; at 700 inside the nested "attention"; the third from another thread, outside every range of that thread
+        assert [r[0] for r in rows] == ["step 0", "attention", "rmsnorm"]
+    # without API records the device start time decides (1000, 6000 and 9500 all lie inside "step 0" only)
+    (tmp_path / "t.100_runtime_trace.csv").unlink()
+    with tracedb.TraceDB(str(tmp_path / "u.db")) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        assert db.rename_kernels_by_marker() == 3
+        names, rows = db.query("select name, calls from top_kernels")
+        assert rows == [("step 0", 3)]
