@@ -688,3 +688,48 @@ def test_kernels_renamed_after_the_marker_range_they_were_launched_in(tmp_path):
         assert db.rename_kernels_by_marker() == 3
         names, rows = db.query("select name, calls from top_kernels")
         assert rows == [("step 0", 3)]
+
+
+def test_sweep_helpers_sizes_and_bus_bandwidth_factors():
+    """The pure parts of the bandwidth sweep: size suffixes, and the bus-bandwidth factors of the rccl-tests harness
+    (all_reduce 2(n-1)/n; all_gather, reduce_scatter, alltoall (n-1)/n; rooted collectives 1)."""
+    from rocm_systems_b200.bench import coll_sweep as cs
+
+    assert [cs.parse_size(s) for s in ("8", "64K", "1M", "8G", "1.5k")] == [8, 65536, 1 << 20, 8 << 30, 1536]
+    assert cs.busbw_factor("all_reduce", 8) == 1.75 and cs.busbw_factor("all_reduce", 2) == 1.0
+    for c in ("all_gather", "reduce_scatter", "alltoall"):
+        assert cs.busbw_factor(c, 8) == 0.875 and cs.busbw_factor(c, 2) == 0.5
+    assert cs.busbw_factor("broadcast", 8) == 1.0 and cs.busbw_factor("reduce", 4) == 1.0
+
+
+def test_headline_summary_of_a_sweep(monkeypatch):
+    """``headline.collectives_vs_nccl`` condenses sweep rows into what the benchmark line carries: the size ladder, per
+    collective the ratio at every size, its minimum with the size it occurs at, the geometric mean and the bus bandwidth
+    of both libraries at the largest size."""
+    import math
+
+    import torch
+
+    from rocm_systems_b200.bench import coll_sweep, headline
+
+    def fake_sweep(comm, colls, sizes, dt, send, recv, warmup, iters, nccl=True):
+        rows = []
+        for c in colls:
+            for i, s in enumerate(sizes):
+                ours = 10.0 + i
+                rows.append({"coll": c, "bytes": s, "ours_us": ours, "nccl_us": ours * (0.5 if (c == "broadcast" and i == 1) else 2.0),
+                             "ours_busbw": 100.0 + i, "nccl_busbw": 50.0 + i})
+        return rows
+
+    monkeypatch.setattr(coll_sweep, "sweep", fake_sweep)
+    monkeypatch.setattr(torch, "empty", lambda *a, **k: type("T", (), {"normal_": lambda self: self})())
+
+    class Comm:
+        device = "cpu"
+
+    out = headline.collectives_vs_nccl(Comm(), max_bytes=1 << 14, min_bytes=1 << 10, factor=4, colls=("all_reduce", "broadcast"))
+    assert out["sizes_bytes"] == [1024, 4096, 16384]
+    ar, bc = out["per_collective"]["all_reduce"], out["per_collective"]["broadcast"]
+    assert ar["ratios"] == [2.0, 2.0, 2.0] and ar["min_ratio_vs_nccl"] == 2.0 and abs(ar["geomean_ratio_vs_nccl"] - 2.0) < 1e-12
+    assert bc["min_ratio_vs_nccl"] == 0.5 and bc["min_ratio_at_bytes"] == 4096 and abs(bc["geomean_ratio_vs_nccl"] - math.exp((2 * math.log(2) + math.log(0.5)) / 3)) < 1e-12
+    assert ar["busbw_gbs_at_max"] == 102.0 and ar["nccl_busbw_gbs_at_max"] == 52.0
