@@ -127,6 +127,10 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--pmc-skip", type=int, default=0, help="matching launches to skip first")
     g.add_argument("--pmc-dry-run", action="store_true", help="print the Nsight Compute command line and stop")
     g.add_argument("--list-pmc", action="store_true", help="list the derived counters and stop")
+    g = ap.add_argument_group("job files")
+    g.add_argument("-i", "--input", default="", metavar="FILE",
+                   help="YAML or JSON file with a list `jobs:`; each job is a set of this launcher's options (long names, dashes or underscores), "
+                        "run as a pass of its own into <output-directory>/pass_<n>/ with the options of the command line as defaults")
     g = ap.add_argument_group("tools")
     g.add_argument("--tool-library", action="append", default=[], help="extra dispatch-table tool(s) to load into the communication library")
     ap.add_argument("command", nargs=argparse.REMAINDER, help="-- command to run")
@@ -181,8 +185,67 @@ def write_counter_collection(cs, kernels, peaks: dict, path: str) -> int:
     return n
 
 
+def load_jobs(path: str) -> List[dict]:
+    """The jobs of an input file (the reference launcher's --input: several differently configured passes over one command)."""
+    text = Path(path).read_text()
+    if path.endswith(".json"):
+        doc = json.loads(text)
+    else:
+        import yaml
+
+        doc = yaml.safe_load(text)
+    jobs = doc.get("jobs") if isinstance(doc, dict) else doc
+    if not isinstance(jobs, list) or not all(isinstance(j, dict) for j in jobs) or not jobs:
+        raise ValueError(f"{path}: expected a non-empty list `jobs:` of option mappings")
+    return jobs
+
+
+def job_argv(job: dict) -> List[str]:
+    """One job as command-line words: `kernel_trace: true` -> --kernel-trace, `pmc: [a, b]` -> --pmc a b, `top: 5` -> --top 5."""
+    out: List[str] = []
+    for key, val in job.items():
+        flag = "--" + str(key).replace("_", "-")
+        if isinstance(val, bool):
+            if val:
+                out.append(flag)
+        elif isinstance(val, (list, tuple)):
+            out += [flag, *[str(v) for v in val]]
+        elif val is not None:
+            out += [flag, str(val)]
+    return out
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
     a = parser().parse_args(argv)
+    if a.input:
+        try:
+            jobs = load_jobs(a.input)
+        except (OSError, ValueError) as e:
+            print(f"prof: {e}", file=sys.stderr)
+            return 2
+        split = argv.index("--") if "--" in argv else len(argv)
+        head, tail = argv[:split], argv[split:]
+        drop, keep = {"-i", "--input"}, []
+        skip = False
+        for w in head:          # the command line without the job file itself
+            if skip:
+                skip = False
+                continue
+            if w in drop:
+                skip = True
+                continue
+            if w.startswith("--input="):
+                continue
+            keep.append(w)
+        worst = 0
+        for n, job in enumerate(jobs):
+            words = job_argv({k: v for k, v in job.items() if k not in ("output_directory", "output-directory")})
+            outdir = str(Path(job.get("output_directory", job.get("output-directory", a.output_directory))) / f"pass_{n}")
+            print(f"prof: pass {n}: {' '.join(words) or '(defaults)'} -> {outdir}", file=sys.stderr)
+            rc = main([*keep, *words, "-d", outdir, *tail])
+            worst = worst or rc
+        return worst
     cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
     if a.list_pmc:
         from . import counters

@@ -733,3 +733,22 @@ def test_headline_summary_of_a_sweep(monkeypatch):
     assert ar["ratios"] == [2.0, 2.0, 2.0] and ar["min_ratio_vs_nccl"] == 2.0 and abs(ar["geomean_ratio_vs_nccl"] - 2.0) < 1e-12
     assert bc["min_ratio_vs_nccl"] == 0.5 and bc["min_ratio_at_bytes"] == 4096 and abs(bc["geomean_ratio_vs_nccl"] - math.exp((2 * math.log(2) + math.log(0.5)) / 3)) < 1e-12
     assert ar["busbw_gbs_at_max"] == 102.0 and ar["nccl_busbw_gbs_at_max"] == 52.0
+
+
+def test_profiler_launcher_job_file(tmp_path):
+    """``prof --input jobs.yaml``: every job is a pass of its own with the command line as defaults."""
+    from rocm_systems_b200.tools import prof
+
+    assert prof.job_argv({"kernel_trace": True, "coll-trace": False, "pmc": ["hbm_gbs", "tflops"], "top": 5, "kernel_include_regex": "gemm"}) == \
+        ["--kernel-trace", "--pmc", "hbm_gbs", "tflops", "--top", "5", "--kernel-include-regex", "gemm"]
+    (tmp_path / "jobs.yaml").write_text("jobs:\n  - marker_trace: true\n    stats: true\n  - marker_trace: true\n    output_format: [json]\n    output_file: second\n")
+    child = "from rocm_systems_b200.utils import markers\nwith markers.range('phase'):\n    markers.mark('tick')\n"
+    e = dict(os.environ, PYTHONPATH=str(ROOT))
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "-i", str(tmp_path / "jobs.yaml"), "-d", str(tmp_path / "o"), "--",
+                        sys.executable, "-c", child], env=e, capture_output=True, text=True, timeout=180)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert (tmp_path / "o" / "pass_0" / "trace.db").exists() and (tmp_path / "o" / "pass_0" / "trace_regions.csv").exists()
+    assert (tmp_path / "o" / "pass_1" / "second.json").exists() and not (tmp_path / "o" / "pass_1" / "second.db").exists()
+    assert "MARKER_API" in p.stdout and "pass 1" in p.stderr
+    (tmp_path / "bad.json").write_text('{"jobs": []}')
+    assert prof.main(["-i", str(tmp_path / "bad.json"), "--", "true"]) == 2
