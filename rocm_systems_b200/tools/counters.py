@@ -28,6 +28,7 @@ panels of derived metrics per dispatch): the counters grouped by panel, the warp
 verdict on what bounds the launch:
 
     python -m rocm_systems_b200.tools.counters prof.ncu-rep --analyze --peaks MEASURED_PEAKS.json
+    python -m rocm_systems_b200.tools.counters before.ncu-rep --compare after.ncu-rep --min-change 5 --kernel-filter gemm
 
 The capture never locks the GPU's clocks (``--clock-control none``) and is bounded by ``-k`` / ``-c``; ``--print-command``
 shows the ``ncu`` line without running anything.
@@ -294,6 +295,47 @@ def analyze(cs: "CounterSet", kernels, peaks: dict, args: dict) -> List[dict]:
     return out
 
 
+def compare(cs: "CounterSet", base, other, peaks: dict, args: dict) -> List[dict]:
+    """Two captures of the same program side by side (the reference's analyze mode with a baseline path): launches are
+    paired by kernel name in order of appearance (the i-th launch of a name in one capture with the i-th in the other);
+    every counter both could evaluate is listed with its value in each and the relative change."""
+    def by_name(kernels):
+        seen: Dict[str, int] = {}
+        out = {}
+        for k in kernels:
+            i = seen.get(k.name, 0)
+            seen[k.name] = i + 1
+            out[(k.name, i)] = k
+        return out
+
+    a, b = by_name(base), by_name(other)
+    rows = []
+    for key in a:
+        if key not in b:
+            continue
+        va, vb = cs.evaluate(dict(a[key].raw), peaks, args), cs.evaluate(dict(b[key].raw), peaks, args)
+        counters_ = []
+        for d in cs.defs:
+            x, y = va.get(d["name"]), vb.get(d["name"])
+            if x is None or y is None or x != x or y != y:
+                continue
+            counters_.append({"name": d["name"], "unit": d.get("unit", ""), "base": x, "other": y, "change_pct": (y - x) / abs(x) * 100 if x else None})
+        rows.append({"kernel": key[0], "launch": key[1], "counters": counters_})
+    return rows
+
+
+def format_comparison(rows: Sequence[dict], threshold_pct: float = 0.0) -> str:
+    lines = []
+    for r in rows:
+        lines.append(f"== {r['kernel']} (launch {r['launch']})")
+        for c in r["counters"]:
+            ch = c["change_pct"]
+            if ch is not None and abs(ch) < threshold_pct:
+                continue
+            lines.append(f"     {c['name']:<30} {c['base']:>12.4g} -> {c['other']:>12.4g} {c['unit']:<24} {'' if ch is None else f'{ch:+.1f} %'}")
+    return "\n".join(lines)
+
+
 def format_analysis(items: Sequence[dict]) -> str:
     lines = []
     for it in items:
@@ -320,6 +362,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--arg", action="append", default=[], help="NAME=VALUE readable as arg.NAME")
     ap.add_argument("--list", action="store_true", help="print the definitions and the raw metrics they need")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--compare", default="", metavar="OTHER", help="a second report or CSV of the same program: counters of matching launches side by side with the change")
+    ap.add_argument("--min-change", type=float, default=0.0, metavar="PCT", help="with --compare: only counters that changed by at least this much")
+    ap.add_argument("--kernel-filter", default="", metavar="REGEX", help="with --analyze / --compare: only launches whose kernel name matches")
     ap.add_argument("--analyze", action="store_true", help="per launch: the counters grouped by panel (speed of light, memory, caches, compute, "
                     "occupancy, launch), the warp stall ranking and a one-line verdict on what bounds it")
     ap.add_argument("--collect", action="store_true", help="run the command after -- under Nsight Compute for the metrics the counters need, then evaluate")
@@ -370,8 +415,15 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         for k in roofline.read_ncu(path):
             raw = dict(k.raw) if hasattr(k, "raw") else {}
             rows.append({"kernel": k.name, **cs.evaluate(raw, peaks, args)})
+    keep = (lambda ks: [k for k in ks if re.search(a.kernel_filter, k.name)]) if a.kernel_filter else (lambda ks: list(ks))
+    if a.compare:
+        if len(a.inputs) != 1:
+            ap.error("--compare takes exactly one input to compare OTHER with")
+        rows_ = compare(cs, keep(roofline.read_ncu(a.inputs[0])), keep(roofline.read_ncu(a.compare)), peaks, args)
+        print(json.dumps(rows_, indent=1) if a.json else format_comparison(rows_, a.min_change))
+        return 0
     if a.analyze:
-        items = [it for path in a.inputs for it in analyze(cs, roofline.read_ncu(path), peaks, args)]
+        items = [it for path in a.inputs for it in analyze(cs, keep(roofline.read_ncu(path)), peaks, args)]
         print(json.dumps(items, indent=1) if a.json else format_analysis(items))
         return 0
     if a.json:

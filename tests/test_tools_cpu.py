@@ -752,3 +752,25 @@ def test_profiler_launcher_job_file(tmp_path):
     assert "MARKER_API" in p.stdout and "pass 1" in p.stderr
     (tmp_path / "bad.json").write_text('{"jobs": []}')
     assert prof.main(["-i", str(tmp_path / "bad.json"), "--", "true"]) == 2
+
+
+def test_counter_comparison_of_two_captures(tmp_path, capsys):
+    from rocm_systems_b200.tools import counters
+
+    base = _analyze_csv()
+    rows = [list(r) for r in ANALYZE_ROWS]
+    rows[0][1] = "80"          # streamKernel: 100 us -> 80 us
+    rows[1][7] = "90"          # mmaKernel: tensor pipe 82 -> 90 %
+    q = lambda cells: ",".join(f'"{c}"' for c in cells)  # noqa: E731
+    other = "\n".join([q([c for c, _ in ANALYZE_COLS]), q([u for _, u in ANALYZE_COLS])] + [q(r) for r in rows]) + "\n"
+    (tmp_path / "a.csv").write_text(base)
+    (tmp_path / "b.csv").write_text(other)
+    (tmp_path / "p.json").write_text('{"hbm_gbs": 6650.0, "bf16_tflops": 1600.0}')
+    assert counters.main([str(tmp_path / "a.csv"), "--compare", str(tmp_path / "b.csv"), "--peaks", str(tmp_path / "p.json"), "--json"]) == 0
+    res = {r["kernel"]: {c["name"]: c for c in r["counters"]} for r in json.loads(capsys.readouterr().out)}
+    assert abs(res["streamKernel"]["duration_us"]["change_pct"] + 20.0) < 1e-9 and abs(res["streamKernel"]["hbm_gbs"]["change_pct"] - 25.0) < 1e-9
+    assert abs(res["mmaKernel"]["tensor_active_pct"]["other"] - 90.0) < 1e-9 and res["waitKernel"]["duration_us"]["change_pct"] == 0
+    assert counters.main([str(tmp_path / "a.csv"), "--compare", str(tmp_path / "b.csv"), "--peaks", str(tmp_path / "p.json"), "--min-change", "5",
+                          "--kernel-filter", "stream"]) == 0
+    text = capsys.readouterr().out
+    assert "== streamKernel" in text and "mmaKernel" not in text and "duration_us" in text and "dram_read_mb" not in text
