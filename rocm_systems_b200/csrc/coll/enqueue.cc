@@ -10,6 +10,15 @@
 
 namespace b200 {
 
+// Flag-in-data kernels: up to 16 CTAs for the latency-bound sizes; beyond that one per 16 KiB of the message past 256 KiB,
+// or one per 64 KiB of lines a rank stores into its peers (2 x bytes x (n - 1): between eight ranks a CTA of a 256 KiB
+// all-reduce would otherwise store 224 KiB of lines by itself), whichever is more, up to 64.
+int llCtaCap(size_t bytes, int nranks) {
+  const int bySize = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
+  const size_t stored = bytes * 2 * (size_t)std::max(1, nranks - 1);
+  return std::max(bySize, (int)std::min<size_t>(64, stored >> 16));
+}
+
 namespace {
 
 struct DeviceGuard {
@@ -61,15 +70,6 @@ ncclResult_t resolveOp(Comm* c, int op, ncclDataType_t dt, ResolvedOp* out) {
   out->devPtr = pm.devPtr;
   out->bits = pm.bits;
   return ncclSuccess;
-}
-
-// Flag-in-data kernels: up to 16 CTAs for the latency-bound sizes; beyond that one per 16 KiB of the message past 256 KiB,
-// or one per 64 KiB of lines a rank stores into its peers (2 x bytes x (n - 1): between eight ranks a CTA of a 256 KiB
-// all-reduce would otherwise store 224 KiB of lines by itself), whichever is more, up to 64.
-int llCtaCap(size_t bytes, int nranks) {
-  const int bySize = bytes <= (256u << 10) ? 16 : std::min(64, std::max(16, (int)(bytes >> 14)));
-  const size_t stored = bytes * 2 * (size_t)std::max(1, nranks - 1);
-  return std::max(bySize, (int)std::min<size_t>(64, stored >> 16));
 }
 
 int ctasFor(const Comm* c, size_t bytes, int algo) {

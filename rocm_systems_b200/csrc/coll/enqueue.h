@@ -36,6 +36,7 @@ struct P2pReq {
 ncclResult_t enqueueP2pGroup(Comm* c, std::vector<P2pReq>& ops);
 // All-to-all of chunks small enough for the flag-in-data buffers (llAllToAllFits), as one kernel.
 bool llAllToAllFits(Comm* c, size_t bytesPerPeer);
+int llCtaCap(size_t bytes, int nranks);
 // All-to-all of large chunks through the staging halves (peer stores, one barrier per step), as one kernel.
 void stagedAllToAllArgs(Comm* c, const void* send, void* recv, size_t count, ncclDataType_t dt, int forceCtas, CollArgs* args, DevComm* dc, int* ctas);
 ncclResult_t enqueueStagedAllToAll(Comm* c, int apiId, const void* send, void* recv, size_t count, ncclDataType_t dt, cudaStream_t stream);

@@ -814,9 +814,9 @@ extern "C" {
 // a multicast alias, without any device or peer: the algorithm (1 flag-in-data, 2 peer loads, 3 in-switch),
 // CTAs, whether the zero-copy path applies (never here: the buffers are not in a window) and the number of
 // pipeline chunks. Honours the environment and the tuning file exactly as a real communicator does.
-// `kind`: 0 all-reduce, 1 reduce-scatter, 2 reduce, 3 all-gather, 4 broadcast.
+// `kind`: 0 all-reduce, 1 reduce-scatter, 2 reduce, 3 all-gather, 4 broadcast, 5 all-to-all (count per pair; algorithm 4 = send/recv FIFOs).
 ncclResult_t b200collPlanDry(int nranks, int nvls, int kind, size_t count, ncclDataType_t dt, ncclRedOp_t op, b200collPlanInfo* out) {
-  if (!out || nranks < 1 || nranks > kMaxRanks || kind < 0 || kind > COLL_BROADCAST || (int)dt < 0 || (int)dt >= ncclNumTypes)
+  if (!out || nranks < 1 || nranks > kMaxRanks || kind < 0 || kind > COLL_ALLTOALL || (int)dt < 0 || (int)dt >= ncclNumTypes)
     BFAIL(ncclInvalidArgument, "b200collPlanDry: bad argument");
   const Flags& fl = Flags::get();
   auto c = std::make_unique<Comm>();
@@ -832,6 +832,28 @@ ncclResult_t b200collPlanDry(int nranks, int nvls, int kind, size_t count, ncclD
   if (c->maxCtas > kMaxCtas) c->maxCtas = kMaxCtas;
   if (c->minCtas > c->maxCtas) c->minCtas = c->maxCtas;
   loadTuning(c.get());
+  if (kind == COLL_ALLTOALL) {
+    // `count` elements per pair, as ncclAllToAll decides (ordinary buffers): 1 flag-in-data kernel, 2 staged kernel by peer
+    // stores (chunks = its steps), 4 grouped send/recv over the FIFOs.
+    const size_t chunk = count * dtypeSize(dt);
+    out->direct = 0;
+    if (nranks == 1 || chunk == 0) {
+      out->algo = ALGO_P2P; out->ctas = 1; out->chunks = 1;
+    } else if (llAllToAllFits(c.get(), chunk)) {
+      out->algo = ALGO_LL;
+      out->ctas = std::max(1, std::min((int)((chunk / 8 + kCollThreads - 1) / kCollThreads), std::min(llCtaCap(chunk, nranks), std::max(16, c->maxCtas))));
+      out->chunks = 0;
+    } else if (fl.a2aStagedMin >= 0 ? chunk >= (size_t)fl.a2aStagedMin : chunk >= ((size_t)1 << 20)) {
+      CollArgs args;
+      DevComm dc;
+      int ctas = 0;
+      stagedAllToAllArgs(c.get(), nullptr, nullptr, count, dt, 0, &args, &dc, &ctas);
+      out->algo = ALGO_P2P; out->ctas = ctas; out->chunks = c->stageParity;
+    } else {
+      out->algo = 4; out->ctas = 0; out->chunks = (chunk + fl.p2pChunkBytes - 1) / fl.p2pChunkBytes;
+    }
+    return ncclSuccess;
+  }
   CollReq r{};
   r.kind = kind;
   r.send = reinterpret_cast<const void*>(0x10000);  // never dereferenced on the host; aligned, outside any window

@@ -15,8 +15,8 @@ from typing import Optional, Sequence
 
 from .. import _lib
 
-COLLS = {"all_reduce": 0, "reduce_scatter": 1, "reduce": 2, "all_gather": 3, "broadcast": 4}
-ALGOS = {1: "flag-in-data", 2: "peer loads", 3: "in-switch"}
+COLLS = {"all_reduce": 0, "reduce_scatter": 1, "reduce": 2, "all_gather": 3, "broadcast": 4, "alltoall": 5}
+ALGOS = {1: "flag-in-data", 2: "peer loads/stores", 3: "in-switch", 4: "send/recv FIFOs"}
 DTYPES = {"int8": (0, 1), "uint8": (1, 1), "int32": (2, 4), "uint32": (3, 4), "int64": (4, 8), "uint64": (5, 8), "half": (6, 2), "float": (7, 4),
           "double": (8, 8), "bfloat16": (9, 2)}
 OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "avg": 4}
@@ -52,7 +52,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     a = ap.parse_args(argv)
     es = DTYPES[a.dtype][1]
     size, top = _size(a.minbytes), _size(a.maxbytes)
-    print(f"# {a.coll}, {a.nranks} ranks, {a.dtype} {a.op}, multicast {'no' if a.no_nvls else 'yes'}; bytes are per-rank counts for all_gather / reduce_scatter")
+    print(f"# {a.coll}, {a.nranks} ranks, {a.dtype} {a.op}, multicast {'no' if a.no_nvls else 'yes'}; bytes are per-rank counts for all_gather / reduce_scatter and per pair for alltoall")
     print(f"{'bytes':>14}  {'algorithm':<14} {'CTAs':>5} {'chunks':>7}")
     while size <= top:
         p = plan(a.nranks, not a.no_nvls, a.coll, max(1, size // es), a.dtype, a.op)

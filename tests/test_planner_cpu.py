@@ -141,3 +141,25 @@ def test_planner_invariants_over_random_messages():
         r = plan([[8, 1, kind, s, F32, SUM] for s in sizes])
         chunk_counts = [x[4] for x in r]
         assert chunk_counts == sorted(chunk_counts) and chunk_counts[-1] > 1
+
+
+def test_all_to_all_takes_one_of_three_paths():
+    """ncclAllToAll on ordinary buffers, by bytes per pair: the flag-in-data kernel up to the slice limit, the staged kernel by peer
+    stores from 1 MiB (steps = slots of a staging half), the send/recv FIFOs in between; the switch moves with the environment."""
+    A2A, FIFO = 5, 4
+    MiB = 1 << 20
+    r = plan([
+        [8, 1, A2A, 64 * 1024, F32, SUM],          # 256 KiB per pair between eight ranks: flag-in-data
+        [8, 1, A2A, 64 * 1024 + 4, F32, SUM],      # just above: FIFOs
+        [8, 1, A2A, MiB // 4, F32, SUM],           # 1 MiB per pair: staged
+        [8, 1, A2A, 64 * MiB // 4, F32, SUM],      # 64 MiB per pair: 8 MiB slots -> 8 steps
+        [2, 1, A2A, 2 * MiB // 4, F32, SUM],       # two ranks: flag-in-data up to 2 MiB per pair
+        [2, 1, A2A, 64 * MiB // 4, F32, SUM],      # 32 MiB slots -> 2 steps
+    ])
+    assert [x[0] for x in r] == [0] * 6
+    assert [x[1] for x in r] == [LL, FIFO, P2P, P2P, LL, P2P]
+    assert [x[4] for x in r] == [0, 1, 1, 8, 0, 2]
+    off = plan([[8, 1, A2A, 64 * MiB // 4, F32, SUM]], {"B200COLL_A2A_STAGED_MIN": "1G"})[0]
+    assert off[1] == FIFO and off[4] == 128      # 512 KiB FIFO slots
+    always = plan([[8, 1, A2A, 64 * 1024 + 4, F32, SUM]], {"B200COLL_A2A_STAGED_MIN": "0"})[0]
+    assert always[1] == P2P
