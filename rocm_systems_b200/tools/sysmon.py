@@ -1,5 +1,6 @@
-"""Background system sampler: GPU readings (through NVML), host CPU and memory, and the resident
-set of chosen processes, on the same clock as the tracers, written as counter tracks.
+"""Background system sampler: GPU readings (through NVML), host CPU utilisation, frequency, load and memory, and per chosen
+process its resident set, CPU utilisation, thread count, page faults and context switches, on the same clock as the tracers,
+written as counter tracks.
 
 The counterpart of the reference's process sampler in its system profiler (rocprofiler-systems:
 background thread reading amd-smi, CPU frequency and memory while the application runs, shown as
@@ -46,6 +47,62 @@ def _rss(pid: int) -> Optional[int]:
     return None
 
 
+def _cpu_freq_mhz() -> Optional[float]:
+    """Mean current frequency of the host CPUs (cpufreq when the kernel exposes it, else the `cpu MHz` lines of /proc/cpuinfo)."""
+    import glob
+
+    vals = []
+    for path in glob.glob("/sys/devices/system/cpu/cpu[0-9]*/cpufreq/scaling_cur_freq"):
+        try:
+            with open(path) as f:
+                vals.append(int(f.read()) / 1000.0)
+        except (OSError, ValueError):
+            pass
+    if not vals:
+        try:
+            with open("/proc/cpuinfo") as f:
+                vals = [float(line.split(":")[1]) for line in f if line.lower().startswith("cpu mhz")]
+        except (OSError, ValueError):
+            vals = []
+    return sum(vals) / len(vals) if vals else None
+
+
+def _loadavg() -> Optional[float]:
+    try:
+        with open("/proc/loadavg") as f:
+            return float(f.read().split()[0])
+    except (OSError, ValueError):
+        return None
+
+
+def _proc_stat(pid: int) -> Optional[Dict[str, int]]:
+    """CPU ticks (user + system), page faults and thread count of a process from /proc/<pid>/stat."""
+    try:
+        with open(f"/proc/{pid}/stat") as f:
+            text = f.read()
+    except OSError:
+        return None
+    rest = text[text.rfind(")") + 2:].split()     # the command may contain spaces and parentheses: fields start behind the last ')'
+    try:
+        return {"minflt": int(rest[7]), "majflt": int(rest[9]), "ticks": int(rest[11]) + int(rest[12]), "threads": int(rest[17])}
+    except (IndexError, ValueError):
+        return None
+
+
+def _proc_ctx_switches(pid: int) -> Optional[Tuple[int, int]]:
+    try:
+        vol = invol = None
+        with open(f"/proc/{pid}/status") as f:
+            for line in f:
+                if line.startswith("voluntary_ctxt_switches:"):
+                    vol = int(line.split()[1])
+                elif line.startswith("nonvoluntary_ctxt_switches:"):
+                    invol = int(line.split()[1])
+        return (vol, invol) if vol is not None and invol is not None else None
+    except (OSError, ValueError):
+        return None
+
+
 class SystemSampler:
     """Background thread that samples GPU readings (NVML) and host counters at a fixed period; a context manager."""
 
@@ -56,6 +113,7 @@ class SystemSampler:
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self.gpu_fields = list(gpu_fields)
+        self._last_proc: Dict[int, Tuple[int, int]] = {}   # pid -> (monotonic ns, cpu ticks) of the previous sample
         self.smi = None
         self.ngpu = 0
         if gpu:
@@ -78,10 +136,32 @@ class SystemSampler:
         mem = _meminfo()
         if mem:
             self.samples.append(("host_mem_used_bytes", -1, now, float(mem.get("MemTotal", 0) - mem.get("MemAvailable", 0))))
+        freq = _cpu_freq_mhz()
+        if freq is not None:
+            self.samples.append(("host_cpu_freq_mhz", -1, now, freq))
+        load = _loadavg()
+        if load is not None:
+            self.samples.append(("host_load_1min", -1, now, load))
         for pid in self.pids:
             r = _rss(pid)
             if r is not None:
                 self.samples.append(("process_rss_bytes", pid, now, float(r)))
+            st = _proc_stat(pid)
+            if st is not None:
+                self.samples.append(("process_threads", pid, now, float(st["threads"])))
+                self.samples.append(("process_page_faults_minor", pid, now, float(st["minflt"])))
+                self.samples.append(("process_page_faults_major", pid, now, float(st["majflt"])))
+                last = self._last_proc.get(pid)
+                if last is not None and now > last[0]:
+                    import os
+
+                    hz = os.sysconf("SC_CLK_TCK") or 100
+                    self.samples.append(("process_cpu_util_percent", pid, now, 100.0 * (st["ticks"] - last[1]) / hz / ((now - last[0]) / 1e9)))
+                self._last_proc[pid] = (now, st["ticks"])
+            cs = _proc_ctx_switches(pid)
+            if cs is not None:
+                self.samples.append(("process_ctx_switches_voluntary", pid, now, float(cs[0])))
+                self.samples.append(("process_ctx_switches_involuntary", pid, now, float(cs[1])))
         if self.smi is not None:
             for d in range(self.ngpu):
                 for f in self.gpu_fields:

@@ -774,3 +774,31 @@ def test_counter_comparison_of_two_captures(tmp_path, capsys):
                           "--kernel-filter", "stream"]) == 0
     text = capsys.readouterr().out
     assert "== streamKernel" in text and "mmaKernel" not in text and "duration_us" in text and "dram_read_mb" not in text
+
+
+def test_system_sampler_host_and_process_counters(tmp_path):
+    """Without NVML the sampler still records the host (utilisation, frequency, load, memory) and, per watched process,
+    resident set, CPU utilisation, threads, page faults and context switches."""
+    import threading
+
+    from rocm_systems_b200.tools import sysmon
+
+    st = sysmon._proc_stat(os.getpid())
+    assert st is not None and st["threads"] >= 1 and st["ticks"] >= 0 and st["minflt"] > 0
+    stop = threading.Event()
+    worker = threading.Thread(target=lambda: [sum(range(20000)) for _ in iter(lambda: stop.is_set(), True)])
+    worker.start()
+    with sysmon.SystemSampler(period_ms=30, pids=[os.getpid(), 2 ** 22 + 12345], gpu=False) as s:   # the second pid does not exist: skipped
+        import time
+
+        time.sleep(0.35)
+    stop.set()
+    worker.join()
+    names = {n for n, _, _, _ in s.samples}
+    assert {"host_cpu_util_percent", "host_mem_used_bytes", "host_load_1min", "process_rss_bytes", "process_threads", "process_cpu_util_percent",
+            "process_page_faults_minor", "process_ctx_switches_voluntary"} <= names
+    assert all(dev == os.getpid() for n, dev, _, _ in s.samples if n.startswith("process_"))
+    threads = [v for n, _, _, v in s.samples if n == "process_threads"]
+    assert max(threads) >= 2                                  # this thread and the worker at least
+    assert all(v >= 0 for n, _, _, v in s.samples if n == "process_cpu_util_percent")
+    assert s.write_csv(str(tmp_path / "s.csv")) == len(s.samples)
