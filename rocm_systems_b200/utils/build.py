@@ -148,6 +148,19 @@ def build_sampler() -> Path | None:
     return out
 
 
+def build_causal() -> Path | None:
+    """The causal profiler (preload library, plain C++, no CUDA)."""
+    src = CSRC / "prof" / "causal.cc"
+    if not src.exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200causal.so"
+    hdr = CSRC / "include" / "b200coll" / "causal.h"
+    if not out.exists() or out.stat().st_mtime_ns < max(src.stat().st_mtime_ns, hdr.stat().st_mtime_ns):
+        _run(["g++", "-O2", "-g", "-std=c++17", "-fPIC", "-shared", f"-I{CSRC / 'include'}", str(src), "-o", str(out), "-lpthread", "-ldl"])
+    return out
+
+
 def build_perf(verbose_ptxas: bool = False) -> list[Path]:
     """rccl-tests-style benchmark binaries (one per collective) linked against the library."""
     BIN.mkdir(exist_ok=True)
@@ -240,6 +253,8 @@ def build_all(verbose_ptxas: bool = False) -> dict:
     res["prof"] = str(prof) if prof else None
     samp = build_sampler()
     res["sampler"] = str(samp) if samp else None
+    causal = build_causal()
+    res["causal"] = str(causal) if causal else None
     ext = build_torch_ext()
     res["torch_ext"] = str(ext) if ext else None
     return res

@@ -1,0 +1,145 @@
+"""The causal profiler (csrc/prof/causal.cc, tools/causal.py) on a native program whose answer is known: every iteration
+runs ``cpu_slow_func`` and ``cpu_fast_func`` side by side and waits for both, the fast one doing 80 % of the slow one's
+work. Making the slow one 20 % faster must speed the program up by about 20 %, 30 % faster by no more (the fast one is
+the bound then), and making the fast one faster by nothing. This is the reference's own end-to-end validation
+(rocprofiler-systems tests/rocprof-sys-causal-tests.cmake: slow-func 10/20/30 -> 10/20/20, fast-func -> 0/0/0, checked by
+tests/validate-causal-json.py), on both ways the target hands work to its threads: threads created and joined per
+iteration, and a pool woken through a mutex and condition variables."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from rocm_systems_b200.tools import causal
+
+ROOT = Path(__file__).resolve().parent.parent
+LIB = ROOT / "rocm_systems_b200" / "lib" / "libb200causal.so"
+
+
+@pytest.fixture(scope="module")
+def target(tmp_path_factory):
+    from rocm_systems_b200.utils import build
+
+    assert build.build_causal() == LIB
+    exe = tmp_path_factory.mktemp("causal") / "causal_target"
+    subprocess.run(["g++", "-O1", "-g", "-std=c++17", f"-I{ROOT / 'rocm_systems_b200' / 'csrc' / 'include'}", "-o", str(exe),
+                    str(ROOT / "tests" / "native" / "causal_target.cc"), "-lpthread", "-ldl"], check=True)
+    return exe
+
+
+TEXT = "\n".join([
+    "startup\ttime=1",
+    "experiment\tselected=f\tspeedup=0.00\tduration=1000\tselected-samples=5\treal-duration=1000\tpaused=0",
+    "throughput-point\tname=it\tdelta=10",
+    "latency-point\tname=item\tarrivals=10\tdepartures=10\tdifference=0",
+    "experiment\tselected=f\tspeedup=0.00\tduration=1100\tselected-samples=5",
+    "throughput-point\tname=it\tdelta=10",
+    "experiment\tselected=f\tspeedup=0.50\tduration=800\tselected-samples=5\treal-duration=1200\tpaused=400",
+    "throughput-point\tname=it\tdelta=10",
+    "experiment\tselected=g\tspeedup=0.50\tduration=800\tselected-samples=5",     # no baseline for g: not reported
+    "throughput-point\tname=it\tdelta=10",
+    "runtime\ttime=99\tsamples=20",
+    "throughput-point\tname=stray\tdelta=1",                                       # outside an experiment: ignored
+])
+
+
+def test_parse_and_predictions():
+    ex = causal.parse(TEXT)
+    assert len(ex) == 4 and ex[2]["speedup"] == 50 and ex[2]["real_duration"] == 1200 and ex[1]["real_duration"] == 1100
+    assert ex[0]["latency"]["item"]["departures"] == 10 and "stray" not in ex[3]["throughput"]
+    res = causal.analyze(ex)
+    by = {(r["selected"], r["point"], r["kind"]): r for r in res}
+    assert set(by) == {("f", "it", "throughput"), ("f", "item", "latency")}
+    r = by[("f", "it", "throughput")]
+    assert r["baseline_period_ns"] == pytest.approx(105.0)
+    rows = {row["speedup"]: row for row in r["rows"]}
+    assert rows[0]["program_speedup"] == pytest.approx(0.0) and rows[0]["experiments"] == 2
+    assert rows[50]["program_speedup"] == pytest.approx(100 * (1 - 80 / 105))
+    assert r["impact"] == pytest.approx(0.5 * rows[50]["program_speedup"])            # area under the curve per unit of speed-up
+    assert causal.analyze(ex, point="nope") == []
+    assert causal.analyze(ex, min_experiments=2)[0]["rows"][-1]["speedup"] == 0      # the single run at 50 % is dropped
+    assert "f  [throughput point: it]" in causal.format_report(res)
+    assert causal.validate(res, [("f", "it", 50, 24.0, 2.0)]) == []
+    assert len(causal.validate(res, [("f", "it", 50, 60.0, 2.0), ("f", "it", 70, 0.0, 2.0)])) == 2
+
+
+def test_end_to_end_plan_and_environment(tmp_path):
+    ap_args = ["run", "-o", str(tmp_path / "x.coz"), "-e", "-n", "2", "-s", "0", "20", "-F", "^a$", "^b$", "--", "prog"]
+    import argparse  # noqa: F401
+
+    captured = {}
+    real_run = causal.cmd_run
+    try:
+        causal.cmd_run = lambda a: captured.setdefault("a", a) and 0
+        causal.main(ap_args)
+    finally:
+        causal.cmd_run = real_run
+    a = captured["a"]
+    jobs = causal.plan(a)
+    assert len(jobs) == 2 * 2 * 2 and {j["function"] for j in jobs} == {"^a$", "^b$"} and {j["speedup"] for j in jobs} == {0, 20}
+    env = causal.environment(a, 20, "^a$")
+    assert env["B200CAUSAL_END_TO_END"] == "1" and env["B200CAUSAL_FIXED_SPEEDUP"] == "20" and env["B200CAUSAL_FUNCTION_SCOPE"] == "^a$"
+    assert env["LD_PRELOAD"].split(":")[0] == str(LIB) and env["B200CAUSAL_FILE"].endswith("x.coz")
+    a.end_to_end = False
+    assert causal.plan(a) == [{"speedup": None, "function": None}] * 2
+
+
+def _spread_ok(results):
+    """A loaded machine shows as a wide spread of the baseline; then the numbers mean nothing either way."""
+    return all(r["baseline_stddev"] < 6.0 for r in results)
+
+
+def test_end_to_end_predictions_match_the_known_answer(target, tmp_path):
+    out = tmp_path / "e2e.coz"
+    rc = causal.main(["run", "-o", str(out), "-e", "-n", "2", "-s", "0", "20", "30", "-F", "^cpu_slow_func$", "^cpu_fast_func$", "--",
+                      str(target), "24", "80", "4000000", "spawn"])
+    assert rc == 0
+    ex = causal.parse(out.read_text())
+    assert len(ex) == 12 and {e["selected"] for e in ex} == {"cpu_slow_func", "cpu_fast_func"}
+    assert all(e["throughput"]["iteration"] == 24 and e["latency"]["item"]["departures"] == 24 for e in ex)
+    assert all(e["selected_samples"] > 20 for e in ex)
+    assert all((e["real_duration"] > e["duration"]) == (e["speedup"] > 0) for e in ex)   # pauses only when something is sped up
+    res = causal.analyze(ex, point="iteration")
+    if not _spread_ok(res):
+        pytest.skip("baseline runs differ by more than 6 %: the machine is busy")
+    bad = causal.validate(res, [("cpu_slow_func", "iteration", 20, 20.0, 7.0), ("cpu_slow_func", "iteration", 30, 20.0, 8.0),
+                                ("cpu_fast_func", "iteration", 20, 0.0, 7.0), ("cpu_fast_func", "iteration", 30, 0.0, 7.0)])
+    assert bad == [], causal.format_report(res)
+    # The report command on the same file, with the checks as arguments.
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.causal", "report", str(out), "--point", "iteration", "--validate",
+                        "cpu_slow_func", "iteration", "20", "20", "9"], capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0 and "cpu_slow_func  [throughput point: iteration]" in r.stdout, r.stdout + r.stderr
+
+
+def test_experiments_drawn_while_a_thread_pool_runs(target, tmp_path):
+    out = tmp_path / "pool.coz"
+    env = dict(os.environ, LD_PRELOAD=str(LIB), B200CAUSAL_FILE=str(out), B200CAUSAL_FIXED_SPEEDUP="0,20", B200CAUSAL_EXPERIMENT_SECONDS="0.4",
+               B200CAUSAL_RANDOM_SEED="11", B200CAUSAL_VERBOSE="1")
+    r = subprocess.run([str(target), "260", "80", "2000000", "pool"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "done 260" in r.stdout
+    assert "Starting causal experiment #1" in r.stderr
+    text = out.read_text()
+    assert text.startswith("startup\ttime=") and text.rstrip().splitlines()[-1].startswith("runtime\ttime=")
+    ex = causal.parse(text)
+    assert len(ex) >= 8
+    assert {e["selected"] for e in ex} <= {"cpu_slow_func", "cpu_fast_func", "main"} or all("Worker" in s or "cpu_" in s or s == "main" for s in {e["selected"] for e in ex})
+    assert {e["speedup"] for e in ex} == {0, 20}
+    res = [x for x in causal.analyze(ex, point="iteration") if x["selected"] in ("cpu_slow_func", "cpu_fast_func")]
+    if len(res) < 2 or not _spread_ok(res) or any(len(x["rows"]) < 2 for x in res):
+        pytest.skip("not both functions drawn at both speed-ups, or a busy machine")
+    by = {x["selected"]: {row["speedup"]: row["program_speedup"] for row in x["rows"]} for x in res}
+    assert by["cpu_slow_func"][20] > by["cpu_fast_func"][20] + 6.0, causal.format_report(res)
+    assert 10.0 < by["cpu_slow_func"][20] < 30.0 and abs(by["cpu_fast_func"][20]) < 9.0, causal.format_report(res)
+
+
+def test_without_the_library_the_marks_do_nothing(target):
+    r = subprocess.run([str(target), "2", "80", "100000"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "done 2" in r.stdout
+    from rocm_systems_b200.utils import causal as marks
+
+    marks.progress("x")
+    with marks.item("y"):
+        pass
+    assert marks.active() is False
