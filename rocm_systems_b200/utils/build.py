@@ -148,6 +148,18 @@ def build_sampler() -> Path | None:
     return out
 
 
+def build_kokkosp() -> Path | None:
+    """The Kokkos Tools library that turns Kokkos callbacks into marker ranges (plain C++; finds the markers at run time)."""
+    src = CSRC / "trace" / "kokkosp.cc"
+    if not src.exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200kokkosp.so"
+    if not out.exists() or out.stat().st_mtime_ns < src.stat().st_mtime_ns:
+        _run(["g++", "-O2", "-g", "-std=c++17", "-fPIC", "-shared", str(src), "-o", str(out), "-ldl"])
+    return out
+
+
 def build_causal() -> Path | None:
     """The causal profiler (preload library, plain C++, no CUDA)."""
     src = CSRC / "prof" / "causal.cc"
@@ -253,6 +265,8 @@ def build_all(verbose_ptxas: bool = False) -> dict:
     res["prof"] = str(prof) if prof else None
     samp = build_sampler()
     res["sampler"] = str(samp) if samp else None
+    kk = build_kokkosp()
+    res["kokkosp"] = str(kk) if kk else None
     causal = build_causal()
     res["causal"] = str(causal) if causal else None
     ext = build_torch_ext()
