@@ -77,7 +77,7 @@ def test_launcher_carries_kokkos_regions_into_the_database(driver, tmp_path):
     r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "--stats", "-d", str(tmp_path), "-o", "run", "--",
                         str(exe), str(lib)], capture_output=True, text=True, cwd=ROOT, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "MARKER_API  parallel_for: axpy" in r.stdout and "9 records" in r.stdout, r.stdout
+    assert "MARKER_API  parallel_for: axpy" in r.stdout and "9 records" in r.stderr, r.stdout + r.stderr
     import sqlite3
 
     db = sqlite3.connect(str(out) + ".db")
