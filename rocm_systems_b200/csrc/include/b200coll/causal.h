@@ -28,6 +28,7 @@ typedef struct {
   int resetFile;             /* truncate the file instead of appending */
   uint64_t seed;             /* 0: from the clock */
   int verbose;
+  const char* sourceRanges;  /* source-line scope: file of "<name>\t<lo>-<hi>,..." (hex addresses of the executable's ELF file); replaces the function scope */
 } b200causalConfig_t;
 
 /* 0 on success; -1 already running, -2 bad argument, -3 nothing in scope, -4 signal or timer set-up failed. */

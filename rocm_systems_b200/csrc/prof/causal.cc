@@ -10,8 +10,8 @@
 // experiment.cpp runs the experiments, sampling.cpp samples, delay.cpp keeps the global and per-thread pause counts,
 // components/blocking_gotcha.cpp and unblocking_gotcha.cpp wrap the pthread calls, components/progress_point.cpp counts;
 // settings ROCPROFSYS_CAUSAL_* in source/lib/core/config.cpp:706-812; user macros in
-// source/lib/rocprof-sys-user/rocprofiler-systems/causal.h). Function scope only: a line scope needs the DWARF line
-// tables, which this library does not read.
+// source/lib/rocprof-sys-user/rocprofiler-systems/causal.h). Function scope by default; for a source-line scope the
+// launcher decodes the executable's line table and hands the address ranges of the chosen lines over in a file.
 //
 // Pauses and dependencies. Each thread keeps how much pause it has served (`local`); the experiment keeps how much is owed
 // (`gOwed`). A thread serves the difference when it is sampled and before it does anything that can wake another thread
@@ -24,7 +24,7 @@
 // tick, not the nominal rate, sets the granularity and the arithmetic stays right.
 //
 // Ways in: LD_PRELOAD=libb200causal.so with B200CAUSAL_FILE (and _BINARY_SCOPE, _FUNCTION_SCOPE, _FUNCTION_EXCLUDE,
-// _FIXED_SPEEDUP, _FREQ, _EXPERIMENT_SECONDS, _DELAY, _DURATION, _END_TO_END, _FILE_RESET, _RANDOM_SEED, _VERBOSE), or
+// _FIXED_SPEEDUP, _SOURCE_RANGES, _FREQ, _EXPERIMENT_SECONDS, _DELAY, _DURATION, _END_TO_END, _FILE_RESET, _RANDOM_SEED, _VERBOSE), or
 // b200causalStart / b200causalStop from the program. Output: the text format of the Coz profiler (experiment /
 // throughput-point / latency-point lines), which `tools/causal.py` turns into speed-up tables.
 #include <cxxabi.h>
@@ -83,9 +83,12 @@ int64_t pauseNs(int64_t ns) {
 }
 
 // ---------------------------------------------------------------- functions in scope (read once, before sampling starts)
+// One address range that can be selected: a function, or one of the ranges the compiler made of a source line. Ranges of
+// the same `entry` are sped up together.
 struct Func {
   uintptr_t lo, hi;
   std::string name;
+  int entry = -1;
 };
 std::vector<Func>* gFuncs = nullptr;  // sorted by lo, never changed while the handler can run
 
@@ -152,7 +155,7 @@ void readSymbols(const char* path, uintptr_t bias, std::vector<Func>& out) {
           const ElfW(Sym)& s = syms[i];
           if (ELF64_ST_TYPE(s.st_info) != STT_FUNC || s.st_size == 0 || s.st_shndx == SHN_UNDEF || s.st_name >= str.sh_size) continue;
           if (!memchr(names + s.st_name, 0, str.sh_size - s.st_name)) continue;
-          out.push_back({bias + s.st_value, bias + s.st_value + s.st_size, demangled(names + s.st_name)});
+          out.push_back({bias + s.st_value, bias + s.st_value + s.st_size, demangled(names + s.st_name), -1});
         }
       }
     }
@@ -188,6 +191,48 @@ int onObject(dl_phdr_info* info, size_t, void* data) {
     a.found.push_back(std::move(f));
   }
   return 0;
+}
+
+int onMainObject(dl_phdr_info* info, size_t, void* data) {
+  *(uintptr_t*)data = (uintptr_t)info->dlpi_addr;
+  return 1;  // the executable is the first object
+}
+
+// Source scope. The line tables are decoded outside (tools/causal.py reads them with readelf); what arrives here is a
+// file of lines "<name>\t<lo>-<hi>,<lo>-<hi>,..." with hexadecimal addresses as they stand in the executable's ELF file.
+// Entries are numbered from 1 << 20 so that they cannot collide with function indices.
+bool readSourceRanges(const char* path, std::vector<Func>& out) {
+  FILE* f = fopen(path, "r");
+  if (!f) return false;
+  uintptr_t bias = 0;
+  dl_iterate_phdr(onMainObject, &bias);
+  char* line = nullptr;
+  size_t cap = 0;
+  int entry = 1 << 20;
+  while (getline(&line, &cap, f) > 0) {
+    char* tab = strchr(line, '\t');
+    if (!tab) continue;
+    *tab = 0;
+    bool any = false;
+    for (char* p = tab + 1; *p;) {
+      char* end = nullptr;
+      const unsigned long long lo = strtoull(p, &end, 16);
+      if (end == p || *end != '-') break;
+      p = end + 1;
+      const unsigned long long hi = strtoull(p, &end, 16);
+      if (end == p) break;
+      if (hi > lo) {
+        out.push_back({bias + (uintptr_t)lo, bias + (uintptr_t)hi, line, entry});
+        any = true;
+      }
+      p = *end == ',' ? end + 1 : end;
+      if (*end != ',') break;
+    }
+    if (any) entry++;
+  }
+  free(line);
+  fclose(f);
+  return true;
 }
 
 // Index of the function that holds `pc`, or -1. Read-only binary search: safe in the signal handler.
@@ -318,7 +363,7 @@ Point* pointFor(const char* name) {
 // ---------------------------------------------------------------- the running experiment
 struct Experiment {
   std::atomic<bool> running{false};
-  std::atomic<uintptr_t> lo{0}, hi{0};
+  std::atomic<int> selected{-1};  // `entry` of the ranges being sped up
   std::atomic<int> percent{0};
   std::atomic<int64_t> selectedSamples{0};
 };
@@ -343,14 +388,15 @@ void onSample(int, siginfo_t*, void*) {
     const int depth = backtrace(pc, kMaxDepth);
     // pc[0] is this handler, pc[1] the signal trampoline, pc[2] the interrupted instruction, the rest return addresses.
     const bool running = gExp.running.load(std::memory_order_acquire);
-    const uintptr_t lo = gExp.lo.load(std::memory_order_relaxed), hi = gExp.hi.load(std::memory_order_relaxed);
+    const int selected = gExp.selected.load(std::memory_order_relaxed);
     bool hit = false;
     int innermost = -1;
-    for (int i = 2; i < depth; i++) {
-      const uintptr_t at = (uintptr_t)pc[i] - (i > 2 ? 1 : 0);
-      if (running && at >= lo && at < hi) hit = true;
-      if (innermost < 0) innermost = funcOf(at);
-      if (hit && innermost >= 0) break;
+    for (int i = 2; i < depth && !hit; i++) {
+      const int r = funcOf((uintptr_t)pc[i] - (i > 2 ? 1 : 0));
+      if (r < 0) continue;
+      if (innermost < 0) innermost = r;
+      if (!running) break;
+      hit = (*gFuncs)[r].entry == selected;
     }
     if (innermost >= 0) {
       gSamples.fetch_add(1, std::memory_order_relaxed);
@@ -438,8 +484,7 @@ int64_t writeExperiment(const Func& f, int percent, const Snapshot& a, const Sna
 }
 
 void beginExperiment(const Func& f, int percent, Snapshot& at) {
-  gExp.lo.store(f.lo);
-  gExp.hi.store(f.hi);
+  gExp.selected.store(f.entry);
   gExp.percent.store(percent);
   gExp.selectedSamples.store(0);
   snapshot(at);
@@ -544,6 +589,7 @@ __attribute__((constructor)) void onLoad() {
   c.functionScope = getenv("B200CAUSAL_FUNCTION_SCOPE");
   c.functionExclude = getenv("B200CAUSAL_FUNCTION_EXCLUDE");
   c.speedups = getenv("B200CAUSAL_FIXED_SPEEDUP");
+  c.sourceRanges = getenv("B200CAUSAL_SOURCE_RANGES");
   c.freqHz = num("B200CAUSAL_FREQ", 1000.0);
   c.experimentSeconds = num("B200CAUSAL_EXPERIMENT_SECONDS", 0.5);
   c.delaySeconds = num("B200CAUSAL_DELAY", 0.0);
@@ -574,12 +620,18 @@ int b200causalStart(const b200causalConfig_t* cfg) {
   scope.function = regexList(cfg->functionScope);
   scope.exclude = regexList(cfg->functionExclude);
   scope.exclude.emplace_back("^_|::_M");  // runtime and standard-library internals are never what one wants to speed up
-  dl_iterate_phdr(onObject, &scope);
+  if (cfg->sourceRanges && *cfg->sourceRanges) {
+    if (!readSourceRanges(cfg->sourceRanges, scope.found)) return -2;
+  } else {
+    dl_iterate_phdr(onObject, &scope);
+  }
   std::sort(scope.found.begin(), scope.found.end(), [](const Func& a, const Func& b) { return a.lo < b.lo || (a.lo == b.lo && a.hi > b.hi); });
   auto* funcs = new std::vector<Func>();
   for (auto& f : scope.found)
     if (funcs->empty() || f.lo >= funcs->back().hi) funcs->push_back(std::move(f));  // aliases and overlaps: keep the first
   if (funcs->empty()) { delete funcs; return -3; }
+  for (size_t i = 0; i < funcs->size(); i++)
+    if ((*funcs)[i].entry < 0) (*funcs)[i].entry = (int)i;  // a function is its own entry; source lines came with theirs
   delete gFuncs;
   gFuncs = funcs;
   delete gCfg;

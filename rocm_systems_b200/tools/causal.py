@@ -8,8 +8,10 @@
 
 ``run`` is the counterpart of the reference's ``rocprof-sys-causal`` launcher (rocprofiler-systems
 source/bin/rocprof-sys-causal/rocprof-sys-causal.cpp: ``-n`` iterations, ``-e`` end-to-end runs with one fixed experiment
-each, ``-s`` speed-ups, ``-F`` / ``-B`` function and binary scopes, ``-d`` delay, ``-t`` duration): with ``-e`` every
-(function scope, speed-up) pair is run ``-n`` times. ``report`` restates what its ``tests/validate-causal-json.py`` computes:
+each, ``-s`` speed-ups, ``-F`` / ``-B`` function and binary scopes, ``-S`` source scope, ``-d`` delay, ``-t`` duration):
+with ``-e`` every (function or source scope, speed-up) pair is run ``-n`` times. With ``-S`` the line table of the
+executable is decoded here (``readelf --debug-dump=decodedline``) and the address ranges of the chosen lines are handed to
+the library, which then selects lines instead of functions. ``report`` restates what its ``tests/validate-causal-json.py`` computes:
 per selected function and progress point, the time per visit at each virtual speed-up against the time per visit at
 speed-up 0 of the same function, with the spread over the experiments, and ``--validate`` checks predictions against
 expected values with a tolerance (exit code 1 on a miss), the way the reference's end-to-end tests do.
@@ -144,8 +146,64 @@ def validate(results: List[dict], checks: List[tuple]) -> List[str]:
     return bad
 
 
+# -------------------------------------------------------------------------------------------------------- source lines
+def decode_line_table(text: str) -> List[tuple]:
+    """Rows of ``readelf --debug-dump=decodedline -W``: ``(path, line, lo, hi)`` for every non-empty address range, where
+    ``path`` is the heading the rows stand under (as the compiler recorded it) and ``hi`` is the address of the next row
+    of the same sequence."""
+    rows: List[tuple] = []          # (path, line or None at the end of a sequence, address)
+    path = ""
+    for raw in text.splitlines():
+        line = raw.rstrip()
+        if not line or line.startswith("Contents of") or line.startswith("File name"):
+            continue
+        if line.endswith(":") and "0x" not in line:
+            path = line[:-1]
+            if path.startswith("CU: "):
+                path = path[4:]
+            continue
+        parts = line.split()
+        if len(parts) < 3 or not parts[2].startswith("0x"):
+            continue
+        rows.append((path, None if parts[1] == "-" else int(parts[1]), int(parts[2], 16)))
+    out = []
+    for (p, ln, addr), (_, _, nxt) in zip(rows, rows[1:]):
+        if ln is not None and nxt > addr:
+            out.append((p, ln, addr, nxt))
+    return out
+
+
+def source_ranges(exe: str, patterns: List[str]) -> Dict[str, List[tuple]]:
+    """Address ranges per source line (``"file.cc:123"``) of ``exe`` for the lines whose ``path:line`` matches one of the
+    regular expressions (a bare file pattern selects every line of the file). Needs debug information (``-g``)."""
+    import re
+
+    r = subprocess.run(["readelf", "--debug-dump=decodedline", "-W", exe], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise SystemExit(f"readelf failed on {exe}: {r.stderr.strip()}")
+    res = [re.compile(p) for p in patterns]
+    merged: Dict[str, List[tuple]] = defaultdict(list)
+    for path, ln, lo, hi in decode_line_table(r.stdout):
+        key = f"{path}:{ln}"
+        if not any(x.search(key) for x in res):
+            continue
+        name = f"{os.path.basename(path)}:{ln}"
+        spans = merged[name]
+        if spans and spans[-1][1] == lo:
+            spans[-1] = (spans[-1][0], hi)
+        else:
+            spans.append((lo, hi))
+    return dict(merged)
+
+
+def write_source_ranges(path: Path, ranges: Dict[str, List[tuple]]) -> None:
+    with open(path, "w") as f:
+        for name, spans in sorted(ranges.items()):
+            f.write(name + "\t" + ",".join(f"{lo:x}-{hi:x}" for lo, hi in sorted(spans)) + "\n")
+
+
 # ------------------------------------------------------------------------------------------------------------------ run
-def environment(a, speedup: Optional[int] = None, function: Optional[str] = None) -> dict:
+def environment(a, speedup: Optional[int] = None, function: Optional[str] = None, source: Optional[str] = None) -> dict:
     env = dict(os.environ)
     lib = str(library())
     env["LD_PRELOAD"] = lib + (":" + env["LD_PRELOAD"] if env.get("LD_PRELOAD") else "")
@@ -157,6 +215,18 @@ def environment(a, speedup: Optional[int] = None, function: Optional[str] = None
         env["B200CAUSAL_FUNCTION_SCOPE"] = ";".join(scope)
     if a.function_exclude:
         env["B200CAUSAL_FUNCTION_EXCLUDE"] = ";".join(a.function_exclude)
+    sources = [source] if source is not None else a.source_scope
+    if sources:
+        import shutil
+
+        exe = shutil.which(a.command[0]) or a.command[0]
+        ranges = source_ranges(exe, sources)
+        if not ranges:
+            raise SystemExit(f"no line of {exe} matches {sources} (is it built with -g?)")
+        table = Path(str(Path(a.output).resolve()) + ".ranges")
+        write_source_ranges(table, ranges)
+        env["B200CAUSAL_SOURCE_RANGES"] = str(table)
+        env.pop("B200CAUSAL_FUNCTION_SCOPE", None)
     speedups = [speedup] if speedup is not None else a.speedups
     if speedups:
         env["B200CAUSAL_FIXED_SPEEDUP"] = ",".join(str(s) for s in speedups)
@@ -175,10 +245,12 @@ def environment(a, speedup: Optional[int] = None, function: Optional[str] = None
 def plan(a) -> List[dict]:
     """The runs ``run`` will make: ``-n`` plain runs, or with ``-e`` one per (function scope, speed-up, iteration)."""
     if not a.end_to_end:
-        return [{"speedup": None, "function": None} for _ in range(a.iterations)]
-    functions = a.function_scope or [None]
+        return [{"speedup": None, "function": None, "source": None} for _ in range(a.iterations)]
     speedups = a.speedups or [0, 10, 20, 30, 40, 50]
-    return [{"speedup": s, "function": f} for _ in range(a.iterations) for f in functions for s in speedups]
+    if a.source_scope:
+        return [{"speedup": s, "function": None, "source": src} for _ in range(a.iterations) for src in a.source_scope for s in speedups]
+    functions = a.function_scope or [None]
+    return [{"speedup": s, "function": f, "source": None} for _ in range(a.iterations) for f in functions for s in speedups]
 
 
 def cmd_run(a) -> int:
@@ -189,7 +261,7 @@ def cmd_run(a) -> int:
         Path(a.output).unlink()
     rc = 0
     for i, job in enumerate(plan(a)):
-        env = environment(a, job["speedup"], job["function"])
+        env = environment(a, job["speedup"], job["function"], job["source"])
         if a.verbose:
             print(f"[causal] run {i + 1}: function scope {job['function'] or a.function_scope or 'all'}, speed-ups {job['speedup'] if job['speedup'] is not None else a.speedups or 'default'}",
                   file=sys.stderr)
@@ -232,6 +304,8 @@ def main(argv=None) -> int:
     r.add_argument("-s", "--speedups", type=int, nargs="*", default=[])
     r.add_argument("-F", "--function-scope", nargs="*", default=[], help="regular expressions on function names")
     r.add_argument("-FE", "--function-exclude", nargs="*", default=[])
+    r.add_argument("-S", "--source-scope", nargs="*", default=[], help="regular expressions on <path>:<line> of the executable's line table "
+                   "(\"solver.cc:120\", or \"solver.cc\" for every line of it): experiments select source lines instead of functions")
     r.add_argument("-B", "--binary-scope", nargs="*", default=[], help="regular expressions on the paths of loaded objects (default: the executable)")
     r.add_argument("-d", "--delay", type=float, default=0.0, help="seconds before the first experiment")
     r.add_argument("-t", "--duration", type=float, default=0.0, help="seconds of experimenting; 0 = the whole run")

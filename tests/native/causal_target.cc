@@ -16,13 +16,17 @@
 #include "b200coll/causal.h"
 
 static volatile double sink;
-static double burn(long n) {
+// Each function has its loop on a line of its own, so that a source-line scope can tell them apart.
+extern "C" __attribute__((noinline)) void cpu_slow_func(long n) {
   double a = 1.0;
-  for (long i = 1; i <= n; i++) a += 1.0 / (double)(i + (long)a % 3);
-  return a;
+  for (long i = 1; i <= n; i++) a += 1.0 / (double)(i + (long)a % 3);  // SLOW_LINE
+  sink = a;
 }
-extern "C" __attribute__((noinline)) void cpu_slow_func(long n) { sink = burn(n); }
-extern "C" __attribute__((noinline)) void cpu_fast_func(long n) { sink = burn(n); }
+extern "C" __attribute__((noinline)) void cpu_fast_func(long n) {
+  double a = 1.0;
+  for (long i = 1; i <= n; i++) a += 1.0 / (double)(i + (long)a % 3);  // FAST_LINE
+  sink = a;
+}
 
 struct Worker {
   std::mutex m;

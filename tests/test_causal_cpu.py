@@ -83,7 +83,7 @@ def test_end_to_end_plan_and_environment(tmp_path):
     assert env["B200CAUSAL_END_TO_END"] == "1" and env["B200CAUSAL_FIXED_SPEEDUP"] == "20" and env["B200CAUSAL_FUNCTION_SCOPE"] == "^a$"
     assert env["LD_PRELOAD"].split(":")[0] == str(LIB) and env["B200CAUSAL_FILE"].endswith("x.coz")
     a.end_to_end = False
-    assert causal.plan(a) == [{"speedup": None, "function": None}] * 2
+    assert causal.plan(a) == [{"speedup": None, "function": None, "source": None}] * 2
 
 
 def _spread_ok(results):
@@ -111,6 +111,57 @@ def test_end_to_end_predictions_match_the_known_answer(target, tmp_path):
     r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.causal", "report", str(out), "--point", "iteration", "--validate",
                         "cpu_slow_func", "iteration", "20", "20", "9"], capture_output=True, text=True, cwd=ROOT)
     assert r.returncode == 0 and "cpu_slow_func  [throughput point: iteration]" in r.stdout, r.stdout + r.stderr
+
+
+LINE_TABLE = """Contents of the .debug_line section:
+
+CU: src/solver.cc:
+File name                            Line number    Starting address    View    Stmt
+solver.cc                                     10              0x1000               x
+solver.cc                                     11              0x1008               x
+solver.cc                                     11              0x1008       1
+solver.cc                                     10              0x1010
+solver.cc                                     12              0x1018               x
+
+/usr/include/c++/13/cmath:
+cmath                                        100              0x1020               x
+cmath                                          -              0x1030
+
+src/solver.cc:
+solver.cc                                     11              0x2000               x
+solver.cc                                      -              0x2004
+"""
+
+
+def test_line_table_rows_become_ranges_per_line(monkeypatch, tmp_path):
+    rows = causal.decode_line_table(LINE_TABLE)
+    assert rows == [("src/solver.cc", 10, 0x1000, 0x1008), ("src/solver.cc", 11, 0x1008, 0x1010), ("src/solver.cc", 10, 0x1010, 0x1018),
+                    ("src/solver.cc", 12, 0x1018, 0x1020), ("/usr/include/c++/13/cmath", 100, 0x1020, 0x1030), ("src/solver.cc", 11, 0x2000, 0x2004)]
+    monkeypatch.setattr(causal.subprocess, "run", lambda *a, **k: type("R", (), {"returncode": 0, "stdout": LINE_TABLE, "stderr": ""})())
+    assert causal.source_ranges("exe", [r"solver\.cc:11$"]) == {"solver.cc:11": [(0x1008, 0x1010), (0x2000, 0x2004)]}
+    every = causal.source_ranges("exe", [r"solver\.cc"])
+    assert set(every) == {"solver.cc:10", "solver.cc:11", "solver.cc:12"} and every["solver.cc:10"] == [(0x1000, 0x1008), (0x1010, 0x1018)]
+    assert causal.source_ranges("exe", ["nothing"]) == {}
+    causal.write_source_ranges(tmp_path / "r", every)
+    assert (tmp_path / "r").read_text().splitlines()[1] == "solver.cc:11\t1008-1010,2000-2004"
+
+
+def test_source_line_scope_matches_the_known_answer(target, tmp_path):
+    src = (ROOT / "tests" / "native" / "causal_target.cc").read_text().splitlines()
+    slow = next(i for i, l in enumerate(src, 1) if "SLOW_LINE" in l and "for (" in l)
+    fast = next(i for i, l in enumerate(src, 1) if "FAST_LINE" in l and "for (" in l)
+    out = tmp_path / "lines.coz"
+    rc = causal.main(["run", "-o", str(out), "-e", "-n", "2", "-s", "0", "20", "-S", rf"causal_target\.cc:{slow}$", rf"causal_target\.cc:{fast}$", "--",
+                      str(target), "24", "80", "4000000", "spawn"])
+    assert rc == 0
+    ex = causal.parse(out.read_text())
+    assert {e["selected"] for e in ex} == {f"causal_target.cc:{slow}", f"causal_target.cc:{fast}"} and len(ex) == 8
+    assert all(e["selected_samples"] > 20 for e in ex)
+    res = causal.analyze(ex, point="iteration")
+    if not _spread_ok(res):
+        pytest.skip("baseline runs differ by more than 6 %: the machine is busy")
+    bad = causal.validate(res, [(f"causal_target.cc:{slow}", "iteration", 20, 20.0, 7.0), (f"causal_target.cc:{fast}", "iteration", 20, 0.0, 7.0)])
+    assert bad == [], causal.format_report(res)
 
 
 def test_experiments_drawn_while_a_thread_pool_runs(target, tmp_path):
