@@ -254,6 +254,31 @@ print('ok')
     assert "ok" in out and "B200COLL_BUFFSIZE" in out and "B200COLL_TRACE " not in out
 
 
+def test_settings_listing_covers_the_tool_libraries(capsys):
+    """Every listed environment name is read somewhere in the package, and the listing can be narrowed by component."""
+    import subprocess as sp
+
+    from rocm_systems_b200.tools import avail
+
+    names = [env for _, env, _, _ in avail.TOOL_SETTINGS]
+    assert len(names) == len(set(names)) >= 35
+    pkg = ROOT / "rocm_systems_b200"
+    for env in names:
+        hit = sp.run(["grep", "-rlF", "--include=*.cc", "--include=*.cu", "--include=*.cuh", "--include=*.h", "--include=*.py", f'"{env}"', str(pkg)],
+                     capture_output=True, text=True).stdout.split()
+        assert [h for h in hit if not h.endswith("tools/avail.py")], env
+    os.environ["B200CAUSAL_FREQ"] = "250"
+    try:
+        assert avail.main(["--component", "causal", "--changed"]) == 0
+    finally:
+        del os.environ["B200CAUSAL_FREQ"]
+    out = capsys.readouterr().out
+    assert out.count("\n") == 1 and out.startswith("B200CAUSAL_FREQ") and "250" in out
+    assert avail.main(["--component", "kokkosp", "--json"]) == 0
+    rows = json.loads(capsys.readouterr().out)
+    assert [r["name"] for r in rows] == ["B200KOKKOSP_MEMORY_EVENTS", "B200KOKKOSP_VERBOSE"] and all(r["component"] == "kokkosp" for r in rows)
+
+
 def test_tuning_table_from_sweeps(tmp_path):
     from rocm_systems_b200.tools import tune
 
