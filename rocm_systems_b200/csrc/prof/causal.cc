@@ -390,18 +390,16 @@ void onSample(int, siginfo_t*, void*) {
     const bool running = gExp.running.load(std::memory_order_acquire);
     const int selected = gExp.selected.load(std::memory_order_relaxed);
     bool hit = false;
-    int innermost = -1;
-    for (int i = 2; i < depth && !hit; i++) {
+    int found[4], nFound = 0;  // the innermost few distinct ranges in scope: callers are candidates too (their time includes the callees')
+    for (int i = 2; i < depth; i++) {
       const int r = funcOf((uintptr_t)pc[i] - (i > 2 ? 1 : 0));
       if (r < 0) continue;
-      if (innermost < 0) innermost = r;
-      if (!running) break;
-      hit = (*gFuncs)[r].entry == selected;
+      if (nFound < 4 && (nFound == 0 || found[nFound - 1] != r)) found[nFound++] = r;
+      if (running && (*gFuncs)[r].entry == selected) hit = true;
+      if (nFound == 4 && (hit || !running)) break;
     }
-    if (innermost >= 0) {
-      gSamples.fetch_add(1, std::memory_order_relaxed);
-      gRecent[gRecentNext.fetch_add(1, std::memory_order_relaxed) % kRecent].store(innermost, std::memory_order_relaxed);
-    }
+    if (nFound > 0) gSamples.fetch_add(1, std::memory_order_relaxed);
+    for (int k = 0; k < nFound; k++) gRecent[gRecentNext.fetch_add(1, std::memory_order_relaxed) % kRecent].store(found[k], std::memory_order_relaxed);
     if (hit) {
       gExp.selectedSamples.fetch_add(1, std::memory_order_relaxed);
       const int64_t owe = stands > 0 ? stands * gExp.percent.load(std::memory_order_relaxed) / 100 : 0;

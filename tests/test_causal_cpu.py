@@ -185,6 +185,26 @@ def test_experiments_drawn_while_a_thread_pool_runs(target, tmp_path):
     assert 10.0 < by["cpu_slow_func"][20] < 30.0 and abs(by["cpu_fast_func"][20]) < 9.0, causal.format_report(res)
 
 
+def test_pipeline_example_under_the_profiler(tmp_path):
+    """The example of the examples folder: experiments select the stage functions (callers of the sampled code are
+    candidates), both kinds of progress point are recorded, and the middle stage is the one whose speed-up pays."""
+    exe = tmp_path / "causal_pipeline"
+    subprocess.run(["g++", "-O1", "-g", "-std=c++17", f"-I{ROOT / 'rocm_systems_b200' / 'csrc' / 'include'}", "-o", str(exe),
+                    str(ROOT / "examples" / "causal_pipeline.cc"), "-lpthread", "-ldl"], check=True)
+    out = tmp_path / "p.coz"
+    rc = causal.main(["run", "-o", str(out), "-s", "0", "40", "--experiment-seconds", "0.3", "--seed", "5", "-F", "^(decode|transform|write_out)$", "--",
+                      str(exe), "7000"])
+    assert rc == 0
+    ex = causal.parse(out.read_text())
+    assert len(ex) >= 8 and {e["selected"] for e in ex} <= {"decode", "transform", "write_out"}
+    assert all("item" in e["throughput"] and "in flight" in e["latency"] for e in ex)
+    res = {r["selected"]: r for r in causal.analyze(ex, point="item")}
+    if "transform" not in res or len(res["transform"]["rows"]) < 2 or not _spread_ok(list(res.values())):
+        pytest.skip("the middle stage was not drawn at both speed-ups, or a busy machine")
+    at40 = {row["speedup"]: row["program_speedup"] for row in res["transform"]["rows"]}[40]
+    assert 22.0 < at40 < 50.0, causal.format_report(list(res.values()))
+
+
 def test_without_the_library_the_marks_do_nothing(target):
     r = subprocess.run([str(target), "2", "80", "100000"], capture_output=True, text=True, timeout=60)
     assert r.returncode == 0 and "done 2" in r.stdout
