@@ -70,6 +70,15 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
         env["B200SAMPLE_CLOCK"] = a.sampling_clock
         if a.sampling_delay > 0:
             env["B200SAMPLE_DELAY"] = str(a.sampling_delay)
+    if a.kokkos_trace:
+        lib = PKG / "lib" / "libb200kokkosp.so"
+        if not lib.exists():
+            raise SystemExit(f"{lib} is missing: run `python -m rocm_systems_b200.utils.build`")
+        old = env.get("KOKKOS_TOOLS_LIBS", "")
+        env["KOKKOS_TOOLS_LIBS"] = f"{lib};{old}" if old else str(lib)
+    if a.preload:
+        old = env.get("LD_PRELOAD", "")
+        env["LD_PRELOAD"] = ":".join([*a.preload, old] if old else a.preload)
     if a.tool_library:
         old = env.get("B200COLL_TOOL_LIBRARIES", "")
         env["B200COLL_TOOL_LIBRARIES"] = ":".join([*a.tool_library, old] if old else a.tool_library)
@@ -94,6 +103,8 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--sync-trace", action="store_true", help="stream/event/context synchronisation")
     g.add_argument("--coll-trace", action="store_true", help="collectives of the communication library")
     g.add_argument("--marker-trace", action="store_true", help="b200tx ranges")
+    g.add_argument("--kokkos-trace", action="store_true", help="Kokkos kernels, fences, deep copies, regions and sections as marker ranges "
+                   "(sets KOKKOS_TOOLS_LIBS to the connector; implies --marker-trace)")
     g.add_argument("--sys-trace", action="store_true", help="everything")
     g.add_argument("--sys-sample", type=int, default=0, metavar="PERIOD_MS",
                    help="sample GPU readings (NVML), host CPU / memory and the command's resident set in the background")
@@ -108,8 +119,11 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--kernel-rename", action="store_true", help="name every kernel after the innermost marker range open on its launching thread at launch "
                    "(needs --marker-trace; with --runtime-trace the launching thread and time are exact)")
     g.add_argument("--truncate-kernels", action="store_true", help="kernel names without return type, namespaces, template and call arguments")
-    g.add_argument("--collection-period", default="", metavar="DELAY_MS:DURATION_MS",
+    g.add_argument("--kernel-iteration-range", nargs="+", default=[], metavar="RANGE",
+                   help="keep only these launches of every kernel, counted from 1 per kernel name: \"[3-5]\" \"8\" \"[20-]\" (applied when the trace is imported)")
+    g.add_argument("--collection-period", default="", metavar="DELAY:DURATION",
                    help="keep only what started in this window after the first record (applied when the trace is imported)")
+    g.add_argument("--collection-period-unit", choices=["hour", "min", "sec", "msec", "usec", "nsec"], default="msec")
     g.add_argument("--max-records", type=int, default=0, help="per kind and process")
     g = ap.add_argument_group("output")
     g.add_argument("-d", "--output-directory", default="prof_out")
@@ -117,6 +131,12 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--output-format", nargs="+", choices=["csv", "json", "pftrace", "db"], default=["csv", "db"])
     g.add_argument("--stats", action="store_true", help="print per-kernel / per-collective statistics")
     g.add_argument("--summary", action="store_true", help="write the statistics as <output>_summary.json as well")
+    g.add_argument("--summary-per-domain", action="store_true", help="statistics of every domain (kernels, copies, each API, markers, collectives) on its own")
+    g.add_argument("--summary-groups", nargs="+", default=[], metavar="REGEX",
+                   help="statistics over unions of domains: one regular expression on domain names per group, e.g. 'KERNEL_DISPATCH|MEMORY_COPY'")
+    g.add_argument("--summary-units", choices=["sec", "msec", "usec", "nsec"], default="nsec")
+    g.add_argument("--summary-output-file", default="", metavar="NAME", help="print the statistics into <output-directory>/NAME.txt instead of the terminal")
+    g.add_argument("--output-config", action="store_true", help="write the options this pass ran with to <output>_config.json")
     g.add_argument("--top", type=int, default=15)
     g = ap.add_argument_group("counter collection")
     g.add_argument("--pmc", nargs="+", default=[], metavar="COUNTER",
@@ -133,6 +153,8 @@ def parser() -> argparse.ArgumentParser:
                         "run as a pass of its own into <output-directory>/pass_<n>/ with the options of the command line as defaults")
     g = ap.add_argument_group("tools")
     g.add_argument("--tool-library", action="append", default=[], help="extra dispatch-table tool(s) to load into the communication library")
+    g.add_argument("--preload", action="append", default=[], metavar="LIBRARY", help="libraries to put in front of LD_PRELOAD (a sanitizer runtime, an allocator)")
+    g.add_argument("--echo", action="store_true", help="print the command and the environment variables this launcher sets before running")
     ap.add_argument("command", nargs=argparse.REMAINDER, help="-- command to run")
     return ap
 
@@ -256,6 +278,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if not cmd:
         print("prof: no command given (put it after --)", file=sys.stderr)
         return 2
+    if a.kokkos_trace:
+        a.marker_trace = True
     if a.sys_trace:
         a.kernel_trace = a.memory_copy_trace = a.runtime_trace = a.sync_trace = a.coll_trace = a.marker_trace = True
     if not (a.kernel_trace or a.memory_copy_trace or a.runtime_trace or a.driver_trace or a.sync_trace or a.coll_trace or a.marker_trace
@@ -266,15 +290,21 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     prefix = str(outdir / a.output_file)
     if a.pmc:
         return collect_counters(a, cmd, prefix)   # a run of its own: a profiled run is not a traced or a timed one
+    env = build_env(a, prefix)
+    if a.echo:
+        changed = {k: v for k, v in sorted(env.items()) if os.environ.get(k) != v}
+        print("prof: " + " ".join(f"{k}={v}" for k, v in changed.items()) + " " + " ".join(cmd), file=sys.stderr)
+    if a.output_config:
+        Path(prefix + "_config.json").write_text(json.dumps({k: v for k, v in vars(a).items() if k != "command"} | {"command": list(cmd)}, indent=1))
     if a.sys_sample > 0:
         from .sysmon import SystemSampler
 
-        child = subprocess.Popen(cmd, env=build_env(a, prefix))
+        child = subprocess.Popen(cmd, env=env)
         with SystemSampler(period_ms=a.sys_sample, pids=[child.pid]) as sampler:
             rc = child.wait()
         sampler.write_csv(prefix + ".sysmon.csv")
     else:
-        rc = subprocess.call(cmd, env=build_env(a, prefix))
+        rc = subprocess.call(cmd, env=env)
     files = collect(prefix)
     if not files:
         print("prof: the command left no trace files (did it use the GPU / the communication library?)", file=sys.stderr)
@@ -286,7 +316,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         total = sum(db.import_csv(f, command=" ".join(cmd)) for f in files)
         if a.collection_period:
             delay, _, duration = a.collection_period.partition(":")
-            db.keep_window(float(delay or 0), float(duration or 0))
+            to_ms = {"hour": 3.6e6, "min": 6e4, "sec": 1e3, "msec": 1.0, "usec": 1e-3, "nsec": 1e-6}[a.collection_period_unit]
+            db.keep_window(float(delay or 0) * to_ms, float(duration or 0) * to_ms)
+        if a.kernel_iteration_range:
+            db.keep_kernel_iterations(tracedb.TraceDB.parse_iteration_ranges(a.kernel_iteration_range))
         if a.kernel_exclude_regex:
             db.drop_kernels(a.kernel_exclude_regex)
         if a.truncate_kernels:
@@ -294,6 +327,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         if a.kernel_rename:
             db.rename_kernels_by_marker()
         summary = db.summary(a.top)
+        if a.summary_per_domain or a.summary_groups:
+            extra = db.domain_summaries(a.top, a.summary_groups)
+            if not a.summary_per_domain:
+                extra["domains"] = {}
+            summary.update(extra)
+        summary = tracedb.scale_units(summary, a.summary_units)
         if "pftrace" in a.output_format:
             db.to_perfetto(prefix + ".perfetto.json")
         if "json" in a.output_format:
@@ -313,7 +352,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
             os.remove(f)
     for f in glob.glob(prefix + ".*.folded"):   # per-process stacks: merged into <output>.folded above
         os.remove(f)
-    if a.stats:
+    if a.summary_output_file:
+        with open(outdir / (a.summary_output_file + ".txt"), "w") as f:
+            tracedb.print_summary(summary, file=f)
+    elif a.stats or a.summary_per_domain or a.summary_groups:
         tracedb.print_summary(summary)
     if a.summary:
         Path(prefix + "_summary.json").write_text(json.dumps(summary, indent=1))

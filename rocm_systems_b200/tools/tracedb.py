@@ -276,6 +276,74 @@ class TraceDB:
         self.db.commit()
         return n
 
+    @staticmethod
+    def parse_iteration_ranges(words: Sequence[str]) -> List[tuple]:
+        """``["[1-3]", "5", "[8-]"]`` -> ``[(1, 3), (5, 5), (8, None)]``: 1-based launch numbers, closed ranges, open end."""
+        out = []
+        for w in words:
+            for part in w.strip().strip("[]").split(","):
+                part = part.strip()
+                if not part:
+                    continue
+                lo, dash, hi = part.partition("-")
+                if not lo.isdigit() or (dash and hi and not hi.isdigit()):
+                    raise ValueError(f"not a range of launch numbers: {w!r}")
+                out.append((int(lo), int(hi) if hi else (None if dash else int(lo))))
+        return out
+
+    def keep_kernel_iterations(self, ranges: Sequence[tuple]) -> int:
+        """Numbers the launches of every kernel name 1, 2, 3, ... in order of start (per process) and keeps only those whose
+        number falls in one of ``ranges`` (the reference launcher's --kernel-iteration-range: profile the steady state of
+        every kernel, not its first launches). Returns how many kernel rows were deleted."""
+        seen: dict = {}
+        drop = []
+        for kid, pid, name_id in self.db.execute("select id, process_id, name_id from kernel_dispatch order by start_ns, id"):
+            n = seen[(pid, name_id)] = seen.get((pid, name_id), 0) + 1
+            if not any(lo <= n and (hi is None or n <= hi) for lo, hi in ranges):
+                drop.append((kid,))
+        self.db.executemany("delete from kernel_dispatch where id = ?", drop)
+        self.db.commit()
+        return len(drop)
+
+    def domain_rows(self) -> List[tuple]:
+        """Every timed record as ``(domain, name, duration_ns)``: kernels (KERNEL_DISPATCH), copies (MEMORY_COPY, by
+        direction), API and marker regions (their category), collectives (COLLECTIVE, device time)."""
+        rows = [("KERNEL_DISPATCH", n, d) for n, d in self.db.execute("select name, duration_ns from kernels")]
+        rows += [("MEMORY_COPY", n, d) for n, d in self.db.execute("select s.value, m.end_ns - m.start_ns from memory_copy m join string s on s.id = m.direction_id")]
+        rows += [(c, n, d) for c, n, d in self.db.execute("select category, name, duration_ns from regions")]
+        rows += [("COLLECTIVE", n, d) for n, d in self.db.execute("select name, device_ns from collectives")]
+        return rows
+
+    @staticmethod
+    def summarize_rows(rows: Sequence[tuple], top: int, with_domain: bool = False) -> List[dict]:
+        acc: dict = {}
+        for domain, name, dur in rows:
+            key = (domain, name) if with_domain else (name,)
+            a = acc.setdefault(key, [0, 0, None, None])
+            a[0] += 1
+            a[1] += dur or 0
+            a[2] = dur if a[2] is None or dur < a[2] else a[2]
+            a[3] = dur if a[3] is None or dur > a[3] else a[3]
+        total = sum(a[1] for a in acc.values()) or 1
+        out = []
+        for key, (calls, tot, lo, hi) in sorted(acc.items(), key=lambda kv: -kv[1][1])[:top]:
+            row = {"domain": key[0]} if with_domain else {}
+            row.update({"name": key[-1], "calls": calls, "total_ns": tot, "mean_ns": tot / calls, "min_ns": lo, "max_ns": hi, "percent": 100.0 * tot / total})
+            out.append(row)
+        return out
+
+    def domain_summaries(self, top: int = 15, groups: Sequence[str] = ()) -> dict:
+        """``{"domains": {domain: rows}, "groups": {pattern: rows}}``: the statistics of every domain on its own (share within
+        the domain), and of every requested union of domains (a regular expression on domain names; share within the
+        union, rows labelled with their domain) -- the reference launcher's --summary-per-domain and --summary-groups."""
+        rows = self.domain_rows()
+        domains = sorted({r[0] for r in rows})
+        out = {"domains": {d: self.summarize_rows([r for r in rows if r[0] == d], top) for d in domains}, "groups": {}}
+        for pattern in groups:
+            rx = re.compile(pattern)
+            out["groups"][pattern] = self.summarize_rows([r for r in rows if rx.fullmatch(r[0])], top, with_domain=True)
+        return out
+
     def merge(self, other_path: str) -> None:
         """Appends another database (for example another rank's) into this one."""
         src = sqlite3.connect(other_path)
@@ -438,7 +506,34 @@ def format_table(names: Sequence[str], rows: Iterable[Sequence], max_width: int 
     return "\n".join(lines)
 
 
+UNITS = {"nsec": 1.0, "usec": 1e3, "msec": 1e6, "sec": 1e9}
+
+
+def scale_units(summary, unit: str):
+    """The same summary with every ``*_ns`` column divided into ``unit`` and renamed (``total_ns`` -> ``total_usec``)."""
+    if unit == "nsec":
+        return summary
+    div = UNITS[unit]
+    if isinstance(summary, dict):
+        out = {}
+        for k, v in summary.items():
+            if isinstance(k, str) and k.endswith("_ns") and isinstance(v, (int, float)):
+                out[k[:-3] + "_" + unit] = v / div
+            else:
+                out[k] = scale_units(v, unit)
+        return out
+    if isinstance(summary, list):
+        return [scale_units(v, unit) for v in summary]
+    return summary
+
+
 def print_summary(summary: dict, file=sys.stdout) -> None:
+    for kind, label in (("domains", "DOMAIN"), ("groups", "GROUP")):
+        for key, rows in (summary.get(kind) or {}).items():
+            if rows:
+                print(f"\n== {label} {key} ==", file=file)
+                names = list(rows[0].keys())
+                print(format_table(names, [[r[n] for n in names] for r in rows]), file=file)
     titles = {"kernels": "KERNEL_DISPATCH", "collectives": "COLLECTIVES (device time)", "regions": "API / MARKER REGIONS",
               "memory_copies": "MEMORY_COPY", "busy": "DEVICE BUSY", "counters": "SAMPLED COUNTERS", "host_samples": "HOST CALL-STACK SAMPLES"}
     for key, title in titles.items():

@@ -488,6 +488,64 @@ def test_tracedb_postprocessing_filters(tmp_path):
         assert rows == [(6000,), (9500,)] and gone == 1 + 2 + 2      # one kernel, both collectives and their two API regions
 
 
+def test_tracedb_iteration_ranges_domains_groups_and_units(tmp_path):
+    """Launch numbers per kernel (--kernel-iteration-range), statistics per domain and over unions of domains
+    (--summary-per-domain, --summary-groups) and the unit of the time columns (--summary-units)."""
+    from rocm_systems_b200.tools import tracedb
+
+    T = tracedb.TraceDB
+    assert T.parse_iteration_ranges(["[1-3]", "5", "[8-]", "[10,12-13]"]) == [(1, 3), (5, 5), (8, None), (10, 10), (12, 13)]
+    with pytest.raises(ValueError):
+        T.parse_iteration_ranges(["[a-3]"])
+    (tmp_path / "t.100_kernel_trace.csv").write_text(KERNEL_CSV)
+    (tmp_path / "t.rank0.csv").write_text(COLL_CSV)
+    (tmp_path / "t.markers.100.csv").write_text(MARK_CSV)
+    with T(str(tmp_path / "a.db")) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        doms = db.domain_summaries(top=5, groups=["KERNEL_DISPATCH|COLLECTIVE", "MARKER_.*"])
+        assert set(doms["domains"]) == {"KERNEL_DISPATCH", "COLLECTIVE", "MARKER_API", "B200COLL_API"}
+        k = doms["domains"]["KERNEL_DISPATCH"]
+        assert [r["name"] for r in k] == ["gemmKernel<Cfg>", "rmsnorm"] and k[0]["calls"] == 2 and k[0]["total_ns"] == 7000
+        assert k[0]["min_ns"] == 3000 and k[0]["max_ns"] == 4000 and k[0]["percent"] == pytest.approx(100 * 7000 / 7500)
+        union = doms["groups"]["KERNEL_DISPATCH|COLLECTIVE"]
+        assert [(r["domain"], r["name"]) for r in union] == [("COLLECTIVE", "ncclAllReduce"), ("KERNEL_DISPATCH", "gemmKernel<Cfg>"), ("KERNEL_DISPATCH", "rmsnorm")]
+        assert union[0]["percent"] == pytest.approx(100 * 18000 / 25500)
+        assert [r["name"] for r in doms["groups"]["MARKER_.*"]] == ["step 0"]
+        scaled = tracedb.scale_units(doms, "usec")
+        row = scaled["domains"]["KERNEL_DISPATCH"][0]
+        assert "total_ns" not in row and row["total_usec"] == pytest.approx(7.0) and row["mean_usec"] == pytest.approx(3.5) and row["calls"] == 2
+        assert tracedb.scale_units(doms, "nsec") is doms
+        import io
+
+        buf = io.StringIO()
+        tracedb.print_summary(dict(db.summary(), **scaled), file=buf)
+        assert "== DOMAIN KERNEL_DISPATCH ==" in buf.getvalue() and "== GROUP MARKER_.* ==" in buf.getvalue() and "total_usec" in buf.getvalue()
+        # second launch of every kernel only: gemmKernel's second, nothing of rmsnorm (launched once)
+        assert db.keep_kernel_iterations([(2, 2)]) == 2
+        assert db.query("select name, start_ns from kernels")[1] == [("gemmKernel<Cfg>", 6000)]
+
+
+def test_prof_launcher_summary_and_environment_options(tmp_path, capsys):
+    """--kokkos-trace, --preload and --echo reach the environment of the command; --output-config records the pass."""
+    from rocm_systems_b200.tools import prof
+    from rocm_systems_b200.utils import build
+
+    lib = build.build_kokkosp()
+    a = prof.parser().parse_args(["--kokkos-trace", "--preload", "/x/liba.so", "--preload", "/x/libb.so", "--summary-groups", "A|B", "--summary-units", "msec",
+                                  "--kernel-iteration-range", "[2-4]", "--collection-period", "1:2", "--collection-period-unit", "sec", "--", "true"])
+    env = prof.build_env(a, str(tmp_path / "t"))
+    assert env["KOKKOS_TOOLS_LIBS"].split(";")[0] == str(lib)
+    assert env["LD_PRELOAD"].split(":")[:2] == ["/x/liba.so", "/x/libb.so"]
+    assert a.summary_groups == ["A|B"] and a.summary_units == "msec" and a.kernel_iteration_range == ["[2-4]"] and a.collection_period_unit == "sec"
+    rc = prof.main(["--marker-trace", "--echo", "--output-config", "-d", str(tmp_path), "-o", "run", "--", sys.executable, "-c", "pass"])
+    assert rc == 0
+    err = capsys.readouterr().err
+    assert "B200COLL_TRACE=1" in err and "-c pass" in err
+    cfg = json.loads((tmp_path / "run_config.json").read_text())
+    assert cfg["marker_trace"] is True and cfg["echo"] is True and cfg["command"][-2:] == ["-c", "pass"]
+
+
 def test_prof_launcher_applies_filters(tmp_path):
     from rocm_systems_b200.tools import prof
 
