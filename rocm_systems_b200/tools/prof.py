@@ -88,7 +88,7 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
 def collect(prefix: str) -> List[str]:
     """Every trace file the children left behind."""
     files = sorted(set(glob.glob(prefix + ".*_kernel_trace.csv") + glob.glob(prefix + ".*_memory_copy_trace.csv") +
-                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv") + glob.glob(prefix + ".sysmon.csv") +
+                       glob.glob(prefix + ".*_cuda_api_trace.csv") + glob.glob(prefix + ".rank*.csv") + glob.glob(prefix + ".markers.*.csv") + glob.glob(prefix + ".pytrace.*.csv") + glob.glob(prefix + ".sysmon.csv") +
                        glob.glob(prefix + ".*.samples.csv")))
     return files
 

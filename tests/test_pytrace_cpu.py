@@ -1,0 +1,125 @@
+"""The Python function tracer (tools/pytrace.py): ranges per call with correct nesting and threads, the include / exclude /
+restrict filters, labels, C calls, the builtin ``profile`` mode, the exit code of the script, and the hand-over to the
+tracing launcher's database. The reference exercises its Python profiler the same way: example scripts run under
+``python -m rocprofsys`` with label and filter options, then checks of the recorded function names
+(rocprofiler-systems tests/rocprof-sys-python-tests.cmake)."""
+import csv
+import sqlite3
+import subprocess
+import sys
+import threading
+from pathlib import Path
+
+from rocm_systems_b200.tools import pytrace
+
+ROOT = Path(__file__).resolve().parent.parent
+
+SCRIPT = '''
+import sys, time, threading
+def leaf(n):
+    return sum(range(n))
+def middle(n):
+    time.sleep(0.002)
+    return leaf(n) + leaf(n // 2)
+class Model:
+    def step(self, k):
+        return [middle(1000 * k) for _ in range(2)]
+def _private():
+    return leaf(3)
+def worker():
+    middle(10)
+if __name__ == "__main__":
+    m = Model()
+    for k in range(3):
+        m.step(k + 1)
+    _private()
+    t = threading.Thread(target=worker); t.start(); t.join()
+    print("script done", sys.argv[1:])
+    sys.exit(int(sys.argv[1]) if len(sys.argv) > 1 else 0)
+'''
+
+
+def _run(tmp_path, *opts, args=()):
+    script = tmp_path / "traced.py"
+    script.write_text(SCRIPT)
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.pytrace", "-o", str(tmp_path / "run"), *opts, "--", str(script), *args],
+                       capture_output=True, text=True, cwd=ROOT, timeout=120)
+    files = list(tmp_path.glob("run.pytrace.*.csv"))
+    assert len(files) == 1, r.stderr
+    with open(files[0]) as f:
+        return r, list(csv.DictReader(f))
+
+
+def test_calls_become_nested_ranges_on_every_thread(tmp_path):
+    r, rows = _run(tmp_path, "--stats", args=("3", "x"))
+    assert r.returncode == 3 and "script done ['3', 'x']" in r.stdout          # the script's arguments and exit code pass through
+    assert "Model.step" in r.stdout and "calls" in r.stdout                    # --stats
+    names = [x["Function"] for x in rows]
+    assert names.count("Model.step") == 3 and names.count("middle") == 7 and names.count("leaf") == 15 and names.count("worker") == 1
+    assert all(x["Domain"] == "PYTHON_FUNCTION" for x in rows)
+    span = lambda x: (int(x["Start_Timestamp"]), int(x["End_Timestamp"]))  # noqa: E731
+    steps = [x for x in rows if x["Function"] == "Model.step"]
+    for m in (x for x in rows if x["Function"] == "middle" and x["Thread_Id"] == steps[0]["Thread_Id"]):
+        assert any(span(s)[0] <= span(m)[0] and span(m)[1] <= span(s)[1] and int(m["Depth"]) > int(s["Depth"]) for s in steps)
+        assert span(m)[1] - span(m)[0] >= 2_000_000                             # it sleeps 2 ms
+    w = next(x for x in rows if x["Function"] == "worker")
+    assert w["Thread_Id"] != steps[0]["Thread_Id"]                              # the thread started under the tracer is traced, with its own id
+    assert not any("genexpr" in n or "listcomp" in n for n in names)
+
+
+def test_filters_labels_and_minimum_duration(tmp_path):
+    _, rows = _run(tmp_path, "-R", "^(leaf|middle|_private)$", "-E", "^_", "--label", "file", "line")
+    names = {x["Function"] for x in rows}
+    assert names == {"leaf [traced.py:3]", "middle [traced.py:5]"}             # restrict keeps three, exclude drops _private
+    for f in tmp_path.glob("run.pytrace.*.csv"):
+        f.unlink()
+    _, rows = _run(tmp_path, "-E", "^_", "-I", "_private", "--min-duration-us", "1500")
+    names = [x["Function"] for x in rows]
+    assert "leaf" not in names and names.count("middle") == 7                  # only the calls that sleep are long enough
+    p = pytrace.Profiler(exclude_functions=["^_"], include_functions=["^_keep"], restrict_modules=["pkg/"])
+    assert p.wanted("_keep_me", "/x/pkg/a.py") and not p.wanted("_drop", "/x/pkg/a.py") and p.wanted("f", "/x/pkg/a.py")
+    assert not p.wanted("_keep_me", "/x/other/a.py")                            # restrict wins over include
+    assert not pytrace.Profiler().wanted("f", "<frozen importlib._bootstrap>")
+
+
+def test_in_process_use_c_calls_and_arguments():
+    def inner(a, b=2):
+        return len([a, b])
+
+    p = pytrace.Profiler(trace_c=True, label=["args"], restrict_functions=["inner", "len"])
+    assert p.runcall(inner, 5) == 2
+    names = [r[0] for r in p.records]
+    assert any(n.startswith("test_in_process_use_c_calls_and_arguments.<locals>.inner(a=5, b=2)") for n in names) and "builtins.len" in names
+    by = {r[0].split("(")[0]: r for r in p.records}
+    assert by["builtins.len"][4] > by["test_in_process_use_c_calls_and_arguments.<locals>.inner"][4]   # the C call is one level deeper
+    assert p.stats(1)[0]["calls"] == 1
+    # A tracer left no hook behind, and a second one can start; decorators pass through while one is active.
+    assert sys.getprofile() is None and threading.getprofile() is None if hasattr(threading, "getprofile") else True
+    q = pytrace.Profiler(restrict_functions=["inner"])
+    with q:
+        pytrace.profile(inner)(1)
+    assert len(q.records) == 1 and len(pytrace.profile.records) == 0
+
+
+def test_builtin_mode_traces_only_what_the_script_marks(tmp_path):
+    script = tmp_path / "marked.py"
+    script.write_text("def a():\n    return 1\n@profile\ndef b():\n    return a() + a()\na()\nb()\nwith profile:\n    a()\nprint('ok')\n")
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.pytrace", "-b", "-o", str(tmp_path / "m"), "-R", "^[ab]$", "--", str(script)],
+                       capture_output=True, text=True, cwd=ROOT, timeout=120)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr
+    with open(next(tmp_path.glob("m.pytrace.*.csv"))) as f:
+        names = [x["Function"] for x in csv.DictReader(f)]
+    assert sorted(names) == ["a", "a", "a", "b"]                                # not the unmarked first a()
+
+
+def test_launcher_puts_python_ranges_into_the_database(tmp_path):
+    script = tmp_path / "traced.py"
+    script.write_text(SCRIPT)
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "--summary-per-domain", "-d", str(tmp_path), "-o", "run", "--",
+                        sys.executable, "-m", "rocm_systems_b200.tools.pytrace", "-R", "^(leaf|middle|Model)", "--", str(script)],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "== DOMAIN PYTHON_FUNCTION ==" in r.stdout
+    db = sqlite3.connect(str(tmp_path / "run.db"))
+    rows = db.execute("select name, count(*) from regions where category = 'PYTHON_FUNCTION' group by name").fetchall()
+    assert dict(rows) == {"Model.step": 3, "middle": 7, "leaf": 15, "Model": 1}
