@@ -42,10 +42,16 @@ struct NvmlFns {
   nvmlReturn_t (*supportedEvents)(nvmlDevice_t, unsigned long long*) = nullptr;
   nvmlReturn_t (*registerEvents)(nvmlDevice_t, unsigned long long, nvmlEventSet_t) = nullptr;
   nvmlReturn_t (*eventSetWait)(nvmlEventSet_t, nvmlEventData_t*, unsigned int) = nullptr;
+  nvmlReturn_t (*gpmSupport)(nvmlDevice_t, nvmlGpmSupport_t*) = nullptr;
+  nvmlReturn_t (*gpmSampleAlloc)(nvmlGpmSample_t*) = nullptr;
+  nvmlReturn_t (*gpmSampleFree)(nvmlGpmSample_t) = nullptr;
+  nvmlReturn_t (*gpmSampleGet)(nvmlDevice_t, nvmlGpmSample_t) = nullptr;
+  nvmlReturn_t (*gpmMetricsGet)(nvmlGpmMetricsGet_t*) = nullptr;
 };
 extern NvmlFns gN;
 bool ready();
 b200smi_status_t deviceHandle(int device, nvmlDevice_t* h);
+void activityReset();     // topo.cc: frees the activity samples (called at the last shutdown)
 void watchStopLocked();  // health.cc: stops the sampler thread (called at the last shutdown)
 
 }  // namespace smi

@@ -9,8 +9,10 @@
 #include <nvml.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
 
 #include <mutex>
+#include <utility>
 
 #include "b200coll/smi.h"
 #include "mem.h"
@@ -73,6 +75,11 @@ static bool loadNvml() {
   sym("nvmlDeviceGetSupportedEventTypes", &gN.supportedEvents, false);
   sym("nvmlDeviceRegisterEvents", &gN.registerEvents, false);
   sym("nvmlEventSetWait_v2", &gN.eventSetWait, false);
+  sym("nvmlGpmQueryDeviceSupport", &gN.gpmSupport, false);
+  sym("nvmlGpmSampleAlloc", &gN.gpmSampleAlloc, false);
+  sym("nvmlGpmSampleFree", &gN.gpmSampleFree, false);
+  sym("nvmlGpmSampleGet", &gN.gpmSampleGet, false);
+  sym("nvmlGpmMetricsGet", &gN.gpmMetricsGet, false);
   if (!ok) {
     dlclose(gLib);
     gLib = nullptr;
@@ -106,6 +113,39 @@ static void countLinks(nvmlDevice_t h, uint32_t* total, uint32_t* active) {
 }  // namespace smi
 }  // namespace b200
 
+namespace {
+struct ActivityState {
+  nvmlGpmSample_t prev = nullptr, cur = nullptr;
+  uint64_t prevNs = 0;          // when `prev` was taken; 0: none yet
+  uint64_t resultNs = 0;
+  b200smi_activity_t result{};
+  int supported = -1;           // -1 not asked yet
+};
+std::mutex gActMu;
+ActivityState gAct[64];
+
+uint64_t monoNs() {
+  timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+}
+}  // namespace
+
+namespace b200 {
+namespace smi {
+void activityReset() {  // at the last shutdown: the samples belong to the library that is about to be closed
+  std::lock_guard<std::mutex> lk(gActMu);
+  for (auto& a : gAct) {
+    if (gN.gpmSampleFree) {
+      if (a.prev) gN.gpmSampleFree(a.prev);
+      if (a.cur) gN.gpmSampleFree(a.cur);
+    }
+    a = ActivityState{};
+  }
+}
+}  // namespace smi
+}  // namespace b200
+
 using namespace b200::smi;
 
 extern "C" {
@@ -124,6 +164,7 @@ b200smi_status_t b200smi_shutdown(void) {
   if (gRef == 0) return B200SMI_ERR_NOT_LOADED;
   if (--gRef == 0) {
     watchStopLocked();
+    activityReset();
     gN.shutdown();
   }
   return B200SMI_OK;
@@ -196,8 +237,79 @@ b200smi_status_t b200smi_device_info(int device, b200smi_device_info_t* info) {
   return B200SMI_OK;
 }
 
+// ---- activity from performance-monitoring samples --------------------------------------------------------------------
+// Two samples bracket an interval; the driver turns the pair into percentages and rates. Per device the previous sample
+// is kept, so a periodic reader (the watch thread, a monitor loop) pays one sample per period and gets the activity of
+// exactly that period. This is what the reference's telemetry gets from its profiler plug-in
+// (rdc/rdc_libs/rdc_modules/rdc_rocp/RdcRocpBase.cpp: occupancy, active cycles, FLOP rates as watchable fields),
+// without programming counters: the samples come from the driver's always-on monitoring block.
+b200smi_status_t b200smi_activity(int device, b200smi_activity_t* out) {
+  if (!out) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (device >= 64) return B200SMI_ERR_INVALID;
+  if (!gN.gpmSampleAlloc || !gN.gpmSampleGet || !gN.gpmMetricsGet) return B200SMI_ERR_NOT_SUPPORTED;
+  std::lock_guard<std::mutex> lk(gActMu);
+  ActivityState& a = gAct[device];
+  if (a.supported < 0) {
+    a.supported = 1;
+    if (gN.gpmSupport) {
+      nvmlGpmSupport_t sup;
+      memset(&sup, 0, sizeof(sup));
+      sup.version = NVML_GPM_SUPPORT_VERSION;
+      if (gN.gpmSupport(h, &sup) != NVML_SUCCESS || !sup.isSupportedDevice) a.supported = 0;
+    }
+  }
+  if (!a.supported) return B200SMI_ERR_NOT_SUPPORTED;
+  uint64_t now = monoNs();
+  if (a.resultNs && now - a.resultNs < 50000000ull) {  // several fields read in a row share one interval
+    *out = a.result;
+    return B200SMI_OK;
+  }
+  if (!a.prev && gN.gpmSampleAlloc(&a.prev) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  if (!a.cur && gN.gpmSampleAlloc(&a.cur) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  if (!a.prevNs || now - a.prevNs > 5000000000ull) {
+    if (gN.gpmSampleGet(h, a.prev) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+    a.prevNs = now;
+    timespec nap{0, 100000000};
+    nanosleep(&nap, nullptr);
+    now = monoNs();
+  }
+  if (gN.gpmSampleGet(h, a.cur) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  static const unsigned ids[] = {NVML_GPM_METRIC_SM_UTIL, NVML_GPM_METRIC_SM_OCCUPANCY, NVML_GPM_METRIC_ANY_TENSOR_UTIL, NVML_GPM_METRIC_DRAM_BW_UTIL,
+                                 NVML_GPM_METRIC_FP64_UTIL, NVML_GPM_METRIC_FP32_UTIL, NVML_GPM_METRIC_FP16_UTIL, NVML_GPM_METRIC_PCIE_TX_PER_SEC,
+                                 NVML_GPM_METRIC_PCIE_RX_PER_SEC, NVML_GPM_METRIC_NVLINK_TOTAL_TX_PER_SEC, NVML_GPM_METRIC_NVLINK_TOTAL_RX_PER_SEC};
+  constexpr unsigned n = sizeof(ids) / sizeof(ids[0]);
+  static nvmlGpmMetricsGet_t req;  // large (one slot per metric the driver knows): not on the stack; gActMu is held
+  memset(&req, 0, sizeof(req));
+  req.version = NVML_GPM_METRICS_GET_VERSION;
+  req.numMetrics = n;
+  req.sample1 = a.prev;
+  req.sample2 = a.cur;
+  for (unsigned i = 0; i < n; i++) req.metrics[i].metricId = ids[i];
+  if (gN.gpmMetricsGet(&req) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  double v[n];
+  for (unsigned i = 0; i < n; i++) v[i] = req.metrics[i].nvmlReturn == NVML_SUCCESS ? req.metrics[i].value : -1.0;
+  a.result = b200smi_activity_t{(now - a.prevNs) / 1e6, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10]};
+  a.resultNs = now;
+  std::swap(a.prev, a.cur);
+  a.prevNs = now;
+  *out = a.result;
+  return B200SMI_OK;
+}
+
 b200smi_status_t b200smi_read_field(int device, int field, double* value) {
   if (!value) return B200SMI_ERR_INVALID;
+  if (field >= B200SMI_FIELD_SM_ACTIVE && field <= B200SMI_FIELD_NVLINK_RX_MIBS) {
+    b200smi_activity_t act;
+    b200smi_status_t ast = b200smi_activity(device, &act);
+    if (ast != B200SMI_OK) return ast;
+    const double vals[] = {act.smActivePct, act.smOccupancyPct, act.tensorActivePct, act.dramActivePct, act.fp64ActivePct, act.fp32ActivePct,
+                           act.fp16ActivePct, act.pcieTxMiBs, act.pcieRxMiBs, act.nvlinkTxMiBs, act.nvlinkRxMiBs};
+    *value = vals[field - B200SMI_FIELD_SM_ACTIVE];
+    return *value < 0 ? B200SMI_ERR_NOT_SUPPORTED : B200SMI_OK;
+  }
   b200smi_device_info_t i;
   b200smi_status_t st = b200smi_device_info(device, &i);
   if (st != B200SMI_OK) return st;

@@ -60,8 +60,21 @@ typedef struct {
 typedef enum {
   B200SMI_FIELD_SM_CLOCK = 1, B200SMI_FIELD_MEM_CLOCK, B200SMI_FIELD_POWER, B200SMI_FIELD_TEMP, B200SMI_FIELD_MEM_USED,
   B200SMI_FIELD_GPU_UTIL, B200SMI_FIELD_MEM_UTIL, B200SMI_FIELD_ECC_CORRECTED, B200SMI_FIELD_ECC_UNCORRECTED,
-  B200SMI_FIELD_THROTTLE_REASONS, B200SMI_FIELD_NVLINK_ACTIVE, B200SMI_FIELD_COUNT_
+  B200SMI_FIELD_THROTTLE_REASONS, B200SMI_FIELD_NVLINK_ACTIVE,
+  /* Activity over the interval since the previous reading, from the driver's performance-monitoring samples (no
+   * profiler attached, no replay): percentages of peak, and traffic in MiB/s. */
+  B200SMI_FIELD_SM_ACTIVE, B200SMI_FIELD_SM_OCCUPANCY, B200SMI_FIELD_TENSOR_ACTIVE, B200SMI_FIELD_DRAM_ACTIVE,
+  B200SMI_FIELD_FP64_ACTIVE, B200SMI_FIELD_FP32_ACTIVE, B200SMI_FIELD_FP16_ACTIVE,
+  B200SMI_FIELD_PCIE_TX_MIBS, B200SMI_FIELD_PCIE_RX_MIBS, B200SMI_FIELD_NVLINK_TX_MIBS, B200SMI_FIELD_NVLINK_RX_MIBS,
+  B200SMI_FIELD_COUNT_
 } b200smi_field_t;
+
+/* All activity readings of one device over one interval. A value the device does not report is negative. */
+typedef struct {
+  double intervalMs;
+  double smActivePct, smOccupancyPct, tensorActivePct, dramActivePct, fp64ActivePct, fp32ActivePct, fp16ActivePct;
+  double pcieTxMiBs, pcieRxMiBs, nvlinkTxMiBs, nvlinkRxMiBs;
+} b200smi_activity_t;
 
 typedef struct { uint64_t timestampNs; double value; } b200smi_sample_t;
 typedef struct { double min, max, avg, last; uint64_t samples; } b200smi_stats_t;
@@ -75,6 +88,10 @@ const char* b200smi_status_string(b200smi_status_t s);
 b200smi_status_t b200smi_device_count(int* count);
 b200smi_status_t b200smi_device_info(int device, b200smi_device_info_t* info);
 b200smi_status_t b200smi_read_field(int device, int field, double* value);
+/* Activity between the previous call for this device and now. The first call (or one more than 5 s after the previous)
+ * takes two samples 100 ms apart itself; calls less than 50 ms after the previous one return its result again.
+ * B200SMI_ERR_NOT_SUPPORTED when the driver or the device has no performance-monitoring samples. */
+b200smi_status_t b200smi_activity(int device, b200smi_activity_t* out);
 b200smi_status_t b200smi_link(int from, int to, b200smi_link_t* link);
 /* Driver version string, compute processes on a device, NVLink error counters summed over the
  * device's links, and the PCIe link it trains at (rocm-smi: --showdriverversion, --showpids,

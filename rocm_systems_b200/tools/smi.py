@@ -19,7 +19,11 @@ import sys
 from .. import _lib
 
 FIELDS = {"sm_clock": 1, "mem_clock": 2, "power": 3, "temp": 4, "mem_used": 5, "gpu_util": 6, "mem_util": 7, "ecc_corrected": 8,
-          "ecc_uncorrected": 9, "throttle_reasons": 10, "nvlink_active": 11}
+          "ecc_uncorrected": 9, "throttle_reasons": 10, "nvlink_active": 11,
+          # activity over the interval since the previous reading (percent of peak; MiB/s)
+          "sm_active": 12, "sm_occupancy": 13, "tensor_active": 14, "dram_active": 15, "fp64_active": 16, "fp32_active": 17, "fp16_active": 18,
+          "pcie_tx_mibs": 19, "pcie_rx_mibs": 20, "nvlink_tx_mibs": 21, "nvlink_rx_mibs": 22}
+ACTIVITY_FIELDS = [f for f, i in FIELDS.items() if i >= 12]
 REASON_BITS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
                0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
 LINK_TYPES = {0: "SELF", 1: "NVLINK", 2: "PCIE", 3: "UNKNOWN"}
@@ -70,6 +74,11 @@ class Event(ctypes.Structure):
 
 EVENT_NAMES = {0x1: "ecc_single_bit", 0x2: "ecc_double_bit", 0x4: "pstate", 0x8: "xid", 0x10: "clock", 0x80: "power_source"}
 ERR_TIMEOUT = 6
+
+
+class Activity(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_double) for n in ("intervalMs", "smActivePct", "smOccupancyPct", "tensorActivePct", "dramActivePct", "fp64ActivePct",
+                                                "fp32ActivePct", "fp16ActivePct", "pcieTxMiBs", "pcieRxMiBs", "nvlinkTxMiBs", "nvlinkRxMiBs")]
 
 
 class Smi:
@@ -185,6 +194,18 @@ class Smi:
         self._ck(self.lib.b200smi_nvlink_errors(dev, ctypes.byref(e)))
         return {f[0]: getattr(e, f[0]) for f in NvlinkErrors._fields_}
 
+    def activity(self, dev: int) -> dict:
+        """Activity since the previous call for this device (the first call measures 100 ms itself): SM busy, occupancy,
+        tensor / DRAM / FP pipes in percent of peak, PCIe and NVLink traffic in MiB/s; ``None`` where the device reports
+        nothing. Raises when the driver has no performance-monitoring samples."""
+        a = Activity()
+        self.lib.b200smi_activity.argtypes = [ctypes.c_int, ctypes.POINTER(Activity)]
+        self._ck(self.lib.b200smi_activity(dev, ctypes.byref(a)))
+        names = {"intervalMs": "interval_ms", "smActivePct": "sm_active_pct", "smOccupancyPct": "sm_occupancy_pct", "tensorActivePct": "tensor_active_pct",
+                 "dramActivePct": "dram_active_pct", "fp64ActivePct": "fp64_active_pct", "fp32ActivePct": "fp32_active_pct", "fp16ActivePct": "fp16_active_pct",
+                 "pcieTxMiBs": "pcie_tx_mibs", "pcieRxMiBs": "pcie_rx_mibs", "nvlinkTxMiBs": "nvlink_tx_mibs", "nvlinkRxMiBs": "nvlink_rx_mibs"}
+        return {names[f[0]]: (None if getattr(a, f[0]) < 0 else round(getattr(a, f[0]), 3)) for f in Activity._fields_}
+
     def pcie(self, dev: int) -> dict:
         g, w = ctypes.c_uint32(), ctypes.c_uint32()
         self._ck(self.lib.b200smi_pcie(dev, ctypes.byref(g), ctypes.byref(w)))
@@ -255,6 +276,9 @@ def _sub_main(argv) -> int:
         subs[name] = sp
     subs["monitor"].add_argument("-w", "--watch", type=float, default=1.0, metavar="SECONDS", help="interval between lines")
     subs["monitor"].add_argument("-i", "--iterations", type=int, default=1, help="how many intervals (0: until interrupted)")
+    for name in ("metric", "monitor"):
+        subs[name].add_argument("--activity", action="store_true", help="SM / tensor / DRAM activity and PCIe / NVLink traffic over the interval "
+                                "(performance-monitoring samples of the driver; no profiler involved)")
     subs["event"].add_argument("-t", "--timeout", type=float, default=5.0, metavar="SECONDS", help="stop after this long without an event")
     a = ap.parse_args(argv)
     try:
@@ -311,6 +335,8 @@ def _sub_main(argv) -> int:
                          "memory_util_pct": d["memUtilPct"], "ecc_corrected": d["eccCorrected"], "ecc_uncorrected": d["eccUncorrected"],
                          "nvlink_active": d["nvlinkActive"], "nvlink_replay": e["replay"], "nvlink_recovery": e["recovery"], "nvlink_crc": e["crcFlit"] + e["crcData"],
                          "throttle": ",".join(d["throttleReasonNames"]) or "none"})
+            if a.activity:
+                rows[-1].update({k: v for k, v in smi.activity(g).items() if k != "interval_ms"})
         emit(rows)
     elif a.cmd == "topology":
         rows = []
@@ -334,6 +360,9 @@ def _sub_main(argv) -> int:
                     d = smi.info(g)
                     rows.append({"gpu": g, "power_w": round(d["powerMilliwatt"] / 1000, 1), "temperature_c": d["temperatureC"], "sm_clock_mhz": d["smClockMhz"],
                                  "gpu_util_pct": d["gpuUtilPct"], "memory_util_pct": d["memUtilPct"], "memory_used_gib": round(d["memUsedBytes"] / 2**30, 2)})
+                    if a.activity:   # over the interval since the previous line
+                        act = smi.activity(g)
+                        rows[-1].update({k: act[k] for k in ("sm_active_pct", "tensor_active_pct", "dram_active_pct", "nvlink_tx_mibs", "nvlink_rx_mibs")})
                 emit(rows)
                 i += 1
                 if a.iterations == 0 or i < a.iterations:
@@ -369,6 +398,7 @@ def main(argv=None) -> int:
     ap.add_argument("--shownvlinkerrors", action="store_true", help="replay / recovery / CRC counters summed over each GPU's links")
     ap.add_argument("--showbus", action="store_true", help="PCIe generation and width")
     ap.add_argument("--showmodes", action="store_true", help="compute, persistence, MIG and ECC modes (read only)")
+    ap.add_argument("--showactivity", action="store_true", help="SM busy / occupancy / tensor / DRAM / FP activity and PCIe / NVLink traffic over 100 ms")
     ap.add_argument("--showevents", type=float, default=0.0, metavar="SECONDS",
                     help="print XID / ECC / power-state / clock events as they happen; stops after this long without one")
     ap.add_argument("--json", action="store_true")
@@ -416,6 +446,15 @@ def main(argv=None) -> int:
         if not a.json:
             for i, m in enumerate(out["modes"]):
                 print(f"GPU{i}: compute mode {m['compute_mode']}, persistence {m['persistence']}, MIG {m['mig']}, ECC {m['ecc']}")
+    if a.showactivity:
+        out["activity"] = [smi.activity(i) for i in range(n)]
+        if not a.json:
+            fmt = lambda v, unit: "n/a" if v is None else f"{v:g}{unit}"  # noqa: E731
+            for i, v in enumerate(out["activity"]):
+                print(f"GPU{i}: SM busy {fmt(v['sm_active_pct'], ' %')}, occupancy {fmt(v['sm_occupancy_pct'], ' %')}, tensor {fmt(v['tensor_active_pct'], ' %')}, "
+                      f"DRAM {fmt(v['dram_active_pct'], ' %')}, fp64/32/16 {fmt(v['fp64_active_pct'], '')}/{fmt(v['fp32_active_pct'], '')}/{fmt(v['fp16_active_pct'], '')} %, "
+                      f"PCIe tx/rx {fmt(v['pcie_tx_mibs'], '')}/{fmt(v['pcie_rx_mibs'], '')} MiB/s, NVLink tx/rx {fmt(v['nvlink_tx_mibs'], '')}/{fmt(v['nvlink_rx_mibs'], '')} MiB/s "
+                      f"(over {v['interval_ms']:.0f} ms)")
     if a.showevents > 0:
         out["events"] = []
         for ev in smi.events(timeout_ms=int(a.showevents * 1000)):
@@ -435,7 +474,7 @@ def main(argv=None) -> int:
         if not a.json:
             for i, d in enumerate(infos):
                 print(f"GPU{i}: " + "; ".join(singles[k](d) for k in asked))
-    only_new = bool(asked) or a.showevents > 0 or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    only_new = bool(asked) or a.showevents > 0 or a.showactivity or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
               ("typeName", "Link type between two GPUs", a.showtopotype), ("maxBandwidthMBps", "Max bandwidth (MB/s per direction)", a.shownodesbw),
               ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]

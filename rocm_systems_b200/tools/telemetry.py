@@ -27,7 +27,7 @@ import urllib.request
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import List, Optional, Sequence
 
-from .smi import FIELDS, REASON_BITS, Smi
+from .smi import ACTIVITY_FIELDS, FIELDS, REASON_BITS, Smi
 
 DEFAULT_FIELDS = ["sm_clock", "mem_clock", "power", "temp", "mem_used", "gpu_util", "mem_util", "ecc_corrected", "ecc_uncorrected",
                   "throttle_reasons", "nvlink_active"]
@@ -44,6 +44,18 @@ PROM = {
     "ecc_uncorrected": ("b200_ecc_uncorrected_total", "uncorrected ECC errors (volatile)", 1.0),
     "throttle_reasons": ("b200_clock_event_reasons", "bit mask of active clock event reasons", 1.0),
     "nvlink_active": ("b200_nvlink_active_links", "NVLink links in the active state", 1.0),
+    # activity over the sampling period (the field group "activity"; what the reference's profiler plug-in adds to its telemetry)
+    "sm_active": ("b200_sm_active_percent", "share of SMs that were busy", 1.0),
+    "sm_occupancy": ("b200_sm_occupancy_percent", "resident warps against the maximum", 1.0),
+    "tensor_active": ("b200_tensor_active_percent", "share of time the tensor pipes were busy", 1.0),
+    "dram_active": ("b200_dram_bandwidth_percent", "DRAM bandwidth used against the maximum", 1.0),
+    "fp64_active": ("b200_fp64_active_percent", "share of time the FP64 pipes were busy", 1.0),
+    "fp32_active": ("b200_fp32_active_percent", "share of time the FP32 pipes were busy", 1.0),
+    "fp16_active": ("b200_fp16_active_percent", "share of time the FP16 pipes were busy", 1.0),
+    "pcie_tx_mibs": ("b200_pcie_tx_bytes_per_second", "PCIe traffic from the GPU", 1048576.0),
+    "pcie_rx_mibs": ("b200_pcie_rx_bytes_per_second", "PCIe traffic to the GPU", 1048576.0),
+    "nvlink_tx_mibs": ("b200_nvlink_tx_bytes_per_second", "NVLink traffic from the GPU, all links", 1048576.0),
+    "nvlink_rx_mibs": ("b200_nvlink_rx_bytes_per_second", "NVLink traffic to the GPU, all links", 1048576.0),
 }
 
 
@@ -57,7 +69,7 @@ class Telemetry:
         self.watching = False
         self.jobs: dict = {}
         self.groups: dict = {"all": list(self.devices)}          # device groups by name
-        self.field_groups: dict = {"default": list(DEFAULT_FIELDS)}
+        self.field_groups: dict = {"default": list(DEFAULT_FIELDS), "activity": list(ACTIVITY_FIELDS)}
         self.device_events: List[dict] = []                      # XID / ECC / clock events seen by the listener
         self._event_thread: Optional[threading.Thread] = None
         self._event_stop = threading.Event()
@@ -244,8 +256,16 @@ class Telemetry:
         return out
 
     def latest(self) -> dict:
-        """{device: {field: value}} read now (not from the history)."""
-        return {d: {f: self.smi.read(d, f) for f in self.fields} for d in self.devices}
+        """{device: {field: value}} read now (not from the history); ``None`` for a field this device does not report."""
+        def read(d, f):
+            try:
+                return self.smi.read(d, f)
+            except RuntimeError as e:
+                if "not supported" in str(e):
+                    return None
+                raise
+
+        return {d: {f: read(d, f) for f in self.fields} for d in self.devices}
 
     def history(self, dev: int, field: str, max_n: int = 4096) -> list:
         return self.smi.history(dev, field, max_n)
@@ -312,12 +332,13 @@ class Telemetry:
             lines.append(f"# HELP {name} {help_}")
             lines.append(f"# TYPE {name} {kind}")
             for d in self.devices:
-                lines.append(f'{name}{{gpu="{d}",uuid="{infos[d]["uuid"]}"}} {vals[d][f] * scale:g}')
+                if vals[d][f] is not None:
+                    lines.append(f'{name}{{gpu="{d}",uuid="{infos[d]["uuid"]}"}} {vals[d][f] * scale:.12g}')
         if "throttle_reasons" in self.fields:
             lines.append("# HELP b200_clock_event_reason one series per reason; 1 while it is active")
             lines.append("# TYPE b200_clock_event_reason gauge")
             for d in self.devices:
-                mask = int(vals[d]["throttle_reasons"])
+                mask = int(vals[d]["throttle_reasons"] or 0)
                 for bit, reason in REASON_BITS.items():
                     lines.append(f'b200_clock_event_reason{{gpu="{d}",reason="{reason}"}} {1 if mask & bit else 0}')
         try:  # link error counters, where the driver exposes them

@@ -5,6 +5,9 @@
  *   FAKE_NVML_TEMP=<celsius>       temperature of every GPU
  *   FAKE_NVML_RAMP=1               power rises by 10 W on every read (for watch / policy tests)
  *   FAKE_NVML_EVENTS=<gpu>:<type>:<data>[,...]   events the event set hands out, one per wait, then time-outs
+ *   FAKE_NVML_GPM=0                the performance-monitoring samples are reported as unsupported
+ *   FAKE_NVML_TENSOR=<percent>     tensor activity every GPU reports (default 62.5); NVLink traffic is 1000 MiB/s per
+ *                                  sample taken between the two samples of a request, so it shows which pair was used
  * The last power limit a setter wrote is kept in memory and returned by the getter. */
 #include <stdio.h>
 #include <stdlib.h>
@@ -103,4 +106,40 @@ nvmlReturn_t nvmlEventSetWait_v2(nvmlEventSet_t s, nvmlEventData_t* out, unsigne
   }
   usleep((timeoutms > 50 ? 50 : timeoutms) * 1000);
   return 10; /* NVML_ERROR_TIMEOUT */
+}
+
+/* ---- performance-monitoring samples: a sample remembers its sequence number; a metrics request reports fixed
+ * percentages, the number of samples between its two samples as NVLink traffic, and "not available" for FP64. ---- */
+typedef struct fake_sample { int seq; } *nvmlGpmSample_t;
+typedef struct { unsigned int version; unsigned int isSupportedDevice; } nvmlGpmSupport_t;
+typedef struct { unsigned int metricId; nvmlReturn_t nvmlReturn; double value; struct { char* shortName; char* longName; char* unit; } metricInfo; } nvmlGpmMetric_t;
+#define FAKE_GPM_METRIC_MAX 210
+typedef struct { unsigned int version; unsigned int numMetrics; nvmlGpmSample_t sample1, sample2; nvmlGpmMetric_t metrics[FAKE_GPM_METRIC_MAX]; } nvmlGpmMetricsGet_t;
+static int sample_seq = 0;
+nvmlReturn_t nvmlGpmQueryDeviceSupport(nvmlDevice_t d, nvmlGpmSupport_t* s) { (void)d; s->isSupportedDevice = envint("FAKE_NVML_GPM", 1) ? 1 : 0; return NVML_SUCCESS; }
+nvmlReturn_t nvmlGpmSampleAlloc(nvmlGpmSample_t* s) { *s = calloc(1, sizeof(struct fake_sample)); return *s ? NVML_SUCCESS : 20; }
+nvmlReturn_t nvmlGpmSampleFree(nvmlGpmSample_t s) { free(s); return NVML_SUCCESS; }
+nvmlReturn_t nvmlGpmSampleGet(nvmlDevice_t d, nvmlGpmSample_t s) { (void)d; s->seq = ++sample_seq; return NVML_SUCCESS; }
+nvmlReturn_t nvmlGpmMetricsGet(nvmlGpmMetricsGet_t* r) {
+  if (r->version != 1 || !r->sample1 || !r->sample2 || r->sample2->seq <= r->sample1->seq) return NVML_ERROR_INVALID_ARGUMENT;
+  const char* t = getenv("FAKE_NVML_TENSOR");
+  for (unsigned i = 0; i < r->numMetrics; i++) {
+    nvmlGpmMetric_t* m = &r->metrics[i];
+    m->nvmlReturn = NVML_SUCCESS;
+    switch (m->metricId) {
+      case 2: m->value = 91.0; break;                       /* SM busy */
+      case 3: m->value = 48.5; break;                       /* occupancy */
+      case 5: m->value = t ? atof(t) : 62.5; break;         /* any tensor */
+      case 10: m->value = 33.0; break;                      /* DRAM */
+      case 11: m->nvmlReturn = 3; m->value = 0; break;      /* FP64: not available */
+      case 12: m->value = 7.0; break;
+      case 13: m->value = 1.0; break;
+      case 20: m->value = 120.0; break;
+      case 21: m->value = 80.0; break;
+      case 60: m->value = 900.0 * (r->sample2->seq - r->sample1->seq); break;   /* NVLink RX */
+      case 61: m->value = 1000.0 * (r->sample2->seq - r->sample1->seq); break;  /* NVLink TX */
+      default: m->nvmlReturn = NVML_ERROR_INVALID_ARGUMENT; break;
+    }
+  }
+  return NVML_SUCCESS;
 }

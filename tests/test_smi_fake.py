@@ -210,3 +210,78 @@ def test_subcommand_front_end(fake_nvml):
     assert "580.159.fake" in run("version")
     p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "metric", "-g", "9"], env=e, capture_output=True, text=True)
     assert p.returncode == 2 and "no GPU 9" in p.stderr
+
+
+def test_activity_from_monitoring_samples(fake_nvml):
+    """Activity fields: the first reading brackets 100 ms itself, readings in quick succession share one interval, a later
+    one spans from the previous sample to now (the stand-in reports the number of samples in the interval as NVLink
+    traffic), a metric the device does not report comes back as unsupported, and the watch thread records them."""
+    out = _run("""
+import time
+from rocm_systems_b200.tools.smi import Smi, FIELDS, ACTIVITY_FIELDS
+s = Smi()
+t0 = time.time()
+a = s.activity(0)
+assert 0.09 < time.time() - t0 < 1.0 and 90 <= a['interval_ms'] < 1000
+assert a['tensor_active_pct'] == 40.0 and a['sm_active_pct'] == 91.0 and a['sm_occupancy_pct'] == 48.5 and a['dram_active_pct'] == 33.0
+assert a['fp64_active_pct'] is None and a['pcie_tx_mibs'] == 120.0
+assert a['nvlink_tx_mibs'] == 1000.0 and a['nvlink_rx_mibs'] == 900.0            # two consecutive samples
+assert s.activity(0) == a                                                          # within 50 ms: the same interval again
+assert s.read(0, 'tensor_active') == 40.0 and s.read(0, 'nvlink_rx_mibs') == 900.0
+try:
+    s.read(0, 'fp64_active'); raise SystemExit('fp64 should be unsupported')
+except RuntimeError as e:
+    assert 'not supported' in str(e)
+time.sleep(0.12)
+b = s.activity(0)                                                                  # one new sample: previous -> now
+assert b['nvlink_tx_mibs'] == 1000.0 and 100 <= b['interval_ms'] < 1000
+c = s.activity(1)                                                                  # another device has its own samples
+assert c['nvlink_tx_mibs'] == 1000.0
+assert len(ACTIVITY_FIELDS) == 11 and FIELDS['nvlink_rx_mibs'] == 22
+s.watch_start([0], ['tensor_active', 'power'], period_ms=60, keep=50)
+time.sleep(0.4)
+hist = s.history(0, 'tensor_active')
+s.watch_stop()
+assert len(hist) >= 3 and all(v == 40.0 for _, v in hist), hist
+print('ok')
+""", fake_nvml, {"FAKE_NVML_TENSOR": "40"})
+    assert "ok" in out
+    out = _run("""
+from rocm_systems_b200.tools.smi import Smi
+try:
+    Smi().activity(0); raise SystemExit('should be unsupported')
+except RuntimeError as e:
+    assert 'not supported' in str(e)
+print('ok')
+""", fake_nvml, {"FAKE_NVML_GPM": "0"})
+    assert "ok" in out
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showactivity"], env=e, capture_output=True, text=True)
+    assert p.returncode == 0 and p.stdout.count("tensor 62.5 %") == 2 and "fp64/32/16 n/a/7/1 %" in p.stdout, p.stdout + p.stderr
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "metric", "--activity", "--json", "-g", "1"], env=e, capture_output=True, text=True)
+    import json
+    row = json.loads(p.stdout)[0]
+    assert row["gpu"] == 1 and row["tensor_active_pct"] == 62.5 and row["fp64_active_pct"] is None and row["power_w"] == 200.0
+
+
+def test_telemetry_activity_field_group_and_prometheus(fake_nvml):
+    out = _run("""
+import time
+from rocm_systems_b200.tools.telemetry import Telemetry
+t = Telemetry()
+assert 'tensor_active' in t.field_groups['activity'] and len(t.field_groups['activity']) == 11
+t.create_group('pair', [0, 1])
+t.watch('pair', 'activity', period_ms=60, keep=100)
+time.sleep(0.35)
+vals = t.latest()
+assert vals[0]['tensor_active'] == 62.5 and vals[1]['fp64_active'] is None
+text = t.prometheus()
+assert 'b200_tensor_active_percent{gpu="1",' in text and 'b200_fp64_active_percent{gpu=' not in text
+line = next(l for l in text.splitlines() if l.startswith('b200_nvlink_tx_bytes_per_second{gpu="0"'))
+assert float(line.split()[-1]) % 1048576000.0 == 0                       # MiB/s scaled to bytes per second
+hist = t.history(1, 'dram_active')
+assert len(hist) >= 2 and all(v == 33.0 for _, v in hist)
+t.stop()
+print('ok')
+""", fake_nvml)
+    assert "ok" in out
