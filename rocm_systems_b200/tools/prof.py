@@ -108,6 +108,9 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--sys-trace", action="store_true", help="everything")
     g.add_argument("--sys-sample", type=int, default=0, metavar="PERIOD_MS",
                    help="sample GPU readings (NVML), host CPU / memory and the command's resident set in the background")
+    g.add_argument("--sys-sample-fields", nargs="+", default=None, metavar="FIELD",
+                   help="GPU readings to sample (names of tools/smi.py; default sm_clock power temp gpu_util mem_used); the activity fields "
+                        "tensor_active, sm_active, dram_active, nvlink_tx_mibs, nvlink_rx_mibs, ... put tensor-pipe and NVLink load next to the kernels")
     g.add_argument("--host-sampling", action="store_true", help="sample the call stacks of the host threads")
     g.add_argument("--sampling-freq", type=float, default=100.0, metavar="HZ")
     g.add_argument("--sampling-clock", choices=["cpu", "wall"], default="cpu",
@@ -297,10 +300,15 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if a.output_config:
         Path(prefix + "_config.json").write_text(json.dumps({k: v for k, v in vars(a).items() if k != "command"} | {"command": list(cmd)}, indent=1))
     if a.sys_sample > 0:
-        from .sysmon import SystemSampler
+        from .smi import FIELDS
+        from .sysmon import GPU_FIELDS, SystemSampler
 
+        unknown = [f for f in (a.sys_sample_fields or []) if f not in FIELDS]
+        if unknown:
+            print(f"prof: unknown --sys-sample-fields {unknown}; known: {', '.join(FIELDS)}", file=sys.stderr)
+            return 2
         child = subprocess.Popen(cmd, env=env)
-        with SystemSampler(period_ms=a.sys_sample, pids=[child.pid]) as sampler:
+        with SystemSampler(period_ms=a.sys_sample, pids=[child.pid], gpu_fields=a.sys_sample_fields or GPU_FIELDS) as sampler:
             rc = child.wait()
         sampler.write_csv(prefix + ".sysmon.csv")
     else:

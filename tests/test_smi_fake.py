@@ -285,3 +285,19 @@ t.stop()
 print('ok')
 """, fake_nvml)
     assert "ok" in out
+
+
+def test_launcher_samples_activity_fields_next_to_the_trace(fake_nvml, tmp_path):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2", FAKE_NVML_TENSOR="77")
+    base = [sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "--sys-sample", "40", "-d", str(tmp_path), "-o", "run"]
+    p = subprocess.run([*base, "--sys-sample-fields", "tensor_active", "nvlink_tx_mibs", "power", "--stats", "--", sys.executable, "-c", "import time; time.sleep(0.5)"],
+                       env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr
+    import sqlite3
+
+    db = sqlite3.connect(str(tmp_path / "run.db"))
+    got = dict(db.execute("select s.value, avg(c.value) from counter_sample c join string s on s.id = c.name_id group by s.value").fetchall())
+    assert got["gpu_tensor_active"] == 77.0 and got["gpu_power"] == 200.0 and got["gpu_nvlink_tx_mibs"] >= 1000.0 and "gpu_sm_clock" not in got
+    assert "gpu_tensor_active" in p.stdout                                       # the sampled-counters table of --stats
+    p = subprocess.run([*base, "--sys-sample-fields", "nope", "--", "true"], env=e, capture_output=True, text=True, timeout=60)
+    assert p.returncode == 2 and "unknown --sys-sample-fields" in p.stderr
