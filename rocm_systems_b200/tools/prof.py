@@ -76,6 +76,13 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
             raise SystemExit(f"{lib} is missing: run `python -m rocm_systems_b200.utils.build`")
         old = env.get("KOKKOS_TOOLS_LIBS", "")
         env["KOKKOS_TOOLS_LIBS"] = f"{lib};{old}" if old else str(lib)
+    if a.openmp_trace:
+        lib = PKG / "lib" / "libb200ompt.so"
+        if not lib.exists():
+            raise SystemExit(f"{lib} is missing: run `python -m rocm_systems_b200.utils.build`")
+        old = env.get("OMP_TOOL_LIBRARIES", "")
+        env["OMP_TOOL_LIBRARIES"] = f"{lib}:{old}" if old else str(lib)
+        env["OMP_TOOL"] = "enabled"
     if a.preload:
         old = env.get("LD_PRELOAD", "")
         env["LD_PRELOAD"] = ":".join([*a.preload, old] if old else a.preload)
@@ -116,6 +123,8 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--sampling-clock", choices=["cpu", "wall"], default="cpu",
                    help="cpu: samples in proportion to CPU time used; wall: every thread every period, blocked ones included")
     g.add_argument("--sampling-delay", type=float, default=0.0, metavar="SECONDS")
+    g.add_argument("--openmp-trace", action="store_true", help="OpenMP parallel regions, tasks, worksharing, barriers and target regions as marker ranges "
+                   "(sets OMP_TOOL_LIBRARIES to the OMPT tool; implies --marker-trace)")
     g = ap.add_argument_group("filtering")
     g.add_argument("--kernel-include-regex", default="")
     g.add_argument("--kernel-exclude-regex", default="", help="drop kernels whose name matches (applied when the trace is imported)")
@@ -281,7 +290,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if not cmd:
         print("prof: no command given (put it after --)", file=sys.stderr)
         return 2
-    if a.kokkos_trace:
+    if a.kokkos_trace or a.openmp_trace:
         a.marker_trace = True
     if a.sys_trace:
         a.kernel_trace = a.memory_copy_trace = a.runtime_trace = a.sync_trace = a.coll_trace = a.marker_trace = True

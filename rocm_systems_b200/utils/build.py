@@ -160,6 +160,19 @@ def build_kokkosp() -> Path | None:
     return out
 
 
+def build_ompt() -> Path | None:
+    """The OpenMP tool (OMPT) that turns OpenMP regions into marker ranges; needs the OMPT header the CUDA toolkit ships."""
+    src = CSRC / "trace" / "ompt.cc"
+    cuda_inc = Path(NVCC).resolve().parents[1] / "include"
+    if not src.exists() or not (cuda_inc / "Openmp" / "omp-tools.h").exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200ompt.so"
+    if not out.exists() or out.stat().st_mtime_ns < src.stat().st_mtime_ns:
+        _run(["g++", "-O2", "-g", "-std=c++17", "-fPIC", "-shared", f"-I{cuda_inc}", str(src), "-o", str(out), "-ldl"])
+    return out
+
+
 def build_causal() -> Path | None:
     """The causal profiler (preload library, plain C++, no CUDA)."""
     src = CSRC / "prof" / "causal.cc"
@@ -267,6 +280,8 @@ def build_all(verbose_ptxas: bool = False) -> dict:
     res["sampler"] = str(samp) if samp else None
     kk = build_kokkosp()
     res["kokkosp"] = str(kk) if kk else None
+    om = build_ompt()
+    res["ompt"] = str(om) if om else None
     causal = build_causal()
     res["causal"] = str(causal) if causal else None
     ext = build_torch_ext()
