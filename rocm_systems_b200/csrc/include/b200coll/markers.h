@@ -26,6 +26,9 @@ int b200txRangePush(const char* message);        /* returns the new nesting dept
 int b200txRangePop(void);                        /* returns the depth popped, -1 when nothing was open */
 uint64_t b200txRangeStart(const char* message);  /* ranges that may end on another thread */
 void b200txRangeStop(uint64_t id);
+/* A range that is already over, with its times on CLOCK_MONOTONIC (for tools that decide afterwards what is worth
+ * recording). Returns the range id, 0 when recording is off. */
+uint64_t b200txRangeAt(const char* message, uint64_t beginNs, uint64_t endNs);
 /* Recording is off until enabled (or B200COLL_TRACE=1 is in the environment). */
 void b200txEnable(int on);
 /* Copies up to `max` finished records; returns how many exist. */

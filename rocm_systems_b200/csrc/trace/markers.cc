@@ -112,6 +112,16 @@ void b200txRangeStop(uint64_t id) {
   gOpen.erase(it);
 }
 
+uint64_t b200txRangeAt(const char* message, uint64_t beginNs, uint64_t endNs) {
+  if (!enabled()) return 0;
+  b200tx_record_t r = make(message, gNextId.fetch_add(1), (uint32_t)tlsStack.size());
+  r.beginNs = beginNs;
+  r.endNs = endNs < beginNs ? beginNs : endNs;
+  std::lock_guard<std::mutex> lk(gMu);
+  gDone.push_back(r);
+  return r.id;
+}
+
 uint64_t b200txGet(b200tx_record_t* out, uint64_t max) {
   std::lock_guard<std::mutex> lk(gMu);
   const uint64_t n = gDone.size() < max ? gDone.size() : max;

@@ -62,6 +62,9 @@ TOOL_SETTINGS = [
     ("causal", "B200CAUSAL_VERBOSE", "0", "announce every experiment on stderr"),
     ("kokkosp", "B200KOKKOSP_MEMORY_EVENTS", "0", "a marker per Kokkos allocation and deallocation"),
     ("kokkosp", "B200KOKKOSP_VERBOSE", "0", "say on stderr that the connector was loaded"),
+    ("instrument", "B200INSTR_PREFIX", "", "prefix of the function statistics and coverage files; setting it switches libb200instr.so on"),
+    ("instrument", "B200INSTR_MIN_US", "100", "calls at least this long become marker ranges (negative: none)"),
+    ("instrument", "B200INSTR_MAX_DEPTH", "64", "calls nested deeper than this are counted, not timed"),
     ("ompt", "B200OMPT_VERBOSE", "0", "say on stderr what the OpenMP runtime offered and how many callbacks it accepted"),
     ("smi", "B200SMI_NVML_LIBRARY", "libnvidia-ml.so.1", "NVML library to load (tests point it at a stand-in)"),
     ("smi", "B200SMI_ALLOW_SET", "0", "must be 1, together with --allow-set, before any setter acts"),
@@ -87,7 +90,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--changed", action="store_true", help="only settings whose value differs from the default")
     ap.add_argument("--all", action="store_true", help="also the settings of the tool libraries and tools")
-    ap.add_argument("--component", nargs="+", default=None, help="only these components (coll, prof, sample, causal, kokkosp, ompt, smi, perf, model); implies --all")
+    ap.add_argument("--component", nargs="+", default=None, help="only these components (coll, prof, sample, causal, kokkosp, ompt, instrument, smi, perf, model); implies --all")
     a = ap.parse_args(argv)
     rows = [dict(r, component=r.get("component", "coll")) for r in settings()]
     if a.all or a.component:

@@ -173,6 +173,18 @@ def build_ompt() -> Path | None:
     return out
 
 
+def build_instrument() -> Path | None:
+    """Entry / exit hooks for code compiled with -finstrument-functions: function statistics, marker ranges, coverage."""
+    src = CSRC / "prof" / "instrument.cc"
+    if not src.exists():
+        return None
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libb200instr.so"
+    if not out.exists() or out.stat().st_mtime_ns < src.stat().st_mtime_ns:
+        _run(["g++", "-O2", "-g", "-std=c++17", "-fPIC", "-shared", str(src), "-o", str(out), "-ldl"])
+    return out
+
+
 def build_causal() -> Path | None:
     """The causal profiler (preload library, plain C++, no CUDA)."""
     src = CSRC / "prof" / "causal.cc"
@@ -282,6 +294,8 @@ def build_all(verbose_ptxas: bool = False) -> dict:
     res["kokkosp"] = str(kk) if kk else None
     om = build_ompt()
     res["ompt"] = str(om) if om else None
+    ins = build_instrument()
+    res["instrument"] = str(ins) if ins else None
     causal = build_causal()
     res["causal"] = str(causal) if causal else None
     ext = build_torch_ext()

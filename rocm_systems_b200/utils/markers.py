@@ -34,6 +34,8 @@ def _l():
         lib.b200txRangeStart.argtypes = [ctypes.c_char_p]
         lib.b200txRangeStart.restype = ctypes.c_uint64
         lib.b200txRangeStop.argtypes = [ctypes.c_uint64]
+        lib.b200txRangeAt.argtypes = [ctypes.c_char_p, ctypes.c_uint64, ctypes.c_uint64]
+        lib.b200txRangeAt.restype = ctypes.c_uint64
         lib.b200txEnable.argtypes = [ctypes.c_int]
         lib.b200txGet.argtypes = [ctypes.c_void_p, ctypes.c_uint64]
         lib.b200txGet.restype = ctypes.c_uint64
@@ -52,6 +54,11 @@ def mark(message: str) -> None:
 
 def range_push(message: str) -> int:
     return int(_l().b200txRangePush(message.encode()))
+
+
+def range_at(message: str, begin_ns: int, end_ns: int) -> int:
+    """Records a range that is already over (times on ``time.monotonic_ns()``'s clock); returns its id, 0 when recording is off."""
+    return int(_l().b200txRangeAt(message.encode(), int(begin_ns), int(end_ns)))
 
 
 def range_pop() -> int:

@@ -49,18 +49,20 @@ with markers.range('outer'):
         markers.mark('point')
 rid = markers.range_start('async')
 markers.range_stop(rid)
+assert markers.range_at('earlier', 1000, 3000) > rid
 recs = markers.records()
 names = [r['message'] for r in recs]
-assert names == ['point', 'inner', 'outer', 'async'], names
+assert names == ['point', 'inner', 'outer', 'async', 'earlier'], names
+assert recs[-1]['begin_ns'] == 1000 and recs[-1]['end_ns'] == 3000
 by = {{r['message']: r for r in recs}}
 assert by['inner']['depth'] == 1 and by['outer']['depth'] == 0 and by['point']['depth'] == 2
 assert by['outer']['begin_ns'] <= by['inner']['begin_ns'] <= by['inner']['end_ns'] <= by['outer']['end_ns']
-assert markers.write_csv(r'{tmp_path}/m.csv') == 4
+assert markers.write_csv(r'{tmp_path}/m.csv') == 5
 assert 'b200coll' in markers.build_info()
 print('ok')
 """)
     assert "ok" in out
-    assert (tmp_path / "m.csv").read_text().count("MARKER_API") == 4
+    assert (tmp_path / "m.csv").read_text().count("MARKER_API") == 5
 
 
 def test_markers_written_at_exit_under_trace_env(tmp_path):
