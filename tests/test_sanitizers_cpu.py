@@ -116,3 +116,28 @@ def test_planner_and_tuning_loader_under_sanitizers(tmp_path):
         r = subprocess.run([str(exe)], env=e, capture_output=True, text=True, timeout=300)
         assert r.returncode == 0 and "planner under sanitizers: 0 bad" in r.stdout, (name, (r.stdout + r.stderr)[-3000:])
         assert "AddressSanitizer" not in r.stderr and "runtime error" not in r.stderr, (name, r.stderr[-3000:])
+
+
+def test_instrumentation_hooks_and_kokkos_connector_under_asan(tmp_path):
+    """The entry / exit hooks (lock-free function table, per-thread stacks, symbol-table reader) with their instrumented
+    target, and the Kokkos connector with its driver, all built with ASan + UBSan in one process each: no report, same
+    results."""
+    san = ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer", "-g", "-O1", "-std=c++17"]
+    exe = tmp_path / "instr_asan"
+    p = subprocess.run(["g++", *san, "-finstrument-functions", "-finstrument-functions-exclude-file-list=/usr/include,/usr/lib",
+                        str(ROOT / "tests" / "native" / "instrument_target.cc"), str(CSRC / "prof" / "instrument.cc"), "-o", str(exe), "-lpthread", "-ldl"],
+                       capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    env = dict(os.environ, B200INSTR_PREFIX=str(tmp_path / "i"), B200INSTR_MIN_US="-1", ASAN_OPTIONS="detect_leaks=0:abort_on_error=0")
+    r = subprocess.run([str(exe)], env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "instrument target done 3" in r.stdout and "ERROR" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
+    rows = next(tmp_path.glob("i.*.functions.csv")).read_text()
+    assert '"inner(int)",7,' in rows and '"outer()",3,' in rows
+    exe = tmp_path / "kk_asan"
+    p = subprocess.run(["g++", *san, "-rdynamic", str(ROOT / "tests" / "native" / "kokkosp_driver.cc"), "-o", str(exe), "-ldl", "-lpthread"], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    lib = tmp_path / "libkk_asan.so"
+    p = subprocess.run(["g++", *san, "-fPIC", "-shared", str(CSRC / "trace" / "kokkosp.cc"), "-o", str(lib), "-ldl"], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    r = subprocess.run([str(exe), str(lib)], env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0"), capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.startswith("ids ") and "ERROR" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
