@@ -506,6 +506,37 @@ def format_table(names: Sequence[str], rows: Iterable[Sequence], max_width: int 
     return "\n".join(lines)
 
 
+def diff(base: "TraceDB", other: "TraceDB", domains: Sequence[str] = ("KERNEL_DISPATCH", "COLLECTIVE", "MEMORY_COPY"), min_change: float = 0.0,
+         top: int = 30) -> List[dict]:
+    """Two traces of the same program side by side: per (domain, name) the calls, total and mean time in each and the change
+    of the total in percent of the base; rows sorted by the absolute change in time, names that exist on one side only
+    included. ``min_change`` (percent) hides rows that moved less. The question it answers is the one a timing regression
+    asks: which kernel or collective got slower, and by how much of the whole."""
+    def table(db):
+        acc: dict = {}
+        for domain, name, dur in db.domain_rows():
+            if domain in domains:
+                a = acc.setdefault((domain, name), [0, 0])
+                a[0] += 1
+                a[1] += dur or 0
+        return acc
+
+    a, b = table(base), table(other)
+    whole = sum(v[1] for v in a.values()) or 1
+    out = []
+    for key in set(a) | set(b):
+        ca, ta = a.get(key, (0, 0))
+        cb, tb = b.get(key, (0, 0))
+        change = 100.0 * (tb - ta) / ta if ta else float("inf")
+        if ta and abs(change) < min_change:
+            continue
+        out.append({"domain": key[0], "name": key[1], "base_calls": ca, "calls": cb, "base_total_ns": ta, "total_ns": tb,
+                    "base_mean_ns": ta / ca if ca else 0.0, "mean_ns": tb / cb if cb else 0.0, "change_percent": change,
+                    "share_of_base_percent": 100.0 * (tb - ta) / whole})
+    out.sort(key=lambda r: -abs(r["total_ns"] - r["base_total_ns"]))
+    return out[:top]
+
+
 UNITS = {"nsec": 1.0, "usec": 1e3, "msec": 1e6, "sec": 1e9}
 
 
@@ -558,6 +589,18 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("db")
     p.add_argument("--top", type=int, default=15)
     p.add_argument("--json", action="store_true")
+    p.add_argument("--per-domain", action="store_true", help="statistics of every domain on its own")
+    p.add_argument("--groups", nargs="+", default=[], metavar="REGEX", help="statistics over unions of domains")
+    p.add_argument("--units", choices=list(UNITS), default="nsec")
+    p = sub.add_parser("diff", help="two traces of one program: what got slower or faster, per kernel / collective / copy")
+    p.add_argument("base")
+    p.add_argument("other")
+    p.add_argument("--domains", nargs="+", default=["KERNEL_DISPATCH", "COLLECTIVE", "MEMORY_COPY"])
+    p.add_argument("--min-change", type=float, default=0.0, metavar="PERCENT")
+    p.add_argument("--top", type=int, default=30)
+    p.add_argument("--units", choices=list(UNITS), default="usec")
+    p.add_argument("--json", action="store_true")
+    p.add_argument("--fail-above", type=float, default=None, metavar="PERCENT", help="exit code 1 when the summed time of the chosen domains grew by more")
     p = sub.add_parser("query")
     p.add_argument("db")
     p.add_argument("sql")
@@ -578,7 +621,29 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     elif a.cmd == "summary":
         with TraceDB(a.db) as db:
             s = db.summary(a.top)
+            if a.per_domain or a.groups:
+                extra = db.domain_summaries(a.top, a.groups)
+                if not a.per_domain:
+                    extra["domains"] = {}
+                s.update(extra)
+        s = scale_units(s, a.units)
         print(json.dumps(s, indent=1)) if a.json else print_summary(s)
+    elif a.cmd == "diff":
+        with TraceDB(a.base) as x, TraceDB(a.other) as y:
+            rows = diff(x, y, a.domains, a.min_change, a.top)
+            ta = sum(d for dom, _, d in x.domain_rows() if dom in a.domains)
+            tb = sum(d for dom, _, d in y.domain_rows() if dom in a.domains)
+        growth = 100.0 * (tb - ta) / ta if ta else 0.0
+        if a.json:
+            print(json.dumps({"base_total_ns": ta, "total_ns": tb, "change_percent": growth, "rows": rows}, indent=1))
+        else:
+            scaled = scale_units(rows, a.units)
+            if scaled:
+                names = list(scaled[0].keys())
+                print(format_table(names, [[r[n] for n in names] for r in scaled]))
+            print(f"\ntotal of {', '.join(a.domains)}: {ta / UNITS[a.units]:.2f} -> {tb / UNITS[a.units]:.2f} {a.units} ({growth:+.2f} %)")
+        if a.fail_above is not None and growth > a.fail_above:
+            return 1
     elif a.cmd == "query":
         with TraceDB(a.db) as db:
             names, rows = db.query(a.sql)

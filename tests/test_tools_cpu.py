@@ -528,6 +528,40 @@ def test_tracedb_iteration_ranges_domains_groups_and_units(tmp_path):
         assert db.query("select name, start_ns from kernels")[1] == [("gemmKernel<Cfg>", 6000)]
 
 
+def test_tracedb_diff_names_what_got_slower(tmp_path, capsys):
+    """Two traces of one program: the slower kernel leads the table, a kernel that exists on one side only is listed, the
+    threshold hides what did not move, and --fail-above turns the comparison into a check."""
+    from rocm_systems_b200.tools import tracedb
+
+    slow = KERNEL_CSV.replace(",6000,9000,", ",6000,12000,").replace('"rmsnorm",3,9500,10000', '"rmsnorm2",3,12500,13000')
+    for name, text in (("a", KERNEL_CSV), ("b", slow)):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "t.100_kernel_trace.csv").write_text(text)
+        (d / "t.rank0.csv").write_text(COLL_CSV)
+        assert tracedb.main(["import", str(d / "t.100_kernel_trace.csv"), str(d / "t.rank0.csv"), "-o", str(d / "t.db")]) == 0
+    capsys.readouterr()
+    with tracedb.TraceDB(str(tmp_path / "a" / "t.db")) as x, tracedb.TraceDB(str(tmp_path / "b" / "t.db")) as y:
+        rows = tracedb.diff(x, y)
+        assert [r["name"] for r in rows[:3]] == ["gemmKernel<Cfg>", "rmsnorm", "rmsnorm2"] or [r["name"] for r in rows[:3]] == ["gemmKernel<Cfg>", "rmsnorm2", "rmsnorm"]
+        g = rows[0]
+        assert g["base_total_ns"] == 7000 and g["total_ns"] == 10000 and g["change_percent"] == pytest.approx(100 * 3000 / 7000) and g["calls"] == 2
+        assert g["share_of_base_percent"] == pytest.approx(100 * 3000 / 25500)
+        gone = next(r for r in rows if r["name"] == "rmsnorm")
+        assert gone["calls"] == 0 and gone["change_percent"] == -100.0
+        new = next(r for r in rows if r["name"] == "rmsnorm2")
+        assert new["base_calls"] == 0 and new["change_percent"] == float("inf")
+        assert {r["name"] for r in tracedb.diff(x, y, min_change=50.0)} == {"rmsnorm", "rmsnorm2"}        # the collective did not move; the GEMM moved 43 %
+        assert [r["name"] for r in tracedb.diff(x, y, domains=["COLLECTIVE"])] == ["ncclAllReduce"]
+    assert tracedb.main(["diff", str(tmp_path / "a" / "t.db"), str(tmp_path / "b" / "t.db"), "--fail-above", "20"]) == 0
+    out = capsys.readouterr().out
+    assert "gemmKernel<Cfg>" in out and "base_total_usec" in out and "(+11.76 %)" in out                    # 25500 -> 28500 ns
+    assert tracedb.main(["diff", str(tmp_path / "a" / "t.db"), str(tmp_path / "b" / "t.db"), "--fail-above", "5", "--json"]) == 1
+    assert json.loads(capsys.readouterr().out)["change_percent"] == pytest.approx(100 * 3000 / 25500)
+    assert tracedb.main(["summary", str(tmp_path / "a" / "t.db"), "--per-domain", "--units", "usec"]) == 0
+    assert "== DOMAIN KERNEL_DISPATCH ==" in capsys.readouterr().out
+
+
 def test_prof_launcher_summary_and_environment_options(tmp_path, capsys):
     """--kokkos-trace, --preload and --echo reach the environment of the command; --output-config records the pass."""
     from rocm_systems_b200.tools import prof
