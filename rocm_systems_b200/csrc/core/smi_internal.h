@@ -42,6 +42,16 @@ struct NvmlFns {
   nvmlReturn_t (*supportedEvents)(nvmlDevice_t, unsigned long long*) = nullptr;
   nvmlReturn_t (*registerEvents)(nvmlDevice_t, unsigned long long, nvmlEventSet_t) = nullptr;
   nvmlReturn_t (*eventSetWait)(nvmlEventSet_t, nvmlEventData_t*, unsigned int) = nullptr;
+  nvmlReturn_t (*serial)(nvmlDevice_t, char*, unsigned int) = nullptr;
+  nvmlReturn_t (*partNumber)(nvmlDevice_t, char*, unsigned int) = nullptr;
+  nvmlReturn_t (*vbios)(nvmlDevice_t, char*, unsigned int) = nullptr;
+  nvmlReturn_t (*inforomImage)(nvmlDevice_t, char*, unsigned int) = nullptr;
+  nvmlReturn_t (*pstate)(nvmlDevice_t, nvmlPstates_t*) = nullptr;
+  nvmlReturn_t (*powerConstraints)(nvmlDevice_t, unsigned int*, unsigned int*) = nullptr;
+  nvmlReturn_t (*energy)(nvmlDevice_t, unsigned long long*) = nullptr;
+  nvmlReturn_t (*remappedRows)(nvmlDevice_t, unsigned int*, unsigned int*, unsigned int*, unsigned int*) = nullptr;
+  nvmlReturn_t (*setLockedClocks)(nvmlDevice_t, unsigned int, unsigned int) = nullptr;
+  nvmlReturn_t (*resetLockedClocks)(nvmlDevice_t) = nullptr;
   nvmlReturn_t (*gpmSupport)(nvmlDevice_t, nvmlGpmSupport_t*) = nullptr;
   nvmlReturn_t (*gpmSampleAlloc)(nvmlGpmSample_t*) = nullptr;
   nvmlReturn_t (*gpmSampleFree)(nvmlGpmSample_t) = nullptr;

@@ -75,6 +75,16 @@ static bool loadNvml() {
   sym("nvmlDeviceGetSupportedEventTypes", &gN.supportedEvents, false);
   sym("nvmlDeviceRegisterEvents", &gN.registerEvents, false);
   sym("nvmlEventSetWait_v2", &gN.eventSetWait, false);
+  sym("nvmlDeviceGetSerial", &gN.serial, false);
+  sym("nvmlDeviceGetBoardPartNumber", &gN.partNumber, false);
+  sym("nvmlDeviceGetVbiosVersion", &gN.vbios, false);
+  sym("nvmlDeviceGetInforomImageVersion", &gN.inforomImage, false);
+  sym("nvmlDeviceGetPerformanceState", &gN.pstate, false);
+  sym("nvmlDeviceGetPowerManagementLimitConstraints", &gN.powerConstraints, false);
+  sym("nvmlDeviceGetTotalEnergyConsumption", &gN.energy, false);
+  sym("nvmlDeviceGetRemappedRows", &gN.remappedRows, false);
+  sym("nvmlDeviceSetGpuLockedClocks", &gN.setLockedClocks, false);
+  sym("nvmlDeviceResetGpuLockedClocks", &gN.resetLockedClocks, false);
   sym("nvmlGpmQueryDeviceSupport", &gN.gpmSupport, false);
   sym("nvmlGpmSampleAlloc", &gN.gpmSampleAlloc, false);
   sym("nvmlGpmSampleFree", &gN.gpmSampleFree, false);
@@ -386,6 +396,62 @@ b200smi_status_t b200smi_set_power_limit(int device, uint32_t milliwatt, int all
   if (st != B200SMI_OK) return st;
   if (!gN.setPowerLimit) return B200SMI_ERR_NOT_SUPPORTED;
   return gN.setPowerLimit(h, milliwatt) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+static bool settersAllowed(int allow) {
+  const char* env = getenv("B200SMI_ALLOW_SET");
+  return allow && env && strcmp(env, "1") == 0;
+}
+
+b200smi_status_t b200smi_set_locked_clocks(int device, uint32_t minMhz, uint32_t maxMhz, int allow) {
+  if (!settersAllowed(allow)) return B200SMI_ERR_PERMISSION;
+  if (minMhz == 0 || maxMhz < minMhz) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.setLockedClocks) return B200SMI_ERR_NOT_SUPPORTED;
+  return gN.setLockedClocks(h, minMhz, maxMhz) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+b200smi_status_t b200smi_reset_locked_clocks(int device, int allow) {
+  if (!settersAllowed(allow)) return B200SMI_ERR_PERMISSION;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.resetLockedClocks) return B200SMI_ERR_NOT_SUPPORTED;
+  return gN.resetLockedClocks(h) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+b200smi_status_t b200smi_identity(int device, b200smi_identity_t* out) {
+  if (!out) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  memset(out, 0, sizeof(*out));
+  out->performanceState = -1;
+  out->powerLimitMinMilliwatt = out->powerLimitMaxMilliwatt = out->energyMillijoule = -1;
+  out->remappedCorrectable = out->remappedUncorrectable = out->remapPending = out->remapFailed = -1;
+  if (gN.serial && gN.serial(h, out->serial, sizeof(out->serial)) != NVML_SUCCESS) out->serial[0] = 0;
+  if (gN.partNumber && gN.partNumber(h, out->partNumber, sizeof(out->partNumber)) != NVML_SUCCESS) out->partNumber[0] = 0;
+  if (gN.vbios && gN.vbios(h, out->vbios, sizeof(out->vbios)) != NVML_SUCCESS) out->vbios[0] = 0;
+  if (gN.inforomImage && gN.inforomImage(h, out->inforomImage, sizeof(out->inforomImage)) != NVML_SUCCESS) out->inforomImage[0] = 0;
+  nvmlPstates_t ps;
+  if (gN.pstate && gN.pstate(h, &ps) == NVML_SUCCESS && ps != NVML_PSTATE_UNKNOWN) out->performanceState = (int)ps;
+  unsigned int lo = 0, hi = 0;
+  if (gN.powerConstraints && gN.powerConstraints(h, &lo, &hi) == NVML_SUCCESS) {
+    out->powerLimitMinMilliwatt = lo;
+    out->powerLimitMaxMilliwatt = hi;
+  }
+  unsigned long long mj = 0;
+  if (gN.energy && gN.energy(h, &mj) == NVML_SUCCESS) out->energyMillijoule = (int64_t)mj;
+  unsigned int corr = 0, unc = 0, pending = 0, failed = 0;
+  if (gN.remappedRows && gN.remappedRows(h, &corr, &unc, &pending, &failed) == NVML_SUCCESS) {
+    out->remappedCorrectable = (int)corr;
+    out->remappedUncorrectable = (int)unc;
+    out->remapPending = (int)pending;
+    out->remapFailed = (int)failed;
+  }
+  return B200SMI_OK;
 }
 
 }  // extern "C"

@@ -107,6 +107,19 @@ b200smi_status_t b200smi_pcie(int device, uint32_t* generation, uint32_t* width)
 typedef struct { int computeMode, persistence, mig, ecc; } b200smi_modes_t;
 b200smi_status_t b200smi_modes(int device, b200smi_modes_t* out);
 
+/* Identity and lifetime readings (rocm-smi: --showserial, --showvbios, --showperflevel, --showmaxpower, --showenergycounter,
+ * --showretiredpages): serial and part numbers, firmware versions, performance state (0 = fastest), the range the power limit
+ * may be set in, energy drawn since the driver was loaded, and rows of device memory remapped after errors. A string the
+ * driver does not report is empty, a number is -1. */
+typedef struct {
+  char serial[32], partNumber[64], vbios[32], inforomImage[32];
+  int performanceState;
+  int64_t powerLimitMinMilliwatt, powerLimitMaxMilliwatt;
+  int64_t energyMillijoule;
+  int remappedCorrectable, remappedUncorrectable, remapPending, remapFailed;
+} b200smi_identity_t;
+b200smi_status_t b200smi_identity(int device, b200smi_identity_t* out);
+
 /* Asynchronous events of all devices (read only). Types are NVML's bits. */
 #define B200SMI_EVENT_ECC_SINGLE 0x1ull
 #define B200SMI_EVENT_ECC_DOUBLE 0x2ull
@@ -134,6 +147,10 @@ b200smi_status_t b200smi_policy_clear(void);
 b200smi_status_t b200smi_health(int device, int* level, char* reason, int reasonLen);
 /* Setter (off unless allowed twice, see the top of this header). */
 b200smi_status_t b200smi_set_power_limit(int device, uint32_t milliwatt, int allow);
+/* Locks the SM clock into [minMhz, maxMhz], or (reset) hands it back to the driver. The same double gate as the power limit;
+ * a lock outlasts the process, so whoever sets one resets it. */
+b200smi_status_t b200smi_set_locked_clocks(int device, uint32_t minMhz, uint32_t maxMhz, int allow);
+b200smi_status_t b200smi_reset_locked_clocks(int device, int allow);
 
 #ifdef __cplusplus
 }

@@ -6,7 +6,7 @@ showTypeTopology :3372, showNodesBw :3460) on top of the native ``b200smi_*`` AP
     python -m rocm_systems_b200.tools.smi --showtopo [--json]
     python -m rocm_systems_b200.tools.smi metric -g 0 1 --csv        # subcommands: version list static metric topology process monitor event
 
-Setters (``--setpowerlimit``) do nothing unless ``--allow-set`` is given AND B200SMI_ALLOW_SET=1 is
+Setters (``--setpowerlimit``, ``--setclocks``, ``--resetclocks``) do nothing unless ``--allow-set`` is given AND B200SMI_ALLOW_SET=1 is
 in the environment; GPUs on shared hosts must be left as they were found.
 """
 from __future__ import annotations
@@ -74,6 +74,13 @@ class Event(ctypes.Structure):
 
 EVENT_NAMES = {0x1: "ecc_single_bit", 0x2: "ecc_double_bit", 0x4: "pstate", 0x8: "xid", 0x10: "clock", 0x80: "power_source"}
 ERR_TIMEOUT = 6
+
+
+class Identity(ctypes.Structure):
+    _fields_ = [("serial", ctypes.c_char * 32), ("partNumber", ctypes.c_char * 64), ("vbios", ctypes.c_char * 32), ("inforomImage", ctypes.c_char * 32),
+                ("performanceState", ctypes.c_int), ("powerLimitMinMilliwatt", ctypes.c_int64), ("powerLimitMaxMilliwatt", ctypes.c_int64),
+                ("energyMillijoule", ctypes.c_int64), ("remappedCorrectable", ctypes.c_int), ("remappedUncorrectable", ctypes.c_int),
+                ("remapPending", ctypes.c_int), ("remapFailed", ctypes.c_int)]
 
 
 class Activity(ctypes.Structure):
@@ -241,6 +248,30 @@ class Smi:
     def set_power_limit(self, dev: int, milliwatt: int, allow: bool) -> None:
         self._ck(self.lib.b200smi_set_power_limit(dev, milliwatt, int(allow)))
 
+    def set_locked_clocks(self, dev: int, min_mhz: int, max_mhz: int, allow: bool) -> None:
+        """Locks the SM clock into a range (outlasts the process: reset it afterwards). Refused unless allowed twice over."""
+        self.lib.b200smi_set_locked_clocks.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int]
+        self._ck(self.lib.b200smi_set_locked_clocks(dev, min_mhz, max_mhz, int(allow)))
+
+    def reset_locked_clocks(self, dev: int, allow: bool) -> None:
+        self.lib.b200smi_reset_locked_clocks.argtypes = [ctypes.c_int, ctypes.c_int]
+        self._ck(self.lib.b200smi_reset_locked_clocks(dev, int(allow)))
+
+    def identity(self, dev: int) -> dict:
+        """Serial and part number, firmware versions, performance state, settable power range (W), energy since the driver
+        loaded (J), remapped memory rows; ``None`` where the driver reports nothing."""
+        i = Identity()
+        self.lib.b200smi_identity.argtypes = [ctypes.c_int, ctypes.POINTER(Identity)]
+        self._ck(self.lib.b200smi_identity(dev, ctypes.byref(i)))
+        text = lambda b: b.decode(errors="replace") or None  # noqa: E731
+        num = lambda v, scale=1: None if v < 0 else v / scale  # noqa: E731
+        return {"serial": text(i.serial), "part_number": text(i.partNumber), "vbios": text(i.vbios), "inforom_image": text(i.inforomImage),
+                "performance_state": None if i.performanceState < 0 else i.performanceState,
+                "power_limit_min_w": num(i.powerLimitMinMilliwatt, 1000), "power_limit_max_w": num(i.powerLimitMaxMilliwatt, 1000),
+                "energy_j": num(i.energyMillijoule, 1000),
+                "remapped_rows": None if i.remappedCorrectable < 0 else {"correctable": i.remappedCorrectable, "uncorrectable": i.remappedUncorrectable,
+                                                                          "pending": bool(i.remapPending), "failed": bool(i.remapFailed)}}
+
 
 def _matrix(smi: Smi, key: str, n: int):
     return [[smi.link(i, j)[key] for j in range(n)] for i in range(n)]
@@ -320,8 +351,10 @@ def _sub_main(argv) -> int:
     elif a.cmd == "static":
         rows = []
         for g in gpus:
-            d, m, pc = smi.info(g), smi.modes(g), smi.pcie(g)
-            rows.append({"gpu": g, "name": d["name"], "bus_id": d["busId"], "uuid": d["uuid"], "memory_total_gib": round(d["memTotalBytes"] / 2**30, 1),
+            d, m, pc, ident = smi.info(g), smi.modes(g), smi.pcie(g), smi.identity(g)
+            rows.append({"gpu": g, "name": d["name"], "bus_id": d["busId"], "uuid": d["uuid"], "serial": ident["serial"], "part_number": ident["part_number"],
+                         "vbios": ident["vbios"], "power_limit_range_w": None if ident["power_limit_max_w"] is None else
+                         f"{ident['power_limit_min_w']:.0f}-{ident['power_limit_max_w']:.0f}", "memory_total_gib": round(d["memTotalBytes"] / 2**30, 1),
                          "sm_clock_max_mhz": d["smClockMaxMhz"], "memory_clock_max_mhz": d["memClockMaxMhz"], "power_limit_w": d["powerLimitMilliwatt"] / 1000,
                          "pcie_generation": pc["generation"], "pcie_width": pc["width"], "nvlink_links": d["nvlinkCount"], "compute_mode": m["compute_mode"],
                          "persistence": m["persistence"], "mig": m["mig"], "ecc": m["ecc"]})
@@ -402,7 +435,13 @@ def main(argv=None) -> int:
     ap.add_argument("--showevents", type=float, default=0.0, metavar="SECONDS",
                     help="print XID / ECC / power-state / clock events as they happen; stops after this long without one")
     ap.add_argument("--json", action="store_true")
+    for flag, help_ in (("--showserial", "serial and part number"), ("--showvbios", "VBIOS version"), ("--showfwinfo", "VBIOS and InfoROM image versions"),
+                        ("--showperflevel", "performance state (P0 = fastest)"), ("--showmaxpower", "range the power limit can be set in"),
+                        ("--showenergycounter", "energy drawn since the driver was loaded"), ("--showretiredpages", "rows of device memory remapped after errors")):
+        ap.add_argument(flag, action="store_true", help=help_ + " (one line per GPU)")
     ap.add_argument("--setpowerlimit", nargs=2, metavar=("GPU", "WATTS"))
+    ap.add_argument("--setclocks", nargs=3, metavar=("GPU", "MIN_MHZ", "MAX_MHZ"), help="lock the SM clock into a range (stays until --resetclocks)")
+    ap.add_argument("--resetclocks", metavar="GPU", help="hand the SM clock back to the driver")
     ap.add_argument("--allow-set", action="store_true", help="required (with B200SMI_ALLOW_SET=1) before any setter acts")
     a = ap.parse_args(argv)
     try:
@@ -419,6 +458,16 @@ def main(argv=None) -> int:
         except RuntimeError as e:
             print(f"b200-smi: {e}", file=sys.stderr)
             return 2
+    for what, act in (("setclocks", lambda v: smi.set_locked_clocks(int(v[0]), int(v[1]), int(v[2]), a.allow_set)),
+                      ("resetclocks", lambda v: smi.reset_locked_clocks(int(v), a.allow_set))):
+        v = getattr(a, what)
+        if v:
+            try:
+                act(v)
+                print(f"{what}: done for GPU {v[0] if isinstance(v, list) else v}")
+            except RuntimeError as e:
+                print(f"b200-smi: {e}", file=sys.stderr)
+                return 2
     if a.showdriverversion or a.showall:
         out["driver_version"] = smi.driver_version()
         if not a.json:
@@ -446,6 +495,20 @@ def main(argv=None) -> int:
         if not a.json:
             for i, m in enumerate(out["modes"]):
                 print(f"GPU{i}: compute mode {m['compute_mode']}, persistence {m['persistence']}, MIG {m['mig']}, ECC {m['ecc']}")
+    id_flags = {"showserial": lambda d: f"serial {d['serial'] or 'n/a'}, part number {d['part_number'] or 'n/a'}", "showvbios": lambda d: f"VBIOS {d['vbios'] or 'n/a'}",
+                "showfwinfo": lambda d: f"VBIOS {d['vbios'] or 'n/a'}, InfoROM image {d['inforom_image'] or 'n/a'}",
+                "showperflevel": lambda d: "n/a" if d["performance_state"] is None else f"P{d['performance_state']}",
+                "showmaxpower": lambda d: "n/a" if d["power_limit_max_w"] is None else f"power limit settable in {d['power_limit_min_w']:.0f} - {d['power_limit_max_w']:.0f} W",
+                "showenergycounter": lambda d: "n/a" if d["energy_j"] is None else f"{d['energy_j']:.1f} J since the driver was loaded",
+                "showretiredpages": lambda d: "n/a" if d["remapped_rows"] is None else
+                f"remapped rows: {d['remapped_rows']['correctable']} correctable, {d['remapped_rows']['uncorrectable']} uncorrectable"
+                f"{', remap pending' if d['remapped_rows']['pending'] else ''}{', REMAP FAILED' if d['remapped_rows']['failed'] else ''}"}
+    id_asked = [k for k in id_flags if getattr(a, k)]
+    if id_asked:
+        out["identity"] = [smi.identity(i) for i in range(n)]
+        if not a.json:
+            for i, d in enumerate(out["identity"]):
+                print(f"GPU{i}: " + "; ".join(id_flags[k](d) for k in id_asked))
     if a.showactivity:
         out["activity"] = [smi.activity(i) for i in range(n)]
         if not a.json:
@@ -474,7 +537,7 @@ def main(argv=None) -> int:
         if not a.json:
             for i, d in enumerate(infos):
                 print(f"GPU{i}: " + "; ".join(singles[k](d) for k in asked))
-    only_new = bool(asked) or a.showevents > 0 or a.showactivity or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    only_new = bool(asked) or bool(id_asked) or bool(a.setclocks) or bool(a.resetclocks) or a.showevents > 0 or a.showactivity or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
               ("typeName", "Link type between two GPUs", a.showtopotype), ("maxBandwidthMBps", "Max bandwidth (MB/s per direction)", a.shownodesbw),
               ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]

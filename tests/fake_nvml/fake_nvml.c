@@ -36,7 +36,8 @@ nvmlReturn_t nvmlDeviceGetHandleByIndex_v2(unsigned int i, nvmlDevice_t* d) { if
 nvmlReturn_t nvmlDeviceGetName(nvmlDevice_t d, char* s, unsigned int n) { (void)d; snprintf(s, n, "NVIDIA B200 (fake)"); return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetUUID(nvmlDevice_t d, char* s, unsigned int n) { snprintf(s, n, "GPU-fake-%04d", d->idx); return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetPciInfo_v3(nvmlDevice_t d, nvmlPciInfo_t* p) { memset(p, 0, sizeof(*p)); snprintf(p->busId, sizeof(p->busId), "00000000:%02X:00.0", 0x10 + d->idx); return NVML_SUCCESS; }
-nvmlReturn_t nvmlDeviceGetClockInfo(nvmlDevice_t d, int t, unsigned int* c) { (void)d; *c = t == 1 /*SM*/ ? 1500 : 3996; return NVML_SUCCESS; }
+static unsigned int locked_max[16];
+nvmlReturn_t nvmlDeviceGetClockInfo(nvmlDevice_t d, int t, unsigned int* c) { *c = t == 1 /*SM*/ ? (locked_max[d->idx] ? locked_max[d->idx] : 1500) : 3996; return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetMaxClockInfo(nvmlDevice_t d, int t, unsigned int* c) { (void)d; *c = t == 1 ? 1965 : 3996; return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetPowerUsage(nvmlDevice_t d, unsigned int* mw) { (void)d; reads++; *mw = 200000 + (envint("FAKE_NVML_RAMP", 0) ? reads * 10000 : 0); return NVML_SUCCESS; }
 nvmlReturn_t nvmlDeviceGetEnforcedPowerLimit(nvmlDevice_t d, unsigned int* mw) { *mw = power_limit[d->idx]; return NVML_SUCCESS; }
@@ -107,6 +108,21 @@ nvmlReturn_t nvmlEventSetWait_v2(nvmlEventSet_t s, nvmlEventData_t* out, unsigne
   usleep((timeoutms > 50 ? 50 : timeoutms) * 1000);
   return 10; /* NVML_ERROR_TIMEOUT */
 }
+
+/* ---- identity, lifetime counters, clock locks (kept in memory, shown by the clock getter) ---- */
+static unsigned int locked_min[16];
+nvmlReturn_t nvmlDeviceGetSerial(nvmlDevice_t d, char* s, unsigned int n) { snprintf(s, n, "165012345%04d", d->idx); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetBoardPartNumber(nvmlDevice_t d, char* s, unsigned int n) { (void)d; snprintf(s, n, "699-2G525-0200-000"); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetVbiosVersion(nvmlDevice_t d, char* s, unsigned int n) { (void)d; snprintf(s, n, "97.00.88.00.0F"); return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetInforomImageVersion(nvmlDevice_t d, char* s, unsigned int n) { (void)d; (void)s; (void)n; return 3; /* not supported */ }
+nvmlReturn_t nvmlDeviceGetPerformanceState(nvmlDevice_t d, int* p) { (void)d; *p = 0; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetPowerManagementLimitConstraints(nvmlDevice_t d, unsigned int* lo, unsigned int* hi) { (void)d; *lo = 200000; *hi = 1000000; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetTotalEnergyConsumption(nvmlDevice_t d, unsigned long long* mj) { *mj = 123456789ull + (unsigned long long)d->idx; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceGetRemappedRows(nvmlDevice_t d, unsigned int* c, unsigned int* u, unsigned int* pend, unsigned int* fail) {
+  *c = envint("FAKE_NVML_ECC", -1) == d->idx ? 2 : 0; *u = 0; *pend = 0; *fail = 0; return NVML_SUCCESS;
+}
+nvmlReturn_t nvmlDeviceSetGpuLockedClocks(nvmlDevice_t d, unsigned int lo, unsigned int hi) { locked_min[d->idx] = lo; locked_max[d->idx] = hi; return NVML_SUCCESS; }
+nvmlReturn_t nvmlDeviceResetGpuLockedClocks(nvmlDevice_t d) { locked_min[d->idx] = locked_max[d->idx] = 0; return NVML_SUCCESS; }
 
 /* ---- performance-monitoring samples: a sample remembers its sequence number; a metrics request reports fixed
  * percentages, the number of samples between its two samples as NVLink traffic, and "not available" for FP64. ---- */

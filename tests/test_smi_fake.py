@@ -301,3 +301,52 @@ def test_launcher_samples_activity_fields_next_to_the_trace(fake_nvml, tmp_path)
     assert "gpu_tensor_active" in p.stdout                                       # the sampled-counters table of --stats
     p = subprocess.run([*base, "--sys-sample-fields", "nope", "--", "true"], env=e, capture_output=True, text=True, timeout=60)
     assert p.returncode == 2 and "unknown --sys-sample-fields" in p.stderr
+
+
+def test_identity_readings_and_gated_clock_lock(fake_nvml):
+    out = _run("""
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+d = s.identity(2)
+assert d['serial'] == '1650123450002' and d['part_number'] == '699-2G525-0200-000' and d['vbios'] == '97.00.88.00.0F' and d['inforom_image'] is None
+assert d['performance_state'] == 0 and d['power_limit_min_w'] == 200.0 and d['power_limit_max_w'] == 1000.0
+assert abs(d['energy_j'] - 123456.791) < 1e-6 and d['remapped_rows'] == {'correctable': 0, 'uncorrectable': 0, 'pending': False, 'failed': False}
+assert s.identity(1)['remapped_rows']['correctable'] == 2
+for call in (lambda: s.set_locked_clocks(0, 1200, 1500, True), lambda: s.reset_locked_clocks(0, True)):
+    try:
+        call(); raise SystemExit('setter ran without B200SMI_ALLOW_SET')
+    except RuntimeError as e:
+        assert 'disabled' in str(e)
+print('ok')
+""", fake_nvml, {"FAKE_NVML_ECC": "1"})
+    assert "ok" in out
+    out = _run("""
+from rocm_systems_b200.tools.smi import Smi
+s = Smi()
+try:
+    s.set_locked_clocks(0, 1200, 1500, False); raise SystemExit('setter ran without allow')
+except RuntimeError as e:
+    assert 'disabled' in str(e)
+try:
+    s.set_locked_clocks(0, 1500, 1200, True); raise SystemExit('min above max accepted')
+except RuntimeError as e:
+    assert 'invalid' in str(e)
+s.set_locked_clocks(0, 1200, 1350, True)
+assert s.info(0)['smClockMhz'] == 1350 and s.info(1)['smClockMhz'] == 1500       # the stand-in shows the lock in its clock reading
+s.reset_locked_clocks(0, True)
+assert s.info(0)['smClockMhz'] == 1500
+print('ok')
+""", fake_nvml, {"B200SMI_ALLOW_SET": "1"})
+    assert "ok" in out
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showserial", "--showperflevel", "--showmaxpower", "--showenergycounter",
+                        "--showretiredpages", "--showfwinfo"], env=e, capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    assert "GPU1: serial 1650123450001, part number 699-2G525-0200-000; VBIOS 97.00.88.00.0F, InfoROM image n/a; P0; power limit settable in 200 - 1000 W;" in p.stdout, p.stdout
+    assert "J since the driver was loaded; remapped rows: 0 correctable, 0 uncorrectable" in p.stdout and "Name" not in p.stdout
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--setclocks", "0", "1200", "1400", "--allow-set"], env=e, capture_output=True, text=True)
+    assert p.returncode == 2 and "disabled" in p.stderr                                    # the environment half of the gate is missing
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "static", "--json", "-g", "0"], env=e, capture_output=True, text=True)
+    import json
+    row = json.loads(p.stdout)[0]
+    assert row["serial"] == "1650123450000" and row["vbios"] == "97.00.88.00.0F" and row["power_limit_range_w"] == "200-1000"
