@@ -558,7 +558,8 @@ def scale_units(summary, unit: str):
     return summary
 
 
-def print_summary(summary: dict, file=sys.stdout) -> None:
+def print_summary(summary: dict, file=None) -> None:
+    file = file or sys.stdout    # looked up when called: the caller may have redirected it since this module was loaded
     for kind, label in (("domains", "DOMAIN"), ("groups", "GROUP")):
         for key, rows in (summary.get(kind) or {}).items():
             if rows:
