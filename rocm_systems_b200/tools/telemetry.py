@@ -457,6 +457,72 @@ def _client(url: str, endpoint: str, **q) -> object:
     return body if path == "/metrics" else json.loads(body)
 
 
+class Reader:
+    """Periodic reader for programs that want the values themselves (a logger, a scheduler, a plug-in of another monitoring
+    system): subclass it and override ``handle_field``, or pass ``on_field``. Embedded (its own ``Telemetry`` in this
+    process) when ``url`` is None, else a client of a running daemon. The reference ships the same helper for its daemon
+    (rdc/python_binding/RdcReader.py: ``RdcReader(ip_port, field_ids, update_freq, ...)`` with ``process()`` calling
+    ``handle_field(gpu_index, value)``), and builds its Prometheus and collectd plug-ins on it.
+
+        class Log(Reader):
+            def handle_field(self, device, field, value, timestamp_ns): print(device, field, value)
+        Log(fields=["power", "tensor_active"], period_ms=500).run(iterations=10)
+    """
+
+    def __init__(self, url: Optional[str] = None, fields: Optional[Sequence[str]] = None, devices: Optional[Sequence[int]] = None, period_ms: int = 1000,
+                 on_field=None, telemetry: Optional[Telemetry] = None):
+        self.url = url
+        self.fields = list(fields or DEFAULT_FIELDS)
+        unknown = [f for f in self.fields if f not in FIELDS]
+        if unknown:
+            raise ValueError(f"unknown field(s) {unknown}; known: {', '.join(FIELDS)}")
+        self.period_ms = period_ms
+        self.on_field = on_field
+        self.t = None
+        if url is None:
+            self.t = telemetry or Telemetry()
+            self.t.fields = list(self.fields)
+            self.devices = list(devices) if devices is not None else list(self.t.devices)
+            self.t.devices = list(self.devices)
+        else:
+            known = [d["index"] if isinstance(d, dict) and "index" in d else i for i, d in enumerate(_client(url, "/api/devices"))]
+            self.devices = list(devices) if devices is not None else known
+        self.reads = 0
+
+    def handle_field(self, device: int, field: str, value: Optional[float], timestamp_ns: int) -> None:
+        if self.on_field:
+            self.on_field(device, field, value, timestamp_ns)
+
+    def process(self) -> int:
+        """One round: every (device, field) once; returns how many values were handed over (unsupported ones are skipped)."""
+        now = time.time_ns()
+        if self.t is not None:
+            latest = self.t.latest()
+        else:
+            latest = {int(k): v for k, v in _client(self.url, "/api/latest").items()}
+        n = 0
+        for d in self.devices:
+            for f in self.fields:
+                v = latest.get(d, {}).get(f)
+                if v is not None:
+                    self.handle_field(d, f, v, now)
+                    n += 1
+        self.reads += 1
+        return n
+
+    def run(self, iterations: int = 0, stop: Optional[threading.Event] = None) -> None:
+        """Calls ``process`` every period until ``iterations`` rounds are done (0: until ``stop`` is set)."""
+        i = 0
+        while (iterations == 0 or i < iterations) and not (stop and stop.is_set()):
+            t0 = time.monotonic()
+            self.process()
+            i += 1
+            if iterations == 0 or i < iterations:
+                left = self.period_ms / 1000.0 - (time.monotonic() - t0)
+                if left > 0:
+                    (stop.wait(left) if stop else time.sleep(left))
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="telemetry", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)

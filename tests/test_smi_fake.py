@@ -350,3 +350,37 @@ print('ok')
     import json
     row = json.loads(p.stdout)[0]
     assert row["serial"] == "1650123450000" and row["vbios"] == "97.00.88.00.0F" and row["power_limit_range_w"] == "200-1000"
+
+
+def test_telemetry_reader_embedded_and_against_a_daemon(fake_nvml):
+    out = _run("""
+import threading, time
+from rocm_systems_b200.tools.telemetry import Reader, Telemetry, serve
+seen = []
+class Log(Reader):
+    def handle_field(self, device, field, value, timestamp_ns):
+        seen.append((device, field, value))
+r = Log(fields=['power', 'tensor_active', 'fp64_active'], devices=[0, 2], period_ms=20)
+r.run(iterations=3)
+assert r.reads == 3 and len(seen) == 3 * 2 * 2                      # fp64 is unsupported on the stand-in: skipped
+assert {s[0] for s in seen} == {0, 2} and {s[1] for s in seen} == {'power', 'tensor_active'} and all(s[2] in (200.0, 62.5) for s in seen)
+try:
+    Reader(fields=['nope']); raise SystemExit('unknown field accepted')
+except ValueError:
+    pass
+# against a daemon
+t = Telemetry()
+srv = serve(t, '127.0.0.1', 0)
+port = srv.server_address[1]
+threading.Thread(target=srv.serve_forever, daemon=True).start()
+got = []
+c = Reader(url=f'http://127.0.0.1:{port}', fields=['temp', 'sm_clock'], period_ms=10, on_field=lambda d, f, v, ts: got.append((d, f, v)))
+assert c.devices == list(range(8))
+assert c.process() == 16 and ((3, 'temp', 45.0) in got) and ((7, 'sm_clock', 1500.0) in got)
+stop = threading.Event()
+th = threading.Thread(target=c.run, kwargs={'stop': stop}); th.start(); time.sleep(0.1); stop.set(); th.join(2)
+assert not th.is_alive() and c.reads >= 3
+srv.shutdown()
+print('ok')
+""", fake_nvml)
+    assert "ok" in out
