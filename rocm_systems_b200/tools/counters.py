@@ -38,6 +38,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 import re
 import sys
 from pathlib import Path
@@ -352,6 +353,48 @@ def format_analysis(items: Sequence[dict]) -> str:
     return "\n".join(lines)
 
 
+def html_report(items: Sequence[dict], title: str = "Kernel analysis") -> str:
+    """The analysis as one self-contained HTML page (no scripts, no external files): per launch the verdict, one table per
+    panel with a bar for every percentage, and the stall ranking as bars. The reference offers its analysis in a browser
+    too (rocprofiler-compute src/rocprof_compute_analyze/analysis_webui.py); this is the static counterpart."""
+    import html
+
+    def esc(x) -> str:
+        return html.escape(str(x))
+
+    def bar(frac: float, color: str) -> str:
+        w = max(0.0, min(1.0, frac)) * 100.0
+        return f'<div class="bar"><div style="width:{w:.1f}%;background:{color}"></div></div>'
+
+    out = ["<!doctype html><html><head><meta charset='utf-8'>", f"<title>{esc(title)}</title>",
+           "<style>body{font:14px/1.4 system-ui,sans-serif;margin:2em;max-width:1100px}h2{margin-top:2em;font-size:16px;word-break:break-all}"
+           "table{border-collapse:collapse;width:100%;margin:.4em 0 1em}td,th{padding:2px 8px;text-align:left;border-bottom:1px solid #ddd;vertical-align:top}"
+           "td.n{text-align:right;font-variant-numeric:tabular-nums;white-space:nowrap}.bar{width:160px;height:10px;background:#eee;border-radius:2px}"
+           ".bar div{height:10px;border-radius:2px}.verdict{background:#f4f4f4;padding:.5em .8em;border-left:4px solid #888}h3{font-size:13px;margin:.8em 0 .2em;"
+           "text-transform:uppercase;color:#555}nav a{display:block;word-break:break-all}</style></head><body>", f"<h1>{esc(title)}</h1>", "<nav>"]
+    for i, it in enumerate(items):
+        out.append(f'<a href="#k{i}">{i}. {esc(it["kernel"][:140])}</a>')
+    out.append("</nav>")
+    for i, it in enumerate(items):
+        out.append(f'<h2 id="k{i}">{i}. {esc(it["kernel"])}</h2><p class="verdict">{esc(it["verdict"])}</p>')
+        for panel, rows in it["panels"].items():
+            out.append(f"<h3>{esc(panel.replace('_', ' '))}</h3><table><tr><th>counter</th><th>value</th><th>unit</th><th></th><th>meaning</th></tr>")
+            for r in rows:
+                pct = "%" in r["unit"] or "percent" in r["unit"]
+                cell = bar(r["value"] / 100.0, "#4a90d9" if r["value"] < 80 else "#d9534f") if pct else ""
+                out.append(f'<tr><td>{esc(r["name"])}</td><td class="n">{r["value"]:.4g}</td><td>{esc(r["unit"])}</td><td>{cell}</td><td>{esc(r["description"])}</td></tr>')
+            out.append("</table>")
+        if it["stalls"]:
+            top = max(s_["warps_per_issue"] for s_ in it["stalls"]) or 1.0
+            out.append("<h3>stalls (stalled warps per issued instruction)</h3><table><tr><th>reason</th><th>value</th><th></th><th>meaning</th></tr>")
+            for s_ in it["stalls"]:
+                out.append(f'<tr><td>{esc(s_["reason"])}</td><td class="n">{s_["warps_per_issue"]:.3g}</td><td>{bar(s_["warps_per_issue"] / top, "#e0a030")}</td>'
+                           f'<td>{esc(s_["meaning"])}</td></tr>')
+            out.append("</table>")
+    out.append("</body></html>")
+    return "\n".join(out)
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     from . import roofline
 
@@ -367,6 +410,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--kernel-filter", default="", metavar="REGEX", help="with --analyze / --compare: only launches whose kernel name matches")
     ap.add_argument("--analyze", action="store_true", help="per launch: the counters grouped by panel (speed of light, memory, caches, compute, "
                     "occupancy, launch), the warp stall ranking and a one-line verdict on what bounds it")
+    ap.add_argument("--html", default="", metavar="FILE", help="with --analyze: write the analysis as one self-contained HTML page as well")
     ap.add_argument("--collect", action="store_true", help="run the command after -- under Nsight Compute for the metrics the counters need, then evaluate")
     ap.add_argument("--counter", action="append", default=[], help="with --collect: only these definitions (default: all)")
     ap.add_argument("-k", "--kernel", default="", help="with --collect: regular expression of the kernels to capture")
@@ -424,6 +468,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return 0
     if a.analyze:
         items = [it for path in a.inputs for it in analyze(cs, keep(roofline.read_ncu(path)), peaks, args)]
+        if a.html:
+            with open(a.html, "w") as f:
+                f.write(html_report(items, "Kernel analysis: " + ", ".join(os.path.basename(p) for p in a.inputs)))
         print(json.dumps(items, indent=1) if a.json else format_analysis(items))
         return 0
     if a.json:

@@ -707,6 +707,13 @@ def test_counter_analysis_panels_stalls_and_verdicts(tmp_path, capsys):
     assert counters.main([str(tmp_path / "raw.csv"), "--analyze", "--peaks", str(tmp_path / "p.json")]) == 0
     text = capsys.readouterr().out
     assert "== waitKernel" in text and "[stalls" in text and "under-filled" in text and "[memory]" in text
+    # and as one self-contained page
+    assert counters.main([str(tmp_path / "raw.csv"), "--analyze", "--peaks", str(tmp_path / "p.json"), "--html", str(tmp_path / "a.html")]) == 0
+    page = (tmp_path / "a.html").read_text()
+    assert page.startswith("<!doctype html>") and page.count("<h2 id=") == 3 and "under-filled" in page and "<script" not in page and "http" not in page
+    assert 'href="#k2"' in page and "stalls (stalled warps per issued instruction)" in page and 'class="bar"' in page
+    evil = counters.html_report([{"kernel": "k<img src=x>", "verdict": "a & b", "panels": {}, "stalls": []}])
+    assert "<img" not in evil and "k&lt;img src=x&gt;" in evil and "a &amp; b" in evil
 
 
 def test_profiler_launcher_counter_collection(tmp_path, capsys):
