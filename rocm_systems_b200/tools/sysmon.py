@@ -197,5 +197,45 @@ class SystemSampler:
         with open(path, "w") as f:
             f.write('"Counter","Device","Timestamp","Value"\n')
             for name, dev, ts, val in self.samples:
-                f.write(f'"{name}",{dev},{ts},{val:.6g}\n')
+                f.write(f'"{name}",{dev},{ts},{val:.12g}\n')
         return len(self.samples)
+
+
+def main(argv=None) -> int:
+    """``python -m rocm_systems_b200.tools.sysmon [-p PID ...] [--period-ms 100] [--duration S] [--fields F ...] -o out.csv [-- command]``:
+    sample for ``--duration`` seconds, or for as long as the command after ``--`` runs (its process is watched too), and write
+    the samples as a counter CSV that ``tools/tracedb.py import`` takes."""
+    import argparse
+    import subprocess
+    import sys
+    import time
+
+    ap = argparse.ArgumentParser(prog="sysmon", description="Sample GPU, host and per-process counters into a CSV.")
+    ap.add_argument("-p", "--pid", type=int, action="append", default=[], help="process to watch (repeatable)")
+    ap.add_argument("--period-ms", type=int, default=100)
+    ap.add_argument("--duration", type=float, default=0.0, help="seconds to sample when no command is given")
+    ap.add_argument("--fields", nargs="+", default=list(GPU_FIELDS), help="GPU readings (names of tools/smi.py)")
+    ap.add_argument("--no-gpu", action="store_true")
+    ap.add_argument("-o", "--output", default="sysmon.csv")
+    ap.add_argument("command", nargs=argparse.REMAINDER)
+    a = ap.parse_args(argv)
+    cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
+    if not cmd and a.duration <= 0:
+        ap.error("give --duration or a command after --")
+    rc = 0
+    child = subprocess.Popen(cmd) if cmd else None
+    pids = list(a.pid) + ([child.pid] if child else [])
+    with SystemSampler(period_ms=a.period_ms, pids=pids, gpu=not a.no_gpu, gpu_fields=a.fields) as s:
+        if child:
+            rc = child.wait()
+        else:
+            time.sleep(a.duration)
+    n = s.write_csv(a.output)
+    print(f"sysmon: {n} samples of {len({x[0] for x in s.samples})} counters in {a.output}", file=sys.stderr)
+    return rc
+
+
+if __name__ == "__main__":
+    import sys
+
+    sys.exit(main())

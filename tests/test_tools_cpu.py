@@ -256,6 +256,31 @@ print('ok')
     assert "ok" in out and "B200COLL_BUFFSIZE" in out and "B200COLL_TRACE " not in out
 
 
+def test_system_sampler_command_line_and_console_scripts(tmp_path):
+    """The sampler around a command, its CSV into the database, and every console script of the package resolves."""
+    import subprocess as sp
+    import tomllib
+    import importlib
+
+    from rocm_systems_b200.tools import tracedb
+
+    out = tmp_path / "s.csv"
+    r = sp.run([sys.executable, "-m", "rocm_systems_b200.tools.sysmon", "--no-gpu", "--period-ms", "30", "-o", str(out), "--", sys.executable, "-c",
+                "import time; time.sleep(0.3); raise SystemExit(4)"], capture_output=True, text=True, cwd=ROOT, timeout=120)
+    assert r.returncode == 4 and "samples of" in r.stderr                       # the command's exit code passes through
+    with tracedb.TraceDB(str(tmp_path / "s.db")) as db:
+        assert db.import_csv(str(out)) >= 20
+        names = {n for (n,) in db.query("select distinct s.value from counter_sample c join string s on s.id = c.name_id")[1]}
+    assert {"host_cpu_util_percent", "process_rss_bytes", "process_threads"} <= names
+    rss = [float(l.rsplit(",", 1)[1]) for l in out.read_text().splitlines() if l.startswith('"process_rss_bytes"')]
+    assert all(v == int(v) and v > 1e6 for v in rss)                             # whole bytes: not rounded to six digits
+    scripts = tomllib.loads((ROOT / "pyproject.toml").read_text())["project"]["scripts"]
+    assert len(scripts) >= 15
+    for name, target in scripts.items():
+        mod, fn = target.split(":")
+        assert callable(getattr(importlib.import_module(mod), fn)), name
+
+
 def test_settings_listing_covers_the_tool_libraries(capsys):
     """Every listed environment name is read somewhere in the package, and the listing can be narrowed by component."""
     import subprocess as sp
