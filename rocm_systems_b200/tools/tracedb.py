@@ -455,6 +455,27 @@ class TraceDB:
             if e > s:
                 events.append({"ph": "X", "pid": pid, "tid": "collectives (device)", "name": name, "cat": "collective", "ts": s / 1e3,
                                "dur": (e - s) / 1e3, "args": {"bytes": nbytes, "rank": rank}})
+        # Arrows from the host call to the device work it started, by correlation id: a runtime / driver launch to its kernel,
+        # a collective call to its device interval (the reference's Perfetto output draws the same flows).
+        marker = self.db.execute("select id from string where value = 'MARKER_API'").fetchone()
+        flow = 0
+        calls: dict = {}
+        for ppid, pid, tid, cat, corr, st in self.db.execute(
+                "select r.process_id, p.pid, r.tid, c.value, r.correlation_id, r.start_ns from region r join process p on p.id = r.process_id"
+                " join string c on c.id = r.category_id where r.correlation_id != 0 and r.category_id != ?", (marker[0] if marker else -1,)):
+            calls.setdefault((ppid, corr, cat == "B200COLL_API"), (pid, f"{cat} {tid}", st))
+        for ppid, corr, dev, stream, st in self.db.execute("select process_id, correlation_id, device, stream, start_ns from kernel_dispatch where correlation_id != 0"):
+            src = calls.get((ppid, corr, False))
+            if src and src[2] <= st:
+                flow += 1
+                events.append({"ph": "s", "id": flow, "pid": src[0], "tid": src[1], "ts": src[2] / 1e3, "name": "launch", "cat": "flow"})
+                events.append({"ph": "f", "bp": "e", "id": flow, "pid": src[0], "tid": f"gpu{dev} stream {stream}", "ts": st / 1e3, "name": "launch", "cat": "flow"})
+        for ppid, corr, st, en in self.db.execute("select process_id, correlation_id, device_start_ns, device_end_ns from collective where correlation_id != 0"):
+            src = calls.get((ppid, corr, True))
+            if src and en > st and src[2] <= st:
+                flow += 1
+                events.append({"ph": "s", "id": flow, "pid": src[0], "tid": src[1], "ts": src[2] / 1e3, "name": "collective", "cat": "flow"})
+                events.append({"ph": "f", "bp": "e", "id": flow, "pid": src[0], "tid": "collectives (device)", "ts": st / 1e3, "name": "collective", "cat": "flow"})
         # Communication volume as cumulative counter tracks per rank, classified the way the reference's system profiler does
         # (rocprofiler-systems source/lib/rocprof-sys/library/rocprofiler-sdk/rccl.cpp:105-180): gather-like and reducing
         # collectives and receives count as received bytes, broadcast / reduce-scatter / sends as sent bytes.

@@ -109,11 +109,13 @@ def test_tracedb_import_summary_convert(tmp_path):
         cats = {r["category"] for r in s["regions"]}
         assert cats == {"B200COLL_API", "MARKER_API"}
         ev = db.to_perfetto(str(tmp_path / "t.json"))
-        assert ev == 1 + 3 + 3 + 2 + 2  # process name, kernels, regions (2 API + 1 marker), device-side collectives, comm-volume counter points
+        assert ev == 1 + 3 + 3 + 2 + 2 + 4  # process name, kernels, regions (2 API + 1 marker), device-side collectives, comm-volume counter points, 2 call -> device arrows
         files = db.to_csv(str(tmp_path / "out"))
         assert any(f.endswith("_top_kernels.csv") for f in files)
     doc = json.loads((tmp_path / "t.json").read_text())
-    assert {e["ph"] for e in doc["traceEvents"]} == {"M", "X", "C"}
+    assert {e["ph"] for e in doc["traceEvents"]} == {"M", "X", "C", "s", "f"}
+    arrows = sorted((e for e in doc["traceEvents"] if e["ph"] in "sf"), key=lambda e: (e["id"], e["ph"] == "f"))
+    assert [(e["ph"], e["tid"], e["ts"]) for e in arrows[:2]] == [("s", "B200COLL_API 100", 0.9), ("f", "collectives (device)", 2.0)]   # call at 900 ns, device at 2000 ns
     vol = [e for e in doc["traceEvents"] if e["ph"] == "C"]
     assert [e["name"] for e in vol] == ["Comm Recv (bytes)"] * 2 and [e["args"]["value"] for e in vol] == [4194304, 8388608]   # all-reduce counts as received; cumulative
     # a second rank's database merges in
@@ -484,6 +486,29 @@ srv.shutdown(); t.stop()
 print('ok')
 """, {"B200SMI_NVML_LIBRARY": fake_nvml, "FAKE_NVML_GPUS": "2", "FAKE_NVML_RAMP": "1"})
     assert "ok" in out
+
+
+def test_perfetto_export_draws_launch_arrows(tmp_path):
+    """A runtime API record and the kernel with the same correlation id are joined by a flow; a kernel without a call record
+    and a marker range are not."""
+    from rocm_systems_b200.tools import tracedb
+
+    (tmp_path / "t.100_kernel_trace.csv").write_text(KERNEL_CSV)
+    (tmp_path / "t.100_cuda_api_trace.csv").write_text(
+        '"Domain","Function","Process_Id","Thread_Id","Correlation_Id","Start_Timestamp","End_Timestamp"\n'
+        '"CUDA_RUNTIME_API","cudaLaunchKernel",100,101,1,800,850\n"CUDA_RUNTIME_API","cudaLaunchKernel",100,101,3,9000,9100\n'
+        '"CUDA_RUNTIME_API","cudaMalloc",100,101,0,100,200\n')
+    (tmp_path / "t.markers.100.csv").write_text(MARK_CSV)
+    with tracedb.TraceDB(str(tmp_path / "t.db")) as db:
+        for p in sorted(tmp_path.glob("t.*csv")):
+            db.import_csv(str(p))
+        db.to_perfetto(str(tmp_path / "t.json"))
+    ev = json.loads((tmp_path / "t.json").read_text())["traceEvents"]
+    starts = {e["id"]: e for e in ev if e["ph"] == "s"}
+    ends = {e["id"]: e for e in ev if e["ph"] == "f"}
+    assert len(starts) == len(ends) == 2 and all(e["bp"] == "e" for e in ends.values())
+    pairs = sorted((starts[i]["ts"], ends[i]["ts"], starts[i]["tid"], ends[i]["tid"]) for i in starts)
+    assert pairs == [(0.8, 1.0, "CUDA_RUNTIME_API 101", "gpu0 stream 7"), (9.0, 9.5, "CUDA_RUNTIME_API 101", "gpu0 stream 7")]
 
 
 def test_tracedb_postprocessing_filters(tmp_path):
