@@ -276,6 +276,12 @@ def test_system_sampler_command_line_and_console_scripts(tmp_path):
     assert {"host_cpu_util_percent", "process_rss_bytes", "process_threads"} <= names
     rss = [float(l.rsplit(",", 1)[1]) for l in out.read_text().splitlines() if l.startswith('"process_rss_bytes"')]
     assert all(v == int(v) and v > 1e6 for v in rss)                             # whole bytes: not rounded to six digits
+    from rocm_systems_b200 import __main__ as door
+
+    for name in door.TOOLS:                                                     # every tool the package door lists exists and has a main()
+        assert callable(importlib.import_module("rocm_systems_b200.tools." + name).main), name
+    assert {p.stem for p in (ROOT / "rocm_systems_b200" / "tools").glob("*.py")} - {"__init__"} == set(door.TOOLS)
+    assert door.main(["nope"]) == 2 and door.main([]) == 0 and door.main(["instrument", "flags"]) == 0
     scripts = tomllib.loads((ROOT / "pyproject.toml").read_text())["project"]["scripts"]
     assert len(scripts) >= 15
     for name, target in scripts.items():
