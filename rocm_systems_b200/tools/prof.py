@@ -161,7 +161,7 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--list-pmc", action="store_true", help="list the derived counters and stop")
     g = ap.add_argument_group("job files")
     g.add_argument("-i", "--input", default="", metavar="FILE",
-                   help="YAML or JSON file with a list `jobs:`; each job is a set of this launcher's options (long names, dashes or underscores), "
+                   help="YAML or JSON file with a list `jobs:` (or a .txt file with one `pmc: COUNTER ...` line per pass and optional `kernel: NAME ...`); each job is a set of this launcher's options (long names, dashes or underscores), "
                         "run as a pass of its own into <output-directory>/pass_<n>/ with the options of the command line as defaults")
     g = ap.add_argument_group("tools")
     g.add_argument("--tool-library", action="append", default=[], help="extra dispatch-table tool(s) to load into the communication library")
@@ -224,6 +224,17 @@ def load_jobs(path: str) -> List[dict]:
     text = Path(path).read_text()
     if path.endswith(".json"):
         doc = json.loads(text)
+    elif path.endswith(".txt"):
+        # The reference's plain-text form: every `pmc:` line is one counter-collection pass; `kernel:` narrows all of them.
+        passes, kernels = [], []
+        for raw in text.splitlines():
+            line = raw.split("#", 1)[0].strip()
+            key, _, rest = line.partition(":")
+            if key.strip() == "pmc" and rest.split():
+                passes.append(rest.split())
+            elif key.strip() == "kernel" and rest.split():
+                kernels += rest.split()
+        doc = {"jobs": [dict({"pmc": p}, **({"pmc_kernel": "|".join(kernels)} if kernels else {})) for p in passes]}
     else:
         import yaml
 

@@ -934,6 +934,12 @@ def test_profiler_launcher_job_file(tmp_path):
     assert "MARKER_API" in p.stdout and "pass 1" in p.stderr
     (tmp_path / "bad.json").write_text('{"jobs": []}')
     assert prof.main(["-i", str(tmp_path / "bad.json"), "--", "true"]) == 2
+    # the plain-text form: one counter-collection pass per `pmc:` line
+    (tmp_path / "in.txt").write_text("# two passes\npmc: hbm_gbs tflops\npmc: tensor_active_pct   # second\nkernel: gemmKernel rmsnorm\nrange: 0:1\n")
+    assert prof.load_jobs(str(tmp_path / "in.txt")) == [{"pmc": ["hbm_gbs", "tflops"], "pmc_kernel": "gemmKernel|rmsnorm"},
+                                                        {"pmc": ["tensor_active_pct"], "pmc_kernel": "gemmKernel|rmsnorm"}]
+    (tmp_path / "none.txt").write_text("nothing here\n")
+    assert prof.main(["-i", str(tmp_path / "none.txt"), "--", "true"]) == 2
 
 
 def test_counter_comparison_of_two_captures(tmp_path, capsys):
