@@ -790,6 +790,13 @@ ncclResult_t b200collTraceGet(ncclComm_t comm, b200collTraceRecordC* out, size_t
   *n = c->tracer->copyOut(out, max);
   return ncclSuccess;
 }
+ncclResult_t b200collTraceDropped(ncclComm_t comm, uint64_t* dropped) {
+  Comm* c = asComm(comm);
+  BCHECK(commCheck(c));
+  if (!dropped) BFAIL(ncclInvalidArgument, "null pointer");
+  *dropped = c->tracer ? c->tracer->dropped() : 0;
+  return ncclSuccess;
+}
 ncclResult_t b200collTraceClear(ncclComm_t comm) {
   Comm* c = asComm(comm);
   BCHECK(commCheck(c));

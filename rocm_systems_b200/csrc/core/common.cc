@@ -108,6 +108,8 @@ static void load(Flags& f) {
   if (const char* v = envOf("TOOL_LIBRARIES", false)) f.toolLibs = v;
   f.traceEnable = parseInt(envOf("TRACE", false), 0);
   if (const char* v = envOf("TRACE_FILE", false)) f.traceFile = v;
+  f.traceMaxRecords = parseInt(envOf("TRACE_MAX_RECORDS", false), 0);
+  if (f.traceMaxRecords < 0) f.traceMaxRecords = 0;
   if (const char* v = envOf("FAIL_KEY", false)) f.failKey = v;
   f.ipcLegacy = parseInt(envOf("IPC_MODE_LEGACY", false), 0);
   f.checkSymmetric = parseInt(envOf("CHECK_SYMMETRIC", false), 0);
@@ -270,6 +272,7 @@ const SettingDoc kSettings[] = {
     {"TOOL_LIBRARIES", false, "", "':'-separated shared objects given the dispatch table through b200coll_tool_configure"},
     {"TRACE", false, "0", "1: record host and device times of every collective (and b200tx ranges)"},
     {"TRACE_FILE", false, "", "prefix of the CSV files written when a communicator is destroyed / at exit"},
+    {"TRACE_MAX_RECORDS", false, "0", "0: keep every collective record (lossless); N: keep the first N per communicator, count the rest as dropped"},
     {"FAIL_KEY", false, "", "comma list of host-side fault-injection points (tests only)"},
     {"IPC_MODE_LEGACY", false, "0", "1: share memory through cudaIpc handles instead of VMM file descriptors"},
 };
@@ -300,6 +303,7 @@ std::string currentValue(const Flags& f, const std::string& n) {
   if (n == "TOOL_LIBRARIES") return f.toolLibs;
   if (n == "TRACE") return num(f.traceEnable);
   if (n == "TRACE_FILE") return f.traceFile;
+  if (n == "TRACE_MAX_RECORDS") return num(f.traceMaxRecords);
   if (n == "FAIL_KEY") return f.failKey;
   if (n == "IPC_MODE_LEGACY") return num(f.ipcLegacy);
   return "";

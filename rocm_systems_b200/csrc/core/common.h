@@ -117,6 +117,7 @@ struct Flags {
   int emulateRanks = 0;           // EMULATE_RANKS: several ranks may share one GPU; such communicators only serve b200collEmu*
   int traceEnable = 0;           // TRACE: record per-collective device timestamps
   std::string traceFile;         // TRACE_FILE: CSV written at communicator destroy
+  long long traceMaxRecords = 0; // TRACE_MAX_RECORDS: 0 keeps every record; N keeps the first N per communicator and counts the rest
   std::string failKey;           // FAIL_KEY: host-side fault-injection points (tests)
   int ipcLegacy = 0;             // IPC_MODE_LEGACY: cudaIpc handles instead of VMM fds
   int graphRegister = 1;

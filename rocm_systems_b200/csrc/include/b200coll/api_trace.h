@@ -128,6 +128,8 @@ typedef struct {
 ncclResult_t b200collTraceEnable(ncclComm_t comm, int on);
 /* Synchronises the device, then copies up to `max` records; returns how many exist in *n. */
 ncclResult_t b200collTraceGet(ncclComm_t comm, b200collTraceRecordC* out, size_t max, size_t* n);
+/* Records that were not kept because B200COLL_TRACE_MAX_RECORDS was reached (0 without a limit). */
+ncclResult_t b200collTraceDropped(ncclComm_t comm, uint64_t* dropped);
 ncclResult_t b200collTraceClear(ncclComm_t comm);
 ncclResult_t b200collTraceWrite(ncclComm_t comm, const char* path, const char* format /* "csv" | "perfetto" */);
 const char* b200collApiName(int apiId);

@@ -108,8 +108,21 @@ void Tracer::end(bool launchedKernel) {
     ringUsed_--;  // give the untouched slot back
     curSlot_ = -1;
   }
+  // Lossless by default; with a limit the first records are kept and later ones only counted (the two buffer policies of the
+  // reference's record buffers, rocprofiler-sdk source/lib/rocprofiler-sdk/buffer.hpp:141-166). A dropped record's ring slot
+  // is simply never read back.
+  const long long limit = Flags::get().traceMaxRecords;
+  if (limit > 0 && (long long)recs_.size() >= limit) {
+    dropped_++;
+    return;
+  }
   recs_.push_back(cur_);
   slotOf_.push_back(launchedKernel ? curSlot_ : -1);
+}
+
+uint64_t Tracer::dropped() {
+  std::lock_guard<std::mutex> lk(mu_);
+  return dropped_;
 }
 
 void Tracer::drain() {

@@ -32,6 +32,7 @@ class Tracer {
   void end(bool launchedKernel);
   void drain();  // device stamps -> host records (synchronises the device)
   size_t size();
+  uint64_t dropped();
   size_t copyOut(b200collTraceRecordC* out, size_t max);
   void clear();
   bool writeCsv(const std::string& path);
@@ -49,6 +50,7 @@ class Tracer {
   int curSlot_ = -1;
   bool open_ = false;
   uint64_t nextCorr_ = 1;
+  uint64_t dropped_ = 0;         // records not kept because of TRACE_MAX_RECORDS
 };
 
 }  // namespace b200
