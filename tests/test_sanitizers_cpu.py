@@ -141,3 +141,20 @@ def test_instrumentation_hooks_and_kokkos_connector_under_asan(tmp_path):
     assert p.returncode == 0, p.stderr[-3000:]
     r = subprocess.run([str(exe), str(lib)], env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0"), capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and r.stdout.startswith("ids ") and "ERROR" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
+
+
+def test_causal_profiler_under_asan(tmp_path):
+    """The causal profiler (signal handler, thread slots, pthread wrappers, symbol-table reader, experiment loop) built with
+    ASan + UBSan and preloaded into its thread-pool target, also built that way: experiments are recorded and no report."""
+    san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g", "-O1", "-std=c++17", f"-I{CSRC / 'include'}"]
+    lib, exe, out = tmp_path / "libcausal_asan.so", tmp_path / "target_asan", tmp_path / "c.coz"
+    p = subprocess.run(["g++", *san, "-fPIC", "-shared", str(CSRC / "prof" / "causal.cc"), "-o", str(lib), "-lpthread", "-ldl"], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    p = subprocess.run(["g++", *san, str(ROOT / "tests" / "native" / "causal_target.cc"), "-o", str(exe), "-lpthread", "-ldl"], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr[-3000:]
+    asan = subprocess.run(["g++", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    env = dict(os.environ, LD_PRELOAD=f"{asan}:{lib}", ASAN_OPTIONS="verify_asan_link_order=0:detect_leaks=0:abort_on_error=0", B200CAUSAL_FILE=str(out),
+               B200CAUSAL_FIXED_SPEEDUP="0,30", B200CAUSAL_EXPERIMENT_SECONDS="0.25")
+    r = subprocess.run([str(exe), "50", "80", "1500000", "pool"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "done 50" in r.stdout and "ERROR" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
+    assert out.read_text().count("experiment\t") >= 2
