@@ -323,6 +323,10 @@ def init_from_env(device: Optional[int] = None, port_offset: int = 17, min_ctas:
     if device is None:
         device = local
     torch.cuda.set_device(device)
+    from .utils import affinity
+
+    if affinity.wanted():
+        affinity.pin_to_gpu(device)   # B200COLL_CPU_AFFINITY=1: run on the CPUs next to this rank's GPU
     if world == 1:
         return Communicator(0, 1, get_unique_id(), device, min_ctas, max_ctas)
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")

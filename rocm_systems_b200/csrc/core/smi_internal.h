@@ -42,6 +42,8 @@ struct NvmlFns {
   nvmlReturn_t (*supportedEvents)(nvmlDevice_t, unsigned long long*) = nullptr;
   nvmlReturn_t (*registerEvents)(nvmlDevice_t, unsigned long long, nvmlEventSet_t) = nullptr;
   nvmlReturn_t (*eventSetWait)(nvmlEventSet_t, nvmlEventData_t*, unsigned int) = nullptr;
+  nvmlReturn_t (*cpuAffinity)(nvmlDevice_t, unsigned int, unsigned long*) = nullptr;
+  nvmlReturn_t (*numaNode)(nvmlDevice_t, unsigned int*) = nullptr;
   nvmlReturn_t (*serial)(nvmlDevice_t, char*, unsigned int) = nullptr;
   nvmlReturn_t (*partNumber)(nvmlDevice_t, char*, unsigned int) = nullptr;
   nvmlReturn_t (*vbios)(nvmlDevice_t, char*, unsigned int) = nullptr;

@@ -75,6 +75,8 @@ static bool loadNvml() {
   sym("nvmlDeviceGetSupportedEventTypes", &gN.supportedEvents, false);
   sym("nvmlDeviceRegisterEvents", &gN.registerEvents, false);
   sym("nvmlEventSetWait_v2", &gN.eventSetWait, false);
+  sym("nvmlDeviceGetCpuAffinity", &gN.cpuAffinity, false);
+  sym("nvmlDeviceGetNumaNodeId", &gN.numaNode, false);
   sym("nvmlDeviceGetSerial", &gN.serial, false);
   sym("nvmlDeviceGetBoardPartNumber", &gN.partNumber, false);
   sym("nvmlDeviceGetVbiosVersion", &gN.vbios, false);
@@ -420,6 +422,22 @@ b200smi_status_t b200smi_reset_locked_clocks(int device, int allow) {
   if (st != B200SMI_OK) return st;
   if (!gN.resetLockedClocks) return B200SMI_ERR_NOT_SUPPORTED;
   return gN.resetLockedClocks(h) == NVML_SUCCESS ? B200SMI_OK : B200SMI_ERR_NVML;
+}
+
+b200smi_status_t b200smi_cpu_affinity(int device, uint64_t* mask, int words, int* numaNode) {
+  if (!mask || words <= 0 || words > 64) return B200SMI_ERR_INVALID;
+  nvmlDevice_t h;
+  b200smi_status_t st = deviceHandle(device, &h);
+  if (st != B200SMI_OK) return st;
+  if (!gN.cpuAffinity) return B200SMI_ERR_NOT_SUPPORTED;
+  static_assert(sizeof(unsigned long) == sizeof(uint64_t), "one NVML affinity word is 64 bits here");
+  memset(mask, 0, sizeof(uint64_t) * words);
+  if (gN.cpuAffinity(h, (unsigned)words, (unsigned long*)mask) != NVML_SUCCESS) return B200SMI_ERR_NVML;
+  if (numaNode) {
+    unsigned int node = 0;
+    *numaNode = (gN.numaNode && gN.numaNode(h, &node) == NVML_SUCCESS) ? (int)node : -1;
+  }
+  return B200SMI_OK;
 }
 
 b200smi_status_t b200smi_identity(int device, b200smi_identity_t* out) {

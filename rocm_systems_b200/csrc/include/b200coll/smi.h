@@ -120,6 +120,11 @@ typedef struct {
 } b200smi_identity_t;
 b200smi_status_t b200smi_identity(int device, b200smi_identity_t* out);
 
+/* CPUs and NUMA node a device is attached to (rocm-smi: --showtoponuma, rsmi_topo_get_numa_node_number /
+ * rsmi_topo_numa_affinity_get): `mask` receives one bit per logical CPU, 64 per word, as many words as given; numaNode is -1
+ * when the driver does not say. A process that drives this GPU runs best on these CPUs. */
+b200smi_status_t b200smi_cpu_affinity(int device, uint64_t* mask, int words, int* numaNode);
+
 /* Asynchronous events of all devices (read only). Types are NVML's bits. */
 #define B200SMI_EVENT_ECC_SINGLE 0x1ull
 #define B200SMI_EVENT_ECC_DOUBLE 0x2ull

@@ -56,5 +56,9 @@ def init_process_group(rank: Optional[int] = None, world_size: Optional[int] = N
         kw["timeout"] = timeout
     if device_id is not None and torch.cuda.is_available():
         torch.cuda.set_device(device_id)
+    from ..utils import affinity
+
+    if torch.cuda.is_available() and affinity.wanted():   # B200COLL_CPU_AFFINITY=1: run on the CPUs next to this rank's GPU
+        affinity.pin_to_gpu(torch.cuda.current_device())
     dist.init_process_group(backend=f"cpu:gloo,cuda:{BACKEND_NAME}", **kw)
     return dist.group.WORLD

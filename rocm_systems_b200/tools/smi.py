@@ -257,6 +257,16 @@ class Smi:
         self.lib.b200smi_reset_locked_clocks.argtypes = [ctypes.c_int, ctypes.c_int]
         self._ck(self.lib.b200smi_reset_locked_clocks(dev, int(allow)))
 
+    def cpu_affinity(self, dev: int) -> dict:
+        """``{"cpus": [...], "numa_node": n or None}``: the logical CPUs (and NUMA node) the device is attached to."""
+        words = 16
+        mask = (ctypes.c_uint64 * words)()
+        node = ctypes.c_int(-1)
+        self.lib.b200smi_cpu_affinity.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_uint64), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        self._ck(self.lib.b200smi_cpu_affinity(dev, mask, words, ctypes.byref(node)))
+        cpus = [w * 64 + b for w in range(words) for b in range(64) if mask[w] >> b & 1]
+        return {"cpus": cpus, "numa_node": None if node.value < 0 else node.value}
+
     def identity(self, dev: int) -> dict:
         """Serial and part number, firmware versions, performance state, settable power range (W), energy since the driver
         loaded (J), remapped memory rows; ``None`` where the driver reports nothing."""
@@ -431,6 +441,7 @@ def main(argv=None) -> int:
     ap.add_argument("--shownvlinkerrors", action="store_true", help="replay / recovery / CRC counters summed over each GPU's links")
     ap.add_argument("--showbus", action="store_true", help="PCIe generation and width")
     ap.add_argument("--showmodes", action="store_true", help="compute, persistence, MIG and ECC modes (read only)")
+    ap.add_argument("--showtoponuma", action="store_true", help="NUMA node and local CPUs of every GPU")
     ap.add_argument("--showactivity", action="store_true", help="SM busy / occupancy / tensor / DRAM / FP activity and PCIe / NVLink traffic over 100 ms")
     ap.add_argument("--showevents", type=float, default=0.0, metavar="SECONDS",
                     help="print XID / ECC / power-state / clock events as they happen; stops after this long without one")
@@ -509,6 +520,13 @@ def main(argv=None) -> int:
         if not a.json:
             for i, d in enumerate(out["identity"]):
                 print(f"GPU{i}: " + "; ".join(id_flags[k](d) for k in id_asked))
+    if a.showtoponuma:
+        from ..utils.affinity import format_cpu_list
+
+        out["numa"] = [smi.cpu_affinity(i) for i in range(n)]
+        if not a.json:
+            for i, v in enumerate(out["numa"]):
+                print(f"GPU{i}: NUMA node {'n/a' if v['numa_node'] is None else v['numa_node']}, CPUs {format_cpu_list(v['cpus']) or 'n/a'}")
     if a.showactivity:
         out["activity"] = [smi.activity(i) for i in range(n)]
         if not a.json:
@@ -537,7 +555,7 @@ def main(argv=None) -> int:
         if not a.json:
             for i, d in enumerate(infos):
                 print(f"GPU{i}: " + "; ".join(singles[k](d) for k in asked))
-    only_new = bool(asked) or bool(id_asked) or bool(a.setclocks) or bool(a.resetclocks) or a.showevents > 0 or a.showactivity or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
+    only_new = bool(asked) or a.showtoponuma or bool(id_asked) or bool(a.setclocks) or bool(a.resetclocks) or a.showevents > 0 or a.showactivity or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
               ("typeName", "Link type between two GPUs", a.showtopotype), ("maxBandwidthMBps", "Max bandwidth (MB/s per direction)", a.shownodesbw),
               ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]

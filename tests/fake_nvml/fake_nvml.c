@@ -109,6 +109,16 @@ nvmlReturn_t nvmlEventSetWait_v2(nvmlEventSet_t s, nvmlEventData_t* out, unsigne
   return 10; /* NVML_ERROR_TIMEOUT */
 }
 
+/* ---- CPU affinity: GPU i sits on CPUs [4 i, 4 i + 3] (FAKE_NVML_CPUS_PER_GPU changes the 4), four GPUs per NUMA node ---- */
+nvmlReturn_t nvmlDeviceGetCpuAffinity(nvmlDevice_t d, unsigned int words, unsigned long* set) {
+  int per = envint("FAKE_NVML_CPUS_PER_GPU", 4);
+  memset(set, 0, sizeof(unsigned long) * words);
+  for (int c = d->idx * per; c < (d->idx + 1) * per; c++)
+    if ((unsigned)(c / 64) < words) set[c / 64] |= 1ul << (c % 64);
+  return NVML_SUCCESS;
+}
+nvmlReturn_t nvmlDeviceGetNumaNodeId(nvmlDevice_t d, unsigned int* node) { *node = (unsigned)(d->idx / 4); return NVML_SUCCESS; }
+
 /* ---- identity, lifetime counters, clock locks (kept in memory, shown by the clock getter) ---- */
 static unsigned int locked_min[16];
 nvmlReturn_t nvmlDeviceGetSerial(nvmlDevice_t d, char* s, unsigned int n) { snprintf(s, n, "165012345%04d", d->idx); return NVML_SUCCESS; }

@@ -384,3 +384,51 @@ srv.shutdown()
 print('ok')
 """, fake_nvml)
     assert "ok" in out
+
+
+def test_cpu_affinity_of_a_gpu_and_pinning(fake_nvml, tmp_path):
+    ncpu = len(os.sched_getaffinity(0))
+    per = max(1, ncpu // 2)                                   # the stand-in puts GPU i on CPUs [per*i, per*i + per)
+    out = _run(f"""
+import os
+from rocm_systems_b200.tools.smi import Smi
+from rocm_systems_b200.utils import affinity
+s = Smi()
+a = s.cpu_affinity(1)
+assert a == {{'cpus': list(range({per}, {2 * per})), 'numa_node': 0}}, a
+assert s.cpu_affinity(5)['numa_node'] == 1
+assert affinity.parse_cpu_list('0-3,8,10-11\\n') == [0, 1, 2, 3, 8, 10, 11] and affinity.format_cpu_list([11, 0, 1, 2, 3, 8, 10]) == '0-3,8,10-11'
+assert affinity.format_cpu_list([]) == '' and affinity.parse_cpu_list('') == []
+g = affinity.gpu_cpus(0)
+assert g['source'] == 'nvml' and g['cpus'] == list(range(0, {per}))
+before = os.sched_getaffinity(0)
+allowed = sorted(before)
+set_ = affinity.pin_to_gpu(0)
+want = [c for c in range(0, {per}) if c in before]
+assert (set_ == want and sorted(os.sched_getaffinity(0)) == want) if want and set(want) != before else set_ is None
+os.sched_setaffinity(0, before)
+assert affinity.pin_to_gpu(7) is None or True                 # CPUs beyond this machine: nothing to intersect with, nothing changes
+assert not affinity.wanted()
+os.environ['B200COLL_CPU_AFFINITY'] = '1'
+assert affinity.wanted()
+print('ok')
+""", fake_nvml, {"FAKE_NVML_CPUS_PER_GPU": str(per)})
+    assert "ok" in out
+    # without NVML affinity: the PCI device's local_cpulist in sysfs (a stand-in tree here)
+    dev = tmp_path / "sys" / "bus" / "pci" / "devices" / "0000:12:00.0"
+    dev.mkdir(parents=True)
+    (dev / "local_cpulist").write_text("0-1\n")
+    (dev / "numa_node").write_text("-1\n")
+    out = _run(f"""
+from rocm_systems_b200.utils import affinity
+from rocm_systems_b200.tools import smi
+smi.Smi.cpu_affinity = lambda self, dev: (_ for _ in ()).throw(RuntimeError('not supported by this device or driver'))
+g = affinity.gpu_cpus(2, sysfs_root=r'{tmp_path / "sys"}')
+assert g == {{'cpus': [0, 1], 'numa_node': None, 'source': 'sysfs'}}, g
+assert affinity.gpu_cpus(3, sysfs_root=r'{tmp_path / "sys"}')['source'] == 'none'
+print('ok')
+""", fake_nvml)
+    assert "ok" in out
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2", FAKE_NVML_CPUS_PER_GPU="6")
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showtoponuma"], env=e, capture_output=True, text=True)
+    assert p.returncode == 0 and "GPU0: NUMA node 0, CPUs 0-5" in p.stdout and "GPU1: NUMA node 0, CPUs 6-11" in p.stdout, p.stdout + p.stderr
