@@ -28,6 +28,7 @@ typedef struct {
   int resetFile;             /* truncate the file instead of appending */
   uint64_t seed;             /* 0: from the clock */
   int verbose;
+  const char* backend;       /* "auto" (default: perf, else timer), "perf" (per-thread CPU-clock events), "timer" (ITIMER_PROF) */
   const char* sourceRanges;  /* source-line scope: file of "<name>\t<lo>-<hi>,..." (hex addresses of the executable's ELF file); replaces the function scope */
 } b200causalConfig_t;
 

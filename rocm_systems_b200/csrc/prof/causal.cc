@@ -19,23 +19,27 @@
 // woken by another thread (lock, condition, join, barrier, semaphore) is credited what became owed while it was blocked:
 // the thread that woke it has already served that, or is the one being sped up.
 //
-// Samples come from ITIMER_PROF (the kernel signals a thread that is running, in proportion to CPU time). A sample stands
-// for the CPU time its thread used since that thread's previous sample, read from the thread's CPU clock, so the scheduler
-// tick, not the nominal rate, sets the granularity and the arithmetic stays right.
+// Samples come from per-thread CPU-clock events where the kernel allows them, else from ITIMER_PROF (see "sample sources"
+// below); either way the kernel signals a thread in proportion to the CPU time it uses. A sample stands for the CPU time its
+// thread used since that thread's previous sample, read from the thread's CPU clock, so whatever the real granularity of the
+// source is, the arithmetic stays right.
 //
 // Ways in: LD_PRELOAD=libb200causal.so with B200CAUSAL_FILE (and _BINARY_SCOPE, _FUNCTION_SCOPE, _FUNCTION_EXCLUDE,
-// _FIXED_SPEEDUP, _SOURCE_RANGES, _FREQ, _EXPERIMENT_SECONDS, _DELAY, _DURATION, _END_TO_END, _FILE_RESET, _RANDOM_SEED, _VERBOSE), or
+// _FIXED_SPEEDUP, _SOURCE_RANGES, _BACKEND, _FREQ, _EXPERIMENT_SECONDS, _DELAY, _DURATION, _END_TO_END, _FILE_RESET, _RANDOM_SEED, _VERBOSE), or
 // b200causalStart / b200causalStop from the program. Output: the text format of the Coz profiler (experiment /
 // throughput-point / latency-point lines), which `tools/causal.py` turns into speed-up tables.
 #include <cxxabi.h>
 #include <dlfcn.h>
 #include <elf.h>
 #include <execinfo.h>
+#include <dirent.h>
 #include <fcntl.h>
 #include <link.h>
+#include <linux/perf_event.h>
 #include <pthread.h>
 #include <semaphore.h>
 #include <signal.h>
+#include <sys/ioctl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <sys/syscall.h>
@@ -261,6 +265,7 @@ struct Thread {
   int64_t lastCpuNs = 0;          // thread CPU clock at its previous sample
   int blocked = 0;                // inside a blocking call: the handler does not pause it (the wake-up credits it instead)
   int keyed = 0;                  // the exit hook is set (never done inside the handler)
+  int perfFd = -1;                // perf backend: this thread's CPU-clock event (threads that started under the profiler)
 };
 constexpr int kMaxThreads = 2048;
 Thread gThreads[kMaxThreads];
@@ -280,11 +285,77 @@ Thread* mySlot(int64_t inherit = -1) {
       t->lastCpuNs = threadCpuNs();
       t->blocked = 0;
       t->keyed = 0;
+      t->perfFd = -1;
       tMe = t;
       return t;
     }
   }
   return nullptr;  // more threads than slots: this one is neither paused nor credited
+}
+
+// ---------------------------------------------------------------- sample sources
+// timer  ITIMER_PROF: one process-wide timer on CPU time; the kernel checks it at scheduler ticks, so a sample stands for a
+//        whole tick (10 ms on a 100 Hz kernel) whatever rate was asked for.
+// perf   one software CPU-clock event per thread (perf_event_open, driven by a high-resolution timer): samples at the rate
+//        asked for, so pauses come in much smaller lumps. Each overflow disables its event (a limit of one), signals the
+//        thread that owns it, and the handler arms it again: no ring buffer is mapped, nothing is read from the event.
+// The reference offers the same two (ROCPROFSYS_CAUSAL_BACKEND = perf | timer | auto, rocprofiler-systems
+// source/lib/core/config.cpp:706-716; source/lib/rocprof-sys/library/perf.cpp).
+std::atomic<bool> gPerf{false};
+int64_t gPerfPeriodNs = 1000000;
+constexpr int kMaxEarly = 1024;  // threads that existed before the profiler started: (tid, fd), closed when it stops
+int gEarlyFd[kMaxEarly];
+int gEarlyCount = 0;
+
+int openCpuClock(pid_t tid) {
+  perf_event_attr a;
+  memset(&a, 0, sizeof(a));
+  a.size = sizeof(a);
+  a.type = PERF_TYPE_SOFTWARE;
+  a.config = PERF_COUNT_SW_CPU_CLOCK;
+  a.sample_period = (uint64_t)gPerfPeriodNs;
+  a.disabled = 1;
+  a.exclude_kernel = 1;
+  a.exclude_hv = 1;
+  const int fd = (int)syscall(SYS_perf_event_open, &a, tid, -1, -1, PERF_FLAG_FD_CLOEXEC);
+  if (fd < 0) return -1;
+  f_owner_ex owner{F_OWNER_TID, tid};
+  if (fcntl(fd, F_SETFL, fcntl(fd, F_GETFL) | O_ASYNC) != 0 || fcntl(fd, F_SETSIG, SIGPROF) != 0 || fcntl(fd, F_SETOWN_EX, &owner) != 0 ||
+      ioctl(fd, PERF_EVENT_IOC_REFRESH, 1) != 0) {
+    close(fd);
+    return -1;
+  }
+  return fd;
+}
+
+// An event for every thread that already runs (the calling thread included). False when the first one cannot be opened:
+// the kernel or the container does not allow it.
+bool openPerfForExistingThreads() {
+  DIR* d = opendir("/proc/self/task");
+  if (!d) return false;
+  bool any = false;
+  while (dirent* e = readdir(d)) {
+    if (e->d_name[0] < '0' || e->d_name[0] > '9' || gEarlyCount >= kMaxEarly) continue;
+    const int fd = openCpuClock((pid_t)atoi(e->d_name));
+    if (fd >= 0) {
+      gEarlyFd[gEarlyCount++] = fd;
+      any = true;
+    }
+  }
+  closedir(d);
+  return any;
+}
+
+void closePerf() {
+  for (int i = 0; i < gEarlyCount; i++) close(gEarlyFd[i]);
+  gEarlyCount = 0;
+  for (auto& t : gThreads) {
+    const int fd = t.perfFd;
+    if (fd >= 0 && t.used.load() == 0) {  // slots still in use close their own when their thread ends
+      t.perfFd = -1;
+      close(fd);
+    }
+  }
 }
 
 // Outside the handler: make sure the slot goes back when the thread ends.
@@ -331,6 +402,10 @@ void onThreadExit(void* p) {
   pthread_sigmask(SIG_BLOCK, &s, nullptr);
   Thread* t = (Thread*)p;
   if (gActive.load()) serve(t);
+  if (t->perfFd >= 0) {
+    close(t->perfFd);
+    t->perfFd = -1;
+  }
   tMe = nullptr;
   t->used.store(0, std::memory_order_release);
 }
@@ -375,9 +450,10 @@ std::atomic<uint64_t> gRecentNext{0};
 pid_t gControllerTid = 0;
 constexpr int kMaxDepth = 32;
 
-void onSample(int, siginfo_t*, void*) {
+void onSample(int, siginfo_t* info, void*) {
   if (!gActive.load(std::memory_order_relaxed)) return;
   const int saved = errno;
+  const int armFd = (info && info->si_code == POLL_HUP && gPerf.load(std::memory_order_relaxed)) ? info->si_fd : -1;
   gInHandler.fetch_add(1, std::memory_order_acquire);
   Thread* me = mySlot();
   if (me && (pid_t)syscall(SYS_gettid) != gControllerTid) {
@@ -413,6 +489,7 @@ void onSample(int, siginfo_t*, void*) {
       me->lastCpuNs = threadCpuNs();
     }
   }
+  if (armFd >= 0) ioctl(armFd, PERF_EVENT_IOC_REFRESH, 1);  // the overflow disabled the event: one more sample, please
   gInHandler.fetch_sub(1, std::memory_order_release);
   errno = saved;
 }
@@ -424,6 +501,7 @@ struct Config {
   double freqHz = 1000.0, experimentSeconds = 0.5, delaySeconds = 0.0, durationSeconds = 0.0;
   bool endToEnd = false, verbose = false;
   uint64_t seed = 0;
+  std::string backend = "auto";
 };
 Config* gCfg = nullptr;
 pthread_t gController;
@@ -588,6 +666,7 @@ __attribute__((constructor)) void onLoad() {
   c.functionExclude = getenv("B200CAUSAL_FUNCTION_EXCLUDE");
   c.speedups = getenv("B200CAUSAL_FIXED_SPEEDUP");
   c.sourceRanges = getenv("B200CAUSAL_SOURCE_RANGES");
+  c.backend = getenv("B200CAUSAL_BACKEND");
   c.freqHz = num("B200CAUSAL_FREQ", 1000.0);
   c.experimentSeconds = num("B200CAUSAL_EXPERIMENT_SECONDS", 0.5);
   c.delaySeconds = num("B200CAUSAL_DELAY", 0.0);
@@ -644,6 +723,8 @@ int b200causalStart(const b200causalConfig_t* cfg) {
   gCfg->endToEnd = cfg->endToEnd != 0;
   gCfg->verbose = cfg->verbose != 0;
   gCfg->seed = cfg->seed;
+  gCfg->backend = (cfg->backend && *cfg->backend) ? cfg->backend : "auto";
+  if (gCfg->backend != "auto" && gCfg->backend != "perf" && gCfg->backend != "timer") return -2;
   if (cfg->resetFile) {
     const int fd = open(cfg->file, O_WRONLY | O_CREAT | O_TRUNC | O_CLOEXEC, 0644);
     if (fd >= 0) close(fd);
@@ -683,6 +764,22 @@ int b200causalStart(const b200causalConfig_t* cfg) {
     if (pthread_create(&gController, nullptr, controllerMain, nullptr) != 0) { gActive.store(false); return -4; }
     gControllerUp = true;
   }
+  gPerf.store(false);
+  if (gCfg->backend != "timer") {
+    gPerfPeriodNs = std::max<int64_t>(50000, (int64_t)(1e9 / freq));
+    gPerf.store(true);  // before the first event is armed: its handler has to arm it again
+    if (openPerfForExistingThreads()) {
+      if (gCfg->verbose) fprintf(stderr, "[b200causal] samples from per-thread CPU-clock events every %lld us\n", (long long)(gPerfPeriodNs / 1000));
+      return 0;
+    }
+    gPerf.store(false);
+    if (gCfg->backend == "perf") {
+      fprintf(stderr, "[b200causal] per-thread CPU-clock events are not available here (perf_event_open: %s)\n", strerror(errno));
+      b200causalStop();
+      return -4;
+    }
+  }
+  if (gCfg->verbose) fprintf(stderr, "[b200causal] samples from the process CPU-time timer (scheduler-tick granularity)\n");
   const long us = std::max(1L, (long)(1e6 / freq));
   itimerval tv;
   tv.it_interval.tv_sec = us / 1000000;
@@ -701,6 +798,7 @@ int b200causalStop(void) {
   itimerval tv;
   memset(&tv, 0, sizeof(tv));
   setitimer(ITIMER_PROF, &tv, nullptr);
+  closePerf();
   if (gControllerUp) {
     void* r = nullptr;
     pthread_join(gController, &r);  // ends and writes the experiment it was in
@@ -842,7 +940,10 @@ struct StartArgs {
 static void* startThread(void* p) {
   StartArgs a = *(StartArgs*)p;
   free(p);
-  if (gActive.load()) keyed(mySlot(a.inherit));
+  if (gActive.load()) {
+    Thread* t = keyed(mySlot(a.inherit));
+    if (t && gPerf.load() && t->perfFd < 0) t->perfFd = openCpuClock((pid_t)syscall(SYS_gettid));
+  }
   return a.fn(a.arg);
 }
 int pthread_create(pthread_t* th, const pthread_attr_t* attr, void* (*fn)(void*), void* arg) {

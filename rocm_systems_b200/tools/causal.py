@@ -230,6 +230,7 @@ def environment(a, speedup: Optional[int] = None, function: Optional[str] = None
     speedups = [speedup] if speedup is not None else a.speedups
     if speedups:
         env["B200CAUSAL_FIXED_SPEEDUP"] = ",".join(str(s) for s in speedups)
+    env["B200CAUSAL_BACKEND"] = a.backend
     env["B200CAUSAL_FREQ"] = str(a.freq)
     env["B200CAUSAL_EXPERIMENT_SECONDS"] = str(a.experiment_seconds)
     env["B200CAUSAL_DELAY"] = str(a.delay)
@@ -309,6 +310,9 @@ def main(argv=None) -> int:
     r.add_argument("-B", "--binary-scope", nargs="*", default=[], help="regular expressions on the paths of loaded objects (default: the executable)")
     r.add_argument("-d", "--delay", type=float, default=0.0, help="seconds before the first experiment")
     r.add_argument("-t", "--duration", type=float, default=0.0, help="seconds of experimenting; 0 = the whole run")
+    r.add_argument("--backend", choices=["auto", "perf", "timer"], default="auto",
+                   help="sample source: per-thread CPU-clock events (perf: samples at --freq), the process CPU-time timer (timer: one sample per "
+                        "scheduler tick), or perf where the kernel allows it and timer otherwise (auto)")
     r.add_argument("--freq", type=float, default=1000.0)
     r.add_argument("--experiment-seconds", type=float, default=0.5)
     r.add_argument("--seed", type=int, default=0)
