@@ -158,7 +158,7 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--pmc-count", type=int, default=5, help="launches to capture (a capture replays every launch several times: keep it small)")
     g.add_argument("--pmc-skip", type=int, default=0, help="matching launches to skip first")
     g.add_argument("--pmc-dry-run", action="store_true", help="print the Nsight Compute command line and stop")
-    g.add_argument("--list-pmc", action="store_true", help="list the derived counters and stop")
+    g.add_argument("-L", "--list-avail", "--list-pmc", dest="list_pmc", action="store_true", help="list the derived counters and stop")
     g = ap.add_argument_group("job files")
     g.add_argument("-i", "--input", default="", metavar="FILE",
                    help="YAML or JSON file with a list `jobs:` (or a .txt file with one `pmc: COUNTER ...` line per pass and optional `kernel: NAME ...`); each job is a set of this launcher's options (long names, dashes or underscores), "
