@@ -289,6 +289,21 @@ def test_system_sampler_command_line_and_console_scripts(tmp_path):
         assert callable(getattr(importlib.import_module(mod), fn)), name
 
 
+def test_python_reference_is_current():
+    """docs/python_api.md is what the generator writes from today's code (regenerate it after changing a public signature)."""
+    import io
+    from contextlib import redirect_stdout
+
+    from rocm_systems_b200.utils import apidoc
+
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert apidoc.main([]) == 0
+    text = buf.getvalue()
+    assert "not importable here" not in text and text.count("\n## `") == len(apidoc.MODULES)
+    assert text == (ROOT / "docs" / "python_api.md").read_text(), "run: python -m rocm_systems_b200.utils.apidoc > docs/python_api.md"
+
+
 def test_settings_listing_covers_the_tool_libraries(capsys):
     """Every listed environment name is read somewhere in the package, and the listing can be narrowed by component."""
     import subprocess as sp
