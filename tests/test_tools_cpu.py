@@ -302,6 +302,12 @@ def test_python_reference_is_current():
     text = buf.getvalue()
     assert "not importable here" not in text and text.count("\n## `") == len(apidoc.MODULES)
     assert text == (ROOT / "docs" / "python_api.md").read_text(), "run: python -m rocm_systems_b200.utils.apidoc > docs/python_api.md"
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert apidoc.main(["--c"]) == 0
+    c = buf.getvalue()
+    assert "ncclResult_t ncclAllReduce(const void* sendbuff" in c and "b200smi_status_t b200smi_activity(int device" in c and c.count("\n- `") > 200
+    assert c == (ROOT / "docs" / "c_api.md").read_text(), "run: python -m rocm_systems_b200.utils.apidoc --c > docs/c_api.md"
 
 
 def test_settings_listing_covers_the_tool_libraries(capsys):
