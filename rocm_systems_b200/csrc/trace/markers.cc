@@ -1,6 +1,7 @@
 #include "b200coll/markers.h"
 
 #include <cuda_runtime_api.h>
+#include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -46,12 +47,45 @@ void writeAtExit() {
   fclose(f);
 }
 
+// A traced program that is ended by a signal would leave no file: with B200COLL_TRACE_SIGNALS=1 (the tracing launcher sets
+// it unless told otherwise) the ranges are written when SIGTERM, SIGINT, SIGQUIT or SIGABRT arrives, then the signal takes
+// its default course. Only where the program has no handler of its own for that signal. The reference's launcher installs
+// the same kind of handlers (rocprofv3 --disable-signal-handlers switches them off) so that an aborted run keeps its output.
+void onFatalSignal(int sig) {
+  static std::atomic<int> once{0};
+  if (once.exchange(1) == 0) {
+    if (gMu.try_lock()) {  // the interrupted thread may hold it: then there is nothing safe to do
+      gMu.unlock();
+      writeAtExit();
+    }
+  }
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+
+void installSignalFlush() {
+  const char* v = getenv("B200COLL_TRACE_SIGNALS");
+  if (!v || !*v || !strcmp(v, "0")) return;
+  for (int sig : {SIGTERM, SIGINT, SIGQUIT, SIGABRT}) {
+    struct sigaction old;
+    if (sigaction(sig, nullptr, &old) != 0 || old.sa_handler != SIG_DFL) continue;
+    struct sigaction sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.sa_handler = onFatalSignal;
+    sigemptyset(&sa.sa_mask);
+    sigaction(sig, &sa, nullptr);
+  }
+}
+
 bool enabled() {
   int e = gEnabled.load();
   if (e < 0) {
     e = b200::Flags::get().traceEnable ? 1 : 0;
     int expected = -1;
-    if (gEnabled.compare_exchange_strong(expected, e) && e == 1) atexit(writeAtExit);
+    if (gEnabled.compare_exchange_strong(expected, e) && e == 1) {
+      atexit(writeAtExit);
+      installSignalFlush();
+    }
   }
   return gEnabled.load() == 1;
 }

@@ -59,6 +59,8 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
     if a.coll_trace or a.marker_trace:
         env["B200COLL_TRACE"] = "1"
         env["B200COLL_TRACE_FILE"] = prefix
+        if not a.disable_signal_handlers:
+            env["B200COLL_TRACE_SIGNALS"] = "1"    # a run ended by SIGTERM / SIGINT / SIGABRT still writes its marker ranges
     if a.host_sampling:
         lib = PKG / "lib" / "libb200sample.so"
         if not lib.exists():
@@ -166,6 +168,9 @@ def parser() -> argparse.ArgumentParser:
     g = ap.add_argument_group("tools")
     g.add_argument("--tool-library", action="append", default=[], help="extra dispatch-table tool(s) to load into the communication library")
     g.add_argument("--preload", action="append", default=[], metavar="LIBRARY", help="libraries to put in front of LD_PRELOAD (a sanitizer runtime, an allocator)")
+    g.add_argument("--disable-signal-handlers", action="store_true",
+                   help="do not flush the marker ranges when the command is ended by SIGTERM / SIGINT / SIGQUIT / SIGABRT (by default they are "
+                        "written, then the signal takes its course; handlers of the program itself are never replaced)")
     g.add_argument("--echo", action="store_true", help="print the command and the environment variables this launcher sets before running")
     ap.add_argument("command", nargs=argparse.REMAINDER, help="-- command to run")
     return ap
@@ -333,6 +338,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         sampler.write_csv(prefix + ".sysmon.csv")
     else:
         rc = subprocess.call(cmd, env=env)
+    if rc < 0:
+        rc = 128 - rc     # ended by a signal: the shell's convention for the exit status
     files = collect(prefix)
     if not files:
         print("prof: the command left no trace files (did it use the GPU / the communication library?)", file=sys.stderr)

@@ -277,6 +277,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if a.setup:
         exec(compile(Path(a.setup).read_text(), a.setup, "exec"), {"__name__": "__setup__"})  # noqa: S102
     rc = 0
+    import signal
+
+    def ended(signum, frame):   # an ended run keeps what it traced: leave through the `finally` below
+        raise SystemExit(128 + signum)
+
+    if signal.getsignal(signal.SIGTERM) == signal.SIG_DFL:
+        signal.signal(signal.SIGTERM, ended)
     try:
         if a.builtin:
             profile = prof

@@ -1011,3 +1011,26 @@ def test_system_sampler_host_and_process_counters(tmp_path):
     assert max(threads) >= 2                                  # this thread and the worker at least
     assert all(v >= 0 for n, _, _, v in s.samples if n == "process_cpu_util_percent")
     assert s.write_csv(str(tmp_path / "s.csv")) == len(s.samples)
+
+
+def test_a_run_ended_by_a_signal_keeps_its_ranges(tmp_path):
+    """Markers under the launcher and the Python tracer: SIGTERM in mid-run still leaves the files, and the exit status says
+    how the run ended; with --disable-signal-handlers the marker file is not written."""
+    import signal
+    import subprocess as sp
+
+    child = ("import os, signal\nfrom rocm_systems_b200.utils import markers\nwith markers.range('before the end'):\n    pass\n"
+             "os.kill(os.getpid(), signal.SIGTERM)\nimport time; time.sleep(5)\n")
+    e = dict(os.environ, PYTHONPATH=str(ROOT))
+    base = [sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "-d"]
+    p = sp.run([*base, str(tmp_path / "a"), "-o", "run", "--", sys.executable, "-c", child], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 128 + signal.SIGTERM, (p.returncode, p.stderr)
+    assert "before the end" in (tmp_path / "a" / "run_regions.csv").read_text()
+    p = sp.run([*base, str(tmp_path / "b"), "-o", "run", "--disable-signal-handlers", "--", sys.executable, "-c", child], env=e, capture_output=True, text=True, timeout=120)
+    assert p.returncode == 128 + signal.SIGTERM and not (tmp_path / "b" / "run_regions.csv").exists()
+    script = tmp_path / "s.py"
+    script.write_text("import os, signal\ndef work():\n    return 1\nwork()\nos.kill(os.getpid(), signal.SIGTERM)\nimport time; time.sleep(5)\n")
+    p = sp.run([sys.executable, "-m", "rocm_systems_b200.tools.pytrace", "-o", str(tmp_path / "py"), "-R", "^work$", "--", str(script)], env=e, capture_output=True,
+               text=True, cwd=ROOT, timeout=120)
+    assert p.returncode == 128 + signal.SIGTERM and "1 calls" in p.stderr
+    assert '"work"' in next(tmp_path.glob("py.pytrace.*.csv")).read_text()
