@@ -159,6 +159,29 @@ void atExitWrite() {
   }
 }
 
+// With B200SAMPLE_SIGNALS=1 (the tracing launcher sets it) a program ended by SIGTERM / SIGINT / SIGQUIT / SIGABRT still
+// writes its samples, then the signal takes its default course; a handler of the program's own is never replaced.
+void onFatalSignal(int sig) {
+  static std::atomic<int> once{0};
+  if (once.exchange(1) == 0) atExitWrite();
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+
+void installSignalFlush() {
+  const char* v = getenv("B200SAMPLE_SIGNALS");
+  if (!v || !*v || !strcmp(v, "0")) return;
+  for (int sig : {SIGTERM, SIGINT, SIGQUIT, SIGABRT}) {
+    struct sigaction old;
+    if (sigaction(sig, nullptr, &old) != 0 || old.sa_handler != SIG_DFL) continue;
+    struct sigaction sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.sa_handler = onFatalSignal;
+    sigemptyset(&sa.sa_mask);
+    sigaction(sig, &sa, nullptr);
+  }
+}
+
 // A forked child starts with an empty ring and no timer (interval timers are not inherited, nor is the sampler thread).
 void inChild() {
   gRunning.store(false);
@@ -178,7 +201,10 @@ __attribute__((constructor)) void onLoad() {
   const double freq = f ? atof(f) : 100.0;
   const int mode = (c && !strcmp(c, "wall")) ? B200SAMPLE_WALL : B200SAMPLE_CPU;
   const double delay = d ? atof(d) : 0.0;
-  if (b200sampleStartDelayed(freq, mode, delay) == 0) atexit(atExitWrite);
+  if (b200sampleStartDelayed(freq, mode, delay) == 0) {
+    atexit(atExitWrite);
+    installSignalFlush();
+  }
 }
 
 }  // namespace

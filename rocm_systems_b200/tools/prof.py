@@ -70,6 +70,8 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
         env["B200SAMPLE_PREFIX"] = prefix
         env["B200SAMPLE_FREQ"] = str(a.sampling_freq)
         env["B200SAMPLE_CLOCK"] = a.sampling_clock
+        if not a.disable_signal_handlers:
+            env["B200SAMPLE_SIGNALS"] = "1"
         if a.sampling_delay > 0:
             env["B200SAMPLE_DELAY"] = str(a.sampling_delay)
     if a.kokkos_trace:

@@ -128,3 +128,23 @@ assert abs(sum(share for _, share in s.top(10000)) - 1.0) < 1e-9
 """
     p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=dict(os.environ, PYTHONPATH=str(ROOT)))
     assert p.returncode == 0, p.stdout + p.stderr
+
+
+def test_samples_survive_a_terminating_signal(target, tmp_path):
+    import signal
+    import time
+
+    prefix = tmp_path / "killed"
+    env = dict(os.environ, LD_PRELOAD=str(LIB), B200SAMPLE_PREFIX=str(prefix), B200SAMPLE_FREQ="200", B200SAMPLE_SIGNALS="1")
+    p = subprocess.Popen([str(target)], env=env, stdout=subprocess.DEVNULL)
+    time.sleep(0.5)
+    p.send_signal(signal.SIGTERM)
+    assert p.wait(timeout=30) == -signal.SIGTERM                        # the signal still ends the program
+    stacks = _folded(next(tmp_path.glob("killed.*.folded")))
+    assert sum(stacks.values()) >= 20 and any(s.endswith("burn_cycles") for s in stacks)
+    env.pop("B200SAMPLE_SIGNALS")
+    env["B200SAMPLE_PREFIX"] = str(tmp_path / "lost")
+    p = subprocess.Popen([str(target)], env=env, stdout=subprocess.DEVNULL)
+    time.sleep(0.3)
+    p.send_signal(signal.SIGTERM)
+    assert p.wait(timeout=30) == -signal.SIGTERM and not list(tmp_path.glob("lost.*"))
