@@ -7,6 +7,9 @@
 #include <memory>
 #include <dlfcn.h>
 #include <string.h>
+#include <strings.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <fstream>
@@ -607,10 +610,30 @@ ncclResult_t pncclGroupEnd(void) {
 static b200collApiFuncTable gTable;
 static std::once_flag gTableOnce;
 
+// Secure mode (B200COLL_TOOL_SECURE=1): a tool library is code that runs inside every rank, so only libraries named by an
+// absolute path, owned by root or by this user and writable by nobody else are loaded, and a tool symbol that merely happens
+// to be in the process is not trusted. B200COLL_TOOL_REGISTER_ENABLED=0 switches tool loading off altogether. The reference's
+// registration shim has the same two switches (rocprofiler-register README: ROCPROFILER_REGISTER_ENABLED, _SECURE).
+static bool trustedToolFile(const std::string& path, std::string* why) {
+  if (path.empty() || path[0] != '/') { *why = "not an absolute path"; return false; }
+  struct stat st;
+  if (stat(path.c_str(), &st) != 0 || !S_ISREG(st.st_mode)) { *why = "not a regular file"; return false; }
+  if (st.st_uid != 0 && st.st_uid != geteuid()) { *why = "owned by another user"; return false; }
+  if (st.st_mode & (S_IWGRP | S_IWOTH)) { *why = "writable by group or others"; return false; }
+  return true;
+}
+
 static void loadTools() {
+  auto on = [](const char* name, bool dflt) {
+    const char* v = getenv(name);
+    return (v && *v) ? (strcmp(v, "0") != 0 && strcasecmp(v, "false") != 0 && strcasecmp(v, "off") != 0) : dflt;
+  };
+  if (!on("B200COLL_TOOL_REGISTER_ENABLED", true)) return;
+  const bool secure = on("B200COLL_TOOL_SECURE", false);
   // A tool already in the process (linked or LD_PRELOADed) …
   std::vector<b200collToolConfigure_fn> fns;
-  if (void* sym = dlsym(RTLD_DEFAULT, "b200coll_tool_configure")) fns.push_back((b200collToolConfigure_fn)sym);
+  if (!secure)
+    if (void* sym = dlsym(RTLD_DEFAULT, "b200coll_tool_configure")) fns.push_back((b200collToolConfigure_fn)sym);
   // … and every library named in B200COLL_TOOL_LIBRARIES.
   const std::string& libs = Flags::get().toolLibs;
   size_t pos = 0;
@@ -619,6 +642,11 @@ static void loadTools() {
     std::string one = libs.substr(pos, c == std::string::npos ? std::string::npos : c - pos);
     pos = c == std::string::npos ? libs.size() : c + 1;
     if (one.empty()) continue;
+    std::string why;
+    if (secure && !trustedToolFile(one, &why)) {
+      BWARN("tool library '%s' refused in secure mode: %s", one.c_str(), why.c_str());
+      continue;
+    }
     void* h = dlopen(one.c_str(), RTLD_NOW | RTLD_LOCAL);
     if (!h) {
       BWARN("tool library '%s' could not be loaded: %s", one.c_str(), dlerror());

@@ -76,6 +76,8 @@ TOOL_SETTINGS = [
     ("perf", "NCCL_TESTS_SPLIT_MASK", "", "older spelling of NCCL_TESTS_SPLIT=AND <mask>"),
     ("model", "B200COLL_CPU_AFFINITY", "0", "1: pin each rank's process to the CPUs its GPU is attached to when the process group or communicator is made"),
     ("model", "B200_LINEAR_GEMM", "", "which GEMM the model's linear layers use (own kernel by default; cublas for comparison)"),
+    ("coll", "B200COLL_TOOL_REGISTER_ENABLED", "1", "0: load no tool library and hand the dispatch table to nobody"),
+    ("coll", "B200COLL_TOOL_SECURE", "0", "1: only tool libraries named by an absolute path, owned by root or this user and writable by nobody else"),
     ("coll", "B200COLL_TRACE_SIGNALS", "0", "1: write the marker ranges when SIGTERM / SIGINT / SIGQUIT / SIGABRT ends the program (the launcher sets it)"),
     ("coll", "B200COLL_EMULATE_RANKS", "", "run the multi-rank kernels of the self-tests as one cooperative kernel over this many ranks"),
     ("coll", "B200COLL_SAMPLE_TOOL_OUTPUT", "", "where the example tool library writes its call log"),

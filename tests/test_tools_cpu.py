@@ -39,6 +39,41 @@ assert v.value == 22005, v.value
     assert "ncclGetVersion calls=3" in text and "payload_bytes=0" in text
 
 
+def test_tool_loading_switches(tmp_path):
+    """Off switch and secure mode of tool loading: an absolute path to a file nobody else can write is loaded, a relative
+    path or a file others can write is refused with a warning, and with registration off nothing is loaded."""
+    import shutil
+    import stat
+
+    from rocm_systems_b200.utils import build
+
+    tool = build.build_sample_tool()
+    good = tmp_path / "libtool.so"
+    shutil.copy(tool, good)
+    good.chmod(0o755)
+    loose = tmp_path / "libloose.so"
+    shutil.copy(tool, loose)
+    loose.chmod(0o777)
+    code = "import ctypes\nfrom rocm_systems_b200 import _lib\nlib = _lib.load()\nv = ctypes.c_int()\nassert lib.ncclGetVersion(ctypes.byref(v)) == 0\n"
+
+    def run(libs, **env):
+        out = tmp_path / f"out_{len(list(tmp_path.glob('out_*')))}.txt"
+        e = dict(os.environ, PYTHONPATH=str(ROOT), B200COLL_TOOL_LIBRARIES=libs, B200COLL_SAMPLE_TOOL_OUTPUT=str(out), B200COLL_DEBUG="WARN", **env)
+        p = subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True, timeout=120, cwd=tmp_path)
+        assert p.returncode == 0, p.stderr
+        return out.exists() and "ncclGetVersion calls=1" in out.read_text(), p.stdout + p.stderr
+
+    assert run(str(good))[0]
+    assert run(str(good), B200COLL_TOOL_SECURE="1")[0]
+    loaded, log = run(str(loose), B200COLL_TOOL_SECURE="1")
+    assert not loaded and "refused in secure mode: writable by group or others" in log
+    loaded, log = run("libtool.so", B200COLL_TOOL_SECURE="1")
+    assert not loaded and "not an absolute path" in log
+    assert run("libtool.so")[0] is False or True      # without secure mode a relative name is left to the dynamic loader's search
+    assert not run(str(good), B200COLL_TOOL_REGISTER_ENABLED="0")[0]
+    assert stat.S_IMODE(loose.stat().st_mode) == 0o777
+
+
 def test_markers_nest_and_write_csv(tmp_path):
     out = _py(f"""
 from rocm_systems_b200.utils import markers
