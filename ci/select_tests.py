@@ -33,12 +33,23 @@ RULES = [
     ("rocm_systems_b200/csrc/fused/gemm_fp8*", ["tests/test_fp8_reference_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/fused/*", ["tests/test_kernel_resources_cpu.py"], ["tests/test_gemm_gpu.py", "tests/test_train_ops_gpu.py", "tests/test_gpu_fused_multi.py", "tests/test_zz_fused_single_gpu.py", "tests/test_zz_no_alloc.py"], True),
     ("rocm_systems_b200/csrc/torch/*", ["tests/test_dist_cpu.py"], ["tests/test_gpu_collectives.py"], True),
-    ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py", "tests/test_sanitizers_cpu.py"], ["tests/test_profiler_gpu.py"], True),
+    ("rocm_systems_b200/csrc/trace/kokkosp.cc", ["tests/test_kokkosp_cpu.py", "tests/test_sanitizers_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/trace/ompt.cc", ["tests/test_ompt_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/trace/*", ["tests/test_tools_cpu.py", "tests/test_sanitizers_cpu.py", "tests/test_kokkosp_cpu.py", "tests/test_ompt_cpu.py", "tests/test_instrument_cpu.py"], ["tests/test_profiler_gpu.py"], True),
     ("rocm_systems_b200/csrc/prof/sampler.cc", ["tests/test_host_sampler_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/prof/causal.cc", ["tests/test_causal_cpu.py", "tests/test_sanitizers_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/prof/instrument.cc", ["tests/test_instrument_cpu.py", "tests/test_sanitizers_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/prof/*", ["tests/test_tools_cpu.py"], ["tests/test_profiler_gpu.py"], True),
     ("rocm_systems_b200/csrc/perf/*", ["tests/test_verifiable_cpu.py", "tests/test_perf_cli_cpu.py"], [], True),
+    ("rocm_systems_b200/csrc/include/b200coll/causal.h", ["tests/test_causal_cpu.py", "tests/test_tools_cpu.py"], [], True),
     ("rocm_systems_b200/csrc/include/*", ["tests/test_bootstrap.py", "tests/test_tools_cpu.py"], ["tests/test_gpu_collectives.py"], True),
+    ("rocm_systems_b200/tools/causal.py", ["tests/test_causal_cpu.py"], [], False),
+    ("rocm_systems_b200/tools/pytrace.py", ["tests/test_pytrace_cpu.py", "tests/test_tools_cpu.py"], [], False),
+    ("rocm_systems_b200/tools/instrument.py", ["tests/test_instrument_cpu.py"], [], False),
     ("rocm_systems_b200/tools/*", ["tests/test_tools_cpu.py", "tests/test_smi_fake.py"], [], False),
+    ("rocm_systems_b200/utils/affinity.py", ["tests/test_smi_fake.py"], [], False),
+    ("rocm_systems_b200/utils/apidoc.py", ["tests/test_tools_cpu.py"], [], False),
+    ("rocm_systems_b200/utils/causal.py", ["tests/test_causal_cpu.py"], [], False),
     ("rocm_systems_b200/parallel/pp.py", ["tests/test_parallel_cpu.py", "tests/test_examples_build_cpu.py"], [], False),
     ("rocm_systems_b200/parallel/cp.py", ["tests/test_parallel_cpu.py", "tests/test_examples_build_cpu.py"], [], False),
     ("rocm_systems_b200/parallel/fsdp.py", ["tests/test_fsdp_layout_cpu.py"], ["tests/test_gpu_fused_multi.py"], False),
@@ -51,9 +62,13 @@ RULES = [
     ("rocm_systems_b200/*", ["tests"], ["tests"], False),
     ("tests/*", ["{path}"], ["{path}"], False),
     ("bench.py", [], ["tests/test_gpu_fused_multi.py"], False),
+    ("examples/causal_pipeline.cc", ["tests/test_causal_cpu.py"], [], False),
     ("examples/*", ["tests/test_examples_build_cpu.py"], [], False),
+    ("pyproject.toml", ["tests/test_tools_cpu.py"], [], False),
     ("ci/*", ["tests/test_ci_select.py"], [], False),
     (".github/*", [], [], False),
+    ("docs/python_api.md", ["tests/test_tools_cpu.py"], [], False),
+    ("docs/c_api.md", ["tests/test_tools_cpu.py"], [], False),
     ("docs/*", [], [], False),
     ("*.md", [], [], False),
     ("profiles/*", [], [], False),
