@@ -66,6 +66,7 @@ RULES = [
     ("examples/*", ["tests/test_examples_build_cpu.py"], [], False),
     ("pyproject.toml", ["tests/test_tools_cpu.py"], [], False),
     ("ci/*", ["tests/test_ci_select.py"], [], False),
+    ("Makefile", [], [], False),
     (".github/*", [], [], False),
     ("docs/python_api.md", ["tests/test_tools_cpu.py"], [], False),
     ("docs/c_api.md", ["tests/test_tools_cpu.py"], [], False),
