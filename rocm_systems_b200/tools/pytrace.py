@@ -51,7 +51,7 @@ class Profiler:
     def __init__(self, include_functions: Sequence[str] = (), exclude_functions: Sequence[str] = (), restrict_functions: Sequence[str] = (),
                  include_modules: Sequence[str] = (), exclude_modules: Sequence[str] = (), restrict_modules: Sequence[str] = (),
                  label: Sequence[str] = (), full_filepath: bool = False, trace_c: bool = False, min_duration_us: float = 0.0,
-                 max_records: int = 2_000_000):
+                 max_records: int = 2_000_000, backend: str = "auto"):
         self.inc_f, self.exc_f, self.res_f = _compile(include_functions), _compile([*_DEFAULT_EXCLUDE_FUNCTIONS, *exclude_functions]), _compile(restrict_functions)
         self.inc_m, self.exc_m, self.res_m = _compile(include_modules), _compile([*_DEFAULT_EXCLUDE_MODULES, *exclude_modules]), _compile(restrict_modules)
         self.label = tuple(label)
@@ -63,7 +63,15 @@ class Profiler:
         self.dropped = 0
         self._labels: Dict[object, Optional[str]] = {}     # code object (or C function) -> label, None = filtered out
         self._tls = threading.local()
-        self._lock = threading.Lock()
+        if backend not in ("auto", "monitoring", "setprofile"):
+            raise ValueError("backend is auto, monitoring or setprofile")
+        have = hasattr(sys, "monitoring")
+        if backend == "monitoring" and not have:
+            raise RuntimeError("sys.monitoring needs Python 3.12 or later")
+        # Two ways to hear about calls. sys.monitoring (3.12+): events per code object that can be switched off for the code
+        # objects the filters reject, so what is not traced costs nothing after its first call. sys.setprofile: one hook for
+        # every call and return of every function, filtered inside the hook.
+        self.backend = "monitoring" if (have and backend != "setprofile") else "setprofile"
 
     # ------------------------------------------------------------------ filters and labels
     def wanted(self, func: str, filename: str) -> bool:
@@ -151,11 +159,90 @@ class Profiler:
             parts.append(f"{n}={v[:24]}")
         return ", ".join(parts)
 
+    # ------------------------------------------------------------------ the monitoring callbacks
+    def _mon_start(self, code, offset):
+        label = self._labels.get(code, self)
+        if label is self:
+            label = self._labels[code] = self._label_of(code)
+        if label is None:
+            return sys.monitoring.DISABLE        # never again for this code object
+        if "args" in self.label:
+            label = f"{label}({self._args(sys._getframe(1))})"
+        self._stack().append((label, time.monotonic_ns(), code))
+        return None
+
+    def _mon_end(self, code, offset, value):
+        if self._labels.get(code, self) is None:
+            return sys.monitoring.DISABLE
+        self._mon_pop(code)
+        return None
+
+    def _mon_unwind(self, code, offset, exc):     # left by an exception: cannot be switched off per code object
+        if self._labels.get(code) is not None:
+            self._mon_pop(code)
+
+    def _mon_pop(self, code) -> None:
+        stack = self._stack()
+        if stack and stack[-1][2] is code:
+            label, t0, _ = stack.pop()
+            self._finish(label, t0, len(stack))
+
+    def _mon_call(self, code, offset, func, arg0):
+        if self._labels.get(code, self) is None or type(func).__name__ not in ("builtin_function_or_method", "method_descriptor", "wrapper_descriptor"):
+            return None
+        label = self._labels.get(func, self)
+        if label is self:
+            name = getattr(func, "__qualname__", getattr(func, "__name__", "?"))
+            mod = getattr(func, "__module__", None) or ""
+            full = f"{mod}.{name}" if mod else name
+            label = self._labels[func] = full if self.wanted(full, f"<builtin {mod}>") else None
+        self._stack().append((label, time.monotonic_ns(), func))
+        return None
+
+    def _mon_c_end(self, code, offset, func, arg0):
+        stack = self._stack()
+        if stack and stack[-1][2] is func:
+            label, t0, _ = stack.pop()
+            if label is not None:
+                self._finish(label, t0, len(stack))
+
+    def _start_monitoring(self) -> None:
+        m = sys.monitoring
+        self._tool = m.PROFILER_ID
+        if m.get_tool(self._tool) is not None:
+            raise RuntimeError(f"another profiler ({m.get_tool(self._tool)}) already uses sys.monitoring")
+        m.use_tool_id(self._tool, "b200-pytrace")
+        E = m.events
+        m.register_callback(self._tool, E.PY_START, self._mon_start)
+        m.register_callback(self._tool, E.PY_RESUME, self._mon_start)
+        m.register_callback(self._tool, E.PY_RETURN, self._mon_end)
+        m.register_callback(self._tool, E.PY_YIELD, self._mon_end)
+        m.register_callback(self._tool, E.PY_UNWIND, self._mon_unwind)
+        events = E.PY_START | E.PY_RESUME | E.PY_RETURN | E.PY_YIELD | E.PY_UNWIND
+        if self.trace_c:
+            m.register_callback(self._tool, E.CALL, self._mon_call)
+            m.register_callback(self._tool, E.C_RETURN, self._mon_c_end)
+            m.register_callback(self._tool, E.C_RAISE, self._mon_c_end)
+            events |= E.CALL | E.C_RETURN | E.C_RAISE
+        m.set_events(self._tool, events)
+
+    def _stop_monitoring(self) -> None:
+        m = sys.monitoring
+        m.set_events(self._tool, 0)
+        for ev in (m.events.PY_START, m.events.PY_RESUME, m.events.PY_RETURN, m.events.PY_YIELD, m.events.PY_UNWIND, m.events.CALL, m.events.C_RETURN,
+                   m.events.C_RAISE):
+            m.register_callback(self._tool, ev, None)
+        m.free_tool_id(self._tool)
+        m.restart_events()          # what was switched off for this run is heard again by the next one
+
     # ------------------------------------------------------------------ control
     def start(self) -> "Profiler":
         if Profiler._active is not None:
             raise RuntimeError("a Python tracer is already active")
         Profiler._active = self
+        if self.backend == "monitoring":
+            self._start_monitoring()
+            return self
         threading.setprofile(self._hook)
         if hasattr(threading, "setprofile_all_threads"):
             threading.setprofile_all_threads(self._hook)
@@ -164,14 +251,17 @@ class Profiler:
 
     def stop(self) -> "Profiler":
         if Profiler._active is self:
-            sys.setprofile(None)
-            threading.setprofile(None)
-            if hasattr(threading, "setprofile_all_threads"):
-                threading.setprofile_all_threads(None)
+            if self.backend == "monitoring":
+                self._stop_monitoring()
+            else:
+                sys.setprofile(None)
+                threading.setprofile(None)
+                if hasattr(threading, "setprofile_all_threads"):
+                    threading.setprofile_all_threads(None)
             Profiler._active = None
             stack = getattr(self._tls, "stack", None)
             while stack:                     # ranges still open on this thread end now (the frames that called start())
-                label, t0 = stack.pop()
+                label, t0 = stack.pop()[:2]
                 if label is not None:
                     self._finish(label, t0, len(stack))
         return self
@@ -257,6 +347,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--trace-c", action="store_true", help="calls of C functions (builtins, extension modules) too")
     ap.add_argument("--min-duration-us", type=float, default=0.0, help="drop calls shorter than this")
     ap.add_argument("--max-records", type=int, default=2_000_000)
+    ap.add_argument("--backend", choices=["auto", "monitoring", "setprofile"], default="auto",
+                    help="monitoring (Python 3.12+): functions the filters reject cost nothing after their first call; setprofile: one hook for every call")
     ap.add_argument("--stats", action="store_true", help="print the functions by inclusive time when the script ends")
     ap.add_argument("--top", type=int, default=20)
     ap.add_argument("script", nargs=argparse.REMAINDER, help="-- script and its arguments")
@@ -273,7 +365,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         script = found
     global profile
     prof = Profiler(a.function_include, a.function_exclude, a.function_restrict, a.module_include, a.module_exclude, a.module_restrict, a.label,
-                    a.full_filepath, a.trace_c, a.min_duration_us, a.max_records)
+                    a.full_filepath, a.trace_c, a.min_duration_us, a.max_records, a.backend)
     if a.setup:
         exec(compile(Path(a.setup).read_text(), a.setup, "exec"), {"__name__": "__setup__"})  # noqa: S102
     rc = 0

