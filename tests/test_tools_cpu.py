@@ -310,7 +310,7 @@ def test_system_sampler_command_line_and_console_scripts(tmp_path):
         names = {n for (n,) in db.query("select distinct s.value from counter_sample c join string s on s.id = c.name_id")[1]}
     assert {"host_cpu_util_percent", "process_rss_bytes", "process_threads"} <= names
     rss = [float(l.rsplit(",", 1)[1]) for l in out.read_text().splitlines() if l.startswith('"process_rss_bytes"')]
-    assert all(v == int(v) and v > 1e6 for v in rss)                             # whole bytes: not rounded to six digits
+    assert all(v == int(v) for v in rss) and max(rss) > 1e6 and max(rss) % 4096 == 0   # whole bytes (pages), not rounded to six digits
     from rocm_systems_b200 import __main__ as door
 
     for name in door.TOOLS:                                                     # every tool the package door lists exists and has a main()
