@@ -6,6 +6,7 @@
 #ifndef B200COLL_MARKERS_H_
 #define B200COLL_MARKERS_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -37,6 +38,9 @@ void b200txClear(void);
 
 /* Library version and build description (cf. rocm-core's getROCmVersion / rocm_version.cpp). */
 const char* b200collBuildInfo(void);
+/* File this library was loaded from and the prefix it is installed under (the directory above its lib/); 0 on success.
+ * (cf. rocm-core's getROCmInstallPath.) Either buffer may be NULL. */
+int b200collGetInstallPath(char* library, size_t libraryLen, char* prefix, size_t prefixLen);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,8 @@
 #include "b200coll/markers.h"
 
 #include <cuda_runtime_api.h>
+#include <dlfcn.h>
+#include <limits.h>
 #include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -11,6 +13,7 @@
 #include <atomic>
 #include <map>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include "../core/common.h"
@@ -175,6 +178,25 @@ const char* b200collBuildInfo(void) {
   snprintf(buf, sizeof(buf), "b200coll 0.1.0 (NCCL API %d.%d.%d) sm_100a cuda-runtime %d.%d built " __DATE__, NCCL_MAJOR, NCCL_MINOR, NCCL_PATCH, rt / 1000,
            (rt % 1000) / 10);
   return buf;
+}
+
+// Where this library was loaded from, and the directory above its lib/ (the install prefix), found from the address of this
+// very function: what the reference's rocm-core answers with getROCmInstallPath (rocm-core/rocm_getpath.cpp).
+int b200collGetInstallPath(char* library, size_t libraryLen, char* prefix, size_t prefixLen) {
+  Dl_info info;
+  if (!dladdr((void*)&b200collGetInstallPath, &info) || !info.dli_fname) return -1;
+  char resolved[4096];
+  const char* path = realpath(info.dli_fname, resolved) ? resolved : info.dli_fname;
+  if (library && libraryLen) snprintf(library, libraryLen, "%s", path);
+  if (prefix && prefixLen) {
+    std::string p = path;
+    for (int up = 0; up < 2; up++) {  // drop the file name, then the lib directory
+      const size_t slash = p.rfind('/');
+      p = slash == std::string::npos || slash == 0 ? "/" : p.substr(0, slash);
+    }
+    snprintf(prefix, prefixLen, "%s", p.c_str());
+  }
+  return 0;
 }
 
 }  // extern "C"

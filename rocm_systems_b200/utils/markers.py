@@ -111,5 +111,15 @@ def write_csv(path: str, pid: int | None = None) -> int:
     return len(rows)
 
 
+def install_path() -> dict:
+    """``{"library": file the native library was loaded from, "prefix": the directory above its lib/}``."""
+    lib = _l()
+    lib.b200collGetInstallPath.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
+    a, b = ctypes.create_string_buffer(4096), ctypes.create_string_buffer(4096)
+    if lib.b200collGetInstallPath(a, 4096, b, 4096) != 0:
+        raise RuntimeError("the library cannot tell where it was loaded from")
+    return {"library": a.value.decode(), "prefix": b.value.decode()}
+
+
 def build_info() -> str:
     return _l().b200collBuildInfo().decode()

@@ -94,6 +94,8 @@ assert by['inner']['depth'] == 1 and by['outer']['depth'] == 0 and by['point']['
 assert by['outer']['begin_ns'] <= by['inner']['begin_ns'] <= by['inner']['end_ns'] <= by['outer']['end_ns']
 assert markers.write_csv(r'{tmp_path}/m.csv') == 5
 assert 'b200coll' in markers.build_info()
+where = markers.install_path()
+assert where['library'].endswith('/lib/libb200coll.so') and where['library'].startswith(where['prefix'] + '/') and where['prefix'].endswith('rocm_systems_b200')
 print('ok')
 """)
     assert "ok" in out
