@@ -447,6 +447,14 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
             print(f"counters: ncu exited with {rc}", file=sys.stderr)
             return rc
         a.inputs = [a.output + ".ncu-rep"]
+        try:   # the machine the capture was taken on, beside it (the reference keeps a sysinfo file with every profiled workload)
+            from . import info
+
+            with open(a.output + "_sysinfo.json", "w") as f:
+                json.dump({"host": info.host_info(), "devices": info.device_info(), "library": info.library_info(), "command": command,
+                           "counters": [d["name"] for d in cs.defs]}, f, indent=1)
+        except Exception as e:  # noqa: BLE001  a note beside the capture must not fail the capture
+            print(f"counters: no sysinfo file ({type(e).__name__}: {e})", file=sys.stderr)
     if a.list:
         for d in cs.defs:
             print(f"{d['name']:<22} [{d.get('unit', '')}] = {d['expression']}\n{'':<22} {d.get('description', '')}")
