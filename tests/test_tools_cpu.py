@@ -830,6 +830,28 @@ def test_counter_analysis_panels_stalls_and_verdicts(tmp_path, capsys):
     assert "<img" not in evil and "k&lt;img src=x&gt;" in evil and "a &amp; b" in evil
 
 
+def test_counter_collection_leaves_a_machine_description(tmp_path, capsys, monkeypatch):
+    """--collect with the Nsight Compute run and the report reader replaced: the capture is followed by a sysinfo file (or,
+    where the machine cannot be described, by a note), never by a failure."""
+    import subprocess as sp
+
+    from rocm_systems_b200.tools import counters, roofline
+
+    calls = []
+    monkeypatch.setattr(sp, "call", lambda cmd, **k: calls.append(cmd) or 0)
+    monkeypatch.setattr(roofline, "read_ncu", lambda path: roofline.parse_ncu_csv(_analyze_csv()))
+    (tmp_path / "p.json").write_text('{"hbm_gbs": 6650.0, "bf16_tflops": 1600.0}')
+    out = tmp_path / "cap"
+    rc = counters.main(["--collect", "--counter", "hbm_gbs", "-k", "stream", "-c", "1", "-o", str(out), "--peaks", str(tmp_path / "p.json"), "--", "python", "x.py"])
+    text = capsys.readouterr()
+    assert rc == 0 and calls and calls[0][0] == "ncu" and "--clock-control" in calls[0] and "streamKernel" in text.out
+    info = tmp_path / "cap_sysinfo.json"
+    assert info.exists() or "no sysinfo file" in text.err
+    if info.exists():
+        doc = json.loads(info.read_text())
+        assert doc["command"] == ["python", "x.py"] and doc["counters"] == ["hbm_gbs"] and "host" in doc
+
+
 def test_profiler_launcher_counter_collection(tmp_path, capsys):
     """``prof --pmc``: the Nsight Compute line asks for exactly the raw metrics of the chosen counters (bounded, clocks
     untouched), and a capture becomes one row per (launch, counter)."""
