@@ -539,7 +539,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("-c", "--count", type=int, default=0)
     p.add_argument("-d", "--delay-ms", type=int, default=1000)
     p.add_argument("-e", "--fields", nargs="+", default=["sm_clock", "power", "temp", "gpu_util", "mem_used"])
+    p.add_argument("-f", "--fieldgroup", default="", help="a field group instead of -e: default, activity")
     p.add_argument("-i", "--devices", nargs="+", type=int)
+    p.add_argument("-l", "--list-fields", action="store_true", help="list the fields and field groups that can be watched and stop")
     sub.add_parser("health", help="one health verdict per device")
     p = sub.add_parser("diag", help="short diagnostics per device")
     p.add_argument("--level", type=int, default=1, choices=[1, 2])
@@ -607,6 +609,21 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                 print(f"    {c['check']:<18} {'ok' if c['pass'] else 'FAILED':<7} {c['detail']}")
         return 0 if all(r["pass"] for r in res) else 1
     elif a.cmd == "dmon":
+        if a.list_fields:
+            for f in FIELDS:
+                print(f"{f:<18} {PROM[f][1] if f in PROM else ''}")
+            for name, members in t.field_groups.items():
+                print(f"group {name}: {' '.join(members)}")
+            return 0
+        if a.fieldgroup:
+            if a.fieldgroup not in t.field_groups:
+                print(f"telemetry: no field group {a.fieldgroup!r}; known: {', '.join(t.field_groups)}", file=sys.stderr)
+                return 2
+            a.fields = list(t.field_groups[a.fieldgroup])
+        unknown = [f for f in a.fields if f not in FIELDS]
+        if unknown:
+            print(f"telemetry: unknown field(s) {unknown}; `dmon -l` lists them", file=sys.stderr)
+            return 2
         t.fields = a.fields
         if a.devices:
             t.devices = a.devices
@@ -614,7 +631,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         n = 0
         while a.count == 0 or n < a.count:
             for d, vals in t.latest().items():
-                print(f"{d}\t" + "\t".join(f"{vals[f]:g}" for f in a.fields), flush=True)
+                print(f"{d}\t" + "\t".join("n/a" if vals[f] is None else f"{vals[f]:g}" for f in a.fields), flush=True)
             n += 1
             if a.count == 0 or n < a.count:
                 time.sleep(a.delay_ms / 1e3)

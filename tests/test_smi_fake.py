@@ -432,3 +432,19 @@ print('ok')
     e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2", FAKE_NVML_CPUS_PER_GPU="6")
     p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", "--showtoponuma"], env=e, capture_output=True, text=True)
     assert p.returncode == 0 and "GPU0: NUMA node 0, CPUs 0-5" in p.stdout and "GPU1: NUMA node 0, CPUs 6-11" in p.stdout, p.stdout + p.stderr
+
+
+def test_dmon_field_groups_listing_and_unsupported_fields(fake_nvml):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2")
+    base = [sys.executable, "-m", "rocm_systems_b200.tools.telemetry", "dmon"]
+    p = subprocess.run([*base, "-f", "activity", "-c", "1"], env=e, capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0, p.stderr
+    lines = p.stdout.strip().splitlines()
+    head = lines[0].split("\t")
+    assert head[0] == "GPU" and "tensor_active" in head and len(lines) == 3
+    row = dict(zip(head, lines[1].split("\t")))
+    assert row["tensor_active"] == "62.5" and row["fp64_active"] == "n/a" and row["sm_active"] == "91"
+    p = subprocess.run([*base, "-l"], env=e, capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and "tensor_active" in p.stdout and "group activity: sm_active" in p.stdout and "group default:" in p.stdout
+    assert subprocess.run([*base, "-e", "nope", "-c", "1"], env=e, capture_output=True, text=True, timeout=60).returncode == 2
+    assert subprocess.run([*base, "-f", "nope", "-c", "1"], env=e, capture_output=True, text=True, timeout=60).returncode == 2
