@@ -43,3 +43,21 @@ def test_parallel_examples_run_on_cpu_ranks(example, port, marker, extra):
                         "--master-port", str(port), str(ROOT / "examples" / example), *extra], capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert marker in p.stdout
+
+
+def test_python_tracing_example_under_the_launcher(tmp_path):
+    """examples/trace_python_step.py under the launcher and the Python tracer: marker ranges of the steps and their phases and
+    the Python calls of the example end up in one database, the phases inside their step."""
+    import sqlite3
+    import sys
+
+    p = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--marker-trace", "-d", str(tmp_path), "-o", "run", "--",
+                        sys.executable, "-m", "rocm_systems_b200.tools.pytrace", "-MR", "trace_python_step", "--", str(ROOT / "examples" / "trace_python_step.py"),
+                        "--steps", "3"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert p.returncode == 0 and "trace_python_step OK" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+    db = sqlite3.connect(str(tmp_path / "run.db"))
+    got = {(c, n): k for c, n, k in db.execute("select category, name, count(*) from regions group by 1, 2")}
+    assert got[("MARKER_API", "forward + backward")] == 3 and got[("MARKER_API", "step 1")] == 1 and got[("PYTHON_FUNCTION", "forward_backward")] == 3
+    step = db.execute("select start_ns, end_ns from regions where name = 'step 2'").fetchone()
+    inner = db.execute("select start_ns, end_ns from regions where category = 'MARKER_API' and name = 'optimizer' order by start_ns desc limit 1").fetchone()
+    assert step[0] <= inner[0] <= inner[1] <= step[1]
