@@ -294,13 +294,15 @@ def _print_matrix(title: str, m, n: int) -> None:
         print(f"GPU{i:<4}" + "".join(f"{str(m[i][j]):<12}" for j in range(n)))
 
 
-SUBCOMMANDS = ("version", "list", "static", "metric", "topology", "process", "monitor", "event")
+SUBCOMMANDS = ("version", "list", "static", "firmware", "bad-pages", "metric", "nvlink", "topology", "process", "monitor", "event", "set", "reset")
 
 
 def _sub_main(argv) -> int:
     """The subcommand front end (the layout of the reference's newer amd-smi command line: ``list``, ``static``, ``metric``,
-    ``topology``, ``process``, ``monitor``, ``event``, ``version``), over the same readings as the flag front end. Every
-    subcommand takes ``-g GPU [GPU ...]`` and ``--json`` / ``--csv``; nothing here changes a device."""
+    ``firmware``, ``bad-pages``, ``xgmi`` (here ``nvlink``), ``topology``, ``process``, ``monitor``, ``event``, ``set``, ``reset``,
+    ``version``), over the same readings as the flag front end. Every subcommand takes ``-g GPU [GPU ...]`` and ``--json`` /
+    ``--csv``. Only ``set`` and ``reset`` can change a device, and only with ``--allow-set`` and B200SMI_ALLOW_SET=1; ``reset``
+    hands locked clocks back to the driver, it never resets a GPU."""
     ap = argparse.ArgumentParser(prog="b200-smi")
     sub = ap.add_subparsers(dest="cmd", required=True)
     subs = {}
@@ -308,6 +310,9 @@ def _sub_main(argv) -> int:
                         ("static", "what does not change while the GPU runs: product, bus, limits, modes, link count"),
                         ("metric", "what does: clocks, power, temperature, memory, utilisation, ECC totals, NVLink error counters, throttle reasons"),
                         ("topology", "link type, hops, weight, bandwidth and peer access between every pair"),
+                        ("firmware", "VBIOS and InfoROM image versions"), ("bad-pages", "rows of device memory remapped after errors"),
+                        ("nvlink", "links up, error counters and, with --activity, traffic per GPU"),
+                        ("set", "power limit or SM clock range (refused unless allowed twice over)"), ("reset", "hand locked SM clocks back to the driver"),
                         ("process", "compute processes per GPU"), ("monitor", "one line of readings per GPU and interval"),
                         ("event", "XID / ECC / power-state / clock events as they happen")):
         sp = sub.add_parser(name, help=help_)
@@ -317,7 +322,12 @@ def _sub_main(argv) -> int:
         subs[name] = sp
     subs["monitor"].add_argument("-w", "--watch", type=float, default=1.0, metavar="SECONDS", help="interval between lines")
     subs["monitor"].add_argument("-i", "--iterations", type=int, default=1, help="how many intervals (0: until interrupted)")
-    for name in ("metric", "monitor"):
+    subs["set"].add_argument("--power-limit", type=float, metavar="WATTS")
+    subs["set"].add_argument("--clocks", type=int, nargs=2, metavar=("MIN_MHZ", "MAX_MHZ"))
+    subs["reset"].add_argument("--clocks", action="store_true", help="the only thing that can be reset")
+    for name in ("set", "reset"):
+        subs[name].add_argument("--allow-set", action="store_true", help="required, together with B200SMI_ALLOW_SET=1")
+    for name in ("metric", "monitor", "nvlink"):
         subs[name].add_argument("--activity", action="store_true", help="SM / tensor / DRAM activity and PCIe / NVLink traffic over the interval "
                                 "(performance-monitoring samples of the driver; no profiler involved)")
     subs["event"].add_argument("-t", "--timeout", type=float, default=5.0, metavar="SECONDS", help="stop after this long without an event")
@@ -358,6 +368,42 @@ def _sub_main(argv) -> int:
         emit([{"tool": "b200-smi", "package": __version__, "driver": smi.driver_version()}])
     elif a.cmd == "list":
         emit([{"gpu": g, "bus_id": smi.info(g)["busId"], "uuid": smi.info(g)["uuid"]} for g in gpus])
+    elif a.cmd == "firmware":
+        emit([{"gpu": g, "vbios": smi.identity(g)["vbios"], "inforom_image": smi.identity(g)["inforom_image"], "driver": smi.driver_version()} for g in gpus])
+    elif a.cmd == "bad-pages":
+        rows = []
+        for g in gpus:
+            r = smi.identity(g)["remapped_rows"]
+            rows.append({"gpu": g, **(r if r is not None else {"correctable": None, "uncorrectable": None, "pending": None, "failed": None})})
+        emit(rows)
+    elif a.cmd == "nvlink":
+        rows = []
+        for g in gpus:
+            d, e = smi.info(g), smi.nvlink_errors(g)
+            rows.append({"gpu": g, "links": d["nvlinkCount"], "links_up": d["nvlinkActive"], "replay": e["replay"], "recovery": e["recovery"],
+                         "crc_flit": e["crcFlit"], "crc_data": e["crcData"]})
+            if a.activity:
+                act = smi.activity(g)
+                rows[-1].update({"tx_mibs": act["nvlink_tx_mibs"], "rx_mibs": act["nvlink_rx_mibs"]})
+        emit(rows)
+    elif a.cmd in ("set", "reset"):
+        try:
+            for g in gpus if a.gpu is not None else []:
+                if a.cmd == "set" and a.power_limit is not None:
+                    smi.set_power_limit(g, int(a.power_limit * 1000), a.allow_set)
+                if a.cmd == "set" and a.clocks:
+                    smi.set_locked_clocks(g, a.clocks[0], a.clocks[1], a.allow_set)
+                if a.cmd == "reset" and a.clocks:
+                    smi.reset_locked_clocks(g, a.allow_set)
+            if a.gpu is None:
+                print("b200-smi: name the GPUs with -g; nothing is set on all GPUs by default", file=sys.stderr)
+                smi.close()
+                return 2
+            emit([{"gpu": g, "done": a.cmd} for g in gpus])
+        except RuntimeError as e:
+            print(f"b200-smi: {e}", file=sys.stderr)
+            smi.close()
+            return 2
     elif a.cmd == "static":
         rows = []
         for g in gpus:

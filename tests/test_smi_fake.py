@@ -448,3 +448,24 @@ def test_dmon_field_groups_listing_and_unsupported_fields(fake_nvml):
     assert p.returncode == 0 and "tensor_active" in p.stdout and "group activity: sm_active" in p.stdout and "group default:" in p.stdout
     assert subprocess.run([*base, "-e", "nope", "-c", "1"], env=e, capture_output=True, text=True, timeout=60).returncode == 2
     assert subprocess.run([*base, "-f", "nope", "-c", "1"], env=e, capture_output=True, text=True, timeout=60).returncode == 2
+
+
+def test_more_subcommands_firmware_bad_pages_nvlink_set_reset(fake_nvml):
+    import json
+
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="2", FAKE_NVML_ECC="1")
+    run = lambda *args, **env: subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", *args], env=dict(e, **env), capture_output=True, text=True)  # noqa: E731
+    fw = json.loads(run("firmware", "--json").stdout)
+    assert fw[0]["vbios"] == "97.00.88.00.0F" and fw[0]["inforom_image"] is None and fw[1]["driver"] == "580.159.fake"
+    bp = json.loads(run("bad-pages", "--json").stdout)
+    assert bp[0]["correctable"] == 0 and bp[1]["correctable"] == 2 and bp[1]["failed"] is False
+    nv = json.loads(run("nvlink", "--activity", "--json", "-g", "1").stdout)
+    assert nv == [{"gpu": 1, "links": 18, "links_up": 18, "replay": nv[0]["replay"], "recovery": nv[0]["recovery"], "crc_flit": nv[0]["crc_flit"],
+                   "crc_data": nv[0]["crc_data"], "tx_mibs": 1000.0, "rx_mibs": 900.0}]
+    p = run("set", "--clocks", "1200", "1400", "-g", "0", "--allow-set")
+    assert p.returncode == 2 and "disabled" in p.stderr                                   # the environment half of the gate is missing
+    p = run("set", "--clocks", "1200", "1400", "--allow-set", B200SMI_ALLOW_SET="1")
+    assert p.returncode == 2 and "name the GPUs" in p.stderr                              # never on all GPUs by default
+    p = run("set", "--clocks", "1200", "1400", "--power-limit", "800", "-g", "0", "--allow-set", B200SMI_ALLOW_SET="1")
+    assert p.returncode == 0 and "GPU 0: done set" in p.stdout, p.stderr
+    assert run("reset", "--clocks", "-g", "0", "--allow-set", B200SMI_ALLOW_SET="1").returncode == 0
