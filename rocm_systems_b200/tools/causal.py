@@ -82,7 +82,8 @@ def _std(xs: Iterable[float]) -> float:
 
 def analyze(experiments: List[dict], point: Optional[str] = None, min_experiments: int = 1) -> List[dict]:
     """One entry per (selected function, progress point) that has a baseline (speed-up 0): ``{selected, point, kind,
-    baseline_period_ns, rows: [{speedup, program_speedup, stddev, experiments}], impact}``. The program speed-up at s is
+    baseline_period_ns, rows: [{speedup, program_speedup, stddev, experiments}], impact}``. For a latency point the period is
+    the time an item spends in flight where that can be told (Little's law), else the time per departure. The program speed-up at s is
     ``100 * (1 - period_s / period_0)`` with ``period = sum(duration) / sum(visits)`` over the experiments at s; the spread
     is that of the per-experiment speed-ups; ``impact`` is the area under the curve per unit of virtual speed-up (what the
     reference sorts by)."""
@@ -93,26 +94,40 @@ def analyze(experiments: List[dict], point: Optional[str] = None, min_experiment
                 groups[(e["selected"], name, "throughput")][e["speedup"]].append((visits, e["duration"]))
         for name, lat in e["latency"].items():
             if lat["departures"] > 0:
-                groups[(e["selected"], name, "latency")][e["speedup"]].append((lat["departures"], e["duration"]))
+                # (departures, duration, items in flight when the experiment ended, arrivals)
+                groups[(e["selected"], name, "latency")][e["speedup"]].append((lat["departures"], e["duration"], max(lat["difference"], 0), lat["arrivals"]))
     out = []
     for (selected, name, kind), by in sorted(groups.items()):
         if point is not None and name != point:
             continue
         if 0 not in by:
             continue
-        base = sum(d for _, d in by[0]) / sum(v for v, _ in by[0])
-        base_spread = _std([100.0 * (1.0 - (d / v) / base) for v, d in by[0]])
+        # A latency point with items in flight at the ends of its experiments gives the time an item spends between begin and
+        # end by Little's law: items in flight (averaged over the experiments, weighted by their length) / arrival rate
+        # = sum(in flight x duration) / sum(arrivals). Where nothing was in flight when the experiments ended (whole runs,
+        # strictly sequential items) the time per departure is what is left to compare.
+        little = kind == "latency" and all(sum(r[2] * r[1] for r in runs) > 0 and sum(r[3] for r in runs) > 0 for runs in by.values())
+
+        def period_of(runs):
+            if little:
+                return sum(r[2] * r[1] for r in runs) / sum(r[3] for r in runs)
+            return sum(r[1] for r in runs) / sum(r[0] for r in runs)
+
+        def one(r):
+            return (r[2] * r[1] / r[3]) if (little and r[3]) else r[1] / r[0]
+
+        base = period_of(by[0])
+        base_spread = _std([100.0 * (1.0 - one(r) / base) for r in by[0]])
         rows = []
         for s in sorted(by):
             runs = by[s]
             if len(runs) < min_experiments:
                 continue
-            period = sum(d for _, d in runs) / sum(v for v, _ in runs)
-            rows.append({"speedup": s, "program_speedup": 100.0 * (1.0 - period / base),
-                         "stddev": _std([100.0 * (1.0 - (d / v) / base) for v, d in runs]), "experiments": len(runs)})
+            rows.append({"speedup": s, "program_speedup": 100.0 * (1.0 - period_of(runs) / base),
+                         "stddev": _std([100.0 * (1.0 - one(r) / base) for r in runs]), "experiments": len(runs)})
         area = sum(0.5 * (a["program_speedup"] + b["program_speedup"]) * (b["speedup"] - a["speedup"]) for a, b in zip(rows, rows[1:]))
         span = rows[-1]["speedup"] - rows[0]["speedup"] if len(rows) > 1 else 0
-        out.append({"selected": selected, "point": name, "kind": kind, "baseline_period_ns": base, "baseline_stddev": base_spread, "rows": rows,
+        out.append({"selected": selected, "point": name, "kind": kind + (" (time in flight)" if little else ""), "baseline_period_ns": base, "baseline_stddev": base_spread, "rows": rows,
                     "impact": area / span if span else 0.0})
     out.sort(key=lambda r: -r["impact"])
     return out

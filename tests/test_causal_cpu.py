@@ -65,6 +65,26 @@ def test_parse_and_predictions():
     assert len(causal.validate(res, [("f", "it", 50, 60.0, 2.0), ("f", "it", 70, 0.0, 2.0)])) == 2
 
 
+def test_latency_point_by_littles_law():
+    """Items in flight at the ends of the experiments turn a latency point into the time an item spends in flight:
+    sum(in flight x duration) / sum(arrivals); with nothing in flight the time per departure is compared instead."""
+    text = "\n".join([
+        "experiment\tselected=f\tspeedup=0.00\tduration=1000\tselected-samples=5",
+        "latency-point\tname=q\tarrivals=10\tdepartures=10\tdifference=4",
+        "experiment\tselected=f\tspeedup=0.00\tduration=3000\tselected-samples=5",
+        "latency-point\tname=q\tarrivals=30\tdepartures=28\tdifference=6",
+        "experiment\tselected=f\tspeedup=0.50\tduration=1000\tselected-samples=5",
+        "latency-point\tname=q\tarrivals=20\tdepartures=20\tdifference=4",
+    ])
+    r = causal.analyze(causal.parse(text))[0]
+    assert r["kind"] == "latency (time in flight)"
+    assert r["baseline_period_ns"] == pytest.approx((4 * 1000 + 6 * 3000) / 40)          # 550 ns in flight per item
+    rows = {row["speedup"]: row["program_speedup"] for row in r["rows"]}
+    assert rows[50] == pytest.approx(100 * (1 - (4 * 1000 / 20) / 550))
+    plain = causal.analyze(causal.parse(text.replace("difference=4", "difference=0").replace("difference=6", "difference=0")))[0]
+    assert plain["kind"] == "latency" and plain["baseline_period_ns"] == pytest.approx(4000 / 38)
+
+
 def test_end_to_end_plan_and_environment(tmp_path):
     ap_args = ["run", "-o", str(tmp_path / "x.coz"), "-e", "-n", "2", "-s", "0", "20", "-F", "^a$", "^b$", "--", "prog"]
     import argparse  # noqa: F401
