@@ -492,6 +492,7 @@ def main(argv=None) -> int:
     ap.add_argument("--showevents", type=float, default=0.0, metavar="SECONDS",
                     help="print XID / ECC / power-state / clock events as they happen; stops after this long without one")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("-d", "--device", nargs="+", type=int, default=None, metavar="GPU", help="only these GPUs in the per-GPU listings (default: all)")
     for flag, help_ in (("--showserial", "serial and part number"), ("--showvbios", "VBIOS version"), ("--showfwinfo", "VBIOS and InfoROM image versions"),
                         ("--showperflevel", "performance state (P0 = fastest)"), ("--showmaxpower", "range the power limit can be set in"),
                         ("--showenergycounter", "energy drawn since the driver was loaded"), ("--showretiredpages", "rows of device memory remapped after errors")):
@@ -507,6 +508,10 @@ def main(argv=None) -> int:
         print(f"b200-smi: {e}", file=sys.stderr)
         return 1
     n = smi.count()
+    devs = list(range(n)) if a.device is None else list(a.device)
+    if any(not 0 <= d < n for d in devs):
+        print(f"b200-smi: no GPU {next(d for d in devs if not 0 <= d < n)} (there are {n})", file=sys.stderr)
+        return 2
     out = {}
     if a.setpowerlimit:
         try:
@@ -530,27 +535,27 @@ def main(argv=None) -> int:
         if not a.json:
             print(f"Driver version: {out['driver_version']}")
     if a.showpids:
-        out["processes"] = {i: smi.processes(i) for i in range(n)}
+        out["processes"] = {i: smi.processes(i) for i in devs}
         if not a.json:
             print(f"{'GPU':<4}{'PID':<10}{'Memory GiB':<12}Name")
             for i, ps in out["processes"].items():
                 for pr in ps:
                     print(f"{i:<4}{pr['pid']:<10}{pr['used_memory_bytes'] / 2**30:<12.2f}{pr['name']}")
     if a.shownvlinkerrors:
-        out["nvlink_errors"] = [smi.nvlink_errors(i) for i in range(n)]
+        out["nvlink_errors"] = [smi.nvlink_errors(i) for i in devs]
         if not a.json:
             print(f"{'GPU':<4}{'links':<7}{'replay':<10}{'recovery':<10}{'crc flit':<10}{'crc data':<10}")
-            for i, e in enumerate(out["nvlink_errors"]):
+            for i, e in zip(devs, out["nvlink_errors"]):
                 print(f"{i:<4}{e['linksRead']:<7}{e['replay']:<10}{e['recovery']:<10}{e['crcFlit']:<10}{e['crcData']:<10}")
     if a.showbus:
-        out["pcie"] = [smi.pcie(i) for i in range(n)]
+        out["pcie"] = [smi.pcie(i) for i in devs]
         if not a.json:
-            for i, e in enumerate(out["pcie"]):
+            for i, e in zip(devs, out["pcie"]):
                 print(f"GPU{i}: PCIe gen {e['generation']} x{e['width']}")
     if a.showmodes:
-        out["modes"] = [smi.modes(i) for i in range(n)]
+        out["modes"] = [smi.modes(i) for i in devs]
         if not a.json:
-            for i, m in enumerate(out["modes"]):
+            for i, m in zip(devs, out["modes"]):
                 print(f"GPU{i}: compute mode {m['compute_mode']}, persistence {m['persistence']}, MIG {m['mig']}, ECC {m['ecc']}")
     id_flags = {"showserial": lambda d: f"serial {d['serial'] or 'n/a'}, part number {d['part_number'] or 'n/a'}", "showvbios": lambda d: f"VBIOS {d['vbios'] or 'n/a'}",
                 "showfwinfo": lambda d: f"VBIOS {d['vbios'] or 'n/a'}, InfoROM image {d['inforom_image'] or 'n/a'}",
@@ -562,22 +567,22 @@ def main(argv=None) -> int:
                 f"{', remap pending' if d['remapped_rows']['pending'] else ''}{', REMAP FAILED' if d['remapped_rows']['failed'] else ''}"}
     id_asked = [k for k in id_flags if getattr(a, k)]
     if id_asked:
-        out["identity"] = [smi.identity(i) for i in range(n)]
+        out["identity"] = [smi.identity(i) for i in devs]
         if not a.json:
-            for i, d in enumerate(out["identity"]):
+            for i, d in zip(devs, out["identity"]):
                 print(f"GPU{i}: " + "; ".join(id_flags[k](d) for k in id_asked))
     if a.showtoponuma:
         from ..utils.affinity import format_cpu_list
 
-        out["numa"] = [smi.cpu_affinity(i) for i in range(n)]
+        out["numa"] = [smi.cpu_affinity(i) for i in devs]
         if not a.json:
-            for i, v in enumerate(out["numa"]):
+            for i, v in zip(devs, out["numa"]):
                 print(f"GPU{i}: NUMA node {'n/a' if v['numa_node'] is None else v['numa_node']}, CPUs {format_cpu_list(v['cpus']) or 'n/a'}")
     if a.showactivity:
-        out["activity"] = [smi.activity(i) for i in range(n)]
+        out["activity"] = [smi.activity(i) for i in devs]
         if not a.json:
             fmt = lambda v, unit: "n/a" if v is None else f"{v:g}{unit}"  # noqa: E731
-            for i, v in enumerate(out["activity"]):
+            for i, v in zip(devs, out["activity"]):
                 print(f"GPU{i}: SM busy {fmt(v['sm_active_pct'], ' %')}, occupancy {fmt(v['sm_occupancy_pct'], ' %')}, tensor {fmt(v['tensor_active_pct'], ' %')}, "
                       f"DRAM {fmt(v['dram_active_pct'], ' %')}, fp64/32/16 {fmt(v['fp64_active_pct'], '')}/{fmt(v['fp32_active_pct'], '')}/{fmt(v['fp16_active_pct'], '')} %, "
                       f"PCIe tx/rx {fmt(v['pcie_tx_mibs'], '')}/{fmt(v['pcie_rx_mibs'], '')} MiB/s, NVLink tx/rx {fmt(v['nvlink_tx_mibs'], '')}/{fmt(v['nvlink_rx_mibs'], '')} MiB/s "
@@ -596,10 +601,10 @@ def main(argv=None) -> int:
                "showthrottle": lambda d: ",".join(d["throttleReasonNames"]) or "-"}
     asked = [k for k in singles if getattr(a, k)]
     if asked:
-        infos = [smi.info(i) for i in range(n)]
+        infos = [smi.info(i) for i in devs]
         out["devices"] = infos
         if not a.json:
-            for i, d in enumerate(infos):
+            for i, d in zip(devs, infos):
                 print(f"GPU{i}: " + "; ".join(singles[k](d) for k in asked))
     only_new = bool(asked) or a.showtoponuma or bool(id_asked) or bool(a.setclocks) or bool(a.resetclocks) or a.showevents > 0 or a.showactivity or a.showmodes or a.showpids or a.shownvlinkerrors or a.showbus or a.showdriverversion
     tables = [("weight", "Weight between two GPUs", a.showtopoweight), ("hops", "Hops between two GPUs", a.showtopohops),
@@ -607,10 +612,10 @@ def main(argv=None) -> int:
               ("p2pAccessible", "Peer access between two GPUs", a.showtopoaccess)]
     one_table = any(t[2] for t in tables)
     if a.showall or not (a.showtopo or one_table or a.showhealth or a.setpowerlimit or only_new):
-        out["devices"] = [smi.info(i) for i in range(n)]
+        out["devices"] = [smi.info(i) for i in devs]
         if not a.json:
             print(f"{'GPU':<4}{'Name':<22}{'Bus':<18}{'SM MHz':<12}{'Power W':<10}{'Temp C':<8}{'Mem used/total GiB':<22}{'NVLink':<8}{'Throttle'}")
-            for i, d in enumerate(out["devices"]):
+            for i, d in zip(devs, out["devices"]):
                 print(f"{i:<4}{d['name'][:20]:<22}{d['busId']:<18}{str(d['smClockMhz']) + '/' + str(d['smClockMaxMhz']):<12}{d['powerMilliwatt'] / 1000:<10.1f}"
                       f"{d['temperatureC']:<8}{d['memUsedBytes'] / 2**30:>6.1f} / {d['memTotalBytes'] / 2**30:<11.1f}{str(d['nvlinkActive']) + '/' + str(d['nvlinkCount']):<8}"
                       f"{','.join(d['throttleReasonNames']) or '-'}")
@@ -628,9 +633,9 @@ def main(argv=None) -> int:
                 if on:
                     _print_matrix(title, out["topology"][k], n)
     if a.showhealth:
-        out["health"] = [dict(zip(("level", "reason"), smi.health(i))) for i in range(n)]
+        out["health"] = [dict(zip(("level", "reason"), smi.health(i))) for i in devs]
         if not a.json:
-            for i, h in enumerate(out["health"]):
+            for i, h in zip(devs, out["health"]):
                 print(f"GPU{i}: {('PASS', 'WARN', 'FAIL')[h['level']]} - {h['reason']}")
     if a.json:
         print(json.dumps(out, indent=1))

@@ -469,3 +469,16 @@ def test_more_subcommands_firmware_bad_pages_nvlink_set_reset(fake_nvml):
     p = run("set", "--clocks", "1200", "1400", "--power-limit", "800", "-g", "0", "--allow-set", B200SMI_ALLOW_SET="1")
     assert p.returncode == 0 and "GPU 0: done set" in p.stdout, p.stderr
     assert run("reset", "--clocks", "-g", "0", "--allow-set", B200SMI_ALLOW_SET="1").returncode == 0
+
+
+def test_flag_front_end_device_selection(fake_nvml):
+    e = dict(os.environ, B200SMI_NVML_LIBRARY=fake_nvml, PYTHONPATH=str(ROOT), FAKE_NVML_GPUS="4")
+    run = lambda *args: subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.smi", *args], env=e, capture_output=True, text=True)  # noqa: E731
+    p = run("--showtemp", "--showserial", "-d", "2", "3")
+    assert p.returncode == 0 and "GPU2:" in p.stdout and "GPU3: serial 1650123450003" in p.stdout and "GPU0" not in p.stdout and "GPU1" not in p.stdout, p.stdout + p.stderr
+    import json
+    doc = json.loads(run("--showbus", "--shownvlinkerrors", "--json", "-d", "1").stdout)
+    assert len(doc["pcie"]) == 1 and len(doc["nvlink_errors"]) == 1
+    assert run("--showtemp", "-d", "9").returncode == 2
+    p = run("--showall")
+    assert p.returncode == 0 and all(f"GPU{i}" in p.stdout or f"\n{i} " in p.stdout or str(i) in p.stdout for i in range(4))
