@@ -204,7 +204,7 @@ def test_both_sample_sources(target, tmp_path, backend, announcement):
     ex = causal.parse(out.read_text())
     assert len(ex) == 2
     per_second = ex[0]["selected_samples"] / (ex[0]["real_duration"] / 1e9)
-    assert per_second > (500 if backend == "perf" else 20), per_second     # 1 kHz asked for; the timer gives one sample per scheduler tick
+    assert per_second > (250 if backend == "perf" else 20), per_second     # 1 kHz of CPU time asked for (less per wall second on a busy machine); the timer gives one sample per scheduler tick
     res = causal.analyze(ex, point="iteration")
     assert causal.validate(res, [("cpu_slow_func", "iteration", 20, 20.0, 7.0)]) == [], causal.format_report(res)
 
