@@ -35,7 +35,8 @@ def test_statistics_ranges_and_coverage(target, tmp_path):
     assert by["inner(int)"]["inclusive_ns"] == by["inner(int)"]["exclusive_ns"] >= 7 * 1_000_000           # a leaf; it sleeps 1 ms
     o = by["outer()"]
     assert o["inclusive_ns"] >= 3 * 4_000_000 and 3 * 2_000_000 <= o["exclusive_ns"] < o["inclusive_ns"] - 5_000_000
-    assert by["app::Solver::run(int)"]["exclusive_ns"] < 1_000_000 <= by["app::Solver::run(int)"]["inclusive_ns"]
+    r = by["app::Solver::run(int)"]
+    assert r["inclusive_ns"] >= 12_000_000 and r["exclusive_ns"] < r["inclusive_ns"] / 2      # nearly all of its time is in outer()
     assert doc["functions"][0]["function"] == "main"                                                       # sorted by inclusive time
     c = doc["coverage"]
     assert c["functions_defined"] == 6 and c["functions_called"] == 5 and c["uncalled"] == ["never_called()"] and c["percent"] == pytest.approx(83.33)
