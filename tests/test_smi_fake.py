@@ -222,7 +222,7 @@ from rocm_systems_b200.tools.smi import Smi, FIELDS, ACTIVITY_FIELDS
 s = Smi()
 t0 = time.time()
 a = s.activity(0)
-assert 0.09 < time.time() - t0 < 1.0 and 90 <= a['interval_ms'] < 1000
+assert 0.09 < time.time() - t0 < 5.0 and 90 <= a['interval_ms'] < 5000
 assert a['tensor_active_pct'] == 40.0 and a['sm_active_pct'] == 91.0 and a['sm_occupancy_pct'] == 48.5 and a['dram_active_pct'] == 33.0
 assert a['fp64_active_pct'] is None and a['pcie_tx_mibs'] == 120.0
 assert a['nvlink_tx_mibs'] == 1000.0 and a['nvlink_rx_mibs'] == 900.0            # two consecutive samples
@@ -234,7 +234,7 @@ except RuntimeError as e:
     assert 'not supported' in str(e)
 time.sleep(0.12)
 b = s.activity(0)                                                                  # one new sample: previous -> now
-assert b['nvlink_tx_mibs'] == 1000.0 and 100 <= b['interval_ms'] < 1000
+assert b['nvlink_tx_mibs'] == 1000.0 and 100 <= b['interval_ms'] < 5000
 c = s.activity(1)                                                                  # another device has its own samples
 assert c['nvlink_tx_mibs'] == 1000.0
 assert len(ACTIVITY_FIELDS) == 11 and FIELDS['nvlink_rx_mibs'] == 22
