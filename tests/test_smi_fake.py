@@ -243,7 +243,7 @@ s.watch_start([0], ['tensor_active', 'power'], period_ms=60, keep=50)
 time.sleep(0.4)
 hist = s.history(0, 'tensor_active')
 s.watch_stop()
-assert len(hist) >= 3 and all(v == 40.0 for _, v in hist), hist
+assert len(hist) >= 2 and all(v == 40.0 for _, v in hist), hist
 print('ok')
 """, fake_nvml, {"FAKE_NVML_TENSOR": "40"})
     assert "ok" in out
