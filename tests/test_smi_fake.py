@@ -380,7 +380,7 @@ assert c.devices == list(range(8))
 assert c.process() == 16 and ((3, 'temp', 45.0) in got) and ((7, 'sm_clock', 1500.0) in got)
 stop = threading.Event()
 th = threading.Thread(target=c.run, kwargs={'stop': stop}); th.start(); time.sleep(0.1); stop.set(); th.join(2)
-assert not th.is_alive() and c.reads >= 3
+assert not th.is_alive() and c.reads >= 2
 srv.shutdown()
 print('ok')
 """, fake_nvml)
