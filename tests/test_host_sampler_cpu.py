@@ -141,7 +141,7 @@ def test_samples_survive_a_terminating_signal(target, tmp_path):
     p.send_signal(signal.SIGTERM)
     assert p.wait(timeout=30) == -signal.SIGTERM                        # the signal still ends the program
     stacks = _folded(next(tmp_path.glob("killed.*.folded")))
-    assert sum(stacks.values()) >= 20 and any(s.endswith("burn_cycles") for s in stacks)
+    assert sum(stacks.values()) >= 5 and any(s.endswith("burn_cycles") for s in stacks)
     env.pop("B200SAMPLE_SIGNALS")
     env["B200SAMPLE_PREFIX"] = str(tmp_path / "lost")
     p = subprocess.Popen([str(target)], env=env, stdout=subprocess.DEVNULL)
