@@ -8,6 +8,7 @@ under the tracer and then point a validator at the files.
     python -m rocm_systems_b200.tools.validate perfetto trace.perfetto.json --category kernel --min-slices 10 --counter gpu_power
     python -m rocm_systems_b200.tools.validate db trace.db --table kernel_dispatch:10 --table collective:1
     python -m rocm_systems_b200.tools.validate csv out.rank0.csv --column Device_Us --function ncclAllReduce
+    python -m rocm_systems_b200.tools.validate causal exp.coz --min-experiments 8 --selected cpu_slow_func --point iteration
 """
 from __future__ import annotations
 
@@ -19,7 +20,8 @@ import sys
 from typing import List, Optional, Sequence
 
 
-def check_perfetto(path: str, categories: Sequence[str] = (), names: Sequence[str] = (), counters: Sequence[str] = (), min_slices: int = 0) -> List[str]:
+def check_perfetto(path: str, categories: Sequence[str] = (), names: Sequence[str] = (), counters: Sequence[str] = (), min_slices: int = 0,
+                   min_flows: int = 0) -> List[str]:
     errs: List[str] = []
     try:
         doc = json.load(open(path))
@@ -49,6 +51,15 @@ def check_perfetto(path: str, categories: Sequence[str] = (), names: Sequence[st
     for c in counters:
         if not any(t.startswith(c) for t in tracks):
             errs.append(f"no counter track starting with {c!r} (have {sorted(tracks)[:8]})")
+    # arrows: every start has its finish, the finish is not earlier, and there are as many as expected
+    starts = {e.get("id"): e for e in ev if e.get("ph") == "s"}
+    ends = {e.get("id"): e for e in ev if e.get("ph") == "f"}
+    if set(starts) != set(ends):
+        errs.append(f"{len(set(starts) ^ set(ends))} arrows without their other end")
+    if any(ends[i]["ts"] < starts[i]["ts"] for i in starts if i in ends):
+        errs.append("an arrow points back in time")
+    if len(starts) < min_flows:
+        errs.append(f"{len(starts)} arrows, expected at least {min_flows}")
     # slices on one track must not partially overlap (nesting is fine): a sign of mixed clocks
     by_track = {}
     for e in slices:
@@ -113,6 +124,33 @@ def check_csv(path: str, columns: Sequence[str] = (), functions: Sequence[str] =
     return errs
 
 
+def check_causal(path: str, min_experiments: int = 1, selected: Sequence[str] = (), points: Sequence[str] = ()) -> List[str]:
+    """An output file of the causal profiler: experiments are there, have sane durations and a speed-up between 0 and 100 %,
+    the named functions were selected and the named progress points were visited."""
+    import re
+
+    from .causal import parse
+
+    errs: List[str] = []
+    try:
+        ex = parse(open(path).read())
+    except OSError as e:
+        return [f"{path}: {e}"]
+    if len(ex) < min_experiments:
+        errs.append(f"{len(ex)} experiments, expected at least {min_experiments}")
+    for e in ex:
+        if not 0 <= e["speedup"] <= 100 or e["duration"] <= 0 or e["duration"] > e["real_duration"]:
+            errs.append(f"experiment on {e['selected']!r}: speed-up {e['speedup']} %, duration {e['duration']} of {e['real_duration']} ns")
+            break
+    for pat in selected:
+        if not any(re.search(pat, e["selected"]) for e in ex):
+            errs.append(f"no experiment selected a function matching {pat!r}")
+    for name in points:
+        if not any(e["throughput"].get(name, 0) > 0 or e["latency"].get(name, {}).get("departures", 0) > 0 for e in ex):
+            errs.append(f"progress point {name!r} was never visited during an experiment")
+    return errs
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="validate", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="kind", required=True)
@@ -122,6 +160,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("--name", action="append", default=[])
     p.add_argument("--counter", action="append", default=[])
     p.add_argument("--min-slices", type=int, default=0)
+    p.add_argument("--min-flows", type=int, default=0, help="arrows from a host call to the device work it started")
     p = sub.add_parser("db")
     p.add_argument("file")
     p.add_argument("--table", action="append", default=[], metavar="NAME[:MIN_ROWS]")
@@ -130,9 +169,16 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p.add_argument("--column", action="append", default=[])
     p.add_argument("--function", action="append", default=[])
     p.add_argument("--min-rows", type=int, default=1)
+    p = sub.add_parser("causal")
+    p.add_argument("file")
+    p.add_argument("--min-experiments", type=int, default=1)
+    p.add_argument("--selected", action="append", default=[], metavar="REGEX")
+    p.add_argument("--point", action="append", default=[])
     a = ap.parse_args(argv)
     if a.kind == "perfetto":
-        errs = check_perfetto(a.file, a.category, a.name, a.counter, a.min_slices)
+        errs = check_perfetto(a.file, a.category, a.name, a.counter, a.min_slices, a.min_flows)
+    elif a.kind == "causal":
+        errs = check_causal(a.file, a.min_experiments, a.selected, a.point)
     elif a.kind == "db":
         errs = check_db(a.file, a.table)
     else:

@@ -524,6 +524,24 @@ def test_output_validators(tmp_path):
     (tmp_path / "bad.json").write_text(json.dumps(bad))
     assert any("overlap" in e for e in validate.check_perfetto(str(tmp_path / "bad.json")))
     assert validate.main(["db", dbp, "--table", "region:1"]) == 0
+    # arrows: the two collective calls point at their device intervals; a lone or backward arrow is flagged
+    assert validate.check_perfetto(str(tmp_path / "t.json"), min_flows=2) == []
+    assert validate.check_perfetto(str(tmp_path / "t.json"), min_flows=3) == ["2 arrows, expected at least 3"]
+    lone = {"traceEvents": [{"ph": "s", "id": 1, "pid": 1, "tid": "a", "ts": 5}, {"ph": "s", "id": 2, "pid": 1, "tid": "a", "ts": 9},
+                            {"ph": "f", "id": 2, "pid": 1, "tid": "b", "ts": 3}]}
+    (tmp_path / "lone.json").write_text(json.dumps(lone))
+    errs = validate.check_perfetto(str(tmp_path / "lone.json"))
+    assert any("without their other end" in e for e in errs) and any("back in time" in e for e in errs)
+    # the causal profiler's output
+    coz = tmp_path / "e.coz"
+    coz.write_text("startup\ttime=1\nexperiment\tselected=cpu_slow_func\tspeedup=0.20\tduration=800\tselected-samples=5\treal-duration=1000\n"
+                   "throughput-point\tname=iteration\tdelta=10\nruntime\ttime=2\n")
+    assert validate.check_causal(str(coz), 1, ["slow"], ["iteration"]) == []
+    errs = validate.check_causal(str(coz), 3, ["fast"], ["other"])
+    assert len(errs) == 3
+    coz.write_text("experiment\tselected=f\tspeedup=0.20\tduration=1200\tselected-samples=5\treal-duration=1000\n")
+    assert any("duration 1200 of 1000" in e for e in validate.check_causal(str(coz)))
+    assert validate.main(["causal", str(coz)]) == 1
 
 
 def test_telemetry_policy_events_over_http(fake_nvml):
