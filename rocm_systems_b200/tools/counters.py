@@ -405,6 +405,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--arg", action="append", default=[], help="NAME=VALUE readable as arg.NAME")
     ap.add_argument("--list", action="store_true", help="print the definitions and the raw metrics they need")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--list-kernels", action="store_true", help="the kernels of the capture(s) with how often each was captured and its total time, and stop "
+                    "(names to give --kernel-filter)")
     ap.add_argument("--compare", default="", metavar="OTHER", help="a second report or CSV of the same program: counters of matching launches side by side with the change")
     ap.add_argument("--min-change", type=float, default=0.0, metavar="PCT", help="with --compare: only counters that changed by at least this much")
     ap.add_argument("--kernel-filter", default="", metavar="REGEX", help="with --analyze / --compare: only launches whose kernel name matches")
@@ -459,6 +461,21 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         for d in cs.defs:
             print(f"{d['name']:<22} [{d.get('unit', '')}] = {d['expression']}\n{'':<22} {d.get('description', '')}")
         print("\nraw metrics: " + ",".join(cs.required_metrics()))
+        return 0
+    if a.list_kernels:
+        seen: Dict[str, list] = {}
+        for path in a.inputs:
+            for k in roofline.read_ncu(path):
+                raw = dict(k.raw) if hasattr(k, "raw") else {}
+                e = seen.setdefault(k.name, [0, 0.0])
+                e[0] += 1
+                e[1] += float(raw.get("gpu__time_duration.sum", 0.0) or 0.0)
+        rows_ = [{"kernel": n, "launches": c, "total_us": t / 1e3} for n, (c, t) in sorted(seen.items(), key=lambda kv: -kv[1][1])]
+        if a.json:
+            print(json.dumps(rows_, indent=1))
+        else:
+            for r in rows_:
+                print(f"{r['launches']:>5} x {r['total_us']:>12.1f} us  {r['kernel']}")
         return 0
     peaks = roofline.load_peaks(a.peaks)
     args = {k: float(v) for k, v in (s.split("=", 1) for s in a.arg)}

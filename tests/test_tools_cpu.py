@@ -839,6 +839,9 @@ def test_counter_analysis_panels_stalls_and_verdicts(tmp_path, capsys):
     assert counters.main([str(tmp_path / "raw.csv"), "--analyze", "--peaks", str(tmp_path / "p.json")]) == 0
     text = capsys.readouterr().out
     assert "== waitKernel" in text and "[stalls" in text and "under-filled" in text and "[memory]" in text
+    assert counters.main([str(tmp_path / "raw.csv"), "--list-kernels"]) == 0
+    listing = capsys.readouterr().out.splitlines()
+    assert len(listing) == 3 and all(" x " in l and l.rstrip().endswith(("streamKernel", "mmaKernel", "waitKernel")) for l in listing)
     # and as one self-contained page
     assert counters.main([str(tmp_path / "raw.csv"), "--analyze", "--peaks", str(tmp_path / "p.json"), "--html", str(tmp_path / "a.html")]) == 0
     page = (tmp_path / "a.html").read_text()
