@@ -623,8 +623,9 @@ void* controllerMain(void*) {
     napUnlessStopping(length);
     int64_t fewest = -1;
     endExperiment(f, percent, from, &fewest);
-    // Too few visits make a noisy rate: lengthen; plenty: shorten again.
-    if (fewest >= 0 && fewest < 5 && length < 8.0) length *= 2;
+    // Too few visits make a noisy rate (an experiment sees a whole number of them: with N visits the rate is only good to
+    // 1 / N): lengthen; plenty: shorten again.
+    if (fewest >= 0 && fewest < 10 && length < 8.0) length *= 2;
     else if (fewest >= 40 && length > gCfg->experimentSeconds) length /= 2;
     if (!napUnlessStopping(std::min(length / 2, 0.25))) break;  // the threads serve what is still owed before the next baseline
     seen = gRecentNext.load();

@@ -55,7 +55,7 @@ TOOL_SETTINGS = [
     ("causal", "B200CAUSAL_FIXED_SPEEDUP", "0,10,...,100", "virtual speed-ups (percent) to draw from"),
     ("causal", "B200CAUSAL_BACKEND", "auto", "sample source: perf (per-thread CPU-clock events), timer (ITIMER_PROF, one sample per scheduler tick), auto (perf if allowed)"),
     ("causal", "B200CAUSAL_FREQ", "1000", "samples per second of a thread's CPU time (timer backend: the scheduler tick is the floor)"),
-    ("causal", "B200CAUSAL_EXPERIMENT_SECONDS", "0.5", "first length of an experiment; doubled while progress points are visited fewer than 5 times"),
+    ("causal", "B200CAUSAL_EXPERIMENT_SECONDS", "0.5", "first length of an experiment; doubled while progress points are visited fewer than 10 times"),
     ("causal", "B200CAUSAL_DELAY", "0", "seconds before the first experiment"),
     ("causal", "B200CAUSAL_DURATION", "0", "seconds of experimenting (0: until the program ends)"),
     ("causal", "B200CAUSAL_END_TO_END", "0", "one experiment over the whole run"),
