@@ -155,6 +155,6 @@ def test_causal_profiler_under_asan(tmp_path):
     asan = subprocess.run(["g++", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
     env = dict(os.environ, LD_PRELOAD=f"{asan}:{lib}", ASAN_OPTIONS="verify_asan_link_order=0:detect_leaks=0:abort_on_error=0", B200CAUSAL_FILE=str(out),
                B200CAUSAL_FIXED_SPEEDUP="0,30", B200CAUSAL_EXPERIMENT_SECONDS="0.25")
-    r = subprocess.run([str(exe), "50", "80", "1500000", "pool"], env=env, capture_output=True, text=True, timeout=300)
-    assert r.returncode == 0 and "done 50" in r.stdout and "ERROR" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
+    r = subprocess.run([str(exe), "120", "80", "1500000", "pool"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "done 120" in r.stdout and "ERROR" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
     assert out.read_text().count("experiment\t") >= 2
