@@ -14,7 +14,8 @@
 //
 // Two ways in: LD_PRELOAD=libb200sample.so with B200SAMPLE_PREFIX (files <prefix>.<pid>.samples.csv and
 // <prefix>.<pid>.folded), B200SAMPLE_FREQ (Hz, default 100), B200SAMPLE_CLOCK (cpu | wall), B200SAMPLE_DELAY (seconds
-// before the first sample); or b200sampleStart / Stop / Write from the program.
+// before the first sample), B200SAMPLE_DURATION (seconds of sampling, 0 = to the end); or b200sampleStart / Stop / Write
+// from the program.
 #include <cxxabi.h>
 #include <dirent.h>
 #include <dlfcn.h>
@@ -204,6 +205,25 @@ __attribute__((constructor)) void onLoad() {
   if (b200sampleStartDelayed(freq, mode, delay) == 0) {
     atexit(atExitWrite);
     installSignalFlush();
+    // B200SAMPLE_DURATION: sample for this many seconds (after the delay), then stop; the program runs on unsampled and the
+    // files are written when it ends (the reference's sampling duration setting, ROCPROFSYS_SAMPLING_DURATION).
+    const char* dur = getenv("B200SAMPLE_DURATION");
+    static double window = 0.0;
+    window = dur ? atof(dur) : 0.0;
+    if (window > 0.0) {
+      pthread_t th;
+      auto body = +[](void* p) -> void* {
+        const double seconds = *(double*)p;
+        timespec ts{(time_t)seconds, (long)((seconds - (time_t)seconds) * 1e9)};
+        while (nanosleep(&ts, &ts) != 0 && errno == EINTR) {
+        }
+        b200sampleStop();
+        return nullptr;
+      };
+      static double total = 0.0;
+      total = window + (mode == B200SAMPLE_CPU ? delay : 0.0);  // wall mode has slept through the delay already
+      if (pthread_create(&th, nullptr, body, &total) == 0) pthread_detach(th);
+    }
   }
 }
 

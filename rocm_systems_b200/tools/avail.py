@@ -45,6 +45,7 @@ TOOL_SETTINGS = [
     ("sample", "B200SAMPLE_FREQ", "100", "samples per second"),
     ("sample", "B200SAMPLE_CLOCK", "cpu", "cpu: threads that burn CPU time; wall: every thread every period"),
     ("sample", "B200SAMPLE_DELAY", "0", "seconds before the first sample"),
+    ("sample", "B200SAMPLE_DURATION", "0", "seconds of sampling after the delay (0: until the program ends)"),
     ("sample", "B200SAMPLE_SIGNALS", "0", "1: write the samples when SIGTERM / SIGINT / SIGQUIT / SIGABRT ends the program (the launcher sets it)"),
     ("sample", "B200SAMPLE_MAX_SAMPLES", "262144", "samples kept; later ones are counted as dropped"),
     ("causal", "B200CAUSAL_FILE", "", "output of the causal profiler; setting it starts experiments when libb200causal.so is preloaded"),

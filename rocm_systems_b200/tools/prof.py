@@ -74,6 +74,8 @@ def build_env(a: argparse.Namespace, prefix: str) -> dict:
             env["B200SAMPLE_SIGNALS"] = "1"
         if a.sampling_delay > 0:
             env["B200SAMPLE_DELAY"] = str(a.sampling_delay)
+        if a.sampling_duration > 0:
+            env["B200SAMPLE_DURATION"] = str(a.sampling_duration)
     if a.kokkos_trace:
         lib = PKG / "lib" / "libb200kokkosp.so"
         if not lib.exists():
@@ -127,6 +129,7 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--sampling-clock", choices=["cpu", "wall"], default="cpu",
                    help="cpu: samples in proportion to CPU time used; wall: every thread every period, blocked ones included")
     g.add_argument("--sampling-delay", type=float, default=0.0, metavar="SECONDS")
+    g.add_argument("--sampling-duration", type=float, default=0.0, metavar="SECONDS", help="sample for this long after the delay, then let the command run on unsampled (0: to the end)")
     g.add_argument("--openmp-trace", action="store_true", help="OpenMP parallel regions, tasks, worksharing, barriers and target regions as marker ranges "
                    "(sets OMP_TOOL_LIBRARIES to the OMPT tool; implies --marker-trace)")
     g = ap.add_argument_group("filtering")

@@ -148,3 +148,13 @@ def test_samples_survive_a_terminating_signal(target, tmp_path):
     time.sleep(0.3)
     p.send_signal(signal.SIGTERM)
     assert p.wait(timeout=30) == -signal.SIGTERM and not list(tmp_path.glob("lost.*"))
+
+
+def test_sampling_window(target, tmp_path):
+    """B200SAMPLE_DURATION: samples are taken for that long, the program runs on, the files are written at its end."""
+    prefix = tmp_path / "win"
+    env = dict(os.environ, LD_PRELOAD=str(LIB), B200SAMPLE_PREFIX=str(prefix), B200SAMPLE_CLOCK="wall", B200SAMPLE_FREQ="100", B200SAMPLE_DURATION="0.3")
+    subprocess.run([str(target)], env=env, check=True, capture_output=True, timeout=120)
+    rows = next(tmp_path.glob("win.*.samples.csv")).read_text().splitlines()[1:]
+    ts = [int(r.split(",")[0]) for r in rows]
+    assert len(ts) >= 10 and (max(ts) - min(ts)) / 1e9 < 0.6          # the target runs for about a second
