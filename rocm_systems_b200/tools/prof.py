@@ -130,6 +130,9 @@ def parser() -> argparse.ArgumentParser:
                    help="cpu: samples in proportion to CPU time used; wall: every thread every period, blocked ones included")
     g.add_argument("--sampling-delay", type=float, default=0.0, metavar="SECONDS")
     g.add_argument("--sampling-duration", type=float, default=0.0, metavar="SECONDS", help="sample for this long after the delay, then let the command run on unsampled (0: to the end)")
+    g.add_argument("--python-trace", action="store_true", help="Python calls of the command's script as ranges (the command must be `python script.py ...`: it is "
+                   "run under tools/pytrace.py); implies --marker-trace so that everything lands in one database")
+    g.add_argument("--python-restrict", nargs="+", default=[], metavar="REGEX", help="with --python-trace: only functions of modules whose file matches")
     g.add_argument("--openmp-trace", action="store_true", help="OpenMP parallel regions, tasks, worksharing, barriers and target regions as marker ranges "
                    "(sets OMP_TOOL_LIBRARIES to the OMPT tool; implies --marker-trace)")
     g = ap.add_argument_group("filtering")
@@ -179,6 +182,22 @@ def parser() -> argparse.ArgumentParser:
     g.add_argument("--echo", action="store_true", help="print the command and the environment variables this launcher sets before running")
     ap.add_argument("command", nargs=argparse.REMAINDER, help="-- command to run")
     return ap
+
+
+def python_traced(cmd: Sequence[str], restrict: Sequence[str] = ()) -> Optional[List[str]]:
+    """``python [interpreter options] script.py args`` -> the same under the Python function tracer; None when the command is not of
+    that form (``-m`` and ``-c`` have no script file to run)."""
+    if not cmd or not os.path.basename(cmd[0]).startswith("python"):
+        return None
+    i = 1
+    while i < len(cmd) and cmd[i].startswith("-"):
+        if cmd[i] in ("-m", "-c"):
+            return None
+        i += 2 if cmd[i] in ("-W", "-X") else 1
+    if i >= len(cmd) or not cmd[i].endswith(".py"):
+        return None
+    extra = ["-MR", *restrict] if restrict else []
+    return [*cmd[:i], "-m", "rocm_systems_b200.tools.pytrace", *extra, "--", *cmd[i:]]
 
 
 def collect_counters(a, cmd: Sequence[str], prefix: str) -> int:
@@ -311,8 +330,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if not cmd:
         print("prof: no command given (put it after --)", file=sys.stderr)
         return 2
-    if a.kokkos_trace or a.openmp_trace:
+    if a.kokkos_trace or a.openmp_trace or a.python_trace:
         a.marker_trace = True
+    if a.python_trace:
+        cmd = python_traced(cmd, a.python_restrict)
+        if cmd is None:
+            print("prof: --python-trace needs a command of the form `python script.py [arguments]`", file=sys.stderr)
+            return 2
     if a.sys_trace:
         a.kernel_trace = a.memory_copy_trace = a.runtime_trace = a.sync_trace = a.coll_trace = a.marker_trace = True
     if not (a.kernel_trace or a.memory_copy_trace or a.runtime_trace or a.driver_trace or a.sync_trace or a.coll_trace or a.marker_trace

@@ -156,3 +156,21 @@ def test_launcher_puts_python_ranges_into_the_database(tmp_path):
     db = sqlite3.connect(str(tmp_path / "run.db"))
     rows = db.execute("select name, count(*) from regions where category = 'PYTHON_FUNCTION' group by name").fetchall()
     assert dict(rows) == {"Model.step": 3, "middle": 7, "leaf": 15, "Model": 1}
+
+
+def test_launcher_python_trace_option(tmp_path):
+    from rocm_systems_b200.tools import prof
+
+    assert prof.python_traced(["python3", "-u", "train.py", "--steps", "2"], ["my_pkg/"]) == \
+        ["python3", "-u", "-m", "rocm_systems_b200.tools.pytrace", "-MR", "my_pkg/", "--", "train.py", "--steps", "2"]
+    assert prof.python_traced(["python", "-W", "ignore", "a.py"]) == ["python", "-W", "ignore", "-m", "rocm_systems_b200.tools.pytrace", "--", "a.py"]
+    assert prof.python_traced(["python", "-m", "pkg.mod"]) is None and prof.python_traced(["./app"]) is None and prof.python_traced(["python", "-c", "pass"]) is None
+    script = tmp_path / "traced.py"
+    script.write_text(SCRIPT)
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--python-trace", "--python-restrict", "traced", "-d", str(tmp_path), "-o", "run", "--",
+                        sys.executable, str(script)], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    db = sqlite3.connect(str(tmp_path / "run.db"))
+    assert dict(db.execute("select name, count(*) from regions where category = 'PYTHON_FUNCTION' and name in ('middle', 'leaf') group by name")) == {"middle": 7, "leaf": 15}
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--python-trace", "-d", str(tmp_path), "--", "true"], capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 2 and "python script.py" in r.stderr
