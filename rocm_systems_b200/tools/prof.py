@@ -185,9 +185,19 @@ def parser() -> argparse.ArgumentParser:
 
 
 def python_traced(cmd: Sequence[str], restrict: Sequence[str] = ()) -> Optional[List[str]]:
-    """``python [interpreter options] script.py args`` -> the same under the Python function tracer; None when the command is not of
-    that form (``-m`` and ``-c`` have no script file to run)."""
+    """``python [interpreter options] script.py args`` (or a ``python -m torch.distributed.run ... script.py args`` launch) -> the
+    same under the Python function tracer; None when the command is not of that form (``-m`` and ``-c`` have no script file)."""
     if not cmd or not os.path.basename(cmd[0]).startswith("python"):
+        return None
+    extra = ["-MR", *restrict] if restrict else []
+    # A multi-rank launch: `python -m torch.distributed.run <its options> script.py args` runs the tracer as the module of
+    # every rank (`... -m rocm_systems_b200.tools.pytrace -- script.py args`).
+    if len(cmd) > 3 and cmd[1] == "-m" and cmd[2] in ("torch.distributed.run", "torch.distributed.launch"):
+        for j in range(3, len(cmd)):
+            if cmd[j] in ("-m", "--module", "--no-python", "--no_python"):
+                return None
+            if cmd[j].endswith(".py"):
+                return [*cmd[:j], "-m", "rocm_systems_b200.tools.pytrace", *extra, "--", *cmd[j:]]
         return None
     i = 1
     while i < len(cmd) and cmd[i].startswith("-"):
@@ -196,7 +206,6 @@ def python_traced(cmd: Sequence[str], restrict: Sequence[str] = ()) -> Optional[
         i += 2 if cmd[i] in ("-W", "-X") else 1
     if i >= len(cmd) or not cmd[i].endswith(".py"):
         return None
-    extra = ["-MR", *restrict] if restrict else []
     return [*cmd[:i], "-m", "rocm_systems_b200.tools.pytrace", *extra, "--", *cmd[i:]]
 
 

@@ -4,6 +4,7 @@ tracing launcher's database. The reference exercises its Python profiler the sam
 ``python -m rocprofsys`` with label and filter options, then checks of the recorded function names
 (rocprofiler-systems tests/rocprof-sys-python-tests.cmake)."""
 import csv
+import os
 import sqlite3
 import subprocess
 import sys
@@ -174,3 +175,21 @@ def test_launcher_python_trace_option(tmp_path):
     assert dict(db.execute("select name, count(*) from regions where category = 'PYTHON_FUNCTION' and name in ('middle', 'leaf') group by name")) == {"middle": 7, "leaf": 15}
     r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--python-trace", "-d", str(tmp_path), "--", "true"], capture_output=True, text=True, cwd=ROOT)
     assert r.returncode == 2 and "python script.py" in r.stderr
+
+
+def test_python_trace_of_a_multi_rank_launch(tmp_path):
+    """Every rank of a torch.distributed.run launch runs its script under the tracer and writes a file of its own."""
+    from rocm_systems_b200.tools import prof
+
+    cmd = ["python", "-m", "torch.distributed.run", "--nproc-per-node", "2", "train.py", "--x"]
+    assert prof.python_traced(cmd) == ["python", "-m", "torch.distributed.run", "--nproc-per-node", "2", "-m", "rocm_systems_b200.tools.pytrace", "--", "train.py", "--x"]
+    assert prof.python_traced(["python", "-m", "torch.distributed.run", "--nproc-per-node", "2", "-m", "pkg.train"]) is None
+    script = tmp_path / "rank.py"
+    script.write_text("import os\ndef work(r):\n    return r + 1\nwork(int(os.environ['RANK']))\nprint('rank done', os.environ['RANK'])\n")
+    r = subprocess.run([sys.executable, "-m", "rocm_systems_b200.tools.prof", "--python-trace", "--python-restrict", "rank", "-d", str(tmp_path), "-o", "run", "--",
+                        sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29931",
+                        str(script)], capture_output=True, text=True, cwd=ROOT, timeout=600, env=dict(os.environ, PYTHONPATH=str(ROOT)))
+    assert r.returncode == 0 and r.stdout.count("rank done") == 2, r.stdout[-2000:] + r.stderr[-2000:]
+    db = sqlite3.connect(str(tmp_path / "run.db"))
+    rows = db.execute("select count(*), count(distinct pid) from regions where category = 'PYTHON_FUNCTION' and name = 'work'").fetchone()
+    assert rows == (2, 2)
