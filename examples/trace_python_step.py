@@ -1,8 +1,8 @@
 """A toy training loop on the CPU that shows the host-side tracing pieces together: marker ranges around the phases of a
 step, a progress point per step for the causal profiler, and (when run under the Python tracer) a range per Python call.
 
-    python -m rocm_systems_b200.tools.prof --marker-trace --stats --summary-per-domain -d out -o run -- \\
-        python -m rocm_systems_b200.tools.pytrace -MR 'trace_python_step' -- examples/trace_python_step.py --steps 5
+    python -m rocm_systems_b200.tools.prof --python-trace --python-restrict trace_python_step --stats --summary-per-domain -d out -o run -- \\
+        python examples/trace_python_step.py --steps 5
     python -m rocm_systems_b200.tools.tracedb query out/run.db "select category, name, count(*) from regions group by 1, 2"
 
 Nothing here needs a GPU; on one, the same markers line up with kernels and collectives in the same database.
