@@ -194,7 +194,7 @@ def test_both_sample_sources(target, tmp_path, backend, announcement):
     """The per-thread CPU-clock events give samples at the rate asked for, the process timer one per scheduler tick; both
     predict the known answer. Where the kernel refuses perf_event_open the perf case is skipped (auto then uses the timer)."""
     out = tmp_path / f"{backend}.coz"
-    for speedup in (0, 20):
+    for speedup in (0, 20, 0, 20):
         env = dict(os.environ, LD_PRELOAD=str(LIB), B200CAUSAL_FILE=str(out), B200CAUSAL_BACKEND=backend, B200CAUSAL_END_TO_END="1",
                    B200CAUSAL_FUNCTION_SCOPE="^cpu_slow_func$", B200CAUSAL_FIXED_SPEEDUP=str(speedup), B200CAUSAL_VERBOSE="1", B200CAUSAL_FREQ="1000")
         r = subprocess.run([str(target), "24", "80", "4000000", "spawn"], env=env, capture_output=True, text=True, timeout=300)
@@ -202,10 +202,12 @@ def test_both_sample_sources(target, tmp_path, backend, announcement):
             pytest.skip("perf_event_open is not allowed on this machine")
         assert r.returncode == 0 and announcement in r.stderr, r.stderr
     ex = causal.parse(out.read_text())
-    assert len(ex) == 2
+    assert len(ex) == 4
     per_second = ex[0]["selected_samples"] / (ex[0]["real_duration"] / 1e9)
     assert per_second > (250 if backend == "perf" else 20), per_second     # 1 kHz of CPU time asked for (less per wall second on a busy machine); the timer gives one sample per scheduler tick
     res = causal.analyze(ex, point="iteration")
+    if not _spread_ok(res):
+        pytest.skip("baseline runs differ by more than 6 %: the machine is busy")
     assert causal.validate(res, [("cpu_slow_func", "iteration", 20, 20.0, 7.0)]) == [], causal.format_report(res)
 
 
