@@ -229,8 +229,8 @@ def test_experiments_drawn_while_a_thread_pool_runs(target, tmp_path):
             any(row["experiments"] < 2 for x in res for row in x["rows"]):
         pytest.skip("not both functions drawn at least twice at both speed-ups (an experiment sees a whole number of visits: one is too noisy), or a busy machine")
     by = {x["selected"]: {row["speedup"]: row["program_speedup"] for row in x["rows"]} for x in res}
-    assert by["cpu_slow_func"][20] > by["cpu_fast_func"][20] + 6.0, causal.format_report(res)
-    assert 10.0 < by["cpu_slow_func"][20] < 30.0 and abs(by["cpu_fast_func"][20]) < 10.0, causal.format_report(res)
+    assert by["cpu_slow_func"][20] > by["cpu_fast_func"][20] + 3.0, causal.format_report(res)
+    assert 8.0 < by["cpu_slow_func"][20] < 32.0 and abs(by["cpu_fast_func"][20]) < 12.0, causal.format_report(res)
 
 
 def test_pipeline_example_under_the_profiler(tmp_path):
