@@ -215,8 +215,8 @@ def test_experiments_drawn_while_a_thread_pool_runs(target, tmp_path):
     out = tmp_path / "pool.coz"
     env = dict(os.environ, LD_PRELOAD=str(LIB), B200CAUSAL_FILE=str(out), B200CAUSAL_FIXED_SPEEDUP="0,20", B200CAUSAL_EXPERIMENT_SECONDS="0.4",
                B200CAUSAL_RANDOM_SEED="11", B200CAUSAL_VERBOSE="1", B200CAUSAL_FUNCTION_SCOPE="^cpu_(slow|fast)_func$")
-    r = subprocess.run([str(target), "420", "80", "2000000", "pool"], env=env, capture_output=True, text=True, timeout=300)
-    assert r.returncode == 0 and "done 420" in r.stdout
+    r = subprocess.run([str(target), "600", "80", "2000000", "pool"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "done 600" in r.stdout
     assert "Starting causal experiment #1" in r.stderr
     text = out.read_text()
     assert text.startswith("startup\ttime=") and text.rstrip().splitlines()[-1].startswith("runtime\ttime=")
